@@ -1,0 +1,531 @@
+"""Model, quantisation and parallel-mapping configuration.
+
+Parses a Hugging Face ``config.json`` (plus ``hf_quant_config.json`` or an embedded
+``quantization_config``) into the dataclasses the rest of the runtime consumes.
+
+Parity: ``tensorrt_edgellm/config.py`` in the reference (``Mapping`` :365, ``QuantConfig`` :436,
+``MambaConfig`` :528, ``GdnConfig`` :545, ``ModelConfig`` :629, ``ModelConfig.for_rank`` :1150,
+``ModelConfig.from_pretrained`` :1199).  The field names a user touches are kept; the parsing
+code is new and only covers what this runtime executes.
+"""
+from __future__ import annotations
+
+import dataclasses
+import json
+import os
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+import torch
+
+# Quantisation type names (strings, so they survive a JSON round trip).
+QUANT_NONE = "fp16"
+QUANT_NVFP4 = "nvfp4"          # W4A4: NVFP4 weights, activations quantised dynamically
+QUANT_NVFP4_A16 = "nvfp4_a16"  # W4A16: NVFP4 weights, 16-bit activations
+QUANT_INT4_AWQ = "int4_awq"
+QUANT_INT4_GPTQ = "int4_gptq"
+QUANT_FP8 = "fp8"
+
+NVFP4_BLOCK = 16
+AWQ_GROUP = 128
+
+LAYER_ATTENTION = "attention"
+LAYER_MAMBA = "mamba"
+LAYER_GDN = "gdn"
+LAYER_MLP = "mlp"
+LAYER_MOE = "moe"
+
+
+@dataclass
+class Mapping:
+    """Tensor / expert parallel placement of one rank."""
+
+    tp_size: int = 1
+    tp_rank: int = 0
+    ep_size: int = 1
+    ep_rank: int = 0
+
+    def __post_init__(self) -> None:
+        if not (0 <= self.tp_rank < self.tp_size):
+            raise ValueError(f"tp_rank {self.tp_rank} outside [0,{self.tp_size})")
+        if not (0 <= self.ep_rank < self.ep_size):
+            raise ValueError(f"ep_rank {self.ep_rank} outside [0,{self.ep_size})")
+
+    @property
+    def world_size(self) -> int:
+        return max(self.tp_size, self.ep_size)
+
+
+@dataclass
+class QuantConfig:
+    """How the linear layers of a checkpoint are stored."""
+
+    quant_type: str = QUANT_NONE
+    group_size: int = 1
+    kv_cache_quant: Optional[str] = None            # None or "fp8"
+    excluded: List[str] = field(default_factory=list)
+    layer_overrides: Dict[str, str] = field(default_factory=dict)
+    gptq_zero_point_offset: int = 0
+    quantize_activations: bool = True
+    lm_head_quant_type: str = QUANT_NONE
+
+    @property
+    def is_quantized(self) -> bool:
+        return self.quant_type != QUANT_NONE
+
+    @property
+    def uses_nvfp4_weights(self) -> bool:
+        return self.quant_type in (QUANT_NVFP4, QUANT_NVFP4_A16)
+
+    def module_quant_type(self, module_name: str) -> str:
+        """Quantisation of one named linear (exclusions are glob-ish suffix patterns)."""
+        if module_name in self.layer_overrides:
+            return self.layer_overrides[module_name]
+        for pat in self.excluded:
+            p = pat.replace("*", "")
+            if p and p in module_name:
+                return QUANT_NONE
+        return self.quant_type
+
+
+@dataclass
+class MambaConfig:
+    """Mamba2 mixer geometry (Nemotron-H style)."""
+
+    num_heads: int = 64
+    head_dim: int = 64
+    d_state: int = 128
+    n_groups: int = 8
+    conv_kernel: int = 4
+    chunk_size: int = 128
+    dt_limit: float = 50.0
+
+    @property
+    def intermediate_size(self) -> int:
+        return self.num_heads * self.head_dim
+
+    @property
+    def conv_dim(self) -> int:
+        return self.intermediate_size + 2 * self.n_groups * self.d_state
+
+
+@dataclass
+class GdnConfig:
+    """Gated-DeltaNet mixer geometry (Qwen3.5 style)."""
+
+    num_k_heads: int = 16
+    num_v_heads: int = 16
+    head_k_dim: int = 128
+    head_v_dim: int = 128
+    conv_kernel: int = 4
+
+    @property
+    def key_dim(self) -> int:
+        return self.num_k_heads * self.head_k_dim
+
+    @property
+    def value_dim(self) -> int:
+        return self.num_v_heads * self.head_v_dim
+
+    @property
+    def conv_dim(self) -> int:
+        return 2 * self.key_dim + self.value_dim
+
+
+@dataclass
+class ModelConfig:
+    """Architecture description of a decoder (dense, MoE or hybrid)."""
+
+    model_type: str = "llama"
+    vocab_size: int = 32000
+    hidden_size: int = 4096
+    intermediate_size: int = 11008
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 32
+    head_dim: int = 128
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 10000.0
+    rope_scaling: Optional[Dict[str, Any]] = None
+    partial_rotary_factor: float = 1.0
+    max_position_embeddings: int = 32768
+    tie_word_embeddings: bool = False
+    has_qk_norm: bool = False
+    attention_bias: bool = False
+    sliding_window: Optional[int] = None
+    hidden_act: str = "silu"
+    dtype: str = "bfloat16"
+    # MoE
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    shared_expert_intermediate_size: int = 0
+    router_type: str = "softmax_topk"      # or "sigmoid_group_topk"
+    n_group: int = 1
+    topk_group: int = 1
+    routed_scaling_factor: float = 1.0
+    # hybrid
+    layer_types: List[str] = field(default_factory=list)   # mixer type per layer
+    mlp_types: List[str] = field(default_factory=list)     # "mlp" / "moe" / "none" per layer
+    mamba: Optional[MambaConfig] = None
+    gdn: Optional[GdnConfig] = None
+    # draft heads
+    draft_type: Optional[str] = None        # "eagle3" / "mtp"
+    eagle3_target_hidden_size: int = 0
+    eagle3_num_target_layers: int = 3
+    draft_vocab_size: int = 0
+    # quant / parallel
+    quant: QuantConfig = field(default_factory=QuantConfig)
+    mapping: Mapping = field(default_factory=Mapping)
+    bos_token_id: Optional[int] = None
+    eos_token_id: Any = None
+
+    def __post_init__(self) -> None:
+        if self.num_attention_heads % max(self.num_key_value_heads, 1):
+            raise ValueError("num_attention_heads must be a multiple of num_key_value_heads")
+        if not self.layer_types:
+            self.layer_types = [LAYER_ATTENTION] * self.num_hidden_layers
+        if not self.mlp_types:
+            kind = LAYER_MOE if self.num_experts > 0 else LAYER_MLP
+            self.mlp_types = [kind] * self.num_hidden_layers
+        if len(self.layer_types) != self.num_hidden_layers:
+            raise ValueError("layer_types length must equal num_hidden_layers")
+
+    # -- derived ---------------------------------------------------------------------------
+    @property
+    def tp_size(self) -> int:
+        return self.mapping.tp_size
+
+    @property
+    def tp_rank(self) -> int:
+        return self.mapping.tp_rank
+
+    @property
+    def compute_dtype(self) -> torch.dtype:
+        return {"bfloat16": torch.bfloat16, "float16": torch.float16,
+                "float32": torch.float32}[self.dtype]
+
+    @property
+    def is_hybrid(self) -> bool:
+        return any(t != LAYER_ATTENTION for t in self.layer_types)
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    @property
+    def num_attn_layers(self) -> int:
+        return sum(t == LAYER_ATTENTION for t in self.layer_types)
+
+    @property
+    def num_mamba_layers(self) -> int:
+        return sum(t == LAYER_MAMBA for t in self.layer_types)
+
+    @property
+    def num_gdn_layers(self) -> int:
+        return sum(t == LAYER_GDN for t in self.layer_types)
+
+    @property
+    def q_size(self) -> int:
+        return self.num_attention_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    @property
+    def rotary_dim(self) -> int:
+        return int(self.head_dim * self.partial_rotary_factor)
+
+    def for_rank(self, rank: int, world: int, ep: bool = False) -> "ModelConfig":
+        """Copy of this config placed on ``rank`` of ``world`` (TP, or EP when ``ep``)."""
+        cfg = dataclasses.replace(self)
+        cfg.quant = dataclasses.replace(self.quant)
+        if ep:
+            cfg.mapping = Mapping(tp_size=1, tp_rank=0, ep_size=world, ep_rank=rank)
+        else:
+            if self.num_attention_heads % world:
+                raise ValueError(f"{self.num_attention_heads} heads not divisible by TP {world}")
+            cfg.mapping = Mapping(tp_size=world, tp_rank=rank)
+        return cfg
+
+    def to_dict(self) -> Dict[str, Any]:
+        return dataclasses.asdict(self)
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "ModelConfig":
+        d = dict(d)
+        if isinstance(d.get("quant"), dict):
+            d["quant"] = QuantConfig(**d["quant"])
+        if isinstance(d.get("mapping"), dict):
+            d["mapping"] = Mapping(**d["mapping"])
+        if isinstance(d.get("mamba"), dict):
+            d["mamba"] = MambaConfig(**d["mamba"])
+        if isinstance(d.get("gdn"), dict):
+            d["gdn"] = GdnConfig(**d["gdn"])
+        known = {f.name for f in dataclasses.fields(cls)}
+        return cls(**{k: v for k, v in d.items() if k in known})
+
+    # -- HF parsing ------------------------------------------------------------------------
+    @classmethod
+    def from_hf_dict(cls, hf: Dict[str, Any], quant: Optional[QuantConfig] = None,
+                     has_qk_norm: Optional[bool] = None) -> "ModelConfig":
+        llm = hf.get("text_config", hf)
+        model_type = llm.get("model_type", hf.get("model_type", "llama"))
+        heads = int(llm["num_attention_heads"])
+        hidden = int(llm["hidden_size"])
+        head_dim = int(llm.get("head_dim") or hidden // heads)
+        rope_theta = llm.get("rope_theta")
+        rope_scaling = llm.get("rope_scaling") or llm.get("rope_parameters")
+        if rope_theta is None and isinstance(rope_scaling, dict):
+            rope_theta = rope_scaling.get("rope_theta")
+        if isinstance(rope_scaling, dict) and rope_scaling.get("rope_type", rope_scaling.get("type")) in (None, "default"):
+            rope_scaling = None
+        n_layers = int(llm["num_hidden_layers"])
+        layer_types, mlp_types, mamba, gdn = _parse_hybrid(llm, n_layers)
+        if has_qk_norm is None:
+            has_qk_norm = model_type in ("qwen3", "qwen3_moe", "qwen3_next", "qwen3_5")
+        torch_dtype = str(llm.get("torch_dtype", llm.get("dtype", "bfloat16"))).replace("torch.", "")
+        if torch_dtype not in ("bfloat16", "float16", "float32"):
+            torch_dtype = "bfloat16"
+        router = "sigmoid_group_topk" if model_type in ("nemotron_h", "deepseek_v3") and llm.get("n_routed_experts") else "softmax_topk"
+        return cls(
+            model_type=model_type,
+            vocab_size=int(llm["vocab_size"]),
+            hidden_size=hidden,
+            intermediate_size=int(llm.get("intermediate_size", 4 * hidden)),
+            num_hidden_layers=n_layers,
+            num_attention_heads=heads,
+            num_key_value_heads=int(llm.get("num_key_value_heads", heads)),
+            head_dim=head_dim,
+            rms_norm_eps=float(llm.get("rms_norm_eps", llm.get("layer_norm_epsilon", 1e-6))),
+            rope_theta=float(rope_theta if rope_theta is not None else 10000.0),
+            rope_scaling=rope_scaling,
+            partial_rotary_factor=float(llm.get("partial_rotary_factor", 1.0)),
+            max_position_embeddings=int(llm.get("max_position_embeddings", 32768)),
+            tie_word_embeddings=bool(hf.get("tie_word_embeddings", llm.get("tie_word_embeddings", False))),
+            has_qk_norm=bool(has_qk_norm),
+            attention_bias=bool(llm.get("attention_bias", model_type == "qwen2")),
+            sliding_window=llm.get("sliding_window") if llm.get("use_sliding_window", False) else None,
+            hidden_act=llm.get("hidden_act", llm.get("mlp_hidden_act", "silu")),
+            dtype=torch_dtype,
+            num_experts=int(llm.get("num_experts", llm.get("n_routed_experts", 0)) or 0),
+            num_experts_per_tok=int(llm.get("num_experts_per_tok", 0) or 0),
+            moe_intermediate_size=int(llm.get("moe_intermediate_size", 0) or 0),
+            norm_topk_prob=bool(llm.get("norm_topk_prob", True)),
+            shared_expert_intermediate_size=int(llm.get("shared_expert_intermediate_size", llm.get("moe_shared_expert_intermediate_size", 0)) or 0),
+            router_type=router,
+            n_group=int(llm.get("n_group", 1) or 1),
+            topk_group=int(llm.get("topk_group", 1) or 1),
+            routed_scaling_factor=float(llm.get("routed_scaling_factor", 1.0) or 1.0),
+            layer_types=layer_types,
+            mlp_types=mlp_types,
+            mamba=mamba,
+            gdn=gdn,
+            quant=quant or QuantConfig(),
+            bos_token_id=llm.get("bos_token_id"),
+            eos_token_id=llm.get("eos_token_id"),
+        )
+
+    @classmethod
+    def from_pretrained(cls, model_dir: str, mapping: Optional[Mapping] = None) -> "ModelConfig":
+        hf = load_config_dict(model_dir)
+        quant = parse_quant_config(model_dir, hf)
+        cfg = cls.from_hf_dict(hf, quant=quant, has_qk_norm=_detect_qk_norm(model_dir, hf))
+        if mapping is not None:
+            cfg.mapping = mapping
+        return cfg
+
+
+# ------------------------------------------------------------------------------------------
+
+def load_config_dict(model_dir: str) -> Dict[str, Any]:
+    """Read ``config.json`` of a checkpoint directory."""
+    with open(os.path.join(model_dir, "config.json"), "r", encoding="utf-8") as f:
+        return json.load(f)
+
+
+def load_checkpoint_config_dicts(model_dir: str) -> Dict[str, Dict[str, Any]]:
+    """All JSON side files a checkpoint may carry, keyed by role."""
+    out: Dict[str, Dict[str, Any]] = {"config": load_config_dict(model_dir)}
+    for role, name in (("quant", "hf_quant_config.json"), ("generation", "generation_config.json"),
+                       ("tokenizer", "tokenizer_config.json")):
+        p = os.path.join(model_dir, name)
+        if os.path.exists(p):
+            with open(p, "r", encoding="utf-8") as f:
+                out[role] = json.load(f)
+    return out
+
+
+_ALGO_TO_QUANT = {
+    "NVFP4": QUANT_NVFP4, "NVFP4_AWQ": QUANT_NVFP4, "W4A16_NVFP4": QUANT_NVFP4_A16,
+    "W4A16_AWQ": QUANT_INT4_AWQ, "INT4_AWQ": QUANT_INT4_AWQ, "W4A16": QUANT_INT4_AWQ,
+    "W4A16_GPTQ": QUANT_INT4_GPTQ, "FP8": QUANT_FP8,
+}
+
+
+def parse_quant_config(model_dir: str, hf: Optional[Dict[str, Any]] = None) -> QuantConfig:
+    """Detect the quantisation of a checkpoint.
+
+    Understands ModelOpt (``hf_quant_config.json`` with ``quant_algo`` / ``kv_cache_quant_algo`` /
+    ``exclude_modules``), AutoAWQ / GPTQ ``quantization_config`` blocks and compressed-tensors
+    ``config_groups``.  Parity: ``tensorrt_edgellm/config.py:3216-3425``.
+    """
+    hf = hf if hf is not None else load_config_dict(model_dir)
+    p = os.path.join(model_dir, "hf_quant_config.json")
+    qc: Dict[str, Any] = {}
+    if os.path.exists(p):
+        with open(p, "r", encoding="utf-8") as f:
+            qc = json.load(f).get("quantization", {})
+    elif isinstance(hf.get("quantization_config"), dict):
+        qc = hf["quantization_config"]
+    if not qc:
+        return QuantConfig()
+    algo = str(qc.get("quant_algo") or "").upper()
+    method = str(qc.get("quant_method") or "").lower()
+    quant_type = QUANT_NONE
+    group = 1
+    if algo in _ALGO_TO_QUANT:
+        quant_type = _ALGO_TO_QUANT[algo]
+    elif method == "awq":
+        quant_type = QUANT_INT4_AWQ
+    elif method == "gptq":
+        quant_type = QUANT_INT4_GPTQ
+    elif method == "modelopt" and "NVFP4" in str(qc).upper():
+        quant_type = QUANT_NVFP4
+    elif "config_groups" in qc:
+        for grp in qc["config_groups"].values():
+            w = grp.get("weights", {})
+            if w.get("num_bits") == 4 and w.get("type") == "float":
+                quant_type = QUANT_NVFP4 if grp.get("input_activations") else QUANT_NVFP4_A16
+            elif w.get("num_bits") == 4:
+                quant_type = QUANT_INT4_AWQ
+                group = int(w.get("group_size", AWQ_GROUP))
+            elif w.get("num_bits") == 8 and w.get("type") == "float":
+                quant_type = QUANT_FP8
+    if quant_type in (QUANT_NVFP4, QUANT_NVFP4_A16):
+        group = NVFP4_BLOCK
+    elif quant_type in (QUANT_INT4_AWQ, QUANT_INT4_GPTQ):
+        group = int(qc.get("group_size", qc.get("q_group_size", AWQ_GROUP)))
+    kv = qc.get("kv_cache_quant_algo") or (qc.get("kv_cache_scheme") and "fp8")
+    kv = "fp8" if kv and "FP8" in str(kv).upper() else None
+    excluded = list(qc.get("exclude_modules") or qc.get("ignore") or qc.get("modules_to_not_convert") or [])
+    return QuantConfig(quant_type=quant_type, group_size=group, kv_cache_quant=kv, excluded=excluded,
+                       gptq_zero_point_offset=0 if qc.get("sym", True) is False else 0)
+
+
+def _checkpoint_keys(model_dir: str) -> List[str]:
+    idx = os.path.join(model_dir, "model.safetensors.index.json")
+    if os.path.exists(idx):
+        with open(idx, "r", encoding="utf-8") as f:
+            return list(json.load(f).get("weight_map", {}).keys())
+    p = os.path.join(model_dir, "model.safetensors")
+    if os.path.exists(p):
+        from .checkpoint.safetensors_io import SafetensorsFile
+        return SafetensorsFile(p).keys()
+    return []
+
+
+def _detect_qk_norm(model_dir: str, hf: Dict[str, Any]) -> Optional[bool]:
+    keys = _checkpoint_keys(model_dir)
+    if not keys:
+        return None
+    return any(k.endswith("self_attn.q_norm.weight") for k in keys)
+
+
+def _parse_hybrid(llm: Dict[str, Any], n_layers: int):
+    """Per-layer mixer / MLP kinds for hybrid checkpoints (Nemotron-H pattern string or HF
+    ``layer_types`` / ``layers_block_type`` lists)."""
+    layer_types: List[str] = []
+    mlp_types: List[str] = []
+    mamba = gdn = None
+    pattern = llm.get("hybrid_override_pattern")
+    raw = llm.get("layers_block_type") or llm.get("layer_types")
+    if pattern:
+        # Nemotron-H: one character per block: M = mamba, * = attention, - = MLP, E = MoE.
+        for ch in pattern:
+            if ch == "M":
+                layer_types.append(LAYER_MAMBA); mlp_types.append("none")
+            elif ch == "*":
+                layer_types.append(LAYER_ATTENTION); mlp_types.append("none")
+            elif ch == "-":
+                layer_types.append("none"); mlp_types.append(LAYER_MLP)
+            elif ch == "E":
+                layer_types.append("none"); mlp_types.append(LAYER_MOE)
+    elif raw:
+        for t in raw:
+            t = str(t).lower()
+            if "mamba" in t:
+                layer_types.append(LAYER_MAMBA)
+            elif "linear" in t or "gdn" in t or "delta" in t:
+                layer_types.append(LAYER_GDN)
+            else:
+                layer_types.append(LAYER_ATTENTION)
+    if any(t == LAYER_MAMBA for t in layer_types):
+        mamba = MambaConfig(
+            num_heads=int(llm.get("mamba_num_heads", 64)), head_dim=int(llm.get("mamba_head_dim", 64)),
+            d_state=int(llm.get("ssm_state_size", llm.get("mamba_d_state", 128))),
+            n_groups=int(llm.get("n_groups", llm.get("mamba_n_groups", 8))),
+            conv_kernel=int(llm.get("conv_kernel", llm.get("mamba_d_conv", 4))),
+            chunk_size=int(llm.get("chunk_size", llm.get("mamba_chunk_size", 128))))
+    if any(t == LAYER_GDN for t in layer_types):
+        gdn = GdnConfig(
+            num_k_heads=int(llm.get("linear_num_key_heads", 16)), num_v_heads=int(llm.get("linear_num_value_heads", 16)),
+            head_k_dim=int(llm.get("linear_key_head_dim", 128)), head_v_dim=int(llm.get("linear_value_head_dim", 128)),
+            conv_kernel=int(llm.get("linear_conv_kernel_dim", 4)))
+    if layer_types and len(layer_types) != n_layers:
+        layer_types, mlp_types = [], []
+    if layer_types and not mlp_types:
+        mlp_types = []
+    return layer_types, mlp_types, mamba, gdn
+
+
+# ---- canned shapes used by the benchmark configs ------------------------------------------
+
+def qwen3_8b_config(**over: Any) -> ModelConfig:
+    """Qwen3-8B geometry: 36 layers, hidden 4096, 32 q / 8 kv heads, d 128, I 12288, V 151936."""
+    base = dict(model_type="qwen3", vocab_size=151936, hidden_size=4096, intermediate_size=12288,
+                num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                rms_norm_eps=1e-6, rope_theta=1e6, has_qk_norm=True, max_position_embeddings=40960)
+    base.update(over)
+    return ModelConfig(**base)
+
+
+def qwen3_30b_a3b_config(**over: Any) -> ModelConfig:
+    """Qwen3-30B-A3B geometry: 48 layers, hidden 2048, 32 q / 4 kv heads, 128 experts top-8, I_e 768."""
+    base = dict(model_type="qwen3_moe", vocab_size=151936, hidden_size=2048, intermediate_size=6144,
+                num_hidden_layers=48, num_attention_heads=32, num_key_value_heads=4, head_dim=128,
+                rms_norm_eps=1e-6, rope_theta=1e6, has_qk_norm=True, num_experts=128,
+                num_experts_per_tok=8, moe_intermediate_size=768, norm_topk_prob=True)
+    base.update(over)
+    return ModelConfig(**base)
+
+
+def tiny_llama_config(**over: Any) -> ModelConfig:
+    """The CPU plumbing-check model: 2 layers, hidden 256, 4 q / 2 kv heads, d 64, I 688, V 32000."""
+    base = dict(model_type="llama", vocab_size=32000, hidden_size=256, intermediate_size=688,
+                num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                rms_norm_eps=1e-6, rope_theta=1e4, dtype="float32", max_position_embeddings=2048)
+    base.update(over)
+    return ModelConfig(**base)
+
+
+def hybrid_nemotron_config(**over: Any) -> ModelConfig:
+    """Hybrid benchmark shape: 52 layers, every 6th attention, every 4th Mamba layer a gated
+    DeltaNet layer, the rest Mamba2; hidden 4096, MLP 16384."""
+    n = over.pop("num_hidden_layers", 52)
+    types: List[str] = []
+    mamba_seen = 0
+    for i in range(n):
+        if (i + 1) % 6 == 0:
+            types.append(LAYER_ATTENTION)
+        else:
+            mamba_seen += 1
+            types.append(LAYER_GDN if mamba_seen % 4 == 0 else LAYER_MAMBA)
+    base = dict(model_type="nemotron_h_hybrid", vocab_size=131072, hidden_size=4096, intermediate_size=16384,
+                num_hidden_layers=n, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                rms_norm_eps=1e-5, rope_theta=1e4, layer_types=types, hidden_act="relu2",
+                mamba=MambaConfig(), gdn=GdnConfig())
+    base.update(over)
+    return ModelConfig(**base)

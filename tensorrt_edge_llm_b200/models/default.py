@@ -1,0 +1,174 @@
+"""Dense Llama / Qwen-style decoder (pre-norm, GQA, SwiGLU) on the ragged step ABI.
+
+Parity: ``tensorrt_edgellm/models/default/modeling_default.py`` — ``RMSNorm`` :163-182,
+``Attention`` :190-461 (q/k/v column-parallel, o row-parallel, qk-norm before RoPE),
+``fuse_qkv_projections`` :523, ``MLP`` :696-735, ``DecoderLayer`` :743-805, ``Transformer``
+:813-973, ``CausalLM`` :985.  The reference module is an export graph whose attention body
+returns zeros; this one executes: every leaf is an ``ops`` call.
+
+Each row-parallel output (o_proj, down_proj) flows straight into a residual-add + RMSNorm.
+That pair is the seam where tensor parallelism reduces partial sums, so the layer calls
+``comm.add_rmsnorm`` and the communicator decides between a local kernel (TP=1), NCCL
+all-reduce followed by the kernel (baseline) and the fused peer-memory kernel.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..config import ModelConfig
+from ..ops.meta import StepMeta
+from ..parallel.comm import LocalComm
+from .linear import TPMode, make_linear
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, dim: int, eps: float, dtype=torch.bfloat16):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype), requires_grad=False)
+        self.eps = eps
+
+    def forward(self, x):
+        return ops.rmsnorm(x, self.weight, self.eps)
+
+
+class Attention(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, prefix: str):
+        super().__init__()
+        tp = cfg.tp_size
+        self.layer_idx = layer_idx
+        self.head_dim = cfg.head_dim
+        self.num_q_heads = cfg.num_attention_heads // tp
+        self.num_kv_heads = max(cfg.num_key_value_heads // tp, 1)
+        if cfg.num_key_value_heads % tp:
+            raise ValueError("KV heads must be divisible by the TP degree")
+        self.scale = cfg.head_dim ** -0.5
+        self.sliding_window = cfg.sliding_window
+        self.eps = cfg.rms_norm_eps
+        h = cfg.hidden_size
+        self.qkv_proj = make_linear(cfg, f"{prefix}.qkv_proj", h, [cfg.q_size, cfg.kv_size, cfg.kv_size], TPMode.COL,
+                                    sources=["q_proj", "k_proj", "v_proj"], bias=cfg.attention_bias)
+        self.o_proj = make_linear(cfg, f"{prefix}.o_proj", cfg.q_size, [h], TPMode.ROW)
+        if cfg.has_qk_norm:
+            self.q_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, cfg.compute_dtype)
+            self.k_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, cfg.compute_dtype)
+        else:
+            self.q_norm = self.k_norm = None
+
+    def forward(self, x: torch.Tensor, meta: StepMeta, kv_layer: torch.Tensor, cos_sin: torch.Tensor) -> torch.Tensor:
+        qkv = self.qkv_proj(x)
+        q = ops.rope_kv_write(qkv, kv_layer, meta, cos_sin, self.num_q_heads, self.num_kv_heads, self.head_dim,
+                              None if self.q_norm is None else self.q_norm.weight,
+                              None if self.k_norm is None else self.k_norm.weight, self.eps)
+        o = ops.paged_attention(q, kv_layer, meta, self.scale, self.sliding_window)
+        return self.o_proj(o.reshape(o.shape[0], -1))
+
+
+class MLP(nn.Module):
+    def __init__(self, cfg: ModelConfig, prefix: str, intermediate: Optional[int] = None):
+        super().__init__()
+        inter = intermediate or cfg.intermediate_size
+        self.act = cfg.hidden_act
+        if self.act in ("silu", "swiglu"):
+            self.gate_up_proj = make_linear(cfg, f"{prefix}.gate_up_proj", cfg.hidden_size, [inter, inter], TPMode.COL,
+                                            sources=["gate_proj", "up_proj"])
+        else:   # non-gated (relu²) MLP
+            self.gate_up_proj = make_linear(cfg, f"{prefix}.up_proj", cfg.hidden_size, [inter], TPMode.COL,
+                                            sources=["up_proj"])
+        self.down_proj = make_linear(cfg, f"{prefix}.down_proj", inter, [cfg.hidden_size], TPMode.ROW)
+
+    def forward(self, x):
+        gu = self.gate_up_proj(x)
+        a = ops.swiglu(gu) if self.act in ("silu", "swiglu") else ops.relu2(gu)
+        return self.down_proj(a)
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int):
+        super().__init__()
+        p = f"model.layers.{layer_idx}"
+        self.self_attn = Attention(cfg, layer_idx, f"{p}.self_attn")
+        self.mlp = MLP(cfg, f"{p}.mlp")
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.compute_dtype)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.compute_dtype)
+
+    def forward(self, h, residual, meta, kv_layer, cos_sin, comm):
+        if residual is None:
+            residual = h
+            x = self.input_layernorm(h)
+        else:
+            x, residual = comm.add_rmsnorm(h, residual, self.input_layernorm.weight, self.input_layernorm.eps)
+        a = self.self_attn(x, meta, kv_layer, cos_sin)
+        x, residual = comm.add_rmsnorm(a, residual, self.post_attention_layernorm.weight,
+                                       self.post_attention_layernorm.eps)
+        return self.mlp(x), residual
+
+
+class Transformer(nn.Module):
+    def __init__(self, cfg: ModelConfig):
+        super().__init__()
+        self.cfg = cfg
+        self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size, dtype=cfg.compute_dtype)
+        self.embed_tokens.weight.requires_grad_(False)
+        self.layers = nn.ModuleList([DecoderLayer(cfg, i) for i in range(cfg.num_hidden_layers)])
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.compute_dtype)
+
+    def forward(self, ids, meta, kv_cache, cos_sin, comm, inputs_embeds=None, capture_layers=()):
+        h = ops.embedding(ids, self.embed_tokens.weight) if inputs_embeds is None else inputs_embeds
+        residual = None
+        taps = []
+        for i, layer in enumerate(self.layers):
+            h, residual = layer(h, residual, meta, kv_cache[i], cos_sin, comm)
+            if i in capture_layers:
+                taps.append((h.float() + residual.float()).to(h.dtype) if comm.world_size == 1
+                            else comm.all_reduce(h).add_(residual))
+        x, _ = comm.add_rmsnorm(h, residual, self.norm.weight, self.norm.eps)
+        return (x, taps) if capture_layers else x
+
+
+class CausalLM(nn.Module):
+    """Decoder + LM head.  ``forward`` returns logits only for ``meta.logits_idx`` rows."""
+
+    # checkpoint module name → (fused layer attribute, ordered source names)
+    packed_modules = {"qkv_proj": ["q_proj", "k_proj", "v_proj"], "gate_up_proj": ["gate_proj", "up_proj"]}
+
+    def __init__(self, cfg: ModelConfig, comm=None):
+        super().__init__()
+        self.cfg = cfg
+        self.comm = comm or LocalComm()
+        self.model = Transformer(cfg)
+        # The LM head is vocabulary-sharded under TP; the sampler merges per-shard candidates.
+        self.lm_head = make_linear(cfg, "lm_head", cfg.hidden_size, [cfg.vocab_size],
+                                   TPMode.COL if cfg.tp_size > 1 and cfg.vocab_size % cfg.tp_size == 0 else TPMode.REPLICATED)
+        self._cos_sin: Optional[torch.Tensor] = None
+
+    def cos_sin(self, device) -> torch.Tensor:
+        if self._cos_sin is None or self._cos_sin.device != torch.device(device):
+            self._cos_sin = ops.ref.rope_cos_sin(self.cfg.max_position_embeddings, self.cfg.rotary_dim,
+                                                 self.cfg.rope_theta, self.cfg.rope_scaling, device=device)
+        return self._cos_sin
+
+    def hidden_states(self, ids, meta, kv_cache, inputs_embeds=None, capture_layers=()):
+        dev = ids.device if inputs_embeds is None else inputs_embeds.device
+        return self.model(ids, meta, kv_cache, self.cos_sin(dev), self.comm, inputs_embeds, capture_layers)
+
+    def logits_from_hidden(self, x: torch.Tensor, meta: StepMeta) -> torch.Tensor:
+        rows = x if meta.logits_idx.numel() == x.shape[0] else x.index_select(0, meta.logits_idx.long())
+        logits = self.lm_head(rows)
+        if self.lm_head.tp_mode == TPMode.COL and self.comm.world_size > 1:
+            logits = self.comm.all_gather_cols(logits)
+        return logits
+
+    def forward(self, ids: torch.Tensor, meta: StepMeta, kv_cache: torch.Tensor,
+                inputs_embeds: Optional[torch.Tensor] = None) -> torch.Tensor:
+        x = self.hidden_states(ids, meta, kv_cache, inputs_embeds)
+        return self.logits_from_hidden(x, meta)
+
+    def finalize(self):
+        for m in self.modules():
+            if hasattr(m, "finalize") and m is not self:
+                m.finalize()
+        return self

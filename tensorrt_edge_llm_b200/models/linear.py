@@ -1,0 +1,235 @@
+"""Linear layers: dense 16-bit, NVFP4 (W4A4 / W4A16) and INT4-AWQ, with tensor-parallel modes.
+
+Parity: ``tensorrt_edgellm/models/linear.py`` — ``TPMode`` and Column/Row parallel classes
+(:103-576), NVFP4 variants (:440-468, :765-845), INT4 (:647-757), ``make_linear`` (:1085).  The
+reference lowers these to TensorRT nodes and plugins; here each ``forward`` runs the sm_100a
+kernel directly (``ops.cuda``) or the PyTorch statement on CPU.
+
+Checkpoint tensors keep their Hugging Face / ModelOpt names (``weight``, ``weight_scale``,
+``weight_scale_2``, ``input_scale``, ``bias``) so loading is a plain name match; a layer that
+fuses several checkpoint modules (``qkv_proj``, ``gate_up_proj``) lists them in ``sources``.
+"""
+from __future__ import annotations
+
+import enum
+from typing import Dict, List, Optional, Sequence
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..config import (QUANT_INT4_AWQ, QUANT_NONE, QUANT_NVFP4, QUANT_NVFP4_A16, ModelConfig)
+from ..ops import reference as ref
+
+
+class TPMode(enum.Enum):
+    REPLICATED = "replicated"
+    COL = "col"     # output features sharded; no collective
+    ROW = "row"     # input features sharded; partial sums reduced by the caller's collective
+
+
+def _shard(t: torch.Tensor, dim: int, rank: int, world: int) -> torch.Tensor:
+    if world == 1:
+        return t
+    n = t.shape[dim]
+    if n % world:
+        raise ValueError(f"dimension {dim} of size {n} is not divisible by TP {world}")
+    return t.narrow(dim, rank * (n // world), n // world).contiguous()
+
+
+class LinearBase(nn.Module):
+    """Common bookkeeping: logical sizes, TP placement and the checkpoint modules it fuses."""
+
+    def __init__(self, in_features: int, out_features: Sequence[int], tp_mode: TPMode, tp_size: int, tp_rank: int,
+                 sources: Optional[List[str]] = None, bias: bool = False):
+        super().__init__()
+        self.tp_mode, self.tp_size, self.tp_rank = tp_mode, tp_size, tp_rank
+        self.sources = sources
+        self.full_in = in_features
+        self.full_out = list(out_features)
+        self.in_features = in_features // tp_size if tp_mode == TPMode.ROW else in_features
+        self.out_sizes = [o // tp_size if tp_mode == TPMode.COL else o for o in out_features]
+        self.out_features = sum(self.out_sizes)
+        self.has_bias = bias
+
+    # sharding of one source module's tensor (dim 0 = out, dim 1 = in)
+    def shard_out_in(self, t: torch.Tensor) -> torch.Tensor:
+        if self.tp_mode == TPMode.COL:
+            return _shard(t, 0, self.tp_rank, self.tp_size)
+        if self.tp_mode == TPMode.ROW and t.dim() > 1:
+            return _shard(t, 1, self.tp_rank, self.tp_size)
+        return t
+
+    def load_from(self, tensors: List[Dict[str, torch.Tensor]]) -> None:
+        raise NotImplementedError
+
+    def finalize(self) -> None:
+        """Hook run once after loading and device placement (GPU-side repacks)."""
+
+
+class Linear(LinearBase):
+    """16-bit dense linear, ``y = x Wᵀ (+ b)``."""
+
+    def __init__(self, in_features, out_features, tp_mode=TPMode.REPLICATED, tp_size=1, tp_rank=0, sources=None,
+                 bias=False, dtype=torch.bfloat16):
+        super().__init__(in_features, out_features, tp_mode, tp_size, tp_rank, sources, bias)
+        self.weight = nn.Parameter(torch.empty(self.out_features, self.in_features, dtype=dtype), requires_grad=False)
+        self.bias = nn.Parameter(torch.zeros(self.out_features, dtype=dtype), requires_grad=False) if bias else None
+
+    def load_from(self, tensors):
+        ws = [self.shard_out_in(t["weight"]) for t in tensors]
+        self.weight.data.copy_(torch.cat(ws, dim=0).to(self.weight.dtype))
+        if self.bias is not None:
+            bs = []
+            for t in tensors:
+                b = t["bias"]
+                bs.append(_shard(b, 0, self.tp_rank, self.tp_size) if self.tp_mode == TPMode.COL else b)
+            b = torch.cat(bs, dim=0)
+            if self.tp_mode == TPMode.ROW and self.tp_rank != 0:
+                b = torch.zeros_like(b)       # the reduced sum must add the bias once
+            self.bias.data.copy_(b.to(self.bias.dtype))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.linear(x, self.weight, self.bias)
+
+
+class NVFP4Linear(LinearBase):
+    """NVFP4 weights (E2M1 pairs, E4M3 scale per 16 inputs, fp32 ``weight_scale_2``).
+
+    ``quantize_activations`` selects W4A4 (activations quantised per 16-block with the
+    calibrated ``input_scale``, block-scaled tensor-core GEMM) or W4A16.  Fused sources keep
+    one global weight scale per source; it is folded into a per-output-column ``alpha``.
+    """
+
+    def __init__(self, in_features, out_features, tp_mode=TPMode.REPLICATED, tp_size=1, tp_rank=0, sources=None,
+                 bias=False, dtype=torch.bfloat16, quantize_activations=True):
+        super().__init__(in_features, out_features, tp_mode, tp_size, tp_rank, sources, bias)
+        if self.in_features % 16:
+            raise ValueError("NVFP4 needs in_features divisible by 16 on every rank")
+        self.act_dtype = dtype
+        self.quantize_activations = quantize_activations
+        self.register_buffer("weight", torch.zeros(self.out_features, self.in_features // 2, dtype=torch.uint8))
+        self.register_buffer("weight_scale", torch.zeros(self.out_features, self.in_features // 16, dtype=torch.float8_e4m3fn))
+        self.register_buffer("weight_scale_2", torch.ones(len(self.out_sizes), dtype=torch.float32))
+        self.register_buffer("input_scale", torch.ones((), dtype=torch.float32))
+        self.register_buffer("alpha", torch.ones(self.out_features, dtype=torch.float32))
+        self.bias = nn.Parameter(torch.zeros(self.out_features, dtype=dtype), requires_grad=False) if bias else None
+        self._gpu_weight_sf = None      # scale factors repacked for the tensor-core kernel
+
+    def load_from(self, tensors):
+        w = torch.cat([self.shard_out_in(t["weight"]) for t in tensors], dim=0)
+        sf = torch.cat([self.shard_out_in(t["weight_scale"].view(torch.uint8)) for t in tensors], dim=0)
+        self.weight.copy_(w.view(torch.uint8))
+        self.weight_scale.copy_(sf.view(torch.float8_e4m3fn))
+        self.weight_scale_2.copy_(torch.stack([t["weight_scale_2"].float().reshape(()) for t in tensors]))
+        ins = [t["input_scale"].float().reshape(()) for t in tensors if "input_scale" in t]
+        if ins:
+            self.input_scale.copy_(torch.stack(ins).max())
+        self._refresh_alpha()
+        if self.bias is not None:
+            self.bias.data.copy_(torch.cat([t["bias"] for t in tensors]).to(self.bias.dtype))
+
+    def _refresh_alpha(self):
+        per_col = torch.cat([self.weight_scale_2[i].expand(n) for i, n in enumerate(self.out_sizes)])
+        gs = self.input_scale if self.quantize_activations else torch.ones_like(self.input_scale)
+        self.alpha.copy_(per_col * gs)
+
+    @torch.no_grad()
+    def quantize_from(self, weights: List[torch.Tensor], input_scale: float = 1.0 / 448.0) -> None:
+        """Quantise 16-bit weights (one tensor per fused source) into this layer."""
+        packs, sfs, gss = [], [], []
+        for wt in weights:
+            p, sf, gs = ref.nvfp4_quantize(wt.float())
+            packs.append(p); sfs.append(sf.view(torch.uint8)); gss.append(gs)
+        self.weight.copy_(torch.cat(packs, 0))
+        self.weight_scale.copy_(torch.cat(sfs, 0).view(torch.float8_e4m3fn))
+        self.weight_scale_2.copy_(torch.stack(gss))
+        self.input_scale.fill_(float(input_scale))
+        self._refresh_alpha()
+
+    def dequantized_weight(self) -> torch.Tensor:
+        per_row = torch.cat([self.weight_scale_2[i].expand(n) for i, n in enumerate(self.out_sizes)])
+        return ref.nvfp4_dequantize(self.weight, self.weight_scale, torch.ones((), device=self.weight.device)) * per_row[:, None]
+
+    def finalize(self):
+        if self.weight.is_cuda:
+            self._gpu_weight_sf = ops.cuda_ops().nvfp4_swizzle_scales(self.weight_scale)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.is_cuda:
+            if self._gpu_weight_sf is None:
+                self.finalize()
+            return ops.cuda_ops().nvfp4_linear(x, self.weight, self._gpu_weight_sf, self.alpha, self.input_scale,
+                                               self.bias, self.quantize_activations)
+        xa = x.float()
+        if self.quantize_activations:
+            xa = ref.nvfp4_act_qdq(xa, self.input_scale)
+        y = xa @ self.dequantized_weight().t()
+        if self.bias is not None:
+            y = y + self.bias.float()
+        return y.to(x.dtype)
+
+
+class Int4AwqLinear(LinearBase):
+    """INT4 group-wise weights in the ModelOpt prepacked layout (``weight [out/2, in]`` uint8,
+    ``weight_scale [out, in/g]``, optional ``pre_quant_scale [in]``)."""
+
+    def __init__(self, in_features, out_features, tp_mode=TPMode.REPLICATED, tp_size=1, tp_rank=0, sources=None,
+                 bias=False, dtype=torch.bfloat16, group_size=128):
+        super().__init__(in_features, out_features, tp_mode, tp_size, tp_rank, sources, bias)
+        self.group = group_size
+        self.register_buffer("weight", torch.zeros(self.out_features // 2, self.in_features, dtype=torch.uint8))
+        self.register_buffer("weight_scale", torch.ones(self.out_features, self.in_features // group_size, dtype=dtype))
+        self.register_buffer("pre_quant_scale", torch.ones(self.in_features, dtype=dtype))
+        self.bias = nn.Parameter(torch.zeros(self.out_features, dtype=dtype), requires_grad=False) if bias else None
+        self._dense = None
+
+    def load_from(self, tensors):
+        self.weight.copy_(torch.cat([self.shard_out_in(t["weight"].view(torch.uint8)) for t in tensors], 0))
+        self.weight_scale.copy_(torch.cat([self.shard_out_in(t["weight_scale"]) for t in tensors], 0).to(self.weight_scale.dtype))
+        if "pre_quant_scale" in tensors[0]:
+            pq = tensors[0]["pre_quant_scale"]
+            if self.tp_mode == TPMode.ROW:
+                pq = _shard(pq, 0, self.tp_rank, self.tp_size)
+            self.pre_quant_scale.copy_(pq.to(self.pre_quant_scale.dtype))
+
+    @torch.no_grad()
+    def quantize_from(self, weights: List[torch.Tensor]) -> None:
+        w = torch.cat([wt.float() for wt in weights], 0)
+        g = self.group
+        wg = w.reshape(w.shape[0], w.shape[1] // g, g)
+        scale = (wg.abs().amax(-1) / 7.0).clamp(min=1e-8)
+        q = (torch.round(wg / scale[..., None]).clamp(-8, 7) + 8).to(torch.uint8).reshape(w.shape)
+        self.weight.copy_(q[0::2] | (q[1::2] << 4))
+        self.weight_scale.copy_(scale.to(self.weight_scale.dtype))
+        self._dense = None
+
+    def dequantized_weight(self) -> torch.Tensor:
+        return ref.int4_awq_dequantize(self.weight, self.weight_scale, None, self.group)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        xs = (x.float() * self.pre_quant_scale.float()).to(x.dtype)
+        if x.is_cuda:
+            return ops.cuda_ops().int4_awq_linear(xs, self.weight, self.weight_scale, self.group, self.bias)
+        y = xs.float() @ self.dequantized_weight().t()
+        if self.bias is not None:
+            y = y + self.bias.float()
+        return y.to(x.dtype)
+
+
+def make_linear(cfg: ModelConfig, name: str, in_features: int, out_features: Sequence[int],
+                tp_mode: TPMode = TPMode.REPLICATED, sources: Optional[List[str]] = None, bias: bool = False,
+                quantizable: bool = True) -> LinearBase:
+    """Build the linear layer the checkpoint's quantisation calls for.  ``name`` is the fully
+    qualified module name used for exclusion matching (``lm_head`` stays 16-bit unless the
+    checkpoint says otherwise)."""
+    tp_size, tp_rank = (cfg.tp_size, cfg.tp_rank) if tp_mode != TPMode.REPLICATED else (1, 0)
+    qt = cfg.quant.module_quant_type(name) if quantizable else QUANT_NONE
+    if name.endswith("lm_head"):
+        qt = cfg.quant.lm_head_quant_type
+    kw = dict(tp_mode=tp_mode, tp_size=tp_size, tp_rank=tp_rank, sources=sources, bias=bias, dtype=cfg.compute_dtype)
+    if qt in (QUANT_NVFP4, QUANT_NVFP4_A16):
+        return NVFP4Linear(in_features, out_features, quantize_activations=(qt == QUANT_NVFP4 and cfg.quant.quantize_activations), **kw)
+    if qt == QUANT_INT4_AWQ:
+        return Int4AwqLinear(in_features, out_features, group_size=cfg.quant.group_size or 128, **kw)
+    return Linear(in_features, out_features, **kw)

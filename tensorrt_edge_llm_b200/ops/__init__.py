@@ -1,0 +1,119 @@
+"""Operator front end.
+
+Each function executes the hand-written sm_100a kernel when its tensors live on a CUDA
+device and the plain-PyTorch statement (``ops.reference``) on CPU.  There is no silent
+fallback on a GPU: if the native library is missing, the CUDA path raises.
+
+Parity: the custom-op surface of ``tensorrt_edgellm/models/ops.py`` (attention_plugin :145,
+nvfp4 ops :917-951, causal_conv1d :1541, update_ssm_state :1631, gated_delta_net :1908,
+MoE plugins :2017-2209, all_reduce :2754) expressed as directly executable functions.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import reference as ref
+from .meta import StepMeta, build_step_meta
+
+__all__ = ["StepMeta", "build_step_meta", "ref", "cuda_ops"]
+
+
+def cuda_ops():
+    """The ctypes binding module (imported lazily so CPU-only use never touches it)."""
+    from . import cuda as _cuda
+    return _cuda
+
+
+def rmsnorm(x, weight, eps):
+    if x.is_cuda:
+        return cuda_ops().rmsnorm(x, weight, eps)
+    return ref.rmsnorm(x, weight, eps)
+
+
+def add_rmsnorm(x, residual, weight, eps):
+    if x.is_cuda:
+        return cuda_ops().add_rmsnorm(x, residual, weight, eps)
+    return ref.add_rmsnorm(x, residual, weight, eps)
+
+
+def gated_group_rmsnorm(x, z, weight, n_groups, eps):
+    if x.is_cuda:
+        return cuda_ops().gated_group_rmsnorm(x, z, weight, n_groups, eps)
+    return ref.gated_group_rmsnorm(x, z, weight, n_groups, eps)
+
+
+def swiglu(gate_up):
+    if gate_up.is_cuda:
+        return cuda_ops().swiglu(gate_up)
+    return ref.swiglu(gate_up)
+
+
+def relu2(x):
+    if x.is_cuda:
+        return cuda_ops().relu2(x)
+    return ref.relu2(x)
+
+
+def embedding(ids, table):
+    if table.is_cuda:
+        return cuda_ops().embedding(ids, table)
+    return ref.embedding(ids, table)
+
+
+def linear(x, weight, bias=None):
+    if x.is_cuda:
+        return cuda_ops().gemm(x, weight, bias)
+    return ref.linear(x, weight, bias)
+
+
+def rope_kv_write(qkv, kv_layer, meta, cos_sin, num_q_heads, num_kv_heads, head_dim,
+                  q_norm_w=None, k_norm_w=None, eps=1e-6):
+    if qkv.is_cuda:
+        return cuda_ops().rope_kv_write(qkv, kv_layer, meta, cos_sin, num_q_heads, num_kv_heads, head_dim,
+                                        q_norm_w, k_norm_w, eps)
+    return ref.rope_kv_write(qkv, kv_layer, meta, cos_sin, num_q_heads, num_kv_heads, head_dim,
+                             q_norm_w, k_norm_w, eps)
+
+
+def paged_attention(q, kv_layer, meta, scale, sliding_window=None, sinks=None):
+    if q.is_cuda:
+        return cuda_ops().paged_attention(q, kv_layer, meta, scale, sliding_window, sinks)
+    return ref.paged_attention(q, kv_layer, meta, scale, sliding_window, sinks)
+
+
+def argmax(logits):
+    if logits.is_cuda:
+        return cuda_ops().argmax(logits)
+    return ref.argmax(logits)
+
+
+def sample(logits, temperature, top_k, top_p, uniforms):
+    if logits.is_cuda:
+        return cuda_ops().sample(logits, temperature, top_k, top_p, uniforms)
+    return ref.sample(logits, temperature, top_k, top_p, uniforms)
+
+
+def moe_route(logits, top_k, renormalize=True):
+    if logits.is_cuda:
+        return cuda_ops().moe_route_softmax_topk(logits, top_k, renormalize)
+    return ref.moe_route_softmax_topk(logits, top_k, renormalize)
+
+
+def causal_conv1d(x, weight, bias, conv_state, meta, activation=True):
+    if x.is_cuda:
+        return cuda_ops().causal_conv1d(x, weight, bias, conv_state, meta, activation)
+    return ref.causal_conv1d(x, weight, bias, conv_state, meta, activation)
+
+
+def ssm_scan(x, dt, A, B, C, D, dt_bias, ssm_state, meta, z=None, dt_softplus=True, dt_limit=0.0):
+    if x.is_cuda:
+        return cuda_ops().ssm_scan(x, dt, A, B, C, D, dt_bias, ssm_state, meta, z, dt_softplus, dt_limit)
+    return ref.ssm_scan(x, dt, A, B, C, D, dt_bias, ssm_state, meta, z, dt_softplus, dt_limit)
+
+
+def gated_delta_rule(q, k, v, a, b, A_log, dt_bias, state, meta):
+    if q.is_cuda:
+        return cuda_ops().gated_delta_rule(q, k, v, a, b, A_log, dt_bias, state, meta)
+    return ref.gated_delta_rule(q, k, v, a, b, A_log, dt_bias, state, meta)

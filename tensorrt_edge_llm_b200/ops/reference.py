@@ -1,0 +1,508 @@
+"""Plain-PyTorch statements of every operator (fp32 math).
+
+These bodies are (a) the CPU execution path, so the whole runtime steps without a GPU, and
+(b) the numerical oracle each CUDA kernel is tested against.  They favour clarity over speed.
+
+Operator semantics follow the reference's CPU statements: RMSNorm
+(``tensorrt_edgellm/models/default/modeling_default.py:163-182``), rotate-half RoPE and causal
+GQA attention (``unittests/support/references.h:29-65``), NVFP4 math
+(``tensorrt_edgellm/models/ops.py:826-909``), MoE routing
+(``unittests/support/references.cpp:1384-1476``), Mamba2 state update
+(``unittests/cpp/kernels/mamba/mambaSelectiveStateUpdateTests.cu:62-160``), gated delta rule
+(``unittests/cpp/kernels/gdnKernels/gdnCuteDslTests.cu:157-238``).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from .meta import StepMeta
+
+# ------------------------------------------------------------------------------------------
+# norms / activations
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    var = xf.pow(2).mean(-1, keepdim=True)
+    y = xf * torch.rsqrt(var + eps)
+    return (y.to(x.dtype).float() * weight.float()).to(x.dtype)
+
+
+def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float
+                ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``res = x + residual`` (in the activation dtype), ``y = rmsnorm(res)``; returns (y, res)."""
+    res = (x.float() + residual.float()).to(x.dtype)
+    return rmsnorm(res, weight, eps), res
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    return F.layer_norm(x.float(), (x.shape[-1],), weight.float(), None if bias is None else bias.float(), eps).to(x.dtype)
+
+
+def gated_group_rmsnorm(x: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, n_groups: int, eps: float) -> torch.Tensor:
+    """Mamba2 output norm: ``g = x * silu(z)``, RMS-normalise each of ``n_groups`` slices, scale."""
+    g = x.float() * F.silu(z.float())
+    shp = g.shape
+    g = g.reshape(*shp[:-1], n_groups, shp[-1] // n_groups)
+    g = g * torch.rsqrt(g.pow(2).mean(-1, keepdim=True) + eps)
+    return (g.reshape(shp).to(x.dtype).float() * weight.float()).to(x.dtype)
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` where the last dim holds ``[gate | up]`` halves."""
+    g, u = gate_up.float().chunk(2, dim=-1)
+    return (F.silu(g) * u).to(gate_up.dtype)
+
+
+def relu2(x: torch.Tensor) -> torch.Tensor:
+    return F.relu(x.float()).pow(2).to(x.dtype)
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    return table[ids.long()]
+
+
+# ------------------------------------------------------------------------------------------
+# RoPE
+
+
+def rope_cos_sin(max_pos: int, rotary_dim: int, theta: float, scaling: Optional[dict] = None,
+                 device="cpu") -> torch.Tensor:
+    """``[max_pos, rotary_dim]`` table: first half cos, second half sin (fp32).
+
+    Supports the default, ``linear``, ``llama3`` and ``yarn`` frequency scalings
+    (``cpp/kernels/posEncoding/initializeCosSinCache.cu`` in the reference)."""
+    half = rotary_dim // 2
+    inv = 1.0 / (theta ** (torch.arange(0, half, dtype=torch.float64) * 2.0 / rotary_dim))
+    att = 1.0
+    if scaling:
+        kind = scaling.get("rope_type", scaling.get("type", "default"))
+        factor = float(scaling.get("factor", 1.0))
+        if kind == "linear":
+            inv = inv / factor
+        elif kind == "llama3":
+            lo, hi = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
+            orig = float(scaling.get("original_max_position_embeddings", 8192))
+            wavelen = 2 * math.pi / inv
+            smooth = ((orig / wavelen) - lo) / (hi - lo)
+            scaled = torch.where(wavelen > orig / lo, inv / factor,
+                                 torch.where(wavelen < orig / hi, inv, (1 - smooth) * inv / factor + smooth * inv))
+            inv = scaled
+        elif kind == "yarn":
+            orig = float(scaling.get("original_max_position_embeddings", 4096))
+            bf, bs = float(scaling.get("beta_fast", 32)), float(scaling.get("beta_slow", 1))
+
+            def corr(rot):
+                return rotary_dim * math.log(orig / (rot * 2 * math.pi)) / (2 * math.log(theta))
+            lo_i, hi_i = max(math.floor(corr(bf)), 0), min(math.ceil(corr(bs)), half - 1)
+            ramp = ((torch.arange(half, dtype=torch.float64) - lo_i) / max(hi_i - lo_i, 1e-3)).clamp(0, 1)
+            inv = inv / factor * ramp + inv * (1 - ramp)
+            att = float(scaling.get("attention_factor") or (0.1 * math.log(factor) + 1.0))
+    pos = torch.arange(max_pos, dtype=torch.float64)
+    ang = pos[:, None] * inv[None, :]
+    return torch.cat([ang.cos() * att, ang.sin() * att], dim=-1).float().to(device)
+
+
+def apply_rope(x: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor) -> torch.Tensor:
+    """Rotate-half RoPE on ``x [T, H, D]`` for the first ``rotary_dim`` features (fp32 math)."""
+    rd = cos_sin.shape[-1]
+    half = rd // 2
+    cs = cos_sin[positions.long()]
+    cos, sin = cs[:, None, :half].float(), cs[:, None, half:].float()
+    xf = x.float()
+    x1, x2 = xf[..., :half], xf[..., half:rd]
+    out = xf.clone()
+    out[..., :half] = x1 * cos - x2 * sin
+    out[..., half:rd] = x2 * cos + x1 * sin
+    return out.to(x.dtype)
+
+
+def _head_rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return (y.to(x.dtype).float() * w.float()).to(x.dtype)
+
+
+def rope_kv_write(qkv: torch.Tensor, kv_layer: torch.Tensor, meta: StepMeta, cos_sin: torch.Tensor,
+                  num_q_heads: int, num_kv_heads: int, head_dim: int,
+                  q_norm_w: Optional[torch.Tensor] = None, k_norm_w: Optional[torch.Tensor] = None,
+                  eps: float = 1e-6) -> torch.Tensor:
+    """Split packed ``qkv [T,(Hq+2Hkv)D]``, optional per-head q/k RMSNorm, RoPE on q and k,
+    write k and v into the paged cache ``kv_layer [pages, 2, Hkv, P, D]``; returns ``q [T,Hq,D]``.
+    """
+    t = qkv.shape[0]
+    q, k, v = qkv.split([num_q_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * head_dim], dim=-1)
+    q = q.reshape(t, num_q_heads, head_dim)
+    k = k.reshape(t, num_kv_heads, head_dim)
+    v = v.reshape(t, num_kv_heads, head_dim)
+    if q_norm_w is not None:
+        q = _head_rmsnorm(q, q_norm_w, eps)
+    if k_norm_w is not None:
+        k = _head_rmsnorm(k, k_norm_w, eps)
+    q = apply_rope(q, meta.positions, cos_sin)
+    k = apply_rope(k, meta.positions, cos_sin)
+    p = meta.page_size
+    sid = meta.seq_ids.long()
+    if meta.kv_offsets is not None:
+        slot = meta.past_len.long()[sid] + meta.kv_offsets.long()
+    else:
+        slot = meta.past_len.long()[sid] + (torch.arange(t, device=qkv.device) - meta.q_start.long()[sid])
+    page = meta.page_table.long()[sid, slot // p]
+    kv_layer[page, 0, :, slot % p, :] = k.to(kv_layer.dtype)
+    kv_layer[page, 1, :, slot % p, :] = v.to(kv_layer.dtype)
+    return q
+
+
+def gather_kv(kv_layer: torch.Tensor, page_table_row: torch.Tensor, length: int, page_size: int
+              ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Dense ``k, v [Hkv, length, D]`` of one sequence from the paged pool."""
+    n_pages = (length + page_size - 1) // page_size
+    pages = page_table_row[:n_pages].long()
+    blk = kv_layer[pages]                      # [n, 2, Hkv, P, D]
+    k = blk[:, 0].permute(1, 0, 2, 3).reshape(blk.shape[2], -1, blk.shape[-1])[:, :length]
+    v = blk[:, 1].permute(1, 0, 2, 3).reshape(blk.shape[2], -1, blk.shape[-1])[:, :length]
+    return k, v
+
+
+def paged_attention(q: torch.Tensor, kv_layer: torch.Tensor, meta: StepMeta, scale: float,
+                    sliding_window: Optional[int] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal GQA attention of the step's rows over the paged cache (which already holds this
+    step's keys/values).  Row ``i`` of a sequence sees cache slots ``[0, past + i]``
+    (bottom-right aligned causal mask), optionally limited to a sliding window, or the tree
+    mask for speculative verification.  ``q [T,Hq,D]`` → ``[T,Hq,D]``."""
+    t, hq, d = q.shape
+    hkv = kv_layer.shape[2]
+    g = hq // hkv
+    out = torch.empty_like(q)
+    for s in range(meta.num_seqs):
+        r0, ql, past = int(meta.q_start[s]), int(meta.q_len[s]), int(meta.past_len[s])
+        if ql == 0:
+            continue
+        total = past + ql
+        k, v = gather_kv(kv_layer, meta.page_table[s], total, meta.page_size)
+        qs = q[r0:r0 + ql].float().permute(1, 0, 2)                      # [Hq, ql, D]
+        kf = k.float().repeat_interleave(g, dim=0)                        # [Hq, total, D]
+        vf = v.float().repeat_interleave(g, dim=0)
+        sc = torch.matmul(qs, kf.transpose(1, 2)) * scale                 # [Hq, ql, total]
+        rows = torch.arange(ql, device=q.device)[:, None]
+        cols = torch.arange(total, device=q.device)[None, :]
+        if meta.tree_mask is not None:
+            words = meta.tree_mask[r0:r0 + ql].long()                     # [ql, W]
+            new_c = (cols - past).clamp(min=0)
+            bit = (words.gather(1, (new_c // 32).expand(ql, -1)) >> (new_c % 32)) & 1
+            allowed = (cols < past) | ((cols >= past) & (bit == 1))
+        else:
+            allowed = cols <= past + rows
+        if sliding_window is not None:
+            allowed = allowed & (cols > past + rows - sliding_window)
+        sc = sc.masked_fill(~allowed[None], float("-inf"))
+        if sinks is not None:
+            sink = sinks.float().view(hq, 1, 1).expand(hq, ql, 1)
+            pr = torch.softmax(torch.cat([sc, sink], dim=-1), dim=-1)[..., :-1]
+        else:
+            pr = torch.softmax(sc, dim=-1)
+        out[r0:r0 + ql] = torch.matmul(pr, vf).permute(1, 0, 2).to(q.dtype)
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+# NVFP4 (E2M1 values, E4M3 scale per 16 elements, fp32 global scale)
+
+E2M1_LEVELS = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+FP4_MAX = 6.0
+E4M3_MAX = 448.0
+
+
+def _e2m1_table(device) -> torch.Tensor:
+    lv = torch.tensor(E2M1_LEVELS, dtype=torch.float32, device=device)
+    return torch.cat([lv, -lv])
+
+
+def fp4_encode(x: torch.Tensor) -> torch.Tensor:
+    """Round fp32 values (already divided by their scale) to E2M1 codes 0..15, ties to even."""
+    ax = x.abs().clamp(max=FP4_MAX)
+    # thresholds between consecutive levels; ties go to the code with an even mantissa bit
+    code = torch.zeros_like(ax, dtype=torch.uint8)
+    bounds = (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0)
+    tie_up = (False, True, False, True, False, True, False)   # at a tie, go up iff the upper code is even
+    for i, (b, up) in enumerate(zip(bounds, tie_up)):
+        code = torch.where((ax > b) | ((ax == b) & up), torch.full_like(code, i + 1), code)
+    sign = (x < 0) | ((x == 0) & (torch.signbit(x)))
+    return code | (sign.to(torch.uint8) << 3)
+
+
+def fp4_pack(codes: torch.Tensor) -> torch.Tensor:
+    """Pack ``[..., K]`` codes into ``[..., K/2]`` bytes, even index in the low nibble."""
+    return (codes[..., 0::2] | (codes[..., 1::2] << 4)).contiguous()
+
+
+def fp4_unpack(packed: torch.Tensor) -> torch.Tensor:
+    lo, hi = packed & 0xF, packed >> 4
+    return torch.stack([lo, hi], dim=-1).reshape(*packed.shape[:-1], packed.shape[-1] * 2)
+
+
+def nvfp4_quantize(x: torch.Tensor, global_scale: Optional[torch.Tensor] = None
+                   ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Quantise ``x [..., K]`` to NVFP4.
+
+    Returns ``(packed uint8 [..., K/2], block_scale float8_e4m3fn [..., K/16], global_scale fp32)``
+    with ``x ≈ e2m1 * block_scale * global_scale`` and ``global_scale = amax / (6 * 448)``."""
+    xf = x.float()
+    if global_scale is None:
+        global_scale = (xf.abs().amax() / (FP4_MAX * E4M3_MAX)).clamp(min=1e-12)
+    gs = global_scale.float().reshape(())
+    blocks = xf.reshape(*xf.shape[:-1], xf.shape[-1] // 16, 16)
+    amax = blocks.abs().amax(-1)
+    sf = (amax / FP4_MAX / gs).clamp(max=E4M3_MAX).to(torch.float8_e4m3fn)
+    sff = sf.float() * gs
+    scaled = torch.where(sff[..., None] > 0, blocks / sff[..., None].clamp(min=1e-30), torch.zeros_like(blocks))
+    codes = fp4_encode(scaled).reshape(xf.shape)
+    return fp4_pack(codes), sf, gs
+
+
+def nvfp4_dequantize(packed: torch.Tensor, block_scale: torch.Tensor, global_scale: torch.Tensor,
+                     dtype=torch.float32) -> torch.Tensor:
+    codes = fp4_unpack(packed).long()
+    vals = _e2m1_table(packed.device)[codes]
+    k = vals.shape[-1]
+    vals = vals.reshape(*vals.shape[:-1], k // 16, 16) * block_scale.float()[..., None]
+    return (vals.reshape(*vals.shape[:-2], k) * global_scale.float()).to(dtype)
+
+
+def nvfp4_act_qdq(x: torch.Tensor, global_scale: torch.Tensor) -> torch.Tensor:
+    """Fake-quantise activations exactly as the W4A4 GEMM sees them."""
+    p, sf, gs = nvfp4_quantize(x, global_scale)
+    return nvfp4_dequantize(p, sf, gs, x.dtype)
+
+
+def nvfp4_linear(x: torch.Tensor, w_packed: torch.Tensor, w_scale: torch.Tensor, w_scale_2: torch.Tensor,
+                 input_scale: Optional[torch.Tensor], bias: Optional[torch.Tensor] = None,
+                 quantize_activations: bool = True) -> torch.Tensor:
+    w = nvfp4_dequantize(w_packed, w_scale, w_scale_2)
+    xa = x.float()
+    if quantize_activations:
+        gs = input_scale if input_scale is not None else None
+        p, sf, g = nvfp4_quantize(xa, gs)
+        xa = nvfp4_dequantize(p, sf, g)
+    y = xa @ w.t()
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(x.dtype)
+
+
+def int4_awq_dequantize(qweight: torch.Tensor, scales: torch.Tensor, zeros: Optional[torch.Tensor], group: int
+                        ) -> torch.Tensor:
+    """ModelOpt-prepacked INT4: ``qweight [out/2, in]`` uint8 (row 2r in the low nibble, 2r+1 high),
+    ``scales [out, in/group]``; symmetric when ``zeros`` is None (offset 8)."""
+    lo, hi = (qweight & 0xF).float(), (qweight >> 4).float()
+    w = torch.stack([lo, hi], dim=1).reshape(qweight.shape[0] * 2, qweight.shape[1])
+    z = 8.0 if zeros is None else zeros.float().repeat_interleave(group, dim=1)
+    return (w - z) * scales.float().repeat_interleave(group, dim=1)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    y = x.float() @ weight.float().t()
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(x.dtype)
+
+
+# ------------------------------------------------------------------------------------------
+# MoE
+
+
+def moe_route_softmax_topk(logits: torch.Tensor, top_k: int, renormalize: bool = True
+                           ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Softmax over experts then top-k by value (ties → lower index); weights fp32 ``[T,k]``."""
+    probs = torch.softmax(logits.float(), dim=-1)
+    # torch.topk is not guaranteed stable on ties; sort descending with a stable sort instead
+    order = torch.sort(probs, dim=-1, descending=True, stable=True)
+    w, idx = order.values[..., :top_k], order.indices[..., :top_k]
+    if renormalize:
+        w = w / w.sum(-1, keepdim=True)
+    return w, idx.to(torch.int32)
+
+
+def moe_route_sigmoid_group_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, n_group: int,
+                                 topk_group: int, renormalize: bool, scaling: float
+                                 ) -> Tuple[torch.Tensor, torch.Tensor]:
+    s = torch.sigmoid(logits.float())
+    sel = s + (bias.float() if bias is not None else 0.0)
+    t, e = sel.shape
+    grp = sel.view(t, n_group, e // n_group)
+    gscore = grp.topk(min(2, e // n_group), dim=-1).values.sum(-1)
+    gidx = gscore.topk(topk_group, dim=-1).indices
+    gmask = torch.zeros_like(gscore).scatter_(1, gidx, 1.0)
+    masked = sel.masked_fill(gmask.repeat_interleave(e // n_group, dim=1) == 0, float("-inf"))
+    idx = torch.sort(masked, dim=-1, descending=True, stable=True).indices[..., :top_k]
+    w = s.gather(1, idx)
+    if renormalize:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return w * scaling, idx.to(torch.int32)
+
+
+def moe_ffn(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Tensor, w13, w2, act: str = "swiglu"
+            ) -> torch.Tensor:
+    """``y = Σ_k w_k · down_e(act(gate_up_e x))`` with expert weight callables or dense tensors.
+
+    ``w13 [E, 2I, H]`` (gate rows first, then up; ``[E, I, H]`` when ``act == 'relu2'``), ``w2 [E, H, I]``."""
+    t, h = x.shape
+    out = torch.zeros(t, h, dtype=torch.float32, device=x.device)
+    for e in topk_idx.unique().tolist():
+        rows, slot = (topk_idx == e).nonzero(as_tuple=True)
+        if rows.numel() == 0:
+            continue
+        xe = x[rows].float()
+        hmid = xe @ w13[e].float().t()
+        if act == "swiglu":
+            g, u = hmid.chunk(2, dim=-1)
+            hmid = F.silu(g) * u
+        else:
+            hmid = F.relu(hmid).pow(2)
+        hmid = hmid.to(x.dtype).float()
+        ye = hmid @ w2[e].float().t()
+        out.index_add_(0, rows, ye * topk_w[rows, slot].float()[:, None])
+    return out.to(x.dtype)
+
+
+# ------------------------------------------------------------------------------------------
+# Mamba2 / conv1d / gated delta rule
+
+
+def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], conv_state: torch.Tensor,
+                  meta: StepMeta, activation: bool = True) -> torch.Tensor:
+    """Depthwise causal conv over packed rows ``x [T,C]`` with per-sequence rolling history
+    ``conv_state [rows, C, W-1]`` (oldest first) addressed by ``meta.slot_ids``; state updated in place.
+    A sequence with ``past_len == 0`` starts from zero history."""
+    t, c = x.shape
+    w = weight.shape[-1]
+    wf = weight.reshape(c, w).float()
+    out = torch.empty_like(x)
+    for s in range(meta.num_seqs):
+        r0, ql, past, slot = int(meta.q_start[s]), int(meta.q_len[s]), int(meta.past_len[s]), int(meta.slot_ids[s])
+        if ql == 0:
+            continue
+        hist = conv_state[slot].float() if past > 0 else torch.zeros(c, w - 1, device=x.device)
+        seq = torch.cat([hist, x[r0:r0 + ql].float().t()], dim=1)            # [C, W-1+ql]
+        y = F.conv1d(seq[None], wf[:, None, :], None if bias is None else bias.float(), groups=c)[0]
+        if activation:
+            y = F.silu(y)
+        out[r0:r0 + ql] = y.t().to(x.dtype)
+        conv_state[slot] = seq[:, -(w - 1):].to(conv_state.dtype)
+    return out
+
+
+def ssm_scan(x: torch.Tensor, dt: torch.Tensor, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, D: torch.Tensor,
+             dt_bias: torch.Tensor, ssm_state: torch.Tensor, meta: StepMeta, z: Optional[torch.Tensor] = None,
+             dt_softplus: bool = True, dt_limit: float = 0.0) -> torch.Tensor:
+    """Mamba2 selective-state recurrence over packed rows (sequential, fp32).
+
+    ``x [T,nh,hd]``, ``dt [T,nh]``, ``A [nh]`` (negative), ``B,C [T,G,N]``, ``D [nh]``,
+    ``ssm_state [rows, nh, hd, N]`` fp32 updated in place; returns ``y [T,nh,hd]``."""
+    t, nh, hd = x.shape
+    g = B.shape[1]
+    hpg = nh // g
+    out = torch.empty_like(x)
+    for s in range(meta.num_seqs):
+        r0, ql, past, slot = int(meta.q_start[s]), int(meta.q_len[s]), int(meta.past_len[s]), int(meta.slot_ids[s])
+        if ql == 0:
+            continue
+        h = ssm_state[slot].float() if past > 0 else torch.zeros(nh, hd, B.shape[-1], device=x.device)
+        for i in range(r0, r0 + ql):
+            d = dt[i].float() + dt_bias.float()
+            if dt_softplus:
+                d = torch.where(d > 20.0, d, F.softplus(d))
+            if dt_limit > 0:
+                d = d.clamp(max=dt_limit)
+            dA = torch.exp(A.float() * d)                                    # [nh]
+            Bh = B[i].float().repeat_interleave(hpg, dim=0)                   # [nh, N]
+            Ch = C[i].float().repeat_interleave(hpg, dim=0)
+            xi = x[i].float()                                                 # [nh, hd]
+            h = h * dA[:, None, None] + (d[:, None] * xi)[:, :, None] * Bh[:, None, :]
+            y = (h * Ch[:, None, :]).sum(-1) + D.float()[:, None] * xi
+            if z is not None:
+                y = y * F.silu(z[i].float())
+            out[i] = y.to(x.dtype)
+        ssm_state[slot] = h.to(ssm_state.dtype)
+    return out
+
+
+def gated_delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor, b: torch.Tensor,
+                     A_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, meta: StepMeta) -> torch.Tensor:
+    """Gated delta rule over packed rows.  ``q,k [T,hk,K]``, ``v [T,hv,V]``, ``a,b [T,hv]``,
+    ``state [rows, hv, K, V]`` fp32 updated in place; returns ``o [T,hv,V]``."""
+    t, hk, kd = q.shape
+    hv = v.shape[1]
+    rep = hv // hk
+    out = torch.empty_like(v)
+    for s in range(meta.num_seqs):
+        r0, ql, past, slot = int(meta.q_start[s]), int(meta.q_len[s]), int(meta.past_len[s]), int(meta.slot_ids[s])
+        if ql == 0:
+            continue
+        H = state[slot].float() if past > 0 else torch.zeros(hv, kd, v.shape[-1], device=q.device)
+        for i in range(r0, r0 + ql):
+            qi = q[i].float()
+            ki = k[i].float()
+            qi = qi * torch.rsqrt(qi.pow(2).sum(-1, keepdim=True) + 1e-6) * (kd ** -0.5)
+            ki = ki * torch.rsqrt(ki.pow(2).sum(-1, keepdim=True) + 1e-6)
+            qi = qi.repeat_interleave(rep, dim=0)
+            ki = ki.repeat_interleave(rep, dim=0)                              # [hv, K]
+            gdec = torch.exp(-torch.exp(A_log.float()) * F.softplus(a[i].float() + dt_bias.float()))
+            beta = torch.sigmoid(b[i].float())
+            H = H * gdec[:, None, None]
+            pred = torch.einsum("hkv,hk->hv", H, ki)
+            delta = beta[:, None] * (v[i].float() - pred)
+            H = H + ki[:, :, None] * delta[:, None, :]
+            out[i] = torch.einsum("hkv,hk->hv", H, qi).to(v.dtype)
+        state[slot] = H.to(state.dtype)
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+# sampling
+
+
+def apply_token_bitmask(logits: torch.Tensor, bitmask: torch.Tensor) -> torch.Tensor:
+    """Mask (−1e30) every vocabulary entry whose bit is 0 in ``bitmask [rows, ceil(V/32)]`` int32."""
+    v = logits.shape[-1]
+    idx = torch.arange(v, device=logits.device)
+    bits = (bitmask.long()[:, idx // 32] >> (idx % 32)) & 1
+    return torch.where(bits == 1, logits, torch.full_like(logits, -1e30))
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           uniforms: torch.Tensor) -> torch.Tensor:
+    """Per-row top-k / top-p sampling.  ``temperature < 1e-3`` means greedy.  ``uniforms [rows]`` in
+    [0,1) make the draw independent of batch composition (``cpp/sampler/sampling.h:56-160``)."""
+    rows, v = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    for r in range(rows):
+        temp = float(temperature[r])
+        if temp < 1e-3:
+            out[r] = int(torch.argmax(logits[r].float()))
+            continue
+        lg = logits[r].float() / temp
+        k = int(top_k[r])
+        p = float(top_p[r])
+        srt = torch.sort(lg, descending=True, stable=True)
+        vals, idx = srt.values, srt.indices
+        if k > 0:
+            vals, idx = vals[:k], idx[:k]
+        probs = torch.softmax(vals, dim=-1)
+        if p < 1.0:
+            cum = probs.cumsum(-1)
+            keep = (cum - probs) < p
+            probs = torch.where(keep, probs, torch.zeros_like(probs))
+            probs = probs / probs.sum()
+        cum = probs.cumsum(-1)
+        j = int(torch.searchsorted(cum, torch.tensor(float(uniforms[r]) * float(cum[-1]), device=cum.device)).clamp(max=probs.numel() - 1))
+        out[r] = int(idx[j])
+    return out
+
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    return torch.argmax(logits.float(), dim=-1).to(torch.int32)

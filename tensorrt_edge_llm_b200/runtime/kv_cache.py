@@ -1,0 +1,120 @@
+"""Paged KV-cache pool and the host-truth page table.
+
+One device tensor ``[layers, pages, 2, Hkv, page_size, D]`` holds every attention layer's keys
+and values; a (page, K|V, head) slab is contiguous (``page_size × D`` elements), which is the
+tile the attention kernels fetch with one TMA copy.  A logical page of a sequence maps to the
+same physical page index in every layer, so one ``[seats, max_pages]`` table serves the model.
+
+Parity: ``cpp/runtime/kvCacheManager.{h,cpp}`` (per-layer pools ``[2, numPages, 128, Hkv, D]``),
+``cpp/runtime/state/kvPageTable.{h,cpp}`` (host-truth table, −1 = unused, dirty-row upload) and
+``cpp/common/pagedKvTypes.h`` (page size 128; here it is a runtime parameter, 64 by default).
+Page accounting is delegated to the native allocator when the runtime extension is built.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..config import ModelConfig, LAYER_ATTENTION
+
+
+class PageAllocator:
+    """Free-list page allocator with reference counts (shared prefix pages)."""
+
+    def __init__(self, num_pages: int):
+        self.num_pages = num_pages
+        self._free = list(range(num_pages - 1, -1, -1))
+        self._ref = [0] * num_pages
+
+    @property
+    def free_pages(self) -> int:
+        return len(self._free)
+
+    def alloc(self, n: int) -> List[int]:
+        if n > len(self._free):
+            raise MemoryError(f"KV pool exhausted: want {n} pages, {len(self._free)} free")
+        out = [self._free.pop() for _ in range(n)]
+        for p in out:
+            self._ref[p] = 1
+        return out
+
+    def retain(self, pages: Sequence[int]) -> None:
+        for p in pages:
+            if self._ref[p] <= 0:
+                raise ValueError(f"retain of free page {p}")
+            self._ref[p] += 1
+
+    def release(self, pages: Sequence[int]) -> None:
+        for p in pages:
+            if self._ref[p] <= 0:
+                raise ValueError(f"double free of page {p}")
+            self._ref[p] -= 1
+            if self._ref[p] == 0:
+                self._free.append(p)
+
+
+class KVCacheManager:
+    """Owns the pool tensor, the allocator and the per-seat page table."""
+
+    def __init__(self, cfg: ModelConfig, num_pages: int, page_size: int = 64, max_seats: int = 64,
+                 max_pages_per_seq: int = 64, device="cpu", dtype: Optional[torch.dtype] = None,
+                 num_layers: Optional[int] = None):
+        self.cfg = cfg
+        self.page_size = page_size
+        self.max_seats = max_seats
+        self.max_pages_per_seq = max_pages_per_seq
+        self.num_layers = num_layers if num_layers is not None else sum(t == LAYER_ATTENTION for t in cfg.layer_types)
+        hkv = max(cfg.num_key_value_heads // cfg.tp_size, 1)
+        self.dtype = dtype or cfg.compute_dtype
+        self.pool = torch.zeros(self.num_layers, num_pages, 2, hkv, page_size, cfg.head_dim, dtype=self.dtype, device=device)
+        self.alloc = PageAllocator(num_pages)
+        self.table = torch.full((max_seats, max_pages_per_seq), -1, dtype=torch.int32)   # host truth
+        self.lengths = [0] * max_seats
+        self._pages: Dict[int, List[int]] = {}
+
+    @property
+    def bytes_per_token(self) -> int:
+        return self.pool[:, 0, :, :, 0].numel() * self.pool.element_size()
+
+    def capacity_tokens(self, seat: int) -> int:
+        return len(self._pages.get(seat, [])) * self.page_size
+
+    def reserve(self, seat: int, total_tokens: int) -> None:
+        """Grow ``seat``'s page list so it can hold ``total_tokens``."""
+        need = (total_tokens + self.page_size - 1) // self.page_size
+        have = self._pages.setdefault(seat, [])
+        if need > self.max_pages_per_seq:
+            raise ValueError(f"sequence of {total_tokens} tokens exceeds {self.max_pages_per_seq} pages")
+        if need > len(have):
+            new = self.alloc.alloc(need - len(have))
+            self.table[seat, len(have):need] = torch.tensor(new, dtype=torch.int32)
+            have.extend(new)
+
+    def adopt_prefix(self, seat: int, pages: Sequence[int], tokens: int) -> None:
+        """Share already-filled pages (prefix reuse); the seat must be empty."""
+        assert not self._pages.get(seat)
+        self.alloc.retain(pages)
+        self._pages[seat] = list(pages)
+        self.table[seat, :len(pages)] = torch.tensor(list(pages), dtype=torch.int32)
+        self.lengths[seat] = tokens
+
+    def commit(self, seat: int, new_tokens: int) -> None:
+        self.lengths[seat] += new_tokens
+
+    def rewind(self, seat: int, length: int) -> None:
+        """Drop everything after ``length`` tokens (speculative rejection); pages are kept."""
+        assert length <= self.lengths[seat]
+        self.lengths[seat] = length
+
+    def free(self, seat: int) -> None:
+        pages = self._pages.pop(seat, [])
+        self.alloc.release(pages)
+        self.table[seat].fill_(-1)
+        self.lengths[seat] = 0
+
+    def pages_of(self, seat: int) -> List[int]:
+        return list(self._pages.get(seat, []))
+
+    def table_rows(self, seats: Sequence[int]) -> torch.Tensor:
+        return self.table[list(seats)]

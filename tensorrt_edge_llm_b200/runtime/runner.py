@@ -1,0 +1,202 @@
+"""Model runner: executes ragged steps (prefill chunks, decode rows, mixed) on one rank.
+
+This is the counterpart of the reference's ``EngineExecutor`` + ``LLMRankRuntime`` step
+functions (``cpp/runtime/exec/engineExecutor.h:94-271``, ``cpp/runtime/llmRankRuntime.cpp``
+``runBaseModelPrefill`` :4758, ``captureDecodingCUDAGraph`` :5326, vanilla decode
+``cpp/runtime/decoding/vanillaDecoder.cpp:67-181,304-404``) without a TensorRT engine: the
+"engine" is the PyTorch module whose leaves are sm_100a kernels.  Prefill runs eagerly;
+all-resident decode steps replay a CUDA graph per batch size, with device-resident step state
+(lengths, positions, token feedback) so a run of decode steps needs no host round trip.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..ops.meta import StepMeta, build_step_meta
+from .kv_cache import KVCacheManager
+
+
+@dataclass
+class SamplingParams:
+    """Per-request sampling controls (``cpp/sampler/sampling.h:36-100`` semantics)."""
+
+    max_tokens: int = 128
+    temperature: float = 0.0
+    top_k: int = 0
+    top_p: float = 1.0
+    seed: int = 42
+    ignore_eos: bool = False
+    stop_token_ids: Sequence[int] = ()
+    logprobs: int = 0
+
+
+class ModelRunner:
+    def __init__(self, model, kv: KVCacheManager, device="cpu", max_num_tokens: int = 8192):
+        self.model = model
+        self.kv = kv
+        self.device = torch.device(device)
+        self.max_num_tokens = max_num_tokens
+        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self.use_cuda_graphs = self.device.type == "cuda"
+
+    # ---- eager ragged step -----------------------------------------------------------------
+    def _meta(self, seats: Sequence[int], q_lens: Sequence[int], logits_all=False, tree_mask=None,
+              positions=None) -> StepMeta:
+        past = [self.kv.lengths[s] for s in seats]
+        for s, q, p in zip(seats, q_lens, past):
+            self.kv.reserve(s, p + q)
+        return build_step_meta(q_lens, past, self.kv.table_rows(seats), self.kv.page_size, slot_ids=seats,
+                               logits_all=logits_all, device=self.device, tree_mask=tree_mask, positions=positions)
+
+    @torch.no_grad()
+    def step(self, seats: Sequence[int], token_lists: Sequence[Sequence[int]], logits_all=False,
+             commit=True, tree_mask=None, positions=None) -> torch.Tensor:
+        """Run one ragged step; returns logits ``[L, V]`` (last row of each sequence unless
+        ``logits_all``).  KV lengths advance by the rows fed when ``commit``."""
+        q_lens = [len(t) for t in token_lists]
+        meta = self._meta(seats, q_lens, logits_all, tree_mask, positions)
+        flat = [t for ts in token_lists for t in ts]
+        ids = torch.tensor(flat, dtype=torch.int32, device=self.device)
+        logits = self.model(ids, meta, self.kv.pool)
+        if commit:
+            for s, q in zip(seats, q_lens):
+                self.kv.commit(s, q)
+        return logits
+
+    @torch.no_grad()
+    def prefill(self, seats: Sequence[int], prompts: Sequence[Sequence[int]]) -> torch.Tensor:
+        """Chunked prefill of whole prompts; returns the last-token logits ``[N, V]``.
+
+        Sequences are packed into steps of at most ``max_num_tokens`` rows; a prompt longer than
+        the budget is split on page boundaries (``cpp/scheduler/stepPlanner.cpp`` rule)."""
+        n = len(seats)
+        done = [0] * n
+        out: List[Optional[torch.Tensor]] = [None] * n
+        p = self.kv.page_size
+        while any(done[i] < len(prompts[i]) for i in range(n)):
+            budget = self.max_num_tokens
+            step_seats, step_tokens, finishing = [], [], []
+            for i in range(n):
+                rem = len(prompts[i]) - done[i]
+                if rem == 0 or budget == 0:
+                    continue
+                take = min(rem, budget)
+                if take < rem:
+                    take = (take // p) * p
+                    if take == 0:
+                        continue
+                step_seats.append(seats[i])
+                step_tokens.append(prompts[i][done[i]:done[i] + take])
+                finishing.append((i, done[i] + take == len(prompts[i])))
+                done[i] += take
+                budget -= take
+            logits = self.step(step_seats, step_tokens)
+            for row, (i, fin) in enumerate(finishing):
+                if fin:
+                    out[i] = logits[row]
+        return torch.stack(out)  # type: ignore[arg-type]
+
+    # ---- decode ----------------------------------------------------------------------------
+    @torch.no_grad()
+    def decode_greedy(self, seats: Sequence[int], first_tokens: torch.Tensor, steps: int) -> torch.Tensor:
+        """Greedy decode ``steps`` tokens for every seat starting from ``first_tokens [N]``;
+        returns ``[N, steps]`` int32 (the tokens *generated*, not including ``first_tokens``).
+
+        On CUDA the steps replay one captured graph whose device-side state advances by itself;
+        the host copies the token matrix back once at the end."""
+        n = len(seats)
+        for s in seats:
+            self.kv.reserve(s, self.kv.lengths[s] + steps)
+        if self.use_cuda_graphs:
+            g = self._graphs.get(n)
+            if g is None:
+                g = self._graphs[n] = _DecodeGraph(self, n)
+            out = g.run(seats, first_tokens, steps)
+        else:
+            toks = first_tokens.to(torch.int32)
+            cols = []
+            for _ in range(steps):
+                logits = self.step(seats, [[int(t)] for t in toks.tolist()])
+                toks = ops.argmax(logits)
+                cols.append(toks)
+            return torch.stack(cols, dim=1)
+        for s in seats:
+            self.kv.commit(s, steps)
+        return out
+
+
+class _DecodeGraph:
+    """A captured all-resident decode step for a fixed batch size.
+
+    Static device state: ``ids`` (fed back from the sampler), ``past_len`` / ``positions``
+    (advanced by the captured increment), the page-table rows and the output token ring."""
+
+    MAX_STEPS = 4096
+
+    def __init__(self, runner: ModelRunner, n: int):
+        self.r = runner
+        self.n = n
+        dev = runner.device
+        kv = runner.kv
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.ids = torch.zeros(n, **i32)
+        self.meta = StepMeta(
+            q_start=torch.arange(n + 1, **i32), q_len=torch.ones(n, **i32), past_len=torch.zeros(n, **i32),
+            positions=torch.zeros(n, **i32), seq_ids=torch.arange(n, **i32),
+            page_table=torch.full((n, kv.max_pages_per_seq), -1, **i32), slot_ids=torch.zeros(n, **i32),
+            logits_idx=torch.arange(n, **i32), page_size=kv.page_size, num_seqs=n, num_tokens=n,
+            max_q_len=1, max_seq_len=kv.max_pages_per_seq * kv.page_size)
+        self.out = torch.zeros(self.MAX_STEPS, n, **i32)
+        self.step_idx = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self._pin = torch.empty(n * (kv.max_pages_per_seq + 3), dtype=torch.int32, pin_memory=True)
+
+    def _body(self):
+        m = self.meta
+        logits = self.r.model(self.ids, m, self.r.kv.pool)
+        tok = ops.argmax(logits)
+        self.ids.copy_(tok)
+        self.out.index_copy_(0, self.step_idx, tok.unsqueeze(0))
+        self.step_idx.add_(1)
+        m.past_len.add_(1)
+        m.positions.add_(1)
+
+    def _load_state(self, seats, first_tokens):
+        kv = self.r.kv
+        n, mp = self.n, kv.max_pages_per_seq
+        host = self._pin
+        host[:n] = torch.tensor([kv.lengths[s] for s in seats], dtype=torch.int32)
+        host[n:2 * n] = torch.tensor(list(seats), dtype=torch.int32)
+        host[2 * n:3 * n] = first_tokens.to("cpu", torch.int32) if first_tokens.device.type != "cpu" else first_tokens.to(torch.int32)
+        host[3 * n:] = kv.table_rows(seats).reshape(-1)
+        devbuf = host.to(self.r.device, non_blocking=True)
+        self.meta.past_len.copy_(devbuf[:n])
+        self.meta.positions.copy_(devbuf[:n])
+        self.meta.slot_ids.copy_(devbuf[n:2 * n])
+        self.ids.copy_(devbuf[2 * n:3 * n])
+        self.meta.page_table.copy_(devbuf[3 * n:].view(n, mp))
+        self.step_idx.zero_()
+
+    def run(self, seats, first_tokens, steps):
+        assert steps <= self.MAX_STEPS
+        self._load_state(seats, first_tokens)
+        if self.graph is None:
+            # warm up once eagerly (allocator, lazy kernels), restore state, then capture
+            s = torch.cuda.Stream(device=self.r.device)
+            s.wait_stream(torch.cuda.current_stream(self.r.device))
+            with torch.cuda.stream(s):
+                self._body()
+            torch.cuda.current_stream(self.r.device).wait_stream(s)
+            self._load_state(seats, first_tokens)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._body()
+            self.graph = g
+            self._load_state(seats, first_tokens)
+        for _ in range(steps):
+            self.graph.replay()
+        return self.out[:steps].t().contiguous()
