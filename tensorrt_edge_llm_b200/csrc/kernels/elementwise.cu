@@ -1,0 +1,425 @@
+// Bandwidth-bound operators around the GEMMs: RMSNorm (+residual add, +gated group form),
+// SwiGLU / ReLU², embedding gather, RoPE + q/k-norm + paged KV write, arg-max.  All are plain
+// SIMT kernels with 128-bit global accesses; launch grids scale with rows so decode-size calls
+// are a single wave.
+//
+// Reference counterparts: CuTe-DSL rmsnorm (kernelSrcs/rmsnorm_cutedsl/rmsnorm.py),
+// cpp/kernels/posEncoding/applyRopeWriteKV.cu, cpp/kernels/embeddingKernels/embeddingKernels.cu,
+// cpp/kernels/common/argmaxKernel.cu, cpp/kernels/moe/moeActivationKernels.cu.
+#include "host_utils.h"
+#include "tc5_common.cuh"
+
+namespace telb {
+
+template <typename T> struct Vec8 {
+    uint4 u;
+    __device__ __forceinline__ void load(const T* p) { u = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ void store(T* p) const { *reinterpret_cast<uint4*>(p) = u; }
+    __device__ __forceinline__ float get(int i) const { return Cvt<T>::to_f(reinterpret_cast<const T*>(&u)[i]); }
+    __device__ __forceinline__ void set(int i, float v) { reinterpret_cast<T*>(&u)[i] = Cvt<T>::from_f(v); }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    if (l == 0) red[w] = v;
+    __syncthreads();
+    float t = l < nw ? red[l] : 0.f;
+    t = warp_sum(t);
+    __syncthreads();
+    return t;
+}
+
+// y = rmsnorm(x [+ residual]) * w ; optionally writes the summed residual stream.
+// One CTA per row; each thread owns up to kMaxVec 8-element vectors kept in registers.
+template <typename T, int kMaxVec>
+__global__ void rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ w,
+                               T* __restrict__ y, T* __restrict__ res_out, int hidden, float eps) {
+    __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    const int nvec = hidden / 8;
+    Vec8<T> v[kMaxVec];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+        const int idx = threadIdx.x + i * blockDim.x;
+        if (idx < nvec) {
+            v[i].load(x + row * hidden + idx * 8);
+            if (residual) {
+                Vec8<T> r;
+                r.load(residual + row * hidden + idx * 8);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[i].set(j, v[i].get(j) + r.get(j));
+                if (res_out) v[i].store(res_out + row * hidden + idx * 8);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float f = v[i].get(j);
+                ss += f * f;
+            }
+        }
+    }
+    const float tot = block_sum(ss, red);
+    const float inv = rsqrtf(tot / hidden + eps);
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+        const int idx = threadIdx.x + i * blockDim.x;
+        if (idx < nvec) {
+            Vec8<T> wv, o;
+            wv.load(w + idx * 8);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float n = Cvt<T>::to_f(Cvt<T>::from_f(v[i].get(j) * inv));   // cast before the weight multiply
+                o.set(j, n * wv.get(j));
+            }
+            o.store(y + row * hidden + idx * 8);
+        }
+    }
+}
+
+// Mamba2 output norm: g = x * silu(z); RMS-normalise each group of `gsize` features; scale.
+// One CTA per (row, group).
+template <typename T>
+__global__ void gated_group_rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ z, const T* __restrict__ w,
+                                           T* __restrict__ y, int hidden, int gsize, float eps) {
+    __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    const int g = blockIdx.y;
+    const T* xp = x + row * hidden + g * gsize;
+    const T* zp = z + row * hidden + g * gsize;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < gsize; i += blockDim.x) {
+        const float zz = Cvt<T>::to_f(zp[i]);
+        const float gv = Cvt<T>::to_f(xp[i]) * (zz / (1.f + __expf(-zz)));
+        ss += gv * gv;
+    }
+    const float inv = rsqrtf(block_sum(ss, red) / gsize + eps);
+    for (int i = threadIdx.x; i < gsize; i += blockDim.x) {
+        const float zz = Cvt<T>::to_f(zp[i]);
+        const float gv = Cvt<T>::to_f(xp[i]) * (zz / (1.f + __expf(-zz)));
+        const float n = Cvt<T>::to_f(Cvt<T>::from_f(gv * inv));
+        y[row * hidden + g * gsize + i] = Cvt<T>::from_f(n * Cvt<T>::to_f(w[g * gsize + i]));
+    }
+}
+
+// out[t, i] = silu(in[t, i]) * in[t, inter + i]
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, long long rows, int inter) {
+    const long long nvec = rows * (inter / 8);
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < nvec;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long r = idx / (inter / 8);
+        const int c = (int)(idx % (inter / 8)) * 8;
+        Vec8<T> g, u, o;
+        g.load(in + r * 2 * inter + c);
+        u.load(in + r * 2 * inter + inter + c);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float gf = g.get(j);
+            o.set(j, gf / (1.f + __expf(-gf)) * u.get(j));
+        }
+        o.store(out + r * inter + c);
+    }
+}
+
+template <typename T>
+__global__ void relu2_kernel(const T* __restrict__ in, T* __restrict__ out, long long n) {
+    for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8; i < n;
+         i += (long long)gridDim.x * blockDim.x * 8) {
+        Vec8<T> v, o;
+        v.load(in + i);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float f = fmaxf(v.get(j), 0.f);
+            o.set(j, f * f);
+        }
+        o.store(out + i);
+    }
+}
+
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table, T* __restrict__ out,
+                                 int hidden, int vocab) {
+    const size_t row = blockIdx.x;
+    int id = ids[row];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)id * hidden);
+    uint4* dst = reinterpret_cast<uint4*>(out + row * hidden);
+    for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// RoPE + optional per-head RMSNorm on q and k + paged KV write.
+// grid (T, Hq + 2*Hkv), block D/2 threads: thread i owns features i and i + D/2.
+// qkv is token-major packed [T, (Hq + 2 Hkv) * D]; q_out is [T, Hq, D]; the cache layer is
+// [pages, 2, Hkv, P, D].
+template <typename T>
+__global__ void rope_kv_write_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ kv_layer,
+                                     const float* __restrict__ cos_sin, const int* __restrict__ positions,
+                                     const int* __restrict__ seq_ids, const int* __restrict__ q_start,
+                                     const int* __restrict__ past_len, const int* __restrict__ page_table,
+                                     const int* __restrict__ kv_offsets, const T* __restrict__ q_norm_w,
+                                     const T* __restrict__ k_norm_w, int hq, int hkv, int d, int rot_dim, int page_size,
+                                     int max_pages, float eps) {
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    const int h = blockIdx.y;
+    const int half = d / 2;
+    const int i = threadIdx.x;
+    const T* src = qkv + (size_t)t * (hq + 2 * hkv) * d + (size_t)h * d;
+    float a = Cvt<T>::to_f(src[i]);
+    float b = Cvt<T>::to_f(src[i + half]);
+    const bool is_q = h < hq;
+    const bool is_k = !is_q && h < hq + hkv;
+    const T* nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+    if (nw) {
+        const float tot = block_sum(a * a + b * b, red);
+        const float inv = rsqrtf(tot / d + eps);
+        a = Cvt<T>::to_f(Cvt<T>::from_f(a * inv)) * Cvt<T>::to_f(nw[i]);
+        b = Cvt<T>::to_f(Cvt<T>::from_f(b * inv)) * Cvt<T>::to_f(nw[i + half]);
+        a = Cvt<T>::to_f(Cvt<T>::from_f(a));
+        b = Cvt<T>::to_f(Cvt<T>::from_f(b));
+    }
+    if (is_q || is_k) {
+        const int rh = rot_dim / 2;
+        const int pos = positions[t];
+        // rotate-half pairs are (j, j + rot_dim/2) for j < rot_dim/2; with rot_dim == d that is (i, i+half)
+        if (rot_dim == d) {
+            const float c = cos_sin[(size_t)pos * rot_dim + i];
+            const float s = cos_sin[(size_t)pos * rot_dim + rh + i];
+            const float ra = a * c - b * s;
+            const float rb = b * c + a * s;
+            a = ra;
+            b = rb;
+        } else {
+            // partial rotary: stage the head in shared memory and rotate the leading rot_dim features
+            __shared__ float stage[512];
+            stage[i] = a;
+            stage[i + half] = b;
+            __syncthreads();
+            for (int j = i; j < rh; j += blockDim.x) {
+                const float c = cos_sin[(size_t)pos * rot_dim + j];
+                const float s = cos_sin[(size_t)pos * rot_dim + rh + j];
+                const float x1 = stage[j], x2 = stage[j + rh];
+                stage[j] = x1 * c - x2 * s;
+                stage[j + rh] = x2 * c + x1 * s;
+            }
+            __syncthreads();
+            a = stage[i];
+            b = stage[i + half];
+        }
+    }
+    if (is_q) {
+        T* dst = q_out + ((size_t)t * hq + h) * d;
+        dst[i] = Cvt<T>::from_f(a);
+        dst[i + half] = Cvt<T>::from_f(b);
+    } else {
+        const int s = seq_ids[t];
+        const int off = kv_offsets ? kv_offsets[t] : (t - q_start[s]);
+        const int slot = past_len[s] + off;
+        const int page = page_table[(size_t)s * max_pages + slot / page_size];
+        if (page < 0) return;      // unreserved page: skip instead of writing out of bounds
+        const int kvh = is_k ? h - hq : h - hq - hkv;
+        T* dst = kv_layer + ((((size_t)page * 2 + (is_k ? 0 : 1)) * hkv + kvh) * page_size + slot % page_size) * d;
+        dst[i] = Cvt<T>::from_f(a);
+        dst[i + half] = Cvt<T>::from_f(b);
+    }
+}
+
+// arg-max over the vocabulary, one CTA per row (ties → lowest index).
+template <typename T>
+__global__ void argmax_kernel(const T* __restrict__ logits, int* __restrict__ out, int vocab, long long stride) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const T* p = logits + blockIdx.x * stride;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = Cvt<T>::to_f(p[i]);
+        if (v > best || (v == best && i < bi)) {
+            best = v;
+            bi = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) {
+            best = ov;
+            bi = oi;
+        }
+    }
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) {
+        sv[w] = best;
+        si[w] = bi;
+    }
+    __syncthreads();
+    if (w == 0) {
+        const int nw = (blockDim.x + 31) >> 5;
+        best = l < nw ? sv[l] : -INFINITY;
+        bi = l < nw ? si[l] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) {
+                best = ov;
+                bi = oi;
+            }
+        }
+        if (l == 0) out[blockIdx.x] = bi;
+    }
+}
+
+}  // namespace telb
+
+using namespace telb;
+
+#define DISPATCH_T(is_bf16, ...)                 \
+    if (is_bf16) {                               \
+        using T = __nv_bfloat16;                 \
+        __VA_ARGS__                              \
+    } else {                                     \
+        using T = __half;                        \
+        __VA_ARGS__                              \
+    }
+
+extern "C" int telb_rmsnorm(const void* x, const void* residual, const void* w, void* y, void* res_out, long long rows,
+                            int hidden, float eps, int is_bf16, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden % 8) return fail("telb_rmsnorm: hidden must be a multiple of 8");
+    const int nvec = hidden / 8;
+    int threads = nvec >= 512 ? 512 : ((nvec + 31) / 32) * 32;
+    if (threads < 32) threads = 32;
+    const int per = (nvec + threads - 1) / threads;
+    if (per > 8) return fail("telb_rmsnorm: hidden too large (max 32768)");
+    DISPATCH_T(is_bf16, {
+        if (per <= 1) rmsnorm_kernel<T, 1><<<rows, threads, 0, stream>>>((const T*)x, (const T*)residual, (const T*)w, (T*)y, (T*)res_out, hidden, eps);
+        else if (per <= 2) rmsnorm_kernel<T, 2><<<rows, threads, 0, stream>>>((const T*)x, (const T*)residual, (const T*)w, (T*)y, (T*)res_out, hidden, eps);
+        else if (per <= 4) rmsnorm_kernel<T, 4><<<rows, threads, 0, stream>>>((const T*)x, (const T*)residual, (const T*)w, (T*)y, (T*)res_out, hidden, eps);
+        else rmsnorm_kernel<T, 8><<<rows, threads, 0, stream>>>((const T*)x, (const T*)residual, (const T*)w, (T*)y, (T*)res_out, hidden, eps);
+    })
+    TELB_CHECK_LAUNCH("rmsnorm_kernel");
+    return 0;
+}
+
+extern "C" int telb_gated_group_rmsnorm(const void* x, const void* z, const void* w, void* y, long long rows, int hidden,
+                                        int n_groups, float eps, int is_bf16, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    dim3 grid((unsigned)rows, n_groups);
+    DISPATCH_T(is_bf16, {
+        gated_group_rmsnorm_kernel<T><<<grid, 256, 0, stream>>>((const T*)x, (const T*)z, (const T*)w, (T*)y, hidden, hidden / n_groups, eps);
+    })
+    TELB_CHECK_LAUNCH("gated_group_rmsnorm_kernel");
+    return 0;
+}
+
+extern "C" int telb_swiglu(const void* in, void* out, long long rows, int inter, int is_bf16, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (inter % 8) return fail("telb_swiglu: intermediate size must be a multiple of 8");
+    const long long nvec = rows * (inter / 8);
+    long long blocks = (nvec + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    DISPATCH_T(is_bf16, { swiglu_kernel<T><<<(int)blocks, 256, 0, stream>>>((const T*)in, (T*)out, rows, inter); })
+    TELB_CHECK_LAUNCH("swiglu_kernel");
+    return 0;
+}
+
+extern "C" int telb_relu2(const void* in, void* out, long long n, int is_bf16, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (n % 8) return fail("telb_relu2: element count must be a multiple of 8");
+    long long blocks = (n / 8 + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    DISPATCH_T(is_bf16, { relu2_kernel<T><<<(int)blocks, 256, 0, stream>>>((const T*)in, (T*)out, n); })
+    TELB_CHECK_LAUNCH("relu2_kernel");
+    return 0;
+}
+
+extern "C" int telb_embedding(const int* ids, const void* table, void* out, long long rows, int hidden, int vocab,
+                              int is_bf16, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden % 8) return fail("telb_embedding: hidden must be a multiple of 8");
+    DISPATCH_T(is_bf16, { embedding_kernel<T><<<(unsigned)rows, 128, 0, stream>>>(ids, (const T*)table, (T*)out, hidden, vocab); })
+    TELB_CHECK_LAUNCH("embedding_kernel");
+    return 0;
+}
+
+extern "C" int telb_rope_kv_write(const void* qkv, void* q_out, void* kv_layer, const float* cos_sin,
+                                  const int* positions, const int* seq_ids, const int* q_start, const int* past_len,
+                                  const int* page_table, const int* kv_offsets, const void* q_norm_w,
+                                  const void* k_norm_w, int tokens, int hq, int hkv, int d, int rot_dim, int page_size,
+                                  int max_pages, float eps, int is_bf16, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (d % 2 || d > 512) return fail("telb_rope_kv_write: head_dim must be even and <= 512");
+    dim3 grid(tokens, hq + 2 * hkv);
+    DISPATCH_T(is_bf16, {
+        rope_kv_write_kernel<T><<<grid, d / 2, 0, stream>>>((const T*)qkv, (T*)q_out, (T*)kv_layer, cos_sin, positions, seq_ids, q_start,
+                                                            past_len, page_table, kv_offsets, (const T*)q_norm_w,
+                                                            (const T*)k_norm_w, hq, hkv, d, rot_dim, page_size, max_pages, eps);
+    })
+    TELB_CHECK_LAUNCH("rope_kv_write_kernel");
+    return 0;
+}
+
+namespace telb {
+__global__ void argmax_f32_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab, long long stride) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const float* p = logits + blockIdx.x * stride;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = p[i];
+        if (v > best || (v == best && i < bi)) {
+            best = v;
+            bi = i;
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) {
+            best = ov;
+            bi = oi;
+        }
+    }
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) {
+        sv[w] = best;
+        si[w] = bi;
+    }
+    __syncthreads();
+    if (w == 0) {
+        const int nw = (blockDim.x + 31) >> 5;
+        best = l < nw ? sv[l] : -INFINITY;
+        bi = l < nw ? si[l] : 0x7fffffff;
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) {
+                best = ov;
+                bi = oi;
+            }
+        }
+        if (l == 0) out[blockIdx.x] = bi;
+    }
+}
+}  // namespace telb
+
+// dtype: 0 = fp16, 1 = bf16, 2 = fp32
+extern "C" int telb_argmax(const void* logits, int* out, long long rows, int vocab, long long stride, int dtype,
+                           cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (dtype == 2) argmax_f32_kernel<<<(unsigned)rows, 1024, 0, stream>>>((const float*)logits, out, vocab, stride);
+    else if (dtype == 1) argmax_kernel<__nv_bfloat16><<<(unsigned)rows, 1024, 0, stream>>>((const __nv_bfloat16*)logits, out, vocab, stride);
+    else argmax_kernel<__half><<<(unsigned)rows, 1024, 0, stream>>>((const __half*)logits, out, vocab, stride);
+    TELB_CHECK_LAUNCH("argmax_kernel");
+    return 0;
+}

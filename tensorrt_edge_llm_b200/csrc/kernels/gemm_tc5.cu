@@ -1,0 +1,429 @@
+// 16-bit (bf16 / fp16) GEMM on 5th-generation tensor cores:  out[M,N] = x[M,K] · w[N,K]ᵀ
+// (+ bias, × per-column alpha, + residual), fp32 accumulation in TMEM.
+//
+// One persistent, warp-specialised kernel serves both regimes:
+//   * large M (prefill): x is the MMA-M operand (128-row tiles), w the MMA-N operand (256 rows);
+//   * small M (decode):  operands are swapped so the 128-row MMA-M side always streams weights,
+//     the token batch is the MMA-N side (16..128), and K is split across CTAs so that all SMs
+//     pull weights from HBM.  Split partial tiles meet in an fp32 workspace; the CTA that
+//     arrives last at the tile's counter sums them and runs the epilogue (no CTA ever waits on
+//     another CTA).
+// Roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = UMMA issuer + TMEM owner,
+// warps 2-5 = epilogue (one TMEM lane quadrant each).  Accumulators are double-buffered in TMEM
+// so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Reference counterpart: the dense projections are TensorRT MatMul tactics inside the engine and
+// CuTe-DSL `gemm_blackwell.py` for auxiliary GEMMs (kernelSrcs/gemm_cutedsl/); this kernel is
+// written from the PTX up and shares no code with either.
+#include "host_utils.h"
+#include "tc5_common.cuh"
+
+namespace telb {
+
+struct GemmParams {
+    int rows_a, rows_b, k;
+    int splits, kb_per_split, kb_total;
+    int tiles_a, tiles_b;
+    void* c;
+    long long ldc_lane, ldc_col;
+    const void* bias;
+    const float* alpha;
+    const void* residual;
+    int feat_on_lane;
+    int out_bf16;
+    float* ws;
+    int* counters;
+    int* status;
+};
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;                       // 64 x 2 B = one 128-byte swizzle atom
+constexpr int kATileBytes = kBM * kBK * 2;    // 16 KiB
+constexpr int kGemmThreads = 192;
+constexpr int kRasterGroup = 8;
+
+struct TileCoord {
+    int a0, b0, kb0, kb1, tile, split;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int t) {
+    TileCoord c;
+    c.split = t % p.splits;
+    const int tt = t / p.splits;
+    const int per_group = kRasterGroup * p.tiles_b;
+    const int group = tt / per_group;
+    const int within = tt - group * per_group;
+    const int gfirst = group * kRasterGroup;
+    const int gsize = min(kRasterGroup, p.tiles_a - gfirst);
+    const int ta = gfirst + within % gsize;
+    const int tb = within / gsize;
+    c.tile = tb * p.tiles_a + ta;
+    c.a0 = ta * kBM;
+    c.kb0 = c.split * p.kb_per_split;
+    c.kb1 = min(p.kb_total, c.kb0 + p.kb_per_split);
+    c.b0 = tb;   // multiplied by BN by the caller
+    return c;
+}
+
+template <typename T>
+__device__ __forceinline__ void epilogue_store(const GemmParams& p, const float (&v)[32], int row, int col0,
+                                               int ncols_valid) {
+    // v[j] belongs to (row, col0 + j)
+    T* cptr = reinterpret_cast<T*>(p.c);
+    const T* rptr = reinterpret_cast<const T*>(p.residual);
+    const T* bptr = reinterpret_cast<const T*>(p.bias);
+    float o[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        float x = v[j];
+        if (j < ncols_valid) {
+            const int f = p.feat_on_lane ? row : (col0 + j);
+            if (p.alpha) x *= p.alpha[f];
+            if (bptr) x += Cvt<T>::to_f(bptr[f]);
+            if (rptr) x += Cvt<T>::to_f(rptr[row * p.ldc_lane + (long long)(col0 + j) * p.ldc_col]);
+        }
+        o[j] = x;
+    }
+    if (p.ldc_col == 1) {
+        T* dst = cptr + row * p.ldc_lane + col0;
+        const bool vec_ok = (ncols_valid == 32) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+        if (vec_ok) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint4 u;
+                u.x = Cvt<T>::pack2(o[q * 8 + 0], o[q * 8 + 1]);
+                u.y = Cvt<T>::pack2(o[q * 8 + 2], o[q * 8 + 3]);
+                u.z = Cvt<T>::pack2(o[q * 8 + 4], o[q * 8 + 5]);
+                u.w = Cvt<T>::pack2(o[q * 8 + 6], o[q * 8 + 7]);
+                reinterpret_cast<uint4*>(dst)[q] = u;
+            }
+        } else {
+            for (int j = 0; j < ncols_valid; ++j) dst[j] = Cvt<T>::from_f(o[j]);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (j < ncols_valid) cptr[row * p.ldc_lane + (long long)(col0 + j) * p.ldc_col] = Cvt<T>::from_f(o[j]);
+    }
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, GemmParams p) {
+    constexpr int kBTileBytes = BN * kBK * 2;
+    constexpr int kStageBytes = kATileBytes + kBTileBytes;
+    constexpr int kAccStride = BN < 32 ? 32 : BN;          // TMEM columns per accumulator buffer
+    constexpr int kTmemCols = 2 * kAccStride;               // power of two for every BN used here
+    constexpr int kChunks = (BN + 31) / 32;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * kStageBytes);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* tfull_bar = empty_bar + STAGES;
+    uint64_t* tempty_bar = tfull_bar + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    volatile uint32_t* last_flag = tmem_slot + 2;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int total_tiles = p.tiles_a * p.tiles_b * p.splits;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&tfull_bar[s], 1);
+            mbar_init(&tempty_bar[s], 128);
+        }
+        *abort_flag = 0;
+        *last_flag = 0;
+        mbar_fence_init();
+        prefetch_tensormap(&tma_a);
+        prefetch_tensormap(&tma_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const TileCoord tc = decode_tile(p, t);
+                for (int kb = tc.kb0; kb < tc.kb1; ++kb) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sa = smem + stage * kStageBytes;
+                    mbar_expect_tx(&full_bar[stage], kStageBytes);
+                    tma_load_2d(sa, &tma_a, &full_bar[stage], kb * kBK, tc.a0);
+                    tma_load_2d(sa + kATileBytes, &tma_b, &full_bar[stage], kb * kBK, tc.b0 * BN);
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- UMMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = idesc_f16(kBM, BN, p.out_bf16 != 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const TileCoord tc = decode_tile(p, t);
+                if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout)) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * kAccStride;
+                for (int kb = tc.kb0; kb < tc.kb1; ++kb) {
+                    if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kStatusMmaTimeout)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint8_t* sa = smem + stage * kStageBytes;
+                    const uint64_t da = smem_desc_sw128(sa);
+                    const uint64_t db = smem_desc_sw128(sa + kATileBytes);
+#pragma unroll
+                    for (int k = 0; k < kBK / 16; ++k)   // 16 elements = 32 bytes = 2 descriptor units
+                        umma_f16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > tc.kb0 || k > 0) ? 1u : 0u);
+                    umma_commit(&empty_bar[stage]);
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok) break;
+                umma_commit(&tfull_bar[acc]);
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1;
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue (4 warps, 128 threads) ----------------
+        const int quad = warp & 3;
+        const int lrow = quad * 32 + lane;     // row inside the 128-row tile == TMEM lane
+        const int etid = (warp - 2) * 32 + lane;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+            const TileCoord tc = decode_tile(p, t);
+            const int b0 = tc.b0 * BN;
+            if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout)) break;
+            tc_fence_after_sync();
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kAccStride;
+            const int row = tc.a0 + lrow;
+            const bool row_ok = row < p.rows_a;
+            if (p.splits == 1) {
+#pragma unroll 1
+                for (int c = 0; c < kChunks; ++c) {
+                    float v[32];
+                    if constexpr (BN >= 32) {
+                        uint32_t r[32];
+                        tmem_ld_x32(t_addr + c * 32, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                    } else {
+                        uint32_t r[16];
+                        tmem_ld_x16(t_addr, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = j < 16 ? __uint_as_float(r[j & 15]) : 0.f;
+                    }
+                    const int col0 = b0 + c * 32;
+                    int nvalid = min(min(32, BN - c * 32), p.rows_b - col0);
+                    if (row_ok && nvalid > 0) {
+                        if (p.out_bf16) epilogue_store<__nv_bfloat16>(p, v, row, col0, nvalid);
+                        else epilogue_store<__half>(p, v, row, col0, nvalid);
+                    }
+                }
+                tc_fence_before_sync();
+                mbar_arrive(&tempty_bar[acc]);
+            } else {
+                // split-K: park the fp32 partial tile, the last split to arrive reduces all of them
+                float* wtile = p.ws + (static_cast<size_t>(tc.tile) * p.splits + tc.split) * (size_t)(BN * kBM);
+#pragma unroll 1
+                for (int c = 0; c < kChunks; ++c) {
+                    if constexpr (BN >= 32) {
+                        uint32_t r[32];
+                        tmem_ld_x32(t_addr + c * 32, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) wtile[(c * 32 + j) * kBM + lrow] = __uint_as_float(r[j]);
+                    } else {
+                        uint32_t r[16];
+                        tmem_ld_x16(t_addr, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) wtile[j * kBM + lrow] = __uint_as_float(r[j]);
+                    }
+                }
+                tc_fence_before_sync();
+                mbar_arrive(&tempty_bar[acc]);     // TMEM buffer is free again
+                __threadfence();
+                named_barrier_sync(1, 128);
+                if (etid == 0) {
+                    const int prev = atomicAdd(&p.counters[tc.tile], 1);
+                    const bool last = prev == p.splits - 1;
+                    if (last) p.counters[tc.tile] = 0;     // ready for the next launch / graph replay
+                    *last_flag = last ? 1u : 0u;
+                }
+                named_barrier_sync(1, 128);
+                const bool is_last = *last_flag != 0;
+                if (is_last) {
+                    __threadfence();
+                    const float* wbase = p.ws + static_cast<size_t>(tc.tile) * p.splits * (size_t)(BN * kBM);
+#pragma unroll 1
+                    for (int c = 0; c < kChunks; ++c) {
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = 0.f;
+                        const int ncol = min(32, BN - c * 32);
+                        for (int s = 0; s < p.splits; ++s) {
+                            const float* wt = wbase + static_cast<size_t>(s) * (BN * kBM);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (j < ncol) v[j] += __ldcg(&wt[(c * 32 + j) * kBM + lrow]);
+                        }
+                        const int col0 = b0 + c * 32;
+                        int nvalid = min(ncol, p.rows_b - col0);
+                        if (row_ok && nvalid > 0) {
+                            if (p.out_bf16) epilogue_store<__nv_bfloat16>(p, v, row, col0, nvalid);
+                            else epilogue_store<__half>(p, v, row, col0, nvalid);
+                        }
+                    }
+                }
+                named_barrier_sync(1, 128);    // last_flag may be rewritten only after everyone read it
+            }
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1;
+            }
+        }
+    }
+
+    // ---------------- common exit ----------------
+    if (*abort_flag) {
+        // Give copies that are still in flight time to land before shared memory is handed back.
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
+    constexpr int kStageBytes = kATileBytes + BN * kBK * 2;
+    constexpr int smem = STAGES * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc5_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return fail("cudaFuncSetAttribute(gemm_tc5)", e);
+        configured = true;
+    }
+    const int total = p.tiles_a * p.tiles_b * p.splits;
+    const int grid = total < sm_count() ? total : sm_count();
+    gemm_tc5_kernel<BN, STAGES><<<grid, kGemmThreads, smem, stream>>>(ta, tb, p);
+    TELB_CHECK_LAUNCH("gemm_tc5_kernel");
+    return 0;
+}
+
+}  // namespace telb
+
+using namespace telb;
+
+extern "C" const char* telb_last_error() { return g_last_error; }
+
+// out[M,N] = x[M,K] · w[N,K]^T  (16-bit row-major operands, K % 8 == 0).
+//   bias / alpha : per output column (may be null);  residual : [M,N] like out (may be null)
+//   ws / counters: split-K scratch, used only by the small-M path (ws_bytes may be 0 → no split)
+//   mode         : 0 = choose, 1 = force large-M layout, 2 = force swapped layout
+extern "C" int telb_gemm_f16(const void* x, const void* w, void* out, int M, int N, int K, const void* bias,
+                             const float* alpha, const void* residual, int is_bf16, void* ws, long long ws_bytes,
+                             int* counters, int n_counters, int* status, int mode, int force_splits,
+                             cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (K % 8) return fail("telb_gemm_f16: K must be a multiple of 8");
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return fail("telb_gemm_f16: operands must be 16-byte aligned");
+    const CUtensorMapDataType dt = is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const bool swapped = mode == 2 || (mode == 0 && M <= 128);
+    GemmParams p{};
+    p.k = K;
+    p.kb_total = (K + kBK - 1) / kBK;
+    p.c = out;
+    p.bias = bias;
+    p.alpha = alpha;
+    p.residual = residual;
+    p.out_bf16 = is_bf16;
+    p.ws = static_cast<float*>(ws);
+    p.counters = counters;
+    p.status = status;
+    CUtensorMap ta, tb;
+    int bn;
+    if (swapped) {
+        bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+        p.rows_a = N;
+        p.rows_b = M;
+        p.ldc_lane = 1;
+        p.ldc_col = N;
+        p.feat_on_lane = 1;
+        if (make_tmap_2d(&ta, dt, 2, w, N, K, (uint64_t)K * 2, kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+        if (make_tmap_2d(&tb, dt, 2, x, M, K, (uint64_t)K * 2, bn, kBK, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+    } else {
+        bn = (N >= 256) ? 256 : (N > 64 ? 128 : 64);
+        p.rows_a = M;
+        p.rows_b = N;
+        p.ldc_lane = N;
+        p.ldc_col = 1;
+        p.feat_on_lane = 0;
+        if (make_tmap_2d(&ta, dt, 2, x, M, K, (uint64_t)K * 2, kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+        if (make_tmap_2d(&tb, dt, 2, w, N, K, (uint64_t)K * 2, bn, kBK, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+    }
+    p.tiles_a = (p.rows_a + kBM - 1) / kBM;
+    p.tiles_b = (p.rows_b + bn - 1) / bn;
+    const int tiles = p.tiles_a * p.tiles_b;
+    int splits = 1;
+    if (swapped && ws && counters) {
+        const int want = force_splits > 0 ? force_splits : (2 * sm_count() + tiles - 1) / tiles;
+        const int max_by_k = p.kb_total / 4 > 0 ? p.kb_total / 4 : 1;
+        splits = want < max_by_k ? want : max_by_k;
+        if (force_splits > 0) splits = force_splits < p.kb_total ? force_splits : p.kb_total;
+        if (splits > 32) splits = 32;
+        while (splits > 1 && ((long long)tiles * splits * bn * kBM * 4 > ws_bytes || tiles > n_counters)) --splits;
+        if (splits < 1) splits = 1;
+    }
+    p.kb_per_split = (p.kb_total + splits - 1) / splits;
+    p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;   // no empty split
+    switch (bn) {
+        case 16: return launch_gemm<16, 8>(ta, tb, p, stream);
+        case 32: return launch_gemm<32, 8>(ta, tb, p, stream);
+        case 64: return launch_gemm<64, 8>(ta, tb, p, stream);
+        case 128: return launch_gemm<128, 6>(ta, tb, p, stream);
+        default: return launch_gemm<256, 4>(ta, tb, p, stream);
+    }
+}

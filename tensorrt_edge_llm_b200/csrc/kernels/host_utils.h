@@ -1,0 +1,104 @@
+// Host-side helpers for the kernel launchers: tensor-map encoding through the driver entry point
+// (no link-time dependency on libcuda), error reporting, device property cache.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+namespace telb {
+
+// Launchers return 0 on success or a negative code; the last message is kept per thread.
+inline thread_local char g_last_error[512] = {0};
+
+inline int fail(const char* what, cudaError_t e = cudaSuccess) {
+    if (e != cudaSuccess)
+        snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, cudaGetErrorString(e));
+    else
+        snprintf(g_last_error, sizeof(g_last_error), "%s", what);
+    return -1;
+}
+
+#define TELB_CHECK_LAUNCH(name)                                   \
+    do {                                                          \
+        cudaError_t e__ = cudaGetLastError();                     \
+        if (e__ != cudaSuccess) return ::telb::fail(name, e__);   \
+    } while (0)
+
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline PFN_encodeTiled encode_tiled_fn() {
+    static PFN_encodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_encodeTiled>(p);
+    }
+    return fn;
+}
+
+// Row-major 2-D tensor [rows, cols] of `elem_bytes` elements with row pitch `pitch_bytes`; box
+// [box_rows, box_cols].  box_cols * elem_bytes must equal the swizzle span for swizzled maps.
+inline int make_tmap_2d(CUtensorMap* out, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t rows,
+                        uint64_t cols, uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols,
+                        CUtensorMapSwizzle swz, CUtensorMapL2promotion l2 = CU_TENSOR_MAP_L2_PROMOTION_L2_256B) {
+    PFN_encodeTiled enc = encode_tiled_fn();
+    if (!enc) return fail("cuTensorMapEncodeTiled entry point not found");
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    (void)elem_bytes;
+    CUresult r = enc(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                     l2, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(g_last_error, sizeof(g_last_error),
+                 "cuTensorMapEncodeTiled(2d) failed: %d (base %p rows %llu cols %llu pitch %llu box %u x %u)", (int)r,
+                 base, (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)pitch_bytes, box_rows,
+                 box_cols);
+        return -1;
+    }
+    return 0;
+}
+
+// General N-D (N <= 5) map; dims / strides innermost first, strides[i] is the byte pitch of dim i+1.
+inline int make_tmap_nd(CUtensorMap* out, CUtensorMapDataType dt, int rank, const void* base, const uint64_t* dims,
+                        const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swz) {
+    PFN_encodeTiled enc = encode_tiled_fn();
+    if (!enc) return fail("cuTensorMapEncodeTiled entry point not found");
+    cuuint64_t d[5];
+    cuuint64_t s[4];
+    cuuint32_t b[5];
+    cuuint32_t e[5];
+    for (int i = 0; i < rank; ++i) {
+        d[i] = dims[i];
+        b[i] = box[i];
+        e[i] = 1;
+        if (i + 1 < rank) s[i] = strides_bytes[i];
+    }
+    CUresult r = enc(out, dt, rank, const_cast<void*>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled(%dd) failed: %d", rank, (int)r);
+        return -1;
+    }
+    return 0;
+}
+
+inline int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+}  // namespace telb

@@ -1,0 +1,219 @@
+"""ctypes binding of the native sm_100a kernel library (``_lib/libtelb_kernels.so``).
+
+Kernels are launched on the current torch CUDA stream with raw device pointers, so they are
+captured by ``torch.cuda.graph`` like any other launch.  A missing or stale library is an error:
+nothing in this module falls back to PyTorch on a GPU.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .meta import StepMeta
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_lib", "libtelb_kernels.so")
+_lib: Optional[ctypes.CDLL] = None
+
+c_int, c_ll, c_float, c_vp = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise RuntimeError(f"native kernel library not built: {_LIB_PATH} (run `python -m tensorrt_edge_llm_b200.build`)")
+        _lib = ctypes.CDLL(_LIB_PATH)
+        _lib.telb_last_error.restype = ctypes.c_char_p
+    return _lib
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed: {lib().telb_last_error().decode()}")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return c_vp(t.data_ptr()) if t is not None else c_vp(0)
+
+
+def _stream() -> c_vp:
+    return c_vp(torch.cuda.current_stream().cuda_stream)
+
+
+def _is_bf16(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return 1
+    if t.dtype == torch.float16:
+        return 0
+    raise TypeError(f"CUDA kernels take fp16 / bf16 activations, got {t.dtype}")
+
+
+class Workspace:
+    """Per-device scratch shared by kernels that need it: split-K partial tiles and their tile
+    counters (GEMM), split-KV partials (attention) and the status word every bounded wait reports
+    to.  Sized once; kernels fall back to un-split execution when a problem does not fit."""
+
+    _by_device: Dict[int, "Workspace"] = {}
+
+    def __init__(self, device: torch.device, gemm_bytes: int = 64 << 20, attn_floats: int = 32 << 20):
+        self.gemm_ws = torch.empty(gemm_bytes, dtype=torch.uint8, device=device)
+        self.counters = torch.zeros(8192, dtype=torch.int32, device=device)
+        self.attn_ws = torch.empty(attn_floats, dtype=torch.float32, device=device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+
+    @classmethod
+    def get(cls, device: torch.device) -> "Workspace":
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        ws = cls._by_device.get(idx)
+        if ws is None:
+            ws = cls._by_device[idx] = Workspace(torch.device("cuda", idx))
+        return ws
+
+    def check_status(self) -> None:
+        """Raise if any kernel recorded a timed-out wait (synchronises the device)."""
+        code = int(self.status[0].item())
+        if code != 0:
+            self.status.zero_()
+            names = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue", 4: "peer", 5: "bad argument"}
+            raise RuntimeError(f"kernel wait timed out in role: {names.get(code, code)}")
+
+
+# ------------------------------------------------------------------------------------------------
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    rows = x.numel() // x.shape[-1]
+    _check(lib().telb_rmsnorm(_p(x), c_vp(0), _p(weight), _p(y), c_vp(0), c_ll(rows), c_int(x.shape[-1]), c_float(eps),
+                              c_int(_is_bf16(x)), _stream()), "rmsnorm")
+    return y
+
+
+def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float
+                ) -> Tuple[torch.Tensor, torch.Tensor]:
+    x = x.contiguous()
+    residual = residual.contiguous()
+    y = torch.empty_like(x)
+    res = torch.empty_like(x)
+    rows = x.numel() // x.shape[-1]
+    _check(lib().telb_rmsnorm(_p(x), _p(residual), _p(weight), _p(y), _p(res), c_ll(rows), c_int(x.shape[-1]),
+                              c_float(eps), c_int(_is_bf16(x)), _stream()), "add_rmsnorm")
+    return y, res
+
+
+def gated_group_rmsnorm(x, z, weight, n_groups, eps):
+    x, z = x.contiguous(), z.contiguous()
+    y = torch.empty_like(x)
+    rows = x.numel() // x.shape[-1]
+    _check(lib().telb_gated_group_rmsnorm(_p(x), _p(z), _p(weight), _p(y), c_ll(rows), c_int(x.shape[-1]),
+                                          c_int(n_groups), c_float(eps), c_int(_is_bf16(x)), _stream()), "gated_group_rmsnorm")
+    return y
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    gate_up = gate_up.contiguous()
+    inter = gate_up.shape[-1] // 2
+    rows = gate_up.numel() // gate_up.shape[-1]
+    out = torch.empty(*gate_up.shape[:-1], inter, dtype=gate_up.dtype, device=gate_up.device)
+    _check(lib().telb_swiglu(_p(gate_up), _p(out), c_ll(rows), c_int(inter), c_int(_is_bf16(gate_up)), _stream()), "swiglu")
+    return out
+
+
+def relu2(x: torch.Tensor) -> torch.Tensor:
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    _check(lib().telb_relu2(_p(x), _p(out), c_ll(x.numel()), c_int(_is_bf16(x)), _stream()), "relu2")
+    return out
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    ids = ids.to(torch.int32).contiguous()
+    out = torch.empty(ids.numel(), table.shape[1], dtype=table.dtype, device=table.device)
+    _check(lib().telb_embedding(_p(ids), _p(table), _p(out), c_ll(ids.numel()), c_int(table.shape[1]),
+                                c_int(table.shape[0]), c_int(_is_bf16(table)), _stream()), "embedding")
+    return out
+
+
+def gemm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+         alpha: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+         out: Optional[torch.Tensor] = None, mode: int = 0, splits: int = 0) -> torch.Tensor:
+    """``out[M,N] = x[M,K] · weight[N,K]ᵀ (* alpha[N]) (+ bias[N]) (+ residual[M,N])`` on tcgen05."""
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    m, k = x2.shape
+    n = weight.shape[0]
+    if weight.dtype != x.dtype:
+        raise TypeError(f"gemm: activation {x.dtype} and weight {weight.dtype} differ")
+    if out is None:
+        out = torch.empty(m, n, dtype=x.dtype, device=x.device)
+    ws = Workspace.get(x.device)
+    _check(lib().telb_gemm_f16(_p(x2), _p(weight), _p(out), c_int(m), c_int(n), c_int(k), _p(bias), _p(alpha),
+                               _p(residual), c_int(_is_bf16(x)), _p(ws.gemm_ws), c_ll(ws.gemm_ws.numel()),
+                               _p(ws.counters), c_int(ws.counters.numel()), _p(ws.status), c_int(mode), c_int(splits),
+                               _stream()), "gemm")
+    return out.reshape(*lead, n)
+
+
+def rope_kv_write(qkv, kv_layer, meta: StepMeta, cos_sin, num_q_heads, num_kv_heads, head_dim,
+                  q_norm_w=None, k_norm_w=None, eps=1e-6) -> torch.Tensor:
+    qkv = qkv.contiguous()
+    t = qkv.shape[0]
+    q = torch.empty(t, num_q_heads, head_dim, dtype=qkv.dtype, device=qkv.device)
+    assert kv_layer.is_contiguous() and kv_layer.dtype == qkv.dtype
+    _check(lib().telb_rope_kv_write(
+        _p(qkv), _p(q), _p(kv_layer), _p(cos_sin), _p(meta.positions), _p(meta.seq_ids), _p(meta.q_start),
+        _p(meta.past_len), _p(meta.page_table), _p(meta.kv_offsets), _p(q_norm_w), _p(k_norm_w), c_int(t),
+        c_int(num_q_heads), c_int(num_kv_heads), c_int(head_dim), c_int(cos_sin.shape[-1]), c_int(meta.page_size),
+        c_int(meta.page_table.shape[1]), c_float(eps), c_int(_is_bf16(qkv)), _stream()), "rope_kv_write")
+    return q
+
+
+def _attn_splits(meta: StepMeta, hkv: int, group: int) -> int:
+    tq = 128 // group
+    qtiles = (meta.max_q_len + tq - 1) // tq
+    ctas = meta.num_seqs * hkv * qtiles
+    if ctas >= 148 or meta.max_q_len > 4 * tq:
+        return 1
+    kv_tiles = max(1, (meta.max_seq_len + 63) // 64)
+    return max(1, min((2 * 148 + ctas - 1) // ctas, kv_tiles, 32))
+
+
+def paged_attention(q, kv_layer, meta: StepMeta, scale, sliding_window=None, sinks=None, splits: Optional[int] = None
+                    ) -> torch.Tensor:
+    if sinks is not None:
+        raise NotImplementedError("attention sinks are not implemented in the CUDA kernel yet")
+    q = q.contiguous()
+    t, hq, d = q.shape
+    hkv = kv_layer.shape[2]
+    out = torch.empty_like(q)
+    ws = Workspace.get(q.device)
+    if splits is None:
+        splits = _attn_splits(meta, hkv, hq // hkv)
+    tm = meta.tree_mask
+    _check(lib().telb_paged_attention(
+        _p(q), _p(kv_layer), _p(out), _p(meta.q_start), _p(meta.q_len), _p(meta.past_len), _p(meta.page_table),
+        _p(tm), c_int(tm.shape[1] if tm is not None else 0), c_int(meta.num_seqs), c_int(t), c_int(meta.max_q_len),
+        c_int(kv_layer.shape[0]), c_int(meta.page_table.shape[1]), c_int(meta.page_size), c_int(hq), c_int(hkv),
+        c_int(d), c_float(scale), c_int(sliding_window or 0), c_int(splits), _p(ws.attn_ws), c_ll(ws.attn_ws.numel()),
+        c_int(_is_bf16(q)), _p(ws.status), _stream()), "paged_attention")
+    return out
+
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    assert logits.dim() == 2 and logits.stride(1) == 1
+    out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    dt = 2 if logits.dtype == torch.float32 else _is_bf16(logits)
+    _check(lib().telb_argmax(_p(logits), _p(out), c_ll(logits.shape[0]), c_int(logits.shape[1]),
+                             c_ll(logits.stride(0)), c_int(dt), _stream()), "argmax")
+    return out
+
+
+def sample(logits, temperature, top_k, top_p, uniforms):
+    from . import sampling_cuda
+    return sampling_cuda.sample(logits, temperature, top_k, top_p, uniforms)

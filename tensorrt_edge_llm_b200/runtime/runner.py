@@ -100,6 +100,29 @@ class ModelRunner:
                     out[i] = logits[row]
         return torch.stack(out)  # type: ignore[arg-type]
 
+    # ---- sampling --------------------------------------------------------------------------
+    def sample(self, logits: torch.Tensor, sp: SamplingParams, step: int = 0) -> torch.Tensor:
+        """Next token per row.  Greedy when ``temperature < 1e-3``; otherwise per-row top-k/top-p
+        with a counter-based uniform per (seed, row, step) so draws do not depend on batch position."""
+        if sp.temperature < 1e-3:
+            return ops.argmax(logits)
+        n = logits.shape[0]
+        g = torch.Generator(device="cpu").manual_seed(sp.seed * 1000003 + step)
+        u = torch.rand(n, generator=g).to(logits.device)
+        dev = logits.device
+        return ops.sample(logits, torch.full((n,), sp.temperature, device=dev), torch.full((n,), sp.top_k, device=dev, dtype=torch.int32),
+                          torch.full((n,), sp.top_p, device=dev), u)
+
+    @torch.no_grad()
+    def decode_sampled(self, seats, first_tokens, steps, sp: SamplingParams) -> torch.Tensor:
+        toks = first_tokens.to(torch.int32)
+        cols = []
+        for i in range(steps):
+            logits = self.step(seats, [[int(t)] for t in toks.tolist()])
+            toks = self.sample(logits, sp, step=i + 1)
+            cols.append(toks)
+        return torch.stack(cols, dim=1)
+
     # ---- decode ----------------------------------------------------------------------------
     @torch.no_grad()
     def decode_greedy(self, seats: Sequence[int], first_tokens: torch.Tensor, steps: int) -> torch.Tensor:

@@ -1,0 +1,196 @@
+"""Numerics of the sm_100a kernels against the plain-PyTorch fp32 statements of the same ops."""
+import math
+
+import pytest
+import torch
+
+from tensorrt_edge_llm_b200.ops import build_step_meta
+from tensorrt_edge_llm_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def cu():
+    from tensorrt_edge_llm_b200.ops import cuda
+    cuda.lib()
+    return cuda
+
+
+def _sync_check(cu):
+    torch.cuda.synchronize()
+    cu.Workspace.get(torch.device("cuda", 0)).check_status()
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,hidden", [(1, 4096), (7, 2048), (64, 4096), (3, 256), (5, 12288)])
+def test_rmsnorm(cu, dtype, rows, hidden):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(rows, hidden, device="cuda", generator=g).to(dtype)
+    r = torch.randn(rows, hidden, device="cuda", generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(hidden, device="cuda", generator=g)).to(dtype)
+    y = cu.rmsnorm(x, w, 1e-6)
+    assert _rel_err(y, ref.rmsnorm(x, w, 1e-6)) < 2e-3
+    y2, res = cu.add_rmsnorm(x, r, w, 1e-6)
+    y2r, resr = ref.add_rmsnorm(x, r, w, 1e-6)
+    assert torch.equal(res, resr)
+    assert _rel_err(y2, y2r) < 2e-3
+    _sync_check(cu)
+
+
+def test_swiglu_relu2_embedding_argmax(cu):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    gu = torch.randn(33, 2 * 1536, device="cuda", generator=g).bfloat16()
+    assert _rel_err(cu.swiglu(gu), ref.swiglu(gu)) < 4e-3
+    x = torch.randn(9, 1024, device="cuda", generator=g).bfloat16()
+    assert _rel_err(cu.relu2(x), ref.relu2(x)) < 4e-3
+    table = torch.randn(1000, 512, device="cuda", generator=g).bfloat16()
+    ids = torch.randint(0, 1000, (77,), device="cuda", generator=g, dtype=torch.int32)
+    assert torch.equal(cu.embedding(ids, table), table[ids.long()])
+    logits = torch.randn(5, 151936, device="cuda", generator=g).bfloat16()
+    assert torch.equal(cu.argmax(logits).long(), logits.float().argmax(-1))
+    lf = torch.randn(3, 32000, device="cuda", generator=g)
+    assert torch.equal(cu.argmax(lf).long(), lf.argmax(-1))
+    z = torch.randn(4, 1024, device="cuda", generator=g).bfloat16()
+    w = torch.randn(1024, device="cuda", generator=g).bfloat16()
+    assert _rel_err(cu.gated_group_rmsnorm(x[:4], z, w, 8, 1e-5), ref.gated_group_rmsnorm(x[:4], z, w, 8, 1e-5)) < 4e-3
+    _sync_check(cu)
+
+
+GEMM_SHAPES = [
+    # (M, N, K)  large-M layout
+    (256, 512, 256), (1024, 6144, 4096), (300, 1000, 512), (129, 320, 192), (4096, 4096, 4096),
+    # small-M (swapped, split-K) layout
+    (1, 4096, 4096), (8, 6144, 4096), (16, 4096, 12288), (33, 1024, 512), (64, 24576, 4096), (100, 4096, 4096),
+    (7, 151936, 4096),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
+def test_gemm(cu, dtype, m, n, k):
+    if dtype == torch.float16 and (m, n, k) not in [(256, 512, 256), (8, 6144, 4096), (129, 320, 192)]:
+        pytest.skip("fp16 covered on a subset")
+    g = torch.Generator(device="cuda").manual_seed(m * 7 + n)
+    x = (torch.randn(m, k, device="cuda", generator=g) * 0.5).to(dtype)
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.05).to(dtype)
+    y = cu.gemm(x, w)
+    torch.cuda.synchronize()
+    yr = x.float() @ w.float().t()
+    assert _rel_err(y, yr) < 6e-3, f"rel err {_rel_err(y, yr)}"
+    _sync_check(cu)
+
+
+def test_gemm_epilogue_and_modes(cu):
+    g = torch.Generator(device="cuda").manual_seed(5)
+    for m, mode in [(48, 2), (48, 1), (200, 1), (200, 2)]:
+        n, k = 768, 1024
+        x = (torch.randn(m, k, device="cuda", generator=g) * 0.5).bfloat16()
+        w = (torch.randn(n, k, device="cuda", generator=g) * 0.05).bfloat16()
+        b = torch.randn(n, device="cuda", generator=g).bfloat16()
+        a = torch.rand(n, device="cuda", generator=g) + 0.5
+        r = torch.randn(m, n, device="cuda", generator=g).bfloat16()
+        y = cu.gemm(x, w, bias=b, alpha=a, residual=r, mode=mode)
+        yr = (x.float() @ w.float().t()) * a + b.float() + r.float()
+        assert _rel_err(y, yr) < 6e-3, (m, mode, _rel_err(y, yr))
+    # repeated split-K launches reuse the self-resetting tile counters
+    x = (torch.randn(4, 4096, device="cuda", generator=g)).bfloat16()
+    w = (torch.randn(512, 4096, device="cuda", generator=g) * 0.05).bfloat16()
+    yr = x.float() @ w.float().t()
+    for s in (1, 4, 16, 4):
+        assert _rel_err(cu.gemm(x, w, splits=s), yr) < 6e-3
+    _sync_check(cu)
+
+
+def _paged_setup(q_lens, past_lens, hq, hkv, d, page, dtype, seed=0, extra_pages=3):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    n = len(q_lens)
+    max_pages = max((q + p + page - 1) // page for q, p in zip(q_lens, past_lens)) + 1
+    total_pages = n * max_pages + extra_pages
+    perm = torch.randperm(total_pages, generator=torch.Generator().manual_seed(seed))
+    table = torch.full((n, max_pages), -1, dtype=torch.int32)
+    k = 0
+    for s in range(n):
+        need = (q_lens[s] + past_lens[s] + page - 1) // page
+        table[s, :need] = perm[k:k + need].to(torch.int32)
+        k += need
+    kv = (torch.randn(total_pages, 2, hkv, page, d, device="cuda", generator=g)).to(dtype)
+    meta = build_step_meta(q_lens, past_lens, table, page, device="cuda")
+    t = sum(q_lens)
+    q = torch.randn(t, hq, d, device="cuda", generator=g).to(dtype)
+    return q, kv, meta
+
+
+ATTN_CASES = [
+    # q_lens, past_lens, hq, hkv, d, page
+    ([1], [100], 32, 8, 128, 64),
+    ([1, 1, 1], [5, 64, 700], 32, 8, 128, 64),
+    ([128], [0], 32, 8, 128, 64),
+    ([200, 37], [0, 91], 8, 2, 128, 64),
+    ([64, 1, 300], [64, 1000, 17], 16, 4, 128, 64),
+    ([70], [130], 4, 4, 128, 64),
+    ([33, 1], [10, 200], 8, 1, 64, 64),
+    ([150], [50], 32, 8, 128, 128),
+]
+
+
+@pytest.mark.parametrize("case", ATTN_CASES)
+def test_paged_attention(cu, case):
+    q_lens, past_lens, hq, hkv, d, page = case
+    q, kv, meta = _paged_setup(q_lens, past_lens, hq, hkv, d, page, torch.bfloat16, seed=len(q_lens))
+    scale = d ** -0.5
+    out = cu.paged_attention(q, kv, meta, scale)
+    torch.cuda.synchronize()
+    outr = ref.paged_attention(q, kv, meta, scale)
+    assert _rel_err(out, outr) < 1.5e-2, _rel_err(out, outr)
+    _sync_check(cu)
+
+
+def test_paged_attention_splits_window_tree(cu):
+    q, kv, meta = _paged_setup([1, 1], [900, 333], 32, 8, 128, 64, torch.bfloat16, seed=9)
+    scale = 128 ** -0.5
+    outr = ref.paged_attention(q, kv, meta, scale)
+    for s in (1, 2, 5, 16):
+        assert _rel_err(cu.paged_attention(q, kv, meta, scale, splits=s), outr) < 1.5e-2, s
+    q, kv, meta = _paged_setup([96, 1], [200, 500], 8, 2, 128, 64, torch.float16, seed=3)
+    outr = ref.paged_attention(q, kv, meta, scale, sliding_window=128)
+    assert _rel_err(cu.paged_attention(q, kv, meta, scale, sliding_window=128), outr) < 1.5e-2
+    # speculative tree: 12 new rows per sequence with a random ancestor mask (row sees itself)
+    q, kv, meta = _paged_setup([12, 12], [77, 300], 32, 8, 128, 64, torch.bfloat16, seed=4)
+    gm = torch.Generator().manual_seed(0)
+    bits = (torch.rand(24, 12, generator=gm) < 0.5) | torch.eye(12).repeat(2, 1).bool()
+    bits = torch.tril(bits.view(2, 12, 12)).view(24, 12)
+    words = (bits.long() << torch.arange(12)).sum(-1).to(torch.int32).view(24, 1)
+    meta.tree_mask = words.cuda()
+    outr = ref.paged_attention(q, kv, meta, scale)
+    assert _rel_err(cu.paged_attention(q, kv, meta, scale, splits=1), outr) < 1.5e-2
+    assert _rel_err(cu.paged_attention(q, kv, meta, scale, splits=3), outr) < 1.5e-2
+    _sync_check(cu)
+
+
+@pytest.mark.parametrize("qk_norm", [False, True])
+def test_rope_kv_write(cu, qk_norm):
+    hq, hkv, d, page = 8, 2, 128, 64
+    q_lens, past = [5, 1, 70], [0, 130, 60]
+    g = torch.Generator(device="cuda").manual_seed(2)
+    t = sum(q_lens)
+    n = len(q_lens)
+    table = torch.arange(n * 4, dtype=torch.int32).view(n, 4)
+    meta = build_step_meta(q_lens, past, table, page, device="cuda")
+    qkv = torch.randn(t, (hq + 2 * hkv) * d, device="cuda", generator=g).bfloat16()
+    cs = ref.rope_cos_sin(512, d, 1e6, device="cuda")
+    qw = (1 + 0.1 * torch.randn(d, device="cuda", generator=g)).bfloat16() if qk_norm else None
+    kw = (1 + 0.1 * torch.randn(d, device="cuda", generator=g)).bfloat16() if qk_norm else None
+    kv1 = torch.zeros(n * 4, 2, hkv, page, d, device="cuda", dtype=torch.bfloat16)
+    kv2 = kv1.clone()
+    q1 = cu.rope_kv_write(qkv, kv1, meta, cs, hq, hkv, d, qw, kw, 1e-6)
+    q2 = ref.rope_kv_write(qkv, kv2, meta, cs, hq, hkv, d, qw, kw, 1e-6)
+    assert _rel_err(q1, q2) < 6e-3
+    assert _rel_err(kv1, kv2) < 6e-3
+    assert torch.equal(kv1 == 0, kv2 == 0)
+    _sync_check(cu)
