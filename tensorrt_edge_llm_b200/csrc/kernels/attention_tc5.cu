@@ -385,30 +385,31 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     }
 }
 
-// Merge split partials: out = Σ_s 2^(lse_s - max) O_s / Σ_s 2^(lse_s - max).  One warp per (token, head).
+// Merge split partials: out = Σ_s 2^(lse_s - max) O_s / Σ_s 2^(lse_s - max).
+// One CTA of D threads per (token, head); splits (<= 32) are weighted by lanes of warp 0 first so
+// the D-wide accumulation issues all of its loads independently.
 template <int D, typename T>
 __global__ void attn_combine_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_lse, T* __restrict__ out,
                                     int total_rows /* T*Hq */, int splits) {
-    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (row >= total_rows) return;
-    float mx = -INFINITY;
-    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, ws_lse[(size_t)s * total_rows + row]);
-    float acc[D / 32];
+    __shared__ float w[32];
+    const int row = blockIdx.x;
+    const int d = threadIdx.x;
+    if (threadIdx.x < 32) {
+        const float l = threadIdx.x < splits ? ws_lse[(size_t)threadIdx.x * total_rows + row] : -INFINITY;
+        float mx = l;
 #pragma unroll
-    for (int i = 0; i < D / 32; ++i) acc[i] = 0.f;
-    float den = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float l = ws_lse[(size_t)s * total_rows + row];
-        const float w = (l == -INFINITY) ? 0.f : exp2f(l - mx);
-        den += w;
-        const float* o = ws_o + ((size_t)s * total_rows + row) * D;
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float e = (l == -INFINITY) ? 0.f : exp2f(l - mx);
+        float den = e;
 #pragma unroll
-        for (int i = 0; i < D / 32; ++i) acc[i] += w * o[i * 32 + lane];
+        for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+        w[threadIdx.x] = den > 0.f ? e / den : 0.f;
     }
-    const float inv = den > 0.f ? 1.f / den : 0.f;
-#pragma unroll
-    for (int i = 0; i < D / 32; ++i) out[(size_t)row * D + i * 32 + lane] = Cvt<T>::from_f(acc[i] * inv);
+    __syncthreads();
+    float acc = 0.f;
+#pragma unroll 8
+    for (int s = 0; s < splits; ++s) acc += w[s] * __ldcg(&ws_o[((size_t)s * total_rows + row) * D + d]);
+    out[(size_t)row * D + d] = Cvt<T>::from_f(acc);
 }
 
 template <int D, typename T>
@@ -426,7 +427,7 @@ static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tkv, const Attn
     TELB_CHECK_LAUNCH("attn_tc5_kernel");
     if (p.splits > 1) {
         const int rows = p.total_tokens * p.hq;
-        attn_combine_kernel<D, T><<<(rows + 7) / 8, 256, 0, stream>>>(p.ws_o, p.ws_lse, reinterpret_cast<T*>(p.out), rows, p.splits);
+        attn_combine_kernel<D, T><<<rows, D, 0, stream>>>(p.ws_o, p.ws_lse, reinterpret_cast<T*>(p.out), rows, p.splits);
         TELB_CHECK_LAUNCH("attn_combine_kernel");
     }
     return 0;

@@ -413,10 +413,79 @@ __global__ void argmax_f32_kernel(const float* __restrict__ logits, int* __restr
 }
 }  // namespace telb
 
-// dtype: 0 = fp16, 1 = bf16, 2 = fp32
+namespace telb {
+// Two-level arg-max for decode-size batches: `nblk` CTAs per row each reduce a slice and publish
+// a packed (order-preserving value bits, inverted index) key with atomicMax; the CTA that arrives
+// last at the row's counter writes the winning index and re-arms the scratch for the next launch.
+template <typename T>
+__global__ void argmax_split_kernel(const T* __restrict__ logits, int* __restrict__ out, int vocab, long long stride,
+                                    unsigned long long* __restrict__ keys, int* __restrict__ counters) {
+    __shared__ unsigned long long sk[32];
+    const int row = blockIdx.y;
+    const int nblk = gridDim.x;
+    const int per = (vocab + nblk - 1) / nblk;
+    const int lo = blockIdx.x * per, hi = min(vocab, lo + per);
+    const T* p = logits + row * stride;
+    unsigned long long best = 0ull;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        float v;
+        if constexpr (sizeof(T) == 4) v = (float)p[i]; else v = Cvt<T>::to_f(p[i]);
+        uint32_t u = __float_as_uint(v);
+        u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+        const unsigned long long key = ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)i);
+        best = key > best ? key : best;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+    }
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) sk[w] = best;
+    __syncthreads();
+    if (w == 0) {
+        const int nw = (blockDim.x + 31) >> 5;
+        best = l < nw ? sk[l] : 0ull;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+            best = other > best ? other : best;
+        }
+        if (l == 0) {
+            atomicMax(&keys[row], best);
+            __threadfence();
+            const int prev = atomicAdd(&counters[row], 1);
+            if (prev == nblk - 1) {
+                __threadfence();
+                const unsigned long long k = atomicExch(&keys[row], 0ull);
+                counters[row] = 0;
+                out[row] = (int)(0xFFFFFFFFu - (uint32_t)(k & 0xFFFFFFFFull));
+            }
+        }
+    }
+}
+template <> struct Cvt<float> {
+    static __device__ __forceinline__ float to_f(float v) { return v; }
+    static __device__ __forceinline__ float from_f(float v) { return v; }
+};
+}  // namespace telb
+
+// dtype: 0 = fp16, 1 = bf16, 2 = fp32.  `keys` (rows x u64, zeroed once) and `counters` (rows x int,
+// zeroed once) are scratch for the split form used when rows are few; pass null to force one CTA per row.
 extern "C" int telb_argmax(const void* logits, int* out, long long rows, int vocab, long long stride, int dtype,
-                           cudaStream_t stream) {
+                           void* keys, int* counters, int scratch_rows, cudaStream_t stream) {
     if (rows <= 0) return 0;
+    if (keys && counters && rows <= scratch_rows && rows * 8 <= 4 * 148 && vocab >= 8192) {
+        int nblk = (int)((2 * 148 + rows - 1) / rows);
+        if (nblk > 64) nblk = 64;
+        dim3 grid(nblk, (unsigned)rows);
+        unsigned long long* k = (unsigned long long*)keys;
+        if (dtype == 2) argmax_split_kernel<float><<<grid, 512, 0, stream>>>((const float*)logits, out, vocab, stride, k, counters);
+        else if (dtype == 1) argmax_split_kernel<__nv_bfloat16><<<grid, 512, 0, stream>>>((const __nv_bfloat16*)logits, out, vocab, stride, k, counters);
+        else argmax_split_kernel<__half><<<grid, 512, 0, stream>>>((const __half*)logits, out, vocab, stride, k, counters);
+        TELB_CHECK_LAUNCH("argmax_split_kernel");
+        return 0;
+    }
     if (dtype == 2) argmax_f32_kernel<<<(unsigned)rows, 1024, 0, stream>>>((const float*)logits, out, vocab, stride);
     else if (dtype == 1) argmax_kernel<__nv_bfloat16><<<(unsigned)rows, 1024, 0, stream>>>((const __nv_bfloat16*)logits, out, vocab, stride);
     else argmax_kernel<__half><<<(unsigned)rows, 1024, 0, stream>>>((const __half*)logits, out, vocab, stride);

@@ -1,0 +1,246 @@
+// Pieces shared by the tcgen05 GEMM kernels (16-bit and NVFP4): launch parameters, the persistent
+// tile order, and the epilogue that turns an fp32 accumulator row into 16-bit output with the
+// optional per-feature scale, bias and residual.
+#pragma once
+
+#include "host_utils.h"
+#include "tc5_common.cuh"
+
+namespace telb {
+
+struct GemmParams {
+    int rows_a, rows_b, k;
+    int splits, kb_per_split, kb_total;
+    int tiles_a, tiles_b;
+    void* c;
+    long long ldc_lane, ldc_col;
+    const void* bias;
+    const float* alpha;
+    const void* residual;
+    int feat_on_lane;
+    int out_bf16;
+    float* ws;
+    int* counters;
+    int* status;
+};
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;                       // 64 x 2 B = one 128-byte swizzle atom
+constexpr int kATileBytes = kBM * kBK * 2;    // 16 KiB
+constexpr int kGemmThreads = 192;
+constexpr int kRasterGroup = 8;
+
+struct TileCoord {
+    int a0, b0, kb0, kb1, tile, split;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int t) {
+    TileCoord c;
+    c.split = t % p.splits;
+    const int tt = t / p.splits;
+    const int per_group = kRasterGroup * p.tiles_b;
+    const int group = tt / per_group;
+    const int within = tt - group * per_group;
+    const int gfirst = group * kRasterGroup;
+    const int gsize = min(kRasterGroup, p.tiles_a - gfirst);
+    const int ta = gfirst + within % gsize;
+    const int tb = within / gsize;
+    c.tile = tb * p.tiles_a + ta;
+    c.a0 = ta * kBM;
+    c.kb0 = c.split * p.kb_per_split;
+    c.kb1 = min(p.kb_total, c.kb0 + p.kb_per_split);
+    c.b0 = tb;   // multiplied by BN by the caller
+    return c;
+}
+
+template <typename T>
+__device__ __forceinline__ void epilogue_store(const GemmParams& p, const float (&v)[32], int row, int col0,
+                                               int ncols_valid) {
+    // v[j] belongs to (row, col0 + j)
+    T* cptr = reinterpret_cast<T*>(p.c);
+    const T* rptr = reinterpret_cast<const T*>(p.residual);
+    const T* bptr = reinterpret_cast<const T*>(p.bias);
+    float o[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        float x = v[j];
+        if (j < ncols_valid) {
+            const int f = p.feat_on_lane ? row : (col0 + j);
+            if (p.alpha) x *= p.alpha[f];
+            if (bptr) x += Cvt<T>::to_f(bptr[f]);
+            if (rptr) x += Cvt<T>::to_f(rptr[row * p.ldc_lane + (long long)(col0 + j) * p.ldc_col]);
+        }
+        o[j] = x;
+    }
+    if (p.ldc_col == 1) {
+        T* dst = cptr + row * p.ldc_lane + col0;
+        const bool vec_ok = (ncols_valid == 32) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+        if (vec_ok) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint4 u;
+                u.x = Cvt<T>::pack2(o[q * 8 + 0], o[q * 8 + 1]);
+                u.y = Cvt<T>::pack2(o[q * 8 + 2], o[q * 8 + 3]);
+                u.z = Cvt<T>::pack2(o[q * 8 + 4], o[q * 8 + 5]);
+                u.w = Cvt<T>::pack2(o[q * 8 + 6], o[q * 8 + 7]);
+                reinterpret_cast<uint4*>(dst)[q] = u;
+            }
+        } else {
+            for (int j = 0; j < ncols_valid; ++j) dst[j] = Cvt<T>::from_f(o[j]);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (j < ncols_valid) cptr[row * p.ldc_lane + (long long)(col0 + j) * p.ldc_col] = Cvt<T>::from_f(o[j]);
+    }
+}
+
+
+
+// The epilogue role (warps 2-5, 128 threads): drains finished accumulators from TMEM.  Without
+// split-K each thread converts and stores its row.  With split-K it parks the fp32 partial row in
+// the workspace; the CTA that arrives last at the tile's counter sums all partials and stores.
+template <int BN>
+__device__ __forceinline__ void gemm_epilogue_role(const GemmParams& p, uint32_t tmem_base, uint64_t* tfull_bar,
+                                                   uint64_t* tempty_bar, volatile uint32_t* abort_flag,
+                                                   volatile uint32_t* last_flag, int total_tiles, int acc_stride) {
+    constexpr int kChunks = (BN + 31) / 32;
+    const int kAccStride = acc_stride;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int quad = warp & 3;
+    const int lrow = quad * 32 + lane;     // row inside the 128-row tile == TMEM lane
+    const int etid = (warp - 2) * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        const TileCoord tc = decode_tile(p, t);
+        const int b0 = tc.b0 * BN;
+        if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout)) break;
+        tc_fence_after_sync();
+        const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kAccStride;
+        const int row = tc.a0 + lrow;
+        const bool row_ok = row < p.rows_a;
+        if (p.splits == 1) {
+#pragma unroll 1
+            for (int c = 0; c < kChunks; ++c) {
+                float v[32];
+                if constexpr (BN >= 32) {
+                    uint32_t r[32];
+                    tmem_ld_x32(t_addr + c * 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                } else {
+                    uint32_t r[16];
+                    tmem_ld_x16(t_addr, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = j < 16 ? __uint_as_float(r[j & 15]) : 0.f;
+                }
+                const int col0 = b0 + c * 32;
+                int nvalid = min(min(32, BN - c * 32), p.rows_b - col0);
+                if (row_ok && nvalid > 0) {
+                    if (p.out_bf16) epilogue_store<__nv_bfloat16>(p, v, row, col0, nvalid);
+                    else epilogue_store<__half>(p, v, row, col0, nvalid);
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&tempty_bar[acc]);
+        } else {
+            // split-K: park the fp32 partial tile, the last split to arrive reduces all of them
+            float* wtile = p.ws + (static_cast<size_t>(tc.tile) * p.splits + tc.split) * (size_t)(BN * kBM);
+            float4* wrow = reinterpret_cast<float4*>(wtile + (size_t)lrow * BN);
+#pragma unroll 1
+            for (int c = 0; c < kChunks; ++c) {
+                if constexpr (BN >= 32) {
+                    uint32_t r[32];
+                    tmem_ld_x32(t_addr + c * 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        __stcg(&wrow[c * 8 + j], make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                             __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+                } else {
+                    uint32_t r[16];
+                    tmem_ld_x16(t_addr, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        __stcg(&wrow[j], make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                     __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&tempty_bar[acc]);     // TMEM buffer is free again
+            __threadfence();
+            named_barrier_sync(1, 128);
+            if (etid == 0) {
+                const int prev = atomicAdd(&p.counters[tc.tile], 1);
+                const bool last = prev == p.splits - 1;
+                if (last) p.counters[tc.tile] = 0;     // ready for the next launch / graph replay
+                *last_flag = last ? 1u : 0u;
+            }
+            named_barrier_sync(1, 128);
+            const bool is_last = *last_flag != 0;
+            if (is_last) {
+                __threadfence();
+                const float* wbase = p.ws + static_cast<size_t>(tc.tile) * p.splits * (size_t)(BN * kBM);
+#pragma unroll 1
+                for (int c = 0; c < kChunks; ++c) {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = 0.f;
+                    const int ncol = min(32, BN - c * 32);
+                    for (int s = 0; s < p.splits; ++s) {
+                        const float4* wt = reinterpret_cast<const float4*>(wbase + static_cast<size_t>(s) * (BN * kBM) +
+                                                                            (size_t)lrow * BN + c * 32);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            if (j * 4 < ncol) {
+                                const float4 f = __ldcg(&wt[j]);
+                                v[4 * j] += f.x;
+                                v[4 * j + 1] += f.y;
+                                v[4 * j + 2] += f.z;
+                                v[4 * j + 3] += f.w;
+                            }
+                        }
+                    }
+                    const int col0 = b0 + c * 32;
+                    int nvalid = min(ncol, p.rows_b - col0);
+                    if (row_ok && nvalid > 0) {
+                        if (p.out_bf16) epilogue_store<__nv_bfloat16>(p, v, row, col0, nvalid);
+                        else epilogue_store<__half>(p, v, row, col0, nvalid);
+                    }
+                }
+            }
+            named_barrier_sync(1, 128);    // last_flag may be rewritten only after everyone read it
+        }
+        if (++acc == 2) {
+            acc = 0;
+            acc_phase ^= 1;
+        }
+    }
+}
+
+// Split counts are chosen so the work-item total fills whole waves of SMs; each extra split costs
+// a little in the partial-tile reduction, hence the small penalty.
+inline int choose_splits(int tiles, int kb_total, int force_splits) {
+    if (force_splits > 0) return force_splits < kb_total ? force_splits : kb_total;
+    const int sms = sm_count();
+    const int max_s = kb_total / 2 < 16 ? (kb_total / 2 > 0 ? kb_total / 2 : 1) : 16;
+    float best = -1.f;
+    int splits = 1;
+    for (int s = 1; s <= max_s; ++s) {
+        const int items = tiles * s;
+        const int waves = (items + sms - 1) / sms;
+        const float score = (float)items / (float)(waves * sms) - 0.015f * s - 0.01f * waves;
+        if (score > best) {
+            best = score;
+            splits = s;
+        }
+    }
+    return splits;
+}
+
+}  // namespace telb

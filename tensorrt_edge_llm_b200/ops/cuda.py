@@ -30,9 +30,14 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
-def _check(rc: int, what: str) -> None:
+LAUNCHES = 0      # kernels of this library launched (or captured) so far in this process
+
+
+def _check(rc: int, what: str, n: int = 1) -> None:
+    global LAUNCHES
     if rc != 0:
         raise RuntimeError(f"{what} failed: {lib().telb_last_error().decode()}")
+    LAUNCHES += n
 
 
 def _p(t: Optional[torch.Tensor]):
@@ -63,6 +68,8 @@ class Workspace:
         self.counters = torch.zeros(8192, dtype=torch.int32, device=device)
         self.attn_ws = torch.empty(attn_floats, dtype=torch.float32, device=device)
         self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.argmax_keys = torch.zeros(256, dtype=torch.int64, device=device)
+        self.argmax_counters = torch.zeros(256, dtype=torch.int32, device=device)
 
     @classmethod
     def get(cls, device: torch.device) -> "Workspace":
@@ -201,7 +208,7 @@ def paged_attention(q, kv_layer, meta: StepMeta, scale, sliding_window=None, sin
         _p(tm), c_int(tm.shape[1] if tm is not None else 0), c_int(meta.num_seqs), c_int(t), c_int(meta.max_q_len),
         c_int(kv_layer.shape[0]), c_int(meta.page_table.shape[1]), c_int(meta.page_size), c_int(hq), c_int(hkv),
         c_int(d), c_float(scale), c_int(sliding_window or 0), c_int(splits), _p(ws.attn_ws), c_ll(ws.attn_ws.numel()),
-        c_int(_is_bf16(q)), _p(ws.status), _stream()), "paged_attention")
+        c_int(_is_bf16(q)), _p(ws.status), _stream()), "paged_attention", 2 if splits > 1 else 1)
     return out
 
 
@@ -209,11 +216,67 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     assert logits.dim() == 2 and logits.stride(1) == 1
     out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
     dt = 2 if logits.dtype == torch.float32 else _is_bf16(logits)
+    ws = Workspace.get(logits.device)
     _check(lib().telb_argmax(_p(logits), _p(out), c_ll(logits.shape[0]), c_int(logits.shape[1]),
-                             c_ll(logits.stride(0)), c_int(dt), _stream()), "argmax")
+                             c_ll(logits.stride(0)), c_int(dt), _p(ws.argmax_keys), _p(ws.argmax_counters),
+                             c_int(ws.argmax_keys.numel()), _stream()), "argmax")
     return out
 
 
 def sample(logits, temperature, top_k, top_p, uniforms):
     from . import sampling_cuda
     return sampling_cuda.sample(logits, temperature, top_k, top_p, uniforms)
+
+
+# ---- NVFP4 -----------------------------------------------------------------------------------
+
+
+def nvfp4_swizzle_scales(weight_scale: torch.Tensor) -> torch.Tensor:
+    """Row-major E4M3 block scales ``[rows, K/16]`` → the 512-byte atom layout the tensor core reads
+    (``[ceil(rows/128), K/64 padded to whole 256-element stages, 512]`` bytes)."""
+    sf = weight_scale.view(torch.uint8).contiguous()
+    rows, kb = sf.shape
+    k = kb * 16
+    L = lib()
+    L.telb_nvfp4_sf_bytes.restype = c_ll
+    nbytes = L.telb_nvfp4_sf_bytes(c_ll(rows), c_int(k))
+    out = torch.empty(nbytes, dtype=torch.uint8, device=sf.device)
+    _check(L.telb_nvfp4_swizzle_scales(_p(sf), _p(out), c_ll(rows), c_int(k), _stream()), "nvfp4_swizzle_scales")
+    return out
+
+
+def nvfp4_quantize(x: torch.Tensor, global_scale: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Quantise activations ``[M,K]`` to packed E2M1 ``[M,K/2]`` + atom-layout E4M3 scales."""
+    x = x.contiguous()
+    m, k = x.shape
+    L = lib()
+    L.telb_nvfp4_sf_bytes.restype = c_ll
+    nbytes = L.telb_nvfp4_sf_bytes(c_ll(m), c_int(k))
+    xq = torch.empty(m, k // 2, dtype=torch.uint8, device=x.device)
+    padded = (m % 128 != 0) or (k % 256 != 0)
+    sf = (torch.zeros if padded else torch.empty)(nbytes, dtype=torch.uint8, device=x.device)
+    _check(L.telb_nvfp4_quantize(_p(x), _p(xq), _p(sf), _p(global_scale), c_ll(m), c_int(k), c_int(_is_bf16(x)), _stream()),
+           "nvfp4_quantize")
+    return xq, sf
+
+
+def gemm_nvfp4(xq, x_sf, wq, w_sf, alpha, out_dtype, bias=None, residual=None, mode: int = 0, splits: int = 0):
+    m, n, k = xq.shape[0], wq.shape[0], xq.shape[1] * 2
+    out = torch.empty(m, n, dtype=out_dtype, device=xq.device)
+    ws = Workspace.get(xq.device)
+    _check(lib().telb_gemm_nvfp4(_p(xq), _p(x_sf), _p(wq), _p(w_sf), _p(out), c_int(m), c_int(n), c_int(k), _p(alpha),
+                                 _p(bias), _p(residual), c_int(1 if out_dtype == torch.bfloat16 else 0), _p(ws.gemm_ws),
+                                 c_ll(ws.gemm_ws.numel()), _p(ws.counters), c_int(ws.counters.numel()), _p(ws.status),
+                                 c_int(mode), c_int(splits), _stream()), "gemm_nvfp4")
+    return out
+
+
+def nvfp4_linear(x, weight, weight_sf_atoms, alpha, input_scale, bias=None, quantize_activations=True):
+    """NVFP4 linear: dynamic per-16 activation quantisation (calibrated global scale) + block-scaled GEMM."""
+    if not quantize_activations:
+        raise NotImplementedError("W4A16 NVFP4 runs through the W4A4 tensor-core path only when activations are quantised")
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    xq, x_sf = nvfp4_quantize(x2, input_scale)
+    out = gemm_nvfp4(xq, x_sf, weight, weight_sf_atoms, alpha, x.dtype, bias)
+    return out.reshape(*lead, weight.shape[0])

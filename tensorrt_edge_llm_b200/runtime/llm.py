@@ -69,6 +69,11 @@ class LLM:
                  ) -> List[RequestOutput]:
         """Generate for a batch of prompts (static batch: one prefill wave, then decode)."""
         sp = sampling_params or SamplingParams()
+        if isinstance(prompts, torch.Tensor):
+            outs = []
+            for b0 in range(0, prompts.shape[0], self.max_batch_size):
+                outs.extend(self._generate_batch(prompts[b0:b0 + self.max_batch_size], sp))
+            return outs
         ids = self._encode(prompts)
         outs: List[RequestOutput] = []
         for b0 in range(0, len(ids), self.max_batch_size):
@@ -85,7 +90,10 @@ class LLM:
                 raise ValueError(f"prompt of {len(p)} tokens exceeds max_input_len {self.max_input_len}")
             self.kv.reserve(s, len(p) + sp.max_tokens)
         t0 = time.perf_counter()
-        logits = self.runner.prefill(seats, ids)
+        if isinstance(ids, torch.Tensor):
+            logits = self.runner.prefill_tensor(seats, ids)      # pinned host tensor → one H2D copy per chunk
+        else:
+            logits = self.runner.prefill(seats, ids)
         first = self.runner.sample(logits, sp, step=0)
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
@@ -114,7 +122,8 @@ class LLM:
                         reason = "stop"
                         break
             text = self.tokenizer.decode(row) if self.tokenizer is not None else None
-            outs.append(RequestOutput(ids[i], row, text, reason, t1 - t0, t2 - t1))
+            outs.append(RequestOutput(ids[i].tolist() if isinstance(ids, torch.Tensor) else ids[i], row, text, reason,
+                                      t1 - t0, t2 - t1))
         for s in seats:
             self.kv.free(s)
         return outs

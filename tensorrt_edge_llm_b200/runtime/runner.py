@@ -60,7 +60,11 @@ class ModelRunner:
         q_lens = [len(t) for t in token_lists]
         meta = self._meta(seats, q_lens, logits_all, tree_mask, positions)
         flat = [t for ts in token_lists for t in ts]
-        ids = torch.tensor(flat, dtype=torch.int32, device=self.device)
+        if self.device.type == "cuda":
+            host = torch.tensor(flat, dtype=torch.int32).pin_memory()
+            ids = host.to(self.device, non_blocking=True)
+        else:
+            ids = torch.tensor(flat, dtype=torch.int32)
         logits = self.model(ids, meta, self.kv.pool)
         if commit:
             for s, q in zip(seats, q_lens):
@@ -99,6 +103,24 @@ class ModelRunner:
                 if fin:
                     out[i] = logits[row]
         return torch.stack(out)  # type: ignore[arg-type]
+
+    @torch.no_grad()
+    def prefill_tensor(self, seats: Sequence[int], ids: torch.Tensor) -> torch.Tensor:
+        """Prefill equal-length prompts given as one tensor ``[N, S]`` (pinned host or device
+        memory); chunks hold whole sequences.  Returns last-token logits ``[N, V]``."""
+        n, s_len = ids.shape
+        per = max(1, self.max_num_tokens // s_len)
+        outs = []
+        for b0 in range(0, n, per):
+            grp = list(seats[b0:b0 + per])
+            meta = self._meta(grp, [s_len] * len(grp))
+            chunk = ids[b0:b0 + per].reshape(-1)
+            if chunk.device != self.device:
+                chunk = chunk.to(self.device, non_blocking=True)
+            outs.append(self.model(chunk.to(torch.int32), meta, self.kv.pool))
+            for sidx in grp:
+                self.kv.commit(sidx, s_len)
+        return torch.cat(outs, dim=0)
 
     # ---- sampling --------------------------------------------------------------------------
     def sample(self, logits: torch.Tensor, sp: SamplingParams, step: int = 0) -> torch.Tensor:
@@ -215,11 +237,17 @@ class _DecodeGraph:
                 self._body()
             torch.cuda.current_stream(self.r.device).wait_stream(s)
             self._load_state(seats, first_tokens)
+            from ..ops import cuda as _cu
+            before = _cu.LAUNCHES
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 self._body()
             self.graph = g
+            self.launches_per_replay = _cu.LAUNCHES - before
+            _cu.LAUNCHES = before
             self._load_state(seats, first_tokens)
+        from ..ops import cuda as _cu
         for _ in range(steps):
             self.graph.replay()
+        _cu.LAUNCHES += steps * self.launches_per_replay
         return self.out[:steps].t().contiguous()
