@@ -1,0 +1,131 @@
+"""Per-kernel micro-benchmarks with roofline fractions.
+
+    python -m tensorrt_edge_llm_b200.benchmarks.kernel_bench gemm --dtype bf16 --shapes 8192x24576x4096 64x4096x4096
+    python -m tensorrt_edge_llm_b200.benchmarks.kernel_bench attention --batch 64 --past 1024 --q 1
+
+Timing: CUDA events on the launching stream, ``--warmup`` untimed runs, a 256 MiB buffer written
+between timed runs so nothing is served from L2 unless the kernel itself re-reads it.  Fractions
+are reported against ``MEASURED_PEAKS.json`` at the repository root when present ("of measured"),
+else against 6.65 TB/s and 1.59 PFLOP/s ("of fallback").
+
+Counterpart of the reference's kernel benchmark programs (``unittests`` perf modes and
+``examples/cpp/llm_bench.cpp``), restricted to single kernels.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+
+import torch
+
+
+def peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"] * 1e9, d["bf16_tflops"] * 1e12, "of measured"
+    return 6.65e12, 1.59e15, "of fallback"
+
+
+def time_fn(fn, warmup=3, iters=10, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.fill_(1)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e-3)
+    return statistics.median(ts), min(ts)
+
+
+def bench_gemm(args):
+    from ..ops import cuda as cu
+    from ..ops import reference as ref
+    bw, fl, tag = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for shp in args.shapes:
+        m, n, k = (int(v) for v in shp.lower().split("x"))
+        g = torch.Generator(device="cuda").manual_seed(0)
+        if args.dtype == "nvfp4":
+            x = torch.randn(m, k, device="cuda", generator=g).half()
+            wq = torch.randint(0, 256, (n, k // 2), device="cuda", generator=g, dtype=torch.uint8)
+            wsf = torch.randint(40, 60, (n, k // 16), device="cuda", generator=g, dtype=torch.uint8)
+            atoms = cu.nvfp4_swizzle_scales(wsf)
+            gs = torch.full((1,), 1.0 / 448, device="cuda")
+            alpha = torch.ones(n, device="cuda")
+            xq, xsf = cu.nvfp4_quantize(x, gs)
+            fn = lambda: cu.gemm_nvfp4(xq, xsf, wq, atoms, alpha, torch.float16)
+            wbytes = n * k * 0.5625
+            abytes = m * k * 0.5625
+        else:
+            dt = torch.bfloat16 if args.dtype == "bf16" else torch.float16
+            x = torch.randn(m, k, device="cuda", generator=g).to(dt)
+            w = (torch.randn(n, k, device="cuda", generator=g) * 0.05).to(dt)
+            fn = lambda: cu.gemm(x, w)
+            wbytes, abytes = n * k * 2, m * k * 2
+        med, best = time_fn(fn, args.warmup, args.iters, flush)
+        flops = 2.0 * m * n * k
+        byts = wbytes + abytes + m * n * 2
+        roof = max(flops / fl, byts / bw)
+        print(json.dumps({"kernel": f"gemm_{args.dtype}", "M": m, "N": n, "K": k, "median_us": round(med * 1e6, 2),
+                          "best_us": round(best * 1e6, 2), "tflops": round(flops / med / 1e12, 1),
+                          "gbs": round(byts / med / 1e9, 1), "roofline_us": round(roof * 1e6, 2),
+                          "fraction": round(roof / med, 3), "basis": tag + " (bf16 cuBLAS / copy)"}))
+    cu.Workspace.get(torch.device("cuda", 0)).check_status()
+
+
+def bench_attention(args):
+    from ..ops import build_step_meta
+    from ..ops import cuda as cu
+    bw, fl, tag = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    b, past, q = args.batch, args.past, args.q
+    hq, hkv, d, page = args.hq, args.hkv, 128, 64
+    pages_per = (past + q + page - 1) // page
+    table = torch.arange(b * pages_per, dtype=torch.int32).view(b, pages_per)
+    kv = torch.randn(b * pages_per, 2, hkv, page, d, device="cuda").bfloat16()
+    meta = build_step_meta([q] * b, [past] * b, table, page, device="cuda")
+    qt = torch.randn(b * q, hq, d, device="cuda").bfloat16()
+    fn = lambda: cu.paged_attention(qt, kv, meta, d ** -0.5)
+    med, best = time_fn(fn, args.warmup, args.iters, flush)
+    kv_bytes = b * (past + q) * hkv * d * 2 * 2
+    flops = 4.0 * b * hq * d * (q * past + q * (q + 1) / 2)
+    roof = max(flops / fl, kv_bytes / bw)
+    print(json.dumps({"kernel": "paged_attention", "batch": b, "past": past, "q": q, "median_us": round(med * 1e6, 2),
+                      "best_us": round(best * 1e6, 2), "kv_gbs": round(kv_bytes / med / 1e9, 1),
+                      "tflops": round(flops / med / 1e12, 1), "roofline_us": round(roof * 1e6, 2),
+                      "fraction": round(roof / med, 3), "basis": tag}))
+    cu.Workspace.get(torch.device("cuda", 0)).check_status()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "nvfp4"])
+    g.add_argument("--shapes", nargs="+", default=["8192x24576x4096", "8192x4096x12288", "64x24576x4096", "64x4096x4096", "1x4096x4096"])
+    a = sub.add_parser("attention")
+    a.add_argument("--batch", type=int, default=64)
+    a.add_argument("--past", type=int, default=1024)
+    a.add_argument("--q", type=int, default=1)
+    a.add_argument("--hq", type=int, default=32)
+    a.add_argument("--hkv", type=int, default=8)
+    for p in (g, a):
+        p.add_argument("--warmup", type=int, default=3)
+        p.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args()
+    {"gemm": bench_gemm, "attention": bench_attention}[args.cmd](args)
+
+
+if __name__ == "__main__":
+    main()

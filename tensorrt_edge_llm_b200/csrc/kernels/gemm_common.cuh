@@ -53,29 +53,53 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int t) {
     return c;
 }
 
+// One accumulator row chunk (32 fp32 values of row `row`, columns col0..col0+31) → 16-bit output.
+// All register arrays are indexed with compile-time constants only; the common case (a full,
+// 16-byte aligned chunk of a row-major output) moves everything with 128-bit accesses.
 template <typename T>
 __device__ __forceinline__ void epilogue_store(const GemmParams& p, const float (&v)[32], int row, int col0,
                                                int ncols_valid) {
-    // v[j] belongs to (row, col0 + j)
     T* cptr = reinterpret_cast<T*>(p.c);
     const T* rptr = reinterpret_cast<const T*>(p.residual);
     const T* bptr = reinterpret_cast<const T*>(p.bias);
-    float o[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-        float x = v[j];
-        if (j < ncols_valid) {
-            const int f = p.feat_on_lane ? row : (col0 + j);
-            if (p.alpha) x *= p.alpha[f];
-            if (bptr) x += Cvt<T>::to_f(bptr[f]);
-            if (rptr) x += Cvt<T>::to_f(rptr[row * p.ldc_lane + (long long)(col0 + j) * p.ldc_col]);
-        }
-        o[j] = x;
-    }
     if (p.ldc_col == 1) {
         T* dst = cptr + row * p.ldc_lane + col0;
-        const bool vec_ok = (ncols_valid == 32) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
-        if (vec_ok) {
+        const bool fast = (ncols_valid == 32) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) && ((col0 & 7) == 0);
+        if (fast) {
+            float o[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] = v[j];
+            if (p.alpha) {
+                const float4* ap = reinterpret_cast<const float4*>(p.alpha + col0);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const float4 a = __ldg(&ap[q]);
+                    o[4 * q] *= a.x;
+                    o[4 * q + 1] *= a.y;
+                    o[4 * q + 2] *= a.z;
+                    o[4 * q + 3] *= a.w;
+                }
+            }
+            if (bptr) {
+                const uint4* bp = reinterpret_cast<const uint4*>(bptr + col0);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const uint4 b = __ldg(&bp[q]);
+                    const T* e = reinterpret_cast<const T*>(&b);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) o[8 * q + i] += Cvt<T>::to_f(e[i]);
+                }
+            }
+            if (rptr) {
+                const uint4* rp = reinterpret_cast<const uint4*>(rptr + row * p.ldc_lane + col0);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const uint4 b = rp[q];
+                    const T* e = reinterpret_cast<const T*>(&b);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) o[8 * q + i] += Cvt<T>::to_f(e[i]);
+                }
+            }
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 uint4 u;
@@ -85,17 +109,28 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const float 
                 u.w = Cvt<T>::pack2(o[q * 8 + 6], o[q * 8 + 7]);
                 reinterpret_cast<uint4*>(dst)[q] = u;
             }
-        } else {
-            for (int j = 0; j < ncols_valid; ++j) dst[j] = Cvt<T>::from_f(o[j]);
+            return;
         }
-    } else {
+    }
+    // general path: per-element, fully unrolled and predicated (no runtime-indexed arrays)
+    const float a_lane = (p.alpha && p.feat_on_lane) ? __ldg(&p.alpha[row]) : 1.f;
+    const float b_lane = (bptr && p.feat_on_lane) ? Cvt<T>::to_f(bptr[row]) : 0.f;
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-            if (j < ncols_valid) cptr[row * p.ldc_lane + (long long)(col0 + j) * p.ldc_col] = Cvt<T>::from_f(o[j]);
+    for (int j = 0; j < 32; ++j) {
+        if (j < ncols_valid) {
+            float x = v[j];
+            if (p.feat_on_lane) {
+                x = x * a_lane + b_lane;
+            } else {
+                if (p.alpha) x *= __ldg(&p.alpha[col0 + j]);
+                if (bptr) x += Cvt<T>::to_f(bptr[col0 + j]);
+            }
+            const long long o = row * p.ldc_lane + (long long)(col0 + j) * p.ldc_col;
+            if (rptr) x += Cvt<T>::to_f(rptr[o]);
+            cptr[o] = Cvt<T>::from_f(x);
+        }
     }
 }
-
-
 
 // The epilogue role (warps 2-5, 128 threads): drains finished accumulators from TMEM.  Without
 // split-K each thread converts and stores its row.  With split-K it parks the fp32 partial row in

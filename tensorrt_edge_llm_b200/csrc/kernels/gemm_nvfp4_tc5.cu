@@ -283,6 +283,10 @@ __global__ void nvfp4_swizzle_sf_kernel(const uint8_t* __restrict__ in, uint8_t*
 
 using namespace telb;
 
+extern "C" int telb_gemm_skinny(int kind, const void* x, const void* x_sf, const void* w, const void* w_sf, void* out, int M,
+                                int N, int K, const float* alpha, const void* bias, const void* residual, int is_bf16,
+                                int* status, int force_ranks, cudaStream_t stream);
+
 // Number of 64-element K groups the scale buffers are padded to (whole 256-element stages).
 extern "C" int telb_nvfp4_k64_pad(int k) { return ((k + 255) / 256) * 4; }
 
@@ -330,6 +334,8 @@ extern "C" int telb_gemm_nvfp4(const void* xq, const void* x_sf, const void* wq,
                                cudaStream_t stream) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (K % 32) return fail("telb_gemm_nvfp4: K must be a multiple of 32");
+    if (mode == 0 && M <= 128)
+        return telb_gemm_skinny(1, xq, x_sf, wq, w_sf, out, M, N, K, alpha, bias, residual, out_bf16, status, 0, stream);
     const bool swapped = mode == 2 || (mode == 0 && M <= 128);
     GemmParams p{};
     p.k = K;

@@ -168,6 +168,10 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
 
 using namespace telb;
 
+extern "C" int telb_gemm_skinny(int kind, const void* x, const void* x_sf, const void* w, const void* w_sf, void* out, int M,
+                                int N, int K, const float* alpha, const void* bias, const void* residual, int is_bf16,
+                                int* status, int force_ranks, cudaStream_t stream);
+
 extern "C" const char* telb_last_error() { return g_last_error; }
 
 // out[M,N] = x[M,K] · w[N,K]^T  (16-bit row-major operands, K % 8 == 0).
@@ -181,6 +185,8 @@ extern "C" int telb_gemm_f16(const void* x, const void* w, void* out, int M, int
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (K % 8) return fail("telb_gemm_f16: K must be a multiple of 8");
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return fail("telb_gemm_f16: operands must be 16-byte aligned");
+    if (mode == 0 && M <= 128)
+        return telb_gemm_skinny(0, x, nullptr, w, nullptr, out, M, N, K, alpha, bias, residual, is_bf16, status, 0, stream);
     const CUtensorMapDataType dt = is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const bool swapped = mode == 2 || (mode == 0 && M <= 128);
     GemmParams p{};

@@ -280,3 +280,19 @@ def nvfp4_linear(x, weight, weight_sf_atoms, alpha, input_scale, bias=None, quan
     xq, x_sf = nvfp4_quantize(x2, input_scale)
     out = gemm_nvfp4(xq, x_sf, weight, weight_sf_atoms, alpha, x.dtype, bias)
     return out.reshape(*lead, weight.shape[0])
+
+
+def gemm_skinny(x, weight, *, x_sf=None, w_sf=None, alpha=None, bias=None, residual=None, out_dtype=None, ranks: int = 0):
+    """Decode-size GEMM (M <= 128) with an explicit cluster size (``ranks`` K-slices; 0 = choose).
+    16-bit operands when no scale tensors are given, NVFP4 otherwise."""
+    kind = 1 if w_sf is not None else 0
+    m = x.shape[0]
+    n = weight.shape[0]
+    k = x.shape[1] * (2 if kind else 1)
+    dt = out_dtype or x.dtype
+    out = torch.empty(m, n, dtype=dt, device=x.device)
+    ws = Workspace.get(x.device)
+    _check(lib().telb_gemm_skinny(c_int(kind), _p(x), _p(x_sf), _p(weight), _p(w_sf), _p(out), c_int(m), c_int(n), c_int(k),
+                                  _p(alpha), _p(bias), _p(residual), c_int(1 if dt == torch.bfloat16 else 0), _p(ws.status),
+                                  c_int(ranks), _stream()), "gemm_skinny")
+    return out

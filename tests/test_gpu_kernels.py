@@ -226,3 +226,60 @@ def test_gemm_nvfp4(cu, m, n, k):
     y2 = cu.gemm_nvfp4(xr_q, cu.nvfp4_swizzle_scales(xr_sf), wq, w_atoms, alpha, torch.float16)
     assert _rel_err(y2, yr) < 3e-3, _rel_err(y2, yr)
     _sync_check(cu)
+
+
+@pytest.mark.parametrize("m,n,k,ranks", [(1, 4096, 4096, 0), (1, 512, 1024, 1), (8, 6144, 4096, 3), (16, 4096, 12288, 8),
+                                         (33, 1000, 512, 2), (64, 24576, 4096, 0), (100, 4096, 4096, 5), (128, 2048, 2048, 4),
+                                         (7, 151936, 4096, 0), (64, 4096, 4096, 8)])
+def test_gemm_skinny_bf16(cu, m, n, k, ranks):
+    g = torch.Generator(device="cuda").manual_seed(m + n)
+    x = (torch.randn(m, k, device="cuda", generator=g) * 0.5).bfloat16()
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.05).bfloat16()
+    b = torch.randn(n, device="cuda", generator=g).bfloat16()
+    a = torch.rand(n, device="cuda", generator=g) + 0.5
+    r = torch.randn(m, n, device="cuda", generator=g).bfloat16()
+    y = cu.gemm_skinny(x, w, alpha=a, bias=b, residual=r, ranks=ranks)
+    yr = (x.float() @ w.float().t()) * a + b.float() + r.float()
+    assert _rel_err(y, yr) < 6e-3, _rel_err(y, yr)
+    assert _rel_err(cu.gemm_skinny(x, w, ranks=ranks), x.float() @ w.float().t()) < 6e-3
+    _sync_check(cu)
+
+
+@pytest.mark.parametrize("m,n,k,ranks", [(1, 4096, 4096, 0), (8, 6144, 4096, 2), (64, 4096, 12288, 8), (33, 1024, 512, 0),
+                                         (128, 2048, 2048, 4), (64, 24576, 4096, 0), (16, 2048, 768, 3)])
+def test_gemm_skinny_nvfp4(cu, m, n, k, ranks):
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    x = torch.randn(m, k, device="cuda", generator=g).half()
+    w = torch.randn(n, k, device="cuda", generator=g) * 0.05
+    wq, wsf, wgs = ref.nvfp4_quantize(w)
+    gs_x = (x.float().abs().amax() / (6 * 448)).reshape(())
+    xq, xsf, _ = ref.nvfp4_quantize(x, gs_x)
+    yr = ref.nvfp4_dequantize(xq, xsf, gs_x) @ ref.nvfp4_dequantize(wq, wsf, wgs).t()
+    alpha = (wgs * gs_x).expand(n).contiguous()
+    y = cu.gemm_skinny(xq, wq, x_sf=cu.nvfp4_swizzle_scales(xsf), w_sf=cu.nvfp4_swizzle_scales(wsf), alpha=alpha,
+                       out_dtype=torch.float16, ranks=ranks)
+    assert _rel_err(y, yr) < 3e-3, _rel_err(y, yr)
+    _sync_check(cu)
+
+
+def test_skinny_chain_in_cuda_graph(cu):
+    """Back-to-back decode GEMMs launched with programmatic dependent launch, captured and replayed."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = (torch.randn(8, 1024, device="cuda", generator=g) * 0.5).bfloat16()
+    w1 = (torch.randn(2048, 1024, device="cuda", generator=g) * 0.05).bfloat16()
+    w2 = (torch.randn(1024, 2048, device="cuda", generator=g) * 0.05).bfloat16()
+    yr = ((x.float() @ w1.float().t()).bfloat16().float() @ w2.float().t())
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        y = cu.gemm(cu.gemm(x, w1), w2)
+    torch.cuda.current_stream().wait_stream(s)
+    assert _rel_err(y, yr) < 1e-2
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y2 = cu.gemm(cu.gemm(x, w1), w2)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert _rel_err(y2, yr) < 1e-2
+    _sync_check(cu)
