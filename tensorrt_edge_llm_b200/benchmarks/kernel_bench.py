@@ -30,10 +30,23 @@ def peaks():
     return 6.65e12, 1.59e15, "of fallback"
 
 
-def time_fn(fn, warmup=3, iters=10, flush=None):
+def time_fn(fn, warmup=3, iters=10, flush=None, graph_reps=0):
+    """Median / best seconds per call.  ``graph_reps > 0`` captures that many back-to-back calls in
+    a CUDA graph and times the replay (per-call GPU time without host launch cost, but with the
+    operands L2-warm after the first call: use it for latency-bound decode-size kernels)."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
+    if graph_reps > 0:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(graph_reps):
+                fn()
+        inner = fn
+        fn = g.replay
+        scale = 1.0 / graph_reps
+    else:
+        scale = 1.0
     ts = []
     for _ in range(iters):
         if flush is not None:
@@ -44,7 +57,7 @@ def time_fn(fn, warmup=3, iters=10, flush=None):
         fn()
         e1.record()
         torch.cuda.synchronize()
-        ts.append(e0.elapsed_time(e1) * 1e-3)
+        ts.append(e0.elapsed_time(e1) * 1e-3 * scale)
     return statistics.median(ts), min(ts)
 
 
@@ -73,7 +86,7 @@ def bench_gemm(args):
             w = (torch.randn(n, k, device="cuda", generator=g) * 0.05).to(dt)
             fn = lambda: cu.gemm(x, w)
             wbytes, abytes = n * k * 2, m * k * 2
-        med, best = time_fn(fn, args.warmup, args.iters, flush)
+        med, best = time_fn(fn, args.warmup, args.iters, flush, args.graph if m <= 128 else 0)
         flops = 2.0 * m * n * k
         byts = wbytes + abytes + m * n * 2
         roof = max(flops / fl, byts / bw)
@@ -97,7 +110,7 @@ def bench_attention(args):
     meta = build_step_meta([q] * b, [past] * b, table, page, device="cuda")
     qt = torch.randn(b * q, hq, d, device="cuda").bfloat16()
     fn = lambda: cu.paged_attention(qt, kv, meta, d ** -0.5)
-    med, best = time_fn(fn, args.warmup, args.iters, flush)
+    med, best = time_fn(fn, args.warmup, args.iters, flush, args.graph if q <= 4 else 0)
     kv_bytes = b * (past + q) * hkv * d * 2 * 2
     flops = 4.0 * b * hq * d * (q * past + q * (q + 1) / 2)
     roof = max(flops / fl, kv_bytes / bw)
@@ -123,6 +136,7 @@ def main():
     for p in (g, a):
         p.add_argument("--warmup", type=int, default=3)
         p.add_argument("--iters", type=int, default=10)
+        p.add_argument("--graph", type=int, default=0, help="time decode-size calls as N captured launches per replay")
     args = ap.parse_args()
     {"gemm": bench_gemm, "attention": bench_attention}[args.cmd](args)
 

@@ -437,6 +437,23 @@ static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tkv, const Attn
 
 using namespace telb;
 
+// Merge `splits` partial results (ws_o [splits, rows, d] fp32, ws_lse [splits, rows]) into out [rows, d].
+extern "C" int telb_attn_combine(const float* ws_o, const float* ws_lse, void* out, int rows, int splits, int d, int is_bf16,
+                                 cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (d == 128) {
+        if (is_bf16) attn_combine_kernel<128, __nv_bfloat16><<<rows, 128, 0, stream>>>(ws_o, ws_lse, (__nv_bfloat16*)out, rows, splits);
+        else attn_combine_kernel<128, __half><<<rows, 128, 0, stream>>>(ws_o, ws_lse, (__half*)out, rows, splits);
+    } else if (d == 64) {
+        if (is_bf16) attn_combine_kernel<64, __nv_bfloat16><<<rows, 64, 0, stream>>>(ws_o, ws_lse, (__nv_bfloat16*)out, rows, splits);
+        else attn_combine_kernel<64, __half><<<rows, 64, 0, stream>>>(ws_o, ws_lse, (__half*)out, rows, splits);
+    } else {
+        return fail("telb_attn_combine: head_dim must be 64 or 128");
+    }
+    TELB_CHECK_LAUNCH("attn_combine_kernel");
+    return 0;
+}
+
 // q [T,Hq,D], kv_layer [pages,2,Hkv,P,D], out [T,Hq,D]; metadata as in the ragged step ABI.
 // ws must hold splits*T*Hq*(D+1) floats when splits > 1 (pass splits = 1 to avoid scratch).
 extern "C" int telb_paged_attention(const void* q, const void* kv_layer, void* out, const int* q_start,

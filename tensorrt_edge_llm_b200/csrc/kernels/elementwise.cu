@@ -155,9 +155,105 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
 }
 
 // RoPE + optional per-head RMSNorm on q and k + paged KV write.
-// grid (T, Hq + 2*Hkv), block D/2 threads: thread i owns features i and i + D/2.
-// qkv is token-major packed [T, (Hq + 2 Hkv) * D]; q_out is [T, Hq, D]; the cache layer is
-// [pages, 2, Hkv, P, D].
+// One warp per (token, head); lane l owns E = D/64 consecutive features of each half of the head
+// (rotate-half pairs are (i, i + D/2)), so every access is a contiguous E*2-byte vector and the
+// head-wide sum of squares is a warp shuffle.  Requires rot_dim == D (full rotary) and D in
+// {64, 128, 256}; other shapes use the generic kernel below.
+// qkv is token-major packed [T, (Hq + 2 Hkv) * D]; q_out is [T, Hq, D]; cache layer [pages, 2, Hkv, P, D].
+template <typename T, int E>
+__global__ void rope_kv_write_warp_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ kv_layer,
+                                          const float* __restrict__ cos_sin, const int* __restrict__ positions,
+                                          const int* __restrict__ seq_ids, const int* __restrict__ q_start,
+                                          const int* __restrict__ past_len, const int* __restrict__ page_table,
+                                          const int* __restrict__ kv_offsets, const T* __restrict__ q_norm_w,
+                                          const T* __restrict__ k_norm_w, int tokens, int hq, int hkv, int page_size,
+                                          int max_pages, float eps) {
+    constexpr int D = E * 64;
+    constexpr int half = D / 2;
+    const int heads = hq + 2 * hkv;
+    const long long wid = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= (long long)tokens * heads) return;
+    const int t = (int)(wid / heads);
+    const int h = (int)(wid - (long long)t * heads);
+    const T* src = qkv + ((size_t)t * heads + h) * D;
+    float a[E], b[E];
+    {
+        T va[E], vb[E];
+        if constexpr (E == 2) {
+            *reinterpret_cast<uint32_t*>(va) = *reinterpret_cast<const uint32_t*>(src + lane * E);
+            *reinterpret_cast<uint32_t*>(vb) = *reinterpret_cast<const uint32_t*>(src + half + lane * E);
+        } else if constexpr (E == 4) {
+            *reinterpret_cast<uint2*>(va) = *reinterpret_cast<const uint2*>(src + lane * E);
+            *reinterpret_cast<uint2*>(vb) = *reinterpret_cast<const uint2*>(src + half + lane * E);
+        } else {
+            va[0] = src[lane];
+            vb[0] = src[half + lane];
+        }
+#pragma unroll
+        for (int i = 0; i < E; ++i) {
+            a[i] = Cvt<T>::to_f(va[i]);
+            b[i] = Cvt<T>::to_f(vb[i]);
+        }
+    }
+    const bool is_q = h < hq;
+    const bool is_k = !is_q && h < hq + hkv;
+    const T* nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+    if (nw) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < E; ++i) ss += a[i] * a[i] + b[i] * b[i];
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / D + eps);
+#pragma unroll
+        for (int i = 0; i < E; ++i) {
+            a[i] = Cvt<T>::to_f(Cvt<T>::from_f(Cvt<T>::to_f(Cvt<T>::from_f(a[i] * inv)) * Cvt<T>::to_f(nw[lane * E + i])));
+            b[i] = Cvt<T>::to_f(Cvt<T>::from_f(Cvt<T>::to_f(Cvt<T>::from_f(b[i] * inv)) * Cvt<T>::to_f(nw[half + lane * E + i])));
+        }
+    }
+    if (is_q || is_k) {
+        const float* cs = cos_sin + (size_t)positions[t] * D;
+#pragma unroll
+        for (int i = 0; i < E; ++i) {
+            const float c = cs[lane * E + i], sn = cs[half + lane * E + i];
+            const float ra = a[i] * c - b[i] * sn;
+            const float rb = b[i] * c + a[i] * sn;
+            a[i] = ra;
+            b[i] = rb;
+        }
+    }
+    T* dst;
+    if (is_q) {
+        dst = q_out + ((size_t)t * hq + h) * D;
+    } else {
+        const int s = seq_ids[t];
+        const int off = kv_offsets ? kv_offsets[t] : (t - q_start[s]);
+        const int slot = past_len[s] + off;
+        const int page = page_table[(size_t)s * max_pages + slot / page_size];
+        if (page < 0) return;      // unreserved page: skip instead of writing out of bounds
+        const int kvh = is_k ? h - hq : h - hq - hkv;
+        dst = kv_layer + ((((size_t)page * 2 + (is_k ? 0 : 1)) * hkv + kvh) * page_size + slot % page_size) * D;
+    }
+    T oa[E], ob[E];
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+        oa[i] = Cvt<T>::from_f(a[i]);
+        ob[i] = Cvt<T>::from_f(b[i]);
+    }
+    if constexpr (E == 2) {
+        *reinterpret_cast<uint32_t*>(dst + lane * E) = *reinterpret_cast<uint32_t*>(oa);
+        *reinterpret_cast<uint32_t*>(dst + half + lane * E) = *reinterpret_cast<uint32_t*>(ob);
+    } else if constexpr (E == 4) {
+        *reinterpret_cast<uint2*>(dst + lane * E) = *reinterpret_cast<uint2*>(oa);
+        *reinterpret_cast<uint2*>(dst + half + lane * E) = *reinterpret_cast<uint2*>(ob);
+    } else {
+        dst[lane] = oa[0];
+        dst[half + lane] = ob[0];
+    }
+}
+
+// Generic form (any even head_dim <= 512, partial rotary): grid (T, Hq + 2*Hkv), block D/2 threads,
+// thread i owns features i and i + D/2.
 template <typename T>
 __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ kv_layer,
                                      const float* __restrict__ cos_sin, const int* __restrict__ positions,
@@ -358,6 +454,17 @@ extern "C" int telb_rope_kv_write(const void* qkv, void* q_out, void* kv_layer, 
                                   int max_pages, float eps, int is_bf16, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (d % 2 || d > 512) return fail("telb_rope_kv_write: head_dim must be even and <= 512");
+    if (rot_dim == d && (d == 64 || d == 128 || d == 256)) {
+        const long long warps = (long long)tokens * (hq + 2 * hkv);
+        const int blocks = (int)((warps + 7) / 8);
+        DISPATCH_T(is_bf16, {
+            if (d == 128) rope_kv_write_warp_kernel<T, 2><<<blocks, 256, 0, stream>>>((const T*)qkv, (T*)q_out, (T*)kv_layer, cos_sin, positions, seq_ids, q_start, past_len, page_table, kv_offsets, (const T*)q_norm_w, (const T*)k_norm_w, tokens, hq, hkv, page_size, max_pages, eps);
+            else if (d == 64) rope_kv_write_warp_kernel<T, 1><<<blocks, 256, 0, stream>>>((const T*)qkv, (T*)q_out, (T*)kv_layer, cos_sin, positions, seq_ids, q_start, past_len, page_table, kv_offsets, (const T*)q_norm_w, (const T*)k_norm_w, tokens, hq, hkv, page_size, max_pages, eps);
+            else rope_kv_write_warp_kernel<T, 4><<<blocks, 256, 0, stream>>>((const T*)qkv, (T*)q_out, (T*)kv_layer, cos_sin, positions, seq_ids, q_start, past_len, page_table, kv_offsets, (const T*)q_norm_w, (const T*)k_norm_w, tokens, hq, hkv, page_size, max_pages, eps);
+        })
+        TELB_CHECK_LAUNCH("rope_kv_write_warp_kernel");
+        return 0;
+    }
     dim3 grid(tokens, hq + 2 * hkv);
     DISPATCH_T(is_bf16, {
         rope_kv_write_kernel<T><<<grid, d / 2, 0, stream>>>((const T*)qkv, (T*)q_out, (T*)kv_layer, cos_sin, positions, seq_ids, q_start,

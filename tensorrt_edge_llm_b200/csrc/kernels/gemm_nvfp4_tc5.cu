@@ -18,9 +18,8 @@
 // scale repack of cpp/kernels/multiDeviceKernels/scaleConvert.cu; the activation quantiser below
 // corresponds to cpp/kernels/moe/fp4SupportKernels/fp4Quantize.cu and the math of
 // tensorrt_edgellm/models/ops.py:826-909.
-#include <cuda_fp8.h>
-
 #include "gemm_common.cuh"
+#include "nvfp4_common.cuh"
 
 namespace telb {
 
@@ -210,19 +209,6 @@ static int launch_nvfp4(const CUtensorMap& ta, const CUtensorMap& tb, const uint
 // ---- activation quantiser ---------------------------------------------------------------------
 // x [M,K] 16-bit → packed E2M1 [M,K/2] + UE4M3 scales in the atom layout ([ceil(M/128)][k64_pad][512]).
 // One thread per 16-element block.  scale = e4m3(amax / 6 / global), value = rn_e2m1(x / (scale*global)).
-__device__ __forceinline__ uint32_t pack_e2m1x8(const float (&v)[8]) {
-    uint32_t out = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        uint16_t b;
-        // cvt packs {a → high nibble, b → low nibble}; the even element must land in the low nibble
-        asm volatile("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u16.u8 %0, t;\n\t}"
-                     : "=h"(b) : "f"(v[2 * i + 1]), "f"(v[2 * i]));
-        out |= static_cast<uint32_t>(b & 0xFF) << (8 * i);
-    }
-    return out;
-}
-
 template <typename T>
 __global__ void nvfp4_quantize_kernel(const T* __restrict__ x, uint8_t* __restrict__ xq, uint8_t* __restrict__ sf,
                                       const float* __restrict__ global_scale, long long rows, int k, int k64_pad) {
@@ -246,23 +232,10 @@ __global__ void nvfp4_quantize_kernel(const T* __restrict__ x, uint8_t* __restri
             v[8 + i] = Cvt<T>::to_f(e1[i]);
             amax = fmaxf(amax, fmaxf(fabsf(v[i]), fabsf(v[8 + i])));
         }
-        const float s = fminf(amax * (1.f / 6.f) * inv_gs, 448.f);
-        const __nv_fp8_storage_t s8 = __nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3);
-        const float sf_f = __half2float(__half(__nv_cvt_fp8_to_halfraw(s8, __NV_E4M3))) * gs;
-        const float inv = sf_f > 0.f ? 1.f / sf_f : 0.f;
-        float a[8], b[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            a[i] = v[i] * inv;
-            b[i] = v[8 + i] * inv;
-        }
-        uint2 packed;
-        packed.x = pack_e2m1x8(a);
-        packed.y = pack_e2m1x8(b);
+        uint8_t s8;
+        const uint2 packed = nvfp4_quantize_block16(v, amax, gs, inv_gs, s8);
         *reinterpret_cast<uint2*>(xq + r * (k / 2) + kb * 8) = packed;
-        const int rr = (int)(r & 127);
-        const size_t off = ((size_t)(r >> 7) * k64_pad + (kb >> 2)) * 512 + (rr & 31) * 16 + (rr >> 5) * 4 + (kb & 3);
-        sf[off] = s8;
+        sf[sf_atom_offset(r, kb, k64_pad)] = s8;
     }
 }
 
@@ -274,8 +247,7 @@ __global__ void nvfp4_swizzle_sf_kernel(const uint8_t* __restrict__ in, uint8_t*
          idx += (long long)gridDim.x * blockDim.x) {
         const long long r = idx / kblocks;
         const int kb = (int)(idx - r * kblocks);
-        const int rr = (int)(r & 127);
-        out[((size_t)(r >> 7) * k64_pad + (kb >> 2)) * 512 + (rr & 31) * 16 + (rr >> 5) * 4 + (kb & 3)] = in[idx];
+        out[sf_atom_offset(r, kb, k64_pad)] = in[idx];
     }
 }
 

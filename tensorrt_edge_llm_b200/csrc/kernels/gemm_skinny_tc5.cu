@@ -43,11 +43,14 @@ __device__ __forceinline__ uint32_t cluster_rank() {
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
 }
-__device__ __forceinline__ float ld_dsmem_f32(uint32_t local_smem_addr, uint32_t rank) {
+// 16-byte load from the same shared-memory offset in CTA `rank` of the cluster.  Not volatile: the
+// loads of one reduction step are independent and must be free to overlap; ordering against the
+// producers is provided by the cluster barriers around the reduction.
+__device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_smem_addr, uint32_t rank) {
     uint32_t remote;
-    float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    float4 v;
+    asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(rank));
+    asm("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote));
     return v;
 }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
@@ -83,6 +86,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     uint64_t* tfull_bar = empty_bar + STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tfull_bar + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    float* s_alpha = reinterpret_cast<float*>(tmem_slot + 4);      // per-feature scale / bias of this 128-row tile
+    float* s_bias = s_alpha + kBM;
     float* red = reinterpret_cast<float*>(smem);          // aliases the stage ring once the main loop is done
 
     const int warp = threadIdx.x >> 5;
@@ -204,6 +209,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         if (p.alpha) alpha = __ldg(&p.alpha[feat]);
         if (p.bias) bias = Cvt<T>::to_f(reinterpret_cast<const T*>(p.bias)[feat]);
     }
+    if (is_epi) {
+        s_alpha[lrow] = alpha;
+        s_bias[lrow] = bias;
+    }
     bool have_acc = false;
     if (is_epi && nkb > 0) {
         have_acc = mbar_wait(tfull_bar, 0, abort_flag, p.status, kStatusEpilogueTimeout);
@@ -253,21 +262,50 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
             }
         }
         cluster_sync_all();
-        // 2. reduce my slice of the token columns across the cluster
+        // 2. reduce my slice of the token columns across the cluster: one work item is (token column,
+        //    four consecutive features); its `ranks` 16-byte peer loads are issued together.
         if (is_epi) {
             pdl_wait();
+            const int etid = (warp - 2) * 32 + lane;
             const int mcols = min(BN, p.m_tok);
             const int per = (mcols + p.ranks - 1) / p.ranks;
             const int c_lo = rank * per, c_hi = min(mcols, c_lo + per);
-            for (int c = c_lo; c < c_hi; ++c) {
-                const uint32_t addr = smem_u32(&red[c * kBM + lrow]);
-                float v = 0.f;
-                for (int rk = 0; rk < p.ranks; ++rk) v += ld_dsmem_f32(addr, rk);
-                if (feat_ok) {
-                    v = v * alpha + bias;
-                    const size_t o = (size_t)c * p.n_out + feat;
-                    if (resp) v += Cvt<T>::to_f(resp[o]);
-                    outp[o] = Cvt<T>::from_f(v);
+            const int items = max(0, c_hi - c_lo) * 32;
+            const bool vec_out = (p.n_out & 3) == 0;
+            for (int it = etid; it < items; it += 128) {
+                const int c = c_lo + (it >> 5);
+                const int fg = (it & 31) * 4;
+                const uint32_t addr = smem_u32(&red[c * kBM + fg]);
+                float4 part[8];
+#pragma unroll
+                for (int rk = 0; rk < 8; ++rk)
+                    part[rk] = rk < p.ranks ? ld_dsmem_f32x4(addr, rk) : make_float4(0.f, 0.f, 0.f, 0.f);
+                float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int rk = 0; rk < 8; ++rk) {
+                    v[0] += part[rk].x;
+                    v[1] += part[rk].y;
+                    v[2] += part[rk].z;
+                    v[3] += part[rk].w;
+                }
+                const int f0 = a0 + fg;
+                const size_t o = (size_t)c * p.n_out + f0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (f0 + i < p.n_out) {
+                        v[i] = v[i] * s_alpha[fg + i] + s_bias[fg + i];
+                        if (resp) v[i] += Cvt<T>::to_f(resp[o + i]);
+                    }
+                }
+                if (vec_out && f0 + 3 < p.n_out) {
+                    uint2 u;
+                    u.x = Cvt<T>::pack2(v[0], v[1]);
+                    u.y = Cvt<T>::pack2(v[2], v[3]);
+                    *reinterpret_cast<uint2*>(outp + o) = u;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (f0 + i < p.n_out) outp[o + i] = Cvt<T>::from_f(v[i]);
                 }
             }
         }
@@ -289,7 +327,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
 template <int KIND, int BN, typename T>
 static int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const SkinnyParams& p, cudaStream_t stream) {
     using Cfg = SkinnyCfg<KIND, BN>;
-    constexpr int smem = Cfg::kSmemData + 1024 + 256;
+    constexpr int smem = Cfg::kSmemData + 1024 + 256 + 2 * kBM * 4;
     static bool configured = false;
     auto kern = gemm_skinny_kernel<KIND, BN, T>;
     if (!configured) {

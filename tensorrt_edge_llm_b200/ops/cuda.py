@@ -191,18 +191,44 @@ def _attn_splits(meta: StepMeta, hkv: int, group: int) -> int:
     return max(1, min((2 * 148 + ctas - 1) // ctas, kv_tiles, 32))
 
 
-def paged_attention(q, kv_layer, meta: StepMeta, scale, sliding_window=None, sinks=None, splits: Optional[int] = None
-                    ) -> torch.Tensor:
+def _decode_splits(meta: StepMeta, hkv: int) -> int:
+    ctas = meta.num_seqs * hkv
+    if ctas >= 148:
+        return 1
+    tiles = max(1, (meta.max_seq_len + 127) // 128)
+    return max(1, min((148 + ctas - 1) // ctas, tiles, 32))
+
+
+def paged_attention(q, kv_layer, meta: StepMeta, scale, sliding_window=None, sinks=None, splits: Optional[int] = None,
+                    kernel: Optional[str] = None) -> torch.Tensor:
+    """Paged GQA attention.  Decode-shaped steps (``max_q_len * Hq/Hkv <= 16``, head_dim 128, causal)
+    run the token-major XQA-style kernel; everything else the row-major tile kernel.
+    ``kernel`` forces ``"decode"`` or ``"tile"``."""
     if sinks is not None:
         raise NotImplementedError("attention sinks are not implemented in the CUDA kernel yet")
     q = q.contiguous()
     t, hq, d = q.shape
     hkv = kv_layer.shape[2]
+    group = hq // hkv
     out = torch.empty_like(q)
     ws = Workspace.get(q.device)
-    if splits is None:
-        splits = _attn_splits(meta, hkv, hq // hkv)
     tm = meta.tree_mask
+    decode_ok = (tm is None and d == 128 and meta.max_q_len * group <= 16 and 16 % group == 0)
+    use_decode = decode_ok if kernel is None else (kernel == "decode")
+    if use_decode:
+        if not decode_ok:
+            raise ValueError("step is not decode-shaped")
+        if splits is None:
+            splits = _decode_splits(meta, hkv)
+        _check(lib().telb_paged_attention_decode(
+            _p(q), _p(kv_layer), _p(out), _p(meta.q_start), _p(meta.q_len), _p(meta.past_len), _p(meta.page_table),
+            c_int(meta.num_seqs), c_int(t), c_int(meta.max_q_len), c_int(kv_layer.shape[0]), c_int(meta.page_table.shape[1]),
+            c_int(meta.page_size), c_int(hq), c_int(hkv), c_int(d), c_float(scale), c_int(sliding_window or 0), c_int(splits),
+            _p(ws.attn_ws), c_ll(ws.attn_ws.numel()), c_int(_is_bf16(q)), _p(ws.status), _stream()),
+            "paged_attention_decode", 2 if splits > 1 else 1)
+        return out
+    if splits is None:
+        splits = _attn_splits(meta, hkv, group)
     _check(lib().telb_paged_attention(
         _p(q), _p(kv_layer), _p(out), _p(meta.q_start), _p(meta.q_len), _p(meta.past_len), _p(meta.page_table),
         _p(tm), c_int(tm.shape[1] if tm is not None else 0), c_int(meta.num_seqs), c_int(t), c_int(meta.max_q_len),

@@ -144,10 +144,34 @@ def test_paged_attention(cu, case):
     q_lens, past_lens, hq, hkv, d, page = case
     q, kv, meta = _paged_setup(q_lens, past_lens, hq, hkv, d, page, torch.bfloat16, seed=len(q_lens))
     scale = d ** -0.5
-    out = cu.paged_attention(q, kv, meta, scale)
+    out = cu.paged_attention(q, kv, meta, scale, kernel="tile")
     torch.cuda.synchronize()
     outr = ref.paged_attention(q, kv, meta, scale)
     assert _rel_err(out, outr) < 1.5e-2, _rel_err(out, outr)
+    _sync_check(cu)
+
+
+DECODE_CASES = [
+    # q_lens, past_lens, hq, hkv, page
+    ([1], [100], 32, 8, 64), ([1, 1, 1], [5, 64, 700], 32, 8, 64), ([1] * 9, [0, 1, 63, 64, 127, 128, 129, 1000, 2047], 32, 8, 64),
+    ([2, 1, 4], [10, 300, 77], 16, 4, 64), ([1, 1], [200, 31], 8, 8, 64), ([1, 1], [500, 90], 16, 1, 64),
+    ([1, 3], [150, 260], 32, 8, 128), ([1, 1], [900, 333], 4, 2, 64),
+]
+
+
+@pytest.mark.parametrize("case", DECODE_CASES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_paged_attention_decode_kernel(cu, case, dtype):
+    q_lens, past_lens, hq, hkv, page = case
+    q, kv, meta = _paged_setup(q_lens, past_lens, hq, hkv, 128, page, dtype, seed=sum(past_lens))
+    scale = 128 ** -0.5
+    outr = ref.paged_attention(q, kv, meta, scale)
+    for s in (1, 3):
+        out = cu.paged_attention(q, kv, meta, scale, kernel="decode", splits=s)
+        torch.cuda.synchronize()
+        assert _rel_err(out, outr) < 1.5e-2, (s, _rel_err(out, outr))
+    outw = cu.paged_attention(q, kv, meta, scale, kernel="decode", sliding_window=100)
+    assert _rel_err(outw, ref.paged_attention(q, kv, meta, scale, sliding_window=100)) < 1.5e-2
     _sync_check(cu)
 
 
@@ -156,7 +180,7 @@ def test_paged_attention_splits_window_tree(cu):
     scale = 128 ** -0.5
     outr = ref.paged_attention(q, kv, meta, scale)
     for s in (1, 2, 5, 16):
-        assert _rel_err(cu.paged_attention(q, kv, meta, scale, splits=s), outr) < 1.5e-2, s
+        assert _rel_err(cu.paged_attention(q, kv, meta, scale, splits=s, kernel="tile"), outr) < 1.5e-2, s
     q, kv, meta = _paged_setup([96, 1], [200, 500], 8, 2, 128, 64, torch.float16, seed=3)
     outr = ref.paged_attention(q, kv, meta, scale, sliding_window=128)
     assert _rel_err(cu.paged_attention(q, kv, meta, scale, sliding_window=128), outr) < 1.5e-2
