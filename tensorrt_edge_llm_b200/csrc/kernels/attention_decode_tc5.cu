@@ -80,6 +80,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     volatile uint32_t* abort_flag = tmem_slot + 1;
     float* s_red = reinterpret_cast<float*>(tmem_slot + 4);     // [2 parities][4 warps][16] column maxima, then sums
 
+    pdl_prologue();          // step metadata and Q/KV are produced by earlier kernels
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int kvh = blockIdx.x;
@@ -374,7 +375,7 @@ static int launch_decode(const CUtensorMap& tq, const CUtensorMap& tkv, const De
         configured = true;
     }
     dim3 grid(p.hkv, nseq * p.splits);
-    attn_decode_kernel<D, T><<<grid, kDecThreads, smem, stream>>>(tq, tkv, p);
+    TELB_LAUNCH("attn_decode_kernel", (attn_decode_kernel<D, T>), dim3(grid), dim3(kDecThreads), smem, stream, tq, tkv, p);
     TELB_CHECK_LAUNCH("attn_decode_kernel");
     return 0;
 }

@@ -95,6 +95,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_bar + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
+    pdl_prologue();          // step metadata and Q/KV are produced by earlier kernels
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int qt = blockIdx.x;
@@ -391,6 +392,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
 template <int D, typename T>
 __global__ void attn_combine_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_lse, T* __restrict__ out,
                                     int total_rows /* T*Hq */, int splits) {
+    pdl_prologue();
     __shared__ float w[32];
     const int row = blockIdx.x;
     const int d = threadIdx.x;
@@ -423,11 +425,11 @@ static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tkv, const Attn
         configured = true;
     }
     dim3 grid(qtiles, p.hkv, nseq * p.splits);
-    attn_tc5_kernel<D, T><<<grid, kAttnThreads, smem, stream>>>(tq, tkv, p);
+    TELB_LAUNCH("attn_tc5_kernel", (attn_tc5_kernel<D, T>), dim3(grid), dim3(kAttnThreads), smem, stream, tq, tkv, p);
     TELB_CHECK_LAUNCH("attn_tc5_kernel");
     if (p.splits > 1) {
         const int rows = p.total_tokens * p.hq;
-        attn_combine_kernel<D, T><<<rows, D, 0, stream>>>(p.ws_o, p.ws_lse, reinterpret_cast<T*>(p.out), rows, p.splits);
+        TELB_LAUNCH("attn_combine_kernel", (attn_combine_kernel<D, T>), dim3(rows), dim3(D), 0, stream, p.ws_o, p.ws_lse, reinterpret_cast<T*>(p.out), rows, p.splits);
         TELB_CHECK_LAUNCH("attn_combine_kernel");
     }
     return 0;
@@ -442,11 +444,11 @@ extern "C" int telb_attn_combine(const float* ws_o, const float* ws_lse, void* o
                                  cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (d == 128) {
-        if (is_bf16) attn_combine_kernel<128, __nv_bfloat16><<<rows, 128, 0, stream>>>(ws_o, ws_lse, (__nv_bfloat16*)out, rows, splits);
-        else attn_combine_kernel<128, __half><<<rows, 128, 0, stream>>>(ws_o, ws_lse, (__half*)out, rows, splits);
+        if (is_bf16) TELB_LAUNCH("attn_combine_kernel", (attn_combine_kernel<128, __nv_bfloat16>), dim3(rows), dim3(128), 0, stream, ws_o, ws_lse, (__nv_bfloat16*)out, rows, splits);
+        else TELB_LAUNCH("attn_combine_kernel", (attn_combine_kernel<128, __half>), dim3(rows), dim3(128), 0, stream, ws_o, ws_lse, (__half*)out, rows, splits);
     } else if (d == 64) {
-        if (is_bf16) attn_combine_kernel<64, __nv_bfloat16><<<rows, 64, 0, stream>>>(ws_o, ws_lse, (__nv_bfloat16*)out, rows, splits);
-        else attn_combine_kernel<64, __half><<<rows, 64, 0, stream>>>(ws_o, ws_lse, (__half*)out, rows, splits);
+        if (is_bf16) TELB_LAUNCH("attn_combine_kernel", (attn_combine_kernel<64, __nv_bfloat16>), dim3(rows), dim3(64), 0, stream, ws_o, ws_lse, (__nv_bfloat16*)out, rows, splits);
+        else TELB_LAUNCH("attn_combine_kernel", (attn_combine_kernel<64, __half>), dim3(rows), dim3(64), 0, stream, ws_o, ws_lse, (__half*)out, rows, splits);
     } else {
         return fail("telb_attn_combine: head_dim must be 64 or 128");
     }

@@ -41,6 +41,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 template <typename T, int kMaxVec>
 __global__ void rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ w,
                                T* __restrict__ y, T* __restrict__ res_out, int hidden, float eps) {
+    pdl_prologue();
     __shared__ float red[32];
     const size_t row = blockIdx.x;
     const int nvec = hidden / 8;
@@ -88,6 +89,7 @@ __global__ void rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ re
 template <typename T>
 __global__ void gated_group_rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ z, const T* __restrict__ w,
                                            T* __restrict__ y, int hidden, int gsize, float eps) {
+    pdl_prologue();
     __shared__ float red[32];
     const size_t row = blockIdx.x;
     const int g = blockIdx.y;
@@ -111,6 +113,7 @@ __global__ void gated_group_rmsnorm_kernel(const T* __restrict__ x, const T* __r
 // out[t, i] = silu(in[t, i]) * in[t, inter + i]
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, long long rows, int inter) {
+    pdl_prologue();
     const long long nvec = rows * (inter / 8);
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < nvec;
          idx += (long long)gridDim.x * blockDim.x) {
@@ -130,6 +133,7 @@ __global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, lon
 
 template <typename T>
 __global__ void relu2_kernel(const T* __restrict__ in, T* __restrict__ out, long long n) {
+    pdl_prologue();
     for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8; i < n;
          i += (long long)gridDim.x * blockDim.x * 8) {
         Vec8<T> v, o;
@@ -146,6 +150,7 @@ __global__ void relu2_kernel(const T* __restrict__ in, T* __restrict__ out, long
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table, T* __restrict__ out,
                                  int hidden, int vocab) {
+    pdl_prologue();
     const size_t row = blockIdx.x;
     int id = ids[row];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
@@ -168,6 +173,7 @@ __global__ void rope_kv_write_warp_kernel(const T* __restrict__ qkv, T* __restri
                                           const int* __restrict__ kv_offsets, const T* __restrict__ q_norm_w,
                                           const T* __restrict__ k_norm_w, int tokens, int hq, int hkv, int page_size,
                                           int max_pages, float eps) {
+    pdl_prologue();
     constexpr int D = E * 64;
     constexpr int half = D / 2;
     const int heads = hq + 2 * hkv;
@@ -262,6 +268,7 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, T* __restrict__ 
                                      const int* __restrict__ kv_offsets, const T* __restrict__ q_norm_w,
                                      const T* __restrict__ k_norm_w, int hq, int hkv, int d, int rot_dim, int page_size,
                                      int max_pages, float eps) {
+    pdl_prologue();
     __shared__ float red[32];
     const int t = blockIdx.x;
     const int h = blockIdx.y;
@@ -330,6 +337,7 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, T* __restrict__ 
 // arg-max over the vocabulary, one CTA per row (ties → lowest index).
 template <typename T>
 __global__ void argmax_kernel(const T* __restrict__ logits, int* __restrict__ out, int vocab, long long stride) {
+    pdl_prologue();
     __shared__ float sv[32];
     __shared__ int si[32];
     const T* p = logits + blockIdx.x * stride;
@@ -397,10 +405,10 @@ extern "C" int telb_rmsnorm(const void* x, const void* residual, const void* w, 
     const int per = (nvec + threads - 1) / threads;
     if (per > 8) return fail("telb_rmsnorm: hidden too large (max 32768)");
     DISPATCH_T(is_bf16, {
-        if (per <= 1) rmsnorm_kernel<T, 1><<<rows, threads, 0, stream>>>((const T*)x, (const T*)residual, (const T*)w, (T*)y, (T*)res_out, hidden, eps);
-        else if (per <= 2) rmsnorm_kernel<T, 2><<<rows, threads, 0, stream>>>((const T*)x, (const T*)residual, (const T*)w, (T*)y, (T*)res_out, hidden, eps);
-        else if (per <= 4) rmsnorm_kernel<T, 4><<<rows, threads, 0, stream>>>((const T*)x, (const T*)residual, (const T*)w, (T*)y, (T*)res_out, hidden, eps);
-        else rmsnorm_kernel<T, 8><<<rows, threads, 0, stream>>>((const T*)x, (const T*)residual, (const T*)w, (T*)y, (T*)res_out, hidden, eps);
+        if (per <= 1) TELB_LAUNCH("rmsnorm_kernel", (rmsnorm_kernel<T, 1>), dim3(rows), dim3(threads), 0, stream, (const T*)x, (const T*)residual, (const T*)w, (T*)y, (T*)res_out, hidden, eps);
+        else if (per <= 2) TELB_LAUNCH("rmsnorm_kernel", (rmsnorm_kernel<T, 2>), dim3(rows), dim3(threads), 0, stream, (const T*)x, (const T*)residual, (const T*)w, (T*)y, (T*)res_out, hidden, eps);
+        else if (per <= 4) TELB_LAUNCH("rmsnorm_kernel", (rmsnorm_kernel<T, 4>), dim3(rows), dim3(threads), 0, stream, (const T*)x, (const T*)residual, (const T*)w, (T*)y, (T*)res_out, hidden, eps);
+        else TELB_LAUNCH("rmsnorm_kernel", (rmsnorm_kernel<T, 8>), dim3(rows), dim3(threads), 0, stream, (const T*)x, (const T*)residual, (const T*)w, (T*)y, (T*)res_out, hidden, eps);
     })
     TELB_CHECK_LAUNCH("rmsnorm_kernel");
     return 0;
@@ -411,7 +419,7 @@ extern "C" int telb_gated_group_rmsnorm(const void* x, const void* z, const void
     if (rows <= 0) return 0;
     dim3 grid((unsigned)rows, n_groups);
     DISPATCH_T(is_bf16, {
-        gated_group_rmsnorm_kernel<T><<<grid, 256, 0, stream>>>((const T*)x, (const T*)z, (const T*)w, (T*)y, hidden, hidden / n_groups, eps);
+        TELB_LAUNCH("gated_group_rmsnorm_kernel", (gated_group_rmsnorm_kernel<T>), dim3(grid), dim3(256), 0, stream, (const T*)x, (const T*)z, (const T*)w, (T*)y, hidden, hidden / n_groups, eps);
     })
     TELB_CHECK_LAUNCH("gated_group_rmsnorm_kernel");
     return 0;
@@ -423,7 +431,7 @@ extern "C" int telb_swiglu(const void* in, void* out, long long rows, int inter,
     const long long nvec = rows * (inter / 8);
     long long blocks = (nvec + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    DISPATCH_T(is_bf16, { swiglu_kernel<T><<<(int)blocks, 256, 0, stream>>>((const T*)in, (T*)out, rows, inter); })
+    DISPATCH_T(is_bf16, { TELB_LAUNCH("swiglu_kernel", (swiglu_kernel<T>), dim3((int)blocks), dim3(256), 0, stream, (const T*)in, (T*)out, rows, inter); })
     TELB_CHECK_LAUNCH("swiglu_kernel");
     return 0;
 }
@@ -433,7 +441,7 @@ extern "C" int telb_relu2(const void* in, void* out, long long n, int is_bf16, c
     if (n % 8) return fail("telb_relu2: element count must be a multiple of 8");
     long long blocks = (n / 8 + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    DISPATCH_T(is_bf16, { relu2_kernel<T><<<(int)blocks, 256, 0, stream>>>((const T*)in, (T*)out, n); })
+    DISPATCH_T(is_bf16, { TELB_LAUNCH("relu2_kernel", (relu2_kernel<T>), dim3((int)blocks), dim3(256), 0, stream, (const T*)in, (T*)out, n); })
     TELB_CHECK_LAUNCH("relu2_kernel");
     return 0;
 }
@@ -442,7 +450,7 @@ extern "C" int telb_embedding(const int* ids, const void* table, void* out, long
                               int is_bf16, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (hidden % 8) return fail("telb_embedding: hidden must be a multiple of 8");
-    DISPATCH_T(is_bf16, { embedding_kernel<T><<<(unsigned)rows, 128, 0, stream>>>(ids, (const T*)table, (T*)out, hidden, vocab); })
+    DISPATCH_T(is_bf16, { TELB_LAUNCH("embedding_kernel", (embedding_kernel<T>), dim3((unsigned)rows), dim3(128), 0, stream, ids, (const T*)table, (T*)out, hidden, vocab); })
     TELB_CHECK_LAUNCH("embedding_kernel");
     return 0;
 }
@@ -458,18 +466,16 @@ extern "C" int telb_rope_kv_write(const void* qkv, void* q_out, void* kv_layer, 
         const long long warps = (long long)tokens * (hq + 2 * hkv);
         const int blocks = (int)((warps + 7) / 8);
         DISPATCH_T(is_bf16, {
-            if (d == 128) rope_kv_write_warp_kernel<T, 2><<<blocks, 256, 0, stream>>>((const T*)qkv, (T*)q_out, (T*)kv_layer, cos_sin, positions, seq_ids, q_start, past_len, page_table, kv_offsets, (const T*)q_norm_w, (const T*)k_norm_w, tokens, hq, hkv, page_size, max_pages, eps);
-            else if (d == 64) rope_kv_write_warp_kernel<T, 1><<<blocks, 256, 0, stream>>>((const T*)qkv, (T*)q_out, (T*)kv_layer, cos_sin, positions, seq_ids, q_start, past_len, page_table, kv_offsets, (const T*)q_norm_w, (const T*)k_norm_w, tokens, hq, hkv, page_size, max_pages, eps);
-            else rope_kv_write_warp_kernel<T, 4><<<blocks, 256, 0, stream>>>((const T*)qkv, (T*)q_out, (T*)kv_layer, cos_sin, positions, seq_ids, q_start, past_len, page_table, kv_offsets, (const T*)q_norm_w, (const T*)k_norm_w, tokens, hq, hkv, page_size, max_pages, eps);
+            if (d == 128) TELB_LAUNCH("rope_kv_write_warp_kernel", (rope_kv_write_warp_kernel<T, 2>), dim3(blocks), dim3(256), 0, stream, (const T*)qkv, (T*)q_out, (T*)kv_layer, cos_sin, positions, seq_ids, q_start, past_len, page_table, kv_offsets, (const T*)q_norm_w, (const T*)k_norm_w, tokens, hq, hkv, page_size, max_pages, eps);
+            else if (d == 64) TELB_LAUNCH("rope_kv_write_warp_kernel", (rope_kv_write_warp_kernel<T, 1>), dim3(blocks), dim3(256), 0, stream, (const T*)qkv, (T*)q_out, (T*)kv_layer, cos_sin, positions, seq_ids, q_start, past_len, page_table, kv_offsets, (const T*)q_norm_w, (const T*)k_norm_w, tokens, hq, hkv, page_size, max_pages, eps);
+            else TELB_LAUNCH("rope_kv_write_warp_kernel", (rope_kv_write_warp_kernel<T, 4>), dim3(blocks), dim3(256), 0, stream, (const T*)qkv, (T*)q_out, (T*)kv_layer, cos_sin, positions, seq_ids, q_start, past_len, page_table, kv_offsets, (const T*)q_norm_w, (const T*)k_norm_w, tokens, hq, hkv, page_size, max_pages, eps);
         })
         TELB_CHECK_LAUNCH("rope_kv_write_warp_kernel");
         return 0;
     }
     dim3 grid(tokens, hq + 2 * hkv);
     DISPATCH_T(is_bf16, {
-        rope_kv_write_kernel<T><<<grid, d / 2, 0, stream>>>((const T*)qkv, (T*)q_out, (T*)kv_layer, cos_sin, positions, seq_ids, q_start,
-                                                            past_len, page_table, kv_offsets, (const T*)q_norm_w,
-                                                            (const T*)k_norm_w, hq, hkv, d, rot_dim, page_size, max_pages, eps);
+        TELB_LAUNCH("rope_kv_write_kernel", (rope_kv_write_kernel<T>), dim3(grid), dim3(d / 2), 0, stream, (const T*)qkv, (T*)q_out, (T*)kv_layer, cos_sin, positions, seq_ids, q_start, past_len, page_table, kv_offsets, (const T*)q_norm_w, (const T*)k_norm_w, hq, hkv, d, rot_dim, page_size, max_pages, eps);
     })
     TELB_CHECK_LAUNCH("rope_kv_write_kernel");
     return 0;
@@ -477,6 +483,7 @@ extern "C" int telb_rope_kv_write(const void* qkv, void* q_out, void* kv_layer, 
 
 namespace telb {
 __global__ void argmax_f32_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab, long long stride) {
+    pdl_prologue();
     __shared__ float sv[32];
     __shared__ int si[32];
     const float* p = logits + blockIdx.x * stride;
@@ -527,6 +534,7 @@ namespace telb {
 template <typename T>
 __global__ void argmax_split_kernel(const T* __restrict__ logits, int* __restrict__ out, int vocab, long long stride,
                                     unsigned long long* __restrict__ keys, int* __restrict__ counters) {
+    pdl_prologue();
     __shared__ unsigned long long sk[32];
     const int row = blockIdx.y;
     const int nblk = gridDim.x;
@@ -587,15 +595,15 @@ extern "C" int telb_argmax(const void* logits, int* out, long long rows, int voc
         if (nblk > 64) nblk = 64;
         dim3 grid(nblk, (unsigned)rows);
         unsigned long long* k = (unsigned long long*)keys;
-        if (dtype == 2) argmax_split_kernel<float><<<grid, 512, 0, stream>>>((const float*)logits, out, vocab, stride, k, counters);
-        else if (dtype == 1) argmax_split_kernel<__nv_bfloat16><<<grid, 512, 0, stream>>>((const __nv_bfloat16*)logits, out, vocab, stride, k, counters);
-        else argmax_split_kernel<__half><<<grid, 512, 0, stream>>>((const __half*)logits, out, vocab, stride, k, counters);
+        if (dtype == 2) TELB_LAUNCH("argmax_split_kernel", (argmax_split_kernel<float>), dim3(grid), dim3(512), 0, stream, (const float*)logits, out, vocab, stride, k, counters);
+        else if (dtype == 1) TELB_LAUNCH("argmax_split_kernel", (argmax_split_kernel<__nv_bfloat16>), dim3(grid), dim3(512), 0, stream, (const __nv_bfloat16*)logits, out, vocab, stride, k, counters);
+        else TELB_LAUNCH("argmax_split_kernel", (argmax_split_kernel<__half>), dim3(grid), dim3(512), 0, stream, (const __half*)logits, out, vocab, stride, k, counters);
         TELB_CHECK_LAUNCH("argmax_split_kernel");
         return 0;
     }
-    if (dtype == 2) argmax_f32_kernel<<<(unsigned)rows, 1024, 0, stream>>>((const float*)logits, out, vocab, stride);
-    else if (dtype == 1) argmax_kernel<__nv_bfloat16><<<(unsigned)rows, 1024, 0, stream>>>((const __nv_bfloat16*)logits, out, vocab, stride);
-    else argmax_kernel<__half><<<(unsigned)rows, 1024, 0, stream>>>((const __half*)logits, out, vocab, stride);
+    if (dtype == 2) TELB_LAUNCH("argmax_f32_kernel", (argmax_f32_kernel), dim3((unsigned)rows), dim3(1024), 0, stream, (const float*)logits, out, vocab, stride);
+    else if (dtype == 1) TELB_LAUNCH("argmax_kernel", (argmax_kernel<__nv_bfloat16>), dim3((unsigned)rows), dim3(1024), 0, stream, (const __nv_bfloat16*)logits, out, vocab, stride);
+    else TELB_LAUNCH("argmax_kernel", (argmax_kernel<__half>), dim3((unsigned)rows), dim3(1024), 0, stream, (const __half*)logits, out, vocab, stride);
     TELB_CHECK_LAUNCH("argmax_kernel");
     return 0;
 }

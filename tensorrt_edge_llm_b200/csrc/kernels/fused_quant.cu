@@ -26,6 +26,7 @@ __global__ void rmsnorm_quant_kernel(const T* __restrict__ x, const T* __restric
                                      T* __restrict__ res_out, T* __restrict__ y_out, uint8_t* __restrict__ xq,
                                      uint8_t* __restrict__ sf, const float* __restrict__ global_scale, int hidden,
                                      int k64_pad, float eps) {
+    pdl_prologue();
     __shared__ float red[32];
     const size_t row = blockIdx.x;
     const int nunits = hidden / 16;
@@ -109,6 +110,7 @@ __global__ void rmsnorm_quant_kernel(const T* __restrict__ x, const T* __restric
 template <typename T>
 __global__ void swiglu_quant_kernel(const T* __restrict__ in, uint8_t* __restrict__ xq, uint8_t* __restrict__ sf,
                                     const float* __restrict__ global_scale, long long rows, int inter, int k64_pad) {
+    pdl_prologue();
     const int units = inter / 16;
     const long long total = rows * units;
     const float gs = *global_scale;
@@ -159,10 +161,10 @@ extern "C" int telb_rmsnorm_quant(const void* x, const void* residual, const voi
     const int per = (units + threads - 1) / threads;
     if (per > 4) return fail("telb_rmsnorm_quant: hidden too large (max 16384)");
     const int k64 = telb_nvfp4_k64_pad(hidden);
-#define TELB_RQ(T_, U_)                                                                                                   \
-    rmsnorm_quant_kernel<T_, U_><<<(unsigned)rows, threads, 0, stream>>>((const T_*)x, (const T_*)residual, (const T_*)w, \
-                                                                         (T_*)res_out, (T_*)y_out, (uint8_t*)xq,          \
-                                                                         (uint8_t*)sf, global_scale, hidden, k64, eps)
+#define TELB_RQ(T_, U_)                                                                                            \
+    TELB_LAUNCH("rmsnorm_quant_kernel", (rmsnorm_quant_kernel<T_, U_>), dim3((unsigned)rows), dim3(threads), 0, stream, \
+                (const T_*)x, (const T_*)residual, (const T_*)w, (T_*)res_out, (T_*)y_out, (uint8_t*)xq, (uint8_t*)sf, \
+                global_scale, hidden, k64, eps)
     if (is_bf16) {
         if (per <= 1) TELB_RQ(__nv_bfloat16, 1); else if (per <= 2) TELB_RQ(__nv_bfloat16, 2); else TELB_RQ(__nv_bfloat16, 4);
     } else {
@@ -182,11 +184,9 @@ extern "C" int telb_swiglu_quant(const void* in, void* xq, void* sf, const float
     if (blocks > 148 * 16) blocks = 148 * 16;
     const int k64 = telb_nvfp4_k64_pad(inter);
     if (is_bf16)
-        swiglu_quant_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)in, (uint8_t*)xq, (uint8_t*)sf,
-                                                                           global_scale, rows, inter, k64);
+        TELB_LAUNCH("swiglu_quant_kernel", (swiglu_quant_kernel<__nv_bfloat16>), dim3((int)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)in, (uint8_t*)xq, (uint8_t*)sf, global_scale, rows, inter, k64);
     else
-        swiglu_quant_kernel<__half><<<(int)blocks, 256, 0, stream>>>((const __half*)in, (uint8_t*)xq, (uint8_t*)sf, global_scale, rows,
-                                                                    inter, k64);
+        TELB_LAUNCH("swiglu_quant_kernel", (swiglu_quant_kernel<__half>), dim3((int)blocks), dim3(256), 0, stream, (const __half*)in, (uint8_t*)xq, (uint8_t*)sf, global_scale, rows, inter, k64);
     TELB_CHECK_LAUNCH("swiglu_quant_kernel");
     return 0;
 }

@@ -80,6 +80,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
+    pdl_prologue();          // everything above is independent of earlier kernels
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
@@ -201,7 +202,7 @@ static int launch_nvfp4(const CUtensorMap& ta, const CUtensorMap& tb, const uint
     }
     const int total = p.tiles_a * p.tiles_b * p.splits;
     const int grid = total < sm_count() ? total : sm_count();
-    gemm_nvfp4_kernel<BN, STAGES><<<grid, kGemmThreads, smem, stream>>>(ta, tb, sfa, sfb, k64a, k64b, p);
+    TELB_LAUNCH("gemm_nvfp4_kernel", (gemm_nvfp4_kernel<BN, STAGES>), dim3(grid), dim3(kGemmThreads), smem, stream, ta, tb, sfa, sfb, k64a, k64b, p);
     TELB_CHECK_LAUNCH("gemm_nvfp4_kernel");
     return 0;
 }
@@ -212,6 +213,7 @@ static int launch_nvfp4(const CUtensorMap& ta, const CUtensorMap& tb, const uint
 template <typename T>
 __global__ void nvfp4_quantize_kernel(const T* __restrict__ x, uint8_t* __restrict__ xq, uint8_t* __restrict__ sf,
                                       const float* __restrict__ global_scale, long long rows, int k, int k64_pad) {
+    pdl_prologue();
     const int blocks_per_row = k / 16;
     const long long total = rows * blocks_per_row;
     const float gs = *global_scale;
@@ -242,6 +244,7 @@ __global__ void nvfp4_quantize_kernel(const T* __restrict__ x, uint8_t* __restri
 // Row-major scales [rows, k/16] (as stored in checkpoints) → atom layout, zero padded.
 __global__ void nvfp4_swizzle_sf_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, long long rows, int kblocks,
                                         int k64_pad) {
+    pdl_prologue();
     const long long total = rows * kblocks;
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
@@ -275,8 +278,7 @@ extern "C" int telb_nvfp4_swizzle_scales(const void* sf_rowmajor, void* sf_atoms
     const long long total = rows * (k / 16);
     long long blocks = (total + 255) / 256;
     if (blocks > 148 * 32) blocks = 148 * 32;
-    nvfp4_swizzle_sf_kernel<<<(int)blocks, 256, 0, stream>>>((const uint8_t*)sf_rowmajor, (uint8_t*)sf_atoms, rows, k / 16,
-                                                             telb_nvfp4_k64_pad(k));
+    TELB_LAUNCH("nvfp4_swizzle_sf_kernel", (nvfp4_swizzle_sf_kernel), dim3((int)blocks), dim3(256), 0, stream, (const uint8_t*)sf_rowmajor, (uint8_t*)sf_atoms, rows, k / 16, telb_nvfp4_k64_pad(k));
     TELB_CHECK_LAUNCH("nvfp4_swizzle_sf_kernel");
     return 0;
 }
@@ -290,11 +292,9 @@ extern "C" int telb_nvfp4_quantize(const void* x, void* xq, void* sf_atoms, cons
     long long blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (is_bf16)
-        nvfp4_quantize_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, (uint8_t*)xq, (uint8_t*)sf_atoms,
-                                                                             global_scale, rows, k, telb_nvfp4_k64_pad(k));
+        TELB_LAUNCH("nvfp4_quantize_kernel", (nvfp4_quantize_kernel<__nv_bfloat16>), dim3((int)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, (uint8_t*)xq, (uint8_t*)sf_atoms, global_scale, rows, k, telb_nvfp4_k64_pad(k));
     else
-        nvfp4_quantize_kernel<__half><<<(int)blocks, 256, 0, stream>>>((const __half*)x, (uint8_t*)xq, (uint8_t*)sf_atoms, global_scale,
-                                                                      rows, k, telb_nvfp4_k64_pad(k));
+        TELB_LAUNCH("nvfp4_quantize_kernel", (nvfp4_quantize_kernel<__half>), dim3((int)blocks), dim3(256), 0, stream, (const __half*)x, (uint8_t*)xq, (uint8_t*)sf_atoms, global_scale, rows, k, telb_nvfp4_k64_pad(k));
     TELB_CHECK_LAUNCH("nvfp4_quantize_kernel");
     return 0;
 }

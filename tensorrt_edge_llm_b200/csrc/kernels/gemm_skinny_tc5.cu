@@ -53,8 +53,6 @@ __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_smem_addr, uint3
     asm("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote));
     return v;
 }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 template <int KIND, int BN>
 struct SkinnyCfg {
@@ -347,7 +345,7 @@ static int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const Ski
     int na = 0;
     attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attrs[na].val.programmaticStreamSerializationAllowed = 1;
-    ++na;
+    if (pdl_enabled()) ++na;
     if (p.ranks > 1) {
         attrs[na].id = cudaLaunchAttributeClusterDimension;
         attrs[na].val.clusterDim.x = 1;

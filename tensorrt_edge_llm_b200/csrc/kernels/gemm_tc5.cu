@@ -63,6 +63,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
+    pdl_prologue();          // everything above is independent of earlier kernels
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
@@ -159,7 +160,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
     }
     const int total = p.tiles_a * p.tiles_b * p.splits;
     const int grid = total < sm_count() ? total : sm_count();
-    gemm_tc5_kernel<BN, STAGES><<<grid, kGemmThreads, smem, stream>>>(ta, tb, p);
+    TELB_LAUNCH("gemm_tc5_kernel", (gemm_tc5_kernel<BN, STAGES>), dim3(grid), dim3(kGemmThreads), smem, stream, ta, tb, p);
     TELB_CHECK_LAUNCH("gemm_tc5_kernel");
     return 0;
 }

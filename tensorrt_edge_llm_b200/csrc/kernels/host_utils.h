@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 namespace telb {
 
@@ -89,6 +90,39 @@ inline int make_tmap_nd(CUtensorMap* out, CUtensorMapDataType dt, int rank, cons
     }
     return 0;
 }
+
+// Launch with programmatic dependent launch enabled (see pdl_wait in tc5_common.cuh).  Setting the
+// environment variable TELB_DISABLE_PDL=1 falls back to fully serialised launches.
+inline bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("TELB_DISABLE_PDL");
+        v = (e && e[0] == '1') ? 0 : 1;
+    }
+    return v == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+#define TELB_LAUNCH(name, kernel, grid, block, smem, stream, ...)                                   \
+    do {                                                                                            \
+        cudaError_t e__ = ::telb::launch_pdl(kernel, grid, block, smem, stream, __VA_ARGS__);       \
+        if (e__ != cudaSuccess) return ::telb::fail(name, e__);                                     \
+    } while (0)
 
 inline int sm_count() {
     static int n = 0;

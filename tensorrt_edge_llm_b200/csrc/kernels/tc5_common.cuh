@@ -255,6 +255,18 @@ __host__ __device__ constexpr uint32_t idesc_nvfp4(int m, int n) {
     return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+// ---- programmatic dependent launch ----------------------------------------------------------
+// Every kernel of this library is launched with programmatic stream serialisation: it may start
+// while its predecessor in the stream is still running.  `pdl_wait` blocks until the predecessor
+// grid has completed and its writes are visible; nothing that depends on (or could overwrite data
+// of) earlier kernels may happen before it.  `pdl_launch_dependents` lets the successor start.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_prologue() {
+    pdl_wait();
+    pdl_launch_dependents();
+}
+
 // ---- misc -----------------------------------------------------------------------------------
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");

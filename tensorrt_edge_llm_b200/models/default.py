@@ -82,7 +82,7 @@ class MLP(nn.Module):
 
     def forward(self, x):
         gu = self.gate_up_proj(x)
-        a = ops.swiglu(gu) if self.act in ("silu", "swiglu") else ops.relu2(gu)
+        a = ops.swiglu(gu, self.down_proj.fused_input_scale()) if self.act in ("silu", "swiglu") else ops.relu2(gu)
         return self.down_proj(a)
 
 
@@ -96,14 +96,15 @@ class DecoderLayer(nn.Module):
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.compute_dtype)
 
     def forward(self, h, residual, meta, kv_layer, cos_sin, comm):
+        qs_attn = self.self_attn.qkv_proj.fused_input_scale()
         if residual is None:
             residual = h
-            x = self.input_layernorm(h)
+            x = ops.rmsnorm_maybe_quant(h, self.input_layernorm.weight, self.input_layernorm.eps, qs_attn)
         else:
-            x, residual = comm.add_rmsnorm(h, residual, self.input_layernorm.weight, self.input_layernorm.eps)
+            x, residual = comm.add_rmsnorm(h, residual, self.input_layernorm.weight, self.input_layernorm.eps, qs_attn)
         a = self.self_attn(x, meta, kv_layer, cos_sin)
         x, residual = comm.add_rmsnorm(a, residual, self.post_attention_layernorm.weight,
-                                       self.post_attention_layernorm.eps)
+                                       self.post_attention_layernorm.eps, self.mlp.gate_up_proj.fused_input_scale())
         return self.mlp(x), residual
 
 

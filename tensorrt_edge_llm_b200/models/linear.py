@@ -66,6 +66,11 @@ class LinearBase(nn.Module):
     def finalize(self) -> None:
         """Hook run once after loading and device placement (GPU-side repacks)."""
 
+    def fused_input_scale(self) -> Optional[torch.Tensor]:
+        """Global activation scale when this layer wants its input pre-quantised by the producer
+        kernel (NVFP4 W4A4 on a GPU), else None."""
+        return None
+
 
 class Linear(LinearBase):
     """16-bit dense linear, ``y = x Wᵀ (+ b)``."""
@@ -154,6 +159,9 @@ class NVFP4Linear(LinearBase):
     def finalize(self):
         if self.weight.is_cuda:
             self._gpu_weight_sf = ops.cuda_ops().nvfp4_swizzle_scales(self.weight_scale)
+
+    def fused_input_scale(self):
+        return self.input_scale if (self.quantize_activations and self.weight.is_cuda) else None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if x.is_cuda:

@@ -32,10 +32,19 @@ def rmsnorm(x, weight, eps):
     return ref.rmsnorm(x, weight, eps)
 
 
-def add_rmsnorm(x, residual, weight, eps):
+def add_rmsnorm(x, residual, weight, eps, quant_scale=None):
+    """``quant_scale`` (CUDA only): emit the normalised output directly as NVFP4 for the next GEMM."""
     if x.is_cuda:
+        if quant_scale is not None:
+            return cuda_ops().rmsnorm_quant(x, residual, weight, eps, quant_scale)
         return cuda_ops().add_rmsnorm(x, residual, weight, eps)
     return ref.add_rmsnorm(x, residual, weight, eps)
+
+
+def rmsnorm_maybe_quant(x, weight, eps, quant_scale=None):
+    if x.is_cuda and quant_scale is not None:
+        return cuda_ops().rmsnorm_quant(x, None, weight, eps, quant_scale)[0]
+    return rmsnorm(x, weight, eps)
 
 
 def gated_group_rmsnorm(x, z, weight, n_groups, eps):
@@ -44,8 +53,10 @@ def gated_group_rmsnorm(x, z, weight, n_groups, eps):
     return ref.gated_group_rmsnorm(x, z, weight, n_groups, eps)
 
 
-def swiglu(gate_up):
+def swiglu(gate_up, quant_scale=None):
     if gate_up.is_cuda:
+        if quant_scale is not None:
+            return cuda_ops().swiglu_quant(gate_up, quant_scale)
         return cuda_ops().swiglu(gate_up)
     return ref.swiglu(gate_up)
 

@@ -271,6 +271,56 @@ def nvfp4_swizzle_scales(weight_scale: torch.Tensor) -> torch.Tensor:
     return out
 
 
+class QuantActs:
+    """Activations already quantised to NVFP4 by their producer (packed codes + atom-layout scales)."""
+
+    __slots__ = ("xq", "sf", "shape", "dtype")
+
+    def __init__(self, xq: torch.Tensor, sf: torch.Tensor, shape, dtype):
+        self.xq, self.sf, self.shape, self.dtype = xq, sf, tuple(shape), dtype
+
+    @property
+    def is_cuda(self) -> bool:
+        return True
+
+
+def _sf_buffer(nbytes: int, k: int, device) -> torch.Tensor:
+    # Rows beyond M only feed accumulator rows that are never stored, so they may hold anything;
+    # K padding multiplies real rows and must be zero.
+    return (torch.zeros if k % 256 else torch.empty)(nbytes, dtype=torch.uint8, device=device)
+
+
+def rmsnorm_quant(x: torch.Tensor, residual: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                  global_scale: torch.Tensor):
+    """``(residual add +) RMSNorm`` whose output is written as NVFP4 only.  Returns
+    ``(QuantActs, new_residual)`` (``new_residual`` is ``x`` itself when there is no residual)."""
+    x = x.contiguous()
+    m, k = x.shape
+    L = lib()
+    L.telb_nvfp4_sf_bytes.restype = c_ll
+    nbytes = L.telb_nvfp4_sf_bytes(c_ll(m), c_int(k))
+    xq = torch.empty(m, k // 2, dtype=torch.uint8, device=x.device)
+    sf = _sf_buffer(nbytes, k, x.device)
+    res_out = torch.empty_like(x) if residual is not None else None
+    _check(L.telb_rmsnorm_quant(_p(x), _p(residual), _p(weight), _p(res_out), c_vp(0), _p(xq), _p(sf), _p(global_scale),
+                                c_ll(m), c_int(k), c_float(eps), c_int(_is_bf16(x)), _stream()), "rmsnorm_quant")
+    return QuantActs(xq, sf, (m, k), x.dtype), (res_out if residual is not None else x)
+
+
+def swiglu_quant(gate_up: torch.Tensor, global_scale: torch.Tensor) -> QuantActs:
+    gate_up = gate_up.contiguous()
+    m = gate_up.shape[0]
+    inter = gate_up.shape[1] // 2
+    L = lib()
+    L.telb_nvfp4_sf_bytes.restype = c_ll
+    nbytes = L.telb_nvfp4_sf_bytes(c_ll(m), c_int(inter))
+    xq = torch.empty(m, inter // 2, dtype=torch.uint8, device=gate_up.device)
+    sf = _sf_buffer(nbytes, inter, gate_up.device)
+    _check(L.telb_swiglu_quant(_p(gate_up), _p(xq), _p(sf), _p(global_scale), c_ll(m), c_int(inter),
+                               c_int(_is_bf16(gate_up)), _stream()), "swiglu_quant")
+    return QuantActs(xq, sf, (m, inter), gate_up.dtype)
+
+
 def nvfp4_quantize(x: torch.Tensor, global_scale: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """Quantise activations ``[M,K]`` to packed E2M1 ``[M,K/2]`` + atom-layout E4M3 scales."""
     x = x.contiguous()
@@ -279,8 +329,7 @@ def nvfp4_quantize(x: torch.Tensor, global_scale: torch.Tensor) -> Tuple[torch.T
     L.telb_nvfp4_sf_bytes.restype = c_ll
     nbytes = L.telb_nvfp4_sf_bytes(c_ll(m), c_int(k))
     xq = torch.empty(m, k // 2, dtype=torch.uint8, device=x.device)
-    padded = (m % 128 != 0) or (k % 256 != 0)
-    sf = (torch.zeros if padded else torch.empty)(nbytes, dtype=torch.uint8, device=x.device)
+    sf = _sf_buffer(nbytes, k, x.device)
     _check(L.telb_nvfp4_quantize(_p(x), _p(xq), _p(sf), _p(global_scale), c_ll(m), c_int(k), c_int(_is_bf16(x)), _stream()),
            "nvfp4_quantize")
     return xq, sf
@@ -301,6 +350,8 @@ def nvfp4_linear(x, weight, weight_sf_atoms, alpha, input_scale, bias=None, quan
     """NVFP4 linear: dynamic per-16 activation quantisation (calibrated global scale) + block-scaled GEMM."""
     if not quantize_activations:
         raise NotImplementedError("W4A16 NVFP4 runs through the W4A4 tensor-core path only when activations are quantised")
+    if isinstance(x, QuantActs):
+        return gemm_nvfp4(x.xq, x.sf, weight, weight_sf_atoms, alpha, x.dtype, bias)
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1])
     xq, x_sf = nvfp4_quantize(x2, input_scale)

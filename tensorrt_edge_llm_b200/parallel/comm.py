@@ -42,8 +42,8 @@ class LocalComm:
     def all_to_all(self, send: torch.Tensor, send_counts: List[int], recv_counts: List[int]) -> torch.Tensor:
         return send
 
-    def add_rmsnorm(self, x_partial, residual, weight, eps) -> Tuple[torch.Tensor, torch.Tensor]:
-        return ops.add_rmsnorm(x_partial, residual, weight, eps)
+    def add_rmsnorm(self, x_partial, residual, weight, eps, quant_scale=None) -> Tuple[torch.Tensor, torch.Tensor]:
+        return ops.add_rmsnorm(x_partial, residual, weight, eps, quant_scale)
 
     def barrier(self) -> None:
         pass
@@ -103,8 +103,8 @@ class TorchComm(LocalComm):
         self.dist.all_to_all_single(out, send.contiguous(), recv_counts, send_counts, group=self.group)
         return out
 
-    def add_rmsnorm(self, x_partial, residual, weight, eps):
-        return ops.add_rmsnorm(self.all_reduce(x_partial), residual, weight, eps)
+    def add_rmsnorm(self, x_partial, residual, weight, eps, quant_scale=None):
+        return ops.add_rmsnorm(self.all_reduce(x_partial), residual, weight, eps, quant_scale)
 
     def barrier(self):
         self.dist.barrier(group=self.group)

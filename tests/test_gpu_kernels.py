@@ -307,3 +307,36 @@ def test_skinny_chain_in_cuda_graph(cu):
     torch.cuda.synchronize()
     assert _rel_err(y2, yr) < 1e-2
     _sync_check(cu)
+
+
+def test_fused_norm_and_swiglu_quant(cu):
+    g = torch.Generator(device="cuda").manual_seed(11)
+    for rows, hidden in [(5, 4096), (130, 2048), (64, 12288), (3, 768)]:
+        x = torch.randn(rows, hidden, device="cuda", generator=g).half()
+        r = torch.randn(rows, hidden, device="cuda", generator=g).half()
+        w = (1 + 0.1 * torch.randn(hidden, device="cuda", generator=g)).half()
+        gs = torch.tensor([0.01], device="cuda")
+        qa, res = cu.rmsnorm_quant(x, r, w, 1e-6, gs)
+        y_ref, res_ref = ref.add_rmsnorm(x, r, w, 1e-6)
+        assert torch.equal(res, res_ref)
+        xq2, sf2 = cu.nvfp4_quantize(cu.add_rmsnorm(x, r, w, 1e-6)[0], gs)
+        assert (qa.xq == xq2).float().mean().item() > 0.995
+        # dequantised result tracks the 16-bit normalised activations
+        p_ref, sf_ref, _ = ref.nvfp4_quantize(y_ref, gs.reshape(()))
+        assert (qa.xq == p_ref).float().mean().item() > 0.97
+        qa1, res1 = cu.rmsnorm_quant(x, None, w, 1e-6, gs)
+        assert res1 is x
+        assert (qa1.xq == cu.nvfp4_quantize(cu.rmsnorm(x, w, 1e-6), gs)[0]).float().mean().item() > 0.995
+    gu = torch.randn(70, 2 * 1536, device="cuda", generator=g).half()
+    gs = torch.tensor([0.02], device="cuda")
+    qa = cu.swiglu_quant(gu, gs)
+    xq2, sf2 = cu.nvfp4_quantize(cu.swiglu(gu), gs)
+    assert (qa.xq == xq2).float().mean().item() > 0.995
+    # end to end through a GEMM
+    w = torch.randn(512, 1536, device="cuda", generator=g) * 0.05
+    wq, wsf, wgs = ref.nvfp4_quantize(w)
+    alpha = (wgs * gs).expand(512).contiguous()
+    y1 = cu.gemm_nvfp4(qa.xq, qa.sf, wq, cu.nvfp4_swizzle_scales(wsf), alpha, torch.float16)
+    y2 = cu.gemm_nvfp4(xq2, sf2, wq, cu.nvfp4_swizzle_scales(wsf), alpha, torch.float16)
+    assert _rel_err(y1, y2) < 5e-3
+    _sync_check(cu)
