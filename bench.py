@@ -226,9 +226,16 @@ def main() -> int:
         "gpu_launches": int(launches),
     }
     if rank == 0:
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Captured graphs hold NCCL kernels; tearing the communicator down under them can block, so
+        # the ranks synchronise once more and leave without the collective destructor.
+        llm.runner._graphs.clear()
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     return 0
 
 

@@ -1,0 +1,70 @@
+"""Worker run under torch.distributed.run by the tensor-parallel tests (one process per rank).
+
+Builds the same small decoder at TP=1 (rank-local reference) and TP=world, feeds identical
+prompts and compares logits / greedy tokens.  Exits non-zero on mismatch."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    backend, kind, ckpt = sys.argv[1], sys.argv[2], sys.argv[3]
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if backend == "nccl":
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+        dev = torch.device("cuda", torch.cuda.current_device())
+        dist.init_process_group("nccl", device_id=dev)
+    else:
+        dev = torch.device("cpu")
+        dist.init_process_group("gloo")
+    from tensorrt_edge_llm_b200 import AutoModel
+    from tensorrt_edge_llm_b200.config import Mapping
+    from tensorrt_edge_llm_b200.parallel import make_comm
+    from tensorrt_edge_llm_b200.runtime.kv_cache import KVCacheManager
+    from tensorrt_edge_llm_b200.runtime.runner import ModelRunner
+
+    def run(mapping, comm):
+        model = AutoModel.from_pretrained(ckpt, mapping=mapping, comm=comm, device=dev)
+        kv = KVCacheManager(model.cfg, num_pages=24, page_size=64, max_seats=4, max_pages_per_seq=6, device=dev)
+        r = ModelRunner(model, kv, dev)
+        g = torch.Generator().manual_seed(3)
+        prompts = torch.randint(0, model.cfg.vocab_size, (2, 70), generator=g).tolist()
+        logits = r.prefill([0, 1], prompts)
+        first = logits.float().argmax(-1).to(torch.int32)
+        toks = r.decode_greedy([0, 1], first, 6)
+        return logits.float().cpu(), toks.cpu()
+
+    ref_logits, ref_toks = run(None, None)
+    comm = make_comm(kind, dev)
+    tp_logits, tp_toks = run(Mapping(tp_size=world, tp_rank=rank), comm)
+    err = (tp_logits - ref_logits).abs().max().item()
+    scale = ref_logits.abs().max().item()
+    tol = 1e-4 if dev.type == "cpu" else 0.06
+    ok = err <= tol * max(scale, 1.0)
+    same = (tp_toks == ref_toks).float().mean().item()
+    gathered = [None] * world
+    dist.all_gather_object(gathered, tp_toks.tolist())
+    identical = all(g == gathered[0] for g in gathered)
+    if dev.type == "cuda":
+        from tensorrt_edge_llm_b200.ops import cuda as cu
+        torch.cuda.synchronize()
+        cu.Workspace.get(dev).check_status()
+    print(f"rank {rank}: max logit err {err:.3e} (scale {scale:.2f}) token agreement {same:.2f} ranks identical {identical}", flush=True)
+    dist.barrier()
+    bad = not ok or not identical or (dev.type == "cpu" and same < 1.0) or same < 0.5
+    if dev.type == "cuda":
+        # graphs captured with NCCL kernels are still alive: skip the collective destructor
+        sys.stdout.flush()
+        os._exit(1 if bad else 0)
+    dist.destroy_process_group()
+    if bad:
+        sys.exit(1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,86 @@
+"""Tensor parallelism: TP=2 must reproduce TP=1 (CPU ranks over gloo; GPU ranks over NCCL and
+over the fused peer-memory communicator when two GPUs are present)."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from tensorrt_edge_llm_b200.checkpoint import save_file
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _make_ckpt(d, dtype):
+    from transformers import LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig(vocab_size=2048, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                      num_attention_heads=8, num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6,
+                      rope_theta=1e4, max_position_embeddings=1024, tie_word_embeddings=False)
+    torch.manual_seed(0)
+    m = LlamaForCausalLM(cfg).to(dtype).eval()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if "norm" not in n:
+                p.normal_(0.0, 0.05)
+    save_file(dict(m.state_dict()), os.path.join(d, "model.safetensors"))
+    hf = cfg.to_dict()
+    hf["torch_dtype"] = {torch.float32: "float32", torch.bfloat16: "bfloat16"}[dtype]
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(hf, f)
+
+
+def _launch(nproc, backend, kind, ckpt, port):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "_tp_worker.py"),
+           backend, kind, ckpt]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", OMP_NUM_THREADS="2")
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    return r.stdout
+
+
+def test_tp2_matches_tp1_cpu_gloo(tmp_path):
+    _make_ckpt(str(tmp_path), torch.float32)
+    out = _launch(2, "gloo", "nccl", str(tmp_path), 29611)
+    assert "ranks identical True" in out
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind", ["nccl", "fused"])
+def test_tp2_matches_tp1_gpu(tmp_path, kind):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _make_ckpt(str(tmp_path), torch.bfloat16)
+    out = _launch(2, "nccl", kind, str(tmp_path), 29612 if kind == "nccl" else 29613)
+    assert "ranks identical True" in out
+
+
+@pytest.mark.gpu
+def test_fused_allreduce_norm_world1():
+    """The fused all-reduce + add + RMSNorm kernel at world size 1 equals the local kernel."""
+    from tensorrt_edge_llm_b200.ops import cuda as cu
+    import ctypes
+    g = torch.Generator(device="cuda").manual_seed(0)
+    rows, hidden = 37, 2048
+    x = torch.randn(rows, hidden, device="cuda", generator=g).bfloat16()
+    r = torch.randn(rows, hidden, device="cuda", generator=g).bfloat16()
+    w = (1 + 0.1 * torch.randn(hidden, device="cuda", generator=g)).bfloat16()
+    partial = torch.zeros(2 * 256 * hidden, device="cuda", dtype=torch.bfloat16)
+    flags = torch.zeros(2 * 8 * 256, device="cuda", dtype=torch.int32)
+    epoch = torch.zeros(256, device="cuda", dtype=torch.int32)
+    cp = (ctypes.c_void_p * 1)(partial.data_ptr())
+    cf = (ctypes.c_void_p * 1)(flags.data_ptr())
+    y, res = torch.empty_like(x), torch.empty_like(x)
+    ws = cu.Workspace.get(x.device)
+    for _ in range(3):     # epochs advance, buffers alternate
+        cu._check(cu.lib().telb_ar_add_rmsnorm(cu._p(x), cp, cf, cu._p(epoch), cu._p(r), cu._p(w), cu._p(res), cu._p(y), None, None,
+                                               None, 0, 1, rows, hidden, 256, ctypes.c_float(1e-6), 1, cu._p(ws.status),
+                                               cu._stream()), "ar")
+    y2, res2 = cu.add_rmsnorm(x, r, w, 1e-6)
+    torch.cuda.synchronize()
+    assert torch.equal(res, res2)
+    assert torch.equal(y, y2)
+    assert int(epoch[:rows].min()) == 3
+    ws.check_status()
