@@ -1,0 +1,427 @@
+// Python bindings of the native runtime (module `_telb_runtime`).
+//
+// Counterpart of python/nanobind/bindings.cpp in the reference (LLMRuntime, StreamChannel,
+// RequestHandle, RequestEngine, validate_scheduling_options ...).  The model executor is reached
+// through RuntimeSession, which Python subclasses (the PyTorch model runner); every call from the
+// engine's actor thread into Python takes the GIL, and blocking native calls release it.
+#include <pybind11/functional.h>
+#include <pybind11/numpy.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include "json.h"
+#include "paged_kv.h"
+#include "runtime_core.h"
+#include "scheduler.h"
+#include "streaming.h"
+#include "tokenizer.h"
+
+namespace py = pybind11;
+using namespace telb;
+
+class PyRuntimeSession : public RuntimeSession {
+  public:
+    using RuntimeSession::RuntimeSession;
+    SessionCapabilities capabilities() const override {
+        PYBIND11_OVERRIDE_PURE(SessionCapabilities, RuntimeSession, capabilities, );
+    }
+    AdmissionResult admit(uint64_t request_id, const GenerationRequest& req) override {
+        PYBIND11_OVERRIDE_PURE(AdmissionResult, RuntimeSession, admit, request_id, req);
+    }
+    StepResult execute(const StepPlan& plan) override { PYBIND11_OVERRIDE_PURE(StepResult, RuntimeSession, execute, plan); }
+    void release(int slot) override { PYBIND11_OVERRIDE_PURE(void, RuntimeSession, release, slot); }
+};
+
+PYBIND11_MODULE(_telb_runtime, m) {
+    m.doc() = "Native runtime of the B200 Edge-LLM framework: paged KV bookkeeping, scheduler, streaming, tokenizer";
+
+    // ---- paged KV ------------------------------------------------------------------------------
+    py::class_<PageAllocator>(m, "PageAllocator")
+        .def(py::init<int>())
+        .def_property_readonly("free_pages", &PageAllocator::free_pages)
+        .def_property_readonly("num_pages", &PageAllocator::num_pages)
+        .def("alloc", &PageAllocator::alloc)
+        .def("retain", &PageAllocator::retain)
+        .def("release", &PageAllocator::release)
+        .def("refcount", &PageAllocator::refcount);
+    py::class_<KVPageTable>(m, "KVPageTable")
+        .def(py::init<int, int, int, int>(), py::arg("num_pages"), py::arg("page_size"), py::arg("max_seats"),
+             py::arg("max_pages_per_seq"))
+        .def_property_readonly("page_size", &KVPageTable::page_size)
+        .def_property_readonly("max_seats", &KVPageTable::max_seats)
+        .def_property_readonly("max_pages_per_seq", &KVPageTable::max_pages_per_seq)
+        .def_property_readonly("free_pages", &KVPageTable::free_pages)
+        .def("length", &KVPageTable::length)
+        .def("capacity_tokens", &KVPageTable::capacity_tokens)
+        .def("pages", &KVPageTable::pages)
+        .def("reserve", &KVPageTable::reserve)
+        .def("can_reserve", &KVPageTable::can_reserve)
+        .def("adopt_prefix", &KVPageTable::adopt_prefix)
+        .def("commit", &KVPageTable::commit)
+        .def("rewind", &KVPageTable::rewind)
+        .def("free_seat", &KVPageTable::free_seat)
+        .def("take_dirty_rows", &KVPageTable::take_dirty_rows)
+        .def("allocator", &KVPageTable::allocator, py::return_value_policy::reference_internal)
+        .def("rows", [](const KVPageTable& t, const std::vector<int>& seats) {
+            py::array_t<int32_t> out({static_cast<py::ssize_t>(seats.size()), static_cast<py::ssize_t>(t.max_pages_per_seq())});
+            auto o = out.mutable_unchecked<2>();
+            for (size_t i = 0; i < seats.size(); ++i) {
+                const int32_t* r = t.row(seats[i]);
+                for (int j = 0; j < t.max_pages_per_seq(); ++j) o(i, j) = r[j];
+            }
+            return out;
+        });
+    py::class_<ResidentSlotPool>(m, "ResidentSlotPool")
+        .def(py::init<int>())
+        .def("acquire", &ResidentSlotPool::acquire)
+        .def("release", &ResidentSlotPool::release)
+        .def("epoch", &ResidentSlotPool::epoch)
+        .def_property_readonly("in_use", &ResidentSlotPool::in_use)
+        .def_property_readonly("capacity", &ResidentSlotPool::capacity);
+    py::class_<PrefixCache::Match>(m, "PrefixMatch")
+        .def_readonly("pages", &PrefixCache::Match::pages)
+        .def_readonly("tokens", &PrefixCache::Match::tokens);
+    py::class_<PrefixCache>(m, "PrefixCache")
+        .def(py::init<PageAllocator&, int, int>(), py::arg("allocator"), py::arg("page_size"), py::arg("max_records") = 1024,
+             py::keep_alive<1, 2>())
+        .def("lookup", &PrefixCache::lookup)
+        .def("insert", &PrefixCache::insert)
+        .def("evict", &PrefixCache::evict)
+        .def_property_readonly("records", &PrefixCache::records)
+        .def_property_readonly("hits", &PrefixCache::hits)
+        .def_property_readonly("misses", &PrefixCache::misses)
+        .def_static("hash_block", [](uint64_t parent, const std::vector<int32_t>& toks) {
+            return PrefixCache::hash_block(parent, toks.data(), static_cast<int>(toks.size()));
+        });
+
+    // ---- streaming -----------------------------------------------------------------------------
+    py::enum_<FinishReason>(m, "FinishReason")
+        .value("NotFinished", FinishReason::kNotFinished)
+        .value("EndId", FinishReason::kEndId)
+        .value("Length", FinishReason::kLength)
+        .value("Cancelled", FinishReason::kCancelled)
+        .value("Error", FinishReason::kError)
+        .value("StopWords", FinishReason::kStopWords);
+    py::class_<StreamChunk>(m, "StreamChunk")
+        .def(py::init<>())
+        .def_readwrite("token_ids", &StreamChunk::token_ids)
+        .def_readwrite("text", &StreamChunk::text)
+        .def_readwrite("finished", &StreamChunk::finished)
+        .def_readwrite("reason", &StreamChunk::reason);
+    py::class_<GenerationMetrics>(m, "GenerationMetrics")
+        .def_readonly("generated_tokens", &GenerationMetrics::generated_tokens)
+        .def_readonly("time_to_first_token_s", &GenerationMetrics::time_to_first_token_s)
+        .def_readonly("generation_time_s", &GenerationMetrics::generation_time_s)
+        .def_property_readonly("decode_tokens_per_second", &GenerationMetrics::decode_tokens_per_second);
+    py::class_<StreamChannel, std::shared_ptr<StreamChannel>>(m, "StreamChannel")
+        .def_static("create", &StreamChannel::create, py::arg("collect_metrics") = false)
+        .def("push", &StreamChannel::push)
+        .def("finish", &StreamChannel::finish)
+        .def("try_pop", [](StreamChannel& c) -> py::object {
+            StreamChunk ch;
+            if (!c.try_pop(ch)) return py::none();
+            return py::cast(ch);
+        })
+        .def("wait_pop", [](StreamChannel& c, double timeout_s) -> py::object {
+            StreamChunk ch;
+            bool ok;
+            {
+                py::gil_scoped_release rel;
+                ok = c.wait_pop(ch, timeout_s);
+            }
+            if (!ok) return py::none();
+            return py::cast(ch);
+        }, py::arg("timeout_s") = 1.0)
+        .def("cancel", &StreamChannel::cancel)
+        .def_property_readonly("cancelled", &StreamChannel::cancelled)
+        .def("is_finished", &StreamChannel::is_finished)
+        .def("get_reason", &StreamChannel::reason)
+        .def("set_stream_interval", &StreamChannel::set_stream_interval)
+        .def("metrics", &StreamChannel::metrics);
+    m.def("utf8_complete_prefix", [](const py::bytes& b) { return utf8_complete_prefix(std::string(b)); });
+
+    // ---- scheduling ----------------------------------------------------------------------------
+    py::enum_<IfbSchedulingMode>(m, "IfbSchedulingMode")
+        .value("Auto", IfbSchedulingMode::kAuto).value("Mixed", IfbSchedulingMode::kMixed)
+        .value("PrefillFirst", IfbSchedulingMode::kPrefillFirst).value("SingleCohort", IfbSchedulingMode::kSingleCohort);
+    py::enum_<SchedulingPolicy>(m, "SchedulingPolicy").value("Fcfs", SchedulingPolicy::kFcfs).value("Priority", SchedulingPolicy::kPriority);
+    py::enum_<PreemptionMode>(m, "PreemptionMode").value("NoPreemption", PreemptionMode::kNone).value("Pause", PreemptionMode::kPause);
+    py::enum_<WorkKind>(m, "WorkKind").value("Context", WorkKind::kContext).value("Decode", WorkKind::kDecode);
+    py::class_<SchedulingOptions>(m, "SchedulingOptions")
+        .def(py::init<>())
+        .def_readwrite("mode", &SchedulingOptions::mode)
+        .def_readwrite("policy", &SchedulingOptions::policy)
+        .def_readwrite("preemption", &SchedulingOptions::preemption)
+        .def_readwrite("max_num_tokens", &SchedulingOptions::max_num_tokens)
+        .def_readwrite("max_chunk_tokens", &SchedulingOptions::max_chunk_tokens)
+        .def_readwrite("priority_reserved_slots", &SchedulingOptions::priority_reserved_slots)
+        .def_readwrite("max_pause_steps", &SchedulingOptions::max_pause_steps)
+        .def_readwrite("min_request_priority", &SchedulingOptions::min_request_priority);
+    py::class_<SessionCapabilities>(m, "SessionCapabilities")
+        .def(py::init<>())
+        .def_readwrite("compact", &SessionCapabilities::compact)
+        .def_readwrite("max_batch_size", &SessionCapabilities::max_batch_size)
+        .def_readwrite("max_input_length", &SessionCapabilities::max_input_length)
+        .def_readwrite("kv_page_size", &SessionCapabilities::kv_page_size)
+        .def_readwrite("max_kv_tokens", &SessionCapabilities::max_kv_tokens);
+    py::class_<ResolvedSchedulingPolicy>(m, "ResolvedSchedulingPolicy")
+        .def(py::init<>())
+        .def_readwrite("mode", &ResolvedSchedulingPolicy::mode)
+        .def_readwrite("policy", &ResolvedSchedulingPolicy::policy)
+        .def_readwrite("preemption", &ResolvedSchedulingPolicy::preemption)
+        .def_readwrite("max_num_tokens", &ResolvedSchedulingPolicy::max_num_tokens)
+        .def_readwrite("max_chunk_tokens", &ResolvedSchedulingPolicy::max_chunk_tokens)
+        .def_readwrite("priority_reserved_slots", &ResolvedSchedulingPolicy::priority_reserved_slots)
+        .def_readwrite("max_pause_steps", &ResolvedSchedulingPolicy::max_pause_steps);
+    m.def("validate_scheduling_options", &validate_scheduling_options);
+    m.def("resolve_scheduling_policy", &resolve_scheduling_policy);
+    py::class_<ResidentState>(m, "ResidentState")
+        .def(py::init<>())
+        .def_readwrite("slot", &ResidentState::slot)
+        .def_readwrite("epoch", &ResidentState::epoch)
+        .def_readwrite("prompt_len", &ResidentState::prompt_len)
+        .def_readwrite("prefilled", &ResidentState::prefilled)
+        .def_readwrite("generated", &ResidentState::generated)
+        .def_readwrite("priority", &ResidentState::priority)
+        .def_readwrite("arrival", &ResidentState::arrival)
+        .def_readwrite("paused_steps", &ResidentState::paused_steps)
+        .def_readwrite("exclusive", &ResidentState::exclusive);
+    py::class_<StepPlannerLimits>(m, "StepPlannerLimits")
+        .def(py::init<>())
+        .def_readwrite("max_batch_size", &StepPlannerLimits::max_batch_size)
+        .def_readwrite("max_input_length", &StepPlannerLimits::max_input_length)
+        .def_readwrite("kv_page_size", &StepPlannerLimits::kv_page_size);
+    py::class_<PlannedSequence>(m, "PlannedSequence")
+        .def(py::init<>())
+        .def_readwrite("slot", &PlannedSequence::slot)
+        .def_readwrite("epoch", &PlannedSequence::epoch)
+        .def_readwrite("kind", &PlannedSequence::kind)
+        .def_readwrite("start", &PlannedSequence::start)
+        .def_readwrite("length", &PlannedSequence::length)
+        .def_readwrite("last_chunk", &PlannedSequence::last_chunk);
+    py::class_<StepPlan>(m, "StepPlan")
+        .def(py::init<>())
+        .def_readwrite("seqs", &StepPlan::seqs)
+        .def_readwrite("paused", &StepPlan::paused)
+        .def_readwrite("num_context", &StepPlan::num_context)
+        .def_readwrite("num_decode", &StepPlan::num_decode)
+        .def_readwrite("total_tokens", &StepPlan::total_tokens)
+        .def("empty", &StepPlan::empty);
+    py::class_<StepPlanner>(m, "StepPlanner")
+        .def(py::init<StepPlannerLimits, ResolvedSchedulingPolicy>())
+        .def("plan", &StepPlanner::plan);
+
+    py::class_<GenerationRequest>(m, "GenerationRequest")
+        .def(py::init<>())
+        .def_readwrite("prompt_ids", &GenerationRequest::prompt_ids)
+        .def_readwrite("max_tokens", &GenerationRequest::max_tokens)
+        .def_readwrite("temperature", &GenerationRequest::temperature)
+        .def_readwrite("top_k", &GenerationRequest::top_k)
+        .def_readwrite("top_p", &GenerationRequest::top_p)
+        .def_readwrite("seed", &GenerationRequest::seed)
+        .def_readwrite("ignore_eos", &GenerationRequest::ignore_eos)
+        .def_readwrite("stop_token_ids", &GenerationRequest::stop_token_ids)
+        .def_readwrite("priority", &GenerationRequest::priority)
+        .def_readwrite("exclusive", &GenerationRequest::exclusive)
+        .def_readwrite("lora_name", &GenerationRequest::lora_name)
+        .def_readwrite("stream_interval", &GenerationRequest::stream_interval);
+    py::class_<AdmissionResult>(m, "AdmissionResult")
+        .def(py::init<>())
+        .def_readwrite("admitted", &AdmissionResult::admitted)
+        .def_readwrite("slot", &AdmissionResult::slot)
+        .def_readwrite("reused_tokens", &AdmissionResult::reused_tokens)
+        .def_readwrite("reason", &AdmissionResult::reason)
+        .def_readwrite("retry_later", &AdmissionResult::retry_later);
+    py::class_<TokenDelta>(m, "TokenDelta")
+        .def(py::init<>())
+        .def_readwrite("slot", &TokenDelta::slot)
+        .def_readwrite("tokens", &TokenDelta::tokens)
+        .def_readwrite("finished", &TokenDelta::finished)
+        .def_readwrite("reason", &TokenDelta::reason);
+    py::class_<StepResult>(m, "StepResult").def(py::init<>()).def_readwrite("deltas", &StepResult::deltas);
+    py::register_exception<SessionLostError>(m, "SessionLostError");
+    py::class_<RuntimeSession, PyRuntimeSession, std::shared_ptr<RuntimeSession>>(m, "RuntimeSession")
+        .def(py::init<>())
+        .def("capabilities", &RuntimeSession::capabilities)
+        .def("admit", &RuntimeSession::admit)
+        .def("execute", &RuntimeSession::execute)
+        .def("release", &RuntimeSession::release);
+
+    py::class_<EngineConfig>(m, "EngineConfig")
+        .def(py::init<>())
+        .def_readwrite("command_queue_capacity", &EngineConfig::command_queue_capacity)
+        .def_readwrite("max_pending_requests", &EngineConfig::max_pending_requests)
+        .def_readwrite("max_batch_size", &EngineConfig::max_batch_size)
+        .def_readwrite("max_consecutive_session_failures", &EngineConfig::max_consecutive_session_failures)
+        .def_readwrite("idle_wait_s", &EngineConfig::idle_wait_s)
+        .def_readwrite("scheduling", &EngineConfig::scheduling);
+    py::class_<EngineMetrics>(m, "EngineMetrics")
+        .def_readonly("submitted", &EngineMetrics::submitted).def_readonly("refused", &EngineMetrics::refused)
+        .def_readonly("completed", &EngineMetrics::completed).def_readonly("cancelled", &EngineMetrics::cancelled)
+        .def_readonly("failed", &EngineMetrics::failed).def_readonly("admitted_mid_flight", &EngineMetrics::admitted_mid_flight)
+        .def_readonly("stalls_no_capacity", &EngineMetrics::stalls_no_capacity)
+        .def_readonly("stalls_exclusive", &EngineMetrics::stalls_exclusive)
+        .def_readonly("decode_steps", &EngineMetrics::decode_steps).def_readonly("prompt_steps", &EngineMetrics::prompt_steps)
+        .def_readonly("mixed_steps", &EngineMetrics::mixed_steps).def_readonly("step_tokens", &EngineMetrics::step_tokens)
+        .def_readonly("paused_resident_steps", &EngineMetrics::paused_resident_steps)
+        .def_readonly("session_failures", &EngineMetrics::session_failures)
+        .def_readonly("prefix_reused_tokens", &EngineMetrics::prefix_reused_tokens)
+        .def_readonly("queue_latency_s_sum", &EngineMetrics::queue_latency_s_sum);
+    py::class_<EngineStatus>(m, "EngineStatus")
+        .def_readonly("available", &EngineStatus::available)
+        .def_readonly("unavailable_reason", &EngineStatus::unavailable_reason)
+        .def_readonly("queued", &EngineStatus::queued)
+        .def_readonly("resident", &EngineStatus::resident);
+    py::class_<RequestStats>(m, "RequestStats")
+        .def_readonly("prompt_tokens", &RequestStats::prompt_tokens)
+        .def_readonly("generated_tokens", &RequestStats::generated_tokens)
+        .def_readonly("reused_tokens", &RequestStats::reused_tokens)
+        .def_readonly("queue_s", &RequestStats::queue_s).def_readonly("ttft_s", &RequestStats::ttft_s)
+        .def_readonly("total_s", &RequestStats::total_s);
+    py::class_<RequestHandle, std::shared_ptr<RequestHandle>>(m, "RequestHandle")
+        .def_property_readonly("id", &RequestHandle::id)
+        .def("stream", &RequestHandle::stream)
+        .def("ready", &RequestHandle::ready)
+        .def("get", [](RequestHandle& h, double timeout_s) {
+            py::gil_scoped_release rel;
+            return h.get(timeout_s);
+        }, py::arg("timeout_s") = 1e9)
+        .def("reason", &RequestHandle::reason)
+        .def("error", &RequestHandle::error)
+        .def("cancel", &RequestHandle::cancel)
+        .def("stats", &RequestHandle::stats);
+    py::class_<RequestEngine>(m, "RequestEngine")
+        .def(py::init([](EngineConfig cfg, py::function factory) {
+            // The factory and the sessions it returns are Python objects: hold the GIL around every use.
+            auto shared_factory = std::make_shared<py::function>(std::move(factory));
+            SessionFactory f = [shared_factory]() {
+                py::gil_scoped_acquire gil;
+                py::object obj = (*shared_factory)();
+                auto sp = obj.cast<std::shared_ptr<RuntimeSession>>();
+                // The session is a Python object with Python overrides: keep it alive for as long as
+                // the engine holds the pointer, and drop the reference under the GIL.
+                auto keep = std::make_shared<py::object>(std::move(obj));
+                return std::shared_ptr<RuntimeSession>(sp.get(), [sp, keep](RuntimeSession*) mutable {
+                    py::gil_scoped_acquire g;
+                    keep.reset();
+                    sp.reset();
+                });
+            };
+            py::gil_scoped_release rel;       // the constructor opens the first session on this thread, then starts the actor
+            return new RequestEngine(cfg, f);
+        }))
+        .def("submit", [](RequestEngine& e, const GenerationRequest& r) {
+            std::string why;
+            auto h = e.submit(r, &why);
+            return py::make_tuple(h, why);
+        })
+        .def("cancel", &RequestEngine::cancel)
+        .def("shutdown", [](RequestEngine& e) {
+            py::gil_scoped_release rel;
+            e.shutdown();
+        })
+        .def("queued", &RequestEngine::queued)
+        .def("resident", &RequestEngine::resident)
+        .def("metrics", &RequestEngine::metrics)
+        .def("status", &RequestEngine::status)
+        .def("resolved_policy", &RequestEngine::resolved_policy);
+
+    // ---- ragged batch / sampling / config / misc ------------------------------------------------
+    py::class_<RaggedBatch>(m, "RaggedBatch")
+        .def_readonly("q_start", &RaggedBatch::q_start).def_readonly("q_len", &RaggedBatch::q_len)
+        .def_readonly("past_len", &RaggedBatch::past_len).def_readonly("positions", &RaggedBatch::positions)
+        .def_readonly("seq_ids", &RaggedBatch::seq_ids).def_readonly("slot_ids", &RaggedBatch::slot_ids)
+        .def_readonly("logits_idx", &RaggedBatch::logits_idx).def_readonly("num_seqs", &RaggedBatch::num_seqs)
+        .def_readonly("num_tokens", &RaggedBatch::num_tokens).def_readonly("max_q_len", &RaggedBatch::max_q_len)
+        .def_readonly("max_seq_len", &RaggedBatch::max_seq_len);
+    m.def("build_ragged_batch", &RaggedBatchBuilder::build, py::arg("plan"), py::arg("past_lens"), py::arg("logits_all") = false);
+    py::class_<RowSamplingParams>(m, "RowSamplingParams")
+        .def(py::init<>())
+        .def_readwrite("temperature", &RowSamplingParams::temperature)
+        .def_readwrite("top_k", &RowSamplingParams::top_k)
+        .def_readwrite("top_p", &RowSamplingParams::top_p)
+        .def("greedy", &RowSamplingParams::greedy);
+    m.def("request_stable_uniform", &request_stable_uniform);
+    m.def("sample_row", [](py::array_t<float, py::array::c_style | py::array::forcecast> logits, const RowSamplingParams& p, float u) {
+        return sample_row(logits.data(), static_cast<int>(logits.size()), p, u);
+    });
+    py::class_<ParallelConfig>(m, "ParallelConfig")
+        .def(py::init<>())
+        .def_readwrite("world_size", &ParallelConfig::world_size)
+        .def_readwrite("rank", &ParallelConfig::rank)
+        .def_readwrite("launch_mode", &ParallelConfig::launch_mode)
+        .def("validate", &ParallelConfig::validate);
+    py::class_<LLMEngineConfig>(m, "LLMEngineConfig")
+        .def(py::init<>())
+        .def_static("from_json", [](const std::string& text) { return LLMEngineConfig::from_json(Json::parse(text)); })
+        .def("to_json", [](const LLMEngineConfig& c) { return c.to_json().dump(); })
+        .def_readwrite("model_type", &LLMEngineConfig::model_type)
+        .def_readwrite("vocab_size", &LLMEngineConfig::vocab_size)
+        .def_readwrite("hidden_size", &LLMEngineConfig::hidden_size)
+        .def_readwrite("num_layers", &LLMEngineConfig::num_layers)
+        .def_readwrite("num_heads", &LLMEngineConfig::num_heads)
+        .def_readwrite("num_kv_heads", &LLMEngineConfig::num_kv_heads)
+        .def_readwrite("head_dim", &LLMEngineConfig::head_dim)
+        .def_readwrite("max_batch_size", &LLMEngineConfig::max_batch_size)
+        .def_readwrite("max_input_len", &LLMEngineConfig::max_input_len)
+        .def_readwrite("max_kv_cache_capacity", &LLMEngineConfig::max_kv_cache_capacity)
+        .def_readwrite("kv_page_size", &LLMEngineConfig::kv_page_size)
+        .def_readwrite("dtype", &LLMEngineConfig::dtype)
+        .def_readwrite("quantization", &LLMEngineConfig::quantization)
+        .def_readwrite("decoding_strategies", &LLMEngineConfig::decoding_strategies)
+        .def_readwrite("world_size", &LLMEngineConfig::world_size);
+    py::class_<LoraAdapter>(m, "LoraAdapter")
+        .def(py::init<>())
+        .def_readwrite("name", &LoraAdapter::name).def_readwrite("path", &LoraAdapter::path)
+        .def_readwrite("rank", &LoraAdapter::rank).def_readwrite("scale", &LoraAdapter::scale);
+    py::class_<LoRAManager>(m, "LoRAManager")
+        .def(py::init<>())
+        .def("add", &LoRAManager::add).def("remove", &LoRAManager::remove)
+        .def("find", &LoRAManager::find, py::return_value_policy::reference_internal)
+        .def("activate", &LoRAManager::activate)
+        .def("active", &LoRAManager::active, py::return_value_policy::reference_internal)
+        .def("names", &LoRAManager::names);
+    py::class_<DeviceFailureState>(m, "DeviceFailureState")
+        .def(py::init<>())
+        .def("record", &DeviceFailureState::record)
+        .def("failed", &DeviceFailureState::failed)
+        .def("reason", &DeviceFailureState::reason);
+    py::class_<StageTimer>(m, "StageTimer")
+        .def(py::init<>())
+        .def("set_enabled", &StageTimer::set_enabled)
+        .def("begin", &StageTimer::begin)
+        .def("end", &StageTimer::end)
+        .def("reset", &StageTimer::reset)
+        .def("snapshot", [](const StageTimer& t) {
+            py::dict d;
+            for (const auto& kv : t.snapshot())
+                d[py::str(kv.first)] = py::make_tuple(kv.second.count, kv.second.total_s, kv.second.max_s);
+            return d;
+        });
+    m.def("json_roundtrip", [](const std::string& s) { return Json::parse(s).dump(); });
+
+    // ---- tokenizer -----------------------------------------------------------------------------
+    py::class_<Tokenizer>(m, "Tokenizer")
+        .def_static("load_from_hf", &Tokenizer::load_from_hf)
+        .def_static("from_json_text", &Tokenizer::from_json_text, py::arg("tokenizer_json"), py::arg("config_json") = "")
+        .def("encode", &Tokenizer::encode, py::arg("text"), py::arg("add_special_tokens") = false)
+        .def("decode", [](const Tokenizer& t, const std::vector<int32_t>& ids, bool skip) { return py::bytes(t.decode(ids, skip)); },
+             py::arg("ids"), py::arg("skip_special_tokens") = true)
+        .def("id_to_bytes", [](const Tokenizer& t, int32_t id) { return py::bytes(t.id_to_bytes(id)); })
+        .def("id_to_piece", &Tokenizer::id_to_piece)
+        .def("piece_to_id", &Tokenizer::piece_to_id)
+        .def_property_readonly("vocab_size", &Tokenizer::vocab_size)
+        .def_property_readonly("bos_id", &Tokenizer::bos_id)
+        .def_property_readonly("eos_id", &Tokenizer::eos_id)
+        .def("is_special", &Tokenizer::is_special);
+    py::class_<ChatMessage>(m, "ChatMessage")
+        .def(py::init<>())
+        .def(py::init([](const std::string& r, const std::string& c) { return ChatMessage{r, c}; }))
+        .def_readwrite("role", &ChatMessage::role)
+        .def_readwrite("content", &ChatMessage::content);
+    py::class_<ChatTemplate>(m, "ChatTemplate")
+        .def_static("load", &ChatTemplate::load)
+        .def_static("from_template_text", &ChatTemplate::from_template_text, py::arg("template"), py::arg("bos") = "")
+        .def("apply", &ChatTemplate::apply, py::arg("messages"), py::arg("add_generation_prompt") = true,
+             py::arg("enable_thinking") = true);
+}

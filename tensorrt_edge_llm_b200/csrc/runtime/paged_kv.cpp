@@ -1,0 +1,186 @@
+#include "paged_kv.h"
+
+#include <algorithm>
+
+namespace telb {
+
+PageAllocator::PageAllocator(int num_pages) : ref_(num_pages, 0) {
+    free_.reserve(num_pages);
+    for (int p = num_pages - 1; p >= 0; --p) free_.push_back(p);
+}
+
+std::vector<int32_t> PageAllocator::alloc(int n) {
+    if (n > static_cast<int>(free_.size()))
+        throw std::runtime_error("KV pool exhausted: want " + std::to_string(n) + " pages, " + std::to_string(free_.size()) + " free");
+    std::vector<int32_t> out(n);
+    for (int i = 0; i < n; ++i) {
+        out[i] = free_.back();
+        free_.pop_back();
+        ref_[out[i]] = 1;
+    }
+    return out;
+}
+
+void PageAllocator::retain(const std::vector<int32_t>& pages) {
+    for (int32_t p : pages) {
+        if (ref_.at(p) <= 0) throw std::runtime_error("retain of free page " + std::to_string(p));
+        ++ref_[p];
+    }
+}
+
+void PageAllocator::release(const std::vector<int32_t>& pages) {
+    for (int32_t p : pages) {
+        if (ref_.at(p) <= 0) throw std::runtime_error("double free of page " + std::to_string(p));
+        if (--ref_[p] == 0) free_.push_back(p);
+    }
+}
+
+KVPageTable::KVPageTable(int num_pages, int page_size, int max_seats, int max_pages_per_seq)
+    : alloc_(num_pages), page_size_(page_size), max_seats_(max_seats), max_pages_(max_pages_per_seq),
+      table_(static_cast<size_t>(max_seats) * max_pages_per_seq, kUnusedPage), lengths_(max_seats, 0), pages_(max_seats),
+      dirty_(max_seats, 0) {}
+
+bool KVPageTable::can_reserve(int seat, int total_tokens) const {
+    const int need = (total_tokens + page_size_ - 1) / page_size_;
+    if (need > max_pages_) return false;
+    const int have = static_cast<int>(pages_.at(seat).size());
+    return need - have <= alloc_.free_pages();
+}
+
+void KVPageTable::reserve(int seat, int total_tokens) {
+    const int need = (total_tokens + page_size_ - 1) / page_size_;
+    if (need > max_pages_)
+        throw std::runtime_error("sequence of " + std::to_string(total_tokens) + " tokens exceeds " + std::to_string(max_pages_) + " pages");
+    auto& have = pages_.at(seat);
+    if (need > static_cast<int>(have.size())) {
+        const auto fresh = alloc_.alloc(need - static_cast<int>(have.size()));
+        int32_t* r = table_.data() + static_cast<size_t>(seat) * max_pages_;
+        for (int32_t p : fresh) {
+            r[have.size()] = p;
+            have.push_back(p);
+        }
+        dirty_[seat] = 1;
+    }
+}
+
+void KVPageTable::adopt_prefix(int seat, const std::vector<int32_t>& pages, int tokens) {
+    if (!pages_.at(seat).empty()) throw std::runtime_error("adopt_prefix on a non-empty seat");
+    if (static_cast<int>(pages.size()) > max_pages_) throw std::runtime_error("prefix longer than a page-table row");
+    alloc_.retain(pages);
+    pages_[seat] = pages;
+    std::copy(pages.begin(), pages.end(), table_.begin() + static_cast<size_t>(seat) * max_pages_);
+    lengths_[seat] = tokens;
+    dirty_[seat] = 1;
+}
+
+void KVPageTable::rewind(int seat, int length) {
+    if (length > lengths_.at(seat) || length < 0) throw std::runtime_error("rewind beyond the committed length");
+    lengths_[seat] = length;
+}
+
+void KVPageTable::free_seat(int seat) {
+    alloc_.release(pages_.at(seat));
+    pages_[seat].clear();
+    std::fill_n(table_.begin() + static_cast<size_t>(seat) * max_pages_, max_pages_, kUnusedPage);
+    lengths_[seat] = 0;
+    dirty_[seat] = 1;
+}
+
+std::vector<int> KVPageTable::take_dirty_rows() {
+    std::vector<int> rows;
+    for (int s = 0; s < max_seats_; ++s)
+        if (dirty_[s]) {
+            rows.push_back(s);
+            dirty_[s] = 0;
+        }
+    return rows;
+}
+
+ResidentSlotPool::ResidentSlotPool(int n) : epoch_(n, 0), used_(n, 0) {
+    for (int s = n - 1; s >= 0; --s) free_.push_back(s);
+}
+
+int ResidentSlotPool::acquire() {
+    if (free_.empty()) return -1;
+    const int s = free_.back();
+    free_.pop_back();
+    used_[s] = 1;
+    ++epoch_[s];
+    ++in_use_;
+    return s;
+}
+
+void ResidentSlotPool::release(int slot) {
+    if (!used_.at(slot)) throw std::runtime_error("release of a free slot");
+    used_[slot] = 0;
+    free_.push_back(slot);
+    --in_use_;
+}
+
+PrefixCache::PrefixCache(PageAllocator& alloc, int page_size, int max_records)
+    : alloc_(alloc), page_size_(page_size), max_records_(max_records) {}
+
+uint64_t PrefixCache::hash_block(uint64_t parent, const int32_t* tokens, int n) {
+    uint64_t h = 0xcbf29ce484222325ull ^ (parent * 0x9E3779B97F4A7C15ull);     // FNV-1a over the bytes, seeded by the parent
+    const uint8_t* b = reinterpret_cast<const uint8_t*>(tokens);
+    for (int i = 0; i < n * 4; ++i) {
+        h ^= b[i];
+        h *= 0x100000001b3ull;
+    }
+    return h ? h : 1;
+}
+
+PrefixCache::Match PrefixCache::lookup(const std::vector<int32_t>& tokens) {
+    Match m;
+    const int full = (static_cast<int>(tokens.size()) - 1) / page_size_;   // leave >= 1 token to compute
+    uint64_t parent = 0;
+    for (int b = 0; b < full; ++b) {
+        const uint64_t h = hash_block(parent, tokens.data() + static_cast<size_t>(b) * page_size_, page_size_);
+        auto it = map_.find(h);
+        if (it == map_.end()) break;
+        lru_.splice(lru_.begin(), lru_, it->second.lru);
+        m.pages.push_back(it->second.page);
+        m.tokens += page_size_;
+        parent = h;
+    }
+    if (m.tokens > 0) ++hits_; else ++misses_;
+    return m;
+}
+
+int PrefixCache::insert(const std::vector<int32_t>& tokens, int filled_tokens, const std::vector<int32_t>& pages) {
+    const int full = std::min<int>(filled_tokens, static_cast<int>(tokens.size())) / page_size_;
+    uint64_t parent = 0;
+    int added = 0;
+    for (int b = 0; b < full && b < static_cast<int>(pages.size()); ++b) {
+        const uint64_t h = hash_block(parent, tokens.data() + static_cast<size_t>(b) * page_size_, page_size_);
+        parent = h;
+        auto it = map_.find(h);
+        if (it != map_.end()) {
+            lru_.splice(lru_.begin(), lru_, it->second.lru);
+            continue;
+        }
+        if (static_cast<int>(map_.size()) >= max_records_ && evict(1) == 0) break;
+        alloc_.retain({pages[b]});
+        lru_.push_front(h);
+        map_[h] = Entry{pages[b], lru_.begin()};
+        ++added;
+    }
+    return added;
+}
+
+int PrefixCache::evict(int pages_wanted) {
+    int released = 0;
+    while (released < pages_wanted && !lru_.empty()) {
+        const uint64_t h = lru_.back();
+        lru_.pop_back();
+        auto it = map_.find(h);
+        if (it != map_.end()) {
+            alloc_.release({it->second.page});
+            map_.erase(it);
+            ++released;
+        }
+    }
+    return released;
+}
+
+}  // namespace telb
