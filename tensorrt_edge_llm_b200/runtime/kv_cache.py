@@ -72,6 +72,13 @@ class KVCacheManager:
         self.table = torch.full((max_seats, max_pages_per_seq), -1, dtype=torch.int32)   # host truth
         self.lengths = [0] * max_seats
         self._pages: Dict[int, List[int]] = {}
+        # Page accounting lives in the native table when the runtime module is built; the Python
+        # structures above mirror it so callers can read `lengths` / `table` directly.
+        try:
+            from . import native as _rt
+            self.native = _rt.KVPageTable(num_pages, page_size, max_seats, max_pages_per_seq)
+        except ImportError:
+            self.native = None
 
     @property
     def bytes_per_token(self) -> int:
@@ -87,29 +94,44 @@ class KVCacheManager:
         if need > self.max_pages_per_seq:
             raise ValueError(f"sequence of {total_tokens} tokens exceeds {self.max_pages_per_seq} pages")
         if need > len(have):
-            new = self.alloc.alloc(need - len(have))
+            if self.native is not None:
+                self.native.reserve(seat, total_tokens)
+                pages = list(self.native.pages(seat))
+                new = pages[len(have):]
+            else:
+                new = self.alloc.alloc(need - len(have))
             self.table[seat, len(have):need] = torch.tensor(new, dtype=torch.int32)
             have.extend(new)
 
     def adopt_prefix(self, seat: int, pages: Sequence[int], tokens: int) -> None:
         """Share already-filled pages (prefix reuse); the seat must be empty."""
         assert not self._pages.get(seat)
-        self.alloc.retain(pages)
+        if self.native is not None:
+            self.native.adopt_prefix(seat, list(pages), tokens)
+        else:
+            self.alloc.retain(pages)
         self._pages[seat] = list(pages)
         self.table[seat, :len(pages)] = torch.tensor(list(pages), dtype=torch.int32)
         self.lengths[seat] = tokens
 
     def commit(self, seat: int, new_tokens: int) -> None:
         self.lengths[seat] += new_tokens
+        if self.native is not None:
+            self.native.commit(seat, new_tokens)
 
     def rewind(self, seat: int, length: int) -> None:
         """Drop everything after ``length`` tokens (speculative rejection); pages are kept."""
         assert length <= self.lengths[seat]
         self.lengths[seat] = length
+        if self.native is not None:
+            self.native.rewind(seat, length)
 
     def free(self, seat: int) -> None:
         pages = self._pages.pop(seat, [])
-        self.alloc.release(pages)
+        if self.native is not None:
+            self.native.free_seat(seat)
+        else:
+            self.alloc.release(pages)
         self.table[seat].fill_(-1)
         self.lengths[seat] = 0
 

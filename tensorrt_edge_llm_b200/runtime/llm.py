@@ -34,7 +34,8 @@ class LLM:
     def __init__(self, model: Union[str, ModelConfig], *, device: Optional[str] = None, comm=None,
                  max_batch_size: int = 64, max_input_len: int = 2048, max_kv_cache_capacity: int = 2304,
                  page_size: int = 64, max_num_tokens: int = 8192, random_init_seed: Optional[int] = 0,
-                 tokenizer=None, kv_pages: Optional[int] = None):
+                 tokenizer=None, kv_pages: Optional[int] = None, enable_in_flight_batching: bool = False,
+                 enable_prefix_cache: bool = False, scheduling: Optional[dict] = None):
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.device = torch.device(device)
@@ -51,6 +52,72 @@ class LLM:
         self.kv = KVCacheManager(self.cfg, total_pages, page_size, max_seats=max_batch_size,
                                  max_pages_per_seq=pages_per_seq, device=self.device)
         self.runner = ModelRunner(self.model, self.kv, self.device, max_num_tokens=max_num_tokens)
+        self.engine = None
+        if enable_in_flight_batching:
+            self._start_engine(enable_prefix_cache, scheduling or {})
+
+    # ---- in-flight batching --------------------------------------------------------------------------
+    def _start_engine(self, enable_prefix_cache: bool, scheduling: dict) -> None:
+        """Start the native request engine (actor thread) over a model session."""
+        from . import native as rt
+        from .session import ModelSession
+        eos = self.cfg.eos_token_id
+        eos_ids = eos if isinstance(eos, (list, tuple)) else [eos]
+        cfg = rt.EngineConfig()
+        cfg.max_batch_size = self.max_batch_size
+        opts = rt.SchedulingOptions()
+        for k, v in scheduling.items():
+            if k == "mode":
+                v = {"auto": rt.IfbSchedulingMode.Auto, "mixed": rt.IfbSchedulingMode.Mixed,
+                     "prefill_first": rt.IfbSchedulingMode.PrefillFirst, "single_cohort": rt.IfbSchedulingMode.SingleCohort}[v]
+            elif k == "policy":
+                v = {"fcfs": rt.SchedulingPolicy.Fcfs, "priority": rt.SchedulingPolicy.Priority}[v]
+            elif k == "preemption":
+                v = {"none": rt.PreemptionMode.NoPreemption, "pause": rt.PreemptionMode.Pause}[v]
+            setattr(opts, k, v)
+        cfg.scheduling = opts
+        self._rt = rt
+        self.engine = rt.RequestEngine(cfg, lambda: ModelSession(self.runner, eos_ids, enable_prefix_cache, self.max_input_len))
+
+    def _native_request(self, ids, sp: SamplingParams, priority: int = 0):
+        r = self._rt.GenerationRequest()
+        r.prompt_ids = [int(t) for t in ids]
+        r.max_tokens, r.temperature, r.top_k, r.top_p = sp.max_tokens, sp.temperature, sp.top_k, sp.top_p
+        r.seed, r.ignore_eos, r.stop_token_ids, r.priority = sp.seed, sp.ignore_eos, list(sp.stop_token_ids), priority
+        return r
+
+    def submit(self, prompt, sampling_params: Optional[SamplingParams] = None, priority: int = 0):
+        """Queue one request on the in-flight-batching engine; returns the native ``RequestHandle``
+        (``.get()``, ``.stream()``, ``.cancel()``, ``.stats()``).  Raises when the engine refuses it."""
+        if self.engine is None:
+            raise RuntimeError("LLM was built without enable_in_flight_batching")
+        ids = self._encode([prompt])[0]
+        h, why = self.engine.submit(self._native_request(ids, sampling_params or SamplingParams(), priority))
+        if h is None:
+            raise RuntimeError(why)
+        return h
+
+    def generate_stream(self, prompt, sampling_params: Optional[SamplingParams] = None, on_metrics=None):
+        """Yield ``(token_ids, text_delta)`` chunks as they are produced."""
+        h = self.submit(prompt, sampling_params)
+        ch = h.stream()
+        pending = b""
+        while True:
+            c = ch.wait_pop(1.0)
+            if c is None:
+                continue
+            text = None
+            if self.tokenizer is not None and hasattr(self.tokenizer, "id_to_bytes"):
+                for t in c.token_ids:
+                    pending += bytes(self.tokenizer.id_to_bytes(t))
+                n = self._rt.utf8_complete_prefix(pending)        # never emit half a UTF-8 character
+                text, pending = pending[:n].decode("utf-8", "replace"), pending[n:]
+            if c.token_ids or c.finished:
+                yield c.token_ids, text
+            if c.finished:
+                break
+        if on_metrics is not None:
+            on_metrics(ch.metrics())
 
     # ------------------------------------------------------------------------------------------
     def _encode(self, prompts) -> List[List[int]]:
@@ -69,6 +136,21 @@ class LLM:
                  ) -> List[RequestOutput]:
         """Generate for a batch of prompts (static batch: one prefill wave, then decode)."""
         sp = sampling_params or SamplingParams()
+        if self.engine is not None:
+            if isinstance(prompts, torch.Tensor):
+                prompts = prompts.tolist()
+            ids = self._encode(prompts)
+            handles = [self.submit(p, sp) for p in ids]
+            outs = []
+            for p, h in zip(ids, handles):
+                toks = h.get(3600.0)
+                st = h.stats()
+                reason = {self._rt.FinishReason.Length: "length", self._rt.FinishReason.EndId: "stop",
+                          self._rt.FinishReason.StopWords: "stop", self._rt.FinishReason.Cancelled: "cancelled",
+                          self._rt.FinishReason.Error: "error"}.get(h.reason(), "length")
+                text = self.tokenizer.decode(toks) if self.tokenizer is not None else None
+                outs.append(RequestOutput(p, toks, text, reason, st.ttft_s, max(st.total_s - st.ttft_s, 0.0)))
+            return outs
         if isinstance(prompts, torch.Tensor):
             outs = []
             for b0 in range(0, prompts.shape[0], self.max_batch_size):
@@ -129,6 +211,9 @@ class LLM:
         return outs
 
     def close(self):
+        if self.engine is not None:
+            self.engine.shutdown()
+            self.engine = None
         self.runner = None
         self.kv = None
         self.model = None

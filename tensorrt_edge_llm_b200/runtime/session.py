@@ -1,0 +1,146 @@
+"""The model-side implementation of the scheduler's ``RuntimeSession`` seam.
+
+The native ``RequestEngine`` plans steps (chunked prefill + decode rows, compact layout) and
+calls ``execute(plan)``; this session turns a plan into one ragged model step through
+``ModelRunner``, samples the rows that produce tokens and reports deltas.  KV pages come from
+the native ``KVPageTable``; with ``enable_prefix_cache`` full prompt pages are shared between
+requests through the native ``PrefixCache``.
+
+Parity: ``RankRuntimeSession`` (``cpp/runtime/runtimeSession.{h,cpp}``: admit :325, execute :628,
+executeContext/Decode/Compact) and the context-cache request flow
+(``cpp/runtime/contextCacheRequest.*``).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import ops
+from ..ops.meta import build_step_meta
+from . import native as rt
+from .runner import ModelRunner, SamplingParams
+
+
+class _Seq:
+    __slots__ = ("req", "request_id", "tokens", "generated", "last_token", "finished")
+
+    def __init__(self, req, request_id):
+        self.req, self.request_id = req, request_id
+        self.tokens: List[int] = list(req.prompt_ids)
+        self.generated = 0
+        self.last_token: Optional[int] = None
+        self.finished = False
+
+
+class ModelSession(rt.RuntimeSession):
+    def __init__(self, runner: ModelRunner, eos_ids=(), enable_prefix_cache: bool = False, max_input_len: int = 2048):
+        super().__init__()
+        self.runner = runner
+        self.kv = runner.kv
+        self.eos = set(int(e) for e in eos_ids if e is not None)
+        self.max_input_len = max_input_len
+        self.slots = rt.ResidentSlotPool(self.kv.max_seats)
+        self.seqs: Dict[int, _Seq] = {}
+        self.prefix = rt.PrefixCache(self.kv.native.allocator(), self.kv.page_size, 4096) if (
+            enable_prefix_cache and getattr(self.kv, "native", None) is not None) else None
+
+    # ---- seam ------------------------------------------------------------------------------------
+    def capabilities(self):
+        c = rt.SessionCapabilities()
+        c.compact = True
+        c.max_batch_size = self.kv.max_seats
+        c.max_input_length = self.max_input_len
+        c.kv_page_size = self.kv.page_size
+        c.max_kv_tokens = self.kv.max_pages_per_seq * self.kv.page_size
+        return c
+
+    def admit(self, request_id, req):
+        r = rt.AdmissionResult()
+        n = len(req.prompt_ids)
+        need = n + req.max_tokens
+        if n > self.max_input_len or need > self.kv.max_pages_per_seq * self.kv.page_size:
+            r.admitted, r.retry_later, r.reason = False, False, "EDGELLM_INPUT_TOO_LONG: prompt + max_tokens exceed the KV capacity"
+            return r
+        slot = self.slots.acquire()
+        if slot < 0:
+            r.admitted, r.retry_later, r.reason = False, True, "no free seat"
+            return r
+        reused = 0
+        try:
+            if self.prefix is not None:
+                m = self.prefix.lookup(list(req.prompt_ids))
+                if m.tokens:
+                    self.kv.adopt_prefix(slot, m.pages, m.tokens)
+                    reused = m.tokens
+            self.kv.reserve(slot, need)                   # capacity is reserved at seat time: no eviction later
+        except (MemoryError, RuntimeError) as e:
+            self.kv.free(slot)
+            self.slots.release(slot)
+            if self.prefix is not None and self.prefix.evict(8):
+                r.admitted, r.retry_later, r.reason = False, True, "KV pool full (evicted cached prefixes)"
+            else:
+                r.admitted, r.retry_later, r.reason = False, True, f"KV pool full: {e}"
+            return r
+        self.seqs[slot] = _Seq(req, request_id)
+        r.admitted, r.slot, r.reused_tokens = True, slot, reused
+        return r
+
+    def execute(self, plan):
+        seats, token_lists, producers = [], [], []
+        for s in plan.seqs:
+            q = self.seqs[s.slot]
+            if s.kind == rt.WorkKind.Context:
+                toks = q.tokens[s.start:s.start + s.length]
+                produces = s.last_chunk
+            else:
+                toks = [q.last_token]
+                produces = True
+            seats.append(s.slot)
+            token_lists.append(toks)
+            producers.append(produces)
+        logits = self.runner.step(seats, token_lists)      # one row per sequence (its last token)
+        rows = [i for i, p in enumerate(producers) if p]
+        out = rt.StepResult()
+        deltas = []
+        if rows:
+            sel = logits[rows] if len(rows) != logits.shape[0] else logits
+            new = self._sample(sel, [self.seqs[seats[i]] for i in rows])
+            for i, tok in zip(rows, new):
+                q = self.seqs[seats[i]]
+                q.generated += 1
+                q.last_token = tok
+                q.tokens.append(tok)
+                d = rt.TokenDelta()
+                d.slot, d.tokens = seats[i], [tok]
+                if not q.req.ignore_eos and (tok in self.eos or tok in q.req.stop_token_ids):
+                    d.finished = True
+                    d.reason = rt.FinishReason.EndId if tok in self.eos else rt.FinishReason.StopWords
+                deltas.append(d)
+        # a finished prefill publishes its full prompt pages for reuse
+        if self.prefix is not None:
+            for s in plan.seqs:
+                if s.kind == rt.WorkKind.Context and s.last_chunk:
+                    q = self.seqs[s.slot]
+                    self.prefix.insert(list(q.req.prompt_ids), len(q.req.prompt_ids), self.kv.pages_of(s.slot))
+        out.deltas = deltas
+        return out
+
+    def release(self, slot):
+        if slot in self.seqs:
+            del self.seqs[slot]
+            self.kv.free(slot)
+            self.slots.release(slot)
+
+    # ---- sampling --------------------------------------------------------------------------------
+    def _sample(self, logits: torch.Tensor, seqs: List[_Seq]) -> List[int]:
+        if all(q.req.temperature < 1e-3 for q in seqs):
+            return [int(t) for t in ops.argmax(logits).tolist()]
+        n = logits.shape[0]
+        dev = logits.device
+        temp = torch.tensor([q.req.temperature for q in seqs], device=dev)
+        topk = torch.tensor([q.req.top_k for q in seqs], device=dev, dtype=torch.int32)
+        topp = torch.tensor([q.req.top_p for q in seqs], device=dev)
+        # the uniform depends on (seed, request, step) only, so batching never changes a request's draws
+        u = torch.tensor([rt.request_stable_uniform(q.req.seed, q.request_id, q.generated) for q in seqs], device=dev)
+        return [int(t) for t in ops.sample(logits, temp, topk, topp, u).tolist()]
