@@ -68,7 +68,12 @@ def load_weights(model: nn.Module, model_dir: str, strict: bool = True) -> List[
                 bundles.append(b)
             if all(b is not None for b in bundles):
                 mod.load_from(bundles)   # type: ignore[arg-type]
-    lin_prefixes = tuple(n + "." for n, m in model.named_modules() if isinstance(m, LinearBase))
+    custom_prefixes = []
+    for mod_name, mod in model.named_modules():
+        if hasattr(mod, "load_checkpoint") and not isinstance(mod, LinearBase):
+            if mod.load_checkpoint(fetch):
+                custom_prefixes.append(mod_name + ".w")       # stacked expert tensors are filled by the hook
+    lin_prefixes = tuple([n + "." for n, m in model.named_modules() if isinstance(m, LinearBase)] + custom_prefixes)
     for pname, p in list(model.named_parameters()) + list(model.named_buffers()):
         if pname.startswith(lin_prefixes):
             continue
@@ -107,9 +112,9 @@ def init_random_weights(model: nn.Module, seed: int = 0, std: float = 0.02) -> n
             mod.weight.data.copy_(_randn_chunked(tuple(mod.weight.shape), g, std, mod.weight.device).to(mod.weight.dtype))
         elif isinstance(mod, nn.Embedding):
             mod.weight.data.copy_(_randn_chunked(tuple(mod.weight.shape), g, std, mod.weight.device).to(mod.weight.dtype))
-    for pname, p in model.named_parameters():
-        if getattr(p, "_random_init", None) is not None:
-            p._random_init(p, g)
+    for name, mod in model.named_modules():
+        if hasattr(mod, "random_init") and not isinstance(mod, LinearBase):
+            mod.random_init(g, std)
     return model
 
 

@@ -310,7 +310,7 @@ class ModelConfig:
             sliding_window=llm.get("sliding_window") if llm.get("use_sliding_window", False) else None,
             hidden_act=llm.get("hidden_act", llm.get("mlp_hidden_act", "silu")),
             dtype=torch_dtype,
-            num_experts=int(llm.get("num_experts", llm.get("n_routed_experts", 0)) or 0),
+            num_experts=int(llm.get("num_experts") or llm.get("num_local_experts") or llm.get("n_routed_experts") or 0),
             num_experts_per_tok=int(llm.get("num_experts_per_tok", 0) or 0),
             moe_intermediate_size=int(llm.get("moe_intermediate_size", 0) or 0),
             norm_topk_prob=bool(llm.get("norm_topk_prob", True)),

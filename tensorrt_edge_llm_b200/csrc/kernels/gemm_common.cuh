@@ -22,6 +22,10 @@ struct GemmParams {
     float* ws;
     int* counters;
     int* status;
+    // Grouped (mixture-of-experts) mode: 128-row A tile `ta` multiplies the weight block of expert
+    // tile_expert[ta] (rows [e * group_rows_b, (e+1) * group_rows_b) of the B tensor); -1 = unused tile.
+    const int* tile_expert;
+    int group_rows_b;
 };
 
 constexpr int kBM = 128;
@@ -32,6 +36,8 @@ constexpr int kRasterGroup = 8;
 
 struct TileCoord {
     int a0, b0, kb0, kb1, tile, split;
+    int brow;      // first row of the B tensor for this tile
+    bool skip;     // grouped mode: tile beyond the rows in use
 };
 
 __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int t) {
@@ -50,6 +56,13 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int t) {
     c.kb0 = c.split * p.kb_per_split;
     c.kb1 = min(p.kb_total, c.kb0 + p.kb_per_split);
     c.b0 = tb;   // multiplied by BN by the caller
+    c.brow = -1;
+    c.skip = false;
+    if (p.tile_expert) {
+        const int e = p.tile_expert[ta];
+        c.skip = e < 0;
+        c.brow = e * p.group_rows_b;     // caller adds tb * BN
+    }
     return c;
 }
 
@@ -150,7 +163,13 @@ __device__ __forceinline__ void gemm_epilogue_role(const GemmParams& p, uint32_t
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
         const TileCoord tc = decode_tile(p, t);
+        if (tc.skip) continue;
         const int b0 = tc.b0 * BN;
+        GemmParams pt = p;                  // grouped mode: per-expert scale / bias vectors
+        if (p.tile_expert && tc.brow > 0) {
+            if (p.alpha) pt.alpha = p.alpha + tc.brow;
+            if (p.bias) pt.bias = reinterpret_cast<const uint16_t*>(p.bias) + tc.brow;
+        }
         if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout)) break;
         tc_fence_after_sync();
         const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kAccStride;
@@ -176,8 +195,8 @@ __device__ __forceinline__ void gemm_epilogue_role(const GemmParams& p, uint32_t
                 const int col0 = b0 + c * 32;
                 int nvalid = min(min(32, BN - c * 32), p.rows_b - col0);
                 if (row_ok && nvalid > 0) {
-                    if (p.out_bf16) epilogue_store<__nv_bfloat16>(p, v, row, col0, nvalid);
-                    else epilogue_store<__half>(p, v, row, col0, nvalid);
+                    if (p.out_bf16) epilogue_store<__nv_bfloat16>(pt, v, row, col0, nvalid);
+                    else epilogue_store<__half>(pt, v, row, col0, nvalid);
                 }
             }
             tc_fence_before_sync();
@@ -244,8 +263,8 @@ __device__ __forceinline__ void gemm_epilogue_role(const GemmParams& p, uint32_t
                     const int col0 = b0 + c * 32;
                     int nvalid = min(ncol, p.rows_b - col0);
                     if (row_ok && nvalid > 0) {
-                        if (p.out_bf16) epilogue_store<__nv_bfloat16>(p, v, row, col0, nvalid);
-                        else epilogue_store<__half>(p, v, row, col0, nvalid);
+                        if (p.out_bf16) epilogue_store<__nv_bfloat16>(pt, v, row, col0, nvalid);
+                        else epilogue_store<__half>(pt, v, row, col0, nvalid);
                     }
                 }
             }

@@ -91,8 +91,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const TileCoord tc = decode_tile(p, t);
+                if (tc.skip) continue;
                 const int ta = tc.a0 / kBM;
-                const int b0 = tc.b0 * BN;
+                const int b0 = (tc.brow >= 0 ? tc.brow : 0) + tc.b0 * BN;      // row of the B tensor
                 for (int kb = tc.kb0; kb < tc.kb1; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
                         ok = false;
@@ -129,6 +130,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const TileCoord tc = decode_tile(p, t);
+                if (tc.skip) continue;
                 if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout)) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * kAccStride;
@@ -366,4 +368,36 @@ extern "C" int telb_gemm_nvfp4(const void* xq, const void* x_sf, const void* wq,
         case 64: return launch_nvfp4<64, 7>(ta, tb, sfa, sfb, k64, k64, p, stream);
         default: return launch_nvfp4<128, 5>(ta, tb, sfa, sfb, k64, k64, p, stream);
     }
+}
+
+// Grouped NVFP4 GEMM for mixture-of-experts (see telb_gemm_f16_grouped): xq [rows_pad, K/2] with
+// atom-layout scales over the padded row space, wq [experts * N, K/2] with scales over experts * N rows.
+extern "C" int telb_gemm_nvfp4_grouped(const void* xq, const void* x_sf, const void* wq, const void* w_sf, void* out,
+                                       int rows_pad, int N, int K, int experts, const int* tile_expert, const float* alpha,
+                                       int out_bf16, int* status, cudaStream_t stream) {
+    if (rows_pad <= 0) return 0;
+    if (K % 32 || rows_pad % kBM || N % 128) return fail("telb_gemm_nvfp4_grouped: K % 32, rows_pad % 128 and N % 128 must be 0");
+    GemmParams p{};
+    p.k = K;
+    p.kb_total = (K + kFp4BK - 1) / kFp4BK;
+    p.c = out;
+    p.alpha = alpha;
+    p.out_bf16 = out_bf16;
+    p.status = status;
+    p.rows_a = rows_pad;
+    p.rows_b = N;
+    p.ldc_lane = N;
+    p.ldc_col = 1;
+    p.tile_expert = tile_expert;
+    p.group_rows_b = N;
+    const uint64_t kbytes = (uint64_t)K / 2;
+    CUtensorMap ta, tb;
+    if (make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, rows_pad, kbytes, kbytes, kBM, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+    if (make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, (uint64_t)experts * N, kbytes, kbytes, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+    p.tiles_a = rows_pad / kBM;
+    p.tiles_b = N / 128;
+    p.splits = 1;
+    p.kb_per_split = p.kb_total;
+    const int k64 = telb_nvfp4_k64_pad(K);
+    return launch_nvfp4<128, 5>(ta, tb, (const uint8_t*)x_sf, (const uint8_t*)w_sf, k64, k64, p, stream);
 }

@@ -74,6 +74,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const TileCoord tc = decode_tile(p, t);
+                if (tc.skip) continue;
+                const int brow = (tc.brow >= 0 ? tc.brow : 0) + tc.b0 * BN;
                 for (int kb = tc.kb0; kb < tc.kb1; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
                         ok = false;
@@ -82,7 +84,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                     uint8_t* sa = smem + stage * kStageBytes;
                     mbar_expect_tx(&full_bar[stage], kStageBytes);
                     tma_load_2d(sa, &tma_a, &full_bar[stage], kb * kBK, tc.a0);
-                    tma_load_2d(sa + kATileBytes, &tma_b, &full_bar[stage], kb * kBK, tc.b0 * BN);
+                    tma_load_2d(sa + kATileBytes, &tma_b, &full_bar[stage], kb * kBK, brow);
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1;
@@ -101,6 +103,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const TileCoord tc = decode_tile(p, t);
+                if (tc.skip) continue;
                 if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout)) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * kAccStride;
@@ -240,4 +243,39 @@ extern "C" int telb_gemm_f16(const void* x, const void* w, void* out, int M, int
         case 128: return launch_gemm<128, 6>(ta, tb, p, stream);
         default: return launch_gemm<256, 4>(ta, tb, p, stream);
     }
+}
+
+// Grouped form for mixture-of-experts: x [rows_pad, K] is the routed activations in 128-row padded
+// expert segments, w [experts * N, K] the stacked expert weights, tile_expert[rows_pad / 128] the
+// expert of every row tile (-1 = unused).  out [rows_pad, N].  alpha / bias: [experts * N] or null.
+extern "C" int telb_gemm_f16_grouped(const void* x, const void* w, void* out, int rows_pad, int N, int K, int experts,
+                                     const int* tile_expert, const float* alpha, const void* bias, int is_bf16, int* status,
+                                     cudaStream_t stream) {
+    if (rows_pad <= 0) return 0;
+    if (K % 8 || rows_pad % kBM || N % 8) return fail("telb_gemm_f16_grouped: K % 8, rows_pad % 128 and N % 8 must be 0");
+    const CUtensorMapDataType dt = is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    GemmParams p{};
+    p.k = K;
+    p.kb_total = (K + kBK - 1) / kBK;
+    p.c = out;
+    p.alpha = alpha;
+    p.bias = bias;
+    p.out_bf16 = is_bf16;
+    p.status = status;
+    p.rows_a = rows_pad;
+    p.rows_b = N;
+    p.ldc_lane = N;
+    p.ldc_col = 1;
+    p.tile_expert = tile_expert;
+    p.group_rows_b = N;
+    const int bn = N >= 256 && N % 256 == 0 ? 256 : 128;
+    if (N % bn) return fail("telb_gemm_f16_grouped: N must be a multiple of 128");
+    CUtensorMap ta, tb;
+    if (make_tmap_2d(&ta, dt, 2, x, rows_pad, K, (uint64_t)K * 2, kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+    if (make_tmap_2d(&tb, dt, 2, w, (uint64_t)experts * N, K, (uint64_t)K * 2, bn, kBK, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+    p.tiles_a = rows_pad / kBM;
+    p.tiles_b = N / bn;
+    p.splits = 1;
+    p.kb_per_split = p.kb_total;
+    return bn == 256 ? launch_gemm<256, 4>(ta, tb, p, stream) : launch_gemm<128, 6>(ta, tb, p, stream);
 }

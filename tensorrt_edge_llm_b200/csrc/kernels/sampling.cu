@@ -1,0 +1,215 @@
+// Token sampling on the device: per-row temperature / top-k / top-p with a caller-supplied uniform
+// per row (so a request's draws never depend on its batch position), plus the token-bitmask and
+// logit-bias helpers used by guided decoding.
+//
+// One CTA per row:  radix-select the k-th largest logit (k = top_k, or 1024 when only top-p is
+// set — the same candidate cap as the reference), gather the candidates into shared memory, bitonic
+// sort them (value descending, index ascending), softmax with temperature, cut at top-p, sample.
+// Rows with temperature < 1e-3 are greedy.  Among logits exactly equal to the k-th largest value,
+// which ones enter the candidate set is unspecified.
+//
+// Reference counterpart: cpp/sampler/sampling.cu (topKStage1/2, topP kernels, applyTokenBitmask,
+// applyLogitBias); semantics cpp/sampler/sampling.h:56-160 (kMaxSamplingTopK 1024).
+#include "host_utils.h"
+#include "tc5_common.cuh"
+
+namespace telb {
+
+constexpr int kSampleThreads = 1024;
+constexpr int kMaxCand = 1024;
+
+__device__ __forceinline__ uint32_t order_key(float v) {
+    const uint32_t u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_value(uint32_t k) {
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
+}
+
+template <typename T>
+__device__ __forceinline__ float load_logit(const T* p, int i) {
+    if constexpr (sizeof(T) == 4) return static_cast<float>(p[i]);
+    else return Cvt<T>::to_f(p[i]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kSampleThreads)
+sample_kernel(const T* __restrict__ logits, long long stride, int vocab, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ uniforms,
+              int* __restrict__ out) {
+    pdl_prologue();
+    __shared__ unsigned long long cand[kMaxCand];
+    __shared__ float scan[kMaxCand];
+    __shared__ int hist[256];
+    __shared__ int s_misc[4];
+    __shared__ float s_wsum[32];
+    const int row = blockIdx.x;
+    const int tid = threadIdx.x;
+    const T* p = logits + (size_t)row * stride;
+    const float temp = temperature[row];
+    const bool greedy = temp < 1e-3f;
+    int k = greedy ? 1 : top_k[row];
+    if (k <= 0 || k > kMaxCand) k = kMaxCand;
+    if (k > vocab) k = vocab;
+
+    // ---- radix select: key of the k-th largest logit ----
+    uint32_t prefix = 0, mask = 0;
+    int remaining = k;
+    for (int pass = 3; pass >= 0; --pass) {
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        for (int i = tid; i < vocab; i += kSampleThreads) {
+            const uint32_t key = order_key(load_logit(p, i));
+            if ((key & mask) == prefix) atomicAdd(&hist[(key >> (8 * pass)) & 0xFF], 1);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int cum = 0, bin = 255;
+            for (; bin > 0; --bin) {
+                if (cum + hist[bin] >= remaining) break;
+                cum += hist[bin];
+            }
+            s_misc[0] = bin;
+            s_misc[1] = remaining - cum;
+        }
+        __syncthreads();
+        prefix |= static_cast<uint32_t>(s_misc[0]) << (8 * pass);
+        mask |= 0xFFu << (8 * pass);
+        remaining = s_misc[1];
+        __syncthreads();
+    }
+    const uint32_t thresh = prefix;         // `remaining` of the keys equal to it are wanted
+    // ---- gather candidates ----
+    if (tid == 0) { s_misc[2] = 0; s_misc[3] = 0; }
+    cand[tid] = 0ull;
+    __syncthreads();
+    for (int i = tid; i < vocab; i += kSampleThreads) {
+        const uint32_t key = order_key(load_logit(p, i));
+        bool take = key > thresh;
+        if (key == thresh) take = atomicAdd(&s_misc[3], 1) < remaining;
+        if (take) {
+            const int slot = atomicAdd(&s_misc[2], 1);
+            if (slot < kMaxCand) cand[slot] = (static_cast<unsigned long long>(key) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(i));
+        }
+    }
+    __syncthreads();
+    // ---- bitonic sort, descending ----
+    for (int size = 2; size <= kMaxCand; size <<= 1) {
+        for (int strd = size >> 1; strd > 0; strd >>= 1) {
+            const int j = tid ^ strd;
+            if (j > tid) {
+                const unsigned long long a = cand[tid], b = cand[j];
+                const bool desc = (tid & size) == 0;
+                if (desc ? a < b : a > b) { cand[tid] = b; cand[j] = a; }
+            }
+            __syncthreads();
+        }
+    }
+    if (greedy) {
+        if (tid == 0) out[row] = static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(cand[0] & 0xFFFFFFFFull));
+        return;
+    }
+    // ---- softmax over the candidates, inclusive scan ----
+    const float vmax = key_value(static_cast<uint32_t>(cand[0] >> 32));
+    float pr = 0.f;
+    if (tid < k) pr = __expf((key_value(static_cast<uint32_t>(cand[tid] >> 32)) - vmax) / temp);
+    float v = pr;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float n = __shfl_up_sync(0xffffffffu, v, o);
+        if ((tid & 31) >= o) v += n;
+    }
+    if ((tid & 31) == 31) s_wsum[tid >> 5] = v;
+    __syncthreads();
+    if (tid < 32) {
+        float w = s_wsum[tid];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float n = __shfl_up_sync(0xffffffffu, w, o);
+            if (tid >= o) w += n;
+        }
+        s_wsum[tid] = w;
+    }
+    __syncthreads();
+    const float cum = v + ((tid >> 5) > 0 ? s_wsum[(tid >> 5) - 1] : 0.f);
+    scan[tid] = cum;
+    const float total = s_wsum[31];
+    // ---- top-p cut: keep the sorted prefix whose mass before each token is < top_p ----
+    const float tp = top_p[row];
+    const bool kept = tid < k && (tp >= 1.f || (cum - pr) < tp * total);
+    const int n_kept = __syncthreads_count(kept);
+    const float kept_total = scan[max(n_kept, 1) - 1];
+    const float target = uniforms[row] * kept_total;
+    const int below = __syncthreads_count(tid < n_kept && cum <= target);
+    if (tid == 0) {
+        const int pick = min(below, max(n_kept, 1) - 1);
+        out[row] = static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(cand[pick] & 0xFFFFFFFFull));
+    }
+}
+
+// logits[row, i] = -1e30 where bit i of bitmask[row] is 0 (guided decoding); in place.
+template <typename T>
+__global__ void token_bitmask_kernel(T* __restrict__ logits, long long stride, int vocab, const int* __restrict__ bitmask, int words) {
+    pdl_prologue();
+    const int row = blockIdx.y;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < vocab; i += gridDim.x * blockDim.x) {
+        if (!((bitmask[(size_t)row * words + (i >> 5)] >> (i & 31)) & 1)) {
+            if constexpr (sizeof(T) == 4) logits[(size_t)row * stride + i] = -1e30f;
+            else logits[(size_t)row * stride + i] = Cvt<T>::from_f(-6e4f);      // most negative finite half-range value
+        }
+    }
+}
+
+// logits[row, ids[j]] += bias[j] for the sparse bias list of each row.
+template <typename T>
+__global__ void logit_bias_kernel(T* __restrict__ logits, long long stride, const int* __restrict__ ids, const float* __restrict__ bias,
+                                  const int* __restrict__ row_offsets) {
+    pdl_prologue();
+    const int row = blockIdx.x;
+    for (int j = row_offsets[row] + threadIdx.x; j < row_offsets[row + 1]; j += blockDim.x) {
+        T* q = logits + (size_t)row * stride + ids[j];
+        if constexpr (sizeof(T) == 4) *q += bias[j];
+        else *q = Cvt<T>::from_f(Cvt<T>::to_f(*q) + bias[j]);
+    }
+}
+
+}  // namespace telb
+
+using namespace telb;
+
+// dtype: 0 = fp16, 1 = bf16, 2 = fp32
+extern "C" int telb_sample(const void* logits, long long stride, int rows, int vocab, const float* temperature,
+                           const int* top_k, const float* top_p, const float* uniforms, int* out, int dtype,
+                           cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (dtype == 2)
+        TELB_LAUNCH("sample_kernel", (sample_kernel<float>), dim3(rows), dim3(kSampleThreads), 0, stream, (const float*)logits, stride, vocab,
+                    temperature, top_k, top_p, uniforms, out);
+    else if (dtype == 1)
+        TELB_LAUNCH("sample_kernel", (sample_kernel<__nv_bfloat16>), dim3(rows), dim3(kSampleThreads), 0, stream, (const __nv_bfloat16*)logits,
+                    stride, vocab, temperature, top_k, top_p, uniforms, out);
+    else
+        TELB_LAUNCH("sample_kernel", (sample_kernel<__half>), dim3(rows), dim3(kSampleThreads), 0, stream, (const __half*)logits, stride, vocab,
+                    temperature, top_k, top_p, uniforms, out);
+    return 0;
+}
+
+extern "C" int telb_apply_token_bitmask(void* logits, long long stride, int rows, int vocab, const int* bitmask, int dtype,
+                                        cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const int words = (vocab + 31) / 32;
+    const dim3 grid(64, rows), blk(256);
+    if (dtype == 2) TELB_LAUNCH("token_bitmask_kernel", (token_bitmask_kernel<float>), grid, blk, 0, stream, (float*)logits, stride, vocab, bitmask, words);
+    else if (dtype == 1) TELB_LAUNCH("token_bitmask_kernel", (token_bitmask_kernel<__nv_bfloat16>), grid, blk, 0, stream, (__nv_bfloat16*)logits, stride, vocab, bitmask, words);
+    else TELB_LAUNCH("token_bitmask_kernel", (token_bitmask_kernel<__half>), grid, blk, 0, stream, (__half*)logits, stride, vocab, bitmask, words);
+    return 0;
+}
+
+extern "C" int telb_apply_logit_bias(void* logits, long long stride, int rows, const int* ids, const float* bias,
+                                     const int* row_offsets, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (dtype == 2) TELB_LAUNCH("logit_bias_kernel", (logit_bias_kernel<float>), dim3(rows), dim3(128), 0, stream, (float*)logits, stride, ids, bias, row_offsets);
+    else if (dtype == 1) TELB_LAUNCH("logit_bias_kernel", (logit_bias_kernel<__nv_bfloat16>), dim3(rows), dim3(128), 0, stream, (__nv_bfloat16*)logits, stride, ids, bias, row_offsets);
+    else TELB_LAUNCH("logit_bias_kernel", (logit_bias_kernel<__half>), dim3(rows), dim3(128), 0, stream, (__half*)logits, stride, ids, bias, row_offsets);
+    return 0;
+}

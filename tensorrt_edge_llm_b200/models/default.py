@@ -43,14 +43,19 @@ class Attention(nn.Module):
         self.head_dim = cfg.head_dim
         self.num_q_heads = cfg.num_attention_heads // tp
         self.num_kv_heads = max(cfg.num_key_value_heads // tp, 1)
+        kv_ranges = None
         if cfg.num_key_value_heads % tp:
-            raise ValueError("KV heads must be divisible by the TP degree")
+            # fewer KV heads than ranks: each KV head is replicated on tp / Hkv consecutive ranks
+            if tp % cfg.num_key_value_heads:
+                raise ValueError("the TP degree must be a multiple or a divisor of the KV head count")
+            kvh = cfg.tp_rank // (tp // cfg.num_key_value_heads)
+            kv_ranges = [None, (kvh * cfg.head_dim, (kvh + 1) * cfg.head_dim), (kvh * cfg.head_dim, (kvh + 1) * cfg.head_dim)]
         self.scale = cfg.head_dim ** -0.5
         self.sliding_window = cfg.sliding_window
         self.eps = cfg.rms_norm_eps
         h = cfg.hidden_size
         self.qkv_proj = make_linear(cfg, f"{prefix}.qkv_proj", h, [cfg.q_size, cfg.kv_size, cfg.kv_size], TPMode.COL,
-                                    sources=["q_proj", "k_proj", "v_proj"], bias=cfg.attention_bias)
+                                    sources=["q_proj", "k_proj", "v_proj"], bias=cfg.attention_bias, row_ranges=kv_ranges)
         self.o_proj = make_linear(cfg, f"{prefix}.o_proj", cfg.q_size, [h], TPMode.ROW)
         if cfg.has_qk_norm:
             self.q_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, cfg.compute_dtype)
@@ -136,11 +141,13 @@ class CausalLM(nn.Module):
     # checkpoint module name → (fused layer attribute, ordered source names)
     packed_modules = {"qkv_proj": ["q_proj", "k_proj", "v_proj"], "gate_up_proj": ["gate_proj", "up_proj"]}
 
+    transformer_cls = None      # subclasses substitute their own decoder stack
+
     def __init__(self, cfg: ModelConfig, comm=None):
         super().__init__()
         self.cfg = cfg
         self.comm = comm or LocalComm()
-        self.model = Transformer(cfg)
+        self.model = (self.transformer_cls or Transformer)(cfg)
         # The LM head is vocabulary-sharded under TP; the sampler merges per-shard candidates.
         self.lm_head = make_linear(cfg, "lm_head", cfg.hidden_size, [cfg.vocab_size],
                                    TPMode.COL if cfg.tp_size > 1 and cfg.vocab_size % cfg.tp_size == 0 else TPMode.REPLICATED)

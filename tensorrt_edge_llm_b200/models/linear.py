@@ -41,20 +41,27 @@ class LinearBase(nn.Module):
     """Common bookkeeping: logical sizes, TP placement and the checkpoint modules it fuses."""
 
     def __init__(self, in_features: int, out_features: Sequence[int], tp_mode: TPMode, tp_size: int, tp_rank: int,
-                 sources: Optional[List[str]] = None, bias: bool = False):
+                 sources: Optional[List[str]] = None, bias: bool = False, row_ranges=None):
         super().__init__()
         self.tp_mode, self.tp_size, self.tp_rank = tp_mode, tp_size, tp_rank
         self.sources = sources
         self.full_in = in_features
         self.full_out = list(out_features)
+        # row_ranges[i] = (lo, hi) overrides the even column-parallel split of segment i (replicated KV heads)
+        self.row_ranges = row_ranges
         self.in_features = in_features // tp_size if tp_mode == TPMode.ROW else in_features
         self.out_sizes = [o // tp_size if tp_mode == TPMode.COL else o for o in out_features]
+        if row_ranges is not None:
+            self.out_sizes = [(r[1] - r[0]) if r is not None else s for r, s in zip(row_ranges, self.out_sizes)]
         self.out_features = sum(self.out_sizes)
         self.has_bias = bias
 
     # sharding of one source module's tensor (dim 0 = out, dim 1 = in)
-    def shard_out_in(self, t: torch.Tensor) -> torch.Tensor:
+    def shard_out_in(self, t: torch.Tensor, segment: int = 0) -> torch.Tensor:
         if self.tp_mode == TPMode.COL:
+            if self.row_ranges is not None and self.row_ranges[segment] is not None:
+                lo, hi = self.row_ranges[segment]
+                return t[lo:hi].contiguous()
             return _shard(t, 0, self.tp_rank, self.tp_size)
         if self.tp_mode == TPMode.ROW and t.dim() > 1:
             return _shard(t, 1, self.tp_rank, self.tp_size)
@@ -62,6 +69,17 @@ class LinearBase(nn.Module):
 
     def load_from(self, tensors: List[Dict[str, torch.Tensor]]) -> None:
         raise NotImplementedError
+
+    def _split_single_source(self, tensors):
+        """One checkpoint module that holds several logical segments stacked along the output dim
+        (e.g. a Mamba ``in_proj`` = [z | x | B | C | dt]): split it so each segment shards on its own."""
+        if len(tensors) != 1 or len(self.full_out) == 1:
+            return tensors
+        out, off = [], 0
+        for n in self.full_out:
+            out.append({k: (v[off:off + n] if v.dim() >= 1 and v.shape[0] == sum(self.full_out) else v) for k, v in tensors[0].items()})
+            off += n
+        return out
 
     def finalize(self) -> None:
         """Hook run once after loading and device placement (GPU-side repacks)."""
@@ -76,19 +94,20 @@ class Linear(LinearBase):
     """16-bit dense linear, ``y = x Wᵀ (+ b)``."""
 
     def __init__(self, in_features, out_features, tp_mode=TPMode.REPLICATED, tp_size=1, tp_rank=0, sources=None,
-                 bias=False, dtype=torch.bfloat16):
-        super().__init__(in_features, out_features, tp_mode, tp_size, tp_rank, sources, bias)
+                 bias=False, dtype=torch.bfloat16, row_ranges=None):
+        super().__init__(in_features, out_features, tp_mode, tp_size, tp_rank, sources, bias, row_ranges)
         self.weight = nn.Parameter(torch.empty(self.out_features, self.in_features, dtype=dtype), requires_grad=False)
         self.bias = nn.Parameter(torch.zeros(self.out_features, dtype=dtype), requires_grad=False) if bias else None
 
     def load_from(self, tensors):
-        ws = [self.shard_out_in(t["weight"]) for t in tensors]
+        tensors = self._split_single_source(tensors)
+        ws = [self.shard_out_in(t["weight"], i) for i, t in enumerate(tensors)]
         self.weight.data.copy_(torch.cat(ws, dim=0).to(self.weight.dtype))
         if self.bias is not None:
             bs = []
-            for t in tensors:
+            for i, t in enumerate(tensors):
                 b = t["bias"]
-                bs.append(_shard(b, 0, self.tp_rank, self.tp_size) if self.tp_mode == TPMode.COL else b)
+                bs.append(self.shard_out_in(b, i) if self.tp_mode == TPMode.COL else b)
             b = torch.cat(bs, dim=0)
             if self.tp_mode == TPMode.ROW and self.tp_rank != 0:
                 b = torch.zeros_like(b)       # the reduced sum must add the bias once
@@ -107,8 +126,8 @@ class NVFP4Linear(LinearBase):
     """
 
     def __init__(self, in_features, out_features, tp_mode=TPMode.REPLICATED, tp_size=1, tp_rank=0, sources=None,
-                 bias=False, dtype=torch.bfloat16, quantize_activations=True):
-        super().__init__(in_features, out_features, tp_mode, tp_size, tp_rank, sources, bias)
+                 bias=False, dtype=torch.bfloat16, quantize_activations=True, row_ranges=None):
+        super().__init__(in_features, out_features, tp_mode, tp_size, tp_rank, sources, bias, row_ranges)
         if self.in_features % 16:
             raise ValueError("NVFP4 needs in_features divisible by 16 on every rank")
         self.act_dtype = dtype
@@ -122,8 +141,8 @@ class NVFP4Linear(LinearBase):
         self._gpu_weight_sf = None      # scale factors repacked for the tensor-core kernel
 
     def load_from(self, tensors):
-        w = torch.cat([self.shard_out_in(t["weight"]) for t in tensors], dim=0)
-        sf = torch.cat([self.shard_out_in(t["weight_scale"].view(torch.uint8)) for t in tensors], dim=0)
+        w = torch.cat([self.shard_out_in(t["weight"], i) for i, t in enumerate(tensors)], dim=0)
+        sf = torch.cat([self.shard_out_in(t["weight_scale"].view(torch.uint8), i) for i, t in enumerate(tensors)], dim=0)
         self.weight.copy_(w.view(torch.uint8))
         self.weight_scale.copy_(sf.view(torch.float8_e4m3fn))
         self.weight_scale_2.copy_(torch.stack([t["weight_scale_2"].float().reshape(()) for t in tensors]))
@@ -183,8 +202,8 @@ class Int4AwqLinear(LinearBase):
     ``weight_scale [out, in/g]``, optional ``pre_quant_scale [in]``)."""
 
     def __init__(self, in_features, out_features, tp_mode=TPMode.REPLICATED, tp_size=1, tp_rank=0, sources=None,
-                 bias=False, dtype=torch.bfloat16, group_size=128):
-        super().__init__(in_features, out_features, tp_mode, tp_size, tp_rank, sources, bias)
+                 bias=False, dtype=torch.bfloat16, group_size=128, row_ranges=None):
+        super().__init__(in_features, out_features, tp_mode, tp_size, tp_rank, sources, bias, row_ranges)
         self.group = group_size
         self.register_buffer("weight", torch.zeros(self.out_features // 2, self.in_features, dtype=torch.uint8))
         self.register_buffer("weight_scale", torch.ones(self.out_features, self.in_features // group_size, dtype=dtype))
@@ -227,7 +246,7 @@ class Int4AwqLinear(LinearBase):
 
 def make_linear(cfg: ModelConfig, name: str, in_features: int, out_features: Sequence[int],
                 tp_mode: TPMode = TPMode.REPLICATED, sources: Optional[List[str]] = None, bias: bool = False,
-                quantizable: bool = True) -> LinearBase:
+                quantizable: bool = True, row_ranges=None) -> LinearBase:
     """Build the linear layer the checkpoint's quantisation calls for.  ``name`` is the fully
     qualified module name used for exclusion matching (``lm_head`` stays 16-bit unless the
     checkpoint says otherwise)."""
@@ -236,6 +255,8 @@ def make_linear(cfg: ModelConfig, name: str, in_features: int, out_features: Seq
     if name.endswith("lm_head"):
         qt = cfg.quant.lm_head_quant_type
     kw = dict(tp_mode=tp_mode, tp_size=tp_size, tp_rank=tp_rank, sources=sources, bias=bias, dtype=cfg.compute_dtype)
+    if row_ranges is not None:
+        kw["row_ranges"] = row_ranges
     if qt in (QUANT_NVFP4, QUANT_NVFP4_A16):
         return NVFP4Linear(in_features, out_features, quantize_activations=(qt == QUANT_NVFP4 and cfg.quant.quantize_activations), **kw)
     if qt == QUANT_INT4_AWQ:

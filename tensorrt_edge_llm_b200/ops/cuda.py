@@ -249,9 +249,6 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def sample(logits, temperature, top_k, top_p, uniforms):
-    from . import sampling_cuda
-    return sampling_cuda.sample(logits, temperature, top_k, top_p, uniforms)
 
 
 # ---- NVFP4 -----------------------------------------------------------------------------------
@@ -372,4 +369,153 @@ def gemm_skinny(x, weight, *, x_sf=None, w_sf=None, alpha=None, bias=None, resid
     _check(lib().telb_gemm_skinny(c_int(kind), _p(x), _p(x_sf), _p(weight), _p(w_sf), _p(out), c_int(m), c_int(n), c_int(k),
                                   _p(alpha), _p(bias), _p(residual), c_int(1 if dt == torch.bfloat16 else 0), _p(ws.status),
                                   c_int(ranks), _stream()), "gemm_skinny")
+    return out
+
+
+# ---- sampling ----------------------------------------------------------------------------------
+
+
+def _logit_dtype(t: torch.Tensor) -> int:
+    return 2 if t.dtype == torch.float32 else _is_bf16(t)
+
+
+def sample(logits, temperature, top_k, top_p, uniforms) -> torch.Tensor:
+    assert logits.dim() == 2 and logits.stride(1) == 1
+    rows, vocab = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _check(lib().telb_sample(_p(logits), c_ll(logits.stride(0)), c_int(rows), c_int(vocab),
+                             _p(temperature.to(torch.float32).contiguous()), _p(top_k.to(torch.int32).contiguous()),
+                             _p(top_p.to(torch.float32).contiguous()), _p(uniforms.to(torch.float32).contiguous()), _p(out),
+                             c_int(_logit_dtype(logits)), _stream()), "sample")
+    return out
+
+
+def apply_token_bitmask(logits: torch.Tensor, bitmask: torch.Tensor) -> torch.Tensor:
+    """In place: entries whose bit is 0 in ``bitmask [rows, ceil(V/32)]`` become very negative."""
+    _check(lib().telb_apply_token_bitmask(_p(logits), c_ll(logits.stride(0)), c_int(logits.shape[0]), c_int(logits.shape[1]),
+                                          _p(bitmask.to(torch.int32).contiguous()), c_int(_logit_dtype(logits)), _stream()),
+           "apply_token_bitmask")
+    return logits
+
+
+# ---- mixture of experts -------------------------------------------------------------------------
+
+
+def moe_route_softmax_topk(logits, top_k, renormalize=True, bias=None, sigmoid=False, n_group=1, topk_group=1,
+                           scaling=1.0):
+    logits = logits.contiguous()
+    t, e = logits.shape
+    w = torch.empty(t, top_k, dtype=torch.float32, device=logits.device)
+    idx = torch.empty(t, top_k, dtype=torch.int32, device=logits.device)
+    _check(lib().telb_moe_route(_p(logits), _p(w), _p(idx), _p(bias), c_int(t), c_int(e), c_int(top_k), c_int(int(renormalize)),
+                                c_int(int(sigmoid)), c_int(n_group), c_int(topk_group), c_float(scaling), c_int(_is_bf16(logits)),
+                                _stream()), "moe_route")
+    return w, idx
+
+
+class MoeWorkspace:
+    """Routing tables of one MoE call over the padded row space (every expert segment is a multiple
+    of 128 rows, so a 128-row tile belongs to exactly one expert)."""
+
+    def __init__(self, tokens: int, top_k: int, experts_local: int, device):
+        slots = tokens * top_k
+        self.max_tiles = (slots + 127) // 128 + experts_local
+        self.rows_pad = self.max_tiles * 128
+        self.dst_row = torch.empty(slots, dtype=torch.int32, device=device)
+        self.tile_expert = torch.empty(self.max_tiles, dtype=torch.int32, device=device)
+        self.counts = torch.empty(1, dtype=torch.int32, device=device)
+
+
+def moe_align(topk_idx: torch.Tensor, experts: int, expert_lo: int, expert_hi: int) -> MoeWorkspace:
+    t, k = topk_idx.shape
+    ws = MoeWorkspace(t, k, expert_hi - expert_lo, topk_idx.device)
+    _check(lib().telb_moe_align(_p(topk_idx), _p(ws.dst_row), _p(ws.tile_expert), _p(ws.counts), c_int(t * k), c_int(experts),
+                                c_int(expert_lo), c_int(expert_hi), c_int(ws.max_tiles), _stream()), "moe_align")
+    return ws
+
+
+def moe_gather(x: torch.Tensor, ws: MoeWorkspace, top_k: int, quant_scale: Optional[torch.Tensor]):
+    """Routed rows in expert order: NVFP4 ``QuantActs`` when ``quant_scale`` is given, else 16-bit."""
+    x = x.contiguous()
+    t, h = x.shape
+    if quant_scale is None:
+        out = torch.empty(ws.rows_pad, h, dtype=x.dtype, device=x.device)
+        _check(lib().telb_moe_gather(_p(x), _p(ws.dst_row), _p(out), c_vp(0), c_vp(0), c_vp(0), c_int(t * top_k), c_int(top_k),
+                                     c_int(h), c_int(_is_bf16(x)), _stream()), "moe_gather")
+        return out
+    L = lib()
+    L.telb_nvfp4_sf_bytes.restype = c_ll
+    xq = torch.empty(ws.rows_pad, h // 2, dtype=torch.uint8, device=x.device)
+    sf = _sf_buffer(L.telb_nvfp4_sf_bytes(c_ll(ws.rows_pad), c_int(h)), h, x.device)
+    _check(L.telb_moe_gather(_p(x), _p(ws.dst_row), c_vp(0), _p(xq), _p(sf), _p(quant_scale), c_int(t * top_k), c_int(top_k),
+                             c_int(h), c_int(_is_bf16(x)), _stream()), "moe_gather")
+    return QuantActs(xq, sf, (ws.rows_pad, h), x.dtype)
+
+
+def gemm_grouped(x, weight, ws: MoeWorkspace, experts_local: int, alpha=None, bias=None, w_sf=None):
+    """Expert GEMM over the padded rows: ``x`` 16-bit ``[rows_pad, K]`` or ``QuantActs``; ``weight``
+    ``[E_local * N, K]`` (16-bit) or packed NVFP4 ``[E_local * N, K/2]`` with atom scales ``w_sf``."""
+    wsx = Workspace.get(weight.device)
+    if isinstance(x, QuantActs):
+        n = weight.shape[0] // experts_local
+        k = weight.shape[1] * 2
+        out = torch.empty(ws.rows_pad, n, dtype=x.dtype, device=weight.device)
+        _check(lib().telb_gemm_nvfp4_grouped(_p(x.xq), _p(x.sf), _p(weight), _p(w_sf), _p(out), c_int(ws.rows_pad), c_int(n), c_int(k),
+                                             c_int(experts_local), _p(ws.tile_expert), _p(alpha),
+                                             c_int(1 if x.dtype == torch.bfloat16 else 0), _p(wsx.status), _stream()),
+               "gemm_nvfp4_grouped")
+        return out
+    n = weight.shape[0] // experts_local
+    k = weight.shape[1]
+    out = torch.empty(ws.rows_pad, n, dtype=x.dtype, device=x.device)
+    _check(lib().telb_gemm_f16_grouped(_p(x), _p(weight), _p(out), c_int(ws.rows_pad), c_int(n), c_int(k), c_int(experts_local),
+                                       _p(ws.tile_expert), _p(alpha), _p(bias), c_int(_is_bf16(x)), _p(wsx.status), _stream()),
+           "gemm_f16_grouped")
+    return out
+
+
+def moe_combine(y: torch.Tensor, ws: MoeWorkspace, topk_w: torch.Tensor) -> torch.Tensor:
+    t, k = topk_w.shape
+    out = torch.empty(t, y.shape[1], dtype=y.dtype, device=y.device)
+    _check(lib().telb_moe_combine(_p(y), _p(ws.dst_row), _p(topk_w), _p(out), c_int(t), c_int(k), c_int(y.shape[1]),
+                                  c_int(_is_bf16(y)), _stream()), "moe_combine")
+    return out
+
+
+# ---- recurrent layers ---------------------------------------------------------------------------
+
+
+def causal_conv1d(x, weight, bias, conv_state, meta: StepMeta, activation=True):
+    x = x.contiguous()
+    t, c = x.shape
+    w = weight.reshape(c, -1).contiguous()
+    out = torch.empty_like(x)
+    assert conv_state.is_contiguous() and conv_state.dtype == x.dtype
+    _check(lib().telb_causal_conv1d(_p(x), _p(w), _p(bias), _p(conv_state), _p(out), _p(meta.seq_ids), _p(meta.q_start),
+                                    _p(meta.q_len), _p(meta.past_len), _p(meta.slot_ids), c_int(t), c_int(meta.num_seqs), c_int(c),
+                                    c_int(w.shape[1]), c_int(int(activation)), c_int(_is_bf16(x)), _stream()), "causal_conv1d", 2)
+    return out
+
+
+def ssm_scan(x, dt, A, B, C, D, dt_bias, ssm_state, meta: StepMeta, z=None, dt_softplus=True, dt_limit=0.0):
+    x, dt, B, C = x.contiguous(), dt.contiguous(), B.contiguous(), C.contiguous()
+    t, nh, hd = x.shape
+    y = torch.empty_like(x)
+    assert ssm_state.dtype == torch.float32 and ssm_state.is_contiguous()
+    _check(lib().telb_ssm_scan(_p(x), _p(dt), _p(A.float().contiguous()), _p(B), _p(C), _p(D.float().contiguous()),
+                               _p(dt_bias.float().contiguous()), _p(z.contiguous() if z is not None else None), _p(ssm_state), _p(y),
+                               _p(meta.q_start), _p(meta.q_len), _p(meta.past_len), _p(meta.slot_ids), c_int(meta.num_seqs),
+                               c_int(nh), c_int(hd), c_int(B.shape[-1]), c_int(B.shape[1]), c_int(int(dt_softplus)),
+                               c_float(dt_limit), c_int(_is_bf16(x)), _stream()), "ssm_scan")
+    return y
+
+
+def gated_delta_rule(q, k, v, a, b, A_log, dt_bias, state, meta: StepMeta):
+    q, k, v, a, b = (t.contiguous() for t in (q, k, v, a, b))
+    out = torch.empty_like(v)
+    assert state.dtype == torch.float32 and state.is_contiguous()
+    _check(lib().telb_gated_delta_rule(_p(q), _p(k), _p(v), _p(a), _p(b), _p(A_log.float().contiguous()),
+                                       _p(dt_bias.float().contiguous()), _p(state), _p(out), _p(meta.q_start), _p(meta.q_len),
+                                       _p(meta.past_len), _p(meta.slot_ids), c_int(meta.num_seqs), c_int(q.shape[1]), c_int(v.shape[1]),
+                                       c_int(q.shape[2]), c_int(v.shape[2]), c_int(_is_bf16(q)), _stream()), "gated_delta_rule")
     return out

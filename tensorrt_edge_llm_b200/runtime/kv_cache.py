@@ -68,6 +68,15 @@ class KVCacheManager:
         hkv = max(cfg.num_key_value_heads // cfg.tp_size, 1)
         self.dtype = dtype or cfg.compute_dtype
         self.pool = torch.zeros(self.num_layers, num_pages, 2, hkv, page_size, cfg.head_dim, dtype=self.dtype, device=device)
+        # hybrid models: model layer index → attention pool index, plus the recurrent state pools
+        self._attn_index = {}
+        for i, t in enumerate(cfg.layer_types):
+            if t == LAYER_ATTENTION:
+                self._attn_index[i] = len(self._attn_index)
+        self.recurrent = None
+        if cfg.is_hybrid:
+            from ..models.nemotron_h import RecurrentState
+            self.recurrent = RecurrentState(cfg, max_seats, device, self.dtype)
         self.alloc = PageAllocator(num_pages)
         self.table = torch.full((max_seats, max_pages_per_seq), -1, dtype=torch.int32)   # host truth
         self.lengths = [0] * max_seats
@@ -79,6 +88,10 @@ class KVCacheManager:
             self.native = _rt.KVPageTable(num_pages, page_size, max_seats, max_pages_per_seq)
         except ImportError:
             self.native = None
+
+    def kv_layer(self, model_layer: int) -> torch.Tensor:
+        """KV pool of attention layer ``model_layer`` (index into the model's layer list)."""
+        return self.pool[self._attn_index[model_layer]]
 
     @property
     def bytes_per_token(self) -> int:

@@ -42,6 +42,8 @@ class ModelRunner:
         self.max_num_tokens = max_num_tokens
         self._graphs: Dict[int, "_DecodeGraph"] = {}
         self.use_cuda_graphs = self.device.type == "cuda"
+        # hybrid models address attention pools and recurrent state pools through the manager itself
+        self.cache = kv if getattr(model, "needs_cache_set", False) else kv.pool
 
     # ---- eager ragged step -----------------------------------------------------------------
     def _meta(self, seats: Sequence[int], q_lens: Sequence[int], logits_all=False, tree_mask=None,
@@ -65,7 +67,7 @@ class ModelRunner:
             ids = host.to(self.device, non_blocking=True)
         else:
             ids = torch.tensor(flat, dtype=torch.int32)
-        logits = self.model(ids, meta, self.kv.pool)
+        logits = self.model(ids, meta, self.cache)
         if commit:
             for s, q in zip(seats, q_lens):
                 self.kv.commit(s, q)
@@ -117,7 +119,7 @@ class ModelRunner:
             chunk = ids[b0:b0 + per].reshape(-1)
             if chunk.device != self.device:
                 chunk = chunk.to(self.device, non_blocking=True)
-            outs.append(self.model(chunk.to(torch.int32), meta, self.kv.pool))
+            outs.append(self.model(chunk.to(torch.int32), meta, self.cache))
             for sidx in grp:
                 self.kv.commit(sidx, s_len)
         return torch.cat(outs, dim=0)
@@ -202,7 +204,7 @@ class _DecodeGraph:
 
     def _body(self):
         m = self.meta
-        logits = self.r.model(self.ids, m, self.r.kv.pool)
+        logits = self.r.model(self.ids, m, self.r.cache)
         tok = ops.argmax(logits)
         self.ids.copy_(tok)
         self.out.index_copy_(0, self.step_idx, tok.unsqueeze(0))
