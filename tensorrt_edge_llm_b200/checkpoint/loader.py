@@ -37,6 +37,9 @@ def load_weights(model: nn.Module, model_dir: str, strict: bool = True) -> List[
     """Fill ``model`` from the safetensors shards in ``model_dir``; returns unused checkpoint keys."""
     reader = CheckpointReader(model_dir)
     names = _strip_prefixes(reader.keys())
+    remap = getattr(model, "checkpoint_key_remap", None)
+    if remap is not None:       # family-specific renames (a None result drops the tensor)
+        names = {remap(c): k for c, k in names.items() if remap(c) is not None}
     used = set()
 
     def fetch(name: str) -> Optional[torch.Tensor]:
@@ -83,6 +86,8 @@ def load_weights(model: nn.Module, model_dir: str, strict: bool = True) -> List[
         if t.shape != p.shape:
             t = _shard_like(t, p, model)
         p.data.copy_(t.to(p.dtype))
+    if hasattr(model, "finalize_checkpoint"):
+        model.finalize_checkpoint()
     reader_keys = set(reader.keys())
     return sorted(reader_keys - used)
 

@@ -174,6 +174,8 @@ class ModelConfig:
     draft_type: Optional[str] = None        # "eagle3" / "mtp"
     eagle3_target_hidden_size: int = 0
     eagle3_num_target_layers: int = 3
+    eagle3_target_layer_ids: List[int] = field(default_factory=list)   # tapped target layers (default: low / mid / high)
+    eagle3_norm_before_residual: bool = False
     draft_vocab_size: int = 0
     # quant / parallel
     quant: QuantConfig = field(default_factory=QuantConfig)
@@ -326,6 +328,12 @@ class ModelConfig:
             quant=quant or QuantConfig(),
             bos_token_id=llm.get("bos_token_id"),
             eos_token_id=llm.get("eos_token_id"),
+            draft_type="eagle3" if (llm.get("draft_vocab_size") or "eagle" in str(hf.get("architectures", "")).lower()
+                                    or hf.get("speculators_model_type") == "eagle3") else None,
+            draft_vocab_size=int(llm.get("draft_vocab_size", 0) or 0),
+            eagle3_target_hidden_size=int(llm.get("target_hidden_size", 0) or 0),
+            eagle3_target_layer_ids=list((hf.get("eagle_config") or {}).get("eagle_aux_hidden_state_layer_ids", []) or []),
+            eagle3_norm_before_residual=bool(llm.get("norm_before_residual", False)),
         )
 
     @classmethod

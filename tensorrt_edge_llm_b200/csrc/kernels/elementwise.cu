@@ -579,10 +579,6 @@ __global__ void argmax_split_kernel(const T* __restrict__ logits, int* __restric
         }
     }
 }
-template <> struct Cvt<float> {
-    static __device__ __forceinline__ float to_f(float v) { return v; }
-    static __device__ __forceinline__ float from_f(float v) { return v; }
-};
 }  // namespace telb
 
 // dtype: 0 = fp16, 1 = bf16, 2 = fp32.  `keys` (rows x u64, zeroed once) and `counters` (rows x int,

@@ -225,14 +225,17 @@ using namespace telb;
 extern "C" int telb_nvfp4_k64_pad(int k);
 
 extern "C" int telb_moe_route(const void* logits, float* topk_w, int* topk_idx, const float* bias, int tokens, int experts,
-                              int top_k, int renorm, int sigmoid, int n_group, int topk_group, float scaling, int is_bf16,
+                              int top_k, int renorm, int sigmoid, int n_group, int topk_group, float scaling, int dtype,
                               cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (top_k > kMaxTopK || experts > 1024 || n_group > 32) return fail("telb_moe_route: top_k <= 16, experts <= 1024, groups <= 32");
     const int wpb = 4;
     const size_t smem = (size_t)wpb * 2 * experts * sizeof(float);
     const dim3 grid((tokens + wpb - 1) / wpb), block(wpb * 32);
-    if (is_bf16)
+    if (dtype == 2)
+        TELB_LAUNCH("moe_route_kernel", (moe_route_kernel<float>), grid, block, smem, stream, (const float*)logits, topk_w, topk_idx, bias,
+                    tokens, experts, top_k, renorm, sigmoid, n_group, topk_group, scaling);
+    else if (dtype == 1)
         TELB_LAUNCH("moe_route_kernel", (moe_route_kernel<__nv_bfloat16>), grid, block, smem, stream, (const __nv_bfloat16*)logits, topk_w,
                     topk_idx, bias, tokens, experts, top_k, renorm, sigmoid, n_group, topk_group, scaling);
     else

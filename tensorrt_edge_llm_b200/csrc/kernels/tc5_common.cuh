@@ -289,5 +289,9 @@ template <> struct Cvt<__half> {
     static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
     static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
 };
+template <> struct Cvt<float> {
+    static __device__ __forceinline__ float to_f(float v) { return v; }
+    static __device__ __forceinline__ float from_f(float v) { return v; }
+};
 
 }  // namespace telb

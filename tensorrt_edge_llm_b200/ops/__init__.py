@@ -128,3 +128,15 @@ def gated_delta_rule(q, k, v, a, b, A_log, dt_bias, state, meta):
     if q.is_cuda:
         return cuda_ops().gated_delta_rule(q, k, v, a, b, A_log, dt_bias, state, meta)
     return ref.gated_delta_rule(q, k, v, a, b, A_log, dt_bias, state, meta)
+
+
+def spec_accept_greedy(target_tokens, tree_tokens, parents, max_path, force_len=0):
+    if tree_tokens.is_cuda:
+        return cuda_ops().spec_accept_greedy(target_tokens, tree_tokens, parents, max_path, force_len)
+    return ref.spec_accept_greedy(target_tokens, tree_tokens, parents, max_path, force_len)
+
+
+def kv_commit_path(pool, page_table, past_len, path, path_len):
+    if pool.is_cuda:
+        return cuda_ops().kv_commit_path(pool, page_table, past_len, path, path_len)
+    return ref.kv_commit_path(pool, page_table, past_len, path, path_len)

@@ -33,15 +33,27 @@ def lib() -> ctypes.CDLL:
 LAUNCHES = 0      # kernels of this library launched (or captured) so far in this process
 
 
+_DEBUG_SYNC = os.environ.get("TELB_DEBUG_SYNC", "0") == "1"     # synchronise after every op so a device error names its op
+
+
 def _check(rc: int, what: str, n: int = 1) -> None:
     global LAUNCHES
     if rc != 0:
         raise RuntimeError(f"{what} failed: {lib().telb_last_error().decode()}")
     LAUNCHES += n
+    if _DEBUG_SYNC and not torch.cuda.is_current_stream_capturing():
+        try:
+            torch.cuda.synchronize()
+        except RuntimeError as e:
+            raise RuntimeError(f"device error surfaced after {what}: {e}") from None
 
 
 def _p(t: Optional[torch.Tensor]):
-    return c_vp(t.data_ptr()) if t is not None else c_vp(0)
+    if t is None:
+        return c_vp(0)
+    if not t.is_cuda:        # a host pointer handed to a kernel is a device fault, not an exception
+        raise ValueError(f"kernel argument of shape {tuple(t.shape)} lives on {t.device}, not on the GPU")
+    return c_vp(t.data_ptr())
 
 
 def _stream() -> c_vp:
@@ -407,8 +419,8 @@ def moe_route_softmax_topk(logits, top_k, renormalize=True, bias=None, sigmoid=F
     t, e = logits.shape
     w = torch.empty(t, top_k, dtype=torch.float32, device=logits.device)
     idx = torch.empty(t, top_k, dtype=torch.int32, device=logits.device)
-    _check(lib().telb_moe_route(_p(logits), _p(w), _p(idx), _p(bias), c_int(t), c_int(e), c_int(top_k), c_int(int(renormalize)),
-                                c_int(int(sigmoid)), c_int(n_group), c_int(topk_group), c_float(scaling), c_int(_is_bf16(logits)),
+    _check(lib().telb_moe_route(_p(logits), _p(w), _p(idx), _p(bias.float().contiguous() if bias is not None else None), c_int(t), c_int(e), c_int(top_k), c_int(int(renormalize)),
+                                c_int(int(sigmoid)), c_int(n_group), c_int(topk_group), c_float(scaling), c_int(_logit_dtype(logits)),
                                 _stream()), "moe_route")
     return w, idx
 
@@ -519,3 +531,32 @@ def gated_delta_rule(q, k, v, a, b, A_log, dt_bias, state, meta: StepMeta):
                                        _p(meta.past_len), _p(meta.slot_ids), c_int(meta.num_seqs), c_int(q.shape[1]), c_int(v.shape[1]),
                                        c_int(q.shape[2]), c_int(v.shape[2]), c_int(_is_bf16(q)), _stream()), "gated_delta_rule")
     return out
+
+
+# ---- speculative decoding -------------------------------------------------------------------------
+
+
+def spec_accept_greedy(target_tokens, tree_tokens, parents, max_path: int, force_len=0):
+    b, n = tree_tokens.shape
+    dev = tree_tokens.device
+    force = None
+    if isinstance(force_len, torch.Tensor):
+        force = force_len.to(device=dev, dtype=torch.int32).contiguous()
+    elif force_len:
+        force = torch.full((b,), int(force_len), dtype=torch.int32, device=dev)
+    path = torch.zeros(b, max_path, dtype=torch.int32, device=dev)
+    plen = torch.empty(b, dtype=torch.int32, device=dev)
+    bonus = torch.empty(b, dtype=torch.int32, device=dev)
+    _check(lib().telb_spec_accept_greedy(_p(target_tokens.to(torch.int32).contiguous()), _p(tree_tokens.to(torch.int32).contiguous()),
+                                         _p(parents.to(torch.int32).contiguous()), _p(path), _p(plen), _p(bonus), c_int(b), c_int(n),
+                                         c_int(max_path), _p(force), _stream()), "spec_accept_greedy")
+    return path, plen, bonus
+
+
+def kv_commit_path(pool, page_table, past_len, path, path_len) -> None:
+    assert pool.is_contiguous() and pool.element_size() == 2
+    layers, pages, _, hkv, psz, d = pool.shape
+    _check(lib().telb_kv_commit_path(_p(pool), _p(page_table.to(torch.int32).contiguous()), _p(past_len.to(torch.int32).contiguous()),
+                                     _p(path.contiguous()), _p(path_len.contiguous()), c_int(path.shape[0]), c_int(path.shape[1]),
+                                     c_int(page_table.shape[1]), c_int(layers), c_int(pages), c_int(hkv), c_int(psz), c_int(d),
+                                     _stream()), "kv_commit_path")

@@ -506,3 +506,55 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
 
 def argmax(logits: torch.Tensor) -> torch.Tensor:
     return torch.argmax(logits.float(), dim=-1).to(torch.int32)
+
+
+# ------------------------------------------------------------------------------------------
+# speculative decoding
+
+
+def spec_accept_greedy(target_tokens: torch.Tensor, tree_tokens: torch.Tensor, parents: torch.Tensor, max_path: int,
+                       force_len: int = 0) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Greedy tree acceptance.  Node 0 is the root; parents precede children.  From the root, follow
+    the lowest-index child whose token equals the target arg-max at the current node.  Returns
+    ``(path [B, max_path] node indices, path_len [B] (root included), bonus [B])`` where the bonus
+    token is the target arg-max at the last accepted node.  ``force_len > 0`` (an int or a per-sequence tensor) ignores
+    tokens and follows first children until the path holds that many nodes (benchmark mode,
+    ``cpp/kernels/speculative/forceAcceptanceKernels.cu``)."""
+    b, n = tree_tokens.shape
+    path = torch.zeros(b, max_path, dtype=torch.int32, device=tree_tokens.device)
+    plen = torch.ones(b, dtype=torch.int32, device=tree_tokens.device)
+    bonus = torch.zeros(b, dtype=torch.int32, device=tree_tokens.device)
+    for i in range(b):
+        cur, ln = 0, 1
+        fl = int(force_len[i]) if isinstance(force_len, torch.Tensor) else int(force_len)
+        while ln < max_path and not (fl > 0 and ln >= fl):
+            want = int(target_tokens[i, cur])
+            nxt = -1
+            for c in range(cur + 1, n):
+                if int(parents[i, c]) == cur and (fl > 0 or int(tree_tokens[i, c]) == want):
+                    nxt = c
+                    break
+            if nxt < 0:
+                break
+            cur = nxt
+            path[i, ln] = cur
+            ln += 1
+        plen[i] = ln
+        bonus[i] = target_tokens[i, cur]
+    return path, plen, bonus
+
+
+def kv_commit_path(pool: torch.Tensor, page_table: torch.Tensor, past_len: torch.Tensor, path: torch.Tensor,
+                   path_len: torch.Tensor) -> None:
+    """Compact the accepted path in the paged cache ``pool [L, pages, 2, Hkv, P, D]``: the entry at
+    slot ``past + path[j]`` moves to slot ``past + j`` (``j ≥ 1``), in place."""
+    p = pool.shape[4]
+    for i in range(path.shape[0]):
+        past, m = int(past_len[i]), int(path_len[i])
+        rows = []
+        for j in range(1, m):
+            s = past + int(path[i, j])
+            rows.append(pool[:, int(page_table[i, s // p]), :, :, s % p, :].clone())
+        for j, r in zip(range(1, m), rows):
+            s = past + j
+            pool[:, int(page_table[i, s // p]), :, :, s % p, :] = r

@@ -35,10 +35,12 @@ class SamplingParams:
 
 
 class ModelRunner:
-    def __init__(self, model, kv: KVCacheManager, device="cpu", max_num_tokens: int = 8192):
+    def __init__(self, model, kv: KVCacheManager, device=None, max_num_tokens: int = 8192):
         self.model = model
         self.kv = kv
-        self.device = torch.device(device)
+        self.device = torch.device(device) if device is not None else kv.pool.device
+        if self.device != kv.pool.device:
+            raise ValueError(f"runner device {self.device} differs from the KV pool's device {kv.pool.device}")
         self.max_num_tokens = max_num_tokens
         self._graphs: Dict[int, "_DecodeGraph"] = {}
         self.use_cuda_graphs = self.device.type == "cuda"

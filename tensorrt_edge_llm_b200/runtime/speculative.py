@@ -1,0 +1,311 @@
+"""EAGLE-3 tree speculative decoding over the paged ragged step ABI.
+
+One round per call of :meth:`EagleDecoder.round`:
+
+1. grow a draft tree: the draft's distribution after the last accepted token gives the ``top_k``
+   depth-1 candidates; ``draft_steps - 1`` draft forwards (tree-masked, one per depth) expand the
+   ``top_k`` best frontier nodes into ``top_k²`` candidates scored by cumulative log-probability;
+2. keep the ``verify_tokens - 1`` best candidates (closed under ancestors because scores fall
+   along a path) plus the root and verify them with ONE tree-masked target forward;
+3. accept greedily along the tree (kernel), compact the accepted path in the target's paged KV
+   cache in place (kernel), and emit the accepted tokens plus the target's bonus token;
+4. feed the accepted tokens with the target's tapped hidden states to the draft (its KV is
+   rewound to the committed length first), which yields the next round's depth-1 candidates.
+
+Greedy acceptance is lossless: the emitted stream equals plain greedy decoding of the target.
+
+Parity: ``cpp/runtime/decoding/eagleDecoder.cpp`` — ``decodeStep`` (:287-320),
+``constructDraftProposal`` (:502-729), ``runBaseModelVerification`` (:731-871),
+``runDraftModelAcceptToken`` (:873-959), KV headroom (:223-238); tree size cap
+``cpp/common/specDecodeLimits.h:30``; forced acceptance length for benchmarks
+``cpp/runtime/config/runtimeBenchmarkOptions.h``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..ops.meta import build_step_meta
+from .kv_cache import KVCacheManager
+from .runner import ModelRunner
+
+
+@dataclass
+class SpecConfig:
+    draft_steps: int = 4          # tree depth
+    top_k: int = 8                # children kept per node and frontier width
+    verify_tokens: int = 32       # tree nodes verified per round, root included (<= 128)
+    force_accept_len: int = 0     # benchmark mode: nodes accepted per round (root included), tokens ignored
+    force_accept_mean: float = 0.0  # benchmark mode: per-round lengths drawn from a seeded distribution with this mean
+    force_seed: int = 0
+
+    def __post_init__(self):
+        if not 1 <= self.verify_tokens <= 128:
+            raise ValueError("verify_tokens must be in 1..128")
+        if self.draft_steps < 1 or self.top_k < 1:
+            raise ValueError("draft_steps and top_k must be positive")
+        pool = self.top_k + (self.draft_steps - 1) * self.top_k * self.top_k
+        self.verify_tokens = min(self.verify_tokens, pool + 1)
+
+
+@dataclass
+class SpecStats:
+    rounds: int = 0
+    emitted: int = 0
+    draft_forwards: int = 0
+
+    @property
+    def mean_accept_length(self) -> float:
+        return self.emitted / max(self.rounds, 1)
+
+
+def default_tap_layers(num_layers: int) -> List[int]:
+    """Low / middle / high target layers whose hidden states feed the draft (EAGLE-3 convention)."""
+    ids = sorted({min(max(i, 0), num_layers - 1) for i in (2, num_layers // 2, num_layers - 3)})
+    while len(ids) < 3:                      # very shallow test models: reuse the last layer
+        ids.append(ids[-1])
+    return ids
+
+
+class EagleDecoder:
+    def __init__(self, runner: ModelRunner, draft, draft_kv: KVCacheManager, spec: Optional[SpecConfig] = None,
+                 tap_layers: Optional[Sequence[int]] = None):
+        if runner.model.cfg.is_hybrid:
+            raise NotImplementedError("speculative decoding over recurrent layers needs state replay, which is not built")
+        self.r = runner
+        self.model = runner.model
+        self.draft = draft
+        self.dkv = draft_kv
+        self.spec = spec or SpecConfig()
+        self.taps = list(tap_layers or runner.model.cfg.eagle3_target_layer_ids or default_tap_layers(runner.model.cfg.num_hidden_layers))
+        self.device = runner.device
+        self.stats = SpecStats()
+        self._force_gen = None
+        # per seat: pending root token, draft log-probs and hidden after the last accepted token
+        self.root: Dict[int, int] = {}
+        self.lp: Dict[int, torch.Tensor] = {}
+        self.hid: Dict[int, torch.Tensor] = {}
+
+    # ---- helpers ------------------------------------------------------------------------------
+    def _embed(self, ids: torch.Tensor) -> torch.Tensor:
+        return ops.embedding(ids.to(torch.int32), self.model.model.embed_tokens.weight)
+
+    def _target_step(self, seats, rows: torch.Tensor, q_lens, tree_mask=None, positions=None):
+        meta = self.r._meta(seats, q_lens, logits_all=True, tree_mask=tree_mask, positions=positions)
+        uniq = sorted(set(self.taps))
+        x, taps = self.model.hidden_states(rows, meta, self.r.cache, capture_layers=uniq)
+        logits = self.model.logits_from_hidden(x, meta)
+        by_layer = dict(zip(uniq, taps))
+        return logits, torch.cat([by_layer[t] for t in self.taps], dim=-1)
+
+    def _draft_step(self, seats, embeds, feature, q_lens, logits_rows, tree_mask=None, positions=None, commit=False):
+        past = [self.dkv.lengths[s] for s in seats]
+        for s, q, p in zip(seats, q_lens, past):
+            self.dkv.reserve(s, p + q)
+        meta = build_step_meta(q_lens, past, self.dkv.table_rows(seats), self.dkv.page_size, slot_ids=seats, logits_all=True,
+                               device=self.device, tree_mask=tree_mask, positions=positions)
+        meta.logits_idx = torch.as_tensor(logits_rows, dtype=torch.int32, device=self.device)
+        lp, h = self.draft(embeds, feature, meta, self.dkv.pool)
+        if commit:
+            for s, q in zip(seats, q_lens):
+                self.dkv.commit(s, q)
+        self.stats.draft_forwards += 1
+        return lp, h
+
+    # ---- prefill ------------------------------------------------------------------------------
+    @torch.no_grad()
+    def prefill(self, seats: Sequence[int], prompts: Sequence[Sequence[int]]) -> List[int]:
+        """Target prefill with tapped hidden states, then draft prefill.  Returns the first generated
+        token of every sequence (the root of its first tree)."""
+        q_lens = [len(p) for p in prompts]
+        flat = torch.tensor([t for p in prompts for t in p], dtype=torch.int32, device=self.device)
+        logits, taps = self._target_step(seats, flat, q_lens)
+        for s, q in zip(seats, q_lens):
+            self.r.kv.commit(s, q)
+        ends = torch.tensor(q_lens).cumsum(0) - 1
+        first = ops.argmax(logits.index_select(0, ends.to(self.device))).tolist()
+        # draft row i pairs the target feature of position i with the token of position i + 1
+        nxt = flat.clone()
+        nxt[:-1] = flat[1:]
+        nxt[ends.to(self.device)] = torch.tensor(first, dtype=torch.int32, device=self.device)
+        lp, h = self._draft_step(seats, self._embed(nxt), taps, q_lens, ends.tolist(), commit=True)
+        for i, s in enumerate(seats):
+            self.root[s] = int(first[i])
+            self.lp[s] = lp[i]
+            self.hid[s] = h[int(ends[i])]
+        return [int(t) for t in first]
+
+    # ---- one speculative round ----------------------------------------------------------------
+    @torch.no_grad()
+    def round(self, seats: Sequence[int]) -> List[List[int]]:
+        """Returns the tokens emitted for every seat this round (accepted draft tokens + bonus)."""
+        sp, dev = self.spec, self.device
+        b, k, steps, n = len(seats), self.spec.top_k, self.spec.draft_steps, self.spec.verify_tokens
+        d2t = self.draft.d2t.long()
+        lp0 = torch.stack([self.lp[s] for s in seats])                       # [B, Vd]
+        h0 = torch.stack([self.hid[s] for s in seats])                       # [B, H]
+        k1 = min(k, lp0.shape[-1])
+        sc, idx = lp0.topk(k1, dim=-1)
+        # candidate pool (depth-ordered): token, parent pool index (-1 = root), depth, cumulative score
+        p_tok, p_par, p_dep, p_sc = [d2t[idx]], [torch.full((b, k1), -1, device=dev)], [torch.ones(b, k1, dtype=torch.long, device=dev)], [sc]
+        # draft rows fed so far: token, feature, parent row (-1 = none), depth, pool index
+        r_tok, r_feat, r_par, r_dep = d2t[idx], h0[:, None, :].expand(b, k1, h0.shape[-1]), torch.full((b, k1), -1, device=dev), torch.ones(b, k1, dtype=torch.long, device=dev)
+        r_pool, r_sc = torch.arange(k1, device=dev).expand(b, k1), sc
+        front0, kf = 0, k1                                                    # first row / width of the current frontier
+        pool_base = k1
+        ld = [self.dkv.lengths[s] for s in seats]
+        for depth in range(2, steps + 1):
+            rows = r_tok.shape[1]
+            anc = self._ancestors(r_par)                                      # [B, R, R]
+            mask = self._pack_mask(anc)
+            pos = [l + int(d) - 1 for i, l in enumerate(ld) for d in r_dep[i].tolist()]
+            want = [i * rows + front0 + j for i in range(b) for j in range(kf)]
+            lp, h = self._draft_step(seats, self._embed(r_tok.reshape(-1)), r_feat.reshape(b * rows, -1).contiguous(), [rows] * b, want,
+                                     tree_mask=mask, positions=pos)
+            lp = lp.view(b, kf, -1)
+            kc = min(k, lp.shape[-1])
+            csc, cidx = lp.topk(kc, dim=-1)                                   # [B, kf, kc]
+            cum = r_sc[:, front0:front0 + kf, None] + csc
+            ctok = d2t[cidx]
+            cpar = r_pool[:, front0:front0 + kf, None].expand(b, kf, kc)
+            p_tok.append(ctok.reshape(b, -1)); p_par.append(cpar.reshape(b, -1)); p_sc.append(cum.reshape(b, -1))
+            p_dep.append(torch.full((b, kf * kc), depth, dtype=torch.long, device=dev))
+            if depth == steps:
+                break
+            # next frontier: the best `k` of the new candidates
+            kn = min(k, kf * kc)
+            fsc, fsel = cum.reshape(b, -1).topk(kn, dim=-1)
+            fpar_row = front0 + fsel // kc                                    # parent's draft row
+            hrows = h.view(b, rows, -1)
+            r_tok = torch.cat([r_tok, ctok.reshape(b, -1).gather(1, fsel)], dim=1)
+            r_feat = torch.cat([r_feat, hrows.gather(1, fpar_row[..., None].expand(b, kn, hrows.shape[-1]))], dim=1)
+            r_par = torch.cat([r_par, fpar_row], dim=1)
+            r_dep = torch.cat([r_dep, torch.full((b, kn), depth, dtype=torch.long, device=dev)], dim=1)
+            r_pool = torch.cat([r_pool, pool_base + fsel], dim=1)
+            n_new = kf * kc
+            r_sc = torch.cat([r_sc, fsc], dim=1)
+            front0, kf = rows, kn
+            pool_base += n_new
+        p_tok, p_par, p_dep, p_sc = (torch.cat(x, dim=1) for x in (p_tok, p_par, p_dep, p_sc))
+        # ---- choose the verification tree ----
+        npool = p_tok.shape[1]
+        keep = min(n - 1, npool)
+        order = torch.sort(p_sc, dim=1, descending=True, stable=True).indices[:, :keep]
+        sel = torch.sort(order, dim=1).values                                 # pool order = parents first
+        inv = torch.full((b, npool), -1, dtype=torch.long, device=dev)
+        inv.scatter_(1, sel, torch.arange(1, keep + 1, device=dev).expand(b, keep))
+        spar = p_par.gather(1, sel)
+        parents = torch.where(spar < 0, torch.zeros_like(spar), inv.gather(1, spar.clamp(min=0)))
+        nn_ = keep + 1
+        root = torch.tensor([self.root[s] for s in seats], device=dev)
+        tree_tok = torch.cat([root[:, None], p_tok.gather(1, sel)], dim=1)    # [B, nn]
+        tree_par = torch.cat([torch.full((b, 1), -1, device=dev), parents], dim=1)
+        tree_dep = torch.cat([torch.zeros(b, 1, dtype=torch.long, device=dev), p_dep.gather(1, sel)], dim=1)
+        anc = self._ancestors(tree_par)
+        lt = [self.r.kv.lengths[s] for s in seats]
+        pos = [l + int(d) for i, l in enumerate(lt) for d in tree_dep[i].tolist()]
+        logits, taps = self._target_step(seats, tree_tok.reshape(-1).to(torch.int32), [nn_] * b, tree_mask=self._pack_mask(anc), positions=pos)
+        tgt = ops.argmax(logits).view(b, nn_)
+        # ---- accept, commit KV ----
+        max_path = steps + 1
+        path, plen, bonus = ops.spec_accept_greedy(tgt, tree_tok.to(torch.int32), tree_par.to(torch.int32), max_path, self._forced(b))
+        past_t = torch.tensor(lt, dtype=torch.int32, device=dev)
+        ops.kv_commit_path(self.r.kv.pool, self.r.kv.table_rows(seats).to(dev), past_t, path, plen)
+        path_h, plen_h, bonus_h = path.tolist(), plen.tolist(), bonus.tolist()   # the round's one device→host read
+        tok_h = tree_tok.tolist()
+        out: List[List[int]] = []
+        acc_rows, acc_tok, q_lens = [], [], []
+        for i, s in enumerate(seats):
+            m = plen_h[i]
+            self.r.kv.commit(s, m)
+            nodes = path_h[i][:m]
+            emitted = [tok_h[i][j] for j in nodes[1:]] + [bonus_h[i]]
+            out.append(emitted)
+            acc_rows.extend(i * nn_ + j for j in nodes)
+            acc_tok.extend(emitted)
+            q_lens.append(m)
+            self.root[s] = bonus_h[i]
+        # ---- draft catches up on the accepted tokens ----
+        feat = taps.index_select(0, torch.tensor(acc_rows, device=dev))
+        emb = self._embed(torch.tensor(acc_tok, dtype=torch.int32, device=dev))
+        ends = (torch.tensor(q_lens).cumsum(0) - 1).tolist()
+        lp, h = self._draft_step(seats, emb, feat, q_lens, ends, commit=True)
+        for i, s in enumerate(seats):
+            self.lp[s] = lp[i]
+            self.hid[s] = h[ends[i]]
+        self.stats.rounds += b
+        self.stats.emitted += sum(len(e) for e in out)
+        return out
+
+    def _forced(self, b: int):
+        """Forced accept lengths of this round: a constant, or draws in ``1..draft_steps+1`` from a seeded
+        distribution whose mean is ``force_accept_mean`` (random weights accept almost nothing, so
+        benchmarks of the verify / rewind path prescribe the lengths)."""
+        sp = self.spec
+        if sp.force_accept_mean <= 0:
+            return sp.force_accept_len
+        if self._force_gen is None:
+            self._force_gen = torch.Generator().manual_seed(sp.force_seed)
+        hi = sp.draft_steps + 1
+        # binomial on (hi - 1) trials shifted by one has mean 1 + (hi - 1) p
+        p = min(max((sp.force_accept_mean - 1.0) / max(hi - 1, 1), 0.0), 1.0)
+        draws = (torch.rand(b, hi - 1, generator=self._force_gen) < p).sum(-1) + 1
+        return draws.to(torch.int32)
+
+    @staticmethod
+    def _ancestors(parents: torch.Tensor) -> torch.Tensor:
+        """``[B, R, R]`` bool: row r may attend row c iff c is r or one of its ancestors."""
+        b, r = parents.shape
+        a = torch.eye(r, dtype=torch.bool, device=parents.device).expand(b, r, r).clone()
+        p = parents.clamp(min=0)
+        has = (parents >= 0)[..., None]
+        for _ in range(r):
+            up = a.gather(1, p[..., None].expand(b, r, r)) & has
+            new = a | up
+            if torch.equal(new, a):
+                break
+            a = new
+        return a
+
+    @staticmethod
+    def _pack_mask(anc: torch.Tensor) -> torch.Tensor:
+        """Pack ``[B, R, R]`` bool into int32 words ``[B·R, ceil(R/32)]`` (bit c of row r)."""
+        b, r, _ = anc.shape
+        words = (r + 31) // 32
+        pad = torch.zeros(b, r, words * 32, dtype=torch.int64, device=anc.device)
+        pad[..., :r] = anc.long()
+        w = (pad.view(b, r, words, 32) << torch.arange(32, device=anc.device)).sum(-1)
+        w = torch.where(w >= 2 ** 31, w - 2 ** 32, w)
+        return w.to(torch.int32).view(b * r, words)
+
+    # ---- whole-request driver -----------------------------------------------------------------
+    @torch.no_grad()
+    def generate(self, seats: Sequence[int], prompts: Sequence[Sequence[int]], max_new_tokens: int,
+                 eos_token_id: Optional[int] = None) -> List[List[int]]:
+        first = self.prefill(seats, prompts)
+        outs = [[t] for t in first]
+        active = [i for i in range(len(seats)) if not (eos_token_id is not None and first[i] == eos_token_id) and max_new_tokens > 1]
+        while active:
+            emitted = self.round([seats[i] for i in active])
+            still = []
+            for i, e in zip(active, emitted):
+                for t in e:
+                    if len(outs[i]) >= max_new_tokens:
+                        break
+                    outs[i].append(t)
+                    if eos_token_id is not None and t == eos_token_id:
+                        break
+                done = len(outs[i]) >= max_new_tokens or (eos_token_id is not None and outs[i][-1] == eos_token_id)
+                if not done:
+                    still.append(i)
+            active = still
+        return outs
+
+    def release(self, seats: Sequence[int]) -> None:
+        for s in seats:
+            self.r.kv.free(s)
+            self.dkv.free(s)
+            self.root.pop(s, None); self.lp.pop(s, None); self.hid.pop(s, None)

@@ -85,10 +85,7 @@ def test_moe_block_matches_reference(cu, quant, tokens):
     from tensorrt_edge_llm_b200.models.qwen3_moe import MoEBlock
     kw = dict(num_hidden_layers=1, hidden_size=512, moe_intermediate_size=256, num_experts=16, num_experts_per_tok=4)
     cfg = qwen3_30b_a3b_config(**kw)
-    if quant == "nvfp4":
-        cfg.quant = QuantConfig(default="nvfp4")
-    else:
-        cfg.quant = QuantConfig()
+    cfg.quant = QuantConfig(quant_type="nvfp4") if quant == "nvfp4" else QuantConfig()
     blk = MoEBlock(cfg, "model.layers.0.mlp").cuda()
     blk.random_init(torch.Generator().manual_seed(3), std=0.05)
     blk.finalize()

@@ -1,0 +1,136 @@
+"""EAGLE-3 tree speculative decoding on CPU: lossless against plain greedy decoding, with a random
+draft (short acceptances) and with an oracle draft (every round accepts the whole chain)."""
+import torch
+
+from tensorrt_edge_llm_b200 import AutoModel
+from tensorrt_edge_llm_b200.config import tiny_llama_config
+from tensorrt_edge_llm_b200.ops import reference as ref
+from tensorrt_edge_llm_b200.runtime.kv_cache import KVCacheManager
+from tensorrt_edge_llm_b200.runtime.runner import ModelRunner
+from tensorrt_edge_llm_b200.runtime.speculative import EagleDecoder, SpecConfig, default_tap_layers
+
+
+def _target():
+    cfg = tiny_llama_config(num_hidden_layers=4, dtype="float32")
+    return AutoModel.from_config(cfg, random_init=1)
+
+
+def _draft(target_cfg, draft_vocab=0):
+    cfg = tiny_llama_config(num_hidden_layers=1, dtype="float32")
+    cfg.draft_type = "eagle3"
+    cfg.eagle3_target_hidden_size = target_cfg.hidden_size
+    cfg.draft_vocab_size = draft_vocab
+    return AutoModel.from_config(cfg, random_init=2)
+
+
+def _greedy(model, prompts, n_new):
+    kv = KVCacheManager(model.cfg, num_pages=64, page_size=16, max_seats=4, max_pages_per_seq=16)
+    r = ModelRunner(model, kv)
+    seats = list(range(len(prompts)))
+    logits = r.prefill(seats, prompts)
+    outs = [[int(t)] for t in logits.argmax(-1)]
+    for _ in range(n_new - 1):
+        logits = r.step(seats, [[o[-1]] for o in outs])
+        for o, t in zip(outs, logits.argmax(-1)):
+            o.append(int(t))
+    return outs
+
+
+def _decoder(model, draft, spec):
+    kv = KVCacheManager(model.cfg, num_pages=64, page_size=16, max_seats=4, max_pages_per_seq=16)
+    dkv = KVCacheManager(draft.cfg, num_pages=64, page_size=16, max_seats=4, max_pages_per_seq=16, num_layers=1)
+    return EagleDecoder(ModelRunner(model, kv), draft, dkv, spec)
+
+
+def test_tap_layers_and_mask_packing():
+    assert default_tap_layers(36) == [2, 18, 33]
+    assert len(default_tap_layers(2)) == 3
+    parents = torch.tensor([[-1, 0, 0, 1, 3, 2]])
+    anc = EagleDecoder._ancestors(parents)
+    assert anc[0, 4].tolist() == [True, True, False, True, True, False]
+    words = EagleDecoder._pack_mask(anc)
+    assert words.shape == (6, 1) and int(words[4, 0]) == 0b011011
+    big = EagleDecoder._pack_mask(torch.ones(1, 40, 40, dtype=torch.bool))
+    assert big.shape == (40, 2) and int(big[0, 0]) == -1 and int(big[0, 1]) == 0xFF
+
+
+def test_accept_and_commit_reference_ops():
+    tree = torch.tensor([[9, 5, 6, 7, 8, 4]], dtype=torch.int32)
+    par = torch.tensor([[-1, 0, 0, 1, 3, 2]], dtype=torch.int32)
+    tgt = torch.tensor([[5, 7, 0, 8, 1, 0]], dtype=torch.int32)          # root→1 (5) →3 (7) →4 (8) → bonus 1
+    path, plen, bonus = ref.spec_accept_greedy(tgt, tree, par, max_path=5)
+    assert plen.tolist() == [4] and path[0, :4].tolist() == [0, 1, 3, 4] and bonus.tolist() == [1]
+    path, plen, bonus = ref.spec_accept_greedy(tgt, tree, par, max_path=5, force_len=2)
+    assert plen.tolist() == [2] and path[0, :2].tolist() == [0, 1]
+    pool = torch.arange(2 * 4 * 2 * 1 * 4 * 2, dtype=torch.float32).view(2, 4, 2, 1, 4, 2).clone()
+    before = pool.clone()
+    table = torch.tensor([[2, 0, 3, -1]], dtype=torch.int32)
+    path = torch.tensor([[0, 2, 5, 0]], dtype=torch.int32)
+    ref.kv_commit_path(pool, table, torch.tensor([3]), path, torch.tensor([3]))
+    # slot 3+2=5 → 3+1=4 ; slot 3+5=8 → 3+2=5   (page size 4: slot s lives in page table[s // 4], row s % 4)
+    assert torch.equal(pool[:, 0, :, :, 0], before[:, 0, :, :, 1])        # slot 4 ← old slot 5 (page 0 rows 0 ← 1)
+    assert torch.equal(pool[:, 0, :, :, 1], before[:, 3, :, :, 0])        # slot 5 ← old slot 8 (page 3 row 0)
+    assert torch.equal(pool[:, 2], before[:, 2])                           # committed prefix untouched
+
+
+def test_random_draft_is_lossless():
+    model = _target()
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, model.cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 17)]
+    want = _greedy(model, prompts, 12)
+    for spec in (SpecConfig(draft_steps=3, top_k=3, verify_tokens=10), SpecConfig(draft_steps=1, top_k=4, verify_tokens=5)):
+        dec = _decoder(model, _draft(model.cfg), spec)
+        got = dec.generate([0, 1], prompts, 12)
+        assert got == want
+        assert dec.stats.mean_accept_length >= 1.0
+
+
+def test_reduced_draft_vocab_maps_through_d2t():
+    model = _target()
+    draft = _draft(model.cfg, draft_vocab=64)
+    draft.d2t.copy_(torch.arange(64, dtype=torch.int32) * 3)
+    prompts = [[1, 2, 3, 4, 5]]
+    dec = _decoder(model, draft, SpecConfig(draft_steps=2, top_k=2, verify_tokens=6))
+    assert dec.generate([0], prompts, 8) == _greedy(model, prompts, 8)
+
+
+class _OracleDraft(torch.nn.Module):
+    """Predicts the true greedy continuation: the row at position p proposes token p + 2 of the stream."""
+
+    def __init__(self, draft, streams):
+        super().__init__()
+        self.cfg, self.d2t, self.streams = draft.cfg, draft.d2t, streams
+
+    def forward(self, embeds, feature, meta, kv_pool):
+        v = self.d2t.numel()
+        rows = meta.logits_idx.long()
+        lp = torch.full((rows.numel(), v), -30.0) - torch.arange(v) * 1e-3
+        for j, r in enumerate(rows.tolist()):
+            s, p = int(meta.seq_ids[r]), int(meta.positions[r])
+            seq = self.streams[int(meta.slot_ids[s])]
+            if p + 2 < len(seq):
+                lp[j, seq[p + 2]] = 0.0
+        return lp, torch.zeros(embeds.shape[0], self.cfg.hidden_size)
+
+
+def test_oracle_draft_accepts_whole_chain():
+    model = _target()
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, model.cfg.vocab_size, (n,), generator=g).tolist() for n in (6, 11)]
+    want = _greedy(model, prompts, 21)
+    streams = {i: prompts[i] + want[i] for i in range(2)}
+    spec = SpecConfig(draft_steps=4, top_k=2, verify_tokens=12)
+    dec = _decoder(model, _OracleDraft(_draft(model.cfg), streams), spec)
+    got = dec.generate([0, 1], prompts, 21)
+    assert got == want
+    assert dec.stats.mean_accept_length > 4.5            # depth 4 + bonus = 5 tokens per round until the stream ends
+
+
+def test_forced_acceptance_length():
+    model = _target()
+    prompts = [[3, 1, 4, 1, 5, 9, 2, 6]]
+    dec = _decoder(model, _draft(model.cfg), SpecConfig(draft_steps=4, top_k=2, verify_tokens=12, force_accept_len=3))
+    dec.prefill([0], prompts)
+    for _ in range(4):
+        assert len(dec.round([0])[0]) == 3
+    assert dec.r.kv.lengths[0] == len(prompts[0]) + 12 and dec.dkv.lengths[0] == dec.r.kv.lengths[0]
