@@ -218,6 +218,202 @@ __global__ void ar_add_rmsnorm_kernel(ArParams p) {
     if (threadIdx.x == 0) p.row_epoch[row] = e;
 }
 
+
+// ---- reduce-scatter → residual add → RMSNorm (→ NVFP4) → all-gather ---------------------------------
+// Prefill-size messages.  The row-parallel GEMM before this kernel stored every output row straight
+// into its owner's partial buffer (reduce-scatter epilogue, peer stores); here the owner of a row
+//   1. learns that every rank's GEMM has finished (flag per source rank),
+//   2. sums the `world` partial rows in rank order (local reads), adds its shard of the residual
+//      stream (which stays token-sharded between layers) and normalises,
+//   3. pushes the normalised row — 16-bit, or NVFP4 values + scale bytes — into the gathered
+//      activation buffer of every rank (peer stores), and
+//   4. the last CTA of the grid publishes "my shard is gathered" to every rank.
+// The consuming GEMM waits for those flags in its TMA producer (all-gather prologue); with
+// `wait_gather` set the last CTA waits for them itself, so any later kernel may read the buffer.
+struct RsAgParams {
+    const void* partial;                 // local [world][rows_per_rank][hidden]
+    int* gemm_flags[kMaxRanks];          // every rank's "GEMM finished" flags [world]
+    int* ag_flags[kMaxRanks];            // every rank's "shard gathered" flags [world]
+    int* epoch;                          // local: number of completed calls
+    int* ticket;                         // local: CTA arrival counter (0 between calls)
+    const void* residual;                // local shard [rows_local, hidden], or all rows when residual_full
+    int residual_full;
+    const void* weight;
+    void* res_out;                       // local shard [rows_local, hidden]
+    void* gather_y[kMaxRanks];           // every rank's gathered 16-bit activations [rows, hidden] (or null)
+    uint8_t* gather_xq[kMaxRanks];       // every rank's gathered NVFP4 activations [rows, hidden / 2] (or null)
+    uint8_t* gather_sf[kMaxRanks];
+    const float* quant_scale;
+    int rank, world, rows, rows_per_rank, hidden, k64_pad, wait_gather;
+    float eps;
+    int* status;
+};
+
+__device__ __forceinline__ bool wait_flag_ge(const int* f, int e, int* status) {
+    const uint64_t t0 = global_timer_ns();
+    uint32_t it = 0;
+    while (ld_acquire_sys(f) - e < 0) {
+        if ((++it & 255u) == 0 && global_timer_ns() - t0 > kWaitLimitNs) {
+            atomicCAS(status, kStatusOk, kStatusPeerTimeout);
+            return false;
+        }
+    }
+    return true;
+}
+
+template <typename T, int kUnits>
+__global__ void rs_add_rmsnorm_ag_kernel(RsAgParams p) {
+    __shared__ float red[32];
+    __shared__ int s_ok, s_last;
+    pdl_prologue();
+    const int rows_local = max(0, min(p.rows_per_rank, p.rows - p.rank * p.rows_per_rank));
+    const int row = blockIdx.x;                          // local row
+    const int grow = p.rank * p.rows_per_rank + row;     // global row
+    const int nunits = p.hidden / 16;
+    const int e = *p.epoch + 1;
+    const bool has_row = row < rows_local;
+
+    // 1. my GEMM has finished (this kernel runs after it): tell every rank; then wait for theirs
+    if (blockIdx.x == 0 && threadIdx.x < p.world) st_release_sys(p.gemm_flags[threadIdx.x] + p.rank, e);
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (has_row && threadIdx.x < p.world && threadIdx.x != p.rank) {
+        if (!wait_flag_ge(p.gemm_flags[p.rank] + threadIdx.x, e, p.status)) s_ok = 0;
+    }
+    __syncthreads();
+
+    float v[kUnits][16];
+    if (has_row) {
+        // 2. sum the partial rows in rank order
+#pragma unroll
+        for (int u = 0; u < kUnits; ++u) {
+            const int idx = threadIdx.x + u * blockDim.x;
+            if (idx < nunits) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[u][i] = 0.f;
+                for (int r = 0; r < p.world; ++r) {
+                    const T* src = reinterpret_cast<const T*>(p.partial) + ((size_t)r * p.rows_per_rank + row) * p.hidden + idx * 16;
+                    const uint4 a0 = __ldcg(reinterpret_cast<const uint4*>(src)), a1 = __ldcg(reinterpret_cast<const uint4*>(src) + 1);
+                    const T* e0 = reinterpret_cast<const T*>(&a0);
+                    const T* e1 = reinterpret_cast<const T*>(&a1);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        v[u][i] += Cvt<T>::to_f(e0[i]);
+                        v[u][8 + i] += Cvt<T>::to_f(e1[i]);
+                    }
+                }
+            }
+        }
+        // residual add (the reduced projection is rounded once, like a 16-bit all-reduce result)
+        float ss = 0.f;
+        const size_t rrow = p.residual_full ? (size_t)grow : (size_t)row;
+#pragma unroll
+        for (int u = 0; u < kUnits; ++u) {
+            const int idx = threadIdx.x + u * blockDim.x;
+            if (idx < nunits) {
+                T o[16];
+                if (p.residual) {
+                    const T* rs = reinterpret_cast<const T*>(p.residual) + rrow * p.hidden + idx * 16;
+                    const uint4 r0 = reinterpret_cast<const uint4*>(rs)[0], r1 = reinterpret_cast<const uint4*>(rs)[1];
+                    const T* f0 = reinterpret_cast<const T*>(&r0);
+                    const T* f1 = reinterpret_cast<const T*>(&r1);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        o[i] = Cvt<T>::from_f(Cvt<T>::to_f(Cvt<T>::from_f(v[u][i])) + Cvt<T>::to_f(f0[i]));
+                        o[8 + i] = Cvt<T>::from_f(Cvt<T>::to_f(Cvt<T>::from_f(v[u][8 + i])) + Cvt<T>::to_f(f1[i]));
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) o[i] = Cvt<T>::from_f(v[u][i]);
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    v[u][i] = Cvt<T>::to_f(o[i]);
+                    ss += v[u][i] * v[u][i];
+                }
+                if (p.res_out) {
+                    T* dst = reinterpret_cast<T*>(p.res_out) + (size_t)row * p.hidden + idx * 16;
+                    reinterpret_cast<uint4*>(dst)[0] = *reinterpret_cast<uint4*>(&o[0]);
+                    reinterpret_cast<uint4*>(dst)[1] = *reinterpret_cast<uint4*>(&o[8]);
+                }
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+        if (lane == 0) red[wid] = ss;
+        __syncthreads();
+        float tot = lane < nw ? red[lane] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+        const float inv = p.weight ? rsqrtf(tot / p.hidden + p.eps) : 1.f;
+        const float gs = p.quant_scale ? *p.quant_scale : 1.f;
+        const float inv_gs = 1.f / gs;
+        // 3. normalise and push the row to every rank
+#pragma unroll
+        for (int u = 0; u < kUnits; ++u) {
+            const int idx = threadIdx.x + u * blockDim.x;
+            if (idx < nunits) {
+                float y[16];
+                T yo[16];
+                float amax = 0.f;
+                if (p.weight) {
+                    const T* wp = reinterpret_cast<const T*>(p.weight) + idx * 16;
+                    const uint4 w0 = reinterpret_cast<const uint4*>(wp)[0], w1 = reinterpret_cast<const uint4*>(wp)[1];
+                    const T* g0 = reinterpret_cast<const T*>(&w0);
+                    const T* g1 = reinterpret_cast<const T*>(&w1);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float n = Cvt<T>::to_f(Cvt<T>::from_f(v[u][i] * inv));
+                        yo[i] = Cvt<T>::from_f(n * Cvt<T>::to_f(i < 8 ? g0[i] : g1[i - 8]));
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) yo[i] = Cvt<T>::from_f(v[u][i]);
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    y[i] = Cvt<T>::to_f(yo[i]);
+                    amax = fmaxf(amax, fabsf(y[i]));
+                }
+                if (p.gather_y[0]) {
+                    const uint4 q0 = *reinterpret_cast<uint4*>(&yo[0]), q1 = *reinterpret_cast<uint4*>(&yo[8]);
+                    for (int r = 0; r < p.world; ++r) {
+                        T* dst = reinterpret_cast<T*>(p.gather_y[r]) + (size_t)grow * p.hidden + idx * 16;
+                        reinterpret_cast<uint4*>(dst)[0] = q0;
+                        reinterpret_cast<uint4*>(dst)[1] = q1;
+                    }
+                }
+                if (p.gather_xq[0]) {
+                    uint8_t s8;
+                    const uint2 packed = nvfp4_quantize_block16(y, amax, gs, inv_gs, s8);
+                    const size_t sfo = sf_atom_offset(grow, idx, p.k64_pad);
+                    for (int r = 0; r < p.world; ++r) {
+                        *reinterpret_cast<uint2*>(p.gather_xq[r] + (size_t)grow * (p.hidden / 2) + idx * 8) = packed;
+                        p.gather_sf[r][sfo] = s8;
+                    }
+                }
+            }
+        }
+    }
+    // 4. the last CTA publishes this rank's shard
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(p.ticket, 1) == (int)gridDim.x - 1;
+    __syncthreads();
+    if (s_last) {
+        __threadfence_system();
+        if (threadIdx.x < p.world) st_release_sys(p.ag_flags[threadIdx.x] + p.rank, e);
+        if (p.wait_gather && threadIdx.x < p.world && threadIdx.x != p.rank)
+            wait_flag_ge(p.ag_flags[p.rank] + threadIdx.x, e, p.status);
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            *p.ticket = 0;
+            *p.epoch = e;
+        }
+    }
+}
+
 }  // namespace telb
 
 using namespace telb;
@@ -269,5 +465,63 @@ extern "C" int telb_ar_add_rmsnorm(const void* x, void* const* sym_partial, int*
         if (per <= 1) TELB_AR(__half, 1); else if (per <= 2) TELB_AR(__half, 2); else TELB_AR(__half, 4);
     }
 #undef TELB_AR
+    return 0;
+}
+
+// Reduce-scatter (already stored by the GEMM epilogue) + residual + RMSNorm (+ NVFP4) + all-gather push.
+// Pointer tables hold `world` peer mappings each.  gather_y or (gather_xq, gather_sf) selects the output
+// form; weight == null skips the norm.  rows = global row count, rows_per_rank = ceil(rows / world).
+extern "C" int telb_rs_add_rmsnorm_ag(const void* partial, int* const* gemm_flags, int* const* ag_flags, int* epoch, int* ticket,
+                                      const void* residual, int residual_full, const void* weight, void* res_out,
+                                      void* const* gather_y, void* const* gather_xq, void* const* gather_sf,
+                                      const float* quant_scale, int rank, int world, int rows, int rows_per_rank, int hidden,
+                                      float eps, int wait_gather, int is_bf16, int* status, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (world < 1 || world > kMaxRanks) return fail("telb_rs_add_rmsnorm_ag: world size must be in [1, 8]");
+    if (hidden % 16) return fail("telb_rs_add_rmsnorm_ag: hidden must be a multiple of 16");
+    if (rows_per_rank * world < rows) return fail("telb_rs_add_rmsnorm_ag: rows_per_rank * world must cover the rows");
+    if (!gather_y && !gather_xq) return fail("telb_rs_add_rmsnorm_ag: no output buffer");
+    RsAgParams p{};
+    p.partial = partial;
+    for (int r = 0; r < world; ++r) {
+        p.gemm_flags[r] = gemm_flags[r];
+        p.ag_flags[r] = ag_flags[r];
+        if (gather_y) p.gather_y[r] = gather_y[r];
+        if (gather_xq) {
+            p.gather_xq[r] = (uint8_t*)gather_xq[r];
+            p.gather_sf[r] = (uint8_t*)gather_sf[r];
+        }
+    }
+    p.epoch = epoch;
+    p.ticket = ticket;
+    p.residual = residual;
+    p.residual_full = residual_full;
+    p.weight = weight;
+    p.res_out = res_out;
+    p.quant_scale = quant_scale;
+    p.rank = rank;
+    p.world = world;
+    p.rows = rows;
+    p.rows_per_rank = rows_per_rank;
+    p.hidden = hidden;
+    p.k64_pad = telb_nvfp4_k64_pad(hidden);
+    p.wait_gather = wait_gather;
+    p.eps = eps;
+    p.status = status;
+    int rows_local = rows - rank * rows_per_rank;
+    rows_local = rows_local < 0 ? 0 : (rows_local > rows_per_rank ? rows_per_rank : rows_local);
+    const int grid = rows_local > 0 ? rows_local : 1;
+    const int units = hidden / 16;
+    int threads = units >= 256 ? 256 : ((units + 31) / 32) * 32;
+    if (threads < 32) threads = 32;
+    const int per = (units + threads - 1) / threads;
+    if (per > 4) return fail("telb_rs_add_rmsnorm_ag: hidden too large (max 16384)");
+#define TELB_RS(T_, U_) TELB_LAUNCH("rs_add_rmsnorm_ag_kernel", (rs_add_rmsnorm_ag_kernel<T_, U_>), dim3(grid), dim3(threads), 0, stream, p)
+    if (is_bf16) {
+        if (per <= 1) TELB_RS(__nv_bfloat16, 1); else if (per <= 2) TELB_RS(__nv_bfloat16, 2); else TELB_RS(__nv_bfloat16, 4);
+    } else {
+        if (per <= 1) TELB_RS(__half, 1); else if (per <= 2) TELB_RS(__half, 2); else TELB_RS(__half, 4);
+    }
+#undef TELB_RS
     return 0;
 }

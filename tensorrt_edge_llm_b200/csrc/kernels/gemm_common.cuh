@@ -26,13 +26,75 @@ struct GemmParams {
     // tile_expert[ta] (rows [e * group_rows_b, (e+1) * group_rows_b) of the B tensor); -1 = unused tile.
     const int* tile_expert;
     int group_rows_b;
+    // Tensor-parallel fusion (both optional, large-M layout only).
+    //  reduce-scatter epilogue: output row r belongs to rank d = r / rs_rows_per_rank and is stored into
+    //  that rank's partial buffer rs_out[d] (a peer mapping) at row rs_rank * rs_rows_per_rank + (r - d * rpr).
+    void* rs_out[8];
+    int rs_world, rs_rank, rs_rows_per_rank;
+    //  all-gather prologue: rows [o * ag_rows_per_rank, ...) of the A operand were pushed into this GPU's
+    //  memory by rank o; the producer waits for ag_flags[o] to reach *ag_epoch before loading them.
+    const int* ag_flags;
+    const int* ag_epoch;
+    int ag_world, ag_rows_per_rank;
 };
+
+// Fusion request as the host passes it (same fields, plain C layout).
+struct TelbGemmFusion {
+    void* rs_out[8];
+    int rs_world, rs_rank, rs_rows_per_rank, pad0;
+    const int* ag_flags;
+    const int* ag_epoch;
+    int ag_world, ag_rows_per_rank;
+};
+
+inline void apply_fusion(GemmParams& p, const TelbGemmFusion* f) {
+    if (!f) return;
+    for (int i = 0; i < 8; ++i) p.rs_out[i] = f->rs_out[i];
+    p.rs_world = f->rs_world;
+    p.rs_rank = f->rs_rank;
+    p.rs_rows_per_rank = f->rs_rows_per_rank;
+    p.ag_flags = f->ag_flags;
+    p.ag_epoch = f->ag_epoch;
+    p.ag_world = f->ag_world;
+    p.ag_rows_per_rank = f->ag_rows_per_rank;
+}
+
+__device__ __forceinline__ int ld_acquire_sys_s32(const int* ptr) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+    return v;
+}
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;                       // 64 x 2 B = one 128-byte swizzle atom
 constexpr int kATileBytes = kBM * kBK * 2;    // 16 KiB
 constexpr int kGemmThreads = 192;
 constexpr int kRasterGroup = 8;
+
+// Producer side of the all-gather prologue: block until every rank that owns a row of the tile
+// [a0, a0 + 128) has published epoch `e` (bounded; false = gave up, status recorded).  Peers wrote the
+// rows with ordinary stores, the tile is read by TMA: the proxy fence orders the two.
+__device__ __forceinline__ bool ag_wait_rows(const GemmParams& p, int a0, int e, volatile uint32_t* abort_flag) {
+    const int last_row = min(a0 + kBM, p.rows_a) - 1;
+    const int o0 = a0 / p.ag_rows_per_rank, o1 = min(last_row / p.ag_rows_per_rank, p.ag_world - 1);
+    for (int o = o0; o <= o1; ++o) {
+        const uint64_t t0 = global_timer_ns();
+        uint32_t it = 0;
+        while (ld_acquire_sys_s32(p.ag_flags + o) - e < 0) {
+            if ((++it & 63u) == 0) {
+                if (*abort_flag) return false;
+                if (global_timer_ns() - t0 > kWaitLimitNs) {
+                    *abort_flag = 1;
+                    if (p.status) atomicCAS(p.status, kStatusOk, kStatusPeerTimeout);
+                    return false;
+                }
+            }
+        }
+    }
+    asm volatile("fence.proxy.async;" ::: "memory");
+    return true;
+}
+
 
 struct TileCoord {
     int a0, b0, kb0, kb1, tile, split;
@@ -175,6 +237,12 @@ __device__ __forceinline__ void gemm_epilogue_role(const GemmParams& p, uint32_t
         const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kAccStride;
         const int row = tc.a0 + lrow;
         const bool row_ok = row < p.rows_a;
+        int out_row = row;
+        if (p.rs_world > 1 && row_ok) {     // reduce-scatter: this row's partial goes to its owner's buffer
+            const int d = row / p.rs_rows_per_rank;
+            pt.c = p.rs_out[d];
+            out_row = p.rs_rank * p.rs_rows_per_rank + (row - d * p.rs_rows_per_rank);
+        }
         if (p.splits == 1) {
 #pragma unroll 1
             for (int c = 0; c < kChunks; ++c) {
@@ -195,8 +263,8 @@ __device__ __forceinline__ void gemm_epilogue_role(const GemmParams& p, uint32_t
                 const int col0 = b0 + c * 32;
                 int nvalid = min(min(32, BN - c * 32), p.rows_b - col0);
                 if (row_ok && nvalid > 0) {
-                    if (p.out_bf16) epilogue_store<__nv_bfloat16>(pt, v, row, col0, nvalid);
-                    else epilogue_store<__half>(pt, v, row, col0, nvalid);
+                    if (p.out_bf16) epilogue_store<__nv_bfloat16>(pt, v, out_row, col0, nvalid);
+                    else epilogue_store<__half>(pt, v, out_row, col0, nvalid);
                 }
             }
             tc_fence_before_sync();

@@ -89,11 +89,13 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            const int ag_e = p.ag_flags ? *p.ag_epoch : 0;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const TileCoord tc = decode_tile(p, t);
                 if (tc.skip) continue;
                 const int ta = tc.a0 / kBM;
                 const int b0 = (tc.brow >= 0 ? tc.brow : 0) + tc.b0 * BN;      // row of the B tensor
+                if (p.ag_flags && !ag_wait_rows(p, tc.a0, ag_e, abort_flag)) break;
                 for (int kb = tc.kb0; kb < tc.kb1; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
                         ok = false;
@@ -302,16 +304,19 @@ extern "C" int telb_nvfp4_quantize(const void* x, void* xq, void* sf_atoms, cons
 }
 
 // out[M,N] = dequant(xq, x_sf)[M,K] · dequant(wq, w_sf)[N,K]^T * alpha[N] (+bias +residual); K % 32 == 0.
-extern "C" int telb_gemm_nvfp4(const void* xq, const void* x_sf, const void* wq, const void* w_sf, void* out, int M, int N,
-                               int K, const float* alpha, const void* bias, const void* residual, int out_bf16, void* ws,
-                               long long ws_bytes, int* counters, int n_counters, int* status, int mode, int force_splits,
-                               cudaStream_t stream) {
+static int gemm_nvfp4_impl(const void* xq, const void* x_sf, const void* wq, const void* w_sf, void* out, int M, int N,
+                           int K, const float* alpha, const void* bias, const void* residual, int out_bf16, void* ws,
+                           long long ws_bytes, int* counters, int n_counters, int* status, int mode, int force_splits,
+                           const TelbGemmFusion* fusion, cudaStream_t stream) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (K % 32) return fail("telb_gemm_nvfp4: K must be a multiple of 32");
+    if (fusion) mode = 1;         // the fused collectives are written for the large-M layout
+    if (fusion && fusion->rs_world > 1 && residual) return fail("telb_gemm_nvfp4: reduce-scatter epilogue takes no residual");
     if (mode == 0 && M <= 128)
         return telb_gemm_skinny(1, xq, x_sf, wq, w_sf, out, M, N, K, alpha, bias, residual, out_bf16, status, 0, stream);
     const bool swapped = mode == 2 || (mode == 0 && M <= 128);
     GemmParams p{};
+    apply_fusion(p, fusion);
     p.k = K;
     p.kb_total = (K + kFp4BK - 1) / kFp4BK;
     p.c = out;
@@ -368,6 +373,25 @@ extern "C" int telb_gemm_nvfp4(const void* xq, const void* x_sf, const void* wq,
         case 64: return launch_nvfp4<64, 7>(ta, tb, sfa, sfb, k64, k64, p, stream);
         default: return launch_nvfp4<128, 5>(ta, tb, sfa, sfb, k64, k64, p, stream);
     }
+}
+
+extern "C" int telb_gemm_nvfp4(const void* xq, const void* x_sf, const void* wq, const void* w_sf, void* out, int M, int N,
+                               int K, const float* alpha, const void* bias, const void* residual, int out_bf16, void* ws,
+                               long long ws_bytes, int* counters, int n_counters, int* status, int mode, int force_splits,
+                               cudaStream_t stream) {
+    return gemm_nvfp4_impl(xq, x_sf, wq, w_sf, out, M, N, K, alpha, bias, residual, out_bf16, ws, ws_bytes, counters, n_counters,
+                           status, mode, force_splits, nullptr, stream);
+}
+
+// Same GEMM with a tensor-parallel collective fused in: a reduce-scatter epilogue (rows stored into
+// their owner's partial buffer over peer memory) and / or an all-gather prologue (the producer waits
+// for the rows other ranks push into this GPU's copy of the activations).  `out` is unused by the
+// reduce-scatter form.
+extern "C" int telb_gemm_nvfp4_fused(const void* xq, const void* x_sf, const void* wq, const void* w_sf, void* out, int M, int N,
+                                     int K, const float* alpha, const void* bias, int out_bf16, int* status,
+                                     const TelbGemmFusion* fusion, cudaStream_t stream) {
+    return gemm_nvfp4_impl(xq, x_sf, wq, w_sf, out, M, N, K, alpha, bias, nullptr, out_bf16, nullptr, 0, nullptr, 0, status, 1, 1,
+                           fusion, stream);
 }
 
 // Grouped NVFP4 GEMM for mixture-of-experts (see telb_gemm_f16_grouped): xq [rows_pad, K/2] with

@@ -72,10 +72,12 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            const int ag_e = p.ag_flags ? *p.ag_epoch : 0;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const TileCoord tc = decode_tile(p, t);
                 if (tc.skip) continue;
                 const int brow = (tc.brow >= 0 ? tc.brow : 0) + tc.b0 * BN;
+                if (p.ag_flags && !ag_wait_rows(p, tc.a0, ag_e, abort_flag)) break;
                 for (int kb = tc.kb0; kb < tc.kb1; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
                         ok = false;
@@ -182,11 +184,13 @@ extern "C" const char* telb_last_error() { return g_last_error; }
 //   bias / alpha : per output column (may be null);  residual : [M,N] like out (may be null)
 //   ws / counters: split-K scratch, used only by the small-M path (ws_bytes may be 0 → no split)
 //   mode         : 0 = choose, 1 = force large-M layout, 2 = force swapped layout
-extern "C" int telb_gemm_f16(const void* x, const void* w, void* out, int M, int N, int K, const void* bias,
-                             const float* alpha, const void* residual, int is_bf16, void* ws, long long ws_bytes,
-                             int* counters, int n_counters, int* status, int mode, int force_splits,
-                             cudaStream_t stream) {
+static int gemm_f16_impl(const void* x, const void* w, void* out, int M, int N, int K, const void* bias,
+                         const float* alpha, const void* residual, int is_bf16, void* ws, long long ws_bytes,
+                         int* counters, int n_counters, int* status, int mode, int force_splits,
+                         const TelbGemmFusion* fusion, cudaStream_t stream) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (fusion) mode = 1;         // the fused collectives are written for the large-M layout
+    if (fusion && fusion->rs_world > 1 && residual) return fail("telb_gemm_f16: reduce-scatter epilogue takes no residual");
     if (K % 8) return fail("telb_gemm_f16: K must be a multiple of 8");
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return fail("telb_gemm_f16: operands must be 16-byte aligned");
     if (mode == 0 && M <= 128)
@@ -194,6 +198,7 @@ extern "C" int telb_gemm_f16(const void* x, const void* w, void* out, int M, int
     const CUtensorMapDataType dt = is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const bool swapped = mode == 2 || (mode == 0 && M <= 128);
     GemmParams p{};
+    apply_fusion(p, fusion);
     p.k = K;
     p.kb_total = (K + kBK - 1) / kBK;
     p.c = out;
@@ -243,6 +248,22 @@ extern "C" int telb_gemm_f16(const void* x, const void* w, void* out, int M, int
         case 128: return launch_gemm<128, 6>(ta, tb, p, stream);
         default: return launch_gemm<256, 4>(ta, tb, p, stream);
     }
+}
+
+extern "C" int telb_gemm_f16(const void* x, const void* w, void* out, int M, int N, int K, const void* bias,
+                             const float* alpha, const void* residual, int is_bf16, void* ws, long long ws_bytes,
+                             int* counters, int n_counters, int* status, int mode, int force_splits,
+                             cudaStream_t stream) {
+    return gemm_f16_impl(x, w, out, M, N, K, bias, alpha, residual, is_bf16, ws, ws_bytes, counters, n_counters, status, mode,
+                         force_splits, nullptr, stream);
+}
+
+// Same GEMM with a tensor-parallel collective fused in (see TelbGemmFusion): reduce-scatter epilogue
+// and / or all-gather prologue.  `out` is unused by the reduce-scatter form.
+extern "C" int telb_gemm_f16_fused(const void* x, const void* w, void* out, int M, int N, int K, const void* bias,
+                                   const float* alpha, int is_bf16, int* status, const TelbGemmFusion* fusion,
+                                   cudaStream_t stream) {
+    return gemm_f16_impl(x, w, out, M, N, K, bias, alpha, nullptr, is_bf16, nullptr, 0, nullptr, 0, status, 1, 1, fusion, stream);
 }
 
 // Grouped form for mixture-of-experts: x [rows_pad, K] is the routed activations in 128-row padded

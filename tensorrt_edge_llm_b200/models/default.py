@@ -106,10 +106,13 @@ class DecoderLayer(nn.Module):
             residual = h
             x = ops.rmsnorm_maybe_quant(h, self.input_layernorm.weight, self.input_layernorm.eps, qs_attn)
         else:
-            x, residual = comm.add_rmsnorm(h, residual, self.input_layernorm.weight, self.input_layernorm.eps, qs_attn)
+            x, residual = comm.add_rmsnorm(h, residual, self.input_layernorm.weight, self.input_layernorm.eps, qs_attn,
+                                           defer_gather=True)
         a = self.self_attn(x, meta, kv_layer, cos_sin)
+        # the normalised rows feed one GEMM each (QKV above, gate/up below), which may wait for the gather itself
         x, residual = comm.add_rmsnorm(a, residual, self.post_attention_layernorm.weight,
-                                       self.post_attention_layernorm.eps, self.mlp.gate_up_proj.fused_input_scale())
+                                       self.post_attention_layernorm.eps, self.mlp.gate_up_proj.fused_input_scale(),
+                                       defer_gather=True)
         return self.mlp(x), residual
 
 
@@ -126,12 +129,17 @@ class Transformer(nn.Module):
         h = ops.embedding(ids, self.embed_tokens.weight) if inputs_embeds is None else inputs_embeds
         residual = None
         taps = []
+        rs_was = getattr(comm, "rs_enabled", None)
+        if capture_layers and rs_was:
+            comm.rs_enabled = False          # tapping hidden states needs the whole residual stream on every rank
         for i, layer in enumerate(self.layers):
             h, residual = layer(h, residual, meta, kv_cache[i], cos_sin, comm)
             if i in capture_layers:
                 taps.append((h.float() + residual.float()).to(h.dtype) if comm.world_size == 1
                             else comm.all_reduce(h).add_(residual))
         x, _ = comm.add_rmsnorm(h, residual, self.norm.weight, self.norm.eps)
+        if capture_layers and rs_was:
+            comm.rs_enabled = True
         return (x, taps) if capture_layers else x
 
 
@@ -152,6 +160,12 @@ class CausalLM(nn.Module):
         self.lm_head = make_linear(cfg, "lm_head", cfg.hidden_size, [cfg.vocab_size],
                                    TPMode.COL if cfg.tp_size > 1 and cfg.vocab_size % cfg.tp_size == 0 else TPMode.REPLICATED)
         self._cos_sin: Optional[torch.Tensor] = None
+        if self.transformer_cls is None and hasattr(self.comm, "gemm_reduce_scatter"):
+            # dense decoder: every row-parallel projection is followed by comm.add_rmsnorm, so its GEMM may
+            # hand the rows to their owner ranks itself (reduce-scatter epilogue) at prefill sizes
+            for layer in self.model.layers:
+                layer.self_attn.o_proj.rs_comm = self.comm
+                layer.mlp.down_proj.rs_comm = self.comm
 
     def cos_sin(self, device) -> torch.Tensor:
         if self._cos_sin is None or self._cos_sin.device != torch.device(device):

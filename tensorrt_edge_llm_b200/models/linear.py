@@ -40,6 +40,8 @@ def _shard(t: torch.Tensor, dim: int, rank: int, world: int) -> torch.Tensor:
 class LinearBase(nn.Module):
     """Common bookkeeping: logical sizes, TP placement and the checkpoint modules it fuses."""
 
+    rs_comm = None      # set on row-parallel layers whose output may leave through a reduce-scatter epilogue
+
     def __init__(self, in_features: int, out_features: Sequence[int], tp_mode: TPMode, tp_size: int, tp_rank: int,
                  sources: Optional[List[str]] = None, bias: bool = False, row_ranges=None):
         super().__init__()
@@ -114,6 +116,12 @@ class Linear(LinearBase):
             self.bias.data.copy_(b.to(self.bias.dtype))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.is_cuda:
+            if self.rs_comm is not None and self.rs_comm.use_rs(x.shape[0]):
+                return self.rs_comm.gemm_reduce_scatter(self, x)        # rows go straight to their owner rank
+            ag = getattr(x, "ag_wait", None)
+            if ag is not None:                                          # rows still arriving from peers
+                return ops.cuda_ops().gemm_fused(x, self.weight, ag, bias=self.bias)
         return ops.linear(x, self.weight, self.bias)
 
 
@@ -186,6 +194,12 @@ class NVFP4Linear(LinearBase):
         if x.is_cuda:
             if self._gpu_weight_sf is None:
                 self.finalize()
+            if self.quantize_activations:
+                if self.rs_comm is not None and self.rs_comm.use_rs(x.shape[0]):
+                    return self.rs_comm.gemm_reduce_scatter(self, x)
+                ag = getattr(x, "ag_wait", None)
+                if ag is not None:
+                    return ops.cuda_ops().gemm_fused(x, self.weight, ag, w_sf=self._gpu_weight_sf, alpha=self.alpha, bias=self.bias)
             return ops.cuda_ops().nvfp4_linear(x, self.weight, self._gpu_weight_sf, self.alpha, self.input_scale,
                                                self.bias, self.quantize_activations)
         xa = x.float()

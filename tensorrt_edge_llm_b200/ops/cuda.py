@@ -283,10 +283,11 @@ def nvfp4_swizzle_scales(weight_scale: torch.Tensor) -> torch.Tensor:
 class QuantActs:
     """Activations already quantised to NVFP4 by their producer (packed codes + atom-layout scales)."""
 
-    __slots__ = ("xq", "sf", "shape", "dtype")
+    __slots__ = ("xq", "sf", "shape", "dtype", "ag_wait")
 
     def __init__(self, xq: torch.Tensor, sf: torch.Tensor, shape, dtype):
         self.xq, self.sf, self.shape, self.dtype = xq, sf, tuple(shape), dtype
+        self.ag_wait = None      # GemmFusion when the rows are still being gathered from peers
 
     @property
     def is_cuda(self) -> bool:
@@ -366,6 +367,35 @@ def nvfp4_linear(x, weight, weight_sf_atoms, alpha, input_scale, bias=None, quan
     xq, x_sf = nvfp4_quantize(x2, input_scale)
     out = gemm_nvfp4(xq, x_sf, weight, weight_sf_atoms, alpha, x.dtype, bias)
     return out.reshape(*lead, weight.shape[0])
+
+
+class GemmFusion(ctypes.Structure):
+    """Host mirror of ``TelbGemmFusion`` (``csrc/kernels/gemm_common.cuh``)."""
+    _fields_ = [("rs_out", c_vp * 8), ("rs_world", c_int), ("rs_rank", c_int), ("rs_rows_per_rank", c_int), ("pad0", c_int),
+                ("ag_flags", c_vp), ("ag_epoch", c_vp), ("ag_world", c_int), ("ag_rows_per_rank", c_int)]
+
+
+def gemm_fused(x, weight, fusion: GemmFusion, *, w_sf=None, alpha=None, bias=None, out=None, out_dtype=None):
+    """Large-M GEMM with a fused tensor-parallel collective: ``x`` is 16-bit ``[M, K]`` or ``QuantActs``.
+    With a reduce-scatter epilogue the rows land in the peers' partial buffers and nothing is returned."""
+    ws = Workspace.get(weight.device)
+    scatter = fusion.rs_world > 1
+    if isinstance(x, QuantActs):
+        m, n, k = x.xq.shape[0], weight.shape[0], x.xq.shape[1] * 2
+        dt = out_dtype or x.dtype
+        if out is None and not scatter:
+            out = torch.empty(m, n, dtype=dt, device=weight.device)
+        _check(lib().telb_gemm_nvfp4_fused(_p(x.xq), _p(x.sf), _p(weight), _p(w_sf), _p(out), c_int(m), c_int(n), c_int(k), _p(alpha),
+                                           _p(bias), c_int(1 if dt == torch.bfloat16 else 0), _p(ws.status), ctypes.byref(fusion),
+                                           _stream()), "gemm_nvfp4_fused")
+        return out
+    m, k = x.shape
+    n = weight.shape[0]
+    if out is None and not scatter:
+        out = torch.empty(m, n, dtype=x.dtype, device=x.device)
+    _check(lib().telb_gemm_f16_fused(_p(x), _p(weight), _p(out), c_int(m), c_int(n), c_int(k), _p(bias), _p(alpha), c_int(_is_bf16(x)),
+                                     _p(ws.status), ctypes.byref(fusion), _stream()), "gemm_f16_fused")
+    return out
 
 
 def gemm_skinny(x, weight, *, x_sf=None, w_sf=None, alpha=None, bias=None, residual=None, out_dtype=None, ranks: int = 0):

@@ -42,7 +42,9 @@ class LocalComm:
     def all_to_all(self, send: torch.Tensor, send_counts: List[int], recv_counts: List[int]) -> torch.Tensor:
         return send
 
-    def add_rmsnorm(self, x_partial, residual, weight, eps, quant_scale=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    def add_rmsnorm(self, x_partial, residual, weight, eps, quant_scale=None, defer_gather=False) -> Tuple[torch.Tensor, torch.Tensor]:
+        """``defer_gather`` is a hint that the normalised output feeds exactly one GEMM, which may then
+        wait for the gathered rows itself; communicators without a fused gather ignore it."""
         return ops.add_rmsnorm(x_partial, residual, weight, eps, quant_scale)
 
     def barrier(self) -> None:
@@ -103,7 +105,7 @@ class TorchComm(LocalComm):
         self.dist.all_to_all_single(out, send.contiguous(), recv_counts, send_counts, group=self.group)
         return out
 
-    def add_rmsnorm(self, x_partial, residual, weight, eps, quant_scale=None):
+    def add_rmsnorm(self, x_partial, residual, weight, eps, quant_scale=None, defer_gather=False):
         return ops.add_rmsnorm(self.all_reduce(x_partial), residual, weight, eps, quant_scale)
 
     def barrier(self):

@@ -22,6 +22,56 @@ from .comm import TorchComm
 MAX_ROWS = 256
 
 
+class RsPartial:
+    """Marker for a row-parallel projection whose partial rows were stored into their owners'
+    symmetric buffers by the GEMM epilogue; only ``add_rmsnorm`` can consume it."""
+
+    __slots__ = ("rows", "hidden", "dtype", "rows_per_rank")
+    is_cuda = True
+
+    def __init__(self, rows, hidden, dtype, rows_per_rank):
+        self.rows, self.hidden, self.dtype, self.rows_per_rank = rows, hidden, dtype, rows_per_rank
+
+    @property
+    def shape(self):
+        return (self.rows, self.hidden)
+
+
+class _RsState:
+    """Symmetric buffers of the reduce-scatter / all-gather path for one hidden size."""
+
+    def __init__(self, device, hidden: int, dtype: torch.dtype, group, max_tokens: int, cu):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        gname = group.group_name if group is not None else dist.group.WORLD.group_name
+        world = dist.get_world_size(group)
+        self.cap = max_tokens + world
+        L = cu.lib()
+        L.telb_nvfp4_sf_bytes.restype = ctypes.c_longlong
+        sf_bytes = int(L.telb_nvfp4_sf_bytes(ctypes.c_longlong(self.cap), ctypes.c_int(hidden)))
+        self.partial = symm_mem.empty(self.cap * hidden, dtype=dtype, device=device)
+        self.gather_y = symm_mem.empty(self.cap * hidden, dtype=dtype, device=device)
+        self.gather_xq = symm_mem.empty(self.cap * hidden // 2, dtype=torch.uint8, device=device)
+        self.gather_sf = symm_mem.empty(sf_bytes, dtype=torch.uint8, device=device)
+        self.flags = symm_mem.empty(16, dtype=torch.int32, device=device)       # [0:8] GEMM finished, [8:16] shard gathered
+        self.flags.zero_()
+        self.gather_sf.zero_()
+        hs = {n: symm_mem.rendezvous(getattr(self, n), gname) for n in ("partial", "gather_y", "gather_xq", "gather_sf", "flags")}
+        self._handles = hs
+
+        def table(name, offset_bytes=0):
+            return (ctypes.c_void_p * world)(*[int(p) + offset_bytes for p in hs[name].buffer_ptrs])
+
+        self.c_partial, self.c_gather_y = table("partial"), table("gather_y")
+        self.c_gather_xq, self.c_gather_sf = table("gather_xq"), table("gather_sf")
+        self.c_gemm_flags, self.c_ag_flags = table("flags"), table("flags", 32)
+        self.partial_ptrs = [int(p) for p in hs["partial"].buffer_ptrs]
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self.ticket = torch.zeros(1, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+
 class _SymState:
     def __init__(self, device, hidden: int, dtype: torch.dtype, group):
         import torch.distributed as dist
@@ -43,10 +93,90 @@ class _SymState:
 
 
 class FusedComm(TorchComm):
-    def __init__(self, device=None, group=None):
+    def __init__(self, device=None, group=None, rs_max_tokens: int = 8192, rs_min_rows: int = MAX_ROWS + 1):
         super().__init__(group)
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         self._sym: Dict[Tuple[int, torch.dtype], _SymState] = {}
+        self._rs: Dict[Tuple[int, torch.dtype], _RsState] = {}
+        self.rs_max_tokens = rs_max_tokens
+        self.rs_min_rows = rs_min_rows          # below this the one-shot all-reduce is faster
+        self.rs_enabled = True
+        self.rs_single_rank = False             # tests: run the fused path on one rank too
+
+    # ---- prefill path: GEMM → reduce-scatter epilogue, norm, all-gather → GEMM prologue -----------
+    def use_rs(self, rows: int) -> bool:
+        return (self.rs_enabled and (self.world_size > 1 or self.rs_single_rank)
+                and self.rs_min_rows <= rows <= self.rs_max_tokens)
+
+    def _rs_state(self, hidden: int, dtype: torch.dtype) -> _RsState:
+        key = (hidden, dtype)
+        st = self._rs.get(key)
+        if st is None:
+            st = self._rs[key] = _RsState(self.device, hidden, dtype, self.group, self.rs_max_tokens, ops.cuda_ops())
+        return st
+
+    def prepare_rs(self, hidden: int, dtype: torch.dtype) -> None:
+        """Allocate and exchange the reduce-scatter / all-gather buffers up front (collective)."""
+        self._rs_state(hidden, dtype)
+
+    def gemm_reduce_scatter(self, linear, x) -> RsPartial:
+        """Row-parallel projection whose epilogue stores each output row into its owner's partial
+        buffer over peer memory (``x`` 16-bit or NVFP4 ``QuantActs``)."""
+        cu = ops.cuda_ops()
+        rows = x.shape[0]
+        dtype = x.dtype
+        st = self._rs_state(linear.out_features, dtype)
+        rpr = (rows + self.world_size - 1) // self.world_size
+        f = cu.GemmFusion()
+        for r in range(self.world_size):
+            f.rs_out[r] = st.partial_ptrs[r]
+        f.rs_world = max(self.world_size, 2) if self.world_size == 1 else self.world_size
+        f.rs_rank, f.rs_rows_per_rank = self.rank, rpr
+        if self.world_size == 1:                 # single-rank test mode: "scatter" into the local buffer
+            f.rs_out[1] = st.partial_ptrs[0]
+            f.rs_rows_per_rank = rpr = rows
+        ag = getattr(x, "ag_wait", None)
+        if ag is not None:
+            f.ag_flags, f.ag_epoch, f.ag_world, f.ag_rows_per_rank = ag.ag_flags, ag.ag_epoch, ag.ag_world, ag.ag_rows_per_rank
+        if hasattr(linear, "_gpu_weight_sf"):    # NVFP4: quantise 16-bit activations first
+            if not isinstance(x, cu.QuantActs):
+                x2 = x.reshape(-1, x.shape[-1])
+                xq, sf = cu.nvfp4_quantize(x2, linear.input_scale)
+                x = cu.QuantActs(xq, sf, x2.shape, dtype)
+            cu.gemm_fused(x, linear.weight, f, w_sf=linear._gpu_weight_sf, alpha=linear.alpha, bias=linear.bias)
+        else:
+            cu.gemm_fused(x.reshape(-1, x.shape[-1]).contiguous(), linear.weight, f, bias=linear.bias)
+        return RsPartial(rows, linear.out_features, dtype, rpr)
+
+    def _rs_add_rmsnorm(self, part: RsPartial, residual, weight, eps, quant_scale, defer_gather):
+        cu = ops.cuda_ops()
+        st = self._rs_state(part.hidden, part.dtype)
+        rows, hidden, rpr = part.rows, part.hidden, part.rows_per_rank
+        rows_local = max(0, min(rpr, rows - self.rank * rpr))
+        res_out = torch.empty(rows_local, hidden, dtype=part.dtype, device=self.device)
+        full = 1 if (residual is not None and residual.shape[0] == rows and (rows_local != rows or self.world_size == 1)) else 0
+        ws = cu.Workspace.get(self.device)
+        quant = quant_scale is not None
+        cu._check(cu.lib().telb_rs_add_rmsnorm_ag(
+            cu._p(st.partial), st.c_gemm_flags, st.c_ag_flags, cu._p(st.epoch), cu._p(st.ticket), cu._p(residual), ctypes.c_int(full),
+            cu._p(weight), cu._p(res_out), None if quant else st.c_gather_y, st.c_gather_xq if quant else None,
+            st.c_gather_sf if quant else None, cu._p(quant_scale), ctypes.c_int(self.rank), ctypes.c_int(self.world_size),
+            ctypes.c_int(rows), ctypes.c_int(rpr), ctypes.c_int(hidden), ctypes.c_float(eps), ctypes.c_int(0 if defer_gather else 1),
+            ctypes.c_int(cu._is_bf16(res_out)), cu._p(ws.status), cu._stream()), "rs_add_rmsnorm_ag")
+        wait = None
+        if defer_gather and self.world_size > 1:
+            wait = cu.GemmFusion()
+            wait.ag_flags = st.flags.data_ptr() + 32
+            wait.ag_epoch = st.epoch.data_ptr()
+            wait.ag_world, wait.ag_rows_per_rank = self.world_size, rpr
+        if quant:
+            y = cu.QuantActs(st.gather_xq[:rows * hidden // 2].view(rows, hidden // 2), st.gather_sf, (rows, hidden), part.dtype)
+            y.ag_wait = wait
+        else:
+            y = st.gather_y[:rows * hidden].view(rows, hidden)
+            if wait is not None:
+                y.ag_wait = wait
+        return y, res_out
 
     def _state(self, hidden: int, dtype: torch.dtype) -> _SymState:
         key = (hidden, dtype)
@@ -59,7 +189,9 @@ class FusedComm(TorchComm):
         """Allocate and exchange the symmetric buffers up front (collective; call before capture)."""
         self._state(hidden, dtype)
 
-    def add_rmsnorm(self, x_partial, residual, weight, eps, quant_scale=None):
+    def add_rmsnorm(self, x_partial, residual, weight, eps, quant_scale=None, defer_gather=False):
+        if isinstance(x_partial, RsPartial):
+            return self._rs_add_rmsnorm(x_partial, residual, weight, eps, quant_scale, defer_gather)
         rows, hidden = x_partial.shape
         if not x_partial.is_cuda or rows > MAX_ROWS or hidden % 16:
             return super().add_rmsnorm(x_partial, residual, weight, eps, quant_scale)

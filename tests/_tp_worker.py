@@ -13,6 +13,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 def main():
     backend, kind, ckpt = sys.argv[1], sys.argv[2], sys.argv[3]
+    prompt_len = int(sys.argv[4]) if len(sys.argv) > 4 else 70
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     if backend == "nccl":
@@ -33,7 +34,7 @@ def main():
         kv = KVCacheManager(model.cfg, num_pages=24, page_size=64, max_seats=4, max_pages_per_seq=6, device=dev)
         r = ModelRunner(model, kv, dev)
         g = torch.Generator().manual_seed(3)
-        prompts = torch.randint(0, model.cfg.vocab_size, (2, 70), generator=g).tolist()
+        prompts = torch.randint(0, model.cfg.vocab_size, (2, prompt_len), generator=g).tolist()
         logits = r.prefill([0, 1], prompts)
         first = logits.float().argmax(-1).to(torch.int32)
         toks = r.decode_greedy([0, 1], first, 6)
@@ -47,6 +48,9 @@ def main():
     tol = 1e-4 if dev.type == "cpu" else 0.06
     ok = err <= tol * max(scale, 1.0)
     same = (tp_toks == ref_toks).float().mean().item()
+    if kind == "fused" and 2 * prompt_len > 256 and world > 1 and not comm._rs:
+        print(f"rank {rank}: the reduce-scatter path was not taken", flush=True)
+        ok = False
     gathered = [None] * world
     dist.all_gather_object(gathered, tp_toks.tolist())
     identical = all(g == gathered[0] for g in gathered)

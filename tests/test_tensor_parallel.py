@@ -31,10 +31,10 @@ def _make_ckpt(d, dtype):
         json.dump(hf, f)
 
 
-def _launch(nproc, backend, kind, ckpt, port):
+def _launch(nproc, backend, kind, ckpt, port, prompt_len=70):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "_tp_worker.py"),
-           backend, kind, ckpt]
+           backend, kind, ckpt, str(prompt_len)]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", OMP_NUM_THREADS="2")
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
@@ -54,6 +54,17 @@ def test_tp2_matches_tp1_gpu(tmp_path, kind):
         pytest.skip("needs two GPUs")
     _make_ckpt(str(tmp_path), torch.bfloat16)
     out = _launch(2, "nccl", kind, str(tmp_path), 29612 if kind == "nccl" else 29613)
+    assert "ranks identical True" in out
+
+
+@pytest.mark.gpu
+def test_tp2_fused_prefill_reduce_scatter_path(tmp_path):
+    """Prompts long enough (2 x 190 rows) that the row-parallel GEMMs leave through the reduce-scatter
+    epilogue and the column-parallel GEMMs wait for the all-gather in their prologue."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _make_ckpt(str(tmp_path), torch.bfloat16)
+    out = _launch(2, "nccl", "fused", str(tmp_path), 29614, prompt_len=190)
     assert "ranks identical True" in out
 
 
