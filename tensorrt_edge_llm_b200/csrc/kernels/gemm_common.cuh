@@ -207,13 +207,54 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const float 
     }
 }
 
+// A full 32-column chunk of one accumulator row → 64 bytes of 16-bit output, with the per-column
+// scale and bias applied (no residual).  Requires col0 % 8 == 0 and all 32 columns valid.
+template <typename T>
+__device__ __forceinline__ void pack_chunk(const GemmParams& p, const float (&v)[32], int col0, uint4 (&u)[4]) {
+    float o[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) o[j] = v[j];
+    if (p.alpha) {
+        const float4* ap = reinterpret_cast<const float4*>(p.alpha + col0);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float4 a = __ldg(&ap[q]);
+            o[4 * q] *= a.x;
+            o[4 * q + 1] *= a.y;
+            o[4 * q + 2] *= a.z;
+            o[4 * q + 3] *= a.w;
+        }
+    }
+    if (p.bias) {
+        const uint4* bp = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.bias) + col0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint4 b = __ldg(&bp[q]);
+            const T* e = reinterpret_cast<const T*>(&b);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[8 * q + i] += Cvt<T>::to_f(e[i]);
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        u[q].x = Cvt<T>::pack2(o[q * 8 + 0], o[q * 8 + 1]);
+        u[q].y = Cvt<T>::pack2(o[q * 8 + 2], o[q * 8 + 3]);
+        u[q].z = Cvt<T>::pack2(o[q * 8 + 4], o[q * 8 + 5]);
+        u[q].w = Cvt<T>::pack2(o[q * 8 + 6], o[q * 8 + 7]);
+    }
+}
+
+constexpr int kRsStageRowBytes = 144;                        // 64 columns x 2 B + 16 B pad (conflict-free 16 B accesses)
+constexpr int kRsStageBytes = 4 * 32 * kRsStageRowBytes;     // one 32-row slab per epilogue warp
+
 // The epilogue role (warps 2-5, 128 threads): drains finished accumulators from TMEM.  Without
 // split-K each thread converts and stores its row.  With split-K it parks the fp32 partial row in
 // the workspace; the CTA that arrives last at the tile's counter sums all partials and stores.
 template <int BN>
 __device__ __forceinline__ void gemm_epilogue_role(const GemmParams& p, uint32_t tmem_base, uint64_t* tfull_bar,
                                                    uint64_t* tempty_bar, volatile uint32_t* abort_flag,
-                                                   volatile uint32_t* last_flag, int total_tiles, int acc_stride) {
+                                                   volatile uint32_t* last_flag, int total_tiles, int acc_stride,
+                                                   uint8_t* rs_stage = nullptr) {
     constexpr int kChunks = (BN + 31) / 32;
     const int kAccStride = acc_stride;
     const int warp = threadIdx.x >> 5;
@@ -243,7 +284,51 @@ __device__ __forceinline__ void gemm_epilogue_role(const GemmParams& p, uint32_t
             pt.c = p.rs_out[d];
             out_row = p.rs_rank * p.rs_rows_per_rank + (row - d * p.rs_rows_per_rank);
         }
-        if (p.splits == 1) {
+        if (p.splits == 1 && p.rs_world > 1 && rs_stage != nullptr && BN >= 64) {
+            // Reduce-scatter epilogue.  A lane owns a row, but 64-byte pieces of 32 different rows per store
+            // make poor use of NVLink: two 32-column chunks are transposed through a per-warp slab of shared
+            // memory and leave as whole 128-byte lines, four rows per store instruction.
+            uint8_t* slab = rs_stage + quad * (32 * kRsStageRowBytes);
+            const int seg = lane & 7, rsub = lane >> 3;
+            if constexpr (BN >= 64) {
+#pragma unroll 1
+                for (int c = 0; c < kChunks; c += 2) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t r[32];
+                        tmem_ld_x32(t_addr + (c + h) * 32, r);
+                        tmem_ld_wait();
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                        uint4 u[4];
+                        const int col0 = min(b0 + (c + h) * 32, max(p.rows_b - 32, 0));   // clamp: columns past N are not stored
+                        if (p.out_bf16) pack_chunk<__nv_bfloat16>(pt, v, col0, u);
+                        else pack_chunk<__half>(pt, v, col0, u);
+                        uint4* dst = reinterpret_cast<uint4*>(slab + lane * kRsStageRowBytes + h * 64);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) dst[q] = u[q];
+                    }
+                    __syncwarp();
+                    const int colseg = b0 + c * 32 + seg * 8;           // first of this lane's 8 columns
+#pragma unroll
+                    for (int rr = 0; rr < 32; rr += 4) {
+                        const int lr = rr + rsub;
+                        const int grow = tc.a0 + quad * 32 + lr;
+                        if (grow < p.rows_a && colseg + 8 <= p.rows_b) {
+                            const int d = grow / p.rs_rows_per_rank;
+                            const size_t orow = (size_t)p.rs_rank * p.rs_rows_per_rank + (grow - d * p.rs_rows_per_rank);
+                            const uint4 val = *reinterpret_cast<const uint4*>(slab + lr * kRsStageRowBytes + seg * 16);
+                            uint16_t* base = reinterpret_cast<uint16_t*>(p.rs_out[d]);
+                            *reinterpret_cast<uint4*>(base + orow * (size_t)p.ldc_lane + colseg) = val;
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&tempty_bar[acc]);
+        } else if (p.splits == 1) {
 #pragma unroll 1
             for (int c = 0; c < kChunks; ++c) {
                 float v[32];

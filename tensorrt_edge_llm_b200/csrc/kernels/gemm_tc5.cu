@@ -136,7 +136,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             }
         }
     } else {
-        gemm_epilogue_role<BN>(p, tmem_base, tfull_bar, tempty_bar, abort_flag, last_flag, total_tiles, kAccStride);
+        gemm_epilogue_role<BN>(p, tmem_base, tfull_bar, tempty_bar, abort_flag, last_flag, total_tiles, kAccStride,
+                               smem + STAGES * kStageBytes + 256);
     }
 
     // ---------------- common exit ----------------
@@ -156,7 +157,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 template <int BN, int STAGES>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
     constexpr int kStageBytes = kATileBytes + BN * kBK * 2;
-    constexpr int smem = STAGES * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+    constexpr int smem = STAGES * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/ + kRsStageBytes;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc5_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

@@ -54,6 +54,15 @@ def main():
     gathered = [None] * world
     dist.all_gather_object(gathered, tp_toks.tolist())
     identical = all(g == gathered[0] for g in gathered)
+    # cross-rank view: every rank must hold the same TP logits, and the rank-local references must agree too
+    both = [None] * world
+    dist.all_gather_object(both, (tp_logits, ref_logits))
+    tp_spread = max((b[0] - both[0][0]).abs().max().item() for b in both)
+    ref_spread = max((b[1] - both[0][1]).abs().max().item() for b in both)
+    per_seq = (tp_logits - ref_logits).abs().amax(-1).tolist()
+    print(f"rank {rank}: per-sequence err {per_seq} tp spread over ranks {tp_spread:.3e} ref spread over ranks {ref_spread:.3e}", flush=True)
+    if tp_spread > 0:
+        ok = False
     if dev.type == "cuda":
         from tensorrt_edge_llm_b200.ops import cuda as cu
         torch.cuda.synchronize()
