@@ -78,7 +78,7 @@ def save_file(tensors: Dict[str, torch.Tensor], path: str, metadata: Optional[Di
     blobs = []
     for name, t in tensors.items():
         t = t.detach().contiguous().cpu()
-        raw = t.view(torch.uint8).reshape(-1).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""    # reshape first: 0-d tensors cannot be re-viewed
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
         off += len(raw)
         blobs.append(raw)

@@ -328,6 +328,9 @@ __device__ __forceinline__ void gemm_epilogue_role(const GemmParams& p, uint32_t
             }
             tc_fence_before_sync();
             mbar_arrive(&tempty_bar[acc]);
+            // the peer stores of this tile are performed system-wide before the thread moves on, so the
+            // "GEMM finished" flag that a later kernel publishes can never overtake them
+            __threadfence_system();
         } else if (p.splits == 1) {
 #pragma unroll 1
             for (int c = 0; c < kChunks; ++c) {

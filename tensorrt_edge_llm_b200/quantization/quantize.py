@@ -1,0 +1,132 @@
+from __future__ import annotations
+
+import json
+import os
+import shutil
+from typing import Dict, Iterable, List, Optional, Sequence
+
+import torch
+
+from ..checkpoint.safetensors_io import CheckpointReader, save_file
+from ..ops import reference as ref
+
+_LINEAR_SUFFIXES = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj", "in_proj", "out_proj",
+                    "in_proj_qkv", "in_proj_z", "fc1", "fc2")
+_ALGOS = {"nvfp4": "NVFP4", "int4_awq": "W4A16_AWQ", "fp16": None, "bf16": None}
+
+
+def build_quant_config(quantization: str, exclude: Sequence[str] = ("lm_head",), kv_cache_quantization: Optional[str] = None,
+                       group_size: Optional[int] = None) -> dict:
+    """The ``hf_quant_config.json`` body for ``quantization`` ∈ {nvfp4, int4_awq}."""
+    if quantization not in _ALGOS or _ALGOS[quantization] is None:
+        raise ValueError(f"unsupported quantization {quantization!r}; choose nvfp4 or int4_awq")
+    if kv_cache_quantization not in (None, "fp8"):
+        raise ValueError("kv_cache_quantization must be fp8 or unset")
+    return {"producer": {"name": "tensorrt_edge_llm_b200"},
+            "quantization": {"quant_algo": _ALGOS[quantization], "group_size": group_size or (16 if quantization == "nvfp4" else 128),
+                             "kv_cache_quant_algo": "FP8" if kv_cache_quantization == "fp8" else None,
+                             "exclude_modules": list(exclude)}}
+
+
+def _is_target(name: str, shape, exclude: Sequence[str]) -> bool:
+    if not name.endswith(".weight") or len(shape) != 2:
+        return False
+    mod = name[:-len(".weight")]
+    if any(mod == e or mod.endswith("." + e) or e.strip("*") in mod for e in exclude):
+        return False
+    return mod.rsplit(".", 1)[-1] in _LINEAR_SUFFIXES
+
+
+@torch.no_grad()
+def calibrate_input_scales(model_dir: str, calib_ids: Optional[torch.Tensor] = None, num_samples: int = 8, seq_len: int = 128,
+                           device: str = "cpu") -> Dict[str, float]:
+    """Max-calibrate the input of every linear layer: run the 16-bit model over calibration token ids
+    and record ``amax / (6 · 448)`` per checkpoint module (fused layers share their input, so every
+    source module gets the same scale).  Without calibration ids, seeded uniform ids are used."""
+    from ..model import AutoModel
+    from ..models.linear import LinearBase
+    from ..runtime.kv_cache import KVCacheManager
+    from ..runtime.runner import ModelRunner
+    model = AutoModel.from_pretrained(model_dir, device=device)
+    cfg = model.cfg
+    if calib_ids is None:
+        g = torch.Generator().manual_seed(0)
+        calib_ids = torch.randint(0, cfg.vocab_size, (num_samples, seq_len), generator=g)
+    amax: Dict[str, float] = {}
+    hooks = []
+    for name, mod in model.named_modules():
+        if isinstance(mod, LinearBase):
+            def pre(m, args, name=name):
+                x = args[0]
+                if isinstance(x, torch.Tensor):
+                    amax[name] = max(amax.get(name, 0.0), float(x.detach().abs().max()))
+            hooks.append(mod.register_forward_pre_hook(pre))
+    page = 64
+    pages_per_seq = (calib_ids.shape[1] + page - 1) // page + 1
+    kv = KVCacheManager(cfg, num_pages=pages_per_seq * 2, page_size=page, max_seats=2, max_pages_per_seq=pages_per_seq, device=device)
+    runner = ModelRunner(model, kv)
+    runner.use_cuda_graphs = False
+    for row in calib_ids.tolist():
+        runner.prefill([0], [row])
+        kv.free(0)
+    for h in hooks:
+        h.remove()
+    scales: Dict[str, float] = {}
+    for name, mod in model.named_modules():
+        if isinstance(mod, LinearBase) and name in amax:
+            parent = name.rsplit(".", 1)[0] if "." in name else ""
+            for s in (mod.sources or [name.rsplit(".", 1)[-1]]):
+                scales[(parent + "." if parent else "") + s] = max(amax[name], 1e-6) / (ref.FP4_MAX * ref.E4M3_MAX)
+    return scales
+
+
+@torch.no_grad()
+def quantize_and_export(model_dir: str, out_dir: str, quantization: str = "nvfp4", exclude: Sequence[str] = ("lm_head",),
+                        kv_cache_quantization: Optional[str] = None, calib_ids: Optional[torch.Tensor] = None,
+                        calibrate: bool = True, device: str = "cpu", group_size: int = 128) -> dict:
+    """Quantise the linear layers of a 16-bit checkpoint and write a unified quantised checkpoint."""
+    qcfg = build_quant_config(quantization, exclude, kv_cache_quantization, None if quantization == "nvfp4" else group_size)
+    os.makedirs(out_dir, exist_ok=True)
+    scales = calibrate_input_scales(model_dir, calib_ids, device=device) if (calibrate and quantization == "nvfp4") else {}
+    reader = CheckpointReader(model_dir)
+    out: Dict[str, torch.Tensor] = {}
+    n_q = 0
+    for key in reader.keys():
+        t = reader.get(key)
+        canon = key
+        for pre in ("model.language_model.", "language_model.model."):
+            if canon.startswith(pre):
+                canon = "model." + canon[len(pre):]
+        if not _is_target(canon, t.shape, exclude):
+            out[key] = t.clone()
+            continue
+        base = key[:-len(".weight")]
+        w = t.to(device).float()
+        if quantization == "nvfp4":
+            if w.shape[1] % 16:
+                out[key] = t.clone()
+                continue
+            packed, sf, gs = ref.nvfp4_quantize(w)
+            out[key] = packed.cpu()
+            out[base + ".weight_scale"] = sf.cpu()
+            out[base + ".weight_scale_2"] = gs.reshape(()).cpu()
+            mod = canon[:-len(".weight")]
+            out[base + ".input_scale"] = torch.tensor(scales.get(mod, 1.0 / 448.0), dtype=torch.float32)
+        else:
+            g = group_size
+            if w.shape[1] % g or w.shape[0] % 2:
+                out[key] = t.clone()
+                continue
+            wg = w.reshape(w.shape[0], w.shape[1] // g, g)
+            scale = (wg.abs().amax(-1) / 7.0).clamp(min=1e-8)
+            q = (torch.round(wg / scale[..., None]).clamp(-8, 7) + 8).to(torch.uint8).reshape(w.shape)
+            out[key] = (q[0::2] | (q[1::2] << 4)).cpu()
+            out[base + ".weight_scale"] = scale.to(t.dtype).cpu()
+        n_q += 1
+    save_file(out, os.path.join(out_dir, "model.safetensors"))
+    for fname in os.listdir(model_dir):
+        if fname.endswith((".json", ".jinja", ".txt", ".model")) and not fname.startswith("model.safetensors") and fname != "hf_quant_config.json":
+            shutil.copy(os.path.join(model_dir, fname), os.path.join(out_dir, fname))
+    with open(os.path.join(out_dir, "hf_quant_config.json"), "w", encoding="utf-8") as f:
+        json.dump(qcfg, f, indent=1)
+    return {"quantized_linears": n_q, "tensors": len(out), "config": qcfg}

@@ -1,0 +1,279 @@
+"""FastAPI application: health, model list, OpenAI chat / completions / responses, Anthropic messages.
+
+Parity: ``tensorrt_edgellm/server/api/routes.py`` (:104 ``/health``, :150 ``/health/ready``, :169
+``/v1/models``, :181 ``/v1/chat/completions``, :194 ``/v1/responses``, :238 ``/v1/completions``, :260
+``/v1/messages``, :274 ``/v1/messages/count_tokens``), error shapes of ``api/errors.py`` and the
+429 / 503 admission behaviour of ``runtime/engine_client.py``.  Audio routes need the speech models
+and are not served."""
+from __future__ import annotations
+
+import json
+import time
+import uuid
+from typing import Any, Dict, List, Optional
+
+from fastapi import FastAPI, Request
+from fastapi.responses import JSONResponse, StreamingResponse
+
+from ..chat_template import ChatTemplate
+from ..runtime.llm import LLM
+from ..runtime.runner import SamplingParams
+from .config import ApiConfig
+from .engine_client import EngineClient, EngineUnavailable, QueueFull, QueueTimeout
+
+
+def _error(status: int, message: str, etype: str = "invalid_request_error", code: Optional[str] = None) -> JSONResponse:
+    return JSONResponse(status_code=status, content={"error": {"message": message, "type": etype, "param": None, "code": code}})
+
+
+def _sampling(body: Dict[str, Any], default_max: int = 256) -> SamplingParams:
+    max_tokens = body.get("max_completion_tokens") or body.get("max_tokens") or body.get("max_output_tokens") or default_max
+    stop_ids = body.get("stop_token_ids") or []
+    sp = SamplingParams(temperature=float(body.get("temperature", 0.7) if body.get("temperature") is not None else 0.7),
+                        top_k=int(body.get("top_k", 50) or 0), top_p=float(body.get("top_p", 0.9) if body.get("top_p") is not None else 0.9),
+                        seed=int(body.get("seed", 42) or 42), ignore_eos=bool(body.get("ignore_eos", False)),
+                        stop_token_ids=tuple(int(t) for t in stop_ids))
+    sp.max_tokens = int(max_tokens)
+    if sp.max_tokens < 1:
+        raise ValueError("max_tokens must be at least 1")
+    return sp
+
+
+def _truncate_at_stop(text: str, stops) -> (str, bool):
+    if isinstance(stops, str):
+        stops = [stops]
+    cut = min((text.find(s) for s in (stops or []) if s and s in text), default=-1)
+    return (text[:cut], True) if cut >= 0 else (text, False)
+
+
+def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optional[ChatTemplate] = None,
+               model_name: str = "") -> FastAPI:
+    api = api or ApiConfig()
+    client = EngineClient(llm, api.max_queued_requests, api.queue_timeout)
+    template = chat_template or ChatTemplate()
+    name = api.served_model_name or model_name or "model"
+    app = FastAPI(title="tensorrt_edge_llm_b200", version="1")
+    app.state.client, app.state.started = client, time.time()
+
+    @app.middleware("http")
+    async def auth(request: Request, call_next):
+        if api.api_key and request.url.path.startswith("/v1"):
+            got = request.headers.get("authorization", "")
+            key = request.headers.get("x-api-key", "")
+            if got != f"Bearer {api.api_key}" and key != api.api_key:
+                return _error(401, "invalid API key", "authentication_error")
+        return await call_next(request)
+
+    def encode(text: str) -> List[int]:
+        if llm.tokenizer is None:
+            raise ValueError("this server has no tokenizer: send token ids (prompt as a list of integers)")
+        return list(llm.tokenizer.encode(text))
+
+    def decode(ids: List[int]) -> str:
+        if llm.tokenizer is None:
+            return ""
+        t = llm.tokenizer.decode(ids)
+        return t.decode("utf-8", "replace") if isinstance(t, (bytes, bytearray)) else t
+
+    def check_len(ids: List[int]) -> Optional[JSONResponse]:
+        if not ids:
+            return _error(400, "empty prompt")
+        if len(ids) > llm.max_input_len:
+            return _error(400, f"prompt has {len(ids)} tokens, the server accepts {llm.max_input_len}", code="context_length_exceeded")
+        return None
+
+    async def run(ids: List[int], sp: SamplingParams, priority: int = 0):
+        try:
+            return await client.generate(ids, sp, priority), None
+        except QueueFull as e:
+            return None, _error(429, f"server is at capacity: {e}", "rate_limit_error")
+        except (QueueTimeout, EngineUnavailable) as e:
+            return None, _error(503, f"engine unavailable: {e}", "service_unavailable")
+        except (ValueError, RuntimeError) as e:
+            return None, _error(400, str(e))
+
+    def sse(gen):
+        return StreamingResponse(gen, media_type="text/event-stream", headers={"Cache-Control": "no-cache", "X-Accel-Buffering": "no"})
+
+    # ---- health / models -----------------------------------------------------------------------------------
+    @app.get("/health")
+    async def health():
+        running, waiting = client.admission.depth
+        return {"status": "ok", "uptime_s": round(time.time() - app.state.started, 1), "running": running, "queued": waiting}
+
+    @app.get("/health/ready")
+    async def ready():
+        ok, why = client.ready()
+        return {"status": "ready"} if ok else _error(503, why or "not ready", "service_unavailable")
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": name, "object": "model", "created": int(app.state.started), "owned_by": "local",
+                                            "max_model_len": llm.max_input_len}]}
+
+    # ---- OpenAI chat completions ---------------------------------------------------------------------------
+    @app.post("/v1/chat/completions")
+    async def chat_completions(request: Request):
+        try:
+            body = await request.json()
+            messages = body["messages"]
+            if not isinstance(messages, list) or not messages:
+                raise ValueError("messages must be a non-empty list")
+            sp = _sampling(body)
+            prompt = template.apply(messages, True, body.get("tools"), bool((body.get("chat_template_kwargs") or {}).get("enable_thinking", True)))
+            ids = encode(prompt)
+        except (KeyError, ValueError, TypeError, json.JSONDecodeError) as e:
+            return _error(400, f"bad request: {e}")
+        bad = check_len(ids)
+        if bad:
+            return bad
+        rid, created = f"chatcmpl-{uuid.uuid4().hex[:24]}", int(time.time())
+        priority = int(body.get("priority", 0) or 0)
+        if body.get("stream"):
+            async def events():
+                head = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": name}
+                yield "data: " + json.dumps({**head, "choices": [{"index": 0, "delta": {"role": "assistant", "content": ""}, "finish_reason": None}]}) + "\n\n"
+                n_out = 0
+                try:
+                    async for d in client.stream(ids, sp, priority):
+                        n_out += len(d.token_ids)
+                        if d.text:
+                            yield "data: " + json.dumps({**head, "choices": [{"index": 0, "delta": {"content": d.text}, "finish_reason": None}]}) + "\n\n"
+                        if d.finished:
+                            yield "data: " + json.dumps({**head, "choices": [{"index": 0, "delta": {}, "finish_reason": d.finish_reason or "stop"}],
+                                                         "usage": {"prompt_tokens": len(ids), "completion_tokens": n_out, "total_tokens": len(ids) + n_out}}) + "\n\n"
+                except (QueueFull, QueueTimeout, EngineUnavailable) as e:
+                    yield "data: " + json.dumps({"error": {"message": str(e), "type": "service_unavailable"}}) + "\n\n"
+                yield "data: [DONE]\n\n"
+            return sse(events())
+        out, err = await run(ids, sp, priority)
+        if err:
+            return err
+        text, stopped = _truncate_at_stop(out.text if out.text is not None else decode(out.token_ids), body.get("stop"))
+        return {"id": rid, "object": "chat.completion", "created": created, "model": name,
+                "choices": [{"index": 0, "message": {"role": "assistant", "content": text},
+                             "finish_reason": "stop" if stopped else out.finish_reason, "token_ids": out.token_ids}],
+                "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out.token_ids), "total_tokens": len(ids) + len(out.token_ids)}}
+
+    # ---- OpenAI completions --------------------------------------------------------------------------------
+    @app.post("/v1/completions")
+    async def completions(request: Request):
+        try:
+            body = await request.json()
+            prompt = body["prompt"]
+            ids = [int(t) for t in prompt] if isinstance(prompt, list) and prompt and not isinstance(prompt[0], str) else encode(
+                prompt if isinstance(prompt, str) else prompt[0])
+            sp = _sampling(body, default_max=16)
+        except (KeyError, ValueError, TypeError, IndexError, json.JSONDecodeError) as e:
+            return _error(400, f"bad request: {e}")
+        bad = check_len(ids)
+        if bad:
+            return bad
+        rid, created = f"cmpl-{uuid.uuid4().hex[:24]}", int(time.time())
+        if body.get("stream"):
+            async def events():
+                async for d in client.stream(ids, sp):
+                    yield "data: " + json.dumps({"id": rid, "object": "text_completion", "created": created, "model": name,
+                                                 "choices": [{"index": 0, "text": d.text, "token_ids": d.token_ids,
+                                                              "finish_reason": d.finish_reason if d.finished else None}]}) + "\n\n"
+                yield "data: [DONE]\n\n"
+            return sse(events())
+        out, err = await run(ids, sp)
+        if err:
+            return err
+        text, stopped = _truncate_at_stop(out.text if out.text is not None else decode(out.token_ids), body.get("stop"))
+        return {"id": rid, "object": "text_completion", "created": created, "model": name,
+                "choices": [{"index": 0, "text": text, "token_ids": out.token_ids, "finish_reason": "stop" if stopped else out.finish_reason}],
+                "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out.token_ids), "total_tokens": len(ids) + len(out.token_ids)}}
+
+    # ---- OpenAI responses (text in, text out) ---------------------------------------------------------------
+    @app.post("/v1/responses")
+    async def responses(request: Request):
+        try:
+            body = await request.json()
+            inp = body["input"]
+            messages = [{"role": "user", "content": inp}] if isinstance(inp, str) else [
+                {"role": m.get("role", "user"), "content": m.get("content", "")} for m in inp]
+            if body.get("instructions"):
+                messages.insert(0, {"role": "system", "content": body["instructions"]})
+            sp = _sampling(body)
+            ids = encode(template.apply(messages, True))
+        except (KeyError, ValueError, TypeError, AttributeError, json.JSONDecodeError) as e:
+            return _error(400, f"bad request: {e}")
+        bad = check_len(ids)
+        if bad:
+            return bad
+        out, err = await run(ids, sp)
+        if err:
+            return err
+        text = out.text if out.text is not None else decode(out.token_ids)
+        return {"id": f"resp_{uuid.uuid4().hex[:24]}", "object": "response", "created_at": int(time.time()), "status": "completed", "model": name,
+                "output": [{"type": "message", "id": f"msg_{uuid.uuid4().hex[:24]}", "role": "assistant", "status": "completed",
+                            "content": [{"type": "output_text", "text": text, "annotations": []}]}],
+                "output_text": text,
+                "usage": {"input_tokens": len(ids), "output_tokens": len(out.token_ids), "total_tokens": len(ids) + len(out.token_ids)}}
+
+    # ---- Anthropic messages --------------------------------------------------------------------------------
+    def anthropic_messages(body: Dict[str, Any]) -> List[Dict[str, Any]]:
+        msgs: List[Dict[str, Any]] = []
+        system = body.get("system")
+        if system:
+            msgs.append({"role": "system", "content": system if isinstance(system, str) else
+                         "".join(b.get("text", "") for b in system if isinstance(b, dict))})
+        for m in body["messages"]:
+            c = m.get("content", "")
+            if not isinstance(c, str):
+                c = "".join(b.get("text", "") for b in c if isinstance(b, dict) and b.get("type") == "text")
+            msgs.append({"role": m["role"], "content": c})
+        return msgs
+
+    @app.post("/v1/messages")
+    async def messages(request: Request):
+        try:
+            body = await request.json()
+            if "max_tokens" not in body:
+                raise ValueError("max_tokens is required")
+            sp = _sampling(body)
+            sp.stop_token_ids = tuple(sp.stop_token_ids)
+            ids = encode(template.apply(anthropic_messages(body), True))
+        except (KeyError, ValueError, TypeError, json.JSONDecodeError) as e:
+            return JSONResponse(status_code=400, content={"type": "error", "error": {"type": "invalid_request_error", "message": str(e)}})
+        bad = check_len(ids)
+        if bad:
+            return bad
+        mid = f"msg_{uuid.uuid4().hex[:24]}"
+        if body.get("stream"):
+            async def events():
+                def ev(kind, data):
+                    return f"event: {kind}\ndata: {json.dumps({'type': kind, **data})}\n\n"
+                yield ev("message_start", {"message": {"id": mid, "type": "message", "role": "assistant", "model": name, "content": [],
+                                                       "stop_reason": None, "usage": {"input_tokens": len(ids), "output_tokens": 0}}})
+                yield ev("content_block_start", {"index": 0, "content_block": {"type": "text", "text": ""}})
+                n_out, reason = 0, "end_turn"
+                async for d in client.stream(ids, sp):
+                    n_out += len(d.token_ids)
+                    if d.text:
+                        yield ev("content_block_delta", {"index": 0, "delta": {"type": "text_delta", "text": d.text}})
+                    if d.finished:
+                        reason = "max_tokens" if d.finish_reason == "length" else "end_turn"
+                yield ev("content_block_stop", {"index": 0})
+                yield ev("message_delta", {"delta": {"stop_reason": reason, "stop_sequence": None}, "usage": {"output_tokens": n_out}})
+                yield ev("message_stop", {})
+            return sse(events())
+        out, err = await run(ids, sp)
+        if err:
+            return err
+        text, stopped = _truncate_at_stop(out.text if out.text is not None else decode(out.token_ids), body.get("stop_sequences"))
+        return {"id": mid, "type": "message", "role": "assistant", "model": name, "content": [{"type": "text", "text": text}],
+                "stop_reason": "stop_sequence" if stopped else ("max_tokens" if out.finish_reason == "length" else "end_turn"),
+                "stop_sequence": None, "usage": {"input_tokens": len(ids), "output_tokens": len(out.token_ids)}}
+
+    @app.post("/v1/messages/count_tokens")
+    async def count_tokens(request: Request):
+        try:
+            body = await request.json()
+            return {"input_tokens": len(encode(template.apply(anthropic_messages(body), True)))}
+        except (KeyError, ValueError, TypeError, json.JSONDecodeError) as e:
+            return JSONResponse(status_code=400, content={"type": "error", "error": {"type": "invalid_request_error", "message": str(e)}})
+
+    return app

@@ -1,0 +1,50 @@
+"""``trtedge serve <checkpoint>``: load the model, start the request engine, run uvicorn.
+
+Parity: ``tensorrt_edgellm/server/cli.py`` / ``__main__.py``.  There is no engine build or cache step:
+the checkpoint is loaded straight into device memory."""
+from __future__ import annotations
+
+import os
+import sys
+from typing import Optional, Sequence
+
+from .config import ServerConfig, ServerConfigError, parse_server_config
+
+
+def build_llm(cfg: ServerConfig):
+    from ..chat_template import ChatTemplate
+    from ..runtime.llm import LLM
+    m = cfg.model
+    tok = None
+    try:
+        from ..runtime import native as rt
+        if os.path.exists(os.path.join(m.model, "tokenizer.json")):
+            tok = rt.Tokenizer.load_from_hf(m.model)
+    except ImportError:
+        tok = None
+    llm = LLM(m.model, device=m.device or None, max_batch_size=m.max_batch_size, max_input_len=m.max_input_len,
+              max_kv_cache_capacity=m.max_kv_cache_capacity, page_size=m.kv_page_size, max_num_tokens=m.max_num_tokens or 8192,
+              tokenizer=tok, enable_in_flight_batching=m.enable_in_flight_batching,
+              enable_prefix_cache=m.context_cache_config.enabled, scheduling=m.scheduling_dict() if m.enable_in_flight_batching else None)
+    return llm, ChatTemplate.load(m.model)
+
+
+def main(argv: Optional[Sequence[str]] = None) -> int:
+    try:
+        cfg = parse_server_config(argv)
+    except ServerConfigError as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 2
+    import uvicorn
+    from .app import create_app
+    llm, template = build_llm(cfg)
+    app = create_app(llm, cfg.api, template, model_name=os.path.basename(os.path.normpath(cfg.model.model)))
+    try:
+        uvicorn.run(app, host=cfg.api.host, port=cfg.api.port, log_level=cfg.api.log_level)
+    finally:
+        llm.close()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,150 @@
+"""HTTP surface on CPU: OpenAI / Anthropic routes, SSE streaming, auth, admission (429 / 503), config validation."""
+import json
+import threading
+
+import pytest
+import torch
+from fastapi.testclient import TestClient
+
+from tensorrt_edge_llm_b200.chat_template import ChatTemplate
+from tensorrt_edge_llm_b200.config import tiny_llama_config
+from tensorrt_edge_llm_b200.runtime.llm import LLM
+from tensorrt_edge_llm_b200.server.app import create_app
+from tensorrt_edge_llm_b200.server.config import ApiConfig, ServerConfigError, parse_server_config
+from tensorrt_edge_llm_b200.server.engine_client import AdmissionController, QueueFull, QueueTimeout
+
+
+class ByteTokenizer:
+    """One token per UTF-8 byte (ids 3..258); enough to drive the text routes."""
+
+    def encode(self, text, add_special_tokens=False):
+        return [b + 3 for b in text.encode("utf-8")]
+
+    def decode(self, ids, skip_special_tokens=True):
+        return bytes((i - 3) % 256 for i in ids).decode("utf-8", "replace")
+
+    def id_to_bytes(self, i):
+        return bytes([(i - 3) % 256])
+
+
+@pytest.fixture(scope="module")
+def llm():
+    cfg = tiny_llama_config(num_hidden_layers=2, dtype="float32")
+    m = LLM(cfg, device="cpu", max_batch_size=4, max_input_len=256, max_kv_cache_capacity=320, page_size=16, tokenizer=ByteTokenizer(),
+            enable_in_flight_batching=True)
+    yield m
+    m.close()
+
+
+@pytest.fixture(scope="module")
+def client(llm):
+    return TestClient(create_app(llm, ApiConfig(served_model_name="tiny", api_key="sekret"), ChatTemplate()))
+
+
+AUTH = {"Authorization": "Bearer sekret"}
+
+
+def test_health_models_and_auth(client):
+    assert client.get("/health").json()["status"] == "ok"
+    assert client.get("/health/ready").status_code == 200
+    assert client.get("/v1/models").status_code == 401
+    assert client.get("/v1/models", headers={"x-api-key": "sekret"}).json()["data"][0]["id"] == "tiny"
+
+
+def test_chat_completion_and_determinism(client):
+    body = {"model": "tiny", "messages": [{"role": "user", "content": "hello"}], "max_tokens": 6, "temperature": 0}
+    a = client.post("/v1/chat/completions", json=body, headers=AUTH).json()
+    b = client.post("/v1/chat/completions", json=body, headers=AUTH).json()
+    assert a["object"] == "chat.completion" and a["usage"]["completion_tokens"] == 6
+    assert a["choices"][0]["token_ids"] == b["choices"][0]["token_ids"]
+    assert a["choices"][0]["finish_reason"] in ("length", "stop")
+    assert a["usage"]["prompt_tokens"] == len("<|im_start|>user\nhello<|im_end|>\n<|im_start|>assistant\n")
+
+
+def test_chat_stream_matches_blocking(client):
+    body = {"messages": [{"role": "user", "content": [{"type": "text", "text": "count"}]}], "max_tokens": 5, "temperature": 0}
+    want = client.post("/v1/chat/completions", json=body, headers=AUTH).json()
+    with client.stream("POST", "/v1/chat/completions", json={**body, "stream": True}, headers=AUTH) as r:
+        assert r.status_code == 200 and r.headers["content-type"].startswith("text/event-stream")
+        events = [l[6:] for l in r.iter_lines() if l.startswith("data: ")]
+    assert events[-1] == "[DONE]"
+    chunks = [json.loads(e) for e in events[:-1]]
+    assert chunks[0]["choices"][0]["delta"]["role"] == "assistant"
+    assert chunks[-1]["usage"]["completion_tokens"] == 5 and chunks[-1]["choices"][0]["finish_reason"] is not None
+    text = "".join(c["choices"][0]["delta"].get("content", "") for c in chunks)
+    assert text == want["choices"][0]["message"]["content"]
+
+
+def test_completions_with_token_ids_and_errors(client):
+    r = client.post("/v1/completions", json={"prompt": [5, 6, 7, 8], "max_tokens": 3, "temperature": 0}, headers=AUTH).json()
+    assert len(r["choices"][0]["token_ids"]) == 3 and r["usage"]["prompt_tokens"] == 4
+    assert client.post("/v1/completions", json={"max_tokens": 3}, headers=AUTH).status_code == 400
+    too_long = client.post("/v1/completions", json={"prompt": list(range(3, 400)), "max_tokens": 1}, headers=AUTH)
+    assert too_long.status_code == 400 and too_long.json()["error"]["code"] == "context_length_exceeded"
+    assert client.post("/v1/chat/completions", json={"messages": []}, headers=AUTH).status_code == 400
+
+
+def test_anthropic_messages_and_count(client):
+    body = {"model": "tiny", "max_tokens": 4, "temperature": 0, "system": "be brief", "messages": [{"role": "user", "content": "hi"}]}
+    r = client.post("/v1/messages", json=body, headers=AUTH).json()
+    assert r["type"] == "message" and r["usage"]["output_tokens"] == 4 and r["stop_reason"] in ("max_tokens", "end_turn")
+    n = client.post("/v1/messages/count_tokens", json=body, headers=AUTH).json()["input_tokens"]
+    assert n == r["usage"]["input_tokens"]
+    assert client.post("/v1/messages", json={"messages": [{"role": "user", "content": "x"}]}, headers=AUTH).status_code == 400
+    with client.stream("POST", "/v1/messages", json={**body, "stream": True}, headers=AUTH) as s:
+        kinds = [l[7:] for l in s.iter_lines() if l.startswith("event: ")]
+    assert kinds[0] == "message_start" and kinds[-1] == "message_stop" and "content_block_delta" in kinds
+
+
+def test_responses_route(client):
+    r = client.post("/v1/responses", json={"input": "ping", "instructions": "pong", "max_output_tokens": 3, "temperature": 0}, headers=AUTH).json()
+    assert r["object"] == "response" and r["usage"]["output_tokens"] == 3 and r["output"][0]["content"][0]["type"] == "output_text"
+
+
+def test_admission_controller_limits():
+    ac = AdmissionController(slots=1, max_queued=1, timeout_s=0.2)
+    ac.acquire()
+    errs = []
+
+    def waiter():
+        try:
+            ac.acquire()
+            ac.release()
+        except Exception as e:
+            errs.append(e)
+
+    t = threading.Thread(target=waiter)
+    t.start()
+    import time
+    time.sleep(0.05)
+    with pytest.raises(QueueFull):          # one runs, one waits, the third is refused
+        ac.acquire()
+    t.join()
+    assert len(errs) == 1 and isinstance(errs[0], QueueTimeout)
+    ac.release()
+    ac.acquire()
+    ac.release()
+    assert ac.depth == (0, 0)
+
+
+def test_server_config_validation():
+    cfg = parse_server_config(["/ckpt", "--enable-in-flight-batching", "--scheduling-policy", "priority", "--preemption", "pause",
+                               "--max-batch-size", "8", "--speculative-config", '{"method": "eagle3", "draft_model": "/d", "verify_tokens": 60}'])
+    assert cfg.model.scheduling_dict()["preemption"] == "pause" and cfg.model.speculative_config.verify_tokens == 60
+    with pytest.raises(ServerConfigError):
+        parse_server_config(["/ckpt", "--scheduling-policy", "priority"])                   # needs IFB
+    with pytest.raises(ServerConfigError):
+        parse_server_config(["/ckpt", "--enable-in-flight-batching", "--preemption", "pause"])   # needs priority policy
+    with pytest.raises(ServerConfigError):
+        parse_server_config(["/ckpt", "--speculative-config", '{"method": "medusa"}'])
+    with pytest.raises(ServerConfigError):
+        parse_server_config(["/ckpt", "--max-kv-cache-capacity", "100", "--max-input-len", "200"])
+
+
+def test_jinja_chat_template(tmp_path):
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps({
+        "bos_token": "<s>", "eos_token": {"content": "</s>"},
+        "chat_template": "{{ bos_token }}{% for m in messages %}[{{ m.role }}] {{ m.content }}{{ eos_token }}{% endfor %}{% if add_generation_prompt %}[assistant]{% endif %}"}))
+    t = ChatTemplate.load(str(tmp_path))
+    assert t.apply([{"role": "user", "content": "a"}, {"role": "assistant", "content": [{"type": "text", "text": "b"}]}]) == \
+        "<s>[user] a</s>[assistant] b</s>[assistant]"

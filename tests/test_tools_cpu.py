@@ -1,0 +1,131 @@
+"""Command-line tools on CPU: quantise-and-reload, LoRA processing / merging, vocabulary reduction, build check."""
+import json
+import os
+
+import pytest
+import torch
+
+from tensorrt_edge_llm_b200 import AutoModel
+from tensorrt_edge_llm_b200.checkpoint import save_file
+from tensorrt_edge_llm_b200.checkpoint.safetensors_io import SafetensorsFile
+from tensorrt_edge_llm_b200.cli import main as trtedge
+from tensorrt_edge_llm_b200.runtime.kv_cache import KVCacheManager
+from tensorrt_edge_llm_b200.runtime.runner import ModelRunner
+
+
+@pytest.fixture(scope="module")
+def ckpt(tmp_path_factory):
+    from transformers import LlamaConfig, LlamaForCausalLM
+    d = str(tmp_path_factory.mktemp("ckpt"))
+    cfg = LlamaConfig(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=32, rms_norm_eps=1e-6, rope_theta=1e4, max_position_embeddings=256,
+                      tie_word_embeddings=False, bos_token_id=1, eos_token_id=2)
+    torch.manual_seed(0)
+    m = LlamaForCausalLM(cfg).float().eval()
+    save_file(dict(m.state_dict()), os.path.join(d, "model.safetensors"))
+    hf = cfg.to_dict()
+    hf["torch_dtype"] = "float32"
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(hf, f)
+    return d
+
+
+def _logits(model_dir, ids):
+    model = AutoModel.from_pretrained(model_dir)
+    kv = KVCacheManager(model.cfg, num_pages=8, page_size=16, max_seats=2, max_pages_per_seq=4)
+    return ModelRunner(model, kv).prefill([0], [ids]).float()
+
+
+def test_quantize_nvfp4_and_reload(ckpt, tmp_path):
+    out = str(tmp_path / "q")
+    assert trtedge(["quantize", "llm", "--model_dir", ckpt, "--output_dir", out, "--quantization", "nvfp4"]) == 0
+    qc = json.load(open(os.path.join(out, "hf_quant_config.json")))["quantization"]
+    assert qc["quant_algo"] == "NVFP4" and qc["group_size"] == 16 and "lm_head" in qc["exclude_modules"]
+    f = SafetensorsFile(os.path.join(out, "model.safetensors"))
+    base = "model.layers.0.self_attn.q_proj"
+    assert f.info(base + ".weight") == (torch.uint8, [128, 64]) and f.info(base + ".weight_scale")[0] == torch.float8_e4m3fn
+    assert f.info(base + ".input_scale")[1] == [] and f.info("lm_head.weight")[0] == torch.float32
+    # q/k/v read the same activations, so calibration gives them one input scale
+    assert float(f.get(base + ".input_scale")) == float(f.get("model.layers.0.self_attn.k_proj.input_scale")) > 0
+    ids = list(range(5, 45))
+    a, b = _logits(ckpt, ids), _logits(out, ids)
+    cos = torch.nn.functional.cosine_similarity(a - a.mean(), b - b.mean(), dim=-1)
+    assert float(cos) > 0.95                      # 4-bit weights and activations on a tiny random model
+
+
+def test_quantize_int4_awq(ckpt, tmp_path):
+    out = str(tmp_path / "q4")
+    assert trtedge(["quantize", "--model_dir", ckpt, "--output_dir", out, "--quantization", "int4_awq", "--group-size", "64"]) == 0
+    f = SafetensorsFile(os.path.join(out, "model.safetensors"))
+    assert f.info("model.layers.1.mlp.down_proj.weight") == (torch.uint8, [64, 256])
+    assert f.info("model.layers.1.mlp.down_proj.weight_scale")[1] == [128, 4]
+    ids = list(range(5, 45))
+    a, b = _logits(ckpt, ids), _logits(out, ids)
+    assert float(torch.nn.functional.cosine_similarity(a - a.mean(), b - b.mean(), dim=-1)) > 0.97
+
+
+def _adapter(d, r=4, alpha=8.0):
+    os.makedirs(d, exist_ok=True)
+    g = torch.Generator().manual_seed(1)
+    t = {}
+    for mod, (o, i) in {"model.layers.0.self_attn.q_proj": (128, 128), "model.layers.1.mlp.down_proj": (128, 256)}.items():
+        t[f"base_model.model.{mod}.lora_A.weight"] = torch.randn(r, i, generator=g) * 0.1
+        t[f"base_model.model.{mod}.lora_B.weight"] = torch.randn(o, r, generator=g) * 0.1
+    save_file(t, os.path.join(d, "adapter_model.safetensors"))
+    with open(os.path.join(d, "adapter_config.json"), "w") as f:
+        json.dump({"r": r, "lora_alpha": alpha, "target_modules": ["q_proj", "down_proj"]}, f)
+    return t
+
+
+def test_lora_process_and_merge(ckpt, tmp_path):
+    ad = str(tmp_path / "adapter")
+    t = _adapter(ad)
+    out = str(tmp_path / "lora_rt")
+    assert trtedge(["process-lora", "--input_dir", ad, "--output_dir", out]) == 0
+    f = SafetensorsFile(os.path.join(out, "lora_weights.safetensors"))
+    b = f.get("lora_B_model.layers.0.self_attn.q_proj").float()
+    assert torch.allclose(b, (t["base_model.model.model.layers.0.self_attn.q_proj.lora_B.weight"] * 2.0).half().float())
+    assert json.load(open(os.path.join(out, "lora_config.json")))["rank"] == 4
+    merged = str(tmp_path / "merged")
+    assert trtedge(["merge-lora", "--model_dir", ckpt, "--lora_dir", ad, "--output_dir", merged]) == 0
+    w0 = SafetensorsFile(os.path.join(ckpt, "model.safetensors")).get("model.layers.1.mlp.down_proj.weight")
+    w1 = SafetensorsFile(os.path.join(merged, "model.safetensors")).get("model.layers.1.mlp.down_proj.weight")
+    delta = 2.0 * t["base_model.model.model.layers.1.mlp.down_proj.lora_B.weight"] @ t["base_model.model.model.layers.1.mlp.down_proj.lora_A.weight"]
+    assert torch.allclose(w1 - w0, delta, atol=1e-5)
+    assert trtedge(["insert-lora", "--lora_dir", ad]) == 0
+    assert not torch.allclose(_logits(ckpt, [3, 4, 5]), _logits(merged, [3, 4, 5]))
+
+
+def test_reduce_vocab(ckpt, tmp_path):
+    corpus = str(tmp_path / "ids.json")
+    json.dump([[7, 7, 7, 9, 9, 400], [9, 400, 400, 400, 11]], open(corpus, "w"))
+    out = str(tmp_path / "rv")
+    assert trtedge(["reduce-vocab", "--model_dir", ckpt, "--output_dir", out, "--keep", "5", "--corpus-ids", corpus]) == 0
+    f = SafetensorsFile(os.path.join(out, "vocab_map.safetensors"))
+    vm = f.get("vocab_map").tolist()
+    assert vm == [1, 2, 7, 9, 400]                 # bos / eos forced, then the three most frequent
+    head = SafetensorsFile(os.path.join(ckpt, "model.safetensors")).get("lm_head.weight")
+    assert torch.equal(f.get("lm_head.weight"), head[vm])
+    from tensorrt_edge_llm_b200.vocab_reduction import map_to_full
+    assert map_to_full(torch.tensor([4, 0]), torch.tensor(vm)).tolist() == [400, 1]
+
+
+def test_build_checks_checkpoint(ckpt, tmp_path):
+    out = str(tmp_path / "built")
+    assert trtedge(["build", ckpt, "--output_dir", out, "--tensor-parallel-size", "2", "--max-batch-size", "4"]) == 0
+    rc = json.load(open(os.path.join(out, "runtime_config.json")))
+    assert rc["deployment"]["tensor_parallel_size"] == 2 and rc["model"]["hidden_size"] == 128
+    broken = str(tmp_path / "broken")
+    os.makedirs(broken)
+    f = SafetensorsFile(os.path.join(ckpt, "model.safetensors"))
+    save_file({k: f.get(k).clone() for k in f.keys() if "layers.1.mlp.up_proj" not in k}, os.path.join(broken, "model.safetensors"))
+    json.dump(json.load(open(os.path.join(ckpt, "config.json"))), open(os.path.join(broken, "config.json"), "w"))
+    assert trtedge(["build", broken]) == 1
+    assert trtedge(["--version"]) == 0 and trtedge([]) == 2
+
+
+def test_reference_package_name_resolves():
+    import tensorrt_edgellm
+    from tensorrt_edgellm.server import LLM, SamplingParams  # noqa: F401
+    from tensorrt_edgellm.config import ModelConfig, QuantConfig  # noqa: F401
+    assert tensorrt_edgellm.AutoModel is AutoModel and "serve" in tensorrt_edgellm.cli.COMMANDS
