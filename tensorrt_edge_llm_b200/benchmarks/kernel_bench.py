@@ -109,7 +109,15 @@ def bench_attention(args):
     kv = torch.randn(b * pages_per, 2, hkv, page, d, device="cuda").bfloat16()
     meta = build_step_meta([q] * b, [past] * b, table, page, device="cuda")
     qt = torch.randn(b * q, hq, d, device="cuda").bfloat16()
-    fn = lambda: cu.paged_attention(qt, kv, meta, d ** -0.5)
+    if args.variant >= 0:
+        cu._check(cu.lib().telb_set_decode_variant(args.variant), "set_decode_variant", 0)
+    fn = lambda: cu.paged_attention(qt, kv, meta, d ** -0.5, splits=args.splits or None)
+    out = fn()
+    if args.check:      # numerics against the fp32 statement of the op
+        from ..ops import reference as ref
+        want = ref.paged_attention(qt, kv, meta, d ** -0.5)
+        err = ((out.float() - want.float()).norm() / want.float().norm()).item()
+        assert err < 8e-3, err
     med, best = time_fn(fn, args.warmup, args.iters, flush, args.graph if q <= 4 else 0)
     kv_bytes = b * (past + q) * hkv * d * 2 * 2
     flops = 4.0 * b * hq * d * (q * past + q * (q + 1) / 2)
@@ -117,7 +125,7 @@ def bench_attention(args):
     print(json.dumps({"kernel": "paged_attention", "batch": b, "past": past, "q": q, "median_us": round(med * 1e6, 2),
                       "best_us": round(best * 1e6, 2), "kv_gbs": round(kv_bytes / med / 1e9, 1),
                       "tflops": round(flops / med / 1e12, 1), "roofline_us": round(roof * 1e6, 2),
-                      "fraction": round(roof / med, 3), "basis": tag}))
+                      "fraction": round(roof / med, 3), "basis": tag, "variant": args.variant, "splits": args.splits}))
     cu.Workspace.get(torch.device("cuda", 0)).check_status()
 
 
@@ -133,6 +141,9 @@ def main():
     a.add_argument("--q", type=int, default=1)
     a.add_argument("--hq", type=int, default=32)
     a.add_argument("--hkv", type=int, default=8)
+    a.add_argument("--variant", type=int, default=-1, help="decode kernel ring / residency variant (see telb_set_decode_variant)")
+    a.add_argument("--splits", type=int, default=0, help="KV splits (0 = heuristic)")
+    a.add_argument("--check", action="store_true", help="compare with the fp32 reference first")
     for p in (g, a):
         p.add_argument("--warmup", type=int, default=3)
         p.add_argument("--iters", type=int, default=10)

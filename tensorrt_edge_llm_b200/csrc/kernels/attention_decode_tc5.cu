@@ -40,7 +40,6 @@ struct DecParams {
 constexpr int kDecThreads = 192;
 constexpr int kDecTile = 128;      // cached tokens per tile
 constexpr int kDecN = 16;          // (query token, head) columns
-constexpr int kDecStages = 3;
 
 __device__ __forceinline__ float warp_max_f32(float v) {
     float r;
@@ -48,8 +47,12 @@ __device__ __forceinline__ float warp_max_f32(float v) {
     return r;
 }
 
-template <int D, typename T>
-__global__ void __launch_bounds__(kDecThreads, 1)
+// KS / VS: depth of the K and V tile rings; MINB: CTAs that must fit on one SM (two co-resident CTAs with
+// shallow rings hide each other's per-tile synchronisation latency; one CTA with deep rings prefetches further).
+// NC: how many of the 16 MMA columns can be live (query tokens x heads per KV head, rounded up to 4 / 8 / 16);
+// the softmax registers and loops are sized by it.
+template <int D, typename T, int KS, int VS, int MINB, int NC>
+__global__ void __launch_bounds__(kDecThreads, MINB)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_kv, DecParams p) {
     constexpr int kDChunks = D / 64;
     constexpr int kChunkBytes = kDecTile * 128;                 // [128 tokens x 64 d]
@@ -62,16 +65,16 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* s_k = smem;
-    uint8_t* s_v = s_k + kDecStages * kKvBytes;
-    uint8_t* s_q = s_v + kDecStages * kKvBytes;
+    uint8_t* s_v = s_k + KS * kKvBytes;
+    uint8_t* s_q = s_v + VS * kKvBytes;
     uint8_t* s_p = s_q + ((kQBytes + 1023) & ~1023);
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_p + 2 * kPBytes);
     uint64_t* q_full = bars;
     uint64_t* k_full = bars + 1;
-    uint64_t* k_empty = k_full + kDecStages;
-    uint64_t* v_full = k_empty + kDecStages;
-    uint64_t* v_empty = v_full + kDecStages;
-    uint64_t* s_full = v_empty + kDecStages;
+    uint64_t* k_empty = k_full + KS;
+    uint64_t* v_full = k_empty + KS;
+    uint64_t* v_empty = v_full + VS;
+    uint64_t* s_full = v_empty + VS;
     uint64_t* s_free = s_full + 2;
     uint64_t* p_full = s_free + 2;
     uint64_t* p_free = p_full + 2;
@@ -102,9 +105,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < kDecStages; ++s) {
+        for (int s = 0; s < KS; ++s) {
             mbar_init(&k_full[s], 1);
             mbar_init(&k_empty[s], 1);
+        }
+        for (int s = 0; s < VS; ++s) {
             mbar_init(&v_full[s], 1);
             mbar_init(&v_empty[s], 1);
         }
@@ -142,8 +147,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             const int pages_per_tile = kDecTile / p.page_size;          // 2 for 64-token pages, 1 for 128
             const int rows_per_load = kDecTile / pages_per_tile;
             for (int j = 0; j < ntiles; ++j) {
-                const int stage = j % kDecStages;
-                const uint32_t ph = ((j / kDecStages) & 1) ^ 1;
+                const int ks = j % KS, vs = j % VS;
+                const uint32_t kph = ((j / KS) & 1) ^ 1, vph = ((j / VS) & 1) ^ 1;
                 const int tile = j0 + j;
                 int rows[2];
 #pragma unroll
@@ -154,19 +159,19 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
                     if (page < 0) page = 0;                              // masked anyway
                     rows[h] = ((page * 2 + 0) * p.hkv + kvh) * p.page_size;
                 }
-                if (!mbar_wait(&k_empty[stage], ph, abort_flag, p.status, kStatusProducerTimeout)) break;
-                mbar_expect_tx(&k_full[stage], kKvBytes);
+                if (!mbar_wait(&k_empty[ks], kph, abort_flag, p.status, kStatusProducerTimeout)) break;
+                mbar_expect_tx(&k_full[ks], kKvBytes);
                 for (int h = 0; h < pages_per_tile; ++h)
 #pragma unroll
                     for (int c = 0; c < kDChunks; ++c)
-                        tma_load_2d(s_k + stage * kKvBytes + c * kChunkBytes + h * rows_per_load * 128, &tma_kv, &k_full[stage],
+                        tma_load_2d(s_k + ks * kKvBytes + c * kChunkBytes + h * rows_per_load * 128, &tma_kv, &k_full[ks],
                                     c * 64, rows[h]);
-                if (!mbar_wait(&v_empty[stage], ph, abort_flag, p.status, kStatusProducerTimeout)) break;
-                mbar_expect_tx(&v_full[stage], kKvBytes);
+                if (!mbar_wait(&v_empty[vs], vph, abort_flag, p.status, kStatusProducerTimeout)) break;
+                mbar_expect_tx(&v_full[vs], kKvBytes);
                 for (int h = 0; h < pages_per_tile; ++h)
 #pragma unroll
                     for (int c = 0; c < kDChunks; ++c)
-                        tma_load_2d(s_v + stage * kKvBytes + c * kChunkBytes + h * rows_per_load * 128, &tma_kv, &v_full[stage],
+                        tma_load_2d(s_v + vs * kKvBytes + c * kChunkBytes + h * rows_per_load * 128, &tma_kv, &v_full[vs],
                                     c * 64, rows[h] + p.hkv * p.page_size);
             }
         }
@@ -176,7 +181,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             const uint32_t idesc_s = idesc_f16(128, kDecN, kBf16);                    // A = K (K-major), B = Q (K-major)
             const uint32_t idesc_o = idesc_f16(128, kDecN, kBf16, /*a_mn_major=*/true);   // A = Vᵀ (MN-major), B = Pᵀ (K-major)
             auto issue_s = [&](int j) {
-                const int stage = j % kDecStages;
+                const int stage = j % KS;
                 const uint64_t dk = smem_desc_sw128(s_k + stage * kKvBytes);
                 const uint64_t dq = smem_desc_sw128(s_q);
                 const uint32_t d_tmem = tmem_base + (j & 1) * 16;
@@ -198,15 +203,15 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             for (int j = 0; j < ntiles && ok; ++j) {
                 if (j + 1 < ntiles) {
                     const int jn = j + 1;
-                    ok = mbar_wait(&k_full[jn % kDecStages], (jn / kDecStages) & 1, abort_flag, p.status, kStatusMmaTimeout) &&
+                    ok = mbar_wait(&k_full[jn % KS], (jn / KS) & 1, abort_flag, p.status, kStatusMmaTimeout) &&
                          mbar_wait(&s_free[jn & 1], ((jn >> 1) & 1) ^ 1, abort_flag, p.status, kStatusMmaTimeout);
                     if (!ok) break;
                     tc_fence_after_sync();
                     issue_s(jn);
                 }
-                const int stage = j % kDecStages;
+                const int stage = j % VS;
                 ok = mbar_wait(&p_full[j & 1], (j >> 1) & 1, abort_flag, p.status, kStatusMmaTimeout) &&
-                     mbar_wait(&v_full[stage], (j / kDecStages) & 1, abort_flag, p.status, kStatusMmaTimeout);
+                     mbar_wait(&v_full[stage], (j / VS) & 1, abort_flag, p.status, kStatusMmaTimeout);
                 if (!ok) break;
                 tc_fence_after_sync();
                 // A = Vᵀ: 64-wide d chunks are kChunkBytes apart (leading offset), 8-token groups 1024 B apart
@@ -228,9 +233,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
         const int ncol = qlen * p.group;                // live columns (<= 16)
         const int gshift = 31 - __clz(p.group);         // the group size is a power of two
-        float m_used[kDecN], l_part[kDecN];
+        float m_used[NC], l_part[NC];
 #pragma unroll
-        for (int c = 0; c < kDecN; ++c) {
+        for (int c = 0; c < NC; ++c) {
             m_used[c] = -INFINITY;
             l_part[c] = 0.f;
         }
@@ -239,18 +244,18 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             const int b = j & 1;
             if (!mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout)) { ok = false; break; }
             tc_fence_after_sync();
-            uint32_t raw[16];
-            tmem_ld_x16(lane_addr + b * 16, raw);
+            uint32_t raw[NC];
+            tmem_ld_n<NC>(lane_addr + b * 16, raw);
             tmem_ld_wait();
             tc_fence_before_sync();
             mbar_arrive(&s_free[b]);
             const int tk = (j0 + j) * kDecTile + r;     // absolute cache slot of this thread's token
-            float s[kDecN];
+            float s[NC];
             float* red = s_red + b * 64;
             // Only the live columns (query tokens x heads of this sequence) are processed; `ncol`
             // is uniform across the CTA, so the guards below do not diverge.
 #pragma unroll
-            for (int c = 0; c < kDecN; ++c) {
+            for (int c = 0; c < NC; ++c) {
                 if (c < ncol) {
                     const int qi = c >> gshift;
                     bool vis = tk <= past + qi;
@@ -264,9 +269,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             }
             named_barrier_sync(1, 128);
             bool any_need = false;
-            float f[kDecN];
+            float f[NC];
 #pragma unroll
-            for (int c = 0; c < kDecN; ++c) {
+            for (int c = 0; c < NC; ++c) {
                 f[c] = 1.f;
                 if (c < ncol) {
                     const float mt = fmaxf(fmaxf(red[c], red[16 + c]), fmaxf(red[32 + c], red[48 + c]));
@@ -279,25 +284,29 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
                     }
                 }
             }
+            // P buffer b is free once PV(j-2) has completed.  This wait is taken for every use of the buffer, so its
+            // parity is exact; it also pins how far the tensor pipe can lag behind this warp.
+            if (!mbar_wait(&p_free[b], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kStatusEpilogueTimeout)) { ok = false; break; }
             if (j > 0 && any_need) {
-                if (!mbar_wait(o_bar, (j - 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout)) { ok = false; break; }
+                // O may only be rescaled after PV(j-1) has landed: that is the next completion of the other P
+                // buffer's barrier (a parity wait on a barrier that is polled only now and then could alias).
+                if (!mbar_wait(&p_free[b ^ 1], ((j - 1) >> 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout)) { ok = false; break; }
                 tc_fence_after_sync();
-                uint32_t o[16];
-                tmem_ld_x16(lane_addr + 32, o);
+                uint32_t o[NC];
+                tmem_ld_n<NC>(lane_addr + 32, o);
                 tmem_ld_wait();
 #pragma unroll
-                for (int c = 0; c < kDecN; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * f[c]);
-                tmem_st_x16(lane_addr + 32, o);
+                for (int c = 0; c < NC; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * f[c]);
+                tmem_st_n<NC>(lane_addr + 32, o);
                 tmem_st_wait();
                 tc_fence_before_sync();
             }
-            if (!mbar_wait(&p_free[b], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kStatusEpilogueTimeout)) { ok = false; break; }
             // Pᵀ[c][token]: row c is 128 tokens = two 128-byte swizzled chunks of 64 tokens.  Dead
             // columns keep whatever the buffer holds; their outputs are never read.
             uint8_t* pbase = s_p + b * kPBytes + (r >> 6) * (kDecN * 128);
             const int tl = r & 63;
 #pragma unroll
-            for (int c = 0; c < kDecN; ++c) {
+            for (int c = 0; c < NC; ++c) {
                 if (c < ncol) {
                     const float mref = m_used[c] == -INFINITY ? 0.f : m_used[c];
                     const float e = exp2f(s[c] - mref);
@@ -313,24 +322,26 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         float* red = s_red;         // reuse: [4 warps][16]
         named_barrier_sync(1, 128);
 #pragma unroll
-        for (int c = 0; c < kDecN; ++c) {
+        for (int c = 0; c < NC; ++c) {
             float v = l_part[c];
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
             if (lane == c) red[(warp - 2) * 16 + c] = v;
         }
         named_barrier_sync(1, 128);
-        if (ok && ntiles > 0) ok = mbar_wait(o_bar, (ntiles - 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout);
+        // every PV has completed once the last tile's commit has: commits complete in issue order
+        if (ok && ntiles > 0)
+            ok = mbar_wait(&p_free[(ntiles - 1) & 1], ((ntiles - 1) >> 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout);
         if (ok) {
             tc_fence_after_sync();
-            uint32_t o[16];
+            uint32_t o[NC];
             if (ntiles > 0) {
-                tmem_ld_x16(lane_addr + 32, o);
+                tmem_ld_n<NC>(lane_addr + 32, o);
                 tmem_ld_wait();
             }
             if (r < D) {
 #pragma unroll
-                for (int c = 0; c < kDecN; ++c) {
+                for (int c = 0; c < NC; ++c) {
                     if (c < ncol) {
                         const float l = red[c] + red[16 + c] + red[32 + c] + red[48 + c];
                         const float val = (ntiles > 0 && l > 0.f) ? __uint_as_float(o[c]) / l : 0.f;
@@ -364,20 +375,38 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     }
 }
 
-template <int D, typename T>
-static int launch_decode(const CUtensorMap& tq, const CUtensorMap& tkv, const DecParams& p, int nseq, cudaStream_t stream) {
+template <int D, typename T, int KS, int VS, int MINB, int NC>
+static int launch_decode_variant(const CUtensorMap& tq, const CUtensorMap& tkv, const DecParams& p, int nseq, cudaStream_t stream) {
     constexpr int kv = (D / 64) * kDecTile * 128;
-    constexpr int smem = 2 * kDecStages * kv + 4096 + 2 * 2 * kDecN * 128 + 1024 + 1024;
+    constexpr int smem = (KS + VS) * kv + 4096 + 2 * 2 * kDecN * 128 + 1024 + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, T, KS, VS, MINB, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail("cudaFuncSetAttribute(attn_decode)", e);
         configured = true;
     }
     dim3 grid(p.hkv, nseq * p.splits);
-    TELB_LAUNCH("attn_decode_kernel", (attn_decode_kernel<D, T>), dim3(grid), dim3(kDecThreads), smem, stream, tq, tkv, p);
+    TELB_LAUNCH("attn_decode_kernel", (attn_decode_kernel<D, T, KS, VS, MINB, NC>), dim3(grid), dim3(kDecThreads), smem, stream, tq, tkv, p);
     TELB_CHECK_LAUNCH("attn_decode_kernel");
     return 0;
+}
+
+static int g_decode_variant = 1;      // measured fastest at batch 8..64 with 1k context
+
+template <int D, typename T, int NC>
+static int launch_decode_nc(const CUtensorMap& tq, const CUtensorMap& tkv, const DecParams& p, int nseq, cudaStream_t stream) {
+    switch (g_decode_variant) {
+        case 1: return launch_decode_variant<D, T, 1, 1, 2, NC>(tq, tkv, p, nseq, stream);     // 2 CTAs / SM, single-stage rings
+        case 2: return launch_decode_variant<D, T, 2, 1, 2, NC>(tq, tkv, p, nseq, stream);     // 2 CTAs / SM, K prefetched one tile ahead
+        default: return launch_decode_variant<D, T, 3, 3, 1, NC>(tq, tkv, p, nseq, stream);    // 1 CTA / SM, three-stage rings
+    }
+}
+
+template <int D, typename T>
+static int launch_decode(const CUtensorMap& tq, const CUtensorMap& tkv, const DecParams& p, int nseq, int max_cols, cudaStream_t stream) {
+    if (max_cols <= 4) return launch_decode_nc<D, T, 4>(tq, tkv, p, nseq, stream);
+    if (max_cols <= 8) return launch_decode_nc<D, T, 8>(tq, tkv, p, nseq, stream);
+    return launch_decode_nc<D, T, 16>(tq, tkv, p, nseq, stream);
 }
 
 }  // namespace telb
@@ -386,6 +415,13 @@ using namespace telb;
 
 extern "C" int telb_attn_combine(const float* ws_o, const float* ws_lse, void* out, int rows, int splits, int d, int is_bf16,
                                  cudaStream_t stream);
+
+// Ring depth / residency variant of the decode kernel (0, 1 or 2: see launch_decode); process-wide.
+extern "C" int telb_set_decode_variant(int v) {
+    if (v < 0 || v > 2) return fail("telb_set_decode_variant: variant must be 0, 1 or 2");
+    g_decode_variant = v;
+    return 0;
+}
 
 // Decode-shaped steps only: max_q_len * (Hq/Hkv) <= 16.  Same tensors as telb_paged_attention.
 extern "C" int telb_paged_attention_decode(const void* q, const void* kv_layer, void* out, const int* q_start,
@@ -435,8 +471,8 @@ extern "C" int telb_paged_attention_decode(const void* q, const void* kv_layer, 
         const uint32_t box_rows = page_size == 64 ? 64 : 128;
         if (make_tmap_2d(&tkv, dt, 2, kv_layer, rows, d, (uint64_t)d * 2, box_rows, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
     }
-    const int rc = is_bf16 ? launch_decode<128, __nv_bfloat16>(tq, tkv, p, num_seqs, stream)
-                           : launch_decode<128, __half>(tq, tkv, p, num_seqs, stream);
+    const int rc = is_bf16 ? launch_decode<128, __nv_bfloat16>(tq, tkv, p, num_seqs, max_q_len * group, stream)
+                           : launch_decode<128, __half>(tq, tkv, p, num_seqs, max_q_len * group, stream);
     if (rc) return rc;
     if (splits > 1) return telb_attn_combine(p.ws_o, p.ws_lse, out, total_tokens * hq, splits, d, is_bf16, stream);
     return 0;

@@ -277,11 +277,14 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
             }
             const float m_new = fmaxf(m_used, mx);
             const bool need = row_valid && (m_new > m_used + kRescaleThreshold);
+            // P buffer b is free once P·V of tile j-2 has completed; this wait is taken at every use of the buffer, so
+            // its parity is exact (a barrier polled only now and then could be two phases ahead and alias).
+            if (!mbar_wait(&p_free[b], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kStatusEpilogueTimeout)) { ok = false; break; }
             if (j == 0) {
                 if (row_valid) m_used = m_new;
             } else if (__any_sync(0xffffffffu, need)) {
-                // O must be quiescent: every earlier P·V has completed
-                if (!mbar_wait(o_bar, (j - 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout)) { ok = false; break; }
+                // O must be quiescent: P·V of tile j-1 is the next completion of the other buffer's barrier
+                if (!mbar_wait(&p_free[b ^ 1], ((j - 1) >> 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout)) { ok = false; break; }
                 tc_fence_after_sync();
                 const float f = need ? exp2f(m_used - m_new) : 1.f;
 #pragma unroll 1
@@ -300,7 +303,6 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
                     m_used = m_new;
                 }
             }
-            if (!mbar_wait(&p_free[b], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kStatusEpilogueTimeout)) { ok = false; break; }
             uint8_t* prow = s_p + b * kPBytes + (r >> 3) * 1024 + (r & 7) * 128;
             if (row_valid) {
                 const float mref = m_used == -INFINITY ? 0.f : m_used;
@@ -329,7 +331,9 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
             mbar_arrive(&p_full[b]);
         }
         // ---- epilogue ----
-        if (ok && ntiles > 0) ok = mbar_wait(o_bar, (ntiles - 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout);
+        // commits complete in issue order: the last tile's completion covers every earlier P·V
+        if (ok && ntiles > 0)
+            ok = mbar_wait(&p_free[(ntiles - 1) & 1], ((ntiles - 1) >> 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout);
         if (ok) {
             tc_fence_after_sync();
             const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
