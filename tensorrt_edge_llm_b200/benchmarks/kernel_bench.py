@@ -107,18 +107,35 @@ def bench_attention(args):
     pages_per = (past + q + page - 1) // page
     table = torch.arange(b * pages_per, dtype=torch.int32).view(b, pages_per)
     kv = torch.randn(b * pages_per, 2, hkv, page, d, device="cuda").bfloat16()
+    kv_alt = kv.clone()          # graph timing alternates two pools so a replay never re-reads L2-resident K/V
     meta = build_step_meta([q] * b, [past] * b, table, page, device="cuda")
     qt = torch.randn(b * q, hq, d, device="cuda").bfloat16()
     if args.variant >= 0:
         cu._check(cu.lib().telb_set_decode_variant(args.variant), "set_decode_variant", 0)
-    fn = lambda: cu.paged_attention(qt, kv, meta, d ** -0.5, splits=args.splits or None)
+    flip = [0]
+
+    def fn():
+        flip[0] ^= 1
+        return cu.paged_attention(qt, kv if flip[0] else kv_alt, meta, d ** -0.5, splits=args.splits or None)
+
     out = fn()
     if args.check:      # numerics against the fp32 statement of the op
         from ..ops import reference as ref
         want = ref.paged_attention(qt, kv, meta, d ** -0.5)
         err = ((out.float() - want.float()).norm() / want.float().norm()).item()
         assert err < 8e-3, err
-    med, best = time_fn(fn, args.warmup, args.iters, flush, args.graph if q <= 4 else 0)
+    # a single launch timed with events also counts the host time to encode descriptors and launch: decode-size
+    # calls are therefore timed as a captured chain of launches
+    med, best = time_fn(fn, args.warmup, args.iters, flush, (args.graph or 8) if q <= 4 else 0)
+    if args.trace:      # per-tile timeline of the first CTA (ns since it started)
+        tr = torch.zeros(3, 64, 4, dtype=torch.int64, device="cuda")
+        cu.paged_attention(qt, kv, meta, d ** -0.5, splits=args.splits or None, trace=tr)
+        torch.cuda.synchronize()
+        tiles = min(64, args.trace_tiles or (past + q + 127) // 128)
+        names = {0: ("k_slot_free", "v_slot_free"), 1: ("issue_S", "issue_PV"), 2: ("S_ready", "max_exchanged", "P_published")}
+        for role, evs in names.items():
+            for e, nm in enumerate(evs):
+                print(f"trace {nm:>14}: " + " ".join(f"{int(tr[role, j, e]):6d}" for j in range(tiles)))
     kv_bytes = b * (past + q) * hkv * d * 2 * 2
     flops = 4.0 * b * hq * d * (q * past + q * (q + 1) / 2)
     roof = max(flops / fl, kv_bytes / bw)
@@ -144,6 +161,8 @@ def main():
     a.add_argument("--variant", type=int, default=-1, help="decode kernel ring / residency variant (see telb_set_decode_variant)")
     a.add_argument("--splits", type=int, default=0, help="KV splits (0 = heuristic)")
     a.add_argument("--check", action="store_true", help="compare with the fp32 reference first")
+    a.add_argument("--trace", action="store_true", help="print the per-tile timeline of the first CTA of the decode kernel")
+    a.add_argument("--trace-tiles", type=int, default=0, help="tiles of the first CTA to print (it walks several items)")
     for p in (g, a):
         p.add_argument("--warmup", type=int, default=3)
         p.add_argument("--iters", type=int, default=10)

@@ -33,13 +33,23 @@ struct DecParams {
     int max_pages, page_size;
     int hq, hkv, group;
     int splits, total_tokens, window;
+    int num_seqs, num_items;        // items = sequences x KV heads x splits, walked by persistent CTAs
     float scale_log2;
     int* status;
+    // Optional timeline of CTA 0: trace[role][tile][event] in ns since the CTA started (role 0 producer,
+    // 1 MMA issuer, 2 softmax; 4 events per tile, 64 tiles at most).  Null in normal use.
+    unsigned long long* trace;
 };
 
 constexpr int kDecThreads = 192;
 constexpr int kDecTile = 128;      // cached tokens per tile
 constexpr int kDecN = 16;          // (query token, head) columns
+constexpr int kTraceTiles = 64;
+
+__device__ __forceinline__ void trace_at(const DecParams& p, unsigned long long t0, int role, int tile, int ev) {
+    if (p.trace && blockIdx.x == 0 && tile < kTraceTiles)
+        p.trace[(role * kTraceTiles + tile) * 4 + ev] = global_timer_ns() - t0;
+}
 
 __device__ __forceinline__ float warp_max_f32(float v) {
     float r;
@@ -47,10 +57,40 @@ __device__ __forceinline__ float warp_max_f32(float v) {
     return r;
 }
 
-// KS / VS: depth of the K and V tile rings; MINB: CTAs that must fit on one SM (two co-resident CTAs with
-// shallow rings hide each other's per-tile synchronisation latency; one CTA with deep rings prefetches further).
+// One unit of work: the cached tokens [j0, j0 + ntiles) x 128 of one (sequence, KV head).
+struct DecItem {
+    int seq, kvh, split, qlen, past, qrow0, j0, ntiles;
+};
+
+// Items are ordered KV head fastest, so CTAs that run side by side read neighbouring slabs of the same pages.
+__device__ __forceinline__ DecItem decode_item(const DecParams& p, int item) {
+    DecItem it;
+    it.kvh = item % p.hkv;
+    const int rest = item / p.hkv;
+    it.split = rest % p.splits;
+    it.seq = rest / p.splits;
+    it.qlen = p.q_len[it.seq];
+    it.past = p.past_len[it.seq];
+    it.qrow0 = p.q_start[it.seq];
+    const int kv_end = it.past + it.qlen;
+    int tile_lo = 0;
+    if (p.window > 0) tile_lo = max(0, it.past - p.window + 1) / kDecTile;
+    const int tile_hi = (kv_end + kDecTile - 1) / kDecTile;
+    const int per = (tile_hi - tile_lo + p.splits - 1) / p.splits;
+    it.j0 = tile_lo + it.split * per;
+    it.ntiles = it.qlen > 0 ? max(0, min(tile_hi, it.j0 + per) - it.j0) : 0;
+    return it;
+}
+
+// KS / VS: depth of the K and V tile rings; MINB: CTAs that must fit on one SM (co-resident CTAs with shallow
+// rings hide each other's per-tile synchronisation latency; one CTA with deep rings prefetches further).
 // NC: how many of the 16 MMA columns can be live (query tokens x heads per KV head, rounded up to 4 / 8 / 16);
 // the softmax registers and loops are sized by it.
+//
+// The grid is persistent: CTA b walks items b, b + gridDim.x, ...  The K/V rings, the four score buffers and the
+// two P buffers keep cycling across item boundaries (flat tile counter), Q and the O accumulator are double
+// buffered per item, so the next item's loads and scores overlap the previous item's epilogue and no CTA slot
+// idles while another wave of CTAs starts up.
 template <int D, typename T, int KS, int VS, int MINB, int NC>
 __global__ void __launch_bounds__(kDecThreads, MINB)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_kv, DecParams p) {
@@ -59,52 +99,48 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     constexpr int kKvBytes = kDChunks * kChunkBytes;            // one K or V tile
     constexpr int kQBytes = kDChunks * kDecN * 128;
     constexpr int kPBytes = 2 * kDecN * 128;                    // Pᵀ: [16 cols x 128 tokens] bf16, two 64-token chunks
-    constexpr int kTmemCols = 64;                               // S0 @0, S1 @16, O @32 (16 columns each)
+    constexpr int kSBufs = 4;                                   // score buffers S0..S3 @ 0, 16, 32, 48
+    constexpr int kOCol = kSBufs * 16;                          // O accumulators O0, O1 (16 columns each)
+    constexpr int kTmemCols = 128;
     constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* s_k = smem;
     uint8_t* s_v = s_k + KS * kKvBytes;
-    uint8_t* s_q = s_v + VS * kKvBytes;
-    uint8_t* s_p = s_q + ((kQBytes + 1023) & ~1023);
+    uint8_t* s_q = s_v + VS * kKvBytes;                         // two Q buffers
+    uint8_t* s_p = s_q + 2 * kQBytes;                           // two P buffers
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_p + 2 * kPBytes);
     uint64_t* q_full = bars;
-    uint64_t* k_full = bars + 1;
+    uint64_t* q_free = q_full + 2;
+    uint64_t* k_full = q_free + 2;
     uint64_t* k_empty = k_full + KS;
     uint64_t* v_full = k_empty + KS;
     uint64_t* v_empty = v_full + VS;
     uint64_t* s_full = v_empty + VS;
-    uint64_t* s_free = s_full + 2;
-    uint64_t* p_full = s_free + 2;
+    uint64_t* s_free = s_full + kSBufs;
+    uint64_t* p_full = s_free + kSBufs;
     uint64_t* p_free = p_full + 2;
-    uint64_t* o_bar = p_free + 2;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_bar + 1);
+    uint64_t* o_full = p_free + 2;
+    uint64_t* o_free = o_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_free + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    float* s_red = reinterpret_cast<float*>(tmem_slot + 4);     // [2 parities][4 warps][16] column maxima, then sums
+    float* s_red = reinterpret_cast<float*>(tmem_slot + 4);     // [2 parities][4 warps][16] column maxima
+    float* s_sum = s_red + 128;                                 // [4 warps][16] column sums (item epilogue)
 
     pdl_prologue();          // step metadata and Q/KV are produced by earlier kernels
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int kvh = blockIdx.x;
-    const int seq = blockIdx.y / p.splits;
-    const int split = blockIdx.y - seq * p.splits;
-    const int qlen = p.q_len[seq];
-    const int past = p.past_len[seq];
-    const int qrow0 = p.q_start[seq];
-    if (qlen <= 0) return;
-
-    const int kv_end = past + qlen;
-    int tile_lo = 0;
-    if (p.window > 0) tile_lo = max(0, past - p.window + 1) / kDecTile;
-    const int tile_hi_all = (kv_end + kDecTile - 1) / kDecTile;
-    const int per = (tile_hi_all - tile_lo + p.splits - 1) / p.splits;
-    const int j0 = tile_lo + split * per;
-    const int j1 = min(tile_hi_all, j0 + per);
-    const int ntiles = max(0, j1 - j0);
 
     if (threadIdx.x == 0) {
-        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&q_full[s], 1);
+            mbar_init(&q_free[s], 1);
+            mbar_init(&p_full[s], 128);
+            mbar_init(&p_free[s], 1);
+            mbar_init(&o_full[s], 1);
+            mbar_init(&o_free[s], 128);
+        }
         for (int s = 0; s < KS; ++s) {
             mbar_init(&k_full[s], 1);
             mbar_init(&k_empty[s], 1);
@@ -113,13 +149,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             mbar_init(&v_full[s], 1);
             mbar_init(&v_empty[s], 1);
         }
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < kSBufs; ++s) {
             mbar_init(&s_full[s], 1);
             mbar_init(&s_free[s], 128);
-            mbar_init(&p_full[s], 128);
-            mbar_init(&p_free[s], 1);
         }
-        mbar_init(o_bar, 1);
         *abort_flag = 0;
         mbar_fence_init();
         prefetch_tensormap(&tma_q);
@@ -135,95 +168,166 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    const unsigned long long t_start = p.trace ? global_timer_ns() : 0ull;
 
     if (warp == 0) {
         // ------------------------------ producer ------------------------------
-        if (lane == 0 && ntiles > 0) {
-            // Q columns: (query token qi, head g) → row qi*G + g of a [16 x D] K-major tile
-            mbar_expect_tx(q_full, kQBytes);
+        // The whole warp walks the tiles: every lane fetches the page ids of one tile ahead of time (one coalesced
+        // read per 32 tiles instead of dependent global loads on the issuing thread), lane 0 issues the TMA copies.
+        const int pages_per_tile = kDecTile / p.page_size;          // 2 for 64-token pages, 1 for 128
+        const int rows_per_load = kDecTile / pages_per_tile;
+        bool ok = true;
+        int jg = 0, ig = 0;
+        for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
+            const DecItem it = decode_item(p, item);
+            if (it.ntiles <= 0) continue;
+            if (lane == 0) {
+                // Q columns: (query token qi, head g) → row qi*G + g of a [16 x D] K-major tile
+                ok = mbar_wait(&q_free[ig & 1], ((ig >> 1) & 1) ^ 1, abort_flag, p.status, kStatusProducerTimeout);
+                if (ok) {
+                    mbar_expect_tx(&q_full[ig & 1], kQBytes);
 #pragma unroll
-            for (int c = 0; c < kDChunks; ++c)
-                tma_load_3d(s_q + c * (kDecN * 128), &tma_q, q_full, c * 64, kvh * p.group, qrow0);
-            const int pages_per_tile = kDecTile / p.page_size;          // 2 for 64-token pages, 1 for 128
-            const int rows_per_load = kDecTile / pages_per_tile;
-            for (int j = 0; j < ntiles; ++j) {
-                const int ks = j % KS, vs = j % VS;
-                const uint32_t kph = ((j / KS) & 1) ^ 1, vph = ((j / VS) & 1) ^ 1;
-                const int tile = j0 + j;
-                int rows[2];
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    int page = -1;
-                    const int lp = tile * pages_per_tile + h;
-                    if (h < pages_per_tile && lp < p.max_pages) page = p.page_table[(size_t)seq * p.max_pages + lp];
-                    if (page < 0) page = 0;                              // masked anyway
-                    rows[h] = ((page * 2 + 0) * p.hkv + kvh) * p.page_size;
+                    for (int c = 0; c < kDChunks; ++c)
+                        tma_load_3d(s_q + (ig & 1) * kQBytes + c * (kDecN * 128), &tma_q, &q_full[ig & 1], c * 64, it.kvh * p.group, it.qrow0);
                 }
-                if (!mbar_wait(&k_empty[ks], kph, abort_flag, p.status, kStatusProducerTimeout)) break;
-                mbar_expect_tx(&k_full[ks], kKvBytes);
-                for (int h = 0; h < pages_per_tile; ++h)
-#pragma unroll
-                    for (int c = 0; c < kDChunks; ++c)
-                        tma_load_2d(s_k + ks * kKvBytes + c * kChunkBytes + h * rows_per_load * 128, &tma_kv, &k_full[ks],
-                                    c * 64, rows[h]);
-                if (!mbar_wait(&v_empty[vs], vph, abort_flag, p.status, kStatusProducerTimeout)) break;
-                mbar_expect_tx(&v_full[vs], kKvBytes);
-                for (int h = 0; h < pages_per_tile; ++h)
-#pragma unroll
-                    for (int c = 0; c < kDChunks; ++c)
-                        tma_load_2d(s_v + vs * kKvBytes + c * kChunkBytes + h * rows_per_load * 128, &tma_kv, &v_full[vs],
-                                    c * 64, rows[h] + p.hkv * p.page_size);
             }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            for (int base = 0; base < it.ntiles && ok; base += 32) {
+                int pg[2] = {0, 0};
+                if (base + lane < it.ntiles) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int lp = (it.j0 + base + lane) * pages_per_tile + h;
+                        int page = -1;
+                        if (h < pages_per_tile && lp < p.max_pages) page = p.page_table[(size_t)it.seq * p.max_pages + lp];
+                        pg[h] = page < 0 ? 0 : page;                     // masked anyway
+                    }
+                }
+                const int cnt = min(32, it.ntiles - base);
+                for (int jj = 0; jj < cnt && ok; ++jj, ++jg) {
+                    const int page0 = __shfl_sync(0xffffffffu, pg[0], jj), page1 = __shfl_sync(0xffffffffu, pg[1], jj);
+                    if (lane == 0) {
+                        const int ks = jg % KS, vs = jg % VS;
+                        const uint32_t kph = ((jg / KS) & 1) ^ 1, vph = ((jg / VS) & 1) ^ 1;
+                        const int rows[2] = {((page0 * 2 + 0) * p.hkv + it.kvh) * p.page_size, ((page1 * 2 + 0) * p.hkv + it.kvh) * p.page_size};
+                        ok = mbar_wait(&k_empty[ks], kph, abort_flag, p.status, kStatusProducerTimeout);
+                        if (ok) {
+                            trace_at(p, t_start, 0, jg, 0);         // K slot free, K loads issued next
+                            mbar_expect_tx(&k_full[ks], kKvBytes);
+                            for (int h = 0; h < pages_per_tile; ++h)
+#pragma unroll
+                                for (int c = 0; c < kDChunks; ++c)
+                                    tma_load_2d(s_k + ks * kKvBytes + c * kChunkBytes + h * rows_per_load * 128, &tma_kv, &k_full[ks],
+                                                c * 64, rows[h]);
+                            ok = mbar_wait(&v_empty[vs], vph, abort_flag, p.status, kStatusProducerTimeout);
+                        }
+                        if (ok) {
+                            trace_at(p, t_start, 0, jg, 1);         // V slot free, V loads issued next
+                            mbar_expect_tx(&v_full[vs], kKvBytes);
+                            for (int h = 0; h < pages_per_tile; ++h)
+#pragma unroll
+                                for (int c = 0; c < kDChunks; ++c)
+                                    tma_load_2d(s_v + vs * kKvBytes + c * kChunkBytes + h * rows_per_load * 128, &tma_kv, &v_full[vs],
+                                                c * 64, rows[h] + p.hkv * p.page_size);
+                        }
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                }
+            }
+            ++ig;
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0 && ntiles > 0) {
+        if (lane == 0) {
             const uint32_t idesc_s = idesc_f16(128, kDecN, kBf16);                    // A = K (K-major), B = Q (K-major)
             const uint32_t idesc_o = idesc_f16(128, kDecN, kBf16, /*a_mn_major=*/true);   // A = Vᵀ (MN-major), B = Pᵀ (K-major)
-            auto issue_s = [&](int j) {
-                const int stage = j % KS;
-                const uint64_t dk = smem_desc_sw128(s_k + stage * kKvBytes);
-                const uint64_t dq = smem_desc_sw128(s_q);
-                const uint32_t d_tmem = tmem_base + (j & 1) * 16;
-#pragma unroll
-                for (int k = 0; k < D / 16; ++k) {
-                    const int c = k >> 2, kk = k & 3;
-                    umma_f16(d_tmem, dk + (uint64_t)((c * kChunkBytes) >> 4) + 2 * kk, dq + (uint64_t)((c * kDecN * 128) >> 4) + 2 * kk,
-                             idesc_s, k > 0 ? 1u : 0u);
-                }
-                umma_commit(&k_empty[stage]);
-                umma_commit(&s_full[j & 1]);
+            // Two cursors walk the same item list: scores (S = K Qᵀ) run up to kSBufs tiles ahead of P·V, so the
+            // score MMA is never on the softmax → P·V dependency chain.
+            struct Cursor {
+                int item, ig, j, jg, ntiles;       // current item, its ordinal among non-empty items, tile in item, flat tile
             };
-            bool ok = mbar_wait(q_full, 0, abort_flag, p.status, kStatusMmaTimeout) &&
-                      mbar_wait(&k_full[0], 0, abort_flag, p.status, kStatusMmaTimeout);
-            if (ok) {
-                tc_fence_after_sync();
-                issue_s(0);
-            }
-            for (int j = 0; j < ntiles && ok; ++j) {
-                if (j + 1 < ntiles) {
-                    const int jn = j + 1;
-                    ok = mbar_wait(&k_full[jn % KS], (jn / KS) & 1, abort_flag, p.status, kStatusMmaTimeout) &&
-                         mbar_wait(&s_free[jn & 1], ((jn >> 1) & 1) ^ 1, abort_flag, p.status, kStatusMmaTimeout);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    issue_s(jn);
+            auto advance = [&](Cursor& c) {        // move to the next non-empty item of this CTA (ntiles = 0 at the end)
+                c.ntiles = 0;
+                while (c.item < p.num_items) {
+                    const DecItem it = decode_item(p, c.item);
+                    if (it.ntiles > 0) {
+                        c.ntiles = it.ntiles;
+                        return;
+                    }
+                    c.item += gridDim.x;
                 }
-                const int stage = j % VS;
-                ok = mbar_wait(&p_full[j & 1], (j >> 1) & 1, abort_flag, p.status, kStatusMmaTimeout) &&
-                     mbar_wait(&v_full[stage], (j / VS) & 1, abort_flag, p.status, kStatusMmaTimeout);
-                if (!ok) break;
-                tc_fence_after_sync();
-                // A = Vᵀ: 64-wide d chunks are kChunkBytes apart (leading offset), 8-token groups 1024 B apart
-                const uint64_t dv = smem_desc_sw128_mn(s_v + stage * kKvBytes, kChunkBytes, 1024);
-                const uint64_t dp = smem_desc_sw128(s_p + (j & 1) * kPBytes);
+            };
+            Cursor cs{(int)blockIdx.x, 0, 0, 0, 0}, cp{(int)blockIdx.x, 0, 0, 0, 0};
+            advance(cs);
+            advance(cp);
+            bool ok = true;
+            const long long spin0 = clock64();
+            unsigned int idle = 0;
+            while (ok && cp.ntiles > 0) {
+                bool progressed = false;
+                if (cs.ntiles > 0 && cs.jg < cp.jg + kSBufs && (cs.j > 0 || mbar_try_wait(&q_full[cs.ig & 1], (cs.ig >> 1) & 1)) &&
+                    mbar_try_wait(&k_full[cs.jg % KS], (cs.jg / KS) & 1) && mbar_try_wait(&s_free[cs.jg % kSBufs], ((cs.jg / kSBufs) & 1) ^ 1)) {
+                    tc_fence_after_sync();
+                    trace_at(p, t_start, 1, cs.jg, 0);      // K tile landed and S buffer free: S = K Qᵀ issued
+                    const int stage = cs.jg % KS;
+                    const uint64_t dk = smem_desc_sw128(s_k + stage * kKvBytes);
+                    const uint64_t dq = smem_desc_sw128(s_q + (cs.ig & 1) * kQBytes);
+                    const uint32_t d_tmem = tmem_base + (cs.jg % kSBufs) * 16;
 #pragma unroll
-                for (int k = 0; k < kDecTile / 16; ++k)     // 16 tokens per MMA: 2048 B of V rows, 32 B of a P row
-                    umma_f16(tmem_base + 32, dv + (uint64_t)((k * 2048) >> 4), dp + (uint64_t)(((k >> 2) * (kDecN * 128)) >> 4) + 2 * (k & 3),
-                             idesc_o, (j > 0 || k > 0) ? 1u : 0u);
-                umma_commit(&v_empty[stage]);
-                umma_commit(&p_free[j & 1]);
-                umma_commit(o_bar);
+                    for (int k = 0; k < D / 16; ++k) {
+                        const int c = k >> 2, kk = k & 3;
+                        umma_f16(d_tmem, dk + (uint64_t)((c * kChunkBytes) >> 4) + 2 * kk, dq + (uint64_t)((c * kDecN * 128) >> 4) + 2 * kk,
+                                 idesc_s, k > 0 ? 1u : 0u);
+                    }
+                    umma_commit(&k_empty[stage]);
+                    umma_commit(&s_full[cs.jg % kSBufs]);
+                    ++cs.j;
+                    ++cs.jg;
+                    if (cs.j == cs.ntiles) {                // last score tile of the item: its Q buffer may be refilled
+                        umma_commit(&q_free[cs.ig & 1]);
+                        cs.item += gridDim.x;
+                        ++cs.ig;
+                        cs.j = 0;
+                        advance(cs);
+                    }
+                    progressed = true;
+                }
+                if (cp.jg < cs.jg && mbar_try_wait(&p_full[cp.jg & 1], (cp.jg >> 1) & 1) && mbar_try_wait(&v_full[cp.jg % VS], (cp.jg / VS) & 1) &&
+                    (cp.j > 0 || mbar_try_wait(&o_free[cp.ig & 1], ((cp.ig >> 1) & 1) ^ 1))) {
+                    tc_fence_after_sync();
+                    trace_at(p, t_start, 1, cp.jg, 1);      // P written and V tile landed: O += Vᵀ Pᵀ issued
+                    const int stage = cp.jg % VS;
+                    // A = Vᵀ: 64-wide d chunks are kChunkBytes apart (leading offset), 8-token groups 1024 B apart
+                    const uint64_t dv = smem_desc_sw128_mn(s_v + stage * kKvBytes, kChunkBytes, 1024);
+                    const uint64_t dp = smem_desc_sw128(s_p + (cp.jg & 1) * kPBytes);
+                    const uint32_t d_o = tmem_base + kOCol + (cp.ig & 1) * 16;
+#pragma unroll
+                    for (int k = 0; k < kDecTile / 16; ++k)     // 16 tokens per MMA: 2048 B of V rows, 32 B of a P row
+                        umma_f16(d_o, dv + (uint64_t)((k * 2048) >> 4), dp + (uint64_t)(((k >> 2) * (kDecN * 128)) >> 4) + 2 * (k & 3),
+                                 idesc_o, (cp.j > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&v_empty[stage]);
+                    umma_commit(&p_free[cp.jg & 1]);
+                    ++cp.j;
+                    ++cp.jg;
+                    if (cp.j == cp.ntiles) {                // the item's accumulator is complete
+                        umma_commit(&o_full[cp.ig & 1]);
+                        cp.item += gridDim.x;
+                        ++cp.ig;
+                        cp.j = 0;
+                        advance(cp);
+                    }
+                    progressed = true;
+                }
+                if (progressed) {
+                    idle = 0;
+                } else if ((++idle & 1023u) == 0) {         // bounded: give up after about two seconds without progress
+                    if (*abort_flag) ok = false;
+                    else if (idle > (1u << 20) && clock64() - spin0 > kSpinLimitCycles) {
+                        *abort_flag = 1u;
+                        if (p.status) atomicCAS(p.status, kStatusOk, kStatusMmaTimeout);
+                        ok = false;
+                    }
+                }
             }
         }
     } else {
@@ -231,135 +335,147 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         const int quad = warp & 3;
         const int r = quad * 32 + lane;                 // cached token within the tile == TMEM lane (S); feature d (O)
         const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
-        const int ncol = qlen * p.group;                // live columns (<= 16)
         const int gshift = 31 - __clz(p.group);         // the group size is a power of two
-        float m_used[NC], l_part[NC];
-#pragma unroll
-        for (int c = 0; c < NC; ++c) {
-            m_used[c] = -INFINITY;
-            l_part[c] = 0.f;
-        }
         bool ok = true;
-        for (int j = 0; j < ntiles && ok; ++j) {
-            const int b = j & 1;
-            if (!mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout)) { ok = false; break; }
-            tc_fence_after_sync();
-            uint32_t raw[NC];
-            tmem_ld_n<NC>(lane_addr + b * 16, raw);
-            tmem_ld_wait();
-            tc_fence_before_sync();
-            mbar_arrive(&s_free[b]);
-            const int tk = (j0 + j) * kDecTile + r;     // absolute cache slot of this thread's token
-            float s[NC];
-            float* red = s_red + b * 64;
-            // Only the live columns (query tokens x heads of this sequence) are processed; `ncol`
-            // is uniform across the CTA, so the guards below do not diverge.
+        int jg = 0, ig = 0;
+        for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
+            const DecItem it = decode_item(p, item);
+            if (it.qlen <= 0) continue;
+            const int ncol = it.qlen * p.group;         // live columns (<= NC)
+            float m_used[NC], l_part[NC];
 #pragma unroll
             for (int c = 0; c < NC; ++c) {
-                if (c < ncol) {
-                    const int qi = c >> gshift;
-                    bool vis = tk <= past + qi;
-                    if (p.window > 0) vis = vis && tk > past + qi - p.window;
-                    s[c] = vis ? __uint_as_float(raw[c]) * p.scale_log2 : -INFINITY;
-                    const float wm = warp_max_f32(s[c]);
-                    if (lane == c) red[(warp - 2) * 16 + c] = wm;
-                } else {
-                    s[c] = -INFINITY;
-                }
+                m_used[c] = -INFINITY;
+                l_part[c] = 0.f;
             }
-            named_barrier_sync(1, 128);
-            bool any_need = false;
-            float f[NC];
+            const uint32_t o_addr = lane_addr + kOCol + (ig & 1) * 16;
+            for (int j = 0; j < it.ntiles && ok; ++j, ++jg) {
+                const int b = jg & 1;                   // P buffer
+                const int sb = jg % kSBufs;             // score buffer
+                if (!mbar_wait(&s_full[sb], (jg / kSBufs) & 1, abort_flag, p.status, kStatusEpilogueTimeout)) { ok = false; break; }
+                tc_fence_after_sync();
+                if (threadIdx.x == 64) trace_at(p, t_start, 2, jg, 0);     // scores ready
+                uint32_t raw[NC];
+                tmem_ld_n<NC>(lane_addr + sb * 16, raw);
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                mbar_arrive(&s_free[sb]);
+                const int tk = (it.j0 + j) * kDecTile + r;     // absolute cache slot of this thread's token
+                float s[NC];
+                float* red = s_red + b * 64;
+                // Only the live columns (query tokens x heads of this sequence) are processed; `ncol`
+                // is uniform across the CTA, so the guards below do not diverge.
 #pragma unroll
-            for (int c = 0; c < NC; ++c) {
-                f[c] = 1.f;
-                if (c < ncol) {
-                    const float mt = fmaxf(fmaxf(red[c], red[16 + c]), fmaxf(red[32 + c], red[48 + c]));
-                    const float m_new = fmaxf(m_used[c], mt);
-                    if (m_new > m_used[c] + 8.0f) {               // uniform across the CTA
-                        f[c] = (m_used[c] == -INFINITY) ? 0.f : exp2f(m_used[c] - m_new);
-                        l_part[c] *= f[c];
-                        m_used[c] = m_new;
-                        any_need = true;
+                for (int c = 0; c < NC; ++c) {
+                    if (c < ncol) {
+                        const int qi = c >> gshift;
+                        bool vis = tk <= it.past + qi;
+                        if (p.window > 0) vis = vis && tk > it.past + qi - p.window;
+                        s[c] = vis ? __uint_as_float(raw[c]) * p.scale_log2 : -INFINITY;
+                        const float wm = warp_max_f32(s[c]);
+                        if (lane == c) red[(warp - 2) * 16 + c] = wm;
+                    } else {
+                        s[c] = -INFINITY;
                     }
                 }
-            }
-            // P buffer b is free once PV(j-2) has completed.  This wait is taken for every use of the buffer, so its
-            // parity is exact; it also pins how far the tensor pipe can lag behind this warp.
-            if (!mbar_wait(&p_free[b], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kStatusEpilogueTimeout)) { ok = false; break; }
-            if (j > 0 && any_need) {
-                // O may only be rescaled after PV(j-1) has landed: that is the next completion of the other P
-                // buffer's barrier (a parity wait on a barrier that is polled only now and then could alias).
-                if (!mbar_wait(&p_free[b ^ 1], ((j - 1) >> 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout)) { ok = false; break; }
-                tc_fence_after_sync();
-                uint32_t o[NC];
-                tmem_ld_n<NC>(lane_addr + 32, o);
-                tmem_ld_wait();
+                named_barrier_sync(1, 128);
+                if (threadIdx.x == 64) trace_at(p, t_start, 2, jg, 1);     // column maxima exchanged
+                bool any_need = false;
+                float f[NC];
 #pragma unroll
-                for (int c = 0; c < NC; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * f[c]);
-                tmem_st_n<NC>(lane_addr + 32, o);
-                tmem_st_wait();
-                tc_fence_before_sync();
+                for (int c = 0; c < NC; ++c) {
+                    f[c] = 1.f;
+                    if (c < ncol) {
+                        const float mt = fmaxf(fmaxf(red[c], red[16 + c]), fmaxf(red[32 + c], red[48 + c]));
+                        const float m_new = fmaxf(m_used[c], mt);
+                        if (m_new > m_used[c] + 8.0f) {               // uniform across the CTA
+                            f[c] = (m_used[c] == -INFINITY) ? 0.f : exp2f(m_used[c] - m_new);
+                            l_part[c] *= f[c];
+                            m_used[c] = m_new;
+                            any_need = true;
+                        }
+                    }
+                }
+                // P buffer b is free once the P·V two tiles back has completed.  This wait is taken for every use of the
+                // buffer, so its parity is exact; it also pins how far the tensor pipe can lag behind this warp.
+                if (!mbar_wait(&p_free[b], ((jg >> 1) & 1) ^ 1, abort_flag, p.status, kStatusEpilogueTimeout)) { ok = false; break; }
+                if (j > 0 && any_need) {
+                    // O may only be rescaled after the previous tile's P·V has landed: that is the next completion of the
+                    // other P buffer's barrier (a parity wait on a barrier polled only now and then could alias).
+                    if (!mbar_wait(&p_free[b ^ 1], ((jg - 1) >> 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    uint32_t o[NC];
+                    tmem_ld_n<NC>(o_addr, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * f[c]);
+                    tmem_st_n<NC>(o_addr, o);
+                    tmem_st_wait();
+                    tc_fence_before_sync();
+                }
+                // Pᵀ[c][token]: row c is 128 tokens = two 128-byte swizzled chunks of 64 tokens.  Dead columns hold the
+                // zeros written at start-up.
+                uint8_t* pbase = s_p + b * kPBytes + (r >> 6) * (kDecN * 128);
+                const int tl = r & 63;
+#pragma unroll
+                for (int c = 0; c < NC; ++c) {
+                    if (c < ncol) {
+                        const float mref = m_used[c] == -INFINITY ? 0.f : m_used[c];
+                        const float e = exp2f(s[c] - mref);
+                        l_part[c] += e;
+                        T* dst = reinterpret_cast<T*>(pbase + (c >> 3) * 1024 + (c & 7) * 128 + ((((tl >> 3) ^ (c & 7)) & 7) << 4) + (tl & 7) * 2);
+                        *dst = Cvt<T>::from_f(e);
+                    } else if (c < kDecN) {
+                        // a shorter sequence may follow a longer one in this CTA: clear columns it no longer uses
+                        T* dst = reinterpret_cast<T*>(pbase + (c >> 3) * 1024 + (c & 7) * 128 + ((((tl >> 3) ^ (c & 7)) & 7) << 4) + (tl & 7) * 2);
+                        *dst = Cvt<T>::from_f(0.f);
+                    }
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(&p_full[b]);
+                if (threadIdx.x == 64) trace_at(p, t_start, 2, jg, 2);     // probabilities published
             }
-            // Pᵀ[c][token]: row c is 128 tokens = two 128-byte swizzled chunks of 64 tokens.  Dead
-            // columns keep whatever the buffer holds; their outputs are never read.
-            uint8_t* pbase = s_p + b * kPBytes + (r >> 6) * (kDecN * 128);
-            const int tl = r & 63;
+            if (!ok) break;
+            // ---- item epilogue: column sums across the 128 threads, then O / l ----
+            named_barrier_sync(1, 128);
 #pragma unroll
             for (int c = 0; c < NC; ++c) {
-                if (c < ncol) {
-                    const float mref = m_used[c] == -INFINITY ? 0.f : m_used[c];
-                    const float e = exp2f(s[c] - mref);
-                    l_part[c] += e;
-                    T* dst = reinterpret_cast<T*>(pbase + (c >> 3) * 1024 + (c & 7) * 128 + ((((tl >> 3) ^ (c & 7)) & 7) << 4) + (tl & 7) * 2);
-                    *dst = Cvt<T>::from_f(e);
-                }
+                float v = l_part[c];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == c) s_sum[(warp - 2) * 16 + c] = v;
             }
-            fence_proxy_async_smem();
-            mbar_arrive(&p_full[b]);
-        }
-        // ---- epilogue: column sums across the 128 threads, then O / l ----
-        float* red = s_red;         // reuse: [4 warps][16]
-        named_barrier_sync(1, 128);
-#pragma unroll
-        for (int c = 0; c < NC; ++c) {
-            float v = l_part[c];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (lane == c) red[(warp - 2) * 16 + c] = v;
-        }
-        named_barrier_sync(1, 128);
-        // every PV has completed once the last tile's commit has: commits complete in issue order
-        if (ok && ntiles > 0)
-            ok = mbar_wait(&p_free[(ntiles - 1) & 1], ((ntiles - 1) >> 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout);
-        if (ok) {
-            tc_fence_after_sync();
+            named_barrier_sync(1, 128);
             uint32_t o[NC];
-            if (ntiles > 0) {
-                tmem_ld_n<NC>(lane_addr + 32, o);
+            if (it.ntiles > 0) {
+                if (!mbar_wait(&o_full[ig & 1], (ig >> 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout)) { ok = false; break; }
+                tc_fence_after_sync();
+                tmem_ld_n<NC>(o_addr, o);
                 tmem_ld_wait();
+                tc_fence_before_sync();
+                mbar_arrive(&o_free[ig & 1]);           // the accumulator may be overwritten by the item after next
             }
             if (r < D) {
 #pragma unroll
                 for (int c = 0; c < NC; ++c) {
                     if (c < ncol) {
-                        const float l = red[c] + red[16 + c] + red[32 + c] + red[48 + c];
-                        const float val = (ntiles > 0 && l > 0.f) ? __uint_as_float(o[c]) / l : 0.f;
+                        const float l = s_sum[c] + s_sum[16 + c] + s_sum[32 + c] + s_sum[48 + c];
+                        const float val = (it.ntiles > 0 && l > 0.f) ? __uint_as_float(o[c]) / l : 0.f;
                         const int qi = c >> gshift, g = c - (qi << gshift);
-                        const size_t tok = (size_t)qrow0 + qi;
-                        const int head = kvh * p.group + g;
+                        const size_t tok = (size_t)it.qrow0 + qi;
+                        const int head = it.kvh * p.group + g;
                         if (p.splits == 1) {
                             reinterpret_cast<T*>(p.out)[(tok * p.hq + head) * D + r] = Cvt<T>::from_f(val);
                         } else {
-                            p.ws_o[(((size_t)split * p.total_tokens + tok) * p.hq + head) * D + r] = val;
+                            p.ws_o[(((size_t)it.split * p.total_tokens + tok) * p.hq + head) * D + r] = val;
                             if (r == 0)
-                                p.ws_lse[((size_t)split * p.total_tokens + tok) * p.hq + head] =
-                                    (ntiles > 0 && l > 0.f) ? m_used[c] + log2f(l) : -INFINITY;
+                                p.ws_lse[((size_t)it.split * p.total_tokens + tok) * p.hq + head] =
+                                    (it.ntiles > 0 && l > 0.f) ? m_used[c] + log2f(l) : -INFINITY;
                         }
                     }
                 }
             }
-            tc_fence_before_sync();
+            if (it.ntiles > 0) ++ig;
         }
     }
 
@@ -378,14 +494,15 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
 template <int D, typename T, int KS, int VS, int MINB, int NC>
 static int launch_decode_variant(const CUtensorMap& tq, const CUtensorMap& tkv, const DecParams& p, int nseq, cudaStream_t stream) {
     constexpr int kv = (D / 64) * kDecTile * 128;
-    constexpr int smem = (KS + VS) * kv + 4096 + 2 * 2 * kDecN * 128 + 1024 + 1024;
+    constexpr int smem = (KS + VS) * kv + 2 * 4096 + 2 * 2 * kDecN * 128 + 1024 + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, T, KS, VS, MINB, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail("cudaFuncSetAttribute(attn_decode)", e);
         configured = true;
     }
-    dim3 grid(p.hkv, nseq * p.splits);
+    const int slots = MINB * sm_count();
+    const int grid = p.num_items < slots ? p.num_items : slots;
     TELB_LAUNCH("attn_decode_kernel", (attn_decode_kernel<D, T, KS, VS, MINB, NC>), dim3(grid), dim3(kDecThreads), smem, stream, tq, tkv, p);
     TELB_CHECK_LAUNCH("attn_decode_kernel");
     return 0;
@@ -397,7 +514,7 @@ template <int D, typename T, int NC>
 static int launch_decode_nc(const CUtensorMap& tq, const CUtensorMap& tkv, const DecParams& p, int nseq, cudaStream_t stream) {
     switch (g_decode_variant) {
         case 1: return launch_decode_variant<D, T, 1, 1, 2, NC>(tq, tkv, p, nseq, stream);     // 2 CTAs / SM, single-stage rings
-        case 2: return launch_decode_variant<D, T, 2, 1, 2, NC>(tq, tkv, p, nseq, stream);     // 2 CTAs / SM, K prefetched one tile ahead
+        case 2: return launch_decode_variant<D, T, 2, 2, 1, NC>(tq, tkv, p, nseq, stream);     // 1 CTA / SM, two-stage rings
         default: return launch_decode_variant<D, T, 3, 3, 1, NC>(tq, tkv, p, nseq, stream);    // 1 CTA / SM, three-stage rings
     }
 }
@@ -423,12 +540,31 @@ extern "C" int telb_set_decode_variant(int v) {
     return 0;
 }
 
+extern "C" int telb_paged_attention_decode_traced(const void* q, const void* kv_layer, void* out, const int* q_start,
+                                                  const int* q_len, const int* past_len, const int* page_table, int num_seqs,
+                                                  int total_tokens, int max_q_len, int num_pages, int max_pages, int page_size,
+                                                  int hq, int hkv, int d, float scale, int window, int splits, float* ws,
+                                                  long long ws_floats, int is_bf16, int* status, unsigned long long* trace,
+                                                  cudaStream_t stream);
+
 // Decode-shaped steps only: max_q_len * (Hq/Hkv) <= 16.  Same tensors as telb_paged_attention.
 extern "C" int telb_paged_attention_decode(const void* q, const void* kv_layer, void* out, const int* q_start,
                                            const int* q_len, const int* past_len, const int* page_table, int num_seqs,
                                            int total_tokens, int max_q_len, int num_pages, int max_pages, int page_size,
                                            int hq, int hkv, int d, float scale, int window, int splits, float* ws,
                                            long long ws_floats, int is_bf16, int* status, cudaStream_t stream) {
+    return telb_paged_attention_decode_traced(q, kv_layer, out, q_start, q_len, past_len, page_table, num_seqs, total_tokens, max_q_len,
+                                              num_pages, max_pages, page_size, hq, hkv, d, scale, window, splits, ws, ws_floats, is_bf16,
+                                              status, nullptr, stream);
+}
+
+// Same call with a timeline buffer (3 x 64 x 4 u64, zeroed by the caller) filled by the first CTA.
+extern "C" int telb_paged_attention_decode_traced(const void* q, const void* kv_layer, void* out, const int* q_start,
+                                                  const int* q_len, const int* past_len, const int* page_table, int num_seqs,
+                                                  int total_tokens, int max_q_len, int num_pages, int max_pages, int page_size,
+                                                  int hq, int hkv, int d, float scale, int window, int splits, float* ws,
+                                                  long long ws_floats, int is_bf16, int* status, unsigned long long* trace,
+                                                  cudaStream_t stream) {
     if (num_seqs <= 0 || total_tokens <= 0) return 0;
     if (d != 128) return fail("telb_paged_attention_decode: head_dim must be 128");
     if (page_size != 64 && page_size != 128) return fail("telb_paged_attention_decode: page size must be 64 or 128");
@@ -451,10 +587,13 @@ extern "C" int telb_paged_attention_decode(const void* q, const void* kv_layer, 
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = status;
+    p.trace = trace;
+    p.num_seqs = num_seqs;
     if (splits < 1) splits = 1;
     if (splits > 32) splits = 32;
     while (splits > 1 && (long long)splits * total_tokens * hq * (d + 1) > ws_floats) --splits;
     p.splits = splits;
+    p.num_items = num_seqs * hkv * splits;
     p.ws_o = ws;
     p.ws_lse = ws ? ws + (size_t)splits * total_tokens * hq * d : nullptr;
     const CUtensorMapDataType dt = is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;

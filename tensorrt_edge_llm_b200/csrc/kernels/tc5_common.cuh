@@ -26,6 +26,7 @@ enum : int {
 };
 
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s per wait, then give up
+constexpr long long kSpinLimitCycles = 4000000000ll;   // the same bound in SM cycles (about 2 s at 2 GHz, longer when clocks drop)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -74,12 +75,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           int* status, int code) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
+    // The SM cycle counter is a register read; the nanosecond timer is a slow memory-mapped one, so it is
+    // consulted only after the cheap bound has expired.
+    const long long c0 = clock64();
     for (uint32_t it = 0;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 63u) == 63u) {
             if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
+            if (clock64() - c0 > kSpinLimitCycles) {
                 *abort_flag = 1u;
                 if (status) atomicCAS(status, kStatusOk, code);
                 return false;

@@ -212,7 +212,7 @@ def _decode_splits(meta: StepMeta, hkv: int) -> int:
 
 
 def paged_attention(q, kv_layer, meta: StepMeta, scale, sliding_window=None, sinks=None, splits: Optional[int] = None,
-                    kernel: Optional[str] = None) -> torch.Tensor:
+                    kernel: Optional[str] = None, trace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Paged GQA attention.  Decode-shaped steps (``max_q_len * Hq/Hkv <= 16``, head_dim 128, causal)
     run the token-major XQA-style kernel; everything else the row-major tile kernel.
     ``kernel`` forces ``"decode"`` or ``"tile"``."""
@@ -232,11 +232,11 @@ def paged_attention(q, kv_layer, meta: StepMeta, scale, sliding_window=None, sin
             raise ValueError("step is not decode-shaped")
         if splits is None:
             splits = _decode_splits(meta, hkv)
-        _check(lib().telb_paged_attention_decode(
+        _check(lib().telb_paged_attention_decode_traced(
             _p(q), _p(kv_layer), _p(out), _p(meta.q_start), _p(meta.q_len), _p(meta.past_len), _p(meta.page_table),
             c_int(meta.num_seqs), c_int(t), c_int(meta.max_q_len), c_int(kv_layer.shape[0]), c_int(meta.page_table.shape[1]),
             c_int(meta.page_size), c_int(hq), c_int(hkv), c_int(d), c_float(scale), c_int(sliding_window or 0), c_int(splits),
-            _p(ws.attn_ws), c_ll(ws.attn_ws.numel()), c_int(_is_bf16(q)), _p(ws.status), _stream()),
+            _p(ws.attn_ws), c_ll(ws.attn_ws.numel()), c_int(_is_bf16(q)), _p(ws.status), _p(trace), _stream()),
             "paged_attention_decode", 2 if splits > 1 else 1)
         return out
     if splits is None:
