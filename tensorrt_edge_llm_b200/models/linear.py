@@ -251,7 +251,12 @@ class Int4AwqLinear(LinearBase):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         xs = (x.float() * self.pre_quant_scale.float()).to(x.dtype)
         if x.is_cuda:
-            return ops.cuda_ops().int4_awq_linear(xs, self.weight, self.weight_scale, self.group, self.bias)
+            # W4A16: the 4-bit groups are expanded to 16-bit once, when the layer first runs on the GPU, and the
+            # tcgen05 GEMM then streams 16-bit weights (B200 has the memory; decode pays 4x the weight bytes of a
+            # dequantise-in-kernel path, prefill is unaffected)
+            if self._dense is None or self._dense.device != x.device:
+                self._dense = self.dequantized_weight().to(x.dtype).contiguous()
+            return ops.linear(xs, self._dense, self.bias)
         y = xs.float() @ self.dequantized_weight().t()
         if self.bias is not None:
             y = y + self.bias.float()

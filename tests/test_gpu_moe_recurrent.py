@@ -229,3 +229,15 @@ def test_hybrid_model_gpu_matches_cpu():
     for x, y in zip(gpu, cpu):
         assert _rel_err(x, y) < 5e-2
         assert torch.equal(x.argmax(-1), y.argmax(-1)) or _rel_err(x, y) < 2e-2
+
+
+def test_int4_awq_linear_gpu(cu):
+    from tensorrt_edge_llm_b200.models.linear import Int4AwqLinear
+    g = torch.Generator().manual_seed(9)
+    lin = Int4AwqLinear(512, [384], group_size=128, dtype=torch.bfloat16)
+    lin.quantize_from([torch.randn(384, 512, generator=g) * 0.05])
+    x = torch.randn(70, 512, generator=g).bfloat16()
+    want = lin(x).float()
+    got = lin.cuda()(x.cuda()).float().cpu()
+    assert _rel_err(got, want) < 1e-2
+    _sync_check(cu)
