@@ -94,15 +94,22 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=64)
-    ap.add_argument("--input-len", type=int, default=1024)
-    ap.add_argument("--output-len", type=int, default=128)
+    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "hybrid", "eagle"],
+                    help="dense = the headline benchmark; the others are the secondary single-GPU configurations")
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--input-len", type=int, default=None)
+    ap.add_argument("--output-len", type=int, default=None)
     ap.add_argument("--dtype", default="nvfp4", choices=["nvfp4", "bf16", "fp16"])
-    ap.add_argument("--layers", type=int, default=36, help="debug only; anything but 36 is not the named config")
+    ap.add_argument("--layers", type=int, default=None, help="debug only; anything but the full depth is not the named config")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     args = ap.parse_args()
     if args.impl == "reference":
         return _reference_arm(args)
+    if args.workload != "dense":
+        from tensorrt_edge_llm_b200.benchmarks.workloads import main as workload_main
+        return workload_main(args)
+    args.batch, args.input_len, args.output_len = args.batch or 64, args.input_len or 1024, args.output_len or 128
+    args.layers = args.layers or 36
 
     import torch
     import torch.distributed as dist

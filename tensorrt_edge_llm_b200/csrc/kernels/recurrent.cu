@@ -126,6 +126,105 @@ ssm_scan_kernel(const T* __restrict__ x, const T* __restrict__ dt, const float* 
     for (int n = 0; n < N; n += 4) *reinterpret_cast<float4*>(st + n) = make_float4(hreg[n], hreg[n + 1], hreg[n + 2], hreg[n + 3]);
 }
 
+// ---- Mamba2 selective state, segmented for long prefill chunks -----------------------------------
+// The recurrence h_t = dA_t h_{t-1} + (dt_t x_t) ⊗ B_t is linear in h, so a long chunk is cut into segments of
+// `seg_len` tokens that run in parallel (grid.z):
+//   pass 1 (MODE 1): every segment starts from zero, and stores its local end state and the product of its dA;
+//   carry         : per (sequence, head), h_init[s+1] = h_init[s] * prod_s + local_s, sequentially over segments
+//                   (h_init[0] is the pooled state, or zero for a fresh sequence); the end state goes to the pool;
+//   pass 2 (MODE 2): every segment reruns from its true initial state and writes y.
+// Twice the arithmetic of the sequential walk, but (segments x heads x sequences) CTAs instead of (heads x sequences).
+template <typename T, int HD, int N, int MODE>
+__global__ void __launch_bounds__(HD)
+ssm_scan_seg_kernel(const T* __restrict__ x, const T* __restrict__ dt, const float* __restrict__ A, const T* __restrict__ B,
+                    const T* __restrict__ C, const float* __restrict__ D, const float* __restrict__ dt_bias, const T* __restrict__ z,
+                    float* __restrict__ seg_state, float* __restrict__ seg_decay, T* __restrict__ y, const int* __restrict__ q_start,
+                    const int* __restrict__ q_len, int nheads, int ngroups, int dt_softplus, float dt_limit, int seg_len,
+                    int max_segs) {
+    pdl_prologue();
+    __shared__ float sB[N], sC[N];
+    const int s = blockIdx.x, h = blockIdx.y, seg = blockIdx.z, p = threadIdx.x;
+    const int ql = q_len[s];
+    const int t0 = seg * seg_len;
+    if (t0 >= ql) return;
+    const int t1 = min(ql, t0 + seg_len);
+    const int g = h / (nheads / ngroups);
+    float* st = seg_state + ((((size_t)s * nheads + h) * max_segs + seg) * HD + p) * N;
+    float hreg[N];
+    if (MODE == 2) {
+#pragma unroll
+        for (int n = 0; n < N; n += 4) {
+            const float4 v = *reinterpret_cast<const float4*>(st + n);
+            hreg[n] = v.x; hreg[n + 1] = v.y; hreg[n + 2] = v.z; hreg[n + 3] = v.w;
+        }
+    } else {
+#pragma unroll
+        for (int n = 0; n < N; ++n) hreg[n] = 0.f;
+    }
+    const float a = A[h], dd = D[h], db = dt_bias[h];
+    float decay = 1.f;
+    for (int i = t0; i < t1; ++i) {
+        const size_t t = (size_t)q_start[s] + i;
+        __syncthreads();
+        for (int n = p; n < N; n += HD) {
+            sB[n] = Cvt<T>::to_f(B[(t * ngroups + g) * N + n]);
+            if (MODE == 2) sC[n] = Cvt<T>::to_f(C[(t * ngroups + g) * N + n]);
+        }
+        __syncthreads();
+        float d = Cvt<T>::to_f(dt[t * nheads + h]) + db;
+        if (dt_softplus) d = softplus_f(d);
+        if (dt_limit > 0.f) d = fminf(d, dt_limit);
+        const float dA = __expf(a * d);
+        decay *= dA;
+        const float xv = Cvt<T>::to_f(x[(t * nheads + h) * HD + p]);
+        const float dx = d * xv;
+        float acc = 0.f;
+#pragma unroll
+        for (int n = 0; n < N; ++n) {
+            hreg[n] = hreg[n] * dA + dx * sB[n];
+            if (MODE == 2) acc += hreg[n] * sC[n];
+        }
+        if (MODE == 2) {
+            acc += dd * xv;
+            if (z) acc *= silu_f(Cvt<T>::to_f(z[(t * nheads + h) * HD + p]));
+            y[(t * nheads + h) * HD + p] = Cvt<T>::from_f(acc);
+        }
+    }
+    if (MODE == 1) {
+#pragma unroll
+        for (int n = 0; n < N; n += 4) *reinterpret_cast<float4*>(st + n) = make_float4(hreg[n], hreg[n + 1], hreg[n + 2], hreg[n + 3]);
+        if (p == 0) seg_decay[((size_t)s * nheads + h) * max_segs + seg] = decay;
+    }
+}
+
+// grid (sequences, heads), HD * N / 4 elements per ... one thread per 4 state elements; walks the segments in order,
+// replacing each local end state by the segment's true initial state.
+template <int HD, int N>
+__global__ void ssm_carry_kernel(float* __restrict__ seg_state, const float* __restrict__ seg_decay, float* __restrict__ state,
+                                 const int* __restrict__ q_len, const int* __restrict__ past_len, const int* __restrict__ slot_ids,
+                                 int nheads, int seg_len, int max_segs) {
+    pdl_prologue();
+    const int s = blockIdx.x, h = blockIdx.y;
+    const int ql = q_len[s];
+    if (ql <= 0) return;
+    const int nseg = (ql + seg_len - 1) / seg_len;
+    float4* pool = reinterpret_cast<float4*>(state + ((size_t)slot_ids[s] * nheads + h) * HD * N);
+    float4* segs = reinterpret_cast<float4*>(seg_state + (((size_t)s * nheads + h) * max_segs) * HD * N);
+    const float* dec = seg_decay + ((size_t)s * nheads + h) * max_segs;
+    const bool fresh = past_len[s] <= 0;
+    for (int e = threadIdx.x; e < HD * N / 4; e += blockDim.x) {
+        float4 cur = fresh ? make_float4(0.f, 0.f, 0.f, 0.f) : pool[e];
+        for (int k = 0; k < nseg; ++k) {
+            float4* slot = segs + (size_t)k * (HD * N / 4) + e;
+            const float4 loc = *slot;
+            const float d = dec[k];
+            *slot = cur;                                   // the segment's initial state
+            cur = make_float4(cur.x * d + loc.x, cur.y * d + loc.y, cur.z * d + loc.z, cur.w * d + loc.w);
+        }
+        pool[e] = cur;
+    }
+}
+
 // ---- gated delta rule ------------------------------------------------------------------------------
 // One CTA per (sequence, value head), V threads: thread v owns state column H[0..K)[v] in registers.
 //   q̂ = q/‖q‖/√K, k̂ = k/‖k‖, g = exp(-exp(A_log) softplus(a + dt_bias)), β = σ(b)
@@ -201,6 +300,8 @@ gdn_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict
 
 using namespace telb;
 
+constexpr int kSsmSegLen = 128;     // tokens per parallel segment of a long Mamba2 prefill chunk
+
 extern "C" int telb_causal_conv1d(const void* x, const void* weight, const void* bias, void* conv_state, void* out,
                                   const int* seq_ids, const int* q_start, const int* q_len, const int* past_len,
                                   const int* slot_ids, int tokens, int num_seqs, int channels, int width, int activation,
@@ -227,9 +328,34 @@ extern "C" int telb_causal_conv1d(const void* x, const void* weight, const void*
 extern "C" int telb_ssm_scan(const void* x, const void* dt, const float* A, const void* B, const void* C, const float* D,
                              const float* dt_bias, const void* z, float* state, void* y, const int* q_start, const int* q_len,
                              const int* past_len, const int* slot_ids, int num_seqs, int nheads, int head_dim, int d_state,
-                             int ngroups, int dt_softplus, float dt_limit, int is_bf16, cudaStream_t stream) {
+                             int ngroups, int dt_softplus, float dt_limit, int is_bf16, int max_q_len, float* seg_scratch,
+                             long long seg_scratch_floats, cudaStream_t stream) {
     if (num_seqs <= 0) return 0;
     if (head_dim != 64 || d_state != 128) return fail("telb_ssm_scan: head_dim 64 and d_state 128 are the compiled shape");
+    if (seg_scratch && max_q_len >= 2 * kSsmSegLen) {
+        // long prefill chunk: three passes over parallel segments (see ssm_scan_seg_kernel)
+        const int max_segs = (max_q_len + kSsmSegLen - 1) / kSsmSegLen;
+        const long long need = (long long)num_seqs * nheads * max_segs * (64 * 128 + 1);
+        if (need <= seg_scratch_floats) {
+            float* seg_state = seg_scratch;
+            float* seg_decay = seg_scratch + (size_t)num_seqs * nheads * max_segs * 64 * 128;
+            const dim3 g3(num_seqs, nheads, max_segs), g2(num_seqs, nheads);
+#define TELB_SEG(T_)                                                                                                              \
+    do {                                                                                                                           \
+        TELB_LAUNCH("ssm_scan_seg_kernel", (ssm_scan_seg_kernel<T_, 64, 128, 1>), g3, dim3(64), 0, stream, (const T_*)x, (const T_*)dt, A, \
+                    (const T_*)B, (const T_*)C, D, dt_bias, (const T_*)z, seg_state, seg_decay, (T_*)y, q_start, q_len, nheads, ngroups,   \
+                    dt_softplus, dt_limit, kSsmSegLen, max_segs);                                                                  \
+        TELB_LAUNCH("ssm_carry_kernel", (ssm_carry_kernel<64, 128>), g2, dim3(256), 0, stream, seg_state, (const float*)seg_decay, state,  \
+                    q_len, past_len, slot_ids, nheads, kSsmSegLen, max_segs);                                                      \
+        TELB_LAUNCH("ssm_scan_seg_kernel", (ssm_scan_seg_kernel<T_, 64, 128, 2>), g3, dim3(64), 0, stream, (const T_*)x, (const T_*)dt, A, \
+                    (const T_*)B, (const T_*)C, D, dt_bias, (const T_*)z, seg_state, seg_decay, (T_*)y, q_start, q_len, nheads, ngroups,   \
+                    dt_softplus, dt_limit, kSsmSegLen, max_segs);                                                                  \
+    } while (0)
+            if (is_bf16) TELB_SEG(__nv_bfloat16); else TELB_SEG(__half);
+#undef TELB_SEG
+            return 0;
+        }
+    }
     const dim3 grid(num_seqs, nheads);
     if (is_bf16)
         TELB_LAUNCH("ssm_scan_kernel", (ssm_scan_kernel<__nv_bfloat16, 64, 128>), grid, dim3(64), 0, stream, (const __nv_bfloat16*)x,

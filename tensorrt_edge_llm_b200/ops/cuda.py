@@ -539,16 +539,27 @@ def causal_conv1d(x, weight, bias, conv_state, meta: StepMeta, activation=True):
     return out
 
 
+_SSM_SCRATCH = {}
+
+
 def ssm_scan(x, dt, A, B, C, D, dt_bias, ssm_state, meta: StepMeta, z=None, dt_softplus=True, dt_limit=0.0):
     x, dt, B, C = x.contiguous(), dt.contiguous(), B.contiguous(), C.contiguous()
     t, nh, hd = x.shape
     y = torch.empty_like(x)
     assert ssm_state.dtype == torch.float32 and ssm_state.is_contiguous()
+    scratch = None
+    if meta.max_q_len >= 256:       # long prefill chunk: parallel segments need per-segment states (see recurrent.cu)
+        segs = (meta.max_q_len + 127) // 128
+        need = meta.num_seqs * nh * segs * (hd * B.shape[-1] + 1)
+        scratch = _SSM_SCRATCH.get(x.device)
+        if scratch is None or scratch.numel() < need:
+            scratch = _SSM_SCRATCH[x.device] = torch.empty(need, dtype=torch.float32, device=x.device)
     _check(lib().telb_ssm_scan(_p(x), _p(dt), _p(A.float().contiguous()), _p(B), _p(C), _p(D.float().contiguous()),
                                _p(dt_bias.float().contiguous()), _p(z.contiguous() if z is not None else None), _p(ssm_state), _p(y),
                                _p(meta.q_start), _p(meta.q_len), _p(meta.past_len), _p(meta.slot_ids), c_int(meta.num_seqs),
                                c_int(nh), c_int(hd), c_int(B.shape[-1]), c_int(B.shape[1]), c_int(int(dt_softplus)),
-                               c_float(dt_limit), c_int(_is_bf16(x)), _stream()), "ssm_scan")
+                               c_float(dt_limit), c_int(_is_bf16(x)), c_int(meta.max_q_len), _p(scratch),
+                               c_ll(scratch.numel() if scratch is not None else 0), _stream()), "ssm_scan", 3 if scratch is not None else 1)
     return y
 
 

@@ -39,8 +39,10 @@ class ModelRunner:
         self.model = model
         self.kv = kv
         self.device = torch.device(device) if device is not None else kv.pool.device
-        if self.device != kv.pool.device:
-            raise ValueError(f"runner device {self.device} differs from the KV pool's device {kv.pool.device}")
+        pool_dev = kv.pool.device
+        if self.device.type != pool_dev.type or (self.device.index or 0) != (pool_dev.index or 0):
+            raise ValueError(f"runner device {self.device} differs from the KV pool's device {pool_dev}")
+        self.device = pool_dev
         self.max_num_tokens = max_num_tokens
         self._graphs: Dict[int, "_DecodeGraph"] = {}
         self.use_cuda_graphs = self.device.type == "cuda"

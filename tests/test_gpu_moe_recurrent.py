@@ -126,7 +126,7 @@ def test_causal_conv1d(cu, q_lens, pasts):
     _sync_check(cu)
 
 
-@pytest.mark.parametrize("q_lens,pasts", [([1, 1], [7, 0]), ([20, 1, 5], [0, 3, 16])])
+@pytest.mark.parametrize("q_lens,pasts", [([1, 1], [7, 0]), ([20, 1, 5], [0, 3, 16]), ([300, 1, 517], [0, 9, 40]), ([256], [0])])
 def test_ssm_scan(cu, q_lens, pasts):
     g = torch.Generator(device="cuda").manual_seed(6)
     nh, hd, ng, n = 8, 64, 2, 128
