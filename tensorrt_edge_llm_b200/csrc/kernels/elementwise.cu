@@ -84,6 +84,53 @@ __global__ void rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ re
     }
 }
 
+// LayerNorm: y = (x - mean) / sqrt(var + eps) * w (+ b).  One CTA per row, two passes over registers.
+template <typename T, int kMaxVec>
+__global__ void layernorm_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b, T* __restrict__ y,
+                                 int hidden, float eps) {
+    pdl_prologue();
+    __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    const int nvec = hidden / 8;
+    Vec8<T> v[kMaxVec];
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+        const int idx = threadIdx.x + i * blockDim.x;
+        if (idx < nvec) {
+            v[i].load(x + row * hidden + idx * 8);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum += v[i].get(j);
+        }
+    }
+    const float mean = block_sum(sum, red) / hidden;
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+        const int idx = threadIdx.x + i * blockDim.x;
+        if (idx < nvec) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float d = v[i].get(j) - mean;
+                ss += d * d;
+            }
+        }
+    }
+    const float inv = rsqrtf(block_sum(ss, red) / hidden + eps);
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+        const int idx = threadIdx.x + i * blockDim.x;
+        if (idx < nvec) {
+            Vec8<T> wv, bv, o;
+            wv.load(w + idx * 8);
+            if (b) bv.load(b + idx * 8);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o.set(j, (v[i].get(j) - mean) * inv * wv.get(j) + (b ? bv.get(j) : 0.f));
+            o.store(y + row * hidden + idx * 8);
+        }
+    }
+}
+
 // Mamba2 output norm: g = x * silu(z); RMS-normalise each group of `gsize` features; scale.
 // One CTA per (row, group).
 template <typename T>
@@ -411,6 +458,25 @@ extern "C" int telb_rmsnorm(const void* x, const void* residual, const void* w, 
         else TELB_LAUNCH("rmsnorm_kernel", (rmsnorm_kernel<T, 8>), dim3(rows), dim3(threads), 0, stream, (const T*)x, (const T*)residual, (const T*)w, (T*)y, (T*)res_out, hidden, eps);
     })
     TELB_CHECK_LAUNCH("rmsnorm_kernel");
+    return 0;
+}
+
+extern "C" int telb_layernorm(const void* x, const void* w, const void* b, void* y, long long rows, int hidden, float eps,
+                              int is_bf16, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden % 8) return fail("telb_layernorm: hidden must be a multiple of 8");
+    const int nvec = hidden / 8;
+    int threads = nvec >= 512 ? 512 : ((nvec + 31) / 32) * 32;
+    if (threads < 32) threads = 32;
+    const int per = (nvec + threads - 1) / threads;
+    if (per > 8) return fail("telb_layernorm: hidden too large (max 32768)");
+    DISPATCH_T(is_bf16, {
+        if (per <= 1) TELB_LAUNCH("layernorm_kernel", (layernorm_kernel<T, 1>), dim3(rows), dim3(threads), 0, stream, (const T*)x, (const T*)w, (const T*)b, (T*)y, hidden, eps);
+        else if (per <= 2) TELB_LAUNCH("layernorm_kernel", (layernorm_kernel<T, 2>), dim3(rows), dim3(threads), 0, stream, (const T*)x, (const T*)w, (const T*)b, (T*)y, hidden, eps);
+        else if (per <= 4) TELB_LAUNCH("layernorm_kernel", (layernorm_kernel<T, 4>), dim3(rows), dim3(threads), 0, stream, (const T*)x, (const T*)w, (const T*)b, (T*)y, hidden, eps);
+        else TELB_LAUNCH("layernorm_kernel", (layernorm_kernel<T, 8>), dim3(rows), dim3(threads), 0, stream, (const T*)x, (const T*)w, (const T*)b, (T*)y, hidden, eps);
+    })
+    TELB_CHECK_LAUNCH("layernorm_kernel");
     return 0;
 }
 

@@ -1,0 +1,129 @@
+"""LoRA adapters at run time: named adapters attached to a model's linear layers, switched in O(1).
+
+``y = W x + B (A x)`` with ``A [r, in]`` and ``B [out, r]`` (``alpha / r`` folded into B by
+``process_lora_weights``).  The low-rank pair runs as two small GEMMs; the second one adds the base
+projection's output in its epilogue (``residual``), so an adapted layer costs no extra elementwise pass.
+Fused layers (q/k/v, gate/up) take one adapter per source projection: A matrices are stacked, and each B
+writes its own column block.
+
+Parity: ``cpp/runtime/state/loraManager.{h,cpp}`` (named adapters, O(1) switch by rebinding ``lora_A_*`` /
+``lora_B_*`` tensors; ``docs/source/user_guide/features/lora.md:15-52``)."""
+from __future__ import annotations
+
+import json
+import os
+from typing import Dict, List, Optional, Tuple
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..checkpoint.safetensors_io import SafetensorsFile
+from ..models.linear import LinearBase, TPMode
+
+
+class _Adapted:
+    """Low-rank weights of one linear layer for one adapter: per source, (A [r, in], B [out_src, r], column offset)."""
+
+    def __init__(self):
+        self.parts: List[Tuple[torch.Tensor, torch.Tensor, int]] = []
+
+
+class LoraLinear(nn.Module):
+    """Wraps a linear layer; adds the active adapter's low-rank update to its output."""
+
+    def __init__(self, base: LinearBase):
+        super().__init__()
+        self.base = base
+        self.adapters: Dict[str, _Adapted] = {}
+        self.active: Optional[_Adapted] = None
+
+    def __getattr__(self, name):            # the model reads attributes such as fused_input_scale, tp_mode, weight
+        try:
+            return super().__getattr__(name)
+        except AttributeError:
+            return getattr(super().__getattr__("base"), name)
+
+    def forward(self, x):
+        y = self.base(x)
+        ad = self.active
+        if ad is None or not isinstance(y, torch.Tensor):
+            return y
+        x16 = x if isinstance(x, torch.Tensor) else None
+        if x16 is None:
+            raise RuntimeError("LoRA needs 16-bit activations: disable fused activation quantisation for adapted layers")
+        for a, b, col in ad.parts:
+            t = ops.linear(x16, a)                                        # [T, r]
+            n = b.shape[0]
+            if col == 0 and n == y.shape[-1]:
+                y = y + ops.linear(t, b) if not y.is_cuda else ops.cuda_ops().gemm(t, b, residual=y)
+            else:
+                y[..., col:col + n] += ops.linear(t, b)
+        return y
+
+
+class LoraManager:
+    """Loads processed adapters (``lora_weights.safetensors`` + ``lora_config.json``) and binds them to a model."""
+
+    def __init__(self, model: nn.Module):
+        self.model = model
+        self.names: List[str] = []
+        self.active: Optional[str] = None
+        self._wrapped: Dict[str, LoraLinear] = {}
+
+    def _wrap(self, module_name: str) -> LoraLinear:
+        if module_name in self._wrapped:
+            return self._wrapped[module_name]
+        parent_name, _, leaf = module_name.rpartition(".")
+        parent = self.model.get_submodule(parent_name) if parent_name else self.model
+        base = getattr(parent, leaf)
+        if not isinstance(base, LinearBase):
+            raise TypeError(f"{module_name} is not a linear layer")
+        w = LoraLinear(base)
+        setattr(parent, leaf, w)
+        self._wrapped[module_name] = w
+        return w
+
+    def _locate(self, ckpt_module: str) -> Tuple[str, int, LinearBase]:
+        """Runtime module, source index of a checkpoint module name (``…self_attn.q_proj`` → ``…self_attn.qkv_proj``, 0)."""
+        name = ckpt_module
+        for pre in ("base_model.model.",):
+            if name.startswith(pre):
+                name = name[len(pre):]
+        parent, _, leaf = name.rpartition(".")
+        for mod_name, mod in self.model.named_modules():
+            base = mod.base if isinstance(mod, LoraLinear) else mod
+            if not isinstance(base, LinearBase):
+                continue
+            p2, _, l2 = mod_name.rpartition(".")
+            if p2 != parent and not parent.endswith(p2) and not p2.endswith(parent):
+                continue
+            srcs = base.sources or [l2]
+            if leaf in srcs and (p2 == parent or p2.endswith(parent) or parent.endswith(p2)):
+                return mod_name, srcs.index(leaf), base
+        raise KeyError(f"adapter module {ckpt_module} has no counterpart in the model")
+
+    def load_adapter(self, name: str, adapter_dir: str) -> None:
+        f = SafetensorsFile(os.path.join(adapter_dir, "lora_weights.safetensors"))
+        with open(os.path.join(adapter_dir, "lora_config.json"), "r", encoding="utf-8") as fh:
+            meta = json.load(fh)
+        for ckpt_mod in meta["modules"]:
+            mod_name, src, base = self._locate(ckpt_mod)
+            a, b = f.get(f"lora_A_{ckpt_mod}").clone(), f.get(f"lora_B_{ckpt_mod}").clone()
+            dev, dt = base.weight.device, getattr(base, "act_dtype", None) or (base.weight.dtype if base.weight.dtype.is_floating_point else torch.bfloat16)
+            if base.tp_mode == TPMode.COL and base.tp_size > 1:
+                b = b.chunk(base.tp_size, 0)[base.tp_rank]
+            elif base.tp_mode == TPMode.ROW and base.tp_size > 1:
+                a = a.chunk(base.tp_size, 1)[base.tp_rank]
+            col = sum(base.out_sizes[:src])
+            w = self._wrap(mod_name)
+            w.adapters.setdefault(name, _Adapted()).parts.append((a.to(dev, dt).contiguous(), b.to(dev, dt).contiguous(), col))
+        if name not in self.names:
+            self.names.append(name)
+
+    def set_active(self, name: Optional[str]) -> None:
+        if name is not None and name not in self.names:
+            raise KeyError(f"unknown adapter {name!r}; loaded: {self.names}")
+        for w in self._wrapped.values():
+            w.active = w.adapters.get(name) if name is not None else None
+        self.active = name

@@ -47,6 +47,12 @@ def rmsnorm_maybe_quant(x, weight, eps, quant_scale=None):
     return rmsnorm(x, weight, eps)
 
 
+def layernorm(x, weight, bias, eps):
+    if x.is_cuda:
+        return cuda_ops().layernorm(x, weight, bias, eps)
+    return ref.layernorm(x, weight, bias, eps)
+
+
 def gated_group_rmsnorm(x, z, weight, n_groups, eps):
     if x.is_cuda:
         return cuda_ops().gated_group_rmsnorm(x, z, weight, n_groups, eps)

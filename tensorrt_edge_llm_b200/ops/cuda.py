@@ -124,6 +124,15 @@ def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, e
     return y, res
 
 
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    rows = x.numel() // x.shape[-1]
+    _check(lib().telb_layernorm(_p(x), _p(weight), _p(bias), _p(y), c_ll(rows), c_int(x.shape[-1]), c_float(eps), c_int(_is_bf16(x)),
+                                _stream()), "layernorm")
+    return y
+
+
 def gated_group_rmsnorm(x, z, weight, n_groups, eps):
     x, z = x.contiguous(), z.contiguous()
     y = torch.empty_like(x)

@@ -241,3 +241,14 @@ def test_int4_awq_linear_gpu(cu):
     got = lin.cuda()(x.cuda()).float().cpu()
     assert _rel_err(got, want) < 1e-2
     _sync_check(cu)
+
+
+@pytest.mark.parametrize("rows,hidden", [(5, 1024), (33, 1152), (2, 8192)])
+def test_layernorm(cu, rows, hidden):
+    g = torch.Generator(device="cuda").manual_seed(10)
+    x = (torch.randn(rows, hidden, device="cuda", generator=g) * 2 + 0.5).bfloat16()
+    w = (1 + 0.1 * torch.randn(hidden, device="cuda", generator=g)).bfloat16()
+    b = (0.1 * torch.randn(hidden, device="cuda", generator=g)).bfloat16()
+    assert _rel_err(cu.layernorm(x, w, b, 1e-5), ref.layernorm(x, w, b, 1e-5)) < 4e-3
+    assert _rel_err(cu.layernorm(x, w, None, 1e-5), ref.layernorm(x, w, None, 1e-5)) < 4e-3
+    _sync_check(cu)

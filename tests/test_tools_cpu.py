@@ -96,6 +96,32 @@ def test_lora_process_and_merge(ckpt, tmp_path):
     assert not torch.allclose(_logits(ckpt, [3, 4, 5]), _logits(merged, [3, 4, 5]))
 
 
+def test_lora_runtime_adapter_equals_merged_checkpoint(ckpt, tmp_path):
+    from tensorrt_edge_llm_b200.lora import LoraManager
+    ad, rt_dir, merged = str(tmp_path / "adapter"), str(tmp_path / "rt"), str(tmp_path / "merged")
+    _adapter(ad)
+    assert trtedge(["process-lora", "--input_dir", ad, "--output_dir", rt_dir, "--dtype", "bfloat16"]) == 0
+    assert trtedge(["merge-lora", "--model_dir", ckpt, "--lora_dir", ad, "--output_dir", merged]) == 0
+    ids = list(range(5, 40))
+    model = AutoModel.from_pretrained(ckpt)
+    mgr = LoraManager(model)
+    mgr.load_adapter("style", rt_dir)
+    kv = KVCacheManager(model.cfg, num_pages=8, page_size=16, max_seats=2, max_pages_per_seq=4)
+    r = ModelRunner(model, kv)
+    base = r.prefill([0], [ids]).float()
+    kv.free(0)
+    mgr.set_active("style")
+    adapted = r.prefill([0], [ids]).float()
+    kv.free(0)
+    mgr.set_active(None)
+    again = r.prefill([0], [ids]).float()
+    want = _logits(merged, ids)
+    assert torch.allclose(base, again) and not torch.allclose(base, adapted, atol=1e-4)
+    assert (adapted - want).abs().max() < 2e-2 * want.abs().max()          # adapter weights are stored in bf16
+    with pytest.raises(KeyError):
+        mgr.set_active("missing")
+
+
 def test_reduce_vocab(ckpt, tmp_path):
     corpus = str(tmp_path / "ids.json")
     json.dump([[7, 7, 7, 9, 9, 400], [9, 400, 400, 400, 11]], open(corpus, "w"))
