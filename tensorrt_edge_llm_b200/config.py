@@ -244,8 +244,10 @@ class ModelConfig:
         """Copy of this config placed on ``rank`` of ``world`` (TP, or EP when ``ep``)."""
         cfg = dataclasses.replace(self)
         cfg.quant = dataclasses.replace(self.quant)
-        if ep:
-            cfg.mapping = Mapping(tp_size=1, tp_rank=0, ep_size=world, ep_rank=rank)
+        if ep:      # attention and dense projections tensor-parallel, experts sharded by expert id
+            if self.num_attention_heads % world or self.num_experts % world:
+                raise ValueError(f"{self.num_attention_heads} heads / {self.num_experts} experts not divisible by {world} ranks")
+            cfg.mapping = Mapping(tp_size=world, tp_rank=rank, ep_size=world, ep_rank=rank)
         else:
             if self.num_attention_heads % world:
                 raise ValueError(f"{self.num_attention_heads} heads not divisible by TP {world}")

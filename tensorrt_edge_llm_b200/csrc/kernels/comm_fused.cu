@@ -245,6 +245,9 @@ struct RsAgParams {
     uint8_t* gather_sf[kMaxRanks];
     const float* quant_scale;
     int rank, world, rows, rows_per_rank, hidden, k64_pad, wait_gather;
+    // partial slots summed: [slot_base, slot_base + sum_slots).  A single local slot (an expert-parallel MoE block already
+    // delivered complete rows for this rank's tokens) needs no "GEMM finished" handshake.
+    int sum_slots, slot_base;
     float eps;
     int* status;
 };
@@ -277,7 +280,7 @@ __global__ void rs_add_rmsnorm_ag_kernel(RsAgParams p) {
     if (blockIdx.x == 0 && threadIdx.x < p.world) st_release_sys(p.gemm_flags[threadIdx.x] + p.rank, e);
     if (threadIdx.x == 0) s_ok = 1;
     __syncthreads();
-    if (has_row && threadIdx.x < p.world && threadIdx.x != p.rank) {
+    if (has_row && p.sum_slots > 1 && threadIdx.x < p.world && threadIdx.x != p.rank) {
         if (!wait_flag_ge(p.gemm_flags[p.rank] + threadIdx.x, e, p.status)) s_ok = 0;
     }
     __syncthreads();
@@ -291,7 +294,7 @@ __global__ void rs_add_rmsnorm_ag_kernel(RsAgParams p) {
             if (idx < nunits) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) v[u][i] = 0.f;
-                for (int r = 0; r < p.world; ++r) {
+                for (int r = p.slot_base; r < p.slot_base + p.sum_slots; ++r) {
                     const T* src = reinterpret_cast<const T*>(p.partial) + ((size_t)r * p.rows_per_rank + row) * p.hidden + idx * 16;
                     const uint4 a0 = __ldcg(reinterpret_cast<const uint4*>(src)), a1 = __ldcg(reinterpret_cast<const uint4*>(src) + 1);
                     const T* e0 = reinterpret_cast<const T*>(&a0);
@@ -475,9 +478,15 @@ extern "C" int telb_rs_add_rmsnorm_ag(const void* partial, int* const* gemm_flag
                                       const void* residual, int residual_full, const void* weight, void* res_out,
                                       void* const* gather_y, void* const* gather_xq, void* const* gather_sf,
                                       const float* quant_scale, int rank, int world, int rows, int rows_per_rank, int hidden,
-                                      float eps, int wait_gather, int is_bf16, int* status, cudaStream_t stream) {
+                                      float eps, int wait_gather, int is_bf16, int* status, int sum_slots, int slot_base,
+                                      cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (world < 1 || world > kMaxRanks) return fail("telb_rs_add_rmsnorm_ag: world size must be in [1, 8]");
+    if (sum_slots <= 0) {
+        sum_slots = world;
+        slot_base = 0;
+    }
+    if (slot_base < 0 || slot_base + sum_slots > world) return fail("telb_rs_add_rmsnorm_ag: partial slot range outside [0, world)");
     if (hidden % 16) return fail("telb_rs_add_rmsnorm_ag: hidden must be a multiple of 16");
     if (rows_per_rank * world < rows) return fail("telb_rs_add_rmsnorm_ag: rows_per_rank * world must cover the rows");
     if (!gather_y && !gather_xq) return fail("telb_rs_add_rmsnorm_ag: no output buffer");
@@ -506,6 +515,8 @@ extern "C" int telb_rs_add_rmsnorm_ag(const void* partial, int* const* gemm_flag
     p.hidden = hidden;
     p.k64_pad = telb_nvfp4_k64_pad(hidden);
     p.wait_gather = wait_gather;
+    p.sum_slots = sum_slots;
+    p.slot_base = slot_base;
     p.eps = eps;
     p.status = status;
     int rows_local = rows - rank * rows_per_rank;

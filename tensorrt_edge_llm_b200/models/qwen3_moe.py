@@ -162,9 +162,13 @@ class MoEBlock(nn.Module):
             return w13.view(e, 2 * i, h), w2.view(e, h, i)
         return self.w13.view(e, 2 * i, h), self.w2.view(e, h, i)
 
+    ep_comm = None      # a communicator with `moe_all_to_all` (set by the model when experts are sharded over ranks)
+
     def forward(self, x):
         if isinstance(x, torch.Tensor) and not x.is_cuda:
             return self._forward_reference(x)
+        if self.ep_comm is not None and self.ep_size > 1 and self.ep_comm.use_rs(x.shape[0]):
+            return self.ep_comm.moe_all_to_all(self, x)       # prefill: token-sharded all-to-all over peer memory
         cu = ops.cuda_ops()
         xa = x            # the router always sees 16-bit activations
         logits = self.gate(xa)
@@ -241,3 +245,12 @@ class MoETransformer(Transformer):
 @register_model("qwen3_moe", "qwen2_moe", "mixtral")
 class MoECausalLM(CausalLM):
     transformer_cls = MoETransformer
+
+    def __init__(self, cfg: ModelConfig, comm=None):
+        super().__init__(cfg, comm)
+        if cfg.mapping.ep_size > 1 and hasattr(self.comm, "moe_all_to_all"):
+            # Prefill-size steps keep the residual stream token-sharded: the attention output leaves through the
+            # reduce-scatter epilogue and the experts exchange token rows all-to-all (see FusedComm).
+            for layer in self.model.layers:
+                layer.self_attn.o_proj.rs_comm = self.comm
+                layer.mlp.ep_comm = self.comm

@@ -525,9 +525,11 @@ def gemm_grouped(x, weight, ws: MoeWorkspace, experts_local: int, alpha=None, bi
     return out
 
 
-def moe_combine(y: torch.Tensor, ws: MoeWorkspace, topk_w: torch.Tensor) -> torch.Tensor:
+def moe_combine(y: torch.Tensor, ws, topk_w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[t] = Σ_k w[t,k] · y[ws.dst_row[t*K + k]]`` (slots with a negative row contribute nothing)."""
     t, k = topk_w.shape
-    out = torch.empty(t, y.shape[1], dtype=y.dtype, device=y.device)
+    if out is None:
+        out = torch.empty(t, y.shape[1], dtype=y.dtype, device=y.device)
     _check(lib().telb_moe_combine(_p(y), _p(ws.dst_row), _p(topk_w), _p(out), c_int(t), c_int(k), c_int(y.shape[1]),
                                   c_int(_is_bf16(y)), _stream()), "moe_combine")
     return out

@@ -26,11 +26,13 @@ class RsPartial:
     """Marker for a row-parallel projection whose partial rows were stored into their owners'
     symmetric buffers by the GEMM epilogue; only ``add_rmsnorm`` can consume it."""
 
-    __slots__ = ("rows", "hidden", "dtype", "rows_per_rank")
+    __slots__ = ("rows", "hidden", "dtype", "rows_per_rank", "sum_slots", "slot_base")
     is_cuda = True
 
-    def __init__(self, rows, hidden, dtype, rows_per_rank):
+    def __init__(self, rows, hidden, dtype, rows_per_rank, sum_slots=0, slot_base=0):
         self.rows, self.hidden, self.dtype, self.rows_per_rank = rows, hidden, dtype, rows_per_rank
+        # 0 = every rank's slot holds a partial sum; (1, rank) = this rank's slot already holds complete rows
+        self.sum_slots, self.slot_base = sum_slots, slot_base
 
     @property
     def shape(self):
@@ -72,6 +74,39 @@ class _RsState:
         dist.barrier(group)
 
 
+class _EpState:
+    """Symmetric buffers of the expert-parallel all-to-all for one (hidden, dtype, top_k)."""
+
+    def __init__(self, device, hidden: int, dtype: torch.dtype, group, tokens_local_cap: int, top_k: int):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        gname = group.group_name if group is not None else dist.group.WORLD.group_name
+        world = dist.get_world_size(group)
+        self.slots_cap = tokens_local_cap * top_k
+        self.recv_rows = symm_mem.empty(world * self.slots_cap * hidden, dtype=dtype, device=device)
+        self.recv_ids = symm_mem.empty(world * self.slots_cap, dtype=torch.int32, device=device)
+        self.comb_rows = symm_mem.empty(self.slots_cap * hidden, dtype=dtype, device=device)
+        self.flags = symm_mem.empty(16, dtype=torch.int32, device=device)
+        self.recv_ids.fill_(-1)
+        self.flags.zero_()
+        hs = {n: symm_mem.rendezvous(getattr(self, n), gname) for n in ("recv_rows", "recv_ids", "comb_rows", "flags")}
+        self._handles = hs
+        self.c = {n: (ctypes.c_void_p * world)(*[int(p) for p in hs[n].buffer_ptrs]) for n in hs}
+        self.epoch = torch.zeros(2, dtype=torch.int32, device=device)        # dispatch, return
+        self.ticket = torch.zeros(2, dtype=torch.int32, device=device)
+        self.arange = torch.arange(self.slots_cap, dtype=torch.int32, device=device)
+        self.prev_slots = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+
+class _Rows:
+    """Minimal stand-in for a routing workspace: slot s reads row s."""
+
+    def __init__(self, dst_row):
+        self.dst_row = dst_row
+
+
 class _SymState:
     def __init__(self, device, hidden: int, dtype: torch.dtype, group):
         import torch.distributed as dist
@@ -98,6 +133,7 @@ class FusedComm(TorchComm):
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         self._sym: Dict[Tuple[int, torch.dtype], _SymState] = {}
         self._rs: Dict[Tuple[int, torch.dtype], _RsState] = {}
+        self._ep: Dict[Tuple[int, torch.dtype, int], _EpState] = {}
         self.rs_max_tokens = rs_max_tokens
         self.rs_min_rows = rs_min_rows          # below this the one-shot all-reduce is faster
         self.rs_enabled = True
@@ -148,6 +184,66 @@ class FusedComm(TorchComm):
             cu.gemm_fused(x.reshape(-1, x.shape[-1]).contiguous(), linear.weight, f, bias=linear.bias)
         return RsPartial(rows, linear.out_features, dtype, rpr)
 
+    # ---- expert parallelism: all-to-all dispatch → grouped expert GEMMs → all-to-all return → weighted combine ----
+    def _ep_state(self, hidden: int, dtype: torch.dtype, top_k: int) -> _EpState:
+        key = (hidden, dtype, top_k)
+        st = self._ep.get(key)
+        if st is None:
+            cap = (self.rs_max_tokens + self.world_size - 1) // self.world_size
+            st = self._ep[key] = _EpState(self.device, hidden, dtype, self.group, cap, top_k)
+        return st
+
+    def moe_all_to_all(self, block, x: torch.Tensor) -> RsPartial:
+        """Expert-parallel MoE over token shards.  ``x`` holds all rows (gathered); this rank routes its own
+        shard, ships every (token, k) row to the rank that owns the expert (peer stores), runs its local experts on
+        what it received, ships the results back and reduces its tokens' top-k rows with the router weights.
+        The result is this rank's complete rows, handed to ``add_rmsnorm`` as an already-reduced shard."""
+        cu = ops.cuda_ops()
+        rows, hidden = x.shape
+        world, rank = self.world_size, self.rank
+        rpr = (rows + world - 1) // world
+        lo, hi = min(rows, rank * rpr), min(rows, (rank + 1) * rpr)
+        t_local = hi - lo
+        st = self._ep_state(hidden, x.dtype, block.top_k)
+        rs = self._rs_state(hidden, x.dtype)
+        ws0 = cu.Workspace.get(self.device)
+        xs = x[lo:hi].contiguous()
+        logits = block.gate(xs)
+        w, idx = cu.moe_route_softmax_topk(logits, block.top_k, block.cfg.norm_topk_prob)
+        epr = block.num_experts // world
+        c = st.c
+        cu._check(cu.lib().telb_ep_dispatch(cu._p(xs), cu._p(idx), c["recv_rows"], c["recv_ids"], c["comb_rows"], c["flags"], ctypes.c_int(rank),
+                                            ctypes.c_int(world), ctypes.c_int(t_local), ctypes.c_int(block.top_k), ctypes.c_int(hidden),
+                                            ctypes.c_int(epr), ctypes.c_int(st.slots_cap), ctypes.c_int(st.prev_slots),
+                                            ctypes.c_void_p(st.epoch.data_ptr()), ctypes.c_void_p(st.ticket.data_ptr()), cu._stream()),
+                  "ep_dispatch")
+        st.prev_slots = t_local * block.top_k
+        cu._check(cu.lib().telb_ep_wait(cu._p(st.flags), ctypes.c_int(0), ctypes.c_int(world), ctypes.c_void_p(st.epoch.data_ptr()),
+                                        cu._p(ws0.status), cu._stream()), "ep_wait")
+        n_recv = world * st.slots_cap
+        ws = cu.moe_align(st.recv_ids.view(n_recv, 1), block.e_local, 0, block.e_local)
+        recv = st.recv_rows.view(n_recv, hidden)
+        if block.nvfp4:
+            if block._w13_sf is None:
+                block.finalize()
+            a = cu.moe_gather(recv, ws, 1, block.input_scale)
+            h1 = cu.gemm_grouped(a, block.w13, ws, block.e_local, alpha=block.w13_alpha, w_sf=block._w13_sf)
+            y = cu.gemm_grouped(cu.swiglu_quant(h1, block.down_input_scale), block.w2, ws, block.e_local, alpha=block.w2_alpha,
+                                w_sf=block._w2_sf)
+        else:
+            a = cu.moe_gather(recv, ws, 1, None)
+            y = cu.gemm_grouped(cu.swiglu(cu.gemm_grouped(a, block.w13, ws, block.e_local)), block.w2, ws, block.e_local)
+        cu._check(cu.lib().telb_ep_return(cu._p(y), cu._p(ws.dst_row), c["recv_rows"], c["recv_ids"], c["comb_rows"], c["flags"],
+                                          ctypes.c_int(rank), ctypes.c_int(world), ctypes.c_int(st.slots_cap), ctypes.c_int(hidden),
+                                          ctypes.c_void_p(st.epoch.data_ptr() + 4), ctypes.c_void_p(st.ticket.data_ptr() + 4), cu._stream()),
+                  "ep_return")
+        cu._check(cu.lib().telb_ep_wait(cu._p(st.flags), ctypes.c_int(1), ctypes.c_int(world), ctypes.c_void_p(st.epoch.data_ptr() + 4),
+                                        cu._p(ws0.status), cu._stream()), "ep_wait")
+        out = rs.partial[rank * rpr * hidden:(rank * rpr + t_local) * hidden].view(t_local, hidden)
+        if t_local > 0:
+            cu.moe_combine(st.comb_rows.view(st.slots_cap, hidden), _Rows(st.arange), w, out=out)
+        return RsPartial(rows, hidden, x.dtype, rpr, sum_slots=1, slot_base=rank)
+
     def _rs_add_rmsnorm(self, part: RsPartial, residual, weight, eps, quant_scale, defer_gather):
         cu = ops.cuda_ops()
         st = self._rs_state(part.hidden, part.dtype)
@@ -162,7 +258,8 @@ class FusedComm(TorchComm):
             cu._p(weight), cu._p(res_out), None if quant else st.c_gather_y, st.c_gather_xq if quant else None,
             st.c_gather_sf if quant else None, cu._p(quant_scale), ctypes.c_int(self.rank), ctypes.c_int(self.world_size),
             ctypes.c_int(rows), ctypes.c_int(rpr), ctypes.c_int(hidden), ctypes.c_float(eps), ctypes.c_int(0 if defer_gather else 1),
-            ctypes.c_int(cu._is_bf16(res_out)), cu._p(ws.status), cu._stream()), "rs_add_rmsnorm_ag")
+            ctypes.c_int(cu._is_bf16(res_out)), cu._p(ws.status), ctypes.c_int(part.sum_slots), ctypes.c_int(part.slot_base),
+            cu._stream()), "rs_add_rmsnorm_ag")
         wait = None
         if defer_gather and self.world_size > 1:
             wait = cu.GemmFusion()

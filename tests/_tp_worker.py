@@ -14,6 +14,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 def main():
     backend, kind, ckpt = sys.argv[1], sys.argv[2], sys.argv[3]
     prompt_len = int(sys.argv[4]) if len(sys.argv) > 4 else 70
+    expert_parallel = len(sys.argv) > 5 and sys.argv[5] == "ep"
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     if backend == "nccl":
@@ -42,7 +43,8 @@ def main():
 
     ref_logits, ref_toks = run(None, None)
     comm = make_comm(kind, dev)
-    tp_logits, tp_toks = run(Mapping(tp_size=world, tp_rank=rank), comm)
+    mapping = Mapping(tp_size=world, tp_rank=rank, ep_size=world if expert_parallel else 1, ep_rank=rank if expert_parallel else 0)
+    tp_logits, tp_toks = run(mapping, comm)
     err = (tp_logits - ref_logits).abs().max().item()
     scale = ref_logits.abs().max().item()
     tol = 1e-4 if dev.type == "cpu" else 0.06
@@ -50,6 +52,9 @@ def main():
     same = (tp_toks == ref_toks).float().mean().item()
     if kind == "fused" and 2 * prompt_len > 256 and world > 1 and not comm._rs:
         print(f"rank {rank}: the reduce-scatter path was not taken", flush=True)
+        ok = False
+    if kind == "fused" and expert_parallel and 2 * prompt_len > 256 and world > 1 and not comm._ep:
+        print(f"rank {rank}: the expert all-to-all path was not taken", flush=True)
         ok = False
     gathered = [None] * world
     dist.all_gather_object(gathered, tp_toks.tolist())

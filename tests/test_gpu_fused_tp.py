@@ -72,7 +72,7 @@ def test_rs_norm_ag_two_emulated_ranks(cu, quant, m):
         cu._check(L.telb_rs_add_rmsnorm_ag(
             cu._p(partial[r]), _table(flags), _table(flags, 32), cu._p(epoch[r]), cu._p(ticket[r]), cu._p(resid), 1, cu._p(gamma),
             cu._p(ro), None if quant else _table(gy), _table(gxq) if quant else None, _table(gsf) if quant else None,
-            cu._p(qscale) if quant else None, r, world, m, rpr, h, ctypes.c_float(1e-6), 0, 1, cu._p(ws.status), cu._stream()), "rs")
+            cu._p(qscale) if quant else None, r, world, m, rpr, h, ctypes.c_float(1e-6), 0, 1, cu._p(ws.status), 0, 0, cu._stream()), "rs")
         res_out.append(ro)
     torch.cuda.synchronize()
     ws.check_status()
@@ -104,3 +104,60 @@ def test_rs_norm_ag_two_emulated_ranks(cu, quant, m):
         assert torch.equal(got, cu.gemm(gy[0], w2, mode=1))
     torch.cuda.synchronize()
     ws.check_status()
+
+
+def test_ep_all_to_all_two_emulated_ranks(cu):
+    """Dispatch → align / gather / grouped GEMM → return → weighted combine, two ranks emulated on one GPU."""
+    g = torch.Generator(device="cuda").manual_seed(5)
+    world, h, top_k, experts, cap_tokens = 2, 256, 2, 8, 200
+    epr, cap = experts // world, cap_tokens * top_k
+    t_local = [150, 97]
+    x = [torch.randn(t, h, device="cuda", generator=g).bfloat16() for t in t_local]
+    idx = [torch.stack([torch.randperm(experts, device="cuda", generator=g)[:top_k] for _ in range(t)]).to(torch.int32) for t in t_local]
+    w = [torch.rand(t, top_k, device="cuda", generator=g) for t in t_local]
+    wexp = [(torch.randn(epr * h, h, device="cuda", generator=g) * 0.05).bfloat16() for _ in range(world)]     # per rank [epr * N, K]
+    recv_rows = [torch.zeros(world * cap * h, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    recv_ids = [torch.full((world * cap,), -1, device="cuda", dtype=torch.int32) for _ in range(world)]
+    comb = [torch.zeros(cap * h, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    flags = [torch.ones(16, device="cuda", dtype=torch.int32) for _ in range(world)]      # epoch 1 already "published"
+    epoch = [torch.zeros(2, device="cuda", dtype=torch.int32) for _ in range(world)]
+    ticket = [torch.zeros(2, device="cuda", dtype=torch.int32) for _ in range(world)]
+    L, ws0 = cu.lib(), cu.Workspace.get(torch.device("cuda", 0))
+    tables = (_table(recv_rows), _table(recv_ids), _table(comb), _table(flags))
+    for r in range(world):
+        cu._check(L.telb_ep_dispatch(cu._p(x[r]), cu._p(idx[r]), *tables, r, world, t_local[r], top_k, h, epr, cap, 0,
+                                     ctypes.c_void_p(epoch[r].data_ptr()), ctypes.c_void_p(ticket[r].data_ptr()), cu._stream()), "dispatch")
+    for r in range(world):
+        cu._check(L.telb_ep_wait(cu._p(flags[r]), 0, world, ctypes.c_void_p(epoch[r].data_ptr()), cu._p(ws0.status), cu._stream()), "wait")
+    torch.cuda.synchronize()
+    for r in range(world):      # every slot of every source carries this rank's local expert id or -1
+        for s in range(world):
+            ids = recv_ids[r].view(world, cap)[s, :t_local[s] * top_k]
+            want = torch.where(idx[s].view(-1) // epr == r, idx[s].view(-1) % epr, torch.full_like(idx[s].view(-1), -1))
+            assert torch.equal(ids, want)
+    for r in range(world):
+        ws = cu.moe_align(recv_ids[r].view(-1, 1), epr, 0, epr)
+        a = cu.moe_gather(recv_rows[r].view(world * cap, h), ws, 1, None)
+        y = cu.gemm_grouped(a, wexp[r], ws, epr)
+        cu._check(L.telb_ep_return(cu._p(y), cu._p(ws.dst_row), *tables, r, world, cap, h, ctypes.c_void_p(epoch[r].data_ptr() + 4),
+                                   ctypes.c_void_p(ticket[r].data_ptr() + 4), cu._stream()), "return")
+    from tensorrt_edge_llm_b200.parallel.fused import _Rows
+    arange = torch.arange(cap, device="cuda", dtype=torch.int32)
+    for r in range(world):
+        cu._check(L.telb_ep_wait(cu._p(flags[r]), 1, world, ctypes.c_void_p(epoch[r].data_ptr() + 4), cu._p(ws0.status), cu._stream()), "wait")
+        out = cu.moe_combine(comb[r].view(cap, h), _Rows(arange), w[r])
+        want = torch.zeros(t_local[r], h, device="cuda")
+        for k in range(top_k):
+            e = idx[r][:, k].long()
+            wk = torch.stack([wexp[int(ee) // epr].view(epr, h, h)[int(ee) % epr] for ee in e]).float()      # [T, N, K]
+            want += w[r][:, k, None] * torch.einsum("tk,tnk->tn", x[r].float(), wk).bfloat16().float()
+        assert _rel_err(out, want) < 1e-2
+    torch.cuda.synchronize()
+    assert [e.tolist() for e in epoch] == [[1, 1], [1, 1]] and all(t.tolist() == [0, 0] for t in ticket)
+    # a shorter step after a longer one: stale ids beyond the new slot count are cleared
+    cu._check(L.telb_ep_dispatch(cu._p(x[0][:10]), cu._p(idx[0][:10].contiguous()), *tables, 0, world, 10, top_k, h, epr, cap,
+                                 t_local[0] * top_k, ctypes.c_void_p(epoch[0].data_ptr()), ctypes.c_void_p(ticket[0].data_ptr()), cu._stream()), "dispatch")
+    torch.cuda.synchronize()
+    for r in range(world):
+        assert int((recv_ids[r].view(world, cap)[0, 10 * top_k:] != -1).sum()) == 0
+    ws0.check_status()

@@ -31,10 +31,40 @@ def _make_ckpt(d, dtype):
         json.dump(hf, f)
 
 
-def _launch(nproc, backend, kind, ckpt, port, prompt_len=70):
+def _make_moe_ckpt(d, dtype):
+    from transformers import Qwen3MoeConfig, Qwen3MoeForCausalLM
+    cfg = Qwen3MoeConfig(vocab_size=2048, hidden_size=512, intermediate_size=1024, moe_intermediate_size=256, num_hidden_layers=2,
+                         num_attention_heads=8, num_key_value_heads=2, head_dim=128, num_experts=8, num_experts_per_tok=2,
+                         norm_topk_prob=True, rms_norm_eps=1e-6, rope_theta=1e4, max_position_embeddings=1024,
+                         decoder_sparse_step=1, mlp_only_layers=[], tie_word_embeddings=False, output_router_logits=False)
+    torch.manual_seed(0)
+    m = Qwen3MoeForCausalLM(cfg).to(dtype).eval()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if "norm" not in n:
+                p.normal_(0.0, 0.05)
+    sd = {}
+    for k, v in m.state_dict().items():
+        if k.endswith("experts.gate_up_proj"):
+            base, i = k[:-len(".gate_up_proj")], v.shape[1] // 2
+            for e in range(v.shape[0]):
+                sd[f"{base}.{e}.gate_proj.weight"], sd[f"{base}.{e}.up_proj.weight"] = v[e, :i].contiguous(), v[e, i:].contiguous()
+        elif k.endswith("experts.down_proj"):
+            for e in range(v.shape[0]):
+                sd[f"{k[:-len('.down_proj')]}.{e}.down_proj.weight"] = v[e].contiguous()
+        else:
+            sd[k] = v
+    save_file(sd, os.path.join(d, "model.safetensors"))
+    hf = cfg.to_dict()
+    hf["torch_dtype"] = {torch.float32: "float32", torch.bfloat16: "bfloat16"}[dtype]
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(hf, f)
+
+
+def _launch(nproc, backend, kind, ckpt, port, prompt_len=70, extra=()):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "_tp_worker.py"),
-           backend, kind, ckpt, str(prompt_len)]
+           backend, kind, ckpt, str(prompt_len), *extra]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", OMP_NUM_THREADS="2")
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
@@ -65,6 +95,25 @@ def test_tp2_fused_prefill_reduce_scatter_path(tmp_path):
         pytest.skip("needs two GPUs")
     _make_ckpt(str(tmp_path), torch.bfloat16)
     out = _launch(2, "nccl", "fused", str(tmp_path), 29614, prompt_len=190)
+    assert "ranks identical True" in out
+
+
+def test_ep2_matches_single_rank_cpu_gloo(tmp_path):
+    """Attention tensor-parallel + experts sharded by id, over gloo: the partial sums reduce to the single-rank model."""
+    _make_moe_ckpt(str(tmp_path), torch.float32)
+    out = _launch(2, "gloo", "nccl", str(tmp_path), 29615, extra=("ep",))
+    assert "ranks identical True" in out
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("prompt_len", [70, 190])
+def test_ep2_fused_gpu(tmp_path, prompt_len):
+    """Expert parallelism on two GPUs: decode-size steps reduce the experts' partial sums in the fused all-reduce;
+    prefill-size steps (2 x 190 rows) ship token rows all-to-all over peer memory."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _make_moe_ckpt(str(tmp_path), torch.bfloat16)
+    out = _launch(2, "nccl", "fused", str(tmp_path), 29616 + (prompt_len > 100), prompt_len=prompt_len, extra=("ep",))
     assert "ranks identical True" in out
 
 
