@@ -43,24 +43,49 @@ def _generate_timed(llm, prompts_dev, out_len, steps, warmup):
     return statistics.median(pre), statistics.median(dec)
 
 
+def _dist():
+    """(rank, world, device, comm) — one process per GPU under torchrun, else a single GPU."""
+    import os
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    comm = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        from ..parallel import make_comm
+        comm = make_comm("fused", dev)
+    return rank, world, dev, comm
+
+
 def run_moe(args) -> dict:
     from ..config import QUANT_NVFP4, QuantConfig, qwen3_30b_a3b_config
     from ..ops import cuda as cu
     from ..runtime.llm import LLM
     b, s, o = args.batch or 32, args.input_len or 2048, args.output_len or 256
+    rank, world, dev, comm = _dist()
     quant = QuantConfig(quant_type=QUANT_NVFP4, group_size=16, excluded=["*self_attn*", "*mlp.gate", "lm_head"])
     cfg = qwen3_30b_a3b_config(dtype="bfloat16", quant=quant, **({"num_hidden_layers": args.layers} if args.layers else {}))
-    llm = LLM(cfg, device="cuda", max_batch_size=b, max_input_len=s, max_kv_cache_capacity=s + o + 64, max_num_tokens=8192)
+    if world > 1:
+        cfg = cfg.for_rank(rank, world, ep=True)       # attention tensor-parallel, experts sharded by id
+    llm = LLM(cfg, device=str(dev), comm=comm, max_batch_size=b, max_input_len=s, max_kv_cache_capacity=s + o + 64, max_num_tokens=8192)
     g = torch.Generator().manual_seed(1234)
-    prompts = torch.randint(0, cfg.vocab_size, (b, s), generator=g, dtype=torch.int32).cuda()
+    prompts = torch.randint(0, cfg.vocab_size, (b, s), generator=g, dtype=torch.int32).to(dev)
     l0 = cu.LAUNCHES
     pre, dec = _generate_timed(llm, prompts, o, args.steps, args.warmup)
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([pre, dec], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        pre, dec = float(t[0]), float(t[1])
     ms = pre + dec
     return {"metric": "output tok/s, Qwen3-30B-A3B-shape MoE (48L, H2048, 128 experts top-8, I768), NVFP4 experts + bf16 attention",
-            "value": round(b * o / (ms / 1e3), 1), "unit": "tok/s", "n_gpus": 1, "ms_per_step": round(ms, 3),
+            "value": round(b * o / (ms / 1e3), 1), "unit": "tok/s", "n_gpus": world, "ms_per_step": round(ms, 3),
             "config": {"global_batch": b, "seq_len": s, "output_len": o, "prefill_ms": round(pre, 3),
-                       "decode_ms_per_token": round(dec / max(1, o - 1), 4), "parallelism": "ep1", "layers": cfg.num_hidden_layers},
-            "gpu_launches": int(cu.LAUNCHES - l0), "data": "synthetic"}
+                       "decode_ms_per_token": round(dec / max(1, o - 1), 4), "parallelism": f"tp{world}-attention + ep{world}-experts",
+                       "layers": cfg.num_hidden_layers, "ep_all_to_all": bool(comm is not None and getattr(comm, "_ep", None))},
+            "gpu_launches": int(cu.LAUNCHES - l0), "data": "synthetic", "_rank": rank, "_world": world, "_llm": llm}
 
 
 def run_hybrid(args) -> dict:
@@ -137,6 +162,18 @@ def run_eagle(args) -> dict:
 def main(args) -> int:
     fn = {"moe": run_moe, "hybrid": run_hybrid, "eagle": run_eagle}[args.workload]
     out = fn(args)
+    rank, world, llm = out.pop("_rank", 0), out.pop("_world", 1), out.pop("_llm", None)
     out.update({"steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "dtype": "bf16" if args.workload != "moe" else "nvfp4-experts/bf16"})
-    print(json.dumps(out), flush=True)
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if world > 1:       # graphs hold collective kernels: leave without the communicator's destructor
+        import os
+        import sys
+        import torch.distributed as dist
+        if llm is not None:
+            llm.runner._graphs.clear()
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
     return 0
