@@ -80,6 +80,8 @@ class EagleDecoder:
         self.draft = draft
         self.dkv = draft_kv
         self.spec = spec or SpecConfig()
+        if tap_layers is None and getattr(draft.cfg, "draft_type", None) == "mtp":
+            tap_layers = [runner.model.cfg.num_hidden_layers - 1]       # an MTP head reads the target's last hidden state
         self.taps = list(tap_layers or runner.model.cfg.eagle3_target_layer_ids or default_tap_layers(runner.model.cfg.num_hidden_layers))
         self.device = runner.device
         self.stats = SpecStats()

@@ -134,3 +134,25 @@ def test_forced_acceptance_length():
     for _ in range(4):
         assert len(dec.round([0])[0]) == 3
     assert dec.r.kv.lengths[0] == len(prompts[0]) + 12 and dec.dkv.lengths[0] == dec.r.kv.lengths[0]
+
+
+def test_mtp_head_is_lossless_and_shares_lm_head():
+    model = _target()
+    cfg = tiny_llama_config(num_hidden_layers=1, dtype="float32")
+    cfg.draft_type = "mtp"
+    head = AutoModel.from_config(cfg, random_init=4)
+    assert type(head).__name__ == "MtpDraft"
+    head.share_lm_head(model)
+    assert head.lm_head is model.lm_head
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, model.cfg.vocab_size, (n,), generator=g).tolist() for n in (7, 13)]
+    want = _greedy(model, prompts, 10)
+    dec = _decoder(model, head, SpecConfig(draft_steps=3, top_k=1, verify_tokens=4))       # a chain of three drafts
+    assert dec.taps == [model.cfg.num_hidden_layers - 1]
+    assert dec.generate([0, 1], prompts, 10) == want
+    assert MtpDraftRemap("mtp.fc.weight") == "fc.weight" and MtpDraftRemap("mtp.layers.0.mlp.up_proj.weight") == "layers.0.mlp.up_proj.weight"
+
+
+from tensorrt_edge_llm_b200.models.mtp import MtpDraft  # noqa: E402
+
+MtpDraftRemap = MtpDraft.checkpoint_key_remap
