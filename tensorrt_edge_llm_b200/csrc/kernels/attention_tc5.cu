@@ -42,7 +42,7 @@ struct AttnParams {
     int tq;                    // query tokens per tile = 128 / group
     int splits;
     int total_tokens;
-    int window;                // sliding window, 0 = none
+    int window;                // sliding window, 0 = none, -1 = no causal mask (every row sees every cached and new token)
     float scale_log2;          // softmax scale * log2(e)
     int out_bf16;
     int* status;
@@ -110,7 +110,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     if (tok0 >= qlen) return;                            // uniform per CTA, before any barrier / TMEM use
 
     // KV tile range of this CTA
-    int kv_end = past + (p.tree_mask ? qlen : min(qlen, tok0 + p.tq));
+    int kv_end = past + ((p.tree_mask || p.window < 0) ? qlen : min(qlen, tok0 + p.tq));
     int tile_lo = 0;
     if (p.window > 0) tile_lo = max(0, past + tok0 - p.window + 1) / kKvTile;
     const int tile_hi_all = (kv_end + kKvTile - 1) / kKvTile;
@@ -267,6 +267,8 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
                     if (mask_row) {
                         const int nc = c - past;
                         vis = c < past || (nc < qlen && ((mask_row[nc >> 5] >> (nc & 31)) & 1));
+                    } else if (p.window < 0) {
+                        vis = c < past + qlen;                      // bidirectional (vision / audio encoders)
                     } else {
                         vis = c <= causal_limit;
                     }

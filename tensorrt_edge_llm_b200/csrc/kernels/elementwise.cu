@@ -194,6 +194,25 @@ __global__ void relu2_kernel(const T* __restrict__ in, T* __restrict__ out, long
     }
 }
 
+// GELU, exact (erf) or tanh approximation, elementwise over n values (n % 8 == 0).
+template <typename T>
+__global__ void gelu_kernel(const T* __restrict__ in, T* __restrict__ out, long long n, int tanh_approx) {
+    pdl_prologue();
+    for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8; i < n;
+         i += (long long)gridDim.x * blockDim.x * 8) {
+        Vec8<T> v, o;
+        v.load(in + i);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float x = v.get(j);
+            const float y = tanh_approx ? 0.5f * x * (1.f + tanhf(0.7978845608f * (x + 0.044715f * x * x * x)))
+                                        : 0.5f * x * (1.f + erff(x * 0.70710678f));
+            o.set(j, y);
+        }
+        o.store(out + i);
+    }
+}
+
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table, T* __restrict__ out,
                                  int hidden, int vocab) {
@@ -509,6 +528,16 @@ extern "C" int telb_relu2(const void* in, void* out, long long n, int is_bf16, c
     if (blocks > 148 * 16) blocks = 148 * 16;
     DISPATCH_T(is_bf16, { TELB_LAUNCH("relu2_kernel", (relu2_kernel<T>), dim3((int)blocks), dim3(256), 0, stream, (const T*)in, (T*)out, n); })
     TELB_CHECK_LAUNCH("relu2_kernel");
+    return 0;
+}
+
+extern "C" int telb_gelu(const void* in, void* out, long long n, int tanh_approx, int is_bf16, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (n % 8) return fail("telb_gelu: element count must be a multiple of 8");
+    long long blocks = (n / 8 + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    DISPATCH_T(is_bf16, { TELB_LAUNCH("gelu_kernel", (gelu_kernel<T>), dim3((int)blocks), dim3(256), 0, stream, (const T*)in, (T*)out, n, tanh_approx); })
+    TELB_CHECK_LAUNCH("gelu_kernel");
     return 0;
 }
 

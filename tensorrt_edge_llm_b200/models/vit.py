@@ -1,0 +1,161 @@
+"""Vision transformer encoder + projector producing embeddings for the language model.
+
+Pre-LayerNorm ViT blocks (learned position embeddings, bidirectional attention, GELU MLP) over image patches,
+followed by an optional ``merge × merge`` spatial merge and a two-layer projector into the LLM's hidden size —
+the common shape of the InternViT / CLIP / Qwen-VL style encoders.  The attention runs the same paged tile kernel
+as the decoder with the causal mask switched off (``ops.paged_attention(..., causal=False)``): an image is one
+"sequence" whose patches are written to a scratch KV pool and attended in full.
+
+Parity: the visual encoders of ``tensorrt_edgellm/models/*vl*`` with ``vit_attention_plugin``
+(``tensorrt_edgellm/models/ops.py:406``) and the runner contract of ``cpp/multimodal/`` (image → embedding rows that
+replace the image-token rows of the prompt)."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..ops.meta import build_step_meta
+
+
+@dataclass
+class VisionConfig:
+    hidden_size: int = 1024
+    num_hidden_layers: int = 24
+    num_attention_heads: int = 16
+    intermediate_size: int = 4096
+    patch_size: int = 14
+    image_size: int = 448
+    in_channels: int = 3
+    layer_norm_eps: float = 1e-6
+    spatial_merge: int = 2                 # merge x merge neighbouring patches become one LLM token
+    out_hidden_size: int = 4096            # the language model's hidden size
+    gelu_tanh: bool = False
+    dtype: str = "bfloat16"
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden_size // self.num_attention_heads
+
+    @property
+    def grid(self) -> int:
+        return self.image_size // self.patch_size
+
+    @property
+    def compute_dtype(self) -> torch.dtype:
+        return getattr(torch, self.dtype)
+
+
+class _LayerNorm(nn.Module):
+    def __init__(self, dim, eps, dtype):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype), requires_grad=False)
+        self.bias = nn.Parameter(torch.zeros(dim, dtype=dtype), requires_grad=False)
+        self.eps = eps
+
+    def forward(self, x):
+        return ops.layernorm(x, self.weight, self.bias, self.eps)
+
+
+class _Linear(nn.Module):
+    def __init__(self, i, o, dtype):
+        super().__init__()
+        self.weight = nn.Parameter(torch.zeros(o, i, dtype=dtype), requires_grad=False)
+        self.bias = nn.Parameter(torch.zeros(o, dtype=dtype), requires_grad=False)
+
+    def forward(self, x):
+        return ops.linear(x, self.weight, self.bias)
+
+
+class VitBlock(nn.Module):
+    def __init__(self, cfg: VisionConfig):
+        super().__init__()
+        dt, h = cfg.compute_dtype, cfg.hidden_size
+        self.cfg = cfg
+        self.norm1, self.norm2 = _LayerNorm(h, cfg.layer_norm_eps, dt), _LayerNorm(h, cfg.layer_norm_eps, dt)
+        self.qkv, self.proj = _Linear(h, 3 * h, dt), _Linear(h, h, dt)
+        self.fc1, self.fc2 = _Linear(h, cfg.intermediate_size, dt), _Linear(cfg.intermediate_size, h, dt)
+
+    def forward(self, x, meta, kv_layer, no_rope):
+        c = self.cfg
+        qkv = self.qkv(self.norm1(x))
+        q = ops.rope_kv_write(qkv, kv_layer, meta, no_rope, c.num_attention_heads, c.num_attention_heads, c.head_dim)
+        a = ops.paged_attention(q, kv_layer, meta, c.head_dim ** -0.5, causal=False)
+        x = x + self.proj(a.reshape(a.shape[0], -1))
+        return x + self.fc2(ops.gelu(self.fc1(self.norm2(x)), c.gelu_tanh))
+
+
+class VisionEncoder(nn.Module):
+    """``forward(patches [N_img, grid², C·P·P])`` → ``[N_img · (grid / merge)², out_hidden]`` embedding rows."""
+
+    def __init__(self, cfg: VisionConfig):
+        super().__init__()
+        if cfg.head_dim not in (64, 128):
+            raise ValueError("the attention kernel takes head dimensions of 64 or 128")
+        if cfg.grid % cfg.spatial_merge:
+            raise ValueError("the patch grid must be divisible by the spatial merge factor")
+        self.cfg = cfg
+        dt, h = cfg.compute_dtype, cfg.hidden_size
+        self.patch_embed = _Linear(cfg.in_channels * cfg.patch_size ** 2, h, dt)
+        self.pos_embed = nn.Parameter(torch.zeros(cfg.grid ** 2, h, dtype=dt), requires_grad=False)
+        self.blocks = nn.ModuleList([VitBlock(cfg) for _ in range(cfg.num_hidden_layers)])
+        self.norm = _LayerNorm(h, cfg.layer_norm_eps, dt)
+        m2 = cfg.spatial_merge ** 2
+        self.merger_fc1, self.merger_fc2 = _Linear(h * m2, h * m2, dt), _Linear(h * m2, cfg.out_hidden_size, dt)
+        self._kv: Optional[torch.Tensor] = None
+
+    @torch.no_grad()
+    def random_init(self, seed: int = 0, std: float = 0.02):
+        g = torch.Generator().manual_seed(seed)
+        for name, p in self.named_parameters():
+            if name.endswith("weight") and p.dim() == 2 or name == "pos_embed":
+                p.copy_((torch.randn(p.shape, generator=g) * std).to(p.dtype))
+        return self
+
+    @staticmethod
+    def patchify(images: torch.Tensor, patch: int) -> torch.Tensor:
+        """``[N, C, H, W]`` pixels → ``[N, (H/P)(W/P), C·P·P]`` row-major patches."""
+        n, c, hh, ww = images.shape
+        x = images.reshape(n, c, hh // patch, patch, ww // patch, patch).permute(0, 2, 4, 1, 3, 5)
+        return x.reshape(n, (hh // patch) * (ww // patch), c * patch * patch)
+
+    def _scratch_kv(self, n_img: int, tokens: int, device) -> torch.Tensor:
+        page = 64
+        pages = n_img * ((tokens + page - 1) // page)
+        c = self.cfg
+        if self._kv is None or self._kv.shape[0] < pages or self._kv.device != device:
+            self._kv = torch.zeros(pages, 2, c.num_attention_heads, page, c.head_dim, dtype=c.compute_dtype, device=device)
+        return self._kv
+
+    def forward(self, patches: torch.Tensor) -> torch.Tensor:
+        c = self.cfg
+        n_img, tokens, _ = patches.shape
+        dev = patches.device
+        x = self.patch_embed(patches.reshape(n_img * tokens, -1).to(c.compute_dtype)) + self.pos_embed[:tokens].repeat(n_img, 1)
+        page = 64
+        per = (tokens + page - 1) // page
+        table = torch.arange(n_img * per, dtype=torch.int32).view(n_img, per)
+        meta = build_step_meta([tokens] * n_img, [0] * n_img, table, page, device=dev)
+        kv = self._scratch_kv(n_img, tokens, dev)
+        no_rope = torch.zeros(tokens, 0, dtype=torch.float32, device=dev)          # rotary width 0: keys are stored as they are
+        for blk in self.blocks:
+            x = blk(x, meta, kv, no_rope)
+        x = self.norm(x)
+        m, g = c.spatial_merge, int(round(tokens ** 0.5))
+        x = x.view(n_img, g // m, m, g // m, m, c.hidden_size).permute(0, 1, 3, 2, 4, 5).reshape(n_img * (g // m) ** 2, m * m * c.hidden_size)
+        return self.merger_fc2(ops.gelu(self.merger_fc1(x.contiguous()), c.gelu_tanh))
+
+
+def merge_image_embeddings(token_ids: Sequence[int], text_embeds: torch.Tensor, image_embeds: torch.Tensor, image_token_id: int
+                           ) -> torch.Tensor:
+    """Replace the rows of ``text_embeds`` at ``image_token_id`` positions by the image embedding rows, in order."""
+    ids = torch.as_tensor(list(token_ids), device=text_embeds.device)
+    pos = (ids == image_token_id).nonzero(as_tuple=True)[0]
+    if pos.numel() != image_embeds.shape[0]:
+        raise ValueError(f"prompt has {pos.numel()} image tokens but the encoder produced {image_embeds.shape[0]} rows")
+    out = text_embeds.clone()
+    out[pos] = image_embeds.to(out.dtype)
+    return out

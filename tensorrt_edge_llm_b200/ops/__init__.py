@@ -73,6 +73,12 @@ def relu2(x):
     return ref.relu2(x)
 
 
+def gelu(x, tanh_approx=False):
+    if x.is_cuda:
+        return cuda_ops().gelu(x, tanh_approx)
+    return torch.nn.functional.gelu(x.float(), approximate="tanh" if tanh_approx else "none").to(x.dtype)
+
+
 def embedding(ids, table):
     if table.is_cuda:
         return cuda_ops().embedding(ids, table)
@@ -94,10 +100,10 @@ def rope_kv_write(qkv, kv_layer, meta, cos_sin, num_q_heads, num_kv_heads, head_
                              q_norm_w, k_norm_w, eps)
 
 
-def paged_attention(q, kv_layer, meta, scale, sliding_window=None, sinks=None):
+def paged_attention(q, kv_layer, meta, scale, sliding_window=None, sinks=None, causal=True):
     if q.is_cuda:
-        return cuda_ops().paged_attention(q, kv_layer, meta, scale, sliding_window, sinks)
-    return ref.paged_attention(q, kv_layer, meta, scale, sliding_window, sinks)
+        return cuda_ops().paged_attention(q, kv_layer, meta, scale, sliding_window, sinks, causal=causal)
+    return ref.paged_attention(q, kv_layer, meta, scale, sliding_window, sinks, causal=causal)
 
 
 def argmax(logits):

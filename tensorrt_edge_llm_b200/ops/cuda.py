@@ -158,6 +158,13 @@ def relu2(x: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def gelu(x: torch.Tensor, tanh_approx: bool = False) -> torch.Tensor:
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    _check(lib().telb_gelu(_p(x), _p(out), c_ll(x.numel()), c_int(int(tanh_approx)), c_int(_is_bf16(x)), _stream()), "gelu")
+    return out
+
+
 def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     ids = ids.to(torch.int32).contiguous()
     out = torch.empty(ids.numel(), table.shape[1], dtype=table.dtype, device=table.device)
@@ -221,10 +228,12 @@ def _decode_splits(meta: StepMeta, hkv: int) -> int:
 
 
 def paged_attention(q, kv_layer, meta: StepMeta, scale, sliding_window=None, sinks=None, splits: Optional[int] = None,
-                    kernel: Optional[str] = None, trace: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    kernel: Optional[str] = None, trace: Optional[torch.Tensor] = None, causal: bool = True) -> torch.Tensor:
     """Paged GQA attention.  Decode-shaped steps (``max_q_len * Hq/Hkv <= 16``, head_dim 128, causal)
     run the token-major XQA-style kernel; everything else the row-major tile kernel.
-    ``kernel`` forces ``"decode"`` or ``"tile"``."""
+    ``kernel`` forces ``"decode"`` or ``"tile"``; ``causal=False`` lets every row see every token of its sequence."""
+    if not causal:
+        sliding_window, kernel = -1, "tile"
     if sinks is not None:
         raise NotImplementedError("attention sinks are not implemented in the CUDA kernel yet")
     q = q.contiguous()

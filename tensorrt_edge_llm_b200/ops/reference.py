@@ -169,7 +169,7 @@ def gather_kv(kv_layer: torch.Tensor, page_table_row: torch.Tensor, length: int,
 
 
 def paged_attention(q: torch.Tensor, kv_layer: torch.Tensor, meta: StepMeta, scale: float,
-                    sliding_window: Optional[int] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    sliding_window: Optional[int] = None, sinks: Optional[torch.Tensor] = None, causal: bool = True) -> torch.Tensor:
     """Causal GQA attention of the step's rows over the paged cache (which already holds this
     step's keys/values).  Row ``i`` of a sequence sees cache slots ``[0, past + i]``
     (bottom-right aligned causal mask), optionally limited to a sliding window, or the tree
@@ -195,9 +195,11 @@ def paged_attention(q: torch.Tensor, kv_layer: torch.Tensor, meta: StepMeta, sca
             new_c = (cols - past).clamp(min=0)
             bit = (words.gather(1, (new_c // 32).expand(ql, -1)) >> (new_c % 32)) & 1
             allowed = (cols < past) | ((cols >= past) & (bit == 1))
+        elif not causal:
+            allowed = (cols < total) & (rows >= 0)
         else:
             allowed = cols <= past + rows
-        if sliding_window is not None:
+        if sliding_window is not None and causal:
             allowed = allowed & (cols > past + rows - sliding_window)
         sc = sc.masked_fill(~allowed[None], float("-inf"))
         if sinks is not None:

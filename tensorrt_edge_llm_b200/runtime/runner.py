@@ -111,6 +111,22 @@ class ModelRunner:
         return torch.stack(out)  # type: ignore[arg-type]
 
     @torch.no_grad()
+    def prefill_embeds(self, seats: Sequence[int], embeds: Sequence[torch.Tensor]) -> torch.Tensor:
+        """Prefill from embedding rows instead of token ids (multimodal prompts: text rows with the image / audio
+        rows already merged in).  One step; returns last-row logits ``[N, V]``."""
+        q_lens = [int(e.shape[0]) for e in embeds]
+        meta = self._meta(seats, q_lens)
+        x = torch.cat([e.to(self.device) for e in embeds], dim=0).to(self.model.cfg.compute_dtype)
+        logits = self.model(None, meta, self.cache, inputs_embeds=x)
+        for s, q in zip(seats, q_lens):
+            self.kv.commit(s, q)
+        return logits
+
+    def embed_tokens(self, ids: Sequence[int]) -> torch.Tensor:
+        t = torch.tensor(list(ids), dtype=torch.int32, device=self.device)
+        return ops.embedding(t, self.model.model.embed_tokens.weight)
+
+    @torch.no_grad()
     def prefill_tensor(self, seats: Sequence[int], ids: torch.Tensor) -> torch.Tensor:
         """Prefill equal-length prompts given as one tensor ``[N, S]`` (pinned host or device
         memory); chunks hold whole sequences.  Returns last-token logits ``[N, V]``."""

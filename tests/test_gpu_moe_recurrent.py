@@ -252,3 +252,18 @@ def test_layernorm(cu, rows, hidden):
     assert _rel_err(cu.layernorm(x, w, b, 1e-5), ref.layernorm(x, w, b, 1e-5)) < 4e-3
     assert _rel_err(cu.layernorm(x, w, None, 1e-5), ref.layernorm(x, w, None, 1e-5)) < 4e-3
     _sync_check(cu)
+
+
+def test_vision_encoder_gpu_matches_cpu(cu):
+    from tensorrt_edge_llm_b200.models.vit import VisionConfig, VisionEncoder
+    cfg = VisionConfig(hidden_size=256, num_hidden_layers=2, num_attention_heads=4, intermediate_size=512, patch_size=4, image_size=64,
+                       out_hidden_size=512, dtype="bfloat16")
+    enc = VisionEncoder(cfg).random_init(0, std=0.05)
+    patches = VisionEncoder.patchify(torch.randn(2, 3, 64, 64, generator=torch.Generator().manual_seed(3)), 4)      # 256 patches each
+    want = enc(patches).float()
+    got = enc.cuda()(patches.cuda()).float().cpu()
+    assert got.shape == (2 * 64, 512) and _rel_err(got, want) < 3e-2
+    x = torch.randn(40, 64, generator=torch.Generator().manual_seed(4)).bfloat16()
+    for approx in (False, True):
+        assert _rel_err(cu.gelu(x.cuda(), approx).cpu(), torch.nn.functional.gelu(x.float(), approximate="tanh" if approx else "none")) < 5e-3
+    _sync_check(cu)
