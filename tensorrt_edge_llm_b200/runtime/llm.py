@@ -53,6 +53,12 @@ class LLM:
                                  max_pages_per_seq=pages_per_seq, device=self.device)
         self.runner = ModelRunner(self.model, self.kv, self.device, max_num_tokens=max_num_tokens)
         self.engine = None
+        from .debug import LayerDumper, forced_tokens_from_env
+        self._dumper = LayerDumper.from_env()
+        if self._dumper is not None:
+            self._dumper.attach(self.model)
+            self.runner.use_cuda_graphs = False        # hooks do not run inside a replayed graph
+        self._forced = forced_tokens_from_env()
         if enable_in_flight_batching:
             self._start_engine(enable_prefix_cache, scheduling or {})
 
@@ -180,7 +186,13 @@ class LLM:
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
         t1 = time.perf_counter()
-        if sp.max_tokens > 1:
+        if self._forced is not None:
+            # teacher forcing: feed the listed ids step by step and return them as the output
+            forced = [self._forced[i][:sp.max_tokens] for i in range(n)]
+            for k in range(max(len(f) for f in forced) - 1):
+                self.runner.step(seats, [[f[min(k, len(f) - 1)]] for f in forced])
+            toks = torch.tensor([f + [f[-1]] * (sp.max_tokens - len(f)) for f in forced], dtype=torch.int32)
+        elif sp.max_tokens > 1:
             if sp.temperature < 1e-3:
                 rest = self.runner.decode_greedy(seats, first, sp.max_tokens - 1)
             else:

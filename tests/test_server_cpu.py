@@ -148,3 +148,24 @@ def test_jinja_chat_template(tmp_path):
     t = ChatTemplate.load(str(tmp_path))
     assert t.apply([{"role": "user", "content": "a"}, {"role": "assistant", "content": [{"type": "text", "text": "b"}]}]) == \
         "<s>[user] a</s>[assistant] b</s>[assistant]"
+
+
+def test_online_benchmark_against_the_app(llm):
+    import asyncio
+
+    import httpx
+
+    from tensorrt_edge_llm_b200.benchmarks.online import percentile, run_workload, synthetic_workload
+    assert percentile([1, 2, 3, 4], 50) == 2.5 and percentile([], 99) is None and percentile([5], 95) == 5
+    app = create_app(llm, ApiConfig(served_model_name="tiny"), ChatTemplate())
+    reqs = synthetic_workload(5, rate=50.0, prompt_len=4, max_tokens=4)
+    assert reqs[0]["at_s"] == 0.0 and all(b["at_s"] >= a["at_s"] for a, b in zip(reqs, reqs[1:]))
+
+    async def go():
+        async with httpx.AsyncClient(transport=httpx.ASGITransport(app=app), base_url="http://test") as client:
+            return await run_workload(reqs, "http://test", "tiny", client=client)
+
+    rep = asyncio.run(go())
+    assert rep["requests"] == 5 and rep["completed"] == 5 and rep["failed"] == 0
+    assert rep["output_tokens"] == 20 and rep["output_tokens_per_s"] > 0
+    assert rep["ttft_s"]["p50"] is not None and rep["latency_s"]["p99"] >= rep["latency_s"]["p50"]
