@@ -111,7 +111,10 @@ def bench_attention(args):
     meta = build_step_meta([q] * b, [past] * b, table, page, device="cuda")
     qt = torch.randn(b * q, hq, d, device="cuda").bfloat16()
     if args.variant >= 0:
-        cu._check(cu.lib().telb_set_decode_variant(args.variant), "set_decode_variant", 0)
+        if q > 4:
+            cu._check(cu.lib().telb_set_attn_variant(args.variant), "set_attn_variant", 0)
+        else:
+            cu._check(cu.lib().telb_set_decode_variant(args.variant), "set_decode_variant", 0)
     flip = [0]
 
     def fn():

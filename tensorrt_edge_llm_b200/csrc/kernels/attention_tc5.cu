@@ -50,7 +50,6 @@ struct AttnParams {
 
 constexpr int kAttnThreads = 192;
 constexpr int kKvTile = 64;
-constexpr int kKvStages = 4;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 
 __device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -65,8 +64,10 @@ __device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t (&r)[
         : "memory");
 }
 
-template <int D, typename T>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+// KVS: depth of the K and V tile rings; MINB: CTAs resident per SM.  Two resident CTAs with single-stage rings let
+// one CTA's MMAs run under the other's softmax; one CTA with deep rings prefetches further ahead.
+template <int D, typename T, int KVS, int MINB>
+__global__ void __launch_bounds__(kAttnThreads, MINB)
 attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_kv, AttnParams p) {
     constexpr int kDChunks = D / 64;
     constexpr int kQBytes = 128 * D * 2;
@@ -79,15 +80,15 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* s_q = smem;
     uint8_t* s_k = s_q + kQBytes;
-    uint8_t* s_v = s_k + kKvStages * kKvBytes;
-    uint8_t* s_p = s_v + kKvStages * kKvBytes;
+    uint8_t* s_v = s_k + KVS * kKvBytes;
+    uint8_t* s_p = s_v + KVS * kKvBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_p + 2 * kPBytes);
     uint64_t* q_full = bars;
     uint64_t* k_full = bars + 1;
-    uint64_t* k_empty = k_full + kKvStages;
-    uint64_t* v_full = k_empty + kKvStages;
-    uint64_t* v_empty = v_full + kKvStages;
-    uint64_t* s_full = v_empty + kKvStages;
+    uint64_t* k_empty = k_full + KVS;
+    uint64_t* v_full = k_empty + KVS;
+    uint64_t* v_empty = v_full + KVS;
+    uint64_t* s_full = v_empty + KVS;
     uint64_t* s_free = s_full + 2;
     uint64_t* p_full = s_free + 2;
     uint64_t* p_free = p_full + 2;
@@ -121,7 +122,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < kKvStages; ++s) {
+        for (int s = 0; s < KVS; ++s) {
             mbar_init(&k_full[s], 1);
             mbar_init(&k_empty[s], 1);
             mbar_init(&v_full[s], 1);
@@ -157,8 +158,8 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
                 tma_load_3d(s_q + c * (128 * 128), &tma_q, q_full, c * 64, kvh * p.group, qrow0 + tok0);
             const int tiles_per_page = p.page_size / kKvTile;
             for (int j = 0; j < ntiles; ++j) {
-                const int stage = j % kKvStages;
-                const uint32_t ph = ((j / kKvStages) & 1) ^ 1;
+                const int stage = j % KVS;
+                const uint32_t ph = ((j / KVS) & 1) ^ 1;
                 const int tile = j0 + j;
                 int page = p.page_table[(size_t)seq * p.max_pages + tile / tiles_per_page];
                 if (page < 0) page = 0;              // unreserved page: read page 0, the mask hides it
@@ -183,7 +184,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
             const uint32_t idesc_s = idesc_f16(128, kKvTile, kBf16);
             const uint32_t idesc_o = idesc_f16(128, D, kBf16, false, true);
             auto issue_s = [&](int j) {
-                const int stage = j % kKvStages;
+                const int stage = j % KVS;
                 const uint64_t dq = smem_desc_sw128(s_q);
                 const uint64_t dk = smem_desc_sw128(s_k + stage * kKvBytes);
                 const uint32_t d_tmem = tmem_base + (j & 1) * kKvTile;
@@ -205,15 +206,15 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
             for (int j = 0; j < ntiles && ok; ++j) {
                 if (j + 1 < ntiles) {
                     const int jn = j + 1;
-                    ok = mbar_wait(&k_full[jn % kKvStages], (jn / kKvStages) & 1, abort_flag, p.status, kStatusMmaTimeout) &&
+                    ok = mbar_wait(&k_full[jn % KVS], (jn / KVS) & 1, abort_flag, p.status, kStatusMmaTimeout) &&
                          mbar_wait(&s_free[jn & 1], ((jn >> 1) & 1) ^ 1, abort_flag, p.status, kStatusMmaTimeout);
                     if (!ok) break;
                     tc_fence_after_sync();
                     issue_s(jn);
                 }
-                const int stage = j % kKvStages;
+                const int stage = j % KVS;
                 ok = mbar_wait(&p_full[j & 1], (j >> 1) & 1, abort_flag, p.status, kStatusMmaTimeout) &&
-                     mbar_wait(&v_full[stage], (j / kKvStages) & 1, abort_flag, p.status, kStatusMmaTimeout);
+                     mbar_wait(&v_full[stage], (j / KVS) & 1, abort_flag, p.status, kStatusMmaTimeout);
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint64_t dp = smem_desc_sw128(s_p + (j & 1) * kPBytes);
@@ -420,18 +421,18 @@ __global__ void attn_combine_kernel(const float* __restrict__ ws_o, const float*
     out[(size_t)row * D + d] = Cvt<T>::from_f(acc);
 }
 
-template <int D, typename T>
-static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tkv, const AttnParams& p, int qtiles, int nseq,
-                       cudaStream_t stream) {
-    constexpr int smem = 128 * D * 2 + 2 * kKvStages * kKvTile * D * 2 + 2 * 128 * kKvTile * 2 + 1024 + 512;
+template <int D, typename T, int KVS, int MINB>
+static int launch_attn_variant(const CUtensorMap& tq, const CUtensorMap& tkv, const AttnParams& p, int qtiles, int nseq,
+                               cudaStream_t stream) {
+    constexpr int smem = 128 * D * 2 + 2 * KVS * kKvTile * D * 2 + 2 * 128 * kKvTile * 2 + 1024 + 512;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_tc5_kernel<D, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_tc5_kernel<D, T, KVS, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail("cudaFuncSetAttribute(attn_tc5)", e);
         configured = true;
     }
     dim3 grid(qtiles, p.hkv, nseq * p.splits);
-    TELB_LAUNCH("attn_tc5_kernel", (attn_tc5_kernel<D, T>), dim3(grid), dim3(kAttnThreads), smem, stream, tq, tkv, p);
+    TELB_LAUNCH("attn_tc5_kernel", (attn_tc5_kernel<D, T, KVS, MINB>), dim3(grid), dim3(kAttnThreads), smem, stream, tq, tkv, p);
     TELB_CHECK_LAUNCH("attn_tc5_kernel");
     if (p.splits > 1) {
         const int rows = p.total_tokens * p.hq;
@@ -441,9 +442,24 @@ static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tkv, const Attn
     return 0;
 }
 
+static int g_attn_variant = 0;
+
+template <int D, typename T>
+static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tkv, const AttnParams& p, int qtiles, int nseq, cudaStream_t stream) {
+    if (g_attn_variant == 1) return launch_attn_variant<D, T, 1, 2>(tq, tkv, p, qtiles, nseq, stream);     // 2 CTAs / SM, single-stage rings
+    return launch_attn_variant<D, T, 4, 1>(tq, tkv, p, qtiles, nseq, stream);                              // 1 CTA / SM, four-stage rings
+}
+
 }  // namespace telb
 
 using namespace telb;
+
+// Ring depth / residency variant of the tile attention kernel (0 or 1: see launch_attn); process-wide.
+extern "C" int telb_set_attn_variant(int v) {
+    if (v < 0 || v > 1) return fail("telb_set_attn_variant: variant must be 0 or 1");
+    g_attn_variant = v;
+    return 0;
+}
 
 // Merge `splits` partial results (ws_o [splits, rows, d] fp32, ws_lse [splits, rows]) into out [rows, d].
 extern "C" int telb_attn_combine(const float* ws_o, const float* ws_lse, void* out, int rows, int splits, int d, int is_bf16,

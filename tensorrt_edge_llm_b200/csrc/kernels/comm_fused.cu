@@ -113,18 +113,28 @@ __global__ void ar_add_rmsnorm_kernel(ArParams p) {
         for (int u = 0; u < kUnits; ++u) {
             const int idx = threadIdx.x + u * blockDim.x;
             if (idx < nunits) {
+                // every peer's 32 bytes are requested before any of them is consumed: the NVLink round trips overlap
+                uint4 pa[kMaxRanks], pb[kMaxRanks];
+#pragma unroll
+                for (int r = 0; r < kMaxRanks; ++r) {
+                    if (r < p.world && r != p.rank) {
+                        const T* src = reinterpret_cast<const T*>(p.sym_partial[r]) + ((size_t)par * p.max_rows + row) * p.hidden + idx * 16;
+                        pa[r] = ld_peer_v4(src);
+                        pb[r] = ld_peer_v4(src + 8);
+                    }
+                }
                 float acc[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-                for (int r = 0; r < p.world; ++r) {
+#pragma unroll
+                for (int r = 0; r < kMaxRanks; ++r) {
+                    if (r >= p.world) continue;
                     if (r == p.rank) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i) acc[i] += v[u][i];
                     } else {
-                        const T* src = reinterpret_cast<const T*>(p.sym_partial[r]) + ((size_t)par * p.max_rows + row) * p.hidden + idx * 16;
-                        const uint4 a0 = ld_peer_v4(src), a1 = ld_peer_v4(src + 8);
-                        const T* e0 = reinterpret_cast<const T*>(&a0);
-                        const T* e1 = reinterpret_cast<const T*>(&a1);
+                        const T* e0 = reinterpret_cast<const T*>(&pa[r]);
+                        const T* e1 = reinterpret_cast<const T*>(&pb[r]);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             acc[i] += Cvt<T>::to_f(e0[i]);
