@@ -152,3 +152,10 @@ def kv_commit_path(pool, page_table, past_len, path, path_len):
     if pool.is_cuda:
         return cuda_ops().kv_commit_path(pool, page_table, past_len, path, path_len)
     return ref.kv_commit_path(pool, page_table, past_len, path, path_len)
+
+
+def apply_token_bitmask(logits, bitmask):
+    """Entries whose bit is 0 in ``bitmask [rows, ceil(V/32)]`` become very negative (guided decoding)."""
+    if logits.is_cuda:
+        return cuda_ops().apply_token_bitmask(logits, bitmask)
+    return ref.apply_token_bitmask(logits, bitmask)

@@ -39,6 +39,24 @@ def _sampling(body: Dict[str, Any], default_max: int = 256) -> SamplingParams:
     return sp
 
 
+def _guided(body: Dict[str, Any]):
+    """OpenAI ``response_format`` and the ``guided_choice`` / ``guided_regex`` / ``guided_json`` extensions → matcher parameters."""
+    from ..runtime.guided import GuidedDecodingParams
+    if body.get("guided_choice"):
+        return GuidedDecodingParams("choice", choices=list(body["guided_choice"]))
+    if body.get("guided_regex"):
+        return GuidedDecodingParams("regex", pattern=str(body["guided_regex"]))
+    if body.get("guided_json"):
+        return GuidedDecodingParams("json_schema", json_schema=body["guided_json"])
+    rf = body.get("response_format") or {}
+    if rf.get("type") == "json_object":
+        return GuidedDecodingParams("json_object")
+    if rf.get("type") == "json_schema":
+        schema = (rf.get("json_schema") or {}).get("schema")
+        return GuidedDecodingParams("json_schema", json_schema=schema)
+    return None
+
+
 def _truncate_at_stop(text: str, stops) -> (str, bool):
     if isinstance(stops, str):
         stops = [stops]
@@ -129,6 +147,21 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
             return bad
         rid, created = f"chatcmpl-{uuid.uuid4().hex[:24]}", int(time.time())
         priority = int(body.get("priority", 0) or 0)
+        try:
+            guided = _guided(body)
+        except ValueError as e:
+            return _error(400, f"bad request: {e}")
+        if guided is not None:
+            try:
+                out = await client.generate_guided(ids, sp, guided)
+            except (QueueFull, QueueTimeout, EngineUnavailable) as e:
+                return _error(503 if not isinstance(e, QueueFull) else 429, str(e), "service_unavailable")
+            except ValueError as e:
+                return _error(400, str(e))
+            return {"id": rid, "object": "chat.completion", "created": created, "model": name,
+                    "choices": [{"index": 0, "message": {"role": "assistant", "content": out.text}, "finish_reason": out.finish_reason,
+                                 "token_ids": out.token_ids}],
+                    "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out.token_ids), "total_tokens": len(ids) + len(out.token_ids)}}
         if body.get("stream"):
             async def events():
                 head = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": name}
