@@ -104,7 +104,8 @@ class CheckpointReader:
                 self._where = dict(json.load(f)["weight_map"])
         else:
             for fn in sorted(os.listdir(model_dir)):
-                if fn.endswith(".safetensors"):
+                # side files (reduced vocabulary, processed LoRA) are not model shards
+                if fn.endswith(".safetensors") and fn not in ("vocab_map.safetensors", "lora_weights.safetensors"):
                     for k in self._open(fn).keys():
                         self._where[k] = fn
 

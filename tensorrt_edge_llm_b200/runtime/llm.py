@@ -35,7 +35,7 @@ class LLM:
                  max_batch_size: int = 64, max_input_len: int = 2048, max_kv_cache_capacity: int = 2304,
                  page_size: int = 64, max_num_tokens: int = 8192, random_init_seed: Optional[int] = 0,
                  tokenizer=None, kv_pages: Optional[int] = None, enable_in_flight_batching: bool = False,
-                 enable_prefix_cache: bool = False, scheduling: Optional[dict] = None):
+                 enable_prefix_cache: bool = False, scheduling: Optional[dict] = None, draft_model=None, speculative=None):
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.device = torch.device(device)
@@ -45,6 +45,9 @@ class LLM:
             self.model = AutoModel.from_pretrained(model, comm=comm, device=self.device)
         self.cfg = self.model.cfg
         self.tokenizer = tokenizer
+        self._vocab_map = None
+        if isinstance(model, str):
+            self._vocab_map = self._load_reduced_vocab(model)
         self.max_batch_size = max_batch_size
         self.max_input_len = max_input_len
         pages_per_seq = (max_kv_cache_capacity + page_size - 1) // page_size
@@ -52,7 +55,25 @@ class LLM:
         self.kv = KVCacheManager(self.cfg, total_pages, page_size, max_seats=max_batch_size,
                                  max_pages_per_seq=pages_per_seq, device=self.device)
         self.runner = ModelRunner(self.model, self.kv, self.device, max_num_tokens=max_num_tokens)
+        self.runner.vocab_map = self._vocab_map
         self.engine = None
+        # Speculative decoding (EAGLE-3 / MTP draft head): greedy requests on the static-batch path run draft → verify rounds.
+        self.spec_decoder = None
+        if draft_model is not None:
+            from .speculative import EagleDecoder, SpecConfig
+            draft = (AutoModel.from_config(draft_model, device=self.device, random_init=random_init_seed)
+                     if isinstance(draft_model, ModelConfig) else AutoModel.from_pretrained(draft_model, device=self.device))
+            if hasattr(draft, "share_lm_head") and not isinstance(draft_model, ModelConfig):
+                draft.share_lm_head(self.model)
+            spec = speculative or SpecConfig()
+            headroom = spec.verify_tokens + spec.draft_steps * spec.top_k
+            sp_pages = (max_kv_cache_capacity + headroom + page_size - 1) // page_size
+            self.kv = KVCacheManager(self.cfg, (kv_pages or sp_pages * max_batch_size + 1), page_size, max_seats=max_batch_size,
+                                     max_pages_per_seq=sp_pages, device=self.device)
+            self.runner = ModelRunner(self.model, self.kv, self.device, max_num_tokens=max_num_tokens)
+            dkv = KVCacheManager(draft.cfg, sp_pages * max_batch_size + 1, page_size, max_seats=max_batch_size, max_pages_per_seq=sp_pages,
+                                 device=self.device, num_layers=1)
+            self.spec_decoder = EagleDecoder(self.runner, draft, dkv, spec)
         from .debug import LayerDumper, forced_tokens_from_env
         self._dumper = LayerDumper.from_env()
         if self._dumper is not None:
@@ -61,6 +82,22 @@ class LLM:
         self._forced = forced_tokens_from_env()
         if enable_in_flight_batching:
             self._start_engine(enable_prefix_cache, scheduling or {})
+
+    def _load_reduced_vocab(self, model_dir: str):
+        """``vocab_map.safetensors`` next to the checkpoint (``trtedge reduce-vocab``): swap in the reduced LM head."""
+        import os
+        from ..checkpoint.safetensors_io import SafetensorsFile
+        p = os.path.join(model_dir, "vocab_map.safetensors")
+        if not os.path.exists(p) or self.cfg.tp_size > 1:
+            return None
+        f = SafetensorsFile(p)
+        from ..models.linear import Linear
+        w = f.get("lm_head.weight")
+        dtype = next(self.model.parameters()).dtype
+        head = Linear(w.shape[1], [w.shape[0]], dtype=dtype)
+        head.weight.data.copy_(w.to(dtype))
+        self.model.lm_head = head.to(self.device)
+        return f.get("vocab_map").clone().to(self.device, torch.int32)
 
     # ---- in-flight batching --------------------------------------------------------------------------
     def _start_engine(self, enable_prefix_cache: bool, scheduling: dict) -> None:
@@ -168,7 +205,28 @@ class LLM:
             outs.extend(self._generate_batch(ids[b0:b0 + self.max_batch_size], sp))
         return outs
 
+    def _generate_speculative(self, ids: List[List[int]], sp: SamplingParams) -> List[RequestOutput]:
+        """Greedy generation through draft → tree verify rounds (lossless: same tokens as plain greedy decoding)."""
+        dec = self.spec_decoder
+        n = len(ids)
+        seats = list(range(n))
+        dec.release(seats)
+        eos = self.cfg.eos_token_id
+        eos_id = None if sp.ignore_eos else (eos[0] if isinstance(eos, (list, tuple)) and eos else eos)
+        t0 = time.perf_counter()
+        toks = dec.generate(seats, [list(map(int, p)) for p in ids], sp.max_tokens, eos_id)
+        t1 = time.perf_counter()
+        dec.release(seats)
+        outs = []
+        for p, row in zip(ids, toks):
+            reason = "stop" if (eos_id is not None and row and row[-1] == eos_id) else "length"
+            text = self.tokenizer.decode(row) if self.tokenizer is not None else None
+            outs.append(RequestOutput(list(p), row, text, reason, 0.0, t1 - t0))
+        return outs
+
     def _generate_batch(self, ids: List[List[int]], sp: SamplingParams) -> List[RequestOutput]:
+        if self.spec_decoder is not None and sp.temperature < 1e-3 and not isinstance(ids, torch.Tensor):
+            return self._generate_speculative(ids, sp)
         n = len(ids)
         seats = list(range(n))
         for s in seats:

@@ -48,6 +48,8 @@ class ModelRunner:
         self.use_cuda_graphs = self.device.type == "cuda"
         # hybrid models address attention pools and recurrent state pools through the manager itself
         self.cache = kv if getattr(model, "needs_cache_set", False) else kv.pool
+        # reduced-vocabulary LM head: logits cover `vocab_map.numel()` columns, column c is token vocab_map[c]
+        self.vocab_map: Optional[torch.Tensor] = None
 
     # ---- eager ragged step -----------------------------------------------------------------
     def _meta(self, seats: Sequence[int], q_lens: Sequence[int], logits_all=False, tree_mask=None,
@@ -149,13 +151,20 @@ class ModelRunner:
         """Next token per row.  Greedy when ``temperature < 1e-3``; otherwise per-row top-k/top-p
         with a counter-based uniform per (seed, row, step) so draws do not depend on batch position."""
         if sp.temperature < 1e-3:
-            return ops.argmax(logits)
+            return self.pick(logits)
         n = logits.shape[0]
         g = torch.Generator(device="cpu").manual_seed(sp.seed * 1000003 + step)
         u = torch.rand(n, generator=g).to(logits.device)
         dev = logits.device
-        return ops.sample(logits, torch.full((n,), sp.temperature, device=dev), torch.full((n,), sp.top_k, device=dev, dtype=torch.int32),
-                          torch.full((n,), sp.top_p, device=dev), u)
+        return self.to_full_vocab(ops.sample(logits, torch.full((n,), sp.temperature, device=dev),
+                                             torch.full((n,), sp.top_k, device=dev, dtype=torch.int32), torch.full((n,), sp.top_p, device=dev), u))
+
+    def to_full_vocab(self, cols: torch.Tensor) -> torch.Tensor:
+        return cols if self.vocab_map is None else self.vocab_map[cols.long()]
+
+    def pick(self, logits: torch.Tensor) -> torch.Tensor:
+        """Greedy token per row, as ids of the full vocabulary."""
+        return self.to_full_vocab(ops.argmax(logits))
 
     @torch.no_grad()
     def decode_sampled(self, seats, first_tokens, steps, sp: SamplingParams) -> torch.Tensor:
@@ -188,7 +197,7 @@ class ModelRunner:
             cols = []
             for _ in range(steps):
                 logits = self.step(seats, [[int(t)] for t in toks.tolist()])
-                toks = ops.argmax(logits)
+                toks = self.pick(logits)
                 cols.append(toks)
             return torch.stack(cols, dim=1)
         for s in seats:
@@ -225,7 +234,7 @@ class _DecodeGraph:
     def _body(self):
         m = self.meta
         logits = self.r.model(self.ids, m, self.r.cache)
-        tok = ops.argmax(logits)
+        tok = self.r.pick(logits)
         self.ids.copy_(tok)
         self.out.index_copy_(0, self.step_idx, tok.unsqueeze(0))
         self.step_idx.add_(1)

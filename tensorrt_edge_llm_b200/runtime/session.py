@@ -135,7 +135,7 @@ class ModelSession(rt.RuntimeSession):
     # ---- sampling --------------------------------------------------------------------------------
     def _sample(self, logits: torch.Tensor, seqs: List[_Seq]) -> List[int]:
         if all(q.req.temperature < 1e-3 for q in seqs):
-            return [int(t) for t in ops.argmax(logits).tolist()]
+            return [int(t) for t in self.runner.pick(logits).tolist()]
         n = logits.shape[0]
         dev = logits.device
         temp = torch.tensor([q.req.temperature for q in seqs], device=dev)
@@ -143,4 +143,4 @@ class ModelSession(rt.RuntimeSession):
         topp = torch.tensor([q.req.top_p for q in seqs], device=dev)
         # the uniform depends on (seed, request, step) only, so batching never changes a request's draws
         u = torch.tensor([rt.request_stable_uniform(q.req.seed, q.request_id, q.generated) for q in seqs], device=dev)
-        return [int(t) for t in ops.sample(logits, temp, topk, topp, u).tolist()]
+        return [int(t) for t in self.runner.to_full_vocab(ops.sample(logits, temp, topk, topp, u)).tolist()]

@@ -22,7 +22,14 @@ def build_llm(cfg: ServerConfig):
             tok = rt.Tokenizer.load_from_hf(m.model)
     except ImportError:
         tok = None
-    llm = LLM(m.model, device=m.device or None, max_batch_size=m.max_batch_size, max_input_len=m.max_input_len,
+    spec_kw = {}
+    if m.speculative_config is not None and m.speculative_config.draft_model:
+        from ..runtime.speculative import SpecConfig
+        sc = m.speculative_config
+        spec_kw = {"draft_model": sc.draft_model,
+                   "speculative": SpecConfig(draft_steps=sc.num_speculative_tokens or 4, top_k=sc.draft_top_k or 8,
+                                             verify_tokens=sc.verify_tokens or 32)}
+    llm = LLM(m.model, device=m.device or None, **spec_kw, max_batch_size=m.max_batch_size, max_input_len=m.max_input_len,
               max_kv_cache_capacity=m.max_kv_cache_capacity, page_size=m.kv_page_size, max_num_tokens=m.max_num_tokens or 8192,
               tokenizer=tok, enable_in_flight_batching=m.enable_in_flight_batching,
               enable_prefix_cache=m.context_cache_config.enabled, scheduling=m.scheduling_dict() if m.enable_in_flight_batching else None)

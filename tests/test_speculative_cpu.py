@@ -156,3 +156,21 @@ def test_mtp_head_is_lossless_and_shares_lm_head():
 from tensorrt_edge_llm_b200.models.mtp import MtpDraft  # noqa: E402
 
 MtpDraftRemap = MtpDraft.checkpoint_key_remap
+
+
+def test_llm_generate_with_draft_model_is_lossless():
+    from tensorrt_edge_llm_b200.runtime.llm import LLM
+    from tensorrt_edge_llm_b200.runtime.runner import SamplingParams
+    cfg = tiny_llama_config(num_hidden_layers=4, dtype="float32")
+    dcfg = tiny_llama_config(num_hidden_layers=1, dtype="float32")
+    dcfg.draft_type, dcfg.eagle3_target_hidden_size = "eagle3", cfg.hidden_size
+    kw = dict(device="cpu", max_batch_size=2, max_input_len=64, max_kv_cache_capacity=128, page_size=16, random_init_seed=1)
+    plain = LLM(cfg, **kw)
+    spec = LLM(cfg, draft_model=dcfg, speculative=SpecConfig(draft_steps=3, top_k=2, verify_tokens=8), **kw)
+    prompts = [[3, 1, 4, 1, 5], [9, 2, 6, 5, 3, 5, 8]]
+    sp = SamplingParams(max_tokens=9, ignore_eos=True)
+    a, b = plain.generate(prompts, sp), spec.generate(prompts, sp)
+    assert [o.token_ids for o in a] == [o.token_ids for o in b]
+    assert spec.spec_decoder.stats.rounds > 0 and spec.kv.lengths[0] == 0          # seats released afterwards
+    # sampled requests fall back to ordinary decoding
+    assert len(spec.generate(prompts, SamplingParams(max_tokens=4, temperature=0.8, ignore_eos=True))[0].token_ids) == 4

@@ -136,6 +136,35 @@ def test_reduce_vocab(ckpt, tmp_path):
     assert map_to_full(torch.tensor([4, 0]), torch.tensor(vm)).tolist() == [400, 1]
 
 
+def test_reduced_vocab_at_run_time(ckpt, tmp_path):
+    """An LLM opened on a directory that holds ``vocab_map.safetensors`` runs the reduced head and returns full-vocabulary ids."""
+    import shutil
+    from tensorrt_edge_llm_b200.runtime.llm import LLM, SamplingParams
+    from tensorrt_edge_llm_b200.vocab_reduction import reduce_vocab
+    prompts = [[5, 9, 33, 70], [8, 2, 44]]
+    sp = SamplingParams(max_tokens=6, temperature=0.0)
+    full = [o.token_ids for o in LLM(ckpt, max_batch_size=2, max_kv_cache_capacity=128, device="cpu").generate(prompts, sp)]
+    vocab = AutoModel.from_pretrained(ckpt).cfg.vocab_size
+    # every token kept, in a shuffled order: the outputs must not change
+    perm_dir = str(tmp_path / "perm")
+    shutil.copytree(ckpt, perm_dir)
+    reduce_vocab(ckpt, perm_dir, torch.randperm(vocab, generator=torch.Generator().manual_seed(1)))
+    llm = LLM(perm_dir, max_batch_size=2, max_kv_cache_capacity=128, device="cpu")
+    assert llm.model.lm_head.out_features == vocab
+    assert [o.token_ids for o in llm.generate(prompts, sp)] == full
+    # a strict subset: every generated id lies in it, with and without in-flight batching
+    sub_dir = str(tmp_path / "sub")
+    shutil.copytree(ckpt, sub_dir)
+    keep = torch.arange(3, vocab, 7)
+    reduce_vocab(ckpt, sub_dir, keep)
+    allowed = set(keep.tolist())
+    for ifb in (False, True):
+        llm = LLM(sub_dir, max_batch_size=2, max_kv_cache_capacity=128, device="cpu", enable_in_flight_batching=ifb)
+        assert llm.model.lm_head.out_features == keep.numel()
+        for o in llm.generate(prompts, SamplingParams(max_tokens=6, temperature=0.8, top_k=20, seed=3)):
+            assert len(o.token_ids) > 0 and set(o.token_ids) <= allowed
+
+
 def test_build_checks_checkpoint(ckpt, tmp_path):
     out = str(tmp_path / "built")
     assert trtedge(["build", ckpt, "--output_dir", out, "--tensor-parallel-size", "2", "--max-batch-size", "4"]) == 0
