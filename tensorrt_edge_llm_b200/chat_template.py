@@ -59,6 +59,7 @@ class ChatTemplate:
         self.special = special or {"bos_token": "", "eos_token": ""}
         self._native = native
         self._jinja = None
+        self.source = jinja_text or ""
         if jinja_text:
             from jinja2.sandbox import ImmutableSandboxedEnvironment
 

@@ -102,9 +102,15 @@ PYBIND11_MODULE(_telb_runtime, m) {
         .value("Cancelled", FinishReason::kCancelled)
         .value("Error", FinishReason::kError)
         .value("StopWords", FinishReason::kStopWords);
+    py::class_<TokenLogprobs>(m, "TokenLogprobs")
+        .def(py::init<>())
+        .def_readwrite("chosen", &TokenLogprobs::chosen)
+        .def_readwrite("top_ids", &TokenLogprobs::top_ids)
+        .def_readwrite("top_values", &TokenLogprobs::top_values);
     py::class_<StreamChunk>(m, "StreamChunk")
         .def(py::init<>())
         .def_readwrite("token_ids", &StreamChunk::token_ids)
+        .def_readwrite("logprobs", &StreamChunk::logprobs)
         .def_readwrite("text", &StreamChunk::text)
         .def_readwrite("finished", &StreamChunk::finished)
         .def_readwrite("reason", &StreamChunk::reason);
@@ -115,7 +121,7 @@ PYBIND11_MODULE(_telb_runtime, m) {
         .def_property_readonly("decode_tokens_per_second", &GenerationMetrics::decode_tokens_per_second);
     py::class_<StreamChannel, std::shared_ptr<StreamChannel>>(m, "StreamChannel")
         .def_static("create", &StreamChannel::create, py::arg("collect_metrics") = false)
-        .def("push", &StreamChannel::push)
+        .def("push", &StreamChannel::push, py::arg("tokens"), py::arg("logprobs") = TokenLogprobs())
         .def("finish", &StreamChannel::finish)
         .def("try_pop", [](StreamChannel& c) -> py::object {
             StreamChunk ch;
@@ -224,7 +230,12 @@ PYBIND11_MODULE(_telb_runtime, m) {
         .def_readwrite("priority", &GenerationRequest::priority)
         .def_readwrite("exclusive", &GenerationRequest::exclusive)
         .def_readwrite("lora_name", &GenerationRequest::lora_name)
-        .def_readwrite("stream_interval", &GenerationRequest::stream_interval);
+        .def_readwrite("stream_interval", &GenerationRequest::stream_interval)
+        .def_readwrite("num_logprobs", &GenerationRequest::num_logprobs)
+        .def_readwrite("guided_type", &GenerationRequest::guided_type)
+        .def_readwrite("guided_spec", &GenerationRequest::guided_spec)
+        .def_readwrite("logit_bias_ids", &GenerationRequest::logit_bias_ids)
+        .def_readwrite("logit_bias_values", &GenerationRequest::logit_bias_values);
     py::class_<AdmissionResult>(m, "AdmissionResult")
         .def(py::init<>())
         .def_readwrite("admitted", &AdmissionResult::admitted)
@@ -236,6 +247,7 @@ PYBIND11_MODULE(_telb_runtime, m) {
         .def(py::init<>())
         .def_readwrite("slot", &TokenDelta::slot)
         .def_readwrite("tokens", &TokenDelta::tokens)
+        .def_readwrite("logprobs", &TokenDelta::logprobs)
         .def_readwrite("finished", &TokenDelta::finished)
         .def_readwrite("reason", &TokenDelta::reason);
     py::class_<StepResult>(m, "StepResult").def(py::init<>()).def_readwrite("deltas", &StepResult::deltas);
@@ -286,6 +298,7 @@ PYBIND11_MODULE(_telb_runtime, m) {
             py::gil_scoped_release rel;
             return h.get(timeout_s);
         }, py::arg("timeout_s") = 1e9)
+        .def("logprobs", &RequestHandle::logprobs)
         .def("reason", &RequestHandle::reason)
         .def("error", &RequestHandle::error)
         .def("cancel", &RequestHandle::cancel)

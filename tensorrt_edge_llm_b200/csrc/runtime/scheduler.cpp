@@ -158,6 +158,10 @@ std::vector<int32_t> RequestHandle::get(double timeout_s) {
     if (!done_) throw std::runtime_error("request timed out");
     return tokens_;
 }
+TokenLogprobs RequestHandle::logprobs() const {
+    std::lock_guard<std::mutex> lk(mu_);
+    return logprobs_;
+}
 FinishReason RequestHandle::reason() const {
     std::lock_guard<std::mutex> lk(mu_);
     return reason_;
@@ -427,9 +431,10 @@ void RequestEngine::run_step() {
                     r.handle->stats_.ttft_s = std::chrono::duration<double>(r.handle->t_first_ - r.handle->t_submit_).count();
                 }
                 r.handle->tokens_.insert(r.handle->tokens_.end(), d.tokens.begin(), d.tokens.end());
+                r.handle->logprobs_.append(d.logprobs);
             }
             r.st.generated += static_cast<int>(d.tokens.size());
-            r.handle->channel_->push(d.tokens);
+            r.handle->channel_->push(d.tokens, d.logprobs);
         }
         FinishReason why = d.finished ? d.reason : FinishReason::kNotFinished;
         if (why == FinishReason::kNotFinished && r.st.generated >= r.req.max_tokens) why = FinishReason::kLength;

@@ -130,6 +130,11 @@ struct GenerationRequest {
     bool exclusive = false;
     std::string lora_name;
     int stream_interval = 1;
+    int num_logprobs = -1;                  // -1 = none; 0 = the chosen token's only; k = plus the k most likely
+    std::string guided_type;                // "", "json_object", "json_schema", "regex", "choice"
+    std::string guided_spec;                // JSON text of the constraint's parameters
+    std::vector<int32_t> logit_bias_ids;    // additive bias on these token ids ...
+    std::vector<float> logit_bias_values;   // ... by these amounts, before sampling
 };
 
 struct AdmissionResult {
@@ -143,6 +148,7 @@ struct AdmissionResult {
 struct TokenDelta {
     int slot = -1;
     std::vector<int32_t> tokens;
+    TokenLogprobs logprobs;                 // empty unless the request asked for them
     bool finished = false;
     FinishReason reason = FinishReason::kNotFinished;
 };
@@ -203,6 +209,7 @@ class RequestHandle {
     bool ready() const;
     // Blocks until the request finishes; returns all generated tokens.
     std::vector<int32_t> get(double timeout_s = 1e9);
+    TokenLogprobs logprobs() const;         // of the tokens generated so far
     FinishReason reason() const;
     std::string error() const;
     void cancel() { channel_->cancel(); }
@@ -216,6 +223,7 @@ class RequestHandle {
     std::condition_variable cv_;
     bool done_ = false;
     std::vector<int32_t> tokens_;
+    TokenLogprobs logprobs_;
     FinishReason reason_ = FinishReason::kNotFinished;
     std::string error_;
     RequestStats stats_;

@@ -19,10 +19,11 @@ void StreamChannel::flush_locked(bool force) {
     if (!force && static_cast<int>(pending_.size()) < interval_) return;
     StreamChunk c;
     c.token_ids.swap(pending_);
+    std::swap(c.logprobs, pending_lp_);
     q_.push_back(std::move(c));
 }
 
-void StreamChannel::push(const std::vector<int32_t>& tokens) {
+void StreamChannel::push(const std::vector<int32_t>& tokens, const TokenLogprobs& logprobs) {
     {
         std::lock_guard<std::mutex> lk(mu_);
         if (finished_) return;
@@ -31,6 +32,7 @@ void StreamChannel::push(const std::vector<int32_t>& tokens) {
         t_last_ = now;
         generated_ += static_cast<int>(tokens.size());
         pending_.insert(pending_.end(), tokens.begin(), tokens.end());
+        pending_lp_.append(logprobs);
         flush_locked(false);
     }
     cv_.notify_all();
@@ -44,6 +46,7 @@ void StreamChannel::finish(FinishReason reason) {
         reason_ = reason;
         StreamChunk c;
         c.token_ids.swap(pending_);
+        std::swap(c.logprobs, pending_lp_);
         c.finished = true;
         c.reason = reason;
         q_.push_back(std::move(c));

@@ -20,8 +20,23 @@ namespace telb {
 enum class FinishReason { kNotFinished = 0, kEndId, kLength, kCancelled, kError, kStopWords };
 const char* to_string(FinishReason r);
 
+// Log-probabilities that travel with generated tokens: `chosen[i]` belongs to token i; when the request
+// asked for the k most likely alternatives, `top_ids` / `top_values` hold k entries per token.
+struct TokenLogprobs {
+    std::vector<float> chosen;
+    std::vector<int32_t> top_ids;
+    std::vector<float> top_values;
+    bool empty() const { return chosen.empty(); }
+    void append(const TokenLogprobs& o) {
+        chosen.insert(chosen.end(), o.chosen.begin(), o.chosen.end());
+        top_ids.insert(top_ids.end(), o.top_ids.begin(), o.top_ids.end());
+        top_values.insert(top_values.end(), o.top_values.begin(), o.top_values.end());
+    }
+};
+
 struct StreamChunk {
     std::vector<int32_t> token_ids;
+    TokenLogprobs logprobs;
     std::string text;            // filled by a detokenising consumer, empty otherwise
     bool finished = false;
     FinishReason reason = FinishReason::kNotFinished;
@@ -42,7 +57,7 @@ class StreamChannel {
         return std::shared_ptr<StreamChannel>(new StreamChannel(collect_metrics));
     }
     // producer side (actor thread)
-    void push(const std::vector<int32_t>& tokens);
+    void push(const std::vector<int32_t>& tokens, const TokenLogprobs& logprobs = TokenLogprobs());
     void finish(FinishReason reason);
     // consumer side
     bool try_pop(StreamChunk& out);
@@ -61,6 +76,7 @@ class StreamChannel {
     std::condition_variable cv_;
     std::deque<StreamChunk> q_;
     std::vector<int32_t> pending_;
+    TokenLogprobs pending_lp_;
     std::atomic<bool> cancelled_{false};
     bool finished_ = false;
     FinishReason reason_ = FinishReason::kNotFinished;

@@ -262,6 +262,9 @@ class GuidedDecoder:
             return
         piece = self.token_texts[token] if 0 <= token < len(self.token_texts) else None
         if piece is None or not self.matcher.viable(self.text + piece):
+            if not self.eos and self.matcher.complete(self.text):      # nothing can follow and the model has no end token: done
+                self.finished = True
+                return
             raise ValueError(f"token {token} violates the constraint after {self.text!r}")
         self.text += piece
 

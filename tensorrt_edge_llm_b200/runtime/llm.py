@@ -17,6 +17,7 @@ import torch
 from ..config import (QUANT_NVFP4, Mapping, ModelConfig, QuantConfig)
 from ..model import AutoModel
 from .kv_cache import KVCacheManager
+from . import logits as lp
 from .runner import ModelRunner, SamplingParams
 
 
@@ -28,6 +29,7 @@ class RequestOutput:
     finish_reason: str = "length"
     ttft_s: float = 0.0
     decode_s: float = 0.0
+    logprobs: Optional[List[dict]] = None      # per token: {"token_id", "logprob", "top": [(id, logprob), ...]}
 
 
 class LLM:
@@ -56,6 +58,8 @@ class LLM:
                                  max_pages_per_seq=pages_per_seq, device=self.device)
         self.runner = ModelRunner(self.model, self.kv, self.device, max_num_tokens=max_num_tokens)
         self.runner.vocab_map = self._vocab_map
+        eos0 = self.cfg.eos_token_id
+        self.guided_vocab = lp.GuidedVocabulary(tokenizer, self.cfg.vocab_size, eos0 if isinstance(eos0, (list, tuple)) else [eos0])
         self.engine = None
         # Speculative decoding (EAGLE-3 / MTP draft head): greedy requests on the static-batch path run draft → verify rounds.
         self.spec_decoder = None
@@ -120,14 +124,32 @@ class LLM:
             setattr(opts, k, v)
         cfg.scheduling = opts
         self._rt = rt
-        self.engine = rt.RequestEngine(cfg, lambda: ModelSession(self.runner, eos_ids, enable_prefix_cache, self.max_input_len))
+        self.engine = rt.RequestEngine(cfg, lambda: ModelSession(self.runner, eos_ids, enable_prefix_cache, self.max_input_len,
+                                                                 self.guided_vocab))
 
     def _native_request(self, ids, sp: SamplingParams, priority: int = 0):
         r = self._rt.GenerationRequest()
         r.prompt_ids = [int(t) for t in ids]
         r.max_tokens, r.temperature, r.top_k, r.top_p = sp.max_tokens, sp.temperature, sp.top_k, sp.top_p
         r.seed, r.ignore_eos, r.stop_token_ids, r.priority = sp.seed, sp.ignore_eos, list(sp.stop_token_ids), priority
+        if sp.logprobs is not None:
+            r.num_logprobs = int(sp.logprobs)
+        if sp.logit_bias:
+            r.logit_bias_ids = [int(k) for k in sp.logit_bias]
+            r.logit_bias_values = [float(v) for v in sp.logit_bias.values()]
+        if sp.guided is not None:
+            r.guided_type, r.guided_spec = lp.guided_to_wire(sp.guided)
         return r
+
+    @staticmethod
+    def _logprob_rows(tokens, rep) -> Optional[List[dict]]:
+        """Native ``TokenLogprobs`` → one dict per generated token."""
+        if rep is None or not rep.chosen:
+            return None
+        n = len(rep.chosen)
+        k = len(rep.top_ids) // n if n else 0
+        return [{"token_id": int(tokens[i]) if i < len(tokens) else None, "logprob": float(rep.chosen[i]),
+                 "top": [(int(rep.top_ids[i * k + j]), float(rep.top_values[i * k + j])) for j in range(k)]} for i in range(n)]
 
     def submit(self, prompt, sampling_params: Optional[SamplingParams] = None, priority: int = 0):
         """Queue one request on the in-flight-batching engine; returns the native ``RequestHandle``
@@ -192,7 +214,10 @@ class LLM:
                           self._rt.FinishReason.StopWords: "stop", self._rt.FinishReason.Cancelled: "cancelled",
                           self._rt.FinishReason.Error: "error"}.get(h.reason(), "length")
                 text = self.tokenizer.decode(toks) if self.tokenizer is not None else None
-                outs.append(RequestOutput(p, toks, text, reason, st.ttft_s, max(st.total_s - st.ttft_s, 0.0)))
+                if reason == "error" and h.error():
+                    raise ValueError(h.error()) if "EDGELLM_BAD_REQUEST" in h.error() else RuntimeError(h.error())
+                outs.append(RequestOutput(p, toks, text, reason, st.ttft_s, max(st.total_s - st.ttft_s, 0.0),
+                                          self._logprob_rows(toks, h.logprobs())))
             return outs
         if isinstance(prompts, torch.Tensor):
             outs = []
@@ -224,7 +249,62 @@ class LLM:
             outs.append(RequestOutput(list(p), row, text, reason, 0.0, t1 - t0))
         return outs
 
+    def _generate_processed(self, ids: List[List[int]], sp: SamplingParams) -> List[RequestOutput]:
+        """Static-batch generation with per-step logits processing (bias, constraint mask, log-probabilities)."""
+        n = len(ids)
+        seats = list(range(n))
+        for s in seats:
+            self.kv.free(s)
+        for s, p in zip(seats, ids):
+            self.kv.reserve(s, len(p) + sp.max_tokens)
+        states = [lp.make_row_state(self.guided_vocab, guided=sp.guided, logit_bias=sp.logit_bias, num_logprobs=sp.logprobs,
+                                    vocab_size=self.cfg.vocab_size) for _ in range(n)]
+        eos = self.cfg.eos_token_id
+        eos_set = set(int(e) for e in (eos if isinstance(eos, (list, tuple)) else [eos]) if e is not None) | set(sp.stop_token_ids)
+        was, self.runner.use_cuda_graphs = self.runner.use_cuda_graphs, False
+        rows: List[List[int]] = [[] for _ in range(n)]
+        reports: List[List[dict]] = [[] for _ in range(n)]
+        reasons = ["length"] * n
+        live = list(range(n))
+        t0 = time.perf_counter()
+        try:
+            logits = self.runner.prefill(seats, [list(map(int, p)) for p in ids])
+            t1 = time.perf_counter()
+            for step in range(sp.max_tokens):
+                st = [states[i] for i in live]
+                proc = lp.process(logits, st)
+                toks = [int(t) for t in self.runner.sample(proc, sp, step=step).tolist()]
+                reps = lp.logprobs(proc, toks, st)
+                done = lp.advance(st, toks)
+                keep = []
+                for j, i in enumerate(live):
+                    if done[j]:
+                        reasons[i] = "stop"
+                        continue
+                    rows[i].append(toks[j])
+                    if reps[j] is not None:
+                        reports[i].append({"token_id": toks[j], "logprob": reps[j].chosen[0],
+                                           "top": list(zip(reps[j].top_ids[0], reps[j].top_values[0]))})
+                    if not sp.ignore_eos and toks[j] in eos_set:
+                        reasons[i] = "stop"
+                        continue
+                    keep.append(j)
+                if not keep or step == sp.max_tokens - 1:
+                    break
+                live_next = [live[j] for j in keep]
+                logits = self.runner.step([seats[i] for i in live_next], [[rows[i][-1]] for i in live_next])
+                live = live_next
+        finally:
+            self.runner.use_cuda_graphs = was
+            for s in seats:
+                self.kv.free(s)
+        t2 = time.perf_counter()
+        return [RequestOutput(list(ids[i]), rows[i], self.tokenizer.decode(rows[i]) if self.tokenizer is not None else None, reasons[i],
+                              t1 - t0, t2 - t1, reports[i] or None) for i in range(n)]
+
     def _generate_batch(self, ids: List[List[int]], sp: SamplingParams) -> List[RequestOutput]:
+        if sp.needs_logits_processing:
+            return self._generate_processed([p.tolist() for p in ids] if isinstance(ids, torch.Tensor) else ids, sp)
         if self.spec_decoder is not None and sp.temperature < 1e-3 and not isinstance(ids, torch.Tensor):
             return self._generate_speculative(ids, sp)
         n = len(ids)

@@ -31,7 +31,13 @@ class SamplingParams:
     seed: int = 42
     ignore_eos: bool = False
     stop_token_ids: Sequence[int] = ()
-    logprobs: int = 0
+    logprobs: Optional[int] = None          # None = off; k = report the chosen token's log-probability and the k most likely
+    logit_bias: Optional[dict] = None       # token id → additive bias on its logit
+    guided: Optional[object] = None         # runtime.guided.GuidedDecodingParams
+
+    @property
+    def needs_logits_processing(self) -> bool:
+        return self.logprobs is not None or bool(self.logit_bias) or self.guided is not None
 
 
 class ModelRunner:

@@ -18,12 +18,13 @@ import torch
 
 from .. import ops
 from ..ops.meta import build_step_meta
+from . import logits as lp
 from . import native as rt
 from .runner import ModelRunner, SamplingParams
 
 
 class _Seq:
-    __slots__ = ("req", "request_id", "tokens", "generated", "last_token", "finished")
+    __slots__ = ("req", "request_id", "tokens", "generated", "last_token", "finished", "row_state")
 
     def __init__(self, req, request_id):
         self.req, self.request_id = req, request_id
@@ -31,12 +32,15 @@ class _Seq:
         self.generated = 0
         self.last_token: Optional[int] = None
         self.finished = False
+        self.row_state = None            # logits.RowState when the request biases, constrains or reports log-probabilities
 
 
 class ModelSession(rt.RuntimeSession):
-    def __init__(self, runner: ModelRunner, eos_ids=(), enable_prefix_cache: bool = False, max_input_len: int = 2048):
+    def __init__(self, runner: ModelRunner, eos_ids=(), enable_prefix_cache: bool = False, max_input_len: int = 2048,
+                 guided_vocab=None):
         super().__init__()
         self.runner = runner
+        self.guided_vocab = guided_vocab
         self.kv = runner.kv
         self.eos = set(int(e) for e in eos_ids if e is not None)
         self.max_input_len = max_input_len
@@ -62,6 +66,18 @@ class ModelSession(rt.RuntimeSession):
         if n > self.max_input_len or need > self.kv.max_pages_per_seq * self.kv.page_size:
             r.admitted, r.retry_later, r.reason = False, False, "EDGELLM_INPUT_TOO_LONG: prompt + max_tokens exceed the KV capacity"
             return r
+        row_state = None
+        if req.guided_type or req.logit_bias_ids or req.num_logprobs >= 0:
+            try:
+                if req.guided_type and self.runner.vocab_map is not None:
+                    raise ValueError("guided decoding is not combined with a reduced vocabulary")
+                row_state = lp.make_row_state(
+                    self.guided_vocab, guided=lp.guided_from_wire(req.guided_type, req.guided_spec),
+                    logit_bias=dict(zip(req.logit_bias_ids, req.logit_bias_values)) or None,
+                    num_logprobs=req.num_logprobs if req.num_logprobs >= 0 else None, vocab_size=self.runner.model.cfg.vocab_size)
+            except ValueError as e:
+                r.admitted, r.retry_later, r.reason = False, False, f"EDGELLM_BAD_REQUEST: {e}"
+                return r
         slot = self.slots.acquire()
         if slot < 0:
             r.admitted, r.retry_later, r.reason = False, True, "no free seat"
@@ -83,6 +99,7 @@ class ModelSession(rt.RuntimeSession):
                 r.admitted, r.retry_later, r.reason = False, True, f"KV pool full: {e}"
             return r
         self.seqs[slot] = _Seq(req, request_id)
+        self.seqs[slot].row_state = row_state
         r.admitted, r.slot, r.reused_tokens = True, slot, reused
         return r
 
@@ -105,15 +122,30 @@ class ModelSession(rt.RuntimeSession):
         deltas = []
         if rows:
             sel = logits[rows] if len(rows) != logits.shape[0] else logits
-            new = self._sample(sel, [self.seqs[seats[i]] for i in rows])
-            for i, tok in zip(rows, new):
+            row_seqs = [self.seqs[seats[i]] for i in rows]
+            states = [q.row_state for q in row_seqs]
+            special = any(st is not None for st in states)
+            if special:
+                sel = lp.process(sel, states)
+            new = self._sample(sel, row_seqs)
+            if special:
+                reports = lp.logprobs(sel, new, states)
+                constraint_done = lp.advance(states, new)
+            for j, (i, tok) in enumerate(zip(rows, new)):
                 q = self.seqs[seats[i]]
                 q.generated += 1
                 q.last_token = tok
                 q.tokens.append(tok)
                 d = rt.TokenDelta()
                 d.slot, d.tokens = seats[i], [tok]
-                if not q.req.ignore_eos and (tok in self.eos or tok in q.req.stop_token_ids):
+                if special and reports[j] is not None:
+                    rep = rt.TokenLogprobs()
+                    rep.chosen, rep.top_ids, rep.top_values = reports[j].chosen, reports[j].top_ids[0], reports[j].top_values[0]
+                    d.logprobs = rep
+                if special and constraint_done[j]:
+                    d.tokens = []                        # the end-of-sequence token that closes a constraint is not output
+                    d.finished, d.reason = True, rt.FinishReason.EndId
+                elif not q.req.ignore_eos and (tok in self.eos or tok in q.req.stop_token_ids):
                     d.finished = True
                     d.reason = rt.FinishReason.EndId if tok in self.eos else rt.FinishReason.StopWords
                 deltas.append(d)

@@ -18,6 +18,7 @@ from fastapi.responses import JSONResponse, StreamingResponse
 from ..chat_template import ChatTemplate
 from ..runtime.llm import LLM
 from ..runtime.runner import SamplingParams
+from . import parsing
 from .config import ApiConfig
 from .engine_client import EngineClient, EngineUnavailable, QueueFull, QueueTimeout
 
@@ -36,6 +37,19 @@ def _sampling(body: Dict[str, Any], default_max: int = 256) -> SamplingParams:
     sp.max_tokens = int(max_tokens)
     if sp.max_tokens < 1:
         raise ValueError("max_tokens must be at least 1")
+    # chat form: logprobs=true + top_logprobs=k; completions form: logprobs=k
+    want = body.get("logprobs")
+    if isinstance(want, bool):
+        sp.logprobs = int(body.get("top_logprobs") or 0) if want else None
+    elif want is not None:
+        sp.logprobs = int(want)
+    if sp.logprobs is not None and not 0 <= sp.logprobs <= 50:
+        raise ValueError("top_logprobs must be in 0..50")
+    bias = body.get("logit_bias")
+    if bias:
+        if not isinstance(bias, dict):
+            raise ValueError("logit_bias must map token ids to biases")
+        sp.logit_bias = {int(k): float(v) for k, v in bias.items()}
     return sp
 
 
@@ -70,6 +84,7 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
     client = EngineClient(llm, api.max_queued_requests, api.queue_timeout)
     template = chat_template or ChatTemplate()
     name = api.served_model_name or model_name or "model"
+    reasoning = parsing.resolve_reasoning_parser(api.reasoning_parser, getattr(template, "source", ""))
     app = FastAPI(title="tensorrt_edge_llm_b200", version="1")
     app.state.client, app.state.started = client, time.time()
 
@@ -138,10 +153,12 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
             if not isinstance(messages, list) or not messages:
                 raise ValueError("messages must be a non-empty list")
             sp = _sampling(body)
+            tool_cfg = parsing.validate_tool_request(body)
             prompt = template.apply(messages, True, body.get("tools"), bool((body.get("chat_template_kwargs") or {}).get("enable_thinking", True)))
             ids = encode(prompt)
         except (KeyError, ValueError, TypeError, json.JSONDecodeError) as e:
             return _error(400, f"bad request: {e}")
+        want_parse = reasoning is not None or tool_cfg.parse_output
         bad = check_len(ids)
         if bad:
             return bad
@@ -158,34 +175,66 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
                 return _error(503 if not isinstance(e, QueueFull) else 429, str(e), "service_unavailable")
             except ValueError as e:
                 return _error(400, str(e))
-            return {"id": rid, "object": "chat.completion", "created": created, "model": name,
-                    "choices": [{"index": 0, "message": {"role": "assistant", "content": out.text}, "finish_reason": out.finish_reason,
-                                 "token_ids": out.token_ids}],
-                    "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out.token_ids), "total_tokens": len(ids) + len(out.token_ids)}}
-        if body.get("stream"):
+        elif body.get("stream"):
             async def events():
                 head = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": name}
                 yield "data: " + json.dumps({**head, "choices": [{"index": 0, "delta": {"role": "assistant", "content": ""}, "finish_reason": None}]}) + "\n\n"
                 n_out = 0
+                sp_parser = parsing.StreamingAssistantOutputParser(tool_cfg, reasoning) if want_parse else None
+
+                def chunks(events):
+                    for e in events:
+                        if e["type"] == "content":
+                            delta = {"content": e["text"]}
+                        elif e["type"] == "reasoning":
+                            delta = {"reasoning_content": e["text"]}
+                        else:
+                            delta = {"tool_calls": [e["call"].to_openai(e["index"])]}
+                        yield "data: " + json.dumps({**head, "choices": [{"index": 0, "delta": delta, "finish_reason": None}]}) + "\n\n"
                 try:
                     async for d in client.stream(ids, sp, priority):
                         n_out += len(d.token_ids)
-                        if d.text:
+                        if d.text and sp_parser is not None:
+                            for c in chunks(sp_parser.feed(d.text)):
+                                yield c
+                        elif d.text:
                             yield "data: " + json.dumps({**head, "choices": [{"index": 0, "delta": {"content": d.text}, "finish_reason": None}]}) + "\n\n"
                         if d.finished:
-                            yield "data: " + json.dumps({**head, "choices": [{"index": 0, "delta": {}, "finish_reason": d.finish_reason or "stop"}],
+                            fin = d.finish_reason or "stop"
+                            if sp_parser is not None:
+                                for c in chunks(sp_parser.flush()):
+                                    yield c
+                                if sp_parser.saw_tool_call and fin == "stop":
+                                    fin = "tool_calls"
+                            yield "data: " + json.dumps({**head, "choices": [{"index": 0, "delta": {}, "finish_reason": fin}],
                                                          "usage": {"prompt_tokens": len(ids), "completion_tokens": n_out, "total_tokens": len(ids) + n_out}}) + "\n\n"
                 except (QueueFull, QueueTimeout, EngineUnavailable) as e:
                     yield "data: " + json.dumps({"error": {"message": str(e), "type": "service_unavailable"}}) + "\n\n"
                 yield "data: [DONE]\n\n"
             return sse(events())
-        out, err = await run(ids, sp, priority)
-        if err:
-            return err
+        else:
+            out, err = await run(ids, sp, priority)
+            if err:
+                return err
         text, stopped = _truncate_at_stop(out.text if out.text is not None else decode(out.token_ids), body.get("stop"))
+        message: Dict[str, Any] = {"role": "assistant", "content": text}
+        finish = "stop" if stopped else out.finish_reason
+        choice_extra: Dict[str, Any] = {}
+        if out.logprobs:
+            choice_extra["logprobs"] = {"content": [
+                {"token": decode([e["token_id"]]), "token_id": e["token_id"], "logprob": e["logprob"],
+                 "top_logprobs": [{"token": decode([t]), "token_id": t, "logprob": v} for t, v in e["top"]]} for e in out.logprobs]}
+        if want_parse:
+            parsed = parsing.parse_assistant_output(text, tool_cfg, reasoning)
+            message["content"] = parsed.content or (None if parsed.tool_calls else "")
+            if parsed.reasoning:
+                message["reasoning_content"] = parsed.reasoning
+            if parsed.tool_calls:
+                message["tool_calls"] = [c.to_openai() for c in parsed.tool_calls]
+                if finish == "stop":
+                    finish = "tool_calls"
         return {"id": rid, "object": "chat.completion", "created": created, "model": name,
-                "choices": [{"index": 0, "message": {"role": "assistant", "content": text},
-                             "finish_reason": "stop" if stopped else out.finish_reason, "token_ids": out.token_ids}],
+                "choices": [{"index": 0, "message": message, "finish_reason": finish, "token_ids": out.token_ids, **choice_extra}],
                 "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out.token_ids), "total_tokens": len(ids) + len(out.token_ids)}}
 
     # ---- OpenAI completions --------------------------------------------------------------------------------
@@ -215,8 +264,13 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
         if err:
             return err
         text, stopped = _truncate_at_stop(out.text if out.text is not None else decode(out.token_ids), body.get("stop"))
+        extra: Dict[str, Any] = {}
+        if out.logprobs:
+            extra["logprobs"] = {"tokens": [decode([e["token_id"]]) for e in out.logprobs], "token_ids": [e["token_id"] for e in out.logprobs],
+                                 "token_logprobs": [e["logprob"] for e in out.logprobs],
+                                 "top_logprobs": [{str(t): v for t, v in e["top"]} for e in out.logprobs]}
         return {"id": rid, "object": "text_completion", "created": created, "model": name,
-                "choices": [{"index": 0, "text": text, "token_ids": out.token_ids, "finish_reason": "stop" if stopped else out.finish_reason}],
+                "choices": [{"index": 0, "text": text, "token_ids": out.token_ids, "finish_reason": "stop" if stopped else out.finish_reason, **extra}],
                 "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out.token_ids), "total_tokens": len(ids) + len(out.token_ids)}}
 
     # ---- OpenAI responses (text in, text out) ---------------------------------------------------------------

@@ -104,24 +104,10 @@ class EngineClient:
         finally:
             self.admission.release()
 
-    def _guided_blocking(self, ids: Sequence[int], sp: SamplingParams, guided) -> RequestOutput:
-        """Constrained requests run one at a time on the static path (mask → sample → advance every step)."""
-        from ..runtime.guided import generate_guided
-        self.admission.acquire()
-        try:
-            with self._lock:
-                seat = self.llm.max_batch_size - 1 if self.llm.engine is None else None
-                if seat is None:
-                    raise EngineUnavailable("guided decoding is served without in-flight batching")
-                toks = generate_guided(self.llm, ids, guided, sp.max_tokens, seat=seat)
-            text = self.llm.tokenizer.decode(toks)
-            text = text.decode("utf-8", "replace") if isinstance(text, (bytes, bytearray)) else text
-            return RequestOutput(list(ids), toks, text, "stop" if len(toks) < sp.max_tokens else "length")
-        finally:
-            self.admission.release()
-
-    async def generate_guided(self, ids: Sequence[int], sp: SamplingParams, guided) -> RequestOutput:
-        return await asyncio.get_running_loop().run_in_executor(None, self._guided_blocking, ids, sp, guided)
+    async def generate_guided(self, ids: Sequence[int], sp: SamplingParams, guided, priority: int = 0) -> RequestOutput:
+        """Constrained request: the constraint rides on the sampling parameters, so it batches like any other request."""
+        import dataclasses
+        return await self.generate(ids, dataclasses.replace(sp, guided=guided), priority)
 
     async def generate(self, ids: Sequence[int], sp: SamplingParams, priority: int = 0) -> RequestOutput:
         return await asyncio.get_running_loop().run_in_executor(None, self._generate_blocking, ids, sp, priority)

@@ -169,3 +169,46 @@ def test_online_benchmark_against_the_app(llm):
     assert rep["requests"] == 5 and rep["completed"] == 5 and rep["failed"] == 0
     assert rep["output_tokens"] == 20 and rep["output_tokens_per_s"] > 0
     assert rep["ttft_s"]["p50"] is not None and rep["latency_s"]["p99"] >= rep["latency_s"]["p50"]
+
+
+def test_chat_tool_call_and_reasoning_parsing(llm):
+    """A completion forced (by a choice constraint) to be a wrapped call comes back as ``tool_calls``."""
+    c = TestClient(create_app(llm, ApiConfig(served_model_name="tiny", reasoning_parser="think"), ChatTemplate()))
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {"type": "object"}}}]
+    call = '<think>look it up</think><tool_call>{"name": "get_weather", "arguments": {"city": "Paris"}}</tool_call>'
+    body = {"messages": [{"role": "user", "content": "weather?"}], "tools": tools, "guided_choice": [call], "max_tokens": 120, "temperature": 0}
+    r = c.post("/v1/chat/completions", json=body).json()
+    msg = r["choices"][0]["message"]
+    assert msg["tool_calls"][0]["function"] == {"name": "get_weather", "arguments": '{"city": "Paris"}'}
+    assert msg["reasoning_content"] == "look it up" and msg["content"] is None
+    assert r["choices"][0]["finish_reason"] == "tool_calls"
+    assert c.post("/v1/chat/completions", json={**body, "tools": [{"type": "function"}]}).status_code == 400
+    # with tool_choice "none" the text stays text
+    r = c.post("/v1/chat/completions", json={**body, "tool_choice": "none"}).json()
+    assert "tool_calls" not in r["choices"][0]["message"] and "<tool_call>" in r["choices"][0]["message"]["content"]
+
+
+def test_logprobs_and_logit_bias(client, llm):
+    body = {"prompt": [5, 9, 33], "max_tokens": 4, "temperature": 0, "logprobs": 3}
+    r = client.post("/v1/completions", json=body, headers=AUTH).json()["choices"][0]
+    lp = r["logprobs"]
+    assert len(lp["token_logprobs"]) == 4 and lp["token_ids"] == r["token_ids"]
+    for tid, chosen, top in zip(lp["token_ids"], lp["token_logprobs"], lp["top_logprobs"]):
+        assert len(top) == 3 and chosen <= 0.0
+        assert abs(max(top.values()) - chosen) < 1e-5 and str(tid) in top          # greedy: the chosen token leads the list
+    # a large bias forces the token; a ban removes the otherwise greedy token
+    forced = client.post("/v1/completions", json={**body, "logit_bias": {"77": 100}}, headers=AUTH).json()["choices"][0]
+    assert forced["token_ids"] == [77] * 4 and all(abs(v) < 1e-3 for v in forced["logprobs"]["token_logprobs"])
+    banned = client.post("/v1/completions", json={**body, "logit_bias": {str(r["token_ids"][0]): -100}}, headers=AUTH).json()["choices"][0]
+    assert banned["token_ids"][0] != r["token_ids"][0]
+    chat = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3, "temperature": 0,
+                                                     "logprobs": True, "top_logprobs": 2}, headers=AUTH).json()["choices"][0]
+    assert len(chat["logprobs"]["content"]) == 3 and len(chat["logprobs"]["content"][0]["top_logprobs"]) == 2
+    assert client.post("/v1/completions", json={**body, "logprobs": 99}, headers=AUTH).status_code == 400
+    # the static-batch path reports the same numbers
+    from tensorrt_edge_llm_b200.runtime.llm import SamplingParams as SP
+    static = LLM(llm.cfg, device="cpu", max_batch_size=2, max_input_len=64, max_kv_cache_capacity=128, page_size=16)
+    static.model.load_state_dict(llm.model.state_dict())
+    out = static.generate([[5, 9, 33]], SP(max_tokens=4, temperature=0.0, logprobs=3))[0]
+    assert out.token_ids == r["token_ids"]
+    assert all(abs(a["logprob"] - b) < 1e-4 for a, b in zip(out.logprobs, lp["token_logprobs"]))
