@@ -15,7 +15,8 @@ from torch import nn
 from ..models.linear import LinearBase, NVFP4Linear, Int4AwqLinear
 from .safetensors_io import CheckpointReader
 
-_LINEAR_FIELDS = ("weight", "weight_scale", "weight_scale_2", "input_scale", "bias", "pre_quant_scale")
+_LINEAR_FIELDS = ("weight", "weight_scale", "weight_scale_2", "input_scale", "bias", "pre_quant_scale",
+                  "qweight", "qzeros", "scales", "g_idx", "weight_scale_inv")
 
 
 def _strip_prefixes(keys) -> Dict[str, str]:
@@ -61,10 +62,12 @@ def load_weights(model: nn.Module, model_dir: str, strict: bool = True) -> List[
                     t = fetch(f"{base}.{fld}")
                     if t is not None:
                         b[fld] = t
-                if "weight" not in b:
+                if "weight_scale_inv" in b:                      # block-free FP8 exports name the scale this way
+                    b.setdefault("weight_scale", b.pop("weight_scale_inv"))
+                if "weight" not in b and "qweight" not in b:
                     if mod_name == "lm_head" and getattr(model, "cfg", None) is not None and model.cfg.tie_word_embeddings:
                         b["weight"] = fetch("model.embed_tokens.weight")
-                    if b.get("weight") is None:
+                    if b.get("weight") is None and "qweight" not in b:
                         if strict:
                             raise KeyError(f"checkpoint has no tensor {base}.weight")
                         b = None

@@ -9,7 +9,7 @@ def main(argv=None) -> int:
     p.add_argument("kind", nargs="?", default="llm", choices=["llm", "draft"])
     p.add_argument("--model_dir", "--model-dir", required=True)
     p.add_argument("--output_dir", "--output-dir", required=True)
-    p.add_argument("--quantization", default="nvfp4", choices=["nvfp4", "int4_awq"])
+    p.add_argument("--quantization", default="nvfp4", choices=["nvfp4", "int4_awq", "int4_gptq", "fp8", "int8_sq", "mxfp8", "q8_0"])
     p.add_argument("--kv-cache-quantization", "--kv_cache_quantization", default=None, choices=[None, "fp8"])
     p.add_argument("--exclude", nargs="*", default=["lm_head"])
     p.add_argument("--calib-ids", default="", help="JSON file with a list of token-id lists; default: seeded uniform ids")

@@ -25,6 +25,11 @@ QUANT_NVFP4_A16 = "nvfp4_a16"  # W4A16: NVFP4 weights, 16-bit activations
 QUANT_INT4_AWQ = "int4_awq"
 QUANT_INT4_GPTQ = "int4_gptq"
 QUANT_FP8 = "fp8"
+QUANT_INT8_SQ = "int8_sq"
+QUANT_MXFP8 = "mxfp8"
+QUANT_Q8_0 = "q8_0"
+# formats that are expanded to 16-bit when the checkpoint is loaded
+EXPANDED_QUANT_TYPES = (QUANT_INT4_GPTQ, QUANT_FP8, QUANT_INT8_SQ, QUANT_MXFP8, QUANT_Q8_0)
 
 NVFP4_BLOCK = 16
 AWQ_GROUP = 128
@@ -65,7 +70,8 @@ class QuantConfig:
     kv_cache_quant: Optional[str] = None            # None or "fp8"
     excluded: List[str] = field(default_factory=list)
     layer_overrides: Dict[str, str] = field(default_factory=dict)
-    gptq_zero_point_offset: int = 0
+    gptq_zero_point_offset: int = 1                 # GPTQ v1 checkpoints store zero - 1
+    awq_layout: str = "modelopt"                    # "modelopt" (prepacked uint8) or "autoawq" (int32 qweight / qzeros / scales)
     quantize_activations: bool = True
     lm_head_quant_type: str = QUANT_NONE
 
@@ -371,7 +377,9 @@ def load_checkpoint_config_dicts(model_dir: str) -> Dict[str, Dict[str, Any]]:
 _ALGO_TO_QUANT = {
     "NVFP4": QUANT_NVFP4, "NVFP4_AWQ": QUANT_NVFP4, "W4A16_NVFP4": QUANT_NVFP4_A16,
     "W4A16_AWQ": QUANT_INT4_AWQ, "INT4_AWQ": QUANT_INT4_AWQ, "W4A16": QUANT_INT4_AWQ,
-    "W4A16_GPTQ": QUANT_INT4_GPTQ, "FP8": QUANT_FP8,
+    "W4A16_GPTQ": QUANT_INT4_GPTQ, "FP8": QUANT_FP8, "FP8_PER_CHANNEL_PER_TOKEN": QUANT_FP8,
+    "W8A8_SQ_PER_CHANNEL": QUANT_INT8_SQ, "INT8_SQ": QUANT_INT8_SQ, "INT8_SMOOTHQUANT": QUANT_INT8_SQ,
+    "MXFP8": QUANT_MXFP8, "Q8_0": QUANT_Q8_0,
 }
 
 
@@ -402,6 +410,8 @@ def parse_quant_config(model_dir: str, hf: Optional[Dict[str, Any]] = None) -> Q
         quant_type = QUANT_INT4_AWQ
     elif method == "gptq":
         quant_type = QUANT_INT4_GPTQ
+    elif method == "fp8":
+        quant_type = QUANT_FP8
     elif method == "modelopt" and "NVFP4" in str(qc).upper():
         quant_type = QUANT_NVFP4
     elif "config_groups" in qc:
@@ -422,7 +432,8 @@ def parse_quant_config(model_dir: str, hf: Optional[Dict[str, Any]] = None) -> Q
     kv = "fp8" if kv and "FP8" in str(kv).upper() else None
     excluded = list(qc.get("exclude_modules") or qc.get("ignore") or qc.get("modules_to_not_convert") or [])
     return QuantConfig(quant_type=quant_type, group_size=group, kv_cache_quant=kv, excluded=excluded,
-                       gptq_zero_point_offset=0 if qc.get("sym", True) is False else 0)
+                       awq_layout="autoawq" if method == "awq" else "modelopt",
+                       gptq_zero_point_offset=0 if str(qc.get("checkpoint_format", "gptq")).lower() == "gptq_v2" else 1)
 
 
 def _checkpoint_keys(model_dir: str) -> List[str]:

@@ -18,7 +18,7 @@ import torch
 from torch import nn
 
 from .. import ops
-from ..config import (QUANT_INT4_AWQ, QUANT_NONE, QUANT_NVFP4, QUANT_NVFP4_A16, ModelConfig)
+from ..config import (EXPANDED_QUANT_TYPES, QUANT_INT4_AWQ, QUANT_NONE, QUANT_NVFP4, QUANT_NVFP4_A16, ModelConfig)
 from ..ops import reference as ref
 
 
@@ -263,6 +263,29 @@ class Int4AwqLinear(LinearBase):
         return y.to(x.dtype)
 
 
+class ExpandedLinear(Linear):
+    """A linear whose checkpoint stores a weight-only format (GPTQ, AutoAWQ, FP8, INT8-SQ, MXFP8, Q8_0): the tensors
+    are decoded to a dense matrix once while loading and the layer then runs as a 16-bit :class:`Linear`.
+
+    Parity: the weight-only members of ``tensorrt_edgellm/models/linear.py:647-920`` and their plugins
+    (``int4GroupwiseGemmPlugin``, ``q8_0LinearPlugin`` …); here the tcgen05 16-bit GEMM serves all of them."""
+
+    def __init__(self, in_features, out_features, quant_type: str, zero_point_offset: int = 1, **kw):
+        super().__init__(in_features, out_features, **kw)
+        self.quant_type, self.zero_point_offset = quant_type, zero_point_offset
+
+    def load_from(self, tensors):
+        from ..checkpoint.repacking import decode_bundle
+        dense = []
+        for t in tensors:
+            w = decode_bundle(t, self.quant_type, self.zero_point_offset)
+            b = {"weight": w if w is not None else t["weight"]}
+            if "bias" in t:
+                b["bias"] = t["bias"]
+            dense.append(b)
+        super().load_from(dense)
+
+
 def make_linear(cfg: ModelConfig, name: str, in_features: int, out_features: Sequence[int],
                 tp_mode: TPMode = TPMode.REPLICATED, sources: Optional[List[str]] = None, bias: bool = False,
                 quantizable: bool = True, row_ranges=None) -> LinearBase:
@@ -279,5 +302,9 @@ def make_linear(cfg: ModelConfig, name: str, in_features: int, out_features: Seq
     if qt in (QUANT_NVFP4, QUANT_NVFP4_A16):
         return NVFP4Linear(in_features, out_features, quantize_activations=(qt == QUANT_NVFP4 and cfg.quant.quantize_activations), **kw)
     if qt == QUANT_INT4_AWQ:
+        if cfg.quant.awq_layout == "autoawq":
+            return ExpandedLinear(in_features, out_features, quant_type=qt, **kw)
         return Int4AwqLinear(in_features, out_features, group_size=cfg.quant.group_size or 128, **kw)
+    if qt in EXPANDED_QUANT_TYPES:
+        return ExpandedLinear(in_features, out_features, quant_type=qt, zero_point_offset=cfg.quant.gptq_zero_point_offset, **kw)
     return Linear(in_features, out_features, **kw)

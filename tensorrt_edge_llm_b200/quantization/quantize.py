@@ -12,14 +12,15 @@ from ..ops import reference as ref
 
 _LINEAR_SUFFIXES = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj", "in_proj", "out_proj",
                     "in_proj_qkv", "in_proj_z", "fc1", "fc2")
-_ALGOS = {"nvfp4": "NVFP4", "int4_awq": "W4A16_AWQ", "fp16": None, "bf16": None}
+_ALGOS = {"nvfp4": "NVFP4", "int4_awq": "W4A16_AWQ", "int4_gptq": "W4A16_GPTQ", "fp8": "FP8", "int8_sq": "W8A8_SQ_PER_CHANNEL",
+          "mxfp8": "MXFP8", "q8_0": "Q8_0", "fp16": None, "bf16": None}
 
 
 def build_quant_config(quantization: str, exclude: Sequence[str] = ("lm_head",), kv_cache_quantization: Optional[str] = None,
                        group_size: Optional[int] = None) -> dict:
-    """The ``hf_quant_config.json`` body for ``quantization`` ∈ {nvfp4, int4_awq}."""
+    """The ``hf_quant_config.json`` body for one of the supported weight formats."""
     if quantization not in _ALGOS or _ALGOS[quantization] is None:
-        raise ValueError(f"unsupported quantization {quantization!r}; choose nvfp4 or int4_awq")
+        raise ValueError(f"unsupported quantization {quantization!r}; choose one of {sorted(k for k, v in _ALGOS.items() if v)}")
     if kv_cache_quantization not in (None, "fp8"):
         raise ValueError("kv_cache_quantization must be fp8 or unset")
     return {"producer": {"name": "tensorrt_edge_llm_b200"},
@@ -112,6 +113,16 @@ def quantize_and_export(model_dir: str, out_dir: str, quantization: str = "nvfp4
             out[base + ".weight_scale_2"] = gs.reshape(()).cpu()
             mod = canon[:-len(".weight")]
             out[base + ".input_scale"] = torch.tensor(scales.get(mod, 1.0 / 448.0), dtype=torch.float32)
+        elif quantization in ("int4_gptq", "fp8", "int8_sq", "mxfp8", "q8_0"):
+            from ..checkpoint import repacking as rp
+            g = group_size
+            if (quantization == "int4_gptq" and (w.shape[1] % g or w.shape[0] % 8)) or w.shape[1] % 32:
+                out[key] = t.clone()
+                continue
+            enc = {"int4_gptq": lambda x: rp.encode_gptq(x, g), "fp8": rp.encode_fp8, "int8_sq": rp.encode_int8_sq,
+                   "mxfp8": rp.encode_mxfp8, "q8_0": rp.encode_q8_0}[quantization](w.cpu())
+            for name, v in enc.items():
+                out[base + "." + name] = v.reshape(-1) if v.dim() == 0 else v
         else:
             g = group_size
             if w.shape[1] % g or w.shape[0] % 2:

@@ -184,3 +184,47 @@ def test_reference_package_name_resolves():
     from tensorrt_edgellm.server import LLM, SamplingParams  # noqa: F401
     from tensorrt_edgellm.config import ModelConfig, QuantConfig  # noqa: F401
     assert tensorrt_edgellm.AutoModel is AutoModel and "serve" in tensorrt_edgellm.cli.COMMANDS
+
+
+@pytest.mark.parametrize("fmt", ["gptq", "awq", "fp8", "int8_sq", "mxfp8", "q8_0"])
+def test_weight_only_checkpoint_formats_load(ckpt, tmp_path, fmt):
+    """A checkpoint whose linears are stored as GPTQ / AutoAWQ / FP8 / INT8-SQ / MXFP8 / Q8_0 loads and tracks the 16-bit model."""
+    from tensorrt_edge_llm_b200.checkpoint import repacking as R
+    enc = {"gptq": lambda w: R.encode_gptq(w, 64), "awq": lambda w: R.encode_autoawq(w, 64), "fp8": R.encode_fp8,
+           "int8_sq": R.encode_int8_sq, "mxfp8": R.encode_mxfp8, "q8_0": R.encode_q8_0}[fmt]
+    qcfg = {"gptq": {"quant_method": "gptq", "bits": 4, "group_size": 64}, "awq": {"quant_method": "awq", "bits": 4, "group_size": 64},
+            "fp8": {"quant_method": "fp8"}, "int8_sq": {"quant_algo": "W8A8_SQ_PER_CHANNEL"}, "mxfp8": {"quant_algo": "MXFP8"},
+            "q8_0": {"quant_algo": "Q8_0"}}[fmt]
+    out = str(tmp_path / fmt)
+    os.makedirs(out)
+    f = SafetensorsFile(os.path.join(ckpt, "model.safetensors"))
+    tensors = {}
+    for k in f.keys():
+        t = f.get(k).clone()
+        if k.endswith("_proj.weight"):
+            base = k[:-len("weight")]
+            for name, v in enc(t).items():
+                tensors[base + name] = v.reshape(-1) if v.dim() == 0 else v
+        else:
+            tensors[k] = t
+    save_file(tensors, os.path.join(out, "model.safetensors"))
+    hf = json.load(open(os.path.join(ckpt, "config.json")))
+    hf["quantization_config"] = {**qcfg, "modules_to_not_convert": ["lm_head"]}
+    json.dump(hf, open(os.path.join(out, "config.json"), "w"))
+    ids = [5, 9, 33, 70, 12, 8]
+    a, b = _logits(ckpt, ids), _logits(out, ids)
+    cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0)
+    assert float(cos) > (0.97 if fmt in ("gptq", "awq") else 0.995)
+    from tensorrt_edge_llm_b200.models.linear import ExpandedLinear
+    m = AutoModel.from_pretrained(out)
+    assert sum(isinstance(x, ExpandedLinear) for x in m.modules()) >= 7 * m.cfg.num_hidden_layers - 7
+
+
+def test_quantize_command_other_formats(ckpt, tmp_path):
+    ids = [5, 9, 33, 70, 12, 8]
+    a = _logits(ckpt, ids)
+    for q in ("fp8", "q8_0", "int4_gptq"):
+        out = str(tmp_path / q)
+        assert trtedge(["quantize", "llm", "--model_dir", ckpt, "--output_dir", out, "--quantization", q, "--group-size", "64"]) == 0
+        cos = torch.nn.functional.cosine_similarity(a.flatten(), _logits(out, ids).flatten(), dim=0)
+        assert float(cos) > 0.97
