@@ -17,6 +17,7 @@ import torch
 
 from .. import ops
 from ..ops.meta import StepMeta, build_step_meta
+from .. import profiling as prof
 from .kv_cache import KVCacheManager
 
 
@@ -91,6 +92,11 @@ class ModelRunner:
 
         Sequences are packed into steps of at most ``max_num_tokens`` rows; a prompt longer than
         the budget is split on page boundaries (``cpp/scheduler/stepPlanner.cpp`` rule)."""
+        n = len(seats)
+        with prof.time_stage(prof.PREFILL, batch=n, tokens=sum(len(x) for x in prompts)):
+            return self._prefill(seats, prompts)
+
+    def _prefill(self, seats, prompts) -> torch.Tensor:
         n = len(seats)
         done = [0] * n
         out: List[Optional[torch.Tensor]] = [None] * n
@@ -190,6 +196,10 @@ class ModelRunner:
 
         On CUDA the steps replay one captured graph whose device-side state advances by itself;
         the host copies the token matrix back once at the end."""
+        with prof.time_stage(prof.VANILLA_DECODING, batch=len(seats), tokens=len(seats) * steps):
+            return self._decode_greedy(seats, first_tokens, steps)
+
+    def _decode_greedy(self, seats, first_tokens, steps) -> torch.Tensor:
         n = len(seats)
         for s in seats:
             self.kv.reserve(s, self.kv.lengths[s] + steps)

@@ -17,6 +17,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .. import ops
+from .. import profiling as prof
 from ..ops.meta import build_step_meta
 from . import logits as lp
 from . import native as rt
@@ -104,6 +105,10 @@ class ModelSession(rt.RuntimeSession):
         return r
 
     def execute(self, plan):
+        with prof.time_stage(prof.IFB_EXECUTE, batch=len(plan.seqs), tokens=plan.total_tokens):
+            return self._execute(plan)
+
+    def _execute(self, plan):
         seats, token_lists, producers = [], [], []
         for s in plan.seqs:
             q = self.seqs[s.slot]

@@ -28,6 +28,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from .. import ops
+from .. import profiling as prof
 from ..ops.meta import build_step_meta
 from .kv_cache import KVCacheManager
 from .runner import ModelRunner
@@ -146,6 +147,8 @@ class EagleDecoder:
         """Returns the tokens emitted for every seat this round (accepted draft tokens + bonus)."""
         sp, dev = self.spec, self.device
         b, k, steps, n = len(seats), self.spec.top_k, self.spec.draft_steps, self.spec.verify_tokens
+        timer = prof.timer()
+        stage = timer.begin(prof.SPEC_DRAFT, batch=b)
         d2t = self.draft.d2t.long()
         lp0 = torch.stack([self.lp[s] for s in seats])                       # [B, Vd]
         h0 = torch.stack([self.hid[s] for s in seats])                       # [B, H]
@@ -192,6 +195,8 @@ class EagleDecoder:
             front0, kf = rows, kn
             pool_base += n_new
         p_tok, p_par, p_dep, p_sc = (torch.cat(x, dim=1) for x in (p_tok, p_par, p_dep, p_sc))
+        timer.end(stage)
+        stage = timer.begin(prof.SPEC_VERIFY, batch=b, tokens=b * n)
         # ---- choose the verification tree ----
         npool = p_tok.shape[1]
         keep = min(n - 1, npool)
@@ -211,6 +216,8 @@ class EagleDecoder:
         pos = [l + int(d) for i, l in enumerate(lt) for d in tree_dep[i].tolist()]
         logits, taps = self._target_step(seats, tree_tok.reshape(-1).to(torch.int32), [nn_] * b, tree_mask=self._pack_mask(anc), positions=pos)
         tgt = ops.argmax(logits).view(b, nn_)
+        timer.end(stage)
+        stage = timer.begin(prof.SPEC_ACCEPT, batch=b)
         # ---- accept, commit KV ----
         max_path = steps + 1
         path, plen, bonus = ops.spec_accept_greedy(tgt, tree_tok.to(torch.int32), tree_par.to(torch.int32), max_path, self._forced(b))
@@ -238,6 +245,7 @@ class EagleDecoder:
         for i, s in enumerate(seats):
             self.lp[s] = lp[i]
             self.hid[s] = h[ends[i]]
+        timer.end(stage)
         self.stats.rounds += b
         self.stats.emitted += sum(len(e) for e in out)
         return out
