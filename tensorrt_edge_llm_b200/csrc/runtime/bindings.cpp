@@ -60,6 +60,8 @@ PYBIND11_MODULE(_telb_runtime, m) {
         .def("commit", &KVPageTable::commit)
         .def("rewind", &KVPageTable::rewind)
         .def("free_seat", &KVPageTable::free_seat)
+        .def("retire_before", &KVPageTable::retire_before)
+        .def("live_pages", &KVPageTable::live_pages)
         .def("take_dirty_rows", &KVPageTable::take_dirty_rows)
         .def("allocator", &KVPageTable::allocator, py::return_value_policy::reference_internal)
         .def("rows", [](const KVPageTable& t, const std::vector<int>& seats) {

@@ -78,8 +78,35 @@ void KVPageTable::rewind(int seat, int length) {
     lengths_[seat] = length;
 }
 
+int KVPageTable::retire_before(int seat, int first_live_token) {
+    auto& have = pages_.at(seat);
+    const int upto = std::min(static_cast<int>(have.size()), std::max(first_live_token, 0) / page_size_);
+    int32_t* r = table_.data() + static_cast<size_t>(seat) * max_pages_;
+    std::vector<int32_t> gone;
+    for (int i = 0; i < upto; ++i)
+        if (have[i] != kUnusedPage) {
+            gone.push_back(have[i]);
+            have[i] = kUnusedPage;
+            r[i] = kUnusedPage;
+        }
+    if (!gone.empty()) {
+        alloc_.release(gone);
+        dirty_[seat] = 1;
+    }
+    return static_cast<int>(gone.size());
+}
+
+int KVPageTable::live_pages(int seat) const {
+    int n = 0;
+    for (int32_t p : pages_.at(seat)) n += p != kUnusedPage;
+    return n;
+}
+
 void KVPageTable::free_seat(int seat) {
-    alloc_.release(pages_.at(seat));
+    std::vector<int32_t> live;
+    for (int32_t p : pages_.at(seat))
+        if (p != kUnusedPage) live.push_back(p);
+    alloc_.release(live);
     pages_[seat].clear();
     std::fill_n(table_.begin() + static_cast<size_t>(seat) * max_pages_, max_pages_, kUnusedPage);
     lengths_[seat] = 0;

@@ -53,6 +53,11 @@ class KVPageTable {
     void commit(int seat, int new_tokens) { lengths_.at(seat) += new_tokens; }
     void rewind(int seat, int length);                 // speculative rejection: drop the tail, keep pages
     void free_seat(int seat);
+    // Bounded sliding-window storage: give back every page that lies wholly before `first_live_token`.  The
+    // logical positions stay (their table entries become kUnusedPage), so later pages keep their indices.
+    // Returns the number of pages released.
+    int retire_before(int seat, int first_live_token);
+    int live_pages(int seat) const;
 
     const int32_t* row(int seat) const { return table_.data() + static_cast<size_t>(seat) * max_pages_; }
     const std::vector<int32_t>& table() const { return table_; }

@@ -59,8 +59,16 @@ class KVCacheManager:
 
     def __init__(self, cfg: ModelConfig, num_pages: int, page_size: int = 64, max_seats: int = 64,
                  max_pages_per_seq: int = 64, device="cpu", dtype: Optional[torch.dtype] = None,
-                 num_layers: Optional[int] = None):
+                 num_layers: Optional[int] = None, bounded_swa: Optional[bool] = None):
         self.cfg = cfg
+        # Bounded sliding-window storage (``cpp/runtime/state/boundedSwaKVPageManager.cpp`` in the reference): every
+        # attention layer of the model looks back at most `sliding_window` tokens, so pages that lie wholly before the
+        # window are handed back to the pool as the sequence grows.  Both attention kernels start their KV loop at a
+        # 128-token tile boundary at or below `past - window + 1`; the retire boundary is rounded down the same way.
+        win = getattr(cfg, "sliding_window", None)
+        self.window = int(win) if win else 0
+        self.bounded_swa = bool(self.window) if bounded_swa is None else (bool(bounded_swa) and bool(self.window))
+        self.retired_pages = 0
         self.page_size = page_size
         self.max_seats = max_seats
         self.max_pages_per_seq = max_pages_per_seq
@@ -131,6 +139,37 @@ class KVCacheManager:
         self.lengths[seat] += new_tokens
         if self.native is not None:
             self.native.commit(seat, new_tokens)
+        if self.bounded_swa:
+            self._retire(seat)
+
+    SWA_TILE = 128          # KV tile of the attention kernels: the first tile they touch starts at a multiple of this
+
+    def first_live_token(self, length: int) -> int:
+        return max(0, (length - self.window + 1) // self.SWA_TILE * self.SWA_TILE)
+
+    def swa_live_pages_bound(self, step_tokens: int) -> int:
+        """Most pages one sequence can hold at once when each step appends at most ``step_tokens``."""
+        p = self.page_size
+        return min((self.window + self.SWA_TILE + step_tokens + p - 1) // p + 1, self.max_pages_per_seq)
+
+    def _retire(self, seat: int) -> None:
+        first = self.first_live_token(self.lengths[seat])
+        have = self._pages.get(seat, [])
+        upto = min(len(have), first // self.page_size)
+        if upto == 0 or all(pg < 0 for pg in have[:upto]):
+            return
+        if self.native is not None:
+            self.retired_pages += self.native.retire_before(seat, first)
+        else:
+            gone = [pg for pg in have[:upto] if pg >= 0]
+            self.alloc.release(gone)
+            self.retired_pages += len(gone)
+        for i in range(upto):
+            have[i] = -1
+        self.table[seat, :upto] = -1
+
+    def live_pages(self, seat: int) -> int:
+        return sum(pg >= 0 for pg in self._pages.get(seat, []))
 
     def rewind(self, seat: int, length: int) -> None:
         """Drop everything after ``length`` tokens (speculative rejection); pages are kept."""
@@ -144,7 +183,7 @@ class KVCacheManager:
         if self.native is not None:
             self.native.free_seat(seat)
         else:
-            self.alloc.release(pages)
+            self.alloc.release([pg for pg in pages if pg >= 0])
         self.table[seat].fill_(-1)
         self.lengths[seat] = 0
 

@@ -47,8 +47,10 @@ class ModelSession(rt.RuntimeSession):
         self.max_input_len = max_input_len
         self.slots = rt.ResidentSlotPool(self.kv.max_seats)
         self.seqs: Dict[int, _Seq] = {}
+        # retired sliding-window pages cannot be shared, so bounded storage and the prefix cache exclude each other
         self.prefix = rt.PrefixCache(self.kv.native.allocator(), self.kv.page_size, 4096) if (
-            enable_prefix_cache and getattr(self.kv, "native", None) is not None) else None
+            enable_prefix_cache and getattr(self.kv, "native", None) is not None and not self.kv.bounded_swa) else None
+        self._swa_bound = self.kv.swa_live_pages_bound(runner.max_num_tokens) if self.kv.bounded_swa else 0
 
     # ---- seam ------------------------------------------------------------------------------------
     def capabilities(self):
@@ -90,7 +92,13 @@ class ModelSession(rt.RuntimeSession):
                 if m.tokens:
                     self.kv.adopt_prefix(slot, m.pages, m.tokens)
                     reused = m.tokens
-            self.kv.reserve(slot, need)                   # capacity is reserved at seat time: no eviction later
+            if self.kv.bounded_swa:
+                # pages are taken step by step and handed back as the window moves on; admission keeps the sum of the
+                # residents' worst-case live pages inside the pool, so a later step cannot run out
+                if (len(self.seqs) + 1) * self._swa_bound > self.kv.pool.shape[1]:
+                    raise MemoryError("sliding-window page budget is taken")
+            else:
+                self.kv.reserve(slot, need)               # capacity is reserved at seat time: no eviction later
         except (MemoryError, RuntimeError) as e:
             self.kv.free(slot)
             self.slots.release(slot)
@@ -118,6 +126,8 @@ class ModelSession(rt.RuntimeSession):
             else:
                 toks = [q.last_token]
                 produces = True
+            if self.kv.bounded_swa:
+                self.kv.reserve(s.slot, self.kv.lengths[s.slot] + len(toks))
             seats.append(s.slot)
             token_lists.append(toks)
             producers.append(produces)
