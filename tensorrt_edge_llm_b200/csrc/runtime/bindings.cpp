@@ -10,6 +10,7 @@
 #include <pybind11/stl.h>
 
 #include "json.h"
+#include "media.h"
 #include "paged_kv.h"
 #include "runtime_core.h"
 #include "scheduler.h"
@@ -439,4 +440,76 @@ PYBIND11_MODULE(_telb_runtime, m) {
         .def_static("from_template_text", &ChatTemplate::from_template_text, py::arg("template"), py::arg("bos") = "")
         .def("apply", &ChatTemplate::apply, py::arg("messages"), py::arg("add_generation_prompt") = true,
              py::arg("enable_thinking") = true);
+    // ---- media ---------------------------------------------------------------------------------
+    py::class_<AudioClip>(m, "AudioClip")
+        .def_readonly("sample_rate", &AudioClip::sample_rate)
+        .def_property_readonly("samples", [](const AudioClip& c) { return py::array_t<float>(c.samples.size(), c.samples.data()); });
+    m.def("parse_wav", [](py::bytes b) { return parse_wav(std::string(b)); });
+    m.def("load_wav", &load_wav);
+    m.def("resample_linear", [](py::array_t<float, py::array::c_style | py::array::forcecast> x, int from_rate, int to_rate) {
+        std::vector<float> v(x.data(), x.data() + x.size());
+        const auto y = resample_linear(v, from_rate, to_rate);
+        return py::array_t<float>(y.size(), y.data());
+    });
+    py::class_<MelConfig>(m, "MelConfig")
+        .def(py::init<>())
+        .def_readwrite("sample_rate", &MelConfig::sample_rate)
+        .def_readwrite("n_fft", &MelConfig::n_fft)
+        .def_readwrite("hop", &MelConfig::hop)
+        .def_readwrite("n_mels", &MelConfig::n_mels)
+        .def_readwrite("f_min", &MelConfig::f_min)
+        .def_readwrite("f_max", &MelConfig::f_max)
+        .def_readwrite("whisper_norm", &MelConfig::whisper_norm)
+        .def_readwrite("pad_to_samples", &MelConfig::pad_to_samples);
+    m.def("mel_filterbank", [](const MelConfig& c) {
+        const auto fb = mel_filterbank(c);
+        py::array_t<float> out({static_cast<py::ssize_t>(c.n_mels), static_cast<py::ssize_t>(c.n_fft / 2 + 1)});
+        std::copy(fb.begin(), fb.end(), out.mutable_data());
+        return out;
+    });
+    m.def("log_mel_spectrogram", [](py::array_t<float, py::array::c_style | py::array::forcecast> x, const MelConfig& c) {
+        std::vector<float> v(x.data(), x.data() + x.size());
+        int frames = 0;
+        std::vector<float> mel;
+        {
+            py::gil_scoped_release rel;
+            mel = log_mel_spectrogram(v, c, &frames);
+        }
+        py::array_t<float> out({static_cast<py::ssize_t>(c.n_mels), static_cast<py::ssize_t>(frames)});
+        std::copy(mel.begin(), mel.end(), out.mutable_data());
+        return out;
+    });
+    py::class_<Image>(m, "Image")
+        .def_readonly("width", &Image::width)
+        .def_readonly("height", &Image::height)
+        .def_readonly("channels", &Image::channels)
+        .def_property_readonly("pixels", [](const Image& im) {
+            py::array_t<uint8_t> out({static_cast<py::ssize_t>(im.height), static_cast<py::ssize_t>(im.width), static_cast<py::ssize_t>(im.channels)});
+            std::copy(im.pixels.begin(), im.pixels.end(), out.mutable_data());
+            return out;
+        });
+    m.def("parse_image", [](py::bytes b) { return parse_image(std::string(b)); });
+    m.def("load_image", &load_image);
+    m.def("image_from_array", [](py::array_t<uint8_t, py::array::c_style | py::array::forcecast> a) {
+        if (a.ndim() != 3) throw std::runtime_error("expected an HWC uint8 array");
+        Image im;
+        im.height = static_cast<int>(a.shape(0));
+        im.width = static_cast<int>(a.shape(1));
+        im.channels = static_cast<int>(a.shape(2));
+        im.pixels.assign(a.data(), a.data() + a.size());
+        return im;
+    });
+    m.def("resize_bilinear", &resize_bilinear);
+    m.def("resize_bicubic", &resize_bicubic);
+    m.def("normalize_chw", [](const Image& im, const std::vector<float>& mean, const std::vector<float>& stddev) {
+        const auto v = normalize_chw(im, mean, stddev);
+        py::array_t<float> out({static_cast<py::ssize_t>(im.channels), static_cast<py::ssize_t>(im.height), static_cast<py::ssize_t>(im.width)});
+        std::copy(v.begin(), v.end(), out.mutable_data());
+        return out;
+    });
+    m.def("smart_resize", [](int h, int w, int factor, long long min_pixels, long long max_pixels) {
+        int oh = 0, ow = 0;
+        smart_resize(h, w, factor, min_pixels, max_pixels, &oh, &ow);
+        return py::make_tuple(oh, ow);
+    });
 }
