@@ -12,6 +12,7 @@
 #include "json.h"
 #include "media.h"
 #include "paged_kv.h"
+#include "ple.h"
 #include "runtime_core.h"
 #include "scheduler.h"
 #include "streaming.h"
@@ -512,4 +513,46 @@ PYBIND11_MODULE(_telb_runtime, m) {
         smart_resize(h, w, factor, min_pixels, max_pixels, &oh, &ow);
         return py::make_tuple(oh, ow);
     });
+    // ---- per-layer-embedding store ---------------------------------------------------------------
+    py::class_<PleTable>(m, "PleTable")
+        .def(py::init<const std::string&>())
+        .def_static("write", [](const std::string& path, py::array data, uint32_t layers, uint32_t dtype) {
+            if (data.ndim() != 2 || !(data.flags() & py::array::c_style)) throw std::runtime_error("expected a C-contiguous 2-D array");
+            PleTable::write(path, data.data(), static_cast<uint32_t>(data.shape(0)), static_cast<uint32_t>(data.shape(1) * data.itemsize()), layers, dtype);
+        })
+        .def_property_readonly("rows", &PleTable::rows)
+        .def_property_readonly("row_bytes", &PleTable::row_bytes)
+        .def_property_readonly("layers", &PleTable::layers)
+        .def_property_readonly("dtype", &PleTable::dtype);
+    py::class_<PleRun>(m, "PleRun")
+        .def_readonly("first_row", &PleRun::first_row)
+        .def_readonly("count", &PleRun::count)
+        .def_readonly("staging_row", &PleRun::staging_row);
+    py::class_<PleReadPlan>(m, "PleReadPlan")
+        .def_readonly("slots", &PleReadPlan::slots)
+        .def_readonly("miss_rows", &PleReadPlan::miss_rows)
+        .def_readonly("miss_slots", &PleReadPlan::miss_slots)
+        .def_readonly("runs", &PleReadPlan::runs)
+        .def_readonly("hits", &PleReadPlan::hits)
+        .def_readonly("misses", &PleReadPlan::misses)
+        .def_readonly("deferred", &PleReadPlan::deferred)
+        .def_readonly("bytes", &PleReadPlan::bytes);
+    py::class_<PleIoBudget>(m, "PleIoBudget")
+        .def(py::init<uint64_t, int>(), py::arg("bytes_per_step"), py::arg("burst_steps") = 2)
+        .def("begin_step", &PleIoBudget::begin_step)
+        .def("take", &PleIoBudget::take)
+        .def_property_readonly("available", &PleIoBudget::available);
+    py::class_<PleCache>(m, "PleCache")
+        .def(py::init<int>())
+        .def("plan", &PleCache::plan, py::arg("ids"), py::arg("row_bytes"), py::arg("budget") = nullptr)
+        .def("lookup", &PleCache::lookup)
+        .def_property_readonly("slots", &PleCache::slots)
+        .def_property_readonly("hits", &PleCache::hits)
+        .def_property_readonly("misses", &PleCache::misses);
+    py::class_<PleReadExecutor>(m, "PleReadExecutor")
+        .def(py::init<int>(), py::arg("threads") = 2)
+        .def("read", [](PleReadExecutor& ex, const PleTable& t, const PleReadPlan& plan, uintptr_t staging) {
+            py::gil_scoped_release rel;
+            ex.read(t, plan, reinterpret_cast<uint8_t*>(staging));
+        });
 }
