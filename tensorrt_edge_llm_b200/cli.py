@@ -21,6 +21,7 @@ COMMANDS = {
     "process-lora": ("tensorrt_edge_llm_b200.commands.process_lora_weights", "Process LoRA adapter weights"),
     "merge-lora": ("tensorrt_edge_llm_b200.commands.merge_lora", "Merge a LoRA adapter into a checkpoint"),
     "reduce-vocab": ("tensorrt_edge_llm_b200.commands.reduce_vocab", "Generate reduced-vocabulary artifacts"),
+    "infer": ("tensorrt_edge_llm_b200.commands.infer", "Run a request file and write predictions"),
     "multistage": ("tensorrt_edge_llm_b200.commands.multistage", "Run requests through a multi-stage graph"),
     "bench": ("tensorrt_edge_llm_b200.benchmarks.llm_bench", "Offline benchmark writing report.json"),
 }

@@ -228,3 +228,39 @@ def test_quantize_command_other_formats(ckpt, tmp_path):
         assert trtedge(["quantize", "llm", "--model_dir", ckpt, "--output_dir", out, "--quantization", q, "--group-size", "64"]) == 0
         cos = torch.nn.functional.cosine_similarity(a.flatten(), _logits(out, ids).flatten(), dim=0)
         assert float(cos) > 0.97
+
+
+def test_request_file_parsing_and_run():
+    from tensorrt_edge_llm_b200.chat_template import ChatTemplate
+    from tensorrt_edge_llm_b200.commands.infer import RequestFileError, parse_request_file, run_requests
+    from tensorrt_edge_llm_b200.config import tiny_llama_config
+    from tensorrt_edge_llm_b200.runtime.llm import LLM
+    body = {"temperature": 0.0, "max_generate_length": 5, "num_logprobs": 2, "logit_bias": {"7": -100},
+            "requests": [{"messages": [{"role": "user", "content": "hi"}]},
+                         {"messages": [{"role": "user", "content": [{"type": "text", "text": "yo"}]}], "num_logprobs": 0, "logit_bias": {"9": 100},
+                          "guided_decoding": {"choice": ["ab", "cd"]}, "stop": "b", "sampling_seed": 7}]}
+    reqs = parse_request_file(body)
+    assert reqs[0]["num_logprobs"] == 2 and reqs[0]["logit_bias"] == {7: -100.0} and reqs[0]["guided"] is None and reqs[0]["seed"] == 42
+    assert reqs[1]["num_logprobs"] == 0 and reqs[1]["logit_bias"] == {9: 100.0} and reqs[1]["guided"].type == "choice" and reqs[1]["seed"] == 7
+    for bad in ({}, {"requests": []}, {"requests": [{"messages": [{"role": "robot", "content": "x"}]}]},
+                {"requests": [{"messages": [{"role": "user", "content": "x"}], "num_logprobs": 51}]},
+                {"requests": [{"messages": [{"role": "user", "content": "x"}], "guided_decoding": {"regex": "a", "choice": ["b"]}}]}):
+        with pytest.raises(RequestFileError):
+            parse_request_file(bad)
+
+    class Bytes:
+        def encode(self, text, add_special_tokens=False):
+            return [b + 3 for b in text.encode("utf-8")]
+
+        def decode(self, ids, skip_special_tokens=True):
+            return bytes((i - 3) % 256 for i in ids).decode("utf-8", "replace")
+
+        def id_to_bytes(self, i):
+            return bytes([(i - 3) % 256])
+    llm = LLM(tiny_llama_config(num_hidden_layers=1, vocab_size=300), device="cpu", max_batch_size=1, max_input_len=128, max_kv_cache_capacity=192,
+              page_size=16, tokenizer=Bytes())
+    reqs[1]["logit_bias"] = None
+    res = run_requests(llm, ChatTemplate(), reqs)
+    assert res[0]["output_tokens"] == 5 and len(res[0]["logprobs"]) == 5 and len(res[0]["logprobs"][0]["top"]) == 2
+    assert res[1]["output_text"] in ("a", "cd") and "logprobs" not in res[1]             # "ab" is cut at the stop string
+    llm.close()
