@@ -159,3 +159,72 @@ def merge_image_embeddings(token_ids: Sequence[int], text_embeds: torch.Tensor, 
     out = text_embeds.clone()
     out[pos] = image_embeds.to(out.dtype)
     return out
+
+
+class EncoderCache:
+    """Encoder outputs keyed by a hash of the decoded media bytes, least-recently-used within a byte budget
+    (``--encoder-cache-budget-bytes`` in the reference, ``docs/source/user_guide/features/kv-cache-reuse.md:166-188``):
+    the same image or clip in a later request skips the encoder."""
+
+    def __init__(self, budget_bytes: int):
+        from collections import OrderedDict
+        self.budget, self.used = int(budget_bytes), 0
+        self._items: "OrderedDict[str, torch.Tensor]" = OrderedDict()
+        self.hits = self.misses = 0
+
+    @staticmethod
+    def key(data) -> str:
+        import hashlib
+        if isinstance(data, torch.Tensor):
+            t = data.detach().contiguous().cpu()
+            data = t.view(torch.uint8).numpy().tobytes() + str((tuple(t.shape), t.dtype)).encode()
+        return hashlib.blake2b(bytes(data), digest_size=16).hexdigest()
+
+    def get(self, key: str) -> Optional[torch.Tensor]:
+        v = self._items.get(key)
+        if v is None:
+            self.misses += 1
+            return None
+        self._items.move_to_end(key)
+        self.hits += 1
+        return v
+
+    def put(self, key: str, value: torch.Tensor) -> None:
+        size = value.numel() * value.element_size()
+        if size > self.budget or key in self._items:
+            return
+        while self.used + size > self.budget and self._items:
+            _, old = self._items.popitem(last=False)
+            self.used -= old.numel() * old.element_size()
+        self._items[key] = value
+        self.used += size
+
+    def encode(self, encoder, inputs: torch.Tensor) -> torch.Tensor:
+        """Run ``encoder`` on the items of ``inputs`` (first dimension) that are not cached; rows come back in input order."""
+        keys = [self.key(x) for x in inputs]
+        outs: List[Optional[torch.Tensor]] = [self.get(k) for k in keys]
+        todo = [i for i, o in enumerate(outs) if o is None]
+        if todo:
+            fresh = encoder(inputs[todo])
+            per = fresh.shape[0] // len(todo)
+            for j, i in enumerate(todo):
+                outs[i] = fresh[j * per:(j + 1) * per]
+                self.put(keys[i], outs[i])
+        return torch.cat(outs, 0)
+
+
+def encode_data_parallel(encoder, inputs: torch.Tensor, comm) -> torch.Tensor:
+    """Vision / audio data parallelism over the tensor-parallel ranks: every rank encodes a contiguous shard of the
+    items and the embedding rows are all-gathered, so each rank ends with all rows in input order
+    (``cpp/runtime/visionDataParallel/visionGather.*`` and ``cpp/runtime/multiDevice/runtimeCoordinator.cpp:376-392``).
+    The item count is padded to a multiple of the world size (the padding items repeat the last one and are dropped)."""
+    world, rank = comm.world_size, comm.rank
+    n = inputs.shape[0]
+    if world == 1 or n == 0:
+        return encoder(inputs)
+    per = (n + world - 1) // world
+    idx = torch.arange(rank * per, (rank + 1) * per).clamp(max=n - 1)
+    mine = encoder(inputs[idx])                                   # [per · rows_per_item, H]
+    full = comm.all_gather_rows(mine.contiguous())                # rank-major = input order
+    rows_per_item = mine.shape[0] // per
+    return full[:n * rows_per_item]

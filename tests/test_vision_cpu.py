@@ -62,3 +62,39 @@ def test_multimodal_prefill_through_runner():
     assert torch.allclose(r.prefill_embeds([0], [r.embed_tokens(ids)]), text_only, atol=1e-6)
     nxt = r.step([0], [[3]])                      # decoding continues from the multimodal prefix
     assert nxt.shape[0] == 1 and kv.lengths[0] == len(ids) + 1
+
+
+def test_encoder_cache_and_data_parallel_shards():
+    from tensorrt_edge_llm_b200.models.vit import EncoderCache, encode_data_parallel
+    cfg = VisionConfig(hidden_size=128, num_hidden_layers=1, num_attention_heads=2, intermediate_size=256, patch_size=4, image_size=16,
+                       out_hidden_size=32, dtype="float32")
+    enc = VisionEncoder(cfg).random_init(0, std=0.1)
+    patches = VisionEncoder.patchify(torch.randn(3, 3, 16, 16, generator=torch.Generator().manual_seed(2)), 4)
+    want = enc(patches)
+    calls = []
+
+    def counted(x):
+        calls.append(x.shape[0])
+        return enc(x)
+    cache = EncoderCache(budget_bytes=2 * 4 * 32 * 4 + 8)               # room for two images' rows
+    assert torch.equal(cache.encode(counted, patches), want) and calls == [3]
+    again = cache.encode(counted, patches[[2, 1, 0]])                   # image 0 was evicted by the budget, 1 and 2 are served
+    assert torch.allclose(again, torch.cat([want[8:12], want[4:8], want[0:4]]), atol=1e-6) and calls == [3, 1] and cache.hits == 2
+    assert cache.used <= cache.budget
+
+    class FakeComm:                                                     # two ranks simulated in one process
+        def __init__(self, rank, peers):
+            self.world_size, self.rank, self.peers = 2, rank, peers
+
+        def all_gather_rows(self, x):
+            self.peers[self.rank] = x
+            other = encode_rank(1 - self.rank) if self.peers[1 - self.rank] is None else self.peers[1 - self.rank]
+            self.peers[1 - self.rank] = other
+            return torch.cat([self.peers[0], self.peers[1]], 0)
+
+    def encode_rank(r):
+        per = 2
+        idx = torch.arange(r * per, (r + 1) * per).clamp(max=2)
+        return enc(patches[idx])
+    out = encode_data_parallel(enc, patches, FakeComm(0, [None, None]))
+    assert out.shape == want.shape and torch.allclose(out, want, atol=1e-6)
