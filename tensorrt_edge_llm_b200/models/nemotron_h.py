@@ -47,6 +47,27 @@ class RecurrentState:
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for d in (self.conv, self.ssm, self.gdn) for t in d.values())
 
+    def pools(self):
+        for d in (self.conv, self.ssm, self.gdn):
+            yield from d.values()
+
+    def snapshot(self, seats) -> list:
+        """Copies of the state rows of ``seats`` (the commit policy of speculative verification restores them when a
+        draft chain is only partly accepted; ``cpp/runtime/commitPolicy/`` in the reference)."""
+        idx = torch.as_tensor(list(seats), dtype=torch.long, device=next(self.pools()).device)
+        return [t.index_select(0, idx) for t in self.pools()]
+
+    def restore(self, seats, snap: list, which=None) -> None:
+        """Write back the rows of ``snap`` for ``seats`` (all of them, or the positions listed in ``which``)."""
+        sel = list(range(len(seats))) if which is None else list(which)
+        if not sel:
+            return
+        dev = next(self.pools()).device
+        dst = torch.as_tensor([seats[j] for j in sel], dtype=torch.long, device=dev)
+        src = torch.as_tensor(sel, dtype=torch.long, device=dev)
+        for t, saved in zip(self.pools(), snap):
+            t.index_copy_(0, dst, saved.index_select(0, src))
+
 
 class MambaMixer(nn.Module):
     def __init__(self, cfg: ModelConfig, prefix: str):
@@ -245,10 +266,13 @@ class HybridTransformer(nn.Module):
     def forward(self, ids, meta, cache, cos_sin, comm, inputs_embeds=None, capture_layers=()):
         h = ops.embedding(ids, self.embed_tokens.weight) if inputs_embeds is None else inputs_embeds
         residual = None
-        for layer in self.layers:
+        taps = []
+        for i, layer in enumerate(self.layers):
             h, residual = layer(h, residual, meta, cache, cos_sin, comm)
+            if i in capture_layers:
+                taps.append((h.float() + residual.float()).to(h.dtype) if comm.world_size == 1 else comm.all_reduce(h).add_(residual))
         x, _ = comm.add_rmsnorm(h, residual, self.norm.weight, self.norm.eps)
-        return x
+        return (x, taps) if capture_layers else x
 
 
 @register_model("nemotron_h", "nemotron_h_hybrid", "qwen3_next", "qwen3_5")

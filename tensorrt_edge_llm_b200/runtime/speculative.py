@@ -57,6 +57,7 @@ class SpecStats:
     rounds: int = 0
     emitted: int = 0
     draft_forwards: int = 0
+    replays: int = 0                 # hybrid targets: sequences whose recurrent state was restored and replayed
 
     @property
     def mean_accept_length(self) -> float:
@@ -74,8 +75,13 @@ def default_tap_layers(num_layers: int) -> List[int]:
 class EagleDecoder:
     def __init__(self, runner: ModelRunner, draft, draft_kv: KVCacheManager, spec: Optional[SpecConfig] = None,
                  tap_layers: Optional[Sequence[int]] = None):
-        if runner.model.cfg.is_hybrid:
-            raise NotImplementedError("speculative decoding over recurrent layers needs state replay, which is not built")
+        spec = spec or SpecConfig()
+        # Recurrent layers cannot evaluate a branching tree in one pass: hybrid targets verify a chain (top-k 1) with
+        # the causal mask, and a partly accepted chain is undone by restoring the state rows saved before the
+        # verification and replaying only the accepted tokens.
+        self.hybrid = bool(runner.model.cfg.is_hybrid)
+        if self.hybrid and spec.top_k != 1:
+            raise ValueError("a hybrid (Mamba / DeltaNet) target verifies a draft chain: set top_k = 1")
         self.r = runner
         self.model = runner.model
         self.draft = draft
@@ -214,7 +220,9 @@ class EagleDecoder:
         anc = self._ancestors(tree_par)
         lt = [self.r.kv.lengths[s] for s in seats]
         pos = [l + int(d) for i, l in enumerate(lt) for d in tree_dep[i].tolist()]
-        logits, taps = self._target_step(seats, tree_tok.reshape(-1).to(torch.int32), [nn_] * b, tree_mask=self._pack_mask(anc), positions=pos)
+        state_before = self.r.kv.recurrent.snapshot(seats) if self.hybrid else None
+        logits, taps = self._target_step(seats, tree_tok.reshape(-1).to(torch.int32), [nn_] * b,
+                                         tree_mask=None if self.hybrid else self._pack_mask(anc), positions=None if self.hybrid else pos)
         tgt = ops.argmax(logits).view(b, nn_)
         timer.end(stage)
         stage = timer.begin(prof.SPEC_ACCEPT, batch=b)
@@ -225,6 +233,17 @@ class EagleDecoder:
         ops.kv_commit_path(self.r.kv.pool, self.r.kv.table_rows(seats).to(dev), past_t, path, plen)
         path_h, plen_h, bonus_h = path.tolist(), plen.tolist(), bonus.tolist()   # the round's one device→host read
         tok_h = tree_tok.tolist()
+        if self.hybrid:
+            # commit policy: the recurrent state now holds all nn_ chain tokens; seats that accepted fewer get their
+            # saved rows back and the accepted prefix is run again (KV rows are rewritten with the same values)
+            short = [i for i in range(b) if plen_h[i] < nn_]
+            if short:
+                self.r.kv.recurrent.restore(seats, state_before, short)
+                sub = [seats[i] for i in short]
+                rows = torch.tensor([t for i in short for t in tok_h[i][:plen_h[i]]], dtype=torch.int32, device=dev)
+                meta = self.r._meta(sub, [plen_h[i] for i in short], logits_all=False)
+                self.model.hidden_states(rows, meta, self.r.cache)
+                self.stats.replays += len(short)
         out: List[List[int]] = []
         acc_rows, acc_tok, q_lens = [], [], []
         for i, s in enumerate(seats):

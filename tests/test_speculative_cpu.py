@@ -174,3 +174,34 @@ def test_llm_generate_with_draft_model_is_lossless():
     assert spec.spec_decoder.stats.rounds > 0 and spec.kv.lengths[0] == 0          # seats released afterwards
     # sampled requests fall back to ordinary decoding
     assert len(spec.generate(prompts, SamplingParams(max_tokens=4, temperature=0.8, ignore_eos=True))[0].token_ids) == 4
+
+
+def test_hybrid_target_chain_verify_with_state_replay():
+    """Mamba2 / DeltaNet target: chain verification, recurrent rows restored and replayed after a partial acceptance."""
+    import pytest
+    from tensorrt_edge_llm_b200.config import GdnConfig, MambaConfig, hybrid_nemotron_config
+    cfg = hybrid_nemotron_config(num_hidden_layers=8, vocab_size=500, hidden_size=64, intermediate_size=128, num_attention_heads=4,
+                                 num_key_value_heads=2, head_dim=16, dtype="float32", max_position_embeddings=512,
+                                 mamba=MambaConfig(num_heads=4, head_dim=8, d_state=16, n_groups=2, conv_kernel=4),
+                                 gdn=GdnConfig(num_k_heads=2, num_v_heads=4, head_k_dim=8, head_v_dim=8, conv_kernel=4))
+    model = AutoModel.from_config(cfg, random_init=0)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, 500, (n,), generator=g).tolist() for n in (7, 13)]
+    want = _greedy(model, prompts, 14)
+    dcfg = tiny_llama_config(num_hidden_layers=1, dtype="float32", vocab_size=500, hidden_size=64, intermediate_size=128,
+                             num_attention_heads=4, num_key_value_heads=2, head_dim=16)
+    dcfg.draft_type, dcfg.eagle3_target_hidden_size = "eagle3", 64
+    draft = AutoModel.from_config(dcfg, random_init=2)
+    with pytest.raises(ValueError):
+        _decoder(model, draft, SpecConfig(draft_steps=3, top_k=2, verify_tokens=8))
+    # random draft: almost every chain is cut short, so nearly every round replays
+    dec = _decoder(model, draft, SpecConfig(draft_steps=3, top_k=1, verify_tokens=4))
+    assert dec.generate([0, 1], prompts, 14) == want and dec.stats.replays > 0
+    # oracle draft: whole chains are accepted, no replay until the streams end
+    streams = {i: prompts[i] + want[i] for i in range(2)}
+    dec = _decoder(model, _OracleDraft(draft, streams), SpecConfig(draft_steps=3, top_k=1, verify_tokens=4))
+    assert dec.generate([0, 1], prompts, 14) == want
+    assert dec.stats.mean_accept_length > 3.0
+    # forced partial acceptance exercises restore + replay on every round and still matches
+    dec = _decoder(model, _OracleDraft(draft, streams), SpecConfig(draft_steps=3, top_k=1, verify_tokens=4, force_accept_len=2))
+    assert dec.generate([0, 1], prompts, 14) == want and dec.stats.replays >= 10
