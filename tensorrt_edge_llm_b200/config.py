@@ -159,6 +159,11 @@ class ModelConfig:
     has_qk_norm: bool = False
     attention_bias: bool = False
     sliding_window: Optional[int] = None
+    layer_windows: List[int] = field(default_factory=list)  # per layer: sliding window in tokens, 0 = full attention (empty = `sliding_window` everywhere)
+    rope_local_theta: float = 0.0                   # RoPE base of the sliding-window layers when it differs (Gemma 3)
+    rope_local_scaling: Optional[Dict[str, Any]] = None
+    query_pre_attn_scalar: float = 0.0              # attention scale = this ** -0.5 when set (Gemma), else head_dim ** -0.5
+    final_logit_softcapping: float = 0.0
     hidden_act: str = "silu"
     dtype: str = "bfloat16"
     # MoE
@@ -299,6 +304,11 @@ class ModelConfig:
         torch_dtype = str(llm.get("torch_dtype", llm.get("dtype", "bfloat16"))).replace("torch.", "")
         if torch_dtype not in ("bfloat16", "float16", "float32"):
             torch_dtype = "bfloat16"
+        extra: Dict[str, Any] = {}
+        if str(model_type).startswith("gemma"):
+            extra = _parse_gemma(llm, n_layers)
+            rope_theta, rope_scaling = extra.pop("rope_theta", rope_theta), extra.pop("rope_scaling", rope_scaling)
+            layer_types = []
         router = "sigmoid_group_topk" if model_type in ("nemotron_h", "deepseek_v3") and llm.get("n_routed_experts") else "softmax_topk"
         return cls(
             model_type=model_type,
@@ -317,8 +327,9 @@ class ModelConfig:
             tie_word_embeddings=bool(hf.get("tie_word_embeddings", llm.get("tie_word_embeddings", False))),
             has_qk_norm=bool(has_qk_norm),
             attention_bias=bool(llm.get("attention_bias", model_type == "qwen2")),
-            sliding_window=llm.get("sliding_window") if llm.get("use_sliding_window", False) else None,
-            hidden_act=llm.get("hidden_act", llm.get("mlp_hidden_act", "silu")),
+            sliding_window=llm.get("sliding_window") if (llm.get("use_sliding_window", False) or extra) else None,
+            hidden_act=llm.get("hidden_activation") or llm.get("hidden_act", llm.get("mlp_hidden_act", "silu")),
+            **extra,
             dtype=torch_dtype,
             num_experts=int(llm.get("num_experts") or llm.get("num_local_experts") or llm.get("n_routed_experts") or 0),
             num_experts_per_tok=int(llm.get("num_experts_per_tok", 0) or 0),
@@ -453,6 +464,30 @@ def _detect_qk_norm(model_dir: str, hf: Dict[str, Any]) -> Optional[bool]:
     if not keys:
         return None
     return any(k.endswith("self_attn.q_norm.weight") for k in keys)
+
+
+def _parse_gemma(llm: Dict[str, Any], n_layers: int) -> Dict[str, Any]:
+    """Gemma 2 / 3 text decoders: alternating sliding-window and full-attention layers with their own RoPE bases."""
+    win = int(llm.get("sliding_window") or 0)
+    kinds = llm.get("layer_types")
+    if not kinds:
+        pat = int(llm.get("sliding_window_pattern", 6) or 6)
+        kinds = ["full_attention" if (i + 1) % pat == 0 else "sliding_attention" for i in range(n_layers)]
+    out: Dict[str, Any] = {"layer_windows": [win if "sliding" in str(k) else 0 for k in kinds],
+                           "query_pre_attn_scalar": float(llm.get("query_pre_attn_scalar") or 0.0),
+                           "final_logit_softcapping": float(llm.get("final_logit_softcapping") or 0.0)}
+    rp = llm.get("rope_parameters") or {}
+    full, local = rp.get("full_attention"), rp.get("sliding_attention")
+    if isinstance(full, dict):
+        out["rope_theta"] = full.get("rope_theta", 1e6)
+        out["rope_scaling"] = None if full.get("rope_type", "default") == "default" else full
+        out["rope_local_theta"] = float((local or {}).get("rope_theta", 1e4))
+        out["rope_local_scaling"] = None if (local or {}).get("rope_type", "default") == "default" else local
+    else:
+        out["rope_local_theta"] = float(llm.get("rope_local_base_freq", 0.0) or 0.0)
+    if llm.get("attn_logit_softcapping"):
+        raise ValueError("attention logit soft-capping (Gemma 2) is not supported by the attention kernels")
+    return out
 
 
 def _parse_hybrid(llm: Dict[str, Any], n_layers: int):

@@ -178,6 +178,29 @@ __global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, lon
     }
 }
 
+// out[t, i] = gelu(in[t, i]) * in[t, inter + i]   (tanh form or exact erf form)
+template <typename T>
+__global__ void geglu_kernel(const T* __restrict__ in, T* __restrict__ out, long long rows, int inter, int tanh_approx) {
+    pdl_prologue();
+    const long long nvec = rows * (inter / 8);
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < nvec;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long r = idx / (inter / 8);
+        const int c = (int)(idx % (inter / 8)) * 8;
+        Vec8<T> g, u, o;
+        g.load(in + r * 2 * inter + c);
+        u.load(in + r * 2 * inter + inter + c);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float x = g.get(j);
+            const float act = tanh_approx ? 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)))
+                                          : 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
+            o.set(j, act * u.get(j));
+        }
+        o.store(out + r * inter + c);
+    }
+}
+
 template <typename T>
 __global__ void relu2_kernel(const T* __restrict__ in, T* __restrict__ out, long long n) {
     pdl_prologue();
@@ -518,6 +541,17 @@ extern "C" int telb_swiglu(const void* in, void* out, long long rows, int inter,
     if (blocks > 148 * 16) blocks = 148 * 16;
     DISPATCH_T(is_bf16, { TELB_LAUNCH("swiglu_kernel", (swiglu_kernel<T>), dim3((int)blocks), dim3(256), 0, stream, (const T*)in, (T*)out, rows, inter); })
     TELB_CHECK_LAUNCH("swiglu_kernel");
+    return 0;
+}
+
+extern "C" int telb_geglu(const void* in, void* out, long long rows, int inter, int tanh_approx, int is_bf16, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (inter % 8) return fail("telb_geglu: intermediate size must be a multiple of 8");
+    const long long nvec = rows * (inter / 8);
+    long long blocks = (nvec + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    DISPATCH_T(is_bf16, { TELB_LAUNCH("geglu_kernel", (geglu_kernel<T>), dim3((int)blocks), dim3(256), 0, stream, (const T*)in, (T*)out, rows, inter, tanh_approx); })
+    TELB_CHECK_LAUNCH("geglu_kernel");
     return 0;
 }
 

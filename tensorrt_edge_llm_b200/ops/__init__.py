@@ -67,6 +67,15 @@ def swiglu(gate_up, quant_scale=None):
     return ref.swiglu(gate_up)
 
 
+def geglu(gate_up, tanh_approx=True):
+    """``gelu(gate) * up`` over the fused ``[T, 2·I]`` projection output (GeGLU MLPs)."""
+    if gate_up.is_cuda:
+        return cuda_ops().geglu(gate_up, tanh_approx)
+    inter = gate_up.shape[-1] // 2
+    g = torch.nn.functional.gelu(gate_up[..., :inter].float(), approximate="tanh" if tanh_approx else "none")
+    return (g * gate_up[..., inter:].float()).to(gate_up.dtype)
+
+
 def relu2(x):
     if x.is_cuda:
         return cuda_ops().relu2(x)

@@ -142,6 +142,15 @@ def gated_group_rmsnorm(x, z, weight, n_groups, eps):
     return y
 
 
+def geglu(gate_up: torch.Tensor, tanh_approx: bool = True) -> torch.Tensor:
+    rows, two = gate_up.shape
+    inter = two // 2
+    out = torch.empty(rows, inter, dtype=gate_up.dtype, device=gate_up.device)
+    _check(lib().telb_geglu(_p(gate_up), _p(out), c_ll(rows), c_int(inter), c_int(1 if tanh_approx else 0), c_int(_is_bf16(gate_up)),
+                            _stream()), "geglu")
+    return out
+
+
 def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     gate_up = gate_up.contiguous()
     inter = gate_up.shape[-1] // 2

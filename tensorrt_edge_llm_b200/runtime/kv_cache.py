@@ -66,6 +66,9 @@ class KVCacheManager:
         # window are handed back to the pool as the sequence grows.  Both attention kernels start their KV loop at a
         # 128-token tile boundary at or below `past - window + 1`; the retire boundary is rounded down the same way.
         win = getattr(cfg, "sliding_window", None)
+        per_layer = getattr(cfg, "layer_windows", None)
+        if per_layer:                            # mixed stacks: one full-attention layer keeps every page alive
+            win = max(per_layer) if all(per_layer) else 0
         self.window = int(win) if win else 0
         self.bounded_swa = bool(self.window) if bounded_swa is None else (bool(bounded_swa) and bool(self.window))
         self.retired_pages = 0

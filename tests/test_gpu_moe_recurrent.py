@@ -267,3 +267,27 @@ def test_vision_encoder_gpu_matches_cpu(cu):
     for approx in (False, True):
         assert _rel_err(cu.gelu(x.cuda(), approx).cpu(), torch.nn.functional.gelu(x.float(), approximate="tanh" if approx else "none")) < 5e-3
     _sync_check(cu)
+
+
+@pytest.mark.parametrize("tanh", [True, False])
+def test_geglu(cu, tanh):
+    from tensorrt_edge_llm_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(12)
+    x = (torch.randn(37, 2 * 264, device="cuda", generator=g) * 1.5).bfloat16()
+    want = ops.geglu(x.cpu(), tanh).float()
+    got = cu.geglu(x, tanh).float().cpu()
+    assert (got - want).abs().max() < 2e-2 * want.abs().max()
+    _sync_check(cu)
+
+
+def test_audio_encoder_gpu_matches_cpu(cu):
+    from tensorrt_edge_llm_b200.models.audio import AudioConfig, AudioEncoder
+    cfg = AudioConfig(n_mels=64, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, intermediate_size=512, max_source_positions=100,
+                      avg_pool=2, out_hidden_size=256, dtype="bfloat16")
+    enc = AudioEncoder(cfg).random_init(0, std=0.05)
+    mel = torch.randn(2, 64, 200, generator=torch.Generator().manual_seed(3))
+    want = enc(mel).float()
+    got = enc.to("cuda")(mel.cuda()).float().cpu()
+    assert got.shape == (100, 256)
+    assert (got - want).abs().max() < 0.05 * max(want.abs().max().item(), 1.0)
+    _sync_check(cu)
