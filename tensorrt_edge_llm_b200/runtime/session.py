@@ -12,6 +12,7 @@ executeContext/Decode/Compact) and the context-cache request flow
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from typing import Dict, List, Optional
 
 import torch
@@ -38,7 +39,7 @@ class _Seq:
 
 class ModelSession(rt.RuntimeSession):
     def __init__(self, runner: ModelRunner, eos_ids=(), enable_prefix_cache: bool = False, max_input_len: int = 2048,
-                 guided_vocab=None):
+                 guided_vocab=None, max_snapshots: int = 64):
         super().__init__()
         self.runner = runner
         self.guided_vocab = guided_vocab
@@ -51,6 +52,13 @@ class ModelSession(rt.RuntimeSession):
         self.prefix = rt.PrefixCache(self.kv.native.allocator(), self.kv.page_size, 4096) if (
             enable_prefix_cache and getattr(self.kv, "native", None) is not None and not self.kv.bounded_swa) else None
         self._swa_bound = self.kv.swa_live_pages_bound(runner.max_num_tokens) if self.kv.bounded_swa else 0
+        # Hybrid models: shared KV pages alone do not restore a prefix, the recurrent rows at that boundary are needed
+        # too.  Snapshots are taken at page-aligned prefill boundaries and keyed by the same chained block hash as the
+        # page index (``cpp/runtime/state/contextCache/hybridSnapshotStorage.*`` in the reference).
+        self.hybrid = bool(runner.model.cfg.is_hybrid)
+        self.snapshots: "OrderedDict[int, list]" = OrderedDict()
+        self.max_snapshots = max_snapshots
+        self.snapshot_hits = 0
 
     # ---- seam ------------------------------------------------------------------------------------
     def capabilities(self):
@@ -89,9 +97,12 @@ class ModelSession(rt.RuntimeSession):
         try:
             if self.prefix is not None:
                 m = self.prefix.lookup(list(req.prompt_ids))
-                if m.tokens:
-                    self.kv.adopt_prefix(slot, m.pages, m.tokens)
-                    reused = m.tokens
+                pages, tokens = list(m.pages), m.tokens
+                if tokens and self.hybrid:
+                    pages, tokens = self._restore_snapshot(slot, req.prompt_ids, pages)
+                if tokens:
+                    self.kv.adopt_prefix(slot, pages, tokens)
+                    reused = tokens
             if self.kv.bounded_swa:
                 # pages are taken step by step and handed back as the window moves on; admission keeps the sum of the
                 # residents' worst-case live pages inside the pool, so a later step cannot run out
@@ -116,9 +127,72 @@ class ModelSession(rt.RuntimeSession):
         with prof.time_stage(prof.IFB_EXECUTE, batch=len(plan.seqs), tokens=plan.total_tokens):
             return self._execute(plan)
 
+    # ---- hybrid prefix snapshots ---------------------------------------------------------------
+    def _chain_hashes(self, tokens, n_pages: int):
+        p, h, out = self.kv.page_size, 0, []
+        for i in range(n_pages):
+            h = rt.PrefixCache.hash_block(h, list(tokens[i * p:(i + 1) * p]))
+            out.append(h)
+        return out
+
+    def _restore_snapshot(self, slot: int, prompt_ids, pages):
+        """Longest page prefix of ``pages`` that also has a recurrent snapshot: its rows go into the seat's state."""
+        hashes = self._chain_hashes(prompt_ids, len(pages))
+        for k in range(len(pages), 0, -1):
+            snap = self.snapshots.get(hashes[k - 1])
+            if snap is not None:
+                self.snapshots.move_to_end(hashes[k - 1])
+                self.kv.recurrent.restore([slot], snap)
+                self.snapshot_hits += 1
+                return pages[:k], k * self.kv.page_size
+        return [], 0
+
+    def _take_snapshot(self, slot: int, q, upto_tokens: int) -> None:
+        h = self._chain_hashes(q.req.prompt_ids, upto_tokens // self.kv.page_size)[-1]
+        if h in self.snapshots:
+            self.snapshots.move_to_end(h)
+            return
+        self.snapshots[h] = self.kv.recurrent.snapshot([slot])
+        while len(self.snapshots) > self.max_snapshots:
+            self.snapshots.popitem(last=False)
+
     def _execute(self, plan):
+        seqs = list(plan.seqs)                            # the binding hands out copies: edit and use this one list
+        if self.hybrid and self.prefix is not None:
+            self._prefill_to_page_boundary(seqs)
+        return self._execute_plan(seqs)
+
+    def _prefill_to_page_boundary(self, seqs) -> None:
+        """A prompt's last chunk is cut at the last page boundary: the part before it runs first, the recurrent rows
+        there are saved for later requests with the same prefix, and the plan keeps only the rest."""
+        p = self.kv.page_size
+        head_seats, head_tokens, cut = [], [], []
+        for s in seqs:
+            if s.kind != rt.WorkKind.Context:
+                continue
+            q = self.seqs[s.slot]
+            end = s.start + s.length
+            boundary = end // p * p
+            if s.last_chunk and s.start < boundary < end:
+                head_seats.append(s.slot)
+                head_tokens.append(q.tokens[s.start:boundary])
+                cut.append((s, boundary))
+            elif not s.last_chunk and end % p == 0:
+                cut.append((s, None))                     # ends on a boundary by itself: snapshot after the main step
+        if head_seats:
+            self.runner.step(head_seats, head_tokens)
+        self._snap_after = []
+        for s, boundary in cut:
+            if boundary is None:
+                self._snap_after.append((s.slot, s.start + s.length))
+            else:
+                self._take_snapshot(s.slot, self.seqs[s.slot], boundary)
+                s.length -= boundary - s.start
+                s.start = boundary
+
+    def _execute_plan(self, seqs):
         seats, token_lists, producers = [], [], []
-        for s in plan.seqs:
+        for s in seqs:
             q = self.seqs[s.slot]
             if s.kind == rt.WorkKind.Context:
                 toks = q.tokens[s.start:s.start + s.length]
@@ -164,9 +238,12 @@ class ModelSession(rt.RuntimeSession):
                     d.finished = True
                     d.reason = rt.FinishReason.EndId if tok in self.eos else rt.FinishReason.StopWords
                 deltas.append(d)
+        for slot, upto in getattr(self, "_snap_after", []):
+            self._take_snapshot(slot, self.seqs[slot], upto)
+        self._snap_after = []
         # a finished prefill publishes its full prompt pages for reuse
         if self.prefix is not None:
-            for s in plan.seqs:
+            for s in seqs:
                 if s.kind == rt.WorkKind.Context and s.last_chunk:
                     q = self.seqs[s.slot]
                     self.prefix.insert(list(q.req.prompt_ids), len(q.req.prompt_ids), self.kv.pages_of(s.slot))

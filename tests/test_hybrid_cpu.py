@@ -75,3 +75,29 @@ def test_recurrent_reference_ops_are_consistent():
     outs = [ref.gated_delta_rule(q[i:i + 1], k[i:i + 1], v[i:i + 1], a[i:i + 1], b[i:i + 1], A_log, dtb, s2,
                                  build_step_meta([1], [i], table, 16)) for i in range(t)]
     assert torch.allclose(torch.cat(outs), o_full, atol=1e-5) and torch.allclose(s1, s2, atol=1e-5)
+
+
+def test_prefix_reuse_restores_recurrent_snapshots():
+    """In-flight batching with the prefix cache on a hybrid model: shared pages come with the recurrent rows saved at
+    the same page boundary, so a repeated prompt (and a prompt sharing a prefix) gives the tokens of a cold run."""
+    from tensorrt_edge_llm_b200.runtime.llm import LLM
+    from tensorrt_edge_llm_b200.runtime.runner import SamplingParams
+    cfg = _cfg()
+    g = torch.Generator().manual_seed(11)
+    base = torch.randint(0, 500, (75,), generator=g).tolist()
+    other = base[:48] + torch.randint(0, 500, (20,), generator=g).tolist()          # shares three 16-token pages
+    sp = SamplingParams(max_tokens=6, ignore_eos=True)
+    kw = dict(device="cpu", max_batch_size=2, max_input_len=128, max_kv_cache_capacity=160, page_size=16, enable_in_flight_batching=True,
+              scheduling={"mode": "mixed", "max_num_tokens": 64, "max_chunk_tokens": 32})
+    cold = LLM(cfg, **kw)
+    want_base, want_other = (o.token_ids for o in cold.generate([base, other], sp))
+    cold.close()
+    warm = LLM(cfg, enable_prefix_cache=True, **kw)
+    assert warm.generate([base], sp)[0].token_ids == want_base
+    reused0 = warm.engine.metrics().prefix_reused_tokens
+    assert warm.generate([base], sp)[0].token_ids == want_base                     # 64 of 75 tokens reused with their state
+    assert warm.engine.metrics().prefix_reused_tokens - reused0 == 64
+    # 48 tokens are shared, but snapshots exist where prefill chunks ended (32, 64): the longest usable prefix is 32
+    assert warm.generate([other], sp)[0].token_ids == want_other
+    assert warm.engine.metrics().prefix_reused_tokens - reused0 == 64 + 32
+    warm.close()
