@@ -149,6 +149,80 @@ def bench_attention(args):
     cu.Workspace.get(torch.device("cuda", 0)).check_status()
 
 
+def bench_ops(args):
+    """Bandwidth-bound and recurrent kernels at prefill size (``--tokens`` rows of the Qwen3-8B / hybrid shapes): achieved
+    bytes per second over the algorithmic bytes, against the measured copy bandwidth."""
+    from ..ops import build_step_meta
+    from ..ops import cuda as cu
+    bw, _, tag = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    t, h, inter = args.tokens, 4096, 12288
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(t, h, device="cuda", generator=g).bfloat16()
+    res = torch.randn(t, h, device="cuda", generator=g).bfloat16()
+    w = torch.ones(h, device="cuda").bfloat16()
+    gs = torch.full((1,), 1.0 / 448, device="cuda")
+    gu = torch.randn(t, 2 * inter, device="cuda", generator=g).bfloat16()
+    nf = 0.5625                                                         # NVFP4 bytes per element incl. block scales
+    cases = {
+        "add_rmsnorm": (lambda: cu.add_rmsnorm(x, res, w, 1e-6), t * h * 2 * 4),
+        "add_rmsnorm_quant": (lambda: cu.rmsnorm_quant(x, res, w, 1e-6, gs), t * h * (2 * 3 + nf)),
+        "swiglu_quant": (lambda: cu.swiglu_quant(gu, gs), t * inter * (4 + nf)),
+        "nvfp4_quantize": (lambda: cu.nvfp4_quantize(x, gs), t * h * (2 + nf)),
+    }
+    # RoPE + q/k norm + paged KV write (32 q / 8 kv heads of 128)
+    hq, hkv, d, page = 32, 8, 128, 64
+    seqs = max(t // 1024, 1)
+    per = t // seqs
+    pages_per = (per + page - 1) // page
+    table = torch.arange(seqs * pages_per, dtype=torch.int32).view(seqs, pages_per)
+    meta = build_step_meta([per] * seqs, [0] * seqs, table, page, device="cuda")
+    kvp = torch.zeros(seqs * pages_per, 2, hkv, page, d, device="cuda", dtype=torch.bfloat16)
+    qkv = torch.randn(seqs * per, (hq + 2 * hkv) * d, device="cuda", generator=g).bfloat16()
+    from ..ops import reference as ref
+    cs = ref.rope_cos_sin(per + 8, d, 1e6, None, device="cuda")
+    nw = torch.ones(d, device="cuda").bfloat16()
+    cases["rope_qknorm_kv_write"] = (lambda: cu.rope_kv_write(qkv, kvp, meta, cs, hq, hkv, d, nw, nw, 1e-6),
+                                     seqs * per * ((hq + 2 * hkv) * d * 2 + (hq + 2 * hkv) * d * 2))
+    # Mamba2 segmented scan (64 heads of 64, state 128, 8 groups) and gated DeltaNet (16 / 32 heads of 128)
+    nh, hd, ns, ng = 64, 64, 128, 8
+    xs = torch.randn(seqs * per, nh, hd, device="cuda", generator=g).bfloat16()
+    dt = torch.randn(seqs * per, nh, device="cuda", generator=g).bfloat16()
+    A = -torch.rand(nh, device="cuda", generator=g) - 0.5
+    Bm = torch.randn(seqs * per, ng, ns, device="cuda", generator=g).bfloat16()
+    Cm = torch.randn(seqs * per, ng, ns, device="cuda", generator=g).bfloat16()
+    Dv, dtb = torch.ones(nh, device="cuda"), torch.zeros(nh, device="cuda")
+    st = torch.zeros(seqs, nh, hd, ns, device="cuda")
+    cases["ssm_scan_prefill"] = (lambda: cu.ssm_scan(xs, dt, A, Bm, Cm, Dv, dtb, st, meta),
+                                 seqs * per * (nh * hd * 2 * 2 + nh * 2 + 2 * ng * ns * 2) + seqs * nh * hd * ns * 4 * 2)
+    hk, hv, dk = 16, 32, 128
+    qg = torch.randn(seqs * per, hk, dk, device="cuda", generator=g).bfloat16()
+    kg = torch.nn.functional.normalize(torch.randn(seqs * per, hk, dk, device="cuda", generator=g), dim=-1).bfloat16()
+    vg = torch.randn(seqs * per, hv, dk, device="cuda", generator=g).bfloat16()
+    ag = torch.randn(seqs * per, hv, device="cuda", generator=g).bfloat16()
+    bg = torch.randn(seqs * per, hv, device="cuda", generator=g).bfloat16()
+    gst = torch.zeros(seqs, hv, dk, dk, device="cuda")
+    cases["gated_delta_rule_prefill"] = (lambda: cu.gated_delta_rule(qg, kg, vg, ag, bg, torch.zeros(hv, device="cuda"), torch.zeros(hv, device="cuda"),
+                                                                     gst, meta),
+                                         seqs * per * (2 * hk * dk * 2 + 2 * hv * dk * 2 + 2 * hv * 2) + seqs * hv * dk * dk * 4 * 2)
+    # sampling over the Qwen3 vocabulary
+    logits = torch.randn(64, 151936, device="cuda", generator=g).bfloat16()
+    cases["argmax_b64"] = (lambda: cu.argmax(logits), 64 * 151936 * 2)
+    u = torch.rand(64, device="cuda")
+    tk = torch.full((64,), 50, dtype=torch.int32, device="cuda")
+    cases["sample_topk_topp_b64"] = (lambda: cu.sample(logits, torch.full((64,), 0.8, device="cuda"), tk, torch.full((64,), 0.9, device="cuda"), u),
+                                     64 * 151936 * 2)
+    want = set(args.only) if args.only else None
+    for name, (fn, byts) in cases.items():
+        if want and name not in want:
+            continue
+        med, best = time_fn(fn, args.warmup, args.iters, flush)
+        print(json.dumps({"kernel": name, "tokens": t, "median_us": round(med * 1e6, 2), "best_us": round(best * 1e6, 2),
+                          "algorithmic_mb": round(byts / 1e6, 1), "gbs": round(byts / med / 1e9, 1),
+                          "fraction": round(byts / med / bw, 3), "basis": tag + " (copy bandwidth)"}))
+    cu.Workspace.get(torch.device("cuda", 0)).check_status()
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -166,12 +240,15 @@ def main():
     a.add_argument("--check", action="store_true", help="compare with the fp32 reference first")
     a.add_argument("--trace", action="store_true", help="print the per-tile timeline of the first CTA of the decode kernel")
     a.add_argument("--trace-tiles", type=int, default=0, help="tiles of the first CTA to print (it walks several items)")
-    for p in (g, a):
+    o = sub.add_parser("ops")
+    o.add_argument("--tokens", type=int, default=8192)
+    o.add_argument("--only", nargs="*", default=None)
+    for p in (g, a, o):
         p.add_argument("--warmup", type=int, default=3)
         p.add_argument("--iters", type=int, default=10)
         p.add_argument("--graph", type=int, default=0, help="time decode-size calls as N captured launches per replay")
     args = ap.parse_args()
-    {"gemm": bench_gemm, "attention": bench_attention}[args.cmd](args)
+    {"gemm": bench_gemm, "attention": bench_attention, "ops": bench_ops}[args.cmd](args)
 
 
 if __name__ == "__main__":
