@@ -347,6 +347,101 @@ __global__ void rope_kv_write_warp_kernel(const T* __restrict__ qkv, T* __restri
     }
 }
 
+// Prefill form for head_dim 128: one warp per token walks all heads two at a time (half a warp per head, 8-byte
+// accesses), so the token's cos / sin row, its norm weights and its page look-up are fetched once instead of once per head.
+template <typename T>
+__global__ void rope_kv_write_token_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ kv_layer,
+                                           const float* __restrict__ cos_sin, const int* __restrict__ positions,
+                                           const int* __restrict__ seq_ids, const int* __restrict__ q_start,
+                                           const int* __restrict__ past_len, const int* __restrict__ page_table,
+                                           const int* __restrict__ kv_offsets, const T* __restrict__ q_norm_w,
+                                           const T* __restrict__ k_norm_w, int tokens, int hq, int hkv, int page_size,
+                                           int max_pages, float eps) {
+    pdl_prologue();
+    constexpr int D = 128, half = 64;
+    const int t = (int)((blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5);
+    if (t >= tokens) return;
+    const int lane = threadIdx.x & 31;
+    const int sub = lane >> 4, li = lane & 15;           // which head of the pair, and this lane's 4 features li*4 .. li*4+3
+    const int heads = hq + 2 * hkv;
+    const float* cs = cos_sin + (size_t)positions[t] * D;
+    const float4 c4 = *reinterpret_cast<const float4*>(cs + li * 4);
+    const float4 s4 = *reinterpret_cast<const float4*>(cs + half + li * 4);
+    const float c[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+    float qwa[4], qwb[4], kwa[4], kwb[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        qwa[i] = q_norm_w ? Cvt<T>::to_f(q_norm_w[li * 4 + i]) : 1.f;
+        qwb[i] = q_norm_w ? Cvt<T>::to_f(q_norm_w[half + li * 4 + i]) : 1.f;
+        kwa[i] = k_norm_w ? Cvt<T>::to_f(k_norm_w[li * 4 + i]) : 1.f;
+        kwb[i] = k_norm_w ? Cvt<T>::to_f(k_norm_w[half + li * 4 + i]) : 1.f;
+    }
+    const int s = seq_ids[t];
+    const int off = kv_offsets ? kv_offsets[t] : (t - q_start[s]);
+    const int slot = past_len[s] + off;
+    const int page = page_table[(size_t)s * max_pages + slot / page_size];
+    const T* row = qkv + (size_t)t * heads * D;
+#pragma unroll 4
+    for (int h0 = 0; h0 < heads; h0 += 2) {
+        const int h = h0 + sub;
+        const bool live = h < heads;
+        const bool is_q = h < hq;
+        const bool is_k = !is_q && h < hq + hkv;
+        float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
+        if (live) {
+            const uint2 ua = *reinterpret_cast<const uint2*>(row + (size_t)h * D + li * 4);
+            const uint2 ub = *reinterpret_cast<const uint2*>(row + (size_t)h * D + half + li * 4);
+            const T* ea = reinterpret_cast<const T*>(&ua);
+            const T* eb = reinterpret_cast<const T*>(&ub);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                a[i] = Cvt<T>::to_f(ea[i]);
+                b[i] = Cvt<T>::to_f(eb[i]);
+            }
+        }
+        const bool normed = (is_q && q_norm_w) || (is_k && k_norm_w);
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ss += a[i] * a[i] + b[i] * b[i];
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);      // stays inside the half warp
+        if (normed) {
+            const float inv = rsqrtf(ss / D + eps);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                a[i] = Cvt<T>::to_f(Cvt<T>::from_f(Cvt<T>::to_f(Cvt<T>::from_f(a[i] * inv)) * (is_q ? qwa[i] : kwa[i])));
+                b[i] = Cvt<T>::to_f(Cvt<T>::from_f(Cvt<T>::to_f(Cvt<T>::from_f(b[i] * inv)) * (is_q ? qwb[i] : kwb[i])));
+            }
+        }
+        if (is_q || is_k) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float ra = a[i] * c[i] - b[i] * sn[i];
+                const float rb = b[i] * c[i] + a[i] * sn[i];
+                a[i] = ra;
+                b[i] = rb;
+            }
+        }
+        if (!live) continue;
+        T* dst;
+        if (is_q) {
+            dst = q_out + ((size_t)t * hq + h) * D;
+        } else {
+            if (page < 0) continue;                    // unreserved page: skip instead of writing out of bounds
+            const int kvh = is_k ? h - hq : h - hq - hkv;
+            dst = kv_layer + ((((size_t)page * 2 + (is_k ? 0 : 1)) * hkv + kvh) * page_size + slot % page_size) * D;
+        }
+        T oa[4], ob[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            oa[i] = Cvt<T>::from_f(a[i]);
+            ob[i] = Cvt<T>::from_f(b[i]);
+        }
+        *reinterpret_cast<uint2*>(dst + li * 4) = *reinterpret_cast<uint2*>(oa);
+        *reinterpret_cast<uint2*>(dst + half + li * 4) = *reinterpret_cast<uint2*>(ob);
+    }
+}
+
 // Generic form (any even head_dim <= 512, partial rotary): grid (T, Hq + 2*Hkv), block D/2 threads,
 // thread i owns features i and i + D/2.
 template <typename T>
@@ -591,6 +686,14 @@ extern "C" int telb_rope_kv_write(const void* qkv, void* q_out, void* kv_layer, 
                                   int max_pages, float eps, int is_bf16, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (d % 2 || d > 512) return fail("telb_rope_kv_write: head_dim must be even and <= 512");
+    if (rot_dim == d && d == 128 && tokens >= 1024) {
+        const int blocks = (tokens + 3) / 4;             // 4 warps = 4 tokens per block
+        DISPATCH_T(is_bf16, {
+            TELB_LAUNCH("rope_kv_write_token_kernel", (rope_kv_write_token_kernel<T>), dim3(blocks), dim3(128), 0, stream, (const T*)qkv, (T*)q_out, (T*)kv_layer, cos_sin, positions, seq_ids, q_start, past_len, page_table, kv_offsets, (const T*)q_norm_w, (const T*)k_norm_w, tokens, hq, hkv, page_size, max_pages, eps);
+        })
+        TELB_CHECK_LAUNCH("rope_kv_write_token_kernel");
+        return 0;
+    }
     if (rot_dim == d && (d == 64 || d == 128 || d == 256)) {
         const long long warps = (long long)tokens * (hq + 2 * hkv);
         const int blocks = (int)((warps + 7) / 8);

@@ -4,6 +4,7 @@
 #pragma once
 
 #include "host_utils.h"
+#include "nvfp4_common.cuh"
 #include "tc5_common.cuh"
 
 namespace telb {
@@ -36,6 +37,13 @@ struct GemmParams {
     const int* ag_flags;
     const int* ag_epoch;
     int ag_world, ag_rows_per_rank;
+    // SwiGLU + NVFP4 output (large-M layout, 128-wide tiles over weights whose gate / up rows alternate in blocks of
+    // 64): the epilogue computes silu(gate) * up for the tile's 64 features and stores them quantised — packed codes
+    // into sw_xq [rows, sw_ld bytes] and block scales into the atom-layout buffer sw_sf — instead of 16-bit values.
+    uint8_t* sw_xq;
+    uint8_t* sw_sf;
+    const float* sw_gs;
+    int sw_ld, sw_k64_pad;
 };
 
 // Fusion request as the host passes it (same fields, plain C layout).
@@ -331,6 +339,54 @@ __device__ __forceinline__ void gemm_epilogue_role(const GemmParams& p, uint32_t
             // the peer stores of this tile are performed system-wide before the thread moves on, so the
             // "GEMM finished" flag that a later kernel publishes can never overtake them
             __threadfence_system();
+        } else if (BN == 128 && p.sw_xq != nullptr && p.splits == 1) {
+            if constexpr (BN == 128) {
+                // columns [0, 64) of the tile are gate features f0 .. f0+63, columns [64, 128) the matching up features
+                const float gs = *p.sw_gs;
+                const float inv_gs = 1.f / gs;
+                const int f0 = tc.b0 * 64;
+#pragma unroll 1
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t rg[32], ru[32];
+                    tmem_ld_x32(t_addr + c * 32, rg);
+                    tmem_ld_x32(t_addr + 64 + c * 32, ru);
+                    tmem_ld_wait();
+                    if (row_ok) {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            float y[16];
+                            float amax = 0.f;
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                const int j = h * 16 + i;
+                                float g = __uint_as_float(rg[j]), u = __uint_as_float(ru[j]);
+                                if (pt.alpha) {
+                                    g *= __ldg(&pt.alpha[b0 + c * 32 + j]);
+                                    u *= __ldg(&pt.alpha[b0 + 64 + c * 32 + j]);
+                                }
+                                // the same roundings as the unfused chain: 16-bit GEMM output, 16-bit activation, then quantise
+                                if (p.out_bf16) {
+                                    g = Cvt<__nv_bfloat16>::to_f(Cvt<__nv_bfloat16>::from_f(g));
+                                    u = Cvt<__nv_bfloat16>::to_f(Cvt<__nv_bfloat16>::from_f(u));
+                                    y[i] = Cvt<__nv_bfloat16>::to_f(Cvt<__nv_bfloat16>::from_f(g / (1.f + __expf(-g)) * u));
+                                } else {
+                                    g = Cvt<__half>::to_f(Cvt<__half>::from_f(g));
+                                    u = Cvt<__half>::to_f(Cvt<__half>::from_f(u));
+                                    y[i] = Cvt<__half>::to_f(Cvt<__half>::from_f(g / (1.f + __expf(-g)) * u));
+                                }
+                                amax = fmaxf(amax, fabsf(y[i]));
+                            }
+                            uint8_t s8;
+                            const uint2 packed = nvfp4_quantize_block16(y, amax, gs, inv_gs, s8);
+                            const int blk = (f0 + c * 32 + h * 16) >> 4;
+                            *reinterpret_cast<uint2*>(p.sw_xq + (size_t)row * p.sw_ld + blk * 8) = packed;
+                            p.sw_sf[sf_atom_offset((long long)row, blk, p.sw_k64_pad)] = s8;
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&tempty_bar[acc]);
         } else if (p.splits == 1) {
 #pragma unroll 1
             for (int c = 0; c < kChunks; ++c) {

@@ -304,11 +304,18 @@ extern "C" int telb_nvfp4_quantize(const void* x, void* xq, void* sf_atoms, cons
     return 0;
 }
 
+struct SwigluOut {
+    uint8_t* xq;
+    uint8_t* sf;
+    const float* gs;
+    int ld, k64_pad;
+};
+
 // out[M,N] = dequant(xq, x_sf)[M,K] · dequant(wq, w_sf)[N,K]^T * alpha[N] (+bias +residual); K % 32 == 0.
 static int gemm_nvfp4_impl(const void* xq, const void* x_sf, const void* wq, const void* w_sf, void* out, int M, int N,
                            int K, const float* alpha, const void* bias, const void* residual, int out_bf16, void* ws,
                            long long ws_bytes, int* counters, int n_counters, int* status, int mode, int force_splits,
-                           const TelbGemmFusion* fusion, cudaStream_t stream) {
+                           const TelbGemmFusion* fusion, cudaStream_t stream, const SwigluOut* sw = nullptr) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (K % 32) return fail("telb_gemm_nvfp4: K must be a multiple of 32");
     if (fusion) mode = 1;         // the fused collectives are written for the large-M layout
@@ -318,6 +325,13 @@ static int gemm_nvfp4_impl(const void* xq, const void* x_sf, const void* wq, con
     const bool swapped = mode == 2 || (mode == 0 && M <= 128);
     GemmParams p{};
     apply_fusion(p, fusion);
+    if (sw) {
+        p.sw_xq = sw->xq;
+        p.sw_sf = sw->sf;
+        p.sw_gs = sw->gs;
+        p.sw_ld = sw->ld;
+        p.sw_k64_pad = sw->k64_pad;
+    }
     p.k = K;
     p.kb_total = (K + kFp4BK - 1) / kFp4BK;
     p.c = out;
@@ -393,6 +407,23 @@ extern "C" int telb_gemm_nvfp4_fused(const void* xq, const void* x_sf, const voi
                                      const TelbGemmFusion* fusion, cudaStream_t stream) {
     return gemm_nvfp4_impl(xq, x_sf, wq, w_sf, out, M, N, K, alpha, bias, nullptr, out_bf16, nullptr, 0, nullptr, 0, status, 1, 1,
                            fusion, stream);
+}
+
+// Gate/up projection with the SwiGLU + NVFP4 quantisation done in the epilogue: wq holds 2 * inter rows in which blocks
+// of 64 gate rows alternate with the 64 matching up rows (alpha in the same order); the result is
+// quantised silu(gate) * up [M, inter] as packed codes out_xq [M, inter / 2] and atom-layout scales out_sf (pre-zeroed
+// by the caller when M % 128 or inter % 256 leave padding).  Large-M layout only (M > 128).
+extern "C" int telb_gemm_nvfp4_swiglu(const void* xq, const void* x_sf, const void* wq, const void* w_sf, const float* alpha,
+                                      void* out_xq, void* out_sf, const float* out_global_scale, int M, int N, int K, int out_bf16,
+                                      int* status, const TelbGemmFusion* fusion, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (N % 128 || K % 32) return fail("telb_gemm_nvfp4_swiglu: N must be a multiple of 128 and K of 32");
+    if (fusion && fusion->rs_world > 1) return fail("telb_gemm_nvfp4_swiglu: no reduce-scatter on a column-parallel projection");
+    if (M <= 128) return fail("telb_gemm_nvfp4_swiglu: the fused epilogue exists for the large-M layout (M > 128)");
+    SwigluOut sw{static_cast<uint8_t*>(out_xq), static_cast<uint8_t*>(out_sf), out_global_scale, N / 4 /* inter / 2 bytes per row */,
+                 telb_nvfp4_k64_pad(N / 2)};
+    return gemm_nvfp4_impl(xq, x_sf, wq, w_sf, nullptr, M, N, K, alpha, nullptr, nullptr, out_bf16, nullptr, 0, nullptr, 0, status, 1, 1,
+                           fusion, stream, &sw);
 }
 
 // Grouped NVFP4 GEMM for mixture-of-experts (see telb_gemm_f16_grouped): xq [rows_pad, K/2] with

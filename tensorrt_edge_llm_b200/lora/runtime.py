@@ -79,6 +79,11 @@ class LoraManager:
         base = getattr(parent, leaf)
         if not isinstance(base, LinearBase):
             raise TypeError(f"{module_name} is not a linear layer")
+        if getattr(base, "gate_up_interleaved", False):
+            raise RuntimeError(f"{module_name} already stores interleaved gate / up rows for the fused SwiGLU epilogue; attach adapters "
+                               "before the model's first GPU step or set TELB_DISABLE_SWIGLU_FUSION=1")
+        if hasattr(base, "want_interleave"):
+            base.want_interleave = False             # the low-rank update is added to plain [gate | up] columns
         w = LoraLinear(base)
         setattr(parent, leaf, w)
         self._wrapped[module_name] = w

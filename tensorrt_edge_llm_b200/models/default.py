@@ -13,6 +13,7 @@ all-reduce followed by the kernel (baseline) and the fused peer-memory kernel.
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional, Tuple
 
 import torch
@@ -22,7 +23,7 @@ from .. import ops
 from ..config import ModelConfig
 from ..ops.meta import StepMeta
 from ..parallel.comm import LocalComm
-from .linear import TPMode, make_linear
+from .linear import NVFP4Linear, TPMode, make_linear
 
 
 class RMSNorm(nn.Module):
@@ -84,9 +85,25 @@ class MLP(nn.Module):
             self.gate_up_proj = make_linear(cfg, f"{prefix}.up_proj", cfg.hidden_size, [inter], TPMode.COL,
                                             sources=["up_proj"])
         self.down_proj = make_linear(cfg, f"{prefix}.down_proj", inter, [cfg.hidden_size], TPMode.ROW)
+        # NVFP4 W4A4 on both projections: SwiGLU and the quantisation of the down projection's input move into the
+        # gate/up GEMM's epilogue at prefill sizes (TELB_DISABLE_SWIGLU_FUSION=1 keeps the separate kernel)
+        if (self.act in ("silu", "swiglu") and isinstance(self.gate_up_proj, NVFP4Linear) and isinstance(self.down_proj, NVFP4Linear)
+                and self.gate_up_proj.quantize_activations and self.down_proj.quantize_activations
+                and os.environ.get("TELB_DISABLE_SWIGLU_FUSION", "0") != "1"):
+            self.gate_up_proj.want_interleave = True
 
     def forward(self, x):
-        gu = self.gate_up_proj(x)
+        gp = self.gate_up_proj
+        if getattr(gp, "want_interleave", False) and getattr(x, "is_cuda", False):
+            if gp._gpu_weight_sf is None:
+                gp.finalize()
+            if gp.gate_up_interleaved:
+                scale = self.down_proj.fused_input_scale()
+                rows = x.shape[0]
+                if rows > 128 and not isinstance(x, torch.Tensor):
+                    return self.down_proj(gp.forward_swiglu(x, scale))
+                return self.down_proj(ops.swiglu(gp(x), scale, interleaved=True))
+        gu = gp(x)
         a = ops.swiglu(gu, self.down_proj.fused_input_scale()) if self.act in ("silu", "swiglu") else ops.relu2(gu)
         return self.down_proj(a)
 

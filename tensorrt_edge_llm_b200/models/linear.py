@@ -147,8 +147,19 @@ class NVFP4Linear(LinearBase):
         self.register_buffer("alpha", torch.ones(self.out_features, dtype=torch.float32))
         self.bias = nn.Parameter(torch.zeros(self.out_features, dtype=dtype), requires_grad=False) if bias else None
         self._gpu_weight_sf = None      # scale factors repacked for the tensor-core kernel
+        # gate/up projections feeding an NVFP4 down projection: on the GPU the rows are stored as blocks of 64 gate rows
+        # alternating with their 64 up rows, so one 128-wide GEMM tile holds both halves of 64 SwiGLU outputs and the
+        # epilogue can apply the activation and quantise (``forward_swiglu``).  Requested by the MLP, done in finalize.
+        self.want_interleave = False
+        self.gate_up_interleaved = False
+
+    def _interleave_perm(self) -> torch.Tensor:
+        inter = self.out_sizes[0]
+        blk = torch.arange(inter, device=self.weight.device).view(inter // 64, 64)
+        return torch.stack([blk, blk + inter], dim=1).reshape(-1)          # [g0..63, u0..63, g64..127, u64..127, ...]
 
     def load_from(self, tensors):
+        self.gate_up_interleaved, self._gpu_weight_sf = False, None
         w = torch.cat([self.shard_out_in(t["weight"], i) for i, t in enumerate(tensors)], dim=0)
         sf = torch.cat([self.shard_out_in(t["weight_scale"].view(torch.uint8), i) for i, t in enumerate(tensors)], dim=0)
         self.weight.copy_(w.view(torch.uint8))
@@ -169,6 +180,7 @@ class NVFP4Linear(LinearBase):
     @torch.no_grad()
     def quantize_from(self, weights: List[torch.Tensor], input_scale: float = 1.0 / 448.0) -> None:
         """Quantise 16-bit weights (one tensor per fused source) into this layer."""
+        self.gate_up_interleaved, self._gpu_weight_sf = False, None
         packs, sfs, gss = [], [], []
         for wt in weights:
             p, sf, gs = ref.nvfp4_quantize(wt.float())
@@ -181,11 +193,27 @@ class NVFP4Linear(LinearBase):
 
     def dequantized_weight(self) -> torch.Tensor:
         per_row = torch.cat([self.weight_scale_2[i].expand(n) for i, n in enumerate(self.out_sizes)])
-        return ref.nvfp4_dequantize(self.weight, self.weight_scale, torch.ones((), device=self.weight.device)) * per_row[:, None]
+        w, sf = self.weight, self.weight_scale
+        if self.gate_up_interleaved:             # back to [gate | up] row order
+            inv = torch.argsort(self._interleave_perm())
+            w, sf = w[inv], sf.view(torch.uint8)[inv].view(torch.float8_e4m3fn)
+        return ref.nvfp4_dequantize(w, sf, torch.ones((), device=self.weight.device)) * per_row[:, None]
 
+    @torch.no_grad()
     def finalize(self):
         if self.weight.is_cuda:
+            if (self.want_interleave and not self.gate_up_interleaved and self.bias is None and len(self.out_sizes) == 2
+                    and self.out_sizes[0] == self.out_sizes[1] and self.out_sizes[0] % 64 == 0):
+                perm = self._interleave_perm()
+                self.weight.copy_(self.weight[perm])
+                self.weight_scale.copy_(self.weight_scale.view(torch.uint8)[perm].view(torch.float8_e4m3fn))
+                self.alpha.copy_(self.alpha[perm])
+                self.gate_up_interleaved = True
             self._gpu_weight_sf = ops.cuda_ops().nvfp4_swizzle_scales(self.weight_scale)
+
+    def forward_swiglu(self, x, out_scale: torch.Tensor):
+        """``quantise(silu(gate) * up)`` of this (interleaved) gate/up projection for NVFP4 input rows ``x`` (more than 128)."""
+        return ops.cuda_ops().gemm_nvfp4_swiglu(x, self.weight, self._gpu_weight_sf, self.alpha, out_scale, getattr(x, "ag_wait", None))
 
     def fused_input_scale(self):
         return self.input_scale if (self.quantize_activations and self.weight.is_cuda) else None

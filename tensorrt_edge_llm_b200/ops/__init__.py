@@ -59,11 +59,15 @@ def gated_group_rmsnorm(x, z, weight, n_groups, eps):
     return ref.gated_group_rmsnorm(x, z, weight, n_groups, eps)
 
 
-def swiglu(gate_up, quant_scale=None):
+def swiglu(gate_up, quant_scale=None, interleaved=False):
+    """``interleaved``: the columns hold blocks of 64 gate features followed by their 64 up features (the layout the fused
+    gate/up GEMM epilogue uses) instead of ``[gate | up]``; only the quantising CUDA form takes it."""
     if gate_up.is_cuda:
         if quant_scale is not None:
-            return cuda_ops().swiglu_quant(gate_up, quant_scale)
+            return cuda_ops().swiglu_quant(gate_up, quant_scale, interleaved)
+        assert not interleaved
         return cuda_ops().swiglu(gate_up)
+    assert not interleaved
     return ref.swiglu(gate_up)
 
 

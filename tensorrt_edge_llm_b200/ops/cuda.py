@@ -344,7 +344,24 @@ def rmsnorm_quant(x: torch.Tensor, residual: Optional[torch.Tensor], weight: tor
     return QuantActs(xq, sf, (m, k), x.dtype), (res_out if residual is not None else x)
 
 
-def swiglu_quant(gate_up: torch.Tensor, global_scale: torch.Tensor) -> QuantActs:
+def gemm_nvfp4_swiglu(x: "QuantActs", weight: torch.Tensor, w_sf: torch.Tensor, alpha: torch.Tensor, out_scale: torch.Tensor,
+                      fusion=None) -> "QuantActs":
+    """Gate/up projection whose epilogue applies SwiGLU and quantises to NVFP4: ``weight [2·I, K/2]`` holds blocks of 64
+    gate rows alternating with their up rows; returns the quantised ``[M, I]`` activations (M > 128)."""
+    m, n, k = x.xq.shape[0], weight.shape[0], x.xq.shape[1] * 2
+    inter = n // 2
+    L = lib()
+    L.telb_nvfp4_sf_bytes.restype = c_ll
+    xq = torch.empty(m, inter // 2, dtype=torch.uint8, device=weight.device)
+    sf = _sf_buffer(L.telb_nvfp4_sf_bytes(c_ll(m), c_int(inter)), inter, weight.device)
+    ws = Workspace.get(weight.device)
+    _check(L.telb_gemm_nvfp4_swiglu(_p(x.xq), _p(x.sf), _p(weight), _p(w_sf), _p(alpha), _p(xq), _p(sf), _p(out_scale), c_int(m), c_int(n),
+                                    c_int(k), c_int(1 if x.dtype == torch.bfloat16 else 0), _p(ws.status),
+                                    ctypes.byref(fusion) if fusion is not None else c_vp(0), _stream()), "gemm_nvfp4_swiglu")
+    return QuantActs(xq, sf, (m, inter), x.dtype)
+
+
+def swiglu_quant(gate_up: torch.Tensor, global_scale: torch.Tensor, interleaved: bool = False) -> QuantActs:
     gate_up = gate_up.contiguous()
     m = gate_up.shape[0]
     inter = gate_up.shape[1] // 2
@@ -353,8 +370,8 @@ def swiglu_quant(gate_up: torch.Tensor, global_scale: torch.Tensor) -> QuantActs
     nbytes = L.telb_nvfp4_sf_bytes(c_ll(m), c_int(inter))
     xq = torch.empty(m, inter // 2, dtype=torch.uint8, device=gate_up.device)
     sf = _sf_buffer(nbytes, inter, gate_up.device)
-    _check(L.telb_swiglu_quant(_p(gate_up), _p(xq), _p(sf), _p(global_scale), c_ll(m), c_int(inter),
-                               c_int(_is_bf16(gate_up)), _stream()), "swiglu_quant")
+    _check(L.telb_swiglu_quant_il(_p(gate_up), _p(xq), _p(sf), _p(global_scale), c_ll(m), c_int(inter),
+                                  c_int(_is_bf16(gate_up)), c_int(1 if interleaved else 0), _stream()), "swiglu_quant")
     return QuantActs(xq, sf, (m, inter), gate_up.dtype)
 
 

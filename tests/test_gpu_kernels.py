@@ -220,6 +220,33 @@ def test_rope_kv_write(cu, qk_norm):
     _sync_check(cu)
 
 
+@pytest.mark.parametrize("qk_norm,hq,hkv", [(True, 8, 2), (False, 4, 1), (True, 5, 1)])
+def test_rope_kv_write_prefill_form(cu, qk_norm, hq, hkv):
+    """Enough tokens for the one-warp-per-token kernel (two heads per warp pass; an odd head count leaves half a warp idle)."""
+    d, page = 128, 64
+    q_lens, past = [700, 400], [64, 0]
+    g = torch.Generator(device="cuda").manual_seed(7)
+    t, n = sum(q_lens), 2
+    table = torch.arange(n * 12, dtype=torch.int32).view(n, 12)
+    table[1, 5] = -1                                                    # an unreserved page is skipped, not written
+    meta = build_step_meta(q_lens, past, table, page, device="cuda")
+    qkv = torch.randn(t, (hq + 2 * hkv) * d, device="cuda", generator=g).half()
+    cs = ref.rope_cos_sin(1024, d, 1e4, device="cuda")
+    qw = (1 + 0.1 * torch.randn(d, device="cuda", generator=g)).half() if qk_norm else None
+    kw = (1 + 0.1 * torch.randn(d, device="cuda", generator=g)).half() if qk_norm else None
+    kv1 = torch.zeros(n * 12, 2, hkv, page, d, device="cuda", dtype=torch.float16)
+    kv2 = kv1.clone()
+    q1 = cu.rope_kv_write(qkv, kv1, meta, cs, hq, hkv, d, qw, kw, 1e-6)
+    table2 = table.clone()
+    table2[1, 5] = 23                                                   # the reference writes there; compare everything else
+    meta2 = build_step_meta(q_lens, past, table2, page, device="cuda")
+    q2 = ref.rope_kv_write(qkv, kv2, meta2, cs, hq, hkv, d, qw, kw, 1e-6)
+    assert _rel_err(q1, q2) < 3e-3
+    keep = [i for i in range(n * 12) if i != 23]
+    assert _rel_err(kv1[keep], kv2[keep]) < 3e-3 and torch.equal(kv1[keep] == 0, kv2[keep] == 0)
+    _sync_check(cu)
+
+
 NVFP4_SHAPES = [(256, 512, 512), (1024, 6144, 4096), (300, 1000, 768), (1, 4096, 4096), (8, 6144, 4096),
                 (64, 4096, 12288), (33, 1024, 512), (128, 2048, 2048), (4096, 4096, 4096)]
 
@@ -340,3 +367,65 @@ def test_fused_norm_and_swiglu_quant(cu):
     y2 = cu.gemm_nvfp4(xq2, sf2, wq, cu.nvfp4_swizzle_scales(wsf), alpha, torch.float16)
     assert _rel_err(y1, y2) < 5e-3
     _sync_check(cu)
+
+
+def test_gemm_nvfp4_swiglu_epilogue_matches_unfused_chain():
+    """Gate/up GEMM with SwiGLU + NVFP4 quantisation in the epilogue == GEMM → swiglu_quant, bit for bit."""
+    from tensorrt_edge_llm_b200.ops import cuda as cu
+    torch.manual_seed(0)
+    m, k, inter = 300, 512, 384
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn(m, k, device="cuda", generator=g).half()
+    wq = torch.randint(0, 256, (2 * inter, k // 2), device="cuda", generator=g, dtype=torch.uint8)
+    wsf = torch.randint(48, 58, (2 * inter, k // 16), device="cuda", generator=g, dtype=torch.uint8)
+    alpha = (torch.rand(2 * inter, device="cuda", generator=g) * 0.02 + 0.01)
+    gs_in = torch.full((1,), 1.0 / 448, device="cuda")
+    gs_out = torch.full((1,), 0.004, device="cuda")
+    xq, xsf = cu.nvfp4_quantize(x, gs_in)
+    acts = cu.QuantActs(xq, xsf, (m, k), torch.float16)
+    # unfused: plain [gate | up] weights
+    gu = cu.gemm_nvfp4(xq, xsf, wq, cu.nvfp4_swizzle_scales(wsf), alpha, torch.float16, mode=1)
+    want = cu.swiglu_quant(gu, gs_out)
+    # fused: rows interleaved in blocks of 64
+    blk = torch.arange(inter, device="cuda").view(inter // 64, 64)
+    perm = torch.stack([blk, blk + inter], 1).reshape(-1)
+    w_il, sf_il, a_il = wq[perm].contiguous(), wsf[perm].contiguous(), alpha[perm].contiguous()
+    got = cu.gemm_nvfp4_swiglu(acts, w_il, cu.nvfp4_swizzle_scales(sf_il), a_il, gs_out)
+    torch.cuda.synchronize()
+    assert torch.equal(got.xq, want.xq)
+    assert torch.equal(got.sf[: want.sf.numel()].view(torch.uint8), want.sf.view(torch.uint8)[: got.sf.numel()])
+    # the decode-size path reads the interleaved GEMM output
+    gu_il = cu.gemm_nvfp4(xq, xsf, w_il, cu.nvfp4_swizzle_scales(sf_il), a_il, torch.float16, mode=1)
+    small = cu.swiglu_quant(gu_il, gs_out, interleaved=True)
+    assert torch.equal(small.xq, want.xq)
+    cu.Workspace.get(torch.device("cuda", 0)).check_status()
+
+
+def test_mlp_with_fused_swiglu_matches_unfused(monkeypatch):
+    """A whole NVFP4 MLP: prefill rows through the fused epilogue, decode rows through the interleaved kernel, both equal
+    to the layer built with the fusion switched off."""
+    from tensorrt_edge_llm_b200.config import QUANT_NVFP4, QuantConfig, tiny_llama_config
+    from tensorrt_edge_llm_b200.models.default import MLP
+    from tensorrt_edge_llm_b200 import ops
+    cfg = tiny_llama_config(hidden_size=512, intermediate_size=768, dtype="float16")
+    cfg.quant = QuantConfig(quant_type=QUANT_NVFP4, group_size=16)
+
+    def build():
+        torch.manual_seed(3)
+        mlp = MLP(cfg, "model.layers.0.mlp")
+        gen = torch.Generator().manual_seed(5)
+        mlp.gate_up_proj.quantize_from([torch.randn(768, 512, generator=gen) * 0.05, torch.randn(768, 512, generator=gen) * 0.05])
+        mlp.down_proj.quantize_from([torch.randn(512, 768, generator=gen) * 0.05])
+        return mlp.cuda()
+    fused = build()
+    monkeypatch.setenv("TELB_DISABLE_SWIGLU_FUSION", "1")
+    plain = build()
+    assert fused.gate_up_proj.want_interleave and not plain.gate_up_proj.want_interleave
+    w = torch.ones(512, device="cuda", dtype=torch.float16)
+    for rows in (400, 16):
+        x = torch.randn(rows, 512, device="cuda", generator=torch.Generator(device="cuda").manual_seed(rows)).half()
+        qa = ops.rmsnorm_maybe_quant(x, w, 1e-6, fused.gate_up_proj.fused_input_scale())
+        qb = ops.rmsnorm_maybe_quant(x, w, 1e-6, plain.gate_up_proj.fused_input_scale())
+        assert torch.equal(fused(qa), plain(qb))
+    assert fused.gate_up_proj.gate_up_interleaved and not plain.gate_up_proj.gate_up_interleaved
+    assert torch.equal(fused.gate_up_proj.dequantized_weight(), plain.gate_up_proj.dequantized_weight())
