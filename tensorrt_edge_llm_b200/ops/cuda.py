@@ -23,6 +23,10 @@ c_int, c_ll, c_float, c_vp = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ct
 def lib() -> ctypes.CDLL:
     global _lib
     if _lib is None:
+        # fault-injection hook for tests of the failure path (the reference's TRT_EDGELLM_TEST_FAIL_CUTEDSL_MODULE,
+        # cpp/kernels/cuteDslModuleLoader.cpp:178): the named library "fails to load" deterministically
+        if os.environ.get("TELB_TEST_FAIL_KERNEL_LIBRARY", "") in ("1", os.path.basename(_LIB_PATH)):
+            raise RuntimeError(f"native kernel library {_LIB_PATH} failed to load (TELB_TEST_FAIL_KERNEL_LIBRARY is set)")
         if not os.path.exists(_LIB_PATH):
             raise RuntimeError(f"native kernel library not built: {_LIB_PATH} (run `python -m tensorrt_edge_llm_b200.build`)")
         _lib = ctypes.CDLL(_LIB_PATH)

@@ -359,3 +359,14 @@ def test_chat_template_families(hf_tok):
     assert l3.apply([rt.ChatMessage("user", "hi")]).startswith("<|begin_of_text|><|start_header_id|>user<|end_header_id|>\n\nhi<|eot_id|>")
     l2 = rt.ChatTemplate.from_template_text("[INST] {{ x }} [/INST]", "<s>")
     assert l2.apply(msgs) == "<s>[INST] <<SYS>>\nbe brief\n<</SYS>>\n\nhi [/INST]"
+
+
+def test_kernel_library_load_failure_is_loud(monkeypatch):
+    """The fault-injection switch makes the kernel library fail to load; nothing falls back silently."""
+    from tensorrt_edge_llm_b200.ops import cuda as cu
+    monkeypatch.setattr(cu, "_lib", None)
+    monkeypatch.setenv("TELB_TEST_FAIL_KERNEL_LIBRARY", "1")
+    with pytest.raises(RuntimeError, match="failed to load"):
+        cu.lib()
+    monkeypatch.delenv("TELB_TEST_FAIL_KERNEL_LIBRARY")
+    assert cu.lib() is not None
