@@ -34,7 +34,9 @@ def _guided(spec):
         return GuidedDecodingParams("regex", pattern=str(spec[m]))
     if m == "choice":
         return GuidedDecodingParams("choice", choices=list(spec[m]))
-    raise RequestFileError(f"guided decoding mode {m!r} is not supported (json_object, json_schema, regex and choice are)")
+    if m == "ebnf":
+        return GuidedDecodingParams("ebnf", grammar=str(spec[m]))
+    return GuidedDecodingParams("structural_tag", structural_tag=spec[m] if isinstance(spec[m], dict) else json.loads(spec[m]))
 
 
 def parse_request_file(body: Dict[str, Any]) -> List[Dict[str, Any]]:

@@ -8,7 +8,8 @@ once the text is a complete match.  The bitmask feeds ``ops.apply_token_bitmask`
 
 Parity: ``cpp/runtime/decoding/guidedDecoder.cpp`` (XGrammar matcher → token bitmask, ``GuidedDecodingParams`` types of
 ``cpp/runtime/llmRuntimeUtils.h``).  The matcher here is this package's own: partial regular-expression matching
-(the ``regex`` module) and an incremental JSON recogniser; grammars (EBNF, structural tags) are not built."""
+(the ``regex`` module), an incremental JSON recogniser, and for ``ebnf`` / ``structural_tag`` the Earley recogniser and tag
+scanner of ``runtime/grammar.py``."""
 from __future__ import annotations
 
 import json
@@ -20,15 +21,21 @@ import torch
 
 @dataclass
 class GuidedDecodingParams:
-    type: str                                  # "choice" | "regex" | "json_object" | "json_schema"
+    type: str                                  # "choice" | "regex" | "json_object" | "json_schema" | "ebnf" | "structural_tag"
     choices: Sequence[str] = ()
     pattern: str = ""
     json_schema: Optional[dict] = None
     max_depth: int = 8
+    grammar: str = ""                          # EBNF text ("ebnf")
+    structural_tag: Optional[dict] = None      # {"structures": [...], "triggers": [...]} ("structural_tag")
 
     def __post_init__(self):
-        if self.type not in ("choice", "regex", "json_object", "json_schema"):
+        if self.type not in ("choice", "regex", "json_object", "json_schema", "ebnf", "structural_tag"):
             raise ValueError(f"unsupported guided decoding type {self.type!r}")
+        if self.type == "ebnf" and not self.grammar:
+            raise ValueError("ebnf needs a grammar")
+        if self.type == "structural_tag" and not isinstance(self.structural_tag, dict):
+            raise ValueError("structural_tag needs a specification object")
         if self.type == "choice" and not self.choices:
             raise ValueError("choice needs a non-empty list")
         if self.type == "regex" and not self.pattern:
@@ -208,6 +215,12 @@ def make_matcher(params: GuidedDecodingParams):
         return _RegexMatcher(params.pattern)
     if params.type == "json_schema":
         return _RegexMatcher(schema_to_regex(params.json_schema))
+    if params.type == "ebnf":
+        from .grammar import EbnfMatcher
+        return EbnfMatcher(params.grammar)
+    if params.type == "structural_tag":
+        from .grammar import StructuralTagMatcher
+        return StructuralTagMatcher(params.structural_tag)
     return _JsonObjectMatcher(params.max_depth)
 
 
@@ -267,6 +280,8 @@ class GuidedDecoder:
                 return
             raise ValueError(f"token {token} violates the constraint after {self.text!r}")
         self.text += piece
+        if hasattr(self.matcher, "commit"):            # grammar matchers keep the chart of the accepted text
+            self.matcher.commit(self.text)
 
 
 @torch.no_grad()

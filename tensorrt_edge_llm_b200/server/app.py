@@ -62,9 +62,16 @@ def _guided(body: Dict[str, Any]):
         return GuidedDecodingParams("regex", pattern=str(body["guided_regex"]))
     if body.get("guided_json"):
         return GuidedDecodingParams("json_schema", json_schema=body["guided_json"])
+    if body.get("guided_grammar"):
+        return GuidedDecodingParams("ebnf", grammar=str(body["guided_grammar"]))
+    if body.get("structural_tag"):
+        st = body["structural_tag"]
+        return GuidedDecodingParams("structural_tag", structural_tag=json.loads(st) if isinstance(st, str) else st)
     rf = body.get("response_format") or {}
     if rf.get("type") == "json_object":
         return GuidedDecodingParams("json_object")
+    if rf.get("type") == "structural_tag":
+        return GuidedDecodingParams("structural_tag", structural_tag={k: rf[k] for k in ("structures", "triggers") if k in rf})
     if rf.get("type") == "json_schema":
         schema = (rf.get("json_schema") or {}).get("schema")
         return GuidedDecodingParams("json_schema", json_schema=schema)

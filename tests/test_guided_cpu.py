@@ -97,3 +97,72 @@ def test_server_response_format_and_guided_choice(llm):
                                                   "response_format": {"type": "json_schema", "json_schema": {"schema": schema}}}).json()
     assert isinstance(json.loads(r["choices"][0]["message"]["content"])["go"], bool)
     assert client.post("/v1/chat/completions", json={"messages": msgs, "response_format": {"type": "json_schema"}}).status_code == 400
+
+
+JSONISH = r"""
+root   ::= "{" ws pair ("," ws pair)* "}"
+pair   ::= string ":" ws value
+string ::= "\"" [a-z]+ "\""
+value  ::= [0-9]{1,3} | string | "true" | "false" | list
+list   ::= "[" (value ("," value)*)? "]"
+ws     ::= " "?
+"""
+
+
+def test_ebnf_matcher():
+    from tensorrt_edge_llm_b200.runtime.grammar import EbnfMatcher, GrammarError
+    m = EbnfMatcher(JSONISH)
+    for good in ('{"a":1}', '{ "ab": "cd", "e":[1,22,"x",[true]]}', '{"k":[]}'):
+        assert m.complete(good), good
+        assert all(m.viable(good[:i]) for i in range(len(good) + 1))
+    for bad in ('{"a":1', '{"A":1}', '{"a":1234}', '{"a":1}}', '["a"]'):
+        assert not m.complete(bad), bad
+    assert m.viable('{"a":12') and not m.viable('{"a":1234') and not m.viable("x") and not m.viable('{"a":1}x')
+    # forced continuation (jump-forward): after an opening quote of a key nothing is forced, after `"a"` the colon is
+    assert m.forced_continuation('{"a"') == ":"
+    assert EbnfMatcher('root ::= "hello " name "!"\nname ::= [A-Z] [a-z]*').forced_continuation("") == "hello "
+    # left recursion and nullable rules
+    lr = EbnfMatcher('root ::= expr\nexpr ::= expr "+" term | term\nterm ::= [0-9]+ | "(" expr ")"\n')
+    assert lr.complete("1+(2+33)+4") and lr.viable("1+(2+") and not lr.viable("1++") and not lr.complete("1+(2")
+    assert EbnfMatcher('root ::= "a"* "b"?').complete("") and EbnfMatcher('root ::= ("ab" | "c"){2,}').complete("abcab")
+    assert not EbnfMatcher('root ::= ("ab" | "c"){2,}').complete("c")
+    for broken in ('start ::= "a"', 'root ::= missing', 'root ::= "abc', 'root ::= ("a"'):
+        with pytest.raises(GrammarError):
+            EbnfMatcher(broken)
+    # the chart cache follows committed text and survives a probe that is not an extension
+    m.commit('{"a":')
+    assert m.viable('{"a": 7') and m.viable('{"b"') and m.complete('{"a":7}')
+
+
+def test_structural_tag_matcher():
+    from tensorrt_edge_llm_b200.runtime.grammar import GrammarError, StructuralTagMatcher
+    spec = {"structures": [{"begin": "<function=get_weather>", "schema": {"type": "object", "properties": {"city": {"type": "string"}},
+                                                                          "required": ["city"]}, "end": "</function>"},
+                           {"begin": "<function=now>", "end": "</function>"}],
+            "triggers": ["<function="]}
+    m = StructuralTagMatcher(spec)
+    ok = 'Sure. <function=get_weather>{"city": "Paris"}</function> and <function=now></function> done'
+    assert m.complete(ok) and all(m.viable(ok[:i]) for i in range(len(ok) + 1))
+    assert m.complete("no calls at all") and m.viable("text <fun")
+    assert not m.viable("<function=unknown>") and not m.viable('<function=get_weather>{"town"')
+    assert m.viable('<function=get_weather>{"city": "Pa') and not m.complete('<function=get_weather>{"city": "Pa')
+    with pytest.raises(GrammarError):
+        StructuralTagMatcher({"structures": [{"begin": "<x>", "end": "</x>"}], "triggers": ["<function="]})
+
+
+def test_generate_under_a_grammar():
+    """End to end on a random model: the output is a sentence of the grammar whatever the logits say."""
+    from tensorrt_edge_llm_b200.config import tiny_llama_config
+    from tensorrt_edge_llm_b200.runtime.grammar import EbnfMatcher
+    from tensorrt_edge_llm_b200.runtime.llm import LLM, SamplingParams
+    g = 'root ::= "id-" [0-9]{3} ("-" [a-c]{2})?'
+    cfg = tiny_llama_config(num_hidden_layers=1, vocab_size=300)
+    cfg.eos_token_id = 2
+    llm = LLM(cfg, device="cpu", max_batch_size=2, max_input_len=32, max_kv_cache_capacity=64, page_size=16, tokenizer=ByteTokenizer(),
+              enable_in_flight_batching=True)
+    outs = llm.generate([[5, 6, 7], [9, 9]], SamplingParams(max_tokens=20, temperature=0.9, top_k=40, seed=3,
+                                                            guided=GuidedDecodingParams("ebnf", grammar=g)))
+    m = EbnfMatcher(g)
+    for o in outs:
+        assert m.complete(o.text), o.text
+    llm.close()
