@@ -360,16 +360,29 @@ static int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const Ski
     return 0;
 }
 
-// Cluster size (K ranks).  Two CTAs fit on an SM; when the projection has fewer 128-row tiles than
-// that many slots, K is split so that about every slot streams a slice of the weights.
+// Cluster size (K ranks).  A cluster lives inside one GPC, so what counts is how many clusters of a given size are
+// resident at once: with two CTAs per SM and at least 16 usable SMs in each of the 8 GPCs that is 8 * (32 / r)
+// (48 clusters of 6 or 8 do not fit and run as two waves, 48 clusters of 4 do).  Among the sizes that divide the
+// work the estimate below — waves x (K steps per rank + fixed launch-to-first-byte cost) + reduction cost per rank —
+// picks the cheapest; its constants come from timing the Qwen3-8B decode projections with HBM-resident weights.
 static int choose_ranks(int tiles, int kb_total, int force) {
-    int s = 1;
-    if (force > 0) s = force;
-    else if (tiles < sm_count()) s = (2 * sm_count()) / tiles;
-    if (s > 8) s = 8;
-    if (s > kb_total) s = kb_total;
-    if (s < 1) s = 1;
-    return s;
+    if (force > 0) return force > 8 ? 8 : (force > kb_total ? kb_total : force);
+    static const int cand[6] = {1, 2, 3, 4, 6, 8};
+    int best_r = 1;
+    float best = 1e30f;
+    for (int i = 0; i < 6; ++i) {
+        const int r = cand[i];
+        if (r > kb_total) break;
+        const int capacity = 8 * (32 / r);
+        const int waves = (tiles + capacity - 1) / capacity;
+        const int steps = (kb_total + r - 1) / r;
+        const float est = waves * (steps * 0.35f + 4.0f) + r * 0.15f;
+        if (est < best - 1e-3f) {
+            best = est;
+            best_r = r;
+        }
+    }
+    return best_r;
 }
 
 template <int KIND>
