@@ -220,7 +220,47 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     T* outp = reinterpret_cast<T*>(p.out);
     const T* resp = reinterpret_cast<const T*>(p.residual);
 
-    if (p.ranks == 1) {
+    if (p.ranks == 1 && p.m_tok > 8 && (p.n_out & 3) == 0) {
+        // Many token columns: a lane owns one feature, so direct stores would be 2-byte pieces 2 * n_out apart.  The
+        // tile is transposed through shared memory instead (the stage ring is free once the MMAs have completed) and
+        // leaves as 8-byte stores, 256 contiguous bytes per token and warp.
+        __syncthreads();
+        if (is_epi) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (c0 >= p.m_tok) break;
+                uint32_t r[16];
+                if (have_acc) {
+                    tmem_ld_x16(t_addr + c0, r);
+                    tmem_ld_wait();
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) red[(c0 + j) * kBM + lrow] = have_acc ? __uint_as_float(r[j]) : 0.f;
+            }
+            named_barrier_sync(1, 128);
+            pdl_wait();
+            const int etid = (warp - 2) * 32 + lane;
+            const int items = min(BN, p.m_tok) * 32;
+            for (int it = etid; it < items; it += 128) {
+                const int c = it >> 5;
+                const int fg = (it & 31) * 4;
+                const int f0 = a0 + fg;
+                if (f0 + 3 >= p.n_out) continue;
+                const float4 acc4 = *reinterpret_cast<const float4*>(&red[c * kBM + fg]);
+                float v[4] = {acc4.x, acc4.y, acc4.z, acc4.w};
+                const size_t o = (size_t)c * p.n_out + f0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    v[i] = v[i] * s_alpha[fg + i] + s_bias[fg + i];
+                    if (resp) v[i] += Cvt<T>::to_f(resp[o + i]);
+                }
+                uint2 u;
+                u.x = Cvt<T>::pack2(v[0], v[1]);
+                u.y = Cvt<T>::pack2(v[2], v[3]);
+                *reinterpret_cast<uint2*>(outp + o) = u;
+            }
+        }
+    } else if (p.ranks == 1) {
         if (is_epi) {
             pdl_wait();
 #pragma unroll 1

@@ -281,7 +281,7 @@ def test_gemm_nvfp4(cu, m, n, k):
 
 @pytest.mark.parametrize("m,n,k,ranks", [(1, 4096, 4096, 0), (1, 512, 1024, 1), (8, 6144, 4096, 3), (16, 4096, 12288, 8),
                                          (33, 1000, 512, 2), (64, 24576, 4096, 0), (100, 4096, 4096, 5), (128, 2048, 2048, 4),
-                                         (7, 151936, 4096, 0), (64, 4096, 4096, 8)])
+                                         (7, 151936, 4096, 0), (64, 4096, 4096, 8), (100, 1004, 512, 1), (9, 1002, 512, 1)])
 def test_gemm_skinny_bf16(cu, m, n, k, ranks):
     g = torch.Generator(device="cuda").manual_seed(m + n)
     x = (torch.randn(m, k, device="cuda", generator=g) * 0.5).bfloat16()
