@@ -109,7 +109,8 @@ __global__ void rmsnorm_quant_kernel(const T* __restrict__ x, const T* __restric
 // in [rows, 2*inter] (gate | up) → quantised silu(gate)*up [rows, inter]; one thread per 16 outputs.
 template <typename T>
 __global__ void swiglu_quant_kernel(const T* __restrict__ in, uint8_t* __restrict__ xq, uint8_t* __restrict__ sf,
-                                    const float* __restrict__ global_scale, long long rows, int inter, int k64_pad, int interleaved) {
+                                    const float* __restrict__ global_scale, long long rows, int inter, int k64_pad, int interleaved,
+                                    const int* __restrict__ tile_rows) {
     pdl_prologue();
     const int units = inter / 16;
     const long long total = rows * units;
@@ -119,6 +120,7 @@ __global__ void swiglu_quant_kernel(const T* __restrict__ in, uint8_t* __restric
          idx += (long long)gridDim.x * blockDim.x) {
         const long long r = idx / units;
         const int u = (int)(idx - r * units);
+        if (tile_rows && (int)(r & 127) >= tile_rows[r >> 7]) continue;       // padding row of a grouped (MoE) buffer
         // plain layout: [gate(inter) | up(inter)]; interleaved: blocks of 64 gate features followed by their 64 up features
         const T* gp = interleaved ? in + r * 2 * inter + (u >> 2) * 128 + (u & 3) * 16 : in + r * 2 * inter + u * 16;
         const T* up = interleaved ? gp + 64 : gp + inter;
@@ -178,6 +180,8 @@ extern "C" int telb_rmsnorm_quant(const void* x, const void* residual, const voi
 
 extern "C" int telb_swiglu_quant_il(const void* in, void* xq, void* sf, const float* global_scale, long long rows, int inter,
                                     int is_bf16, int interleaved, cudaStream_t stream);
+extern "C" int telb_swiglu_quant_rows(const void* in, void* xq, void* sf, const float* global_scale, long long rows, int inter,
+                                      int is_bf16, int interleaved, const int* tile_rows, cudaStream_t stream);
 
 extern "C" int telb_swiglu_quant(const void* in, void* xq, void* sf, const float* global_scale, long long rows, int inter,
                                  int is_bf16, cudaStream_t stream) {
@@ -186,6 +190,12 @@ extern "C" int telb_swiglu_quant(const void* in, void* xq, void* sf, const float
 
 extern "C" int telb_swiglu_quant_il(const void* in, void* xq, void* sf, const float* global_scale, long long rows, int inter,
                                     int is_bf16, int interleaved, cudaStream_t stream) {
+    return telb_swiglu_quant_rows(in, xq, sf, global_scale, rows, inter, is_bf16, interleaved, nullptr, stream);
+}
+
+// `tile_rows` (optional): rows in use per 128-row tile of a grouped buffer; the other rows are skipped.
+extern "C" int telb_swiglu_quant_rows(const void* in, void* xq, void* sf, const float* global_scale, long long rows, int inter,
+                                      int is_bf16, int interleaved, const int* tile_rows, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (inter % 16) return fail("telb_swiglu_quant: intermediate size must be a multiple of 16");
     if (interleaved && inter % 64) return fail("telb_swiglu_quant: the interleaved layout needs an intermediate size that is a multiple of 64");
@@ -194,9 +204,9 @@ extern "C" int telb_swiglu_quant_il(const void* in, void* xq, void* sf, const fl
     if (blocks > 148 * 16) blocks = 148 * 16;
     const int k64 = telb_nvfp4_k64_pad(inter);
     if (is_bf16)
-        TELB_LAUNCH("swiglu_quant_kernel", (swiglu_quant_kernel<__nv_bfloat16>), dim3((int)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)in, (uint8_t*)xq, (uint8_t*)sf, global_scale, rows, inter, k64, interleaved);
+        TELB_LAUNCH("swiglu_quant_kernel", (swiglu_quant_kernel<__nv_bfloat16>), dim3((int)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)in, (uint8_t*)xq, (uint8_t*)sf, global_scale, rows, inter, k64, interleaved, tile_rows);
     else
-        TELB_LAUNCH("swiglu_quant_kernel", (swiglu_quant_kernel<__half>), dim3((int)blocks), dim3(256), 0, stream, (const __half*)in, (uint8_t*)xq, (uint8_t*)sf, global_scale, rows, inter, k64, interleaved);
+        TELB_LAUNCH("swiglu_quant_kernel", (swiglu_quant_kernel<__half>), dim3((int)blocks), dim3(256), 0, stream, (const __half*)in, (uint8_t*)xq, (uint8_t*)sf, global_scale, rows, inter, k64, interleaved, tile_rows);
     TELB_CHECK_LAUNCH("swiglu_quant_kernel");
     return 0;
 }

@@ -25,6 +25,7 @@ struct GemmParams {
     int* status;
     // Grouped (mixture-of-experts) mode: 128-row A tile `ta` multiplies the weight block of expert
     // tile_expert[ta] (rows [e * group_rows_b, (e+1) * group_rows_b) of the B tensor); -1 = unused tile.
+    // tile_expert[tiles_a + ta] = rows of tile ta that hold routed tokens (the rest is padding and is not stored).
     const int* tile_expert;
     int group_rows_b;
     // Tensor-parallel fusion (both optional, large-M layout only).
@@ -285,7 +286,9 @@ __device__ __forceinline__ void gemm_epilogue_role(const GemmParams& p, uint32_t
         tc_fence_after_sync();
         const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kAccStride;
         const int row = tc.a0 + lrow;
-        const bool row_ok = row < p.rows_a;
+        bool row_ok = row < p.rows_a;
+        // grouped mode: rows past the expert's own rows in this tile are padding, their results are never read
+        if (p.tile_expert) row_ok = row_ok && lrow < p.tile_expert[p.tiles_a + tc.a0 / kBM];
         int out_row = row;
         if (p.rs_world > 1 && row_ok) {     // reduce-scatter: this row's partial goes to its owner's buffer
             const int d = row / p.rs_rows_per_rank;

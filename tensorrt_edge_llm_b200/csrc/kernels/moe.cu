@@ -117,6 +117,8 @@ __global__ void moe_route_kernel(const T* __restrict__ logits, float* __restrict
     }
 }
 
+// `tile_expert` has 2 * max_tiles entries: the expert of every 128-row tile (-1 = unused), then the number of rows in use in
+// every tile (the grouped GEMM stores, and the activation kernel between the two GEMMs processes, only those rows).
 // Single CTA.  counts → padded offsets → dst rows (stable within an expert by slot order is not
 // required: the combine reads back through dst_row).  `expert_lo/hi`: experts owned by this rank
 // (expert parallelism); slots routed elsewhere get dst_row = -1.
@@ -142,10 +144,16 @@ __global__ void moe_align_kernel(const int* __restrict__ topk_idx, int* __restri
             cursor[e] = 0;
             const int tiles = (count[e] + 127) / 128;
             for (int t = 0; t < tiles; ++t)
-                if (row / 128 + t < max_tiles) tile_expert[row / 128 + t] = e - expert_lo;
+                if (row / 128 + t < max_tiles) {
+                    tile_expert[row / 128 + t] = e - expert_lo;
+                    tile_expert[max_tiles + row / 128 + t] = min(128, count[e] - t * 128);     // rows in use in this tile
+                }
             row += tiles * 128;
         }
-        for (int t = row / 128; t < max_tiles; ++t) tile_expert[t] = -1;
+        for (int t = row / 128; t < max_tiles; ++t) {
+            tile_expert[t] = -1;
+            tile_expert[max_tiles + t] = 0;
+        }
         counts_out[0] = row;          // padded rows in use
     }
     __syncthreads();

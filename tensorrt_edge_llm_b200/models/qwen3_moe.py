@@ -179,7 +179,7 @@ class MoEBlock(nn.Module):
                 self.finalize()
             a = cu.moe_gather(xa, ws, self.top_k, self.input_scale)
             h1 = cu.gemm_grouped(a, self.w13, ws, self.e_local, alpha=self.w13_alpha, w_sf=self._w13_sf)
-            a2 = cu.swiglu_quant(h1, self.down_input_scale)
+            a2 = cu.swiglu_quant(h1, self.down_input_scale, moe_ws=ws)
             y = cu.gemm_grouped(a2, self.w2, ws, self.e_local, alpha=self.w2_alpha, w_sf=self._w2_sf)
         else:
             a = cu.moe_gather(xa, ws, self.top_k, None)

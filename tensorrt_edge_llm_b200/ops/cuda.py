@@ -365,7 +365,8 @@ def gemm_nvfp4_swiglu(x: "QuantActs", weight: torch.Tensor, w_sf: torch.Tensor, 
     return QuantActs(xq, sf, (m, inter), x.dtype)
 
 
-def swiglu_quant(gate_up: torch.Tensor, global_scale: torch.Tensor, interleaved: bool = False) -> QuantActs:
+def swiglu_quant(gate_up: torch.Tensor, global_scale: torch.Tensor, interleaved: bool = False, moe_ws=None) -> QuantActs:
+    """``moe_ws``: the routing tables of a grouped (mixture-of-experts) buffer; its padding rows are skipped."""
     gate_up = gate_up.contiguous()
     m = gate_up.shape[0]
     inter = gate_up.shape[1] // 2
@@ -374,8 +375,9 @@ def swiglu_quant(gate_up: torch.Tensor, global_scale: torch.Tensor, interleaved:
     nbytes = L.telb_nvfp4_sf_bytes(c_ll(m), c_int(inter))
     xq = torch.empty(m, inter // 2, dtype=torch.uint8, device=gate_up.device)
     sf = _sf_buffer(nbytes, inter, gate_up.device)
-    _check(L.telb_swiglu_quant_il(_p(gate_up), _p(xq), _p(sf), _p(global_scale), c_ll(m), c_int(inter),
-                                  c_int(_is_bf16(gate_up)), c_int(1 if interleaved else 0), _stream()), "swiglu_quant")
+    tile_rows = c_vp(moe_ws.tile_expert.data_ptr() + 4 * moe_ws.max_tiles) if moe_ws is not None else c_vp(0)
+    _check(L.telb_swiglu_quant_rows(_p(gate_up), _p(xq), _p(sf), _p(global_scale), c_ll(m), c_int(inter),
+                                    c_int(_is_bf16(gate_up)), c_int(1 if interleaved else 0), tile_rows, _stream()), "swiglu_quant")
     return QuantActs(xq, sf, (m, inter), gate_up.dtype)
 
 
@@ -512,7 +514,8 @@ class MoeWorkspace:
         self.max_tiles = (slots + 127) // 128 + experts_local
         self.rows_pad = self.max_tiles * 128
         self.dst_row = torch.empty(slots, dtype=torch.int32, device=device)
-        self.tile_expert = torch.empty(self.max_tiles, dtype=torch.int32, device=device)
+        # [0, max_tiles): expert of each 128-row tile (-1 = unused); [max_tiles, 2 max_tiles): rows in use in each tile
+        self.tile_expert = torch.empty(2 * self.max_tiles, dtype=torch.int32, device=device)
         self.counts = torch.empty(1, dtype=torch.int32, device=device)
 
 

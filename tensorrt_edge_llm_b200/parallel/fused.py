@@ -228,7 +228,7 @@ class FusedComm(TorchComm):
                 block.finalize()
             a = cu.moe_gather(recv, ws, 1, block.input_scale)
             h1 = cu.gemm_grouped(a, block.w13, ws, block.e_local, alpha=block.w13_alpha, w_sf=block._w13_sf)
-            y = cu.gemm_grouped(cu.swiglu_quant(h1, block.down_input_scale), block.w2, ws, block.e_local, alpha=block.w2_alpha,
+            y = cu.gemm_grouped(cu.swiglu_quant(h1, block.down_input_scale, moe_ws=ws), block.w2, ws, block.e_local, alpha=block.w2_alpha,
                                 w_sf=block._w2_sf)
         else:
             a = cu.moe_gather(recv, ws, 1, None)

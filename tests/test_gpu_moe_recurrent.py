@@ -66,7 +66,10 @@ def test_moe_align_gather_combine(cu, tokens, experts, top_k, lo, hi):
     assert torch.equal(te[rows // 128], (idx[local] - lo).long())
     n_tiles = int(ws.counts.item()) // 128
     want_tiles = sum((int((idx == e).sum()) + 127) // 128 for e in range(lo, hi))
-    assert n_tiles == want_tiles and torch.all(te[n_tiles:] < 0)
+    assert n_tiles == want_tiles and torch.all(te[n_tiles:ws.max_tiles] < 0)
+    # second half: rows in use per tile; they add up to the local slots and unused tiles hold none
+    tile_rows = te[ws.max_tiles:]
+    assert int(tile_rows.sum()) == int(local.sum()) and torch.all(tile_rows[n_tiles:] == 0) and int(tile_rows.max()) <= 128
     a = cu.moe_gather(x, ws, top_k, None)
     tok = torch.arange(tokens, device="cuda")[:, None].expand(tokens, top_k)[local]
     assert torch.equal(a[rows], x[tok])
