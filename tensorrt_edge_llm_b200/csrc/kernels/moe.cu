@@ -128,8 +128,9 @@ __global__ void moe_align_kernel(const int* __restrict__ topk_idx, int* __restri
     pdl_prologue();
     extern __shared__ int sm[];
     int* count = sm;                  // [experts]
-    int* offset = sm + experts;       // [experts] padded start row
+    int* offset = sm + experts;       // [experts] first tile of the expert's segment
     int* cursor = offset + experts;   // [experts]
+    __shared__ int total_tiles;
     for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
     __syncthreads();
     for (int i = threadIdx.x; i < slots; i += blockDim.x) {
@@ -137,29 +138,49 @@ __global__ void moe_align_kernel(const int* __restrict__ topk_idx, int* __restri
         if (e >= expert_lo && e < expert_hi) atomicAdd(&count[e], 1);
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int row = 0;
-        for (int e = 0; e < experts; ++e) {
-            offset[e] = row;
-            cursor[e] = 0;
-            const int tiles = (count[e] + 127) / 128;
-            for (int t = 0; t < tiles; ++t)
-                if (row / 128 + t < max_tiles) {
-                    tile_expert[row / 128 + t] = e - expert_lo;
-                    tile_expert[max_tiles + row / 128 + t] = min(128, count[e] - t * 128);     // rows in use in this tile
-                }
-            row += tiles * 128;
+    // exclusive prefix sum of the per-expert tile counts: warp 0 walks the experts 32 at a time
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        int carry = 0;
+        for (int e0 = 0; e0 < experts; e0 += 32) {
+            const int e = e0 + lane;
+            const int tiles = e < experts ? (count[e] + 127) / 128 : 0;
+            int incl = tiles;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            if (e < experts) {
+                offset[e] = carry + incl - tiles;
+                cursor[e] = 0;
+            }
+            carry += __shfl_sync(0xffffffffu, incl, 31);
         }
-        for (int t = row / 128; t < max_tiles; ++t) {
-            tile_expert[t] = -1;
-            tile_expert[max_tiles + t] = 0;
+        if (lane == 0) {
+            total_tiles = carry;
+            counts_out[0] = carry * 128;      // padded rows in use
         }
-        counts_out[0] = row;          // padded rows in use
     }
     __syncthreads();
+    // every expert fills in its own tiles; the tiles past the last segment are marked unused
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        const int tiles = (count[e] + 127) / 128;
+        for (int t = 0; t < tiles; ++t) {
+            const int tile = offset[e] + t;
+            if (tile < max_tiles) {
+                tile_expert[tile] = e - expert_lo;
+                tile_expert[max_tiles + tile] = min(128, count[e] - t * 128);     // rows in use in this tile
+            }
+        }
+    }
+    for (int t = total_tiles + threadIdx.x; t < max_tiles; t += blockDim.x) {
+        tile_expert[t] = -1;
+        tile_expert[max_tiles + t] = 0;
+    }
     for (int i = threadIdx.x; i < slots; i += blockDim.x) {
         const int e = topk_idx[i];
-        if (e >= expert_lo && e < expert_hi) dst_row[i] = offset[e] + atomicAdd(&cursor[e], 1);
+        if (e >= expert_lo && e < expert_hi) dst_row[i] = offset[e] * 128 + atomicAdd(&cursor[e], 1);
         else dst_row[i] = -1;
     }
 }
