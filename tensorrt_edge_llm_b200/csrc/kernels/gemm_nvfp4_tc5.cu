@@ -178,7 +178,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         }
     } else {
         gemm_epilogue_role<BN>(p, tmem_base, tfull_bar, tempty_bar, abort_flag, last_flag, total_tiles, kAccStride,
-                               smem + STAGES * kStageBytes + 256);
+                               smem + STAGES * kStageBytes + 256,
+                               reinterpret_cast<float*>(smem + STAGES * kStageBytes + 256 + kRsStageBytes));
     }
 
     if (*abort_flag) {
@@ -198,7 +199,7 @@ static int launch_nvfp4(const CUtensorMap& ta, const CUtensorMap& tb, const uint
                         int k64b, const GemmParams& p, cudaStream_t stream) {
     constexpr int kBGroups = BN > 128 ? BN / 128 : 1;
     constexpr int kStageBytes = kFp4ATileBytes + BN * 128 + kSfStageBytes + kBGroups * kSfStageBytes;
-    constexpr int smem = STAGES * kStageBytes + 1024 + 256 + kRsStageBytes;
+    constexpr int smem = STAGES * kStageBytes + 1024 + 256 + kRsStageBytes + kAlphaStageBytes;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

@@ -137,7 +137,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         }
     } else {
         gemm_epilogue_role<BN>(p, tmem_base, tfull_bar, tempty_bar, abort_flag, last_flag, total_tiles, kAccStride,
-                               smem + STAGES * kStageBytes + 256);
+                               smem + STAGES * kStageBytes + 256,
+                               reinterpret_cast<float*>(smem + STAGES * kStageBytes + 256 + kRsStageBytes));
     }
 
     // ---------------- common exit ----------------
@@ -157,7 +158,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 template <int BN, int STAGES>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
     constexpr int kStageBytes = kATileBytes + BN * kBK * 2;
-    constexpr int smem = STAGES * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/ + kRsStageBytes;
+    constexpr int smem = STAGES * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/ + kRsStageBytes + kAlphaStageBytes;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc5_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
