@@ -223,6 +223,64 @@ def bench_ops(args):
     cu.Workspace.get(torch.device("cuda", 0)).check_status()
 
 
+def bench_moe(args):
+    """One Qwen3-30B-A3B-shape NVFP4 MoE block (128 experts, top-8, H 2048, I 768) at ``--tokens`` rows, as a whole and
+    kernel by kernel.  Calls are timed as captured chains; the whole-block figure rotates over three weight sets (340 MB
+    each) so the expert weights come from HBM as they do in a decode step."""
+    from ..config import QuantConfig, qwen3_30b_a3b_config
+    from ..models.qwen3_moe import MoEBlock
+    from ..ops import cuda as cu
+
+    def chain_us(fns):
+        for f in fns:
+            f()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for f in fns:
+                f()
+        ts = []
+        for _ in range(args.iters):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3 / len(fns))
+        return round(statistics.median(ts), 2)
+
+    cfg = qwen3_30b_a3b_config(num_hidden_layers=1)
+    cfg.quant = QuantConfig(quant_type="nvfp4", group_size=16, excluded=["*self_attn*", "*mlp.gate", "lm_head"])
+    blocks = []
+    for i in range(3):
+        b = MoEBlock(cfg, "model.layers.0.mlp").cuda()
+        b.random_init(torch.Generator().manual_seed(i), std=0.05)
+        b.finalize()
+        blocks.append(b)
+    m = args.tokens
+    x = torch.randn(m, cfg.hidden_size, device="cuda", generator=torch.Generator(device="cuda").manual_seed(0)).bfloat16()
+    print(json.dumps({"kernel": "moe_block", "tokens": m, "us": chain_us([(lambda b=b: b(x)) for b in blocks]),
+                      "expert_weight_mb": round(sum(t.numel() for t in (blocks[0].w13, blocks[0].w2)) * 1.125 / 1e6, 1)}))
+    b = blocks[0]
+    e, k = cfg.num_experts, cfg.num_experts_per_tok
+    logits = b.gate(x)
+    w, idx = cu.moe_route_softmax_topk(logits, k, True)
+    ws = cu.moe_align(idx, e, 0, e)
+    a = cu.moe_gather(x, ws, k, b.input_scale)
+    h1 = cu.gemm_grouped(a, b.w13, ws, e, alpha=b.w13_alpha, w_sf=b._w13_sf)
+    a2 = cu.swiglu_quant(h1, b.down_input_scale, moe_ws=ws)
+    y = cu.gemm_grouped(a2, b.w2, ws, e, alpha=b.w2_alpha, w_sf=b._w2_sf)
+    parts = {"gate": lambda: b.gate(x), "route": lambda: cu.moe_route_softmax_topk(logits, k, True),
+             "align": lambda: cu.moe_align(idx, e, 0, e), "gather_quant": lambda: cu.moe_gather(x, ws, k, b.input_scale),
+             "fc1": lambda: cu.gemm_grouped(a, b.w13, ws, e, alpha=b.w13_alpha, w_sf=b._w13_sf),
+             "swiglu_quant": lambda: cu.swiglu_quant(h1, b.down_input_scale, moe_ws=ws),
+             "fc2": lambda: cu.gemm_grouped(a2, b.w2, ws, e, alpha=b.w2_alpha, w_sf=b._w2_sf),
+             "combine": lambda: cu.moe_combine(y, ws, w)}
+    print(json.dumps({"kernel": "moe_parts_us", "tokens": m, "tiles_in_use": int(ws.counts.item()) // 128,
+                      **{name: chain_us([f] * 8) for name, f in parts.items()}}))
+    cu.Workspace.get(torch.device("cuda", 0)).check_status()
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -243,12 +301,14 @@ def main():
     o = sub.add_parser("ops")
     o.add_argument("--tokens", type=int, default=8192)
     o.add_argument("--only", nargs="*", default=None)
-    for p in (g, a, o):
+    mo = sub.add_parser("moe")
+    mo.add_argument("--tokens", type=int, default=32)
+    for p in (g, a, o, mo):
         p.add_argument("--warmup", type=int, default=3)
         p.add_argument("--iters", type=int, default=10)
         p.add_argument("--graph", type=int, default=0, help="time decode-size calls as N captured launches per replay")
     args = ap.parse_args()
-    {"gemm": bench_gemm, "attention": bench_attention, "ops": bench_ops}[args.cmd](args)
+    {"gemm": bench_gemm, "attention": bench_attention, "ops": bench_ops, "moe": bench_moe}[args.cmd](args)
 
 
 if __name__ == "__main__":
