@@ -35,7 +35,7 @@ def _guided(spec):
     if m == "choice":
         return GuidedDecodingParams("choice", choices=list(spec[m]))
     if m == "ebnf":
-        return GuidedDecodingParams("ebnf", grammar=str(spec[m]))
+        return GuidedDecodingParams("ebnf", grammar=str(spec[m]), jump_forward=bool(spec.get("jump_forward", False)))
     return GuidedDecodingParams("structural_tag", structural_tag=spec[m] if isinstance(spec[m], dict) else json.loads(spec[m]))
 
 

@@ -26,6 +26,7 @@ class GuidedDecodingParams:
     pattern: str = ""
     json_schema: Optional[dict] = None
     max_depth: int = 8
+    jump_forward: bool = False                 # append grammar-forced tokens without a forward pass each (ebnf only)
     grammar: str = ""                          # EBNF text ("ebnf")
     structural_tag: Optional[dict] = None      # {"structures": [...], "triggers": [...]} ("structural_tag")
 
@@ -233,6 +234,7 @@ class GuidedDecoder:
         self.eos = set(int(t) for t in eos_token_ids)
         self.text = ""
         self.finished = False
+        self.jump_forward = bool(params.jump_forward) and hasattr(self.matcher, "forced_continuation")
 
     @staticmethod
     def vocabulary(tokenizer, vocab_size: int) -> List[Optional[str]]:
@@ -268,6 +270,27 @@ class GuidedDecoder:
         w = bits.view(-1, 32).to(torch.int64)
         packed = (w << torch.arange(32)).sum(-1)
         return torch.where(packed >= 2 ** 31, packed - 2 ** 32, packed).to(torch.int32)
+
+    def forced_tokens(self, tokenizer, budget: int) -> List[int]:
+        """Tokens the constraint forces next (``cpp/runtime/decoding/jumpForward.cpp`` in the reference): the grammar allows
+        exactly one continuation for a stretch of characters, so its tokens are appended — and the matcher advanced —
+        without sampling them one forward pass at a time.  At most ``budget`` tokens; never a partial character run that
+        the tokenizer would split differently from the matcher's view (every token is re-checked against the grammar)."""
+        if not self.jump_forward or self.finished or budget <= 0:
+            return []
+        forced = self.matcher.forced_continuation(self.text)
+        if not forced:
+            return []
+        out: List[int] = []
+        for t in tokenizer.encode(forced):
+            t = int(t)
+            piece = self.token_texts[t] if 0 <= t < len(self.token_texts) else None
+            if piece is None or len(out) >= budget or not forced.startswith(piece):
+                break
+            self.advance(t)
+            forced = forced[len(piece):]
+            out.append(t)
+        return out
 
     def advance(self, token: int) -> None:
         if token in self.eos:

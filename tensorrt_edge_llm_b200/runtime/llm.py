@@ -266,6 +266,8 @@ class LLM:
         reports: List[List[dict]] = [[] for _ in range(n)]
         reasons = ["length"] * n
         live = list(range(n))
+        feed: List[List[int]] = [[] for _ in range(n)]
+        self.jump_forward_tokens = 0
         t0 = time.perf_counter()
         try:
             logits = self.runner.prefill(seats, [list(map(int, p)) for p in ids])
@@ -288,11 +290,20 @@ class LLM:
                     if not sp.ignore_eos and toks[j] in eos_set:
                         reasons[i] = "stop"
                         continue
+                    feed[i] = [toks[j]]
+                    dec = states[i].guided
+                    if dec is not None and dec.jump_forward:          # grammar-forced tokens ride along with the sampled one
+                        extra = dec.forced_tokens(self.tokenizer, sp.max_tokens - len(rows[i]))
+                        rows[i] += extra
+                        feed[i] += extra
+                        self.jump_forward_tokens += len(extra)
+                    if len(rows[i]) >= sp.max_tokens:
+                        continue
                     keep.append(j)
-                if not keep or step == sp.max_tokens - 1:
+                if not keep:
                     break
                 live_next = [live[j] for j in keep]
-                logits = self.runner.step([seats[i] for i in live_next], [[rows[i][-1]] for i in live_next])
+                logits = self.runner.step([seats[i] for i in live_next], [feed[i] for i in live_next])
                 live = live_next
         finally:
             self.runner.use_cuda_graphs = was

@@ -91,7 +91,7 @@ def guided_to_wire(params) -> Tuple[str, str]:
     if params is None:
         return "", ""
     return params.type, json.dumps({"choices": list(params.choices), "pattern": params.pattern, "json_schema": params.json_schema,
-                                    "max_depth": params.max_depth, "grammar": params.grammar, "structural_tag": params.structural_tag})
+                                    "max_depth": params.max_depth, "grammar": params.grammar, "structural_tag": params.structural_tag, "jump_forward": params.jump_forward})
 
 
 def process(logits: torch.Tensor, states: Sequence[Optional[RowState]]) -> torch.Tensor:

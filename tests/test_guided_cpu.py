@@ -166,3 +166,25 @@ def test_generate_under_a_grammar():
     for o in outs:
         assert m.complete(o.text), o.text
     llm.close()
+
+
+def test_jump_forward_appends_forced_tokens_without_forward_passes():
+    from tensorrt_edge_llm_b200.runtime.grammar import EbnfMatcher
+    from tensorrt_edge_llm_b200.runtime.llm import LLM, SamplingParams
+    g = 'root ::= "{\\"name\\": \\"" [a-z]{3} "\\", \\"ok\\": " ("true" | "false") "}"'
+    cfg = tiny_llama_config(num_hidden_layers=1, vocab_size=300)
+    cfg.eos_token_id = 2
+    llm = LLM(cfg, device="cpu", max_batch_size=1, max_input_len=32, max_kv_cache_capacity=96, page_size=16, tokenizer=ByteTokenizer())
+    calls = []
+    step = llm.runner.step
+    llm.runner.step = lambda seats, toks, **kw: (calls.append([len(t) for t in toks]), step(seats, toks, **kw))[1]
+    plain = llm.generate([[5, 6]], SamplingParams(max_tokens=60, temperature=0.0, guided=GuidedDecodingParams("ebnf", grammar=g)))[0]
+    n_plain = len(calls)
+    calls.clear()
+    fast = llm.generate([[5, 6]], SamplingParams(max_tokens=60, temperature=0.0,
+                                                 guided=GuidedDecodingParams("ebnf", grammar=g, jump_forward=True)))[0]
+    m = EbnfMatcher(g)
+    assert m.complete(plain.text) and m.complete(fast.text) and fast.text == plain.text
+    # only the three letters and the boolean's first letter are choices: everything else is appended in bulk
+    assert llm.jump_forward_tokens >= 20 and len(calls) < n_plain / 3 and max(max(c) for c in calls) > 5
+    llm.close()
