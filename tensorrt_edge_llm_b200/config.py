@@ -160,6 +160,7 @@ class ModelConfig:
     attention_bias: bool = False
     sliding_window: Optional[int] = None
     layer_windows: List[int] = field(default_factory=list)  # per layer: sliding window in tokens, 0 = full attention (empty = `sliding_window` everywhere)
+    mrope_section: List[int] = field(default_factory=list)   # multimodal RoPE: rotary pairs per (temporal, height, width) component
     rope_local_theta: float = 0.0                   # RoPE base of the sliding-window layers when it differs (Gemma 3)
     rope_local_scaling: Optional[Dict[str, Any]] = None
     query_pre_attn_scalar: float = 0.0              # attention scale = this ** -0.5 when set (Gemma), else head_dim ** -0.5
@@ -295,7 +296,8 @@ class ModelConfig:
         rope_scaling = llm.get("rope_scaling") or llm.get("rope_parameters")
         if rope_theta is None and isinstance(rope_scaling, dict):
             rope_theta = rope_scaling.get("rope_theta")
-        if isinstance(rope_scaling, dict) and rope_scaling.get("rope_type", rope_scaling.get("type")) in (None, "default"):
+        mrope_section = list((rope_scaling or {}).get("mrope_section") or []) if isinstance(rope_scaling, dict) else []
+        if isinstance(rope_scaling, dict) and rope_scaling.get("rope_type", rope_scaling.get("type")) in (None, "default", "mrope"):
             rope_scaling = None
         n_layers = int(llm["num_hidden_layers"])
         layer_types, mlp_types, mamba, gdn = _parse_hybrid(llm, n_layers)
@@ -322,6 +324,7 @@ class ModelConfig:
             rms_norm_eps=float(llm.get("rms_norm_eps", llm.get("layer_norm_epsilon", 1e-6))),
             rope_theta=float(rope_theta if rope_theta is not None else 10000.0),
             rope_scaling=rope_scaling,
+            mrope_section=mrope_section,
             partial_rotary_factor=float(llm.get("partial_rotary_factor", 1.0)),
             max_position_embeddings=int(llm.get("max_position_embeddings", 32768)),
             tie_word_embeddings=bool(hf.get("tie_word_embeddings", llm.get("tie_word_embeddings", False))),

@@ -192,7 +192,12 @@ class CausalLM(nn.Module):
 
     def hidden_states(self, ids, meta, kv_cache, inputs_embeds=None, capture_layers=()):
         dev = ids.device if inputs_embeds is None else inputs_embeds.device
-        return self.model(ids, meta, kv_cache, self.cos_sin(dev), self.comm, inputs_embeds, capture_layers)
+        cs = self.cos_sin(dev)
+        if meta.positions3 is not None and self.cfg.mrope_section and meta.rope_rows is None:
+            # multimodal RoPE: one [T, D] cos / sin row per token, built from its (t, h, w) position, shared by all layers
+            meta.rope_rows = ops.ref.mrope_rows(cs, meta.positions3, self.cfg.mrope_section)
+            meta.rope_pos = torch.arange(meta.num_tokens, dtype=torch.int32, device=dev)
+        return self.model(ids, meta, kv_cache, cs, self.comm, inputs_embeds, capture_layers)
 
     def logits_from_hidden(self, x: torch.Tensor, meta: StepMeta) -> torch.Tensor:
         rows = x if meta.logits_idx.numel() == x.shape[0] else x.index_select(0, meta.logits_idx.long())

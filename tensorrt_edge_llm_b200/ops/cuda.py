@@ -214,8 +214,11 @@ def rope_kv_write(qkv, kv_layer, meta: StepMeta, cos_sin, num_q_heads, num_kv_he
     t = qkv.shape[0]
     q = torch.empty(t, num_q_heads, head_dim, dtype=qkv.dtype, device=qkv.device)
     assert kv_layer.is_contiguous() and kv_layer.dtype == qkv.dtype
+    positions = meta.positions
+    if meta.rope_rows is not None:          # multimodal RoPE: per-row cos / sin tables prepared by the model
+        cos_sin, positions = meta.rope_rows, meta.rope_pos
     _check(lib().telb_rope_kv_write(
-        _p(qkv), _p(q), _p(kv_layer), _p(cos_sin), _p(meta.positions), _p(meta.seq_ids), _p(meta.q_start),
+        _p(qkv), _p(q), _p(kv_layer), _p(cos_sin), _p(positions), _p(meta.seq_ids), _p(meta.q_start),
         _p(meta.past_len), _p(meta.page_table), _p(meta.kv_offsets), _p(q_norm_w), _p(k_norm_w), c_int(t),
         c_int(num_q_heads), c_int(num_kv_heads), c_int(head_dim), c_int(cos_sin.shape[-1]), c_int(meta.page_size),
         c_int(meta.page_table.shape[1]), c_float(eps), c_int(_is_bf16(qkv)), _stream()), "rope_kv_write")

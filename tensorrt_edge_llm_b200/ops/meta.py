@@ -38,6 +38,11 @@ class StepMeta:
     tree_mask: Optional[torch.Tensor] = None
     # KV slot of each row relative to past_len (None = row index within the sequence).
     kv_offsets: Optional[torch.Tensor] = None
+    # Multimodal RoPE: temporal / height / width position of each row, int32 [3, T].  The model turns them into
+    # per-row cos / sin rows (`rope_rows` [T, D], looked up with `rope_pos` = 0..T-1) before its layers run.
+    positions3: Optional[torch.Tensor] = None
+    rope_rows: Optional[torch.Tensor] = None
+    rope_pos: Optional[torch.Tensor] = None
 
     @property
     def is_decode(self) -> bool:

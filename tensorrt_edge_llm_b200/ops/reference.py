@@ -14,7 +14,7 @@ GQA attention (``unittests/support/references.h:29-65``), NVFP4 math
 from __future__ import annotations
 
 import math
-from typing import Optional, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 import torch.nn.functional as F
@@ -107,6 +107,56 @@ def rope_cos_sin(max_pos: int, rotary_dim: int, theta: float, scaling: Optional[
     return torch.cat([ang.cos() * att, ang.sin() * att], dim=-1).float().to(device)
 
 
+def mrope_rows(cos_sin: torch.Tensor, positions3: torch.Tensor, sections: Sequence[int]) -> torch.Tensor:
+    """Multimodal RoPE (Qwen2-VL): rotary pair ``i`` takes its angle from the temporal, height or width position
+    according to ``sections`` (pairs per component, summing to ``D / 2``).  ``cos_sin [P, D]`` is the ordinary table,
+    ``positions3 [3, T]``; returns per-row tables ``[T, D]`` to be looked up with positions ``0..T-1``."""
+    half = cos_sin.shape[-1] // 2
+    if sum(sections) != half or len(sections) != 3:
+        raise ValueError(f"mrope sections {list(sections)} must be three counts summing to {half}")
+    comp = torch.repeat_interleave(torch.arange(3, device=cos_sin.device), torch.tensor(list(sections), device=cos_sin.device))
+    pos = positions3.long().to(cos_sin.device)[comp]                  # [half, T]: position used by pair i at row t
+    cols = torch.arange(half, device=cos_sin.device)[:, None].expand_as(pos)
+    cos = cos_sin[pos, cols]                                          # [half, T]
+    sin = cos_sin[pos, cols + half]
+    return torch.cat([cos.t(), sin.t()], dim=-1).contiguous()
+
+
+def mrope_positions(token_ids: Sequence[int], image_token_id: int, grids: Sequence[Sequence[int]], spatial_merge: int = 2):
+    """3-D positions of a prompt whose images appear as runs of ``image_token_id`` (Qwen2-VL ``get_rope_index``): text rows
+    advance all three components together; an image of grid ``(t, h, w)`` patches (``h``, ``w`` before the spatial
+    merge) occupies ``t · h/m · w/m`` rows whose components count frames, rows and columns from the current offset,
+    and the text after it continues from the largest component plus one.  Returns ``(positions3 [3, T] int32, delta)``
+    with ``delta`` = next position − ``T``, the offset decode steps add to the sequence length."""
+    ids = list(token_ids)
+    out = [[], [], []]
+    nxt, i, img = 0, 0, 0
+    while i < len(ids):
+        if ids[i] != image_token_id:
+            for c in range(3):
+                out[c].append(nxt)
+            nxt += 1
+            i += 1
+            continue
+        if img >= len(grids):
+            raise ValueError("more image runs in the prompt than grids")
+        t, h, w = grids[img]
+        h, w = h // spatial_merge, w // spatial_merge
+        n = t * h * w
+        if ids[i:i + n] != [image_token_id] * n:
+            raise ValueError(f"image {img} needs a run of {n} image tokens")
+        for tt in range(t):
+            for hh in range(h):
+                for ww in range(w):
+                    out[0].append(nxt + tt)
+                    out[1].append(nxt + hh)
+                    out[2].append(nxt + ww)
+        nxt += max(t, h, w)
+        i += n
+        img += 1
+    return torch.tensor(out, dtype=torch.int32), nxt - len(ids)
+
+
 def apply_rope(x: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor) -> torch.Tensor:
     """Rotate-half RoPE on ``x [T, H, D]`` for the first ``rotary_dim`` features (fp32 math)."""
     rd = cos_sin.shape[-1]
@@ -143,8 +193,11 @@ def rope_kv_write(qkv: torch.Tensor, kv_layer: torch.Tensor, meta: StepMeta, cos
         q = _head_rmsnorm(q, q_norm_w, eps)
     if k_norm_w is not None:
         k = _head_rmsnorm(k, k_norm_w, eps)
-    q = apply_rope(q, meta.positions, cos_sin)
-    k = apply_rope(k, meta.positions, cos_sin)
+    pos = meta.positions
+    if meta.rope_rows is not None:          # multimodal RoPE: per-row tables prepared by the model
+        cos_sin, pos = meta.rope_rows, meta.rope_pos
+    q = apply_rope(q, pos, cos_sin)
+    k = apply_rope(k, pos, cos_sin)
     p = meta.page_size
     sid = meta.seq_ids.long()
     if meta.kv_offsets is not None:

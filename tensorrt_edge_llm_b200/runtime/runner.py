@@ -57,12 +57,15 @@ class ModelRunner:
         self.cache = kv if getattr(model, "needs_cache_set", False) else kv.pool
         # reduced-vocabulary LM head: logits cover `vocab_map.numel()` columns, column c is token vocab_map[c]
         self.vocab_map: Optional[torch.Tensor] = None
+        self.rope_delta: dict = {}          # seat → multimodal RoPE position offset of its decode rows
 
     # ---- eager ragged step -----------------------------------------------------------------
     def _meta(self, seats: Sequence[int], q_lens: Sequence[int], logits_all=False, tree_mask=None,
               positions=None) -> StepMeta:
         past = [self.kv.lengths[s] for s in seats]
         for s, q, p in zip(seats, q_lens, past):
+            if p == 0:
+                self.rope_delta.pop(s, None)          # a fresh sequence on this seat
             self.kv.reserve(s, p + q)
         return build_step_meta(q_lens, past, self.kv.table_rows(seats), self.kv.page_size, slot_ids=seats,
                                logits_all=logits_all, device=self.device, tree_mask=tree_mask, positions=positions)
@@ -73,6 +76,12 @@ class ModelRunner:
         """Run one ragged step; returns logits ``[L, V]`` (last row of each sequence unless
         ``logits_all``).  KV lengths advance by the rows fed when ``commit``."""
         q_lens = [len(t) for t in token_lists]
+        for s in seats:
+            if self.kv.lengths[s] == 0:
+                self.rope_delta.pop(s, None)          # a fresh sequence on this seat
+        if positions is None and self.rope_delta and any(self.rope_delta.get(s) for s in seats):
+            # sequences whose prompt held images: text positions run ahead of / behind the cache length by a fixed offset
+            positions = [self.kv.lengths[s] + self.rope_delta.get(s, 0) + j for s, q in zip(seats, q_lens) for j in range(q)]
         meta = self._meta(seats, q_lens, logits_all, tree_mask, positions)
         flat = [t for ts in token_lists for t in ts]
         if self.device.type == "cuda":
@@ -125,11 +134,19 @@ class ModelRunner:
         return torch.stack(out)  # type: ignore[arg-type]
 
     @torch.no_grad()
-    def prefill_embeds(self, seats: Sequence[int], embeds: Sequence[torch.Tensor]) -> torch.Tensor:
+    def prefill_embeds(self, seats: Sequence[int], embeds: Sequence[torch.Tensor], positions3: Optional[Sequence[torch.Tensor]] = None,
+                       rope_deltas: Optional[Sequence[int]] = None) -> torch.Tensor:
         """Prefill from embedding rows instead of token ids (multimodal prompts: text rows with the image / audio
-        rows already merged in).  One step; returns last-row logits ``[N, V]``."""
+        rows already merged in).  One step; returns last-row logits ``[N, V]``.
+
+        ``positions3`` (one ``[3, T_i]`` tensor per sequence, see ``ops.reference.mrope_positions``) switches the step to
+        multimodal RoPE; ``rope_deltas`` are remembered per seat and added to the position of every later decode row."""
         q_lens = [int(e.shape[0]) for e in embeds]
         meta = self._meta(seats, q_lens)
+        if positions3 is not None:
+            meta.positions3 = torch.cat([p.to(torch.int32) for p in positions3], dim=1).to(self.device)
+            for s, d in zip(seats, rope_deltas or [0] * len(seats)):
+                self.rope_delta[s] = int(d)
         x = torch.cat([e.to(self.device) for e in embeds], dim=0).to(self.model.cfg.compute_dtype)
         logits = self.model(None, meta, self.cache, inputs_embeds=x)
         for s, q in zip(seats, q_lens):
@@ -203,7 +220,7 @@ class ModelRunner:
         n = len(seats)
         for s in seats:
             self.kv.reserve(s, self.kv.lengths[s] + steps)
-        if self.use_cuda_graphs:
+        if self.use_cuda_graphs and not any(self.rope_delta.get(s) for s in seats):
             g = self._graphs.get(n)
             if g is None:
                 g = self._graphs[n] = _DecodeGraph(self, n)
