@@ -54,6 +54,10 @@ def parse_request_file(body: Dict[str, Any]) -> List[Dict[str, Any]]:
         n_lp = int(r.get("num_logprobs", top_lp))
         if not 0 <= n_lp <= 50:
             raise RequestFileError(f"requests[{i}]: num_logprobs must be in [0, 50]")
+        if body.get("context_cache_lookup_policy", "use_cache") not in ("use_cache", "bypass"):
+            raise RequestFileError("context_cache_lookup_policy must be use_cache or bypass")
+        if body.get("context_cache_commit_policy", "including_generated_tokens") not in ("none", "prefill_state_only", "including_generated_tokens"):
+            raise RequestFileError("unknown context_cache_commit_policy")
         bias = r.get("logit_bias", body.get("logit_bias"))
         stop = r.get("stop", [])
         out.append({
@@ -68,6 +72,8 @@ def parse_request_file(body: Dict[str, Any]) -> List[Dict[str, Any]]:
             "add_generation_prompt": bool(body.get("add_generation_prompt", True)),
             "enable_thinking": bool(body.get("enable_thinking", False)),
             "disable_spec_decode": bool(r.get("disable_spec_decode", False)), "lora_name": r.get("lora_name"),
+            "cache_lookup": body.get("context_cache_lookup_policy", "use_cache") != "bypass",
+            "cache_commit": body.get("context_cache_commit_policy", "including_generated_tokens"),
         })
     return out
 
@@ -87,7 +93,8 @@ def run_requests(llm, template, requests: List[Dict[str, Any]]) -> List[Dict[str
         prompt = template.apply(r["messages"], r["add_generation_prompt"], None, r["enable_thinking"]) if r["apply_chat_template"] \
             else _text_of(r["messages"])
         sp = SamplingParams(max_tokens=r["max_tokens"], temperature=r["temperature"], top_k=r["top_k"], top_p=r["top_p"], seed=r["seed"],
-                            logprobs=r["num_logprobs"] if r["num_logprobs"] > 0 else None, logit_bias=r["logit_bias"], guided=r["guided"])
+                            logprobs=r["num_logprobs"] if r["num_logprobs"] > 0 else None, logit_bias=r["logit_bias"], guided=r["guided"],
+                            context_cache_lookup=r["cache_lookup"], context_cache_commit=r["cache_commit"])
         o = llm.generate([prompt], sp)[0]
         text = o.text or ""
         reason = o.finish_reason
@@ -95,7 +102,9 @@ def run_requests(llm, template, requests: List[Dict[str, Any]]) -> List[Dict[str
         if cut >= 0:
             text, reason = text[:cut], "stop"
         res = {"output_text": text, "output_ids": o.token_ids, "finish_reason": reason, "input_tokens": len(o.prompt_token_ids),
-               "output_tokens": len(o.token_ids), "ttft_s": o.ttft_s}
+               "output_tokens": len(o.token_ids), "ttft_s": o.ttft_s, "reused_input_tokens": o.reused_input_tokens}
+        if o.spec_stats:
+            res["spec_decode"] = o.spec_stats
         if o.logprobs:
             res["logprobs"] = [{"token_id": e["token_id"], "logprob": e["logprob"],
                                 "top": [{"token_id": t, "logprob": v} for t, v in e["top"]]} for e in o.logprobs]

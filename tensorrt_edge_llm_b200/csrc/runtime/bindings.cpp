@@ -239,7 +239,9 @@ PYBIND11_MODULE(_telb_runtime, m) {
         .def_readwrite("guided_type", &GenerationRequest::guided_type)
         .def_readwrite("guided_spec", &GenerationRequest::guided_spec)
         .def_readwrite("logit_bias_ids", &GenerationRequest::logit_bias_ids)
-        .def_readwrite("logit_bias_values", &GenerationRequest::logit_bias_values);
+        .def_readwrite("logit_bias_values", &GenerationRequest::logit_bias_values)
+        .def_readwrite("cache_lookup", &GenerationRequest::cache_lookup)
+        .def_readwrite("cache_commit", &GenerationRequest::cache_commit);
     py::class_<AdmissionResult>(m, "AdmissionResult")
         .def(py::init<>())
         .def_readwrite("admitted", &AdmissionResult::admitted)

@@ -135,6 +135,10 @@ struct GenerationRequest {
     std::string guided_spec;                // JSON text of the constraint's parameters
     std::vector<int32_t> logit_bias_ids;    // additive bias on these token ids ...
     std::vector<float> logit_bias_values;   // ... by these amounts, before sampling
+    // Context (prefix) cache policies of this request: look the prompt up at admission or bypass the cache; publish
+    // nothing (0), the prompt's full pages (1, "prefill_state_only") or prompt plus generated tokens (2).
+    bool cache_lookup = true;
+    int cache_commit = 1;
 };
 
 struct AdmissionResult {

@@ -30,6 +30,8 @@ class RequestOutput:
     ttft_s: float = 0.0
     decode_s: float = 0.0
     logprobs: Optional[List[dict]] = None      # per token: {"token_id", "logprob", "top": [(id, logprob), ...]}
+    reused_input_tokens: int = 0               # prompt tokens served from the prefix cache
+    spec_stats: Optional[dict] = None          # speculative runs: rounds, draft forwards, mean acceptance length
 
 
 class LLM:
@@ -139,6 +141,11 @@ class LLM:
             r.logit_bias_values = [float(v) for v in sp.logit_bias.values()]
         if sp.guided is not None:
             r.guided_type, r.guided_spec = lp.guided_to_wire(sp.guided)
+        r.cache_lookup = bool(sp.context_cache_lookup)
+        try:
+            r.cache_commit = {"none": 0, "prefill_state_only": 1, "including_generated_tokens": 2}[sp.context_cache_commit]
+        except KeyError:
+            raise ValueError(f"unknown context_cache_commit policy {sp.context_cache_commit!r}") from None
         return r
 
     @staticmethod
@@ -217,7 +224,7 @@ class LLM:
                 if reason == "error" and h.error():
                     raise ValueError(h.error()) if "EDGELLM_BAD_REQUEST" in h.error() else RuntimeError(h.error())
                 outs.append(RequestOutput(p, toks, text, reason, st.ttft_s, max(st.total_s - st.ttft_s, 0.0),
-                                          self._logprob_rows(toks, h.logprobs())))
+                                          self._logprob_rows(toks, h.logprobs()), int(st.reused_tokens)))
             return outs
         if isinstance(prompts, torch.Tensor):
             outs = []
@@ -238,15 +245,19 @@ class LLM:
         dec.release(seats)
         eos = self.cfg.eos_token_id
         eos_id = None if sp.ignore_eos else (eos[0] if isinstance(eos, (list, tuple)) and eos else eos)
+        r0, e0, d0 = dec.stats.rounds, dec.stats.emitted, dec.stats.draft_forwards
         t0 = time.perf_counter()
         toks = dec.generate(seats, [list(map(int, p)) for p in ids], sp.max_tokens, eos_id)
         t1 = time.perf_counter()
+        rounds = dec.stats.rounds - r0
+        stats = {"verify_rounds": rounds, "draft_forwards": dec.stats.draft_forwards - d0,
+                 "mean_acceptance_length": (dec.stats.emitted - e0) / max(rounds, 1)}
         dec.release(seats)
         outs = []
         for p, row in zip(ids, toks):
             reason = "stop" if (eos_id is not None and row and row[-1] == eos_id) else "length"
             text = self.tokenizer.decode(row) if self.tokenizer is not None else None
-            outs.append(RequestOutput(list(p), row, text, reason, 0.0, t1 - t0))
+            outs.append(RequestOutput(list(p), row, text, reason, 0.0, t1 - t0, spec_stats=stats))
         return outs
 
     def _generate_processed(self, ids: List[List[int]], sp: SamplingParams) -> List[RequestOutput]:

@@ -35,6 +35,8 @@ class SamplingParams:
     logprobs: Optional[int] = None          # None = off; k = report the chosen token's log-probability and the k most likely
     logit_bias: Optional[dict] = None       # token id → additive bias on its logit
     guided: Optional[object] = None         # runtime.guided.GuidedDecodingParams
+    context_cache_lookup: bool = True       # False = bypass the prefix cache for this request
+    context_cache_commit: str = "prefill_state_only"     # "none" | "prefill_state_only" | "including_generated_tokens"
 
     @property
     def needs_logits_processing(self) -> bool:

@@ -95,7 +95,7 @@ class ModelSession(rt.RuntimeSession):
             return r
         reused = 0
         try:
-            if self.prefix is not None:
+            if self.prefix is not None and req.cache_lookup:
                 m = self.prefix.lookup(list(req.prompt_ids))
                 pages, tokens = list(m.pages), m.tokens
                 if tokens and self.hybrid:
@@ -246,12 +246,20 @@ class ModelSession(rt.RuntimeSession):
             for s in seqs:
                 if s.kind == rt.WorkKind.Context and s.last_chunk:
                     q = self.seqs[s.slot]
-                    self.prefix.insert(list(q.req.prompt_ids), len(q.req.prompt_ids), self.kv.pages_of(s.slot))
+                    if q.req.cache_commit >= 1:
+                        self.prefix.insert(list(q.req.prompt_ids), len(q.req.prompt_ids), self.kv.pages_of(s.slot))
         out.deltas = deltas
         return out
 
     def release(self, slot):
         if slot in self.seqs:
+            q = self.seqs[slot]
+            if self.prefix is not None and q.req.cache_commit >= 2 and not self.hybrid:
+                # "including generated tokens": the full pages of prompt + output become reusable (a follow-up turn that
+                # quotes the answer starts from them); hybrid models publish prompts only, their snapshots end there
+                filled = min(self.kv.lengths[slot], len(q.tokens))
+                if filled > len(q.req.prompt_ids):
+                    self.prefix.insert(list(q.tokens[:filled]), filled, self.kv.pages_of(slot))
             del self.seqs[slot]
             self.kv.free(slot)
             self.slots.release(slot)

@@ -39,3 +39,26 @@ def test_ifb_matches_static_batch_and_reuses_prefix():
     ifb.close()
     static.close()
     assert len(a) == 5
+
+
+def test_context_cache_policies_per_request():
+    cfg = tiny_llama_config()
+    llm = LLM(cfg, device="cpu", max_batch_size=2, max_input_len=256, max_kv_cache_capacity=384,
+              enable_in_flight_batching=True, enable_prefix_cache=True)
+    prompt = _prompts()[2]                                      # 131 tokens = two full 64-token pages
+    sp = SamplingParams(max_tokens=70, ignore_eos=True)
+    first = llm.generate([prompt], SamplingParams(max_tokens=70, ignore_eos=True, context_cache_commit="none"))[0]
+    assert first.reused_input_tokens == 0
+    again = llm.generate([prompt], sp)[0]                       # nothing was published by the first request
+    assert again.reused_input_tokens == 0 and again.token_ids == first.token_ids
+    third = llm.generate([prompt], SamplingParams(max_tokens=70, ignore_eos=True, context_cache_lookup=False,
+                                                  context_cache_commit="including_generated_tokens"))[0]
+    assert third.reused_input_tokens == 0                       # bypassed the lookup although the prompt pages exist now
+    # a follow-up turn that quotes prompt + answer reuses the pages of both (201 tokens → three full pages)
+    turn2 = prompt + third.token_ids + [11, 12, 13]
+    out = llm.generate([turn2], SamplingParams(max_tokens=4, ignore_eos=True))[0]
+    assert out.reused_input_tokens == 192
+    import pytest
+    with pytest.raises(ValueError):
+        llm.generate([prompt], SamplingParams(max_tokens=2, context_cache_commit="sometimes"))
+    llm.close()
