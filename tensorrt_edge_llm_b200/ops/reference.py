@@ -74,8 +74,9 @@ def rope_cos_sin(max_pos: int, rotary_dim: int, theta: float, scaling: Optional[
                  device="cpu") -> torch.Tensor:
     """``[max_pos, rotary_dim]`` table: first half cos, second half sin (fp32).
 
-    Supports the default, ``linear``, ``llama3`` and ``yarn`` frequency scalings
-    (``cpp/kernels/posEncoding/initializeCosSinCache.cu`` in the reference)."""
+    Supports the default, ``linear``, ``dynamic`` (NTK, evaluated at the table length), ``llama3``, ``yarn`` and
+    ``longrope`` (per-pair short / long factors) frequency scalings — the ``RopeType`` set of
+    ``cpp/runtime/llmRuntimeUtils.h`` and ``cpp/kernels/posEncoding/initializeCosSinCache.cu`` in the reference."""
     half = rotary_dim // 2
     inv = 1.0 / (theta ** (torch.arange(0, half, dtype=torch.float64) * 2.0 / rotary_dim))
     att = 1.0
@@ -84,6 +85,21 @@ def rope_cos_sin(max_pos: int, rotary_dim: int, theta: float, scaling: Optional[
         factor = float(scaling.get("factor", 1.0))
         if kind == "linear":
             inv = inv / factor
+        elif kind == "dynamic":
+            # NTK-aware: once the table is longer than the trained context the base grows so that the longest wavelength
+            # still spans it (the table is built once, for `max_pos` positions)
+            orig = float(scaling.get("original_max_position_embeddings", max_pos))
+            if max_pos > orig:
+                base = theta * ((factor * max_pos / orig) - (factor - 1)) ** (rotary_dim / (rotary_dim - 2))
+                inv = 1.0 / (base ** (torch.arange(0, half, dtype=torch.float64) * 2.0 / rotary_dim))
+        elif kind == "longrope":
+            orig = float(scaling.get("original_max_position_embeddings", max_pos))
+            ext = torch.tensor(scaling["long_factor"] if max_pos > orig else scaling["short_factor"], dtype=torch.float64)
+            if ext.numel() != half:
+                raise ValueError(f"longrope factors need {half} entries")
+            inv = inv / ext
+            ratio = max(float(scaling.get("factor", max_pos / orig)), 1.0)
+            att = float(scaling.get("attention_factor") or (1.0 if ratio <= 1.0 else math.sqrt(1 + math.log(ratio) / math.log(orig))))
         elif kind == "llama3":
             lo, hi = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
             orig = float(scaling.get("original_max_position_embeddings", 8192))

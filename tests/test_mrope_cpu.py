@@ -74,3 +74,28 @@ def test_model_prefill_and_decode_with_mrope():
     # a later sequence on the same seat starts clean
     r2.kv.free(0)
     assert torch.allclose(r2.prefill([0], [ids]), base, atol=1e-5) and 0 not in r2.rope_delta
+
+
+def test_rope_scalings_match_hf():
+    """dynamic-NTK and longrope tables against the Hugging Face initialisers."""
+    from transformers import LlamaConfig
+    from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
+    d, theta = 32, 10000.0
+
+    def table(inv, att, n):
+        ang = torch.arange(n, dtype=torch.float64)[:, None] * inv.double()[None, :]
+        return torch.cat([ang.cos() * att, ang.sin() * att], -1).float()
+    cfg = LlamaConfig(hidden_size=64, num_attention_heads=2, head_dim=d, max_position_embeddings=64, rope_theta=theta,
+                      rope_scaling={"rope_type": "dynamic", "factor": 4.0})
+    inv, att = ROPE_INIT_FUNCTIONS["dynamic"](cfg, "cpu", seq_len=256)
+    got = ref.rope_cos_sin(256, d, theta, {"rope_type": "dynamic", "factor": 4.0, "original_max_position_embeddings": 64})
+    assert (got - table(inv, att, 256)).abs().max() < 1e-4
+    short, long_ = [1.0 + 0.05 * i for i in range(d // 2)], [2.0 + 0.3 * i for i in range(d // 2)]
+    sc = {"rope_type": "longrope", "short_factor": short, "long_factor": long_, "factor": 4.0, "original_max_position_embeddings": 64}
+    cfg = LlamaConfig(hidden_size=64, num_attention_heads=2, head_dim=d, max_position_embeddings=256, rope_theta=theta, rope_scaling=dict(sc))
+    inv, att = ROPE_INIT_FUNCTIONS["longrope"](cfg, "cpu", seq_len=256)
+    got = ref.rope_cos_sin(256, d, theta, sc)
+    assert (got - table(inv, att, 256)).abs().max() < 1e-4
+    inv_s, att_s = ROPE_INIT_FUNCTIONS["longrope"](cfg, "cpu", seq_len=32)
+    got_s = ref.rope_cos_sin(64, d, theta, sc)
+    assert (got_s - table(inv_s, att_s, 64)).abs().max() < 1e-4
