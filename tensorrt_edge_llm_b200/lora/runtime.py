@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import json
 import os
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 from torch import nn
@@ -37,6 +37,9 @@ class LoraLinear(nn.Module):
         self.base = base
         self.adapters: Dict[str, _Adapted] = {}
         self.active: Optional[_Adapted] = None
+        # per-step routing for batches that mix adapters: [(first row, end row, adapter name or None)], rows of the step
+        self.segments: Optional[List[Tuple[int, int, Optional[str]]]] = None
+        self.segment_rows = 0
 
     def __getattr__(self, name):            # the model reads attributes such as fused_input_scale, tp_mode, weight
         try:
@@ -44,8 +47,24 @@ class LoraLinear(nn.Module):
         except AttributeError:
             return getattr(super().__getattr__("base"), name)
 
+    def _add(self, y, x16, ad: _Adapted):
+        for a, b, col in ad.parts:
+            t = ops.linear(x16, a)
+            n = b.shape[0]
+            y[..., col:col + n] += ops.linear(t, b)
+
     def forward(self, x):
         y = self.base(x)
+        if self.segments is not None and isinstance(y, torch.Tensor) and y.shape[0] == self.segment_rows:
+            # segment-routed (``cpp/kernels/lora/groupedLoraGemm`` in the reference): every request's rows get the update
+            # of that request's adapter; rows without an adapter pass through
+            if not isinstance(x, torch.Tensor):
+                raise RuntimeError("LoRA needs 16-bit activations: disable fused activation quantisation for adapted layers")
+            for r0, r1, name in self.segments:
+                ad = self.adapters.get(name) if name else None
+                if ad is not None and r1 > r0:
+                    self._add(y[r0:r1], x[r0:r1], ad)
+            return y
         ad = self.active
         if ad is None or not isinstance(y, torch.Tensor):
             return y
@@ -125,6 +144,21 @@ class LoraManager:
             w.adapters.setdefault(name, _Adapted()).parts.append((a.to(dev, dt).contiguous(), b.to(dev, dt).contiguous(), col))
         if name not in self.names:
             self.names.append(name)
+
+    def set_segments(self, segments: Optional[Sequence[Tuple[int, int, Optional[str]]]]) -> None:
+        """Route the rows of the next step(s): ``[(first row, end row, adapter name or None), ...]``; ``None`` returns to
+        the single active adapter.  Unknown names raise before anything runs."""
+        rows = 0
+        if segments is not None:
+            for r0, r1, name in segments:
+                if name and name not in self.names:
+                    raise KeyError(f"unknown adapter {name!r}; loaded: {self.names}")
+                rows = max(rows, r1)
+            if not any(name for _, _, name in segments):
+                segments = None                      # nobody uses an adapter this step: skip the routing entirely
+        for w in self._wrapped.values():
+            w.segments = list(segments) if segments is not None else None
+            w.segment_rows = rows
 
     def set_active(self, name: Optional[str]) -> None:
         if name is not None and name not in self.names:

@@ -60,6 +60,8 @@ class LLM:
                                  max_pages_per_seq=pages_per_seq, device=self.device)
         self.runner = ModelRunner(self.model, self.kv, self.device, max_num_tokens=max_num_tokens)
         self.runner.vocab_map = self._vocab_map
+        self.lora = None
+        self.runner.lora = None
         eos0 = self.cfg.eos_token_id
         self.guided_vocab = lp.GuidedVocabulary(tokenizer, self.cfg.vocab_size, eos0 if isinstance(eos0, (list, tuple)) else [eos0])
         self.engine = None
@@ -88,6 +90,17 @@ class LLM:
         self._forced = forced_tokens_from_env()
         if enable_in_flight_batching:
             self._start_engine(enable_prefix_cache, scheduling or {})
+
+    # ---- LoRA adapters ------------------------------------------------------------------------------
+    def load_lora(self, name: str, adapter_dir: str) -> None:
+        """Load a processed adapter (``trtedge process-lora``) under ``name``; requests choose it with
+        ``SamplingParams(lora_name=...)`` (``cpp/runtime/state/loraManager`` in the reference: named adapters, switched per
+        request without touching the base weights)."""
+        if self.lora is None:
+            from ..lora.runtime import LoraManager
+            self.lora = LoraManager(self.model)
+            self.runner.lora = self.lora
+        self.lora.load_adapter(name, adapter_dir)
 
     def _load_reduced_vocab(self, model_dir: str):
         """``vocab_map.safetensors`` next to the checkpoint (``trtedge reduce-vocab``): swap in the reduced LM head."""
@@ -141,6 +154,10 @@ class LLM:
             r.logit_bias_values = [float(v) for v in sp.logit_bias.values()]
         if sp.guided is not None:
             r.guided_type, r.guided_spec = lp.guided_to_wire(sp.guided)
+        if sp.lora_name:
+            if self.lora is None or sp.lora_name not in self.lora.names:
+                raise ValueError(f"unknown LoRA adapter {sp.lora_name!r}")
+            r.lora_name = sp.lora_name
         r.cache_lookup = bool(sp.context_cache_lookup)
         try:
             r.cache_commit = {"none": 0, "prefill_state_only": 1, "including_generated_tokens": 2}[sp.context_cache_commit]
@@ -325,6 +342,11 @@ class LLM:
                               t1 - t0, t2 - t1, reports[i] or None) for i in range(n)]
 
     def _generate_batch(self, ids: List[List[int]], sp: SamplingParams) -> List[RequestOutput]:
+        if self.lora is not None:                      # static batch: one adapter (or none) for every row
+            if sp.lora_name and sp.lora_name not in self.lora.names:
+                raise ValueError(f"unknown LoRA adapter {sp.lora_name!r}")
+            self.lora.set_segments(None)
+            self.lora.set_active(sp.lora_name)
         if sp.needs_logits_processing:
             return self._generate_processed([p.tolist() for p in ids] if isinstance(ids, torch.Tensor) else ids, sp)
         if self.spec_decoder is not None and sp.temperature < 1e-3 and not isinstance(ids, torch.Tensor):

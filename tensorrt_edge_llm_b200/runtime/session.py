@@ -205,6 +205,13 @@ class ModelSession(rt.RuntimeSession):
             seats.append(s.slot)
             token_lists.append(toks)
             producers.append(produces)
+        lora = getattr(self.runner, "lora", None)
+        if lora is not None:                               # requests of one step may use different adapters
+            segs, r0 = [], 0
+            for slot, toks in zip(seats, token_lists):
+                segs.append((r0, r0 + len(toks), self.seqs[slot].req.lora_name or None))
+                r0 += len(toks)
+            lora.set_segments(segs)
         logits = self.runner.step(seats, token_lists)      # one row per sequence (its last token)
         rows = [i for i, p in enumerate(producers) if p]
         out = rt.StepResult()

@@ -264,3 +264,35 @@ def test_request_file_parsing_and_run():
     assert res[0]["output_tokens"] == 5 and len(res[0]["logprobs"]) == 5 and len(res[0]["logprobs"][0]["top"]) == 2
     assert res[1]["output_text"] in ("a", "cd") and "logprobs" not in res[1]             # "ab" is cut at the stop string
     llm.close()
+
+
+def test_lora_per_request_under_in_flight_batching(ckpt, tmp_path):
+    """Requests of one batch choose different adapters (or none); each gets the tokens of a run with only its adapter."""
+    from tensorrt_edge_llm_b200.runtime.llm import LLM, SamplingParams
+    a1, a2, r1, r2 = (str(tmp_path / n) for n in ("a1", "a2", "r1", "r2"))
+    _adapter(a1, r=4, alpha=64.0)
+    torch.manual_seed(77)
+    _adapter(a2, r=2, alpha=64.0)
+    assert trtedge(["process-lora", "--input_dir", a1, "--output_dir", r1, "--dtype", "bfloat16"]) == 0
+    assert trtedge(["process-lora", "--input_dir", a2, "--output_dir", r2, "--dtype", "bfloat16"]) == 0
+    prompts = [[5, 9, 33, 70, 12], [8, 2, 44, 19], [7, 7, 3, 50, 61, 4]]
+    kw = dict(max_batch_size=3, max_kv_cache_capacity=128, page_size=16, device="cpu")
+
+    def solo(name):
+        llm = LLM(ckpt, **kw)
+        llm.load_lora("one", r1)
+        llm.load_lora("two", r2)
+        outs = [o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=6, lora_name=name, ignore_eos=True))]
+        llm.close()
+        return outs
+    base, one, two = solo(None), solo("one"), solo("two")
+    assert base != one and base != two and one != two
+    ifb = LLM(ckpt, enable_in_flight_batching=True, **kw)
+    ifb.load_lora("one", r1)
+    ifb.load_lora("two", r2)
+    hs = [ifb.submit(p, SamplingParams(max_tokens=6, lora_name=n, ignore_eos=True)) for p, n in zip(prompts, ("one", None, "two"))]
+    got = [h.get(60.0) for h in hs]
+    assert got == [one[0], base[1], two[2]]
+    with pytest.raises(ValueError):
+        ifb.submit(prompts[0], SamplingParams(max_tokens=2, lora_name="three"))
+    ifb.close()
