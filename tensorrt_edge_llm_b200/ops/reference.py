@@ -615,6 +615,75 @@ def spec_accept_greedy(target_tokens: torch.Tensor, tree_tokens: torch.Tensor, p
     return path, plen, bonus
 
 
+def sampling_probs(logits: torch.Tensor, temperature: float, top_k: int = 0, top_p: float = 1.0) -> torch.Tensor:
+    """The distribution the sampler draws from: softmax(logits / T) restricted to the top-k tokens and the smallest
+    top-p nucleus, renormalised (fp32, ``[rows, V]``)."""
+    x = logits.float() / max(float(temperature), 1e-6)
+    if top_k and top_k < x.shape[-1]:
+        kth = x.topk(top_k, dim=-1).values[..., -1:]
+        x = x.masked_fill(x < kth, float("-inf"))
+    p = torch.softmax(x, dim=-1)
+    if top_p < 1.0:
+        sp, si = p.sort(dim=-1, descending=True)
+        keep = (sp.cumsum(-1) - sp) < top_p                   # a token stays while the mass before it is below top_p
+        sp = sp * keep
+        p = torch.zeros_like(p).scatter_(-1, si, sp)
+        p = p / p.sum(-1, keepdim=True)
+    return p
+
+
+def spec_accept_sampling(target_probs: torch.Tensor, tree_tokens: torch.Tensor, parents: torch.Tensor, max_path: int,
+                         uniforms: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Lossless tree acceptance for sampled requests (``cpp/kernels/speculative/speculativeSamplingKernels.cu`` in the
+    reference).  The draft's children of a node are fixed candidates, i.e. point-mass proposals: candidate ``c`` is
+    accepted with probability ``p(c)`` under the node's current target distribution ``p``; on rejection ``c`` is removed
+    from ``p`` and ``p`` renormalised (the residual distribution), and the next sibling is tried.  When no child is
+    accepted — or the node is a leaf — the bonus token is drawn from what is left of ``p``.  Every emitted token is then
+    distributed exactly as if it had been sampled from the target alone.
+
+    ``target_probs [B, N, V]`` (see :func:`sampling_probs`), ``uniforms [B, max_path, K+1]`` in [0, 1): one per sibling
+    trial and one for the bonus draw at each depth.  Returns ``(path, path_len, bonus)`` like the greedy form."""
+    b, n = tree_tokens.shape
+    dev = tree_tokens.device
+    path = torch.zeros(b, max_path, dtype=torch.int32, device=dev)
+    plen = torch.ones(b, dtype=torch.int32, device=dev)
+    bonus = torch.zeros(b, dtype=torch.int32, device=dev)
+    par = parents.tolist()
+    tok = tree_tokens.tolist()
+    u = uniforms.tolist()
+    for i in range(b):
+        cur, ln = 0, 1
+        while True:
+            p = target_probs[i, cur].double().clone()
+            depth = ln - 1
+            nxt = -1
+            if ln < max_path:
+                trial = 0
+                for c in range(cur + 1, n):
+                    if par[i][c] != cur:
+                        continue
+                    mass = float(p.sum())
+                    pc = float(p[tok[i][c]]) / mass if mass > 0 else 0.0
+                    if u[i][depth][min(trial, len(u[i][depth]) - 2)] < pc:
+                        nxt = c
+                        break
+                    p[tok[i][c]] = 0.0                          # rejected: the residual excludes this candidate
+                    trial += 1
+            if nxt < 0:
+                mass = float(p.sum())
+                if mass <= 0:                                   # every token with mass was a rejected candidate (numerically)
+                    p = target_probs[i, cur].double()
+                    mass = float(p.sum())
+                cdf = (p / mass).cumsum(0)
+                bonus[i] = int(torch.searchsorted(cdf, torch.tensor(u[i][depth][-1], dtype=torch.float64)).clamp(max=p.numel() - 1))
+                break
+            cur = nxt
+            path[i, ln] = cur
+            ln += 1
+        plen[i] = ln
+    return path, plen, bonus
+
+
 def kv_commit_path(pool: torch.Tensor, page_table: torch.Tensor, past_len: torch.Tensor, path: torch.Tensor,
                    path_len: torch.Tensor) -> None:
     """Compact the accepted path in the paged cache ``pool [L, pages, 2, Hkv, P, D]``: the entry at

@@ -264,7 +264,8 @@ class LLM:
         eos_id = None if sp.ignore_eos else (eos[0] if isinstance(eos, (list, tuple)) and eos else eos)
         r0, e0, d0 = dec.stats.rounds, dec.stats.emitted, dec.stats.draft_forwards
         t0 = time.perf_counter()
-        toks = dec.generate(seats, [list(map(int, p)) for p in ids], sp.max_tokens, eos_id)
+        sampling = None if sp.temperature < 1e-3 else {"temperature": sp.temperature, "top_k": sp.top_k, "top_p": sp.top_p, "seed": sp.seed}
+        toks = dec.generate(seats, [list(map(int, p)) for p in ids], sp.max_tokens, eos_id, sampling=sampling)
         t1 = time.perf_counter()
         rounds = dec.stats.rounds - r0
         stats = {"verify_rounds": rounds, "draft_forwards": dec.stats.draft_forwards - d0,
@@ -349,7 +350,7 @@ class LLM:
             self.lora.set_active(sp.lora_name)
         if sp.needs_logits_processing:
             return self._generate_processed([p.tolist() for p in ids] if isinstance(ids, torch.Tensor) else ids, sp)
-        if self.spec_decoder is not None and sp.temperature < 1e-3 and not isinstance(ids, torch.Tensor):
+        if self.spec_decoder is not None and not isinstance(ids, torch.Tensor) and (sp.temperature < 1e-3 or not self.cfg.is_hybrid):
             return self._generate_speculative(ids, sp)
         n = len(ids)
         seats = list(range(n))

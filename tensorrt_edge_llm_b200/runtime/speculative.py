@@ -93,6 +93,8 @@ class EagleDecoder:
         self.device = runner.device
         self.stats = SpecStats()
         self._force_gen = None
+        self.sampling: Optional[dict] = None       # {"temperature", "top_k", "top_p", "seed"} for sampled requests, None = greedy
+        self._sample_gen = None
         # per seat: pending root token, draft log-probs and hidden after the last accepted token
         self.root: Dict[int, int] = {}
         self.lp: Dict[int, torch.Tensor] = {}
@@ -135,7 +137,13 @@ class EagleDecoder:
         for s, q in zip(seats, q_lens):
             self.r.kv.commit(s, q)
         ends = torch.tensor(q_lens).cumsum(0) - 1
-        first = ops.argmax(logits.index_select(0, ends.to(self.device))).tolist()
+        last = logits.index_select(0, ends.to(self.device))
+        if self.sampling is None:
+            first = ops.argmax(last).tolist()
+        else:                                   # sampled request: the first token is a draw from the target distribution too
+            pr = ops.ref.sampling_probs(last, self.sampling["temperature"], self.sampling["top_k"], self.sampling["top_p"])
+            u = self._uniforms(len(seats), 1, 1)[:, 0, 0].to(pr.device)
+            first = torch.searchsorted(pr.double().cumsum(-1), u.double()[:, None]).clamp(max=pr.shape[-1] - 1)[:, 0].tolist()
         # draft row i pairs the target feature of position i with the token of position i + 1
         nxt = flat.clone()
         nxt[:-1] = flat[1:]
@@ -228,7 +236,16 @@ class EagleDecoder:
         stage = timer.begin(prof.SPEC_ACCEPT, batch=b)
         # ---- accept, commit KV ----
         max_path = steps + 1
-        path, plen, bonus = ops.spec_accept_greedy(tgt, tree_tok.to(torch.int32), tree_par.to(torch.int32), max_path, self._forced(b))
+        if self.sampling is None:
+            path, plen, bonus = ops.spec_accept_greedy(tgt, tree_tok.to(torch.int32), tree_par.to(torch.int32), max_path, self._forced(b))
+        else:
+            # lossless for sampled requests: sibling-by-sibling rejection against the target distribution of each node,
+            # bonus token from the residual (see ops.reference.spec_accept_sampling)
+            sm = self.sampling
+            probs = ops.ref.sampling_probs(logits, sm["temperature"], sm["top_k"], sm["top_p"]).view(b, nn_, -1)
+            path, plen, bonus = ops.ref.spec_accept_sampling(probs, tree_tok.to(torch.int32), tree_par.to(torch.int32), max_path,
+                                                              self._uniforms(b, max_path, k + 1))
+            path, plen, bonus = path.to(dev), plen.to(dev), bonus.to(dev)
         past_t = torch.tensor(lt, dtype=torch.int32, device=dev)
         ops.kv_commit_path(self.r.kv.pool, self.r.kv.table_rows(seats).to(dev), past_t, path, plen)
         path_h, plen_h, bonus_h = path.tolist(), plen.tolist(), bonus.tolist()   # the round's one device→host read
@@ -268,6 +285,12 @@ class EagleDecoder:
         self.stats.rounds += b
         self.stats.emitted += sum(len(e) for e in out)
         return out
+
+    def _uniforms(self, b: int, depth: int, width: int) -> torch.Tensor:
+        """Seeded uniforms of the sampled-acceptance path (one generator per decoder, advanced every call)."""
+        if self._sample_gen is None:
+            self._sample_gen = torch.Generator().manual_seed(int((self.sampling or {}).get("seed", 0)))
+        return torch.rand(b, depth, width, generator=self._sample_gen)
 
     def _forced(self, b: int):
         """Forced accept lengths of this round: a constant, or draws in ``1..draft_steps+1`` from a seeded
@@ -313,7 +336,13 @@ class EagleDecoder:
     # ---- whole-request driver -----------------------------------------------------------------
     @torch.no_grad()
     def generate(self, seats: Sequence[int], prompts: Sequence[Sequence[int]], max_new_tokens: int,
-                 eos_token_id: Optional[int] = None) -> List[List[int]]:
+                 eos_token_id: Optional[int] = None, sampling: Optional[dict] = None) -> List[List[int]]:
+        """``sampling`` = ``{"temperature", "top_k", "top_p", "seed"}`` switches the verification from greedy matching to
+        rejection sampling; the emitted tokens are then distributed as plain sampling from the target would be."""
+        if sampling is not None and self.hybrid:
+            raise NotImplementedError("sampled speculative decoding on hybrid targets is not built")
+        self.sampling = dict(sampling) if sampling is not None and sampling.get("temperature", 0.0) >= 1e-3 else None
+        self._sample_gen = None
         first = self.prefill(seats, prompts)
         outs = [[t] for t in first]
         active = [i for i in range(len(seats)) if not (eos_token_id is not None and first[i] == eos_token_id) and max_new_tokens > 1]

@@ -205,3 +205,64 @@ def test_hybrid_target_chain_verify_with_state_replay():
     # forced partial acceptance exercises restore + replay on every round and still matches
     dec = _decoder(model, _OracleDraft(draft, streams), SpecConfig(draft_steps=3, top_k=1, verify_tokens=4, force_accept_len=2))
     assert dec.generate([0, 1], prompts, 14) == want and dec.stats.replays >= 10
+
+
+def test_sampled_acceptance_reference_follows_the_target_distribution():
+    torch.manual_seed(0)
+    v = 8
+    p_root = torch.tensor([0.3, 0.05, 0.2, 0.1, 0.15, 0.05, 0.1, 0.05])
+    probs = torch.zeros(1, 4, v)
+    probs[0, 0] = p_root
+    probs[0, 1:] = torch.softmax(torch.randn(3, v), -1)
+    tree, par = torch.tensor([[7, 0, 2, 5]]), torch.tensor([[-1, 0, 0, 0]])
+    n = 6000
+    u = torch.rand(n, 1, 2, 4, generator=torch.Generator().manual_seed(1))
+    cnt, accepted = torch.zeros(v), 0
+    for k in range(n):
+        path, plen, bonus = ref.spec_accept_sampling(probs, tree, par, 2, u[k])
+        accepted += int(plen[0] > 1)
+        cnt[int(tree[0, path[0, 1]]) if plen[0] > 1 else int(bonus[0])] += 1
+    assert (cnt / n - p_root).abs().max() < 0.02
+    assert abs(accepted / n - float(p_root[[0, 2, 5]].sum())) < 0.03           # a child is accepted exactly when its token is drawn
+    pr = ref.sampling_probs(torch.tensor([[2.0, 1.0, 0.0, -1.0]]), 1.0, top_k=2)
+    assert pr[0, 2:].sum() == 0 and abs(float(pr[0, 0]) - 0.7311) < 1e-3
+    pr = ref.sampling_probs(torch.tensor([[2.0, 1.0, 0.0, -1.0]]), 1.0, top_p=0.7)
+    assert pr[0, 2:].sum() == 0 and abs(float(pr.sum()) - 1) < 1e-6
+
+
+def test_sampled_speculative_decoding_matches_plain_sampling_in_distribution():
+    """Second emitted token over many seeds: its empirical distribution is the exact marginal of the target model."""
+    cfg = tiny_llama_config(num_hidden_layers=2, dtype="float32", vocab_size=16, hidden_size=64, intermediate_size=128,
+                            num_attention_heads=2, num_key_value_heads=1, head_dim=32)
+    model = AutoModel.from_config(cfg, random_init=5)
+    with torch.no_grad():
+        model.lm_head.weight.mul_(8.0)                        # sharpen the distribution so that tokens differ in mass
+    dcfg = tiny_llama_config(num_hidden_layers=1, dtype="float32", vocab_size=16, hidden_size=64, intermediate_size=128,
+                             num_attention_heads=2, num_key_value_heads=1, head_dim=32)
+    dcfg.draft_type, dcfg.eagle3_target_hidden_size = "eagle3", 64
+    draft = AutoModel.from_config(dcfg, random_init=6)
+    prompt = [3, 7, 1, 12, 5]
+    temp = 0.9
+    # exact marginal of the second token
+    kv = KVCacheManager(cfg, num_pages=16, page_size=16, max_seats=1, max_pages_per_seq=4)
+    r = ModelRunner(model, kv)
+    p1 = ref.sampling_probs(r.prefill([0], [prompt]), temp)[0]
+    exact = torch.zeros(16)
+    for t1 in range(16):
+        if p1[t1] < 1e-6:
+            continue
+        kv.free(0)
+        r.prefill([0], [prompt])
+        exact += p1[t1] * ref.sampling_probs(r.step([0], [[t1]]), temp)[0]
+    dec = _decoder(model, draft, SpecConfig(draft_steps=2, top_k=3, verify_tokens=8))
+    n = 700
+    c1, c2 = torch.zeros(16), torch.zeros(16)
+    for seed in range(n):
+        dec.release([0])
+        out = dec.generate([0], [prompt], 2, sampling={"temperature": temp, "top_k": 0, "top_p": 1.0, "seed": seed})[0]
+        c1[out[0]] += 1
+        c2[out[1]] += 1
+    tv1 = 0.5 * (c1 / n - p1).abs().sum()
+    tv2 = 0.5 * (c2 / n - exact).abs().sum()
+    assert tv1 < 0.09 and tv2 < 0.09, (float(tv1), float(tv2))
+    assert float(exact.max()) < 0.9                            # the check is not vacuous: mass is spread over several tokens
