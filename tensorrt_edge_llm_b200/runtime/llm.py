@@ -39,7 +39,8 @@ class LLM:
                  max_batch_size: int = 64, max_input_len: int = 2048, max_kv_cache_capacity: int = 2304,
                  page_size: int = 64, max_num_tokens: int = 8192, random_init_seed: Optional[int] = 0,
                  tokenizer=None, kv_pages: Optional[int] = None, enable_in_flight_batching: bool = False,
-                 enable_prefix_cache: bool = False, scheduling: Optional[dict] = None, draft_model=None, speculative=None):
+                 enable_prefix_cache: bool = False, scheduling: Optional[dict] = None, draft_model=None, speculative=None,
+                 context_cache_max_records: int = 4096, context_cache_max_snapshots: int = 64):
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.device = torch.device(device)
@@ -89,6 +90,7 @@ class LLM:
             self.runner.use_cuda_graphs = False        # hooks do not run inside a replayed graph
         self._forced = forced_tokens_from_env()
         if enable_in_flight_batching:
+            self._cache_limits = (int(context_cache_max_records), int(context_cache_max_snapshots) or 64)
             self._start_engine(enable_prefix_cache, scheduling or {})
 
     # ---- LoRA adapters ------------------------------------------------------------------------------
@@ -140,7 +142,8 @@ class LLM:
         cfg.scheduling = opts
         self._rt = rt
         self.engine = rt.RequestEngine(cfg, lambda: ModelSession(self.runner, eos_ids, enable_prefix_cache, self.max_input_len,
-                                                                 self.guided_vocab))
+                                                                 self.guided_vocab, max_snapshots=self._cache_limits[1],
+                                                                 max_records=self._cache_limits[0]))
 
     def _native_request(self, ids, sp: SamplingParams, priority: int = 0):
         r = self._rt.GenerationRequest()

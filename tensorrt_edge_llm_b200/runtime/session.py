@@ -39,7 +39,7 @@ class _Seq:
 
 class ModelSession(rt.RuntimeSession):
     def __init__(self, runner: ModelRunner, eos_ids=(), enable_prefix_cache: bool = False, max_input_len: int = 2048,
-                 guided_vocab=None, max_snapshots: int = 64):
+                 guided_vocab=None, max_snapshots: int = 64, max_records: int = 4096):
         super().__init__()
         self.runner = runner
         self.guided_vocab = guided_vocab
@@ -49,7 +49,7 @@ class ModelSession(rt.RuntimeSession):
         self.slots = rt.ResidentSlotPool(self.kv.max_seats)
         self.seqs: Dict[int, _Seq] = {}
         # retired sliding-window pages cannot be shared, so bounded storage and the prefix cache exclude each other
-        self.prefix = rt.PrefixCache(self.kv.native.allocator(), self.kv.page_size, 4096) if (
+        self.prefix = rt.PrefixCache(self.kv.native.allocator(), self.kv.page_size, max_records) if (
             enable_prefix_cache and getattr(self.kv, "native", None) is not None and not self.kv.bounded_swa) else None
         self._swa_bound = self.kv.swa_live_pages_bound(runner.max_num_tokens) if self.kv.bounded_swa else 0
         # Hybrid models: shared KV pages alone do not restore a prefix, the recurrent rows at that boundary are needed

@@ -32,7 +32,8 @@ def build_llm(cfg: ServerConfig):
     llm = LLM(m.model, device=m.device or None, **spec_kw, max_batch_size=m.max_batch_size, max_input_len=m.max_input_len,
               max_kv_cache_capacity=m.max_kv_cache_capacity, page_size=m.kv_page_size, max_num_tokens=m.max_num_tokens or 8192,
               tokenizer=tok, enable_in_flight_batching=m.enable_in_flight_batching,
-              enable_prefix_cache=m.context_cache_config.enabled, scheduling=m.scheduling_dict() if m.enable_in_flight_batching else None)
+              enable_prefix_cache=m.context_cache_config.enabled, context_cache_max_records=m.context_cache_config.max_records,
+              context_cache_max_snapshots=m.context_cache_config.max_snapshots, scheduling=m.scheduling_dict() if m.enable_in_flight_batching else None)
     return llm, ChatTemplate.load(m.model)
 
 
