@@ -228,3 +228,39 @@ def encode_data_parallel(encoder, inputs: torch.Tensor, comm) -> torch.Tensor:
     full = comm.all_gather_rows(mine.contiguous())                # rank-major = input order
     rows_per_item = mine.shape[0] // per
     return full[:n * rows_per_item]
+
+
+def dart_prune(embeds: torch.Tensor, keep: int, num_pivots: int = 8) -> torch.Tensor:
+    """Duplication-aware visual-token pruning (the DART pruner of ``cpp/runtime/preprocess/`` / ``cpp/kernels/dart`` in
+    the reference): a few pivot rows are chosen — those with the largest norm, spread over the image — and the rows most
+    similar (cosine) to any pivot are dropped as duplicates until ``keep`` rows remain.  Returns the sorted indices of
+    the rows to keep; pivots always survive."""
+    n = embeds.shape[0]
+    if keep >= n:
+        return torch.arange(n, device=embeds.device)
+    x = torch.nn.functional.normalize(embeds.float(), dim=-1)
+    num_pivots = max(1, min(num_pivots, keep))
+    # one pivot per contiguous stripe of the image (its highest-norm row), so pivots do not cluster in one corner
+    norms = embeds.float().norm(dim=-1)
+    bounds = torch.linspace(0, n, num_pivots + 1).long()
+    pivots = torch.stack([bounds[i] + norms[bounds[i]:bounds[i + 1]].argmax() for i in range(num_pivots) if bounds[i + 1] > bounds[i]])
+    sim = (x @ x[pivots].t()).amax(dim=-1)                      # closeness of every row to its nearest pivot
+    sim[pivots] = -2.0                                          # pivots are kept unconditionally
+    order = sim.argsort()                                       # least redundant first
+    return order[:keep].sort().values
+
+
+def sample_video_frames(num_frames: int, video_fps: float, target_fps: float = 2.0, min_frames: int = 4, max_frames: int = 768,
+                        multiple_of: int = 2) -> List[int]:
+    """Frame indices to decode from a video (``tensorrt_edgellm/server/media/video_sampling.py``): about ``target_fps``
+    frames per second, clamped to ``[min_frames, max_frames]`` and rounded to ``multiple_of`` (temporal patching pairs
+    frames), spread evenly over the clip."""
+    if num_frames <= 0 or video_fps <= 0:
+        raise ValueError("a video needs frames and a frame rate")
+    want = num_frames / video_fps * target_fps
+    want = min(max(want, min_frames), max_frames, num_frames)
+    want = max(multiple_of, int(want // multiple_of) * multiple_of)
+    want = min(want, num_frames - num_frames % multiple_of if num_frames >= multiple_of else num_frames)
+    if want <= 1:
+        return [0]
+    return [int(round(i * (num_frames - 1) / (want - 1))) for i in range(want)]

@@ -98,3 +98,23 @@ def test_encoder_cache_and_data_parallel_shards():
         return enc(patches[idx])
     out = encode_data_parallel(enc, patches, FakeComm(0, [None, None]))
     assert out.shape == want.shape and torch.allclose(out, want, atol=1e-6)
+
+
+def test_dart_pruning_and_video_frame_sampling():
+    from tensorrt_edge_llm_b200.models.vit import dart_prune, sample_video_frames
+    g = torch.Generator().manual_seed(0)
+    base = torch.randn(12, 32, generator=g)
+    # 12 distinct rows, then 20 near-copies of row 3 (the row with the largest norm, hence a pivot)
+    base[3] *= 4
+    rows = torch.cat([base, base[3:4].repeat(20, 1) + 0.01 * torch.randn(20, 32, generator=g)])
+    keep = dart_prune(rows, keep=14, num_pivots=2)
+    kept = set(keep.tolist())
+    assert keep.numel() == 14 and torch.equal(keep, keep.sort().values)
+    family = {3} | set(range(12, 32))                           # 21 near-identical rows: only the pivots among them survive
+    assert len(kept & family) == 3 and kept >= set(range(12)) - {3}
+    assert torch.equal(dart_prune(rows, keep=100), torch.arange(32))
+    idx = sample_video_frames(num_frames=300, video_fps=30.0, target_fps=2.0)
+    assert len(idx) == 20 and idx[0] == 0 and idx[-1] == 299 and idx == sorted(idx)
+    assert len(sample_video_frames(30, 30.0)) == 4              # short clip: the minimum
+    assert len(sample_video_frames(100000, 25.0, max_frames=64)) == 64
+    assert sample_video_frames(3, 30.0) == [0, 2]
