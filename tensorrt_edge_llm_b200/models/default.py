@@ -151,6 +151,12 @@ class Transformer(nn.Module):
             comm.rs_enabled = False          # tapping hidden states needs the whole residual stream on every rank
         for i, layer in enumerate(self.layers):
             h, residual = layer(h, residual, meta, kv_cache[i], cos_sin, comm)
+            if meta.deepstack is not None and i in meta.deepstack:
+                # deepstack binding (``cpp/runtime/features/deepstackBinding.cpp`` in the reference): the hidden state of a
+                # row is h + residual here, so adding the level's features to h adds them to the stream
+                rows, feats = meta.deepstack[i]
+                h = h.index_add(0, rows.to(h.device), (feats.to(h.device, h.dtype) / comm.world_size) if comm.world_size > 1
+                                else feats.to(h.device, h.dtype))
             if i in capture_layers:
                 taps.append((h.float() + residual.float()).to(h.dtype) if comm.world_size == 1
                             else comm.all_reduce(h).add_(residual))

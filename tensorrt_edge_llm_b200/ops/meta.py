@@ -40,6 +40,9 @@ class StepMeta:
     kv_offsets: Optional[torch.Tensor] = None
     # Multimodal RoPE: temporal / height / width position of each row, int32 [3, T].  The model turns them into
     # per-row cos / sin rows (`rope_rows` [T, D], looked up with `rope_pos` = 0..T-1) before its layers run.
+    # Deepstack (Qwen3-VL): {layer index: (row indices int64 [M], features [M, H])} — vision features of intermediate
+    # encoder levels that are added to the hidden state of the image rows after the given decoder layers.
+    deepstack: Optional[dict] = None
     positions3: Optional[torch.Tensor] = None
     rope_rows: Optional[torch.Tensor] = None
     rope_pos: Optional[torch.Tensor] = None
@@ -51,6 +54,8 @@ class StepMeta:
     def to(self, device) -> "StepMeta":
         kw = {}
         for k, v in self.__dict__.items():
+            if isinstance(v, dict):
+                v = {kk: tuple(t.to(device, non_blocking=True) for t in vv) for kk, vv in v.items()}
             kw[k] = v.to(device, non_blocking=True) if isinstance(v, torch.Tensor) else v
         return StepMeta(**kw)
 

@@ -138,7 +138,7 @@ class ModelRunner:
 
     @torch.no_grad()
     def prefill_embeds(self, seats: Sequence[int], embeds: Sequence[torch.Tensor], positions3: Optional[Sequence[torch.Tensor]] = None,
-                       rope_deltas: Optional[Sequence[int]] = None) -> torch.Tensor:
+                       rope_deltas: Optional[Sequence[int]] = None, deepstack: Optional[dict] = None) -> torch.Tensor:
         """Prefill from embedding rows instead of token ids (multimodal prompts: text rows with the image / audio
         rows already merged in).  One step; returns last-row logits ``[N, V]``.
 
@@ -146,6 +146,9 @@ class ModelRunner:
         multimodal RoPE; ``rope_deltas`` are remembered per seat and added to the position of every later decode row."""
         q_lens = [int(e.shape[0]) for e in embeds]
         meta = self._meta(seats, q_lens)
+        if deepstack:
+            # {layer: (row indices into the packed step, features)}: intermediate vision levels joining the early layers
+            meta.deepstack = {int(k): (torch.as_tensor(r, dtype=torch.int64, device=self.device), f.to(self.device)) for k, (r, f) in deepstack.items()}
         if positions3 is not None:
             meta.positions3 = torch.cat([p.to(torch.int32) for p in positions3], dim=1).to(self.device)
             for s, d in zip(seats, rope_deltas or [0] * len(seats)):

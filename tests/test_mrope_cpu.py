@@ -99,3 +99,35 @@ def test_rope_scalings_match_hf():
     inv_s, att_s = ROPE_INIT_FUNCTIONS["longrope"](cfg, "cpu", seq_len=32)
     got_s = ref.rope_cos_sin(64, d, theta, sc)
     assert (got_s - table(inv_s, att_s, 64)).abs().max() < 1e-4
+
+
+def test_deepstack_features_join_the_early_layers():
+    """Adding level features after layer k equals running the layers by hand with the addition in between."""
+    cfg = tiny_llama_config(num_hidden_layers=3, vocab_size=300)
+    model = AutoModel.from_config(cfg, random_init=0)
+    kv = KVCacheManager(cfg, num_pages=8, page_size=16, max_seats=2, max_pages_per_seq=4)
+    r = ModelRunner(model, kv)
+    ids = [3, 4, 9, 9, 9, 5, 6]
+    emb = r.embed_tokens(ids)
+    base = r.prefill_embeds([0], [emb])
+    g = torch.Generator().manual_seed(2)
+    f0, f1 = torch.randn(3, cfg.hidden_size, generator=g) * 0.5, torch.randn(3, cfg.hidden_size, generator=g) * 0.5
+    rows = [2, 3, 4]
+    kv.free(0)
+    got = r.prefill_embeds([0], [emb], deepstack={0: (rows, f0), 1: (rows, f1)})
+    assert (got - base).abs().max() > 1e-3
+    # by hand
+    from tensorrt_edge_llm_b200 import ops
+    kv.free(0)
+    meta = r._meta([0], [len(ids)])
+    cs = model.cos_sin("cpu")
+    h, res = emb.clone(), None
+    for i, layer in enumerate(model.model.layers):
+        h, res = layer(h, res, meta, kv.pool[i], cs, model.comm)
+        if i == 0:
+            h[rows] += f0
+        if i == 1:
+            h[rows] += f1
+    x, _ = ops.add_rmsnorm(h, res, model.model.norm.weight, model.model.norm.eps)
+    want = model.logits_from_hidden(x, meta)
+    assert torch.allclose(got, want, atol=1e-5)
