@@ -93,6 +93,8 @@ def gelu(x, tanh_approx=False):
 
 
 def embedding(ids, table):
+    if hasattr(table, "lookup"):              # FP8 / NVFP4 table (models/embedding.py): gather stored rows, then expand
+        return table.lookup(ids)
     if table.is_cuda:
         return cuda_ops().embedding(ids, table)
     return ref.embedding(ids, table)

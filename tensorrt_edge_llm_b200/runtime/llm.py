@@ -40,7 +40,8 @@ class LLM:
                  page_size: int = 64, max_num_tokens: int = 8192, random_init_seed: Optional[int] = 0,
                  tokenizer=None, kv_pages: Optional[int] = None, enable_in_flight_batching: bool = False,
                  enable_prefix_cache: bool = False, scheduling: Optional[dict] = None, draft_model=None, speculative=None,
-                 context_cache_max_records: int = 4096, context_cache_max_snapshots: int = 64):
+                 context_cache_max_records: int = 4096, context_cache_max_snapshots: int = 64,
+                 embedding_quantization: Optional[str] = None):
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.device = torch.device(device)
@@ -49,6 +50,9 @@ class LLM:
         else:
             self.model = AutoModel.from_pretrained(model, comm=comm, device=self.device)
         self.cfg = self.model.cfg
+        if embedding_quantization:                  # "fp8" | "nvfp4": the token table is stored quantised, rows expand on lookup
+            from ..models.embedding import quantize_embedding
+            quantize_embedding(self.model, embedding_quantization)
         self.tokenizer = tokenizer
         self._vocab_map = None
         if isinstance(model, str):

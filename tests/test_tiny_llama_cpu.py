@@ -84,3 +84,29 @@ def test_decode_greedy_matches_stepwise(ckpt):
     for i in range(8):
         t = r2.step([0, 1], [[int(x)] for x in t]).argmax(-1)
         assert torch.equal(t.to(torch.int32), out[:, i])
+
+
+def test_quantized_embedding_tables():
+    import torch
+    from tensorrt_edge_llm_b200.config import tiny_llama_config
+    from tensorrt_edge_llm_b200.models.embedding import QuantizedEmbedding
+    from tensorrt_edge_llm_b200.runtime.llm import LLM, SamplingParams
+    w = torch.randn(500, 64, generator=torch.Generator().manual_seed(0)) * 0.05
+    ids = torch.tensor([3, 499, 0, 3], dtype=torch.int32)
+    for fmt, tol, ratio in (("fp8", 0.07, 0.6), ("nvfp4", 0.2, 0.35)):
+        q = QuantizedEmbedding.from_dense(w, fmt)
+        got = q(ids)
+        assert got.shape == (4, 64) and (got - w[ids.long()]).abs().max() < tol * w.abs().max()
+        assert torch.equal(got[0], got[3]) and q.table_bytes() < ratio * w.numel() * 4
+    cfg = tiny_llama_config(num_hidden_layers=2)
+    prompts = [[5, 9, 33, 70], [8, 2, 44]]
+    sp = SamplingParams(max_tokens=5)
+    dense = LLM(cfg, device="cpu", max_batch_size=2, max_kv_cache_capacity=128)
+    ref_logits = dense.runner.prefill([0], [prompts[0]]).float()
+    dense.kv.free(0)
+    q8 = LLM(cfg, device="cpu", max_batch_size=2, max_kv_cache_capacity=128, embedding_quantization="fp8")
+    assert type(q8.model.model.embed_tokens).__name__ == "QuantizedEmbedding"
+    lg = q8.runner.prefill([0], [prompts[0]]).float()
+    q8.kv.free(0)
+    cos = torch.nn.functional.cosine_similarity(lg.flatten(), ref_logits.flatten(), dim=0)
+    assert float(cos) > 0.99 and len(q8.generate(prompts, sp)[1].token_ids) == 5
