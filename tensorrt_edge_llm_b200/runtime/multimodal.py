@@ -1,0 +1,146 @@
+"""Multimodal runner: images and audio clips become embedding rows that replace placeholder tokens of the prompt.
+
+The contract of the reference's ``cpp/multimodal/`` runners (``MultimodalRunner`` base and its Qwen-VL style children):
+preprocess the media on the host (decode, smart resize, normalise, patchify / log-mel), run the encoder, splice the
+rows into the text embeddings where the placeholder token ids sit, compute multimodal RoPE positions when the decoder
+uses them, prefill from embeddings, then decode as usual.  Encoders run data-parallel over tensor-parallel ranks and
+their outputs are cached by content hash when a cache is given."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..models.vit import EncoderCache, VisionEncoder, dart_prune, encode_data_parallel
+from ..ops import reference as ref
+from . import native as rt
+
+IMAGE_MEAN = (0.48145466, 0.4578275, 0.40821073)
+IMAGE_STD = (0.26862954, 0.26130258, 0.27577711)
+
+
+@dataclass
+class MultimodalInputs:
+    """One request: text pieces and media in the order they appear."""
+    pieces: List[Tuple[str, object]] = field(default_factory=list)      # ("text", token ids) | ("image", Image) | ("audio", (samples, rate))
+
+    def text(self, ids: Sequence[int]) -> "MultimodalInputs":
+        self.pieces.append(("text", [int(t) for t in ids]))
+        return self
+
+    def image(self, image) -> "MultimodalInputs":
+        self.pieces.append(("image", image))
+        return self
+
+    def audio(self, samples, sample_rate: int) -> "MultimodalInputs":
+        self.pieces.append(("audio", (np.asarray(samples, dtype=np.float32), int(sample_rate))))
+        return self
+
+
+class MultimodalRunner:
+    def __init__(self, llm, vision: Optional[VisionEncoder] = None, audio=None, image_token_id: int = 0, audio_token_id: int = 1,
+                 cache_bytes: int = 0, visual_keep_ratio: float = 1.0, min_pixels: int = 0, max_pixels: int = 0):
+        self.llm, self.vision, self.audio = llm, vision, audio
+        self.image_token_id, self.audio_token_id = image_token_id, audio_token_id
+        self.cache = EncoderCache(cache_bytes) if cache_bytes > 0 else None
+        self.keep_ratio = visual_keep_ratio
+        self.min_pixels, self.max_pixels = min_pixels, max_pixels
+        self.device = llm.device
+
+    # ---- media → rows ------------------------------------------------------------------------------------
+    def _image_patches(self, image) -> torch.Tensor:
+        """Decode-side preprocessing: resize to the encoder's square input, normalise, cut into patches ``[1, grid², C·P·P]``."""
+        c = self.vision.cfg
+        if isinstance(image, (bytes, bytearray)):
+            image = rt.parse_image(bytes(image))
+        elif isinstance(image, str):
+            image = rt.load_image(image)
+        elif isinstance(image, np.ndarray):
+            image = rt.image_from_array(np.ascontiguousarray(image, dtype=np.uint8))
+        if (image.width, image.height) != (c.image_size, c.image_size):
+            image = rt.resize_bicubic(image, c.image_size, c.image_size)
+        chw = torch.from_numpy(rt.normalize_chw(image, list(IMAGE_MEAN), list(IMAGE_STD)))
+        return VisionEncoder.patchify(chw[None], c.patch_size)
+
+    def encode_images(self, images: Sequence) -> List[torch.Tensor]:
+        if not images:
+            return []
+        if self.vision is None:
+            raise ValueError("this runner has no vision encoder")
+        patches = torch.cat([self._image_patches(im) for im in images], 0).to(self.device)
+        enc = (lambda x: encode_data_parallel(self.vision, x, self.llm.model.comm))
+        rows = self.cache.encode(enc, patches) if self.cache is not None else enc(patches)
+        per = rows.shape[0] // len(images)
+        out = [rows[i * per:(i + 1) * per] for i in range(len(images))]
+        if self.keep_ratio < 1.0:                        # visual-token pruning: near-duplicate rows of an image are dropped
+            out = [r[dart_prune(r, max(1, int(round(r.shape[0] * self.keep_ratio))))] for r in out]
+        return out
+
+    def encode_audio(self, clips: Sequence[Tuple[np.ndarray, int]]) -> List[torch.Tensor]:
+        if not clips:
+            return []
+        if self.audio is None:
+            raise ValueError("this runner has no audio encoder")
+        from ..models.audio import audio_features
+        c = self.audio.cfg
+        seconds = 2 * c.max_source_positions // 100
+        out = []
+        for samples, rate in clips:
+            mel = audio_features(samples, rate, n_mels=c.n_mels, chunk_seconds=seconds).to(self.device)
+            out.append(self.cache.encode(self.audio, mel) if self.cache is not None else self.audio(mel))
+        return out
+
+    # ---- request → prompt rows ----------------------------------------------------------------------------
+    def build(self, req: MultimodalInputs):
+        """Token ids with placeholder runs, the embedding rows with media spliced in, and (for multimodal-RoPE decoders)
+        the 3-D positions and decode offset."""
+        images = self.encode_images([p for k, p in req.pieces if k == "image"])
+        clips = self.encode_audio([p for k, p in req.pieces if k == "audio"])
+        ids: List[int] = []
+        media_rows: List[torch.Tensor] = []
+        grids = []
+        ii = ai = 0
+        for kind, payload in req.pieces:
+            if kind == "text":
+                ids += payload
+            elif kind == "image":
+                rows = images[ii]
+                ii += 1
+                ids += [self.image_token_id] * rows.shape[0]
+                media_rows.append(rows)
+                side = int(round(rows.shape[0] ** 0.5))
+                grids.append((1, side, side) if side * side == rows.shape[0] else (1, 1, rows.shape[0]))
+            else:
+                rows = clips[ai]
+                ai += 1
+                ids += [self.audio_token_id] * rows.shape[0]
+                media_rows.append(rows)
+        runner = self.llm.runner
+        safe = [t if t not in (self.image_token_id, self.audio_token_id) else 0 for t in ids]
+        emb = runner.embed_tokens(safe).clone()
+        if media_rows:
+            pos = torch.tensor([i for i, t in enumerate(ids) if t in (self.image_token_id, self.audio_token_id)], device=emb.device)
+            emb[pos] = torch.cat(media_rows, 0).to(emb.device, emb.dtype)
+        positions3 = delta = None
+        if self.llm.cfg.mrope_section:
+            # audio runs advance like text; image runs use their (t, h, w) grid (rows are already merged: merge factor 1)
+            img_only = [t if t != self.audio_token_id else -1 for t in ids]
+            positions3, delta = ref.mrope_positions(img_only, self.image_token_id, grids, spatial_merge=1)
+        return ids, emb, positions3, delta
+
+    @torch.no_grad()
+    def generate(self, req: MultimodalInputs, max_tokens: int = 32, seat: int = 0) -> List[int]:
+        ids, emb, positions3, delta = self.build(req)
+        runner, kv = self.llm.runner, self.llm.kv
+        kv.free(seat)
+        kv.reserve(seat, len(ids) + max_tokens)
+        logits = runner.prefill_embeds([seat], [emb], positions3=None if positions3 is None else [positions3],
+                                       rope_deltas=None if positions3 is None else [delta])
+        first = runner.pick(logits)
+        out = [int(first[0])]
+        if max_tokens > 1:
+            out += runner.decode_greedy([seat], first, max_tokens - 1)[0].tolist()
+        kv.free(seat)
+        return out

@@ -1,0 +1,66 @@
+"""Multimodal runner on CPU: image and audio rows spliced into the prompt, multimodal RoPE, encoder cache, pruning."""
+import numpy as np
+import torch
+
+from tensorrt_edge_llm_b200.config import tiny_llama_config
+from tensorrt_edge_llm_b200.models.audio import AudioConfig, AudioEncoder
+from tensorrt_edge_llm_b200.models.vit import VisionConfig, VisionEncoder
+from tensorrt_edge_llm_b200.runtime.llm import LLM
+from tensorrt_edge_llm_b200.runtime.multimodal import MultimodalInputs, MultimodalRunner
+
+
+def _llm(mrope):
+    cfg = tiny_llama_config(num_hidden_layers=2, vocab_size=300, hidden_size=128, intermediate_size=256, num_attention_heads=2,
+                            num_key_value_heads=1, head_dim=64)
+    if mrope:
+        cfg.mrope_section = [8, 12, 12]
+    return LLM(cfg, device="cpu", max_batch_size=1, max_input_len=256, max_kv_cache_capacity=320, page_size=16)
+
+
+def _encoders():
+    v = VisionEncoder(VisionConfig(hidden_size=128, num_hidden_layers=1, num_attention_heads=2, intermediate_size=256, patch_size=4,
+                                   image_size=16, out_hidden_size=128, spatial_merge=2, dtype="float32")).random_init(1, std=0.1)
+    a = AudioEncoder(AudioConfig(n_mels=16, hidden_size=128, num_hidden_layers=1, num_attention_heads=2, intermediate_size=256,
+                                 max_source_positions=50, avg_pool=2, out_hidden_size=128, dtype="float32")).random_init(2)
+    return v, a
+
+
+def test_image_and_audio_rows_replace_placeholders():
+    llm = _llm(mrope=True)
+    v, a = _encoders()
+    mm = MultimodalRunner(llm, v, a, image_token_id=298, audio_token_id=299, cache_bytes=1 << 20)
+    rng = np.random.default_rng(0)
+    img = rng.integers(0, 256, (20, 24, 3), dtype=np.uint8)              # resized to the encoder's 16 x 16 input
+    t = np.arange(16000) / 16000.0
+    req = MultimodalInputs().text([5, 6, 7]).image(img).text([8, 9]).audio(0.3 * np.sin(2 * np.pi * 330 * t), 16000).text([10])
+    ids, emb, pos3, delta = mm.build(req)
+    assert ids.count(298) == 4 and ids.count(299) == 25 and len(ids) == 3 + 4 + 2 + 25 + 1 and emb.shape == (len(ids), 128)
+    text_rows = llm.runner.embed_tokens([5, 6, 7])
+    assert torch.equal(emb[:3], text_rows) and not torch.equal(emb[3], llm.runner.embed_tokens([0])[0])
+    # the 2 x 2 image block shares its temporal position and spans two rows / columns; text after it continues at +2
+    assert pos3[:, 3:7].tolist() == [[3, 3, 3, 3], [3, 3, 4, 4], [3, 4, 3, 4]] and pos3[:, 7].tolist() == [5, 5, 5]
+    assert delta == -2
+    out1 = mm.generate(req, max_tokens=5)
+    assert mm.cache.misses == 2 and len(out1) == 5
+    out2 = mm.generate(req, max_tokens=5)                                 # both encoders are served from the cache
+    assert out2 == out1 and mm.cache.hits >= 2
+    other = MultimodalInputs().text([5, 6, 7]).image(255 - img).text([8, 9]).audio(0.3 * np.sin(2 * np.pi * 330 * t), 16000).text([10])
+    assert not torch.equal(mm.build(other)[1][3:7], emb[3:7])
+    llm.close()
+
+
+def test_pruning_shortens_the_prompt_and_plain_rope_decoders_work():
+    llm = _llm(mrope=False)
+    v, _ = _encoders()
+    v8 = VisionEncoder(VisionConfig(hidden_size=128, num_hidden_layers=1, num_attention_heads=2, intermediate_size=256, patch_size=4,
+                                    image_size=32, out_hidden_size=128, spatial_merge=2, dtype="float32")).random_init(1, std=0.1)
+    img = np.zeros((32, 32, 3), dtype=np.uint8)                           # a flat image: its 16 rows are near-duplicates
+    img[:8, :8] = 255
+    full = MultimodalRunner(llm, v8, image_token_id=298)
+    pruned = MultimodalRunner(llm, v8, image_token_id=298, visual_keep_ratio=0.5)
+    req = MultimodalInputs().text([3, 4]).image(img).text([5])
+    ids_f, _, p3, _ = full.build(req)
+    ids_p, emb_p, _, _ = pruned.build(req)
+    assert ids_f.count(298) == 16 and ids_p.count(298) == 8 and p3 is None and emb_p.shape[0] == len(ids_p)
+    assert len(pruned.generate(req, max_tokens=3)) == 3
+    llm.close()
