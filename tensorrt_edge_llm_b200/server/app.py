@@ -78,6 +78,49 @@ def _guided(body: Dict[str, Any]):
     return None
 
 
+_IMG, _AUD = "\x00IMG\x00", "\x00AUD\x00"
+
+
+def _media_bytes(ref: str) -> bytes:
+    """``data:…;base64,…`` URI, ``file://`` URI or a local path → bytes (no network fetches)."""
+    import base64
+    if ref.startswith("data:"):
+        return base64.b64decode(ref.split(",", 1)[1])
+    if ref.startswith(("http://", "https://")):
+        raise ValueError("remote media URLs are not fetched; send a data: URI or a local path")
+    with open(ref[7:] if ref.startswith("file://") else ref, "rb") as f:
+        return f.read()
+
+
+def _split_media(messages):
+    """Content parts → plain-text messages with markers where media sits, plus the media in order of appearance."""
+    media, flat = [], []
+    for m in messages:
+        c = m.get("content")
+        if not isinstance(c, list):
+            flat.append(m)
+            continue
+        text = ""
+        for part in c:
+            kind = part.get("type")
+            if kind == "text":
+                text += part.get("text", "")
+            elif kind in ("image", "image_url"):
+                src = part.get("image") or (part.get("image_url") or {}).get("url")
+                media.append(("image", _media_bytes(str(src))))
+                text += _IMG
+            elif kind in ("audio", "input_audio", "audio_url"):
+                src = part.get("audio") or (part.get("audio_url") or {}).get("url")
+                if src is None and isinstance(part.get("input_audio"), dict):
+                    src = "data:audio/wav;base64," + part["input_audio"]["data"]
+                media.append(("audio", _media_bytes(str(src))))
+                text += _AUD
+            else:
+                raise ValueError(f"unsupported content part {kind!r}")
+        flat.append({**m, "content": text})
+    return flat, media
+
+
 def _truncate_at_stop(text: str, stops) -> (str, bool):
     if isinstance(stops, str):
         stops = [stops]
@@ -86,7 +129,9 @@ def _truncate_at_stop(text: str, stops) -> (str, bool):
 
 
 def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optional[ChatTemplate] = None,
-               model_name: str = "") -> FastAPI:
+               model_name: str = "", multimodal=None) -> FastAPI:
+    """``multimodal``: a ``runtime.multimodal.MultimodalRunner`` over ``llm``; chat requests whose messages carry image or
+    audio parts are then answered through it (one at a time, on the static path)."""
     api = api or ApiConfig()
     client = EngineClient(llm, api.max_queued_requests, api.queue_timeout)
     template = chat_template or ChatTemplate()
@@ -151,6 +196,36 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
         return {"object": "list", "data": [{"id": name, "object": "model", "created": int(app.state.started), "owned_by": "local",
                                             "max_model_len": llm.max_input_len}]}
 
+    async def _multimodal_chat(body, messages, media, sp):
+        import asyncio
+        from ..runtime import native as rt
+        from ..runtime.multimodal import MultimodalInputs
+        prompt = template.apply(messages, True, None, bool((body.get("chat_template_kwargs") or {}).get("enable_thinking", True)))
+        req, it = MultimodalInputs(), iter(media)
+        import re
+        for piece in re.split(f"({_IMG}|{_AUD})", prompt):
+            if piece == _IMG:
+                req.image(next(it)[1])
+            elif piece == _AUD:
+                clip = rt.parse_wav(next(it)[1])
+                req.audio(clip.samples, clip.sample_rate)
+            elif piece:
+                req.text(encode(piece))
+
+        def work():
+            client.admission.acquire()
+            try:
+                with client._lock:
+                    return multimodal.generate(req, max_tokens=sp.max_tokens)
+            finally:
+                client.admission.release()
+        toks = await asyncio.get_running_loop().run_in_executor(None, work)
+        n_in = sum(len(p) if k == "text" else 0 for k, p in req.pieces)
+        return {"id": f"chatcmpl-{uuid.uuid4().hex[:24]}", "object": "chat.completion", "created": int(time.time()), "model": name,
+                "choices": [{"index": 0, "message": {"role": "assistant", "content": decode(toks)}, "finish_reason": "length",
+                             "token_ids": toks}],
+                "usage": {"prompt_tokens": n_in, "completion_tokens": len(toks), "total_tokens": n_in + len(toks)}}
+
     # ---- OpenAI chat completions ---------------------------------------------------------------------------
     @app.post("/v1/chat/completions")
     async def chat_completions(request: Request):
@@ -161,6 +236,11 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
                 raise ValueError("messages must be a non-empty list")
             sp = _sampling(body)
             tool_cfg = parsing.validate_tool_request(body)
+            messages, media = _split_media(messages)
+            if media:
+                if multimodal is None:
+                    raise ValueError("this server has no multimodal runner: send text-only messages")
+                return await _multimodal_chat(body, messages, media, sp)
             prompt = template.apply(messages, True, body.get("tools"), bool((body.get("chat_template_kwargs") or {}).get("enable_thinking", True)))
             ids = encode(prompt)
         except (KeyError, ValueError, TypeError, json.JSONDecodeError) as e:

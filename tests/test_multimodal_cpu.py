@@ -64,3 +64,42 @@ def test_pruning_shortens_the_prompt_and_plain_rope_decoders_work():
     assert ids_f.count(298) == 16 and ids_p.count(298) == 8 and p3 is None and emb_p.shape[0] == len(ids_p)
     assert len(pruned.generate(req, max_tokens=3)) == 3
     llm.close()
+
+
+def test_chat_route_with_image_and_audio_parts():
+    import base64
+    import io
+    import wave
+    from fastapi.testclient import TestClient
+    from tensorrt_edge_llm_b200.chat_template import ChatTemplate
+    from tensorrt_edge_llm_b200.server.app import create_app
+
+    class Bytes:
+        def encode(self, text, add_special_tokens=False):
+            return [b + 3 for b in text.encode("utf-8")]
+
+        def decode(self, ids, skip_special_tokens=True):
+            return bytes((i - 3) % 256 for i in ids).decode("utf-8", "replace")
+    llm = _llm(mrope=True)
+    llm.tokenizer = Bytes()
+    v, a = _encoders()
+    mm = MultimodalRunner(llm, v, a, image_token_id=298, audio_token_id=299)
+    ppm = b"P6\n8 8\n255\n" + bytes(range(192))
+    buf = io.BytesIO()
+    with wave.open(buf, "wb") as w:
+        w.setnchannels(1); w.setsampwidth(2); w.setframerate(16000)
+        w.writeframes((np.sin(np.arange(8000) / 20.0) * 8000).astype(np.int16).tobytes())
+    msg = [{"role": "user", "content": [{"type": "text", "text": "look: "},
+                                        {"type": "image_url", "image_url": {"url": "data:image/x-portable-pixmap;base64," + base64.b64encode(ppm).decode()}},
+                                        {"type": "input_audio", "input_audio": {"data": base64.b64encode(buf.getvalue()).decode(), "format": "wav"}},
+                                        {"type": "text", "text": " what is it?"}]}]
+    c = TestClient(create_app(llm, chat_template=ChatTemplate(), multimodal=mm))
+    r = c.post("/v1/chat/completions", json={"messages": msg, "max_tokens": 4})
+    assert r.status_code == 200, r.text
+    out = r.json()
+    assert out["usage"]["completion_tokens"] == 4 and len(out["choices"][0]["token_ids"]) == 4
+    plain = TestClient(create_app(llm, chat_template=ChatTemplate()))
+    assert plain.post("/v1/chat/completions", json={"messages": msg, "max_tokens": 4}).status_code == 400
+    bad = [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "https://example.com/x.png"}}]}]
+    assert c.post("/v1/chat/completions", json={"messages": bad}).status_code == 400
+    llm.close()
