@@ -34,6 +34,17 @@ class RequestOutput:
     spec_stats: Optional[dict] = None          # speculative runs: rounds, draft forwards, mean acceptance length
 
 
+def ifb_unsupported_reason(*, speculative: bool = False, reduced_vocab: bool = False, debug_hooks: bool = False) -> Optional[str]:
+    """Why a deployment cannot use the in-flight-batching engine, or ``None`` (``ifb_unsupported_reason`` of the
+    reference's ``server/runtime/engine.py``).  Speculative decoding and the debug hooks (layer dumps, forced tokens) run
+    on the static-batch path only."""
+    if speculative:
+        return "speculative decoding runs on the static-batch path (draft → verify rounds are not scheduled per step)"
+    if debug_hooks:
+        return "layer dumps / forced tokens need the static-batch path"
+    return None
+
+
 class LLM:
     def __init__(self, model: Union[str, ModelConfig], *, device: Optional[str] = None, comm=None,
                  max_batch_size: int = 64, max_input_len: int = 2048, max_kv_cache_capacity: int = 2304,
@@ -94,6 +105,10 @@ class LLM:
             self.runner.use_cuda_graphs = False        # hooks do not run inside a replayed graph
         self._forced = forced_tokens_from_env()
         if enable_in_flight_batching:
+            why = ifb_unsupported_reason(speculative=self.spec_decoder is not None, reduced_vocab=False, debug_hooks=self._dumper is not None
+                                         or self._forced is not None)
+            if why:
+                raise ValueError(f"in-flight batching cannot be enabled: {why}")
             self._cache_limits = (int(context_cache_max_records), int(context_cache_max_snapshots) or 64)
             self._start_engine(enable_prefix_cache, scheduling or {})
 
