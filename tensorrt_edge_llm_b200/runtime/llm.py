@@ -36,10 +36,10 @@ class RequestOutput:
 
 def ifb_unsupported_reason(*, speculative: bool = False, reduced_vocab: bool = False, debug_hooks: bool = False) -> Optional[str]:
     """Why a deployment cannot use the in-flight-batching engine, or ``None`` (``ifb_unsupported_reason`` of the
-    reference's ``server/runtime/engine.py``).  Speculative decoding and the debug hooks (layer dumps, forced tokens) run
-    on the static-batch path only."""
-    if speculative:
-        return "speculative decoding runs on the static-batch path (draft → verify rounds are not scheduled per step)"
+    reference's ``server/runtime/engine.py``).  The debug hooks (layer dumps, forced tokens) run on the static-batch path
+    only; speculative decoding is scheduled by the engine (one draft → verify round per step and resident row)."""
+    if speculative and reduced_vocab:
+        return "speculative decoding verifies over the full vocabulary"
     if debug_hooks:
         return "layer dumps / forced tokens need the static-batch path"
     return None
@@ -105,8 +105,7 @@ class LLM:
             self.runner.use_cuda_graphs = False        # hooks do not run inside a replayed graph
         self._forced = forced_tokens_from_env()
         if enable_in_flight_batching:
-            why = ifb_unsupported_reason(speculative=self.spec_decoder is not None, reduced_vocab=False, debug_hooks=self._dumper is not None
-                                         or self._forced is not None)
+            why = ifb_unsupported_reason(debug_hooks=self._dumper is not None or self._forced is not None)
             if why:
                 raise ValueError(f"in-flight batching cannot be enabled: {why}")
             self._cache_limits = (int(context_cache_max_records), int(context_cache_max_snapshots) or 64)
@@ -149,6 +148,10 @@ class LLM:
         cfg = rt.EngineConfig()
         cfg.max_batch_size = self.max_batch_size
         opts = rt.SchedulingOptions()
+        if self.spec_decoder is not None:
+            # the draft must see whole prompts: no chunked prefill, and a step budget that holds the longest prompt
+            scheduling = {**scheduling, "max_chunk_tokens": self.max_input_len,
+                          "max_num_tokens": max(int(scheduling.get("max_num_tokens", 0) or 0), self.max_input_len + self.max_batch_size)}
         for k, v in scheduling.items():
             if k == "mode":
                 v = {"auto": rt.IfbSchedulingMode.Auto, "mixed": rt.IfbSchedulingMode.Mixed,
@@ -162,7 +165,7 @@ class LLM:
         self._rt = rt
         self.engine = rt.RequestEngine(cfg, lambda: ModelSession(self.runner, eos_ids, enable_prefix_cache, self.max_input_len,
                                                                  self.guided_vocab, max_snapshots=self._cache_limits[1],
-                                                                 max_records=self._cache_limits[0]))
+                                                                 max_records=self._cache_limits[0], spec_decoder=self.spec_decoder))
 
     def _native_request(self, ids, sp: SamplingParams, priority: int = 0):
         r = self._rt.GenerationRequest()

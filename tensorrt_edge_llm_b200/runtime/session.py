@@ -39,10 +39,15 @@ class _Seq:
 
 class ModelSession(rt.RuntimeSession):
     def __init__(self, runner: ModelRunner, eos_ids=(), enable_prefix_cache: bool = False, max_input_len: int = 2048,
-                 guided_vocab=None, max_snapshots: int = 64, max_records: int = 4096):
+                 guided_vocab=None, max_snapshots: int = 64, max_records: int = 4096, spec_decoder=None):
         super().__init__()
         self.runner = runner
         self.guided_vocab = guided_vocab
+        # Speculative decoding under in-flight batching: resident decode rows advance by one draft → verify round per
+        # step (several tokens per delta), whole prompts are prefilled through the decoder so the draft sees them too.
+        self.spec = spec_decoder
+        if spec_decoder is not None:
+            enable_prefix_cache = False        # the draft's own KV has no shared prefix pages
         self.kv = runner.kv
         self.eos = set(int(e) for e in eos_ids if e is not None)
         self.max_input_len = max_input_len
@@ -78,6 +83,12 @@ class ModelSession(rt.RuntimeSession):
             r.admitted, r.retry_later, r.reason = False, False, "EDGELLM_INPUT_TOO_LONG: prompt + max_tokens exceed the KV capacity"
             return r
         row_state = None
+        if self.spec is not None:
+            if req.temperature >= 1e-3 or req.guided_type or req.logit_bias_ids or req.num_logprobs >= 0:
+                r.admitted, r.retry_later = False, False
+                r.reason = "EDGELLM_BAD_REQUEST: this deployment decodes speculatively; it serves greedy requests without logits processing"
+                return r
+            need += self.spec.spec.verify_tokens + 8           # head room of one verification tree
         if req.guided_type or req.logit_bias_ids or req.num_logprobs >= 0:
             try:
                 if req.guided_type and self.runner.vocab_map is not None:
@@ -158,6 +169,8 @@ class ModelSession(rt.RuntimeSession):
 
     def _execute(self, plan):
         seqs = list(plan.seqs)                            # the binding hands out copies: edit and use this one list
+        if self.spec is not None:
+            return self._execute_speculative(seqs)
         if self.hybrid and self.prefix is not None:
             self._prefill_to_page_boundary(seqs)
         return self._execute_plan(seqs)
@@ -189,6 +202,44 @@ class ModelSession(rt.RuntimeSession):
                 self._take_snapshot(s.slot, self.seqs[s.slot], boundary)
                 s.length -= boundary - s.start
                 s.start = boundary
+
+    def _execute_speculative(self, seqs):
+        ctx = [s for s in seqs if s.kind == rt.WorkKind.Context]
+        dec = [s for s in seqs if s.kind != rt.WorkKind.Context]
+        deltas = []
+
+        def emit(slot, tokens):
+            q = self.seqs[slot]
+            d = rt.TokenDelta()
+            d.slot = slot
+            keep = []
+            for t in tokens[:max(q.req.max_tokens - q.generated, 0)]:
+                keep.append(int(t))
+                if not q.req.ignore_eos and (t in self.eos or t in q.req.stop_token_ids):
+                    d.finished = True
+                    d.reason = rt.FinishReason.EndId if t in self.eos else rt.FinishReason.StopWords
+                    break
+            q.generated += len(keep)
+            q.tokens += keep
+            if keep:
+                q.last_token = keep[-1]
+            d.tokens = keep
+            deltas.append(d)
+        if ctx:
+            for s in ctx:
+                if s.start != 0 or not s.last_chunk:
+                    raise RuntimeError("speculative decoding prefills whole prompts: raise max_chunk_tokens to the longest prompt")
+            slots = [s.slot for s in ctx]
+            first = self.spec.prefill(slots, [self.seqs[x].tokens[:] for x in slots])
+            for slot, t in zip(slots, first):
+                emit(slot, [t])
+        if dec:
+            slots = [s.slot for s in dec]
+            for slot, toks in zip(slots, self.spec.round(slots)):
+                emit(slot, toks)
+        out = rt.StepResult()
+        out.deltas = deltas
+        return out
 
     def _execute_plan(self, seqs):
         seats, token_lists, producers = [], [], []
@@ -268,6 +319,8 @@ class ModelSession(rt.RuntimeSession):
                 if filled > len(q.req.prompt_ids):
                     self.prefix.insert(list(q.tokens[:filled]), filled, self.kv.pages_of(slot))
             del self.seqs[slot]
+            if self.spec is not None:
+                self.spec.release([slot])
             self.kv.free(slot)
             self.slots.release(slot)
 

@@ -266,3 +266,32 @@ def test_sampled_speculative_decoding_matches_plain_sampling_in_distribution():
     tv2 = 0.5 * (c2 / n - exact).abs().sum()
     assert tv1 < 0.09 and tv2 < 0.09, (float(tv1), float(tv2))
     assert float(exact.max()) < 0.9                            # the check is not vacuous: mass is spread over several tokens
+
+
+def test_speculative_decoding_under_in_flight_batching():
+    """Requests arriving at different times share draft → verify rounds; every output equals plain greedy decoding."""
+    from tensorrt_edge_llm_b200.runtime.llm import LLM, SamplingParams
+    cfg = tiny_llama_config(num_hidden_layers=4, dtype="float32")
+    dcfg = tiny_llama_config(num_hidden_layers=1, dtype="float32")
+    dcfg.draft_type, dcfg.eagle3_target_hidden_size = "eagle3", cfg.hidden_size
+    g = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 40, 17, 5)]
+    plain = LLM(cfg, device="cpu", max_batch_size=2, max_input_len=64, max_kv_cache_capacity=128, page_size=16, random_init_seed=1)
+    want = [o.token_ids for o in plain.generate(prompts, SamplingParams(max_tokens=11, ignore_eos=True))]
+    plain.close()
+    llm = LLM(cfg, device="cpu", max_batch_size=2, max_input_len=64, max_kv_cache_capacity=128, page_size=16, random_init_seed=1,
+              draft_model=dcfg, speculative=SpecConfig(draft_steps=3, top_k=2, verify_tokens=8), enable_in_flight_batching=True)
+    outs = llm.generate(prompts, SamplingParams(max_tokens=11, ignore_eos=True))          # four requests over two seats
+    assert [o.token_ids for o in outs] == want
+    assert llm.spec_decoder.stats.rounds > 0 and llm.engine.metrics().completed == 4
+    # streaming delivers several tokens per chunk and the same sequence
+    streamed, sizes = [], []
+    for toks, _ in llm.generate_stream(prompts[1], SamplingParams(max_tokens=11, ignore_eos=True)):
+        streamed += toks
+        sizes.append(len(toks))
+    assert streamed == want[1]
+    # sampled requests are refused with a reason instead of being decoded greedily
+    import pytest
+    with pytest.raises(ValueError, match="speculatively"):
+        llm.generate([prompts[0]], SamplingParams(max_tokens=4, temperature=0.8))
+    llm.close()
