@@ -1,0 +1,54 @@
+"""In-flight batching with tensor parallelism: rank 0 schedules, the other ranks follow.
+
+The reference keeps tensor-parallel deployments on its one-request-at-a-time path (``docs/source/user_guide/examples/
+server.md:634-636``).  Here the request engine runs on rank 0 only; every state change of its session that touches the
+model — a seat reserved, a step executed, a seat released — is mirrored to the other ranks as a small broadcast *before*
+rank 0 runs it, and the followers replay it on their own shard (their own KV pool and page ids; only seats, token ids and
+lengths have to agree).  The collectives inside the model step then meet on all ranks.  Sampling happens on rank 0; the
+followers never look at logits."""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import torch.distributed as dist
+
+
+class StepMirror:
+    """Rank 0 → all: ordered stream of session operations (``broadcast_object_list`` over the given group)."""
+
+    def __init__(self, group=None, src: int = 0):
+        self.group, self.src = group, src
+        self.sent = 0
+
+    def send(self, op: tuple) -> None:
+        dist.broadcast_object_list([op], src=self.src, group=self.group)
+        self.sent += 1
+
+    def recv(self) -> tuple:
+        box = [None]
+        dist.broadcast_object_list(box, src=self.src, group=self.group)
+        return box[0]
+
+
+def serve_follower(runner, mirror: StepMirror) -> int:
+    """Replay rank 0's session on this rank until it says stop; returns the number of steps executed."""
+    kv, steps = runner.kv, 0
+    while True:
+        op = mirror.recv()
+        kind = op[0]
+        if kind == "stop":
+            return steps
+        if kind == "noop":                 # keep-alive while the engine is idle
+            continue
+        if kind == "reserve":
+            _, slot, need = op
+            kv.free(slot)
+            kv.reserve(slot, need)
+        elif kind == "step":
+            _, seats, token_lists = op
+            runner.step(list(seats), [list(t) for t in token_lists])
+            steps += 1
+        elif kind == "release":
+            kv.free(op[1])
+        else:
+            raise RuntimeError(f"unknown mirrored operation {kind!r}")

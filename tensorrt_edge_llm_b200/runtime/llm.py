@@ -52,14 +52,14 @@ class LLM:
                  tokenizer=None, kv_pages: Optional[int] = None, enable_in_flight_batching: bool = False,
                  enable_prefix_cache: bool = False, scheduling: Optional[dict] = None, draft_model=None, speculative=None,
                  context_cache_max_records: int = 4096, context_cache_max_snapshots: int = 64,
-                 embedding_quantization: Optional[str] = None):
+                 embedding_quantization: Optional[str] = None, tp_mirror=None, mapping: Optional[Mapping] = None):
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.device = torch.device(device)
         if isinstance(model, ModelConfig):
             self.model = AutoModel.from_config(model, comm=comm, device=self.device, random_init=random_init_seed)
         else:
-            self.model = AutoModel.from_pretrained(model, comm=comm, device=self.device)
+            self.model = AutoModel.from_pretrained(model, comm=comm, device=self.device, **({"mapping": mapping} if mapping else {}))
         self.cfg = self.model.cfg
         if embedding_quantization:                  # "fp8" | "nvfp4": the token table is stored quantised, rows expand on lookup
             from ..models.embedding import quantize_embedding
@@ -104,7 +104,11 @@ class LLM:
             self._dumper.attach(self.model)
             self.runner.use_cuda_graphs = False        # hooks do not run inside a replayed graph
         self._forced = forced_tokens_from_env()
+        self._tp_mirror = tp_mirror
         if enable_in_flight_batching:
+            if self.cfg.tp_size > 1 and tp_mirror is None:
+                raise ValueError("in-flight batching with tensor parallelism needs tp_mirror (rank 0 schedules, the other ranks run "
+                                 "parallel.tp_serving.serve_follower)")
             why = ifb_unsupported_reason(debug_hooks=self._dumper is not None or self._forced is not None)
             if why:
                 raise ValueError(f"in-flight batching cannot be enabled: {why}")
@@ -165,7 +169,8 @@ class LLM:
         self._rt = rt
         self.engine = rt.RequestEngine(cfg, lambda: ModelSession(self.runner, eos_ids, enable_prefix_cache, self.max_input_len,
                                                                  self.guided_vocab, max_snapshots=self._cache_limits[1],
-                                                                 max_records=self._cache_limits[0], spec_decoder=self.spec_decoder))
+                                                                 max_records=self._cache_limits[0], spec_decoder=self.spec_decoder,
+                                                                 mirror=self._tp_mirror))
 
     def _native_request(self, ids, sp: SamplingParams, priority: int = 0):
         r = self._rt.GenerationRequest()
@@ -434,6 +439,8 @@ class LLM:
         if self.engine is not None:
             self.engine.shutdown()
             self.engine = None
+            if self._tp_mirror is not None:
+                self._tp_mirror.send(("stop",))
         self.runner = None
         self.kv = None
         self.model = None

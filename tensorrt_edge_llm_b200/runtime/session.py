@@ -39,12 +39,18 @@ class _Seq:
 
 class ModelSession(rt.RuntimeSession):
     def __init__(self, runner: ModelRunner, eos_ids=(), enable_prefix_cache: bool = False, max_input_len: int = 2048,
-                 guided_vocab=None, max_snapshots: int = 64, max_records: int = 4096, spec_decoder=None):
+                 guided_vocab=None, max_snapshots: int = 64, max_records: int = 4096, spec_decoder=None, mirror=None):
         super().__init__()
         self.runner = runner
         self.guided_vocab = guided_vocab
         # Speculative decoding under in-flight batching: resident decode rows advance by one draft → verify round per
         # step (several tokens per delta), whole prompts are prefilled through the decoder so the draft sees them too.
+        # tensor parallelism: operations that touch the model are broadcast to the follower ranks first (parallel/tp_serving.py)
+        self.mirror = mirror
+        if mirror is not None:
+            if spec_decoder is not None:
+                raise ValueError("speculative decoding is not mirrored to follower ranks")
+            enable_prefix_cache = False        # shared prefix pages are not mirrored
         self.spec = spec_decoder
         if spec_decoder is not None:
             enable_prefix_cache = False        # the draft's own KV has no shared prefix pages
@@ -121,6 +127,8 @@ class ModelSession(rt.RuntimeSession):
                     raise MemoryError("sliding-window page budget is taken")
             else:
                 self.kv.reserve(slot, need)               # capacity is reserved at seat time: no eviction later
+                if self.mirror is not None:
+                    self.mirror.send(("reserve", slot, need))
         except (MemoryError, RuntimeError) as e:
             self.kv.free(slot)
             self.slots.release(slot)
@@ -263,6 +271,8 @@ class ModelSession(rt.RuntimeSession):
                 segs.append((r0, r0 + len(toks), self.seqs[slot].req.lora_name or None))
                 r0 += len(toks)
             lora.set_segments(segs)
+        if self.mirror is not None:
+            self.mirror.send(("step", seats, token_lists))
         logits = self.runner.step(seats, token_lists)      # one row per sequence (its last token)
         rows = [i for i, p in enumerate(producers) if p]
         out = rt.StepResult()
@@ -321,6 +331,8 @@ class ModelSession(rt.RuntimeSession):
             del self.seqs[slot]
             if self.spec is not None:
                 self.spec.release([slot])
+            if self.mirror is not None:
+                self.mirror.send(("release", slot))
             self.kv.free(slot)
             self.slots.release(slot)
 

@@ -144,3 +144,13 @@ def test_fused_allreduce_norm_world1():
     assert torch.equal(y, y2)
     assert int(epoch[:rows].min()) == 3
     ws.check_status()
+
+
+def test_in_flight_batching_with_tensor_parallel_ranks_cpu_gloo(tmp_path):
+    """Rank 0 schedules (chunked prefill, mid-flight admission), rank 1 replays the mirrored steps; tokens equal TP 1."""
+    _make_ckpt(str(tmp_path), torch.float32)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29641", os.path.join(ROOT, "tests", "_tp_ifb_worker.py"), str(tmp_path)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=dict(os.environ, OMP_NUM_THREADS="2"))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "rank 0: match True" in r.stdout and "rank 1: followed" in r.stdout
