@@ -29,9 +29,34 @@ def build_llm(cfg: ServerConfig):
         spec_kw = {"draft_model": sc.draft_model,
                    "speculative": SpecConfig(draft_steps=sc.num_speculative_tokens or 4, top_k=sc.draft_top_k or 8,
                                              verify_tokens=sc.verify_tokens or 32)}
-    llm = LLM(m.model, device=m.device or None, **spec_kw, max_batch_size=m.max_batch_size, max_input_len=m.max_input_len,
+    tp_kw = {}
+    if m.tensor_parallel_size > 1:
+        # one process per GPU (launched with ``python -m torch.distributed.run --nproc-per-node N -m … serve …``): rank 0
+        # serves HTTP and schedules, the other ranks follow its steps (parallel/tp_serving.py)
+        import datetime
+        import torch
+        import torch.distributed as dist
+        from ..config import Mapping
+        from ..parallel import make_comm
+        from ..parallel.tp_serving import StepMirror
+        rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+        if world != m.tensor_parallel_size:
+            raise ServerConfigError(f"--tensor-parallel-size {m.tensor_parallel_size} needs that many ranks (WORLD_SIZE is {world})")
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        cuda = torch.cuda.is_available() and (m.device or "cuda").startswith("cuda")
+        if cuda:
+            torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+        if not dist.is_initialized():               # a long timeout: followers wait in a broadcast while the server is idle
+            dist.init_process_group("nccl" if cuda else "gloo", timeout=datetime.timedelta(days=7))
+        dev = torch.device("cuda", torch.cuda.current_device()) if cuda else torch.device("cpu")
+        tp_kw = {"comm": make_comm("fused" if cuda else "nccl", dev), "mapping": Mapping(tp_size=world, tp_rank=rank),
+                 "tp_mirror": StepMirror() if m.enable_in_flight_batching else None}
+        m.device = str(dev)
+        if rank != 0:
+            tp_kw["tp_mirror"] = None
+    llm = LLM(m.model, device=m.device or None, **spec_kw, **tp_kw, max_batch_size=m.max_batch_size, max_input_len=m.max_input_len,
               max_kv_cache_capacity=m.max_kv_cache_capacity, page_size=m.kv_page_size, max_num_tokens=m.max_num_tokens or 8192,
-              tokenizer=tok, enable_in_flight_batching=m.enable_in_flight_batching,
+              tokenizer=tok, enable_in_flight_batching=m.enable_in_flight_batching and int(os.environ.get("RANK", "0")) == 0,
               enable_prefix_cache=m.context_cache_config.enabled, context_cache_max_records=m.context_cache_config.max_records,
               context_cache_max_snapshots=m.context_cache_config.max_snapshots, scheduling=m.scheduling_dict() if m.enable_in_flight_batching else None)
     return llm, ChatTemplate.load(m.model)
@@ -46,6 +71,13 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     import uvicorn
     from .app import create_app
     llm, template = build_llm(cfg)
+    if cfg.model.tensor_parallel_size > 1 and int(os.environ.get("RANK", "0")) != 0:
+        from ..parallel.tp_serving import StepMirror, serve_follower
+        if not cfg.model.enable_in_flight_batching:
+            print("error: tensor-parallel serving needs --enable-in-flight-batching (rank 0 schedules, the others follow)", file=sys.stderr)
+            return 2
+        serve_follower(llm.runner, StepMirror())
+        return 0
     app = create_app(llm, cfg.api, template, model_name=os.path.basename(os.path.normpath(cfg.model.model)))
     try:
         uvicorn.run(app, host=cfg.api.host, port=cfg.api.port, log_level=cfg.api.log_level)
