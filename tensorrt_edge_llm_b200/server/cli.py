@@ -68,14 +68,14 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     except ServerConfigError as e:
         print(f"error: {e}", file=sys.stderr)
         return 2
+    if cfg.model.tensor_parallel_size > 1 and not cfg.model.enable_in_flight_batching:
+        print("error: tensor-parallel serving needs --enable-in-flight-batching (rank 0 schedules, the others follow)", file=sys.stderr)
+        return 2
     import uvicorn
     from .app import create_app
     llm, template = build_llm(cfg)
     if cfg.model.tensor_parallel_size > 1 and int(os.environ.get("RANK", "0")) != 0:
         from ..parallel.tp_serving import StepMirror, serve_follower
-        if not cfg.model.enable_in_flight_batching:
-            print("error: tensor-parallel serving needs --enable-in-flight-batching (rank 0 schedules, the others follow)", file=sys.stderr)
-            return 2
         serve_follower(llm.runner, StepMirror())
         return 0
     app = create_app(llm, cfg.api, template, model_name=os.path.basename(os.path.normpath(cfg.model.model)))
