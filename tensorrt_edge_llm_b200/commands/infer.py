@@ -94,7 +94,8 @@ def run_requests(llm, template, requests: List[Dict[str, Any]]) -> List[Dict[str
             else _text_of(r["messages"])
         sp = SamplingParams(max_tokens=r["max_tokens"], temperature=r["temperature"], top_k=r["top_k"], top_p=r["top_p"], seed=r["seed"],
                             logprobs=r["num_logprobs"] if r["num_logprobs"] > 0 else None, logit_bias=r["logit_bias"], guided=r["guided"],
-                            context_cache_lookup=r["cache_lookup"], context_cache_commit=r["cache_commit"])
+                            context_cache_lookup=r["cache_lookup"], context_cache_commit=r["cache_commit"],
+                            disable_spec_decode=r["disable_spec_decode"])
         o = llm.generate([prompt], sp)[0]
         text = o.text or ""
         reason = o.finish_reason

@@ -241,7 +241,8 @@ PYBIND11_MODULE(_telb_runtime, m) {
         .def_readwrite("logit_bias_ids", &GenerationRequest::logit_bias_ids)
         .def_readwrite("logit_bias_values", &GenerationRequest::logit_bias_values)
         .def_readwrite("cache_lookup", &GenerationRequest::cache_lookup)
-        .def_readwrite("cache_commit", &GenerationRequest::cache_commit);
+        .def_readwrite("cache_commit", &GenerationRequest::cache_commit)
+        .def_readwrite("disable_spec_decode", &GenerationRequest::disable_spec_decode);
     py::class_<AdmissionResult>(m, "AdmissionResult")
         .def(py::init<>())
         .def_readwrite("admitted", &AdmissionResult::admitted)

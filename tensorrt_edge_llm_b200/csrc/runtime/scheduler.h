@@ -139,6 +139,7 @@ struct GenerationRequest {
     // nothing (0), the prompt's full pages (1, "prefill_state_only") or prompt plus generated tokens (2).
     bool cache_lookup = true;
     int cache_commit = 1;
+    bool disable_spec_decode = false;       // decode this request token by token even on a speculative deployment
 };
 
 struct AdmissionResult {

@@ -188,6 +188,7 @@ class LLM:
             if self.lora is None or sp.lora_name not in self.lora.names:
                 raise ValueError(f"unknown LoRA adapter {sp.lora_name!r}")
             r.lora_name = sp.lora_name
+        r.disable_spec_decode = bool(sp.disable_spec_decode)
         r.cache_lookup = bool(sp.context_cache_lookup)
         try:
             r.cache_commit = {"none": 0, "prefill_state_only": 1, "including_generated_tokens": 2}[sp.context_cache_commit]

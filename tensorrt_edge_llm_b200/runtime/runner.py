@@ -35,6 +35,7 @@ class SamplingParams:
     logprobs: Optional[int] = None          # None = off; k = report the chosen token's log-probability and the k most likely
     logit_bias: Optional[dict] = None       # token id → additive bias on its logit
     guided: Optional[object] = None         # runtime.guided.GuidedDecodingParams
+    disable_spec_decode: bool = False       # on a speculative deployment: decode this request token by token
     lora_name: Optional[str] = None         # adapter (loaded with LLM.load_lora) applied to this request's rows
     context_cache_lookup: bool = True       # False = bypass the prefix cache for this request
     context_cache_commit: str = "prefill_state_only"     # "none" | "prefill_state_only" | "including_generated_tokens"

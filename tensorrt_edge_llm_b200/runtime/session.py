@@ -26,7 +26,7 @@ from .runner import ModelRunner, SamplingParams
 
 
 class _Seq:
-    __slots__ = ("req", "request_id", "tokens", "generated", "last_token", "finished", "row_state")
+    __slots__ = ("req", "request_id", "tokens", "generated", "last_token", "finished", "row_state", "plain")
 
     def __init__(self, req, request_id):
         self.req, self.request_id = req, request_id
@@ -89,12 +89,12 @@ class ModelSession(rt.RuntimeSession):
             r.admitted, r.retry_later, r.reason = False, False, "EDGELLM_INPUT_TOO_LONG: prompt + max_tokens exceed the KV capacity"
             return r
         row_state = None
+        plain = True
         if self.spec is not None:
-            if req.temperature >= 1e-3 or req.guided_type or req.logit_bias_ids or req.num_logprobs >= 0:
-                r.admitted, r.retry_later = False, False
-                r.reason = "EDGELLM_BAD_REQUEST: this deployment decodes speculatively; it serves greedy requests without logits processing"
-                return r
-            need += self.spec.spec.verify_tokens + 8           # head room of one verification tree
+            # sampled, constrained or opted-out requests are decoded token by token next to the speculative ones
+            plain = bool(req.disable_spec_decode or req.temperature >= 1e-3 or req.guided_type or req.logit_bias_ids or req.num_logprobs >= 0)
+            if not plain:
+                need += self.spec.spec.verify_tokens + 8       # head room of one verification tree
         if req.guided_type or req.logit_bias_ids or req.num_logprobs >= 0:
             try:
                 if req.guided_type and self.runner.vocab_map is not None:
@@ -139,6 +139,7 @@ class ModelSession(rt.RuntimeSession):
             return r
         self.seqs[slot] = _Seq(req, request_id)
         self.seqs[slot].row_state = row_state
+        self.seqs[slot].plain = plain
         r.admitted, r.slot, r.reused_tokens = True, slot, reused
         return r
 
@@ -178,7 +179,12 @@ class ModelSession(rt.RuntimeSession):
     def _execute(self, plan):
         seqs = list(plan.seqs)                            # the binding hands out copies: edit and use this one list
         if self.spec is not None:
-            return self._execute_speculative(seqs)
+            fast = [s for s in seqs if not self.seqs[s.slot].plain]
+            slow = [s for s in seqs if self.seqs[s.slot].plain]
+            out = self._execute_speculative(fast) if fast else rt.StepResult()
+            if slow:
+                out.deltas = list(out.deltas) + list(self._execute_plan(slow).deltas)
+            return out
         if self.hybrid and self.prefix is not None:
             self._prefill_to_page_boundary(seqs)
         return self._execute_plan(seqs)

@@ -290,8 +290,12 @@ def test_speculative_decoding_under_in_flight_batching():
         streamed += toks
         sizes.append(len(toks))
     assert streamed == want[1]
-    # sampled requests are refused with a reason instead of being decoded greedily
-    import pytest
-    with pytest.raises(ValueError, match="speculatively"):
-        llm.generate([prompts[0]], SamplingParams(max_tokens=4, temperature=0.8))
+    # opted-out and sampled requests run token by token beside the speculative ones
+    rounds = llm.spec_decoder.stats.rounds
+    hs = [llm.submit(prompts[0], SamplingParams(max_tokens=11, ignore_eos=True, disable_spec_decode=True)),
+          llm.submit(prompts[2], SamplingParams(max_tokens=11, ignore_eos=True))]
+    got = [h.get(60.0) for h in hs]
+    assert got == [want[0], want[2]] and llm.spec_decoder.stats.rounds > rounds
+    sampled = llm.generate([prompts[0]], SamplingParams(max_tokens=6, temperature=0.8, top_k=20, seed=4, ignore_eos=True))[0]
+    assert len(sampled.token_ids) == 6
     llm.close()
