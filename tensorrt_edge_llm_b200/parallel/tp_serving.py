@@ -17,6 +17,12 @@ class StepMirror:
     """Rank 0 → all: ordered stream of session operations (``broadcast_object_list`` over the given group)."""
 
     def __init__(self, group=None, src: int = 0):
+        # A group of its own (gloo, host memory) with a week-long timeout: followers sit in this broadcast while the
+        # server is idle, which must not trip the watchdog of the group the model's collectives use.  Every rank has to
+        # construct the mirror (creating a group is collective).
+        if group is None:
+            import datetime
+            group = dist.new_group(backend="gloo", timeout=datetime.timedelta(days=7))
         self.group, self.src = group, src
         self.sent = 0
 

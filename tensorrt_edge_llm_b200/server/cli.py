@@ -33,7 +33,6 @@ def build_llm(cfg: ServerConfig):
     if m.tensor_parallel_size > 1:
         # one process per GPU (launched with ``python -m torch.distributed.run --nproc-per-node N -m … serve …``): rank 0
         # serves HTTP and schedules, the other ranks follow its steps (parallel/tp_serving.py)
-        import datetime
         import torch
         import torch.distributed as dist
         from ..config import Mapping
@@ -46,14 +45,15 @@ def build_llm(cfg: ServerConfig):
         cuda = torch.cuda.is_available() and (m.device or "cuda").startswith("cuda")
         if cuda:
             torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
-        if not dist.is_initialized():               # a long timeout: followers wait in a broadcast while the server is idle
-            dist.init_process_group("nccl" if cuda else "gloo", timeout=datetime.timedelta(days=7))
+        if not dist.is_initialized():
+            dist.init_process_group("nccl" if cuda else "gloo")
         dev = torch.device("cuda", torch.cuda.current_device()) if cuda else torch.device("cpu")
         tp_kw = {"comm": make_comm("fused" if cuda else "nccl", dev), "mapping": Mapping(tp_size=world, tp_rank=rank),
-                 "tp_mirror": StepMirror() if m.enable_in_flight_batching else None}
+                 "tp_mirror": None}
+        build_llm.mirror = StepMirror()             # collective: every rank creates the mirror's group here
+        if rank == 0 and m.enable_in_flight_batching:
+            tp_kw["tp_mirror"] = build_llm.mirror
         m.device = str(dev)
-        if rank != 0:
-            tp_kw["tp_mirror"] = None
     llm = LLM(m.model, device=m.device or None, **spec_kw, **tp_kw, max_batch_size=m.max_batch_size, max_input_len=m.max_input_len,
               max_kv_cache_capacity=m.max_kv_cache_capacity, page_size=m.kv_page_size, max_num_tokens=m.max_num_tokens or 8192,
               tokenizer=tok, enable_in_flight_batching=m.enable_in_flight_batching and int(os.environ.get("RANK", "0")) == 0,
@@ -75,8 +75,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     from .app import create_app
     llm, template = build_llm(cfg)
     if cfg.model.tensor_parallel_size > 1 and int(os.environ.get("RANK", "0")) != 0:
-        from ..parallel.tp_serving import StepMirror, serve_follower
-        serve_follower(llm.runner, StepMirror())
+        from ..parallel.tp_serving import serve_follower
+        serve_follower(llm.runner, build_llm.mirror)
         return 0
     app = create_app(llm, cfg.api, template, model_name=os.path.basename(os.path.normpath(cfg.model.model)))
     try:
