@@ -92,12 +92,13 @@ inline int make_tmap_nd(CUtensorMap* out, CUtensorMapDataType dt, int rank, cons
 }
 
 // Launch with programmatic dependent launch enabled (see pdl_wait in tc5_common.cuh).  Setting the
-// environment variable TELB_DISABLE_PDL=1 falls back to fully serialised launches.
+// environment variable TELB_DISABLE_PDL=1 (or the reference's EDGELLM_ENABLE_PDL=0) falls back to fully serialised launches.
 inline bool pdl_enabled() {
     static int v = -1;
     if (v < 0) {
         const char* e = getenv("TELB_DISABLE_PDL");
-        v = (e && e[0] == '1') ? 0 : 1;
+        const char* r = getenv("EDGELLM_ENABLE_PDL");
+        v = ((e && e[0] == '1') || (r && r[0] == '0')) ? 0 : 1;
     }
     return v == 1;
 }

@@ -8,6 +8,7 @@ or a :class:`ModelConfig` (random-init weights, for benchmarks without network a
 from __future__ import annotations
 
 import dataclasses
+import os
 import time
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence, Union
@@ -256,6 +257,8 @@ class LLM:
                  ) -> List[RequestOutput]:
         """Generate for a batch of prompts (static batch: one prefill wave, then decode)."""
         sp = sampling_params or SamplingParams()
+        if os.environ.get("EDGELLM_IGNORE_EOS", "0") == "1" and not sp.ignore_eos:      # benchmark switch of the reference
+            sp = dataclasses.replace(sp, ignore_eos=True)
         if self.engine is not None:
             if isinstance(prompts, torch.Tensor):
                 prompts = prompts.tolist()

@@ -10,6 +10,8 @@ all-resident decode steps replay a CUDA graph per batch size, with device-reside
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
 
@@ -56,7 +58,8 @@ class ModelRunner:
         self.device = pool_dev
         self.max_num_tokens = max_num_tokens
         self._graphs: Dict[int, "_DecodeGraph"] = {}
-        self.use_cuda_graphs = self.device.type == "cuda"
+        # EDGELLM_DISABLE_CUDA_GRAPH=1 (the reference's switch, cpp/runtime/multiDevice/runtimeCoordinator.cpp:680) keeps decode eager
+        self.use_cuda_graphs = self.device.type == "cuda" and os.environ.get("EDGELLM_DISABLE_CUDA_GRAPH", "0") != "1"
         # hybrid models address attention pools and recurrent state pools through the manager itself
         self.cache = kv if getattr(model, "needs_cache_set", False) else kv.pool
         # reduced-vocabulary LM head: logits cover `vocab_map.numel()` columns, column c is token vocab_map[c]
