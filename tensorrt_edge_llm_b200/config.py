@@ -95,6 +95,43 @@ class QuantConfig:
 
 
 @dataclass
+class DiffusionConfig:
+    """Block-diffusion generation parameters (``tensorrt_edgellm/config.py:576`` ``DiffusionConfig``): a canvas of
+    ``canvas_length`` tokens is denoised with bidirectional attention for at most ``max_denoising_steps`` passes while the
+    sampling temperature falls from ``t_max`` to ``t_min``; the entropy-bound sampler keeps the lowest-entropy positions
+    whose summed entropy (all but the largest) stays within ``entropy_bound`` and re-noises the rest; a block has converged
+    when every arg-max has been stable for more than ``stability_window`` passes and the mean entropy is below
+    ``entropy_threshold``."""
+
+    canvas_length: int = 256
+    max_denoising_steps: int = 48
+    t_max: float = 0.8
+    t_min: float = 0.4
+    sampler_type: str = "entropy_bound"
+    entropy_bound: float = 0.1
+    entropy_threshold: float = 0.005
+    stability_window: int = 2
+    self_conditioning_enabled: bool = True
+    self_conditioning_size: int = 0
+
+    @classmethod
+    def from_hf(cls, hf: Dict[str, Any], gen: Optional[Dict[str, Any]] = None) -> "DiffusionConfig":
+        gen = gen or {}
+        own = hf.get("diffusion") or {}
+        look = lambda k, d: own.get(k, gen.get(k, hf.get(k, d)))
+        sampler = gen.get("sampler_config") or own.get("sampler_config") or {}
+        name = str(sampler.get("_cls_name", own.get("sampler_type", "entropy_bound"))).lower().replace("_", "")
+        return cls(canvas_length=int(look("canvas_length", 256)), max_denoising_steps=int(look("max_denoising_steps", 48)),
+                   t_max=float(look("t_max", 0.8)), t_min=float(look("t_min", 0.4)),
+                   sampler_type="entropy_bound" if "entropybound" in name else name,
+                   entropy_bound=float(sampler.get("entropy_bound", look("entropy_bound", 0.1))),
+                   entropy_threshold=float(sampler.get("entropy_threshold", look("entropy_threshold", 0.005))),
+                   stability_window=int(sampler.get("stability_window", look("stability_window", 2))),
+                   self_conditioning_enabled=bool(look("self_conditioning_enabled", True)),
+                   self_conditioning_size=int(look("self_conditioning_size", 0) or 0))
+
+
+@dataclass
 class MambaConfig:
     """Mamba2 mixer geometry (Nemotron-H style)."""
 
@@ -182,6 +219,7 @@ class ModelConfig:
     mlp_types: List[str] = field(default_factory=list)     # "mlp" / "moe" / "none" per layer
     mamba: Optional[MambaConfig] = None
     gdn: Optional[GdnConfig] = None
+    diffusion: Optional[DiffusionConfig] = None      # block-diffusion checkpoints (model_type "diffusion_gemma")
     # draft heads
     draft_type: Optional[str] = None        # "eagle3" / "mtp"
     eagle3_target_hidden_size: int = 0
@@ -280,6 +318,8 @@ class ModelConfig:
             d["mamba"] = MambaConfig(**d["mamba"])
         if isinstance(d.get("gdn"), dict):
             d["gdn"] = GdnConfig(**d["gdn"])
+        if isinstance(d.get("diffusion"), dict):
+            d["diffusion"] = DiffusionConfig(**d["diffusion"])
         known = {f.name for f in dataclasses.fields(cls)}
         return cls(**{k: v for k, v in d.items() if k in known})
 
@@ -307,8 +347,10 @@ class ModelConfig:
         if torch_dtype not in ("bfloat16", "float16", "float32"):
             torch_dtype = "bfloat16"
         extra: Dict[str, Any] = {}
-        if str(model_type).startswith("gemma"):
+        if str(model_type).startswith("gemma") or model_type == "diffusion_gemma":
             extra = _parse_gemma(llm, n_layers)
+            if model_type == "diffusion_gemma":
+                extra["diffusion"] = DiffusionConfig.from_hf(hf, hf.get("generation_config"))
             rope_theta, rope_scaling = extra.pop("rope_theta", rope_theta), extra.pop("rope_scaling", rope_scaling)
             layer_types = []
         router = "sigmoid_group_topk" if model_type in ("nemotron_h", "deepseek_v3") and llm.get("n_routed_experts") else "softmax_topk"
@@ -361,6 +403,10 @@ class ModelConfig:
     @classmethod
     def from_pretrained(cls, model_dir: str, mapping: Optional[Mapping] = None) -> "ModelConfig":
         hf = load_config_dict(model_dir)
+        gen_path = os.path.join(model_dir, "generation_config.json")
+        if hf.get("model_type") == "diffusion_gemma" and os.path.exists(gen_path) and "generation_config" not in hf:
+            with open(gen_path, "r", encoding="utf-8") as f:
+                hf["generation_config"] = json.load(f)
         quant = parse_quant_config(model_dir, hf)
         cfg = cls.from_hf_dict(hf, quant=quant, has_qk_norm=_detect_qk_norm(model_dir, hf))
         if mapping is not None:

@@ -71,7 +71,9 @@ class LLM:
             self._vocab_map = self._load_reduced_vocab(model)
         self.max_batch_size = max_batch_size
         self.max_input_len = max_input_len
-        pages_per_seq = (max_kv_cache_capacity + page_size - 1) // page_size
+        # block-diffusion checkpoints write a whole canvas beyond the committed tokens in every denoise pass
+        canvas_headroom = self.cfg.diffusion.canvas_length if self.cfg.diffusion is not None else 0
+        pages_per_seq = (max_kv_cache_capacity + canvas_headroom + page_size - 1) // page_size
         total_pages = kv_pages or (pages_per_seq * max_batch_size + 1)
         self.kv = KVCacheManager(self.cfg, total_pages, page_size, max_seats=max_batch_size,
                                  max_pages_per_seq=pages_per_seq, device=self.device)
@@ -84,6 +86,12 @@ class LLM:
         self.engine = None
         # Speculative decoding (EAGLE-3 / MTP draft head): greedy requests on the static-batch path run draft → verify rounds.
         self.spec_decoder = None
+        self.diffusion_decoder = None
+        if self.cfg.diffusion is not None:
+            if draft_model is not None or enable_in_flight_batching:
+                raise ValueError("block-diffusion checkpoints decode whole blocks: no draft model, no in-flight batching")
+            from .block_diffusion import BlockDiffusionDecoder
+            self.diffusion_decoder = BlockDiffusionDecoder(self.runner)
         if draft_model is not None:
             from .speculative import EagleDecoder, SpecConfig
             draft = (AutoModel.from_config(draft_model, device=self.device, random_init=random_init_seed)
@@ -288,6 +296,34 @@ class LLM:
             outs.extend(self._generate_batch(ids[b0:b0 + self.max_batch_size], sp))
         return outs
 
+    def _generate_diffusion(self, ids: List[List[int]], sp: SamplingParams) -> List[RequestOutput]:
+        """Block-diffusion checkpoints: denoise and commit one canvas at a time (``runtime/block_diffusion.py``).  The
+        model's own sampler replaces temperature / top-k / top-p; ``seed`` seeds the canvas and Gumbel noise."""
+        if sp.needs_logits_processing:
+            raise ValueError("block-diffusion decoding takes no logit bias, log-probabilities or output constraints")
+        dec = self.diffusion_decoder
+        for p in ids:
+            if len(p) > self.max_input_len:
+                raise ValueError(f"prompt of {len(p)} tokens exceeds max_input_len {self.max_input_len}")
+        eos = self.cfg.eos_token_id
+        eos_set = set(eos if isinstance(eos, (list, tuple)) else [eos]) if eos is not None else set()
+        eos_set |= set(sp.stop_token_ids)
+        seats = list(range(len(ids)))
+        b0, p0 = dec.stats.blocks, dec.stats.denoise_passes
+        t0 = time.perf_counter()
+        toks = dec.generate(seats, ids, sp.max_tokens, () if sp.ignore_eos else sorted(eos_set),
+                            max_denoising_steps=int(sp.max_denoising_steps or 0), seed=sp.seed)
+        t1 = time.perf_counter()
+        stats = {"blocks": dec.stats.blocks - b0, "denoise_passes": dec.stats.denoise_passes - p0}
+        outs = []
+        for p, row in zip(ids, toks):
+            reason = "stop" if (row and not sp.ignore_eos and row[-1] in eos_set) else "length"
+            text = self.tokenizer.decode(row) if self.tokenizer is not None else None
+            outs.append(RequestOutput(list(p), row, text, reason, 0.0, t1 - t0, spec_stats=stats))
+        for s in seats:
+            self.kv.free(s)
+        return outs
+
     def _generate_speculative(self, ids: List[List[int]], sp: SamplingParams) -> List[RequestOutput]:
         """Greedy generation through draft → tree verify rounds (lossless: same tokens as plain greedy decoding)."""
         dec = self.spec_decoder
@@ -382,6 +418,8 @@ class LLM:
                 raise ValueError(f"unknown LoRA adapter {sp.lora_name!r}")
             self.lora.set_segments(None)
             self.lora.set_active(sp.lora_name)
+        if self.diffusion_decoder is not None:
+            return self._generate_diffusion([p.tolist() for p in ids] if isinstance(ids, torch.Tensor) else ids, sp)
         if sp.needs_logits_processing:
             return self._generate_processed([p.tolist() for p in ids] if isinstance(ids, torch.Tensor) else ids, sp)
         if self.spec_decoder is not None and not isinstance(ids, torch.Tensor) and (sp.temperature < 1e-3 or not self.cfg.is_hybrid):

@@ -41,6 +41,7 @@ class SamplingParams:
     lora_name: Optional[str] = None         # adapter (loaded with LLM.load_lora) applied to this request's rows
     context_cache_lookup: bool = True       # False = bypass the prefix cache for this request
     context_cache_commit: str = "prefill_state_only"     # "none" | "prefill_state_only" | "including_generated_tokens"
+    max_denoising_steps: int = 0            # block-diffusion checkpoints: denoise passes per block (0 = the checkpoint's default)
 
     @property
     def needs_logits_processing(self) -> bool:
