@@ -176,10 +176,12 @@ class LLM:
             setattr(opts, k, v)
         cfg.scheduling = opts
         self._rt = rt
-        self.engine = rt.RequestEngine(cfg, lambda: ModelSession(self.runner, eos_ids, enable_prefix_cache, self.max_input_len,
-                                                                 self.guided_vocab, max_snapshots=self._cache_limits[1],
-                                                                 max_records=self._cache_limits[0], spec_decoder=self.spec_decoder,
-                                                                 mirror=self._tp_mirror))
+        def make_session():
+            self.session = ModelSession(self.runner, eos_ids, enable_prefix_cache, self.max_input_len, self.guided_vocab,
+                                        max_snapshots=self._cache_limits[1], max_records=self._cache_limits[0],
+                                        spec_decoder=self.spec_decoder, mirror=self._tp_mirror)
+            return self.session             # kept for its counters (prefix hits, jump-forward tokens); the engine thread owns it
+        self.engine = rt.RequestEngine(cfg, make_session)
 
     def _native_request(self, ids, sp: SamplingParams, priority: int = 0):
         r = self._rt.GenerationRequest()

@@ -26,7 +26,7 @@ from .runner import ModelRunner, SamplingParams
 
 
 class _Seq:
-    __slots__ = ("req", "request_id", "tokens", "generated", "last_token", "finished", "row_state", "plain")
+    __slots__ = ("req", "request_id", "tokens", "generated", "last_token", "finished", "row_state", "plain", "feed")
 
     def __init__(self, req, request_id):
         self.req, self.request_id = req, request_id
@@ -35,6 +35,7 @@ class _Seq:
         self.last_token: Optional[int] = None
         self.finished = False
         self.row_state = None            # logits.RowState when the request biases, constrains or reports log-probabilities
+        self.feed: List[int] = []        # emitted tokens whose KV is not written yet, when more than the last one (jump-forward)
 
 
 class ModelSession(rt.RuntimeSession):
@@ -70,6 +71,7 @@ class ModelSession(rt.RuntimeSession):
         self.snapshots: "OrderedDict[int, list]" = OrderedDict()
         self.max_snapshots = max_snapshots
         self.snapshot_hits = 0
+        self.jump_forward_tokens = 0       # tokens appended because a grammar left no choice (no forward pass of their own)
 
     # ---- seam ------------------------------------------------------------------------------------
     def capabilities(self):
@@ -263,7 +265,8 @@ class ModelSession(rt.RuntimeSession):
                 toks = q.tokens[s.start:s.start + s.length]
                 produces = s.last_chunk
             else:
-                toks = [q.last_token]
+                toks = q.feed or [q.last_token]
+                q.feed = []
                 produces = True
             if self.kv.bounded_swa:
                 self.kv.reserve(s.slot, self.kv.lengths[s.slot] + len(toks))
@@ -311,6 +314,18 @@ class ModelSession(rt.RuntimeSession):
                 elif not q.req.ignore_eos and (tok in self.eos or tok in q.req.stop_token_ids):
                     d.finished = True
                     d.reason = rt.FinishReason.EndId if tok in self.eos else rt.FinishReason.StopWords
+                elif (special and states[j] is not None and getattr(states[j].guided, "jump_forward", False)
+                      and states[j].num_logprobs < 0):       # a log-probability report has one row per sampled token
+                    # jump-forward (cpp/runtime/decoding/jumpForward.cpp): tokens the grammar forces next are emitted with
+                    # the sampled one and fed together in the sequence's next decode row (one row of several tokens)
+                    extra = states[j].guided.forced_tokens(self.guided_vocab.tokenizer, q.req.max_tokens - q.generated)
+                    if extra:
+                        d.tokens = [tok] + extra
+                        q.feed = [tok] + extra
+                        q.tokens += extra
+                        q.generated += len(extra)
+                        q.last_token = extra[-1]
+                        self.jump_forward_tokens += len(extra)
                 deltas.append(d)
         for slot, upto in getattr(self, "_snap_after", []):
             self._take_snapshot(slot, self.seqs[slot], upto)

@@ -188,3 +188,37 @@ def test_jump_forward_appends_forced_tokens_without_forward_passes():
     # only the three letters and the boolean's first letter are choices: everything else is appended in bulk
     assert llm.jump_forward_tokens >= 20 and len(calls) < n_plain / 3 and max(max(c) for c in calls) > 5
     llm.close()
+
+
+def test_jump_forward_under_in_flight_batching():
+    """The request engine's session emits grammar-forced tokens with the sampled one and feeds them as one multi-token row."""
+    from tensorrt_edge_llm_b200.runtime.grammar import EbnfMatcher
+    from tensorrt_edge_llm_b200.runtime.llm import LLM, SamplingParams
+    g = 'root ::= "{\\"name\\": \\"" [a-z]{3} "\\", \\"ok\\": " ("true" | "false") "}"'
+    cfg = tiny_llama_config(num_hidden_layers=1, vocab_size=300)
+    cfg.eos_token_id = 2
+    llm = LLM(cfg, device="cpu", max_batch_size=2, max_input_len=32, max_kv_cache_capacity=96, page_size=16, tokenizer=ByteTokenizer(),
+              enable_in_flight_batching=True)
+    calls = []
+    step = llm.runner.step
+    llm.runner.step = lambda seats, toks, **kw: (calls.append([len(t) for t in toks]), step(seats, toks, **kw))[1]
+    sp = lambda jf, **kw: SamplingParams(max_tokens=60, temperature=0.0, guided=GuidedDecodingParams("ebnf", grammar=g, jump_forward=jf), **kw)
+    plain = llm.generate([[5, 6]], sp(False))[0]
+    n_plain = len(calls)
+    calls.clear()
+    fast = llm.generate([[5, 6]], sp(True))[0]
+    m = EbnfMatcher(g)
+    assert m.complete(plain.text) and fast.text == plain.text and fast.finish_reason == plain.finish_reason
+    assert llm.session.jump_forward_tokens >= 20 and len(calls) < n_plain / 3 and max(max(c) for c in calls) > 5
+    # two requests in one batch, one of them without jump-forward, and a budget that ends inside a forced run
+    before = llm.session.jump_forward_tokens
+    a, b = llm.generate([[5, 6], [7, 8, 9]], sp(True))
+    assert a.text == plain.text and m.complete(b.text)
+    short = llm.generate([[5, 6]], SamplingParams(max_tokens=7, temperature=0.0,
+                                                  guided=GuidedDecodingParams("ebnf", grammar=g, jump_forward=True)))[0]
+    assert short.token_ids == plain.token_ids[:7] and short.finish_reason == "length"
+    # a log-probability report keeps one row per token: such a request decodes token by token
+    mark = llm.session.jump_forward_tokens
+    lp_out = llm.generate([[5, 6]], sp(True, logprobs=1))[0]
+    assert lp_out.text == plain.text and len(lp_out.logprobs) == len(lp_out.token_ids) and llm.session.jump_forward_tokens == mark > before
+    llm.close()
