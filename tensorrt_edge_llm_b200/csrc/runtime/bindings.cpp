@@ -494,6 +494,10 @@ PYBIND11_MODULE(_telb_runtime, m) {
         });
     m.def("parse_image", [](py::bytes b) { return parse_image(std::string(b)); });
     m.def("load_image", &load_image);
+    m.def("decode_png", [](py::bytes b) { return decode_png(std::string(b)); });
+    m.def("decode_jpeg", [](py::bytes b) { return decode_jpeg(std::string(b)); });
+    m.def("inflate_zlib", [](py::bytes b, size_t max_output) { return py::bytes(inflate_zlib(std::string(b), max_output)); },
+          py::arg("stream"), py::arg("max_output") = size_t(1) << 30);
     m.def("image_from_array", [](py::array_t<uint8_t, py::array::c_style | py::array::forcecast> a) {
         if (a.ndim() != 3) throw std::runtime_error("expected an HWC uint8 array");
         Image im;

@@ -1,0 +1,308 @@
+// Sequential Huffman JPEG decoder (ITU T.81 baseline / extended sequential, 8-bit samples).
+//
+// Flow: markers → quantisation tables (DQT), Huffman tables (DHT), frame header (SOF0 / SOF1), restart interval (DRI) →
+// for every MCU of the scan: per component block, a DC difference and run-length coded AC coefficients in zig-zag order
+// → dequantise → 8×8 inverse DCT → planes → chroma interpolated up to the luma grid → YCbCr → RGB.
+// Counterpart in the reference: the stb_image header behind cpp/runtime/imageUtils.cpp.
+#include "media.h"
+
+#include <algorithm>
+#include <array>
+#include <cmath>
+#include <cstring>
+#include <stdexcept>
+
+namespace telb {
+namespace {
+
+[[noreturn]] void bad(const char* what) { throw std::runtime_error(what); }
+
+const uint8_t kZigzag[64] = {0,  1,  8,  16, 9,  2,  3,  10, 17, 24, 32, 25, 18, 11, 4,  5,  12, 19, 26, 33, 40, 48,
+                             41, 34, 27, 20, 13, 6,  7,  14, 21, 28, 35, 42, 49, 56, 57, 50, 43, 36, 29, 22, 15, 23,
+                             30, 37, 44, 51, 58, 59, 52, 45, 38, 31, 39, 46, 53, 60, 61, 54, 47, 55, 62, 63};
+
+struct JHuff {
+    bool set = false;
+    std::array<int, 18> mincode{}, maxcode{}, valptr{};
+    std::vector<uint8_t> vals;
+    void build(const uint8_t* counts, const uint8_t* symbols, int total) {
+        vals.assign(symbols, symbols + total);
+        int code = 0, k = 0;
+        for (int len = 1; len <= 16; ++len) {
+            valptr[len] = k;
+            mincode[len] = code;
+            code += counts[len - 1];
+            k += counts[len - 1];
+            maxcode[len] = counts[len - 1] ? code - 1 : -1;
+            code <<= 1;
+        }
+        set = true;
+    }
+};
+
+struct BitsMsb {
+    const uint8_t* p;
+    size_t n, at;
+    uint32_t buf = 0;
+    int cnt = 0;
+    bool hit_marker = false;
+    int bit() {
+        if (cnt == 0) {
+            uint8_t b = 0;
+            if (!hit_marker && at < n) {
+                b = p[at];
+                if (b == 0xff) {
+                    if (at + 1 < n && p[at + 1] == 0x00) {
+                        at += 2;                                 // stuffed zero after a data byte of 0xff
+                    } else {
+                        hit_marker = true;                       // a marker: the scan's data is over, feed zeros
+                        b = 0;
+                    }
+                } else {
+                    ++at;
+                }
+            }
+            buf = b;
+            cnt = 8;
+        }
+        --cnt;
+        return (buf >> cnt) & 1;
+    }
+    int bits(int k) {
+        int v = 0;
+        for (int i = 0; i < k; ++i) v = (v << 1) | bit();
+        return v;
+    }
+    void reset() { cnt = 0; hit_marker = false; }
+};
+
+int decode_symbol(BitsMsb& s, const JHuff& h) {
+    int code = 0;
+    for (int len = 1; len <= 16; ++len) {
+        code = (code << 1) | s.bit();
+        if (h.maxcode[len] >= 0 && code <= h.maxcode[len] && code >= h.mincode[len]) return h.vals[h.valptr[len] + code - h.mincode[len]];
+    }
+    bad("invalid Huffman code in a JPEG scan");
+}
+
+inline int extend(int v, int bits) { return bits && v < (1 << (bits - 1)) ? v - (1 << bits) + 1 : v; }
+
+struct Component {
+    int id = 0, h = 1, v = 1, tq = 0, td = 0, ta = 0, pred = 0;
+    int stride = 0, rows = 0;
+    std::vector<uint8_t> plane;
+};
+
+void idct8x8(const float* in, uint8_t* out, int stride) {
+    static float c[8][8];
+    static bool init = false;
+    if (!init) {
+        for (int x = 0; x < 8; ++x)
+            for (int u = 0; u < 8; ++u) c[x][u] = (u == 0 ? std::sqrt(0.125f) : 0.5f) * std::cos((2 * x + 1) * u * 3.14159265358979323846f / 16);
+        init = true;
+    }
+    float tmp[64];
+    for (int y = 0; y < 8; ++y)                      // rows: sum over horizontal frequency u
+        for (int x = 0; x < 8; ++x) {
+            float s = 0;
+            for (int u = 0; u < 8; ++u) s += c[x][u] * in[y * 8 + u];
+            tmp[y * 8 + x] = s;
+        }
+    for (int x = 0; x < 8; ++x)                      // columns: sum over vertical frequency v
+        for (int y = 0; y < 8; ++y) {
+            float s = 0;
+            for (int v = 0; v < 8; ++v) s += c[y][v] * tmp[v * 8 + x];
+            const int q = static_cast<int>(std::lround(s + 128.f));
+            out[y * stride + x] = static_cast<uint8_t>(std::min(std::max(q, 0), 255));
+        }
+}
+
+}  // namespace
+
+Image decode_jpeg(const std::string& bytes) {
+    const uint8_t* p = reinterpret_cast<const uint8_t*>(bytes.data());
+    const size_t n = bytes.size();
+    if (n < 4 || p[0] != 0xff || p[1] != 0xd8) bad("not a JPEG file");
+    std::array<std::array<uint16_t, 64>, 4> qt{};
+    std::array<JHuff, 4> dc, ac;
+    std::vector<Component> comps;
+    int width = 0, height = 0, restart = 0, adobe_transform = -1;
+    size_t at = 2;
+    bool decoded = false;
+    while (at + 4 <= n && !decoded) {
+        if (p[at] != 0xff) { ++at; continue; }
+        const int marker = p[at + 1];
+        if (marker == 0xff) { ++at; continue; }       // fill bytes
+        at += 2;
+        if (marker == 0xd8 || marker == 0x01 || (marker >= 0xd0 && marker <= 0xd7)) continue;
+        if (marker == 0xd9) break;
+        if (at + 2 > n) bad("truncated JPEG segment");
+        const size_t len = (p[at] << 8) | p[at + 1];
+        if (len < 2 || at + len > n) bad("truncated JPEG segment");
+        const uint8_t* d = p + at + 2;
+        const size_t dn = len - 2;
+        if (marker == 0xdb) {                                           // DQT
+            size_t i = 0;
+            while (i < dn) {
+                const int pq = d[i] >> 4, tq = d[i] & 15;
+                ++i;
+                if (tq > 3 || i + (pq ? 128 : 64) > dn) bad("bad JPEG quantisation table");
+                for (int k = 0; k < 64; ++k) {
+                    qt[tq][kZigzag[k]] = pq ? static_cast<uint16_t>((d[i] << 8) | d[i + 1]) : d[i];
+                    i += pq ? 2 : 1;
+                }
+            }
+        } else if (marker == 0xc4) {                                    // DHT
+            size_t i = 0;
+            while (i + 17 <= dn) {
+                const int tc = d[i] >> 4, th = d[i] & 15;
+                int total = 0;
+                for (int k = 0; k < 16; ++k) total += d[i + 1 + k];
+                if (tc > 1 || th > 3 || total > 256 || i + 17 + total > dn) bad("bad JPEG Huffman table");
+                (tc ? ac : dc)[th].build(d + i + 1, d + i + 17, total);
+                i += 17 + total;
+            }
+        } else if (marker == 0xc0 || marker == 0xc1) {                  // SOF0 / SOF1
+            if (dn < 6 || d[0] != 8) bad("only 8-bit JPEG images are read");
+            height = (d[1] << 8) | d[2];
+            width = (d[3] << 8) | d[4];
+            const int nc = d[5];
+            if ((nc != 1 && nc != 3) || dn < 6 + 3 * static_cast<size_t>(nc)) bad("JPEG images with one or three components are read");
+            if (width <= 0 || height <= 0 || width > (1 << 15) || height > (1 << 15)) bad("JPEG size out of range");
+            comps.assign(nc, Component());
+            for (int k = 0; k < nc; ++k) {
+                comps[k].id = d[6 + 3 * k];
+                comps[k].h = d[7 + 3 * k] >> 4;
+                comps[k].v = d[7 + 3 * k] & 15;
+                comps[k].tq = d[8 + 3 * k];
+                if (comps[k].h < 1 || comps[k].h > 2 || comps[k].v < 1 || comps[k].v > 2 || comps[k].tq > 3) bad("JPEG sampling factors other than 1 and 2 are not read");
+            }
+        } else if (marker == 0xc2) {
+            bad("progressive JPEG images are not read (re-encode as baseline)");
+        } else if (marker >= 0xc3 && marker <= 0xcf && marker != 0xc4 && marker != 0xc8 && marker != 0xcc) {
+            bad("this JPEG coding process (lossless, hierarchical or arithmetic) is not read");
+        } else if (marker == 0xdd) {                                    // DRI
+            if (dn < 2) bad("bad JPEG restart interval");
+            restart = (d[0] << 8) | d[1];
+        } else if (marker == 0xee) {                                    // APP14 "Adobe": colour transform flag
+            if (dn >= 12 && !std::memcmp(d, "Adobe", 5)) adobe_transform = d[11];
+        } else if (marker == 0xda) {                                    // SOS: decode the (single) scan
+            if (comps.empty()) bad("JPEG scan before its frame header");
+            const int ns = d[0];
+            if (ns != static_cast<int>(comps.size()) || dn < 1 + 2 * static_cast<size_t>(ns) + 3) bad("JPEG scans must hold every component (non-interleaved scans are not read)");
+            for (int k = 0; k < ns; ++k) {
+                const int id = d[1 + 2 * k];
+                auto it = std::find_if(comps.begin(), comps.end(), [&](const Component& c) { return c.id == id; });
+                if (it == comps.end()) bad("JPEG scan names an unknown component");
+                it->td = d[2 + 2 * k] >> 4;
+                it->ta = d[2 + 2 * k] & 15;
+                if (it->td > 3 || it->ta > 3 || !dc[it->td].set || !ac[it->ta].set) bad("JPEG scan uses a Huffman table that was not defined");
+            }
+            int hmax = 1, vmax = 1;
+            for (auto& c : comps) { hmax = std::max(hmax, c.h); vmax = std::max(vmax, c.v); }
+            const int mcux = (width + 8 * hmax - 1) / (8 * hmax), mcuy = (height + 8 * vmax - 1) / (8 * vmax);
+            for (auto& c : comps) {
+                c.stride = mcux * c.h * 8;
+                c.rows = mcuy * c.v * 8;
+                c.plane.assign(static_cast<size_t>(c.stride) * c.rows, 0);
+                c.pred = 0;
+            }
+            BitsMsb s{p, n, at + len};
+            int until_restart = restart;
+            float block[64];
+            for (int my = 0; my < mcuy; ++my)
+                for (int mx = 0; mx < mcux; ++mx) {
+                    if (restart && until_restart == 0) {
+                        // byte-align, step over the RSTn marker, reset the DC predictors
+                        s.reset();
+                        while (s.at + 1 < n && !(p[s.at] == 0xff && p[s.at + 1] >= 0xd0 && p[s.at + 1] <= 0xd7)) ++s.at;
+                        if (s.at + 1 >= n) bad("JPEG restart marker missing");
+                        s.at += 2;
+                        for (auto& c : comps) c.pred = 0;
+                        until_restart = restart;
+                    }
+                    for (auto& c : comps)
+                        for (int by = 0; by < c.v; ++by)
+                            for (int bx = 0; bx < c.h; ++bx) {
+                                std::fill(block, block + 64, 0.f);
+                                const int t = decode_symbol(s, dc[c.td]);
+                                if (t > 11) bad("bad JPEG DC category");
+                                c.pred += extend(s.bits(t), t);
+                                block[0] = static_cast<float>(c.pred) * qt[c.tq][0];
+                                for (int k = 1; k < 64;) {
+                                    const int rs = decode_symbol(s, ac[c.ta]);
+                                    const int r = rs >> 4, sz = rs & 15;
+                                    if (sz == 0) {
+                                        if (r == 15) { k += 16; continue; }
+                                        break;                         // end of block
+                                    }
+                                    k += r;
+                                    if (k > 63) bad("JPEG AC run leaves the block");
+                                    const int z = kZigzag[k];
+                                    block[z] = static_cast<float>(extend(s.bits(sz), sz)) * qt[c.tq][z];
+                                    ++k;
+                                }
+                                const int x0 = (mx * c.h + bx) * 8, y0 = (my * c.v + by) * 8;
+                                idct8x8(block, &c.plane[static_cast<size_t>(y0) * c.stride + x0], c.stride);
+                            }
+                    if (restart) --until_restart;
+                }
+            decoded = true;
+        }
+        at += len;
+    }
+    if (!decoded) bad("JPEG file without image data");
+    int hmax = 1, vmax = 1;
+    for (auto& c : comps) { hmax = std::max(hmax, c.h); vmax = std::max(vmax, c.v); }
+    Image im;
+    im.width = width;
+    im.height = height;
+    im.channels = 3;
+    im.pixels.resize(static_cast<size_t>(width) * height * 3);
+    const bool ycc = comps.size() == 3 && adobe_transform != 0;
+    for (int y = 0; y < height; ++y)
+        for (int x = 0; x < width; ++x) {
+            int v[3] = {0, 128, 128};
+            for (size_t k = 0; k < comps.size(); ++k) {
+                const Component& c = comps[k];
+                if (c.h == hmax && c.v == vmax) {
+                    v[k] = c.plane[static_cast<size_t>(y) * c.stride + x];
+                    continue;
+                }
+                // subsampled plane: triangle filter between the two nearest samples per axis (weights 3/4 and 1/4, the
+                // "fancy upsampling" of the common decoders), edges replicated
+                const int cw = (width * c.h + hmax - 1) / hmax, ch = (height * c.v + vmax - 1) / vmax;
+                int x0 = x, x1 = x, y0 = y, y1 = y;
+                if (c.h != hmax) {
+                    x0 = x >> 1;
+                    x1 = std::min(std::max((x & 1) ? x0 + 1 : x0 - 1, 0), cw - 1);
+                }
+                if (c.v != vmax) {
+                    y0 = y >> 1;
+                    y1 = std::min(std::max((y & 1) ? y0 + 1 : y0 - 1, 0), ch - 1);
+                }
+                auto at_ = [&](int yy, int xx) { return static_cast<int>(c.plane[static_cast<size_t>(yy) * c.stride + xx]); };
+                const int wx1 = c.h != hmax ? 1 : 0, wy1 = c.v != vmax ? 1 : 0;       // weights in quarters: far sample, near sample
+                const int wx_near = 4 - wx1, wy_near = 4 - wy1;
+                const int sum = wy_near * (wx_near * at_(y0, x0) + wx1 * at_(y0, x1)) + wy1 * (wx_near * at_(y1, x0) + wx1 * at_(y1, x1));
+                v[k] = (sum + 8) >> 4;
+            }
+            uint8_t* px = &im.pixels[(static_cast<size_t>(y) * width + x) * 3];
+            if (comps.size() == 1) {
+                px[0] = px[1] = px[2] = static_cast<uint8_t>(v[0]);
+            } else if (ycc) {
+                const float Y = static_cast<float>(v[0]), cb = v[1] - 128.f, cr = v[2] - 128.f;
+                auto clamp8 = [](float f) { return static_cast<uint8_t>(std::min(std::max(static_cast<int>(std::lround(f)), 0), 255)); };
+                px[0] = clamp8(Y + 1.402f * cr);
+                px[1] = clamp8(Y - 0.344136f * cb - 0.714136f * cr);
+                px[2] = clamp8(Y + 1.772f * cb);
+            } else {
+                px[0] = static_cast<uint8_t>(v[0]);
+                px[1] = static_cast<uint8_t>(v[1]);
+                px[2] = static_cast<uint8_t>(v[2]);
+            }
+        }
+    return im;
+}
+
+}  // namespace telb

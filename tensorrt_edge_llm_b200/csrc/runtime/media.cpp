@@ -201,6 +201,8 @@ int next_int(const std::string& b, size_t& at) {
 
 Image parse_image(const std::string& b) {
     Image im;
+    if (b.size() >= 8 && static_cast<uint8_t>(b[0]) == 0x89 && b[1] == 'P' && b[2] == 'N' && b[3] == 'G') return decode_png(b);
+    if (b.size() >= 3 && static_cast<uint8_t>(b[0]) == 0xff && static_cast<uint8_t>(b[1]) == 0xd8) return decode_jpeg(b);
     if (b.size() >= 2 && b[0] == 'P' && (b[1] == '6' || b[1] == '5')) {
         size_t at = 2;
         im.channels = b[1] == '6' ? 3 : 1;
@@ -245,7 +247,7 @@ Image parse_image(const std::string& b) {
         }
         return im;
     }
-    throw std::runtime_error("unsupported image container (binary PPM / PGM and uncompressed BMP are read)");
+    throw std::runtime_error("unsupported image container (PNG, baseline JPEG, binary PPM / PGM and uncompressed BMP are read)");
 }
 
 Image load_image(const std::string& path) { return parse_image(read_file(path)); }

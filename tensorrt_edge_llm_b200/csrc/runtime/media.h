@@ -3,7 +3,8 @@
 //
 // Counterparts in the reference: cpp/runtime/{audioLoader,audioUtils,melSpectrogram,imageUtils}.cpp (which lean on
 // the third-party miniaudio and stb single-header libraries; here the formats that need no entropy decoder are
-// parsed directly: RIFF/WAVE PCM16 / PCM24 / PCM32 / float32, binary PPM / PGM and uncompressed BMP).
+// parsed directly: RIFF/WAVE PCM16 / PCM24 / PCM32 / float32, binary PPM / PGM and uncompressed BMP; PNG and
+// sequential JPEG have decoders of their own in image_codecs.cpp / jpeg_decoder.cpp).
 #pragma once
 
 #include <cstdint>
@@ -43,7 +44,11 @@ struct Image {
     std::vector<uint8_t> pixels;     // HWC
 };
 
-Image parse_image(const std::string& bytes);                         // PPM (P6), PGM (P5), BMP 24 / 32 bit
+Image parse_image(const std::string& bytes);                         // by magic: PNG, JPEG, PPM (P6), PGM (P5), BMP 24 / 32 bit
+Image decode_png(const std::string& bytes);                          // non-interlaced; always returns RGB
+Image decode_jpeg(const std::string& bytes);                         // sequential Huffman (baseline); always returns RGB
+// RFC 1950 zlib stream → bytes; throws when the output would exceed `max_output`.
+std::string inflate_zlib(const std::string& stream, size_t max_output);
 Image load_image(const std::string& path);
 Image resize_bilinear(const Image& im, int out_w, int out_h);
 Image resize_bicubic(const Image& im, int out_w, int out_h);
