@@ -13,6 +13,7 @@ from typing import List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
+from ..models.qwen_vl_vision import QwenVisionEncoder, patchify_frames
 from ..models.vit import EncoderCache, VisionEncoder, dart_prune, encode_data_parallel
 from ..ops import reference as ref
 from . import native as rt
@@ -48,6 +49,7 @@ class MultimodalRunner:
         self.keep_ratio = visual_keep_ratio
         self.min_pixels, self.max_pixels = min_pixels, max_pixels
         self.device = llm.device
+        self._grids: List[Tuple[int, int, int]] = []      # (t, rows, columns) of each encoded image in language-model tokens
 
     # ---- media → rows ------------------------------------------------------------------------------------
     def _image_patches(self, image) -> torch.Tensor:
@@ -64,11 +66,51 @@ class MultimodalRunner:
         chw = torch.from_numpy(rt.normalize_chw(image, list(IMAGE_MEAN), list(IMAGE_STD)))
         return VisionEncoder.patchify(chw[None], c.patch_size)
 
+    def _decode(self, image):
+        if isinstance(image, (bytes, bytearray)):
+            return rt.parse_image(bytes(image))
+        if isinstance(image, str):
+            return rt.load_image(image)
+        if isinstance(image, np.ndarray):
+            return rt.image_from_array(np.ascontiguousarray(image, dtype=np.uint8))
+        return image
+
+    def _encode_qwen(self, images: Sequence) -> List[torch.Tensor]:
+        """Qwen-VL towers take images at (nearly) their own aspect ratio: sides are rounded to multiples of patch × merge
+        inside the pixel budget, and every image brings its own ``(t, h, w)`` grid."""
+        c = self.vision.cfg
+        factor = c.patch_size * c.spatial_merge_size
+        lo = self.min_pixels or 4 * factor * factor
+        hi = self.max_pixels or 1280 * factor * factor
+        mats, grids = [], []
+        for im in images:
+            im = self._decode(im)
+            hh, ww = rt.smart_resize(im.height, im.width, factor, lo, hi)
+            if (im.height, im.width) != (hh, ww):
+                im = rt.resize_bicubic(im, ww, hh)
+            chw = torch.from_numpy(rt.normalize_chw(im, list(IMAGE_MEAN), list(IMAGE_STD)))
+            m, g = patchify_frames(chw[None], c)
+            mats.append(m)
+            grids.append(g)
+        rows = self.vision(torch.cat(mats, 0).to(self.device), grids)
+        m = c.spatial_merge_size
+        self._grids = [(t, h // m, w // m) for t, h, w in grids]
+        out, at = [], 0
+        for t, h, w in self._grids:
+            out.append(rows[at:at + t * h * w])
+            at += t * h * w
+        return out
+
     def encode_images(self, images: Sequence) -> List[torch.Tensor]:
+        self._grids = []
         if not images:
             return []
         if self.vision is None:
             raise ValueError("this runner has no vision encoder")
+        if isinstance(self.vision, QwenVisionEncoder):
+            if self.keep_ratio < 1.0:
+                raise ValueError("visual-token pruning is not combined with grid-shaped (multimodal RoPE) image rows")
+            return self._encode_qwen(images)
         patches = torch.cat([self._image_patches(im) for im in images], 0).to(self.device)
         enc = (lambda x: encode_data_parallel(self.vision, x, self.llm.model.comm))
         rows = self.cache.encode(enc, patches) if self.cache is not None else enc(patches)
@@ -111,7 +153,10 @@ class MultimodalRunner:
                 ids += [self.image_token_id] * rows.shape[0]
                 media_rows.append(rows)
                 side = int(round(rows.shape[0] ** 0.5))
-                grids.append((1, side, side) if side * side == rows.shape[0] else (1, 1, rows.shape[0]))
+                if self._grids:
+                    grids.append(self._grids[ii - 1])
+                else:
+                    grids.append((1, side, side) if side * side == rows.shape[0] else (1, 1, rows.shape[0]))
             else:
                 rows = clips[ai]
                 ai += 1

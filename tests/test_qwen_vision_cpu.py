@@ -1,0 +1,127 @@
+"""Qwen2-VL / Qwen2.5-VL vision towers against the Hugging Face implementations (same random weights, fp32)."""
+import pytest
+import torch
+
+from tensorrt_edge_llm_b200.models.qwen_vl_vision import (QwenVisionConfig, QwenVisionEncoder, patchify_frames, rotary_rows, window_order)
+
+GRIDS = [(1, 6, 10), (2, 4, 4), (1, 2, 2)]
+
+
+def _patches(cfg, grids, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(sum(t * h * w for t, h, w in grids), cfg.patch_dim, generator=g)
+
+
+def test_qwen2_5_vl_window_attention_matches_hf():
+    from transformers.models.qwen2_5_vl.configuration_qwen2_5_vl import Qwen2_5_VLVisionConfig
+    from transformers.models.qwen2_5_vl.modeling_qwen2_5_vl import Qwen2_5_VisionTransformerPretrainedModel
+    hc = Qwen2_5_VLVisionConfig(depth=4, hidden_size=80, intermediate_size=96, num_heads=4, patch_size=14, spatial_merge_size=2,
+                                temporal_patch_size=2, window_size=56, out_hidden_size=48, fullatt_block_indexes=[1, 3])
+    hc._attn_implementation = "eager"
+    torch.manual_seed(0)
+    hf = Qwen2_5_VisionTransformerPretrainedModel(hc).eval().float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "norm" in n or "ln_q" in n or n.endswith("bias"):
+                p.copy_(torch.randn_like(p) * 0.3 + (1.0 if n.endswith("weight") else 0.0))
+    cfg = QwenVisionConfig.from_hf(hc.to_dict())
+    cfg.dtype = "float32"
+    assert cfg.gated_mlp and cfg.window_size == 56 and cfg.head_dim == 20 and cfg.padded_head_dim == 64
+    enc = QwenVisionEncoder(cfg)
+    left = enc.load_hf_state_dict({"visual." + k: v for k, v in hf.state_dict().items()})
+    assert left == []
+    x = _patches(cfg, GRIDS)
+    with torch.no_grad():
+        want = hf(x, grid_thw=torch.tensor(GRIDS)).pooler_output
+    got = enc(x, GRIDS)
+    assert got.shape == want.shape == (sum(t * h * w for t, h, w in GRIDS) // 4, 48)
+    assert (got - want).abs().max() < 2e-4 * max(1.0, want.abs().max().item())
+    # the window order is a permutation, windows at the edges are smaller, and every frame is covered
+    order, lengths = window_order(GRIDS, 56, 2, 14)
+    assert sorted(order.tolist()) == list(range(15 + 8 + 1)) and sum(lengths) == x.shape[0]
+    assert lengths[:6] == [16, 16, 8, 8, 8, 4]              # 3 × 5 merged units in 2 × 2 windows: 2x2, 2x2, 2x1, 1x2, 1x2, 1x1 units
+
+
+def test_qwen2_vl_full_attention_matches_hf():
+    from transformers.models.qwen2_vl.configuration_qwen2_vl import Qwen2VLVisionConfig
+    from transformers.models.qwen2_vl.modeling_qwen2_vl import Qwen2VisionTransformerPretrainedModel
+    hc = Qwen2VLVisionConfig(depth=3, embed_dim=64, hidden_size=40, mlp_ratio=2, num_heads=4, patch_size=14, spatial_merge_size=2,
+                             temporal_patch_size=2)
+    hc._attn_implementation = "eager"
+    torch.manual_seed(1)
+    hf = Qwen2VisionTransformerPretrainedModel(hc).eval().float()
+    cfg = QwenVisionConfig.from_hf(hc.to_dict())
+    cfg.dtype = "float32"
+    assert not cfg.gated_mlp and cfg.window_size == 0 and cfg.intermediate_size == 128 and cfg.out_hidden_size == 40
+    enc = QwenVisionEncoder(cfg)
+    assert enc.load_hf_state_dict(hf.state_dict(), prefix="") == []
+    x = _patches(cfg, GRIDS, seed=2)
+    with torch.no_grad():
+        out = hf(x, grid_thw=torch.tensor(GRIDS))
+    want = out.pooler_output if hasattr(out, "pooler_output") else out
+    got = enc(x, GRIDS)
+    assert (got - want).abs().max() < 2e-4 * max(1.0, want.abs().max().item())
+
+
+def test_rotary_rows_and_patchify():
+    t = rotary_rows([(1, 4, 6)], 16, 2)
+    assert t.shape == (24, 16)
+    # block order: the first four patches are rows 0-1 × columns 0-1; row angles sit in pairs 0..3, column angles in 4..7
+    inv0 = 1.0
+    assert torch.allclose(t[1, 4], torch.cos(torch.tensor(1.0 * inv0))) and torch.allclose(t[2, 0], torch.cos(torch.tensor(1.0 * inv0)))
+    assert torch.allclose(t[0, :8], torch.ones(8)) and torch.allclose(t[0, 8:], torch.zeros(8))
+    cfg = QwenVisionConfig(depth=1, hidden_size=64, num_heads=1, intermediate_size=64, out_hidden_size=32, dtype="float32")
+    img = torch.arange(3 * 56 * 84, dtype=torch.float32).reshape(1, 3, 56, 84)
+    p, grid = patchify_frames(img, cfg)
+    assert grid == (1, 4, 6) and p.shape == (24, 3 * 2 * 14 * 14)
+    # patch 1 of the first block is row 0, column 1; channel 0, both temporal copies hold the same pixels
+    first = p[1].reshape(3, 2, 14, 14)
+    assert torch.equal(first[0, 0], img[0, 0, :14, 14:28]) and torch.equal(first[0, 1], first[0, 0])
+    # patch 2 of the first block is row 1, column 0
+    assert torch.equal(p[2].reshape(3, 2, 14, 14)[1, 0], img[0, 1, 14:28, :14])
+    with pytest.raises(ValueError):
+        patchify_frames(torch.zeros(1, 3, 50, 84), cfg)
+    enc = QwenVisionEncoder(cfg).random_init(0)
+    with pytest.raises(ValueError):
+        enc(p[:-1], [grid])
+
+
+def test_multimodal_runner_with_qwen_tower():
+    """End to end: image bytes → smart resize → patches → tower → rows spliced into the prompt with grid-shaped 3-D positions."""
+    import numpy as np
+    from tensorrt_edge_llm_b200.config import tiny_llama_config
+    from tensorrt_edge_llm_b200.runtime import native as rt
+    from tensorrt_edge_llm_b200.runtime.llm import LLM
+    from tensorrt_edge_llm_b200.runtime.multimodal import MultimodalInputs, MultimodalRunner
+    cfg = tiny_llama_config(num_hidden_layers=2, vocab_size=200, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                            dtype="float32")
+    cfg.mrope_section = [2, 3, 3]
+    llm = LLM(cfg, device="cpu", max_batch_size=1, max_input_len=256, max_kv_cache_capacity=320, page_size=16)
+    vc = QwenVisionConfig(depth=2, hidden_size=64, num_heads=4, intermediate_size=64, out_hidden_size=64, window_size=56,
+                          fullatt_block_indexes=[1], dtype="float32")
+    tower = QwenVisionEncoder(vc).random_init(3)
+    mm = MultimodalRunner(llm, vision=tower, image_token_id=7, min_pixels=28 * 28 * 4, max_pixels=28 * 28 * 40)
+    rng = np.random.default_rng(0)
+    wide = rng.integers(0, 255, (60, 170, 3), dtype=np.uint8)                 # → 56 × 168: grid 4 × 12 patches, 2 × 6 tokens
+    tall = rng.integers(0, 255, (120, 50, 3), dtype=np.uint8)
+    req = MultimodalInputs().text([3, 4]).image(wide).text([5]).image(tall).text([6, 8])
+    ids, emb, pos3, delta = mm.build(req)
+    g0, g1 = mm._grids
+    assert g0 == (1, 2, 6) and g1[0] == 1 and g1[1] > g1[2]
+    n0, n1 = g0[1] * g0[2], g1[1] * g1[2]
+    assert ids.count(7) == n0 + n1 and emb.shape == (len(ids), 64)
+    # positions of the first image: rows count 0..1, columns 0..5 from the text offset 2
+    img0 = pos3[:, 2:2 + n0]
+    assert img0[0].tolist() == [2] * n0 and img0[1].tolist() == [2 + r for r in range(2) for _ in range(6)]
+    assert img0[2].tolist() == [2 + c for _ in range(2) for c in range(6)]
+    assert delta == int(pos3.max()) + 1 - len(ids)
+    out = mm.generate(req, max_tokens=4)
+    assert len(out) == 4
+    # PNG bytes go through the native decoder to the same rows
+    PIL = pytest.importorskip("PIL.Image")
+    import io
+    buf = io.BytesIO()
+    PIL.fromarray(wide).save(buf, "PNG")
+    rows_png = mm.encode_images([buf.getvalue()])[0]
+    rows_arr = mm.encode_images([wide])[0]
+    assert torch.equal(rows_png, rows_arr)
