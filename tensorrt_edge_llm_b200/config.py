@@ -371,7 +371,7 @@ class ModelConfig:
             max_position_embeddings=int(llm.get("max_position_embeddings", 32768)),
             tie_word_embeddings=bool(hf.get("tie_word_embeddings", llm.get("tie_word_embeddings", False))),
             has_qk_norm=bool(has_qk_norm),
-            attention_bias=bool(llm.get("attention_bias", model_type == "qwen2")),
+            attention_bias=bool(llm.get("attention_bias", str(model_type).startswith("qwen2"))),     # Qwen2 family (text, MoE, VL): q/k/v carry a bias
             sliding_window=llm.get("sliding_window") if (llm.get("use_sliding_window", False) or extra) else None,
             hidden_act=llm.get("hidden_activation") or llm.get("hidden_act", llm.get("mlp_hidden_act", "silu")),
             **extra,

@@ -251,6 +251,30 @@ class QwenVisionEncoder(nn.Module):
             put(lin.bias, take(name + ".bias"))
         return sorted(set(sd) - used)
 
+    @classmethod
+    def from_pretrained(cls, model_dir: str, device="cpu", dtype: Optional[str] = None) -> "QwenVisionEncoder":
+        """Build the tower from a Qwen2-VL / Qwen2.5-VL checkpoint directory (``vision_config`` of ``config.json``, tensors
+        named ``visual.*`` or ``model.visual.*`` in its safetensors files)."""
+        import json
+        import os
+        from ..checkpoint.safetensors_io import CheckpointReader
+        with open(os.path.join(model_dir, "config.json"), "r", encoding="utf-8") as f:
+            hf = json.load(f)
+        if "vision_config" not in hf:
+            raise ValueError(f"{model_dir} has no vision_config")
+        cfg = QwenVisionConfig.from_hf(hf["vision_config"])
+        cfg.dtype = dtype or str(hf.get("torch_dtype", hf.get("dtype", "bfloat16"))).replace("torch.", "")
+        enc = cls(cfg)
+        reader = CheckpointReader(model_dir)
+        names = [k for k in reader.keys() if k.startswith(("visual.", "model.visual."))]
+        if not names:
+            raise ValueError(f"{model_dir} holds no visual.* tensors")
+        prefix = "model.visual." if names[0].startswith("model.") else "visual."
+        left = enc.load_hf_state_dict({k: reader.get(k) for k in names}, prefix=prefix)
+        if left:
+            raise ValueError(f"unused vision tensors: {left[:4]}…")
+        return enc.to(device)
+
     # ---- forward ---------------------------------------------------------------------------------
     def _meta(self, lengths: Sequence[int], device):
         pages = [(n + self.PAGE - 1) // self.PAGE for n in lengths]

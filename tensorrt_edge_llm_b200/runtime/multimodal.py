@@ -51,6 +51,20 @@ class MultimodalRunner:
         self.device = llm.device
         self._grids: List[Tuple[int, int, int]] = []      # (t, rows, columns) of each encoded image in language-model tokens
 
+    @classmethod
+    def from_pretrained(cls, llm, model_dir: str, **kw) -> Optional["MultimodalRunner"]:
+        """Runner for a vision-language checkpoint directory, or ``None`` when ``config.json`` names no vision tower this
+        build has (Qwen2-VL and Qwen2.5-VL are built).  The image placeholder id comes from ``image_token_id``."""
+        import json
+        import os
+        with open(os.path.join(model_dir, "config.json"), "r", encoding="utf-8") as f:
+            hf = json.load(f)
+        kind = str(hf.get("model_type", ""))
+        if "vision_config" not in hf or kind not in ("qwen2_vl", "qwen2_5_vl"):
+            return None
+        tower = QwenVisionEncoder.from_pretrained(model_dir, device=llm.device, dtype=llm.cfg.dtype)
+        return cls(llm, vision=tower, image_token_id=int(hf.get("image_token_id", 151655)), **kw)
+
     # ---- media → rows ------------------------------------------------------------------------------------
     def _image_patches(self, image) -> torch.Tensor:
         """Decode-side preprocessing: resize to the encoder's square input, normalise, cut into patches ``[1, grid², C·P·P]``."""

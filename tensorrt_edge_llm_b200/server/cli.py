@@ -78,7 +78,11 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         from ..parallel.tp_serving import serve_follower
         serve_follower(llm.runner, build_llm.mirror)
         return 0
-    app = create_app(llm, cfg.api, template, model_name=os.path.basename(os.path.normpath(cfg.model.model)))
+    multimodal = None
+    if os.path.isdir(cfg.model.model):                   # vision-language checkpoints bring their tower along
+        from ..runtime.multimodal import MultimodalRunner
+        multimodal = MultimodalRunner.from_pretrained(llm, cfg.model.model)
+    app = create_app(llm, cfg.api, template, model_name=os.path.basename(os.path.normpath(cfg.model.model)), multimodal=multimodal)
     try:
         uvicorn.run(app, host=cfg.api.host, port=cfg.api.port, log_level=cfg.api.log_level)
     finally:

@@ -125,3 +125,57 @@ def test_multimodal_runner_with_qwen_tower():
     rows_png = mm.encode_images([buf.getvalue()])[0]
     rows_arr = mm.encode_images([wide])[0]
     assert torch.equal(rows_png, rows_arr)
+
+
+def test_runner_from_a_vision_language_checkpoint(tmp_path):
+    """A Qwen2.5-VL style directory (nested text_config, ``model.language_model.*`` and ``model.visual.*`` tensors) loads into the
+    language model and the tower; the tower's rows equal the Hugging Face tower's."""
+    import json
+    import os
+    from transformers.models.qwen2_5_vl.configuration_qwen2_5_vl import Qwen2_5_VLVisionConfig
+    from transformers.models.qwen2_5_vl.modeling_qwen2_5_vl import Qwen2_5_VisionTransformerPretrainedModel
+    from tensorrt_edge_llm_b200.checkpoint import save_file
+    from tensorrt_edge_llm_b200.runtime.llm import LLM
+    from tensorrt_edge_llm_b200.runtime.multimodal import MultimodalRunner
+    vc = Qwen2_5_VLVisionConfig(depth=2, hidden_size=64, intermediate_size=64, num_heads=4, window_size=56, out_hidden_size=64,
+                                fullatt_block_indexes=[1])
+    vc._attn_implementation = "eager"
+    torch.manual_seed(4)
+    tower = Qwen2_5_VisionTransformerPretrainedModel(vc).eval().float()
+    text = dict(model_type="qwen2_5_vl_text", vocab_size=160, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, max_position_embeddings=512, rms_norm_eps=1e-6, rope_theta=10000.0, tie_word_embeddings=True,
+                rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]}, dtype="float32")
+    g = torch.Generator().manual_seed(5)
+    sd = {"model.visual." + k: v.contiguous() for k, v in tower.state_dict().items()}
+    lm = "model.language_model."
+    sd[lm + "embed_tokens.weight"] = torch.randn(160, 64, generator=g) * 0.05
+    sd[lm + "norm.weight"] = torch.ones(64)
+    for i in range(2):
+        p = f"{lm}layers.{i}."
+        for name, shape in (("self_attn.q_proj", (64, 64)), ("self_attn.k_proj", (32, 64)), ("self_attn.v_proj", (32, 64)), ("self_attn.o_proj", (64, 64)),
+                            ("mlp.gate_proj", (128, 64)), ("mlp.up_proj", (128, 64)), ("mlp.down_proj", (64, 128))):
+            sd[p + name + ".weight"] = torch.randn(*shape, generator=g) * 0.05
+        for name, n in (("self_attn.q_proj", 64), ("self_attn.k_proj", 32), ("self_attn.v_proj", 32)):
+            sd[p + name + ".bias"] = torch.randn(n, generator=g) * 0.05
+        sd[p + "input_layernorm.weight"] = torch.ones(64)
+        sd[p + "post_attention_layernorm.weight"] = torch.ones(64)
+    d = str(tmp_path)
+    save_file(sd, os.path.join(d, "model.safetensors"))
+    json.dump({"model_type": "qwen2_5_vl", "architectures": ["Qwen2_5_VLForConditionalGeneration"], "image_token_id": 150, "dtype": "float32",
+               "text_config": text, "vision_config": vc.to_dict(), "tie_word_embeddings": True}, open(os.path.join(d, "config.json"), "w"))
+    llm = LLM(d, device="cpu", max_batch_size=1, max_input_len=256, max_kv_cache_capacity=320, page_size=16)
+    assert llm.cfg.mrope_section == [2, 3, 3] and llm.cfg.attention_bias
+    mm = MultimodalRunner.from_pretrained(llm, d)
+    assert mm is not None and mm.image_token_id == 150 and mm.vision.cfg.window_size == 56
+    x = _patches(mm.vision.cfg, [(1, 4, 8)], seed=6)
+    with torch.no_grad():
+        want = tower(x, grid_thw=torch.tensor([[1, 4, 8]])).pooler_output
+    assert (mm.vision(x, [(1, 4, 8)]) - want).abs().max() < 2e-4
+    from tensorrt_edge_llm_b200.runtime.multimodal import MultimodalInputs
+    import numpy as np
+    img = np.random.default_rng(1).integers(0, 255, (56, 112, 3), dtype=np.uint8)
+    out = mm.generate(MultimodalInputs().text([11, 12]).image(img).text([13]), max_tokens=3)
+    assert len(out) == 3
+    # a text-only checkpoint has no tower
+    json.dump({"model_type": "llama", **text}, open(os.path.join(d, "config.json"), "w"))
+    assert MultimodalRunner.from_pretrained(llm, d) is None
