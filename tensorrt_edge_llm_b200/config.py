@@ -227,6 +227,12 @@ class ModelConfig:
     eagle3_target_layer_ids: List[int] = field(default_factory=list)   # tapped target layers (default: low / mid / high)
     eagle3_norm_before_residual: bool = False
     draft_vocab_size: int = 0
+    # DFlash block draft (draft_type "dflash"): tapped target layers, proposal block length, id of the mask token, and whether
+    # row i's hidden state predicts position i + 1 (shifted labels) instead of its own position
+    dflash_target_layer_ids: List[int] = field(default_factory=list)
+    dflash_block_size: int = 16
+    dflash_mask_token_id: int = 0
+    dflash_shift_label: bool = False
     # quant / parallel
     quant: QuantConfig = field(default_factory=QuantConfig)
     mapping: Mapping = field(default_factory=Mapping)
@@ -392,8 +398,13 @@ class ModelConfig:
             quant=quant or QuantConfig(),
             bos_token_id=llm.get("bos_token_id"),
             eos_token_id=llm.get("eos_token_id"),
-            draft_type="eagle3" if (llm.get("draft_vocab_size") or "eagle" in str(hf.get("architectures", "")).lower()
-                                    or hf.get("speculators_model_type") == "eagle3") else None,
+            draft_type="dflash" if (llm.get("dflash_config") or "dflash" in str(hf.get("architectures", "")).lower()) else (
+                "eagle3" if (llm.get("draft_vocab_size") or "eagle" in str(hf.get("architectures", "")).lower()
+                             or hf.get("speculators_model_type") == "eagle3") else None),
+            dflash_target_layer_ids=list((llm.get("dflash_config") or {}).get("target_layer_ids", []) or []),
+            dflash_block_size=int((llm.get("dflash_config") or {}).get("block_size", llm.get("block_size", 16)) or 16),
+            dflash_mask_token_id=int((llm.get("dflash_config") or {}).get("mask_token_id", llm.get("mask_token_id", 0)) or 0),
+            dflash_shift_label=bool((llm.get("dflash_config") or {}).get("shift_label", llm.get("dflash_shift_label", False))),
             draft_vocab_size=int(llm.get("draft_vocab_size", 0) or 0),
             eagle3_target_hidden_size=int(llm.get("target_hidden_size", 0) or 0),
             eagle3_target_layer_ids=list((hf.get("eagle_config") or {}).get("eagle_aux_hidden_state_layer_ids", []) or []),

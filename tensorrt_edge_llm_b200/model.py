@@ -30,13 +30,15 @@ def _ensure_builtin():
     from .models.default import CausalLM
     for t in ("llama", "qwen2", "qwen3", "mistral", "phi3", "gemma", "default"):
         _REGISTRY[t] = CausalLM
-    from .models import qwen3_moe, nemotron_h, eagle3, mtp, gemma, diffusion_gemma  # noqa: F401  (register themselves)
+    from .models import qwen3_moe, nemotron_h, eagle3, mtp, gemma, diffusion_gemma, dflash  # noqa: F401  (register themselves)
 
 
 def model_class_for(cfg: ModelConfig):
     _ensure_builtin()
     if cfg.draft_type == "eagle3":
         return _REGISTRY["eagle3"]
+    if cfg.draft_type == "dflash":
+        return _REGISTRY["dflash"]
     if cfg.draft_type == "mtp":
         return _REGISTRY["mtp"]
     if cfg.model_type in _REGISTRY:

@@ -1,0 +1,185 @@
+"""DFlash speculative decoding: a block draft proposes ``block - 1`` tokens per round, the target verifies them as a chain.
+
+Round for one sequence whose target cache holds ``n`` tokens and whose last accepted token ``y0`` is not in it yet::
+
+    draft   : block [y0, mask × (B-1)] at positions n .. n+B-1 over the draft cache (context rows 0 .. n-1) → d1 .. d(B-1)
+    target  : causal pass over [y0, d1 .. d(B-1)] with tapped hidden states → its own next token after every row
+    accept  : the longest prefix of d that equals the target's choices, plus the target's token after it (a+1 tokens)
+    commit  : target cache advances by a+1 rows (y0, d1 .. da); their tapped hidden states become a+1 new context rows
+              of the draft cache; the next round's y0 is the bonus token
+
+The output is exactly the target's greedy continuation.  Parity: ``cpp/runtime/decoding/dflashDecoder.cpp`` (round
+structure, delta lengths, block layout) with the draft of ``models/dflash.py``.  Greedy requests only; hybrid targets are
+not supported (a partly accepted chain would need the recurrent state rolled back)."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from .. import ops
+from .. import profiling as prof
+from ..ops.meta import build_step_meta
+from .block_diffusion import full_mask
+from .kv_cache import KVCacheManager
+from .speculative import default_tap_layers
+
+
+@dataclass
+class DFlashStats:
+    rounds: int = 0
+    emitted: int = 0
+    draft_forwards: int = 0
+
+    @property
+    def mean_accept_length(self) -> float:
+        return self.emitted / max(self.rounds, 1)
+
+
+@dataclass
+class _Headroom:
+    verify_tokens: int
+
+
+class DFlashDecoder:
+    name = "dflash"
+    is_speculative = True
+
+    def __init__(self, runner, draft, draft_kv: KVCacheManager, block_size: Optional[int] = None, mask_token_id: Optional[int] = None):
+        self.r, self.model, self.draft, self.dkv = runner, runner.model, draft, draft_kv
+        if getattr(self.model.cfg, "is_hybrid", False):
+            raise ValueError("DFlash decoding is not available for hybrid (recurrent-state) targets")
+        self.device = runner.device
+        self.block = int(block_size or draft.cfg.dflash_block_size)
+        self.mask_id = int(draft.cfg.dflash_mask_token_id if mask_token_id is None else mask_token_id)
+        if not 2 <= self.block <= 64:
+            raise ValueError("DFlash block size must be between 2 and 64")
+        n = self.model.cfg.num_hidden_layers
+        self.taps = list(draft.cfg.dflash_target_layer_ids) or default_tap_layers(n)
+        if draft.embed_tokens is None:
+            draft.share_with(self.model)
+        self.stats = DFlashStats()
+        self.spec = _Headroom(self.block)          # what the request engine's session reads for KV head room
+        self.sampling = None                       # greedy verification only
+        self.root: Dict[int, int] = {}
+        self._mask_cache: Dict[int, torch.Tensor] = {}
+
+    def kv_headroom(self) -> int:
+        return self.block
+
+    # ---- steps --------------------------------------------------------------------------------
+    def _target_step(self, seats, rows: torch.Tensor, q_lens):
+        meta = self.r._meta(seats, q_lens, logits_all=True)
+        uniq = sorted(set(self.taps))
+        x, taps = self.model.hidden_states(rows, meta, self.r.cache, capture_layers=uniq)
+        by_layer = dict(zip(uniq, taps))
+        return self.model.logits_from_hidden(x, meta), torch.cat([by_layer[t] for t in self.taps], dim=-1)
+
+    def _write_context(self, seats, feats: torch.Tensor, q_lens) -> None:
+        past = [self.dkv.lengths[s] for s in seats]
+        for s, q, p in zip(seats, q_lens, past):
+            self.dkv.reserve(s, p + q + self.block)
+        meta = build_step_meta(q_lens, past, self.dkv.table_rows(seats), self.dkv.page_size, slot_ids=seats, device=self.device)
+        self.draft.write_context(feats, meta, self.dkv.pool)
+        for s, q in zip(seats, q_lens):
+            self.dkv.commit(s, q)
+
+    def _propose(self, seats) -> torch.Tensor:
+        """Draft tokens ``[N, block - 1]`` after each sequence's current root."""
+        n, b = len(seats), self.block
+        ids = torch.full((n, b), self.mask_id, dtype=torch.int32)
+        ids[:, 0] = torch.tensor([self.root[s] for s in seats], dtype=torch.int32)
+        embeds = ops.embedding(ids.reshape(-1).to(self.device), self.draft.embed_tokens.weight)
+        scale = getattr(self.model.model, "embed_scale", 1.0)
+        if scale != 1.0:
+            embeds = (embeds * torch.tensor(scale, dtype=embeds.dtype)).to(embeds.dtype)
+        past = [self.dkv.lengths[s] for s in seats]
+        if n not in self._mask_cache:
+            self._mask_cache[n] = full_mask(n * b, b, self.device)
+        meta = build_step_meta([b] * n, past, self.dkv.table_rows(seats), self.dkv.page_size, slot_ids=seats, logits_all=True,
+                               device=self.device, tree_mask=self._mask_cache[n])
+        logits = self.draft.propose(embeds, meta, self.dkv.pool)        # block rows are written past the context, never committed
+        self.stats.draft_forwards += 1
+        return ops.argmax(logits).view(n, b)[:, 1:].to("cpu")
+
+    # ---- prefill / round -----------------------------------------------------------------------
+    @torch.no_grad()
+    def prefill(self, seats: Sequence[int], prompts: Sequence[Sequence[int]]) -> List[int]:
+        q_lens = [len(p) for p in prompts]
+        flat = torch.tensor([t for p in prompts for t in p], dtype=torch.int32, device=self.device)
+        with prof.time_stage(prof.PREFILL, batch=len(seats), tokens=int(flat.numel())):
+            logits, feats = self._target_step(seats, flat, q_lens)
+            for s, q in zip(seats, q_lens):
+                self.r.kv.commit(s, q)
+                self.dkv.free(s)
+            ends = torch.tensor(q_lens).cumsum(0) - 1
+            first = ops.argmax(logits.index_select(0, ends.to(self.device))).tolist()
+            self._write_context(seats, feats, q_lens)
+        for s, t in zip(seats, first):
+            self.root[s] = int(t)
+        return [int(t) for t in first]
+
+    @torch.no_grad()
+    def round(self, seats: Sequence[int], forced_accept: Optional[Sequence[int]] = None) -> List[List[int]]:
+        """One draft → verify round; returns the new tokens of every sequence (accepted drafts + the target's next token).
+        ``forced_accept`` prescribes the accepted draft count per sequence (benchmarks with random weights)."""
+        n, b = len(seats), self.block
+        drafts = self._propose(seats)                                     # [N, B-1] host
+        chain = torch.cat([torch.tensor([[self.root[s]] for s in seats], dtype=torch.int64), drafts.long()], dim=1)
+        rows = chain.reshape(-1).to(torch.int32).to(self.device)
+        logits, feats = self._target_step(seats, rows, [b] * n)           # rows written at n .. n+B-1, not committed yet
+        choice = ops.argmax(logits).view(n, b).to("cpu")                  # target's token after each chain row
+        out: List[List[int]] = []
+        keep_rows, keep_lens = [], []
+        for i, s in enumerate(seats):
+            a = 0
+            limit = b - 1 if forced_accept is None else min(int(forced_accept[i]), b - 1)
+            while a < limit and (forced_accept is not None or int(drafts[i, a]) == int(choice[i, a])):
+                a += 1
+            toks = [int(t) for t in drafts[i, :a]] + [int(choice[i, a])]
+            out.append(toks)
+            self.r.kv.commit(s, a + 1)                                    # y0 and the accepted drafts are real history now
+            keep_rows.append(torch.arange(i * b, i * b + a + 1))
+            keep_lens.append(a + 1)
+            self.root[s] = toks[-1]
+        self._write_context(seats, feats.index_select(0, torch.cat(keep_rows).to(self.device)), keep_lens)
+        self.stats.rounds += 1
+        self.stats.emitted += sum(len(t) for t in out)
+        return out
+
+    @torch.no_grad()
+    def generate(self, seats: Sequence[int], prompts: Sequence[Sequence[int]], max_new_tokens: int, eos_id: Optional[int] = None,
+                 sampling=None) -> List[List[int]]:
+        if sampling is not None:
+            raise ValueError("DFlash decoding verifies greedy requests only")
+        for s in seats:
+            self.r.kv.free(s)
+        first = self.prefill(seats, prompts)
+        out = [[t] for t in first]
+        live = [i for i in range(len(seats)) if not (eos_id is not None and first[i] == eos_id) and max_new_tokens > 1]
+        while live:
+            cur = [seats[i] for i in live]
+            room = min(self.r.kv.max_pages_per_seq * self.r.kv.page_size - self.r.kv.lengths[s] for s in cur)
+            if room < self.block:
+                break
+            new = self.round(cur)
+            nxt = []
+            for i, toks in zip(live, new):
+                for t in toks:
+                    if len(out[i]) >= max_new_tokens:
+                        break
+                    out[i].append(t)
+                    if eos_id is not None and t == eos_id:
+                        break
+                done = len(out[i]) >= max_new_tokens or (eos_id is not None and out[i][-1] == eos_id)
+                if not done:
+                    nxt.append(i)
+            live = nxt
+        return out
+
+    def release(self, seats: Sequence[int]) -> None:
+        for s in seats:
+            self.r.kv.free(s)
+            self.dkv.free(s)
+            self.root.pop(s, None)

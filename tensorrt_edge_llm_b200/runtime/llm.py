@@ -99,14 +99,19 @@ class LLM:
             if hasattr(draft, "share_lm_head") and not isinstance(draft_model, ModelConfig):
                 draft.share_lm_head(self.model)
             spec = speculative or SpecConfig()
-            headroom = spec.verify_tokens + spec.draft_steps * spec.top_k
+            is_dflash = draft.cfg.draft_type == "dflash"
+            headroom = draft.cfg.dflash_block_size + 8 if is_dflash else spec.verify_tokens + spec.draft_steps * spec.top_k
             sp_pages = (max_kv_cache_capacity + headroom + page_size - 1) // page_size
             self.kv = KVCacheManager(self.cfg, (kv_pages or sp_pages * max_batch_size + 1), page_size, max_seats=max_batch_size,
                                      max_pages_per_seq=sp_pages, device=self.device)
             self.runner = ModelRunner(self.model, self.kv, self.device, max_num_tokens=max_num_tokens)
             dkv = KVCacheManager(draft.cfg, sp_pages * max_batch_size + 1, page_size, max_seats=max_batch_size, max_pages_per_seq=sp_pages,
-                                 device=self.device, num_layers=1)
-            self.spec_decoder = EagleDecoder(self.runner, draft, dkv, spec)
+                                 device=self.device, num_layers=draft.cfg.num_hidden_layers if is_dflash else 1)
+            if is_dflash:                      # block draft over target-derived keys / values (runtime/dflash.py)
+                from .dflash import DFlashDecoder
+                self.spec_decoder = DFlashDecoder(self.runner, draft, dkv)
+            else:
+                self.spec_decoder = EagleDecoder(self.runner, draft, dkv, spec)
         from .debug import LayerDumper, forced_tokens_from_env
         self._dumper = LayerDumper.from_env()
         if self._dumper is not None:
@@ -424,7 +429,8 @@ class LLM:
             return self._generate_diffusion([p.tolist() for p in ids] if isinstance(ids, torch.Tensor) else ids, sp)
         if sp.needs_logits_processing:
             return self._generate_processed([p.tolist() for p in ids] if isinstance(ids, torch.Tensor) else ids, sp)
-        if self.spec_decoder is not None and not isinstance(ids, torch.Tensor) and (sp.temperature < 1e-3 or not self.cfg.is_hybrid):
+        greedy_only = self.cfg.is_hybrid or getattr(self.spec_decoder, "name", "") == "dflash"
+        if self.spec_decoder is not None and not isinstance(ids, torch.Tensor) and (sp.temperature < 1e-3 or not greedy_only):
             return self._generate_speculative(ids, sp)
         n = len(ids)
         seats = list(range(n))

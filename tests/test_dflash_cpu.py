@@ -1,0 +1,128 @@
+"""DFlash block-draft speculative decoding on tiny random models: losslessness, cache bookkeeping, acceptance."""
+import torch
+
+from tensorrt_edge_llm_b200 import AutoModel
+from tensorrt_edge_llm_b200.config import ModelConfig, tiny_llama_config
+from tensorrt_edge_llm_b200.runtime.dflash import DFlashDecoder
+from tensorrt_edge_llm_b200.runtime.kv_cache import KVCacheManager
+from tensorrt_edge_llm_b200.runtime.runner import ModelRunner
+
+
+def _pair(block=6, shift=False, layers=2):
+    tcfg = tiny_llama_config(num_hidden_layers=4, vocab_size=120, dtype="float32")
+    target = AutoModel.from_config(tcfg, random_init=0)
+    kv = KVCacheManager(tcfg, num_pages=32, page_size=16, max_seats=3, max_pages_per_seq=10)
+    runner = ModelRunner(target, kv)
+    dcfg = tiny_llama_config(num_hidden_layers=layers, vocab_size=120, dtype="float32")
+    dcfg.draft_type, dcfg.dflash_block_size, dcfg.dflash_mask_token_id, dcfg.dflash_shift_label = "dflash", block, 119, shift
+    dcfg.dflash_target_layer_ids = [0, 1, 3]
+    draft = AutoModel.from_config(dcfg, random_init=1)
+    assert type(draft).__name__ == "DFlashDraft"
+    dkv = KVCacheManager(dcfg, num_pages=32, page_size=16, max_seats=3, max_pages_per_seq=10, num_layers=layers)
+    return runner, draft, dkv, tcfg
+
+
+def _greedy(tcfg, prompts, n):
+    target = AutoModel.from_config(tcfg, random_init=0)
+    kv = KVCacheManager(tcfg, num_pages=32, page_size=16, max_seats=3, max_pages_per_seq=10)
+    r = ModelRunner(target, kv)
+    first = r.prefill(list(range(len(prompts))), prompts).argmax(-1)
+    rest = r.decode_greedy(list(range(len(prompts))), first, n - 1)
+    return torch.cat([first[:, None], rest], 1).tolist()
+
+
+def test_lossless_and_bookkeeping():
+    for shift in (False, True):
+        runner, draft, dkv, tcfg = _pair(block=6, shift=shift)
+        dec = DFlashDecoder(runner, draft, dkv)
+        prompts = [[5, 6, 7, 8, 9, 10, 11], [20, 21, 22]]
+        out = dec.generate([0, 1], prompts, 24)
+        assert out == _greedy(tcfg, prompts, 24)                       # exactly the target's greedy continuation
+        # target cache: every emitted token but the last (the pending root); draft context rows: one per cached target token
+        for s, p, o in zip([0, 1], prompts, out):
+            assert runner.kv.lengths[s] == dkv.lengths[s]
+            assert len(p) + len(o) - 1 <= runner.kv.lengths[s] + 6     # generation may overshoot the budget by less than a block
+        assert dec.stats.rounds >= 4 and dec.stats.draft_forwards == dec.stats.rounds
+        dec.release([0, 1])
+        assert runner.kv.lengths[0] == 0 and dkv.lengths[0] == 0
+
+
+def test_draft_that_knows_the_answer_is_accepted_whole():
+    """Replace the draft's proposal with the target's own continuation: every round accepts block - 1 tokens."""
+    runner, draft, dkv, tcfg = _pair(block=5)
+    dec = DFlashDecoder(runner, draft, dkv)
+    prompts = [[3, 1, 4, 1, 5, 9, 2, 6]]
+    want = _greedy(tcfg, prompts, 40)[0]
+    pos = {"at": 1}
+
+    def oracle(seats):
+        d = torch.tensor([want[pos["at"]:pos["at"] + 4]])
+        dec.stats.draft_forwards += 1
+        return d
+    dec._propose = oracle
+    first = dec.prefill([0], prompts)
+    assert first == [want[0]]
+    got = list(first)
+    for _ in range(4):
+        new = dec.round([0])[0]
+        assert len(new) == 5                                           # four drafts + the bonus token
+        got += new
+        pos["at"] += 5
+    assert got == want[:21] and dec.stats.mean_accept_length == 5.0
+    assert runner.kv.lengths[0] == len(prompts[0]) + 20 and dkv.lengths[0] == runner.kv.lengths[0]
+
+
+def test_forced_accept_and_eos():
+    runner, draft, dkv, tcfg = _pair(block=4)
+    dec = DFlashDecoder(runner, draft, dkv)
+    dec.prefill([0, 1], [[1, 2, 3], [4, 5, 6, 7]])
+    new = dec.round([0, 1], forced_accept=[3, 1])
+    assert [len(t) for t in new] == [4, 2]
+    assert runner.kv.lengths[0] == 3 + 4 and runner.kv.lengths[1] == 4 + 2
+    dec.release([0, 1])
+    want = _greedy(tcfg, [[1, 2, 3]], 12)[0]
+    eos = want[5]
+    cut = dec.generate([0], [[1, 2, 3]], 12, eos_id=eos)[0]
+    assert cut == want[:want.index(eos) + 1]
+
+
+def test_context_rows_hold_projected_target_features():
+    """The draft cache's keys are k_norm/RoPE(k_proj(norm(fc(taps)))) of the target rows — checked for layer 0, row 2."""
+    from tensorrt_edge_llm_b200.ops import reference as ref
+    runner, draft, dkv, tcfg = _pair(block=4)
+    dec = DFlashDecoder(runner, draft, dkv)
+    prompt = [9, 8, 7, 6, 5]
+    dec.prefill([0], [prompt])
+    meta = runner._meta([1], [5], logits_all=True)                     # recompute the taps on another seat
+    x, taps = runner.model.hidden_states(torch.tensor(prompt, dtype=torch.int32), meta, runner.cache, capture_layers=[0, 1, 3])
+    h = draft.project(torch.cat(taps, -1))
+    a = draft.layers[0].self_attn
+    qkv = a.qkv_proj(h)
+    k = qkv[:, a.num_q_heads * a.head_dim:(a.num_q_heads + a.num_kv_heads) * a.head_dim].reshape(5, a.num_kv_heads, a.head_dim)
+    if a.k_norm is not None:
+        k = ref._head_rmsnorm(k, a.k_norm.weight, a.eps)
+    k = ref.apply_rope(k, torch.arange(5), draft.cos_sin("cpu"))
+    page = int(dkv.table_rows([0])[0, 0])
+    assert (dkv.pool[0][page, 0, :, 2, :] - k[2]).abs().max() < 1e-5
+
+
+def test_llm_with_a_dflash_draft_static_and_in_flight():
+    from tensorrt_edge_llm_b200.runtime.llm import LLM, SamplingParams
+    tcfg = tiny_llama_config(num_hidden_layers=4, vocab_size=120, dtype="float32")
+    dcfg = tiny_llama_config(num_hidden_layers=2, vocab_size=120, dtype="float32")
+    dcfg.draft_type, dcfg.dflash_block_size, dcfg.dflash_mask_token_id = "dflash", 5, 119
+    prompts = [[5, 6, 7, 8], [20, 21, 22, 23, 24, 25]]
+    plain = LLM(tcfg, device="cpu", max_batch_size=2, max_input_len=32, max_kv_cache_capacity=96, page_size=16)
+    want = [o.token_ids for o in plain.generate(prompts, SamplingParams(max_tokens=18, ignore_eos=True))]
+    llm = LLM(tcfg, device="cpu", max_batch_size=2, max_input_len=32, max_kv_cache_capacity=96, page_size=16, draft_model=dcfg)
+    assert type(llm.spec_decoder).__name__ == "DFlashDecoder" and llm.spec_decoder.dkv.pool.shape[0] == 2
+    outs = llm.generate(prompts, SamplingParams(max_tokens=18, ignore_eos=True))
+    assert [o.token_ids for o in outs] == want and outs[0].spec_stats["verify_rounds"] >= 3
+    # sampled requests take the plain path on a DFlash deployment
+    samp = llm.generate(prompts[:1], SamplingParams(max_tokens=6, ignore_eos=True, temperature=0.8, top_k=20, seed=1))[0]
+    assert len(samp.token_ids) == 6 and samp.spec_stats is None
+    ifb = LLM(tcfg, device="cpu", max_batch_size=2, max_input_len=32, max_kv_cache_capacity=96, page_size=16, draft_model=dcfg,
+              enable_in_flight_batching=True)
+    got = [o.token_ids for o in ifb.generate(prompts, SamplingParams(max_tokens=18, ignore_eos=True))]
+    ifb.close()
+    assert got == want
