@@ -1,4 +1,5 @@
-"""Qwen2-VL / Qwen2.5-VL vision transformer: variable image grids, 2-D rotary positions, window attention, patch merger.
+"""Qwen2-VL / Qwen2.5-VL / Qwen3-VL vision transformer: variable image grids, 2-D rotary positions, window attention, patch
+merger, interpolated position table and deepstack taps (Qwen3-VL).
 
 Input is the image processor's patch matrix ``[S, C · T_p · P · P]`` (patches of all images and video frames back to
 back, each image in ``merge × merge`` block order) plus one ``(t, h, w)`` grid per image.  The encoder
@@ -48,10 +49,26 @@ class QwenVisionConfig:
     eps: float = 1e-6
     rope_theta: float = 10000.0
     dtype: str = "bfloat16"
+    # Qwen3-VL: tanh-GELU MLP, biased patch embedding, a learned position table (a square grid, interpolated bilinearly to
+    # each image's grid) next to the rotary positions, and "deepstack" mergers that tap the listed blocks
+    mlp_act: str = ""                                        # "" = by gated_mlp (swiglu / quick_gelu); "gelu_tanh"
+    patch_bias: bool = False
+    num_position_embeddings: int = 0
+    deepstack_visual_indexes: List[int] = field(default_factory=list)
 
     @classmethod
     def from_hf(cls, v: Dict) -> "QwenVisionConfig":
-        """``vision_config`` of a Qwen2-VL (``embed_dim`` / ``mlp_ratio``) or Qwen2.5-VL (``intermediate_size`` / windows) checkpoint."""
+        """``vision_config`` of a Qwen2-VL (``embed_dim`` / ``mlp_ratio``), Qwen2.5-VL (``intermediate_size`` / windows) or Qwen3-VL
+        (``num_position_embeddings`` / ``deepstack_visual_indexes``) checkpoint."""
+        if "num_position_embeddings" in v or "deepstack_visual_indexes" in v:         # Qwen3-VL
+            return cls(depth=int(v["depth"]), hidden_size=int(v["hidden_size"]), num_heads=int(v["num_heads"]),
+                       intermediate_size=int(v["intermediate_size"]), in_channels=int(v.get("in_channels", 3)),
+                       patch_size=int(v.get("patch_size", 16)), temporal_patch_size=int(v.get("temporal_patch_size", 2)),
+                       spatial_merge_size=int(v.get("spatial_merge_size", 2)), out_hidden_size=int(v["out_hidden_size"]), window_size=0,
+                       fullatt_block_indexes=[], gated_mlp=False, patch_bias=True,
+                       mlp_act="gelu_tanh" if "tanh" in str(v.get("hidden_act", "gelu_pytorch_tanh")) else "gelu",
+                       num_position_embeddings=int(v.get("num_position_embeddings", 2304)),
+                       deepstack_visual_indexes=list(v.get("deepstack_visual_indexes", [8, 16, 24])))
         if "embed_dim" in v:                                 # Qwen2-VL
             h = int(v["embed_dim"])
             return cls(depth=int(v["depth"]), hidden_size=h, num_heads=int(v["num_heads"]), intermediate_size=int(h * v.get("mlp_ratio", 4)),
@@ -162,9 +179,41 @@ class QwenVisionBlock(nn.Module):
         y = self.fc1(self.norm2(x))
         if c.gated_mlp:
             y = ops.swiglu(y)
+        elif c.mlp_act in ("gelu_tanh", "gelu"):
+            y = ops.gelu(y, c.mlp_act == "gelu_tanh")
         else:
             y = (y.float() * torch.sigmoid(1.702 * y.float())).to(y.dtype)               # quick GELU
         return x + self.fc2(y)
+
+
+class _DeepstackMerger(nn.Module):
+    def __init__(self, cfg: QwenVisionConfig):
+        super().__init__()
+        wide = cfg.hidden_size * cfg.spatial_merge_size ** 2
+        self.norm = _Norm(wide, 1e-6, cfg.compute_dtype, False)
+        self.fc1, self.fc2 = _Lin(wide, wide, cfg.compute_dtype), _Lin(wide, cfg.out_hidden_size, cfg.compute_dtype)
+
+    def forward(self, x):
+        return self.fc2(ops.gelu(self.fc1(self.norm(x.reshape(-1, self.norm.weight.shape[0]).contiguous()))))
+
+
+def interpolated_positions(table: torch.Tensor, grids: Sequence[Sequence[int]], merge: int) -> torch.Tensor:
+    """Rows of the learned ``side × side`` position table resampled bilinearly (corners aligned) to every image's
+    ``h × w`` grid, repeated per frame and laid out in ``merge × merge`` block order: ``[S, H]``."""
+    side = int(round(table.shape[0] ** 0.5))
+    out = []
+    for t, h, w in grids:
+        ys, xs = torch.linspace(0, side - 1, h), torch.linspace(0, side - 1, w)
+        y0, x0 = ys.int(), xs.int()
+        y1, x1 = (y0 + 1).clamp(max=side - 1), (x0 + 1).clamp(max=side - 1)
+        dy, dx = (ys - y0)[:, None], (xs - x0)[None, :]
+        tb = table.float()
+        g = lambda yy, xx: tb[(yy[:, None] * side + xx[None, :]).long().reshape(-1).to(table.device)].reshape(h, w, -1)
+        wgt = lambda a: a.to(table.device)[..., None]
+        p = (g(y0, x0) * wgt((1 - dy) * (1 - dx)) + g(y0, x1) * wgt((1 - dy) * dx) + g(y1, x0) * wgt(dy * (1 - dx)) + g(y1, x1) * wgt(dy * dx))
+        p = p.reshape(h // merge, merge, w // merge, merge, -1).permute(0, 2, 1, 3, 4).reshape(h * w, -1)
+        out.append(p.repeat(int(t), 1))
+    return torch.cat(out, 0).to(table.dtype)
 
 
 class QwenVisionEncoder(nn.Module):
@@ -177,11 +226,16 @@ class QwenVisionEncoder(nn.Module):
         self.cfg = cfg
         dt, h = cfg.compute_dtype, cfg.hidden_size
         self.patch_embed = _Lin(cfg.patch_dim, h, dt)
-        self.patch_embed.bias = None                         # the checkpoint's Conv3d has no bias
+        if not cfg.patch_bias:
+            self.patch_embed.bias = None                     # Qwen2 / 2.5: the checkpoint's Conv3d has no bias
+        self.pos_embed = (nn.Parameter(torch.zeros(cfg.num_position_embeddings, h, dtype=dt), requires_grad=False)
+                          if cfg.num_position_embeddings else None)
         self.blocks = nn.ModuleList([QwenVisionBlock(cfg) for _ in range(cfg.depth)])
         m2 = cfg.spatial_merge_size ** 2
         self.ln_q = _Norm(h, 1e-6, dt, cfg.gated_mlp)
         self.merger_fc1, self.merger_fc2 = _Lin(h * m2, h * m2, dt), _Lin(h * m2, cfg.out_hidden_size, dt)
+        # deepstack: merged features of intermediate blocks (norm over the merged row, then the same two-layer shape)
+        self.deepstack = nn.ModuleList([_DeepstackMerger(cfg) for _ in cfg.deepstack_visual_indexes])
         self._kv: Optional[torch.Tensor] = None
 
     # ---- weights ---------------------------------------------------------------------------------
@@ -224,6 +278,11 @@ class QwenVisionEncoder(nn.Module):
                 raise ValueError(f"shape {tuple(value.shape)} does not fit {tuple(param.shape)}")
             param.copy_(value.to(param.dtype))
         put(self.patch_embed.weight, take("patch_embed.proj.weight").reshape(c.hidden_size, -1))
+        if c.patch_bias:
+            put(self.patch_embed.bias, take("patch_embed.proj.bias"))
+        if self.pos_embed is not None:
+            put(self.pos_embed, take("pos_embed.weight"))
+        q3 = bool(c.num_position_embeddings)                 # Qwen3-VL tensor names
         for i, b in enumerate(self.blocks):
             p = f"blocks.{i}."
             for norm, name in ((b.norm1, "norm1"), (b.norm2, "norm2")):
@@ -240,15 +299,23 @@ class QwenVisionEncoder(nn.Module):
                 put(b.fc2.weight, take(p + "mlp.down_proj.weight"))
                 put(b.fc2.bias, take(p + "mlp.down_proj.bias"))
             else:
-                for lin, name in ((b.fc1, "mlp.fc1"), (b.fc2, "mlp.fc2")):
+                for lin, name in ((b.fc1, "mlp.linear_fc1" if q3 else "mlp.fc1"), (b.fc2, "mlp.linear_fc2" if q3 else "mlp.fc2")):
                     put(lin.weight, take(p + name + ".weight"))
                     put(lin.bias, take(p + name + ".bias"))
-        put(self.ln_q.weight, take("merger.ln_q.weight"))
+        ln = "merger.norm" if q3 else "merger.ln_q"
+        put(self.ln_q.weight, take(ln + ".weight"))
         if self.ln_q.bias is not None:
-            put(self.ln_q.bias, take("merger.ln_q.bias"))
-        for lin, name in ((self.merger_fc1, "merger.mlp.0"), (self.merger_fc2, "merger.mlp.2")):
+            put(self.ln_q.bias, take(ln + ".bias"))
+        for lin, name in ((self.merger_fc1, "merger.linear_fc1" if q3 else "merger.mlp.0"), (self.merger_fc2, "merger.linear_fc2" if q3 else "merger.mlp.2")):
             put(lin.weight, take(name + ".weight"))
             put(lin.bias, take(name + ".bias"))
+        for k, dm in enumerate(self.deepstack):
+            p = f"deepstack_merger_list.{k}."
+            put(dm.norm.weight, take(p + "norm.weight"))
+            put(dm.norm.bias, take(p + "norm.bias"))
+            for lin, name in ((dm.fc1, "linear_fc1"), (dm.fc2, "linear_fc2")):
+                put(lin.weight, take(p + name + ".weight"))
+                put(lin.bias, take(p + name + ".bias"))
         return sorted(set(sd) - used)
 
     @classmethod
@@ -286,7 +353,9 @@ class QwenVisionEncoder(nn.Module):
         return build_step_meta(list(lengths), [0] * len(lengths), table, self.PAGE, device=device), at
 
     @torch.no_grad()
-    def forward(self, patches: torch.Tensor, grids: Sequence[Sequence[int]]) -> torch.Tensor:
+    def forward(self, patches: torch.Tensor, grids: Sequence[Sequence[int]], return_deepstack: bool = False):
+        """``return_deepstack``: also return the list of deepstack features (one ``[S / merge², out_hidden]`` tensor per tapped
+        block, in the order of ``deepstack_visual_indexes``)."""
         c = self.cfg
         m2 = c.spatial_merge_size ** 2
         dev = patches.device
@@ -296,7 +365,9 @@ class QwenVisionEncoder(nn.Module):
             raise ValueError(f"patch matrix {tuple(patches.shape)} does not fit grids {grids} (want [{total}, {c.patch_dim}])")
         if any(h % c.spatial_merge_size or w % c.spatial_merge_size for _, h, w in grids):
             raise ValueError("grid heights and widths must be multiples of the spatial merge size")
-        x = ops.linear(patches.to(c.compute_dtype), self.patch_embed.weight)
+        x = ops.linear(patches.to(c.compute_dtype), self.patch_embed.weight, self.patch_embed.bias)
+        if self.pos_embed is not None:
+            x = x + interpolated_positions(self.pos_embed, grids, c.spatial_merge_size).to(x.dtype)
         table = self._pad_table(rotary_rows(grids, c.head_dim, c.spatial_merge_size, c.rope_theta)).to(dev)
         frame_meta, frame_pages = self._meta([h * w for t, h, w in grids for _ in range(t)], dev)
         win_meta, win_pages, order = None, 0, None
@@ -313,20 +384,23 @@ class QwenVisionEncoder(nn.Module):
         for meta in (frame_meta, win_meta):
             if meta is not None:
                 meta.rope_rows, meta.rope_pos = table.contiguous(), rows       # every patch reads its own table row
+        taps = []
         for i, blk in enumerate(self.blocks):
             full = win_meta is None or i in c.fullatt_block_indexes
             x = blk(x, frame_meta if full else win_meta, self._kv, table)
+            if i in c.deepstack_visual_indexes:
+                taps.append(self.deepstack[c.deepstack_visual_indexes.index(i)](x))
         x = self.ln_q(x).reshape(total // m2, m2 * c.hidden_size)
         y = self.merger_fc2(ops.gelu(self.merger_fc1(x.contiguous())))
         if order is not None:
             y = y[torch.argsort(order)]
-        return y
+        return (y, taps) if return_deepstack else y
 
     @torch.no_grad()
     def random_init(self, seed: int = 0, std: float = 0.02):
         g = torch.Generator().manual_seed(seed)
         for name, p in self.named_parameters():
-            if name.endswith("weight") and p.dim() == 2:
+            if (name.endswith("weight") and p.dim() == 2) or name == "pos_embed":
                 p.copy_((torch.randn(p.shape, generator=g) * std).to(p.dtype))
         d, dp = self.cfg.head_dim, self.cfg.padded_head_dim
         if d != dp:                                           # keep the padding features zero for random weights too

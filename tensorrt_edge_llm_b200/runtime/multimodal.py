@@ -50,17 +50,19 @@ class MultimodalRunner:
         self.min_pixels, self.max_pixels = min_pixels, max_pixels
         self.device = llm.device
         self._grids: List[Tuple[int, int, int]] = []      # (t, rows, columns) of each encoded image in language-model tokens
+        self._deep: List[torch.Tensor] = []                # deepstack features of the images encoded last (one tensor per level)
+        self.deepstack: Optional[dict] = None              # {decoder layer: (prompt rows, features)} of the prompt built last
 
     @classmethod
     def from_pretrained(cls, llm, model_dir: str, **kw) -> Optional["MultimodalRunner"]:
         """Runner for a vision-language checkpoint directory, or ``None`` when ``config.json`` names no vision tower this
-        build has (Qwen2-VL and Qwen2.5-VL are built).  The image placeholder id comes from ``image_token_id``."""
+        build has (Qwen2-VL, Qwen2.5-VL and Qwen3-VL are built).  The image placeholder id comes from ``image_token_id``."""
         import json
         import os
         with open(os.path.join(model_dir, "config.json"), "r", encoding="utf-8") as f:
             hf = json.load(f)
         kind = str(hf.get("model_type", ""))
-        if "vision_config" not in hf or kind not in ("qwen2_vl", "qwen2_5_vl"):
+        if "vision_config" not in hf or kind not in ("qwen2_vl", "qwen2_5_vl", "qwen3_vl"):
             return None
         tower = QwenVisionEncoder.from_pretrained(model_dir, device=llm.device, dtype=llm.cfg.dtype)
         return cls(llm, vision=tower, image_token_id=int(hf.get("image_token_id", 151655)), **kw)
@@ -106,7 +108,9 @@ class MultimodalRunner:
             m, g = patchify_frames(chw[None], c)
             mats.append(m)
             grids.append(g)
-        rows = self.vision(torch.cat(mats, 0).to(self.device), grids)
+        rows = self.vision(torch.cat(mats, 0).to(self.device), grids, return_deepstack=bool(c.deepstack_visual_indexes))
+        # Qwen3-VL: features of intermediate blocks ride along; they join the language model's first layers (deepstack)
+        rows, self._deep = rows if isinstance(rows, tuple) else (rows, [])
         m = c.spatial_merge_size
         self._grids = [(t, h // m, w // m) for t, h, w in grids]
         out, at = [], 0
@@ -116,7 +120,7 @@ class MultimodalRunner:
         return out
 
     def encode_images(self, images: Sequence) -> List[torch.Tensor]:
-        self._grids = []
+        self._grids, self._deep = [], []
         if not images:
             return []
         if self.vision is None:
@@ -182,6 +186,11 @@ class MultimodalRunner:
         if media_rows:
             pos = torch.tensor([i for i, t in enumerate(ids) if t in (self.image_token_id, self.audio_token_id)], device=emb.device)
             emb[pos] = torch.cat(media_rows, 0).to(emb.device, emb.dtype)
+        self.deepstack = None
+        if self._deep and media_rows:
+            # level k of the tower's deepstack features is added to the image rows after decoder layer k
+            img_pos = torch.tensor([i for i, t in enumerate(ids) if t == self.image_token_id], dtype=torch.int64)
+            self.deepstack = {k: (img_pos, f.to(emb.dtype)) for k, f in enumerate(self._deep)}
         positions3 = delta = None
         if self.llm.cfg.mrope_section:
             # audio runs advance like text; image runs use their (t, h, w) grid (rows are already merged: merge factor 1)
@@ -196,7 +205,7 @@ class MultimodalRunner:
         kv.free(seat)
         kv.reserve(seat, len(ids) + max_tokens)
         logits = runner.prefill_embeds([seat], [emb], positions3=None if positions3 is None else [positions3],
-                                       rope_deltas=None if positions3 is None else [delta])
+                                       rope_deltas=None if positions3 is None else [delta], deepstack=self.deepstack)
         first = runner.pick(logits)
         out = [int(first[0])]
         if max_tokens > 1:

@@ -179,3 +179,64 @@ def test_runner_from_a_vision_language_checkpoint(tmp_path):
     # a text-only checkpoint has no tower
     json.dump({"model_type": "llama", **text}, open(os.path.join(d, "config.json"), "w"))
     assert MultimodalRunner.from_pretrained(llm, d) is None
+
+
+def test_qwen3_vl_tower_and_deepstack_match_hf():
+    from transformers.models.qwen3_vl.configuration_qwen3_vl import Qwen3VLVisionConfig
+    from transformers.models.qwen3_vl.modeling_qwen3_vl import Qwen3VLVisionModel
+    hc = Qwen3VLVisionConfig(depth=4, hidden_size=64, intermediate_size=96, num_heads=4, patch_size=16, spatial_merge_size=2,
+                             temporal_patch_size=2, out_hidden_size=48, num_position_embeddings=36, deepstack_visual_indexes=[0, 2])
+    hc._attn_implementation = "eager"
+    torch.manual_seed(7)
+    hf = Qwen3VLVisionModel(hc).eval().float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "norm" in n or n.endswith("bias"):
+                p.copy_(torch.randn_like(p) * 0.3 + (1.0 if n.endswith("weight") else 0.0))
+    cfg = QwenVisionConfig.from_hf(hc.to_dict())
+    cfg.dtype = "float32"
+    assert cfg.mlp_act == "gelu_tanh" and cfg.patch_bias and cfg.num_position_embeddings == 36 and cfg.deepstack_visual_indexes == [0, 2]
+    enc = QwenVisionEncoder(cfg)
+    assert enc.load_hf_state_dict(hf.state_dict(), prefix="") == []
+    x = _patches(cfg, GRIDS, seed=8)
+    with torch.no_grad():
+        out = hf(x, grid_thw=torch.tensor(GRIDS))
+    rows, taps = enc(x, GRIDS, return_deepstack=True)
+    scale = max(1.0, out.pooler_output.abs().max().item())
+    assert (rows - out.pooler_output).abs().max() < 2e-4 * scale
+    assert len(taps) == 2
+    for got, want in zip(taps, out.deepstack_features):
+        assert got.shape == want.shape and (got - want).abs().max() < 2e-4 * max(1.0, want.abs().max().item())
+
+
+def test_deepstack_features_reach_the_decoder():
+    """A Qwen3-VL style tower feeds its deepstack levels to the language model's first layers through the runner."""
+    import numpy as np
+    from tensorrt_edge_llm_b200.config import tiny_llama_config
+    from tensorrt_edge_llm_b200.runtime.llm import LLM
+    from tensorrt_edge_llm_b200.runtime.multimodal import MultimodalInputs, MultimodalRunner
+    cfg = tiny_llama_config(num_hidden_layers=3, vocab_size=200, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                            dtype="float32")
+    cfg.mrope_section = [2, 3, 3]
+    llm = LLM(cfg, device="cpu", max_batch_size=1, max_input_len=256, max_kv_cache_capacity=320, page_size=16)
+    vc = QwenVisionConfig(depth=3, hidden_size=64, num_heads=4, intermediate_size=64, out_hidden_size=64, window_size=0, fullatt_block_indexes=[],
+                          gated_mlp=False, mlp_act="gelu_tanh", patch_bias=True, patch_size=16, num_position_embeddings=16,
+                          deepstack_visual_indexes=[0, 1], dtype="float32")
+    tower = QwenVisionEncoder(vc).random_init(5, std=0.2)
+    mm = MultimodalRunner(llm, vision=tower, image_token_id=7, min_pixels=32 * 32 * 2, max_pixels=32 * 32 * 30)
+    img = np.random.default_rng(2).integers(0, 255, (64, 96, 3), dtype=np.uint8)
+    req = MultimodalInputs().text([3, 4]).image(img).text([5, 6])
+    ids, emb, pos3, delta = mm.build(req)
+    n_img = ids.count(7)
+    assert n_img == 2 * 3 and sorted(mm.deepstack) == [0, 1]
+    rows, feats = mm.deepstack[1]
+    assert rows.tolist() == list(range(2, 2 + n_img)) and feats.shape == (n_img, 64)
+    with_deep = mm.generate(req, max_tokens=1)
+    # the same prompt without the deepstack levels gives different logits: run the prefill by hand
+    runner = llm.runner
+    llm.kv.free(0)
+    a = runner.prefill_embeds([0], [emb], positions3=[pos3], rope_deltas=[delta], deepstack=mm.deepstack).clone()
+    llm.kv.free(0)
+    b = runner.prefill_embeds([0], [emb], positions3=[pos3], rope_deltas=[delta])
+    llm.kv.free(0)
+    assert (a - b).abs().max() > 1e-3 and int(a.argmax()) == with_deep[0]
