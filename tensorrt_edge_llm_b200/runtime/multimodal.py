@@ -13,6 +13,7 @@ from typing import List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
+from ..models.internvl_vision import InternVisionEncoder, tile_grid
 from ..models.qwen_vl_vision import QwenVisionEncoder, patchify_frames
 from ..models.vit import EncoderCache, VisionEncoder, dart_prune, encode_data_parallel
 from ..ops import reference as ref
@@ -42,12 +43,13 @@ class MultimodalInputs:
 
 class MultimodalRunner:
     def __init__(self, llm, vision: Optional[VisionEncoder] = None, audio=None, image_token_id: int = 0, audio_token_id: int = 1,
-                 cache_bytes: int = 0, visual_keep_ratio: float = 1.0, min_pixels: int = 0, max_pixels: int = 0):
+                 cache_bytes: int = 0, visual_keep_ratio: float = 1.0, min_pixels: int = 0, max_pixels: int = 0, max_tiles: int = 12):
         self.llm, self.vision, self.audio = llm, vision, audio
         self.image_token_id, self.audio_token_id = image_token_id, audio_token_id
         self.cache = EncoderCache(cache_bytes) if cache_bytes > 0 else None
         self.keep_ratio = visual_keep_ratio
         self.min_pixels, self.max_pixels = min_pixels, max_pixels
+        self.max_tiles = max_tiles                         # InternVL dynamic resolution: tiles per image (a thumbnail comes on top)
         self.device = llm.device
         self._grids: List[Tuple[int, int, int]] = []      # (t, rows, columns) of each encoded image in language-model tokens
         self._deep: List[torch.Tensor] = []                # deepstack features of the images encoded last (one tensor per level)
@@ -56,12 +58,15 @@ class MultimodalRunner:
     @classmethod
     def from_pretrained(cls, llm, model_dir: str, **kw) -> Optional["MultimodalRunner"]:
         """Runner for a vision-language checkpoint directory, or ``None`` when ``config.json`` names no vision tower this
-        build has (Qwen2-VL, Qwen2.5-VL and Qwen3-VL are built).  The image placeholder id comes from ``image_token_id``."""
+        build has (Qwen2-VL, Qwen2.5-VL, Qwen3-VL and InternVL are built).  The image placeholder id comes from ``image_token_id``."""
         import json
         import os
         with open(os.path.join(model_dir, "config.json"), "r", encoding="utf-8") as f:
             hf = json.load(f)
         kind = str(hf.get("model_type", ""))
+        if "vision_config" in hf and kind == "internvl":
+            tower = InternVisionEncoder.from_pretrained(model_dir, device=llm.device, dtype=llm.cfg.dtype)
+            return cls(llm, vision=tower, image_token_id=int(hf.get("image_token_id", 151667)), **kw)
         if "vision_config" not in hf or kind not in ("qwen2_vl", "qwen2_5_vl", "qwen3_vl"):
             return None
         tower = QwenVisionEncoder.from_pretrained(model_dir, device=llm.device, dtype=llm.cfg.dtype)
@@ -119,12 +124,42 @@ class MultimodalRunner:
             at += t * h * w
         return out
 
+    def _encode_intern(self, images: Sequence) -> List[torch.Tensor]:
+        """InternVL: every image becomes up to ``max_tiles`` square tiles on the grid closest to its aspect ratio, plus a
+        thumbnail of the whole image when it was split; the rows of all its tiles follow one another in the prompt."""
+        c = self.vision.cfg
+        s = c.image_size
+        tiles, counts = [], []
+        for im in images:
+            im = self._decode(im)
+            cols, rows = tile_grid(im.width, im.height, s, 1, self.max_tiles)
+            big = rt.resize_bicubic(im, cols * s, rows * s)
+            chw = torch.from_numpy(rt.normalize_chw(big, list(self.vision.image_mean), list(self.vision.image_std)))
+            parts = [chw[:, r * s:(r + 1) * s, q * s:(q + 1) * s] for r in range(rows) for q in range(cols)]
+            if len(parts) > 1:
+                thumb = rt.resize_bicubic(im, s, s)
+                parts.append(torch.from_numpy(rt.normalize_chw(thumb, list(self.vision.image_mean), list(self.vision.image_std))))
+            tiles += parts
+            counts.append(len(parts))
+        out_rows = self.vision(torch.stack(tiles).to(self.device))
+        per = out_rows.shape[0] // len(tiles)
+        out, at = [], 0
+        for n in counts:
+            out.append(out_rows[at:at + n * per])
+            at += n * per
+        return out
+
     def encode_images(self, images: Sequence) -> List[torch.Tensor]:
         self._grids, self._deep = [], []
         if not images:
             return []
         if self.vision is None:
             raise ValueError("this runner has no vision encoder")
+        if isinstance(self.vision, InternVisionEncoder):
+            rows = self._encode_intern(images)
+            if self.keep_ratio < 1.0:
+                rows = [r[dart_prune(r, max(1, int(round(r.shape[0] * self.keep_ratio))))] for r in rows]
+            return rows
         if isinstance(self.vision, QwenVisionEncoder):
             if self.keep_ratio < 1.0:
                 raise ValueError("visual-token pruning is not combined with grid-shaped (multimodal RoPE) image rows")
