@@ -143,7 +143,11 @@ class InternVisionEncoder(nn.Module):
         super().__init__()
         self.cfg = cfg
         dt, h = cfg.compute_dtype, cfg.hidden_size
-        self.patch_embed = _Lin(cfg.num_channels * cfg.patch_size ** 2, h, dt)
+        # the tensor-core GEMM wants a reduction length that is a multiple of 8 (16-byte rows): 3 · 14 · 14 = 588 is not, so
+        # the patch matrix and the weight get zero columns up to the next multiple
+        self.patch_dim = cfg.num_channels * cfg.patch_size ** 2
+        self.patch_pad = (-self.patch_dim) % 8
+        self.patch_embed = _Lin(self.patch_dim + self.patch_pad, h, dt)
         self.cls_token = nn.Parameter(torch.zeros(h, dtype=dt), requires_grad=False)
         self.pos_embed = nn.Parameter(torch.zeros(1 + cfg.grid ** 2, h, dtype=dt), requires_grad=False)
         self.blocks = nn.ModuleList([InternVisionBlock(cfg) for _ in range(cfg.num_hidden_layers)])
@@ -168,7 +172,8 @@ class InternVisionEncoder(nn.Module):
                 raise ValueError(f"shape {tuple(value.shape)} does not fit {tuple(param.shape)}")
             param.copy_(value.to(param.dtype))
         e = tower + "embeddings."
-        put(self.patch_embed.weight, take(e + "patch_embeddings.projection.weight").reshape(c.hidden_size, -1))
+        put(self.patch_embed.weight, torch.nn.functional.pad(take(e + "patch_embeddings.projection.weight").reshape(c.hidden_size, -1),
+                                                             (0, self.patch_pad)))
         put(self.patch_embed.bias, take(e + "patch_embeddings.projection.bias"))
         put(self.cls_token, take(e + "cls_token").reshape(-1))
         put(self.pos_embed, take(e + "position_embeddings").reshape(-1, c.hidden_size))
@@ -229,6 +234,8 @@ class InternVisionEncoder(nn.Module):
         for name, p in self.named_parameters():
             if (name.endswith("weight") and p.dim() == 2) or name in ("pos_embed", "cls_token"):
                 p.copy_((torch.randn(p.shape, generator=g) * std).to(p.dtype))
+        if self.patch_pad:
+            self.patch_embed.weight[:, self.patch_dim:] = 0
         return self
 
     @torch.no_grad()
@@ -239,6 +246,8 @@ class InternVisionEncoder(nn.Module):
             raise ValueError(f"tiles must be {c.num_channels} × {c.image_size} × {c.image_size} (got {tuple(pixels.shape[1:])})")
         dev, g, p = pixels.device, c.grid, c.patch_size
         patches = pixels.reshape(n, ch, g, p, g, p).permute(0, 2, 4, 1, 3, 5).reshape(n * g * g, ch * p * p)
+        if self.patch_pad:
+            patches = torch.nn.functional.pad(patches, (0, self.patch_pad))
         x = self.patch_embed(patches.to(c.compute_dtype)).reshape(n, g * g, -1)
         x = torch.cat([self.cls_token.expand(n, 1, -1), x], dim=1) + self.pos_embed[None]
         tokens = 1 + g * g

@@ -198,6 +198,13 @@ def gemm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = N
     n = weight.shape[0]
     if weight.dtype != x.dtype:
         raise TypeError(f"gemm: activation {x.dtype} and weight {weight.dtype} differ")
+    if k % 8:
+        # rows must be 16-byte multiples for the TMA descriptors: zero columns up to the next multiple of 8 change nothing
+        # (patch embeddings with 3 · 14 · 14 = 588 inputs are the case in practice; the padded copies are made per call)
+        pad = 8 - k % 8
+        x2 = torch.nn.functional.pad(x2, (0, pad))
+        weight = torch.nn.functional.pad(weight, (0, pad))
+        k += pad
     if out is None:
         out = torch.empty(m, n, dtype=x.dtype, device=x.device)
     ws = Workspace.get(x.device)
