@@ -233,6 +233,12 @@ class ModelConfig:
     dflash_block_size: int = 16
     dflash_mask_token_id: int = 0
     dflash_shift_label: bool = False
+    # Domino: a DFlash draft whose proposals after the first are corrected one by one by a small recurrent head over a shared
+    # candidate pool (dflash_projector_type "domino")
+    dflash_projector_type: str = ""
+    domino_pool_size: int = 2048
+    domino_proj_dim: int = 256
+    domino_gru_hidden_dim: int = 256
     # quant / parallel
     quant: QuantConfig = field(default_factory=QuantConfig)
     mapping: Mapping = field(default_factory=Mapping)
@@ -405,6 +411,10 @@ class ModelConfig:
             dflash_block_size=int((llm.get("dflash_config") or {}).get("block_size", llm.get("block_size", 16)) or 16),
             dflash_mask_token_id=int((llm.get("dflash_config") or {}).get("mask_token_id", llm.get("mask_token_id", 0)) or 0),
             dflash_shift_label=bool((llm.get("dflash_config") or {}).get("shift_label", llm.get("dflash_shift_label", False))),
+            dflash_projector_type=str((llm.get("dflash_config") or {}).get("projector_type", llm.get("dflash_projector_type", "")) or ""),
+            domino_pool_size=int((llm.get("dflash_config") or {}).get("pool_size", llm.get("domino_pool_size", 2048)) or 2048),
+            domino_proj_dim=int((llm.get("dflash_config") or {}).get("proj_dim", llm.get("domino_proj_dim", 256)) or 256),
+            domino_gru_hidden_dim=int((llm.get("dflash_config") or {}).get("gru_hidden_dim", llm.get("domino_gru_hidden_dim", 256)) or 256),
             draft_vocab_size=int(llm.get("draft_vocab_size", 0) or 0),
             eagle3_target_hidden_size=int(llm.get("target_hidden_size", 0) or 0),
             eagle3_target_layer_ids=list((hf.get("eagle_config") or {}).get("eagle_aux_hidden_state_layer_ids", []) or []),

@@ -38,7 +38,7 @@ def model_class_for(cfg: ModelConfig):
     if cfg.draft_type == "eagle3":
         return _REGISTRY["eagle3"]
     if cfg.draft_type == "dflash":
-        return _REGISTRY["dflash"]
+        return _REGISTRY["domino" if cfg.dflash_projector_type == "domino" else "dflash"]
     if cfg.draft_type == "mtp":
         return _REGISTRY["mtp"]
     if cfg.model_type in _REGISTRY:

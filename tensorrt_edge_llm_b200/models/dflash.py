@@ -108,19 +108,93 @@ class DFlashDraft(nn.Module):
             layer.write_context(h, meta, kv_pool[i], cs)
 
     @torch.no_grad()
-    def propose(self, embeds: torch.Tensor, meta: StepMeta, kv_pool: torch.Tensor) -> torch.Tensor:
-        """Logits ``[T, V]`` (fp32) of the proposal rows; ``meta.tree_mask`` lets every row of a block see the whole block."""
+    def block_hidden(self, embeds: torch.Tensor, meta: StepMeta, kv_pool: torch.Tensor) -> torch.Tensor:
+        """Normalised hidden state ``[T, H]`` of every proposal row, aligned so that row ``i`` of a block describes the token
+        at offset ``i`` after the block's first token (with shifted labels the row is the hidden state of row ``i - 1``)."""
         h = embeds.to(self.cfg.compute_dtype)
         cs = self.cos_sin(h.device)
         for i, layer in enumerate(self.layers):
             h = layer(h, meta, kv_pool[i], cs, self.comm)
         if self.cfg.dflash_shift_label:
-            # row i predicts position i + 1: the row for offset i is the hidden state of row i - 1 (row 0 keeps its own)
             first = meta.q_start[:-1].long()
             shifted = torch.roll(h, 1, dims=0)
             shifted[first] = h[first]
             h = shifted
-        x = ops.rmsnorm(h, self.norm.weight, self.norm.eps)
+        return ops.rmsnorm(h, self.norm.weight, self.norm.eps)
+
+    def head(self, x: torch.Tensor) -> torch.Tensor:
         logits = self.lm_head(x).float()
         cap = self.cfg.final_logit_softcapping
         return torch.tanh(logits / cap) * cap if cap else logits
+
+    @torch.no_grad()
+    def propose(self, embeds: torch.Tensor, meta: StepMeta, kv_pool: torch.Tensor) -> torch.Tensor:
+        """Logits ``[T, V]`` (fp32) of the proposal rows; ``meta.tree_mask`` lets every row of a block see the whole block."""
+        return self.head(self.block_hidden(embeds, meta, kv_pool))
+
+
+@register_model("domino", "domino_draft")
+class DominoDraft(DFlashDraft):
+    """DFlash backbone plus the Domino correction head.
+
+    The block's proposals are not taken independently.  A candidate pool — the ``P`` tokens with the largest logit at any
+    proposal position — is scored per position; the first proposal is the pool's best token at position 1, and every later
+    position ``i`` is corrected by what was chosen before it: a bias-free GRU reads the chosen tokens, and
+
+        c      = SiLU(z_projection(hidden_i) + proj_state · h_gru)
+        score  = base_logits_i[pool] + codebook[pool] · c
+        token  = pool[argmax score]
+
+    Parity: ``tensorrt_edgellm/models/domino/modeling_domino_draft.py`` (pool outputs :107-140) and
+    ``cpp/runtime/decoding/dominoDecoder.cpp:160`` / ``cpp/kernels/speculative/dominoRolloutKernels.h`` (rollout: first
+    proposal, GRU seeded with the last accepted token and the first proposal, one correction + GRU update per position).
+    The pool holds a few thousand candidates, so the rollout is torch ops over ``[batch, P]`` tensors."""
+
+    def __init__(self, cfg: ModelConfig, comm=None):
+        super().__init__(cfg, comm)
+        dt, r, g = cfg.compute_dtype, cfg.domino_proj_dim, cfg.domino_gru_hidden_dim
+        mk = lambda *shape: nn.Parameter(torch.zeros(*shape, dtype=dt), requires_grad=False)
+        self.z_projection = mk(r, cfg.hidden_size)            # checkpoint: domino_pool.z_projection.weight
+        self.codebook = mk(cfg.vocab_size, r)                 # domino_pool.codebook
+        self.gru_input_table = mk(cfg.vocab_size, 3 * g)      # W_ih · embedding(token), gate order r, z, n
+        self.gru_weight_hh = mk(3 * g, g)
+        self.proj_state_weight = mk(r, g)
+
+    @staticmethod
+    def checkpoint_key_remap(key: str) -> Optional[str]:
+        key = DFlashDraft.checkpoint_key_remap(key)
+        return {"domino_pool.z_projection.weight": "z_projection", "domino_pool.codebook": "codebook"}.get(key, key)
+
+    def gru(self, tokens: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+        g = h.shape[-1]
+        x = self.gru_input_table[tokens.long()].float()
+        hh = h @ self.gru_weight_hh.float().t()
+        r = torch.sigmoid(x[:, :g] + hh[:, :g])
+        z = torch.sigmoid(x[:, g:2 * g] + hh[:, g:2 * g])
+        n = torch.tanh(x[:, 2 * g:] + r * hh[:, 2 * g:])
+        return (1 - z) * n + z * h
+
+    @torch.no_grad()
+    def propose_tokens(self, embeds: torch.Tensor, meta: StepMeta, kv_pool: torch.Tensor, last_accepted: torch.Tensor, block: int
+                       ) -> torch.Tensor:
+        """Draft tokens ``[N, block - 1]`` for blocks whose first token is ``last_accepted [N]``."""
+        x = self.block_hidden(embeds, meta, kv_pool)
+        n = x.shape[0] // block
+        hid = x.reshape(n, block, -1)[:, 1:, :]                                   # proposal positions 1 .. block-1
+        logits = self.head(hid.reshape(n * (block - 1), -1)).reshape(n, block - 1, -1)
+        pool = torch.topk(logits.amax(dim=1), min(self.cfg.domino_pool_size, logits.shape[-1]), dim=-1).indices      # [N, P]
+        base = torch.gather(logits, 2, pool[:, None, :].expand(-1, block - 1, -1))                                   # [N, B-1, P]
+        code = self.codebook[pool].float()                                                                           # [N, P, R]
+        zproj = hid[:, 1:, :].float() @ self.z_projection.float().t()                                                # [N, B-2, R]
+        out = torch.empty(n, block - 1, dtype=torch.int64, device=x.device)
+        pick = lambda score: torch.gather(pool, 1, score.argmax(-1, keepdim=True))[:, 0]      # ties → the first (best-ranked) slot
+        out[:, 0] = pick(base[:, 0])
+        h = torch.zeros(n, self.cfg.domino_gru_hidden_dim, device=x.device)
+        h = self.gru(last_accepted, h)
+        h = self.gru(out[:, 0], h)
+        for step in range(block - 2):
+            c = torch.nn.functional.silu(zproj[:, step] + h @ self.proj_state_weight.float().t())
+            out[:, step + 1] = pick(base[:, step + 1] + torch.einsum("npr,nr->np", code, c))
+            if step + 1 < block - 2:
+                h = self.gru(out[:, step + 1], h)
+        return out

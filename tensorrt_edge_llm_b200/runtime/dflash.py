@@ -99,8 +99,10 @@ class DFlashDecoder:
             self._mask_cache[n] = full_mask(n * b, b, self.device)
         meta = build_step_meta([b] * n, past, self.dkv.table_rows(seats), self.dkv.page_size, slot_ids=seats, logits_all=True,
                                device=self.device, tree_mask=self._mask_cache[n])
-        logits = self.draft.propose(embeds, meta, self.dkv.pool)        # block rows are written past the context, never committed
         self.stats.draft_forwards += 1
+        if hasattr(self.draft, "propose_tokens"):                        # Domino: proposals corrected by what precedes them
+            return self.draft.propose_tokens(embeds, meta, self.dkv.pool, ids[:, 0].to(self.device), b).to("cpu")
+        logits = self.draft.propose(embeds, meta, self.dkv.pool)        # block rows are written past the context, never committed
         return ops.argmax(logits).view(n, b)[:, 1:].to("cpu")
 
     # ---- prefill / round -----------------------------------------------------------------------

@@ -126,3 +126,58 @@ def test_llm_with_a_dflash_draft_static_and_in_flight():
     got = [o.token_ids for o in ifb.generate(prompts, SamplingParams(max_tokens=18, ignore_eos=True))]
     ifb.close()
     assert got == want
+
+
+def test_domino_rollout_matches_a_literal_restatement_and_stays_lossless():
+    """The correction head against a per-sequence loop with ``torch.nn.GRUCell`` (bias-free), and the decoder end to end."""
+    tcfg = tiny_llama_config(num_hidden_layers=4, vocab_size=120, dtype="float32")
+    target = AutoModel.from_config(tcfg, random_init=0)
+    kv = KVCacheManager(tcfg, num_pages=32, page_size=16, max_seats=3, max_pages_per_seq=10)
+    runner = ModelRunner(target, kv)
+    dcfg = tiny_llama_config(num_hidden_layers=2, vocab_size=120, dtype="float32")
+    dcfg.draft_type, dcfg.dflash_projector_type, dcfg.dflash_block_size, dcfg.dflash_mask_token_id = "dflash", "domino", 6, 119
+    dcfg.domino_pool_size, dcfg.domino_proj_dim, dcfg.domino_gru_hidden_dim = 16, 8, 10
+    draft = AutoModel.from_config(dcfg, random_init=1)
+    assert type(draft).__name__ == "DominoDraft"
+    g = torch.Generator().manual_seed(5)
+    with torch.no_grad():
+        for p in (draft.z_projection, draft.codebook, draft.gru_input_table, draft.gru_weight_hh, draft.proj_state_weight):
+            p.copy_(torch.randn(p.shape, generator=g) * 0.5)
+    dkv = KVCacheManager(dcfg, num_pages=32, page_size=16, max_seats=3, max_pages_per_seq=10, num_layers=2)
+    dec = DFlashDecoder(runner, draft, dkv)
+    prompts = [[5, 6, 7, 8, 9], [20, 21, 22]]
+    dec.prefill([0, 1], prompts)
+    got = dec._propose([0, 1])                                                   # [2, 5]
+    # literal restatement from the block's hidden states
+    from tensorrt_edge_llm_b200 import ops
+    from tensorrt_edge_llm_b200.ops.meta import build_step_meta
+    from tensorrt_edge_llm_b200.runtime.block_diffusion import full_mask
+    ids = torch.full((2, 6), 119, dtype=torch.int32)
+    ids[:, 0] = torch.tensor([dec.root[0], dec.root[1]], dtype=torch.int32)
+    meta = build_step_meta([6, 6], [dkv.lengths[0], dkv.lengths[1]], dkv.table_rows([0, 1]), 16, slot_ids=[0, 1], logits_all=True,
+                           tree_mask=full_mask(12, 6, "cpu"))
+    x = draft.block_hidden(ops.embedding(ids.reshape(-1), draft.embed_tokens.weight), meta, dkv.pool).reshape(2, 6, -1)
+    cell = torch.nn.GRUCell(1, 10, bias=False)
+    with torch.no_grad():
+        cell.weight_hh.copy_(draft.gru_weight_hh)
+    def gru(tok, h):                                                             # x · W_ih is tabulated per token
+        gi, gh = draft.gru_input_table[tok].float(), h @ cell.weight_hh.t()
+        r = torch.sigmoid(gi[:10] + gh[:10]); z = torch.sigmoid(gi[10:20] + gh[10:20]); n = torch.tanh(gi[20:] + r * gh[20:])
+        return (1 - z) * n + z * h
+    for b in range(2):
+        hid = x[b, 1:]
+        logits = draft.head(hid)
+        pool = torch.topk(logits.max(0).values, 16).indices
+        want = [int(pool[logits[0, pool].argmax()])]
+        h = gru(int(ids[b, 0]), torch.zeros(10))
+        h = gru(want[0], h)
+        for step in range(4):
+            c = torch.nn.functional.silu(draft.z_projection.float() @ hid[step + 1] + draft.proj_state_weight.float() @ h)
+            score = logits[step + 1, pool] + draft.codebook[pool].float() @ c
+            want.append(int(pool[score.argmax()]))
+            if step < 3:
+                h = gru(want[-1], h)
+        assert got[b].tolist() == want
+    # the correction changes proposals but never the output: verification keeps it the target's greedy continuation
+    dec.release([0, 1])
+    assert dec.generate([0, 1], prompts, 20) == _greedy(tcfg, prompts, 20)
