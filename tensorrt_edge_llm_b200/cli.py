@@ -23,6 +23,7 @@ COMMANDS = {
     "reduce-vocab": ("tensorrt_edge_llm_b200.commands.reduce_vocab", "Generate reduced-vocabulary artifacts"),
     "infer": ("tensorrt_edge_llm_b200.commands.infer", "Run a request file and write predictions"),
     "multistage": ("tensorrt_edge_llm_b200.commands.multistage", "Run requests through a multi-stage graph"),
+    "action": ("tensorrt_edge_llm_b200.commands.action", "Vision-language-action inference: reasoning text + trajectory"),
     "bench": ("tensorrt_edge_llm_b200.benchmarks.llm_bench", "Offline benchmark writing report.json"),
 }
 

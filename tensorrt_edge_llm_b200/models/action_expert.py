@@ -158,7 +158,20 @@ class ActionExpert(nn.Module):
             key = key[len("expert."):]
             for flat in ("gate_proj", "up_proj", "down_proj"):
                 key = key.replace(f".mlp_{flat}.", f".mlp.{flat}.")
-        return key
+        return key.replace("action_in_proj.encoder.trunk.", "action_in_proj.encoder.")
+
+    @classmethod
+    def from_pretrained(cls, expert_dir: str, device="cpu", comm=None) -> "ActionExpert":
+        """Expert from a directory with ``config.json`` (the action hyper-parameters, at top level or under ``action_config``)
+        and safetensors files in the reference's naming (``action_in_proj.*``, ``expert.layers.N.*``, ``action_out_proj.*``)."""
+        import json
+        import os
+        from ..checkpoint.loader import load_weights
+        with open(os.path.join(expert_dir, "config.json"), "r", encoding="utf-8") as f:
+            d = json.load(f)
+        model = cls(ActionConfig.from_dict(d.get("action_config", d)), comm)
+        load_weights(model, expert_dir, strict=True)
+        return model.to(device)
 
     def cos_sin(self, device) -> torch.Tensor:
         if self._cos_sin is None or self._cos_sin.device != torch.device(device):

@@ -100,3 +100,49 @@ def test_geometry_must_match_and_history_tokens():
     assert ActionExpert.checkpoint_key_remap("expert.layers.2.mlp_gate_proj.weight") == "layers.2.mlp.gate_proj.weight"
     assert ActionExpert.checkpoint_key_remap("expert.layers.0.self_attn.q_norm.weight") == "layers.0.self_attn.q_norm.weight"
     assert ActionExpert.checkpoint_key_remap("action_out_proj.bias") == "action_out_proj.bias"
+
+
+def test_expert_checkpoint_roundtrip_and_command(tmp_path):
+    """Save an expert under the reference's tensor names, load it back, and run the command's library form."""
+    import json
+    import os
+    from tensorrt_edge_llm_b200.checkpoint import save_file
+    from tensorrt_edge_llm_b200.commands.action import run_requests
+    from tensorrt_edge_llm_b200.runtime.llm import LLM
+    runner, expert, tcfg = _setup()
+    sd = {}
+    for name, t in expert.state_dict().items():
+        if name.startswith("layers."):
+            name = "expert." + name.replace(".mlp.down_proj.", ".mlp_down_proj.")
+        elif name == "norm.weight":
+            name = "expert.norm.weight"
+        name = name.replace("action_in_proj.encoder.", "action_in_proj.encoder.trunk.")
+        sd[name] = t.contiguous()
+    # the fused projections go back to the per-projection tensors a checkpoint holds
+    for i, layer in enumerate(expert.layers):
+        a = layer.self_attn
+        q, k, v = a.qkv_proj.weight.split([a.num_q_heads * 16, a.num_kv_heads * 16, a.num_kv_heads * 16], 0)
+        g, u = layer.mlp.gate_up_proj.weight.chunk(2, 0)
+        for n, t in (("self_attn.q_proj", q), ("self_attn.k_proj", k), ("self_attn.v_proj", v), ("mlp_gate_proj", g), ("mlp_up_proj", u)):
+            sd[f"expert.layers.{i}.{n}.weight"] = t.contiguous()
+        sd.pop(f"expert.layers.{i}.self_attn.qkv_proj.weight")
+        sd.pop(f"expert.layers.{i}.mlp.gate_up_proj.weight")
+    d = str(tmp_path)
+    save_file(sd, os.path.join(d, "model.safetensors"))
+    json.dump({"action_config": dict(vars(expert.action_cfg))}, open(os.path.join(d, "config.json"), "w"))
+    loaded = ActionExpert.from_pretrained(d)
+    x = torch.randn(1, 6, 2, generator=torch.Generator().manual_seed(3))
+    runner.prefill([0], [[5, 6, 7, 8]])
+    meta = runner._meta([0], [6], tree_mask=full_mask(6, 6, "cpu"))
+    assert torch.allclose(loaded.velocity(x, torch.tensor([0.5]), meta, runner.cache), expert.velocity(x, torch.tensor([0.5]), meta, runner.cache),
+                          atol=1e-6)
+    llm = LLM(tcfg, device="cpu", max_batch_size=1, max_input_len=64, max_kv_cache_capacity=128, page_size=16)
+    body = {"requests": [{"prompt_token_ids": [5, 6, 7, 8, 9], "trajectory_history": [[0, 0, 0], [0.5, 0.1, 0]], "max_generate_length": 5, "seed": 3},
+                         {"prompt_token_ids": [9, 8, 7], "max_generate_length": 3}]}
+    expert.action_cfg.num_traj_tokens, expert.action_cfg.traj_token_start = 20, 90
+    res = run_requests(llm, expert, body, num_steps=3)
+    assert len(res) == 2 and len(res[0]["token_ids"]) == 5 and len(res[0]["trajectory"]) == 6 and len(res[0]["trajectory"][0]) == 2
+    again = run_requests(llm, expert, body, num_steps=3)
+    assert again == res                                              # seeded noise: the same trajectories
+    from tensorrt_edge_llm_b200 import cli
+    assert "action" in cli.COMMANDS
