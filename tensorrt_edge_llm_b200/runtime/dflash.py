@@ -8,8 +8,9 @@ Round for one sequence whose target cache holds ``n`` tokens and whose last acce
     commit  : target cache advances by a+1 rows (y0, d1 .. da); their tapped hidden states become a+1 new context rows
               of the draft cache; the next round's y0 is the bonus token
 
-The output is exactly the target's greedy continuation.  Parity: ``cpp/runtime/decoding/dflashDecoder.cpp`` (round
-structure, delta lengths, block layout) with the draft of ``models/dflash.py``.  Greedy requests only; hybrid targets are
+Greedy requests get exactly the target's greedy continuation; sampled requests are verified by rejection sampling along
+the chain (static batches), so every token is distributed as the target's own sample.  Parity: ``cpp/runtime/decoding/dflashDecoder.cpp`` (round
+structure, delta lengths, block layout) with the draft of ``models/dflash.py``.  Hybrid targets are
 not supported (a partly accepted chain would need the recurrent state rolled back)."""
 from __future__ import annotations
 
@@ -61,7 +62,8 @@ class DFlashDecoder:
             draft.share_with(self.model)
         self.stats = DFlashStats()
         self.spec = _Headroom(self.block)          # what the request engine's session reads for KV head room
-        self.sampling = None                       # greedy verification only
+        self.sampling: Optional[dict] = None       # {"temperature", "top_k", "top_p", "seed"}: rejection-sampled verification
+        self._sample_gen: Optional[torch.Generator] = None
         self.root: Dict[int, int] = {}
         self._mask_cache: Dict[int, torch.Tensor] = {}
 
@@ -116,7 +118,13 @@ class DFlashDecoder:
                 self.r.kv.commit(s, q)
                 self.dkv.free(s)
             ends = torch.tensor(q_lens).cumsum(0) - 1
-            first = ops.argmax(logits.index_select(0, ends.to(self.device))).tolist()
+            last = logits.index_select(0, ends.to(self.device))
+            if self.sampling is None:
+                first = ops.argmax(last).tolist()
+            else:                                   # sampled request: the first token is a draw from the target distribution too
+                pr = ops.ref.sampling_probs(last, self.sampling["temperature"], self.sampling["top_k"], self.sampling["top_p"])
+                u = self._uniforms(len(seats), 1, 1)[:, 0, 0].to(pr.device)
+                first = torch.searchsorted(pr.double().cumsum(-1), u.double()[:, None]).clamp(max=pr.shape[-1] - 1)[:, 0].tolist()
             self._write_context(seats, feats, q_lens)
         for s, t in zip(seats, first):
             self.root[s] = int(t)
@@ -131,15 +139,29 @@ class DFlashDecoder:
         chain = torch.cat([torch.tensor([[self.root[s]] for s in seats], dtype=torch.int64), drafts.long()], dim=1)
         rows = chain.reshape(-1).to(torch.int32).to(self.device)
         logits, feats = self._target_step(seats, rows, [b] * n)           # rows written at n .. n+B-1, not committed yet
-        choice = ops.argmax(logits).view(n, b).to("cpu")                  # target's token after each chain row
+        sampled = None
+        if self.sampling is not None and forced_accept is None:
+            # the chain is a tree with one child per node: draft d is kept with the target's probability of d, a rejected
+            # position is redrawn from the target distribution without d, which keeps every token distributed as the target's
+            pr = ops.ref.sampling_probs(logits, self.sampling["temperature"], self.sampling["top_k"], self.sampling["top_p"]).view(n, b, -1)
+            parents = torch.arange(-1, b - 1).repeat(n, 1)
+            path, plen, bonus = ops.ref.spec_accept_sampling(pr.to("cpu"), chain, parents, b, self._uniforms(n, b, 2))
+            sampled = ((plen - 1).tolist(), bonus.tolist())
+            choice = None
+        else:
+            choice = ops.argmax(logits).view(n, b).to("cpu")              # target's token after each chain row
         out: List[List[int]] = []
         keep_rows, keep_lens = [], []
         for i, s in enumerate(seats):
             a = 0
-            limit = b - 1 if forced_accept is None else min(int(forced_accept[i]), b - 1)
-            while a < limit and (forced_accept is not None or int(drafts[i, a]) == int(choice[i, a])):
-                a += 1
-            toks = [int(t) for t in drafts[i, :a]] + [int(choice[i, a])]
+            if sampled is not None:
+                a = int(sampled[0][i])
+                toks = [int(t) for t in drafts[i, :a]] + [int(sampled[1][i])]
+            else:
+                limit = b - 1 if forced_accept is None else min(int(forced_accept[i]), b - 1)
+                while a < limit and (forced_accept is not None or int(drafts[i, a]) == int(choice[i, a])):
+                    a += 1
+                toks = [int(t) for t in drafts[i, :a]] + [int(choice[i, a])]
             out.append(toks)
             self.r.kv.commit(s, a + 1)                                    # y0 and the accepted drafts are real history now
             keep_rows.append(torch.arange(i * b, i * b + a + 1))
@@ -153,8 +175,7 @@ class DFlashDecoder:
     @torch.no_grad()
     def generate(self, seats: Sequence[int], prompts: Sequence[Sequence[int]], max_new_tokens: int, eos_id: Optional[int] = None,
                  sampling=None) -> List[List[int]]:
-        if sampling is not None:
-            raise ValueError("DFlash decoding verifies greedy requests only")
+        self.sampling, self._sample_gen = sampling, None
         for s in seats:
             self.r.kv.free(s)
         first = self.prefill(seats, prompts)
@@ -179,6 +200,11 @@ class DFlashDecoder:
                     nxt.append(i)
             live = nxt
         return out
+
+    def _uniforms(self, b: int, depth: int, width: int) -> torch.Tensor:
+        if self._sample_gen is None:
+            self._sample_gen = torch.Generator().manual_seed(int((self.sampling or {}).get("seed", 0)))
+        return torch.rand(b, depth, width, generator=self._sample_gen)
 
     def release(self, seats: Sequence[int]) -> None:
         for s in seats:

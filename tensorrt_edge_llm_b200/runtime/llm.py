@@ -429,7 +429,7 @@ class LLM:
             return self._generate_diffusion([p.tolist() for p in ids] if isinstance(ids, torch.Tensor) else ids, sp)
         if sp.needs_logits_processing:
             return self._generate_processed([p.tolist() for p in ids] if isinstance(ids, torch.Tensor) else ids, sp)
-        greedy_only = self.cfg.is_hybrid or getattr(self.spec_decoder, "name", "") == "dflash"
+        greedy_only = self.cfg.is_hybrid
         if self.spec_decoder is not None and not isinstance(ids, torch.Tensor) and (sp.temperature < 1e-3 or not greedy_only):
             return self._generate_speculative(ids, sp)
         n = len(ids)

@@ -118,9 +118,9 @@ def test_llm_with_a_dflash_draft_static_and_in_flight():
     assert type(llm.spec_decoder).__name__ == "DFlashDecoder" and llm.spec_decoder.dkv.pool.shape[0] == 2
     outs = llm.generate(prompts, SamplingParams(max_tokens=18, ignore_eos=True))
     assert [o.token_ids for o in outs] == want and outs[0].spec_stats["verify_rounds"] >= 3
-    # sampled requests take the plain path on a DFlash deployment
+    # sampled requests are verified by rejection sampling along the chain
     samp = llm.generate(prompts[:1], SamplingParams(max_tokens=6, ignore_eos=True, temperature=0.8, top_k=20, seed=1))[0]
-    assert len(samp.token_ids) == 6 and samp.spec_stats is None
+    assert len(samp.token_ids) == 6 and samp.spec_stats["verify_rounds"] >= 1
     ifb = LLM(tcfg, device="cpu", max_batch_size=2, max_input_len=32, max_kv_cache_capacity=96, page_size=16, draft_model=dcfg,
               enable_in_flight_batching=True)
     got = [o.token_ids for o in ifb.generate(prompts, SamplingParams(max_tokens=18, ignore_eos=True))]
@@ -181,3 +181,53 @@ def test_domino_rollout_matches_a_literal_restatement_and_stays_lossless():
     # the correction changes proposals but never the output: verification keeps it the target's greedy continuation
     dec.release([0, 1])
     assert dec.generate([0, 1], prompts, 20) == _greedy(tcfg, prompts, 20)
+
+
+def test_sampled_requests_follow_the_target_distribution():
+    """Second and third emitted token over many seeds against the exact marginals of the target model."""
+    from tensorrt_edge_llm_b200.ops import reference as ref
+    kw = dict(dtype="float32", vocab_size=12, hidden_size=64, intermediate_size=128, num_attention_heads=2, num_key_value_heads=1, head_dim=32)
+    cfg = tiny_llama_config(num_hidden_layers=2, **kw)
+    model = AutoModel.from_config(cfg, random_init=5)
+    with torch.no_grad():
+        model.lm_head.weight.mul_(8.0)                        # sharpen the distribution so that tokens differ in mass
+    dcfg = tiny_llama_config(num_hidden_layers=1, **kw)
+    dcfg.draft_type, dcfg.dflash_block_size, dcfg.dflash_mask_token_id = "dflash", 4, 11
+    draft = AutoModel.from_config(dcfg, random_init=6)
+    prompt = [3, 7, 1, 9, 5]
+    temp = 0.9
+    kv = KVCacheManager(cfg, num_pages=16, page_size=16, max_seats=1, max_pages_per_seq=4)
+    r = ModelRunner(model, kv)
+    p1 = ref.sampling_probs(r.prefill([0], [prompt]), temp)[0]
+    exact2 = torch.zeros(12)
+    for t1 in range(12):
+        if p1[t1] < 1e-6:
+            continue
+        kv.free(0)
+        r.prefill([0], [prompt])
+        exact2 += p1[t1] * ref.sampling_probs(r.step([0], [[t1]]), temp)[0]
+    dkv = KVCacheManager(dcfg, num_pages=16, page_size=16, max_seats=1, max_pages_per_seq=4, num_layers=1)
+    dec = DFlashDecoder(r, draft, dkv)
+    n = 700
+    c1, c2 = torch.zeros(12), torch.zeros(12)
+    multi = 0
+    for seed in range(n):
+        dec.release([0])
+        rounds0 = dec.stats.rounds
+        out = dec.generate([0], [prompt], 3, sampling={"temperature": temp, "top_k": 0, "top_p": 1.0, "seed": seed})[0]
+        c1[out[0]] += 1
+        c2[out[1]] += 1
+        multi += int(dec.stats.rounds - rounds0 == 1)          # three tokens from one round: at least one draft was accepted
+    tv1 = 0.5 * (c1 / n - p1).abs().sum()
+    tv2 = 0.5 * (c2 / n - exact2).abs().sum()
+    assert tv1 < 0.09 and tv2 < 0.09, (float(tv1), float(tv2))
+    assert float(exact2.max()) < 0.9 and multi > 0
+    # the same seed gives the same tokens; a cold temperature gives the greedy continuation
+    dec.release([0])
+    a = dec.generate([0], [prompt], 8, sampling={"temperature": temp, "top_k": 0, "top_p": 1.0, "seed": 3})
+    dec.release([0])
+    assert a == dec.generate([0], [prompt], 8, sampling={"temperature": temp, "top_k": 0, "top_p": 1.0, "seed": 3})
+    dec.release([0])
+    cold = dec.generate([0], [prompt], 8, sampling={"temperature": 0.01, "top_k": 0, "top_p": 1.0, "seed": 1})
+    dec.release([0])
+    assert cold == dec.generate([0], [prompt], 8)
