@@ -226,6 +226,67 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
                              "token_ids": toks}],
                 "usage": {"prompt_tokens": n_in, "completion_tokens": len(toks), "total_tokens": n_in + len(toks)}}
 
+    # ---- audio ------------------------------------------------------------------------------------------------
+    @app.post("/v1/audio/transcriptions")
+    async def audio_transcriptions(request: Request):
+        """OpenAI transcription route (``tensorrt_edgellm/server/api/routes.py:283``): a multipart form with the audio ``file``
+        (WAV) and optional ``prompt``, ``language``, ``response_format`` (json | text), ``temperature``.  The clip goes through
+        the audio encoder and the language model answers an instruction to transcribe it."""
+        import asyncio
+        from ..runtime import native as rt
+        from ..runtime.multimodal import MultimodalInputs
+        if multimodal is None or multimodal.audio is None:
+            return _error(400, "the loaded model has no audio encoder: transcription is not available", code="model_capability")
+        try:
+            form = await request.form()
+            upload = form.get("file")
+            if upload is None or not hasattr(upload, "read"):
+                raise ValueError("the form needs an audio 'file'")
+            data = await upload.read()
+            fmt = str(form.get("response_format", "json") or "json")
+            if fmt not in ("json", "text"):
+                raise ValueError("response_format must be json or text")
+            clip = rt.parse_wav(data)
+            hint, language = str(form.get("prompt", "") or ""), str(form.get("language", "") or "")
+            ask = "Transcribe the audio" + (f" (language: {language})" if language else "") + "." + (f" {hint}" if hint else "")
+            prompt = template.apply([{"role": "user", "content": _AUD + ask}], True, None, False)
+            # one clip: text before the marker, the clip, text after it
+            before, _, after = prompt.partition(_AUD)
+            req = MultimodalInputs()
+            if before:
+                req.text(encode(before))
+            req.audio(clip.samples, clip.sample_rate)
+            if after:
+                req.text(encode(after))
+            limit = int(form.get("max_tokens", 256) or 256)
+        except (ValueError, RuntimeError, KeyError) as e:
+            return _error(400, f"bad request: {e}")
+
+        def work():
+            client.admission.acquire()
+            try:
+                with client._lock:
+                    return multimodal.generate(req, max_tokens=limit)
+            finally:
+                client.admission.release()
+        toks = await asyncio.get_running_loop().run_in_executor(None, work)
+        eos = llm.cfg.eos_token_id
+        eos = set(eos if isinstance(eos, (list, tuple)) else [eos]) - {None}
+        cut = next((i for i, t in enumerate(toks) if t in eos), len(toks))
+        text = decode(toks[:cut]).strip()
+        if fmt == "text":
+            from fastapi.responses import PlainTextResponse
+            return PlainTextResponse(text)
+        return {"text": text, "usage": {"type": "tokens", "output_tokens": cut, "seconds": round(len(clip.samples) / max(clip.sample_rate, 1), 3)}}
+
+    @app.get("/v1/voices")
+    async def voices():
+        return {"object": "list", "data": []}              # no speech synthesis stage in this runtime
+
+    @app.post("/v1/audio/speech")
+    async def audio_speech(request: Request):
+        return _error(400, "the loaded model has no speech synthesis stage", code="model_capability")
+
     # ---- OpenAI chat completions ---------------------------------------------------------------------------
     @app.post("/v1/chat/completions")
     async def chat_completions(request: Request):

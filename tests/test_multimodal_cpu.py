@@ -102,4 +102,17 @@ def test_chat_route_with_image_and_audio_parts():
     assert plain.post("/v1/chat/completions", json={"messages": msg, "max_tokens": 4}).status_code == 400
     bad = [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "https://example.com/x.png"}}]}]
     assert c.post("/v1/chat/completions", json={"messages": bad}).status_code == 400
+    # transcription route: multipart upload of the clip, json or plain-text answer
+    r = c.post("/v1/audio/transcriptions", files={"file": ("clip.wav", buf.getvalue(), "audio/wav")},
+               data={"language": "en", "max_tokens": "5"})
+    assert r.status_code == 200 and isinstance(r.json()["text"], str) and r.json()["usage"]["seconds"] == 0.5
+    r = c.post("/v1/audio/transcriptions", files={"file": ("clip.wav", buf.getvalue(), "audio/wav")},
+               data={"response_format": "text", "max_tokens": "3"})
+    assert r.status_code == 200 and r.headers["content-type"].startswith("text/plain")
+    assert c.post("/v1/audio/transcriptions", files={"file": ("clip.wav", b"not a wav", "audio/wav")}).status_code == 400
+    assert c.post("/v1/audio/transcriptions", files={"file": ("clip.wav", buf.getvalue(), "audio/wav")},
+                  data={"response_format": "srt"}).status_code == 400
+    assert plain.post("/v1/audio/transcriptions", files={"file": ("clip.wav", buf.getvalue(), "audio/wav")}).status_code == 400
+    assert c.get("/v1/voices").json() == {"object": "list", "data": []}
+    assert c.post("/v1/audio/speech", json={"input": "hi", "voice": "x"}).status_code == 400
     llm.close()
