@@ -181,15 +181,56 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
         return StreamingResponse(gen, media_type="text/event-stream", headers={"Cache-Control": "no-cache", "X-Accel-Buffering": "no"})
 
     # ---- health / models -----------------------------------------------------------------------------------
+    def _capabilities():
+        spec = llm.spec_decoder
+        audio = multimodal is not None and multimodal.audio is not None
+        vision = multimodal is not None and multimodal.vision is not None
+        return {"chat": True, "transcription": audio, "speech": False,
+                "input_modalities": ["text"] + (["image"] if vision else []) + (["audio"] if audio else []), "output_modalities": ["text"],
+                "max_model_len": llm.kv.max_pages_per_seq * llm.kv.page_size, "max_input_len": llm.max_input_len,
+                "max_batch_size": llm.max_batch_size, "max_num_seqs": llm.max_batch_size, "kv_cache_dtype": str(llm.kv.pool.dtype).replace("torch.", ""),
+                "speculative_decoding": spec is not None or llm.diffusion_decoder is not None,
+                "speculative_method": getattr(spec, "name", "eagle3" if spec is not None else ("block_diffusion" if llm.diffusion_decoder is not None else None)),
+                "context_reuse": bool(getattr(getattr(llm, "session", None), "prefix", None) is not None), "in_flight_batching": llm.engine is not None}
+
+    def _engine_report():
+        """Engine status, scheduling counters and context-cache counters of the native request engine (``None`` without one)."""
+        if llm.engine is None:
+            return None, None, None
+        st, m = llm.engine.status(), llm.engine.metrics()
+        engine = {"serving": bool(st.available), "unavailable_reason": st.unavailable_reason, "queued": int(st.queued), "resident": int(st.resident)}
+        fields = ("submitted", "refused", "completed", "cancelled", "failed", "admitted_mid_flight", "stalls_no_capacity", "stalls_exclusive",
+                  "decode_steps", "prompt_steps", "mixed_steps", "step_tokens", "paused_resident_steps", "session_failures")
+        scheduling = {k: int(getattr(m, k)) for k in fields}
+        scheduling["queue_latency_s_sum"] = float(m.queue_latency_s_sum)
+        sess = getattr(llm, "session", None)
+        cache = None
+        if sess is not None and sess.prefix is not None:
+            cache = {"reused_tokens": int(m.prefix_reused_tokens), "snapshot_hits": int(sess.snapshot_hits), "snapshots": len(sess.snapshots)}
+        return engine, scheduling, cache
+
     @app.get("/health")
     async def health():
+        """Liveness with the engine's counters (``tensorrt_edgellm/server/api/routes.py:104``): 503 once the engine refuses work."""
         running, waiting = client.admission.depth
-        return {"status": "ok", "uptime_s": round(time.time() - app.state.started, 1), "running": running, "queued": waiting}
+        engine, scheduling, cache = _engine_report()
+        healthy = engine is None or engine["serving"]
+        body = {"status": "healthy" if healthy else "unhealthy", "model": name, "uptime_s": round(time.time() - app.state.started, 1),
+                "active_requests": running, "queued_requests": waiting, "running": running, "queued": waiting,
+                "scheduling": scheduling, "context_cache": cache, "engine": engine, "capabilities": _capabilities()}
+        if not healthy:
+            body["reason"] = engine["unavailable_reason"]
+            return JSONResponse(status_code=503, content=body)
+        return body
 
     @app.get("/health/ready")
     async def ready():
         ok, why = client.ready()
-        return {"status": "ready"} if ok else _error(503, why or "not ready", "service_unavailable")
+        running, waiting = client.admission.depth
+        if not ok:
+            return JSONResponse(status_code=503, content={"status": "unavailable", "reason": why or "not ready", "active_requests": running,
+                                                          "queued_requests": waiting, "error": {"message": why or "not ready", "type": "service_unavailable"}})
+        return {"status": "ready", "active_requests": running, "queued_requests": waiting}
 
     @app.get("/v1/models")
     async def models():

@@ -45,8 +45,13 @@ AUTH = {"Authorization": "Bearer sekret"}
 
 
 def test_health_models_and_auth(client):
-    assert client.get("/health").json()["status"] == "ok"
-    assert client.get("/health/ready").status_code == 200
+    h = client.get("/health").json()
+    assert h["status"] == "healthy" and h["model"] == "tiny" and h["engine"]["serving"] and h["active_requests"] == 0
+    caps = h["capabilities"]
+    assert caps["chat"] and caps["in_flight_batching"] and not caps["speech"] and caps["input_modalities"] == ["text"]
+    assert caps["max_batch_size"] == 4 and caps["max_input_len"] == 256 and caps["max_model_len"] == 320 and caps["speculative_method"] is None
+    assert set(h["scheduling"]) >= {"submitted", "completed", "decode_steps", "admitted_mid_flight", "stalls_no_capacity"}
+    assert client.get("/health/ready").json() == {"status": "ready", "active_requests": 0, "queued_requests": 0}
     assert client.get("/v1/models").status_code == 401
     assert client.get("/v1/models", headers={"x-api-key": "sekret"}).json()["data"][0]["id"] == "tiny"
 
