@@ -242,7 +242,8 @@ PYBIND11_MODULE(_telb_runtime, m) {
         .def_readwrite("logit_bias_values", &GenerationRequest::logit_bias_values)
         .def_readwrite("cache_lookup", &GenerationRequest::cache_lookup)
         .def_readwrite("cache_commit", &GenerationRequest::cache_commit)
-        .def_readwrite("disable_spec_decode", &GenerationRequest::disable_spec_decode);
+        .def_readwrite("disable_spec_decode", &GenerationRequest::disable_spec_decode)
+        .def_readwrite("embeds_key", &GenerationRequest::embeds_key);
     py::class_<AdmissionResult>(m, "AdmissionResult")
         .def(py::init<>())
         .def_readwrite("admitted", &AdmissionResult::admitted)

@@ -140,6 +140,7 @@ struct GenerationRequest {
     bool cache_lookup = true;
     int cache_commit = 1;
     bool disable_spec_decode = false;       // decode this request token by token even on a speculative deployment
+    int64_t embeds_key = 0;                 // non-zero: the session holds prompt embedding rows (multimodal prompt) under this key
 };
 
 struct AdmissionResult {

@@ -233,6 +233,22 @@ class LLM:
             raise RuntimeError(why)
         return h
 
+    def submit_multimodal(self, ids: Sequence[int], embeds: torch.Tensor, sampling_params: Optional[SamplingParams] = None, positions3=None,
+                          rope_delta: int = 0, deepstack: Optional[dict] = None, priority: int = 0):
+        """Queue a multimodal prompt on the request engine: ``ids`` hold placeholder tokens where media sits, ``embeds`` the
+        rows actually fed (``runtime.multimodal.MultimodalRunner.build`` makes both).  Returns the request handle."""
+        if self.engine is None:
+            raise RuntimeError("submit_multimodal needs in-flight batching")
+        sp = sampling_params or SamplingParams()
+        req = self._native_request([int(t) for t in ids], sp, priority)
+        req.embeds_key = self.session.register_embeds(list(ids), embeds, positions3, rope_delta, deepstack)
+        req.cache_lookup = False
+        h, why = self.engine.submit(req)
+        if h is None:
+            self.session.mm_store.pop(int(req.embeds_key), None)
+            raise RuntimeError(why)
+        return h
+
     def generate_stream(self, prompt, sampling_params: Optional[SamplingParams] = None, on_metrics=None):
         """Yield ``(token_ids, text_delta)`` chunks as they are produced."""
         h = self.submit(prompt, sampling_params)

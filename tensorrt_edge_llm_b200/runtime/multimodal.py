@@ -7,6 +7,7 @@ uses them, prefill from embeddings, then decode as usual.  Encoders run data-par
 their outputs are cached by content hash when a cache is given."""
 from __future__ import annotations
 
+import threading
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence, Tuple
 
@@ -51,6 +52,7 @@ class MultimodalRunner:
         self.min_pixels, self.max_pixels = min_pixels, max_pixels
         self.max_tiles = max_tiles                         # InternVL dynamic resolution: tiles per image (a thumbnail comes on top)
         self.device = llm.device
+        self._build_lock = threading.Lock()
         self._grids: List[Tuple[int, int, int]] = []      # (t, rows, columns) of each encoded image in language-model tokens
         self._deep: List[torch.Tensor] = []                # deepstack features of the images encoded last (one tensor per level)
         self.deepstack: Optional[dict] = None              # {decoder layer: (prompt rows, features)} of the prompt built last
@@ -235,12 +237,22 @@ class MultimodalRunner:
 
     @torch.no_grad()
     def generate(self, req: MultimodalInputs, max_tokens: int = 32, seat: int = 0) -> List[int]:
-        ids, emb, positions3, delta = self.build(req)
+        with self._build_lock:                 # the encoders keep scratch buffers: one prompt is built at a time
+            ids, emb, positions3, delta = self.build(req)
+            deep = self.deepstack
+        if self.llm.engine is not None:
+            # in-flight batching: the request engine owns the seats; the prompt joins its steps next to everyone else's rows
+            from .runner import SamplingParams
+            h = self.llm.submit_multimodal(ids, emb, SamplingParams(max_tokens=max_tokens, ignore_eos=True), positions3, delta or 0, deep)
+            toks = h.get(3600.0)
+            if h.error():
+                raise RuntimeError(h.error())
+            return [int(t) for t in toks]
         runner, kv = self.llm.runner, self.llm.kv
         kv.free(seat)
         kv.reserve(seat, len(ids) + max_tokens)
         logits = runner.prefill_embeds([seat], [emb], positions3=None if positions3 is None else [positions3],
-                                       rope_deltas=None if positions3 is None else [delta], deepstack=self.deepstack)
+                                       rope_deltas=None if positions3 is None else [delta], deepstack=deep)
         first = runner.pick(logits)
         out = [int(first[0])]
         if max_tokens > 1:

@@ -164,6 +164,33 @@ class ModelRunner:
             self.kv.commit(s, q)
         return logits
 
+    @torch.no_grad()
+    def step_embeds(self, seats: Sequence[int], embeds: Sequence[torch.Tensor], positions3: Optional[Sequence[Optional[torch.Tensor]]] = None,
+                    deepstack: Optional[dict] = None) -> torch.Tensor:
+        """One ragged step whose rows are embedding rows: prompt chunks of multimodal requests next to ordinary prompt chunks
+        and decode rows (already embedded by the caller).  ``positions3[i]`` is the ``[3, T_i]`` position block of sequence
+        ``i`` or ``None`` for text-like rows, which take ``cache length + decode offset + j`` on all three components.
+        ``deepstack`` indexes rows of the packed step.  Commits every row; returns last-row logits ``[N, V]``."""
+        q_lens = [int(e.shape[0]) for e in embeds]
+        for s in seats:
+            if self.kv.lengths[s] == 0:
+                self.rope_delta.pop(s, None)              # a fresh sequence on this seat
+        base = [self.kv.lengths[s] + self.rope_delta.get(s, 0) for s in seats]
+        flat_pos = [b + j for b, q in zip(base, q_lens) for j in range(q)]
+        meta = self._meta(seats, q_lens, positions=flat_pos)
+        if positions3 is not None and any(p is not None for p in positions3):
+            blocks = []
+            for p3, b, q in zip(positions3, base, q_lens):
+                blocks.append(p3.to(torch.int32) if p3 is not None else torch.arange(b, b + q, dtype=torch.int32)[None, :].expand(3, q))
+            meta.positions3 = torch.cat(blocks, dim=1).to(self.device)
+        if deepstack:
+            meta.deepstack = {int(k): (torch.as_tensor(r, dtype=torch.int64, device=self.device), f.to(self.device)) for k, (r, f) in deepstack.items()}
+        x = torch.cat([e.to(self.device) for e in embeds], dim=0).to(self.model.cfg.compute_dtype)
+        logits = self.model(None, meta, self.cache, inputs_embeds=x)
+        for s, q in zip(seats, q_lens):
+            self.kv.commit(s, q)
+        return logits
+
     def embed_tokens(self, ids: Sequence[int]) -> torch.Tensor:
         t = torch.tensor(list(ids), dtype=torch.int32, device=self.device)
         return ops.embedding(t, self.model.model.embed_tokens.weight)

@@ -26,7 +26,7 @@ from .runner import ModelRunner, SamplingParams
 
 
 class _Seq:
-    __slots__ = ("req", "request_id", "tokens", "generated", "last_token", "finished", "row_state", "plain", "feed")
+    __slots__ = ("req", "request_id", "tokens", "generated", "last_token", "finished", "row_state", "plain", "feed", "mm")
 
     def __init__(self, req, request_id):
         self.req, self.request_id = req, request_id
@@ -36,6 +36,7 @@ class _Seq:
         self.finished = False
         self.row_state = None            # logits.RowState when the request biases, constrains or reports log-probabilities
         self.feed: List[int] = []        # emitted tokens whose KV is not written yet, when more than the last one (jump-forward)
+        self.mm: Optional[dict] = None   # multimodal prompt: embedding rows, 3-D positions, decode offset, deepstack levels
 
 
 class ModelSession(rt.RuntimeSession):
@@ -72,6 +73,22 @@ class ModelSession(rt.RuntimeSession):
         self.max_snapshots = max_snapshots
         self.snapshot_hits = 0
         self.jump_forward_tokens = 0       # tokens appended because a grammar left no choice (no forward pass of their own)
+        # multimodal prompts wait here between `register_embeds` (caller's thread) and admission (engine thread)
+        self.mm_store: Dict[int, dict] = {}
+        self._mm_next = 1
+
+    def register_embeds(self, ids, emb: torch.Tensor, positions3=None, delta: int = 0, deepstack: Optional[dict] = None) -> int:
+        """Park a multimodal prompt (placeholder ids, embedding rows with the media spliced in, optional 3-D positions,
+        decode offset and deepstack levels); the returned key goes into ``GenerationRequest.embeds_key``."""
+        if self.mirror is not None or self.spec is not None:
+            raise ValueError("multimodal prompts under in-flight batching need a deployment without tensor-parallel mirroring or speculative decoding")
+        if emb.shape[0] != len(ids):
+            raise ValueError("one embedding row per prompt token is needed")
+        key = self._mm_next
+        self._mm_next += 1
+        self.mm_store[key] = {"emb": emb, "pos3": positions3, "delta": int(delta or 0),
+                              "deepstack": {int(k): (torch.as_tensor(r, dtype=torch.int64), f) for k, (r, f) in (deepstack or {}).items()}}
+        return key
 
     # ---- seam ------------------------------------------------------------------------------------
     def capabilities(self):
@@ -108,13 +125,19 @@ class ModelSession(rt.RuntimeSession):
             except ValueError as e:
                 r.admitted, r.retry_later, r.reason = False, False, f"EDGELLM_BAD_REQUEST: {e}"
                 return r
+        mm = None
+        if req.embeds_key:
+            mm = self.mm_store.get(int(req.embeds_key))
+            if mm is None or mm["emb"].shape[0] != n:
+                r.admitted, r.retry_later, r.reason = False, False, "EDGELLM_BAD_REQUEST: unknown or mismatched multimodal prompt key"
+                return r
         slot = self.slots.acquire()
         if slot < 0:
             r.admitted, r.retry_later, r.reason = False, True, "no free seat"
             return r
         reused = 0
         try:
-            if self.prefix is not None and req.cache_lookup:
+            if self.prefix is not None and req.cache_lookup and mm is None:      # placeholder ids say nothing about the media
                 m = self.prefix.lookup(list(req.prompt_ids))
                 pages, tokens = list(m.pages), m.tokens
                 if tokens and self.hybrid:
@@ -142,6 +165,9 @@ class ModelSession(rt.RuntimeSession):
         self.seqs[slot] = _Seq(req, request_id)
         self.seqs[slot].row_state = row_state
         self.seqs[slot].plain = plain
+        if mm is not None:
+            self.seqs[slot].mm = mm
+            self.mm_store.pop(int(req.embeds_key), None)
         r.admitted, r.slot, r.reused_tokens = True, slot, reused
         return r
 
@@ -282,7 +308,10 @@ class ModelSession(rt.RuntimeSession):
             lora.set_segments(segs)
         if self.mirror is not None:
             self.mirror.send(("step", seats, token_lists))
-        logits = self.runner.step(seats, token_lists)      # one row per sequence (its last token)
+        if any(s.kind == rt.WorkKind.Context and self.seqs[s.slot].mm is not None for s in seqs):
+            logits = self._step_with_embeds(seqs, seats, token_lists)
+        else:
+            logits = self.runner.step(seats, token_lists)      # one row per sequence (its last token)
         rows = [i for i, p in enumerate(producers) if p]
         out = rt.StepResult()
         deltas = []
@@ -335,15 +364,44 @@ class ModelSession(rt.RuntimeSession):
             for s in seqs:
                 if s.kind == rt.WorkKind.Context and s.last_chunk:
                     q = self.seqs[s.slot]
-                    if q.req.cache_commit >= 1:
+                    if q.req.cache_commit >= 1 and q.mm is None:      # placeholder ids of media prompts must not be shared
                         self.prefix.insert(list(q.req.prompt_ids), len(q.req.prompt_ids), self.kv.pages_of(s.slot))
         out.deltas = deltas
         return out
 
+    def _step_with_embeds(self, seqs, seats, token_lists) -> torch.Tensor:
+        """A step that holds a prompt chunk of a multimodal request: every row is fed as an embedding row — media rows from
+        the request's prepared prompt, all other rows (text prompts, decode rows) through the token table."""
+        embeds, pos3, deep = [], [], {}
+        row0 = 0
+        for s, toks in zip(seqs, token_lists):
+            q = self.seqs[s.slot]
+            if q.mm is not None and s.kind == rt.WorkKind.Context:
+                lo, hi = s.start, s.start + s.length
+                embeds.append(q.mm["emb"][lo:hi])
+                pos3.append(None if q.mm["pos3"] is None else q.mm["pos3"][:, lo:hi])
+                for k, (rows, feats) in q.mm["deepstack"].items():
+                    sel = (rows >= lo) & (rows < hi)
+                    if bool(sel.any()):
+                        acc = deep.setdefault(k, ([], []))
+                        acc[0].append(rows[sel] - lo + row0)
+                        acc[1].append(feats[sel.to(feats.device)])
+            else:
+                embeds.append(self.runner.embed_tokens(toks))
+                pos3.append(None)
+            row0 += len(toks)
+        deepstack = {k: (torch.cat(r), torch.cat(f)) for k, (r, f) in deep.items()} or None
+        logits = self.runner.step_embeds(seats, embeds, pos3, deepstack)
+        for s in seqs:
+            q = self.seqs[s.slot]
+            if q.mm is not None and s.kind == rt.WorkKind.Context and s.last_chunk:
+                self.runner.rope_delta[s.slot] = q.mm["delta"]          # decode rows continue after the largest media position
+        return logits
+
     def release(self, slot):
         if slot in self.seqs:
             q = self.seqs[slot]
-            if self.prefix is not None and q.req.cache_commit >= 2 and not self.hybrid:
+            if self.prefix is not None and q.req.cache_commit >= 2 and not self.hybrid and q.mm is None:
                 # "including generated tokens": the full pages of prompt + output become reusable (a follow-up turn that
                 # quotes the answer starts from them); hybrid models publish prompts only, their snapshots end there
                 filled = min(self.kv.lengths[slot], len(q.tokens))

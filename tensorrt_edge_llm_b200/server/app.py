@@ -131,7 +131,8 @@ def _truncate_at_stop(text: str, stops) -> (str, bool):
 def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optional[ChatTemplate] = None,
                model_name: str = "", multimodal=None) -> FastAPI:
     """``multimodal``: a ``runtime.multimodal.MultimodalRunner`` over ``llm``; chat requests whose messages carry image or
-    audio parts are then answered through it (one at a time, on the static path)."""
+    audio parts are then answered through it: on the request engine next to all other requests when in-flight batching is on,
+    otherwise one at a time on the static path."""
     api = api or ApiConfig()
     client = EngineClient(llm, api.max_queued_requests, api.queue_timeout)
     template = chat_template or ChatTemplate()
@@ -256,6 +257,8 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
         def work():
             client.admission.acquire()
             try:
+                if llm.engine is not None:             # the request engine batches it with everything else in flight
+                    return multimodal.generate(req, max_tokens=sp.max_tokens)
                 with client._lock:
                     return multimodal.generate(req, max_tokens=sp.max_tokens)
             finally:
@@ -306,6 +309,8 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
         def work():
             client.admission.acquire()
             try:
+                if llm.engine is not None:
+                    return multimodal.generate(req, max_tokens=limit)
                 with client._lock:
                     return multimodal.generate(req, max_tokens=limit)
             finally:

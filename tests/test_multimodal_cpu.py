@@ -116,3 +116,38 @@ def test_chat_route_with_image_and_audio_parts():
     assert c.get("/v1/voices").json() == {"object": "list", "data": []}
     assert c.post("/v1/audio/speech", json={"input": "hi", "voice": "x"}).status_code == 400
     llm.close()
+
+
+def test_multimodal_requests_under_in_flight_batching():
+    """With the request engine on, multimodal prompts join its steps (chunked, next to text requests) and give the same tokens
+    as the static path."""
+    import threading
+    from tensorrt_edge_llm_b200.runtime.llm import LLM
+    from tensorrt_edge_llm_b200.runtime.runner import SamplingParams
+    cfg = _llm(mrope=True).cfg
+    static = LLM(cfg, device="cpu", max_batch_size=3, max_input_len=256, max_kv_cache_capacity=320, page_size=16)
+    v, a = _encoders()
+    rng = np.random.default_rng(3)
+    img = rng.integers(0, 255, (32, 32, 3), dtype=np.uint8)
+    clip = (np.sin(np.arange(8000) / 15.0) * 0.3).astype(np.float32)
+    reqs = [MultimodalInputs().text([3, 4, 5]).image(img).text([6, 7]),
+            MultimodalInputs().text([8]).audio(clip, 16000).text([9, 10, 11]).image(img).text([12])]
+    mm_static = MultimodalRunner(static, v, a, image_token_id=298, audio_token_id=299)
+    want = [mm_static.generate(r, max_tokens=6) for r in reqs]
+    text_want = static.generate([[20, 21, 22, 23]], SamplingParams(max_tokens=6, ignore_eos=True))[0].token_ids
+    ifb = LLM(cfg, device="cpu", max_batch_size=3, max_input_len=256, max_kv_cache_capacity=320, page_size=16, enable_in_flight_batching=True,
+              enable_prefix_cache=True, scheduling={"max_chunk_tokens": 16, "max_num_tokens": 48})
+    mm = MultimodalRunner(ifb, v, a, image_token_id=298, audio_token_id=299)
+    got = [None, None]
+    th = [threading.Thread(target=lambda i=i: got.__setitem__(i, mm.generate(reqs[i], max_tokens=6))) for i in range(2)]
+    for t in th:
+        t.start()
+    text_got = ifb.generate([[20, 21, 22, 23]], SamplingParams(max_tokens=6, ignore_eos=True))[0].token_ids
+    for t in th:
+        t.join()
+    assert got == want and text_got == text_want
+    # the same placeholder ids with another image must not reuse the first prompt's pages
+    other = MultimodalInputs().text([3, 4, 5]).image(rng.integers(0, 255, (32, 32, 3), dtype=np.uint8)).text([6, 7])
+    assert mm.generate(other, max_tokens=6) == mm_static.generate(other, max_tokens=6)
+    assert ifb.session.mm_store == {}
+    ifb.close()
