@@ -228,6 +228,8 @@ class LLM:
         if self.engine is None:
             raise RuntimeError("LLM was built without enable_in_flight_batching")
         ids = self._encode([prompt])[0]
+        if hasattr(ids, "embeds"):
+            return self.submit_multimodal(ids.ids, ids.embeds, sampling_params, ids.positions3, ids.rope_delta, ids.deepstack, priority)
         h, why = self.engine.submit(self._native_request(ids, sampling_params or SamplingParams(), priority))
         if h is None:
             raise RuntimeError(why)
@@ -275,7 +277,9 @@ class LLM:
     def _encode(self, prompts) -> List[List[int]]:
         out = []
         for p in prompts:
-            if isinstance(p, str):
+            if hasattr(p, "embeds") and hasattr(p, "ids"):        # runtime.multimodal.MultimodalPrompt: passes through as it is
+                out.append(p)
+            elif isinstance(p, str):
                 if self.tokenizer is None:
                     raise ValueError("text prompts need a tokenizer")
                 out.append(list(self.tokenizer.encode(p)))
@@ -305,7 +309,7 @@ class LLM:
                 text = self.tokenizer.decode(toks) if self.tokenizer is not None else None
                 if reason == "error" and h.error():
                     raise ValueError(h.error()) if "EDGELLM_BAD_REQUEST" in h.error() else RuntimeError(h.error())
-                outs.append(RequestOutput(p, toks, text, reason, st.ttft_s, max(st.total_s - st.ttft_s, 0.0),
+                outs.append(RequestOutput(list(p), toks, text, reason, st.ttft_s, max(st.total_s - st.ttft_s, 0.0),
                                           self._logprob_rows(toks, h.logprobs()), int(st.reused_tokens)))
             return outs
         if isinstance(prompts, torch.Tensor):

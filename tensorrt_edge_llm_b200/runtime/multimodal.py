@@ -42,6 +42,23 @@ class MultimodalInputs:
         return self
 
 
+@dataclass
+class MultimodalPrompt:
+    """A prompt ready for the engine: placeholder ids where media sits and the rows actually fed.  Behaves like its id list
+    (``len``, iteration), so request plumbing that counts or echoes prompt tokens needs no special case."""
+    ids: List[int]
+    embeds: torch.Tensor
+    positions3: Optional[torch.Tensor] = None
+    rope_delta: int = 0
+    deepstack: Optional[dict] = None
+
+    def __len__(self) -> int:
+        return len(self.ids)
+
+    def __iter__(self):
+        return iter(self.ids)
+
+
 class MultimodalRunner:
     def __init__(self, llm, vision: Optional[VisionEncoder] = None, audio=None, image_token_id: int = 0, audio_token_id: int = 1,
                  cache_bytes: int = 0, visual_keep_ratio: float = 1.0, min_pixels: int = 0, max_pixels: int = 0, max_tiles: int = 12):
@@ -234,6 +251,13 @@ class MultimodalRunner:
             img_only = [t if t != self.audio_token_id else -1 for t in ids]
             positions3, delta = ref.mrope_positions(img_only, self.image_token_id, grids, spatial_merge=1)
         return ids, emb, positions3, delta
+
+    @torch.no_grad()
+    def prepare(self, req: MultimodalInputs) -> MultimodalPrompt:
+        """Encode the media and build the prompt the request engine takes (``LLM.submit`` / ``LLM.generate`` accept it)."""
+        with self._build_lock:
+            ids, emb, positions3, delta = self.build(req)
+            return MultimodalPrompt(ids, emb, positions3, int(delta or 0), self.deepstack)
 
     @torch.no_grad()
     def generate(self, req: MultimodalInputs, max_tokens: int = 32, seat: int = 0) -> List[int]:

@@ -238,13 +238,12 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
         return {"object": "list", "data": [{"id": name, "object": "model", "created": int(app.state.started), "owned_by": "local",
                                             "max_model_len": llm.max_input_len}]}
 
-    async def _multimodal_chat(body, messages, media, sp):
-        import asyncio
+    def _media_request(prompt, media):
+        """Rendered prompt with media markers → text pieces and decoded media in order."""
+        import re
         from ..runtime import native as rt
         from ..runtime.multimodal import MultimodalInputs
-        prompt = template.apply(messages, True, None, bool((body.get("chat_template_kwargs") or {}).get("enable_thinking", True)))
         req, it = MultimodalInputs(), iter(media)
-        import re
         for piece in re.split(f"({_IMG}|{_AUD})", prompt):
             if piece == _IMG:
                 req.image(next(it)[1])
@@ -253,6 +252,12 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
                 req.audio(clip.samples, clip.sample_rate)
             elif piece:
                 req.text(encode(piece))
+        return req
+
+    async def _multimodal_chat(body, messages, media, sp):
+        import asyncio
+        prompt = template.apply(messages, True, None, bool((body.get("chat_template_kwargs") or {}).get("enable_thinking", True)))
+        req = _media_request(prompt, media)
 
         def work():
             client.admission.acquire()
@@ -347,10 +352,17 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
             if media:
                 if multimodal is None:
                     raise ValueError("this server has no multimodal runner: send text-only messages")
-                return await _multimodal_chat(body, messages, media, sp)
+                if llm.engine is None:
+                    return await _multimodal_chat(body, messages, media, sp)
             prompt = template.apply(messages, True, body.get("tools"), bool((body.get("chat_template_kwargs") or {}).get("enable_thinking", True)))
-            ids = encode(prompt)
-        except (KeyError, ValueError, TypeError, json.JSONDecodeError) as e:
+            if media:
+                # in-flight batching: encode the media now, then the prepared prompt takes the same road as a text prompt
+                # (streaming, tools, reasoning, log-probabilities, priorities)
+                import asyncio
+                ids = await asyncio.get_running_loop().run_in_executor(None, multimodal.prepare, _media_request(prompt, media))
+            else:
+                ids = encode(prompt)
+        except (KeyError, ValueError, TypeError, RuntimeError, json.JSONDecodeError) as e:
             return _error(400, f"bad request: {e}")
         want_parse = reasoning is not None or tool_cfg.parse_output
         bad = check_len(ids)

@@ -97,10 +97,11 @@ class EngineClient:
             ok, why = self.ready()
             if not ok:
                 raise EngineUnavailable(why)
+            prompt = ids if hasattr(ids, "embeds") else list(ids)         # a prepared multimodal prompt passes through
             if self.llm.engine is not None:
-                return self.llm.generate([list(ids)], sp)[0]
+                return self.llm.generate([prompt], sp)[0]
             with self._lock:
-                return self.llm.generate([list(ids)], sp)[0]
+                return self.llm.generate([prompt], sp)[0]
         finally:
             self.admission.release()
 
@@ -128,7 +129,7 @@ class EngineClient:
                 ok, why = self.ready()
                 if not ok:
                     raise EngineUnavailable(why)
-                handle = self.llm.submit(list(ids), sp, priority)
+                handle = self.llm.submit(ids if hasattr(ids, "embeds") else list(ids), sp, priority)
                 ch = handle.stream()
                 pending = b""
                 tok = self.llm.tokenizer
