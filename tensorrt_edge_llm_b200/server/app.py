@@ -107,6 +107,10 @@ def _split_media(messages):
                 text += part.get("text", "")
             elif kind in ("image", "image_url"):
                 src = part.get("image") or (part.get("image_url") or {}).get("url")
+                source = part.get("source")
+                if src is None and isinstance(source, dict):            # Anthropic block: {"type": "base64", "media_type", "data"} or a URL
+                    src = ("data:" + str(source.get("media_type", "image/png")) + ";base64," + str(source.get("data", ""))
+                           if source.get("type") == "base64" else source.get("url"))
                 media.append(("image", _media_bytes(str(src))))
                 text += _IMG
             elif kind in ("audio", "input_audio", "audio_url"):
@@ -516,9 +520,23 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
         for m in body["messages"]:
             c = m.get("content", "")
             if not isinstance(c, str):
+                if any(isinstance(b, dict) and b.get("type") == "image" for b in c):
+                    msgs.append({"role": m["role"], "content": [b for b in c if isinstance(b, dict) and b.get("type") in ("text", "image")]})
+                    continue
                 c = "".join(b.get("text", "") for b in c if isinstance(b, dict) and b.get("type") == "text")
             msgs.append({"role": m["role"], "content": c})
         return msgs
+
+    async def anthropic_prompt(body):
+        """Prompt of an Anthropic request: token ids, or a prepared multimodal prompt when image blocks are present."""
+        msgs, media = _split_media(anthropic_messages(body))
+        text = template.apply(msgs, True)
+        if not media:
+            return encode(text)
+        if multimodal is None or llm.engine is None:
+            raise ValueError("image blocks need a server with a vision tower and in-flight batching")
+        import asyncio
+        return await asyncio.get_running_loop().run_in_executor(None, multimodal.prepare, _media_request(text, media))
 
     @app.post("/v1/messages")
     async def messages(request: Request):
@@ -528,8 +546,8 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
                 raise ValueError("max_tokens is required")
             sp = _sampling(body)
             sp.stop_token_ids = tuple(sp.stop_token_ids)
-            ids = encode(template.apply(anthropic_messages(body), True))
-        except (KeyError, ValueError, TypeError, json.JSONDecodeError) as e:
+            ids = await anthropic_prompt(body)
+        except (KeyError, ValueError, TypeError, RuntimeError, json.JSONDecodeError) as e:
             return JSONResponse(status_code=400, content={"type": "error", "error": {"type": "invalid_request_error", "message": str(e)}})
         bad = check_len(ids)
         if bad:
@@ -565,7 +583,7 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
     async def count_tokens(request: Request):
         try:
             body = await request.json()
-            return {"input_tokens": len(encode(template.apply(anthropic_messages(body), True)))}
+            return {"input_tokens": len(await anthropic_prompt(body))}
         except (KeyError, ValueError, TypeError, json.JSONDecodeError) as e:
             return JSONResponse(status_code=400, content={"type": "error", "error": {"type": "invalid_request_error", "message": str(e)}})
 

@@ -194,4 +194,12 @@ def test_server_multimodal_chat_on_the_request_engine():
     assert again["choices"][0]["message"]["content"] == full["choices"][0]["message"]["content"]
     bad = [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "data:image/png;base64," + base64.b64encode(b"nope").decode()}}]}]
     assert c.post("/v1/chat/completions", json={"messages": bad}).status_code == 400
+    # Anthropic messages with an image block: same prompt rows, same answer
+    amsg = [{"role": "user", "content": [{"type": "text", "text": "look: "},
+                                         {"type": "image", "source": {"type": "base64", "media_type": "image/x-portable-pixmap",
+                                                                      "data": base64.b64encode(ppm).decode()}}]}]
+    r = c.post("/v1/messages", json={"messages": amsg, "max_tokens": 5, "temperature": 0})
+    assert r.status_code == 200, r.text
+    assert r.json()["usage"]["input_tokens"] == full["usage"]["prompt_tokens"]
+    assert c.post("/v1/messages/count_tokens", json={"messages": amsg}).json()["input_tokens"] == full["usage"]["prompt_tokens"]
     llm.close()
