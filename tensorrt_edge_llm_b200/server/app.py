@@ -484,31 +484,91 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
                 "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out.token_ids), "total_tokens": len(ids) + len(out.token_ids)}}
 
     # ---- OpenAI responses (text in, text out) ---------------------------------------------------------------
+    async def prompt_from_messages(messages):
+        """Token ids of rendered messages, or a prepared multimodal prompt when they carry image / audio parts."""
+        msgs, media = _split_media(messages)
+        text = template.apply(msgs, True)
+        if not media:
+            return encode(text)
+        if multimodal is None or llm.engine is None:
+            raise ValueError("image / audio parts need a server with an encoder for them and in-flight batching")
+        import asyncio
+        return await asyncio.get_running_loop().run_in_executor(None, multimodal.prepare, _media_request(text, media))
+
+    def _responses_messages(body):
+        """OpenAI Responses input → chat messages (``input_text`` / ``output_text`` parts are text, ``input_image`` an image)."""
+        inp = body["input"]
+        if isinstance(inp, str):
+            messages = [{"role": "user", "content": inp}]
+        else:
+            messages = []
+            for m in inp:
+                c = m.get("content", "")
+                if isinstance(c, list):
+                    parts = []
+                    for part in c:
+                        kind = part.get("type")
+                        if kind in ("input_text", "output_text", "text"):
+                            parts.append({"type": "text", "text": part.get("text", "")})
+                        elif kind == "input_image":
+                            parts.append({"type": "image_url", "image_url": {"url": part.get("image_url")}})
+                        elif kind == "input_audio":
+                            parts.append(part)
+                        else:
+                            raise ValueError(f"unsupported input part {kind!r}")
+                    c = parts if any(p["type"] != "text" for p in parts) else "".join(p["text"] for p in parts)
+                messages.append({"role": m.get("role", "user"), "content": c})
+        if body.get("instructions"):
+            messages.insert(0, {"role": "system", "content": body["instructions"]})
+        return messages
+
     @app.post("/v1/responses")
     async def responses(request: Request):
         try:
             body = await request.json()
-            inp = body["input"]
-            messages = [{"role": "user", "content": inp}] if isinstance(inp, str) else [
-                {"role": m.get("role", "user"), "content": m.get("content", "")} for m in inp]
-            if body.get("instructions"):
-                messages.insert(0, {"role": "system", "content": body["instructions"]})
             sp = _sampling(body)
-            ids = encode(template.apply(messages, True))
-        except (KeyError, ValueError, TypeError, AttributeError, json.JSONDecodeError) as e:
+            if body.get("max_output_tokens"):
+                sp.max_tokens = int(body["max_output_tokens"])
+            ids = await prompt_from_messages(_responses_messages(body))
+        except (KeyError, ValueError, TypeError, AttributeError, RuntimeError, json.JSONDecodeError) as e:
             return _error(400, f"bad request: {e}")
         bad = check_len(ids)
         if bad:
             return bad
+        rid, mid = f"resp_{uuid.uuid4().hex[:24]}", f"msg_{uuid.uuid4().hex[:24]}"
+
+        def envelope(status, text, n_out):
+            return {"id": rid, "object": "response", "created_at": int(time.time()), "status": status, "model": name,
+                    "output": [] if status == "in_progress" else [
+                        {"type": "message", "id": mid, "role": "assistant", "status": "completed",
+                         "content": [{"type": "output_text", "text": text, "annotations": []}]}],
+                    "output_text": text,
+                    "usage": {"input_tokens": len(ids), "output_tokens": n_out, "total_tokens": len(ids) + n_out}}
+        if body.get("stream"):
+            async def events():
+                seq = 0
+
+                def ev(kind, data):
+                    nonlocal seq
+                    seq += 1
+                    return f"event: {kind}\ndata: {json.dumps({'type': kind, 'sequence_number': seq, **data})}\n\n"
+                yield ev("response.created", {"response": envelope("in_progress", "", 0)})
+                yield ev("response.output_item.added", {"output_index": 0, "item": {"type": "message", "id": mid, "role": "assistant",
+                                                                                   "status": "in_progress", "content": []}})
+                text, n_out = "", 0
+                async for d in client.stream(ids, sp):
+                    n_out += len(d.token_ids)
+                    if d.text:
+                        text += d.text
+                        yield ev("response.output_text.delta", {"item_id": mid, "output_index": 0, "content_index": 0, "delta": d.text})
+                yield ev("response.output_text.done", {"item_id": mid, "output_index": 0, "content_index": 0, "text": text})
+                yield ev("response.completed", {"response": envelope("completed", text, n_out)})
+            return sse(events())
         out, err = await run(ids, sp)
         if err:
             return err
         text = out.text if out.text is not None else decode(out.token_ids)
-        return {"id": f"resp_{uuid.uuid4().hex[:24]}", "object": "response", "created_at": int(time.time()), "status": "completed", "model": name,
-                "output": [{"type": "message", "id": f"msg_{uuid.uuid4().hex[:24]}", "role": "assistant", "status": "completed",
-                            "content": [{"type": "output_text", "text": text, "annotations": []}]}],
-                "output_text": text,
-                "usage": {"input_tokens": len(ids), "output_tokens": len(out.token_ids), "total_tokens": len(ids) + len(out.token_ids)}}
+        return envelope("completed", text, len(out.token_ids))
 
     # ---- Anthropic messages --------------------------------------------------------------------------------
     def anthropic_messages(body: Dict[str, Any]) -> List[Dict[str, Any]]:
@@ -529,14 +589,7 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
 
     async def anthropic_prompt(body):
         """Prompt of an Anthropic request: token ids, or a prepared multimodal prompt when image blocks are present."""
-        msgs, media = _split_media(anthropic_messages(body))
-        text = template.apply(msgs, True)
-        if not media:
-            return encode(text)
-        if multimodal is None or llm.engine is None:
-            raise ValueError("image blocks need a server with a vision tower and in-flight batching")
-        import asyncio
-        return await asyncio.get_running_loop().run_in_executor(None, multimodal.prepare, _media_request(text, media))
+        return await prompt_from_messages(anthropic_messages(body))
 
     @app.post("/v1/messages")
     async def messages(request: Request):

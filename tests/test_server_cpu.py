@@ -104,6 +104,19 @@ def test_anthropic_messages_and_count(client):
 def test_responses_route(client):
     r = client.post("/v1/responses", json={"input": "ping", "instructions": "pong", "max_output_tokens": 3, "temperature": 0}, headers=AUTH).json()
     assert r["object"] == "response" and r["usage"]["output_tokens"] == 3 and r["output"][0]["content"][0]["type"] == "output_text"
+    # typed content parts and streaming events
+    typed = {"input": [{"role": "user", "content": [{"type": "input_text", "text": "pi"}, {"type": "input_text", "text": "ng"}]}],
+             "instructions": "pong", "max_output_tokens": 3, "temperature": 0}
+    same = client.post("/v1/responses", json=typed, headers=AUTH).json()
+    assert same["output_text"] == r["output_text"] and same["usage"]["input_tokens"] == r["usage"]["input_tokens"]
+    with client.stream("POST", "/v1/responses", json={**typed, "stream": True}, headers=AUTH) as sresp:
+        lines = [ln for ln in sresp.iter_lines() if ln]
+    kinds = [ln[7:] for ln in lines if ln.startswith("event: ")]
+    assert kinds[0] == "response.created" and kinds[-1] == "response.completed" and "response.output_text.done" in kinds
+    import json as _js
+    done = _js.loads([ln for ln in lines if ln.startswith("data: ")][-1][6:])
+    assert done["response"]["status"] == "completed" and done["response"]["usage"]["output_tokens"] == 3
+    assert client.post("/v1/responses", json={"input": [{"role": "user", "content": [{"type": "input_file"}]}]}, headers=AUTH).status_code == 400
 
 
 def test_admission_controller_limits():
