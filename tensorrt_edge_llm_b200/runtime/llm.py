@@ -235,6 +235,25 @@ class LLM:
             raise RuntimeError(why)
         return h
 
+    # ---- counters (the names of the reference's Python runtime) ------------------------------------------
+    def get_scheduling_metrics(self) -> Optional[dict]:
+        """Counters of the request engine (``None`` without in-flight batching): submissions, completions, step kinds,
+        mid-flight admissions, stalls — ``cpp/scheduler/requestEngine.cpp:507-563`` in the reference."""
+        if self.engine is None:
+            return None
+        m = self.engine.metrics()
+        names = ("submitted", "refused", "completed", "cancelled", "failed", "admitted_mid_flight", "stalls_no_capacity", "stalls_exclusive",
+                 "decode_steps", "prompt_steps", "mixed_steps", "step_tokens", "paused_resident_steps", "session_failures")
+        return {**{k: int(getattr(m, k)) for k in names}, "queue_latency_s_sum": float(m.queue_latency_s_sum)}
+
+    def get_context_cache_counters(self) -> Optional[dict]:
+        """Prefix-reuse counters (``None`` when context reuse is off)."""
+        sess = getattr(self, "session", None)
+        if self.engine is None or sess is None or sess.prefix is None:
+            return None
+        return {"reused_tokens": int(self.engine.metrics().prefix_reused_tokens), "snapshot_hits": int(sess.snapshot_hits),
+                "snapshots": len(sess.snapshots), "jump_forward_tokens": int(sess.jump_forward_tokens)}
+
     def submit_multimodal(self, ids: Sequence[int], embeds: torch.Tensor, sampling_params: Optional[SamplingParams] = None, positions3=None,
                           rope_delta: int = 0, deepstack: Optional[dict] = None, priority: int = 0):
         """Queue a multimodal prompt on the request engine: ``ids`` hold placeholder tokens where media sits, ``embeds`` the

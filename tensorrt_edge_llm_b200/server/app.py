@@ -202,16 +202,9 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
         """Engine status, scheduling counters and context-cache counters of the native request engine (``None`` without one)."""
         if llm.engine is None:
             return None, None, None
-        st, m = llm.engine.status(), llm.engine.metrics()
+        st = llm.engine.status()
         engine = {"serving": bool(st.available), "unavailable_reason": st.unavailable_reason, "queued": int(st.queued), "resident": int(st.resident)}
-        fields = ("submitted", "refused", "completed", "cancelled", "failed", "admitted_mid_flight", "stalls_no_capacity", "stalls_exclusive",
-                  "decode_steps", "prompt_steps", "mixed_steps", "step_tokens", "paused_resident_steps", "session_failures")
-        scheduling = {k: int(getattr(m, k)) for k in fields}
-        scheduling["queue_latency_s_sum"] = float(m.queue_latency_s_sum)
-        sess = getattr(llm, "session", None)
-        cache = None
-        if sess is not None and sess.prefix is not None:
-            cache = {"reused_tokens": int(m.prefix_reused_tokens), "snapshot_hits": int(sess.snapshot_hits), "snapshots": len(sess.snapshots)}
+        scheduling, cache = llm.get_scheduling_metrics(), llm.get_context_cache_counters()
         return engine, scheduling, cache
 
     @app.get("/health")

@@ -28,6 +28,8 @@ def test_ifb_matches_static_batch_and_reuses_prefix():
     again = ifb.generate([_prompts()[2]], sp)
     assert again[0].token_ids == want[2]
     assert ifb.engine.metrics().prefix_reused_tokens >= 128
+    assert ifb.get_context_cache_counters()["reused_tokens"] >= 128 and ifb.get_scheduling_metrics()["completed"] == 6
+    assert static.get_scheduling_metrics() is None and static.get_context_cache_counters() is None
     # streaming yields the same tokens
     streamed = []
     for toks, _ in ifb.generate_stream(_prompts()[1], sp):
