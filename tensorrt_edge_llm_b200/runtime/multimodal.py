@@ -132,16 +132,28 @@ class MultimodalRunner:
             m, g = patchify_frames(chw[None], c)
             mats.append(m)
             grids.append(g)
-        rows = self.vision(torch.cat(mats, 0).to(self.device), grids, return_deepstack=bool(c.deepstack_visual_indexes))
-        # Qwen3-VL: features of intermediate blocks ride along; they join the language model's first layers (deepstack)
-        rows, self._deep = rows if isinstance(rows, tuple) else (rows, [])
         m = c.spatial_merge_size
         self._grids = [(t, h // m, w // m) for t, h, w in grids]
-        out, at = [], 0
-        for t, h, w in self._grids:
-            out.append(rows[at:at + t * h * w])
-            at += t * h * w
-        return out
+        levels = len(c.deepstack_visual_indexes)
+        # encoder cache: one entry per image, the tower's rows and its deepstack levels side by side ([rows, (1 + levels) · H])
+        keys = [EncoderCache.key(x) for x in mats] if self.cache is not None else [None] * len(mats)
+        packed: List[Optional[torch.Tensor]] = [self.cache.get(k) if self.cache is not None else None for k in keys]
+        todo = [i for i, p in enumerate(packed) if p is None]
+        if todo:
+            res = self.vision(torch.cat([mats[i] for i in todo], 0).to(self.device), [grids[i] for i in todo], return_deepstack=bool(levels))
+            rows, deep = res if isinstance(res, tuple) else (res, [])
+            at = 0
+            for i in todo:
+                t, h, w = self._grids[i]
+                n = t * h * w
+                packed[i] = torch.cat([rows[at:at + n]] + [d[at:at + n] for d in deep], dim=1)
+                if self.cache is not None:
+                    self.cache.put(keys[i], packed[i])
+                at += n
+        width = packed[0].shape[1] // (1 + levels)
+        # Qwen3-VL: features of intermediate blocks ride along; they join the language model's first layers (deepstack)
+        self._deep = [torch.cat([p[:, (k + 1) * width:(k + 2) * width] for p in packed], 0) for k in range(levels)]
+        return [p[:, :width] for p in packed]
 
     def _encode_intern(self, images: Sequence) -> List[torch.Tensor]:
         """InternVL: every image becomes up to ``max_tiles`` square tiles on the grid closest to its aspect ratio, plus a

@@ -240,3 +240,33 @@ def test_deepstack_features_reach_the_decoder():
     b = runner.prefill_embeds([0], [emb], positions3=[pos3], rope_deltas=[delta])
     llm.kv.free(0)
     assert (a - b).abs().max() > 1e-3 and int(a.argmax()) == with_deep[0]
+
+
+def test_encoder_cache_serves_repeated_images_with_their_deepstack_levels():
+    import numpy as np
+    from tensorrt_edge_llm_b200.config import tiny_llama_config
+    from tensorrt_edge_llm_b200.runtime.llm import LLM
+    from tensorrt_edge_llm_b200.runtime.multimodal import MultimodalRunner
+    cfg = tiny_llama_config(num_hidden_layers=2, vocab_size=200, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                            dtype="float32")
+    llm = LLM(cfg, device="cpu", max_batch_size=1, max_input_len=256, max_kv_cache_capacity=320, page_size=16)
+    vc = QwenVisionConfig(depth=2, hidden_size=64, num_heads=4, intermediate_size=64, out_hidden_size=64, window_size=0, fullatt_block_indexes=[],
+                          gated_mlp=False, mlp_act="gelu_tanh", patch_bias=True, patch_size=16, num_position_embeddings=16,
+                          deepstack_visual_indexes=[0], dtype="float32")
+    tower = QwenVisionEncoder(vc).random_init(5, std=0.2)
+    calls = []
+    fwd = tower.forward
+    tower.forward = lambda *a, **k: (calls.append(len(a[1])), fwd(*a, **k))[1]
+    mm = MultimodalRunner(llm, vision=tower, image_token_id=7, cache_bytes=1 << 20, min_pixels=32 * 32 * 2, max_pixels=32 * 32 * 30)
+    rng = np.random.default_rng(4)
+    a, b = (rng.integers(0, 255, (64, 96, 3), dtype=np.uint8) for _ in range(2))
+    first = mm.encode_images([a, b])
+    deep_first = [d.clone() for d in mm._deep]
+    again = mm.encode_images([b, a, b])                                  # all cached: the tower does not run
+    assert calls == [2] and mm.cache.hits == 3
+    assert torch.equal(again[0], first[1]) and torch.equal(again[1], first[0]) and torch.equal(again[2], first[1])
+    n = first[0].shape[0]
+    assert torch.equal(mm._deep[0][n:2 * n], deep_first[0][:n])          # deepstack rows follow their image
+    c = rng.integers(0, 255, (64, 96, 3), dtype=np.uint8)
+    mixed = mm.encode_images([a, c])
+    assert calls == [2, 1] and torch.equal(mixed[0], first[0])
