@@ -96,6 +96,8 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
     from ..chat_template import ChatTemplate
     from ..models.action_expert import ActionExpert
+    from ..server import app as server_app
+    server_app._MEDIA_ROOT["path"] = "/"          # an offline command reads the files its own input names
     from ..runtime import native as rt
     from ..runtime.llm import LLM
     from ..runtime.multimodal import MultimodalRunner

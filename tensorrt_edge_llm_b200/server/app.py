@@ -81,14 +81,28 @@ def _guided(body: Dict[str, Any]):
 _IMG, _AUD = "\x00IMG\x00", "\x00AUD\x00"
 
 
+# Directory under which requests may name local media files ("" = none: only data: URIs are read).  Set by `create_app`
+# from `ApiConfig.allowed_local_media_path` (``--allowed-local-media-path`` in the reference's server as well).
+_MEDIA_ROOT = {"path": ""}
+
+
 def _media_bytes(ref: str) -> bytes:
-    """``data:…;base64,…`` URI, ``file://`` URI or a local path → bytes (no network fetches)."""
+    """``data:…;base64,…`` URI, or a ``file://`` URI / local path under the allowed media directory → bytes (no network
+    fetches; without an allowed directory a request cannot make the server read its files)."""
     import base64
+    import os
     if ref.startswith("data:"):
         return base64.b64decode(ref.split(",", 1)[1])
     if ref.startswith(("http://", "https://")):
-        raise ValueError("remote media URLs are not fetched; send a data: URI or a local path")
-    with open(ref[7:] if ref.startswith("file://") else ref, "rb") as f:
+        raise ValueError("remote media URLs are not fetched; send a data: URI")
+    root = _MEDIA_ROOT["path"]
+    if not root:
+        raise ValueError("local media paths are disabled on this server (start it with --allowed-local-media-path); send a data: URI")
+    path = os.path.realpath(ref[7:] if ref.startswith("file://") else ref)
+    root = os.path.realpath(root)
+    if os.path.commonpath([path, root]) != root:
+        raise ValueError("media path is outside the allowed directory")
+    with open(path, "rb") as f:
         return f.read()
 
 
@@ -138,6 +152,7 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
     audio parts are then answered through it: on the request engine next to all other requests when in-flight batching is on,
     otherwise one at a time on the static path."""
     api = api or ApiConfig()
+    _MEDIA_ROOT["path"] = api.allowed_local_media_path
     client = EngineClient(llm, api.max_queued_requests, api.queue_timeout)
     template = chat_template or ChatTemplate()
     name = api.served_model_name or model_name or "model"

@@ -81,7 +81,11 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     multimodal = None
     if os.path.isdir(cfg.model.model):                   # vision-language checkpoints bring their tower along
         from ..runtime.multimodal import MultimodalRunner
-        multimodal = MultimodalRunner.from_pretrained(llm, cfg.model.model)
+        mc = cfg.model.multimodal_config
+        multimodal = MultimodalRunner.from_pretrained(llm, cfg.model.model, cache_bytes=mc.encoder_cache_budget_bytes)
+        if multimodal is not None and mc.max_image_tokens_per_image and hasattr(multimodal.vision.cfg, "spatial_merge_size"):
+            vc = multimodal.vision.cfg                      # rows per image × pixels per row (patch × merge, squared)
+            multimodal.max_pixels = mc.max_image_tokens_per_image * (vc.patch_size * vc.spatial_merge_size) ** 2
     app = create_app(llm, cfg.api, template, model_name=os.path.basename(os.path.normpath(cfg.model.model)), multimodal=multimodal)
     try:
         uvicorn.run(app, host=cfg.api.host, port=cfg.api.port, log_level=cfg.api.log_level)

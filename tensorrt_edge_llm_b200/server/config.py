@@ -17,14 +17,14 @@ class ServerConfigError(ValueError):
 
 @dataclass
 class SpeculativeConfig:
-    method: str                                    # "eagle3" | "mtp"
+    method: str                                    # "eagle3" | "mtp" | "dflash" | "domino" (the draft checkpoint decides the decoder)
     num_speculative_tokens: Optional[int] = None   # draft depth
     draft_model: str = ""
     draft_top_k: Optional[int] = None
     verify_tokens: Optional[int] = None
 
     def __post_init__(self):
-        if self.method not in ("eagle3", "mtp"):
+        if self.method not in ("eagle3", "mtp", "dflash", "domino"):
             raise ServerConfigError(f"unknown speculative method {self.method!r}")
         for name in ("num_speculative_tokens", "draft_top_k", "verify_tokens"):
             v = getattr(self, name)
@@ -50,6 +50,13 @@ class ContextCacheConfig:
 
 
 @dataclass
+class MultimodalConfig:
+    max_image_tokens_per_image: int = 0
+    max_image_tokens: int = 0
+    encoder_cache_budget_bytes: int = 0
+
+
+@dataclass
 class ModelConfig:
     model: str
     max_input_len: int = 4096
@@ -57,6 +64,7 @@ class ModelConfig:
     max_kv_cache_capacity: int = 8192
     speculative_config: Optional[SpeculativeConfig] = None
     context_cache_config: ContextCacheConfig = field(default_factory=ContextCacheConfig)
+    multimodal_config: MultimodalConfig = field(default_factory=MultimodalConfig)
     enable_in_flight_batching: bool = False
     ifb_scheduling_mode: str = "auto"              # auto | mixed | prefill_first | single_cohort
     max_num_tokens: int = 0                        # 0 = runtime default
@@ -115,6 +123,7 @@ class ApiConfig:
     queue_timeout: float = 600.0
     log_level: str = "info"
     min_request_priority: int = 0
+    allowed_local_media_path: str = ""          # "" = requests may not name files of this machine
 
     def __post_init__(self):
         if not 0 < self.port < 65536:
@@ -144,7 +153,19 @@ def create_argument_parser(prog: str = "trtedge serve") -> argparse.ArgumentPars
     m.add_argument("--preemption", default="none", choices=["none", "pause"])
     m.add_argument("--priority-reserved-slots", type=int, default=0)
     m.add_argument("--max-pause-steps", type=int, default=0)
-    m.add_argument("--enable-context-cache", action="store_true")
+    m.add_argument("--enable-context-cache", "--enable-context-reuse", dest="enable_context_cache", action="store_true",
+                   help="share KV pages (and recurrent-state snapshots) between requests with a common prefix")
+    m.add_argument("--context-cache-max-records", type=int, default=1024)
+    m.add_argument("--context-cache-max-snapshots", type=int, default=0)
+    m.add_argument("--max-image-tokens-per-image", type=int, default=0, help="cap on language-model rows one image may take (0 = tower default)")
+    m.add_argument("--max-image-tokens", type=int, default=0, help="cap on image rows of one request (0 = max-input-len)")
+    m.add_argument("--encoder-cache-budget-bytes", type=int, default=0, help="reuse encoder outputs of repeated media within this budget")
+    for flag in ("--draft-top-k", "--spec-draft-step", "--spec-verify-tokens", "--spec-proposal-tokens", "--max-spec-verify-tokens",
+                 "--max-spec-draft-tokens"):
+        m.add_argument(flag, type=int, default=0, help="override of the matching --speculative-config field")
+    for flag in ("--cache-dir", "--engine-cache-max-size-gb"):
+        m.add_argument(flag, default="", help="accepted for command-line compatibility: checkpoints load directly, no engine is built or cached")
+    m.add_argument("--clear-engine-cache", action="store_true", help="accepted for command-line compatibility (no engine cache exists)")
     m.add_argument("--speculative-config", default="", help='JSON, e.g. {"method": "eagle3", "draft_model": "<dir>"}')
     m.add_argument("--tensor-parallel-size", type=int, default=1)
     m.add_argument("--kv-page-size", type=int, default=64, choices=[64, 128])
@@ -161,6 +182,8 @@ def create_argument_parser(prog: str = "trtedge serve") -> argparse.ArgumentPars
     a.add_argument("--queue-timeout", type=float, default=600.0)
     a.add_argument("--log-level", default="info")
     a.add_argument("--min-request-priority", type=int, default=0)
+    a.add_argument("--allowed-local-media-path", default="", help="directory under which requests may name local media files; "
+                   "without it only data: URIs are read")
     return p
 
 
@@ -173,10 +196,20 @@ def parse_server_config(argv: Optional[Sequence[str]] = None) -> ServerConfig:
             spec = SpeculativeConfig.from_mapping(json.loads(ns.speculative_config))
         except json.JSONDecodeError as e:
             raise ServerConfigError(f"--speculative-config is not valid JSON: {e}") from None
+    if spec is not None:
+        # the reference's separate flags override single fields of the JSON
+        for flag, names in (("draft_top_k", ("draft_top_k", "top_k")), ("spec_draft_step", ("num_speculative_tokens", "draft_steps")),
+                            ("spec_verify_tokens", ("verify_tokens",)), ("max_spec_verify_tokens", ("verify_tokens",))):
+            v = getattr(ns, flag)
+            for name in names:
+                if v and hasattr(spec, name):
+                    setattr(spec, name, v)
     model = ModelConfig(
         model=ns.model, max_input_len=ns.max_input_len, max_batch_size=ns.max_batch_size,
         max_kv_cache_capacity=ns.max_kv_cache_capacity, speculative_config=spec,
-        context_cache_config=ContextCacheConfig(enabled=ns.enable_context_cache),
+        context_cache_config=ContextCacheConfig(enabled=ns.enable_context_cache, max_records=ns.context_cache_max_records,
+                                                max_snapshots=ns.context_cache_max_snapshots),
+        multimodal_config=MultimodalConfig(ns.max_image_tokens_per_image, ns.max_image_tokens, ns.encoder_cache_budget_bytes),
         enable_in_flight_batching=ns.enable_in_flight_batching, ifb_scheduling_mode=ns.ifb_scheduling_mode,
         max_num_tokens=ns.max_num_tokens, max_chunk_tokens=ns.max_chunk_tokens, scheduling_policy=ns.scheduling_policy,
         preemption=ns.preemption, priority_reserved_slots=ns.priority_reserved_slots, max_pause_steps=ns.max_pause_steps,
@@ -184,5 +217,6 @@ def parse_server_config(argv: Optional[Sequence[str]] = None) -> ServerConfig:
     api = ApiConfig(host=ns.host, port=ns.port, served_model_name=ns.served_model_name, api_key=ns.api_key,
                     reasoning_parser=ns.reasoning_parser, tool_call_parser=ns.tool_call_parser,
                     enable_auto_tool_choice=ns.enable_auto_tool_choice, max_queued_requests=ns.max_queued_requests,
-                    queue_timeout=ns.queue_timeout, log_level=ns.log_level, min_request_priority=ns.min_request_priority)
+                    queue_timeout=ns.queue_timeout, log_level=ns.log_level, min_request_priority=ns.min_request_priority,
+                    allowed_local_media_path=ns.allowed_local_media_path)
     return ServerConfig(model=model, api=api)

@@ -230,3 +230,42 @@ def test_logprobs_and_logit_bias(client, llm):
     out = static.generate([[5, 9, 33]], SP(max_tokens=4, temperature=0.0, logprobs=3))[0]
     assert out.token_ids == r["token_ids"]
     assert all(abs(a["logprob"] - b) < 1e-4 for a, b in zip(out.logprobs, lp["token_logprobs"]))
+
+
+def test_local_media_paths_need_an_allowed_directory(tmp_path):
+    """A request cannot make the server read files unless a media directory was configured, and then only beneath it."""
+    from tensorrt_edge_llm_b200.server import app as app_mod
+    inside = tmp_path / "media"
+    inside.mkdir()
+    (inside / "a.ppm").write_bytes(b"P6\n1 1\n255\n\x01\x02\x03")
+    secret = tmp_path / "secret.txt"
+    secret.write_bytes(b"top secret")
+    app_mod._MEDIA_ROOT["path"] = ""
+    with pytest.raises(ValueError, match="disabled"):
+        app_mod._media_bytes(str(inside / "a.ppm"))
+    app_mod._MEDIA_ROOT["path"] = str(inside)
+    try:
+        assert app_mod._media_bytes(str(inside / "a.ppm")).startswith(b"P6")
+        assert app_mod._media_bytes("file://" + str(inside / "a.ppm")).startswith(b"P6")
+        for sneaky in (str(secret), str(inside / ".." / "secret.txt"), "file://" + str(secret)):
+            with pytest.raises(ValueError, match="outside"):
+                app_mod._media_bytes(sneaky)
+        with pytest.raises(ValueError, match="not fetched"):
+            app_mod._media_bytes("https://example.com/x.png")
+        assert app_mod._media_bytes("data:image/png;base64,aGk=") == b"hi"
+    finally:
+        app_mod._MEDIA_ROOT["path"] = ""
+
+
+def test_reference_command_line_flags_are_accepted():
+    from tensorrt_edge_llm_b200.server.config import parse_server_config
+    cfg = parse_server_config(["/ckpt", "--enable-in-flight-batching", "--enable-context-reuse", "--context-cache-max-records", "77",
+                               "--context-cache-max-snapshots", "5", "--allowed-local-media-path", "/data/media", "--max-image-tokens-per-image", "256",
+                               "--encoder-cache-budget-bytes", "1048576", "--cache-dir", "/tmp/x", "--clear-engine-cache",
+                               "--speculative-config", '{"method": "dflash", "draft_model": "/d"}', "--spec-verify-tokens", "24", "--draft-top-k", "4"])
+    cc, mc = cfg.model.context_cache_config, cfg.model.multimodal_config
+    assert (cc.enabled, cc.max_records, cc.max_snapshots) == (True, 77, 5)
+    assert (mc.max_image_tokens_per_image, mc.encoder_cache_budget_bytes) == (256, 1048576)
+    assert cfg.api.allowed_local_media_path == "/data/media"
+    sc = cfg.model.speculative_config
+    assert (sc.method, sc.verify_tokens, sc.draft_top_k) == ("dflash", 24, 4)
