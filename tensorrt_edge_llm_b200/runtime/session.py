@@ -80,8 +80,8 @@ class ModelSession(rt.RuntimeSession):
     def register_embeds(self, ids, emb: torch.Tensor, positions3=None, delta: int = 0, deepstack: Optional[dict] = None) -> int:
         """Park a multimodal prompt (placeholder ids, embedding rows with the media spliced in, optional 3-D positions,
         decode offset and deepstack levels); the returned key goes into ``GenerationRequest.embeds_key``."""
-        if self.mirror is not None or self.spec is not None:
-            raise ValueError("multimodal prompts under in-flight batching need a deployment without tensor-parallel mirroring or speculative decoding")
+        if self.mirror is not None:
+            raise ValueError("multimodal prompts under in-flight batching are not mirrored to tensor-parallel follower ranks")
         if emb.shape[0] != len(ids):
             raise ValueError("one embedding row per prompt token is needed")
         key = self._mm_next
@@ -167,6 +167,7 @@ class ModelSession(rt.RuntimeSession):
         self.seqs[slot].plain = plain
         if mm is not None:
             self.seqs[slot].mm = mm
+            self.seqs[slot].plain = True              # on a speculative deployment media prompts decode token by token
             self.mm_store.pop(int(req.embeds_key), None)
         r.admitted, r.slot, r.reused_tokens = True, slot, reused
         return r

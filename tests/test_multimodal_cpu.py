@@ -203,3 +203,26 @@ def test_server_multimodal_chat_on_the_request_engine():
     assert r.json()["usage"]["input_tokens"] == full["usage"]["prompt_tokens"]
     assert c.post("/v1/messages/count_tokens", json={"messages": amsg}).json()["input_tokens"] == full["usage"]["prompt_tokens"]
     llm.close()
+
+
+def test_multimodal_request_on_a_speculative_deployment():
+    """Media prompts share the engine with speculative text requests and decode token by token themselves."""
+    from tensorrt_edge_llm_b200.config import tiny_llama_config
+    from tensorrt_edge_llm_b200.runtime.llm import LLM
+    from tensorrt_edge_llm_b200.runtime.runner import SamplingParams
+    cfg = _llm(mrope=False).cfg
+    dcfg = tiny_llama_config(num_hidden_layers=1, vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, num_attention_heads=cfg.num_attention_heads,
+                             num_key_value_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim, dtype=cfg.dtype)
+    dcfg.draft_type, dcfg.eagle3_target_hidden_size = "eagle3", cfg.hidden_size
+    static = LLM(cfg, device="cpu", max_batch_size=2, max_input_len=256, max_kv_cache_capacity=320, page_size=16)
+    v, a = _encoders()
+    img = np.random.default_rng(5).integers(0, 255, (32, 32, 3), dtype=np.uint8)
+    req = MultimodalInputs().text([3, 4, 5]).image(img).text([6, 7])
+    want = MultimodalRunner(static, v, a, image_token_id=298, audio_token_id=299).generate(req, max_tokens=5)
+    text_want = static.generate([[20, 21, 22, 23]], SamplingParams(max_tokens=8, ignore_eos=True))[0].token_ids
+    spec = LLM(cfg, device="cpu", max_batch_size=2, max_input_len=256, max_kv_cache_capacity=320, page_size=16, draft_model=dcfg,
+               enable_in_flight_batching=True)
+    mm = MultimodalRunner(spec, v, a, image_token_id=298, audio_token_id=299)
+    assert mm.generate(req, max_tokens=5) == want
+    assert spec.generate([[20, 21, 22, 23]], SamplingParams(max_tokens=8, ignore_eos=True))[0].token_ids == text_want
+    spec.close()
