@@ -5,7 +5,8 @@ server.md:634-636``).  Here the request engine runs on rank 0 only; every state 
 model — a seat reserved, a step executed, a seat released — is mirrored to the other ranks as a small broadcast *before*
 rank 0 runs it, and the followers replay it on their own shard (their own KV pool and page ids; only seats, token ids and
 lengths have to agree).  The collectives inside the model step then meet on all ranks.  Sampling happens on rank 0; the
-followers never look at logits."""
+followers never look at logits.  Steps that hold a chunk of a multimodal prompt ship their embedding rows along
+(``step_embeds``): the media encoders run on rank 0 only."""
 from __future__ import annotations
 
 from typing import List, Sequence
@@ -53,6 +54,13 @@ def serve_follower(runner, mirror: StepMirror) -> int:
         elif kind == "step":
             _, seats, token_lists = op
             runner.step(list(seats), [list(t) for t in token_lists])
+            steps += 1
+        elif kind == "step_embeds":
+            # a step that carries a multimodal prompt chunk: rank 0 ships the embedding rows (host tensors) with the plan
+            _, seats, embeds, pos3, deepstack, deltas = op
+            runner.step_embeds(list(seats), [e.to(runner.device) for e in embeds], pos3, deepstack)
+            for slot, d in deltas:
+                runner.rope_delta[slot] = d
             steps += 1
         elif kind == "release":
             kv.free(op[1])

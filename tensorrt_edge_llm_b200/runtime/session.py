@@ -80,8 +80,6 @@ class ModelSession(rt.RuntimeSession):
     def register_embeds(self, ids, emb: torch.Tensor, positions3=None, delta: int = 0, deepstack: Optional[dict] = None) -> int:
         """Park a multimodal prompt (placeholder ids, embedding rows with the media spliced in, optional 3-D positions,
         decode offset and deepstack levels); the returned key goes into ``GenerationRequest.embeds_key``."""
-        if self.mirror is not None:
-            raise ValueError("multimodal prompts under in-flight batching are not mirrored to tensor-parallel follower ranks")
         if emb.shape[0] != len(ids):
             raise ValueError("one embedding row per prompt token is needed")
         key = self._mm_next
@@ -307,11 +305,11 @@ class ModelSession(rt.RuntimeSession):
                 segs.append((r0, r0 + len(toks), self.seqs[slot].req.lora_name or None))
                 r0 += len(toks)
             lora.set_segments(segs)
-        if self.mirror is not None:
-            self.mirror.send(("step", seats, token_lists))
         if any(s.kind == rt.WorkKind.Context and self.seqs[s.slot].mm is not None for s in seqs):
-            logits = self._step_with_embeds(seqs, seats, token_lists)
+            logits = self._step_with_embeds(seqs, seats, token_lists)          # mirrors itself (rows travel with the plan)
         else:
+            if self.mirror is not None:
+                self.mirror.send(("step", seats, token_lists))
             logits = self.runner.step(seats, token_lists)      # one row per sequence (its last token)
         rows = [i for i, p in enumerate(producers) if p]
         out = rt.StepResult()
@@ -392,11 +390,15 @@ class ModelSession(rt.RuntimeSession):
                 pos3.append(None)
             row0 += len(toks)
         deepstack = {k: (torch.cat(r), torch.cat(f)) for k, (r, f) in deep.items()} or None
+        deltas = [(s.slot, self.seqs[s.slot].mm["delta"]) for s in seqs
+                  if self.seqs[s.slot].mm is not None and s.kind == rt.WorkKind.Context and s.last_chunk]
+        if self.mirror is not None:                  # follower ranks replay the step with the same rows
+            host = lambda t: None if t is None else t.detach().to("cpu")
+            self.mirror.send(("step_embeds", seats, [host(e) for e in embeds], [host(p) for p in pos3],
+                              None if deepstack is None else {k: (host(r), host(f)) for k, (r, f) in deepstack.items()}, deltas))
         logits = self.runner.step_embeds(seats, embeds, pos3, deepstack)
-        for s in seqs:
-            q = self.seqs[s.slot]
-            if q.mm is not None and s.kind == rt.WorkKind.Context and s.last_chunk:
-                self.runner.rope_delta[s.slot] = q.mm["delta"]          # decode rows continue after the largest media position
+        for slot, d in deltas:
+            self.runner.rope_delta[slot] = d         # decode rows continue after the largest media position
         return logits
 
     def release(self, slot):

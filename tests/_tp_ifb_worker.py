@@ -26,13 +26,24 @@ def main():
     if rank == 0:
         single = LLM(ckpt, max_batch_size=8, **kw)
         want = [o.token_ids for o in single.generate(prompts, sp)]
+        # a multimodal-style prompt: placeholder ids whose rows are replaced by "media" embedding rows
+        mm_ids = [3, 4, 5] + [7] * 20 + [6, 8]
+        mm_emb = single.runner.embed_tokens(mm_ids).clone()
+        mm_emb[3:23] = (torch.randn(20, mm_emb.shape[1], generator=g) * 0.05).to(mm_emb.dtype)
+        single.kv.free(0)
+        single.kv.reserve(0, len(mm_ids) + 6)
+        first = single.runner.pick(single.runner.prefill_embeds([0], [mm_emb]))
+        want_mm = [int(first[0])] + single.runner.decode_greedy([0], first, 5)[0].tolist()
         single.close()
         llm = LLM(ckpt, mapping=shard, comm=comm, max_batch_size=2, enable_in_flight_batching=True, tp_mirror=mirror,
                   scheduling={"mode": "mixed", "max_num_tokens": 128, "max_chunk_tokens": 64}, **kw)
         got = [o.token_ids for o in llm.generate(prompts, sp)]
         m = llm.engine.metrics()
+        # the embedding rows travel to the followers with the step (chunked: 25 rows at 16 per chunk)
+        got_mm = [int(t) for t in llm.submit_multimodal(mm_ids, mm_emb, sp).get(600.0)]
         llm.close()                                   # tells the followers to stop
-        ok = got == want and m.completed == 5 and m.admitted_mid_flight >= 1
+        ok = got == want and m.completed == 5 and m.admitted_mid_flight >= 1 and got_mm == want_mm
+        print(f"rank 0: multimodal match {got_mm == want_mm}", flush=True)
         print(f"rank 0: match {got == want}, completed {m.completed}, mid-flight admissions {m.admitted_mid_flight}, mirrored ops {mirror.sent}", flush=True)
     else:
         llm = LLM(ckpt, mapping=shard, comm=comm, max_batch_size=2, **kw)
