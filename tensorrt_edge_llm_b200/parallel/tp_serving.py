@@ -37,9 +37,16 @@ class StepMirror:
         return box[0]
 
 
-def serve_follower(runner, mirror: StepMirror) -> int:
-    """Replay rank 0's session on this rank until it says stop; returns the number of steps executed."""
+def serve_follower(runner, mirror: StepMirror, enable_prefix_cache: bool = False, max_records: int = 4096) -> int:
+    """Replay rank 0's session on this rank until it says stop; returns the number of steps executed.
+
+    ``enable_prefix_cache`` / ``max_records`` must equal rank 0's: the follower then keeps a prefix index of its own and repeats
+    every lookup, adoption, insertion and eviction, so its pages and reference counts stay in step with rank 0's."""
     kv, steps = runner.kv, 0
+    prefix = None
+    if enable_prefix_cache and getattr(kv, "native", None) is not None and not kv.bounded_swa and not runner.model.cfg.is_hybrid:
+        from ..runtime import native as rt
+        prefix = rt.PrefixCache(kv.native.allocator(), kv.page_size, max_records)
     while True:
         op = mirror.recv()
         kind = op[0]
@@ -51,6 +58,26 @@ def serve_follower(runner, mirror: StepMirror) -> int:
             _, slot, need = op
             kv.free(slot)
             kv.reserve(slot, need)
+        elif kind == "admit":
+            _, slot, prompt_ids, need, ok = op
+            kv.free(slot)
+            try:
+                if prefix is not None and prompt_ids is not None:
+                    m = prefix.lookup(list(prompt_ids))
+                    if m.tokens:
+                        kv.adopt_prefix(slot, list(m.pages), m.tokens)
+                if ok:
+                    kv.reserve(slot, need)
+            except (MemoryError, RuntimeError):
+                ok = False
+            if not ok:                         # rank 0 gave the seat back and made room: do the same
+                kv.free(slot)
+                if prefix is not None:
+                    prefix.evict(8)
+        elif kind == "prefix_insert":
+            _, slot, tokens, n = op
+            if prefix is not None:
+                prefix.insert(list(tokens), n, kv.pages_of(slot))
         elif kind == "step":
             _, seats, token_lists = op
             runner.step(list(seats), [list(t) for t in token_lists])

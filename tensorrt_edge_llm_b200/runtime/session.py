@@ -52,7 +52,8 @@ class ModelSession(rt.RuntimeSession):
         if mirror is not None:
             if spec_decoder is not None:
                 raise ValueError("speculative decoding is not mirrored to follower ranks")
-            enable_prefix_cache = False        # shared prefix pages are not mirrored
+            if runner.model.cfg.is_hybrid:
+                enable_prefix_cache = False    # recurrent-state snapshots are not mirrored to follower ranks
         self.spec = spec_decoder
         if spec_decoder is not None:
             enable_prefix_cache = False        # the draft's own KV has no shared prefix pages
@@ -134,8 +135,10 @@ class ModelSession(rt.RuntimeSession):
             r.admitted, r.retry_later, r.reason = False, True, "no free seat"
             return r
         reused = 0
+        looked_up = None                  # prompt ids when the prefix cache was consulted: follower ranks repeat the lookup
         try:
             if self.prefix is not None and req.cache_lookup and mm is None:      # placeholder ids say nothing about the media
+                looked_up = list(req.prompt_ids)
                 m = self.prefix.lookup(list(req.prompt_ids))
                 pages, tokens = list(m.pages), m.tokens
                 if tokens and self.hybrid:
@@ -151,10 +154,14 @@ class ModelSession(rt.RuntimeSession):
             else:
                 self.kv.reserve(slot, need)               # capacity is reserved at seat time: no eviction later
                 if self.mirror is not None:
-                    self.mirror.send(("reserve", slot, need))
+                    # followers repeat lookup → adopt → reserve on their own page table and prefix index (same operations in
+                    # the same order keep their state identical to this rank's)
+                    self.mirror.send(("admit", slot, looked_up, need, True) if self.prefix is not None else ("reserve", slot, need))
         except (MemoryError, RuntimeError) as e:
             self.kv.free(slot)
             self.slots.release(slot)
+            if self.mirror is not None and self.prefix is not None:
+                self.mirror.send(("admit", slot, looked_up, need, False))
             if self.prefix is not None and self.prefix.evict(8):
                 r.admitted, r.retry_later, r.reason = False, True, "KV pool full (evicted cached prefixes)"
             else:
@@ -364,6 +371,8 @@ class ModelSession(rt.RuntimeSession):
                 if s.kind == rt.WorkKind.Context and s.last_chunk:
                     q = self.seqs[s.slot]
                     if q.req.cache_commit >= 1 and q.mm is None:      # placeholder ids of media prompts must not be shared
+                        if self.mirror is not None:
+                            self.mirror.send(("prefix_insert", s.slot, list(q.req.prompt_ids), len(q.req.prompt_ids)))
                         self.prefix.insert(list(q.req.prompt_ids), len(q.req.prompt_ids), self.kv.pages_of(s.slot))
         out.deltas = deltas
         return out
@@ -409,6 +418,8 @@ class ModelSession(rt.RuntimeSession):
                 # quotes the answer starts from them); hybrid models publish prompts only, their snapshots end there
                 filled = min(self.kv.lengths[slot], len(q.tokens))
                 if filled > len(q.req.prompt_ids):
+                    if self.mirror is not None:
+                        self.mirror.send(("prefix_insert", slot, list(q.tokens[:filled]), filled))
                     self.prefix.insert(list(q.tokens[:filled]), filled, self.kv.pages_of(slot))
             del self.seqs[slot]
             if self.spec is not None:

@@ -76,7 +76,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     llm, template = build_llm(cfg)
     if cfg.model.tensor_parallel_size > 1 and int(os.environ.get("RANK", "0")) != 0:
         from ..parallel.tp_serving import serve_follower
-        serve_follower(llm.runner, build_llm.mirror)
+        cc = cfg.model.context_cache_config
+        serve_follower(llm.runner, build_llm.mirror, enable_prefix_cache=cc.enabled, max_records=cc.max_records)
         return 0
     multimodal = None
     if os.path.isdir(cfg.model.model):                   # vision-language checkpoints bring their tower along

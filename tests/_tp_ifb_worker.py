@@ -36,18 +36,23 @@ def main():
         want_mm = [int(first[0])] + single.runner.decode_greedy([0], first, 5)[0].tolist()
         single.close()
         llm = LLM(ckpt, mapping=shard, comm=comm, max_batch_size=2, enable_in_flight_batching=True, tp_mirror=mirror,
-                  scheduling={"mode": "mixed", "max_num_tokens": 128, "max_chunk_tokens": 64}, **kw)
+                  enable_prefix_cache=True, scheduling={"mode": "mixed", "max_num_tokens": 128, "max_chunk_tokens": 64}, **kw)
         got = [o.token_ids for o in llm.generate(prompts, sp)]
+        # the long prompts again: their full pages come from the prefix index, on every rank alike
+        again = [o.token_ids for o in llm.generate([prompts[2], prompts[1]], sp)]
+        reused = llm.engine.metrics().prefix_reused_tokens
         m = llm.engine.metrics()
         # the embedding rows travel to the followers with the step (chunked: 25 rows at 16 per chunk)
         got_mm = [int(t) for t in llm.submit_multimodal(mm_ids, mm_emb, sp).get(600.0)]
         llm.close()                                   # tells the followers to stop
-        ok = got == want and m.completed == 5 and m.admitted_mid_flight >= 1 and got_mm == want_mm
+        ok = (got == want and m.completed == 7 and m.admitted_mid_flight >= 1 and got_mm == want_mm and again == [want[2], want[1]]
+              and reused >= 128)
+        print(f"rank 0: prefix reuse {reused} tokens, repeat match {again == [want[2], want[1]]}", flush=True)
         print(f"rank 0: multimodal match {got_mm == want_mm}", flush=True)
         print(f"rank 0: match {got == want}, completed {m.completed}, mid-flight admissions {m.admitted_mid_flight}, mirrored ops {mirror.sent}", flush=True)
     else:
         llm = LLM(ckpt, mapping=shard, comm=comm, max_batch_size=2, **kw)
-        steps = serve_follower(llm.runner, mirror)
+        steps = serve_follower(llm.runner, mirror, enable_prefix_cache=True)
         ok = steps > 10
         print(f"rank {rank}: followed {steps} steps", flush=True)
     dist.barrier()
