@@ -246,6 +246,10 @@ class LLM:
                  "decode_steps", "prompt_steps", "mixed_steps", "step_tokens", "paused_resident_steps", "session_failures")
         return {**{k: int(getattr(m, k)) for k in names}, "queue_latency_s_sum": float(m.queue_latency_s_sum)}
 
+    def list_voices(self) -> List[str]:
+        """Voices of a speech synthesis stage (the reference's ``LLM.list_voices``); this runtime loads none."""
+        return []
+
     def get_context_cache_counters(self) -> Optional[dict]:
         """Prefix-reuse counters (``None`` when context reuse is off)."""
         sess = getattr(self, "session", None)

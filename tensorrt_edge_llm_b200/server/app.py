@@ -37,6 +37,10 @@ def _sampling(body: Dict[str, Any], default_max: int = 256) -> SamplingParams:
     sp.max_tokens = int(max_tokens)
     if sp.max_tokens < 1:
         raise ValueError("max_tokens must be at least 1")
+    if body.get("max_denoising_steps"):                    # block-diffusion checkpoints: denoise passes per block
+        sp.max_denoising_steps = int(body["max_denoising_steps"])
+    if body.get("disable_spec_decode"):
+        sp.disable_spec_decode = True
     # chat form: logprobs=true + top_logprobs=k; completions form: logprobs=k
     want = body.get("logprobs")
     if isinstance(want, bool):
@@ -344,7 +348,7 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
 
     @app.get("/v1/voices")
     async def voices():
-        return {"object": "list", "data": []}              # no speech synthesis stage in this runtime
+        return {"object": "list", "data": [{"id": v, "object": "voice"} for v in llm.list_voices()]}
 
     @app.post("/v1/audio/speech")
     async def audio_speech(request: Request):
