@@ -193,7 +193,9 @@ class ModelRunner:
 
     def embed_tokens(self, ids: Sequence[int]) -> torch.Tensor:
         t = torch.tensor(list(ids), dtype=torch.int32, device=self.device)
-        return ops.embedding(t, self.model.model.embed_tokens.weight)
+        e = ops.embedding(t, self.model.model.embed_tokens.weight)
+        scale = getattr(self.model.model, "embed_scale", 1.0)      # Gemma multiplies looked-up rows (1.0 once folded into the table)
+        return e if scale == 1.0 else (e * torch.tensor(scale, dtype=e.dtype)).to(e.dtype)
 
     @torch.no_grad()
     def prefill_tensor(self, seats: Sequence[int], ids: torch.Tensor) -> torch.Tensor:

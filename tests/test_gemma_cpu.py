@@ -47,3 +47,19 @@ def test_matches_hf_gemma3(tmp_path):
             ref_next = int(hf(torch.tensor([seq])).logits[0, -1].argmax())
         tok = int(r.step([0], [[tok]])[0].argmax())
         assert tok == ref_next
+
+
+def test_embedding_rows_fed_directly_match_token_ids():
+    """Prompts fed as embedding rows (multimodal path) see the same scaled rows as prompts fed as ids."""
+    from tensorrt_edge_llm_b200.config import ModelConfig
+    hf = dict(model_type="gemma3_text", vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=8, sliding_window=0, layer_types=["full_attention"] * 2, max_position_embeddings=128, dtype="float32")
+    cfg = ModelConfig.from_hf_dict(hf)
+    model = AutoModel.from_config(cfg, random_init=0)               # random init keeps the sqrt(hidden) multiplier outside the table
+    assert model.model.embed_scale != 1.0
+    kv = KVCacheManager(cfg, num_pages=8, page_size=16, max_seats=2, max_pages_per_seq=4)
+    r = ModelRunner(model, kv)
+    ids = [5, 9, 33, 2, 77, 12]
+    a = r.prefill([0], [ids])
+    b = r.prefill_embeds([1], [r.embed_tokens(ids)])
+    assert (a - b).abs().max() < 1e-5
