@@ -233,6 +233,7 @@ class ModelConfig:
     dflash_block_size: int = 16
     dflash_mask_token_id: int = 0
     dflash_shift_label: bool = False
+    dflash_query_causal: bool = False       # JetSpec: block rows attend causally inside the block instead of to the whole block
     # Domino: a DFlash draft whose proposals after the first are corrected one by one by a small recurrent head over a shared
     # candidate pool (dflash_projector_type "domino")
     dflash_projector_type: str = ""
@@ -404,13 +405,15 @@ class ModelConfig:
             quant=quant or QuantConfig(),
             bos_token_id=llm.get("bos_token_id"),
             eos_token_id=llm.get("eos_token_id"),
-            draft_type="dflash" if (llm.get("dflash_config") or "dflash" in str(hf.get("architectures", "")).lower()) else (
+            draft_type="dflash" if (llm.get("dflash_config") or llm.get("jetspec_config")
+                                    or any(k in str(hf.get("architectures", "")).lower() for k in ("dflash", "jetspec", "domino"))) else (
                 "eagle3" if (llm.get("draft_vocab_size") or "eagle" in str(hf.get("architectures", "")).lower()
                              or hf.get("speculators_model_type") == "eagle3") else None),
             dflash_target_layer_ids=list((llm.get("dflash_config") or {}).get("target_layer_ids", []) or []),
             dflash_block_size=int((llm.get("dflash_config") or {}).get("block_size", llm.get("block_size", 16)) or 16),
             dflash_mask_token_id=int((llm.get("dflash_config") or {}).get("mask_token_id", llm.get("mask_token_id", 0)) or 0),
             dflash_shift_label=bool((llm.get("dflash_config") or {}).get("shift_label", llm.get("dflash_shift_label", False))),
+            dflash_query_causal=bool((llm.get("dflash_config") or llm.get("jetspec_config") or {}).get("query_causal", llm.get("dflash_query_causal", False))),
             dflash_projector_type=str((llm.get("dflash_config") or {}).get("projector_type", llm.get("dflash_projector_type", "")) or ""),
             domino_pool_size=int((llm.get("dflash_config") or {}).get("pool_size", llm.get("domino_pool_size", 2048)) or 2048),
             domino_proj_dim=int((llm.get("dflash_config") or {}).get("proj_dim", llm.get("domino_proj_dim", 256)) or 256),

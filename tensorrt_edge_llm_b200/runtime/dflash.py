@@ -97,10 +97,11 @@ class DFlashDecoder:
         if scale != 1.0:
             embeds = (embeds * torch.tensor(scale, dtype=embeds.dtype)).to(embeds.dtype)
         past = [self.dkv.lengths[s] for s in seats]
-        if n not in self._mask_cache:
+        causal = bool(self.draft.cfg.dflash_query_causal)          # JetSpec drafts: each block row sees the rows before it only
+        if not causal and n not in self._mask_cache:
             self._mask_cache[n] = full_mask(n * b, b, self.device)
         meta = build_step_meta([b] * n, past, self.dkv.table_rows(seats), self.dkv.page_size, slot_ids=seats, logits_all=True,
-                               device=self.device, tree_mask=self._mask_cache[n])
+                               device=self.device, tree_mask=None if causal else self._mask_cache[n])
         self.stats.draft_forwards += 1
         if hasattr(self.draft, "propose_tokens"):                        # Domino: proposals corrected by what precedes them
             return self.draft.propose_tokens(embeds, meta, self.dkv.pool, ids[:, 0].to(self.device), b).to("cpu")

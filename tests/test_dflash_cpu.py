@@ -231,3 +231,22 @@ def test_sampled_requests_follow_the_target_distribution():
     cold = dec.generate([0], [prompt], 8, sampling={"temperature": 0.01, "top_k": 0, "top_p": 1.0, "seed": 1})
     dec.release([0])
     assert cold == dec.generate([0], [prompt], 8)
+
+
+def test_causal_block_variant_changes_proposals_not_outputs():
+    """JetSpec-style drafts attend causally inside the block: other proposals, the same (target) output."""
+    runner, draft, dkv, tcfg = _pair(block=6)
+    dec = DFlashDecoder(runner, draft, dkv)
+    prompts = [[5, 6, 7, 8, 9, 10, 11]]
+    dec.prefill([0], prompts)
+    full = dec._propose([0])
+    draft.cfg.dflash_query_causal = True
+    causal = dec._propose([0])
+    assert full.shape == causal.shape == (1, 5) and not torch.equal(full, causal)
+    dec.release([0])
+    assert dec.generate([0], prompts, 16) == _greedy(tcfg, prompts, 16)
+    from tensorrt_edge_llm_b200.config import ModelConfig
+    hf = dict(model_type="qwen3", architectures=["JetSpecDraftModel"], vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=1,
+              num_attention_heads=4, num_key_value_heads=2, jetspec_config={"query_causal": True, "block_size": 8})
+    c = ModelConfig.from_hf_dict(hf)
+    assert c.draft_type == "dflash" and c.dflash_query_causal
