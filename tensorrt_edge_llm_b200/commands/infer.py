@@ -86,12 +86,39 @@ def _text_of(messages) -> str:
     return "\n".join(parts)
 
 
-def run_requests(llm, template, requests: List[Dict[str, Any]]) -> List[Dict[str, Any]]:
+def _with_media(llm, multimodal, messages, render):
+    """Messages with image / audio parts → a prepared multimodal prompt (media files are read from the paths the file names)."""
+    import re
+    from ..runtime import native as rt
+    from ..runtime.multimodal import MultimodalInputs
+    from ..server import app as server_app
+    server_app._MEDIA_ROOT["path"] = "/"              # an offline command reads the files its own input names
+    flat, media = server_app._split_media(messages)
+    if not media:
+        return render(messages)
+    if multimodal is None:
+        raise RequestFileError("the request names media but the checkpoint brings no tower this runtime builds")
+    if llm.tokenizer is None:
+        raise RequestFileError("media requests need a tokenizer")
+    req, it = MultimodalInputs(), iter(media)
+    for piece in re.split(f"({server_app._IMG}|{server_app._AUD})", render(flat)):
+        if piece == server_app._IMG:
+            req.image(next(it)[1])
+        elif piece == server_app._AUD:
+            clip = rt.parse_wav(next(it)[1])
+            req.audio(clip.samples, clip.sample_rate)
+        elif piece:
+            req.text(list(llm.tokenizer.encode(piece)))
+    return multimodal.prepare(req)
+
+
+def run_requests(llm, template, requests: List[Dict[str, Any]], multimodal=None) -> List[Dict[str, Any]]:
     from ..runtime.runner import SamplingParams
     results = []
     for r in requests:
-        prompt = template.apply(r["messages"], r["add_generation_prompt"], None, r["enable_thinking"]) if r["apply_chat_template"] \
-            else _text_of(r["messages"])
+        render = (lambda msgs, r=r: template.apply(msgs, r["add_generation_prompt"], None, r["enable_thinking"])) if r["apply_chat_template"] \
+            else _text_of
+        prompt = _with_media(llm, multimodal, r["messages"], render)
         sp = SamplingParams(max_tokens=r["max_tokens"], temperature=r["temperature"], top_k=r["top_k"], top_p=r["top_p"], seed=r["seed"],
                             logprobs=r["num_logprobs"] if r["num_logprobs"] > 0 else None, logit_bias=r["logit_bias"], guided=r["guided"],
                             context_cache_lookup=r["cache_lookup"], context_cache_commit=r["cache_commit"],
@@ -142,7 +169,8 @@ def main(argv=None) -> int:
     prof.set_profiling_enabled(a.dump_profile)
     mon = prof.MemoryMonitor().start() if a.dump_profile else None
     try:
-        results = run_requests(llm, ChatTemplate.load(a.model_dir), requests)
+        from ..runtime.multimodal import MultimodalRunner
+        results = run_requests(llm, ChatTemplate.load(a.model_dir), requests, MultimodalRunner.from_pretrained(llm, a.model_dir))
     finally:
         peak = mon.stop() if mon else 0
         llm.close()

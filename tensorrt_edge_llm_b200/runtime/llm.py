@@ -342,9 +342,43 @@ class LLM:
             return outs
         ids = self._encode(prompts)
         outs: List[RequestOutput] = []
+        if any(hasattr(p, "embeds") for p in ids):        # prepared multimodal prompts: one at a time on the static path
+            for p in ids:
+                outs.extend([self._generate_multimodal_static(p, sp)] if hasattr(p, "embeds") else self._generate_batch([p], sp))
+            return outs
         for b0 in range(0, len(ids), self.max_batch_size):
             outs.extend(self._generate_batch(ids[b0:b0 + self.max_batch_size], sp))
         return outs
+
+    def _generate_multimodal_static(self, p, sp: SamplingParams) -> RequestOutput:
+        """A prepared multimodal prompt without the request engine: prefill from its embedding rows, then ordinary decode."""
+        if sp.needs_logits_processing:
+            raise ValueError("constrained / biased decoding of multimodal prompts needs in-flight batching")
+        seat, runner = 0, self.runner
+        self.kv.free(seat)
+        self.kv.reserve(seat, len(p) + sp.max_tokens)
+        t0 = time.perf_counter()
+        pos3 = None if p.positions3 is None else [p.positions3]
+        logits = runner.prefill_embeds([seat], [p.embeds], positions3=pos3, rope_deltas=None if pos3 is None else [p.rope_delta],
+                                       deepstack=p.deepstack)
+        first = runner.sample(logits, sp, step=0)
+        t1 = time.perf_counter()
+        toks = [int(first[0])]
+        if sp.max_tokens > 1:
+            rest = (runner.decode_greedy([seat], first, sp.max_tokens - 1) if sp.temperature < 1e-3
+                    else runner.decode_sampled([seat], first, sp.max_tokens - 1, sp))
+            toks += rest[0].tolist()
+        self.kv.free(seat)
+        eos = self.cfg.eos_token_id
+        eos_set = (set(eos if isinstance(eos, (list, tuple)) else [eos]) - {None}) | set(sp.stop_token_ids)
+        reason = "length"
+        if not sp.ignore_eos:
+            for j, t in enumerate(toks):
+                if t in eos_set:
+                    toks, reason = toks[:j + 1], "stop"
+                    break
+        text = self.tokenizer.decode(toks) if self.tokenizer is not None else None
+        return RequestOutput(list(p.ids), toks, text, reason, t1 - t0, time.perf_counter() - t1)
 
     def _generate_diffusion(self, ids: List[List[int]], sp: SamplingParams) -> List[RequestOutput]:
         """Block-diffusion checkpoints: denoise and commit one canvas at a time (``runtime/block_diffusion.py``).  The

@@ -226,3 +226,39 @@ def test_multimodal_request_on_a_speculative_deployment():
     assert mm.generate(req, max_tokens=5) == want
     assert spec.generate([[20, 21, 22, 23]], SamplingParams(max_tokens=8, ignore_eos=True))[0].token_ids == text_want
     spec.close()
+
+
+def test_prepared_prompts_on_the_static_path_and_in_the_infer_command(tmp_path):
+    """``LLM.generate`` takes a prepared multimodal prompt without the request engine too; ``trtedge infer`` builds one from
+    messages that name an image file."""
+    from tensorrt_edge_llm_b200.chat_template import ChatTemplate
+    from tensorrt_edge_llm_b200.commands.infer import parse_request_file, run_requests
+    from tensorrt_edge_llm_b200.runtime.runner import SamplingParams
+
+    class Bytes:
+        def encode(self, text, add_special_tokens=False):
+            return [b + 3 for b in text.encode("utf-8")]
+
+        def decode(self, ids, skip_special_tokens=True):
+            return bytes((i - 3) % 256 for i in ids).decode("utf-8", "replace")
+    llm = _llm(mrope=True)
+    llm.tokenizer = Bytes()
+    v, a = _encoders()
+    mm = MultimodalRunner(llm, v, a, image_token_id=298, audio_token_id=299)
+    img = np.random.default_rng(6).integers(0, 255, (32, 32, 3), dtype=np.uint8)
+    req = MultimodalInputs().text([3, 4, 5]).image(img).text([6, 7])
+    want = mm.generate(req, max_tokens=5)
+    out = llm.generate([mm.prepare(req), [20, 21, 22]], SamplingParams(max_tokens=5, ignore_eos=True))
+    assert out[0].token_ids == want and len(out[1].token_ids) == 5 and out[0].prompt_token_ids.count(298) > 0
+    ppm = tmp_path / "frame.ppm"
+    ppm.write_bytes(b"P6\n32 32\n255\n" + img.tobytes())
+    body = {"max_generate_length": 4, "temperature": 0.0,
+            "requests": [{"messages": [{"role": "user", "content": [{"type": "text", "text": "see "}, {"type": "image", "image": str(ppm)}]}]},
+                         {"messages": [{"role": "user", "content": "plain"}]}]}
+    res = run_requests(llm, ChatTemplate(), parse_request_file(body), mm)
+    assert len(res) == 2 and res[0]["output_tokens"] == 4 and res[0]["input_tokens"] > res[1]["input_tokens"]
+    import pytest
+    from tensorrt_edge_llm_b200.commands.infer import RequestFileError
+    with pytest.raises(RequestFileError):
+        run_requests(llm, ChatTemplate(), parse_request_file(body), None)
+    llm.close()
