@@ -37,6 +37,12 @@ class MultimodalInputs:
         self.pieces.append(("image", image))
         return self
 
+    def video(self, frames: Sequence) -> "MultimodalInputs":
+        """A clip as a list of frames (decoded images, arrays, bytes or paths).  It takes the place of one image whose grid
+        has a time axis: Qwen-VL towers fold ``temporal_patch_size`` frames into one grid step."""
+        self.pieces.append(("image", list(frames)))
+        return self
+
     def audio(self, samples, sample_rate: int) -> "MultimodalInputs":
         self.pieces.append(("audio", (np.asarray(samples, dtype=np.float32), int(sample_rate))))
         return self
@@ -124,12 +130,14 @@ class MultimodalRunner:
         hi = self.max_pixels or 1280 * factor * factor
         mats, grids = [], []
         for im in images:
-            im = self._decode(im)
-            hh, ww = rt.smart_resize(im.height, im.width, factor, lo, hi)
-            if (im.height, im.width) != (hh, ww):
-                im = rt.resize_bicubic(im, ww, hh)
-            chw = torch.from_numpy(rt.normalize_chw(im, list(IMAGE_MEAN), list(IMAGE_STD)))
-            m, g = patchify_frames(chw[None], c)
+            frames = [self._decode(f) for f in (im if isinstance(im, list) else [im])]     # a list is a video clip
+            hh, ww = rt.smart_resize(frames[0].height, frames[0].width, factor, lo, max(hi // max(len(frames) // c.temporal_patch_size, 1), lo))
+            chw = []
+            for f in frames:                                   # every frame of a clip goes to the first frame's size
+                if (f.height, f.width) != (hh, ww):
+                    f = rt.resize_bicubic(f, ww, hh)
+                chw.append(torch.from_numpy(rt.normalize_chw(f, list(IMAGE_MEAN), list(IMAGE_STD))))
+            m, g = patchify_frames(torch.stack(chw), c)
             mats.append(m)
             grids.append(g)
         m = c.spatial_merge_size
@@ -186,6 +194,8 @@ class MultimodalRunner:
             return []
         if self.vision is None:
             raise ValueError("this runner has no vision encoder")
+        if any(isinstance(im, list) for im in images) and not isinstance(self.vision, QwenVisionEncoder):
+            raise ValueError("video clips need a tower with a time axis (Qwen-VL)")
         if isinstance(self.vision, InternVisionEncoder):
             rows = self._encode_intern(images)
             if self.keep_ratio < 1.0:

@@ -131,6 +131,12 @@ def _split_media(messages):
                            if source.get("type") == "base64" else source.get("url"))
                 media.append(("image", _media_bytes(str(src))))
                 text += _IMG
+            elif kind == "video":                                   # a clip as a list of frame images (Qwen-VL request format)
+                frames = part.get("video")
+                if not isinstance(frames, list) or not frames:
+                    raise ValueError("a video part needs a list of frame images (data: URIs or allowed local paths)")
+                media.append(("image", [_media_bytes(str(f)) for f in frames]))
+                text += _IMG
             elif kind in ("audio", "input_audio", "audio_url"):
                 src = part.get("audio") or (part.get("audio_url") or {}).get("url")
                 if src is None and isinstance(part.get("input_audio"), dict):

@@ -270,3 +270,28 @@ def test_encoder_cache_serves_repeated_images_with_their_deepstack_levels():
     c = rng.integers(0, 255, (64, 96, 3), dtype=np.uint8)
     mixed = mm.encode_images([a, c])
     assert calls == [2, 1] and torch.equal(mixed[0], first[0])
+
+
+def test_video_clip_takes_a_grid_with_a_time_axis():
+    import numpy as np
+    from tensorrt_edge_llm_b200.config import tiny_llama_config
+    from tensorrt_edge_llm_b200.runtime.llm import LLM
+    from tensorrt_edge_llm_b200.runtime.multimodal import MultimodalInputs, MultimodalRunner
+    cfg = tiny_llama_config(num_hidden_layers=2, vocab_size=200, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                            dtype="float32")
+    cfg.mrope_section = [2, 3, 3]
+    llm = LLM(cfg, device="cpu", max_batch_size=1, max_input_len=256, max_kv_cache_capacity=320, page_size=16)
+    vc = QwenVisionConfig(depth=2, hidden_size=64, num_heads=4, intermediate_size=64, out_hidden_size=64, window_size=56,
+                          fullatt_block_indexes=[1], dtype="float32")
+    mm = MultimodalRunner(llm, vision=QwenVisionEncoder(vc).random_init(3), image_token_id=7, min_pixels=28 * 28 * 4, max_pixels=28 * 28 * 40)
+    rng = np.random.default_rng(0)
+    frames = [rng.integers(0, 255, (56, 84, 3), dtype=np.uint8) for _ in range(4)]      # four frames → two temporal steps of 2 × 3 tokens
+    req = MultimodalInputs().text([3, 4]).video(frames).text([5])
+    ids, emb, pos3, delta = mm.build(req)
+    assert mm._grids == [(2, 2, 3)] and ids.count(7) == 12
+    clip = pos3[:, 2:14]
+    assert clip[0].tolist() == [2] * 6 + [3] * 6                      # the temporal component advances per grid step
+    assert clip[1].tolist() == [2, 2, 2, 3, 3, 3] * 2 and clip[2].tolist() == [2, 3, 4] * 4
+    assert len(mm.generate(req, max_tokens=3)) == 3
+    still = MultimodalInputs().text([3, 4]).image(frames[0]).text([5])
+    assert mm.build(still)[0].count(7) == 6
