@@ -80,12 +80,32 @@ argmax_static_kernel(const T* __restrict__ logits, int* __restrict__ out, int vo
     }
 }
 
-// Device address of g_scratch on the current device, looked up once per device.
-int scratch_for_current_device(Scratch** ptr) {
+// Device address of g_scratch on the current device, looked up once per device.  The kernel runs on the device
+// that owns `stream`, so a stream that belongs to another device than the current one is refused: the scratch
+// pointer cached for the current device would be another GPU's memory there.
+int scratch_for_current_device(Scratch** ptr, cudaStream_t stream, const void* logits) {
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return telb::fail("telb_argmax_static: cudaGetDevice", e);
     if (dev < 0 || dev >= kMaxDevices) return telb::fail("telb_argmax_static: device ordinal out of range");
+    if (stream != nullptr && stream != cudaStreamLegacy && stream != cudaStreamPerThread) {
+        int sdev = -1;
+        e = cudaStreamGetDevice(stream, &sdev);
+        if (e != cudaSuccess) return telb::fail("telb_argmax_static: cudaStreamGetDevice", e);
+        if (sdev != dev) {
+            snprintf(telb::g_last_error, sizeof(telb::g_last_error),
+                     "telb_argmax_static: the stream belongs to device %d but device %d is current; make the stream's device current first", sdev, dev);
+            return -1;
+        }
+    }
+    cudaPointerAttributes attr{};
+    e = cudaPointerGetAttributes(&attr, logits);
+    if (e != cudaSuccess) return telb::fail("telb_argmax_static: cudaPointerGetAttributes", e);
+    if (attr.type == cudaMemoryTypeDevice && attr.device != dev) {
+        snprintf(telb::g_last_error, sizeof(telb::g_last_error),
+                 "telb_argmax_static: logits live on device %d but device %d is current", attr.device, dev);
+        return -1;
+    }
     std::lock_guard<std::mutex> lock(g_setup_mutex);
     if (g_scratch_ptr[dev] == nullptr) {
         Scratch* found = nullptr;
@@ -111,7 +131,7 @@ extern "C" int telb_argmax_static(const void* logits, int* out, int rows, int vo
     if (dtype < 0 || dtype > 2) return telb::fail("telb_argmax_static: dtype must be 0 (fp16), 1 (bf16) or 2 (fp32)");
     if (logits == nullptr || out == nullptr) return telb::fail("telb_argmax_static: null pointer");
     Scratch* scratch = nullptr;
-    if (scratch_for_current_device(&scratch) != 0) return -1;
+    if (scratch_for_current_device(&scratch, stream, logits) != 0) return -1;
     // Every call starts from zeroed keys and counters, whatever an earlier call left behind.
     cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(Scratch), stream);
     if (e != cudaSuccess) return telb::fail("telb_argmax_static: cudaMemsetAsync", e);

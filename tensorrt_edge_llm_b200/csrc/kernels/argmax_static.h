@@ -16,6 +16,9 @@ extern "C" {
 //   out      rows x int32, device memory
 // Returns 0, or -1 with the reason readable through telb_last_error().  rows above
 // TELB_ARGMAX_STATIC_MAX_ROWS, vocab < 1 or an unknown dtype are refused, nothing is launched.
+// `stream` (any stream, the default one included) and `logits` must belong to the device that is
+// current in the calling thread: the scratch address is looked up for the current device, so a
+// stream or a buffer of another device is refused with an error instead of being used.
 //
 // The first call on each device looks up the device address of the scratch array (with that device
 // current), which may load the module; make that first call before any stream capture begins.

@@ -5,8 +5,10 @@
 // One CTA per row:  radix-select the k-th largest logit (k = top_k, or 1024 when only top-p is
 // set — the same candidate cap as the reference), gather the candidates into shared memory, bitonic
 // sort them (value descending, index ascending), softmax with temperature, cut at top-p, sample.
-// Rows with temperature < 1e-3 are greedy.  Among logits exactly equal to the k-th largest value,
-// which ones enter the candidate set is unspecified.
+// Rows with temperature < 1e-3 are greedy.  Among logits exactly equal to the k-th largest value the
+// ones with the lowest token ids enter the candidate set, so the result never depends on the order in
+// which threads arrive: a greedy row returns the lowest index of the maximum (the same answer as the
+// arg-max kernel) whatever else is in the batch, and seeded sampling is reproducible.
 //
 // Reference counterpart: cpp/sampler/sampling.cu (topKStage1/2, topP kernels, applyTokenBitmask,
 // applyLogitBias); semantics cpp/sampler/sampling.h:56-160 (kMaxSamplingTopK 1024).
@@ -71,6 +73,7 @@ sample_kernel(const T* __restrict__ logits, long long stride, int vocab, const f
             }
             s_misc[0] = bin;
             s_misc[1] = remaining - cum;
+            s_misc[3] = hist[bin];          // after the last pass: how many logits equal the threshold exactly
         }
         __syncthreads();
         prefix |= static_cast<uint32_t>(s_misc[0]) << (8 * pass);
@@ -80,16 +83,55 @@ sample_kernel(const T* __restrict__ logits, long long stride, int vocab, const f
     }
     const uint32_t thresh = prefix;         // `remaining` of the keys equal to it are wanted
     // ---- gather candidates ----
-    if (tid == 0) { s_misc[2] = 0; s_misc[3] = 0; }
+    const int n_equal = s_misc[3];
+    __syncthreads();
+    if (tid == 0) s_misc[2] = 0;
     cand[tid] = 0ull;
     __syncthreads();
+    const bool all_ties = n_equal <= remaining;     // every logit equal to the threshold is wanted: no choice to make
     for (int i = tid; i < vocab; i += kSampleThreads) {
         const uint32_t key = order_key(load_logit(p, i));
-        bool take = key > thresh;
-        if (key == thresh) take = atomicAdd(&s_misc[3], 1) < remaining;
-        if (take) {
+        if (key > thresh || (all_ties && key == thresh)) {
             const int slot = atomicAdd(&s_misc[2], 1);
             if (slot < kMaxCand) cand[slot] = (static_cast<unsigned long long>(key) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(i));
+        }
+    }
+    if (!all_ties) {
+        // More ties than places: the `remaining` lowest token ids win.  Each thread owns a contiguous index range, counts
+        // its ties, a block-wide exclusive scan turns the counts into ranks in index order, and ranks below `remaining`
+        // are taken.  (The slot a candidate lands in is still arbitrary; the sort below orders by value, then index.)
+        const int chunk = (vocab + kSampleThreads - 1) / kSampleThreads;
+        const int lo = min(vocab, tid * chunk), hi = min(vocab, lo + chunk);
+        int cnt = 0;
+        for (int i = lo; i < hi; ++i) cnt += order_key(load_logit(p, i)) == thresh ? 1 : 0;
+        int inc = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, inc, o);
+            if ((tid & 31) >= o) inc += n;
+        }
+        __syncthreads();                             // hist[] is free again (the radix passes are over)
+        if ((tid & 31) == 31) hist[tid >> 5] = inc;
+        __syncthreads();
+        if (tid < 32) {
+            int w = hist[tid];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int n = __shfl_up_sync(0xffffffffu, w, o);
+                if (tid >= o) w += n;
+            }
+            hist[32 + tid] = w;
+        }
+        __syncthreads();
+        int rank = inc - cnt + ((tid >> 5) > 0 ? hist[32 + (tid >> 5) - 1] : 0);
+        if (rank < remaining) {
+            for (int i = lo; i < hi && rank < remaining; ++i) {
+                if (order_key(load_logit(p, i)) == thresh) {
+                    const int slot = atomicAdd(&s_misc[2], 1);
+                    if (slot < kMaxCand) cand[slot] = (static_cast<unsigned long long>(thresh) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(i));
+                    ++rank;
+                }
+            }
         }
     }
     __syncthreads();

@@ -88,8 +88,11 @@ PYBIND11_MODULE(_telb_runtime, m) {
     py::class_<PrefixCache>(m, "PrefixCache")
         .def(py::init<PageAllocator&, int, int>(), py::arg("allocator"), py::arg("page_size"), py::arg("max_records") = 1024,
              py::keep_alive<1, 2>())
-        .def("lookup", &PrefixCache::lookup)
-        .def("insert", &PrefixCache::insert)
+        .def("lookup", &PrefixCache::lookup, py::arg("tokens"), py::arg("seed") = 0)
+        .def("insert", &PrefixCache::insert, py::arg("tokens"), py::arg("filled_tokens"), py::arg("pages"), py::arg("seed") = 0)
+        .def_property_readonly("check_mismatches", &PrefixCache::check_mismatches)
+        .def_static("extras_seed", &PrefixCache::extras_seed, py::arg("adapter") = "", py::arg("adapter_generation") = 0,
+                    py::arg("isolation_key") = "")
         .def("evict", &PrefixCache::evict)
         .def_property_readonly("records", &PrefixCache::records)
         .def_property_readonly("hits", &PrefixCache::hits)

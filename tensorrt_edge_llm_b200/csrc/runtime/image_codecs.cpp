@@ -223,6 +223,7 @@ Image decode_png(const std::string& bytes) {
         at += 12 + static_cast<size_t>(len);
     }
     if (ctype < 0 || w == 0 || h == 0 || w > (1u << 15) || h > (1u << 15)) bad("PNG without a usable header");
+    if (static_cast<uint64_t>(w) * h > max_image_pixels()) bad("PNG image has more pixels than the decoder's limit");
     if (interlace) bad("interlaced (Adam7) PNG images are not read");
     int samples;
     switch (ctype) {

@@ -25,6 +25,7 @@ struct JHuff {
     bool set = false;
     std::array<int, 18> mincode{}, maxcode{}, valptr{};
     std::vector<uint8_t> vals;
+    JHuff() { maxcode.fill(-1); }                    // a table that was never defined matches no code
     void build(const uint8_t* counts, const uint8_t* symbols, int total) {
         vals.assign(symbols, symbols + total);
         int code = 0, k = 0;
@@ -46,9 +47,13 @@ struct BitsMsb {
     uint32_t buf = 0;
     int cnt = 0;
     bool hit_marker = false;
+    int pad_bytes = 0;                  // zero bytes fed after the scan's data ended
     int bit() {
         if (cnt == 0) {
             uint8_t b = 0;
+            // a decoder may read a little past the last data byte (a final code completed by padding); a file whose
+            // header promises far more blocks than its data holds must fail instead of decoding zeros for ever
+            if ((hit_marker || at >= n) && ++pad_bytes > 16) bad("JPEG scan data ends before the image is complete");
             if (!hit_marker && at < n) {
                 b = p[at];
                 if (b == 0xff) {
@@ -73,14 +78,18 @@ struct BitsMsb {
         for (int i = 0; i < k; ++i) v = (v << 1) | bit();
         return v;
     }
-    void reset() { cnt = 0; hit_marker = false; }
+    void reset() { cnt = 0; hit_marker = false; pad_bytes = 0; }
 };
 
 int decode_symbol(BitsMsb& s, const JHuff& h) {
     int code = 0;
     for (int len = 1; len <= 16; ++len) {
         code = (code << 1) | s.bit();
-        if (h.maxcode[len] >= 0 && code <= h.maxcode[len] && code >= h.mincode[len]) return h.vals[h.valptr[len] + code - h.mincode[len]];
+        if (h.maxcode[len] >= 0 && code <= h.maxcode[len] && code >= h.mincode[len]) {
+            const size_t idx = static_cast<size_t>(h.valptr[len] + code - h.mincode[len]);
+            if (idx >= h.vals.size()) break;          // over-subscribed table: the code has no symbol
+            return h.vals[idx];
+        }
     }
     bad("invalid Huffman code in a JPEG scan");
 }
@@ -94,13 +103,14 @@ struct Component {
 };
 
 void idct8x8(const float* in, uint8_t* out, int stride) {
-    static float c[8][8];
-    static bool init = false;
-    if (!init) {
+    // function-local static initialised by a lambda: the language guarantees one initialisation even when several
+    // requests decode images at the same time
+    static const std::array<std::array<float, 8>, 8> c = [] {
+        std::array<std::array<float, 8>, 8> t{};
         for (int x = 0; x < 8; ++x)
-            for (int u = 0; u < 8; ++u) c[x][u] = (u == 0 ? std::sqrt(0.125f) : 0.5f) * std::cos((2 * x + 1) * u * 3.14159265358979323846f / 16);
-        init = true;
-    }
+            for (int u = 0; u < 8; ++u) t[x][u] = (u == 0 ? std::sqrt(0.125f) : 0.5f) * std::cos((2 * x + 1) * u * 3.14159265358979323846f / 16);
+        return t;
+    }();
     float tmp[64];
     for (int y = 0; y < 8; ++y)                      // rows: sum over horizontal frequency u
         for (int x = 0; x < 8; ++x) {
@@ -169,6 +179,7 @@ Image decode_jpeg(const std::string& bytes) {
             const int nc = d[5];
             if ((nc != 1 && nc != 3) || dn < 6 + 3 * static_cast<size_t>(nc)) bad("JPEG images with one or three components are read");
             if (width <= 0 || height <= 0 || width > (1 << 15) || height > (1 << 15)) bad("JPEG size out of range");
+            if (static_cast<uint64_t>(width) * static_cast<uint64_t>(height) > max_image_pixels()) bad("JPEG image has more pixels than the decoder's limit");
             comps.assign(nc, Component());
             for (int k = 0; k < nc; ++k) {
                 comps[k].id = d[6 + 3 * k];
@@ -176,6 +187,8 @@ Image decode_jpeg(const std::string& bytes) {
                 comps[k].v = d[7 + 3 * k] & 15;
                 comps[k].tq = d[8 + 3 * k];
                 if (comps[k].h < 1 || comps[k].h > 2 || comps[k].v < 1 || comps[k].v > 2 || comps[k].tq > 3) bad("JPEG sampling factors other than 1 and 2 are not read");
+                for (int j = 0; j < k; ++j)
+                    if (comps[j].id == comps[k].id) bad("JPEG frame header names a component twice");
             }
         } else if (marker == 0xc2) {
             bad("progressive JPEG images are not read (re-encode as baseline)");
@@ -190,14 +203,18 @@ Image decode_jpeg(const std::string& bytes) {
             if (comps.empty()) bad("JPEG scan before its frame header");
             const int ns = d[0];
             if (ns != static_cast<int>(comps.size()) || dn < 1 + 2 * static_cast<size_t>(ns) + 3) bad("JPEG scans must hold every component (non-interleaved scans are not read)");
+            std::vector<uint8_t> assigned(comps.size(), 0);
             for (int k = 0; k < ns; ++k) {
                 const int id = d[1 + 2 * k];
                 auto it = std::find_if(comps.begin(), comps.end(), [&](const Component& c) { return c.id == id; });
                 if (it == comps.end()) bad("JPEG scan names an unknown component");
+                if (assigned[it - comps.begin()]) bad("JPEG scan names a component twice");
+                assigned[it - comps.begin()] = 1;
                 it->td = d[2 + 2 * k] >> 4;
                 it->ta = d[2 + 2 * k] & 15;
-                if (it->td > 3 || it->ta > 3 || !dc[it->td].set || !ac[it->ta].set) bad("JPEG scan uses a Huffman table that was not defined");
             }
+            for (const auto& c : comps)      // every component, not only the ones the scan header happened to name
+                if (c.td > 3 || c.ta > 3 || !dc[c.td].set || !ac[c.ta].set) bad("JPEG scan uses a Huffman table that was not defined");
             int hmax = 1, vmax = 1;
             for (auto& c : comps) { hmax = std::max(hmax, c.h); vmax = std::max(vmax, c.v); }
             const int mcux = (width + 8 * hmax - 1) / (8 * hmax), mcuy = (height + 8 * vmax - 1) / (8 * vmax);

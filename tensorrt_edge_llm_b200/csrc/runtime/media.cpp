@@ -1,5 +1,8 @@
 #include "media.h"
 
+#include <cstdlib>
+#include <climits>
+
 #include <algorithm>
 #include <cmath>
 #include <complex>
@@ -199,6 +202,19 @@ int next_int(const std::string& b, size_t& at) {
 }
 }  // namespace
 
+uint64_t max_image_pixels() {
+    static const uint64_t limit = [] {
+        const char* e = std::getenv("TELB_MAX_IMAGE_PIXELS");
+        if (e && *e) {
+            char* end = nullptr;
+            const unsigned long long v = std::strtoull(e, &end, 10);
+            if (end != e && v > 0) return static_cast<uint64_t>(v);
+        }
+        return static_cast<uint64_t>(64) << 20;
+    }();
+    return limit;
+}
+
 Image parse_image(const std::string& b) {
     Image im;
     if (b.size() >= 8 && static_cast<uint8_t>(b[0]) == 0x89 && b[1] == 'P' && b[2] == 'N' && b[3] == 'G') return decode_png(b);
@@ -210,6 +226,8 @@ Image parse_image(const std::string& b) {
         im.height = next_int(b, at);
         const int maxv = next_int(b, at);
         if (maxv != 255) throw std::runtime_error("only 8-bit PNM images are read");
+        if (im.width <= 0 || im.height <= 0 || static_cast<uint64_t>(im.width) * static_cast<uint64_t>(im.height) > max_image_pixels())
+            throw std::runtime_error("PNM image size out of range");
         ++at;
         const size_t need = static_cast<size_t>(im.width) * im.height * im.channels;
         if (at + need > b.size()) throw std::runtime_error("truncated PNM image");
@@ -228,6 +246,8 @@ Image parse_image(const std::string& b) {
         const uint16_t bpp = rd<uint16_t>(b, 28);
         const uint32_t comp = rd<uint32_t>(b, 30);
         if ((bpp != 24 && bpp != 32) || (comp != 0 && comp != 3)) throw std::runtime_error("only uncompressed 24 / 32 bit BMP images are read");
+        if (w <= 0 || h == 0 || h == INT32_MIN || static_cast<uint64_t>(w) * static_cast<uint64_t>(std::abs(h)) > max_image_pixels())
+            throw std::runtime_error("BMP image size out of range");
         im.width = w;
         im.height = std::abs(h);
         im.channels = 3;

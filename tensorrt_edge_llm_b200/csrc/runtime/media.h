@@ -44,6 +44,9 @@ struct Image {
     std::vector<uint8_t> pixels;     // HWC
 };
 
+// Upper bound on width x height that the decoders accept before they allocate anything (headers come from untrusted
+// requests).  64 Mpixel by default; `TELB_MAX_IMAGE_PIXELS` overrides it for the process.
+uint64_t max_image_pixels();
 Image parse_image(const std::string& bytes);                         // by magic: PNG, JPEG, PPM (P6), PGM (P5), BMP 24 / 32 bit
 Image decode_png(const std::string& bytes);                          // non-interlaced; always returns RGB
 Image decode_jpeg(const std::string& bytes);                         // sequential Huffman (baseline); always returns RGB

@@ -157,14 +157,51 @@ uint64_t PrefixCache::hash_block(uint64_t parent, const int32_t* tokens, int n) 
     return h ? h : 1;
 }
 
-PrefixCache::Match PrefixCache::lookup(const std::vector<int32_t>& tokens) {
+uint64_t PrefixCache::check_block(uint64_t parent_check, const int32_t* tokens, int n) {
+    // splitmix64-style mixing over whole tokens: shares no structure with the byte-wise FNV-1a of hash_block
+    uint64_t h = parent_check ^ 0xD6E8FEB86659FD93ull;
+    for (int i = 0; i < n; ++i) {
+        uint64_t z = h + 0x9E3779B97F4A7C15ull + static_cast<uint32_t>(tokens[i]);
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        h = z ^ (z >> 31);
+    }
+    return h;
+}
+
+uint64_t PrefixCache::extras_seed(const std::string& adapter, uint64_t adapter_generation, const std::string& isolation_key) {
+    if (adapter.empty() && isolation_key.empty()) return 0;
+    uint64_t h = 0xcbf29ce484222325ull;
+    auto mix = [&h](const void* p, size_t n) {
+        const uint8_t* b = static_cast<const uint8_t*>(p);
+        for (size_t i = 0; i < n; ++i) {
+            h ^= b[i];
+            h *= 0x100000001b3ull;
+        }
+    };
+    mix(adapter.data(), adapter.size());
+    const uint8_t sep = 0xff;
+    mix(&sep, 1);
+    mix(&adapter_generation, sizeof(adapter_generation));
+    mix(&sep, 1);
+    mix(isolation_key.data(), isolation_key.size());
+    return h ? h : 1;
+}
+
+PrefixCache::Match PrefixCache::lookup(const std::vector<int32_t>& tokens, uint64_t seed) {
     Match m;
     const int full = (static_cast<int>(tokens.size()) - 1) / page_size_;   // leave >= 1 token to compute
-    uint64_t parent = 0;
+    uint64_t parent = seed, check = seed;
     for (int b = 0; b < full; ++b) {
-        const uint64_t h = hash_block(parent, tokens.data() + static_cast<size_t>(b) * page_size_, page_size_);
+        const int32_t* blk = tokens.data() + static_cast<size_t>(b) * page_size_;
+        const uint64_t h = hash_block(parent, blk, page_size_);
+        check = check_block(check, blk, page_size_);
         auto it = map_.find(h);
         if (it == map_.end()) break;
+        if (it->second.check != check) {       // same 64-bit key, other content: not this prompt's page
+            ++mismatches_;
+            break;
+        }
         lru_.splice(lru_.begin(), lru_, it->second.lru);
         m.pages.push_back(it->second.page);
         m.tokens += page_size_;
@@ -174,22 +211,28 @@ PrefixCache::Match PrefixCache::lookup(const std::vector<int32_t>& tokens) {
     return m;
 }
 
-int PrefixCache::insert(const std::vector<int32_t>& tokens, int filled_tokens, const std::vector<int32_t>& pages) {
+int PrefixCache::insert(const std::vector<int32_t>& tokens, int filled_tokens, const std::vector<int32_t>& pages, uint64_t seed) {
     const int full = std::min<int>(filled_tokens, static_cast<int>(tokens.size())) / page_size_;
-    uint64_t parent = 0;
+    uint64_t parent = seed, check = seed;
     int added = 0;
     for (int b = 0; b < full && b < static_cast<int>(pages.size()); ++b) {
-        const uint64_t h = hash_block(parent, tokens.data() + static_cast<size_t>(b) * page_size_, page_size_);
+        const int32_t* blk = tokens.data() + static_cast<size_t>(b) * page_size_;
+        const uint64_t h = hash_block(parent, blk, page_size_);
+        check = check_block(check, blk, page_size_);
         parent = h;
         auto it = map_.find(h);
         if (it != map_.end()) {
+            if (it->second.check != check) {   // the slot belongs to other content: the rest of this chain stays uncached
+                ++mismatches_;
+                break;
+            }
             lru_.splice(lru_.begin(), lru_, it->second.lru);
             continue;
         }
         if (static_cast<int>(map_.size()) >= max_records_ && evict(1) == 0) break;
         alloc_.retain({pages[b]});
         lru_.push_front(h);
-        map_[h] = Entry{pages[b], lru_.begin()};
+        map_[h] = Entry{pages[b], check, lru_.begin()};
         ++added;
     }
     return added;

@@ -100,6 +100,13 @@ class PrefixCache {
   public:
     PrefixCache(PageAllocator& alloc, int page_size, int max_records);
     static uint64_t hash_block(uint64_t parent, const int32_t* tokens, int n);
+    // A second, independent hash of the same block (different mixing function and constants).  It is stored with the
+    // entry and compared on every hit, so two prompts must collide in 128 bits before they could share a page.
+    static uint64_t check_block(uint64_t parent_check, const int32_t* tokens, int n);
+    // Seed of a hash chain for everything besides token ids that decides what the KV of a prompt holds: the LoRA
+    // adapter a request runs under (name + load generation) and an optional isolation key.  Requests with different
+    // seeds never see each other's pages.
+    static uint64_t extras_seed(const std::string& adapter, uint64_t adapter_generation, const std::string& isolation_key);
 
     struct Match {
         std::vector<int32_t> pages;
@@ -107,24 +114,27 @@ class PrefixCache {
     };
     // Longest cached prefix of `tokens` in whole pages (never the whole prompt: at least one token
     // is left to compute so the step produces logits).
-    Match lookup(const std::vector<int32_t>& tokens);
+    // `seed` starts the hash chain (0 = base model, no isolation; see extras_seed).
+    Match lookup(const std::vector<int32_t>& tokens, uint64_t seed = 0);
     // Register the first `filled_tokens` (whole pages only) of a sequence whose pages are `pages`.
-    int insert(const std::vector<int32_t>& tokens, int filled_tokens, const std::vector<int32_t>& pages);
+    int insert(const std::vector<int32_t>& tokens, int filled_tokens, const std::vector<int32_t>& pages, uint64_t seed = 0);
     int evict(int pages_wanted);          // returns pages released
     int records() const { return static_cast<int>(map_.size()); }
     uint64_t hits() const { return hits_; }
     uint64_t misses() const { return misses_; }
+    uint64_t check_mismatches() const { return mismatches_; }
 
   private:
     struct Entry {
         int32_t page;
+        uint64_t check;
         std::list<uint64_t>::iterator lru;
     };
     PageAllocator& alloc_;
     int page_size_, max_records_;
     std::unordered_map<uint64_t, Entry> map_;
     std::list<uint64_t> lru_;             // front = most recent
-    uint64_t hits_ = 0, misses_ = 0;
+    uint64_t hits_ = 0, misses_ = 0, mismatches_ = 0;
 };
 
 }  // namespace telb

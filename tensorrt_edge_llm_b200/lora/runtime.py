@@ -89,6 +89,12 @@ class LoraManager:
         self.names: List[str] = []
         self.active: Optional[str] = None
         self._wrapped: Dict[str, LoraLinear] = {}
+        self._generation: Dict[str, int] = {}       # name → number of times an adapter was loaded under it
+
+    def generation(self, name: str) -> int:
+        """Load counter of ``name``: part of the prefix-cache identity, so K/V cached under an adapter that was later
+        replaced under the same name is not reused."""
+        return self._generation.get(name, 0)
 
     def _wrap(self, module_name: str) -> LoraLinear:
         if module_name in self._wrapped:
@@ -131,6 +137,12 @@ class LoraManager:
         f = SafetensorsFile(os.path.join(adapter_dir, "lora_weights.safetensors"))
         with open(os.path.join(adapter_dir, "lora_config.json"), "r", encoding="utf-8") as fh:
             meta = json.load(fh)
+        if name in self.names:                      # reloading under a known name replaces the old weights
+            for w in self._wrapped.values():
+                old = w.adapters.pop(name, None)
+                if old is not None and w.active is old:
+                    w.active = None
+        self._generation[name] = self._generation.get(name, 0) + 1
         for ckpt_mod in meta["modules"]:
             mod_name, src, base = self._locate(ckpt_mod)
             a, b = f.get(f"lora_A_{ckpt_mod}").clone(), f.get(f"lora_B_{ckpt_mod}").clone()

@@ -59,11 +59,11 @@ def serve_follower(runner, mirror: StepMirror, enable_prefix_cache: bool = False
             kv.free(slot)
             kv.reserve(slot, need)
         elif kind == "admit":
-            _, slot, prompt_ids, need, ok = op
+            _, slot, prompt_ids, need, ok, seed = op
             kv.free(slot)
             try:
                 if prefix is not None and prompt_ids is not None:
-                    m = prefix.lookup(list(prompt_ids))
+                    m = prefix.lookup(list(prompt_ids), seed)
                     if m.tokens:
                         kv.adopt_prefix(slot, list(m.pages), m.tokens)
                 if ok:
@@ -75,9 +75,9 @@ def serve_follower(runner, mirror: StepMirror, enable_prefix_cache: bool = False
                 if prefix is not None:
                     prefix.evict(8)
         elif kind == "prefix_insert":
-            _, slot, tokens, n = op
+            _, slot, tokens, n, seed = op
             if prefix is not None:
-                prefix.insert(list(tokens), n, kv.pages_of(slot))
+                prefix.insert(list(tokens), n, kv.pages_of(slot), seed)
         elif kind == "step":
             _, seats, token_lists = op
             runner.step(list(seats), [list(t) for t in token_lists])

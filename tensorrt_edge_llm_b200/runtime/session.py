@@ -89,6 +89,18 @@ class ModelSession(rt.RuntimeSession):
                               "deepstack": {int(k): (torch.as_tensor(r, dtype=torch.int64), f) for k, (r, f) in (deepstack or {}).items()}}
         return key
 
+    def _prefix_seed(self, req) -> int:
+        """Start of a request's block-hash chain: 0 for the base model, else a hash of the adapter's name and load
+        generation (``BlockKeyExtras.adapter`` in ``cpp/runtime/state/contextCache/blockHash.h``).  K/V written under
+        one adapter (LoRA wraps the QKV projection) is never adopted by the base model or by another adapter, and
+        an adapter reloaded under the same name starts a new chain."""
+        name = getattr(req, "lora_name", "") or ""
+        if not name:
+            return 0
+        lora = getattr(self.runner, "lora", None)
+        gen = lora.generation(name) if lora is not None and hasattr(lora, "generation") else 0
+        return int(rt.PrefixCache.extras_seed(name, int(gen), ""))
+
     # ---- seam ------------------------------------------------------------------------------------
     def capabilities(self):
         c = rt.SessionCapabilities()
@@ -139,10 +151,11 @@ class ModelSession(rt.RuntimeSession):
         try:
             if self.prefix is not None and req.cache_lookup and mm is None:      # placeholder ids say nothing about the media
                 looked_up = list(req.prompt_ids)
-                m = self.prefix.lookup(list(req.prompt_ids))
+                seed = self._prefix_seed(req)
+                m = self.prefix.lookup(list(req.prompt_ids), seed)
                 pages, tokens = list(m.pages), m.tokens
                 if tokens and self.hybrid:
-                    pages, tokens = self._restore_snapshot(slot, req.prompt_ids, pages)
+                    pages, tokens = self._restore_snapshot(slot, req.prompt_ids, pages, seed)
                 if tokens:
                     self.kv.adopt_prefix(slot, pages, tokens)
                     reused = tokens
@@ -156,12 +169,13 @@ class ModelSession(rt.RuntimeSession):
                 if self.mirror is not None:
                     # followers repeat lookup → adopt → reserve on their own page table and prefix index (same operations in
                     # the same order keep their state identical to this rank's)
-                    self.mirror.send(("admit", slot, looked_up, need, True) if self.prefix is not None else ("reserve", slot, need))
+                    self.mirror.send(("admit", slot, looked_up, need, True, self._prefix_seed(req)) if self.prefix is not None
+                                     else ("reserve", slot, need))
         except (MemoryError, RuntimeError) as e:
             self.kv.free(slot)
             self.slots.release(slot)
             if self.mirror is not None and self.prefix is not None:
-                self.mirror.send(("admit", slot, looked_up, need, False))
+                self.mirror.send(("admit", slot, looked_up, need, False, self._prefix_seed(req)))
             if self.prefix is not None and self.prefix.evict(8):
                 r.admitted, r.retry_later, r.reason = False, True, "KV pool full (evicted cached prefixes)"
             else:
@@ -182,16 +196,16 @@ class ModelSession(rt.RuntimeSession):
             return self._execute(plan)
 
     # ---- hybrid prefix snapshots ---------------------------------------------------------------
-    def _chain_hashes(self, tokens, n_pages: int):
-        p, h, out = self.kv.page_size, 0, []
+    def _chain_hashes(self, tokens, n_pages: int, seed: int = 0):
+        p, h, out = self.kv.page_size, seed, []
         for i in range(n_pages):
             h = rt.PrefixCache.hash_block(h, list(tokens[i * p:(i + 1) * p]))
             out.append(h)
         return out
 
-    def _restore_snapshot(self, slot: int, prompt_ids, pages):
+    def _restore_snapshot(self, slot: int, prompt_ids, pages, seed: int = 0):
         """Longest page prefix of ``pages`` that also has a recurrent snapshot: its rows go into the seat's state."""
-        hashes = self._chain_hashes(prompt_ids, len(pages))
+        hashes = self._chain_hashes(prompt_ids, len(pages), seed)
         for k in range(len(pages), 0, -1):
             snap = self.snapshots.get(hashes[k - 1])
             if snap is not None:
@@ -202,7 +216,7 @@ class ModelSession(rt.RuntimeSession):
         return [], 0
 
     def _take_snapshot(self, slot: int, q, upto_tokens: int) -> None:
-        h = self._chain_hashes(q.req.prompt_ids, upto_tokens // self.kv.page_size)[-1]
+        h = self._chain_hashes(q.req.prompt_ids, upto_tokens // self.kv.page_size, self._prefix_seed(q.req))[-1]
         if h in self.snapshots:
             self.snapshots.move_to_end(h)
             return
@@ -371,9 +385,10 @@ class ModelSession(rt.RuntimeSession):
                 if s.kind == rt.WorkKind.Context and s.last_chunk:
                     q = self.seqs[s.slot]
                     if q.req.cache_commit >= 1 and q.mm is None:      # placeholder ids of media prompts must not be shared
+                        seed = self._prefix_seed(q.req)
                         if self.mirror is not None:
-                            self.mirror.send(("prefix_insert", s.slot, list(q.req.prompt_ids), len(q.req.prompt_ids)))
-                        self.prefix.insert(list(q.req.prompt_ids), len(q.req.prompt_ids), self.kv.pages_of(s.slot))
+                            self.mirror.send(("prefix_insert", s.slot, list(q.req.prompt_ids), len(q.req.prompt_ids), seed))
+                        self.prefix.insert(list(q.req.prompt_ids), len(q.req.prompt_ids), self.kv.pages_of(s.slot), seed)
         out.deltas = deltas
         return out
 
@@ -418,9 +433,10 @@ class ModelSession(rt.RuntimeSession):
                 # quotes the answer starts from them); hybrid models publish prompts only, their snapshots end there
                 filled = min(self.kv.lengths[slot], len(q.tokens))
                 if filled > len(q.req.prompt_ids):
+                    seed = self._prefix_seed(q.req)
                     if self.mirror is not None:
-                        self.mirror.send(("prefix_insert", slot, list(q.tokens[:filled]), filled))
-                    self.prefix.insert(list(q.tokens[:filled]), filled, self.kv.pages_of(slot))
+                        self.mirror.send(("prefix_insert", slot, list(q.tokens[:filled]), filled, seed))
+                    self.prefix.insert(list(q.tokens[:filled]), filled, self.kv.pages_of(slot), seed)
             del self.seqs[slot]
             if self.spec is not None:
                 self.spec.release([slot])

@@ -174,6 +174,35 @@ def test_gated_delta_rule(cu, q_lens, pasts):
     _sync_check(cu)
 
 
+def test_sampling_ties_take_the_lowest_ids(cu):
+    """Duplicated maxima in a batch that mixes greedy and sampled rows: a greedy row returns the lowest index of the
+    maximum (what the arg-max kernel returns), on every run, and a top-k cut through a run of equal logits keeps the
+    lowest ids."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    rows, vocab = 8, 151936
+    logits = torch.randn(rows, vocab, device="cuda", generator=g).half()
+    big = float(logits.float().max()) + 2.0
+    ties = [[120000, 77, 9031, 150001], [5, 6, 7], [151935, 0], [42], [100, 50000, 60000, 70000, 80000], [3, 2, 1], [99999, 1234], [8, 80]]
+    for r, ids in enumerate(ties):
+        logits[r, ids] = big
+    temp = torch.tensor([0.0, 0.8, 0.0, 1.0, 0.0, 0.0, 0.9, 0.0], device="cuda")
+    top_k = torch.tensor([0, 2, 5, 1, 3, 1, 1, 40], device="cuda", dtype=torch.int32)
+    top_p = torch.ones(rows, device="cuda")
+    u = torch.full((rows,), 0.999, device="cuda")
+    first = None
+    for _ in range(5):
+        got = cu.sample(logits, temp, top_k, top_p, u)
+        first = got if first is None else first
+        assert torch.equal(got, first)                         # arrival order plays no part
+    for r, ids in enumerate(ties):
+        if float(temp[r]) < 1e-3 or int(top_k[r]) == 1:
+            assert int(first[r]) == min(ids)
+        else:                                                   # row 1: top-2 of three equal maxima = the two lowest ids
+            assert int(first[r]) in sorted(ids)[:int(top_k[r])]
+    assert torch.equal(first[temp < 1e-3].long(), cu.argmax(logits)[temp < 1e-3].long())
+    _sync_check(cu)
+
+
 def test_sampling_kernel(cu):
     g = torch.Generator(device="cuda").manual_seed(8)
     rows, vocab = 48, 32000

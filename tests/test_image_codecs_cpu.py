@@ -142,3 +142,52 @@ def test_jpeg_baseline_against_pillow():
         rt.decode_jpeg(data[:200])
     with pytest.raises(RuntimeError, match="unsupported image container"):
         rt.parse_image(b"GIF89a" + b"\x00" * 64)
+
+
+import struct as struct  # noqa: E402
+
+
+def _patch_sos(data: bytes, edit) -> bytes:
+    """Return ``data`` with its start-of-scan header bytes changed by ``edit(header bytearray)``."""
+    b = bytearray(data)
+    i = b.find(b"\xff\xda")
+    n = (b[i + 2] << 8) | b[i + 3]
+    hdr = b[i + 4:i + 2 + n]
+    edit(hdr)
+    b[i + 4:i + 2 + n] = hdr
+    return bytes(b)
+
+
+def test_jpeg_malformed_scan_headers_raise_cleanly():
+    """Crafted files from untrusted requests: a scan that names one component twice (leaving another on tables that were
+    never defined), a frame header with duplicate ids, a header that promises more data than the file holds, and sizes
+    beyond the pixel cap all end in an exception, never in an out-of-bounds read or an endless decode."""
+    a = _img(32, 48, seed=9)
+    data = _save(a, "JPEG", quality=80, subsampling=0)
+
+    def dup_component(h):          # ns=3: make the third entry name the first component again, with table ids 3/3
+        h[5] = h[1]
+        h[6] = 0x33
+    with pytest.raises(RuntimeError, match="twice|not defined"):
+        rt.decode_jpeg(_patch_sos(data, dup_component))
+
+    def undefined_tables(h):       # second component on Huffman tables 2/2, which the file never defines
+        h[4] = 0x22
+    with pytest.raises(RuntimeError, match="not defined"):
+        rt.decode_jpeg(_patch_sos(data, undefined_tables))
+    b = bytearray(data)
+    i = b.find(b"\xff\xc0")
+    b[i + 13] = b[i + 10]            # SOF: second component id := first component id
+    with pytest.raises(RuntimeError, match="twice"):
+        rt.decode_jpeg(bytes(b))
+    # a header that claims a far larger image than the scan data covers: must stop, not decode zeros for megapixels
+    big = bytearray(data)
+    big[i + 5:i + 9] = struct.pack(">HH", 4000, 4000)
+    with pytest.raises(RuntimeError, match="ends before"):
+        rt.decode_jpeg(bytes(big))
+    huge = bytearray(data)
+    huge[i + 5:i + 9] = struct.pack(">HH", 32000, 32000)
+    with pytest.raises(RuntimeError, match="limit"):
+        rt.decode_jpeg(bytes(huge))
+    with pytest.raises(RuntimeError, match="limit|range"):
+        rt.parse_image(b"P6\n30000 30000\n255\n" + b"\x00" * 64)

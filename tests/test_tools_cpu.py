@@ -296,3 +296,33 @@ def test_lora_per_request_under_in_flight_batching(ckpt, tmp_path):
     with pytest.raises(ValueError):
         ifb.submit(prompts[0], SamplingParams(max_tokens=2, lora_name="three"))
     ifb.close()
+
+
+def test_prefix_cache_is_keyed_by_adapter(ckpt, tmp_path):
+    """The same prompt under adapter "one" and then under the base model: the second request must not adopt the first one's
+    KV pages (LoRA wraps the QKV projection, so their K/V differ) and must produce the tokens of a run without the cache."""
+    from tensorrt_edge_llm_b200.runtime.llm import LLM, SamplingParams
+    a1, r1 = str(tmp_path / "a1"), str(tmp_path / "r1")
+    _adapter(a1, r=4, alpha=64.0)
+    assert trtedge(["process-lora", "--input_dir", a1, "--output_dir", r1, "--dtype", "bfloat16"]) == 0
+    prompt = [(7 * i + 3) % 90 + 5 for i in range(41)]               # two full 16-token pages + a tail
+    kw = dict(max_batch_size=2, max_kv_cache_capacity=128, page_size=16, device="cpu", enable_in_flight_batching=True)
+
+    def run(llm, name):
+        return llm.submit(prompt, SamplingParams(max_tokens=6, lora_name=name, ignore_eos=True)).get(60.0)
+    plain = LLM(ckpt, **kw)
+    plain.load_lora("one", r1)
+    want_one, want_base = run(plain, "one"), run(plain, None)
+    plain.close()
+    assert want_one != want_base
+    llm = LLM(ckpt, enable_prefix_cache=True, **kw)
+    llm.load_lora("one", r1)
+    pc = llm.session.prefix
+    assert run(llm, "one") == want_one
+    hits0 = pc.hits
+    assert run(llm, None) == want_base and pc.hits == hits0          # base model: no hit on the adapter's pages
+    assert run(llm, None) == want_base and pc.hits == hits0 + 1      # ... but on its own
+    assert run(llm, "one") == want_one and pc.hits == hits0 + 2
+    llm.load_lora("one", r1)                                         # reloaded under the same name: a new identity
+    assert run(llm, "one") == want_one and pc.hits == hits0 + 2
+    llm.close()

@@ -44,6 +44,30 @@ def test_static_argmax_matches_regular_entry_point(dtype, rows, vocab):
     assert torch.equal(out2, want2) and torch.equal(out, want)
 
 
+def test_static_argmax_on_a_side_stream_and_wrong_device_stream():
+    """A non-default stream of the current device works; a stream (or logits) of another device is refused."""
+    from tensorrt_edge_llm_b200.ops import cuda
+    lib = cuda.lib()
+    g = torch.Generator(device="cuda").manual_seed(11)
+    logits = torch.randn(16, 40000, device="cuda", generator=g).half()
+    want = cuda.argmax(logits)
+    out = torch.full((16,), -1, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        assert _call(lib, logits, out) == 0
+        assert _call(lib, logits, out) == 0
+    side.synchronize()
+    assert torch.equal(out, want)
+    if torch.cuda.device_count() > 1:
+        other = torch.cuda.Stream(device=1)
+        lib.telb_argmax_static.restype = ctypes.c_int
+        rc = lib.telb_argmax_static(ctypes.c_void_p(logits.data_ptr()), ctypes.c_void_p(out.data_ptr()), ctypes.c_int(16), ctypes.c_int(40000),
+                                    ctypes.c_longlong(logits.stride(0)), ctypes.c_int(0), ctypes.c_void_p(other.cuda_stream))
+        assert rc == -1 and b"device" in lib.telb_last_error()
+        torch.cuda.synchronize()
+
+
 def test_static_argmax_rejects_oversize():
     from tensorrt_edge_llm_b200.ops import cuda
     lib = cuda.lib()
