@@ -94,8 +94,9 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "hybrid", "eagle"],
-                    help="dense = the headline benchmark; the others are the secondary single-GPU configurations")
+    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "hybrid", "eagle", "serve"],
+                    help="dense = the headline benchmark; moe / hybrid / eagle are the secondary configurations; serve = the request engine "
+                         "with staggered arrivals (in-flight batching)")
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--input-len", type=int, default=None)
     ap.add_argument("--output-len", type=int, default=None)
@@ -186,6 +187,30 @@ def main() -> int:
     clocks = sampler.stop()
     cu.Workspace.get(dev).check_status()
 
+    # ---- N > 1: the same timed loop with every collective through NCCL (all-reduce, then the local norm kernel; a small
+    # all-gather of per-shard candidates for the greedy pick).  The reference cannot run on this image, so this is the
+    # composition its AllReducePlugin → ncclAllReduce path amounts to, on the same model, kernels and box.
+    nccl_arm = None
+    if world > 1 and args.comm == "fused" and hasattr(comm, "force_nccl"):
+        comm.force_nccl = True
+        runner._graphs.clear()
+        for _ in range(max(2, min(args.warmup, 3))):
+            one_batch_device()
+            flush.fill_(1)
+        n_ms, n_pre, n_dec = [], [], []
+        for _ in range(args.steps):
+            flush.fill_(0)
+            barrier()
+            e0, e1, e2, _t = one_batch_device()
+            barrier()
+            n_ms.append(e0.elapsed_time(e2))
+            n_pre.append(e0.elapsed_time(e1))
+            n_dec.append(e1.elapsed_time(e2))
+        nccl_arm = (sum(n_ms) / len(n_ms), statistics.median(n_pre), statistics.median(n_dec))
+        comm.force_nccl = False
+        runner._graphs.clear()
+        cu.Workspace.get(dev).check_status()
+
     # ---- end to end through the public API: pinned host prompts in, generated tokens out --------
     sp = SamplingParams(max_tokens=O, ignore_eos=True)
     e2e_s, ttft, tpot = [], [], []
@@ -232,6 +257,11 @@ def main() -> int:
                 "d2h_bytes_per_step": int(B * O * 4), "ms_per_step": round(e2e * 1e3, 3)},
         "gpu_launches": int(launches),
     }
+    if nccl_arm is not None:
+        n_ms = maxr(nccl_arm[0])
+        out["nccl_arm"] = {"value": round(B * O / (n_ms / 1e3), 1), "unit": "tok/s", "ms_per_step": round(n_ms, 3),
+                           "prefill_ms": round(maxr(nccl_arm[1]), 3), "decode_ms_per_token": round(maxr(nccl_arm[2]) / max(1, O - 1), 4),
+                           "what": "same model and kernels, every collective through NCCL (torch.distributed) instead of the fused peer-memory kernels"}
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:

@@ -5,6 +5,7 @@ warm-up, synthetic seeded token ids, random-init weights of the named architectu
     python bench.py --workload moe      # Qwen3-30B-A3B shape, NVFP4 experts, batch 32, 2048 in / 256 out
     python bench.py --workload hybrid   # Nemotron-H-style Mamba2 + gated DeltaNet + attention, batch 16, 8192 in / 256 out
     python bench.py --workload eagle    # EAGLE-3 tree speculative decoding on the Qwen3-8B shape, forced accept lengths
+    python bench.py --workload serve    # the served path: native request engine, staggered arrivals, in-flight batching
 """
 from __future__ import annotations
 
@@ -159,11 +160,87 @@ def run_eagle(args) -> dict:
             "gpu_launches": int(cu.LAUNCHES - l0), "data": "synthetic"}
 
 
+def run_serve(args) -> dict:
+    """The served path: requests arrive one by one at the native request engine (``csrc/runtime/scheduler.cpp``), are
+    admitted mid-flight into at most ``batch`` seats, prefilled in chunks next to the running decode rows and decoded by
+    graph replays once a step holds decode rows only.  Reports whole-run output tokens/s (wall clock from the first
+    submission to the last completion: arrivals are host events) and per-request p50 / p95 TTFT and TPOT from the
+    engine's own request statistics.  Prompts are host-side token lists (copied to the device by every step that
+    consumes them); every generated token is read back to the host by the step that produced it."""
+    from ..config import QUANT_NVFP4, QuantConfig, qwen3_8b_config
+    from ..ops import cuda as cu
+    from ..runtime.llm import LLM
+    from ..runtime.runner import SamplingParams
+    b, s, o = args.batch or 64, args.input_len or 1024, args.output_len or 128
+    n_req = max(1, args.steps) * b                    # `steps` waves of `batch` requests
+    gap_s = 0.005                                     # one arrival every 5 ms (200 requests / s offered)
+    act = "float16" if args.dtype in ("nvfp4", "fp16") else "bfloat16"
+    quant = QuantConfig(quant_type=QUANT_NVFP4, group_size=16) if args.dtype == "nvfp4" else QuantConfig()
+    cfg = qwen3_8b_config(dtype=act, quant=quant, **({"num_hidden_layers": args.layers} if args.layers else {}))
+    llm = LLM(cfg, device="cuda", max_batch_size=b, max_input_len=s, max_kv_cache_capacity=s + o + 64, page_size=64,
+              max_num_tokens=8192, random_init_seed=0, enable_in_flight_batching=True,
+              scheduling={"mode": "mixed", "max_num_tokens": 8192, "max_chunk_tokens": 2048})
+    g = torch.Generator().manual_seed(1234)
+    prompts = torch.randint(0, cfg.vocab_size, (n_req, s), generator=g, dtype=torch.int32).tolist()
+    sp = SamplingParams(max_tokens=o, ignore_eos=True)
+
+    def wave(reqs, gap):
+        t0 = time.perf_counter()
+        handles = []
+        for i, p in enumerate(reqs):
+            while time.perf_counter() - t0 < i * gap:
+                time.sleep(0.0005)
+            handles.append(llm.submit(p, sp))
+        outs = [h.get(600.0) for h in handles]
+        torch.cuda.synchronize()
+        return time.perf_counter() - t0, handles, outs
+    # warm-up: a full wave (kernels, allocator) and every decode-graph bucket this seat count can reach
+    for _ in range(max(1, min(args.warmup, 2))):
+        wave(prompts[:b], 0.0)
+    runner = llm.runner
+    warm_seats = list(range(b))
+    for seat in warm_seats:
+        llm.kv.free(seat)
+        llm.kv.reserve(seat, 8)
+    for n in sorted({runner.graph_bucket(k) for k in range(1, b + 1)}):
+        runner.decode_step_graph(warm_seats[:n], [1] * n)
+    for seat in warm_seats:
+        llm.kv.free(seat)
+    torch.cuda.synchronize()
+    l0, g0, m0 = cu.LAUNCHES, llm.session.graph_steps, llm.engine.metrics()
+    wall, handles, outs = wave(prompts, gap_s)
+    m1 = llm.engine.metrics()
+    stats = [h.stats() for h in handles]
+    ttft = sorted(st.ttft_s for st in stats)
+    tpot = sorted((st.total_s - st.ttft_s) / max(1, st.generated_tokens - 1) for st in stats)
+    pct = lambda xs, q: xs[min(len(xs) - 1, int(q * len(xs)))]
+    total = sum(len(x) for x in outs)
+    assert total == n_req * o
+    cu.Workspace.get(torch.device("cuda", torch.cuda.current_device())).check_status()
+    steps_all = (m1.decode_steps - m0.decode_steps) + (m1.prompt_steps - m0.prompt_steps) + (m1.mixed_steps - m0.mixed_steps)
+    out = {"metric": "output tok/s through the request engine (in-flight batching, staggered arrivals), Qwen3-8B shape, 1024 in / 128 out",
+           "value": round(total / wall, 1), "unit": "tok/s", "n_gpus": 1, "ms_per_step": round(wall * 1e3 / max(1, steps_all), 3),
+           "config": {"requests": n_req, "seats": b, "seq_len": s, "output_len": o, "arrival_gap_ms": gap_s * 1e3, "weights": args.dtype,
+                      "p50_ttft_ms": round(pct(ttft, 0.5) * 1e3, 2), "p95_ttft_ms": round(pct(ttft, 0.95) * 1e3, 2),
+                      "p50_tpot_ms": round(pct(tpot, 0.5) * 1e3, 3), "p95_tpot_ms": round(pct(tpot, 0.95) * 1e3, 3),
+                      "engine_steps": int(steps_all), "decode_only_steps": int(m1.decode_steps - m0.decode_steps),
+                      "graph_replay_steps": int(llm.session.graph_steps - g0), "mixed_steps": int(m1.mixed_steps - m0.mixed_steps),
+                      "admitted_mid_flight": int(m1.admitted_mid_flight - m0.admitted_mid_flight), "wall_s": round(wall, 3),
+                      "layers": cfg.num_hidden_layers, "timing": "wall clock (arrivals are host events); per-request figures from the engine"},
+           "e2e": {"value": round(total / wall, 1), "unit": "tok/s", "h2d_bytes_per_step": int(n_req * s * 4 / max(1, steps_all)),
+                   "d2h_bytes_per_step": int(total * 4 / max(1, steps_all))},
+           "gpu_launches": int(cu.LAUNCHES - l0), "data": "synthetic (seeded uniform token ids, random-init weights)",
+           "dtype": "nvfp4-weights/nvfp4-act-gemm/fp16-activations" if args.dtype == "nvfp4" else args.dtype}
+    llm.close()
+    return out
+
+
 def main(args) -> int:
-    fn = {"moe": run_moe, "hybrid": run_hybrid, "eagle": run_eagle}[args.workload]
+    fn = {"moe": run_moe, "hybrid": run_hybrid, "eagle": run_eagle, "serve": run_serve}[args.workload]
     out = fn(args)
     rank, world, llm = out.pop("_rank", 0), out.pop("_world", 1), out.pop("_llm", None)
-    out.update({"steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "dtype": "bf16" if args.workload != "moe" else "nvfp4-experts/bf16"})
+    out.update({"steps": args.steps, "warmup": args.warmup, "higher_is_better": True})
+    out.setdefault("dtype", "bf16" if args.workload != "moe" else "nvfp4-experts/bf16")
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:       # graphs hold collective kernels: leave without the communicator's destructor

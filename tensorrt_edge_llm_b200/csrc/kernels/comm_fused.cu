@@ -24,6 +24,7 @@
 namespace telb {
 
 constexpr int kMaxRanks = 8;
+constexpr int kMaxHidden = 16384;       // 4 units x 256 threads x 16 elements
 
 struct ArParams {
     const void* x;                       // this rank's partial [rows, hidden] (local)
@@ -278,6 +279,9 @@ template <typename T, int kUnits>
 __global__ void rs_add_rmsnorm_ag_kernel(RsAgParams p) {
     __shared__ float red[32];
     __shared__ int s_ok, s_last;
+    // one row of NVFP4 output staged for the push: packed codes (hidden / 2 bytes) and scale bytes (hidden / 16)
+    __shared__ uint4 s_codes[kMaxHidden / 32];
+    __shared__ uint32_t s_sf4[kMaxHidden / 64];
     pdl_prologue();
     const int rows_local = max(0, min(p.rows_per_rank, p.rows - p.rank * p.rows_per_rank));
     const int row = blockIdx.x;                          // local row
@@ -362,6 +366,7 @@ __global__ void rs_add_rmsnorm_ag_kernel(RsAgParams p) {
         const float inv = p.weight ? rsqrtf(tot / p.hidden + p.eps) : 1.f;
         const float gs = p.quant_scale ? *p.quant_scale : 1.f;
         const float inv_gs = 1.f / gs;
+        const bool vec_push = (p.hidden % 64) == 0;
         // 3. normalise and push the row to every rank
 #pragma unroll
         for (int u = 0; u < kUnits; ++u) {
@@ -400,12 +405,31 @@ __global__ void rs_add_rmsnorm_ag_kernel(RsAgParams p) {
                 if (p.gather_xq[0]) {
                     uint8_t s8;
                     const uint2 packed = nvfp4_quantize_block16(y, amax, gs, inv_gs, s8);
-                    const size_t sfo = sf_atom_offset(grow, idx, p.k64_pad);
-                    for (int r = 0; r < p.world; ++r) {
-                        *reinterpret_cast<uint2*>(p.gather_xq[r] + (size_t)grow * (p.hidden / 2) + idx * 8) = packed;
-                        p.gather_sf[r][sfo] = s8;
+                    if (vec_push) {
+                        reinterpret_cast<uint2*>(s_codes)[idx] = packed;
+                        reinterpret_cast<uint8_t*>(s_sf4)[idx] = s8;
+                    } else {
+                        const size_t sfo = sf_atom_offset(grow, idx, p.k64_pad);
+                        for (int r = 0; r < p.world; ++r) {
+                            *reinterpret_cast<uint2*>(p.gather_xq[r] + (size_t)grow * (p.hidden / 2) + idx * 8) = packed;
+                            p.gather_sf[r][sfo] = s8;
+                        }
                     }
                 }
+            }
+        }
+        if (p.gather_xq[0] && vec_push) {
+            // The quantised row leaves as 16-byte code stores and 4-byte scale stores (the four scales of 64 consecutive
+            // inputs are adjacent in the atom layout), consecutive threads on consecutive addresses of one peer, all peers
+            // in flight at once — not one 8-byte and one 1-byte store per block and peer in a serial loop.
+            __syncthreads();
+            const int nchunk = p.hidden / 32, nsf = p.hidden / 64, per_peer = nchunk + nsf;
+            for (int i = threadIdx.x; i < p.world * per_peer; i += blockDim.x) {
+                const int r = i / per_peer, j = i - r * per_peer;
+                if (j < nchunk)
+                    *reinterpret_cast<uint4*>(p.gather_xq[r] + (size_t)grow * (p.hidden / 2) + (size_t)j * 16) = s_codes[j];
+                else
+                    *reinterpret_cast<uint32_t*>(p.gather_sf[r] + sf_atom_offset(grow, (j - nchunk) * 4, p.k64_pad)) = s_sf4[j - nchunk];
             }
         }
     }
@@ -427,11 +451,103 @@ __global__ void rs_add_rmsnorm_ag_kernel(RsAgParams p) {
     }
 }
 
+// ---- vocabulary-sharded greedy pick ----------------------------------------------------------------
+// Each rank holds the logits of its vocabulary shard only.  Instead of gathering [rows, vocab] logits on
+// every rank, a rank finds the best (value, index) of its shard per row (arg-max kernel), packs it into an
+// order-preserving 64-bit key with the *global* token id, stores the key into every peer's table (one
+// 8-byte peer store per row and peer), publishes an epoch flag and, once all peers' flags have arrived,
+// takes the maximum over the `world` keys of each row.  Ties resolve to the lower global id, the same
+// answer as an arg-max over the gathered logits.  world * rows * 8 bytes cross NVLink instead of
+// rows * vocab * 2.  Tables alternate with the epoch parity, like the all-reduce buffers above.
+struct ArgmaxMergeParams {
+    const void* logits;                  // local shard [rows, vocab_local], row pitch `stride`
+    const int* local_idx;                // [rows] arg-max within the shard
+    unsigned long long* sym_keys[kMaxRanks];   // every rank's table [2][kMaxRanks][max_rows]
+    int* sym_flags[kMaxRanks];           // every rank's flags [2][kMaxRanks]
+    int* epoch;                          // local: completed calls
+    int* out;                            // [rows] global token ids
+    long long stride;
+    int rank, world, rows, max_rows, vocab_local, dtype;
+    int* status;
+};
+
+__global__ void argmax_merge_kernel(ArgmaxMergeParams p) {
+    __shared__ int s_ok;
+    pdl_prologue();
+    const int e = *p.epoch + 1;
+    const int par = e & 1;
+    const int row = threadIdx.x;
+    if (row < p.rows) {
+        const int li = p.local_idx[row];
+        float v;
+        if (p.dtype == 2) v = reinterpret_cast<const float*>(p.logits)[(size_t)row * p.stride + li];
+        else if (p.dtype == 1) v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.logits)[(size_t)row * p.stride + li]);
+        else v = __half2float(reinterpret_cast<const __half*>(p.logits)[(size_t)row * p.stride + li]);
+        uint32_t u = __float_as_uint(v);
+        u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+        const uint32_t gid = (uint32_t)(p.rank * p.vocab_local + li);
+        const unsigned long long key = ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - gid);
+        for (int r = 0; r < p.world; ++r) p.sym_keys[r][((size_t)par * kMaxRanks + p.rank) * p.max_rows + row] = key;
+    }
+    __threadfence_system();
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < p.world && threadIdx.x != p.rank) st_release_sys(p.sym_flags[threadIdx.x] + par * kMaxRanks + p.rank, e);
+    if (threadIdx.x < p.world && threadIdx.x != p.rank) {
+        if (!wait_flag_ge(p.sym_flags[p.rank] + par * kMaxRanks + threadIdx.x, e, p.status)) s_ok = 0;
+    }
+    __syncthreads();
+    if (row < p.rows) {
+        unsigned long long best = 0ull;
+        if (s_ok) {
+            for (int r = 0; r < p.world; ++r) {
+                const unsigned long long k = __ldcg(&p.sym_keys[p.rank][((size_t)par * kMaxRanks + r) * p.max_rows + row]);
+                best = k > best ? k : best;
+            }
+        }
+        p.out[row] = (int)(0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFull));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *p.epoch = e;
+}
+
 }  // namespace telb
 
 using namespace telb;
 
 extern "C" int telb_nvfp4_k64_pad(int k);
+
+// Global greedy token per row from vocabulary-sharded logits (see argmax_merge_kernel).  `local_idx` is the arg-max of
+// each row within this rank's shard; sym_keys / sym_flags hold `world` peer mappings of the symmetric tables
+// ([2][8][max_rows] keys, [2][8] flags, zero-initialised); rows <= max_rows <= 1024.
+extern "C" int telb_argmax_merge(const void* logits, long long stride, const int* local_idx, void* const* sym_keys, int* const* sym_flags,
+                                 int* epoch, int* out, int rank, int world, int rows, int max_rows, int vocab_local, int dtype,
+                                 int* status, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (world < 1 || world > kMaxRanks) return fail("telb_argmax_merge: world size must be in [1, 8]");
+    if (rows > max_rows || max_rows > 1024) return fail("telb_argmax_merge: rows <= max_rows <= 1024 is required");
+    if (dtype < 0 || dtype > 2) return fail("telb_argmax_merge: dtype must be 0 (fp16), 1 (bf16) or 2 (fp32)");
+    ArgmaxMergeParams p{};
+    p.logits = logits;
+    p.local_idx = local_idx;
+    for (int r = 0; r < world; ++r) {
+        p.sym_keys[r] = (unsigned long long*)sym_keys[r];
+        p.sym_flags[r] = sym_flags[r];
+    }
+    p.epoch = epoch;
+    p.out = out;
+    p.stride = stride;
+    p.rank = rank;
+    p.world = world;
+    p.rows = rows;
+    p.max_rows = max_rows;
+    p.vocab_local = vocab_local;
+    p.dtype = dtype;
+    p.status = status;
+    int threads = ((rows > world ? rows : world) + 31) / 32 * 32;
+    TELB_LAUNCH("argmax_merge_kernel", (argmax_merge_kernel), dim3(1), dim3(threads), 0, stream, p);
+    return 0;
+}
 
 // All-reduce(x) + residual → res_out; RMSNorm(res_out) * weight → y_out and/or NVFP4 (xq, sf).
 //   sym_partial / sym_flags: `world` device pointers each (peer mappings of the symmetric buffers);

@@ -267,6 +267,9 @@ using namespace telb;
 extern "C" int telb_gemm_skinny(int kind, const void* x, const void* x_sf, const void* w, const void* w_sf, void* out, int M,
                                 int N, int K, const float* alpha, const void* bias, const void* residual, int is_bf16,
                                 int* status, int force_ranks, cudaStream_t stream);
+extern "C" int telb_gemm_skinny_fused(int kind, const void* x, const void* x_sf, const void* w, const void* w_sf, void* out, int M,
+                                      int N, int K, const float* alpha, const void* bias, const void* residual, int is_bf16,
+                                      int* status, int force_ranks, const telb::TelbGemmFusion* fusion, cudaStream_t stream);
 
 // Number of 64-element K groups the scale buffers are padded to (whole 256-element stages).
 extern "C" int telb_nvfp4_k64_pad(int k) { return ((k + 255) / 256) * 4; }
@@ -319,8 +322,11 @@ static int gemm_nvfp4_impl(const void* xq, const void* x_sf, const void* wq, con
                            const TelbGemmFusion* fusion, cudaStream_t stream, const SwigluOut* sw = nullptr) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (K % 32) return fail("telb_gemm_nvfp4: K must be a multiple of 32");
-    if (fusion) mode = 1;         // the fused collectives are written for the large-M layout
     if (fusion && fusion->rs_world > 1 && residual) return fail("telb_gemm_nvfp4: reduce-scatter epilogue takes no residual");
+    // decode-size steps keep the swapped-operand kernel when a collective is fused in (it has the same epilogue / prologue)
+    if (fusion && M <= 128 && !sw && (fusion->rs_world <= 1 || N % 4 == 0))
+        return telb_gemm_skinny_fused(1, xq, x_sf, wq, w_sf, out, M, N, K, alpha, bias, residual, out_bf16, status, 0, fusion, stream);
+    if (fusion) mode = 1;         // otherwise the fused collectives run in the large-M layout
     if (mode == 0 && M <= 128)
         return telb_gemm_skinny(1, xq, x_sf, wq, w_sf, out, M, N, K, alpha, bias, residual, out_bf16, status, 0, stream);
     const bool swapped = mode == 2 || (mode == 0 && M <= 128);

@@ -14,6 +14,14 @@
 //     `griddepcontrol.wait` only before touching activations or writing outputs.
 // No TMA load here uses cluster multicast: every CTA fetches its own K-slice.
 //
+// Tensor-parallel fusion at decode size (both optional, same contract as the large-M kernels):
+//   * reduce-scatter epilogue: the output row of token t belongs to rank t / rows_per_rank and is stored straight
+//     into that rank's partial buffer over peer memory (256 contiguous bytes per warp and token), so the
+//     row-parallel projection needs no copy-in, no pull and only 1/world of a one-shot all-reduce's bytes;
+//   * all-gather prologue: the activation rows were pushed into this GPU's memory by their owner ranks; the
+//     producer warp waits (bounded) for the owners' flags after `griddepcontrol.wait`, while the weight
+//     tiles of the first ring pass are already in flight.
+//
 // Reference counterparts: TensorRT decode tactics; kernelSrcs/nvfp4A16BlackwellGemv (SM110-only
 // CUDA-core GEMV) and `gemm_blackwell_nvfp4_ws_*_tn64` at TP=2.
 #include "gemm_common.cuh"
@@ -32,7 +40,24 @@ struct SkinnyParams {
     const uint8_t* sf_x;
     int sf_k64;
     int* status;
+    // reduce-scatter epilogue (rs_world > 1): token t → rs_out[t / rs_rows_per_rank], row rs_rank * rs_rows_per_rank + t % rs_rows_per_rank
+    void* rs_out[8];
+    int rs_world, rs_rank, rs_rows_per_rank;
+    // all-gather prologue (ag_flags != null): rank o pushed tokens [o * ag_rows_per_rank, ...) and then set ag_flags[o] = *ag_epoch
+    const int* ag_flags;
+    const int* ag_epoch;
+    int ag_world, ag_rows_per_rank;
 };
+
+// Where the four features starting at `feat` of token `tok` are stored: the local output, or the owner rank's partial buffer.
+template <typename T>
+__device__ __forceinline__ T* skinny_out_ptr(const SkinnyParams& p, int tok, int feat) {
+    if (p.rs_world > 1) {
+        const int d = tok / p.rs_rows_per_rank;
+        return reinterpret_cast<T*>(p.rs_out[d]) + ((size_t)p.rs_rank * p.rs_rows_per_rank + (tok - d * p.rs_rows_per_rank)) * p.n_out + feat;
+    }
+    return reinterpret_cast<T*>(p.out) + (size_t)tok * p.n_out + feat;
+}
 
 __device__ __forceinline__ void cluster_sync_all() {
     __syncwarp();
@@ -131,7 +156,27 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
                               2048, &full_bar[j]);
             }
             pdl_wait();
-            for (int j = 0; j < pre; ++j) {
+            bool x_ready = true;
+            if (p.ag_flags) {
+                // the rows of every owner rank below m_tok must have arrived (peers wrote them with plain stores; the
+                // tiles are read by TMA / bulk copies, hence the proxy fence)
+                const int e = *p.ag_epoch;
+                const int o1 = min((p.m_tok - 1) / p.ag_rows_per_rank, p.ag_world - 1);
+                for (int o = 0; o <= o1 && x_ready; ++o) {
+                    const uint64_t t0 = global_timer_ns();
+                    uint32_t it = 0;
+                    while (ld_acquire_sys_s32(p.ag_flags + o) - e < 0) {
+                        if ((++it & 63u) == 0 && (*abort_flag || global_timer_ns() - t0 > kWaitLimitNs)) {
+                            *abort_flag = 1;
+                            if (p.status) atomicCAS(p.status, kStatusOk, kStatusPeerTimeout);
+                            x_ready = false;
+                            break;
+                        }
+                    }
+                }
+                asm volatile("fence.proxy.async;" ::: "memory");
+            }
+            for (int j = 0; j < pre && x_ready; ++j) {
                 uint8_t* sx = smem + j * Cfg::kStage + Cfg::kWTile;
                 tma_load_2d(sx, &tma_x, &full_bar[j], (kb0 + j) * (KIND == 1 ? 128 : 64), 0);
                 if constexpr (KIND == 1)
@@ -139,7 +184,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
             }
             int stage = pre % STAGES;
             uint32_t phase = pre >= STAGES ? 1 : 0;
-            for (int j = pre; j < nkb; ++j) {
+            for (int j = pre; j < nkb && x_ready; ++j) {
                 if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) break;
                 uint8_t* sw = smem + stage * Cfg::kStage;
                 mbar_expect_tx(&full_bar[stage], Cfg::kStage);
@@ -219,8 +264,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
     T* outp = reinterpret_cast<T*>(p.out);
     const T* resp = reinterpret_cast<const T*>(p.residual);
+    const bool scatter = p.rs_world > 1;          // host side guarantees n_out % 4 == 0 and no residual
 
-    if (p.ranks == 1 && p.m_tok > 8 && (p.n_out & 3) == 0) {
+    if (p.ranks == 1 && (p.m_tok > 8 || scatter) && (p.n_out & 3) == 0) {
         // Many token columns: a lane owns one feature, so direct stores would be 2-byte pieces 2 * n_out apart.  The
         // tile is transposed through shared memory instead (the stage ring is free once the MMAs have completed) and
         // leaves as 8-byte stores, 256 contiguous bytes per token and warp.
@@ -257,8 +303,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
                 uint2 u;
                 u.x = Cvt<T>::pack2(v[0], v[1]);
                 u.y = Cvt<T>::pack2(v[2], v[3]);
-                *reinterpret_cast<uint2*>(outp + o) = u;
+                *reinterpret_cast<uint2*>(skinny_out_ptr<T>(p, c, f0)) = u;
             }
+            // peer stores are performed system-wide before this thread moves on, so the "GEMM finished" flag that
+            // the next kernel publishes can never overtake them
+            if (scatter) __threadfence_system();
         }
     } else if (p.ranks == 1) {
         if (is_epi) {
@@ -339,13 +388,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
                     uint2 u;
                     u.x = Cvt<T>::pack2(v[0], v[1]);
                     u.y = Cvt<T>::pack2(v[2], v[3]);
-                    *reinterpret_cast<uint2*>(outp + o) = u;
+                    *reinterpret_cast<uint2*>(skinny_out_ptr<T>(p, c, f0)) = u;
                 } else {
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
                         if (f0 + i < p.n_out) outp[o + i] = Cvt<T>::from_f(v[i]);
                 }
             }
+            if (scatter) __threadfence_system();
         }
         cluster_sync_all();         // peers may still be reading this CTA's partial tile
     }
@@ -446,11 +496,18 @@ using namespace telb;
 extern "C" int telb_nvfp4_k64_pad(int k);
 
 // kind 0: x, w are 16-bit [M,K], [N,K].  kind 1: packed E2M1 [M,K/2], [N,K/2] with atom-layout scales.
-extern "C" int telb_gemm_skinny(int kind, const void* x, const void* x_sf, const void* w, const void* w_sf, void* out, int M,
-                                int N, int K, const float* alpha, const void* bias, const void* residual, int is_bf16,
-                                int* status, int force_ranks, cudaStream_t stream) {
+// `fusion` (may be null) adds the reduce-scatter epilogue and / or the all-gather prologue described at the top.
+extern "C" int telb_gemm_skinny_fused(int kind, const void* x, const void* x_sf, const void* w, const void* w_sf, void* out, int M,
+                                      int N, int K, const float* alpha, const void* bias, const void* residual, int is_bf16,
+                                      int* status, int force_ranks, const TelbGemmFusion* fusion, cudaStream_t stream) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (M > 128) return fail("telb_gemm_skinny: M must be <= 128");
+    if (fusion && fusion->rs_world > 1) {
+        if (residual) return fail("telb_gemm_skinny: reduce-scatter epilogue takes no residual");
+        if (N % 4) return fail("telb_gemm_skinny: reduce-scatter epilogue needs N % 4 == 0");
+        if (fusion->rs_world > 8 || fusion->rs_rows_per_rank <= 0 || (long long)fusion->rs_rows_per_rank * fusion->rs_world < M)
+            return fail("telb_gemm_skinny: reduce-scatter rows_per_rank * world must cover M (world <= 8)");
+    }
     const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
     SkinnyParams p{};
     p.n_out = N;
@@ -462,6 +519,17 @@ extern "C" int telb_gemm_skinny(int kind, const void* x, const void* x_sf, const
     p.residual = residual;
     p.out_bf16 = is_bf16;
     p.status = status;
+    if (fusion) {
+        for (int i = 0; i < 8; ++i) p.rs_out[i] = fusion->rs_out[i];
+        p.rs_world = fusion->rs_world;
+        p.rs_rank = fusion->rs_rank;
+        p.rs_rows_per_rank = fusion->rs_rows_per_rank;
+        p.ag_flags = fusion->ag_flags;
+        p.ag_epoch = fusion->ag_epoch;
+        p.ag_world = fusion->ag_world;
+        p.ag_rows_per_rank = fusion->ag_rows_per_rank;
+        if (p.ag_flags && (p.ag_world < 1 || p.ag_rows_per_rank <= 0)) return fail("telb_gemm_skinny: bad all-gather description");
+    }
     CUtensorMap tw, tx;
     if (kind == 1) {
         if (K % 32) return fail("telb_gemm_skinny: NVFP4 needs K % 32 == 0");
@@ -484,4 +552,10 @@ extern "C" int telb_gemm_skinny(int kind, const void* x, const void* x_sf, const
     p.kb_per_rank = (p.kb_total + ranks - 1) / ranks;
     p.ranks = (p.kb_total + p.kb_per_rank - 1) / p.kb_per_rank;
     return kind == 1 ? dispatch_skinny<1>(tw, tx, p, bn, stream) : dispatch_skinny<0>(tw, tx, p, bn, stream);
+}
+
+extern "C" int telb_gemm_skinny(int kind, const void* x, const void* x_sf, const void* w, const void* w_sf, void* out, int M,
+                                int N, int K, const float* alpha, const void* bias, const void* residual, int is_bf16,
+                                int* status, int force_ranks, cudaStream_t stream) {
+    return telb_gemm_skinny_fused(kind, x, x_sf, w, w_sf, out, M, N, K, alpha, bias, residual, is_bf16, status, force_ranks, nullptr, stream);
 }

@@ -179,6 +179,9 @@ using namespace telb;
 extern "C" int telb_gemm_skinny(int kind, const void* x, const void* x_sf, const void* w, const void* w_sf, void* out, int M,
                                 int N, int K, const float* alpha, const void* bias, const void* residual, int is_bf16,
                                 int* status, int force_ranks, cudaStream_t stream);
+extern "C" int telb_gemm_skinny_fused(int kind, const void* x, const void* x_sf, const void* w, const void* w_sf, void* out, int M,
+                                      int N, int K, const float* alpha, const void* bias, const void* residual, int is_bf16,
+                                      int* status, int force_ranks, const telb::TelbGemmFusion* fusion, cudaStream_t stream);
 
 extern "C" const char* telb_last_error() { return g_last_error; }
 
@@ -191,10 +194,13 @@ static int gemm_f16_impl(const void* x, const void* w, void* out, int M, int N, 
                          int* counters, int n_counters, int* status, int mode, int force_splits,
                          const TelbGemmFusion* fusion, cudaStream_t stream) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
-    if (fusion) mode = 1;         // the fused collectives are written for the large-M layout
     if (fusion && fusion->rs_world > 1 && residual) return fail("telb_gemm_f16: reduce-scatter epilogue takes no residual");
     if (K % 8) return fail("telb_gemm_f16: K must be a multiple of 8");
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return fail("telb_gemm_f16: operands must be 16-byte aligned");
+    // decode-size steps keep the swapped-operand kernel when a collective is fused in (it has the same epilogue / prologue)
+    if (fusion && M <= 128 && (fusion->rs_world <= 1 || N % 4 == 0))
+        return telb_gemm_skinny_fused(0, x, nullptr, w, nullptr, out, M, N, K, alpha, bias, residual, is_bf16, status, 0, fusion, stream);
+    if (fusion) mode = 1;         // otherwise the fused collectives run in the large-M layout
     if (mode == 0 && M <= 128)
         return telb_gemm_skinny(0, x, nullptr, w, nullptr, out, M, N, K, alpha, bias, residual, is_bf16, status, 0, stream);
     const CUtensorMapDataType dt = is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;

@@ -217,6 +217,20 @@ class CausalLM(nn.Module):
         x = self.hidden_states(ids, meta, kv_cache, inputs_embeds)
         return self.logits_from_hidden(x, meta)
 
+    def greedy_tokens(self, ids: torch.Tensor, meta: StepMeta, kv_cache: torch.Tensor) -> torch.Tensor:
+        """Greedy next token of every ``meta.logits_idx`` row (int32 ids of the model's vocabulary).
+
+        With a vocabulary-sharded head each rank reduces its own shard to one (value, id) candidate per row and only
+        those candidates cross the link (``comm.argmax_sharded``): ``world x rows x 8`` bytes instead of the
+        ``rows x vocab`` logits of a full gather.  The result equals ``argmax`` of the gathered logits, ties included."""
+        x = self.hidden_states(ids, meta, kv_cache)
+        sharded = (self.lm_head.tp_mode == TPMode.COL and self.comm.world_size > 1 and hasattr(self.comm, "argmax_sharded")
+                   and type(self).logits_from_hidden is CausalLM.logits_from_hidden)
+        if not sharded:
+            return ops.argmax(self.logits_from_hidden(x, meta))
+        rows = x if meta.logits_idx.numel() == x.shape[0] else x.index_select(0, meta.logits_idx.long())
+        return self.comm.argmax_sharded(self.lm_head(rows))
+
     def finalize(self):
         for m in self.modules():
             if hasattr(m, "finalize") and m is not self:

@@ -108,5 +108,23 @@ class TorchComm(LocalComm):
     def add_rmsnorm(self, x_partial, residual, weight, eps, quant_scale=None, defer_gather=False):
         return ops.add_rmsnorm(self.all_reduce(x_partial), residual, weight, eps, quant_scale)
 
+    def argmax_sharded(self, logits_local: torch.Tensor) -> torch.Tensor:
+        """Greedy token per row from vocabulary-sharded logits ``[rows, vocab / world]`` (rank r holds columns
+        ``[r * vocab / world, ...)``): every rank contributes its best (value, global id) per row, the largest value
+        wins and the lowest id among equals — the arg-max of the gathered logits without gathering them."""
+        vloc = logits_local.shape[1]
+        lf = logits_local.float()
+        vals = lf.max(dim=-1).values
+        # the first maximum of the shard (torch.max does not promise which of several equal maxima it reports)
+        ids = ((lf == vals[:, None]).to(torch.int32).argmax(dim=-1) + self.rank * vloc).to(torch.int64)
+        parts_v = [torch.empty_like(vals) for _ in range(self.world_size)]
+        parts_i = [torch.empty_like(ids) for _ in range(self.world_size)]
+        self.dist.all_gather(parts_v, vals.contiguous(), group=self.group)
+        self.dist.all_gather(parts_i, ids.contiguous(), group=self.group)
+        v, i = torch.stack(parts_v), torch.stack(parts_i)            # [world, rows]
+        best = v.max(dim=0).values
+        masked = torch.where(v == best[None, :], i, torch.full_like(i, torch.iinfo(torch.int64).max))
+        return masked.min(dim=0).values.to(torch.int32)
+
     def barrier(self):
         self.dist.barrier(group=self.group)

@@ -127,9 +127,44 @@ class _SymState:
         dist.barrier(group)
 
 
+class _ArgmaxState:
+    """Symmetric candidate tables of the vocabulary-sharded greedy pick: ``[2][8][MAX_ARGMAX_ROWS]`` 64-bit keys and
+    ``[2][8]`` epoch flags per rank."""
+
+    def __init__(self, device, group):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        gname = group.group_name if group is not None else dist.group.WORLD.group_name
+        world = dist.get_world_size(group)
+        self.keys = symm_mem.empty(2 * 8 * MAX_ARGMAX_ROWS, dtype=torch.int64, device=device)
+        self.flags = symm_mem.empty(16, dtype=torch.int32, device=device)
+        self.keys.zero_()
+        self.flags.zero_()
+        hk, hf = symm_mem.rendezvous(self.keys, gname), symm_mem.rendezvous(self.flags, gname)
+        self._handles = (hk, hf)
+        self.c_keys = (ctypes.c_void_p * world)(*[int(p) for p in hk.buffer_ptrs])
+        self.c_flags = (ctypes.c_void_p * world)(*[int(p) for p in hf.buffer_ptrs])
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+
+MAX_ARGMAX_ROWS = 1024
+
+
+def _default_rs_min_rows() -> int:
+    """Smallest step (rows) that takes the reduce-scatter → norm → all-gather path instead of the one-shot
+    all-reduce.  The one-shot form moves ``(world - 1) x rows x hidden`` 16-bit values into every GPU, the sharded
+    form 1/world of that plus the quantised rows; below a few rows per rank only latency counts and one hop wins."""
+    import os
+    return int(os.environ.get("TELB_RS_MIN_ROWS", "0"))
+
+
 class FusedComm(TorchComm):
-    def __init__(self, device=None, group=None, rs_max_tokens: int = 8192, rs_min_rows: int = MAX_ROWS + 1):
+    def __init__(self, device=None, group=None, rs_max_tokens: int = 8192, rs_min_rows: Optional[int] = None):
         super().__init__(group)
+        if rs_min_rows is None:
+            rs_min_rows = _default_rs_min_rows() or max(16, 2 * self.world_size)
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         self._sym: Dict[Tuple[int, torch.dtype], _SymState] = {}
         self._rs: Dict[Tuple[int, torch.dtype], _RsState] = {}
@@ -138,10 +173,12 @@ class FusedComm(TorchComm):
         self.rs_min_rows = rs_min_rows          # below this the one-shot all-reduce is faster
         self.rs_enabled = True
         self.rs_single_rank = False             # tests: run the fused path on one rank too
+        self.force_nccl = False                 # benchmarks: every entry falls back to the NCCL composition
+        self._argmax: Optional[_ArgmaxState] = None
 
     # ---- prefill path: GEMM → reduce-scatter epilogue, norm, all-gather → GEMM prologue -----------
     def use_rs(self, rows: int) -> bool:
-        return (self.rs_enabled and (self.world_size > 1 or self.rs_single_rank)
+        return (self.rs_enabled and not self.force_nccl and (self.world_size > 1 or self.rs_single_rank)
                 and self.rs_min_rows <= rows <= self.rs_max_tokens)
 
     def _rs_state(self, hidden: int, dtype: torch.dtype) -> _RsState:
@@ -290,7 +327,7 @@ class FusedComm(TorchComm):
         if isinstance(x_partial, RsPartial):
             return self._rs_add_rmsnorm(x_partial, residual, weight, eps, quant_scale, defer_gather)
         rows, hidden = x_partial.shape
-        if not x_partial.is_cuda or rows > MAX_ROWS or hidden % 16:
+        if not x_partial.is_cuda or rows > MAX_ROWS or hidden % 16 or self.force_nccl:
             return super().add_rmsnorm(x_partial, residual, weight, eps, quant_scale)
         cu = ops.cuda_ops()
         st = self._state(hidden, x_partial.dtype)
@@ -314,3 +351,25 @@ class FusedComm(TorchComm):
         if quant_scale is not None:
             return cu.QuantActs(xq, sf, (rows, hidden), x_partial.dtype), res_out
         return y, res_out
+
+    def prepare_argmax(self) -> None:
+        """Allocate and exchange the candidate tables up front (collective; call before capture)."""
+        if self._argmax is None:
+            self._argmax = _ArgmaxState(self.device, self.group)
+
+    def argmax_sharded(self, logits_local: torch.Tensor) -> torch.Tensor:
+        rows, vloc = logits_local.shape
+        if not logits_local.is_cuda or rows > MAX_ARGMAX_ROWS or self.force_nccl or logits_local.stride(1) != 1:
+            return super().argmax_sharded(logits_local)
+        cu = ops.cuda_ops()
+        self.prepare_argmax()
+        st = self._argmax
+        local = cu.argmax(logits_local)
+        out = torch.empty(rows, dtype=torch.int32, device=logits_local.device)
+        ws = cu.Workspace.get(logits_local.device)
+        dt = 2 if logits_local.dtype == torch.float32 else cu._is_bf16(logits_local)
+        cu._check(cu.lib().telb_argmax_merge(
+            cu._p(logits_local), ctypes.c_longlong(logits_local.stride(0)), cu._p(local), st.c_keys, st.c_flags, cu._p(st.epoch), cu._p(out),
+            ctypes.c_int(self.rank), ctypes.c_int(self.world_size), ctypes.c_int(rows), ctypes.c_int(MAX_ARGMAX_ROWS), ctypes.c_int(vloc),
+            ctypes.c_int(dt), cu._p(ws.status), cu._stream()), "argmax_merge")
+        return out

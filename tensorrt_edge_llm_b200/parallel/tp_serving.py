@@ -82,6 +82,13 @@ def serve_follower(runner, mirror: StepMirror, enable_prefix_cache: bool = False
             _, seats, token_lists = op
             runner.step(list(seats), [list(t) for t in token_lists])
             steps += 1
+        elif kind == "decode_graph":
+            _, seats, tokens = op
+            if runner.can_graph_step(list(seats)):
+                runner.decode_step_graph(list(seats), list(tokens))
+            else:                              # CPU ranks (tests): the same step, eagerly
+                runner.step(list(seats), [[int(t)] for t in tokens])
+            steps += 1
         elif kind == "step_embeds":
             # a step that carries a multimodal prompt chunk: rank 0 ships the embedding rows (host tensors) with the plan
             _, seats, embeds, pos3, deepstack, deltas = op

@@ -92,6 +92,7 @@ class KVCacheManager:
         self.table = torch.full((max_seats, max_pages_per_seq), -1, dtype=torch.int32)   # host truth
         self.lengths = [0] * max_seats
         self._pages: Dict[int, List[int]] = {}
+        self.table_version = 0       # bumped whenever a row of `table` changes (device copies compare it to know they are stale)
         # Page accounting lives in the native table when the runtime module is built; the Python
         # structures above mirror it so callers can read `lengths` / `table` directly.
         try:
@@ -126,6 +127,7 @@ class KVCacheManager:
                 new = self.alloc.alloc(need - len(have))
             self.table[seat, len(have):need] = torch.tensor(new, dtype=torch.int32)
             have.extend(new)
+            self.table_version += 1
 
     def adopt_prefix(self, seat: int, pages: Sequence[int], tokens: int) -> None:
         """Share already-filled pages (prefix reuse); the seat must be empty."""
@@ -137,6 +139,7 @@ class KVCacheManager:
         self._pages[seat] = list(pages)
         self.table[seat, :len(pages)] = torch.tensor(list(pages), dtype=torch.int32)
         self.lengths[seat] = tokens
+        self.table_version += 1
 
     def commit(self, seat: int, new_tokens: int) -> None:
         self.lengths[seat] += new_tokens
@@ -170,6 +173,7 @@ class KVCacheManager:
         for i in range(upto):
             have[i] = -1
         self.table[seat, :upto] = -1
+        self.table_version += 1
 
     def live_pages(self, seat: int) -> int:
         return sum(pg >= 0 for pg in self._pages.get(seat, []))
@@ -189,6 +193,7 @@ class KVCacheManager:
             self.alloc.release([pg for pg in pages if pg >= 0])
         self.table[seat].fill_(-1)
         self.lengths[seat] = 0
+        self.table_version += 1
 
     def pages_of(self, seat: int) -> List[int]:
         return list(self._pages.get(seat, []))

@@ -235,6 +235,14 @@ class ModelRunner:
         """Greedy token per row, as ids of the full vocabulary."""
         return self.to_full_vocab(ops.argmax(logits))
 
+    def greedy_step(self, ids: torch.Tensor, meta: StepMeta) -> torch.Tensor:
+        """One model step that ends in the greedy token of every logits row.  Models with a vocabulary-sharded head
+        exchange per-shard candidates instead of gathering the logits (``CausalLM.greedy_tokens``)."""
+        g = getattr(self.model, "greedy_tokens", None)
+        if g is None:
+            return self.pick(self.model(ids, meta, self.cache))
+        return self.to_full_vocab(g(ids, meta, self.cache))
+
     @torch.no_grad()
     def decode_sampled(self, seats, first_tokens, steps, sp: SamplingParams) -> torch.Tensor:
         toks = first_tokens.to(torch.int32)
@@ -246,6 +254,44 @@ class ModelRunner:
         return torch.stack(cols, dim=1)
 
     # ---- decode ----------------------------------------------------------------------------
+    def can_graph_step(self, seats: Sequence[int]) -> bool:
+        """Whether one all-resident greedy decode step of these seats may run from the captured graph."""
+        return (self.use_cuda_graphs and not self.kv.bounded_swa and len(seats) > 0
+                and not any(self.rope_delta.get(s) for s in seats))
+
+    @torch.no_grad()
+    def decode_step_graph(self, seats: Sequence[int], tokens: Sequence[int]) -> List[int]:
+        """One all-resident greedy decode step from the captured graph of this batch size: feeds ``tokens[i]`` to seat
+        ``seats[i]``, commits one KV position per seat and returns the next tokens (one device → host read).
+
+        This is the in-flight-batching form of ``decode_greedy``: the request engine calls it step by step.  While the
+        same seats decode back to back and feed the tokens the graph itself produced, the step state (lengths,
+        positions, page-table rows, token feedback) already sits on the device and the step is a replay plus the read;
+        any other step (a new or departed sequence, an eager step in between, a grown page table) reloads the state first.
+        Reference: the all-resident decode steps of ``docs/source/developer_guide/software-design/in-flight-batching.md:351-372``
+        and ``cpp/runtime/decoding/vanillaDecoder.cpp:446-491`` replay a captured graph the same way."""
+        n = len(seats)
+        nb = self.graph_bucket(n)
+        g = self._graphs.get(nb)
+        if g is None:
+            g = self._graphs[nb] = _DecodeGraph(self, nb)
+        seats, tokens = list(seats), [int(t) for t in tokens]
+        # rows up to the bucket size repeat the last real row (same seat, same token, same position): they recompute and
+        # rewrite exactly what that row writes, and their outputs are dropped
+        seats += [seats[-1]] * (nb - n)
+        tokens += [tokens[-1]] * (nb - n)
+        with prof.time_stage(prof.VANILLA_DECODING, batch=n, tokens=n):
+            return g.step(seats, tokens, n)
+
+    def graph_bucket(self, n: int) -> int:
+        """Batch size of the graph that serves ``n`` decode rows.  A serving run sees every batch size between 1 and the
+        seat count; one capture per size would be dozens of captures, so sizes above 8 share the graph of the next
+        multiple of 8 (the extra rows repeat the last row).  Models with recurrent layers keep exact sizes: a repeated
+        row would advance that sequence's state twice."""
+        if n <= 8 or getattr(self.model.cfg, "is_hybrid", False):
+            return n
+        return min((n + 7) // 8 * 8, max(self.kv.max_seats, n))
+
     @torch.no_grad()
     def decode_greedy(self, seats: Sequence[int], first_tokens: torch.Tensor, steps: int) -> torch.Tensor:
         """Greedy decode ``steps`` tokens for every seat starting from ``first_tokens [N]``;
@@ -303,11 +349,19 @@ class _DecodeGraph:
         self.step_idx = torch.zeros(1, dtype=torch.int64, device=dev)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._pin = torch.empty(n * (kv.max_pages_per_seq + 3), dtype=torch.int32, pin_memory=True)
+        # stepped use (in-flight batching): what the device-side state currently describes, as the host knows it
+        self._tok_pin = torch.empty(n, dtype=torch.int32, pin_memory=True)
+        self._tok_event = torch.cuda.Event()
+        self._key: Optional[tuple] = None
+        self._host_len: List[int] = []
+        self._last_tokens: List[int] = []
+        self._table_version = -1
+        self._ring_used = 0
+        self.reloads = 0              # times a step had to rebuild the device state (diagnostics / tests)
 
     def _body(self):
         m = self.meta
-        logits = self.r.model(self.ids, m, self.r.cache)
-        tok = self.r.pick(logits)
+        tok = self.r.greedy_step(self.ids, m)
         self.ids.copy_(tok)
         self.out.index_copy_(0, self.step_idx, tok.unsqueeze(0))
         self.step_idx.add_(1)
@@ -330,8 +384,42 @@ class _DecodeGraph:
         self.meta.page_table.copy_(devbuf[3 * n:].view(n, mp))
         self.step_idx.zero_()
 
+    def step(self, seats: List[int], tokens: List[int], n_real: Optional[int] = None) -> List[int]:
+        kv = self.r.kv
+        n_real = len(seats) if n_real is None else n_real
+        lens = [kv.lengths[s] for s in seats]
+        for s, ln in zip(seats, lens):
+            if kv.capacity_tokens(s) < ln + 1:
+                kv.reserve(s, ln + 1)                      # bumps kv.table_version: the state below is rebuilt
+        stale = (self.graph is None or self._key != tuple(seats) or self._host_len != lens or self._last_tokens != tokens
+                 or self._table_version != kv.table_version or self._ring_used >= self.MAX_STEPS - 1)
+        if stale:
+            first = torch.tensor(tokens, dtype=torch.int32)
+            self._load_state(seats, first)
+            self._ensure_graph(seats, first)
+            self._key, self._table_version, self._ring_used = tuple(seats), kv.table_version, 0
+            self.reloads += 1
+        from ..ops import cuda as _cu
+        self.graph.replay()
+        _cu.LAUNCHES += self.launches_per_replay
+        self._tok_pin.copy_(self.ids, non_blocking=True)
+        self._tok_event.record()
+        self._tok_event.synchronize()
+        out = self._tok_pin.tolist()
+        self._ring_used += 1
+        self._host_len = [ln + 1 for ln in lens]
+        self._last_tokens = out
+        for s in seats[:n_real]:
+            kv.commit(s, 1)
+        return out[:n_real]
+
+    def _ensure_graph(self, seats, first_tokens):
+        if self.graph is None:
+            self.run(seats, first_tokens, 0)
+
     def run(self, seats, first_tokens, steps):
         assert steps <= self.MAX_STEPS
+        self._key = None                  # a whole run leaves the stepped bookkeeping behind
         self._load_state(seats, first_tokens)
         if self.graph is None:
             # warm up once eagerly (allocator, lazy kernels), restore state, then capture
@@ -344,7 +432,8 @@ class _DecodeGraph:
             from ..ops import cuda as _cu
             before = _cu.LAUNCHES
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            # thread-local capture mode: other threads of a server (media encoders, tokenisation) may call into CUDA meanwhile
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
                 self._body()
             self.graph = g
             self.launches_per_replay = _cu.LAUNCHES - before

@@ -74,6 +74,7 @@ class ModelSession(rt.RuntimeSession):
         self.max_snapshots = max_snapshots
         self.snapshot_hits = 0
         self.jump_forward_tokens = 0       # tokens appended because a grammar left no choice (no forward pass of their own)
+        self.graph_steps = 0               # all-resident decode steps that replayed a captured graph
         # multimodal prompts wait here between `register_embeds` (caller's thread) and admission (engine thread)
         self.mm_store: Dict[int, dict] = {}
         self._mm_next = 1
@@ -326,7 +327,16 @@ class ModelSession(rt.RuntimeSession):
                 segs.append((r0, r0 + len(toks), self.seqs[slot].req.lora_name or None))
                 r0 += len(toks)
             lora.set_segments(segs)
-        if any(s.kind == rt.WorkKind.Context and self.seqs[s.slot].mm is not None for s in seqs):
+        graph_tokens = None
+        if self._graph_step_ok(seqs, seats, token_lists):
+            # every row is a plain greedy decode row: the step replays the captured graph of this batch size, and while the
+            # same sequences keep decoding the step state never leaves the device (ModelRunner.decode_step_graph)
+            if self.mirror is not None:
+                self.mirror.send(("decode_graph", seats, [t[0] for t in token_lists]))
+            graph_tokens = self.runner.decode_step_graph(seats, [t[0] for t in token_lists])
+            self.graph_steps += 1
+            logits = None
+        elif any(s.kind == rt.WorkKind.Context and self.seqs[s.slot].mm is not None for s in seqs):
             logits = self._step_with_embeds(seqs, seats, token_lists)          # mirrors itself (rows travel with the plan)
         else:
             if self.mirror is not None:
@@ -336,13 +346,16 @@ class ModelSession(rt.RuntimeSession):
         out = rt.StepResult()
         deltas = []
         if rows:
-            sel = logits[rows] if len(rows) != logits.shape[0] else logits
             row_seqs = [self.seqs[seats[i]] for i in rows]
             states = [q.row_state for q in row_seqs]
             special = any(st is not None for st in states)
-            if special:
-                sel = lp.process(sel, states)
-            new = self._sample(sel, row_seqs)
+            if graph_tokens is not None:
+                new = graph_tokens
+            else:
+                sel = logits[rows] if len(rows) != logits.shape[0] else logits
+                if special:
+                    sel = lp.process(sel, states)
+                new = self._sample(sel, row_seqs)
             if special:
                 reports = lp.logprobs(sel, new, states)
                 constraint_done = lp.advance(states, new)
@@ -391,6 +404,19 @@ class ModelSession(rt.RuntimeSession):
                         self.prefix.insert(list(q.req.prompt_ids), len(q.req.prompt_ids), self.kv.pages_of(s.slot), seed)
         out.deltas = deltas
         return out
+
+    def _graph_step_ok(self, seqs, seats, token_lists) -> bool:
+        """A step may replay the decode graph when all of its rows are ordinary greedy decode rows: no prompt chunk, no
+        multi-token row (jump-forward), no logits processing (bias, constraint, log-probabilities), no adapter routing, no
+        multimodal position offset, sampling off.  Everything else runs the eager ragged step."""
+        if not self.runner.can_graph_step(seats) or getattr(self.runner, "lora", None) is not None:
+            return False
+        for s, toks in zip(seqs, token_lists):
+            q = self.seqs[s.slot]
+            if (s.kind == rt.WorkKind.Context or len(toks) != 1 or q.row_state is not None or q.mm is not None
+                    or q.req.temperature >= 1e-3):
+                return False
+        return True
 
     def _step_with_embeds(self, seqs, seats, token_lists) -> torch.Tensor:
         """A step that holds a prompt chunk of a multimodal request: every row is fed as an embedding row — media rows from

@@ -43,6 +43,22 @@ def main():
 
     ref_logits, ref_toks = run(None, None)
     comm = make_comm(kind, dev)
+    # vocabulary-sharded greedy pick: candidates per shard instead of gathered logits, ties across shards → lowest id
+    g = torch.Generator().manual_seed(11)
+    full = torch.randn(7, 40 * world, generator=g)
+    full[0, 3] = full[0, 40 * world - 1] = 9.0
+    full[1, 40 * world - 2] = 8.0
+    full[2, 41 % (40 * world)] = full[2, 39] = 7.5
+    want_ids = (full == full.max(-1, keepdim=True).values).to(torch.int32).argmax(-1).to(torch.int32)
+    for dt in ((torch.float32, torch.bfloat16) if backend == "nccl" else (torch.float32,)):
+        shard = full.to(dt)[:, rank * 40:(rank + 1) * 40].contiguous().to(dev)
+        for _ in range(3):                   # epochs advance, tables alternate
+            got_ids = comm.argmax_sharded(shard).cpu()
+        want_dt = (full.to(dt).float() == full.to(dt).float().max(-1, keepdim=True).values).to(torch.int32).argmax(-1).to(torch.int32)
+        if not torch.equal(got_ids, want_dt):
+            print(f"rank {rank}: sharded arg-max {got_ids.tolist()} != {want_dt.tolist()} ({dt})", flush=True)
+            sys.exit(1)
+    del want_ids
     mapping = Mapping(tp_size=world, tp_rank=rank, ep_size=world if expert_parallel else 1, ep_rank=rank if expert_parallel else 0)
     tp_logits, tp_toks = run(mapping, comm)
     err = (tp_logits - ref_logits).abs().max().item()

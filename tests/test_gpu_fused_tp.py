@@ -29,8 +29,9 @@ def _table(tensors, offset=0):
 
 
 @pytest.mark.parametrize("quant", [False, True])
-@pytest.mark.parametrize("m", [300, 1024])
+@pytest.mark.parametrize("m", [24, 64, 300, 1024])
 def test_rs_norm_ag_two_emulated_ranks(cu, quant, m):
+    # m <= 128 runs the decode-size (swapped-operand, cluster split-K) GEMM with the same epilogue / prologue
     g = torch.Generator(device="cuda").manual_seed(m)
     world, h, ks, n2 = 2, 512, 256, 768
     rpr = (m + world - 1) // world
@@ -92,7 +93,7 @@ def test_rs_norm_ag_two_emulated_ranks(cu, quant, m):
         alpha = (w2gs.cuda() * qscale).expand(n2).contiguous()
         acts = cu.QuantActs(gxq[0], gsf[0], (m, h), torch.bfloat16)
         got = cu.gemm_fused(acts, w2q.cuda(), f, w_sf=w2_atoms, alpha=alpha)
-        plain = cu.gemm_nvfp4(gxq[0], gsf[0], w2q.cuda(), w2_atoms, alpha, torch.bfloat16, mode=1)
+        plain = cu.gemm_nvfp4(gxq[0], gsf[0], w2q.cuda(), w2_atoms, alpha, torch.bfloat16, mode=1 if m > 128 else 0)
         assert torch.equal(got, plain)
         y_dq = ref.nvfp4_act_qdq(want_y.float(), qscale)
         w_dq = ref.nvfp4_dequantize(w2q.cuda(), w2sf.cuda(), w2gs.cuda())
@@ -101,7 +102,7 @@ def test_rs_norm_ag_two_emulated_ranks(cu, quant, m):
         assert torch.equal(gy[0], gy[1])
         assert _rel_err(gy[0], want_y) < 8e-3
         got = cu.gemm_fused(gy[0], w2, f)
-        assert torch.equal(got, cu.gemm(gy[0], w2, mode=1))
+        assert torch.equal(got, cu.gemm(gy[0], w2, mode=1 if m > 128 else 0))
     torch.cuda.synchronize()
     ws.check_status()
 
@@ -161,3 +162,31 @@ def test_ep_all_to_all_two_emulated_ranks(cu):
     for r in range(world):
         assert int((recv_ids[r].view(world, cap)[0, 10 * top_k:] != -1).sum()) == 0
     ws0.check_status()
+
+
+def test_argmax_merge_two_emulated_ranks(cu):
+    """Vocabulary-sharded greedy pick: each "rank" publishes its shard's best (value, global id) per row into both tables;
+    the rank that runs last sees every candidate and must return the arg-max of the concatenated logits (lowest id on ties)."""
+    g = torch.Generator(device="cuda").manual_seed(21)
+    world, rows, vloc, max_rows = 2, 37, 5000, 1024
+    full = torch.randn(rows, world * vloc, device="cuda", generator=g).half()
+    full[0, 17] = full[0, vloc + 3] = 9.0                 # tie across shards: id 17 wins
+    full[1, vloc + 100] = full[1, vloc + 4000] = 9.5      # tie inside shard 1: the lower id wins
+    keys = [torch.zeros(2 * 8 * max_rows, device="cuda", dtype=torch.int64) for _ in range(world)]
+    flags = [torch.ones(16, device="cuda", dtype=torch.int32) for _ in range(world)]          # epoch 1 already "published"
+    epoch = [torch.zeros(1, device="cuda", dtype=torch.int32) for _ in range(world)]
+    outs = [torch.full((rows,), -1, device="cuda", dtype=torch.int32) for _ in range(world)]
+    ws = cu.Workspace.get(full.device)
+    L = cu.lib()
+    for r in (1, 0):                                        # rank 0 runs last and sees both shards' candidates
+        shard = full[:, r * vloc:(r + 1) * vloc]            # a strided view: row pitch = world * vloc
+        local = cu.argmax(shard)
+        cu._check(L.telb_argmax_merge(cu._p(shard), ctypes.c_longlong(shard.stride(0)), cu._p(local), _table(keys), _table(flags),
+                                      cu._p(epoch[r]), cu._p(outs[r]), r, world, rows, max_rows, vloc, 0, cu._p(ws.status), cu._stream()),
+                  "argmax_merge")
+    torch.cuda.synchronize()
+    ws.check_status()
+    want = (full.float() == full.float().max(-1, keepdim=True).values).to(torch.int32).argmax(-1).to(torch.int32)
+    assert torch.equal(outs[0], want)
+    assert int(outs[0][0]) == 17 and int(outs[0][1]) == vloc + 100
+    assert [int(e) for e in epoch] == [1, 1]

@@ -61,12 +61,12 @@ def _make_moe_ckpt(d, dtype):
         json.dump(hf, f)
 
 
-def _launch(nproc, backend, kind, ckpt, port, prompt_len=70, extra=()):
+def _launch(nproc, backend, kind, ckpt, port, prompt_len=70, extra=(), env_extra=None):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "_tp_worker.py"),
            backend, kind, ckpt, str(prompt_len), *extra]
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", OMP_NUM_THREADS="2")
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", OMP_NUM_THREADS="2", **(env_extra or {}))
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     return r.stdout
 
@@ -95,6 +95,30 @@ def test_tp2_fused_prefill_reduce_scatter_path(tmp_path):
         pytest.skip("needs two GPUs")
     _make_ckpt(str(tmp_path), torch.bfloat16)
     out = _launch(2, "nccl", "fused", str(tmp_path), 29614, prompt_len=190)
+    assert "ranks identical True" in out
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("prompt_len", [30, 70])
+def test_tp2_fused_decode_size_reduce_scatter_path(tmp_path, prompt_len):
+    """Every step, decode rows included, takes the sharded path: the decode-size GEMM stores its rows into the owner
+    rank's buffer from its epilogue and the next one waits for the gathered rows in its producer warp."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _make_ckpt(str(tmp_path), torch.bfloat16)
+    out = _launch(2, "nccl", "fused", str(tmp_path), 29618 + (prompt_len > 50), prompt_len=prompt_len, env_extra={"TELB_RS_MIN_ROWS": "1"})
+    assert "ranks identical True" in out
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind,prompt_len,rs_min", [("nccl", 70, "0"), ("fused", 70, "0"), ("fused", 190, "0"), ("fused", 30, "1")])
+def test_tp4_matches_tp1_gpu(tmp_path, kind, prompt_len, rs_min):
+    """Four ranks: NCCL composition, fused one-shot all-reduce, fused prefill path and the sharded decode-size path."""
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs four GPUs")
+    _make_ckpt(str(tmp_path), torch.bfloat16)
+    port = 29630 + ["nccl70", "fused70", "fused190", "fused30"].index(f"{kind}{prompt_len}")
+    out = _launch(4, "nccl", kind, str(tmp_path), port, prompt_len=prompt_len, env_extra={"TELB_RS_MIN_ROWS": rs_min} if rs_min != "0" else None)
     assert "ranks identical True" in out
 
 
