@@ -271,6 +271,10 @@ extern "C" int telb_gemm_skinny_fused(int kind, const void* x, const void* x_sf,
                                       int N, int K, const float* alpha, const void* bias, const void* residual, int is_bf16,
                                       int* status, int force_ranks, const telb::TelbGemmFusion* fusion, cudaStream_t stream);
 
+extern "C" int telb_nvfp4_wide_mode();
+extern "C" int telb_gemm_nvfp4_wide_launch(const void* xq, const void* x_sf, const void* wq, const void* w_sf, int M, int N, int K,
+                                           const void* params_blob, int pair, cudaStream_t stream);
+
 // Number of 64-element K groups the scale buffers are padded to (whole 256-element stages).
 extern "C" int telb_nvfp4_k64_pad(int k) { return ((k + 255) / 256) * 4; }
 
@@ -338,6 +342,17 @@ static int gemm_nvfp4_impl(const void* xq, const void* x_sf, const void* wq, con
         p.sw_gs = sw->gs;
         p.sw_ld = sw->ld;
         p.sw_k64_pad = sw->k64_pad;
+    }
+    // prefill-size problems run on 256-wide tiles (a CTA pair per 256 x 256 tile, or one CTA per 128 x 256 tile)
+    const int wide = telb_nvfp4_wide_mode();
+    if (!swapped && wide > 0 && N >= 256 && N % 8 == 0 && M > 128) {
+        p.c = out;
+        p.bias = bias;
+        p.alpha = alpha;
+        p.residual = residual;
+        p.out_bf16 = out_bf16;
+        p.status = status;
+        return telb_gemm_nvfp4_wide_launch(xq, x_sf, wq, w_sf, M, N, K, &p, wide == 2 ? 1 : 0, stream);
     }
     p.k = K;
     p.kb_total = (K + kFp4BK - 1) / kFp4BK;

@@ -279,6 +279,43 @@ def test_gemm_nvfp4(cu, m, n, k):
     _sync_check(cu)
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 512, 512), (1024, 6144, 4096), (300, 1000, 768), (4096, 4096, 4096), (512, 384, 1024),
+                                   (130, 256, 256), (777, 2048, 12288)])
+def test_gemm_nvfp4_wide_tiles_match_the_128_wide_kernel(cu, m, n, k):
+    """The three prefill-size kernels — 128 x 128 tiles, 128 x 256 single CTA, 256 x 256 CTA pair (cta_group::2) — on the same
+    operands: each against the fp32 oracle, and the wide ones against the 128-wide result (same products, same K order)."""
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    x = torch.randn(m, k, device="cuda", generator=g).half()
+    w = torch.randn(n, k, device="cuda", generator=g) * 0.05
+    wq, wsf, wgs = ref.nvfp4_quantize(w)
+    gs_x = (x.float().abs().amax() / (6 * 448)).reshape(1)
+    xq, xsf = cu.nvfp4_quantize(x, gs_x)
+    w_atoms = cu.nvfp4_swizzle_scales(wsf)
+    alpha = (wgs * gs_x).expand(n).contiguous()
+    bias = torch.randn(n, device="cuda", generator=g).half()
+    resid = torch.randn(m, n, device="cuda", generator=g).half()
+    xd = ref.nvfp4_dequantize(*ref.nvfp4_quantize(x, gs_x.reshape(()))[:2], gs_x.reshape(()))
+    yr = xd @ ref.nvfp4_dequantize(wq, wsf, wgs).t()
+    L = cu.lib()
+    old = L.telb_set_nvfp4_wide_mode(0)
+    try:
+        outs = {}
+        for mode in (0, 1, 2):
+            L.telb_set_nvfp4_wide_mode(mode)
+            outs[mode] = cu.gemm_nvfp4(xq, xsf, wq, w_atoms, alpha, torch.float16, mode=1)
+            outs[(mode, "epi")] = cu.gemm_nvfp4(xq, xsf, wq, w_atoms, alpha, torch.float16, bias=bias, residual=resid, mode=1)
+            torch.cuda.synchronize()
+            cu.Workspace.get(torch.device("cuda", 0)).check_status()
+    finally:
+        L.telb_set_nvfp4_wide_mode(old)
+    for mode in (0, 1, 2):
+        assert _rel_err(outs[mode], yr) < 2e-2, (mode, _rel_err(outs[mode], yr))
+        assert _rel_err(outs[(mode, "epi")], yr + bias.float() + resid.float()) < 2e-2
+    for mode in (1, 2):
+        assert _rel_err(outs[mode], outs[0]) < 1e-3, (mode, _rel_err(outs[mode], outs[0]))
+        assert _rel_err(outs[(mode, "epi")], outs[(0, "epi")]) < 1e-3
+
+
 @pytest.mark.parametrize("m,n,k,ranks", [(1, 4096, 4096, 0), (1, 512, 1024, 1), (8, 6144, 4096, 3), (16, 4096, 12288, 8),
                                          (33, 1000, 512, 2), (64, 24576, 4096, 0), (100, 4096, 4096, 5), (128, 2048, 2048, 4),
                                          (7, 151936, 4096, 0), (64, 4096, 4096, 8), (100, 1004, 512, 1), (9, 1002, 512, 1)])
