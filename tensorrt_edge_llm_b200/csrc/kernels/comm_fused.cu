@@ -284,23 +284,24 @@ __global__ void rs_add_rmsnorm_ag_kernel(RsAgParams p) {
     __shared__ uint32_t s_sf4[kMaxHidden / 64];
     pdl_prologue();
     const int rows_local = max(0, min(p.rows_per_rank, p.rows - p.rank * p.rows_per_rank));
-    const int row = blockIdx.x;                          // local row
-    const int grow = p.rank * p.rows_per_rank + row;     // global row
     const int nunits = p.hidden / 16;
     const int e = *p.epoch + 1;
-    const bool has_row = row < rows_local;
+    const bool has_rows = (int)blockIdx.x < rows_local;
 
     // 1. my GEMM has finished (this kernel runs after it): tell every rank; then wait for theirs
     if (blockIdx.x == 0 && threadIdx.x < p.world) st_release_sys(p.gemm_flags[threadIdx.x] + p.rank, e);
     if (threadIdx.x == 0) s_ok = 1;
     __syncthreads();
-    if (has_row && p.sum_slots > 1 && threadIdx.x < p.world && threadIdx.x != p.rank) {
+    if (has_rows && p.sum_slots > 1 && threadIdx.x < p.world && threadIdx.x != p.rank) {
         if (!wait_flag_ge(p.gemm_flags[p.rank] + threadIdx.x, e, p.status)) s_ok = 0;
     }
     __syncthreads();
 
+    // A CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ...: the flag handshake above and the system-scope fence below
+    // (a round trip over the link) are paid once per CTA, not once per row.
     float v[kUnits][16];
-    if (has_row) {
+    for (int row = blockIdx.x; row < rows_local; row += gridDim.x) {
+        const int grow = p.rank * p.rows_per_rank + row;     // global row
         // 2. sum the partial rows in rank order
 #pragma unroll
         for (int u = 0; u < kUnits; ++u) {
@@ -432,6 +433,7 @@ __global__ void rs_add_rmsnorm_ag_kernel(RsAgParams p) {
                     *reinterpret_cast<uint32_t*>(p.gather_sf[r] + sf_atom_offset(grow, (j - nchunk) * 4, p.k64_pad)) = s_sf4[j - nchunk];
             }
         }
+        __syncthreads();          // red[] and the staged row are reused by the next row
     }
     // 4. the last CTA publishes this rank's shard
     __threadfence_system();
@@ -647,7 +649,9 @@ extern "C" int telb_rs_add_rmsnorm_ag(const void* partial, int* const* gemm_flag
     p.status = status;
     int rows_local = rows - rank * rows_per_rank;
     rows_local = rows_local < 0 ? 0 : (rows_local > rows_per_rank ? rows_per_rank : rows_local);
-    const int grid = rows_local > 0 ? rows_local : 1;
+    // one CTA per row up to four CTAs per SM; beyond that the CTAs loop over rows
+    int grid = rows_local > 0 ? rows_local : 1;
+    if (grid > 4 * sm_count()) grid = 4 * sm_count();
     const int units = hidden / 16;
     int threads = units >= 256 ? 256 : ((units + 31) / 32) * 32;
     if (threads < 32) threads = 32;

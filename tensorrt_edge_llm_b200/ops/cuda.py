@@ -605,11 +605,23 @@ def causal_conv1d(x, weight, bias, conv_state, meta: StepMeta, activation=True):
 _SSM_SCRATCH = {}
 
 
+SSD_TC_MIN_Q = 64        # steps whose longest sequence has at least this many new rows take the tensor-core chunk scan
+
+
 def ssm_scan(x, dt, A, B, C, D, dt_bias, ssm_state, meta: StepMeta, z=None, dt_softplus=True, dt_limit=0.0):
     x, dt, B, C = x.contiguous(), dt.contiguous(), B.contiguous(), C.contiguous()
     t, nh, hd = x.shape
     y = torch.empty_like(x)
     assert ssm_state.dtype == torch.float32 and ssm_state.is_contiguous()
+    if (meta.max_q_len >= SSD_TC_MIN_Q and hd == 64 and B.shape[-1] == 128 and os.environ.get("TELB_DISABLE_SSD_TC", "0") != "1"):
+        # prefill: chunked state-space-duality scan on the tensor cores (csrc/kernels/ssd_tc5.cu)
+        ws = Workspace.get(x.device)
+        _check(lib().telb_ssd_chunk_scan(_p(x), _p(dt), _p(A.float().contiguous()), _p(B), _p(C), _p(D.float().contiguous()),
+                                         _p(dt_bias.float().contiguous()), _p(z.contiguous() if z is not None else None), _p(ssm_state), _p(y),
+                                         _p(meta.q_start), _p(meta.q_len), _p(meta.past_len), _p(meta.slot_ids), c_int(meta.num_seqs), c_int(t),
+                                         c_int(nh), c_int(hd), c_int(B.shape[-1]), c_int(B.shape[1]), c_int(int(dt_softplus)),
+                                         c_float(dt_limit), c_int(_is_bf16(x)), _p(ws.status), _stream()), "ssd_chunk_scan")
+        return y
     scratch = None
     if meta.max_q_len >= 256:       # long prefill chunk: parallel segments need per-segment states (see recurrent.cu)
         segs = (meta.max_q_len + 127) // 128

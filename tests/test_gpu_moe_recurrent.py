@@ -145,10 +145,51 @@ def test_ssm_scan(cu, q_lens, pasts):
     meta = _meta(q_lens, pasts)
     st = torch.randn(len(q_lens), nh, hd, n, device="cuda", generator=g)
     st_ref = st.clone()
-    y = cu.ssm_scan(x, dt, A, B, C, D, dtb, st, meta, z=z)
+    old, cu.SSD_TC_MIN_Q = cu.SSD_TC_MIN_Q, 1 << 30          # the sequential / segmented CUDA-core kernels
+    try:
+        y = cu.ssm_scan(x, dt, A, B, C, D, dtb, st, meta, z=z)
+    finally:
+        cu.SSD_TC_MIN_Q = old
     yr = ref.ssm_scan(x, dt, A, B, C, D, dtb, st_ref, meta, z=z)
     assert _rel_err(y, yr) < 6e-3
     assert _rel_err(st, st_ref) < 1e-4
+    _sync_check(cu)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("q_lens,pasts,gate", [([256], [0], True), ([300, 1, 517], [0, 9, 40], True), ([128, 64, 129, 1000], [5, 0, 0, 64], False),
+                                               ([2048, 77], [0, 300], True)])
+def test_ssd_chunk_scan_tensor_cores(cu, q_lens, pasts, gate, dtype):
+    """The chunked state-space-duality scan on tcgen05 against the sequential fp32 recurrence: ragged lengths (whole
+    chunks, partial last chunks, a one-row sequence), carried-in states, with and without the gate.  The four products
+    take 16-bit operands (the decay-masked scores, the rescaled inputs and the carried state are rounded to 16 bits), so
+    the tolerance is that of 16-bit operands with fp32 accumulation."""
+    g = torch.Generator(device="cuda").manual_seed(16)
+    nh, hd, ng, n = 16, 64, 2, 128
+    t = sum(q_lens)
+    x = torch.randn(t, nh, hd, device="cuda", generator=g).to(dtype)
+    z = torch.randn(t, nh, hd, device="cuda", generator=g).to(dtype) if gate else None
+    dt = (torch.randn(t, nh, device="cuda", generator=g) - 1.0).to(dtype)
+    A = -torch.rand(nh, device="cuda", generator=g) - 0.5
+    B = (torch.randn(t, ng, n, device="cuda", generator=g) * 0.3).to(dtype)
+    C = (torch.randn(t, ng, n, device="cuda", generator=g) * 0.3).to(dtype)
+    D = torch.randn(nh, device="cuda", generator=g)
+    dtb = torch.randn(nh, device="cuda", generator=g) * 0.5
+    slots = list(range(len(q_lens)))[::-1]
+    meta = _meta(q_lens, pasts, slots)
+    st = torch.randn(len(q_lens), nh, hd, n, device="cuda", generator=g)
+    st_ref = st.clone()
+    assert max(q_lens) >= cu.SSD_TC_MIN_Q
+    y = cu.ssm_scan(x, dt, A, B, C, D, dtb, st, meta, z=z, dt_limit=0.0)
+    yr = ref.ssm_scan(x, dt, A, B, C, D, dtb, st_ref, meta, z=z)
+    tol = 1.2e-2 if dtype == torch.bfloat16 else 3e-3
+    assert _rel_err(y, yr) < tol, _rel_err(y, yr)
+    assert _rel_err(st, st_ref) < tol, _rel_err(st, st_ref)
+    # per sequence, so a short sequence cannot hide behind a long one
+    r0 = 0
+    for ql in q_lens:
+        assert _rel_err(y[r0:r0 + ql], yr[r0:r0 + ql]) < 2 * tol
+        r0 += ql
     _sync_check(cu)
 
 
