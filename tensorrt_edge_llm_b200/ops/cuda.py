@@ -638,10 +638,21 @@ def ssm_scan(x, dt, A, B, C, D, dt_bias, ssm_state, meta: StepMeta, z=None, dt_s
     return y
 
 
+GDN_TC_MIN_Q = 32        # steps whose longest sequence has at least this many new rows take the tensor-core chunked kernel
+
+
 def gated_delta_rule(q, k, v, a, b, A_log, dt_bias, state, meta: StepMeta):
     q, k, v, a, b = (t.contiguous() for t in (q, k, v, a, b))
     out = torch.empty_like(v)
     assert state.dtype == torch.float32 and state.is_contiguous()
+    if (meta.max_q_len >= GDN_TC_MIN_Q and q.shape[2] == 128 and v.shape[2] == 128 and os.environ.get("TELB_DISABLE_GDN_TC", "0") != "1"):
+        # prefill: chunked (64-token) delta rule with the matrix products on the tensor cores (csrc/kernels/gdn_tc5.cu)
+        ws = Workspace.get(q.device)
+        _check(lib().telb_gdn_chunk_prefill(_p(q), _p(k), _p(v), _p(a), _p(b), _p(A_log.float().contiguous()), _p(dt_bias.float().contiguous()),
+                                            _p(state), _p(out), _p(meta.q_start), _p(meta.q_len), _p(meta.past_len), _p(meta.slot_ids),
+                                            c_int(meta.num_seqs), c_int(q.shape[0]), c_int(q.shape[1]), c_int(v.shape[1]), c_int(q.shape[2]),
+                                            c_int(v.shape[2]), c_int(_is_bf16(q)), _p(ws.status), _stream()), "gdn_chunk_prefill")
+        return out
     _check(lib().telb_gated_delta_rule(_p(q), _p(k), _p(v), _p(a), _p(b), _p(A_log.float().contiguous()),
                                        _p(dt_bias.float().contiguous()), _p(state), _p(out), _p(meta.q_start), _p(meta.q_len),
                                        _p(meta.past_len), _p(meta.slot_ids), c_int(meta.num_seqs), c_int(q.shape[1]), c_int(v.shape[1]),

@@ -208,10 +208,46 @@ def test_gated_delta_rule(cu, q_lens, pasts):
     meta = _meta(q_lens, pasts)
     st = 0.1 * torch.randn(len(q_lens), hv, kd, vd, device="cuda", generator=g)
     st_ref = st.clone()
-    o = cu.gated_delta_rule(q, k, v, a, b, A_log, dtb, st, meta)
+    old, cu.GDN_TC_MIN_Q = cu.GDN_TC_MIN_Q, 1 << 30          # the sequential CUDA-core kernel
+    try:
+        o = cu.gated_delta_rule(q, k, v, a, b, A_log, dtb, st, meta)
+    finally:
+        cu.GDN_TC_MIN_Q = old
     orf = ref.gated_delta_rule(q, k, v, a, b, A_log, dtb, st_ref, meta)
     assert _rel_err(o, orf) < 6e-3
     assert _rel_err(st, st_ref) < 1e-4
+    _sync_check(cu)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("q_lens,pasts", [([64], [0]), ([200, 1, 65], [0, 9, 40]), ([128, 33, 1000], [5, 0, 64]), ([2048], [0])])
+def test_gdn_chunked_prefill_tensor_cores(cu, q_lens, pasts, dtype):
+    """The 64-token chunked gated delta rule (tcgen05 products + per-column forward substitution) against the sequential
+    fp32 recurrence: ragged lengths, carried-in states, two value heads per key head."""
+    g = torch.Generator(device="cuda").manual_seed(17)
+    hk, hv, kd, vd = 2, 4, 128, 128
+    t = sum(q_lens)
+    q = torch.randn(t, hk, kd, device="cuda", generator=g).to(dtype)
+    k = torch.randn(t, hk, kd, device="cuda", generator=g).to(dtype)
+    v = torch.randn(t, hv, vd, device="cuda", generator=g).to(dtype)
+    a = torch.randn(t, hv, device="cuda", generator=g).to(dtype)
+    b = torch.randn(t, hv, device="cuda", generator=g).to(dtype)
+    A_log = torch.randn(hv, device="cuda", generator=g) * 0.5 - 1.0
+    dtb = torch.randn(hv, device="cuda", generator=g) * 0.5
+    slots = list(range(len(q_lens)))[::-1]
+    meta = _meta(q_lens, pasts, slots)
+    st = 0.1 * torch.randn(len(q_lens), hv, kd, vd, device="cuda", generator=g)
+    st_ref = st.clone()
+    assert max(q_lens) >= cu.GDN_TC_MIN_Q
+    o = cu.gated_delta_rule(q, k, v, a, b, A_log, dtb, st, meta)
+    orf = ref.gated_delta_rule(q, k, v, a, b, A_log, dtb, st_ref, meta)
+    tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
+    assert _rel_err(o, orf) < tol, _rel_err(o, orf)
+    assert _rel_err(st, st_ref) < tol, _rel_err(st, st_ref)
+    r0 = 0
+    for ql in q_lens:
+        assert _rel_err(o[r0:r0 + ql], orf[r0:r0 + ql]) < 2 * tol
+        r0 += ql
     _sync_check(cu)
 
 
