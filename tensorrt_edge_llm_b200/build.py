@@ -28,8 +28,8 @@ NVCC = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "--expt-relaxed-constexpr",
               "-diag-suppress", "177", "-diag-suppress", "550"]
-# the RoPE table and other accuracy-critical init code must not use fast-math
-NO_FAST_MATH = {"rope_table.cu"}
+# sources listed here are compiled without --use_fast_math (none at present: the RoPE table is built by torch ops)
+NO_FAST_MATH: set = set()
 
 
 def _newer(src: str, dst: str, deps: List[str]) -> bool:

@@ -54,6 +54,16 @@ class MoEBlock(nn.Module):
         h, i, dt = cfg.hidden_size, self.inter, cfg.compute_dtype
         self.nvfp4 = cfg.quant.module_quant_type(f"{prefix}.experts") == QUANT_NVFP4
         self.gate = Linear(h, [cfg.num_experts], dtype=dt)
+        # Shared expert (Qwen2-MoE / Qwen3-Next style, ``modeling_qwen3_moe.py:331-333`` in the reference): a dense SwiGLU MLP
+        # every token passes through, scaled per token by sigmoid(shared_expert_gate · x) and added to the routed sum.
+        # It is tensor-parallel like a dense MLP, so its partial sum reduces with the routed experts' in the next add + norm.
+        self.shared_expert = None
+        self.shared_expert_gate = None
+        if getattr(cfg, "shared_expert_intermediate_size", 0) > 0:
+            from .default import MLP
+            self.shared_expert = MLP(cfg, f"{prefix}.shared_expert", intermediate=cfg.shared_expert_intermediate_size)
+            self.shared_expert_gate = Linear(h, [1], dtype=dt)
+            self._gate8 = None              # the [1, H] gate padded to eight rows for the tensor-core GEMM
         if self.nvfp4:
             self.register_buffer("w13", torch.zeros(self.e_local * 2 * i, h // 2, dtype=torch.uint8))
             self.register_buffer("w13_scale", torch.zeros(self.e_local * 2 * i, h // 16, dtype=torch.float8_e4m3fn))
@@ -164,7 +174,25 @@ class MoEBlock(nn.Module):
 
     ep_comm = None      # a communicator with `moe_all_to_all` (set by the model when experts are sharded over ranks)
 
+    def _shared(self, x: torch.Tensor) -> torch.Tensor:
+        """sigmoid(gate · x) ⊙ shared_expert(x) for every row (this rank's partial sum under tensor parallelism)."""
+        w = self.shared_expert_gate.weight
+        if x.is_cuda:
+            if self._gate8 is None or self._gate8.device != x.device:
+                self._gate8 = torch.cat([w, torch.zeros(7, w.shape[1], dtype=w.dtype, device=w.device)]).contiguous()
+            g = ops.linear(x, self._gate8)[:, :1]
+        else:
+            g = (x.float() @ w.float().t()).to(x.dtype)
+        return (torch.sigmoid(g.float()) * self.shared_expert(x).float()).to(x.dtype)
+
     def forward(self, x):
+        if self.shared_expert is None:
+            return self._forward_routed(x)
+        if self.ep_comm is not None and self.ep_size > 1 and self.ep_comm.use_rs(x.shape[0]):
+            raise NotImplementedError("shared experts are not combined with the token-sharded expert all-to-all")
+        return self._forward_routed(x) + self._shared(x)
+
+    def _forward_routed(self, x):
         if isinstance(x, torch.Tensor) and not x.is_cuda:
             return self._forward_reference(x)
         if self.ep_comm is not None and self.ep_size > 1 and self.ep_comm.use_rs(x.shape[0]):

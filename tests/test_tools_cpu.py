@@ -326,3 +326,37 @@ def test_prefix_cache_is_keyed_by_adapter(ckpt, tmp_path):
     llm.load_lora("one", r1)                                         # reloaded under the same name: a new identity
     assert run(llm, "one") == want_one and pc.hits == hits0 + 2
     llm.close()
+
+
+def test_runtime_names_of_the_reference_package():
+    """``tensorrt_edgellm.runtime`` carries the reference's runtime class names; ``LLMRuntime`` answers a request file,
+    counts prompt tokens and opens a stepped session over the same model."""
+    import tensorrt_edgellm.runtime as rt_names
+    from tensorrt_edge_llm_b200.config import tiny_llama_config
+    from tensorrt_edge_llm_b200.runtime.llm import LLM
+    for name in ("LLMRuntime", "RequestEngine", "RequestHandle", "StreamChannel", "MultiStageRuntime", "validate_scheduling_options"):
+        assert getattr(rt_names, name) is not None
+
+    class Bytes:
+        def encode(self, text, add_special_tokens=False):
+            return [b + 3 for b in text.encode("utf-8")]
+
+        def decode(self, ids, skip_special_tokens=True):
+            return bytes((i - 3) % 256 for i in ids).decode("utf-8", "replace")
+
+        def id_to_bytes(self, i):
+            return bytes([(i - 3) % 256])
+    llm = LLM(tiny_llama_config(num_hidden_layers=1, vocab_size=300), device="cpu", max_batch_size=2, max_input_len=128,
+              max_kv_cache_capacity=192, page_size=16, tokenizer=Bytes())
+    runtime = rt_names.LLMRuntime(None, llm=llm)
+    body = {"temperature": 0.0, "max_generate_length": 4, "requests": [{"messages": [{"role": "user", "content": "hi"}]},
+                                                                           {"messages": [{"role": "user", "content": "hello there"}]}]}
+    out = runtime.handle_request(body)
+    assert [r["output_tokens"] for r in out["responses"]] == [4, 4]
+    counts = runtime.count_prompt_tokens(json.dumps(body))
+    assert counts[1] > counts[0] > 0 and counts == [r["input_tokens"] for r in out["responses"]]
+    assert runtime.max_batch_size() == 2 and runtime.world_size() == 1 and runtime.owns_global_rank(0) and not runtime.has_draft_model()
+    assert runtime.unavailable_reason() == "" and runtime.capture_decoding_cuda_graph() is False       # no graphs on a CPU
+    sess = runtime.open_session()
+    assert sess.capabilities().max_batch_size == 2 and runtime.get_generation_metrics()["output_tokens"] == 8
+    runtime.close()
