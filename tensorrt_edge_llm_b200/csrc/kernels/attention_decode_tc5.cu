@@ -18,12 +18,18 @@
 #include <type_traits>
 
 #include "host_utils.h"
+#include "nvfp4_common.cuh"
 #include "tc5_common.cuh"
 
 namespace telb {
 
 struct DecParams {
     void* out;
+    // optional NVFP4 output for the projection that follows (splits == 1): packed codes [T, Hq * D / 2], atom-layout scales
+    uint8_t* oq;
+    uint8_t* osf;
+    const float* ogs;
+    int ok64;
     float* ws_o;
     float* ws_lse;
     const int* q_start;
@@ -464,7 +470,16 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
                         const int qi = c >> gshift, g = c - (qi << gshift);
                         const size_t tok = (size_t)it.qrow0 + qi;
                         const int head = it.kvh * p.group + g;
-                        if (p.splits == 1) {
+                        if (p.splits == 1 && p.oq != nullptr) {
+                            // the output projection reads NVFP4: quantise here (16 consecutive dims = 16 consecutive lanes),
+                            // with the rounding of the 16-bit store the unfused path would have made first
+                            const float gs = *p.ogs;
+                            uint8_t s8;
+                            const uint32_t w4 = nvfp4_quantize_lane16(Cvt<T>::to_f(Cvt<T>::from_f(val)), gs, 1.f / gs, s8);
+                            const int col = head * D + r;
+                            if ((lane & 7) == 0) *reinterpret_cast<uint32_t*>(p.oq + tok * (size_t)(p.hq * D / 2) + col / 2) = w4;
+                            if ((lane & 15) == 0) p.osf[sf_atom_offset((long long)tok, col >> 4, p.ok64)] = s8;
+                        } else if (p.splits == 1) {
                             reinterpret_cast<T*>(p.out)[(tok * p.hq + head) * D + r] = Cvt<T>::from_f(val);
                         } else {
                             p.ws_o[(((size_t)it.split * p.total_tokens + tok) * p.hq + head) * D + r] = val;
@@ -532,6 +547,9 @@ using namespace telb;
 
 extern "C" int telb_attn_combine(const float* ws_o, const float* ws_lse, void* out, int rows, int splits, int d, int is_bf16,
                                  cudaStream_t stream);
+extern "C" int telb_attn_combine_quant(const float* ws_o, const float* ws_lse, void* oq, void* osf, const float* ogs, int tokens, int hq,
+                                       int splits, int d, int is_bf16, cudaStream_t stream);
+extern "C" int telb_nvfp4_k64_pad(int k);
 
 // Ring depth / residency variant of the decode kernel (0, 1 or 2: see launch_decode); process-wide.
 extern "C" int telb_set_decode_variant(int v) {
@@ -558,6 +576,11 @@ extern "C" int telb_paged_attention_decode(const void* q, const void* kv_layer, 
                                               status, nullptr, stream);
 }
 
+static int decode_impl(const void* q, const void* kv_layer, void* out, void* oq, void* osf, const float* ogs, const int* q_start,
+                       const int* q_len, const int* past_len, const int* page_table, int num_seqs, int total_tokens, int max_q_len,
+                       int num_pages, int max_pages, int page_size, int hq, int hkv, int d, float scale, int window, int splits, float* ws,
+                       long long ws_floats, int is_bf16, int* status, unsigned long long* trace, cudaStream_t stream);
+
 // Same call with a timeline buffer (3 x 64 x 4 u64, zeroed by the caller) filled by the first CTA.
 extern "C" int telb_paged_attention_decode_traced(const void* q, const void* kv_layer, void* out, const int* q_start,
                                                   const int* q_len, const int* past_len, const int* page_table, int num_seqs,
@@ -565,6 +588,27 @@ extern "C" int telb_paged_attention_decode_traced(const void* q, const void* kv_
                                                   int hq, int hkv, int d, float scale, int window, int splits, float* ws,
                                                   long long ws_floats, int is_bf16, int* status, unsigned long long* trace,
                                                   cudaStream_t stream) {
+    return decode_impl(q, kv_layer, out, nullptr, nullptr, nullptr, q_start, q_len, past_len, page_table, num_seqs, total_tokens, max_q_len,
+                       num_pages, max_pages, page_size, hq, hkv, d, scale, window, splits, ws, ws_floats, is_bf16, status, trace, stream);
+}
+
+// Decode attention whose output is written as NVFP4 only (packed codes out_xq [T, Hq * D / 2], atom-layout scales out_sf over
+// rows T and Hq * D columns, pre-zeroed by the caller where padding exists): the input of the output projection, so a decode
+// layer has no separate quantisation kernel between attention and o_proj.
+extern "C" int telb_paged_attention_decode_quant(const void* q, const void* kv_layer, void* out_xq, void* out_sf, const float* out_global_scale,
+                                                 const int* q_start, const int* q_len, const int* past_len, const int* page_table,
+                                                 int num_seqs, int total_tokens, int max_q_len, int num_pages, int max_pages, int page_size,
+                                                 int hq, int hkv, int d, float scale, int window, int splits, float* ws, long long ws_floats,
+                                                 int is_bf16, int* status, cudaStream_t stream) {
+    if (!out_xq || !out_sf || !out_global_scale) return fail("telb_paged_attention_decode_quant: output buffers and scale are required");
+    return decode_impl(q, kv_layer, nullptr, out_xq, out_sf, out_global_scale, q_start, q_len, past_len, page_table, num_seqs, total_tokens,
+                       max_q_len, num_pages, max_pages, page_size, hq, hkv, d, scale, window, splits, ws, ws_floats, is_bf16, status, nullptr, stream);
+}
+
+static int decode_impl(const void* q, const void* kv_layer, void* out, void* oq, void* osf, const float* ogs, const int* q_start,
+                       const int* q_len, const int* past_len, const int* page_table, int num_seqs, int total_tokens, int max_q_len,
+                       int num_pages, int max_pages, int page_size, int hq, int hkv, int d, float scale, int window, int splits, float* ws,
+                       long long ws_floats, int is_bf16, int* status, unsigned long long* trace, cudaStream_t stream) {
     if (num_seqs <= 0 || total_tokens <= 0) return 0;
     if (d != 128) return fail("telb_paged_attention_decode: head_dim must be 128");
     if (page_size != 64 && page_size != 128) return fail("telb_paged_attention_decode: page size must be 64 or 128");
@@ -574,6 +618,10 @@ extern "C" int telb_paged_attention_decode_traced(const void* q, const void* kv_
     if (kDecN % group) return fail("telb_paged_attention_decode: Hq/Hkv must divide 16");
     DecParams p{};
     p.out = out;
+    p.oq = static_cast<uint8_t*>(oq);
+    p.osf = static_cast<uint8_t*>(osf);
+    p.ogs = ogs;
+    p.ok64 = telb_nvfp4_k64_pad(hq * d);
     p.q_start = q_start;
     p.q_len = q_len;
     p.past_len = past_len;
@@ -613,6 +661,7 @@ extern "C" int telb_paged_attention_decode_traced(const void* q, const void* kv_
     const int rc = is_bf16 ? launch_decode<128, __nv_bfloat16>(tq, tkv, p, num_seqs, max_q_len * group, stream)
                            : launch_decode<128, __half>(tq, tkv, p, num_seqs, max_q_len * group, stream);
     if (rc) return rc;
+    if (splits > 1 && oq) return telb_attn_combine_quant(p.ws_o, p.ws_lse, oq, osf, ogs, total_tokens, hq, splits, d, is_bf16, stream);
     if (splits > 1) return telb_attn_combine(p.ws_o, p.ws_lse, out, total_tokens * hq, splits, d, is_bf16, stream);
     return 0;
 }

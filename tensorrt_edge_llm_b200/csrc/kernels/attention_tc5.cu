@@ -23,6 +23,7 @@
 #include <type_traits>
 
 #include "host_utils.h"
+#include "nvfp4_common.cuh"
 #include "tc5_common.cuh"
 
 namespace telb {
@@ -430,6 +431,40 @@ __global__ void attn_combine_kernel(const float* __restrict__ ws_o, const float*
     out[(size_t)row * D + d] = Cvt<T>::from_f(acc);
 }
 
+// The same merge with the result written as NVFP4 (input of the output projection): thread d of row (token, head) holds
+// output dim d, so a 16-element block is 16 consecutive lanes.
+template <int D, typename T>
+__global__ void attn_combine_quant_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_lse, uint8_t* __restrict__ oq,
+                                          uint8_t* __restrict__ osf, const float* __restrict__ ogs, int total_rows /* T*Hq */, int hq,
+                                          int splits, int k64) {
+    pdl_prologue();
+    __shared__ float w[32];
+    const int row = blockIdx.x;
+    const int d = threadIdx.x;
+    if (threadIdx.x < 32) {
+        const float l = threadIdx.x < splits ? ws_lse[(size_t)threadIdx.x * total_rows + row] : -INFINITY;
+        float mx = l;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float e = (l == -INFINITY) ? 0.f : exp2f(l - mx);
+        float den = e;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+        w[threadIdx.x] = den > 0.f ? e / den : 0.f;
+    }
+    __syncthreads();
+    float acc = 0.f;
+#pragma unroll 8
+    for (int s = 0; s < splits; ++s) acc += w[s] * __ldcg(&ws_o[((size_t)s * total_rows + row) * D + d]);
+    const float gs = *ogs;
+    uint8_t s8;
+    const uint32_t w4 = nvfp4_quantize_lane16(Cvt<T>::to_f(Cvt<T>::from_f(acc)), gs, 1.f / gs, s8);
+    const int tok = row / hq, head = row - tok * hq;
+    const int col = head * D + d;
+    if ((d & 7) == 0) *reinterpret_cast<uint32_t*>(oq + (size_t)tok * (hq * D / 2) + col / 2) = w4;
+    if ((d & 15) == 0) osf[sf_atom_offset((long long)tok, col >> 4, k64)] = s8;
+}
+
 template <int D, typename T, int KVS, int MINB>
 static int launch_attn_variant(const CUtensorMap& tq, const CUtensorMap& tkv, const AttnParams& p, int qtiles, int nseq,
                                cudaStream_t stream) {
@@ -484,6 +519,22 @@ extern "C" int telb_attn_combine(const float* ws_o, const float* ws_lse, void* o
         return fail("telb_attn_combine: head_dim must be 64 or 128");
     }
     TELB_CHECK_LAUNCH("attn_combine_kernel");
+    return 0;
+}
+
+extern "C" int telb_nvfp4_k64_pad(int k);
+
+// The merge with an NVFP4 result: packed codes oq [tokens, hq * d / 2] and atom-layout scales osf over hq * d columns.
+extern "C" int telb_attn_combine_quant(const float* ws_o, const float* ws_lse, void* oq, void* osf, const float* ogs, int tokens, int hq,
+                                       int splits, int d, int is_bf16, cudaStream_t stream) {
+    const int rows = tokens * hq;
+    if (rows <= 0) return 0;
+    if (d != 128) return fail("telb_attn_combine_quant: head_dim must be 128");
+    if (splits > 32) return fail("telb_attn_combine_quant: at most 32 splits");
+    const int k64 = telb_nvfp4_k64_pad(hq * d);
+    if (is_bf16) TELB_LAUNCH("attn_combine_quant_kernel", (attn_combine_quant_kernel<128, __nv_bfloat16>), dim3(rows), dim3(128), 0, stream, ws_o, ws_lse, (uint8_t*)oq, (uint8_t*)osf, ogs, rows, hq, splits, k64);
+    else TELB_LAUNCH("attn_combine_quant_kernel", (attn_combine_quant_kernel<128, __half>), dim3(rows), dim3(128), 0, stream, ws_o, ws_lse, (uint8_t*)oq, (uint8_t*)osf, ogs, rows, hq, splits, k64);
+    TELB_CHECK_LAUNCH("attn_combine_quant_kernel");
     return 0;
 }
 

@@ -22,8 +22,16 @@
 //     producer warp waits (bounded) for the owners' flags after `griddepcontrol.wait`, while the weight
 //     tiles of the first ring pass are already in flight.
 //
-// Reference counterparts: TensorRT decode tactics; kernelSrcs/nvfp4A16BlackwellGemv (SM110-only
+// INT4 group-wise weights (KIND 2, W4A16): the packed 4-bit tile of a K step (4 KB for 128 output rows x 64 inputs) arrives
+// by TMA next to the activation tile; the four warps that later run the epilogue expand it — (q − 8) · scale per
+// group — into the 16-bit, 128-byte-swizzled operand tile the MMA reads, so HBM and L2 only ever see 4-bit weights.
+//
+// Reference counterparts: TensorRT decode tactics; int4 group-wise GEMM / GEMV of
+// cpp/kernels/int4GroupwiseGemmKernels/int4WoqGemmCuda.cu:98-124 and int4WoQGemvCuda.cu:225-253 (mma.sync / CUDA cores);
+// kernelSrcs/nvfp4A16BlackwellGemv (SM110-only
 // CUDA-core GEMV) and `gemm_blackwell_nvfp4_ws_*_tn64` at TP=2.
+#include <type_traits>
+
 #include "gemm_common.cuh"
 
 namespace telb {
@@ -47,7 +55,38 @@ struct SkinnyParams {
     const int* ag_flags;
     const int* ag_epoch;
     int ag_world, ag_rows_per_rank;
+    // INT4 group-wise weights (KIND 2): per-(row, group) scales, 16-bit, [n_out, k / group]
+    const void* w_scale;
+    int group, groups_per_row;
+    // SwiGLU + NVFP4 output (weights whose gate / up rows alternate in blocks of 64, m_tok <= 64): instead of the 16-bit
+    // [m_tok, n_out] result the epilogue stores quantised silu(gate) * up [m_tok, n_out / 2] — packed codes into sw_xq
+    // (row pitch sw_ld bytes) and block scales into the atom-layout buffer sw_sf.
+    uint8_t* sw_xq;
+    uint8_t* sw_sf;
+    const float* sw_gs;
+    int sw_ld, sw_k64_pad;
 };
+
+// 16 SwiGLU outputs of one token from a 128-feature tile row `v` (64 gate features followed by their 64 up features, fp32
+// sums already scaled): the same roundings as the unfused chain — 16-bit GEMM output, 16-bit activation — then quantise.
+template <typename T>
+__device__ __forceinline__ void skinny_swiglu_block(const SkinnyParams& p, const float* v, int tok, int a0, int b) {
+    float y[16];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float g = Cvt<T>::to_f(Cvt<T>::from_f(v[16 * b + i]));
+        const float u = Cvt<T>::to_f(Cvt<T>::from_f(v[64 + 16 * b + i]));
+        y[i] = Cvt<T>::to_f(Cvt<T>::from_f(g / (1.f + __expf(-g)) * u));
+        amax = fmaxf(amax, fabsf(y[i]));
+    }
+    const float gs = *p.sw_gs;
+    uint8_t s8;
+    const uint2 packed = nvfp4_quantize_block16(y, amax, gs, 1.f / gs, s8);
+    const int blk = (a0 / 2 + 16 * b) >> 4;                         // 16-element block index along the intermediate dimension
+    *reinterpret_cast<uint2*>(p.sw_xq + (size_t)tok * p.sw_ld + blk * 8) = packed;
+    p.sw_sf[sf_atom_offset((long long)tok, blk, p.sw_k64_pad)] = s8;
+}
 
 // Where the four features starting at `feat` of token `tok` are stored: the local output, or the owner rank's partial buffer.
 template <typename T>
@@ -84,7 +123,7 @@ struct SkinnyCfg {
     static constexpr int kBKBytes = 128;                                     // one swizzle atom per row
     static constexpr int kWTile = kBM * 128;
     static constexpr int kXTile = BN * 128;
-    static constexpr int kSf = KIND == 1 ? 2 * 2048 : 0;
+    static constexpr int kSf = KIND == 1 ? 2 * 2048 : (KIND == 2 ? 4096 : 0);      // NVFP4 scale atoms, or the packed INT4 tile
     static constexpr int kStage = kWTile + kXTile + kSf;
     static constexpr int kRed = BN * kBM * 4;                                // fp32 partial tile
     static constexpr int kBudget = 98304;
@@ -96,7 +135,43 @@ struct SkinnyCfg {
     static constexpr int kTmemCols = kTmemNeed <= 32 ? 32 : kTmemNeed <= 64 ? 64 : kTmemNeed <= 128 ? 128 : 256;
 };
 
-// KIND 0: bf16/fp16 operands (K per stage = 64), KIND 1: NVFP4 (K per stage = 256).
+// Eight 4-bit codes of one output row (the low or the high nibbles of eight packed bytes) → eight 16-bit values (q − 8) · scale.
+// No integer-to-float conversion: a code OR-ed into the mantissa of a 16-bit constant is the number (C + q) exactly
+// (C = 128 for bf16, 1024 for fp16); subtracting (C + 8) is exact too, and one multiply by the scale rounds once.
+// A 32-bit word holds the codes of inputs k, k+1, k+2, k+3 in its four bytes: the masked word pairs (k, k+2) and
+// (k+1, k+3), and two byte permutes restore the input order.
+template <typename T>
+__device__ __forceinline__ uint4 int4_expand8(uint32_t w0, uint32_t w1, int shift, float scale) {
+    constexpr bool kBf = std::is_same<T, __nv_bfloat16>::value;
+    constexpr uint32_t kMagic = kBf ? 0x43004300u : 0x64006400u;          // 128.0 | 128.0   or   1024.0 | 1024.0
+    constexpr uint32_t kOff = kBf ? 0x43084308u : 0x64086408u;            // 136.0 | 136.0   or   1032.0 | 1032.0
+    const uint32_t a0 = ((w0 >> shift) & 0x000F000Fu) | kMagic, a1 = ((w0 >> (shift + 8)) & 0x000F000Fu) | kMagic;
+    const uint32_t b0 = ((w1 >> shift) & 0x000F000Fu) | kMagic, b1 = ((w1 >> (shift + 8)) & 0x000F000Fu) | kMagic;
+    uint32_t v[4] = {__byte_perm(a0, a1, 0x5410), __byte_perm(a0, a1, 0x7632), __byte_perm(b0, b1, 0x5410), __byte_perm(b0, b1, 0x7632)};
+    uint4 u;
+    uint32_t* o = reinterpret_cast<uint32_t*>(&u);
+    if constexpr (kBf) {
+        const __nv_bfloat162 s2 = __float2bfloat162_rn(scale);
+        const __nv_bfloat162 off = *reinterpret_cast<const __nv_bfloat162*>(&kOff);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 r = __hmul2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&v[i]), off), s2);
+            o[i] = *reinterpret_cast<const uint32_t*>(&r);
+        }
+    } else {
+        const __half2 s2 = __float2half2_rn(scale);
+        const __half2 off = *reinterpret_cast<const __half2*>(&kOff);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __half2 r = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&v[i]), off), s2);
+            o[i] = *reinterpret_cast<const uint32_t*>(&r);
+        }
+    }
+    return u;
+}
+
+// KIND 0: bf16/fp16 operands (K per stage = 64), KIND 1: NVFP4 (K per stage = 256), KIND 2: INT4 group-wise weights
+// expanded to 16 bits in shared memory (K per stage = 64).
 template <int KIND, int BN, typename T>
 __global__ void __launch_bounds__(kGemmThreads, 2)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x, SkinnyParams p) {
@@ -107,7 +182,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::kSmemData);
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* tfull_bar = empty_bar + STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tfull_bar + 1);
+    uint64_t* raw_bar = tfull_bar + 1;                 // KIND 2: the packed tile and the activations of a stage have landed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(raw_bar + STAGES);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     float* s_alpha = reinterpret_cast<float*>(tmem_slot + 4);      // per-feature scale / bias of this 128-row tile
     float* s_bias = s_alpha + kBM;
@@ -123,8 +199,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&full_bar[s], 1);
+            mbar_init(&full_bar[s], KIND == 2 ? 128 : 1);      // KIND 2: the 128 expanding threads fill the operand tile
             mbar_init(&empty_bar[s], 1);
+            mbar_init(&raw_bar[s], 1);
         }
         mbar_init(tfull_bar, 1);
         *abort_flag = 0;
@@ -149,8 +226,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
             const int pre = min(nkb, STAGES);
             for (int j = 0; j < pre; ++j) {
                 uint8_t* sw = smem + j * Cfg::kStage;
-                mbar_expect_tx(&full_bar[j], Cfg::kStage);
-                tma_load_2d(sw, &tma_w, &full_bar[j], (kb0 + j) * (KIND == 1 ? 128 : 64), a0);
+                if constexpr (KIND == 2) {
+                    // packed 4-bit tile: 64 byte rows (two output rows each) x 64 input columns, into the stage's staging area
+                    mbar_expect_tx(&raw_bar[j], 4096 + Cfg::kXTile);
+                    tma_load_2d(sw + Cfg::kWTile + Cfg::kXTile, &tma_w, &raw_bar[j], (kb0 + j) * 64, a0 / 2);
+                } else {
+                    mbar_expect_tx(&full_bar[j], Cfg::kStage);
+                    tma_load_2d(sw, &tma_w, &full_bar[j], (kb0 + j) * (KIND == 1 ? 128 : 64), a0);
+                }
                 if constexpr (KIND == 1)
                     bulk_load(sw + Cfg::kWTile + Cfg::kXTile, p.sf_w + ((size_t)blockIdx.x * p.sf_k64 + (size_t)(kb0 + j) * 4) * 512,
                               2048, &full_bar[j]);
@@ -178,7 +261,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
             }
             for (int j = 0; j < pre && x_ready; ++j) {
                 uint8_t* sx = smem + j * Cfg::kStage + Cfg::kWTile;
-                tma_load_2d(sx, &tma_x, &full_bar[j], (kb0 + j) * (KIND == 1 ? 128 : 64), 0);
+                tma_load_2d(sx, &tma_x, KIND == 2 ? &raw_bar[j] : &full_bar[j], (kb0 + j) * (KIND == 1 ? 128 : 64), 0);
                 if constexpr (KIND == 1)
                     bulk_load(sx + Cfg::kXTile + 2048, p.sf_x + (size_t)(kb0 + j) * 4 * 512, 2048, &full_bar[j]);
             }
@@ -187,9 +270,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
             for (int j = pre; j < nkb && x_ready; ++j) {
                 if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) break;
                 uint8_t* sw = smem + stage * Cfg::kStage;
-                mbar_expect_tx(&full_bar[stage], Cfg::kStage);
-                tma_load_2d(sw, &tma_w, &full_bar[stage], (kb0 + j) * (KIND == 1 ? 128 : 64), a0);
-                tma_load_2d(sw + Cfg::kWTile, &tma_x, &full_bar[stage], (kb0 + j) * (KIND == 1 ? 128 : 64), 0);
+                if constexpr (KIND == 2) {
+                    mbar_expect_tx(&raw_bar[stage], 4096 + Cfg::kXTile);
+                    tma_load_2d(sw + Cfg::kWTile + Cfg::kXTile, &tma_w, &raw_bar[stage], (kb0 + j) * 64, a0 / 2);
+                    tma_load_2d(sw + Cfg::kWTile, &tma_x, &raw_bar[stage], (kb0 + j) * 64, 0);
+                } else {
+                    mbar_expect_tx(&full_bar[stage], Cfg::kStage);
+                    tma_load_2d(sw, &tma_w, &full_bar[stage], (kb0 + j) * (KIND == 1 ? 128 : 64), a0);
+                    tma_load_2d(sw + Cfg::kWTile, &tma_x, &full_bar[stage], (kb0 + j) * (KIND == 1 ? 128 : 64), 0);
+                }
                 if constexpr (KIND == 1) {
                     bulk_load(sw + Cfg::kWTile + Cfg::kXTile, p.sf_w + ((size_t)blockIdx.x * p.sf_k64 + (size_t)(kb0 + j) * 4) * 512,
                               2048, &full_bar[stage]);
@@ -203,7 +292,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         }
     } else if (warp == 1) {
         if (lane == 0 && nkb > 0) {
-            const uint32_t idesc = KIND == 1 ? idesc_nvfp4(kBM, BN) : idesc_f16(kBM, BN, p.out_bf16 != 0);
+            const uint32_t idesc = KIND == 1 ? idesc_nvfp4(kBM, BN) : idesc_f16(kBM, BN, p.out_bf16 != 0);     // KIND 2 multiplies 16-bit tiles
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -241,6 +330,48 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         }
     }
 
+    if constexpr (KIND == 2) {
+        if (warp >= 2) {
+            // ---- expand the packed 4-bit tiles: thread t serves byte row t / 2 (output rows 2 (t/2), 2 (t/2) + 1) and the
+            //      input-column half t % 2 (32 columns = four 16-byte chunks per output row) ----
+            const int t = (warp - 2) * 32 + lane;
+            const int pr = t >> 1, kh = t & 1;
+            const int row0 = 2 * pr, grow = a0 + row0;
+            const T* sc = reinterpret_cast<const T*>(p.w_scale);
+            int stage = 0, cur_group = -1;
+            uint32_t phase = 0;
+            float s0 = 0.f, s1 = 0.f;
+            for (int j = 0; j < nkb; ++j) {
+                const int grp = ((kb0 + j) * 64) / p.group;
+                if (grp != cur_group) {                        // a group spans one or more K steps: fetch its two scales once
+                    cur_group = grp;
+                    s0 = grow < p.n_out ? Cvt<T>::to_f(sc[(size_t)grow * p.groups_per_row + grp]) : 0.f;
+                    s1 = grow + 1 < p.n_out ? Cvt<T>::to_f(sc[(size_t)(grow + 1) * p.groups_per_row + grp]) : 0.f;
+                }
+                if (!mbar_wait(&raw_bar[stage], phase, abort_flag, p.status, kStatusEpilogueTimeout)) break;
+                uint8_t* sw = smem + stage * Cfg::kStage;
+                const uint4* src = reinterpret_cast<const uint4*>(sw + Cfg::kWTile + Cfg::kXTile + pr * 64 + kh * 32);
+                const uint4 pa = src[0], pb = src[1];
+                const uint32_t w[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int chunk = kh * 4 + c;
+                    const int r0 = row0, r1 = row0 + 1;
+                    *reinterpret_cast<uint4*>(sw + (r0 >> 3) * 1024 + (r0 & 7) * 128 + ((chunk ^ (r0 & 7)) << 4)) =
+                        int4_expand8<T>(w[2 * c], w[2 * c + 1], 0, s0);
+                    *reinterpret_cast<uint4*>(sw + (r1 >> 3) * 1024 + (r1 & 7) * 128 + ((chunk ^ (r1 & 7)) << 4)) =
+                        int4_expand8<T>(w[2 * c], w[2 * c + 1], 4, s1);
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(&full_bar[stage]);
+                if (++stage == STAGES) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+        }
+    }
+
     // ---- epilogue ------------------------------------------------------------------------------
     const bool is_epi = warp >= 2;
     const int quad = warp & 3;
@@ -266,7 +397,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     const T* resp = reinterpret_cast<const T*>(p.residual);
     const bool scatter = p.rs_world > 1;          // host side guarantees n_out % 4 == 0 and no residual
 
-    if (p.ranks == 1 && (p.m_tok > 8 || scatter) && (p.n_out & 3) == 0) {
+    if (p.ranks == 1 && (p.m_tok > 8 || scatter || p.sw_xq != nullptr) && (p.n_out & 3) == 0) {
         // Many token columns: a lane owns one feature, so direct stores would be 2-byte pieces 2 * n_out apart.  The
         // tile is transposed through shared memory instead (the stage ring is free once the MMAs have completed) and
         // leaves as 8-byte stores, 256 contiguous bytes per token and warp.
@@ -286,7 +417,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
             named_barrier_sync(1, 128);
             pdl_wait();
             const int etid = (warp - 2) * 32 + lane;
-            const int items = min(BN, p.m_tok) * 32;
+            if (p.sw_xq != nullptr) {
+                // SwiGLU + quantise: one item = (token, block of 16 outputs); the tile row is scaled in place first
+                const int mt = min(BN, p.m_tok);
+                for (int it = etid; it < mt * kBM; it += 128) red[it] = red[it] * s_alpha[it & (kBM - 1)] + s_bias[it & (kBM - 1)];
+                named_barrier_sync(1, 128);
+                for (int it = etid; it < mt * 4; it += 128) skinny_swiglu_block<T>(p, red + (it >> 2) * kBM, it >> 2, a0, it & 3);
+            }
+            const int items = p.sw_xq != nullptr ? 0 : min(BN, p.m_tok) * 32;
             for (int it = etid; it < items; it += 128) {
                 const int c = it >> 5;
                 const int fg = (it & 31) * 4;
@@ -359,6 +497,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
             const int c_lo = rank * per, c_hi = min(mcols, c_lo + per);
             const int items = max(0, c_hi - c_lo) * 32;
             const bool vec_out = (p.n_out & 3) == 0;
+            float* fin = red + BN * kBM;            // SwiGLU mode: this CTA's reduced token columns [per][128], local only
             for (int it = etid; it < items; it += 128) {
                 const int c = c_lo + (it >> 5);
                 const int fg = (it & 31) * 4;
@@ -374,6 +513,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
                     v[1] += part[rk].y;
                     v[2] += part[rk].z;
                     v[3] += part[rk].w;
+                }
+                if (p.sw_xq != nullptr) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) fin[(c - c_lo) * kBM + fg + i] = v[i] * s_alpha[fg + i] + s_bias[fg + i];
+                    continue;
                 }
                 const int f0 = a0 + fg;
                 const size_t o = (size_t)c * p.n_out + f0;
@@ -395,6 +539,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
                         if (f0 + i < p.n_out) outp[o + i] = Cvt<T>::from_f(v[i]);
                 }
             }
+            if (p.sw_xq != nullptr) {
+                named_barrier_sync(1, 128);
+                for (int it = etid; it < max(0, c_hi - c_lo) * 4; it += 128)
+                    skinny_swiglu_block<T>(p, fin + (it >> 2) * kBM, c_lo + (it >> 2), a0, it & 3);
+            }
             if (scatter) __threadfence_system();
         }
         cluster_sync_all();         // peers may still be reading this CTA's partial tile
@@ -412,10 +561,28 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     }
 }
 
+// Whole-matrix expansion of INT4 group-wise weights to 16 bits (prefill-size GEMMs run on the dense tensor-core kernel
+// over a temporary expanded copy; decode-size GEMMs expand tile by tile inside gemm_skinny_kernel and never need it).
+template <typename T>
+__global__ void int4_expand_kernel(const uint8_t* __restrict__ wq, const T* __restrict__ scales, T* __restrict__ out, int n, int k,
+                                   int group) {
+    pdl_prologue();
+    const long long chunks = (long long)(n / 2) * (k / 8);
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < chunks; i += (long long)gridDim.x * blockDim.x) {
+        const int pr = (int)(i / (k / 8)), c = (int)(i - (long long)pr * (k / 8));
+        const uint2 w = *reinterpret_cast<const uint2*>(wq + (size_t)pr * k + c * 8);
+        const int grp = c * 8 / group;
+        const float s0 = Cvt<T>::to_f(scales[(size_t)(2 * pr) * (k / group) + grp]);
+        const float s1 = Cvt<T>::to_f(scales[(size_t)(2 * pr + 1) * (k / group) + grp]);
+        *reinterpret_cast<uint4*>(out + (size_t)(2 * pr) * k + c * 8) = int4_expand8<T>(w.x, w.y, 0, s0);
+        *reinterpret_cast<uint4*>(out + (size_t)(2 * pr + 1) * k + c * 8) = int4_expand8<T>(w.x, w.y, 4, s1);
+    }
+}
+
 template <int KIND, int BN, typename T>
 static int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const SkinnyParams& p, cudaStream_t stream) {
     using Cfg = SkinnyCfg<KIND, BN>;
-    constexpr int smem = Cfg::kSmemData + 1024 + 256 + 2 * kBM * 4;
+    constexpr int smem = Cfg::kSmemData + 1024 + 384 + 2 * kBM * 4;
     static bool configured = false;
     auto kern = gemm_skinny_kernel<KIND, BN, T>;
     if (!configured) {
@@ -497,10 +664,18 @@ extern "C" int telb_nvfp4_k64_pad(int k);
 
 // kind 0: x, w are 16-bit [M,K], [N,K].  kind 1: packed E2M1 [M,K/2], [N,K/2] with atom-layout scales.
 // `fusion` (may be null) adds the reduce-scatter epilogue and / or the all-gather prologue described at the top.
-extern "C" int telb_gemm_skinny_fused(int kind, const void* x, const void* x_sf, const void* w, const void* w_sf, void* out, int M,
-                                      int N, int K, const float* alpha, const void* bias, const void* residual, int is_bf16,
-                                      int* status, int force_ranks, const TelbGemmFusion* fusion, cudaStream_t stream) {
+struct SkinnySwiglu {
+    uint8_t* xq;
+    uint8_t* sf;
+    const float* gs;
+};
+
+static int gemm_skinny_impl(int kind, const void* x, const void* x_sf, const void* w, const void* w_sf, void* out, int M,
+                            int N, int K, const float* alpha, const void* bias, const void* residual, int is_bf16,
+                            int* status, int force_ranks, const TelbGemmFusion* fusion, int group, cudaStream_t stream,
+                            const SkinnySwiglu* sw = nullptr) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (sw && (M > 64 || N % 128 || residual)) return fail("telb_gemm_skinny: the SwiGLU epilogue needs M <= 64, N % 128 == 0 and no residual");
     if (M > 128) return fail("telb_gemm_skinny: M must be <= 128");
     if (fusion && fusion->rs_world > 1) {
         if (residual) return fail("telb_gemm_skinny: reduce-scatter epilogue takes no residual");
@@ -519,6 +694,13 @@ extern "C" int telb_gemm_skinny_fused(int kind, const void* x, const void* x_sf,
     p.residual = residual;
     p.out_bf16 = is_bf16;
     p.status = status;
+    if (sw) {
+        p.sw_xq = sw->xq;
+        p.sw_sf = sw->sf;
+        p.sw_gs = sw->gs;
+        p.sw_ld = N / 4;                              // (N / 2 outputs) / 2 bytes per row
+        p.sw_k64_pad = telb_nvfp4_k64_pad(N / 2);
+    }
     if (fusion) {
         for (int i = 0; i < 8; ++i) p.rs_out[i] = fusion->rs_out[i];
         p.rs_world = fusion->rs_world;
@@ -531,7 +713,18 @@ extern "C" int telb_gemm_skinny_fused(int kind, const void* x, const void* x_sf,
         if (p.ag_flags && (p.ag_world < 1 || p.ag_rows_per_rank <= 0)) return fail("telb_gemm_skinny: bad all-gather description");
     }
     CUtensorMap tw, tx;
-    if (kind == 1) {
+    if (kind == 2) {
+        // w: packed INT4 [N / 2, K] bytes (row r: output rows 2r low nibble, 2r + 1 high nibble); w_sf: 16-bit scales [N, K / group]
+        if (N % 2 || K % 64) return fail("telb_gemm_skinny: INT4 weights need an even N and K % 64 == 0");
+        if (group < 64 || group % 64 || K % group) return fail("telb_gemm_skinny: INT4 group size must be a multiple of 64 that divides K");
+        p.kb_total = K / 64;
+        p.w_scale = w_sf;
+        p.group = group;
+        p.groups_per_row = K / group;
+        const CUtensorMapDataType dt = is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        if (make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w, N / 2, K, K, 64, 64, CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
+        if (make_tmap_2d(&tx, dt, 2, x, M, K, (uint64_t)K * 2, bn, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+    } else if (kind == 1) {
         if (K % 32) return fail("telb_gemm_skinny: NVFP4 needs K % 32 == 0");
         p.kb_total = (K + 255) / 256;
         p.sf_w = (const uint8_t*)w_sf;
@@ -551,7 +744,53 @@ extern "C" int telb_gemm_skinny_fused(int kind, const void* x, const void* x_sf,
     int ranks = choose_ranks(tiles, p.kb_total, force_ranks);
     p.kb_per_rank = (p.kb_total + ranks - 1) / ranks;
     p.ranks = (p.kb_total + p.kb_per_rank - 1) / p.kb_per_rank;
+    if (kind == 2) return dispatch_skinny<2>(tw, tx, p, bn, stream);
     return kind == 1 ? dispatch_skinny<1>(tw, tx, p, bn, stream) : dispatch_skinny<0>(tw, tx, p, bn, stream);
+}
+
+extern "C" int telb_gemm_skinny_fused(int kind, const void* x, const void* x_sf, const void* w, const void* w_sf, void* out, int M,
+                                      int N, int K, const float* alpha, const void* bias, const void* residual, int is_bf16,
+                                      int* status, int force_ranks, const TelbGemmFusion* fusion, cudaStream_t stream) {
+    if (kind != 0 && kind != 1) return fail("telb_gemm_skinny_fused: kind must be 0 (16-bit) or 1 (NVFP4)");
+    return gemm_skinny_impl(kind, x, x_sf, w, w_sf, out, M, N, K, alpha, bias, residual, is_bf16, status, force_ranks, fusion, 0, stream);
+}
+
+// Decode-size gate/up projection with SwiGLU + NVFP4 quantisation in the epilogue (M <= 64): w holds 2 * inter rows in which
+// blocks of 64 gate rows alternate with the 64 matching up rows; the result is quantised silu(gate) * up [M, inter] as packed
+// codes out_xq [M, inter / 2] and atom-layout scales out_sf (pre-zeroed by the caller when inter % 256 leaves padding).
+extern "C" int telb_gemm_skinny_swiglu(int kind, const void* x, const void* x_sf, const void* w, const void* w_sf, const float* alpha,
+                                       void* out_xq, void* out_sf, const float* out_global_scale, int M, int N, int K, int is_bf16,
+                                       int* status, const TelbGemmFusion* fusion, cudaStream_t stream) {
+    if (kind != 0 && kind != 1) return fail("telb_gemm_skinny_swiglu: kind must be 0 (16-bit) or 1 (NVFP4)");
+    if (fusion && fusion->rs_world > 1) return fail("telb_gemm_skinny_swiglu: no reduce-scatter on a column-parallel projection");
+    SkinnySwiglu sw{static_cast<uint8_t*>(out_xq), static_cast<uint8_t*>(out_sf), out_global_scale};
+    return gemm_skinny_impl(kind, x, x_sf, w, w_sf, nullptr, M, N, K, alpha, nullptr, nullptr, is_bf16, status, 0, fusion, 0, stream, &sw);
+}
+
+// W4A16 decode-size GEMM: out[M, N] = x[M, K] · dequant(wq, scales)[N, K]ᵀ (+ bias, + residual), M <= 128.  wq is the
+// ModelOpt-prepacked INT4 layout [N / 2, K] (byte row r holds output rows 2r in the low and 2r + 1 in the high nibbles,
+// codes offset by 8), scales [N, K / group] in the activation dtype.  The 4-bit codes are expanded inside the kernel.
+extern "C" int telb_gemm_skinny_int4(const void* x, const void* wq, const void* scales, void* out, int M, int N, int K, int group,
+                                     const void* bias, const void* residual, int is_bf16, int* status, int force_ranks,
+                                     cudaStream_t stream) {
+    return gemm_skinny_impl(2, x, nullptr, wq, scales, out, M, N, K, nullptr, bias, residual, is_bf16, status, force_ranks, nullptr, group, stream);
+}
+
+// wq [N / 2, K] packed INT4 + scales [N, K / group] → out [N, K] 16-bit, (q − 8) · scale.
+extern "C" int telb_int4_awq_expand(const void* wq, const void* scales, void* out, int N, int K, int group, int is_bf16,
+                                    cudaStream_t stream) {
+    if (N <= 0 || K <= 0) return 0;
+    if (N % 2 || K % 8 || group <= 0 || group % 8 || K % group) return fail("telb_int4_awq_expand: even N, K % 8 == 0 and a group that divides K are required");
+    const long long chunks = (long long)(N / 2) * (K / 8);
+    long long blocks = (chunks + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (is_bf16)
+        TELB_LAUNCH("int4_expand_kernel", (int4_expand_kernel<__nv_bfloat16>), dim3((int)blocks), dim3(256), 0, stream, (const uint8_t*)wq,
+                    (const __nv_bfloat16*)scales, (__nv_bfloat16*)out, N, K, group);
+    else
+        TELB_LAUNCH("int4_expand_kernel", (int4_expand_kernel<__half>), dim3((int)blocks), dim3(256), 0, stream, (const uint8_t*)wq,
+                    (const __half*)scales, (__half*)out, N, K, group);
+    return 0;
 }
 
 extern "C" int telb_gemm_skinny(int kind, const void* x, const void* x_sf, const void* w, const void* w_sf, void* out, int M,

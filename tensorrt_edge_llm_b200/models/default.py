@@ -69,6 +69,10 @@ class Attention(nn.Module):
         q = ops.rope_kv_write(qkv, kv_layer, meta, cos_sin, self.num_q_heads, self.num_kv_heads, self.head_dim,
                               None if self.q_norm is None else self.q_norm.weight,
                               None if self.k_norm is None else self.k_norm.weight, self.eps)
+        gs = self.o_proj.fused_input_scale() if hasattr(self.o_proj, "fused_input_scale") else None
+        if gs is not None and q.is_cuda and ops.cuda_ops().decode_attention_quant_ok(q.shape, kv_layer.shape[2], meta):
+            # decode step into an NVFP4 projection: the attention epilogue quantises for it
+            return self.o_proj(ops.cuda_ops().paged_attention_quant(q, kv_layer, meta, self.scale, self.sliding_window, gs))
         o = ops.paged_attention(q, kv_layer, meta, self.scale, self.sliding_window)
         return self.o_proj(o.reshape(o.shape[0], -1))
 
@@ -100,7 +104,10 @@ class MLP(nn.Module):
             if gp.gate_up_interleaved:
                 scale = self.down_proj.fused_input_scale()
                 rows = x.shape[0]
-                if rows > 128 and not isinstance(x, torch.Tensor):
+                # NVFP4 rows in: prefill sizes fuse in the wide kernel's epilogue, decode sizes in the skinny kernel's
+                small = (rows <= gp.SWIGLU_SMALL_MAX and gp.bias is None
+                         and os.environ.get("TELB_DISABLE_SWIGLU_DECODE_FUSION", "0") != "1")
+                if not isinstance(x, torch.Tensor) and (rows > 128 or small):
                     return self.down_proj(gp.forward_swiglu(x, scale))
                 return self.down_proj(ops.swiglu(gp(x), scale, interleaved=True))
         gu = gp(x)

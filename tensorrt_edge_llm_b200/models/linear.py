@@ -211,9 +211,15 @@ class NVFP4Linear(LinearBase):
                 self.gate_up_interleaved = True
             self._gpu_weight_sf = ops.cuda_ops().nvfp4_swizzle_scales(self.weight_scale)
 
+    SWIGLU_SMALL_MAX = 64        # rows up to which the decode-size kernel carries the SwiGLU epilogue
+
     def forward_swiglu(self, x, out_scale: torch.Tensor):
-        """``quantise(silu(gate) * up)`` of this (interleaved) gate/up projection for NVFP4 input rows ``x`` (more than 128)."""
-        return ops.cuda_ops().gemm_nvfp4_swiglu(x, self.weight, self._gpu_weight_sf, self.alpha, out_scale, getattr(x, "ag_wait", None))
+        """``quantise(silu(gate) * up)`` of this (interleaved) gate/up projection for NVFP4 input rows ``x``: more than 128
+        rows in the prefill kernel's epilogue, up to 64 rows in the decode-size kernel's."""
+        cu = ops.cuda_ops()
+        if x.shape[0] <= self.SWIGLU_SMALL_MAX:
+            return cu.gemm_skinny_swiglu(x, self.weight, self._gpu_weight_sf, self.alpha, out_scale, getattr(x, "ag_wait", None))
+        return cu.gemm_nvfp4_swiglu(x, self.weight, self._gpu_weight_sf, self.alpha, out_scale, getattr(x, "ag_wait", None))
 
     def fused_input_scale(self):
         return self.input_scale if (self.quantize_activations and self.weight.is_cuda) else None
@@ -252,8 +258,10 @@ class Int4AwqLinear(LinearBase):
         self.register_buffer("pre_quant_scale", torch.ones(self.in_features, dtype=dtype))
         self.bias = nn.Parameter(torch.zeros(self.out_features, dtype=dtype), requires_grad=False) if bias else None
         self._dense = None
+        self._pqs_is_one = None          # pre_quant_scale of all ones (a checkpoint without AWQ smoothing): skip the multiply
 
     def load_from(self, tensors):
+        self._pqs_is_one = None
         self.weight.copy_(torch.cat([self.shard_out_in(t["weight"].view(torch.uint8)) for t in tensors], 0))
         self.weight_scale.copy_(torch.cat([self.shard_out_in(t["weight_scale"]) for t in tensors], 0).to(self.weight_scale.dtype))
         if "pre_quant_scale" in tensors[0]:
@@ -277,14 +285,13 @@ class Int4AwqLinear(LinearBase):
         return ref.int4_awq_dequantize(self.weight, self.weight_scale, None, self.group)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        xs = (x.float() * self.pre_quant_scale.float()).to(x.dtype)
+        if self._pqs_is_one is None:
+            self._pqs_is_one = bool((self.pre_quant_scale == 1).all())
+        xs = x if self._pqs_is_one else (x.float() * self.pre_quant_scale.float()).to(x.dtype)
         if x.is_cuda:
-            # W4A16: the 4-bit groups are expanded to 16-bit once, when the layer first runs on the GPU, and the
-            # tcgen05 GEMM then streams 16-bit weights (B200 has the memory; decode pays 4x the weight bytes of a
-            # dequantise-in-kernel path, prefill is unaffected)
-            if self._dense is None or self._dense.device != x.device:
-                self._dense = self.dequantized_weight().to(x.dtype).contiguous()
-            return ops.linear(xs, self._dense, self.bias)
+            # W4A16 with the weights kept in 4 bits: decode-size steps expand the codes tile by tile inside the GEMM
+            # kernel (only 4-bit weights cross HBM); prefill-size steps expand into a temporary and run the dense GEMM
+            return ops.cuda_ops().gemm_int4_awq(xs, self.weight, self.weight_scale, self.group, bias=self.bias)
         y = xs.float() @ self.dequantized_weight().t()
         if self.bias is not None:
             y = y + self.bias.float()

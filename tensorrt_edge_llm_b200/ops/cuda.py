@@ -291,6 +291,40 @@ def paged_attention(q, kv_layer, meta: StepMeta, scale, sliding_window=None, sin
     return out
 
 
+def decode_attention_quant_ok(q_shape, hkv: int, meta: StepMeta) -> bool:
+    """Whether :func:`paged_attention_quant` covers this step (the decode-shaped kernel, head_dim 128)."""
+    t, hq, d = q_shape
+    group = hq // hkv
+    return (meta.tree_mask is None and d == 128 and meta.max_q_len * group <= 16 and 16 % group == 0
+            and os.environ.get("TELB_DISABLE_ATTN_QUANT_FUSION", "0") != "1")
+
+
+def paged_attention_quant(q, kv_layer, meta: StepMeta, scale, sliding_window, out_scale: torch.Tensor,
+                          splits: Optional[int] = None) -> "QuantActs":
+    """Decode-shaped paged attention whose epilogue (or split merge) writes NVFP4 rows ``[T, Hq * D]`` quantised with the
+    global scale ``out_scale`` of the projection that follows, instead of 16-bit rows and a quantisation kernel."""
+    q = q.contiguous()
+    t, hq, d = q.shape
+    hkv = kv_layer.shape[2]
+    if not decode_attention_quant_ok(q.shape, hkv, meta):
+        raise ValueError("step is not decode-shaped")
+    if splits is None:
+        splits = _decode_splits(meta, hkv)
+    L = lib()
+    L.telb_nvfp4_sf_bytes.restype = c_ll
+    width = hq * d
+    xq = torch.empty(t, width // 2, dtype=torch.uint8, device=q.device)
+    sf = _sf_buffer(L.telb_nvfp4_sf_bytes(c_ll(t), c_int(width)), width, q.device)
+    ws = Workspace.get(q.device)
+    _check(L.telb_paged_attention_decode_quant(
+        _p(q), _p(kv_layer), _p(xq), _p(sf), _p(out_scale), _p(meta.q_start), _p(meta.q_len), _p(meta.past_len), _p(meta.page_table),
+        c_int(meta.num_seqs), c_int(t), c_int(meta.max_q_len), c_int(kv_layer.shape[0]), c_int(meta.page_table.shape[1]),
+        c_int(meta.page_size), c_int(hq), c_int(hkv), c_int(d), c_float(scale), c_int(sliding_window or 0), c_int(splits),
+        _p(ws.attn_ws), c_ll(ws.attn_ws.numel()), c_int(_is_bf16(q)), _p(ws.status), _stream()),
+        "paged_attention_decode_quant", 2 if splits > 1 else 1)
+    return QuantActs(xq, sf, (t, width), q.dtype)
+
+
 def argmax(logits: torch.Tensor) -> torch.Tensor:
     assert logits.dim() == 2 and logits.stride(1) == 1
     out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
@@ -372,6 +406,23 @@ def gemm_nvfp4_swiglu(x: "QuantActs", weight: torch.Tensor, w_sf: torch.Tensor, 
     _check(L.telb_gemm_nvfp4_swiglu(_p(x.xq), _p(x.sf), _p(weight), _p(w_sf), _p(alpha), _p(xq), _p(sf), _p(out_scale), c_int(m), c_int(n),
                                     c_int(k), c_int(1 if x.dtype == torch.bfloat16 else 0), _p(ws.status),
                                     ctypes.byref(fusion) if fusion is not None else c_vp(0), _stream()), "gemm_nvfp4_swiglu")
+    return QuantActs(xq, sf, (m, inter), x.dtype)
+
+
+def gemm_skinny_swiglu(x: "QuantActs", weight: torch.Tensor, w_sf: torch.Tensor, alpha: torch.Tensor, out_scale: torch.Tensor,
+                       fusion=None) -> "QuantActs":
+    """Decode-size form of :func:`gemm_nvfp4_swiglu` (M <= 64): the swapped-operand, cluster split-K kernel applies SwiGLU and
+    quantises in its epilogue, so a decode step has no separate activation kernel between the gate/up and down projections."""
+    m, n, k = x.xq.shape[0], weight.shape[0], x.xq.shape[1] * 2
+    inter = n // 2
+    L = lib()
+    L.telb_nvfp4_sf_bytes.restype = c_ll
+    xq = torch.empty(m, inter // 2, dtype=torch.uint8, device=weight.device)
+    sf = _sf_buffer(L.telb_nvfp4_sf_bytes(c_ll(m), c_int(inter)), inter, weight.device)
+    ws = Workspace.get(weight.device)
+    _check(L.telb_gemm_skinny_swiglu(c_int(1), _p(x.xq), _p(x.sf), _p(weight), _p(w_sf), _p(alpha), _p(xq), _p(sf), _p(out_scale), c_int(m),
+                                     c_int(n), c_int(k), c_int(1 if x.dtype == torch.bfloat16 else 0), _p(ws.status),
+                                     ctypes.byref(fusion) if fusion is not None else c_vp(0), _stream()), "gemm_skinny_swiglu")
     return QuantActs(xq, sf, (m, inter), x.dtype)
 
 
@@ -472,6 +523,31 @@ def gemm_skinny(x, weight, *, x_sf=None, w_sf=None, alpha=None, bias=None, resid
                                   _p(alpha), _p(bias), _p(residual), c_int(1 if dt == torch.bfloat16 else 0), _p(ws.status),
                                   c_int(ranks), _stream()), "gemm_skinny")
     return out
+
+
+def gemm_int4_awq(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, group: int, bias=None, residual=None, ranks: int = 0):
+    """W4A16 linear on ModelOpt-prepacked INT4 weights (``wq [N/2, K]`` uint8, ``scales [N, K/group]`` in ``x``'s dtype).
+    Decode-size steps (M <= 128) expand the 4-bit tiles inside the GEMM kernel, so only 4-bit weights cross HBM; larger
+    steps expand the matrix once into a temporary and run the dense tensor-core GEMM (compute-bound there)."""
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    m, k = x2.shape
+    n = wq.shape[0] * 2
+    if scales.dtype != x.dtype:
+        scales = scales.to(x.dtype)
+    ok = n % 2 == 0 and k % 64 == 0 and group >= 64 and group % 64 == 0 and k % group == 0
+    if m <= 128 and ok:
+        out = torch.empty(m, n, dtype=x.dtype, device=x.device)
+        ws = Workspace.get(x.device)
+        _check(lib().telb_gemm_skinny_int4(_p(x2), _p(wq), _p(scales.contiguous()), _p(out), c_int(m), c_int(n), c_int(k), c_int(group), _p(bias),
+                                           _p(residual), c_int(_is_bf16(x)), _p(ws.status), c_int(ranks), _stream()), "gemm_skinny_int4")
+        return out.reshape(*lead, n)
+    dense = torch.empty(n, k, dtype=x.dtype, device=x.device)
+    _check(lib().telb_int4_awq_expand(_p(wq), _p(scales.contiguous()), _p(dense), c_int(n), c_int(k), c_int(group), c_int(_is_bf16(x)), _stream()),
+           "int4_awq_expand")
+    return gemm(x2, dense, bias=bias, residual=residual).reshape(*lead, n)
 
 
 # ---- sampling ----------------------------------------------------------------------------------

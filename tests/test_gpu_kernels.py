@@ -175,6 +175,35 @@ def test_paged_attention_decode_kernel(cu, case, dtype):
     _sync_check(cu)
 
 
+def _sf_rows_index(rows, k):
+    """Byte offsets of the scales of rows [0, rows) in the 512-byte atom layout (padding rows hold anything)."""
+    r = torch.arange(rows).view(-1, 1)
+    kb = torch.arange(k // 16).view(1, -1)
+    k64 = (k + 255) // 256 * 4
+    off = ((r >> 7) * k64 + (kb >> 2)) * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 + (kb & 3)
+    return off.reshape(-1).cuda()
+
+
+@pytest.mark.parametrize("case", DECODE_CASES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_paged_attention_decode_nvfp4_output(cu, case, dtype):
+    """The decode kernel's NVFP4 epilogue (and the quantising split merge) equal the 16-bit output passed through
+    the stand-alone quantiser, bit for bit."""
+    q_lens, past_lens, hq, hkv, page = case
+    q, kv, meta = _paged_setup(q_lens, past_lens, hq, hkv, 128, page, dtype, seed=sum(past_lens))
+    scale = 128 ** -0.5
+    gs = torch.tensor(0.004, device="cuda")
+    for s in (1, 3):
+        out = cu.paged_attention(q, kv, meta, scale, kernel="decode", splits=s)
+        xq_ref, sf_ref = cu.nvfp4_quantize(out.reshape(out.shape[0], -1), gs)
+        qa = cu.paged_attention_quant(q, kv, meta, scale, None, gs, splits=s)
+        torch.cuda.synchronize()
+        assert qa.shape == (q.shape[0], hq * 128)
+        assert torch.equal(qa.xq, xq_ref), s
+        assert torch.equal(qa.sf[_sf_rows_index(q.shape[0], hq * 128)], sf_ref[_sf_rows_index(q.shape[0], hq * 128)]), s
+    _sync_check(cu)
+
+
 def test_paged_attention_splits_window_tree(cu):
     q, kv, meta = _paged_setup([1, 1], [900, 333], 32, 8, 128, 64, torch.bfloat16, seed=9)
     scale = 128 ** -0.5
@@ -350,6 +379,26 @@ def test_gemm_skinny_nvfp4(cu, m, n, k, ranks):
     _sync_check(cu)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,n,k,group,ranks", [(1, 4096, 4096, 128, 0), (8, 6144, 4096, 128, 3), (64, 4096, 12288, 128, 0), (100, 1000, 512, 64, 1),
+                                               (33, 2048, 2048, 128, 8), (300, 1024, 1024, 128, 0), (16, 24576, 4096, 128, 0)])
+def test_gemm_int4_awq_in_kernel(cu, m, n, k, group, ranks, dtype):
+    """W4A16 on ModelOpt-prepacked INT4 weights: decode sizes expand the 4-bit tiles inside the GEMM kernel (every cluster
+    size), larger steps go through the expand kernel + dense GEMM; both against the fp32 statement (q - 8) * scale."""
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    x = torch.randn(m, k, device="cuda", generator=g).to(dtype)
+    wq = torch.randint(0, 256, (n // 2, k), device="cuda", generator=g, dtype=torch.uint8)
+    scales = (torch.rand(n, k // group, device="cuda", generator=g) * 0.02 + 0.005).to(dtype)
+    bias = torch.randn(n, device="cuda", generator=g).to(dtype)
+    wd = ref.int4_awq_dequantize(wq, scales, None, group)
+    want = x.float() @ wd.t() + bias.float()
+    got = cu.gemm_int4_awq(x, wq, scales, group, bias=bias, ranks=ranks)
+    torch.cuda.synchronize()
+    assert got.shape == (m, n)
+    assert _rel_err(got, want) < 6e-3, _rel_err(got, want)
+    _sync_check(cu)
+
+
 def test_skinny_chain_in_cuda_graph(cu):
     """Back-to-back decode GEMMs launched with programmatic dependent launch, captured and replayed."""
     g = torch.Generator(device="cuda").manual_seed(0)
@@ -435,6 +484,31 @@ def test_gemm_nvfp4_swiglu_epilogue_matches_unfused_chain():
     gu_il = cu.gemm_nvfp4(xq, xsf, w_il, cu.nvfp4_swizzle_scales(sf_il), a_il, torch.float16, mode=1)
     small = cu.swiglu_quant(gu_il, gs_out, interleaved=True)
     assert torch.equal(small.xq, want.xq)
+    cu.Workspace.get(torch.device("cuda", 0)).check_status()
+
+
+@pytest.mark.parametrize("m,k,inter", [(1, 512, 384), (8, 4096, 1536), (33, 1024, 768), (64, 4096, 3072), (64, 512, 128)])
+def test_gemm_skinny_swiglu_epilogue_matches_unfused_chain(m, k, inter):
+    """Decode-size gate/up GEMM with SwiGLU + NVFP4 quantisation in its epilogue == skinny GEMM → swiglu_quant, bit for bit
+    (single CTA per tile and every cluster size the chooser picks for these shapes)."""
+    from tensorrt_edge_llm_b200.ops import cuda as cu
+    g = torch.Generator(device="cuda").manual_seed(m + k)
+    x = torch.randn(m, k, device="cuda", generator=g).half()
+    wq = torch.randint(0, 256, (2 * inter, k // 2), device="cuda", generator=g, dtype=torch.uint8)
+    wsf = torch.randint(48, 58, (2 * inter, k // 16), device="cuda", generator=g, dtype=torch.uint8)
+    alpha = (torch.rand(2 * inter, device="cuda", generator=g) * 0.02 + 0.01)
+    gs_in = torch.full((1,), 1.0 / 448, device="cuda")
+    gs_out = torch.full((1,), 0.004, device="cuda")
+    xq, xsf = cu.nvfp4_quantize(x, gs_in)
+    acts = cu.QuantActs(xq, xsf, (m, k), torch.float16)
+    atoms = cu.nvfp4_swizzle_scales(wsf)
+    gu = cu.gemm_nvfp4(xq, xsf, wq, atoms, alpha, torch.float16)                 # decode-size kernel, interleaved rows
+    want = cu.swiglu_quant(gu, gs_out, interleaved=True)
+    got = cu.gemm_skinny_swiglu(acts, wq, atoms, alpha, gs_out)
+    torch.cuda.synchronize()
+    assert torch.equal(got.xq, want.xq)
+    idx = _sf_rows_index(m, inter)                         # rows past m inside the 128-row atom hold anything
+    assert torch.equal(got.sf.view(torch.uint8)[idx], want.sf.view(torch.uint8)[idx])
     cu.Workspace.get(torch.device("cuda", 0)).check_status()
 
 
