@@ -1,6 +1,7 @@
 """The allocation-free arg-max entry point (fixed device scratch) against the regular entry point.
 Collected last on purpose: it must give the same answer alone and after every other GPU test."""
 import ctypes
+import gc
 
 import pytest
 import torch
@@ -36,11 +37,16 @@ def test_static_argmax_matches_regular_entry_point(dtype, rows, vocab):
     want2 = cuda.argmax(logits2)
     out2 = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
     torch.cuda.synchronize()
-    before = torch.cuda.memory_allocated()
-    assert _call(lib, logits2, out2) == 0
-    assert _call(lib, logits, out) == 0
-    torch.cuda.synchronize()
-    assert torch.cuda.memory_allocated() == before
+    gc.collect()                       # cyclic garbage of earlier tests must not be freed inside the measured window
+    gc.disable()
+    try:
+        before = torch.cuda.memory_allocated()
+        assert _call(lib, logits2, out2) == 0
+        assert _call(lib, logits, out) == 0
+        torch.cuda.synchronize()
+        assert torch.cuda.memory_allocated() == before
+    finally:
+        gc.enable()
     assert torch.equal(out2, want2) and torch.equal(out, want)
 
 
