@@ -267,13 +267,11 @@ def bench_moe(args):
     w, idx = cu.moe_route_softmax_topk(logits, k, True)
     ws = cu.moe_align(idx, e, 0, e)
     a = cu.moe_gather(x, ws, k, b.input_scale)
-    h1 = cu.gemm_grouped(a, b.w13, ws, e, alpha=b.w13_alpha, w_sf=b._w13_sf)
-    a2 = cu.swiglu_quant(h1, b.down_input_scale, moe_ws=ws)
+    a2 = b.expert_fc1(a, ws)
     y = cu.gemm_grouped(a2, b.w2, ws, e, alpha=b.w2_alpha, w_sf=b._w2_sf)
     parts = {"gate": lambda: b.gate(x), "route": lambda: cu.moe_route_softmax_topk(logits, k, True),
              "align": lambda: cu.moe_align(idx, e, 0, e), "gather_quant": lambda: cu.moe_gather(x, ws, k, b.input_scale),
-             "fc1": lambda: cu.gemm_grouped(a, b.w13, ws, e, alpha=b.w13_alpha, w_sf=b._w13_sf),
-             "swiglu_quant": lambda: cu.swiglu_quant(h1, b.down_input_scale, moe_ws=ws),
+             "fc1_swiglu_quant": lambda: b.expert_fc1(a, ws),
              "fc2": lambda: cu.gemm_grouped(a2, b.w2, ws, e, alpha=b.w2_alpha, w_sf=b._w2_sf),
              "combine": lambda: cu.moe_combine(y, ws, w)}
     print(json.dumps({"kernel": "moe_parts_us", "tokens": m, "tiles_in_use": int(ws.counts.item()) // 128,

@@ -195,6 +195,7 @@ class ModelConfig:
     tie_word_embeddings: bool = False
     has_qk_norm: bool = False
     attention_bias: bool = False
+    attention_sink_bias: bool = False      # per-query-head learned sink logit joining every softmax denominator
     sliding_window: Optional[int] = None
     layer_windows: List[int] = field(default_factory=list)  # per layer: sliding window in tokens, 0 = full attention (empty = `sliding_window` everywhere)
     mrope_section: List[int] = field(default_factory=list)   # multimodal RoPE: rotary pairs per (temporal, height, width) component
@@ -384,7 +385,8 @@ class ModelConfig:
             max_position_embeddings=int(llm.get("max_position_embeddings", 32768)),
             tie_word_embeddings=bool(hf.get("tie_word_embeddings", llm.get("tie_word_embeddings", False))),
             has_qk_norm=bool(has_qk_norm),
-            attention_bias=bool(llm.get("attention_bias", str(model_type).startswith("qwen2"))),     # Qwen2 family (text, MoE, VL): q/k/v carry a bias
+            attention_bias=bool(llm.get("attention_bias", str(model_type).startswith("qwen2"))),
+            attention_sink_bias=bool(llm.get("attention_sink_bias", False)),     # Qwen2 family (text, MoE, VL): q/k/v carry a bias
             sliding_window=llm.get("sliding_window") if (llm.get("use_sliding_window", False) or extra) else None,
             hidden_act=llm.get("hidden_activation") or llm.get("hidden_act", llm.get("mlp_hidden_act", "silu")),
             **extra,

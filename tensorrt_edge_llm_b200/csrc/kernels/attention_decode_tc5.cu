@@ -41,6 +41,7 @@ struct DecParams {
     int splits, total_tokens, window;
     int num_seqs, num_items;        // items = sequences x KV heads x splits, walked by persistent CTAs
     float scale_log2;
+    const float* sinks;             // [Hq] fp32 per-head sink logits (natural-log units), or null
     int* status;
     // Optional timeline of CTA 0: trace[role][tile][event] in ns since the CTA started (role 0 producer,
     // 1 MMA issuer, 2 softmax; 4 events per tile, 64 tiles at most).  Null in normal use.
@@ -466,10 +467,26 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
                 for (int c = 0; c < NC; ++c) {
                     if (c < ncol) {
                         const float l = s_sum[c] + s_sum[16 + c] + s_sum[32 + c] + s_sum[48 + c];
-                        const float val = (it.ntiles > 0 && l > 0.f) ? __uint_as_float(o[c]) / l : 0.f;
                         const int qi = c >> gshift, g = c - (qi << gshift);
                         const size_t tok = (size_t)it.qrow0 + qi;
                         const int head = it.kvh * p.group + g;
+                        const bool have = it.ntiles > 0 && l > 0.f;
+                        float inv = have ? 1.f / l : 0.f;
+                        float lse = have ? m_used[c] + log2f(l) : -INFINITY;
+                        if (p.sinks != nullptr && it.split == 0) {
+                            // the sink is one more logit with no value row: it only grows the denominator (first split only)
+                            const float z = p.sinks[head] * 1.44269504f;
+                            if (have) {
+                                const float m2 = fmaxf(m_used[c], z);
+                                const float os = exp2f(m_used[c] - m2);
+                                const float l2 = l * os + exp2f(z - m2);
+                                inv = os / l2;
+                                lse = m2 + log2f(l2);
+                            } else {
+                                lse = z;
+                            }
+                        }
+                        const float val = have ? __uint_as_float(o[c]) * inv : 0.f;
                         if (p.splits == 1 && p.oq != nullptr) {
                             // the output projection reads NVFP4: quantise here (16 consecutive dims = 16 consecutive lanes),
                             // with the rounding of the 16-bit store the unfused path would have made first
@@ -483,9 +500,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
                             reinterpret_cast<T*>(p.out)[(tok * p.hq + head) * D + r] = Cvt<T>::from_f(val);
                         } else {
                             p.ws_o[(((size_t)it.split * p.total_tokens + tok) * p.hq + head) * D + r] = val;
-                            if (r == 0)
-                                p.ws_lse[((size_t)it.split * p.total_tokens + tok) * p.hq + head] =
-                                    (it.ntiles > 0 && l > 0.f) ? m_used[c] + log2f(l) : -INFINITY;
+                            if (r == 0) p.ws_lse[((size_t)it.split * p.total_tokens + tok) * p.hq + head] = lse;
                         }
                     }
                 }
@@ -563,7 +578,7 @@ extern "C" int telb_paged_attention_decode_traced(const void* q, const void* kv_
                                                   int total_tokens, int max_q_len, int num_pages, int max_pages, int page_size,
                                                   int hq, int hkv, int d, float scale, int window, int splits, float* ws,
                                                   long long ws_floats, int is_bf16, int* status, unsigned long long* trace,
-                                                  cudaStream_t stream);
+                                                  const float* sinks, cudaStream_t stream);
 
 // Decode-shaped steps only: max_q_len * (Hq/Hkv) <= 16.  Same tensors as telb_paged_attention.
 extern "C" int telb_paged_attention_decode(const void* q, const void* kv_layer, void* out, const int* q_start,
@@ -573,13 +588,13 @@ extern "C" int telb_paged_attention_decode(const void* q, const void* kv_layer, 
                                            long long ws_floats, int is_bf16, int* status, cudaStream_t stream) {
     return telb_paged_attention_decode_traced(q, kv_layer, out, q_start, q_len, past_len, page_table, num_seqs, total_tokens, max_q_len,
                                               num_pages, max_pages, page_size, hq, hkv, d, scale, window, splits, ws, ws_floats, is_bf16,
-                                              status, nullptr, stream);
+                                              status, nullptr, nullptr, stream);
 }
 
 static int decode_impl(const void* q, const void* kv_layer, void* out, void* oq, void* osf, const float* ogs, const int* q_start,
                        const int* q_len, const int* past_len, const int* page_table, int num_seqs, int total_tokens, int max_q_len,
                        int num_pages, int max_pages, int page_size, int hq, int hkv, int d, float scale, int window, int splits, float* ws,
-                       long long ws_floats, int is_bf16, int* status, unsigned long long* trace, cudaStream_t stream);
+                       long long ws_floats, int is_bf16, int* status, unsigned long long* trace, const float* sinks, cudaStream_t stream);
 
 // Same call with a timeline buffer (3 x 64 x 4 u64, zeroed by the caller) filled by the first CTA.
 extern "C" int telb_paged_attention_decode_traced(const void* q, const void* kv_layer, void* out, const int* q_start,
@@ -587,9 +602,9 @@ extern "C" int telb_paged_attention_decode_traced(const void* q, const void* kv_
                                                   int total_tokens, int max_q_len, int num_pages, int max_pages, int page_size,
                                                   int hq, int hkv, int d, float scale, int window, int splits, float* ws,
                                                   long long ws_floats, int is_bf16, int* status, unsigned long long* trace,
-                                                  cudaStream_t stream) {
+                                                  const float* sinks, cudaStream_t stream) {
     return decode_impl(q, kv_layer, out, nullptr, nullptr, nullptr, q_start, q_len, past_len, page_table, num_seqs, total_tokens, max_q_len,
-                       num_pages, max_pages, page_size, hq, hkv, d, scale, window, splits, ws, ws_floats, is_bf16, status, trace, stream);
+                       num_pages, max_pages, page_size, hq, hkv, d, scale, window, splits, ws, ws_floats, is_bf16, status, trace, sinks, stream);
 }
 
 // Decode attention whose output is written as NVFP4 only (packed codes out_xq [T, Hq * D / 2], atom-layout scales out_sf over
@@ -599,16 +614,16 @@ extern "C" int telb_paged_attention_decode_quant(const void* q, const void* kv_l
                                                  const int* q_start, const int* q_len, const int* past_len, const int* page_table,
                                                  int num_seqs, int total_tokens, int max_q_len, int num_pages, int max_pages, int page_size,
                                                  int hq, int hkv, int d, float scale, int window, int splits, float* ws, long long ws_floats,
-                                                 int is_bf16, int* status, cudaStream_t stream) {
+                                                 int is_bf16, int* status, const float* sinks, cudaStream_t stream) {
     if (!out_xq || !out_sf || !out_global_scale) return fail("telb_paged_attention_decode_quant: output buffers and scale are required");
     return decode_impl(q, kv_layer, nullptr, out_xq, out_sf, out_global_scale, q_start, q_len, past_len, page_table, num_seqs, total_tokens,
-                       max_q_len, num_pages, max_pages, page_size, hq, hkv, d, scale, window, splits, ws, ws_floats, is_bf16, status, nullptr, stream);
+                       max_q_len, num_pages, max_pages, page_size, hq, hkv, d, scale, window, splits, ws, ws_floats, is_bf16, status, nullptr, sinks, stream);
 }
 
 static int decode_impl(const void* q, const void* kv_layer, void* out, void* oq, void* osf, const float* ogs, const int* q_start,
                        const int* q_len, const int* past_len, const int* page_table, int num_seqs, int total_tokens, int max_q_len,
                        int num_pages, int max_pages, int page_size, int hq, int hkv, int d, float scale, int window, int splits, float* ws,
-                       long long ws_floats, int is_bf16, int* status, unsigned long long* trace, cudaStream_t stream) {
+                       long long ws_floats, int is_bf16, int* status, unsigned long long* trace, const float* sinks, cudaStream_t stream) {
     if (num_seqs <= 0 || total_tokens <= 0) return 0;
     if (d != 128) return fail("telb_paged_attention_decode: head_dim must be 128");
     if (page_size != 64 && page_size != 128) return fail("telb_paged_attention_decode: page size must be 64 or 128");
@@ -622,6 +637,7 @@ static int decode_impl(const void* q, const void* kv_layer, void* out, void* oq,
     p.osf = static_cast<uint8_t*>(osf);
     p.ogs = ogs;
     p.ok64 = telb_nvfp4_k64_pad(hq * d);
+    p.sinks = sinks;
     p.q_start = q_start;
     p.q_len = q_len;
     p.past_len = past_len;

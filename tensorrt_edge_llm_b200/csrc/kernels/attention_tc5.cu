@@ -45,6 +45,7 @@ struct AttnParams {
     int total_tokens;
     int window;                // sliding window, 0 = none, -1 = no causal mask (every row sees every cached and new token)
     float scale_log2;          // softmax scale * log2(e)
+    const float* sinks;        // [Hq] fp32 per-head sink logits (natural-log units) joining every row's softmax denominator, or null
     int out_bf16;
     int* status;
 };
@@ -349,9 +350,23 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
             ok = mbar_wait(&p_free[(ntiles - 1) & 1], ((ntiles - 1) >> 1) & 1, abort_flag, p.status, kStatusEpilogueTimeout);
         if (ok) {
             tc_fence_after_sync();
-            const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
             const size_t tok = (size_t)qrow0 + qi;
             const int head = kvh * p.group + g;
+            float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+            float lse = l_sum > 0.f ? m_used + log2f(l_sum) : -INFINITY;
+            if (p.sinks != nullptr && split == 0 && row_valid) {
+                // the sink is one more logit with no value row: it only grows the denominator (first split only)
+                const float z = p.sinks[head] * 1.44269504f;
+                if (l_sum > 0.f) {
+                    const float m2 = fmaxf(m_used, z);
+                    const float os = exp2f(m_used - m2);
+                    const float l2 = l_sum * os + exp2f(z - m2);
+                    inv = os / l2;
+                    lse = m2 + log2f(l2);
+                } else {
+                    lse = z;
+                }
+            }
 #pragma unroll 1
             for (int c = 0; c < D / 32; ++c) {
                 float v[32];
@@ -385,8 +400,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
                 }
             }
             if (row_valid && p.splits > 1)
-                p.ws_lse[((size_t)split * p.total_tokens + tok) * p.hq + head] =
-                    l_sum > 0.f ? m_used + log2f(l_sum) : -INFINITY;
+                p.ws_lse[((size_t)split * p.total_tokens + tok) * p.hq + head] = lse;
             tc_fence_before_sync();
         }
     }
@@ -545,7 +559,7 @@ extern "C" int telb_paged_attention(const void* q, const void* kv_layer, void* o
                                     const int* tree_mask, int mask_words, int num_seqs, int total_tokens,
                                     int max_q_len, int num_pages, int max_pages, int page_size, int hq, int hkv, int d,
                                     float scale, int window, int splits, float* ws, long long ws_floats, int is_bf16,
-                                    int* status, cudaStream_t stream) {
+                                    int* status, const float* sinks, cudaStream_t stream) {
     if (num_seqs <= 0 || total_tokens <= 0) return 0;
     if (d != 64 && d != 128) return fail("telb_paged_attention: head_dim must be 64 or 128");
     if (page_size != 64 && page_size != 128) return fail("telb_paged_attention: page size must be 64 or 128");
@@ -570,6 +584,7 @@ extern "C" int telb_paged_attention(const void* q, const void* kv_layer, void* o
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.out_bf16 = is_bf16;
+    p.sinks = sinks;
     p.status = status;
     if (splits < 1) splits = 1;
     while (splits > 1 && (long long)splits * total_tokens * hq * (d + 1) > ws_floats) --splits;

@@ -450,9 +450,33 @@ extern "C" int telb_gemm_nvfp4_swiglu(const void* xq, const void* x_sf, const vo
 
 // Grouped NVFP4 GEMM for mixture-of-experts (see telb_gemm_f16_grouped): xq [rows_pad, K/2] with
 // atom-layout scales over the padded row space, wq [experts * N, K/2] with scales over experts * N rows.
+static int gemm_nvfp4_grouped_impl(const void* xq, const void* x_sf, const void* wq, const void* w_sf, void* out, int rows_pad, int N, int K,
+                                   int experts, const int* tile_expert, const float* alpha, int out_bf16, int* status, cudaStream_t stream,
+                                   const SwigluOut* sw);
+
 extern "C" int telb_gemm_nvfp4_grouped(const void* xq, const void* x_sf, const void* wq, const void* w_sf, void* out,
                                        int rows_pad, int N, int K, int experts, const int* tile_expert, const float* alpha,
                                        int out_bf16, int* status, cudaStream_t stream) {
+    return gemm_nvfp4_grouped_impl(xq, x_sf, wq, w_sf, out, rows_pad, N, K, experts, tile_expert, alpha, out_bf16, status, stream, nullptr);
+}
+
+// Grouped gate/up projection with SwiGLU and the NVFP4 quantisation of the second expert GEMM's input in the epilogue.
+// Every expert's N = 2 * inter weight rows alternate in blocks of 64 (gate features f .. f+63, then the matching up
+// features); the output is packed codes out_xq [rows_pad, inter / 2] with atom-layout scales over rows_pad rows and inter
+// columns (padding rows of a tile are not written).  Reference counterpart: the activation-fusion grouped GEMM of
+// kernelSrcs/nvfp4_moe_cutedsl/blockscaled_contiguous_gather_grouped_gemm_act_fusion.py.
+extern "C" int telb_gemm_nvfp4_grouped_swiglu(const void* xq, const void* x_sf, const void* wq, const void* w_sf, void* out_xq, void* out_sf,
+                                              const float* out_global_scale, int rows_pad, int N, int K, int experts, const int* tile_expert,
+                                              const float* alpha, int out_bf16, int* status, cudaStream_t stream) {
+    if (N % 128) return fail("telb_gemm_nvfp4_grouped_swiglu: 2 * inter must be a multiple of 128");
+    if (!out_xq || !out_sf || !out_global_scale) return fail("telb_gemm_nvfp4_grouped_swiglu: output buffers and scale are required");
+    SwigluOut sw{static_cast<uint8_t*>(out_xq), static_cast<uint8_t*>(out_sf), out_global_scale, N / 4, telb_nvfp4_k64_pad(N / 2)};
+    return gemm_nvfp4_grouped_impl(xq, x_sf, wq, w_sf, nullptr, rows_pad, N, K, experts, tile_expert, alpha, out_bf16, status, stream, &sw);
+}
+
+static int gemm_nvfp4_grouped_impl(const void* xq, const void* x_sf, const void* wq, const void* w_sf, void* out, int rows_pad, int N, int K,
+                                   int experts, const int* tile_expert, const float* alpha, int out_bf16, int* status, cudaStream_t stream,
+                                   const SwigluOut* sw) {
     if (rows_pad <= 0) return 0;
     if (K % 32 || rows_pad % kBM || N % 128) return fail("telb_gemm_nvfp4_grouped: K % 32, rows_pad % 128 and N % 128 must be 0");
     GemmParams p{};
@@ -468,6 +492,13 @@ extern "C" int telb_gemm_nvfp4_grouped(const void* xq, const void* x_sf, const v
     p.ldc_col = 1;
     p.tile_expert = tile_expert;
     p.group_rows_b = N;
+    if (sw) {
+        p.sw_xq = sw->xq;
+        p.sw_sf = sw->sf;
+        p.sw_gs = sw->gs;
+        p.sw_ld = sw->ld;
+        p.sw_k64_pad = sw->k64_pad;
+    }
     const uint64_t kbytes = (uint64_t)K / 2;
     CUtensorMap ta, tb;
     if (make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, rows_pad, kbytes, kbytes, kBM, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;

@@ -63,6 +63,12 @@ class Attention(nn.Module):
             self.k_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, cfg.compute_dtype)
         else:
             self.q_norm = self.k_norm = None
+        if getattr(cfg, "attention_sink_bias", False):
+            # one learned logit per (local) query head with no value row: it only grows the softmax denominator
+            # (reference: tensorrt_edgellm/config.py:691-692, the draft models' attention_sink_bias buffer)
+            self.register_buffer("attention_sink_bias", torch.zeros(self.num_q_heads, dtype=torch.float32))
+        else:
+            self.attention_sink_bias = None
 
     def forward(self, x: torch.Tensor, meta: StepMeta, kv_layer: torch.Tensor, cos_sin: torch.Tensor) -> torch.Tensor:
         qkv = self.qkv_proj(x)
@@ -70,10 +76,11 @@ class Attention(nn.Module):
                               None if self.q_norm is None else self.q_norm.weight,
                               None if self.k_norm is None else self.k_norm.weight, self.eps)
         gs = self.o_proj.fused_input_scale() if hasattr(self.o_proj, "fused_input_scale") else None
+        sinks = self.attention_sink_bias
         if gs is not None and q.is_cuda and ops.cuda_ops().decode_attention_quant_ok(q.shape, kv_layer.shape[2], meta):
             # decode step into an NVFP4 projection: the attention epilogue quantises for it
-            return self.o_proj(ops.cuda_ops().paged_attention_quant(q, kv_layer, meta, self.scale, self.sliding_window, gs))
-        o = ops.paged_attention(q, kv_layer, meta, self.scale, self.sliding_window)
+            return self.o_proj(ops.cuda_ops().paged_attention_quant(q, kv_layer, meta, self.scale, self.sliding_window, gs, sinks=sinks))
+        o = ops.paged_attention(q, kv_layer, meta, self.scale, self.sliding_window, sinks)
         return self.o_proj(o.reshape(o.shape[0], -1))
 
 

@@ -17,6 +17,8 @@ from __future__ import annotations
 
 from typing import Optional
 
+import os
+
 import torch
 from torch import nn
 
@@ -123,7 +125,7 @@ class MoEBlock(nn.Module):
     def _refresh_alpha(self):
         i, h = self.inter, self.cfg.hidden_size
         a13 = self.w13_scale_2.repeat_interleave(i, dim=1).reshape(-1) * self.input_scale
-        self.w13_alpha.copy_(a13)
+        self.w13_alpha.copy_(self._interleave(a13) if self._w13_interleaved else a13)
         self.w2_alpha.copy_(self.w2_scale_2.repeat_interleave(h) * self.down_input_scale)
 
     @torch.no_grad()
@@ -156,9 +158,27 @@ class MoEBlock(nn.Module):
         if self.nvfp4:
             self._refresh_alpha()
 
+    _w13_interleaved = False      # gate / up rows of every expert alternate in blocks of 64 (set by finalize on the GPU)
+
+    def _interleave(self, t: torch.Tensor, inverse: bool = False) -> torch.Tensor:
+        """[E * 2I, ...] with each expert's rows as [gate I | up I]  <->  blocks of 64 gate rows, 64 up rows, ..."""
+        e, i = self.e_local, self.inter
+        rest = t.shape[1:]
+        if inverse:
+            return t.reshape(e, i // 64, 2, 64, *rest).transpose(1, 2).reshape(e * 2 * i, *rest)
+        return t.reshape(e, 2, i // 64, 64, *rest).transpose(1, 2).reshape(e * 2 * i, *rest)
+
     def finalize(self):
         if self.nvfp4 and self.w13.is_cuda:
             cu = ops.cuda_ops()
+            if (not self._w13_interleaved and self.inter % 64 == 0
+                    and os.environ.get("TELB_DISABLE_MOE_SWIGLU_FUSION", "0") != "1"):
+                # the expert gate/up GEMM applies SwiGLU in its epilogue: a 128-wide output tile must hold 64 gate features
+                # and the matching 64 up features
+                self.w13.copy_(self._interleave(self.w13))
+                self.w13_scale.view(torch.uint8).copy_(self._interleave(self.w13_scale.view(torch.uint8)))
+                self.w13_alpha.copy_(self._interleave(self.w13_alpha))
+                self._w13_interleaved = True
             self._w13_sf = cu.nvfp4_swizzle_scales(self.w13_scale)
             self._w2_sf = cu.nvfp4_swizzle_scales(self.w2_scale)
 
@@ -167,7 +187,11 @@ class MoEBlock(nn.Module):
         i, h, e = self.inter, self.cfg.hidden_size, self.e_local
         if self.nvfp4:
             ones = torch.ones((), device=self.w13.device)
-            w13 = ref.nvfp4_dequantize(self.w13, self.w13_scale, ones) * self.w13_scale_2.repeat_interleave(i, dim=1).reshape(-1, 1)
+            w13q, w13s = self.w13, self.w13_scale
+            if self._w13_interleaved:
+                w13q = self._interleave(w13q, inverse=True)
+                w13s = self._interleave(w13s.view(torch.uint8), inverse=True).view(torch.float8_e4m3fn)
+            w13 = ref.nvfp4_dequantize(w13q, w13s, ones) * self.w13_scale_2.repeat_interleave(i, dim=1).reshape(-1, 1)
             w2 = ref.nvfp4_dequantize(self.w2, self.w2_scale, ones) * self.w2_scale_2.repeat_interleave(h).reshape(-1, 1)
             return w13.view(e, 2 * i, h), w2.view(e, h, i)
         return self.w13.view(e, 2 * i, h), self.w2.view(e, h, i)
@@ -192,6 +216,14 @@ class MoEBlock(nn.Module):
             raise NotImplementedError("shared experts are not combined with the token-sharded expert all-to-all")
         return self._forward_routed(x) + self._shared(x)
 
+    def expert_fc1(self, a, ws):
+        """NVFP4 rows of the padded expert layout → quantised SwiGLU activations for the second expert GEMM."""
+        cu = ops.cuda_ops()
+        if self._w13_interleaved:
+            return cu.gemm_grouped_swiglu(a, self.w13, ws, self.e_local, self.w13_alpha, self._w13_sf, self.down_input_scale)
+        h1 = cu.gemm_grouped(a, self.w13, ws, self.e_local, alpha=self.w13_alpha, w_sf=self._w13_sf)
+        return cu.swiglu_quant(h1, self.down_input_scale, moe_ws=ws)
+
     def _forward_routed(self, x):
         if isinstance(x, torch.Tensor) and not x.is_cuda:
             return self._forward_reference(x)
@@ -206,8 +238,7 @@ class MoEBlock(nn.Module):
             if self._w13_sf is None:
                 self.finalize()
             a = cu.moe_gather(xa, ws, self.top_k, self.input_scale)
-            h1 = cu.gemm_grouped(a, self.w13, ws, self.e_local, alpha=self.w13_alpha, w_sf=self._w13_sf)
-            a2 = cu.swiglu_quant(h1, self.down_input_scale, moe_ws=ws)
+            a2 = self.expert_fc1(a, ws)
             y = cu.gemm_grouped(a2, self.w2, ws, self.e_local, alpha=self.w2_alpha, w_sf=self._w2_sf)
         else:
             a = cu.moe_gather(xa, ws, self.top_k, None)

@@ -163,6 +163,20 @@ def spec_accept_greedy(target_tokens, tree_tokens, parents, max_path, force_len=
     return ref.spec_accept_greedy(target_tokens, tree_tokens, parents, max_path, force_len)
 
 
+def eagle_tree_meta(parents, base_pos, depth_base, pos_offset):
+    """``(mask [B*R, W], depth [B, R], positions [B*R])`` of a batch of trees given as parent tables."""
+    if parents.is_cuda:
+        return cuda_ops().eagle_tree_meta(parents, base_pos, depth_base, pos_offset)
+    return ref.eagle_tree_meta(parents, base_pos, depth_base, pos_offset)
+
+
+def eagle_select_verify(p_sc, p_tok, p_par, p_dep, root, keep):
+    """Verification tree ``(tokens, parents, depths)``: the ``keep`` best pool candidates in pool order behind the root."""
+    if p_sc.is_cuda:
+        return cuda_ops().eagle_select_verify(p_sc, p_tok, p_par, p_dep, root, keep)
+    return ref.eagle_select_verify(p_sc, p_tok, p_par, p_dep, root, keep)
+
+
 def kv_commit_path(pool, page_table, past_len, path, path_len):
     if pool.is_cuda:
         return cuda_ops().kv_commit_path(pool, page_table, past_len, path, path_len)

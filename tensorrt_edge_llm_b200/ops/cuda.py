@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import threading
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -40,8 +41,17 @@ LAUNCHES = 0      # kernels of this library launched (or captured) so far in thi
 _DEBUG_SYNC = os.environ.get("TELB_DEBUG_SYNC", "0") == "1"     # synchronise after every op so a device error names its op
 
 
+# Tensors whose pointers were taken for the launch being assembled.  A converted temporary (``x.to(int32)`` written inline
+# in an argument list) would otherwise be freed as soon as its pointer is extracted, and the caching allocator may hand the
+# same bytes to the next inline conversion of the same call, before the kernel has been enqueued.
+_KEEP = threading.local()
+
+
 def _check(rc: int, what: str, n: int = 1) -> None:
     global LAUNCHES
+    held = getattr(_KEEP, "tensors", None)
+    if held:
+        held.clear()                      # the launch is enqueued: stream order protects the memory from here on
     if rc != 0:
         raise RuntimeError(f"{what} failed: {lib().telb_last_error().decode()}")
     LAUNCHES += n
@@ -57,6 +67,12 @@ def _p(t: Optional[torch.Tensor]):
         return c_vp(0)
     if not t.is_cuda:        # a host pointer handed to a kernel is a device fault, not an exception
         raise ValueError(f"kernel argument of shape {tuple(t.shape)} lives on {t.device}, not on the GPU")
+    held = getattr(_KEEP, "tensors", None)
+    if held is None:
+        held = _KEEP.tensors = []
+    if len(held) > 4096:                  # pointers taken outside a _check-wrapped call must not accumulate
+        held.clear()
+    held.append(t)
     return c_vp(t.data_ptr())
 
 
@@ -258,7 +274,7 @@ def paged_attention(q, kv_layer, meta: StepMeta, scale, sliding_window=None, sin
     if not causal:
         sliding_window, kernel = -1, "tile"
     if sinks is not None:
-        raise NotImplementedError("attention sinks are not implemented in the CUDA kernel yet")
+        sinks = sinks.to(device=q.device, dtype=torch.float32).contiguous()
     q = q.contiguous()
     t, hq, d = q.shape
     hkv = kv_layer.shape[2]
@@ -277,7 +293,7 @@ def paged_attention(q, kv_layer, meta: StepMeta, scale, sliding_window=None, sin
             _p(q), _p(kv_layer), _p(out), _p(meta.q_start), _p(meta.q_len), _p(meta.past_len), _p(meta.page_table),
             c_int(meta.num_seqs), c_int(t), c_int(meta.max_q_len), c_int(kv_layer.shape[0]), c_int(meta.page_table.shape[1]),
             c_int(meta.page_size), c_int(hq), c_int(hkv), c_int(d), c_float(scale), c_int(sliding_window or 0), c_int(splits),
-            _p(ws.attn_ws), c_ll(ws.attn_ws.numel()), c_int(_is_bf16(q)), _p(ws.status), _p(trace), _stream()),
+            _p(ws.attn_ws), c_ll(ws.attn_ws.numel()), c_int(_is_bf16(q)), _p(ws.status), _p(trace), _p(sinks), _stream()),
             "paged_attention_decode", 2 if splits > 1 else 1)
         return out
     if splits is None:
@@ -287,7 +303,7 @@ def paged_attention(q, kv_layer, meta: StepMeta, scale, sliding_window=None, sin
         _p(tm), c_int(tm.shape[1] if tm is not None else 0), c_int(meta.num_seqs), c_int(t), c_int(meta.max_q_len),
         c_int(kv_layer.shape[0]), c_int(meta.page_table.shape[1]), c_int(meta.page_size), c_int(hq), c_int(hkv),
         c_int(d), c_float(scale), c_int(sliding_window or 0), c_int(splits), _p(ws.attn_ws), c_ll(ws.attn_ws.numel()),
-        c_int(_is_bf16(q)), _p(ws.status), _stream()), "paged_attention", 2 if splits > 1 else 1)
+        c_int(_is_bf16(q)), _p(ws.status), _p(sinks), _stream()), "paged_attention", 2 if splits > 1 else 1)
     return out
 
 
@@ -300,7 +316,7 @@ def decode_attention_quant_ok(q_shape, hkv: int, meta: StepMeta) -> bool:
 
 
 def paged_attention_quant(q, kv_layer, meta: StepMeta, scale, sliding_window, out_scale: torch.Tensor,
-                          splits: Optional[int] = None) -> "QuantActs":
+                          splits: Optional[int] = None, sinks: Optional[torch.Tensor] = None) -> "QuantActs":
     """Decode-shaped paged attention whose epilogue (or split merge) writes NVFP4 rows ``[T, Hq * D]`` quantised with the
     global scale ``out_scale`` of the projection that follows, instead of 16-bit rows and a quantisation kernel."""
     q = q.contiguous()
@@ -320,7 +336,8 @@ def paged_attention_quant(q, kv_layer, meta: StepMeta, scale, sliding_window, ou
         _p(q), _p(kv_layer), _p(xq), _p(sf), _p(out_scale), _p(meta.q_start), _p(meta.q_len), _p(meta.past_len), _p(meta.page_table),
         c_int(meta.num_seqs), c_int(t), c_int(meta.max_q_len), c_int(kv_layer.shape[0]), c_int(meta.page_table.shape[1]),
         c_int(meta.page_size), c_int(hq), c_int(hkv), c_int(d), c_float(scale), c_int(sliding_window or 0), c_int(splits),
-        _p(ws.attn_ws), c_ll(ws.attn_ws.numel()), c_int(_is_bf16(q)), _p(ws.status), _stream()),
+        _p(ws.attn_ws), c_ll(ws.attn_ws.numel()), c_int(_is_bf16(q)), _p(ws.status),
+        _p(None if sinks is None else sinks.to(device=q.device, dtype=torch.float32).contiguous()), _stream()),
         "paged_attention_decode_quant", 2 if splits > 1 else 1)
     return QuantActs(xq, sf, (t, width), q.dtype)
 
@@ -653,6 +670,24 @@ def gemm_grouped(x, weight, ws: MoeWorkspace, experts_local: int, alpha=None, bi
     return out
 
 
+def gemm_grouped_swiglu(x: "QuantActs", weight, ws: MoeWorkspace, experts_local: int, alpha, w_sf, out_scale: torch.Tensor) -> "QuantActs":
+    """Expert gate/up GEMM over the padded rows whose epilogue applies SwiGLU and quantises to NVFP4 for the second expert GEMM
+    (each expert's ``2 * inter`` weight rows alternate gate / up in blocks of 64).  Padding rows are left unwritten."""
+    n = weight.shape[0] // experts_local
+    k = weight.shape[1] * 2
+    inter = n // 2
+    L = lib()
+    L.telb_nvfp4_sf_bytes.restype = c_ll
+    xq = torch.empty(ws.rows_pad, inter // 2, dtype=torch.uint8, device=weight.device)
+    sf = _sf_buffer(L.telb_nvfp4_sf_bytes(c_ll(ws.rows_pad), c_int(inter)), inter, weight.device)
+    wsx = Workspace.get(weight.device)
+    _check(L.telb_gemm_nvfp4_grouped_swiglu(_p(x.xq), _p(x.sf), _p(weight), _p(w_sf), _p(xq), _p(sf), _p(out_scale), c_int(ws.rows_pad),
+                                            c_int(n), c_int(k), c_int(experts_local), _p(ws.tile_expert), _p(alpha),
+                                            c_int(1 if x.dtype == torch.bfloat16 else 0), _p(wsx.status), _stream()),
+           "gemm_nvfp4_grouped_swiglu")
+    return QuantActs(xq, sf, (ws.rows_pad, inter), x.dtype)
+
+
 def moe_combine(y: torch.Tensor, ws, topk_w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out[t] = Σ_k w[t,k] · y[ws.dst_row[t*K + k]]`` (slots with a negative row contribute nothing)."""
     t, k = topk_w.shape
@@ -750,16 +785,49 @@ def spec_accept_greedy(target_tokens, tree_tokens, parents, max_path: int, force
     path = torch.zeros(b, max_path, dtype=torch.int32, device=dev)
     plen = torch.empty(b, dtype=torch.int32, device=dev)
     bonus = torch.empty(b, dtype=torch.int32, device=dev)
-    _check(lib().telb_spec_accept_greedy(_p(target_tokens.to(torch.int32).contiguous()), _p(tree_tokens.to(torch.int32).contiguous()),
-                                         _p(parents.to(torch.int32).contiguous()), _p(path), _p(plen), _p(bonus), c_int(b), c_int(n),
+    tt, tr, pa = target_tokens.to(torch.int32).contiguous(), tree_tokens.to(torch.int32).contiguous(), parents.to(torch.int32).contiguous()
+    _check(lib().telb_spec_accept_greedy(_p(tt), _p(tr), _p(pa), _p(path), _p(plen), _p(bonus), c_int(b), c_int(n),
                                          c_int(max_path), _p(force), _stream()), "spec_accept_greedy")
     return path, plen, bonus
+
+
+def eagle_tree_meta(parents: torch.Tensor, base_pos: torch.Tensor, depth_base: int, pos_offset: int):
+    """Packed ancestor mask ``[B * R, ceil(R / 32)]``, depths ``[B, R]`` and positions ``[B * R]`` of a batch of trees given as
+    parent tables ``[B, R]`` (parents precede children, ``-1`` = none): one kernel, nothing read back."""
+    b, r = parents.shape
+    dev = parents.device
+    words = (r + 31) // 32
+    par = parents.to(torch.int32).contiguous()
+    mask = torch.empty(b * r, words, dtype=torch.int32, device=dev)
+    depth = torch.empty(b, r, dtype=torch.int32, device=dev)
+    pos = torch.empty(b * r, dtype=torch.int32, device=dev)
+    base = base_pos.to(device=dev, dtype=torch.int32).contiguous()
+    _check(lib().telb_eagle_tree_meta(_p(par), _p(base), _p(mask), _p(depth), _p(pos),
+                                      c_int(b), c_int(r), c_int(words), c_int(depth_base), c_int(pos_offset), _stream()), "eagle_tree_meta")
+    return mask, depth, pos
+
+
+def eagle_select_verify(p_sc, p_tok, p_par, p_dep, root, keep: int):
+    """The ``keep`` best candidates of each sequence's pool ``[B, P]`` in pool order behind the root: tokens, parents (indices into
+    the tree, root = -1 for slot 0) and depths, each ``[B, keep + 1]`` int32."""
+    b, pool = p_sc.shape
+    dev = p_sc.device
+    i32 = lambda t: t.to(device=dev, dtype=torch.int32).contiguous()
+    # converted copies stay referenced until the launch: a temporary freed after its pointer was taken would hand its
+    # memory to the next conversion
+    sc, ptok, ppar, pdep, rt = p_sc.float().contiguous(), i32(p_tok), i32(p_par), i32(p_dep), i32(root)
+    tok = torch.empty(b, keep + 1, dtype=torch.int32, device=dev)
+    par = torch.empty_like(tok)
+    dep = torch.empty_like(tok)
+    _check(lib().telb_eagle_select_verify(_p(sc), _p(ptok), _p(ppar), _p(pdep), _p(rt),
+                                          c_int(b), c_int(pool), c_int(keep), _p(tok), _p(par), _p(dep), _stream()), "eagle_select_verify")
+    return tok, par, dep
 
 
 def kv_commit_path(pool, page_table, past_len, path, path_len) -> None:
     assert pool.is_contiguous() and pool.element_size() == 2
     layers, pages, _, hkv, psz, d = pool.shape
-    _check(lib().telb_kv_commit_path(_p(pool), _p(page_table.to(torch.int32).contiguous()), _p(past_len.to(torch.int32).contiguous()),
-                                     _p(path.contiguous()), _p(path_len.contiguous()), c_int(path.shape[0]), c_int(path.shape[1]),
+    pt, pl, pth, pln = page_table.to(torch.int32).contiguous(), past_len.to(torch.int32).contiguous(), path.contiguous(), path_len.contiguous()
+    _check(lib().telb_kv_commit_path(_p(pool), _p(pt), _p(pl), _p(pth), _p(pln), c_int(path.shape[0]), c_int(path.shape[1]),
                                      c_int(page_table.shape[1]), c_int(layers), c_int(pages), c_int(hkv), c_int(psz), c_int(d),
                                      _stream()), "kv_commit_path")

@@ -76,7 +76,10 @@ def build_step_meta(q_lens: Sequence[int], past_lens: Sequence[int], page_table:
     for i, (q, p) in enumerate(zip(q_lens, past_lens)):
         pos.extend(range(int(p), int(p) + int(q)))
         sid.extend([i] * int(q))
-    if positions is not None:
+    pos_t = None
+    if isinstance(positions, torch.Tensor):          # already on the device (tree steps): no host copy of the values
+        pos_t = positions.to(device=device, dtype=torch.int32).reshape(-1)
+    elif positions is not None:
         pos = [int(x) for x in positions]
     if logits_all:
         lidx = list(range(t))
@@ -85,7 +88,7 @@ def build_step_meta(q_lens: Sequence[int], past_lens: Sequence[int], page_table:
     i32 = dict(dtype=torch.int32, device=device)
     return StepMeta(
         q_start=torch.tensor(q_start, **i32), q_len=torch.tensor(list(q_lens), **i32),
-        past_len=torch.tensor(list(past_lens), **i32), positions=torch.tensor(pos, **i32),
+        past_len=torch.tensor(list(past_lens), **i32), positions=pos_t if pos_t is not None else torch.tensor(pos, **i32),
         seq_ids=torch.tensor(sid, **i32), page_table=page_table.to(device=device, dtype=torch.int32),
         slot_ids=torch.tensor(list(slot_ids) if slot_ids is not None else list(range(n)), **i32),
         logits_idx=torch.tensor(lidx, **i32), page_size=page_size, num_seqs=n, num_tokens=t,

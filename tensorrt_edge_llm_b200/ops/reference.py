@@ -698,3 +698,56 @@ def kv_commit_path(pool: torch.Tensor, page_table: torch.Tensor, past_len: torch
         for j, r in zip(range(1, m), rows):
             s = past + j
             pool[:, int(page_table[i, s // p]), :, :, s % p, :] = r
+
+
+# ------------------------------------------------------------------------------------------
+# EAGLE tree construction (host formulation of the device kernels)
+
+
+def eagle_ancestors(parents: torch.Tensor) -> torch.Tensor:
+    """``[B, R, R]`` bool: row r may attend row c iff c is r or one of its ancestors."""
+    b, r = parents.shape
+    a = torch.eye(r, dtype=torch.bool, device=parents.device).expand(b, r, r).clone()
+    p = parents.long().clamp(min=0)
+    has = (parents >= 0)[..., None]
+    for _ in range(r):
+        up = a.gather(1, p[..., None].expand(b, r, r)) & has
+        new = a | up
+        if torch.equal(new, a):
+            break
+        a = new
+    return a
+
+
+def eagle_pack_mask(anc: torch.Tensor) -> torch.Tensor:
+    """Pack ``[B, R, R]`` bool into int32 words ``[B * R, ceil(R / 32)]`` (bit c of row r)."""
+    b, r, _ = anc.shape
+    words = (r + 31) // 32
+    pad = torch.zeros(b, r, words * 32, dtype=torch.int64, device=anc.device)
+    pad[..., :r] = anc.long()
+    w = (pad.view(b, r, words, 32) << torch.arange(32, device=anc.device)).sum(-1)
+    w = torch.where(w >= 2 ** 31, w - 2 ** 32, w)
+    return w.to(torch.int32).view(b * r, words)
+
+
+def eagle_tree_meta(parents: torch.Tensor, base_pos: torch.Tensor, depth_base: int, pos_offset: int):
+    anc = eagle_ancestors(parents)
+    depth = (anc.sum(-1) - 1 + depth_base).to(torch.int32)
+    pos = (base_pos.to(parents.device).long()[:, None] + depth.long() + pos_offset).to(torch.int32).reshape(-1)
+    return eagle_pack_mask(anc), depth, pos
+
+
+def eagle_select_verify(p_sc, p_tok, p_par, p_dep, root, keep: int):
+    b, npool = p_sc.shape
+    dev = p_sc.device
+    order = torch.sort(p_sc.float(), dim=1, descending=True, stable=True).indices[:, :keep]
+    sel = torch.sort(order, dim=1).values                                 # pool order = parents first
+    inv = torch.zeros((b, npool), dtype=torch.long, device=dev)           # a parent that was not kept re-attaches to the root
+    inv.scatter_(1, sel, torch.arange(1, keep + 1, device=dev).expand(b, keep))
+    spar = p_par.long().gather(1, sel)
+    parents = torch.where(spar < 0, torch.zeros_like(spar), inv.gather(1, spar.clamp(min=0)))
+    i32 = torch.int32
+    tok = torch.cat([root.to(dev).long()[:, None], p_tok.long().gather(1, sel)], dim=1).to(i32)
+    par = torch.cat([torch.full((b, 1), -1, device=dev, dtype=torch.long), parents], dim=1).to(i32)
+    dep = torch.cat([torch.zeros(b, 1, dtype=torch.long, device=dev), p_dep.long().gather(1, sel)], dim=1).to(i32)
+    return tok, par, dep

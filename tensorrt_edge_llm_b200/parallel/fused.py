@@ -264,9 +264,7 @@ class FusedComm(TorchComm):
             if block._w13_sf is None:
                 block.finalize()
             a = cu.moe_gather(recv, ws, 1, block.input_scale)
-            h1 = cu.gemm_grouped(a, block.w13, ws, block.e_local, alpha=block.w13_alpha, w_sf=block._w13_sf)
-            y = cu.gemm_grouped(cu.swiglu_quant(h1, block.down_input_scale, moe_ws=ws), block.w2, ws, block.e_local, alpha=block.w2_alpha,
-                                w_sf=block._w2_sf)
+            y = cu.gemm_grouped(block.expert_fc1(a, ws), block.w2, ws, block.e_local, alpha=block.w2_alpha, w_sf=block._w2_sf)
         else:
             a = cu.moe_gather(recv, ws, 1, None)
             y = cu.gemm_grouped(cu.swiglu(cu.gemm_grouped(a, block.w13, ws, block.e_local)), block.w2, ws, block.e_local)

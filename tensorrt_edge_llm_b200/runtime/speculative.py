@@ -175,12 +175,11 @@ class EagleDecoder:
         r_pool, r_sc = torch.arange(k1, device=dev).expand(b, k1), sc
         front0, kf = 0, k1                                                    # first row / width of the current frontier
         pool_base = k1
-        ld = [self.dkv.lengths[s] for s in seats]
+        ld = torch.tensor([self.dkv.lengths[s] for s in seats], dtype=torch.int32).to(dev, non_blocking=True)
         for depth in range(2, steps + 1):
             rows = r_tok.shape[1]
-            anc = self._ancestors(r_par)                                      # [B, R, R]
-            mask = self._pack_mask(anc)
-            pos = [l + int(d) - 1 for i, l in enumerate(ld) for d in r_dep[i].tolist()]
+            # ancestor mask and RoPE positions of the draft rows, built on the device from the parent table
+            mask, _, pos = ops.eagle_tree_meta(r_par, ld, 1, -1)
             want = [i * rows + front0 + j for i in range(b) for j in range(kf)]
             lp, h = self._draft_step(seats, self._embed(r_tok.reshape(-1)), r_feat.reshape(b * rows, -1).contiguous(), [rows] * b, want,
                                      tree_mask=mask, positions=pos)
@@ -214,23 +213,16 @@ class EagleDecoder:
         # ---- choose the verification tree ----
         npool = p_tok.shape[1]
         keep = min(n - 1, npool)
-        order = torch.sort(p_sc, dim=1, descending=True, stable=True).indices[:, :keep]
-        sel = torch.sort(order, dim=1).values                                 # pool order = parents first
-        inv = torch.full((b, npool), -1, dtype=torch.long, device=dev)
-        inv.scatter_(1, sel, torch.arange(1, keep + 1, device=dev).expand(b, keep))
-        spar = p_par.gather(1, sel)
-        parents = torch.where(spar < 0, torch.zeros_like(spar), inv.gather(1, spar.clamp(min=0)))
         nn_ = keep + 1
-        root = torch.tensor([self.root[s] for s in seats], device=dev)
-        tree_tok = torch.cat([root[:, None], p_tok.gather(1, sel)], dim=1)    # [B, nn]
-        tree_par = torch.cat([torch.full((b, 1), -1, device=dev), parents], dim=1)
-        tree_dep = torch.cat([torch.zeros(b, 1, dtype=torch.long, device=dev), p_dep.gather(1, sel)], dim=1)
-        anc = self._ancestors(tree_par)
+        root = torch.tensor([self.root[s] for s in seats], dtype=torch.int32).to(dev, non_blocking=True)
         lt = [self.r.kv.lengths[s] for s in seats]
-        pos = [l + int(d) for i, l in enumerate(lt) for d in tree_dep[i].tolist()]
+        lt_dev = torch.tensor(lt, dtype=torch.int32).to(dev, non_blocking=True)
+        # best `keep` candidates in pool order behind the root, then the tree's mask and positions: two kernels, no host read
+        tree_tok, tree_par, tree_dep = ops.eagle_select_verify(p_sc, p_tok, p_par, p_dep, root, keep)
+        tmask, _, pos = ops.eagle_tree_meta(tree_par, lt_dev, 0, 0)
         state_before = self.r.kv.recurrent.snapshot(seats) if self.hybrid else None
         logits, taps = self._target_step(seats, tree_tok.reshape(-1).to(torch.int32), [nn_] * b,
-                                         tree_mask=None if self.hybrid else self._pack_mask(anc), positions=None if self.hybrid else pos)
+                                         tree_mask=None if self.hybrid else tmask, positions=None if self.hybrid else pos)
         tgt = ops.argmax(logits).view(b, nn_)
         timer.end(stage)
         stage = timer.begin(prof.SPEC_ACCEPT, batch=b)
@@ -246,7 +238,7 @@ class EagleDecoder:
             path, plen, bonus = ops.ref.spec_accept_sampling(probs, tree_tok.to(torch.int32), tree_par.to(torch.int32), max_path,
                                                               self._uniforms(b, max_path, k + 1))
             path, plen, bonus = path.to(dev), plen.to(dev), bonus.to(dev)
-        past_t = torch.tensor(lt, dtype=torch.int32, device=dev)
+        past_t = lt_dev
         ops.kv_commit_path(self.r.kv.pool, self.r.kv.table_rows(seats).to(dev), past_t, path, plen)
         path_h, plen_h, bonus_h = path.tolist(), plen.tolist(), bonus.tolist()   # the round's one device→host read
         tok_h = tree_tok.tolist()
@@ -310,28 +302,12 @@ class EagleDecoder:
     @staticmethod
     def _ancestors(parents: torch.Tensor) -> torch.Tensor:
         """``[B, R, R]`` bool: row r may attend row c iff c is r or one of its ancestors."""
-        b, r = parents.shape
-        a = torch.eye(r, dtype=torch.bool, device=parents.device).expand(b, r, r).clone()
-        p = parents.clamp(min=0)
-        has = (parents >= 0)[..., None]
-        for _ in range(r):
-            up = a.gather(1, p[..., None].expand(b, r, r)) & has
-            new = a | up
-            if torch.equal(new, a):
-                break
-            a = new
-        return a
+        return ops.ref.eagle_ancestors(parents)
 
     @staticmethod
     def _pack_mask(anc: torch.Tensor) -> torch.Tensor:
         """Pack ``[B, R, R]`` bool into int32 words ``[B·R, ceil(R/32)]`` (bit c of row r)."""
-        b, r, _ = anc.shape
-        words = (r + 31) // 32
-        pad = torch.zeros(b, r, words * 32, dtype=torch.int64, device=anc.device)
-        pad[..., :r] = anc.long()
-        w = (pad.view(b, r, words, 32) << torch.arange(32, device=anc.device)).sum(-1)
-        w = torch.where(w >= 2 ** 31, w - 2 ** 32, w)
-        return w.to(torch.int32).view(b * r, words)
+        return ops.ref.eagle_pack_mask(anc)
 
     # ---- whole-request driver -----------------------------------------------------------------
     @torch.no_grad()

@@ -204,6 +204,23 @@ def test_paged_attention_decode_nvfp4_output(cu, case, dtype):
     _sync_check(cu)
 
 
+@pytest.mark.parametrize("kernel,case", [("tile", ([200, 37], [0, 91], 8, 2, 128, 64)), ("tile", ([33, 1], [10, 200], 8, 1, 64, 64)),
+                                         ("decode", ([1, 1, 1], [5, 64, 700], 32, 8, 128, 64)), ("decode", ([2, 1, 4], [10, 300, 77], 16, 4, 128, 64))])
+def test_paged_attention_sinks(cu, kernel, case):
+    """Per-head sink logits (one extra softmax column without a value row) in both kernels, with and without KV splits."""
+    q_lens, past_lens, hq, hkv, d, page = case
+    q, kv, meta = _paged_setup(q_lens, past_lens, hq, hkv, d, page, torch.bfloat16, seed=5)
+    scale = d ** -0.5
+    sinks = torch.linspace(-3.0, 6.0, hq, device="cuda")
+    outr = ref.paged_attention(q, kv, meta, scale, sinks=sinks)
+    assert _rel_err(outr, ref.paged_attention(q, kv, meta, scale)) > 0.05          # the sinks matter in this case
+    for s in (1, 3):
+        out = cu.paged_attention(q, kv, meta, scale, sinks=sinks, kernel=kernel, splits=s)
+        torch.cuda.synchronize()
+        assert _rel_err(out, outr) < 1.5e-2, (s, _rel_err(out, outr))
+    _sync_check(cu)
+
+
 def test_paged_attention_splits_window_tree(cu):
     q, kv, meta = _paged_setup([1, 1], [900, 333], 32, 8, 128, 64, torch.bfloat16, seed=9)
     scale = 128 ** -0.5

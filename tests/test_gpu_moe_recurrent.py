@@ -104,6 +104,35 @@ def test_moe_block_matches_reference(cu, quant, tokens):
     _sync_check(cu)
 
 
+@pytest.mark.parametrize("tokens", [5, 300])
+def test_moe_fused_fc1_swiglu_matches_unfused(cu, tokens, monkeypatch):
+    """Expert gate/up GEMM with SwiGLU + quantisation in its epilogue (interleaved expert rows) == GEMM then swiglu_quant."""
+    from tensorrt_edge_llm_b200.config import QuantConfig, qwen3_30b_a3b_config
+    from tensorrt_edge_llm_b200.models.qwen3_moe import MoEBlock
+    kw = dict(num_hidden_layers=1, hidden_size=512, moe_intermediate_size=256, num_experts=16, num_experts_per_tok=4)
+    cfg = qwen3_30b_a3b_config(**kw)
+    cfg.quant = QuantConfig(quant_type="nvfp4")
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(tokens, 512, device="cuda", generator=g).bfloat16()
+    outs = []
+    for fused in (True, False):
+        if fused:
+            monkeypatch.delenv("TELB_DISABLE_MOE_SWIGLU_FUSION", raising=False)
+        else:
+            monkeypatch.setenv("TELB_DISABLE_MOE_SWIGLU_FUSION", "1")
+        blk = MoEBlock(cfg, "model.layers.0.mlp").cuda()
+        blk.random_init(torch.Generator().manual_seed(3), std=0.05)
+        blk.finalize()
+        assert blk._w13_interleaved == fused
+        blk.input_scale.fill_(float(x.abs().max()) / (6.0 * 448.0))
+        blk.down_input_scale.fill_(0.5 / (6.0 * 448.0))
+        blk._refresh_alpha()
+        outs.append(blk(x))
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1])
+    _sync_check(cu)
+
+
 def _meta(q_lens, pasts, slots=None):
     table = torch.zeros(len(q_lens), 1, dtype=torch.int32)
     m = build_step_meta(q_lens, pasts, table, 64, slot_ids=slots)

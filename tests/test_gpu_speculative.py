@@ -37,6 +37,53 @@ def test_spec_accept_greedy(cu, b, n):
             assert torch.equal(got[0][i, :m].cpu(), want[0][i, :m])
 
 
+@pytest.mark.parametrize("b,n", [(1, 10), (4, 60), (16, 128), (3, 33)])
+def test_eagle_tree_meta_kernel(cu, b, n):
+    """Ancestor mask, depth and positions of random trees (and of forests whose rows hang under an absent root)."""
+    g = torch.Generator().manual_seed(b * 100 + n)
+    _, par = _random_tree(g, b, n)
+    forest = par.clone()
+    forest[:, : min(5, n)] = -1                                          # several parentless rows, as in a draft step
+    base = torch.randint(0, 3000, (b,), generator=g, dtype=torch.int32)
+    for table, depth_base, off in ((par, 0, 0), (forest, 1, -1)):
+        want = ref.eagle_tree_meta(table, base, depth_base, off)
+        got = cu.eagle_tree_meta(table.cuda(), base.cuda(), depth_base, off)
+        torch.cuda.synchronize()
+        for w, gt in zip(want, got):
+            assert torch.equal(gt.cpu(), w)
+
+
+@pytest.mark.parametrize("b,k,steps,n", [(1, 10, 6, 60), (4, 4, 3, 12), (16, 10, 6, 60), (2, 8, 4, 128)])
+def test_eagle_select_verify_kernel(cu, b, k, steps, n):
+    """Pool → verification tree: same nodes, order, parents and depths as the sort-based formulation (ties included)."""
+    g = torch.Generator().manual_seed(k * steps)
+    pool = k + (steps - 1) * k * k
+    # a pool shaped like the draft's: depth-1 candidates, then k*k children per later depth with non-increasing scores
+    sc = [-(torch.rand(b, k, generator=g) * 2)]
+    par = [torch.full((b, k), -1, dtype=torch.int32)]
+    dep = [torch.ones(b, k, dtype=torch.int32)]
+    front = torch.arange(k).expand(b, k)
+    base = k
+    for d in range(2, steps + 1):
+        psc = torch.cat(sc, 1).gather(1, front)
+        csc = psc[:, :, None] - (torch.rand(b, k, k, generator=g) * 2).round(decimals=1)     # rounded: equal scores occur
+        sc.append(csc.reshape(b, -1))
+        par.append(front[:, :, None].expand(b, k, k).reshape(b, -1).to(torch.int32))
+        dep.append(torch.full((b, k * k), d, dtype=torch.int32))
+        front = base + csc.reshape(b, -1).topk(k, dim=-1).indices
+        base += k * k
+    p_sc, p_par, p_dep = torch.cat(sc, 1), torch.cat(par, 1), torch.cat(dep, 1)
+    assert p_sc.shape[1] == pool
+    p_tok = torch.randint(0, 32000, (b, pool), generator=g, dtype=torch.int32)
+    root = torch.randint(0, 32000, (b,), generator=g, dtype=torch.int32)
+    keep = min(n - 1, pool)
+    want = ref.eagle_select_verify(p_sc, p_tok, p_par, p_dep, root, keep)
+    got = cu.eagle_select_verify(p_sc.cuda(), p_tok.cuda(), p_par.cuda(), p_dep.cuda(), root.cuda(), keep)
+    torch.cuda.synchronize()
+    for w, gt in zip(want, got):
+        assert torch.equal(gt.cpu(), w)
+
+
 @pytest.mark.parametrize("d,psz", [(128, 64), (64, 128)])
 def test_kv_commit_path(cu, d, psz):
     g = torch.Generator().manual_seed(d)
