@@ -1,4 +1,4 @@
-"""Secondary benchmark workloads (one GPU): the MoE, hybrid and speculative-decoding configurations that sit
+"""Secondary benchmark workloads (one GPU, or one process per GPU under torchrun for moe / hybrid / eagle): the MoE, hybrid and speculative-decoding configurations that sit
 next to the dense headline benchmark.  Each prints one JSON line with device-timed numbers (CUDA events after
 warm-up, synthetic seeded token ids, random-init weights of the named architecture).
 
@@ -89,25 +89,38 @@ def run_moe(args) -> dict:
             "gpu_launches": int(cu.LAUNCHES - l0), "data": "synthetic", "_rank": rank, "_world": world, "_llm": llm}
 
 
+def _max_over_ranks(world, dev, *vals):
+    if world <= 1:
+        return vals
+    import torch.distributed as dist
+    t = torch.tensor(list(vals), device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return tuple(float(v) for v in t)
+
+
 def run_hybrid(args) -> dict:
     from ..config import hybrid_nemotron_config
     from ..ops import cuda as cu
     from ..runtime.llm import LLM
     b, s, o = args.batch or 16, args.input_len or 8192, args.output_len or 256
+    rank, world, dev, comm = _dist()
     cfg = hybrid_nemotron_config(dtype="bfloat16", **({"num_hidden_layers": args.layers} if args.layers else {}))
+    if world > 1:
+        cfg = cfg.for_rank(rank, world)
     # recurrent layers walk a sequence in order, so prefill chunks carry several sequences side by side
-    llm = LLM(cfg, device="cuda", max_batch_size=b, max_input_len=s, max_kv_cache_capacity=s + o + 64, max_num_tokens=4 * 8192)
+    llm = LLM(cfg, device=str(dev), comm=comm, max_batch_size=b, max_input_len=s, max_kv_cache_capacity=s + o + 64, max_num_tokens=4 * 8192)
     g = torch.Generator().manual_seed(1234)
-    prompts = torch.randint(0, cfg.vocab_size, (b, s), generator=g, dtype=torch.int32).cuda()
+    prompts = torch.randint(0, cfg.vocab_size, (b, s), generator=g, dtype=torch.int32).to(dev)
     l0 = cu.LAUNCHES
     pre, dec = _generate_timed(llm, prompts, o, args.steps, args.warmup)
+    pre, dec = _max_over_ranks(world, dev, pre, dec)
     ms = pre + dec
     return {"metric": "output tok/s, Nemotron-H-style hybrid (Mamba2 + gated DeltaNet + GQA attention), bf16",
-            "value": round(b * o / (ms / 1e3), 1), "unit": "tok/s", "n_gpus": 1, "ms_per_step": round(ms, 3),
+            "value": round(b * o / (ms / 1e3), 1), "unit": "tok/s", "n_gpus": world, "ms_per_step": round(ms, 3),
             "config": {"global_batch": b, "seq_len": s, "output_len": o, "prefill_ms": round(pre, 3),
-                       "decode_ms_per_token": round(dec / max(1, o - 1), 4), "layers": cfg.num_hidden_layers,
+                       "decode_ms_per_token": round(dec / max(1, o - 1), 4), "layers": cfg.num_hidden_layers, "parallelism": f"tp{world}",
                        "layer_types": {t: cfg.layer_types.count(t) for t in sorted(set(cfg.layer_types))}},
-            "gpu_launches": int(cu.LAUNCHES - l0), "data": "synthetic"}
+            "gpu_launches": int(cu.LAUNCHES - l0), "data": "synthetic", "_rank": rank, "_world": world, "_llm": llm}
 
 
 def run_eagle(args) -> dict:
@@ -118,10 +131,12 @@ def run_eagle(args) -> dict:
     from ..runtime.runner import ModelRunner
     from ..runtime.speculative import EagleDecoder, SpecConfig
     b, s, rounds = args.batch or 4, args.input_len or 2048, args.output_len or 32
-    dev = torch.device("cuda", 0)
+    rank, world, dev, comm = _dist()
     kw = {"num_hidden_layers": args.layers} if args.layers else {}
     cfg = qwen3_8b_config(dtype="bfloat16", **kw)
-    model = AutoModel.from_config(cfg, device=dev, random_init=0)
+    if world > 1:                   # the target is tensor-parallel; the one-layer draft runs replicated on every rank
+        cfg = cfg.for_rank(rank, world)
+    model = AutoModel.from_config(cfg, device=dev, random_init=0, **({"comm": comm} if comm is not None else {}))
     dcfg = qwen3_8b_config(dtype="bfloat16", num_hidden_layers=1)
     dcfg.draft_type, dcfg.eagle3_target_hidden_size, dcfg.has_qk_norm = "eagle3", cfg.hidden_size, False
     draft = AutoModel.from_config(dcfg, device=dev, random_init=1)
@@ -143,6 +158,9 @@ def run_eagle(args) -> dict:
     for _ in range(args.warmup):
         dec.round(seats)
     torch.cuda.synchronize()
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
     emitted0, r0 = dec.stats.emitted, dec.stats.rounds
     e0, e1 = _events(2)
     e0.record()
@@ -150,14 +168,16 @@ def run_eagle(args) -> dict:
         dec.round(seats)
     e1.record()
     torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
+    (ms,) = _max_over_ranks(world, dev, e0.elapsed_time(e1))
     emitted = dec.stats.emitted - emitted0
     return {"metric": "output tok/s, EAGLE-3 tree speculative decoding on the Qwen3-8B shape (bf16), top-k 10, depth 6, 60 verify tokens",
-            "value": round(emitted / (ms / 1e3), 1), "unit": "tok/s", "n_gpus": 1, "ms_per_round": round(ms / rounds, 3),
+            "value": round(emitted / (ms / 1e3), 1), "unit": "tok/s", "n_gpus": world, "ms_per_round": round(ms / rounds, 3),
             "config": {"global_batch": b, "prompt_len": s, "rounds": rounds, "mean_accept_length": round(emitted / (rounds * b), 3),
                        "forced_accept_mean": 3.5, "prefill_s": round(t1 - t0, 3), "draft_forwards_per_round": spec.draft_steps,
-                       "layers": cfg.num_hidden_layers, "note": "eager rounds (one device→host read per round); accept lengths are prescribed"},
-            "gpu_launches": int(cu.LAUNCHES - l0), "data": "synthetic"}
+                       "layers": cfg.num_hidden_layers, "parallelism": f"tp{world} target, replicated draft",
+                       "note": "eager rounds; tree mask, positions and verify-tree selection are built on the device, one "
+                               "device→host read per round (accepted path); accept lengths are prescribed"},
+            "gpu_launches": int(cu.LAUNCHES - l0), "data": "synthetic", "_rank": rank, "_world": world}
 
 
 def run_serve(args) -> dict:

@@ -237,7 +237,11 @@ class CausalLM(nn.Module):
         With a vocabulary-sharded head each rank reduces its own shard to one (value, id) candidate per row and only
         those candidates cross the link (``comm.argmax_sharded``): ``world x rows x 8`` bytes instead of the
         ``rows x vocab`` logits of a full gather.  The result equals ``argmax`` of the gathered logits, ties included."""
-        x = self.hidden_states(ids, meta, kv_cache)
+        return self.greedy_from_hidden(self.hidden_states(ids, meta, kv_cache), meta)
+
+    def greedy_from_hidden(self, x: torch.Tensor, meta: StepMeta) -> torch.Tensor:
+        """The greedy pick of :meth:`greedy_tokens` for final hidden states that the caller already holds (speculative
+        verification keeps the tapped layers of the same pass)."""
         sharded = (self.lm_head.tp_mode == TPMode.COL and self.comm.world_size > 1 and hasattr(self.comm, "argmax_sharded")
                    and type(self).logits_from_hidden is CausalLM.logits_from_hidden)
         if not sharded:

@@ -172,9 +172,12 @@ class MoEBlock(nn.Module):
         if self.nvfp4 and self.w13.is_cuda:
             cu = ops.cuda_ops()
             if (not self._w13_interleaved and self.inter % 64 == 0
-                    and os.environ.get("TELB_DISABLE_MOE_SWIGLU_FUSION", "0") != "1"):
-                # the expert gate/up GEMM applies SwiGLU in its epilogue: a 128-wide output tile must hold 64 gate features
-                # and the matching 64 up features
+                    and os.environ.get("TELB_MOE_SWIGLU_FUSION", "0") == "1"):
+                # Opt-in: the expert gate/up GEMM applies SwiGLU + quantisation in its epilogue (a 128-wide output tile then
+                # holds 64 gate features and the matching 64 up features).  Off by default because it measured slower on a
+                # B200: expert GEMMs have short K loops (hidden 2048 = 8 K steps), so the epilogue sits on the critical path
+                # and one row per lane leaves most lanes idle on the sparsely filled tiles of a decode step (FC1 58.6 -> 89.1 us
+                # at 32 tokens, 311 -> 398 us at 8192 tokens, Qwen3-30B-A3B shape); the separate element-wise kernel wins.
                 self.w13.copy_(self._interleave(self.w13))
                 self.w13_scale.view(torch.uint8).copy_(self._interleave(self.w13_scale.view(torch.uint8)))
                 self.w13_alpha.copy_(self._interleave(self.w13_alpha))

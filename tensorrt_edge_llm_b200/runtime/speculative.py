@@ -104,11 +104,18 @@ class EagleDecoder:
     def _embed(self, ids: torch.Tensor) -> torch.Tensor:
         return ops.embedding(ids.to(torch.int32), self.model.model.embed_tokens.weight)
 
-    def _target_step(self, seats, rows: torch.Tensor, q_lens, tree_mask=None, positions=None):
+    def _target_step(self, seats, rows: torch.Tensor, q_lens, tree_mask=None, positions=None, greedy=False):
+        """Target pass over ``rows`` with the tapped layers; returns ``(logits, taps)``, or ``(arg-max ids, taps)`` when
+        ``greedy`` (a vocabulary-sharded head then exchanges one candidate per row and rank instead of the logits)."""
         meta = self.r._meta(seats, q_lens, logits_all=True, tree_mask=tree_mask, positions=positions)
         uniq = sorted(set(self.taps))
         x, taps = self.model.hidden_states(rows, meta, self.r.cache, capture_layers=uniq)
-        logits = self.model.logits_from_hidden(x, meta)
+        if greedy and hasattr(self.model, "greedy_from_hidden"):
+            logits = self.model.greedy_from_hidden(x, meta)
+        else:
+            logits = self.model.logits_from_hidden(x, meta)
+            if greedy:
+                logits = ops.argmax(logits)
         by_layer = dict(zip(uniq, taps))
         return logits, torch.cat([by_layer[t] for t in self.taps], dim=-1)
 
@@ -221,9 +228,10 @@ class EagleDecoder:
         tree_tok, tree_par, tree_dep = ops.eagle_select_verify(p_sc, p_tok, p_par, p_dep, root, keep)
         tmask, _, pos = ops.eagle_tree_meta(tree_par, lt_dev, 0, 0)
         state_before = self.r.kv.recurrent.snapshot(seats) if self.hybrid else None
-        logits, taps = self._target_step(seats, tree_tok.reshape(-1).to(torch.int32), [nn_] * b,
-                                         tree_mask=None if self.hybrid else tmask, positions=None if self.hybrid else pos)
-        tgt = ops.argmax(logits).view(b, nn_)
+        greedy = self.sampling is None
+        logits, taps = self._target_step(seats, tree_tok.reshape(-1).to(torch.int32), [nn_] * b, tree_mask=None if self.hybrid else tmask,
+                                         positions=None if self.hybrid else pos, greedy=greedy)
+        tgt = logits.view(b, nn_) if greedy else None
         timer.end(stage)
         stage = timer.begin(prof.SPEC_ACCEPT, batch=b)
         # ---- accept, commit KV ----

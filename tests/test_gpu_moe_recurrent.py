@@ -117,9 +117,9 @@ def test_moe_fused_fc1_swiglu_matches_unfused(cu, tokens, monkeypatch):
     outs = []
     for fused in (True, False):
         if fused:
-            monkeypatch.delenv("TELB_DISABLE_MOE_SWIGLU_FUSION", raising=False)
+            monkeypatch.setenv("TELB_MOE_SWIGLU_FUSION", "1")
         else:
-            monkeypatch.setenv("TELB_DISABLE_MOE_SWIGLU_FUSION", "1")
+            monkeypatch.delenv("TELB_MOE_SWIGLU_FUSION", raising=False)
         blk = MoEBlock(cfg, "model.layers.0.mlp").cuda()
         blk.random_init(torch.Generator().manual_seed(3), std=0.05)
         blk.finalize()
