@@ -5,7 +5,8 @@
 //
 //   ep_dispatch   one CTA per (token, k): stores the activation row into the owner rank's receive buffer
 //                 [src][slot][H] (peer store) and the slot's local expert id into EVERY rank's id table
-//                 [src][slot] (-1 where the slot is not for that rank); the last CTA publishes the rank's epoch.
+//                 [src][slot] (-1 where the slot is not for that rank, and for the unused tail of the step's slot
+//                 stride); the last CTA publishes the rank's epoch.  The stride is per step (rows per rank x top_k).
 //   ep_wait       bounded wait until every source rank has published the epoch (one tiny CTA).
 //                 The receiving rank then runs moe_align / gather / grouped GEMMs over the id table as usual.
 //   ep_return     one CTA per received slot with a valid expert: stores the expert output row back into the
@@ -57,7 +58,8 @@ __device__ __forceinline__ void ep_publish(const EpPeers& peers, int which, int 
     }
 }
 
-// grid = slots (tokens_local * top_k); x [tokens_local, hidden] 16-bit; topk_idx [tokens_local, top_k] global expert ids.
+// grid = slots_cap CTAs (the step's slot stride: every rank's segment of the id tables is rewritten in full, so no stale
+// entry of an earlier, longer step survives); x [tokens_local, hidden] 16-bit; topk_idx [tokens_local, top_k] global expert ids.
 __global__ void ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ topk_idx, EpPeers peers, int rank, int world,
                                    int slots, int slots_cap, int top_k, int hidden, int experts_per_rank, int* epoch, int* ticket) {
     pdl_prologue();
@@ -72,17 +74,10 @@ __global__ void ep_dispatch_kernel(const uint4* __restrict__ x, const int* __res
         const uint4* src = x + (size_t)(slot / top_k) * (hidden / 8);
         uint4* dst = reinterpret_cast<uint4*>(peers.recv_rows[dest]) + ((size_t)rank * slots_cap + slot) * (hidden / 8);
         for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dst[i] = src[i];
+    } else if (slot < slots_cap && threadIdx.x < world) {
+        peers.recv_ids[threadIdx.x][(size_t)rank * slots_cap + slot] = -1;      // unused tail of this rank's segment
     }
     ep_publish(peers, 0, rank, world, epoch, ticket);
-}
-
-// Unused tail of this rank's slots in every id table must read -1 (a shorter step may follow a longer one):
-// grid covers [slots, slots_cap) of the id tables; folded into the dispatch launch by the host as a second kernel.
-__global__ void ep_clear_ids_kernel(EpPeers peers, int rank, int world, int slots, int prev_slots, int slots_cap) {
-    pdl_prologue();
-    const int i = slots + blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < prev_slots && i < slots_cap)
-        for (int r = 0; r < world; ++r) peers.recv_ids[r][(size_t)rank * slots_cap + i] = -1;
 }
 
 // One CTA: wait until flags[which][src] >= *epoch for every source rank (epoch was advanced by this rank's own publish).
@@ -131,20 +126,20 @@ static int fill_peers(EpPeers& p, void* const* recv_rows, int* const* recv_ids, 
     return 0;
 }
 
-// Pointer tables hold `world` peer mappings each.  prev_slots: slot count of the previous call (ids beyond `slots` are reset).
+// Pointer tables hold `world` peer mappings each.  `slots_stride` is the slot count every rank reserves per source rank in this
+// step (the same number on every rank, e.g. rows-per-rank x top_k; at most the buffers' capacity): the receive areas are laid
+// out [source][slots_stride], so the work of a step follows its size, not the capacity.
 extern "C" int telb_ep_dispatch(const void* x, const int* topk_idx, void* const* recv_rows, int* const* recv_ids, void* const* comb_rows,
                                 int* const* flags, int rank, int world, int tokens_local, int top_k, int hidden, int experts_per_rank,
-                                int slots_cap, int prev_slots, int* epoch, int* ticket, cudaStream_t stream) {
+                                int slots_stride, int* epoch, int* ticket, cudaStream_t stream) {
     const int slots = tokens_local * top_k;
-    if (slots > slots_cap) return fail("telb_ep_dispatch: more routed rows than the receive buffers hold");
+    if (slots_stride < 1) return fail("telb_ep_dispatch: slot stride must be positive");
+    if (slots > slots_stride) return fail("telb_ep_dispatch: more routed rows than the step's slot stride");
     if (hidden % 8) return fail("telb_ep_dispatch: hidden must be a multiple of 8");
     EpPeers p{};
     if (fill_peers(p, recv_rows, recv_ids, comb_rows, flags, world)) return -1;
-    if (prev_slots > slots)
-        TELB_LAUNCH("ep_clear_ids_kernel", ep_clear_ids_kernel, dim3((prev_slots - slots + 255) / 256), dim3(256), 0, stream, p, rank, world,
-                    slots, prev_slots, slots_cap);
-    TELB_LAUNCH("ep_dispatch_kernel", ep_dispatch_kernel, dim3(slots > 0 ? slots : 1), dim3(128), 0, stream, (const uint4*)x, topk_idx, p, rank,
-                world, slots, slots_cap, top_k, hidden, experts_per_rank, epoch, ticket);
+    TELB_LAUNCH("ep_dispatch_kernel", ep_dispatch_kernel, dim3(slots_stride), dim3(128), 0, stream, (const uint4*)x, topk_idx, p, rank,
+                world, slots, slots_stride, top_k, hidden, experts_per_rank, epoch, ticket);
     return 0;
 }
 

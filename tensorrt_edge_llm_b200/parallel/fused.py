@@ -95,7 +95,6 @@ class _EpState:
         self.epoch = torch.zeros(2, dtype=torch.int32, device=device)        # dispatch, return
         self.ticket = torch.zeros(2, dtype=torch.int32, device=device)
         self.arange = torch.arange(self.slots_cap, dtype=torch.int32, device=device)
-        self.prev_slots = 0
         torch.cuda.synchronize(device)
         dist.barrier(group)
 
@@ -249,17 +248,21 @@ class FusedComm(TorchComm):
         w, idx = cu.moe_route_softmax_topk(logits, block.top_k, block.cfg.norm_topk_prob)
         epr = block.num_experts // world
         c = st.c
+        # the slot stride follows the step (every rank derives it from the global row count), so a decode step touches a few
+        # hundred slots instead of the buffers' prefill-size capacity
+        stride = max(1, rpr * block.top_k)
+        if stride > st.slots_cap:
+            raise ValueError(f"{rows} rows exceed the expert all-to-all capacity of {st.slots_cap // block.top_k * world} rows")
         cu._check(cu.lib().telb_ep_dispatch(cu._p(xs), cu._p(idx), c["recv_rows"], c["recv_ids"], c["comb_rows"], c["flags"], ctypes.c_int(rank),
                                             ctypes.c_int(world), ctypes.c_int(t_local), ctypes.c_int(block.top_k), ctypes.c_int(hidden),
-                                            ctypes.c_int(epr), ctypes.c_int(st.slots_cap), ctypes.c_int(st.prev_slots),
+                                            ctypes.c_int(epr), ctypes.c_int(stride),
                                             ctypes.c_void_p(st.epoch.data_ptr()), ctypes.c_void_p(st.ticket.data_ptr()), cu._stream()),
                   "ep_dispatch")
-        st.prev_slots = t_local * block.top_k
         cu._check(cu.lib().telb_ep_wait(cu._p(st.flags), ctypes.c_int(0), ctypes.c_int(world), ctypes.c_void_p(st.epoch.data_ptr()),
                                         cu._p(ws0.status), cu._stream()), "ep_wait")
-        n_recv = world * st.slots_cap
-        ws = cu.moe_align(st.recv_ids.view(n_recv, 1), block.e_local, 0, block.e_local)
-        recv = st.recv_rows.view(n_recv, hidden)
+        n_recv = world * stride
+        ws = cu.moe_align(st.recv_ids.view(-1)[:n_recv].view(n_recv, 1), block.e_local, 0, block.e_local)
+        recv = st.recv_rows.view(-1)[:n_recv * hidden].view(n_recv, hidden)
         if block.nvfp4:
             if block._w13_sf is None:
                 block.finalize()
@@ -269,14 +272,14 @@ class FusedComm(TorchComm):
             a = cu.moe_gather(recv, ws, 1, None)
             y = cu.gemm_grouped(cu.swiglu(cu.gemm_grouped(a, block.w13, ws, block.e_local)), block.w2, ws, block.e_local)
         cu._check(cu.lib().telb_ep_return(cu._p(y), cu._p(ws.dst_row), c["recv_rows"], c["recv_ids"], c["comb_rows"], c["flags"],
-                                          ctypes.c_int(rank), ctypes.c_int(world), ctypes.c_int(st.slots_cap), ctypes.c_int(hidden),
+                                          ctypes.c_int(rank), ctypes.c_int(world), ctypes.c_int(stride), ctypes.c_int(hidden),
                                           ctypes.c_void_p(st.epoch.data_ptr() + 4), ctypes.c_void_p(st.ticket.data_ptr() + 4), cu._stream()),
                   "ep_return")
         cu._check(cu.lib().telb_ep_wait(cu._p(st.flags), ctypes.c_int(1), ctypes.c_int(world), ctypes.c_void_p(st.epoch.data_ptr() + 4),
                                         cu._p(ws0.status), cu._stream()), "ep_wait")
         out = rs.partial[rank * rpr * hidden:(rank * rpr + t_local) * hidden].view(t_local, hidden)
         if t_local > 0:
-            cu.moe_combine(st.comb_rows.view(st.slots_cap, hidden), _Rows(st.arange), w, out=out)
+            cu.moe_combine(st.comb_rows.view(-1)[:stride * hidden].view(stride, hidden), _Rows(st.arange), w, out=out)
         return RsPartial(rows, hidden, x.dtype, rpr, sum_slots=1, slot_base=rank)
 
     def _rs_add_rmsnorm(self, part: RsPartial, residual, weight, eps, quant_scale, defer_gather):

@@ -126,7 +126,7 @@ def test_ep_all_to_all_two_emulated_ranks(cu):
     L, ws0 = cu.lib(), cu.Workspace.get(torch.device("cuda", 0))
     tables = (_table(recv_rows), _table(recv_ids), _table(comb), _table(flags))
     for r in range(world):
-        cu._check(L.telb_ep_dispatch(cu._p(x[r]), cu._p(idx[r]), *tables, r, world, t_local[r], top_k, h, epr, cap, 0,
+        cu._check(L.telb_ep_dispatch(cu._p(x[r]), cu._p(idx[r]), *tables, r, world, t_local[r], top_k, h, epr, cap,
                                      ctypes.c_void_p(epoch[r].data_ptr()), ctypes.c_void_p(ticket[r].data_ptr()), cu._stream()), "dispatch")
     for r in range(world):
         cu._check(L.telb_ep_wait(cu._p(flags[r]), 0, world, ctypes.c_void_p(epoch[r].data_ptr()), cu._p(ws0.status), cu._stream()), "wait")
@@ -155,9 +155,9 @@ def test_ep_all_to_all_two_emulated_ranks(cu):
         assert _rel_err(out, want) < 1e-2
     torch.cuda.synchronize()
     assert [e.tolist() for e in epoch] == [[1, 1], [1, 1]] and all(t.tolist() == [0, 0] for t in ticket)
-    # a shorter step after a longer one: stale ids beyond the new slot count are cleared
+    # a shorter step after a longer one: the whole segment of the slot stride is rewritten, so no stale id survives
     cu._check(L.telb_ep_dispatch(cu._p(x[0][:10]), cu._p(idx[0][:10].contiguous()), *tables, 0, world, 10, top_k, h, epr, cap,
-                                 t_local[0] * top_k, ctypes.c_void_p(epoch[0].data_ptr()), ctypes.c_void_p(ticket[0].data_ptr()), cu._stream()), "dispatch")
+                                 ctypes.c_void_p(epoch[0].data_ptr()), ctypes.c_void_p(ticket[0].data_ptr()), cu._stream()), "dispatch")
     torch.cuda.synchronize()
     for r in range(world):
         assert int((recv_ids[r].view(world, cap)[0, 10 * top_k:] != -1).sum()) == 0

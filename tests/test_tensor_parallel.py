@@ -142,6 +142,18 @@ def test_ep2_fused_gpu(tmp_path, prompt_len):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("prompt_len", [30, 190])
+def test_ep4_fused_gpu(tmp_path, prompt_len):
+    """Expert parallelism on four GPUs (two experts per rank in the test checkpoint): decode-size and prefill-size steps
+    through the peer-memory all-to-all, every rank's tokens equal to the single-rank model's."""
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs four GPUs")
+    _make_moe_ckpt(str(tmp_path), torch.bfloat16)
+    out = _launch(4, "nccl", "fused", str(tmp_path), 29640 + (prompt_len > 100), prompt_len=prompt_len, extra=("ep",))
+    assert "ranks identical True" in out
+
+
+@pytest.mark.gpu
 def test_fused_allreduce_norm_world1():
     """The fused all-reduce + add + RMSNorm kernel at world size 1 equals the local kernel."""
     from tensorrt_edge_llm_b200.ops import cuda as cu
