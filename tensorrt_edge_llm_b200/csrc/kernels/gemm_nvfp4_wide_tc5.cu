@@ -20,12 +20,14 @@
 // starts while the other half is still being converted and stored:
 //     columns [0,256) accumulator 0, [128,384) accumulator 1, [384,480) two scale buffers of 48 columns.
 //
-// Pair protocol: both CTAs run the same tile sequence.  Each CTA's producer warp fills its own stage ring.
-// CTA 0 (the leader) issues every `tcgen05.cp` / `tcgen05.mma` (with `.cta_group::2` they act on both CTAs'
-// shared memory and TMEM); CTA 1's warp 1 relays "my stage is full" to the leader with a remote mbarrier
-// arrive.  Stage release and "accumulator full" reach both CTAs through the multicast commit; "accumulator
-// drained" comes back from all 256 epilogue threads of the pair as arrives on the leader's barriers.  Every
-// wait is bounded, as in the other kernels.
+// Pair protocol: both CTAs run the same tile sequence.  Each CTA's producer warp fills its own stage ring
+// with `cp.async.bulk.tensor ... .cta_group::2` loads (no multicast) whose byte counts complete on the
+// LEADER's "stage full" barrier, armed by the leader for both CTAs' bytes; the scale atoms travel as tiled
+// loads over a [atoms, 512 B] view of the scale buffers for the same reason.  CTA 0 (the leader) issues every
+// `tcgen05.cp` / `tcgen05.mma` (with `.cta_group::2` they act on both CTAs' shared memory and TMEM).  Stage
+// release and "accumulator full" reach both CTAs through the multicast commit; "accumulator drained" comes
+// back from all 256 epilogue threads of the pair as arrives on the leader's barriers.  Every wait is bounded,
+// as in the other kernels.
 //
 // Fusions carried over from the 128-wide kernel: reduce-scatter epilogue (rows leave as 128-byte lines to
 // their owner rank's buffer), all-gather prologue (the producer waits for the rows' owner flags), SwiGLU +
@@ -71,6 +73,20 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t rank
     uint32_t remote;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(bar)), "r"(rank));
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
+// Shared-memory address of `ptr`'s counterpart in CTA `rank` of the cluster (shared::cluster window).
+__device__ __forceinline__ uint32_t cluster_addr_of(const void* ptr, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(ptr)), "r"(rank));
+    return remote;
+}
+// Tiled TMA load of a CTA pair (no multicast): the data lands in THIS CTA's shared memory, the byte count completes on the
+// mbarrier at `bar_cluster_addr`, which may belong to the other CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
 }
 // ---- cta_group::2 forms ------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc2(uint32_t* smem_dst, uint32_t ncols) {
@@ -118,6 +134,7 @@ __device__ __forceinline__ WideTile wide_tile(const GemmParams& p, int t) {
 template <bool PAIR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_nvfp4_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                       const __grid_constant__ CUtensorMap tma_sfa, const __grid_constant__ CUtensorMap tma_sfb,
                        const uint8_t* __restrict__ sf_a, const uint8_t* __restrict__ sf_b, int sf_k64_a, int sf_k64_b, GemmParams p) {
     using Cfg = WideCfg<PAIR>;
     constexpr int STAGES = Cfg::kStages;
@@ -156,6 +173,10 @@ gemm_nvfp4_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
         mbar_fence_init();
         prefetch_tensormap(&tma_a);
         prefetch_tensormap(&tma_b);
+        if constexpr (PAIR) {
+            prefetch_tensormap(&tma_sfa);
+            prefetch_tensormap(&tma_sfb);
+        }
     }
     if (warp == 1) {
         if constexpr (PAIR) {
@@ -197,12 +218,25 @@ gemm_nvfp4_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
                     uint8_t* sb = sa + Cfg::kATile;
                     uint8_t* ssa = sb + Cfg::kBTile;
                     uint8_t* ssb = ssa + Cfg::kSfA;
-                    mbar_expect_tx(&full_bar[stage], Cfg::kStage);
-                    tma_load_2d(sa, &tma_a, &full_bar[stage], kb * 128, a0);
-                    tma_load_2d(sb, &tma_b, &full_bar[stage], kb * 128, brow);
-                    bulk_load(ssa, sf_a + ((size_t)ta * sf_k64_a + (size_t)kb * 4) * 512, 2048, &full_bar[stage]);
-                    bulk_load(ssb, sf_b + ((size_t)tb0 * sf_k64_b + (size_t)kb * 4) * 512, 2048, &full_bar[stage]);
-                    bulk_load(ssb + 2048, sf_b + ((size_t)tb1 * sf_k64_b + (size_t)kb * 4) * 512, 2048, &full_bar[stage]);
+                    if constexpr (PAIR) {
+                        // every load of both CTAs completes on the LEADER's barrier (armed by the leader for both stages'
+                        // bytes), so the issuer learns that the pair's operands are in place without a relay hop; the scale
+                        // atoms travel as tiled loads too (rows of 512 bytes), since only those can signal the peer's barrier
+                        const uint32_t fb = cluster_addr_of(&full_bar[stage], 0);
+                        if (leader) mbar_expect_tx(&full_bar[stage], 2 * Cfg::kStage);
+                        tma_load_2d_pair(sa, &tma_a, fb, kb * 128, a0);
+                        tma_load_2d_pair(sb, &tma_b, fb, kb * 128, brow);
+                        tma_load_2d_pair(ssa, &tma_sfa, fb, 0, ta * sf_k64_a + kb * 4);
+                        tma_load_2d_pair(ssb, &tma_sfb, fb, 0, tb0 * sf_k64_b + kb * 4);
+                        tma_load_2d_pair(ssb + 2048, &tma_sfb, fb, 0, tb1 * sf_k64_b + kb * 4);
+                    } else {
+                        mbar_expect_tx(&full_bar[stage], Cfg::kStage);
+                        tma_load_2d(sa, &tma_a, &full_bar[stage], kb * 128, a0);
+                        tma_load_2d(sb, &tma_b, &full_bar[stage], kb * 128, brow);
+                        bulk_load(ssa, sf_a + ((size_t)ta * sf_k64_a + (size_t)kb * 4) * 512, 2048, &full_bar[stage]);
+                        bulk_load(ssb, sf_b + ((size_t)tb0 * sf_k64_b + (size_t)kb * 4) * 512, 2048, &full_bar[stage]);
+                        bulk_load(ssb + 2048, sf_b + ((size_t)tb1 * sf_k64_b + (size_t)kb * 4) * 512, 2048, &full_bar[stage]);
+                    }
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1;
@@ -230,12 +264,6 @@ gemm_nvfp4_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
                     if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kStatusMmaTimeout)) {
                         ok = false;
                         break;
-                    }
-                    if constexpr (PAIR) {
-                        if (!mbar_wait(&peer_full[stage], phase, abort_flag, p.status, kStatusMmaTimeout)) {
-                            ok = false;
-                            break;
-                        }
                     }
                     tc_fence_after_sync();
                     const uint8_t* sa = smem + stage * Cfg::kStage;
@@ -275,24 +303,6 @@ gemm_nvfp4_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
                 if (!ok) break;
                 if constexpr (PAIR) umma_commit2(&tfull_bar[acc], 3);
                 else umma_commit(&tfull_bar[acc]);
-            }
-        } else if (lane == 0 && PAIR) {
-            // ---------------- relay (second CTA): tell the leader when a stage of this CTA is full ----------------
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int t = cid; t < total_tiles && ok; t += ncl) {
-                for (int kb = 0; kb < p.kb_total; ++kb) {
-                    if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kStatusMmaTimeout)) {
-                        ok = false;
-                        break;
-                    }
-                    mbar_arrive_cluster(&peer_full[stage], 0);
-                    if (++stage == STAGES) {
-                        stage = 0;
-                        phase ^= 1;
-                    }
-                }
             }
         }
     } else {
@@ -446,8 +456,8 @@ gemm_nvfp4_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
 }
 
 template <bool PAIR>
-static int launch_wide(const CUtensorMap& ta, const CUtensorMap& tb, const uint8_t* sfa, const uint8_t* sfb, int k64a, int k64b,
-                       const GemmParams& p, cudaStream_t stream) {
+static int launch_wide(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsfa, const CUtensorMap& tsfb, const uint8_t* sfa,
+                       const uint8_t* sfb, int k64a, int k64b, const GemmParams& p, cudaStream_t stream) {
     using Cfg = WideCfg<PAIR>;
     auto kern = gemm_nvfp4_wide_kernel<PAIR>;
     static int max_clusters = 0;
@@ -502,7 +512,7 @@ static int launch_wide(const CUtensorMap& ta, const CUtensorMap& tb, const uint8
     }
     cfg.attrs = attrs;
     cfg.numAttrs = na;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, sfa, sfb, k64a, k64b, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tsfa, tsfb, sfa, sfb, k64a, k64b, p);
     if (e != cudaSuccess) return fail("cudaLaunchKernelEx(gemm_nvfp4_wide)", e);
     return 0;
 }
@@ -552,6 +562,14 @@ extern "C" int telb_gemm_nvfp4_wide_launch(const void* xq, const void* x_sf, con
     CUtensorMap ta, tb;
     if (make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, M, kbytes, kbytes, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
     if (make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, N, kbytes, kbytes, pair ? 128 : 256, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
-    return pair ? launch_wide<true>(ta, tb, (const uint8_t*)x_sf, (const uint8_t*)w_sf, k64, k64, p, stream)
-                : launch_wide<false>(ta, tb, (const uint8_t*)x_sf, (const uint8_t*)w_sf, k64, k64, p, stream);
+    // the pair kernel fetches scale atoms with tiled loads: the scale buffers seen as rows of 512 bytes (128 x u32), four atoms
+    // (one 256-element K step of one 128-row tile) per box
+    CUtensorMap tsa = ta, tsb = tb;
+    if (pair) {
+        const uint64_t atoms_a = (uint64_t)((M + 127) / 128) * k64, atoms_b = (uint64_t)((N + 127) / 128) * k64;
+        if (make_tmap_2d(&tsa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, x_sf, atoms_a, 128, 512, 4, 128, CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
+        if (make_tmap_2d(&tsb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w_sf, atoms_b, 128, 512, 4, 128, CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
+    }
+    return pair ? launch_wide<true>(ta, tb, tsa, tsb, (const uint8_t*)x_sf, (const uint8_t*)w_sf, k64, k64, p, stream)
+                : launch_wide<false>(ta, tb, tsa, tsb, (const uint8_t*)x_sf, (const uint8_t*)w_sf, k64, k64, p, stream);
 }
