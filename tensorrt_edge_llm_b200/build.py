@@ -68,7 +68,9 @@ def build_kernels(force=False, verbose=False) -> str:
                     print(out)
     lib = os.path.join(LIBDIR, "libtelb_kernels.so")
     if jobs or not os.path.exists(lib):
-        _run([NVCC, "-shared", "-o", lib] + objs + ["-lcudart_static", "-lpthread", "-ldl", "-lrt"])
+        # link beside the target and rename: a process (or a snapshot of the tree) never sees a half-written library
+        _run([NVCC, "-shared", "-o", lib + ".tmp"] + objs + ["-lcudart_static", "-lpthread", "-ldl", "-lrt"])
+        os.replace(lib + ".tmp", lib)
     return lib
 
 
@@ -97,7 +99,8 @@ def build_runtime(force=False, verbose=False) -> str:
     ext = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
     lib = os.path.join(LIBDIR, "_telb_runtime" + ext)
     if jobs or not os.path.exists(lib):
-        _run([cxx, "-shared", "-o", lib] + objs + ["-pthread"])
+        _run([cxx, "-shared", "-o", lib + ".tmp"] + objs + ["-pthread"])
+        os.replace(lib + ".tmp", lib)
     return lib
 
 

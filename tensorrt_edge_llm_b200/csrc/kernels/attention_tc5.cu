@@ -75,7 +75,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     constexpr int kQBytes = 128 * D * 2;
     constexpr int kKvBytes = kKvTile * D * 2;            // one K or V tile
     constexpr int kPBytes = 128 * kKvTile * 2;
-    constexpr int kTmemCols = 256;                       // S0 | S1 | O (D <= 128)
+    constexpr int kTmemCols = D <= 128 ? 256 : 512;      // S0 | S1 | O (D columns)
     constexpr uint32_t kOCol = 128;
 
     extern __shared__ uint8_t smem_raw[];
@@ -504,6 +504,9 @@ static int g_attn_variant = 1;       // measured 4-8 % faster than the deep-ring
 
 template <int D, typename T>
 static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tkv, const AttnParams& p, int qtiles, int nseq, cudaStream_t stream) {
+    // 256-wide heads (Gemma family): the Q tile alone is 64 KB and O takes 256 TMEM columns, so one CTA per SM with
+    // single-stage K / V rings is the only shape that fits
+    if constexpr (D > 128) return launch_attn_variant<D, T, 1, 1>(tq, tkv, p, qtiles, nseq, stream);
     if (g_attn_variant == 1) return launch_attn_variant<D, T, 1, 2>(tq, tkv, p, qtiles, nseq, stream);     // 2 CTAs / SM, single-stage rings
     return launch_attn_variant<D, T, 4, 1>(tq, tkv, p, qtiles, nseq, stream);                              // 1 CTA / SM, four-stage rings
 }
@@ -529,8 +532,11 @@ extern "C" int telb_attn_combine(const float* ws_o, const float* ws_lse, void* o
     } else if (d == 64) {
         if (is_bf16) TELB_LAUNCH("attn_combine_kernel", (attn_combine_kernel<64, __nv_bfloat16>), dim3(rows), dim3(64), 0, stream, ws_o, ws_lse, (__nv_bfloat16*)out, rows, splits);
         else TELB_LAUNCH("attn_combine_kernel", (attn_combine_kernel<64, __half>), dim3(rows), dim3(64), 0, stream, ws_o, ws_lse, (__half*)out, rows, splits);
+    } else if (d == 256) {
+        if (is_bf16) TELB_LAUNCH("attn_combine_kernel", (attn_combine_kernel<256, __nv_bfloat16>), dim3(rows), dim3(256), 0, stream, ws_o, ws_lse, (__nv_bfloat16*)out, rows, splits);
+        else TELB_LAUNCH("attn_combine_kernel", (attn_combine_kernel<256, __half>), dim3(rows), dim3(256), 0, stream, ws_o, ws_lse, (__half*)out, rows, splits);
     } else {
-        return fail("telb_attn_combine: head_dim must be 64 or 128");
+        return fail("telb_attn_combine: head_dim must be 64, 128 or 256");
     }
     TELB_CHECK_LAUNCH("attn_combine_kernel");
     return 0;
@@ -561,7 +567,7 @@ extern "C" int telb_paged_attention(const void* q, const void* kv_layer, void* o
                                     float scale, int window, int splits, float* ws, long long ws_floats, int is_bf16,
                                     int* status, const float* sinks, cudaStream_t stream) {
     if (num_seqs <= 0 || total_tokens <= 0) return 0;
-    if (d != 64 && d != 128) return fail("telb_paged_attention: head_dim must be 64 or 128");
+    if (d != 64 && d != 128 && d != 256) return fail("telb_paged_attention: head_dim must be 64, 128 or 256");
     if (page_size != 64 && page_size != 128) return fail("telb_paged_attention: page size must be 64 or 128");
     if (hq % hkv) return fail("telb_paged_attention: Hq must be a multiple of Hkv");
     const int group = hq / hkv;
@@ -607,6 +613,10 @@ extern "C" int telb_paged_attention(const void* q, const void* kv_layer, void* o
     if (d == 128) {
         if (is_bf16) return launch_attn<128, __nv_bfloat16>(tq, tkv, p, qtiles, num_seqs, stream);
         return launch_attn<128, __half>(tq, tkv, p, qtiles, num_seqs, stream);
+    }
+    if (d == 256) {
+        if (is_bf16) return launch_attn<256, __nv_bfloat16>(tq, tkv, p, qtiles, num_seqs, stream);
+        return launch_attn<256, __half>(tq, tkv, p, qtiles, num_seqs, stream);
     }
     if (is_bf16) return launch_attn<64, __nv_bfloat16>(tq, tkv, p, qtiles, num_seqs, stream);
     return launch_attn<64, __half>(tq, tkv, p, qtiles, num_seqs, stream);

@@ -78,6 +78,10 @@ class ModelRunner:
         return build_step_meta(q_lens, past, self.kv.table_rows(seats), self.kv.page_size, slot_ids=seats,
                                logits_all=logits_all, device=self.device, tree_mask=tree_mask, positions=positions)
 
+    def rope_delta_empty(self) -> bool:
+        """No resident sequence carries a multimodal position offset (captured passes take positions as given)."""
+        return not any(self.rope_delta.values())
+
     @torch.no_grad()
     def step(self, seats: Sequence[int], token_lists: Sequence[Sequence[int]], logits_all=False,
              commit=True, tree_mask=None, positions=None) -> torch.Tensor:

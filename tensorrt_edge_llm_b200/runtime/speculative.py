@@ -72,6 +72,76 @@ def default_tap_layers(num_layers: int) -> List[int]:
     return ids
 
 
+class _VerifyGraph:
+    """One captured tree-verification pass of the target for a fixed (batch, tree size): token ids, positions, ancestor
+    mask, cache lengths and page-table rows live in static device buffers that are refilled before every replay (the first
+    three by device-to-device copies from the tree kernels' outputs, so the tree never visits the host)."""
+
+    def __init__(self, dec: "EagleDecoder", b: int, nn: int):
+        from ..ops.meta import StepMeta
+        r = dec.r
+        dev, kv = r.device, r.kv
+        i32 = dict(dtype=torch.int32, device=dev)
+        t = b * nn
+        self.dec, self.b, self.nn = dec, b, nn
+        self.ids = torch.zeros(t, **i32)
+        self.meta = StepMeta(
+            q_start=torch.arange(0, t + 1, nn, **i32), q_len=torch.full((b,), nn, **i32), past_len=torch.zeros(b, **i32),
+            positions=torch.zeros(t, **i32), seq_ids=torch.arange(b, **i32).repeat_interleave(nn),
+            page_table=torch.full((b, kv.max_pages_per_seq), -1, **i32), slot_ids=torch.zeros(b, **i32),
+            logits_idx=torch.arange(t, **i32), page_size=kv.page_size, num_seqs=b, num_tokens=t, max_q_len=nn,
+            max_seq_len=kv.max_pages_per_seq * kv.page_size, tree_mask=torch.zeros(t, (nn + 31) // 32, **i32))
+        self._pin = torch.empty(b * (kv.max_pages_per_seq + 2), dtype=torch.int32, pin_memory=True)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.tgt = self.taps = None
+        self.launches = 0
+
+    def _body(self):
+        dec = self.dec
+        uniq = sorted(set(dec.taps))
+        x, taps = dec.model.hidden_states(self.ids, self.meta, dec.r.cache, capture_layers=uniq)
+        by_layer = dict(zip(uniq, taps))
+        return dec.model.greedy_from_hidden(x, self.meta), torch.cat([by_layer[t] for t in dec.taps], dim=-1)
+
+    def _load(self, seats, tree_tok, positions, mask):
+        kv, b = self.dec.r.kv, self.b
+        host = self._pin
+        host[:b] = torch.tensor([kv.lengths[s] for s in seats], dtype=torch.int32)
+        host[b:2 * b] = torch.tensor(list(seats), dtype=torch.int32)
+        host[2 * b:] = kv.table_rows(seats).reshape(-1)
+        devbuf = host.to(self.dec.device, non_blocking=True)
+        m = self.meta
+        m.past_len.copy_(devbuf[:b])
+        m.slot_ids.copy_(devbuf[b:2 * b])
+        m.page_table.copy_(devbuf[2 * b:].view(b, -1))
+        self.ids.copy_(tree_tok.reshape(-1))
+        m.positions.copy_(positions.reshape(-1))
+        m.tree_mask.copy_(mask)
+
+    def run(self, seats, tree_tok, positions, mask):
+        from ..ops import cuda as cu
+        kv = self.dec.r.kv
+        for s in seats:
+            kv.reserve(s, kv.lengths[s] + self.nn)
+        self._load(seats, tree_tok, positions, mask)
+        if self.graph is None:
+            side = torch.cuda.Stream(device=self.dec.device)           # one eager pass first: lazy set-up, allocator warm-up
+            side.wait_stream(torch.cuda.current_stream(self.dec.device))
+            with torch.cuda.stream(side):
+                self._body()
+            torch.cuda.current_stream(self.dec.device).wait_stream(side)
+            before = cu.LAUNCHES
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                self.tgt, self.taps = self._body()
+            self.graph = g
+            self.launches = cu.LAUNCHES - before
+            cu.LAUNCHES = before
+        self.graph.replay()
+        cu.LAUNCHES += self.launches
+        return self.tgt, self.taps
+
+
 class EagleDecoder:
     def __init__(self, runner: ModelRunner, draft, draft_kv: KVCacheManager, spec: Optional[SpecConfig] = None,
                  tap_layers: Optional[Sequence[int]] = None):
@@ -96,6 +166,7 @@ class EagleDecoder:
         self.sampling: Optional[dict] = None       # {"temperature", "top_k", "top_p", "seed"} for sampled requests, None = greedy
         self._sample_gen = None
         # per seat: pending root token, draft log-probs and hidden after the last accepted token
+        self._verify_graphs: Dict[tuple, _VerifyGraph] = {}
         self.root: Dict[int, int] = {}
         self.lp: Dict[int, torch.Tensor] = {}
         self.hid: Dict[int, torch.Tensor] = {}
@@ -161,6 +232,15 @@ class EagleDecoder:
             self.lp[s] = lp[i]
             self.hid[s] = h[int(ends[i])]
         return [int(t) for t in first]
+
+    def _graph_verify_ok(self, greedy: bool) -> bool:
+        """Tree verification replays from a CUDA graph on the GPU for greedy requests of attention-only targets (recurrent
+        layers need the state snapshot / replay around the pass); ``EDGELLM_DISABLE_CUDA_GRAPH=1`` or ``use_verify_graph =
+        False`` keep the eager pass."""
+        import os
+        return (greedy and not self.hybrid and self.device.type == "cuda" and getattr(self, "use_verify_graph", True)
+                and hasattr(self.model, "greedy_from_hidden") and os.environ.get("EDGELLM_DISABLE_CUDA_GRAPH", "0") != "1"
+                and self.r.rope_delta_empty())
 
     # ---- one speculative round ----------------------------------------------------------------
     @torch.no_grad()
@@ -229,8 +309,15 @@ class EagleDecoder:
         tmask, _, pos = ops.eagle_tree_meta(tree_par, lt_dev, 0, 0)
         state_before = self.r.kv.recurrent.snapshot(seats) if self.hybrid else None
         greedy = self.sampling is None
-        logits, taps = self._target_step(seats, tree_tok.reshape(-1).to(torch.int32), [nn_] * b, tree_mask=None if self.hybrid else tmask,
-                                         positions=None if self.hybrid else pos, greedy=greedy)
+        if self._graph_verify_ok(greedy):
+            # fixed (batch, tree size) and a tree that already lives on the device: the whole target pass replays from a graph
+            vg = self._verify_graphs.get((b, nn_))
+            if vg is None:
+                vg = self._verify_graphs[(b, nn_)] = _VerifyGraph(self, b, nn_)
+            logits, taps = vg.run(seats, tree_tok, pos, tmask)
+        else:
+            logits, taps = self._target_step(seats, tree_tok.reshape(-1).to(torch.int32), [nn_] * b, tree_mask=None if self.hybrid else tmask,
+                                             positions=None if self.hybrid else pos, greedy=greedy)
         tgt = logits.view(b, nn_) if greedy else None
         timer.end(stage)
         stage = timer.begin(prof.SPEC_ACCEPT, batch=b)

@@ -136,6 +136,9 @@ ATTN_CASES = [
     ([70], [130], 4, 4, 128, 64),
     ([33, 1], [10, 200], 8, 1, 64, 64),
     ([150], [50], 32, 8, 128, 128),
+    ([70, 33], [130, 10], 8, 2, 256, 64),           # 256-wide heads (Gemma family)
+    ([1, 1, 1], [300, 77, 1000], 8, 4, 256, 64),
+    ([260], [0], 4, 1, 256, 128),
 ]
 
 
@@ -148,6 +151,10 @@ def test_paged_attention(cu, case):
     torch.cuda.synchronize()
     outr = ref.paged_attention(q, kv, meta, scale)
     assert _rel_err(out, outr) < 1.5e-2, _rel_err(out, outr)
+    if d == 256:                                     # split-KV merge and sliding window on the wide-head instantiation
+        assert _rel_err(cu.paged_attention(q, kv, meta, scale, kernel="tile", splits=3), outr) < 1.5e-2
+        outw = cu.paged_attention(q, kv, meta, scale, sliding_window=64)
+        assert _rel_err(outw, ref.paged_attention(q, kv, meta, scale, sliding_window=64)) < 1.5e-2
     _sync_check(cu)
 
 
