@@ -83,7 +83,7 @@ def build_runtime(force=False, verbose=False) -> str:
         return ""
     import pybind11
     os.makedirs(BUILD, exist_ok=True)
-    headers = [os.path.join(rdir, f) for f in os.listdir(rdir) if f.endswith((".h", ".hpp"))]
+    headers = [os.path.join(rdir, f) for f in os.listdir(rdir) if f.endswith((".h", ".hpp", ".inc"))]
     inc = ["-I" + pybind11.get_include(), "-I" + sysconfig.get_paths()["include"], "-I" + rdir]
     cxx = shutil.which("g++") or "g++"
     flags = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-Wextra", "-Wno-unused-parameter", "-fvisibility=hidden", "-pthread"]

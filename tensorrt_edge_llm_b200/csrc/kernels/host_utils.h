@@ -7,6 +7,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <stdlib.h>
+#include <string.h>
 
 namespace telb {
 
@@ -43,21 +44,75 @@ inline PFN_encodeTiled encode_tiled_fn() {
     return fn;
 }
 
+// Encoded tensor maps are remembered per thread, keyed by everything that goes into them (base pointer, extents, pitches,
+// box, type, swizzle): a map depends on nothing else, so a later launch over the same buffer and shape copies the 128
+// bytes instead of calling the driver again.  Direct-mapped, 512 entries; a colliding key simply replaces the entry.
+struct TmapKey {
+    uint64_t base;
+    uint64_t dims[5];
+    uint64_t strides[4];
+    uint32_t box[5];
+    uint32_t dt, rank, swz, l2;
+};
+struct TmapEntry {
+    TmapKey key;
+    CUtensorMap map;
+    bool used;
+};
+inline TmapEntry* tmap_cache_slot(const TmapKey& k) {
+    static thread_local TmapEntry* table = nullptr;
+    if (!table) table = static_cast<TmapEntry*>(calloc(512, sizeof(TmapEntry)));
+    if (!table) return nullptr;
+    uint64_t h = 1469598103934665603ull;
+    const uint64_t* w = reinterpret_cast<const uint64_t*>(&k);
+    for (size_t i = 0; i < sizeof(TmapKey) / 8; ++i) h = (h ^ w[i]) * 1099511628211ull;
+    return &table[(h ^ (h >> 29)) & 511];
+}
+inline int encode_tmap_cached(CUtensorMap* out, CUtensorMapDataType dt, int rank, const void* base, const cuuint64_t* dims,
+                              const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle swz, CUtensorMapL2promotion l2) {
+    TmapKey k;
+    memset(&k, 0, sizeof(k));
+    k.base = reinterpret_cast<uint64_t>(base);
+    for (int i = 0; i < rank; ++i) {
+        k.dims[i] = dims[i];
+        k.box[i] = box[i];
+        if (i + 1 < rank) k.strides[i] = strides[i];
+    }
+    k.dt = (uint32_t)dt;
+    k.rank = (uint32_t)rank;
+    k.swz = (uint32_t)swz;
+    k.l2 = (uint32_t)l2;
+    TmapEntry* e = tmap_cache_slot(k);
+    if (e && e->used && memcmp(&e->key, &k, sizeof(k)) == 0) {
+        memcpy(out, &e->map, sizeof(CUtensorMap));
+        return 0;
+    }
+    PFN_encodeTiled enc = encode_tiled_fn();
+    if (!enc) return fail("cuTensorMapEncodeTiled entry point not found");
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUresult r = enc(out, dt, rank, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, l2,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return (int)r;
+    if (e) {
+        e->key = k;
+        memcpy(&e->map, out, sizeof(CUtensorMap));
+        e->used = true;
+    }
+    return 0;
+}
+
 // Row-major 2-D tensor [rows, cols] of `elem_bytes` elements with row pitch `pitch_bytes`; box
 // [box_rows, box_cols].  box_cols * elem_bytes must equal the swizzle span for swizzled maps.
 inline int make_tmap_2d(CUtensorMap* out, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t rows,
                         uint64_t cols, uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols,
                         CUtensorMapSwizzle swz, CUtensorMapL2promotion l2 = CU_TENSOR_MAP_L2_PROMOTION_L2_256B) {
-    PFN_encodeTiled enc = encode_tiled_fn();
-    if (!enc) return fail("cuTensorMapEncodeTiled entry point not found");
     cuuint64_t dims[2] = {cols, rows};
     cuuint64_t strides[1] = {pitch_bytes};
     cuuint32_t box[2] = {box_cols, box_rows};
-    cuuint32_t estr[2] = {1, 1};
     (void)elem_bytes;
-    CUresult r = enc(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
-                     l2, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
+    const int r = encode_tmap_cached(out, dt, 2, base, dims, strides, box, swz, l2);
+    if (r < 0) return r;
+    if (r != 0) {
         snprintf(g_last_error, sizeof(g_last_error),
                  "cuTensorMapEncodeTiled(2d) failed: %d (base %p rows %llu cols %llu pitch %llu box %u x %u)", (int)r,
                  base, (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)pitch_bytes, box_rows,
@@ -70,21 +125,17 @@ inline int make_tmap_2d(CUtensorMap* out, CUtensorMapDataType dt, int elem_bytes
 // General N-D (N <= 5) map; dims / strides innermost first, strides[i] is the byte pitch of dim i+1.
 inline int make_tmap_nd(CUtensorMap* out, CUtensorMapDataType dt, int rank, const void* base, const uint64_t* dims,
                         const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swz) {
-    PFN_encodeTiled enc = encode_tiled_fn();
-    if (!enc) return fail("cuTensorMapEncodeTiled entry point not found");
     cuuint64_t d[5];
     cuuint64_t s[4];
     cuuint32_t b[5];
-    cuuint32_t e[5];
     for (int i = 0; i < rank; ++i) {
         d[i] = dims[i];
         b[i] = box[i];
-        e[i] = 1;
         if (i + 1 < rank) s[i] = strides_bytes[i];
     }
-    CUresult r = enc(out, dt, rank, const_cast<void*>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
+    const int r = encode_tmap_cached(out, dt, rank, base, d, s, b, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    if (r < 0) return r;
+    if (r != 0) {
         snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled(%dd) failed: %d", rank, (int)r);
         return -1;
     }

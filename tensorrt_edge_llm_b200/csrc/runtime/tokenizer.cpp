@@ -34,27 +34,30 @@ static void put_cp(std::string& o, uint32_t cp) {
     }
 }
 
-// ---- approximate Unicode classes ----------------------------------------------------------------
+// ---- Unicode classes of the pre-tokenisation patterns (\p{L}, \p{N}, \s): exact range tables ------------------------
+#include "unicode_tables.inc"
+
+static bool in_ranges(const uint32_t (*r)[2], int n, uint32_t c) {
+    int lo = 0, hi = n - 1;
+    while (lo <= hi) {
+        const int mid = (lo + hi) >> 1;
+        if (c < r[mid][0]) hi = mid - 1;
+        else if (c > r[mid][1]) lo = mid + 1;
+        else return true;
+    }
+    return false;
+}
 static bool is_space_cp(uint32_t c) {
-    return c == ' ' || (c >= 9 && c <= 13) || c == 0x85 || c == 0xA0 || c == 0x1680 || (c >= 0x2000 && c <= 0x200A) ||
-           c == 0x2028 || c == 0x2029 || c == 0x202F || c == 0x205F || c == 0x3000;
+    if (c < 0x80) return c == ' ' || (c >= 9 && c <= 13);
+    return in_ranges(kUnicodeWhiteSpace, kUnicodeWhiteSpace_count, c);
 }
 static bool is_digit_cp(uint32_t c) {
-    return (c >= '0' && c <= '9') || (c >= 0x0660 && c <= 0x0669) || (c >= 0x06F0 && c <= 0x06F9) || (c >= 0x0966 && c <= 0x096F) ||
-           (c >= 0xFF10 && c <= 0xFF19) || c == 0xB2 || c == 0xB3 || c == 0xB9 || (c >= 0xBC && c <= 0xBE);
+    if (c < 0x80) return c >= '0' && c <= '9';
+    return in_ranges(kUnicodeNumber, kUnicodeNumber_count, c);
 }
 static bool is_letter_cp(uint32_t c) {
     if (c < 0x80) return (c >= 'a' && c <= 'z') || (c >= 'A' && c <= 'Z');
-    if (is_space_cp(c) || is_digit_cp(c)) return false;
-    if (c < 0xC0) return c == 0xAA || c == 0xB5 || c == 0xBA;            // Latin-1 symbols are not letters
-    if (c == 0xD7 || c == 0xF7) return false;
-    if (c >= 0x2000 && c <= 0x2BFF) return false;                        // punctuation, symbols, arrows, math, box drawing
-    if (c >= 0x3000 && c <= 0x303F) return false;                        // CJK punctuation
-    if (c >= 0xFE30 && c <= 0xFE6F) return false;
-    if ((c >= 0xFF01 && c <= 0xFF0F) || (c >= 0xFF1A && c <= 0xFF20) || (c >= 0xFF3B && c <= 0xFF40) || (c >= 0xFF5B && c <= 0xFF65)) return false;
-    if (c >= 0x1F000 && c <= 0x1FAFF) return false;                      // emoji & pictographs
-    if (c >= 0xE000 && c <= 0xF8FF) return false;                        // private use
-    return true;
+    return in_ranges(kUnicodeLetter, kUnicodeLetter_count, c);
 }
 
 // ---- loading ------------------------------------------------------------------------------------

@@ -350,6 +350,20 @@ def test_tokenizer_matches_hf(hf_tok):
     assert mine.is_special(mine.eos_id) and mine.decode([mine.eos_id]).decode() == ""
 
 
+def test_tokenizer_unicode_classes_match_hf(hf_tok):
+    """Pre-tokenisation splits on exact Unicode letter / number / white-space classes: scripts, numerals and marks that a
+    hand-written range list gets wrong must split as the Hugging Face regex engine splits them."""
+    tok, d = hf_tok
+    mine = rt.Tokenizer.load_from_hf(d)
+    texts = ["Ⅻ世紀 x²+y³=½ ٣٤٥ ১২৩ ௧௨", "e\u0301cole na\u0308ive", "ไทย123ไทย ᠮᠣᠩᠭᠣᠯ", "αβγ·δ 한국어—テスト　全角", "a\u2028b\u00a0c\u1680d\u001ce",
+             "🙂 emoji👍🏽mix", "ℵ₀ ∑ᵢxᵢ ℃ №5 ㈱ ①②③ 𝒜𝔅 𐍈", "ǅ ʰ ʻokina ˈstress ՙ ֊", "x\u200by\ufeffz \u0600\u06dd"]
+    for text in texts:
+        want = tok.encode(text).ids
+        got = mine.encode(text)
+        assert got == want, (text, got, want)
+        assert mine.decode(got, False).decode() == text
+
+
 def test_chat_template_families(hf_tok):
     _, d = hf_tok
     ct = rt.ChatTemplate.load(d)
