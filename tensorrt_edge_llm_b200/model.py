@@ -68,7 +68,10 @@ class AutoModel:
 
     @staticmethod
     def from_pretrained(model_dir: str, mapping: Optional[Mapping] = None, comm=None, device="cpu"):
+        from .checkpoint.artifacts import is_artifact_dir, load_artifacts
         from .checkpoint.loader import load_weights
+        if is_artifact_dir(model_dir):          # prepared by `trtedge build`: load the rank's tensors as stored
+            return load_artifacts(model_dir, mapping, comm, device)
         cfg = ModelConfig.from_pretrained(model_dir, mapping)
         cls = model_class_for(cfg)
         model = cls(cfg, comm)

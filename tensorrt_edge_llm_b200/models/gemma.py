@@ -128,3 +128,7 @@ class GemmaCausalLM(CausalLM):
         t = self.model
         t.embed_tokens.weight.mul_(torch.tensor(t.embed_scale, dtype=t.embed_tokens.weight.dtype))
         t.embed_scale = 1.0
+
+    def artifacts_loaded(self):
+        """Prepared weights already carry the folded norm offsets and the scaled embedding table."""
+        self.model.embed_scale = 1.0

@@ -179,6 +179,40 @@ def test_build_checks_checkpoint(ckpt, tmp_path):
     assert trtedge(["--version"]) == 0 and trtedge([]) == 2
 
 
+def test_build_writes_artifacts_that_load_without_repacking(ckpt, tmp_path):
+    """`trtedge build` prepares per-rank weights + world / runtime configs; the directory then stands in for the checkpoint:
+    same tensors as a direct sharded load on every rank, same tokens through `LLM`, tampering is detected on request."""
+    from tensorrt_edge_llm_b200 import AutoModel
+    from tensorrt_edge_llm_b200.checkpoint.artifacts import is_artifact_dir, load_artifacts, read_world_config
+    from tensorrt_edge_llm_b200.config import Mapping
+    from tensorrt_edge_llm_b200.runtime.llm import LLM
+    from tensorrt_edge_llm_b200.runtime.runner import SamplingParams
+    out2 = str(tmp_path / "tp2")
+    assert trtedge(["build", ckpt, "--output_dir", out2, "--tensor-parallel-size", "2"]) == 0
+    world = read_world_config(out2)
+    assert is_artifact_dir(out2) and world["tensor_parallel_size"] == 2 and [r["weights"] for r in world["ranks"]] == ["rank0.safetensors", "rank1.safetensors"]
+    for rank in range(2):
+        direct = AutoModel.from_pretrained(ckpt, mapping=Mapping(tp_size=2, tp_rank=rank))
+        loaded = AutoModel.from_pretrained(out2, mapping=Mapping(tp_size=2, tp_rank=rank))
+        a, b = direct.state_dict(), loaded.state_dict()
+        assert a.keys() == b.keys() and all(torch.equal(a[k], b[k]) for k in a)
+    with pytest.raises(ValueError, match="tensor-parallel"):
+        AutoModel.from_pretrained(out2)                                   # prepared for two ranks, asked for one
+    out1 = str(tmp_path / "tp1")
+    assert trtedge(["build", ckpt, "--output_dir", out1, "--max-batch-size", "2"]) == 0
+    prompts, sp = [[5, 9, 33, 70], [8, 2, 44]], SamplingParams(max_tokens=6)
+    want = [o.token_ids for o in LLM(ckpt, max_batch_size=2, max_kv_cache_capacity=128, device="cpu").generate(prompts, sp)]
+    got = [o.token_ids for o in LLM(out1, max_batch_size=2, max_kv_cache_capacity=128, device="cpu").generate(prompts, sp)]
+    assert got == want
+    # a flipped byte in the weight file is caught when verification is requested
+    path = os.path.join(out1, "rank0.safetensors")
+    raw = bytearray(open(path, "rb").read())
+    raw[-1] ^= 0xFF
+    open(path, "wb").write(bytes(raw))
+    with pytest.raises(ValueError, match="sha256"):
+        load_artifacts(out1, verify=True)
+
+
 def test_reference_package_name_resolves():
     import tensorrt_edgellm
     from tensorrt_edgellm.server import LLM, SamplingParams  # noqa: F401
