@@ -104,6 +104,21 @@ def build_runtime(force=False, verbose=False) -> str:
     return lib
 
 
+def build_race_check(sanitizer: str = "thread") -> str:
+    """The native runtime's concurrency check (``csrc/runtime/checks/race_check.cpp``) linked with the runtime sources under a
+    sanitizer (``thread``, ``address`` or ``undefined``); returns the executable's path.  It runs on the host, no GPU."""
+    if sanitizer not in ("thread", "address", "undefined"):
+        raise ValueError("sanitizer must be thread, address or undefined")
+    rdir = os.path.join(CSRC, "runtime")
+    srcs = [os.path.join(rdir, f) for f in sorted(os.listdir(rdir)) if f.endswith(".cpp") and f != "bindings.cpp"]
+    srcs.append(os.path.join(rdir, "checks", "race_check.cpp"))
+    os.makedirs(BUILD, exist_ok=True)
+    exe = os.path.join(BUILD, f"race_check_{sanitizer}")
+    cxx = shutil.which("g++") or "g++"
+    _run([cxx, "-O1", "-g", "-std=c++17", "-fno-omit-frame-pointer", f"-fsanitize={sanitizer}", "-pthread", "-I" + rdir] + srcs + ["-o", exe])
+    return exe
+
+
 def build_all(force=False, verbose=False):
     return build_kernels(force, verbose), build_runtime(force, verbose)
 
@@ -112,5 +127,10 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("-v", "--verbose", action="store_true")
+    ap.add_argument("--sanitize", choices=["thread", "address", "undefined"], default=None,
+                    help="build (only) the native runtime's concurrency check under this sanitizer and print its path")
     a = ap.parse_args()
-    print(build_all(a.force, a.verbose))
+    if a.sanitize:
+        print(build_race_check(a.sanitize))
+    else:
+        print(build_all(a.force, a.verbose))

@@ -10,6 +10,7 @@ all-resident decode steps replay a CUDA graph per batch size, with device-reside
 """
 from __future__ import annotations
 
+import contextlib
 import os
 
 from dataclasses import dataclass
@@ -328,6 +329,21 @@ class ModelRunner:
         return out
 
 
+@contextlib.contextmanager
+def capture_guard():
+    """No cyclic garbage collection while a stream is capturing: a collected object that owns a CUDA graph (an old decoder,
+    a runner of an earlier model) destroys it from this thread, which the capture treats as a prohibited call and dies of."""
+    import gc
+    was = gc.isenabled()
+    gc.collect()
+    gc.disable()
+    try:
+        yield
+    finally:
+        if was:
+            gc.enable()
+
+
 class _DecodeGraph:
     """A captured all-resident decode step for a fixed batch size.
 
@@ -437,7 +453,7 @@ class _DecodeGraph:
             before = _cu.LAUNCHES
             g = torch.cuda.CUDAGraph()
             # thread-local capture mode: other threads of a server (media encoders, tokenisation) may call into CUDA meanwhile
-            with torch.cuda.graph(g, capture_error_mode="thread_local"):
+            with capture_guard(), torch.cuda.graph(g, capture_error_mode="thread_local"):
                 self._body()
             self.graph = g
             self.launches_per_replay = _cu.LAUNCHES - before

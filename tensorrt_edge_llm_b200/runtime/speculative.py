@@ -22,6 +22,7 @@ Parity: ``cpp/runtime/decoding/eagleDecoder.cpp`` — ``decodeStep`` (:287-320),
 """
 from __future__ import annotations
 
+import weakref
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
@@ -83,7 +84,8 @@ class _VerifyGraph:
         dev, kv = r.device, r.kv
         i32 = dict(dtype=torch.int32, device=dev)
         t = b * nn
-        self.dec, self.b, self.nn = dec, b, nn
+        self._dec = weakref.ref(dec)              # the decoder owns this object: no reference cycle through it
+        self.b, self.nn = b, nn
         self.ids = torch.zeros(t, **i32)
         self.meta = StepMeta(
             q_start=torch.arange(0, t + 1, nn, **i32), q_len=torch.full((b,), nn, **i32), past_len=torch.zeros(b, **i32),
@@ -95,6 +97,13 @@ class _VerifyGraph:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.tgt = self.taps = None
         self.launches = 0
+
+    @property
+    def dec(self) -> "EagleDecoder":
+        d = self._dec()
+        if d is None:
+            raise RuntimeError("the decoder of this verification graph is gone")
+        return d
 
     def _body(self):
         dec = self.dec
@@ -132,7 +141,8 @@ class _VerifyGraph:
             torch.cuda.current_stream(self.dec.device).wait_stream(side)
             before = cu.LAUNCHES
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, capture_error_mode="thread_local"):
+            from .runner import capture_guard
+            with capture_guard(), torch.cuda.graph(g, capture_error_mode="thread_local"):
                 self.tgt, self.taps = self._body()
             self.graph = g
             self.launches = cu.LAUNCHES - before
