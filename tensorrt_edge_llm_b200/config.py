@@ -196,6 +196,9 @@ class ModelConfig:
     has_qk_norm: bool = False
     attention_bias: bool = False
     attention_sink_bias: bool = False      # per-query-head learned sink logit joining every softmax denominator
+    # Skip-softmax deployment (`skip_softmax.py`): per-length [[seqlen_bin, S], ...] tables, None = that phase runs dense
+    skip_softmax_prefill_table: Optional[List[List[int]]] = None
+    skip_softmax_decode_table: Optional[List[List[int]]] = None
     sliding_window: Optional[int] = None
     layer_windows: List[int] = field(default_factory=list)  # per layer: sliding window in tokens, 0 = full attention (empty = `sliding_window` everywhere)
     mrope_section: List[int] = field(default_factory=list)   # multimodal RoPE: rotary pairs per (temporal, height, width) component
@@ -368,6 +371,10 @@ class ModelConfig:
             rope_theta, rope_scaling = extra.pop("rope_theta", rope_theta), extra.pop("rope_scaling", rope_scaling)
             layer_types = []
         router = "sigmoid_group_topk" if model_type in ("nemotron_h", "deepseek_v3") and llm.get("n_routed_experts") else "softmax_topk"
+        from .skip_softmax import resolve as _resolve_skip_softmax
+        skip = _resolve_skip_softmax(hf, llm if llm is not hf else None)
+        extra.setdefault("skip_softmax_prefill_table", skip.prefill_table)
+        extra.setdefault("skip_softmax_decode_table", skip.decode_table)
         return cls(
             model_type=model_type,
             vocab_size=int(llm["vocab_size"]),
@@ -385,8 +392,8 @@ class ModelConfig:
             max_position_embeddings=int(llm.get("max_position_embeddings", 32768)),
             tie_word_embeddings=bool(hf.get("tie_word_embeddings", llm.get("tie_word_embeddings", False))),
             has_qk_norm=bool(has_qk_norm),
-            attention_bias=bool(llm.get("attention_bias", str(model_type).startswith("qwen2"))),
-            attention_sink_bias=bool(llm.get("attention_sink_bias", False)),     # Qwen2 family (text, MoE, VL): q/k/v carry a bias
+            attention_bias=bool(llm.get("attention_bias", str(model_type).startswith("qwen2"))),     # Qwen2 family (text, MoE, VL): q/k/v carry a bias
+            attention_sink_bias=bool(llm.get("attention_sink_bias", False)),
             sliding_window=llm.get("sliding_window") if (llm.get("use_sliding_window", False) or extra) else None,
             hidden_act=llm.get("hidden_activation") or llm.get("hidden_act", llm.get("mlp_hidden_act", "silu")),
             **extra,

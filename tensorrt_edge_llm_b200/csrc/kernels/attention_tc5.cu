@@ -46,6 +46,11 @@ struct AttnParams {
     int window;                // sliding window, 0 = none, -1 = no causal mask (every row sees every cached and new token)
     float scale_log2;          // softmax scale * log2(e)
     const float* sinks;        // [Hq] fp32 per-head sink logits (natural-log units) joining every row's softmax denominator, or null
+    // Skip-softmax (BLASST tile vote): skip_thr[seq] = log2(lambda) of the sequence (lambda = S / length, -inf = dense), or null.
+    // A KV tile whose largest score lies more than that below the running maximum for every query row of a warp is not
+    // exponentiated (its P rows are zeros); when all four warps vote so, the tile's P·V products are not issued either.
+    const float* skip_thr;
+    int* skip_stats;           // optional [2]: tiles processed, tiles whose P·V was skipped (diagnostics / tests), or null
     int out_bf16;
     int* status;
 };
@@ -97,6 +102,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     uint64_t* o_bar = p_free + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_bar + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    volatile uint32_t* s_keep = tmem_slot + 4;           // [2 P buffers][4 warps]: the warp computed probabilities for the tile
 
     pdl_prologue();          // step metadata and Q/KV are produced by earlier kernels
     const int warp = threadIdx.x >> 5;
@@ -199,6 +205,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
                 umma_commit(&k_empty[stage]);
                 umma_commit(&s_full[j & 1]);
             };
+            bool o_started = false;                      // the first P·V issued overwrites the accumulator
             bool ok = mbar_wait(q_full, 0, abort_flag, p.status, kStatusMmaTimeout);
             ok = ok && mbar_wait(&k_full[0], 0, abort_flag, p.status, kStatusMmaTimeout);
             if (ok) {
@@ -221,9 +228,18 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
                 tc_fence_after_sync();
                 const uint64_t dp = smem_desc_sw128(s_p + (j & 1) * kPBytes);
                 const uint64_t dv = smem_desc_sw128_mn(s_v + stage * kKvBytes, kKvTile * 128, 1024);
+                const volatile uint32_t* kf = s_keep + (j & 1) * 4;
+                const bool keep = !p.skip_thr || (kf[0] | kf[1] | kf[2] | kf[3]) != 0;
+                if (keep) {
 #pragma unroll
-                for (int k = 0; k < kKvTile / 16; ++k)
-                    umma_f16(tmem_base + kOCol, dp + 2 * k, dv + (uint64_t)(k * 2048 >> 4), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < kKvTile / 16; ++k)
+                        umma_f16(tmem_base + kOCol, dp + 2 * k, dv + (uint64_t)(k * 2048 >> 4), idesc_o, (o_started || k > 0) ? 1u : 0u);
+                    o_started = true;
+                }
+                if (p.skip_stats && (threadIdx.x & 31) == 0) {
+                    atomicAdd(&p.skip_stats[0], 1);
+                    if (!keep) atomicAdd(&p.skip_stats[1], 1);
+                }
                 umma_commit(&v_empty[stage]);
                 umma_commit(&p_free[j & 1]);
                 umma_commit(o_bar);
@@ -241,6 +257,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         const int* mask_row = p.tree_mask ? p.tree_mask + (size_t)(qrow0 + min(qi, qlen - 1)) * p.mask_words : nullptr;
         const int causal_limit = past + qi;             // last visible cache slot
         float m_used = -INFINITY, l_sum = 0.f;
+        const float skip_thr = p.skip_thr ? p.skip_thr[seq] : -INFINITY;
         bool ok = true;
         for (int j = 0; j < ntiles && ok; ++j) {
             const int b = j & 1;
@@ -290,7 +307,10 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
                 }
             }
             const float m_new = fmaxf(m_used, mx);
-            const bool need = row_valid && (m_new > m_used + kRescaleThreshold);
+            // tile vote of this warp: a row keeps the tile when its best score is within the threshold of the running
+            // maximum (a tile that raises the maximum always is); rows of a warp that all vote "skip" write zero probabilities
+            const bool warp_keep = __any_sync(0xffffffffu, row_valid && (mx - m_new >= skip_thr));
+            const bool need = warp_keep && row_valid && (m_new > m_used + kRescaleThreshold);
             // P buffer b is free once P·V of tile j-2 has completed; this wait is taken at every use of the buffer, so
             // its parity is exact (a barrier polled only now and then could be two phases ahead and alias).
             if (!mbar_wait(&p_free[b], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kStatusEpilogueTimeout)) { ok = false; break; }
@@ -307,7 +327,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
                     tmem_ld_x32(lane_addr + kOCol + c * 32, o);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                    for (int i = 0; i < 32; ++i) o[i] = f == 0.f ? 0u : __float_as_uint(__uint_as_float(o[i]) * f);   // 0: nothing accumulated yet
                     tmem_st_x32(lane_addr + kOCol + c * 32, o);
                 }
                 tmem_st_wait();
@@ -318,7 +338,8 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
                 }
             }
             uint8_t* prow = s_p + b * kPBytes + (r >> 3) * 1024 + (r & 7) * 128;
-            if (row_valid) {
+            if (lane == 0) s_keep[b * 4 + quad] = warp_keep ? 1u : 0u;      // published by the arrive on p_full below
+            if (row_valid && warp_keep) {
                 const float mref = m_used == -INFINITY ? 0.f : m_used;
                 float acc = 0.f;
 #pragma unroll
@@ -375,7 +396,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
                     tmem_ld_x32(lane_addr + kOCol + c * 32, o);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(o[i]) * inv;
+                    for (int i = 0; i < 32; ++i) v[i] = inv > 0.f ? __uint_as_float(o[i]) * inv : 0.f;
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = 0.f;
@@ -565,7 +586,7 @@ extern "C" int telb_paged_attention(const void* q, const void* kv_layer, void* o
                                     const int* tree_mask, int mask_words, int num_seqs, int total_tokens,
                                     int max_q_len, int num_pages, int max_pages, int page_size, int hq, int hkv, int d,
                                     float scale, int window, int splits, float* ws, long long ws_floats, int is_bf16,
-                                    int* status, const float* sinks, cudaStream_t stream) {
+                                    int* status, const float* sinks, const float* skip_thr, int* skip_stats, cudaStream_t stream) {
     if (num_seqs <= 0 || total_tokens <= 0) return 0;
     if (d != 64 && d != 128 && d != 256) return fail("telb_paged_attention: head_dim must be 64, 128 or 256");
     if (page_size != 64 && page_size != 128) return fail("telb_paged_attention: page size must be 64 or 128");
@@ -591,6 +612,8 @@ extern "C" int telb_paged_attention(const void* q, const void* kv_layer, void* o
     p.scale_log2 = scale * 1.4426950408889634f;
     p.out_bf16 = is_bf16;
     p.sinks = sinks;
+    p.skip_thr = skip_thr;
+    p.skip_stats = skip_stats;
     p.status = status;
     if (splits < 1) splits = 1;
     while (splits > 1 && (long long)splits * total_tokens * hq * (d + 1) > ws_floats) --splits;

@@ -267,7 +267,8 @@ def _decode_splits(meta: StepMeta, hkv: int) -> int:
 
 
 def paged_attention(q, kv_layer, meta: StepMeta, scale, sliding_window=None, sinks=None, splits: Optional[int] = None,
-                    kernel: Optional[str] = None, trace: Optional[torch.Tensor] = None, causal: bool = True) -> torch.Tensor:
+                    kernel: Optional[str] = None, trace: Optional[torch.Tensor] = None, causal: bool = True,
+                    skip_thr: Optional[torch.Tensor] = None, skip_stats: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Paged GQA attention.  Decode-shaped steps (``max_q_len * Hq/Hkv <= 16``, head_dim 128, causal)
     run the token-major XQA-style kernel; everything else the row-major tile kernel.
     ``kernel`` forces ``"decode"`` or ``"tile"``; ``causal=False`` lets every row see every token of its sequence."""
@@ -283,6 +284,12 @@ def paged_attention(q, kv_layer, meta: StepMeta, scale, sliding_window=None, sin
     ws = Workspace.get(q.device)
     tm = meta.tree_mask
     decode_ok = (tm is None and d == 128 and meta.max_q_len * group <= 16 and 16 % group == 0)
+    if skip_thr is None:
+        skip_thr = meta.skip_thr            # per-sequence skip-softmax thresholds of the step (prefill-size steps only)
+    if skip_thr is not None:
+        skip_thr = skip_thr.to(device=q.device, dtype=torch.float32).contiguous()
+        if kernel is None and meta.max_q_len * group > 16:
+            kernel = "tile"
     use_decode = decode_ok if kernel is None else (kernel == "decode")
     if use_decode:
         if not decode_ok:
@@ -303,7 +310,7 @@ def paged_attention(q, kv_layer, meta: StepMeta, scale, sliding_window=None, sin
         _p(tm), c_int(tm.shape[1] if tm is not None else 0), c_int(meta.num_seqs), c_int(t), c_int(meta.max_q_len),
         c_int(kv_layer.shape[0]), c_int(meta.page_table.shape[1]), c_int(meta.page_size), c_int(hq), c_int(hkv),
         c_int(d), c_float(scale), c_int(sliding_window or 0), c_int(splits), _p(ws.attn_ws), c_ll(ws.attn_ws.numel()),
-        c_int(_is_bf16(q)), _p(ws.status), _p(sinks), _stream()), "paged_attention", 2 if splits > 1 else 1)
+        c_int(_is_bf16(q)), _p(ws.status), _p(sinks), _p(skip_thr), _p(skip_stats), _stream()), "paged_attention", 2 if splits > 1 else 1)
     return out
 
 

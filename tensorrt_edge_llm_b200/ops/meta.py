@@ -46,6 +46,9 @@ class StepMeta:
     positions3: Optional[torch.Tensor] = None
     rope_rows: Optional[torch.Tensor] = None
     rope_pos: Optional[torch.Tensor] = None
+    # Skip-softmax: fp32 [N] log2(lambda) per sequence (lambda = S / sequence length from the deployed scale table; -inf where
+    # the sequence is shorter than the first calibrated length), or None when the deployment runs dense.
+    skip_thr: Optional[torch.Tensor] = None
 
     @property
     def is_decode(self) -> bool:

@@ -76,8 +76,14 @@ class ModelRunner:
             if p == 0:
                 self.rope_delta.pop(s, None)          # a fresh sequence on this seat
             self.kv.reserve(s, p + q)
-        return build_step_meta(q_lens, past, self.kv.table_rows(seats), self.kv.page_size, slot_ids=seats,
+        meta = build_step_meta(q_lens, past, self.kv.table_rows(seats), self.kv.page_size, slot_ids=seats,
                                logits_all=logits_all, device=self.device, tree_mask=tree_mask, positions=positions)
+        table = getattr(self.model.cfg, "skip_softmax_prefill_table", None)
+        if table and tree_mask is None and max(q_lens, default=0) > 1:
+            # skip-softmax deployment: every sequence of a prefill-size step votes with the threshold of its own length
+            from ..skip_softmax import thresholds_log2
+            meta.skip_thr = thresholds_log2(table, [p + q for p, q in zip(past, q_lens)], device=self.device)
+        return meta
 
     def rope_delta_empty(self) -> bool:
         """No resident sequence carries a multimodal position offset (captured passes take positions as given)."""
