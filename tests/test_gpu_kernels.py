@@ -228,6 +228,42 @@ def test_paged_attention_sinks(cu, kernel, case):
     _sync_check(cu)
 
 
+def test_paged_attention_skip_softmax_tile_vote(cu):
+    """BLASST tile vote: with a threshold, tiles whose scores all sit far below the running maximum are dropped (counted by the
+    kernel) and the result stays within the bound the threshold promises; without one (-inf) the kernel is bit-identical to
+    the dense run and drops nothing."""
+    q_lens, past_lens, hq, hkv, d, page = [512, 300], [1024, 0], 8, 2, 128, 64
+    q, kv, meta = _paged_setup(q_lens, past_lens, hq, hkv, d, page, torch.bfloat16, seed=11)
+    # "A-shaped" attention: the first 64 cached tokens and the most recent ones carry the weight, the far field is weak
+    kv[:, 0] *= 0.05
+    table = meta.page_table
+    for s_ in range(2):
+        first = int(table[s_, 0])
+        kv[first, 0] *= 400.0
+    scale = d ** -0.5
+    dense = cu.paged_attention(q, kv, meta, scale, kernel="tile", splits=1)
+    stats = torch.zeros(2, dtype=torch.int32, device="cuda")
+    off = torch.full((2,), float("-inf"), device="cuda")
+    same = cu.paged_attention(q, kv, meta, scale, kernel="tile", splits=1, skip_thr=off, skip_stats=stats)
+    torch.cuda.synchronize()
+    assert torch.equal(same, dense) and int(stats[1]) == 0 and int(stats[0]) > 0
+    lam = 1e-3
+    thr = torch.full((2,), float(torch.log2(torch.tensor(lam))), device="cuda")
+    stats.zero_()
+    got = cu.paged_attention(q, kv, meta, scale, kernel="tile", splits=1, skip_thr=thr, skip_stats=stats)
+    torch.cuda.synchronize()
+    tiles, skipped = int(stats[0]), int(stats[1])
+    assert skipped > 0.2 * tiles, (tiles, skipped)
+    # every dropped weight is below lambda relative to a normaliser of at least one: the error is a small multiple of lambda * L * |V|
+    assert _rel_err(got, dense) < 2e-2, _rel_err(got, dense)
+    assert not torch.isnan(got.float()).any()
+    # per-sequence thresholds: a dense sequence next to a skipping one is bit-identical to its dense result
+    mixed = torch.tensor([float("-inf"), float(thr[0])], device="cuda")
+    got2 = cu.paged_attention(q, kv, meta, scale, kernel="tile", splits=1, skip_thr=mixed)
+    assert torch.equal(got2[:512], dense[:512])
+    _sync_check(cu)
+
+
 def test_paged_attention_splits_window_tree(cu):
     q, kv, meta = _paged_setup([1, 1], [900, 333], 32, 8, 128, 64, torch.bfloat16, seed=9)
     scale = 128 ** -0.5
