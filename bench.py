@@ -103,6 +103,8 @@ def main() -> int:
     ap.add_argument("--dtype", default="nvfp4", choices=["nvfp4", "bf16", "fp16"])
     ap.add_argument("--layers", type=int, default=None, help="debug only; anything but the full depth is not the named config")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--kv-cache-dtype", default="model", choices=["model", "fp8"],
+                    help="KV page storage; anything but the default (the compute type) is not the named headline configuration")
     args = ap.parse_args()
     if args.impl == "reference":
         return _reference_arm(args)
@@ -140,7 +142,7 @@ def main() -> int:
         cfg = cfg.for_rank(rank, world)
     B, S, O = args.batch, args.input_len, args.output_len
     llm = LLM(cfg, device=str(dev), comm=comm, max_batch_size=B, max_input_len=S, max_kv_cache_capacity=S + O + 64,
-              page_size=64, max_num_tokens=8192, random_init_seed=0)
+              page_size=64, max_num_tokens=8192, random_init_seed=0, kv_cache_dtype=args.kv_cache_dtype)
     runner, kv = llm.runner, llm.kv
     g = torch.Generator().manual_seed(1234)
     prompts_host = torch.randint(0, cfg.vocab_size, (B, S), generator=g, dtype=torch.int32).pin_memory()
@@ -245,7 +247,7 @@ def main() -> int:
         "data": "synthetic (seeded uniform token ids, random-init N(0,0.02) weights)",
         "config": {"model": "Qwen3-8B-shape (36L, H4096, 32q/8kv, d128, I12288, V151936)" if args.layers == 36 else f"DEBUG {args.layers} layers",
                    "global_batch": B, "seq_len": S, "output_len": O, "parallelism": f"tp{world}", "page_size": 64,
-                   "weights": args.dtype, "comm": args.comm if world > 1 else "none",
+                   "weights": args.dtype, "kv_cache": args.kv_cache_dtype, "comm": args.comm if world > 1 else "none",
                    "l2": "256 MiB buffer written between timed steps; weights (>= 4.6 GB) exceed L2 every decode step",
                    "prefill_ms": round(maxr(statistics.median(pre_ms)), 3),
                    "decode_ms_per_token": round(maxr(statistics.median(dec_ms)) / max(1, O - 1), 4),

@@ -63,6 +63,8 @@ class Attention(nn.Module):
             self.k_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, cfg.compute_dtype)
         else:
             self.q_norm = self.k_norm = None
+        self.prefix = prefix
+        self.register_buffer("kv_scales", torch.ones(2, dtype=torch.float32))      # FP8 KV cache: K and V dequantisation scales
         if getattr(cfg, "attention_sink_bias", False):
             # one learned logit per (local) query head with no value row: it only grows the softmax denominator
             # (reference: tensorrt_edgellm/config.py:691-692, the draft models' attention_sink_bias buffer)
@@ -70,11 +72,27 @@ class Attention(nn.Module):
         else:
             self.attention_sink_bias = None
 
+    def load_checkpoint(self, fetch) -> bool:
+        """FP8 KV-cache scales of quantised checkpoints (``k_proj.k_scale`` / ``v_proj.v_scale``, one per layer)."""
+        for i, name in enumerate(("k_proj.k_scale", "v_proj.v_scale")):
+            t = fetch(f"{self.prefix}.{name}")
+            if t is not None:
+                self.kv_scales[i] = t.float().reshape(-1)[0]
+        return False
+
     def forward(self, x: torch.Tensor, meta: StepMeta, kv_layer: torch.Tensor, cos_sin: torch.Tensor) -> torch.Tensor:
         qkv = self.qkv_proj(x)
+        pool_layer = None
+        if kv_layer.dtype == torch.float8_e4m3fn:
+            # FP8 pages: attention works on the 16-bit staging copy of the pages this step touches; the new rows are
+            # quantised into the pool (and rounded in the copy) right after they are written
+            pool_layer = kv_layer
+            kv_layer = ops.kv_fp8_prepare(pool_layer, meta, self.kv_scales, qkv.dtype, self.sliding_window or 0)
         q = ops.rope_kv_write(qkv, kv_layer, meta, cos_sin, self.num_q_heads, self.num_kv_heads, self.head_dim,
                               None if self.q_norm is None else self.q_norm.weight,
                               None if self.k_norm is None else self.k_norm.weight, self.eps)
+        if pool_layer is not None:
+            ops.kv_fp8_commit(pool_layer, kv_layer, meta, self.kv_scales)
         gs = self.o_proj.fused_input_scale() if hasattr(self.o_proj, "fused_input_scale") else None
         sinks = self.attention_sink_bias
         if gs is not None and q.is_cuda and ops.cuda_ops().decode_attention_quant_ok(q.shape, kv_layer.shape[2], meta):

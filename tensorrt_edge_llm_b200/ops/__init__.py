@@ -121,6 +121,25 @@ def paged_attention(q, kv_layer, meta, scale, sliding_window=None, sinks=None, c
     return ref.paged_attention(q, kv_layer, meta, scale, sliding_window, sinks, causal=causal)
 
 
+def kv_fp8_prepare(kv_layer, meta, scales, dtype, window=0):
+    """FP8 KV layer → the 16-bit staging layer holding the step's cached pages (new rows are written into it next)."""
+    if kv_layer.is_cuda:
+        cu = cuda_ops()
+        stage = cu.kv_fp8_stage(kv_layer, dtype)
+        cu.kv_fp8_load(kv_layer, stage, meta, scales, window)
+        return stage
+    stage = torch.zeros(kv_layer.shape, dtype=dtype)
+    ref.kv_fp8_load(kv_layer, stage, meta, scales, window)
+    return stage
+
+
+def kv_fp8_commit(kv_layer, stage, meta, scales):
+    """Quantise the step's new rows from the staging layer into the FP8 layer (and round the staged rows the same way)."""
+    if kv_layer.is_cuda:
+        return cuda_ops().kv_fp8_store(kv_layer, stage, meta, scales)
+    return ref.kv_fp8_store(kv_layer, stage, meta, scales)
+
+
 def argmax(logits):
     if logits.is_cuda:
         return cuda_ops().argmax(logits)

@@ -248,6 +248,34 @@ def rope_kv_write(qkv, kv_layer, meta: StepMeta, cos_sin, num_q_heads, num_kv_he
     return q
 
 
+_KV_STAGE: Dict[tuple, torch.Tensor] = {}
+
+
+def kv_fp8_stage(kv_layer: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """The 16-bit staging layer an FP8 KV pool's attention works on (one per device, shape and type, shared by all layers)."""
+    key = (kv_layer.device, tuple(kv_layer.shape), dtype)
+    st = _KV_STAGE.get(key)
+    if st is None:
+        st = _KV_STAGE[key] = torch.zeros(kv_layer.shape, dtype=dtype, device=kv_layer.device)
+    return st
+
+
+def kv_fp8_load(kv_layer: torch.Tensor, stage: torch.Tensor, meta: StepMeta, scales: torch.Tensor, window: int = 0) -> None:
+    """Expand the pages that hold the step's cached tokens from the FP8 layer ``[pages, 2, Hkv, P, D]`` into ``stage``."""
+    _, _, hkv, psz, d = kv_layer.shape
+    _check(lib().telb_kv_fp8_load(_p(kv_layer), _p(stage), _p(meta.past_len), _p(meta.page_table), _p(scales), c_int(meta.num_seqs),
+                                  c_int(meta.page_table.shape[1]), c_int(psz), c_int(hkv), c_int(d), c_int(window or 0),
+                                  c_int(_is_bf16(stage)), _stream()), "kv_fp8_load")
+
+
+def kv_fp8_store(kv_layer: torch.Tensor, stage: torch.Tensor, meta: StepMeta, scales: torch.Tensor) -> None:
+    """Quantise the step's new K / V rows from ``stage`` into the FP8 layer and write the rounded values back to ``stage``."""
+    _, _, hkv, psz, d = kv_layer.shape
+    _check(lib().telb_kv_fp8_store(_p(kv_layer), _p(stage), _p(meta.seq_ids), _p(meta.q_start), _p(meta.past_len), _p(meta.page_table),
+                                   _p(meta.kv_offsets), _p(scales), c_int(meta.num_tokens), c_int(meta.page_table.shape[1]), c_int(psz),
+                                   c_int(hkv), c_int(d), c_int(_is_bf16(stage)), _stream()), "kv_fp8_store")
+
+
 def _attn_splits(meta: StepMeta, hkv: int, group: int) -> int:
     tq = 128 // group
     qtiles = (meta.max_q_len + tq - 1) // tq
@@ -832,7 +860,9 @@ def eagle_select_verify(p_sc, p_tok, p_par, p_dep, root, keep: int):
 
 
 def kv_commit_path(pool, page_table, past_len, path, path_len) -> None:
-    assert pool.is_contiguous() and pool.element_size() == 2
+    assert pool.is_contiguous() and pool.element_size() in (1, 2)
+    if pool.element_size() == 1:            # FP8 pages: a row of D bytes moves as D / 2 16-bit elements
+        pool = pool.view(torch.int16)
     layers, pages, _, hkv, psz, d = pool.shape
     pt, pl, pth, pln = page_table.to(torch.int32).contiguous(), past_len.to(torch.int32).contiguous(), path.contiguous(), path_len.contiguous()
     _check(lib().telb_kv_commit_path(_p(pool), _p(pt), _p(pl), _p(pth), _p(pln), c_int(path.shape[0]), c_int(path.shape[1]),

@@ -751,3 +751,36 @@ def eagle_select_verify(p_sc, p_tok, p_par, p_dep, root, keep: int):
     par = torch.cat([torch.full((b, 1), -1, device=dev, dtype=torch.long), parents], dim=1).to(i32)
     dep = torch.cat([torch.zeros(b, 1, dtype=torch.long, device=dev), p_dep.long().gather(1, sel)], dim=1).to(i32)
     return tok, par, dep
+
+
+# ------------------------------------------------------------------------------------------
+# FP8 (E4M3) KV storage: host formulation of csrc/kernels/kv_fp8.cu
+
+
+def kv_fp8_load(kv_layer: torch.Tensor, stage: torch.Tensor, meta, scales: torch.Tensor, window: int = 0) -> None:
+    psz = kv_layer.shape[3]
+    table = meta.page_table.cpu()
+    sc = scales.float().view(2, 1, 1, 1).to(stage.device)
+    for s in range(meta.num_seqs):
+        past = int(meta.past_len[s])
+        for lp in range((past + psz - 1) // psz):
+            page = int(table[s, lp])
+            if page >= 0:
+                stage[page] = (kv_layer[page].float() * sc).to(stage.dtype)
+
+
+def kv_fp8_store(kv_layer: torch.Tensor, stage: torch.Tensor, meta, scales: torch.Tensor) -> None:
+    psz = kv_layer.shape[3]
+    table = meta.page_table.cpu()
+    sc = scales.float().view(2, 1, 1).to(stage.device)
+    for t in range(meta.num_tokens):
+        s = int(meta.seq_ids[t])
+        off = int(meta.kv_offsets[t]) if meta.kv_offsets is not None else t - int(meta.q_start[s])
+        slot = int(meta.past_len[s]) + off
+        page = int(table[s, slot // psz])
+        if page < 0:
+            continue
+        rows = stage[page, :, :, slot % psz].float()                       # [2, Hkv, D]
+        q = (rows / sc).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+        kv_layer[page, :, :, slot % psz] = q
+        stage[page, :, :, slot % psz] = (q.float() * sc).to(stage.dtype)

@@ -59,7 +59,10 @@ class KVCacheManager:
 
     def __init__(self, cfg: ModelConfig, num_pages: int, page_size: int = 64, max_seats: int = 64,
                  max_pages_per_seq: int = 64, device="cpu", dtype: Optional[torch.dtype] = None,
-                 num_layers: Optional[int] = None, bounded_swa: Optional[bool] = None):
+                 num_layers: Optional[int] = None, bounded_swa: Optional[bool] = None, kv_dtype: Optional[str] = None):
+        """``kv_dtype``: ``"fp8"`` stores keys and values as E4M3 bytes (half the bytes per cached token; the attention layers
+        work on a 16-bit staging copy of the pages a step touches, see ``csrc/kernels/kv_fp8.cu``); ``None`` / ``"auto"`` follows
+        the checkpoint's ``kv_cache_quant`` setting; ``"fp16"`` / ``"bf16"`` / ``"model"`` keep the compute type."""
         self.cfg = cfg
         # Bounded sliding-window storage (``cpp/runtime/state/boundedSwaKVPageManager.cpp`` in the reference): every
         # attention layer of the model looks back at most `sliding_window` tokens, so pages that lie wholly before the
@@ -78,6 +81,13 @@ class KVCacheManager:
         self.num_layers = num_layers if num_layers is not None else sum(t == LAYER_ATTENTION for t in cfg.layer_types)
         hkv = max(cfg.num_key_value_heads // cfg.tp_size, 1)
         self.dtype = dtype or cfg.compute_dtype
+        if kv_dtype in (None, "auto"):
+            kv_dtype = getattr(cfg.quant, "kv_cache_quant", None)
+        self.kv_fp8 = str(kv_dtype).lower() in ("fp8", "fp8_e4m3", "e4m3") and dtype is None
+        if self.kv_fp8:
+            if cfg.head_dim % 16:
+                raise ValueError("an FP8 KV cache needs a head_dim that is a multiple of 16")
+            self.dtype = torch.float8_e4m3fn
         self.pool = torch.zeros(self.num_layers, num_pages, 2, hkv, page_size, cfg.head_dim, dtype=self.dtype, device=device)
         # hybrid models: model layer index → attention pool index, plus the recurrent state pools
         self._attn_index = {}
@@ -87,7 +97,7 @@ class KVCacheManager:
         self.recurrent = None
         if cfg.is_hybrid:
             from ..models.nemotron_h import RecurrentState
-            self.recurrent = RecurrentState(cfg, max_seats, device, self.dtype)
+            self.recurrent = RecurrentState(cfg, max_seats, device, cfg.compute_dtype if self.kv_fp8 else self.dtype)
         self.alloc = PageAllocator(num_pages)
         self.table = torch.full((max_seats, max_pages_per_seq), -1, dtype=torch.int32)   # host truth
         self.lengths = [0] * max_seats

@@ -53,7 +53,8 @@ class LLM:
                  tokenizer=None, kv_pages: Optional[int] = None, enable_in_flight_batching: bool = False,
                  enable_prefix_cache: bool = False, scheduling: Optional[dict] = None, draft_model=None, speculative=None,
                  context_cache_max_records: int = 4096, context_cache_max_snapshots: int = 64,
-                 embedding_quantization: Optional[str] = None, tp_mirror=None, mapping: Optional[Mapping] = None):
+                 embedding_quantization: Optional[str] = None, tp_mirror=None, mapping: Optional[Mapping] = None,
+                 kv_cache_dtype: Optional[str] = None):
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.device = torch.device(device)
@@ -75,8 +76,9 @@ class LLM:
         canvas_headroom = self.cfg.diffusion.canvas_length if self.cfg.diffusion is not None else 0
         pages_per_seq = (max_kv_cache_capacity + canvas_headroom + page_size - 1) // page_size
         total_pages = kv_pages or (pages_per_seq * max_batch_size + 1)
+        # "fp8": E4M3 KV pages (`--kv-cache-quantization fp8` checkpoints select it through their quantisation config)
         self.kv = KVCacheManager(self.cfg, total_pages, page_size, max_seats=max_batch_size,
-                                 max_pages_per_seq=pages_per_seq, device=self.device)
+                                 max_pages_per_seq=pages_per_seq, device=self.device, kv_dtype=kv_cache_dtype)
         self.runner = ModelRunner(self.model, self.kv, self.device, max_num_tokens=max_num_tokens)
         self.runner.vocab_map = self._vocab_map
         self.lora = None
@@ -103,7 +105,7 @@ class LLM:
             headroom = draft.cfg.dflash_block_size + 8 if is_dflash else spec.verify_tokens + spec.draft_steps * spec.top_k
             sp_pages = (max_kv_cache_capacity + headroom + page_size - 1) // page_size
             self.kv = KVCacheManager(self.cfg, (kv_pages or sp_pages * max_batch_size + 1), page_size, max_seats=max_batch_size,
-                                     max_pages_per_seq=sp_pages, device=self.device)
+                                     max_pages_per_seq=sp_pages, device=self.device, kv_dtype=kv_cache_dtype)
             self.runner = ModelRunner(self.model, self.kv, self.device, max_num_tokens=max_num_tokens)
             dkv = KVCacheManager(draft.cfg, sp_pages * max_batch_size + 1, page_size, max_seats=max_batch_size, max_pages_per_seq=sp_pages,
                                  device=self.device, num_layers=draft.cfg.num_hidden_layers if is_dflash else 1)

@@ -55,7 +55,7 @@ def build_llm(cfg: ServerConfig):
             tp_kw["tp_mirror"] = build_llm.mirror
         m.device = str(dev)
     llm = LLM(m.model, device=m.device or None, **spec_kw, **tp_kw, max_batch_size=m.max_batch_size, max_input_len=m.max_input_len,
-              max_kv_cache_capacity=m.max_kv_cache_capacity, page_size=m.kv_page_size, max_num_tokens=m.max_num_tokens or 8192,
+              max_kv_cache_capacity=m.max_kv_cache_capacity, kv_cache_dtype=m.kv_cache_dtype, page_size=m.kv_page_size, max_num_tokens=m.max_num_tokens or 8192,
               tokenizer=tok, enable_in_flight_batching=m.enable_in_flight_batching and int(os.environ.get("RANK", "0")) == 0,
               enable_prefix_cache=m.context_cache_config.enabled, context_cache_max_records=m.context_cache_config.max_records,
               context_cache_max_snapshots=m.context_cache_config.max_snapshots, scheduling=m.scheduling_dict() if m.enable_in_flight_batching else None)

@@ -62,6 +62,7 @@ class ModelConfig:
     max_input_len: int = 4096
     max_batch_size: int = 1
     max_kv_cache_capacity: int = 8192
+    kv_cache_dtype: str = "auto"                   # auto (follow the checkpoint's kv_cache_quant) | fp8 | model
     speculative_config: Optional[SpeculativeConfig] = None
     context_cache_config: ContextCacheConfig = field(default_factory=ContextCacheConfig)
     multimodal_config: MultimodalConfig = field(default_factory=MultimodalConfig)
@@ -145,6 +146,8 @@ def create_argument_parser(prog: str = "trtedge serve") -> argparse.ArgumentPars
     m.add_argument("--max-input-len", type=int, default=4096)
     m.add_argument("--max-batch-size", type=int, default=1)
     m.add_argument("--max-kv-cache-capacity", type=int, default=8192)
+    m.add_argument("--kv-cache-dtype", "--kv-cache-quantization", dest="kv_cache_dtype", default="auto", choices=["auto", "fp8", "model"],
+                   help="KV page storage: fp8 = E4M3 bytes (half the memory per cached token); auto follows the checkpoint")
     m.add_argument("--enable-in-flight-batching", action="store_true")
     m.add_argument("--ifb-scheduling-mode", default="auto", choices=["auto", "mixed", "prefill_first", "single_cohort"])
     m.add_argument("--max-num-tokens", type=int, default=0)
@@ -206,7 +209,7 @@ def parse_server_config(argv: Optional[Sequence[str]] = None) -> ServerConfig:
                     setattr(spec, name, v)
     model = ModelConfig(
         model=ns.model, max_input_len=ns.max_input_len, max_batch_size=ns.max_batch_size,
-        max_kv_cache_capacity=ns.max_kv_cache_capacity, speculative_config=spec,
+        max_kv_cache_capacity=ns.max_kv_cache_capacity, kv_cache_dtype=getattr(ns, "kv_cache_dtype", "auto"), speculative_config=spec,
         context_cache_config=ContextCacheConfig(enabled=ns.enable_context_cache, max_records=ns.context_cache_max_records,
                                                 max_snapshots=ns.context_cache_max_snapshots),
         multimodal_config=MultimodalConfig(ns.max_image_tokens_per_image, ns.max_image_tokens, ns.encoder_cache_budget_bytes),
