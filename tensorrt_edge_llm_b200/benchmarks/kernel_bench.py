@@ -117,8 +117,17 @@ def bench_attention(args):
             cu._check(cu.lib().telb_set_decode_variant(args.variant), "set_decode_variant", 0)
     flip = [0]
 
+    fp8 = getattr(args, "kv_dtype", "model") == "fp8"
+    if fp8:                 # E4M3 pages read in place by the decode kernel (decode-shaped steps only)
+        kv, kv_alt = kv.to(torch.float8_e4m3fn), kv_alt.to(torch.float8_e4m3fn)
+        q8 = qt.to(torch.float8_e4m3fn)
+        kv_scales = torch.ones(2, device="cuda")
+
     def fn():
         flip[0] ^= 1
+        if fp8:
+            return cu.paged_attention_decode_fp8(q8, kv if flip[0] else kv_alt, meta, d ** -0.5, None, kv_scales, torch.bfloat16,
+                                                 splits=args.splits or None)
         return cu.paged_attention(qt, kv if flip[0] else kv_alt, meta, d ** -0.5, splits=args.splits or None)
 
     out = fn()
@@ -139,7 +148,7 @@ def bench_attention(args):
         for role, evs in names.items():
             for e, nm in enumerate(evs):
                 print(f"trace {nm:>14}: " + " ".join(f"{int(tr[role, j, e]):6d}" for j in range(tiles)))
-    kv_bytes = b * (past + q) * hkv * d * 2 * 2
+    kv_bytes = b * (past + q) * hkv * d * 2 * (1 if fp8 else 2)
     flops = 4.0 * b * hq * d * (q * past + q * (q + 1) / 2)
     roof = max(flops / fl, kv_bytes / bw)
     print(json.dumps({"kernel": "paged_attention", "batch": b, "past": past, "q": q, "median_us": round(med * 1e6, 2),
@@ -294,6 +303,7 @@ def main():
     a.add_argument("--variant", type=int, default=-1, help="decode kernel ring / residency variant (see telb_set_decode_variant)")
     a.add_argument("--splits", type=int, default=0, help="KV splits (0 = heuristic)")
     a.add_argument("--check", action="store_true", help="compare with the fp32 reference first")
+    a.add_argument("--kv-dtype", default="model", choices=["model", "fp8"], help="fp8: E4M3 cache pages read in place (decode shapes)")
     a.add_argument("--trace", action="store_true", help="print the per-tile timeline of the first CTA of the decode kernel")
     a.add_argument("--trace-tiles", type=int, default=0, help="tiles of the first CTA to print (it walks several items)")
     o = sub.add_parser("ops")

@@ -42,11 +42,23 @@ struct DecParams {
     int num_seqs, num_items;        // items = sequences x KV heads x splits, walked by persistent CTAs
     float scale_log2;
     const float* sinks;             // [Hq] fp32 per-head sink logits (natural-log units), or null
+    // FP8 (E4M3) cache pages read directly (KV8 kernels): kv_scales[0] multiplies the scores (K dequantisation scale),
+    // kv_scales[1] the output (V scale); probabilities enter the P·V product as E4M3 of 256 x p.
+    const float* kv_scales;
     int* status;
     // Optional timeline of CTA 0: trace[role][tile][event] in ns since the CTA started (role 0 producer,
     // 1 MMA issuer, 2 softmax; 4 events per tile, 64 tiles at most).  Null in normal use.
     unsigned long long* trace;
 };
+
+// E4M3 x E4M3 MMA with fp32 accumulation (K = 32 per instruction); the instruction descriptor has the layout of the 16-bit
+// kind with format code 0 (= E4M3) for both operands.
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
 
 constexpr int kDecThreads = 192;
 constexpr int kDecTile = 128;      // cached tokens per tile
@@ -98,14 +110,19 @@ __device__ __forceinline__ DecItem decode_item(const DecParams& p, int item) {
 // two P buffers keep cycling across item boundaries (flat tile counter), Q and the O accumulator are double
 // buffered per item, so the next item's loads and scores overlap the previous item's epilogue and no CTA slot
 // idles while another wave of CTAs starts up.
-template <int D, typename T, int KS, int VS, int MINB, int NC>
+// KV8: the cache pages (and the Q and P operands) are E4M3 bytes: a 128-byte swizzle span holds 128 elements instead of 64, an
+// MMA consumes 32 of them per instruction instead of 16, everything else (roles, rings, barriers, softmax) is shared.
+template <int D, typename T, int KS, int VS, int MINB, int NC, bool KV8 = false>
 __global__ void __launch_bounds__(kDecThreads, MINB)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_kv, DecParams p) {
-    constexpr int kDChunks = D / 64;
-    constexpr int kChunkBytes = kDecTile * 128;                 // [128 tokens x 64 d]
+    constexpr int kEB = KV8 ? 1 : 2;                            // bytes per operand element
+    constexpr int kSpan = 128 / kEB;                            // elements per 128-byte swizzle span
+    constexpr int kMmaK = KV8 ? 32 : 16;                        // K elements per MMA
+    constexpr int kDChunks = D / kSpan;
+    constexpr int kChunkBytes = kDecTile * 128;                 // [128 tokens x one span of d]
     constexpr int kKvBytes = kDChunks * kChunkBytes;            // one K or V tile
     constexpr int kQBytes = kDChunks * kDecN * 128;
-    constexpr int kPBytes = 2 * kDecN * 128;                    // Pᵀ: [16 cols x 128 tokens] bf16, two 64-token chunks
+    constexpr int kPBytes = (kDecTile / kSpan) * kDecN * 128;   // Pᵀ: [16 cols x 128 tokens], one span of tokens per chunk
     constexpr int kSBufs = 4;                                   // score buffers S0..S3 @ 0, 16, 32, 48
     constexpr int kOCol = kSBufs * 16;                          // O accumulators O0, O1 (16 columns each)
     constexpr int kTmemCols = 128;
@@ -195,7 +212,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
                     mbar_expect_tx(&q_full[ig & 1], kQBytes);
 #pragma unroll
                     for (int c = 0; c < kDChunks; ++c)
-                        tma_load_3d(s_q + (ig & 1) * kQBytes + c * (kDecN * 128), &tma_q, &q_full[ig & 1], c * 64, it.kvh * p.group, it.qrow0);
+                        tma_load_3d(s_q + (ig & 1) * kQBytes + c * (kDecN * 128), &tma_q, &q_full[ig & 1], c * kSpan, it.kvh * p.group, it.qrow0);
                 }
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -225,7 +242,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
 #pragma unroll
                                 for (int c = 0; c < kDChunks; ++c)
                                     tma_load_2d(s_k + ks * kKvBytes + c * kChunkBytes + h * rows_per_load * 128, &tma_kv, &k_full[ks],
-                                                c * 64, rows[h]);
+                                                c * kSpan, rows[h]);
                             ok = mbar_wait(&v_empty[vs], vph, abort_flag, p.status, kStatusProducerTimeout);
                         }
                         if (ok) {
@@ -235,7 +252,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
 #pragma unroll
                                 for (int c = 0; c < kDChunks; ++c)
                                     tma_load_2d(s_v + vs * kKvBytes + c * kChunkBytes + h * rows_per_load * 128, &tma_kv, &v_full[vs],
-                                                c * 64, rows[h] + p.hkv * p.page_size);
+                                                c * kSpan, rows[h] + p.hkv * p.page_size);
                         }
                     }
                     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -246,8 +263,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
-            const uint32_t idesc_s = idesc_f16(128, kDecN, kBf16);                    // A = K (K-major), B = Q (K-major)
-            const uint32_t idesc_o = idesc_f16(128, kDecN, kBf16, /*a_mn_major=*/true);   // A = Vᵀ (MN-major), B = Pᵀ (K-major)
+            // format code 0 is fp16 for the 16-bit kind and E4M3 for the 8-bit kind
+            const uint32_t idesc_s = idesc_f16(128, kDecN, kBf16 && !KV8);                    // A = K (K-major), B = Q (K-major)
+            const uint32_t idesc_o = idesc_f16(128, kDecN, kBf16 && !KV8, /*a_mn_major=*/true);   // A = Vᵀ (MN-major), B = Pᵀ (K-major)
             // Two cursors walk the same item list: scores (S = K Qᵀ) run up to kSBufs tiles ahead of P·V, so the
             // score MMA is never on the softmax → P·V dependency chain.
             struct Cursor {
@@ -281,10 +299,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
                     const uint64_t dq = smem_desc_sw128(s_q + (cs.ig & 1) * kQBytes);
                     const uint32_t d_tmem = tmem_base + (cs.jg % kSBufs) * 16;
 #pragma unroll
-                    for (int k = 0; k < D / 16; ++k) {
+                    for (int k = 0; k < D / kMmaK; ++k) {          // four MMAs per 128-byte span, 32 bytes each
                         const int c = k >> 2, kk = k & 3;
-                        umma_f16(d_tmem, dk + (uint64_t)((c * kChunkBytes) >> 4) + 2 * kk, dq + (uint64_t)((c * kDecN * 128) >> 4) + 2 * kk,
-                                 idesc_s, k > 0 ? 1u : 0u);
+                        const uint64_t da_ = dk + (uint64_t)((c * kChunkBytes) >> 4) + 2 * kk, db_ = dq + (uint64_t)((c * kDecN * 128) >> 4) + 2 * kk;
+                        if constexpr (KV8) umma_f8(d_tmem, da_, db_, idesc_s, k > 0 ? 1u : 0u);
+                        else umma_f16(d_tmem, da_, db_, idesc_s, k > 0 ? 1u : 0u);
                     }
                     umma_commit(&k_empty[stage]);
                     umma_commit(&s_full[cs.jg % kSBufs]);
@@ -309,9 +328,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
                     const uint64_t dp = smem_desc_sw128(s_p + (cp.jg & 1) * kPBytes);
                     const uint32_t d_o = tmem_base + kOCol + (cp.ig & 1) * 16;
 #pragma unroll
-                    for (int k = 0; k < kDecTile / 16; ++k)     // 16 tokens per MMA: 2048 B of V rows, 32 B of a P row
-                        umma_f16(d_o, dv + (uint64_t)((k * 2048) >> 4), dp + (uint64_t)(((k >> 2) * (kDecN * 128)) >> 4) + 2 * (k & 3),
-                                 idesc_o, (cp.j > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < kDecTile / kMmaK; ++k) {    // 16 (32) tokens per MMA: 2048 (4096) B of V rows, 32 B of a P row
+                        const uint64_t da_ = dv + (uint64_t)((k * kMmaK * 128) >> 4), db_ = dp + (uint64_t)(((k >> 2) * (kDecN * 128)) >> 4) + 2 * (k & 3);
+                        if constexpr (KV8) umma_f8(d_o, da_, db_, idesc_o, (cp.j > 0 || k > 0) ? 1u : 0u);
+                        else umma_f16(d_o, da_, db_, idesc_o, (cp.j > 0 || k > 0) ? 1u : 0u);
+                    }
                     umma_commit(&v_empty[stage]);
                     umma_commit(&p_free[cp.jg & 1]);
                     ++cp.j;
@@ -343,6 +364,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         const int r = quad * 32 + lane;                 // cached token within the tile == TMEM lane (S); feature d (O)
         const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
         const int gshift = 31 - __clz(p.group);         // the group size is a power of two
+        // FP8 pages: the K scale multiplies the scores, the V scale and the 1 / 256 of the scaled probabilities the output
+        const float scale_log2 = KV8 ? p.scale_log2 * p.kv_scales[0] : p.scale_log2;
+        const float o_scale = KV8 ? p.kv_scales[1] * (1.f / 256.f) : 1.f;
         bool ok = true;
         int jg = 0, ig = 0;
         for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
@@ -378,7 +402,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
                         const int qi = c >> gshift;
                         bool vis = tk <= it.past + qi;
                         if (p.window > 0) vis = vis && tk > it.past + qi - p.window;
-                        s[c] = vis ? __uint_as_float(raw[c]) * p.scale_log2 : -INFINITY;
+                        s[c] = vis ? __uint_as_float(raw[c]) * scale_log2 : -INFINITY;
                         const float wm = warp_max_f32(s[c]);
                         if (lane == c) red[(warp - 2) * 16 + c] = wm;
                     } else {
@@ -422,20 +446,23 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
                 }
                 // Pᵀ[c][token]: row c is 128 tokens = two 128-byte swizzled chunks of 64 tokens.  Dead columns hold the
                 // zeros written at start-up.
-                uint8_t* pbase = s_p + b * kPBytes + (r >> 6) * (kDecN * 128);
-                const int tl = r & 63;
+                // one 128-byte span of row c holds kSpan tokens; element bytes kEB
+                uint8_t* pbase = s_p + b * kPBytes + (r / kSpan) * (kDecN * 128);
+                const int tl = r % kSpan;
+                constexpr int kPer16 = 16 / kEB;               // tokens per 16-byte swizzle unit
 #pragma unroll
                 for (int c = 0; c < NC; ++c) {
+                    uint8_t* dst = pbase + (c >> 3) * 1024 + (c & 7) * 128 + ((((tl / kPer16) ^ (c & 7)) & 7) << 4) + (tl % kPer16) * kEB;
                     if (c < ncol) {
                         const float mref = m_used[c] == -INFINITY ? 0.f : m_used[c];
                         const float e = exp2f(s[c] - mref);
                         l_part[c] += e;
-                        T* dst = reinterpret_cast<T*>(pbase + (c >> 3) * 1024 + (c & 7) * 128 + ((((tl >> 3) ^ (c & 7)) & 7) << 4) + (tl & 7) * 2);
-                        *dst = Cvt<T>::from_f(e);
+                        if constexpr (KV8) *dst = __nv_cvt_float_to_fp8(e * 256.f, __NV_SATFINITE, __NV_E4M3);
+                        else *reinterpret_cast<T*>(dst) = Cvt<T>::from_f(e);
                     } else if (c < kDecN) {
                         // a shorter sequence may follow a longer one in this CTA: clear columns it no longer uses
-                        T* dst = reinterpret_cast<T*>(pbase + (c >> 3) * 1024 + (c & 7) * 128 + ((((tl >> 3) ^ (c & 7)) & 7) << 4) + (tl & 7) * 2);
-                        *dst = Cvt<T>::from_f(0.f);
+                        if constexpr (KV8) *dst = 0;
+                        else *reinterpret_cast<T*>(dst) = Cvt<T>::from_f(0.f);
                     }
                 }
                 fence_proxy_async_smem();
@@ -486,7 +513,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
                                 lse = z;
                             }
                         }
-                        const float val = have ? __uint_as_float(o[c]) * inv : 0.f;
+                        const float val = have ? __uint_as_float(o[c]) * inv * o_scale : 0.f;
                         if (p.splits == 1 && p.oq != nullptr) {
                             // the output projection reads NVFP4: quantise here (16 consecutive dims = 16 consecutive lanes),
                             // with the rounding of the 16-bit store the unfused path would have made first
@@ -521,19 +548,19 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     }
 }
 
-template <int D, typename T, int KS, int VS, int MINB, int NC>
+template <int D, typename T, int KS, int VS, int MINB, int NC, bool KV8 = false>
 static int launch_decode_variant(const CUtensorMap& tq, const CUtensorMap& tkv, const DecParams& p, int nseq, cudaStream_t stream) {
-    constexpr int kv = (D / 64) * kDecTile * 128;
+    constexpr int kv = (D / (KV8 ? 128 : 64)) * kDecTile * 128;
     constexpr int smem = (KS + VS) * kv + 2 * 4096 + 2 * 2 * kDecN * 128 + 1024 + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, T, KS, VS, MINB, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, T, KS, VS, MINB, NC, KV8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail("cudaFuncSetAttribute(attn_decode)", e);
         configured = true;
     }
     const int slots = MINB * sm_count();
     const int grid = p.num_items < slots ? p.num_items : slots;
-    TELB_LAUNCH("attn_decode_kernel", (attn_decode_kernel<D, T, KS, VS, MINB, NC>), dim3(grid), dim3(kDecThreads), smem, stream, tq, tkv, p);
+    TELB_LAUNCH("attn_decode_kernel", (attn_decode_kernel<D, T, KS, VS, MINB, NC, KV8>), dim3(grid), dim3(kDecThreads), smem, stream, tq, tkv, p);
     TELB_CHECK_LAUNCH("attn_decode_kernel");
     return 0;
 }
@@ -547,6 +574,14 @@ static int launch_decode_nc(const CUtensorMap& tq, const CUtensorMap& tkv, const
         case 2: return launch_decode_variant<D, T, 2, 2, 1, NC>(tq, tkv, p, nseq, stream);     // 1 CTA / SM, two-stage rings
         default: return launch_decode_variant<D, T, 3, 3, 1, NC>(tq, tkv, p, nseq, stream);    // 1 CTA / SM, three-stage rings
     }
+}
+
+// FP8 pages: half the bytes per tile, so two CTAs per SM hold two-stage rings
+template <int D, typename T>
+static int launch_decode_fp8(const CUtensorMap& tq, const CUtensorMap& tkv, const DecParams& p, int nseq, int max_cols, cudaStream_t stream) {
+    if (max_cols <= 4) return launch_decode_variant<D, T, 2, 2, 2, 4, true>(tq, tkv, p, nseq, stream);
+    if (max_cols <= 8) return launch_decode_variant<D, T, 2, 2, 2, 8, true>(tq, tkv, p, nseq, stream);
+    return launch_decode_variant<D, T, 2, 2, 2, 16, true>(tq, tkv, p, nseq, stream);
 }
 
 template <int D, typename T>
@@ -594,7 +629,8 @@ extern "C" int telb_paged_attention_decode(const void* q, const void* kv_layer, 
 static int decode_impl(const void* q, const void* kv_layer, void* out, void* oq, void* osf, const float* ogs, const int* q_start,
                        const int* q_len, const int* past_len, const int* page_table, int num_seqs, int total_tokens, int max_q_len,
                        int num_pages, int max_pages, int page_size, int hq, int hkv, int d, float scale, int window, int splits, float* ws,
-                       long long ws_floats, int is_bf16, int* status, unsigned long long* trace, const float* sinks, cudaStream_t stream);
+                       long long ws_floats, int is_bf16, int* status, unsigned long long* trace, const float* sinks, const float* kv_scales,
+                       cudaStream_t stream);
 
 // Same call with a timeline buffer (3 x 64 x 4 u64, zeroed by the caller) filled by the first CTA.
 extern "C" int telb_paged_attention_decode_traced(const void* q, const void* kv_layer, void* out, const int* q_start,
@@ -604,7 +640,7 @@ extern "C" int telb_paged_attention_decode_traced(const void* q, const void* kv_
                                                   long long ws_floats, int is_bf16, int* status, unsigned long long* trace,
                                                   const float* sinks, cudaStream_t stream) {
     return decode_impl(q, kv_layer, out, nullptr, nullptr, nullptr, q_start, q_len, past_len, page_table, num_seqs, total_tokens, max_q_len,
-                       num_pages, max_pages, page_size, hq, hkv, d, scale, window, splits, ws, ws_floats, is_bf16, status, trace, sinks, stream);
+                       num_pages, max_pages, page_size, hq, hkv, d, scale, window, splits, ws, ws_floats, is_bf16, status, trace, sinks, nullptr, stream);
 }
 
 // Decode attention whose output is written as NVFP4 only (packed codes out_xq [T, Hq * D / 2], atom-layout scales out_sf over
@@ -617,13 +653,31 @@ extern "C" int telb_paged_attention_decode_quant(const void* q, const void* kv_l
                                                  int is_bf16, int* status, const float* sinks, cudaStream_t stream) {
     if (!out_xq || !out_sf || !out_global_scale) return fail("telb_paged_attention_decode_quant: output buffers and scale are required");
     return decode_impl(q, kv_layer, nullptr, out_xq, out_sf, out_global_scale, q_start, q_len, past_len, page_table, num_seqs, total_tokens,
-                       max_q_len, num_pages, max_pages, page_size, hq, hkv, d, scale, window, splits, ws, ws_floats, is_bf16, status, nullptr, sinks, stream);
+                       max_q_len, num_pages, max_pages, page_size, hq, hkv, d, scale, window, splits, ws, ws_floats, is_bf16, status, nullptr, sinks, nullptr, stream);
+}
+
+// Decode attention over FP8 (E4M3) cache pages read in place: `q8` is the query tensor cast to E4M3 [T, Hq, D], `kv_layer` the
+// FP8 layer [pages, 2, Hkv, P, D], `kv_scales` the layer's (K, V) dequantisation scales on the device.  The output is 16-bit
+// (`out`) or, when `out_xq` is given, NVFP4 for the projection that follows.  `is_bf16` names the output / activation type.
+extern "C" int telb_paged_attention_decode_fp8(const void* q8, const void* kv_layer, void* out, void* out_xq, void* out_sf,
+                                               const float* out_global_scale, const float* kv_scales, const int* q_start, const int* q_len,
+                                               const int* past_len, const int* page_table, int num_seqs, int total_tokens, int max_q_len,
+                                               int num_pages, int max_pages, int page_size, int hq, int hkv, int d, float scale, int window,
+                                               int splits, float* ws, long long ws_floats, int is_bf16, int* status, const float* sinks,
+                                               cudaStream_t stream) {
+    if (!kv_scales) return fail("telb_paged_attention_decode_fp8: the K / V scales are required");
+    if (!out && !out_xq) return fail("telb_paged_attention_decode_fp8: no output buffer");
+    if (out_xq && (!out_sf || !out_global_scale)) return fail("telb_paged_attention_decode_fp8: NVFP4 output needs its scale buffers");
+    return decode_impl(q8, kv_layer, out, out_xq, out_sf, out_global_scale, q_start, q_len, past_len, page_table, num_seqs, total_tokens,
+                       max_q_len, num_pages, max_pages, page_size, hq, hkv, d, scale, window, splits, ws, ws_floats, is_bf16, status, nullptr,
+                       sinks, kv_scales, stream);
 }
 
 static int decode_impl(const void* q, const void* kv_layer, void* out, void* oq, void* osf, const float* ogs, const int* q_start,
                        const int* q_len, const int* past_len, const int* page_table, int num_seqs, int total_tokens, int max_q_len,
                        int num_pages, int max_pages, int page_size, int hq, int hkv, int d, float scale, int window, int splits, float* ws,
-                       long long ws_floats, int is_bf16, int* status, unsigned long long* trace, const float* sinks, cudaStream_t stream) {
+                       long long ws_floats, int is_bf16, int* status, unsigned long long* trace, const float* sinks, const float* kv_scales,
+                       cudaStream_t stream) {
     if (num_seqs <= 0 || total_tokens <= 0) return 0;
     if (d != 128) return fail("telb_paged_attention_decode: head_dim must be 128");
     if (page_size != 64 && page_size != 128) return fail("telb_paged_attention_decode: page size must be 64 or 128");
@@ -638,6 +692,7 @@ static int decode_impl(const void* q, const void* kv_layer, void* out, void* oq,
     p.ogs = ogs;
     p.ok64 = telb_nvfp4_k64_pad(hq * d);
     p.sinks = sinks;
+    p.kv_scales = kv_scales;
     p.q_start = q_start;
     p.q_len = q_len;
     p.past_len = past_len;
@@ -660,22 +715,30 @@ static int decode_impl(const void* q, const void* kv_layer, void* out, void* oq,
     p.num_items = num_seqs * hkv * splits;
     p.ws_o = ws;
     p.ws_lse = ws ? ws + (size_t)splits * total_tokens * hq * d : nullptr;
-    const CUtensorMapDataType dt = is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const bool fp8 = kv_scales != nullptr;
+    const CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : (is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+    const uint64_t eb = fp8 ? 1 : 2;                  // bytes per element of Q and of the cache
+    const uint32_t span = fp8 ? 128 : 64;             // elements per 128-byte swizzle span
     CUtensorMap tq, tkv;
     {
-        // Q viewed as [tokens][Hq][D]; one box = (64 features, G heads, 16/G tokens) → 16 rows of 128 B
+        // Q viewed as [tokens][Hq][D]; one box = (one span of features, G heads, 16/G tokens) → 16 rows of 128 B
         const uint64_t dims[3] = {(uint64_t)d, (uint64_t)hq, (uint64_t)total_tokens};
-        const uint64_t strides[2] = {(uint64_t)d * 2, (uint64_t)hq * d * 2};
-        const uint32_t box[3] = {64, (uint32_t)group, (uint32_t)(kDecN / group)};
+        const uint64_t strides[2] = {(uint64_t)d * eb, (uint64_t)hq * d * eb};
+        const uint32_t box[3] = {span, (uint32_t)group, (uint32_t)(kDecN / group)};
         if (make_tmap_nd(&tq, dt, 3, q, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
     }
     {
         const uint64_t rows = (uint64_t)num_pages * 2 * hkv * page_size;
         const uint32_t box_rows = page_size == 64 ? 64 : 128;
-        if (make_tmap_2d(&tkv, dt, 2, kv_layer, rows, d, (uint64_t)d * 2, box_rows, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+        if (make_tmap_2d(&tkv, dt, (int)eb, kv_layer, rows, d, (uint64_t)d * eb, box_rows, span, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
     }
-    const int rc = is_bf16 ? launch_decode<128, __nv_bfloat16>(tq, tkv, p, num_seqs, max_q_len * group, stream)
-                           : launch_decode<128, __half>(tq, tkv, p, num_seqs, max_q_len * group, stream);
+    int rc;
+    if (fp8)
+        rc = is_bf16 ? launch_decode_fp8<128, __nv_bfloat16>(tq, tkv, p, num_seqs, max_q_len * group, stream)
+                     : launch_decode_fp8<128, __half>(tq, tkv, p, num_seqs, max_q_len * group, stream);
+    else
+        rc = is_bf16 ? launch_decode<128, __nv_bfloat16>(tq, tkv, p, num_seqs, max_q_len * group, stream)
+                     : launch_decode<128, __half>(tq, tkv, p, num_seqs, max_q_len * group, stream);
     if (rc) return rc;
     if (splits > 1 && oq) return telb_attn_combine_quant(p.ws_o, p.ws_lse, oq, osf, ogs, total_tokens, hq, splits, d, is_bf16, stream);
     if (splits > 1) return telb_attn_combine(p.ws_o, p.ws_lse, out, total_tokens * hq, splits, d, is_bf16, stream);

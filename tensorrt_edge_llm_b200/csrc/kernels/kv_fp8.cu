@@ -53,14 +53,28 @@ kv_fp8_load_kernel(const uint4* __restrict__ pool, uint4* __restrict__ stage, co
     }
 }
 
-// grid (tokens, 2 * Hkv); block d / 8 threads, eight elements each.
+// grid (tokens, 2 * Hkv [+ Hq]); block d / 8 threads, eight elements each.  Rows past 2 * Hkv cast the token's query heads to
+// E4M3 (saturating, scale 1) for the attention kernel that reads FP8 pages in place.
 template <typename T>
 __global__ void kv_fp8_store_kernel(uint8_t* __restrict__ pool, T* __restrict__ stage, const int* __restrict__ seq_ids,
                                     const int* __restrict__ q_start, const int* __restrict__ past_len, const int* __restrict__ page_table,
                                     const int* __restrict__ kv_offsets, const float* __restrict__ scales, int max_pages, int page_size,
-                                    int hkv, int d) {
+                                    int hkv, int d, const T* __restrict__ q, uint8_t* __restrict__ q8, int hq) {
     pdl_prologue();
     const int t = blockIdx.x;
+    if ((int)blockIdx.y >= 2 * hkv) {
+        const int e0q = threadIdx.x * 8;
+        if (e0q >= d) return;
+        const size_t qrow = ((size_t)t * hq + (blockIdx.y - 2 * hkv)) * d + e0q;
+        const uint4 v = *reinterpret_cast<const uint4*>(q + qrow);
+        const T* x = reinterpret_cast<const T*>(&v);
+        uint2 packed;
+        uint8_t* pb = reinterpret_cast<uint8_t*>(&packed);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) pb[i] = __nv_cvt_float_to_fp8(Cvt<T>::to_f(x[i]), __NV_SATFINITE, __NV_E4M3);
+        *reinterpret_cast<uint2*>(q8 + qrow) = packed;
+        return;
+    }
     const int kv = blockIdx.y / hkv, head = blockIdx.y - kv * hkv;
     const int s = seq_ids[t];
     const int off = kv_offsets ? kv_offsets[t] : (t - q_start[s]);
@@ -105,17 +119,20 @@ extern "C" int telb_kv_fp8_load(const void* pool, void* stage, const int* past_l
     return 0;
 }
 
+// `q` / `q8` (both or neither): the step's query rows [tokens, hq, d] and their E4M3 copy, cast in the same launch.
 extern "C" int telb_kv_fp8_store(void* pool, void* stage, const int* seq_ids, const int* q_start, const int* past_len, const int* page_table,
                                  const int* kv_offsets, const float* scales, int tokens, int max_pages, int page_size, int hkv, int d,
-                                 int is_bf16, cudaStream_t stream) {
+                                 int is_bf16, const void* q, void* q8, int hq, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (d % 8 || d > 1024) return fail("telb_kv_fp8_store: head_dim must be a multiple of 8 (at most 1024)");
-    const dim3 grid(tokens, 2 * hkv), blk((d / 8 + 31) / 32 * 32);
+    if ((q == nullptr) != (q8 == nullptr)) return fail("telb_kv_fp8_store: pass the query rows together with their E4M3 destination");
+    const dim3 grid(tokens, 2 * hkv + (q ? hq : 0)), blk((d / 8 + 31) / 32 * 32);
     if (is_bf16)
         TELB_LAUNCH("kv_fp8_store_kernel", (kv_fp8_store_kernel<__nv_bfloat16>), grid, blk, 0, stream, (uint8_t*)pool, (__nv_bfloat16*)stage,
-                    seq_ids, q_start, past_len, page_table, kv_offsets, scales, max_pages, page_size, hkv, d);
+                    seq_ids, q_start, past_len, page_table, kv_offsets, scales, max_pages, page_size, hkv, d, (const __nv_bfloat16*)q,
+                    (uint8_t*)q8, hq);
     else
         TELB_LAUNCH("kv_fp8_store_kernel", (kv_fp8_store_kernel<__half>), grid, blk, 0, stream, (uint8_t*)pool, (__half*)stage, seq_ids,
-                    q_start, past_len, page_table, kv_offsets, scales, max_pages, page_size, hkv, d);
+                    q_start, past_len, page_table, kv_offsets, scales, max_pages, page_size, hkv, d, (const __half*)q, (uint8_t*)q8, hq);
     return 0;
 }

@@ -72,6 +72,20 @@ class Attention(nn.Module):
         else:
             self.attention_sink_bias = None
 
+    def _forward_fp8_decode(self, qkv, meta, pool_layer, cos_sin):
+        """Decode-shaped step over FP8 pages: the new rows pass through the staging layer only to be quantised into the pool
+        (no page is expanded), the queries are cast to E4M3 in the same launch, and the decode kernel reads the pool in place."""
+        cu = ops.cuda_ops()
+        stage = cu.kv_fp8_stage(pool_layer, qkv.dtype)
+        q = ops.rope_kv_write(qkv, stage, meta, cos_sin, self.num_q_heads, self.num_kv_heads, self.head_dim,
+                              None if self.q_norm is None else self.q_norm.weight,
+                              None if self.k_norm is None else self.k_norm.weight, self.eps)
+        q8 = cu.kv_fp8_store(pool_layer, stage, meta, self.kv_scales, q)
+        gs = self.o_proj.fused_input_scale() if hasattr(self.o_proj, "fused_input_scale") else None
+        o = cu.paged_attention_decode_fp8(q8, pool_layer, meta, self.scale, self.sliding_window, self.kv_scales, qkv.dtype,
+                                          out_scale=gs, sinks=self.attention_sink_bias)
+        return self.o_proj(o if gs is not None else o.reshape(o.shape[0], -1))
+
     def load_checkpoint(self, fetch) -> bool:
         """FP8 KV-cache scales of quantised checkpoints (``k_proj.k_scale`` / ``v_proj.v_scale``, one per layer)."""
         for i, name in enumerate(("k_proj.k_scale", "v_proj.v_scale")):
@@ -84,9 +98,11 @@ class Attention(nn.Module):
         qkv = self.qkv_proj(x)
         pool_layer = None
         if kv_layer.dtype == torch.float8_e4m3fn:
-            # FP8 pages: attention works on the 16-bit staging copy of the pages this step touches; the new rows are
-            # quantised into the pool (and rounded in the copy) right after they are written
             pool_layer = kv_layer
+            if qkv.is_cuda and ops.cuda_ops().fp8_decode_ok((qkv.shape[0], self.num_q_heads, self.head_dim), kv_layer.shape[2], meta):
+                return self._forward_fp8_decode(qkv, meta, pool_layer, cos_sin)
+            # FP8 pages, prefill-size step: attention works on the 16-bit staging copy of the pages this step touches; the new
+            # rows are quantised into the pool (and rounded in the copy) right after they are written
             kv_layer = ops.kv_fp8_prepare(pool_layer, meta, self.kv_scales, qkv.dtype, self.sliding_window or 0)
         q = ops.rope_kv_write(qkv, kv_layer, meta, cos_sin, self.num_q_heads, self.num_kv_heads, self.head_dim,
                               None if self.q_norm is None else self.q_norm.weight,

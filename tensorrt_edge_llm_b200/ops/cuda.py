@@ -268,12 +268,57 @@ def kv_fp8_load(kv_layer: torch.Tensor, stage: torch.Tensor, meta: StepMeta, sca
                                   c_int(_is_bf16(stage)), _stream()), "kv_fp8_load")
 
 
-def kv_fp8_store(kv_layer: torch.Tensor, stage: torch.Tensor, meta: StepMeta, scales: torch.Tensor) -> None:
-    """Quantise the step's new K / V rows from ``stage`` into the FP8 layer and write the rounded values back to ``stage``."""
+def kv_fp8_store(kv_layer: torch.Tensor, stage: torch.Tensor, meta: StepMeta, scales: torch.Tensor, q: Optional[torch.Tensor] = None):
+    """Quantise the step's new K / V rows from ``stage`` into the FP8 layer and write the rounded values back to ``stage``.
+    With ``q`` ``[T, Hq, D]`` the same launch also casts the query rows to E4M3 and returns them (else None)."""
     _, _, hkv, psz, d = kv_layer.shape
+    q8 = None
+    if q is not None:
+        q = q.contiguous()
+        q8 = torch.empty(q.shape, dtype=torch.float8_e4m3fn, device=q.device)
     _check(lib().telb_kv_fp8_store(_p(kv_layer), _p(stage), _p(meta.seq_ids), _p(meta.q_start), _p(meta.past_len), _p(meta.page_table),
                                    _p(meta.kv_offsets), _p(scales), c_int(meta.num_tokens), c_int(meta.page_table.shape[1]), c_int(psz),
-                                   c_int(hkv), c_int(d), c_int(_is_bf16(stage)), _stream()), "kv_fp8_store")
+                                   c_int(hkv), c_int(d), c_int(_is_bf16(stage)), _p(q), _p(q8), c_int(q.shape[1] if q is not None else 0),
+                                   _stream()), "kv_fp8_store")
+    return q8
+
+
+def fp8_decode_ok(q_shape, hkv: int, meta: StepMeta) -> bool:
+    """Whether the decode kernel that reads FP8 pages in place covers this step (decode-shaped, head_dim 128)."""
+    t, hq, d = q_shape
+    group = hq // hkv
+    return (meta.tree_mask is None and d == 128 and meta.max_q_len * group <= 16 and 16 % group == 0
+            and os.environ.get("TELB_DISABLE_FP8_DECODE_ATTN", "0") != "1")
+
+
+def paged_attention_decode_fp8(q8: torch.Tensor, kv_layer: torch.Tensor, meta: StepMeta, scale: float, sliding_window, kv_scales: torch.Tensor,
+                               out_dtype: torch.dtype, out_scale: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
+                               splits: Optional[int] = None):
+    """Decode-shaped attention over FP8 (E4M3) pages read in place.  ``q8``: the query rows cast to E4M3.  Returns 16-bit rows
+    ``[T, Hq, D]`` of ``out_dtype``, or ``QuantActs`` over ``[T, Hq * D]`` when ``out_scale`` (the next projection's NVFP4 input
+    scale) is given."""
+    t, hq, d = q8.shape
+    hkv = kv_layer.shape[2]
+    if splits is None:
+        splits = _decode_splits(meta, hkv)
+    ws = Workspace.get(q8.device)
+    L = lib()
+    out = xq = sf = None
+    if out_scale is None:
+        out = torch.empty(t, hq, d, dtype=out_dtype, device=q8.device)
+    else:
+        L.telb_nvfp4_sf_bytes.restype = c_ll
+        xq = torch.empty(t, hq * d // 2, dtype=torch.uint8, device=q8.device)
+        sf = _sf_buffer(L.telb_nvfp4_sf_bytes(c_ll(t), c_int(hq * d)), hq * d, q8.device)
+    if sinks is not None:
+        sinks = sinks.to(device=q8.device, dtype=torch.float32).contiguous()
+    _check(L.telb_paged_attention_decode_fp8(
+        _p(q8), _p(kv_layer), _p(out), _p(xq), _p(sf), _p(out_scale), _p(kv_scales), _p(meta.q_start), _p(meta.q_len), _p(meta.past_len),
+        _p(meta.page_table), c_int(meta.num_seqs), c_int(t), c_int(meta.max_q_len), c_int(kv_layer.shape[0]), c_int(meta.page_table.shape[1]),
+        c_int(meta.page_size), c_int(hq), c_int(hkv), c_int(d), c_float(scale), c_int(sliding_window or 0), c_int(splits), _p(ws.attn_ws),
+        c_ll(ws.attn_ws.numel()), c_int(1 if out_dtype == torch.bfloat16 else 0), _p(ws.status), _p(sinks), _stream()),
+        "paged_attention_decode_fp8", 2 if splits > 1 else 1)
+    return out if out_scale is None else QuantActs(xq, sf, (t, hq * d), out_dtype)
 
 
 def _attn_splits(meta: StepMeta, hkv: int, group: int) -> int:

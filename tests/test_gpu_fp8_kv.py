@@ -46,6 +46,56 @@ def test_kv_fp8_load_and_store_kernels(dtype):
     cu.Workspace.get(torch.device("cuda", 0)).check_status()
 
 
+@pytest.mark.parametrize("case", [([1], [100], 32, 8, 64), ([1, 1, 1], [5, 64, 700], 32, 8, 64), ([1] * 9, [0, 1, 63, 64, 127, 128, 129, 1000, 2047], 32, 8, 64),
+                                  ([2, 1, 4], [10, 300, 77], 16, 4, 64), ([1, 1], [500, 90], 16, 1, 64), ([1, 3], [150, 260], 32, 8, 128)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_decode_attention_reads_fp8_pages_in_place(case, dtype):
+    """The decode kernel's E4M3 variant (K, V, Q and the probabilities enter the tensor cores as E4M3) against the fp32 statement
+    on the dequantised operands, with and without KV splits, a sliding window and the NVFP4 output epilogue."""
+    from tensorrt_edge_llm_b200.ops import cuda as cu
+    q_lens, past_lens, hq, hkv, page = case
+    d = 128
+    g = torch.Generator().manual_seed(sum(past_lens) + hq)
+    n = len(q_lens)
+    max_pages = max((a + b + page - 1) // page for a, b in zip(q_lens, past_lens)) + 1
+    total = n * max_pages + 2
+    perm = torch.randperm(total, generator=g)
+    table = torch.full((n, max_pages), -1, dtype=torch.int32)
+    k = 0
+    for s_ in range(n):
+        need = (q_lens[s_] + past_lens[s_] + page - 1) // page
+        table[s_, :need] = perm[k:k + need].to(torch.int32)
+        k += need
+    meta = build_step_meta(q_lens, past_lens, table, page).to("cuda")
+    scales = torch.tensor([0.02, 0.05])
+    kv = torch.randn(total, 2, hkv, page, d, generator=g)
+    pool = (kv / scales.view(1, 2, 1, 1, 1)).clamp(-448, 448).to(torch.float8_e4m3fn)
+    kv_deq = (pool.float() * scales.view(1, 2, 1, 1, 1)).to(dtype)
+    q = torch.randn(sum(q_lens), hq, d, generator=g).to(dtype)
+    q8 = q.float().clamp(-448, 448).to(torch.float8_e4m3fn)
+    scale = d ** -0.5
+    meta_c = build_step_meta(q_lens, past_lens, table, page)
+    want = ref.paged_attention(q8.float().to(dtype), kv_deq, meta_c, scale).float()
+    for splits in (1, 3):
+        got = cu.paged_attention_decode_fp8(q8.cuda(), pool.cuda(), meta, scale, None, scales.cuda(), dtype, splits=splits)
+        torch.cuda.synchronize()
+        err = (got.float().cpu() - want).norm() / want.norm()
+        cos = torch.nn.functional.cosine_similarity(got.float().cpu().flatten(), want.flatten(), dim=0)
+        # E4M3 probabilities carry ~3.6 % rms error per element, which the flat attention of random inputs does not average away
+        assert err < 8e-2 and cos > 0.997, (splits, float(err), float(cos))
+    want_w = ref.paged_attention(q8.float().to(dtype), kv_deq, meta_c, scale, sliding_window=100).float()
+    got_w = cu.paged_attention_decode_fp8(q8.cuda(), pool.cuda(), meta, scale, 100, scales.cuda(), dtype)
+    assert (got_w.float().cpu() - want_w).norm() / want_w.norm() < 8e-2
+    # NVFP4 epilogue == the 16-bit output through the stand-alone quantiser
+    gs = torch.tensor(0.004, device="cuda")
+    plain = cu.paged_attention_decode_fp8(q8.cuda(), pool.cuda(), meta, scale, None, scales.cuda(), dtype, splits=1)
+    xq_ref, _ = cu.nvfp4_quantize(plain.reshape(plain.shape[0], -1), gs)
+    qa = cu.paged_attention_decode_fp8(q8.cuda(), pool.cuda(), meta, scale, None, scales.cuda(), dtype, out_scale=gs, splits=1)
+    torch.cuda.synchronize()
+    assert torch.equal(qa.xq, xq_ref)
+    cu.Workspace.get(torch.device("cuda", 0)).check_status()
+
+
 def test_model_with_fp8_kv_tracks_16_bit_cache_eager_and_graph():
     dev = torch.device("cuda", 0)
     cfg = tiny_llama_config(num_hidden_layers=3, vocab_size=512, dtype="bfloat16", head_dim=128, num_attention_heads=4, num_key_value_heads=2,
