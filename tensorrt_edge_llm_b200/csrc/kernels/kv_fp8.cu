@@ -53,51 +53,54 @@ kv_fp8_load_kernel(const uint4* __restrict__ pool, uint4* __restrict__ stage, co
     }
 }
 
-// grid (tokens, 2 * Hkv [+ Hq]); block d / 8 threads, eight elements each.  Rows past 2 * Hkv cast the token's query heads to
-// E4M3 (saturating, scale 1) for the attention kernel that reads FP8 pages in place.
+// One CTA per token: its 2 * Hkv cache rows (and, when given, its Hq query rows, cast to E4M3 with saturation and scale 1 for the
+// attention kernel that reads FP8 pages in place) are walked in pieces of eight elements.
 template <typename T>
-__global__ void kv_fp8_store_kernel(uint8_t* __restrict__ pool, T* __restrict__ stage, const int* __restrict__ seq_ids,
-                                    const int* __restrict__ q_start, const int* __restrict__ past_len, const int* __restrict__ page_table,
-                                    const int* __restrict__ kv_offsets, const float* __restrict__ scales, int max_pages, int page_size,
-                                    int hkv, int d, const T* __restrict__ q, uint8_t* __restrict__ q8, int hq) {
+__global__ void __launch_bounds__(256)
+kv_fp8_store_kernel(uint8_t* __restrict__ pool, T* __restrict__ stage, const int* __restrict__ seq_ids,
+                    const int* __restrict__ q_start, const int* __restrict__ past_len, const int* __restrict__ page_table,
+                    const int* __restrict__ kv_offsets, const float* __restrict__ scales, int max_pages, int page_size,
+                    int hkv, int d, const T* __restrict__ q, uint8_t* __restrict__ q8, int hq) {
     pdl_prologue();
     const int t = blockIdx.x;
-    if ((int)blockIdx.y >= 2 * hkv) {
-        const int e0q = threadIdx.x * 8;
-        if (e0q >= d) return;
-        const size_t qrow = ((size_t)t * hq + (blockIdx.y - 2 * hkv)) * d + e0q;
-        const uint4 v = *reinterpret_cast<const uint4*>(q + qrow);
-        const T* x = reinterpret_cast<const T*>(&v);
-        uint2 packed;
-        uint8_t* pb = reinterpret_cast<uint8_t*>(&packed);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) pb[i] = __nv_cvt_float_to_fp8(Cvt<T>::to_f(x[i]), __NV_SATFINITE, __NV_E4M3);
-        *reinterpret_cast<uint2*>(q8 + qrow) = packed;
-        return;
-    }
-    const int kv = blockIdx.y / hkv, head = blockIdx.y - kv * hkv;
     const int s = seq_ids[t];
     const int off = kv_offsets ? kv_offsets[t] : (t - q_start[s]);
     const int slot = past_len[s] + off;
     const int page = page_table[(size_t)s * max_pages + slot / page_size];
-    if (page < 0) return;
-    const size_t row = ((((size_t)page * 2 + kv) * hkv + head) * page_size + slot % page_size) * d;
-    const float scale = scales[kv];
-    const float inv = scale > 0.f ? 1.f / scale : 0.f;
-    const int e0 = threadIdx.x * 8;
-    if (e0 >= d) return;
-    uint4 v = *reinterpret_cast<const uint4*>(stage + row + e0);
-    T* x = reinterpret_cast<T*>(&v);
-    uint2 packed;
-    uint8_t* pb = reinterpret_cast<uint8_t*>(&packed);
+    const int per_row = d / 8;
+    const int kv_pieces = page >= 0 ? 2 * hkv * per_row : 0;
+    for (int i = threadIdx.x; i < kv_pieces; i += blockDim.x) {
+        const int rowi = i / per_row, e0 = (i - rowi * per_row) * 8;
+        const int kv = rowi / hkv, head = rowi - kv * hkv;
+        const size_t row = ((((size_t)page * 2 + kv) * hkv + head) * page_size + slot % page_size) * d;
+        const float scale = scales[kv];
+        const float inv = scale > 0.f ? 1.f / scale : 0.f;
+        uint4 v = *reinterpret_cast<const uint4*>(stage + row + e0);
+        T* x = reinterpret_cast<T*>(&v);
+        uint2 packed;
+        uint8_t* pb = reinterpret_cast<uint8_t*>(&packed);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const __nv_fp8_storage_t q = __nv_cvt_float_to_fp8(Cvt<T>::to_f(x[i]) * inv, __NV_SATFINITE, __NV_E4M3);
-        pb[i] = q;
-        x[i] = Cvt<T>::from_f(__half2float(__half(__nv_cvt_fp8_to_halfraw(q, __NV_E4M3))) * scale);
+        for (int j = 0; j < 8; ++j) {
+            const __nv_fp8_storage_t qv = __nv_cvt_float_to_fp8(Cvt<T>::to_f(x[j]) * inv, __NV_SATFINITE, __NV_E4M3);
+            pb[j] = qv;
+            x[j] = Cvt<T>::from_f(__half2float(__half(__nv_cvt_fp8_to_halfraw(qv, __NV_E4M3))) * scale);
+        }
+        *reinterpret_cast<uint2*>(pool + row + e0) = packed;
+        *reinterpret_cast<uint4*>(stage + row + e0) = v;
     }
-    *reinterpret_cast<uint2*>(pool + row + e0) = packed;
-    *reinterpret_cast<uint4*>(stage + row + e0) = v;
+    if (q != nullptr) {
+        const int q_pieces = hq * per_row;
+        const size_t base = (size_t)t * hq * d;
+        for (int i = threadIdx.x; i < q_pieces; i += blockDim.x) {
+            const uint4 v = *reinterpret_cast<const uint4*>(q + base + (size_t)i * 8);
+            const T* x = reinterpret_cast<const T*>(&v);
+            uint2 packed;
+            uint8_t* pb = reinterpret_cast<uint8_t*>(&packed);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) pb[j] = __nv_cvt_float_to_fp8(Cvt<T>::to_f(x[j]), __NV_SATFINITE, __NV_E4M3);
+            *reinterpret_cast<uint2*>(q8 + base + (size_t)i * 8) = packed;
+        }
+    }
 }
 
 }  // namespace telb
@@ -126,7 +129,7 @@ extern "C" int telb_kv_fp8_store(void* pool, void* stage, const int* seq_ids, co
     if (tokens <= 0) return 0;
     if (d % 8 || d > 1024) return fail("telb_kv_fp8_store: head_dim must be a multiple of 8 (at most 1024)");
     if ((q == nullptr) != (q8 == nullptr)) return fail("telb_kv_fp8_store: pass the query rows together with their E4M3 destination");
-    const dim3 grid(tokens, 2 * hkv + (q ? hq : 0)), blk((d / 8 + 31) / 32 * 32);
+    const dim3 grid(tokens), blk(256);
     if (is_bf16)
         TELB_LAUNCH("kv_fp8_store_kernel", (kv_fp8_store_kernel<__nv_bfloat16>), grid, blk, 0, stream, (uint8_t*)pool, (__nv_bfloat16*)stage,
                     seq_ids, q_start, past_len, page_table, kv_offsets, scales, max_pages, page_size, hkv, d, (const __nv_bfloat16*)q,
