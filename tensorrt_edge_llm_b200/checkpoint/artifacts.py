@@ -69,9 +69,7 @@ def write_artifacts(model_dir: str, out_dir: str, tensor_parallel_size: int = 1,
     for rank in range(tp):
         mapping = Mapping(tp_size=tp, tp_rank=rank, **({"ep_size": tp, "ep_rank": rank} if expert_parallel else {}))
         cfg = ModelConfig.from_pretrained(model_dir, mapping)
-        with torch.device("meta"):
-            model = model_class_for(cfg)(cfg, None)
-        model = model.to_empty(device="cpu")
+        model = model_class_for(cfg)(cfg, None)       # a real construction: buffers the checkpoint does not carry keep their defaults
         load_weights(model, model_dir, strict=True)
         state = {k: v for k, v in model.state_dict().items()}
         fn = f"rank{rank}.safetensors"

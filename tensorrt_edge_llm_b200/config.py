@@ -373,6 +373,7 @@ class ModelConfig:
         router = "sigmoid_group_topk" if model_type in ("nemotron_h", "deepseek_v3") and llm.get("n_routed_experts") else "softmax_topk"
         from .skip_softmax import resolve as _resolve_skip_softmax
         skip = _resolve_skip_softmax(hf, llm if llm is not hf else None)
+        family_extra = bool(extra)            # family-specific fields parsed above (they decide the sliding-window rule below)
         extra.setdefault("skip_softmax_prefill_table", skip.prefill_table)
         extra.setdefault("skip_softmax_decode_table", skip.decode_table)
         return cls(
@@ -394,7 +395,7 @@ class ModelConfig:
             has_qk_norm=bool(has_qk_norm),
             attention_bias=bool(llm.get("attention_bias", str(model_type).startswith("qwen2"))),     # Qwen2 family (text, MoE, VL): q/k/v carry a bias
             attention_sink_bias=bool(llm.get("attention_sink_bias", False)),
-            sliding_window=llm.get("sliding_window") if (llm.get("use_sliding_window", False) or extra) else None,
+            sliding_window=llm.get("sliding_window") if (llm.get("use_sliding_window", False) or family_extra) else None,
             hidden_act=llm.get("hidden_activation") or llm.get("hidden_act", llm.get("mlp_hidden_act", "silu")),
             **extra,
             dtype=torch_dtype,

@@ -622,6 +622,9 @@ def gemm_skinny(x, weight, *, x_sf=None, w_sf=None, alpha=None, bias=None, resid
     return out
 
 
+INT4_GEMV_MAX_ROWS = 0 if os.environ.get("TELB_DISABLE_INT4_GEMV", "0") == "1" else 4
+
+
 def gemm_int4_awq(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, group: int, bias=None, residual=None, ranks: int = 0):
     """W4A16 linear on ModelOpt-prepacked INT4 weights (``wq [N/2, K]`` uint8, ``scales [N, K/group]`` in ``x``'s dtype).
     Decode-size steps (M <= 128) expand the 4-bit tiles inside the GEMM kernel, so only 4-bit weights cross HBM; larger
@@ -635,6 +638,13 @@ def gemm_int4_awq(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, group
     if scales.dtype != x.dtype:
         scales = scales.to(x.dtype)
     ok = n % 2 == 0 and k % 64 == 0 and group >= 64 and group % 64 == 0 and k % group == 0
+    if m <= INT4_GEMV_MAX_ROWS and ok and m * k * 2 <= 200 * 1024:
+        # one to four rows: a CUDA-core GEMV streams the packed weights once (the tensor-core tile would be almost empty)
+        out = torch.empty(m, n, dtype=x.dtype, device=x.device)
+        _check(lib().telb_gemv_int4(_p(x2), _p(wq), _p(scales.contiguous()), _p(out), c_int(m), c_int(n), c_int(k), c_int(group), _p(bias),
+                                    _p(residual.reshape(m, n).contiguous() if residual is not None else None), c_int(_is_bf16(x)), _stream()),
+               "gemv_int4")
+        return out.reshape(*lead, n)
     if m <= 128 and ok:
         out = torch.empty(m, n, dtype=x.dtype, device=x.device)
         ws = Workspace.get(x.device)
