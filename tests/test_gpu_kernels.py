@@ -459,6 +459,30 @@ def test_gemm_int4_awq_in_kernel(cu, m, n, k, group, ranks, dtype):
     _sync_check(cu)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,n,k,group", [(1, 6144, 4096, 128), (2, 4096, 12288, 128), (3, 1000, 512, 64), (4, 24576, 4096, 128), (1, 64, 128, 64)])
+def test_gemv_int4_awq_few_rows(cu, m, n, k, group, dtype, monkeypatch):
+    """One to four rows take the CUDA-core GEMV (exact code expansion, fp32 sums): against the fp32 statement, with bias and
+    residual, and against the tensor-core path with the GEMV switched off."""
+    g = torch.Generator(device="cuda").manual_seed(m * 7 + n + k)
+    x = torch.randn(m, k, device="cuda", generator=g).to(dtype)
+    wq = torch.randint(0, 256, (n // 2, k), device="cuda", generator=g, dtype=torch.uint8)
+    scales = (torch.rand(n, k // group, device="cuda", generator=g) * 0.02 + 0.005).to(dtype)
+    bias = torch.randn(n, device="cuda", generator=g).to(dtype)
+    res = torch.randn(m, n, device="cuda", generator=g).to(dtype)
+    wd = ref.int4_awq_dequantize(wq, scales, None, group)
+    want = x.float() @ wd.t() + bias.float() + res.float()
+    assert cu.INT4_GEMV_MAX_ROWS == 4
+    got = cu.gemm_int4_awq(x, wq, scales, group, bias=bias, residual=res)
+    torch.cuda.synchronize()
+    assert got.shape == (m, n) and _rel_err(got, want) < 4e-3, _rel_err(got, want)
+    monkeypatch.setattr(cu, "INT4_GEMV_MAX_ROWS", 0)
+    if k % 64 == 0 and group % 64 == 0:
+        other = cu.gemm_int4_awq(x, wq, scales, group, bias=bias, residual=res)
+        assert _rel_err(got, other.float()) < 6e-3
+    _sync_check(cu)
+
+
 def test_skinny_chain_in_cuda_graph(cu):
     """Back-to-back decode GEMMs launched with programmatic dependent launch, captured and replayed."""
     g = torch.Generator(device="cuda").manual_seed(0)
