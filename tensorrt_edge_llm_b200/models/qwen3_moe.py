@@ -215,7 +215,7 @@ class MoEBlock(nn.Module):
     def forward(self, x):
         if self.shared_expert is None:
             return self._forward_routed(x)
-        if self.ep_comm is not None and self.ep_size > 1 and self.ep_comm.use_rs(x.shape[0]):
+        if self.ep_comm is not None and self.ep_size > 1 and self.ep_comm.use_ep_all_to_all(x.shape[0]):
             raise NotImplementedError("shared experts are not combined with the token-sharded expert all-to-all")
         return self._forward_routed(x) + self._shared(x)
 
@@ -230,7 +230,7 @@ class MoEBlock(nn.Module):
     def _forward_routed(self, x):
         if isinstance(x, torch.Tensor) and not x.is_cuda:
             return self._forward_reference(x)
-        if self.ep_comm is not None and self.ep_size > 1 and self.ep_comm.use_rs(x.shape[0]):
+        if self.ep_comm is not None and self.ep_size > 1 and self.ep_comm.use_ep_all_to_all(x.shape[0]):
             return self.ep_comm.moe_all_to_all(self, x)       # prefill: token-sharded all-to-all over peer memory
         cu = ops.cuda_ops()
         xa = x            # the router always sees 16-bit activations
