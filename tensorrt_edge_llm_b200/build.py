@@ -50,7 +50,7 @@ def build_kernels(force=False, verbose=False) -> str:
     kdir = os.path.join(CSRC, "kernels")
     os.makedirs(BUILD, exist_ok=True)
     os.makedirs(LIBDIR, exist_ok=True)
-    headers = [os.path.join(kdir, f) for f in os.listdir(kdir) if f.endswith((".h", ".cuh"))]
+    headers = [os.path.join(kdir, f) for f in os.listdir(kdir) if f.endswith((".h", ".cuh", ".inc"))]
     srcs = sorted(f for f in os.listdir(kdir) if f.endswith(".cu"))
     objs, jobs = [], []
     for f in srcs:

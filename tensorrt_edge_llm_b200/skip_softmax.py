@@ -10,7 +10,7 @@ Checkpoint / flag resolution follows the reference (``tensorrt_edgellm/skip_soft
 ``skip_softmax_prefill_*`` and ``skip_softmax_decode_*`` (text config first, then the checkpoint root); for each phase the first
 of these wins: an explicit table flag (``[]`` = dense), a target-sparsity flag with a matching tier in ``*_scale_tables``, the
 checkpoint's own tier / ``*_scale_table``, a target through the checkpoint's ``*_calibration`` fit ``round(a * exp(b * R))``,
-dense.  The prefill tile kernel (``csrc/kernels/attention_tc5.cu``) implements the vote; decode steps run dense here.
+dense.  The prefill tile kernel (``csrc/kernels/attention_tc5_extra.cu``) implements the vote; decode steps run dense here.
 """
 from __future__ import annotations
 
