@@ -230,6 +230,13 @@ class ModelConfig:
     eagle3_num_target_layers: int = 3
     eagle3_target_layer_ids: List[int] = field(default_factory=list)   # tapped target layers (default: low / mid / high)
     eagle3_norm_before_residual: bool = False
+    # EAGLE-4 additions to the EAGLE-3 draft: one RMSNorm per tapped target layer in front of ``fc``, the final-norm output fed
+    # back as the next step's feature, and a low-rank candidate head (``rank``-wide scores pick ``count`` tokens of the full
+    # vocabulary, which are then scored exactly with their ``lm_head`` rows)
+    eagle_fc_norm: bool = False
+    eagle_norm_output: bool = False
+    draft_candidate_rank: int = 0
+    draft_candidate_count: int = 0
     draft_vocab_size: int = 0
     # DFlash block draft (draft_type "dflash"): tapped target layers, proposal block length, id of the mask token, and whether
     # row i's hidden state predicts position i + 1 (shifted labels) instead of its own position
@@ -241,6 +248,14 @@ class ModelConfig:
     # Domino: a DFlash draft whose proposals after the first are corrected one by one by a small recurrent head over a shared
     # candidate pool (dflash_projector_type "domino")
     dflash_projector_type: str = ""
+    # DFlash 2 (dflash_version 2): a dynamic grouped convolution around every sublayer of the block draft and a chain selector
+    # (per-slot top-k candidates rescored against the token chosen for the slot before through two [V, rank] codebooks)
+    dflash_version: int = 1
+    dflash2_conv_kernel_size: int = 2
+    dflash2_conv_group_size: int = 16
+    dflash2_selector_rank: int = 256
+    dflash2_selector_top_k: int = 16
+    dflash2_output_multiplier: float = 1.0
     domino_pool_size: int = 2048
     domino_proj_dim: int = 256
     domino_gru_hidden_dim: int = 256
@@ -274,6 +289,10 @@ class ModelConfig:
     def compute_dtype(self) -> torch.dtype:
         return {"bfloat16": torch.bfloat16, "float16": torch.float16,
                 "float32": torch.float32}[self.dtype]
+
+    @property
+    def is_eagle4_draft(self) -> bool:
+        return self.draft_type == "eagle3" and (self.eagle_fc_norm or self.eagle_norm_output or self.draft_candidate_count > 0)
 
     @property
     def is_hybrid(self) -> bool:
@@ -418,7 +437,8 @@ class ModelConfig:
             draft_type="dflash" if (llm.get("dflash_config") or llm.get("jetspec_config")
                                     or any(k in str(hf.get("architectures", "")).lower() for k in ("dflash", "jetspec", "domino"))) else (
                 "eagle3" if (llm.get("draft_vocab_size") or "eagle" in str(hf.get("architectures", "")).lower()
-                             or hf.get("speculators_model_type") == "eagle3") else None),
+                             or hf.get("speculators_model_type") == "eagle3"
+                             or (any(llm.get(k) for k in _EAGLE4_KEYS) and (hf.get("eagle_config") or {}).get("use_aux_hidden_state"))) else None),
             dflash_target_layer_ids=list((llm.get("dflash_config") or {}).get("target_layer_ids", []) or []),
             dflash_block_size=int((llm.get("dflash_config") or {}).get("block_size", llm.get("block_size", 16)) or 16),
             dflash_mask_token_id=int((llm.get("dflash_config") or {}).get("mask_token_id", llm.get("mask_token_id", 0)) or 0),
@@ -428,10 +448,12 @@ class ModelConfig:
             domino_pool_size=int((llm.get("dflash_config") or {}).get("pool_size", llm.get("domino_pool_size", 2048)) or 2048),
             domino_proj_dim=int((llm.get("dflash_config") or {}).get("proj_dim", llm.get("domino_proj_dim", 256)) or 256),
             domino_gru_hidden_dim=int((llm.get("dflash_config") or {}).get("gru_hidden_dim", llm.get("domino_gru_hidden_dim", 256)) or 256),
+            **_parse_dflash2(llm, hf),
             draft_vocab_size=int(llm.get("draft_vocab_size", 0) or 0),
             eagle3_target_hidden_size=int(llm.get("target_hidden_size", 0) or 0),
-            eagle3_target_layer_ids=list((hf.get("eagle_config") or {}).get("eagle_aux_hidden_state_layer_ids", []) or []),
             eagle3_norm_before_residual=bool(llm.get("norm_before_residual", False)),
+            **{"eagle3_target_layer_ids": list((hf.get("eagle_config") or {}).get("eagle_aux_hidden_state_layer_ids", []) or []),
+               **_parse_eagle4(llm, hf)},
         )
 
     @classmethod
@@ -570,6 +592,86 @@ def _parse_gemma(llm: Dict[str, Any], n_layers: int) -> Dict[str, Any]:
         out["rope_local_theta"] = float(llm.get("rope_local_base_freq", 0.0) or 0.0)
     if llm.get("attn_logit_softcapping"):
         raise ValueError("attention logit soft-capping (Gemma 2) is not supported by the attention kernels")
+    return out
+
+
+def _parse_dflash2(llm: dict, hf: dict) -> dict:
+    """DFlash 2 fields of a draft checkpoint (architecture ``DFlash2DraftModel``) with the reference's rules
+    (``tensorrt_edgellm/dflash.py:262-305``): block size 2..16, non-causal blocks, unique tapped layers, the convolution and
+    selector sizes spelled out in ``dflash_config``."""
+    archs = {str(a) for a in list(hf.get("architectures") or []) + list(llm.get("architectures") or [])}
+    if "DFlash2DraftModel" not in archs:
+        return {}
+    f = {**(hf.get("dflash_config") or {}), **(llm.get("dflash_config") or {})}
+    for name in ("conv_kernel_size", "conv_group_size", "selector_rank", "selector_top_k"):
+        if name not in f:
+            raise ValueError(f"DFlash V2 requires dflash_config.{name}")
+    causal = f.get("is_causal", llm.get("is_causal", hf.get("is_causal")))
+    if causal is None:
+        raise ValueError("DFlash V2 requires is_causal")
+    if causal:
+        raise ValueError("DFlash V2 draft checkpoint requires is_causal=false")
+    block = int(f.get("block_size", llm.get("block_size", 16)))
+    if not 2 <= block <= 16:
+        raise ValueError(f"DFlash V2 block_size must be in [2, 16], got {block}")
+    ids = list(f.get("target_layer_ids") or llm.get("target_layer_ids") or [])
+    if len(set(ids)) != len(ids):
+        raise ValueError("DFlash V2 target-layer IDs must be unique")
+    taps, group = int(f["conv_kernel_size"]), int(f["conv_group_size"])
+    if not 1 <= taps <= 4 or group < 2 or group % 2:
+        raise ValueError("DFlash V2 convolution: 1 to 4 taps and an even group size")
+    if not 1 <= int(f["selector_top_k"]) <= 32 or not 1 <= int(f["selector_rank"]) <= 1024:
+        raise ValueError("DFlash V2 selector: at most 32 candidates per slot and rank 1024")
+    mult = f.get("output_multiplier")
+    if mult is not None and not float(mult) > 0:
+        raise ValueError(f"DFlash V2 output_multiplier must be positive, got {mult}")
+    return {"dflash_version": 2, "dflash2_conv_kernel_size": taps, "dflash2_conv_group_size": group,
+            "dflash2_selector_rank": int(f["selector_rank"]), "dflash2_selector_top_k": int(f["selector_top_k"]),
+            "dflash2_output_multiplier": float(mult) if mult is not None else 1.0}
+
+
+_EAGLE4_KEYS = ("fc_norm", "norm_output", "efficient_lm_head_config")
+_MAX_CANDIDATES, _MAX_CANDIDATE_RANK = 1024, 1024
+
+
+def _parse_eagle4(llm: dict, hf: dict) -> dict:
+    """EAGLE-4 draft switches of a checkpoint config (``fc_norm``, ``norm_output``, ``efficient_lm_head_config``) with the
+    reference's consistency rules (``tensorrt_edgellm/config.py:2401-2462``): a candidate head is of type ``low_rank``, needs
+    ``norm_output``, scores the full vocabulary and excludes logit soft-capping; none of the switches combines with
+    ``norm_before_residual``."""
+    if not any(llm.get(k) for k in _EAGLE4_KEYS):
+        return {}
+    if llm.get("norm_before_residual") or llm.get("norm_before_fc"):
+        raise ValueError("EAGLE drafts with fc_norm, norm_output or a candidate head do not support norm_before_residual / norm_before_fc")
+    out = {"eagle_fc_norm": bool(llm.get("fc_norm", False)), "eagle_norm_output": bool(llm.get("norm_output", False))}
+    ids = (llm.get("eagle_aux_hidden_state_layer_ids") or (hf.get("eagle_config") or {}).get("eagle_aux_hidden_state_layer_ids")
+           or llm.get("target_layer_ids") or [])
+    n_aux = llm.get("num_aux_hidden_states")
+    if n_aux is not None and ids and int(n_aux) != len(ids):
+        raise ValueError(f"EAGLE draft num_aux_hidden_states={n_aux} does not match its {len(ids)} tapped layers")
+    if ids:
+        out["eagle3_target_layer_ids"] = [int(i) for i in ids]
+        out["eagle3_num_target_layers"] = len(ids)
+    elif n_aux:
+        out["eagle3_num_target_layers"] = int(n_aux)
+    head = llm.get("efficient_lm_head_config")
+    if head:
+        if head.get("type") != "low_rank":
+            raise ValueError(f"EAGLE candidate head type {head.get('type')!r} is not supported; expected 'low_rank'")
+        vocab = int(llm["vocab_size"])
+        count, rank = int(head.get("num_candidates", 0) or 0), int(head.get("rank", 0) or 0)
+        if not 0 < count <= min(vocab, _MAX_CANDIDATES):
+            raise ValueError(f"EAGLE candidate head num_candidates={count} must be in [1, {min(vocab, _MAX_CANDIDATES)}]")
+        if not 0 < rank <= _MAX_CANDIDATE_RANK or rank % 8:
+            raise ValueError(f"EAGLE candidate head rank={rank} must be a multiple of 8 in [8, {_MAX_CANDIDATE_RANK}]")
+        if not out["eagle_norm_output"]:
+            raise ValueError("an EAGLE candidate head requires norm_output=true")
+        if llm.get("final_logit_softcapping") is not None:
+            raise ValueError("an EAGLE candidate head does not support final_logit_softcapping")
+        dv = llm.get("draft_vocab_size")
+        if dv is not None and int(dv) != vocab:
+            raise ValueError(f"an EAGLE candidate head scores the full vocabulary; draft_vocab_size={dv} must equal vocab_size={vocab}")
+        out["draft_candidate_rank"], out["draft_candidate_count"] = rank, count
     return out
 
 

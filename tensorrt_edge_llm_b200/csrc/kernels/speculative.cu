@@ -13,7 +13,17 @@
 //                        order (so parents still precede children), renumber their parents and prepend the
 //                        root: tokens, parents and depths of the verification tree.
 //
-// Reference counterparts: cpp/kernels/speculative/speculativeKernels.cu (acceptGreedy, the tree construction
+//   dflash2_conv         one side of DFlash 2's per-token dynamic grouped depthwise convolution along a proposal block
+//                        (fixed per-channel taps plus per-token, per-group offsets; causal, never across a block edge).
+//   dflash2_selector     DFlash 2's chain selector: one CTA per sequence walks the proposal slots, scoring each slot's
+//                        candidates against the token chosen for the slot before (bilinear codebook term), greedy or sampled.
+//   candidate_rescore    second half of the EAGLE-4 low-rank candidate head: exact fp32 logits of each row's candidate
+//                        tokens from their lm_head rows, candidates ordered by (logit descending, id ascending) and
+//                        log-softmax over the set.  The first half (two small GEMMs and a top-k) runs as library ops.
+//
+// Reference counterparts: cpp/plugins/lowRankCandidateHeadPlugin (candidate head),
+// cpp/kernels/speculative/dflash2GroupedDynamicConv.cu, dflash2CandidateSelector.cu (chain walk),
+// cpp/kernels/speculative/speculativeKernels.cu (acceptGreedy, the tree construction
 // kernels at :509 and :571, commitSpecTargetKVBatchedKernel :1692), forceAcceptanceKernels.cu.
 #include "host_utils.h"
 #include "tc5_common.cuh"
@@ -194,6 +204,190 @@ eagle_select_verify_kernel(const float* __restrict__ p_sc, const int* __restrict
     }
 }
 
+
+// out[t, c] = sum_{k < K, k <= t % block} (base[k, c] + delta[t, k, c / group]) * hidden[t - k, c]  (+ residual[t, c]).
+// One thread per channel pair (group sizes are even, so a pair shares its group); grid (channel pairs / 256, tokens).
+template <typename T, int K>
+__global__ void __launch_bounds__(256) dflash2_conv_kernel(const T* __restrict__ hidden, const T* __restrict__ delta,
+                                                           const T* __restrict__ base, const T* __restrict__ residual,
+                                                           T* __restrict__ out, int H, int block, int group_size) {
+    pdl_prologue();
+    const int t = blockIdx.y;
+    const int pc = blockIdx.x * 256 + threadIdx.x;
+    if (pc * 2 >= H) return;
+    const int c = pc * 2, groups = H / group_size, g = c / group_size, pos = t % block;
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+        if (pos >= k) {
+            const float dyn = Cvt<T>::to_f(delta[((size_t)t * K + k) * groups + g]);
+            const T* b = base + (size_t)k * H + c;
+            const T* x = hidden + (size_t)(t - k) * H + c;
+            s0 = fmaf(Cvt<T>::to_f(b[0]) + dyn, Cvt<T>::to_f(x[0]), s0);
+            s1 = fmaf(Cvt<T>::to_f(b[1]) + dyn, Cvt<T>::to_f(x[1]), s1);
+        }
+    }
+    if (residual != nullptr) {
+        s0 += Cvt<T>::to_f(residual[(size_t)t * H + c]);
+        s1 += Cvt<T>::to_f(residual[(size_t)t * H + c + 1]);
+    }
+    *reinterpret_cast<uint32_t*>(out + (size_t)t * H + c) = Cvt<T>::pack2(s0, s1);
+}
+
+constexpr int kSelMaxTopK = 32;
+constexpr int kSelMaxRank = 1024;
+
+// One CTA of topk warps per sequence; the slots are walked in order because slot s depends on the token chosen for s - 1.
+template <typename T>
+__global__ void __launch_bounds__(1024) dflash2_selector_kernel(const int* __restrict__ cand, const float* __restrict__ unary,
+                                                               const T* __restrict__ projected, const int* __restrict__ anchor,
+                                                               const T* __restrict__ pred_cb, const T* __restrict__ succ_cb,
+                                                               const float* __restrict__ temperatures, const float* __restrict__ uniforms,
+                                                               int* __restrict__ tokens, float* __restrict__ probs, int steps, int topk,
+                                                               int rank, int vocab) {
+    pdl_prologue();
+    __shared__ float s_query[kSelMaxRank];
+    __shared__ float s_score[kSelMaxTopK];
+    __shared__ float s_prob[kSelMaxTopK];
+    __shared__ int s_prev;
+    const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) s_prev = anchor[b];
+    __syncthreads();
+    const bool greedy = temperatures == nullptr || temperatures[b] < 1e-3f;
+    for (int step = 0; step < steps; ++step) {
+        const size_t row = (size_t)b * steps + step;
+        const int prev = s_prev;
+        const bool prev_ok = prev >= 0 && prev < vocab;
+        for (int r = threadIdx.x; r < rank; r += blockDim.x)
+            s_query[r] = prev_ok ? Cvt<T>::to_f(pred_cb[(size_t)prev * rank + r]) * Cvt<T>::to_f(projected[row * rank + r]) : 0.f;
+        __syncthreads();
+        if (warp < topk) {
+            const int c = cand[row * topk + warp];
+            float dot = 0.f;
+            if (c >= 0 && c < vocab) {
+                const T* q = succ_cb + (size_t)c * rank;
+                for (int r = lane; r < rank; r += 32) dot = fmaf(s_query[r], Cvt<T>::to_f(q[r]), dot);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            if (lane == 0) s_score[warp] = unary[row * topk + warp] + dot;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int sel = 0;
+            if (greedy) {
+                float best = -INFINITY;
+                int best_tok = 0x7fffffff;
+                for (int k = 0; k < topk; ++k) {
+                    const int tok = cand[row * topk + k];
+                    if (s_score[k] > best || (s_score[k] == best && tok < best_tok)) {
+                        best = s_score[k];
+                        best_tok = tok;
+                        sel = k;
+                    }
+                }
+                for (int k = 0; k < topk; ++k) s_prob[k] = k == sel ? 1.f : 0.f;
+            } else {
+                const float inv_t = 1.f / temperatures[b];
+                float mx = -INFINITY;
+                for (int k = 0; k < topk; ++k) mx = fmaxf(mx, s_score[k] * inv_t);
+                float sum = 0.f;
+                for (int k = 0; k < topk; ++k) {
+                    s_prob[k] = expf(s_score[k] * inv_t - mx);
+                    sum += s_prob[k];
+                }
+                const float u = fminf(fmaxf(uniforms[row], 0.f), 0.99999994f);
+                float cum = 0.f;
+                sel = topk - 1;
+                bool found = false;
+                for (int k = 0; k < topk; ++k) {
+                    s_prob[k] /= sum;
+                    cum += s_prob[k];
+                    if (!found && u < cum) {
+                        sel = k;
+                        found = true;
+                    }
+                }
+            }
+            s_prev = cand[row * topk + sel];
+            tokens[row] = s_prev;
+        }
+        __syncthreads();
+        if (threadIdx.x < topk) probs[row * topk + threadIdx.x] = s_prob[threadIdx.x];
+        __syncthreads();
+    }
+}
+
+// One CTA per row.  hidden [R, H] and lm_head [V, H] 16-bit, cand [R, kc] int32 (distinct ids per row).
+// Shared memory: H floats (the row), kc floats (logits), kc ints (ids).
+template <typename T>
+__global__ void __launch_bounds__(256) candidate_rescore_kernel(const T* __restrict__ hidden, const T* __restrict__ lm_head,
+                                                                const int* __restrict__ cand, int* __restrict__ out_ids,
+                                                                float* __restrict__ out_lp, int H, int kc, int vocab) {
+    pdl_prologue();
+    extern __shared__ float cr_smem[];
+    float* s_h = cr_smem;
+    float* s_l = s_h + H;
+    int* s_id = reinterpret_cast<int*>(s_l + kc);
+    __shared__ float s_red[8];
+    const int r = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int i = tid; i < H; i += 256) s_h[i] = Cvt<T>::to_f(hidden[(size_t)r * H + i]);
+    __syncthreads();
+    for (int c = warp; c < kc; c += 8) {
+        int id = cand[(size_t)r * kc + c];
+        id = min(max(id, 0), vocab - 1);
+        const uint4* row = reinterpret_cast<const uint4*>(lm_head + (size_t)id * H);
+        float acc = 0.f;
+        for (int i = lane; i < H / 8; i += 32) {
+            const uint4 u = __ldg(row + i);
+            const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) acc += Cvt<T>::to_f(e[q]) * s_h[i * 8 + q];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) {
+            const bool finite = (acc - acc) == 0.f;                 // false for inf and NaN
+            s_l[c] = finite ? acc : -INFINITY;
+            s_id[c] = id;
+        }
+    }
+    __syncthreads();
+    // the maximum, then the log of the sum of exponentials
+    float mx = -INFINITY;
+    for (int c = tid; c < kc; c += 256) mx = fmaxf(mx, s_l[c]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) s_red[warp] = mx;
+    __syncthreads();
+    mx = s_red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, s_red[w]);
+    __syncthreads();
+    float sum = 0.f;
+    for (int c = tid; c < kc; c += 256) sum += (s_l[c] == -INFINITY) ? 0.f : expf(s_l[c] - mx);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) s_red[warp] = sum;
+    __syncthreads();
+    sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) sum += s_red[w];
+    const float lse = sum > 0.f ? mx + logf(sum) : -INFINITY;
+    // rank of every candidate = how many candidates come before it
+    for (int c = tid; c < kc; c += 256) {
+        const float l = s_l[c];
+        const int id = s_id[c];
+        int rank = 0;
+        for (int j = 0; j < kc; ++j) {
+            const float lj = s_l[j];
+            rank += (lj > l || (lj == l && s_id[j] < id)) ? 1 : 0;
+        }
+        out_ids[(size_t)r * kc + rank] = id;
+        out_lp[(size_t)r * kc + rank] = (l == -INFINITY) ? -INFINITY : l - lse;
+    }
+}
+
 }  // namespace telb
 
 using namespace telb;
@@ -250,5 +444,62 @@ extern "C" int telb_kv_commit_path(void* pool, const int* page_table, const int*
     else
         TELB_LAUNCH("kv_commit_path_kernel", (kv_commit_path_kernel<256>), grid, blk, 0, stream, (uint4*)pool, page_table, past_len, path,
                     path_len, max_path, max_pages, num_pages, hkv, page_size);
+    return 0;
+}
+
+// hidden [rows, H], lm_head [vocab, H] (both fp16 or both bf16), cand [rows, kc] int32 with distinct ids per row →
+// out_ids [rows, kc] int32, out_lp [rows, kc] fp32.
+extern "C" int telb_candidate_rescore(const void* hidden, const void* lm_head, const int* cand, int* out_ids, float* out_lp, int rows,
+                                      int H, int kc, int vocab, int is_bf16, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (H % 8 || H > 8192) return fail("telb_candidate_rescore: hidden size must be a multiple of 8, at most 8192");
+    if (kc < 1 || kc > 1024) return fail("telb_candidate_rescore: 1..1024 candidates");
+    const int smem = (H + 2 * kc) * 4;
+    if (is_bf16) TELB_LAUNCH("candidate_rescore_kernel", (candidate_rescore_kernel<__nv_bfloat16>), dim3(rows), dim3(256), smem, stream, (const __nv_bfloat16*)hidden, (const __nv_bfloat16*)lm_head, cand, out_ids, out_lp, H, kc, vocab);
+    else TELB_LAUNCH("candidate_rescore_kernel", (candidate_rescore_kernel<__half>), dim3(rows), dim3(256), smem, stream, (const __half*)hidden, (const __half*)lm_head, cand, out_ids, out_lp, H, kc, vocab);
+    TELB_CHECK_LAUNCH("candidate_rescore_kernel");
+    return 0;
+}
+
+// hidden [tokens, H] holds whole blocks of `block` rows; delta [tokens, K, H / group_size]; base [K, H]; residual [tokens, H] or
+// null; out [tokens, H].  One 16-bit type throughout; 1 to 4 taps.
+extern "C" int telb_dflash2_conv(const void* hidden, const void* delta, const void* base, const void* residual, void* out, int tokens,
+                                 int H, int block, int taps, int group_size, int is_bf16, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (taps < 1 || taps > 4) return fail("telb_dflash2_conv: 1 to 4 taps");
+    if (block < 1 || tokens % block) return fail("telb_dflash2_conv: rows must be whole blocks");
+    if (group_size < 2 || (group_size & 1) || H % group_size) return fail("telb_dflash2_conv: an even group size that divides the hidden size");
+    const dim3 grid((H / 2 + 255) / 256, tokens), blk(256);
+#define TELB_CONV(TT, KK)                                                                                                           \
+    TELB_LAUNCH("dflash2_conv_kernel", (dflash2_conv_kernel<TT, KK>), grid, blk, 0, stream, (const TT*)hidden, (const TT*)delta,    \
+                (const TT*)base, (const TT*)residual, (TT*)out, H, block, group_size)
+#define TELB_CONV_T(TT)                      \
+    do {                                     \
+        if (taps == 1) TELB_CONV(TT, 1);     \
+        else if (taps == 2) TELB_CONV(TT, 2); \
+        else if (taps == 3) TELB_CONV(TT, 3); \
+        else TELB_CONV(TT, 4);               \
+    } while (0)
+    if (is_bf16) TELB_CONV_T(__nv_bfloat16);
+    else TELB_CONV_T(__half);
+#undef TELB_CONV_T
+#undef TELB_CONV
+    TELB_CHECK_LAUNCH("dflash2_conv_kernel");
+    return 0;
+}
+
+// cand / unary [batch, steps, topk], projected [batch, steps, rank], anchor [batch], codebooks [vocab, rank]; temperatures [batch]
+// and uniforms [batch, steps] may be null (greedy) → tokens [batch, steps] int32, probs [batch, steps, topk] fp32.
+extern "C" int telb_dflash2_selector(const int* cand, const float* unary, const void* projected, const int* anchor, const void* pred_cb,
+                                     const void* succ_cb, const float* temperatures, const float* uniforms, int* tokens, float* probs,
+                                     int batch, int steps, int topk, int rank, int vocab, int is_bf16, cudaStream_t stream) {
+    if (batch <= 0 || steps <= 0) return 0;
+    if (topk < 1 || topk > kSelMaxTopK) return fail("telb_dflash2_selector: 1..32 candidates per slot");
+    if (rank < 1 || rank > kSelMaxRank) return fail("telb_dflash2_selector: selector rank 1..1024");
+    if (temperatures != nullptr && uniforms == nullptr) return fail("telb_dflash2_selector: sampled rows need uniforms");
+    const dim3 grid(batch), blk(32 * topk);
+    if (is_bf16) TELB_LAUNCH("dflash2_selector_kernel", (dflash2_selector_kernel<__nv_bfloat16>), grid, blk, 0, stream, cand, unary, (const __nv_bfloat16*)projected, anchor, (const __nv_bfloat16*)pred_cb, (const __nv_bfloat16*)succ_cb, temperatures, uniforms, tokens, probs, steps, topk, rank, vocab);
+    else TELB_LAUNCH("dflash2_selector_kernel", (dflash2_selector_kernel<__half>), grid, blk, 0, stream, cand, unary, (const __half*)projected, anchor, (const __half*)pred_cb, (const __half*)succ_cb, temperatures, uniforms, tokens, probs, steps, topk, rank, vocab);
+    TELB_CHECK_LAUNCH("dflash2_selector_kernel");
     return 0;
 }

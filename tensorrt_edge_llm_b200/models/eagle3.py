@@ -106,6 +106,11 @@ class Eagle3Draft(nn.Module):
         if d.numel() and int(d[0]) == 0 and not torch.equal(d, torch.arange(d.numel(), device=d.device)):
             self.d2t.copy_((d + torch.arange(d.numel(), device=d.device)).to(torch.int32))
 
+    def pick(self, lp: torch.Tensor, k: int):
+        """The ``k`` best proposals of each row of the head's output: ``(log-probabilities [..., k], target token ids [..., k])``."""
+        sc, idx = lp.topk(min(k, lp.shape[-1]), dim=-1)
+        return sc, self.d2t.long()[idx]
+
     def cos_sin(self, device) -> torch.Tensor:
         if self._cos_sin is None or self._cos_sin.device != torch.device(device):
             self._cos_sin = ops.ref.rope_cos_sin(self.cfg.max_position_embeddings, self.cfg.rotary_dim, self.cfg.rope_theta,

@@ -196,6 +196,36 @@ def eagle_select_verify(p_sc, p_tok, p_par, p_dep, root, keep):
     return ref.eagle_select_verify(p_sc, p_tok, p_par, p_dep, root, keep)
 
 
+def dflash2_grouped_dynamic_conv(hidden, delta, base, residual, block, group_size):
+    """``out[t, c] = Σ_k (base[k, c] + delta[t, k, c // group_size]) · hidden[t - k, c]`` over the taps that stay inside row ``t``'s
+    proposal block, plus ``residual`` when given."""
+    if hidden.is_cuda and hidden.dtype in (torch.float16, torch.bfloat16) and group_size % 2 == 0 and base.shape[0] <= 4:
+        return cuda_ops().dflash2_grouped_dynamic_conv(hidden, delta, base, residual, block, group_size)
+    return ref.dflash2_grouped_dynamic_conv(hidden, delta, base, residual, block, group_size)
+
+
+def dflash2_selector_walk(cand_ids, unary, projected, anchor, pred_codebook, succ_codebook, temperatures=None, uniforms=None):
+    """Chain selector of DFlash 2: per slot, the candidate with the best ``unary + <P[prev] ⊙ z, Q[candidate]>`` (or a draw from
+    the softmax of those scores) becomes the slot's token and the next slot's predecessor."""
+    if (cand_ids.is_cuda and projected.dtype in (torch.float16, torch.bfloat16) and pred_codebook.dtype == projected.dtype
+            and succ_codebook.dtype == projected.dtype and cand_ids.shape[-1] <= 32 and projected.shape[-1] <= 1024):
+        return cuda_ops().dflash2_selector_walk(cand_ids, unary, projected, anchor, pred_codebook, succ_codebook, temperatures, uniforms)
+    return ref.dflash2_selector_walk(cand_ids, unary, projected, anchor, pred_codebook, succ_codebook, temperatures, uniforms)
+
+
+def low_rank_candidate_head(hidden, down_proj, up_proj, lm_head, num_candidates):
+    """EAGLE-4 candidate head: ``(ids [R, Kc] int32, log-probabilities [R, Kc] fp32)`` of the ``Kc`` tokens the low-rank
+    scores pick, ordered by their exact logits.  On the GPU the two low-rank products and the top-k are library ops and the
+    exact rescoring, ordering and log-softmax are one kernel."""
+    if hidden.is_cuda and hidden.dtype in (torch.float16, torch.bfloat16) and lm_head.dtype == hidden.dtype:
+        proj = (hidden @ down_proj.to(hidden.dtype).t())                  # fp32 accumulation, rounded to the 16-bit type
+        scores = (proj @ up_proj.to(hidden.dtype).t()).float()
+        scores = torch.nan_to_num(scores, nan=float("-inf"))
+        cand = scores.topk(num_candidates, dim=-1).indices
+        return cuda_ops().candidate_rescore(hidden, lm_head, cand)
+    return ref.low_rank_candidate_head(hidden, down_proj, up_proj, lm_head, num_candidates)
+
+
 def kv_commit_path(pool, page_table, past_len, path, path_len):
     if pool.is_cuda:
         return cuda_ops().kv_commit_path(pool, page_table, past_len, path, path_len)

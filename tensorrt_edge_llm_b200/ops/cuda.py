@@ -914,6 +914,47 @@ def eagle_select_verify(p_sc, p_tok, p_par, p_dep, root, keep: int):
     return tok, par, dep
 
 
+def dflash2_grouped_dynamic_conv(hidden, delta, base, residual, block: int, group_size: int):
+    """One side of DFlash 2's dynamic grouped convolution over whole proposal blocks (16-bit in, 16-bit out)."""
+    assert hidden.dtype in (torch.float16, torch.bfloat16)
+    h, d, b = hidden.contiguous(), delta.to(hidden.dtype).contiguous(), base.to(hidden.dtype).contiguous()
+    r = None if residual is None else residual.to(hidden.dtype).contiguous()
+    out = torch.empty_like(h)
+    _check(lib().telb_dflash2_conv(_p(h), _p(d), _p(b), _p(r), _p(out), c_int(h.shape[0]), c_int(h.shape[1]), c_int(block),
+                                   c_int(b.shape[0]), c_int(group_size), c_int(int(h.dtype == torch.bfloat16)), _stream()), "dflash2_conv")
+    return out
+
+
+def dflash2_selector_walk(cand_ids, unary, projected, anchor, pred_codebook, succ_codebook, temperatures=None, uniforms=None):
+    """DFlash 2's chain selector: ``(tokens [B, S] int64, probabilities [B, S, K] fp32)``."""
+    assert projected.dtype in (torch.float16, torch.bfloat16) and pred_codebook.dtype == projected.dtype == succ_codebook.dtype
+    b, s, k = cand_ids.shape
+    dev = cand_ids.device
+    c, u, z = cand_ids.to(torch.int32).contiguous(), unary.float().contiguous(), projected.contiguous()
+    a, pc, qc = anchor.to(device=dev, dtype=torch.int32).contiguous(), pred_codebook.contiguous(), succ_codebook.contiguous()
+    t = None if temperatures is None else temperatures.to(device=dev, dtype=torch.float32).contiguous()
+    un = None if uniforms is None else uniforms.to(device=dev, dtype=torch.float32).contiguous()
+    tok = torch.empty(b, s, dtype=torch.int32, device=dev)
+    pr = torch.empty(b, s, k, dtype=torch.float32, device=dev)
+    _check(lib().telb_dflash2_selector(_p(c), _p(u), _p(z), _p(a), _p(pc), _p(qc), _p(t), _p(un), _p(tok), _p(pr), c_int(b), c_int(s), c_int(k),
+                                       c_int(z.shape[-1]), c_int(pc.shape[0]), c_int(int(z.dtype == torch.bfloat16)), _stream()),
+           "dflash2_selector")
+    return tok.long(), pr
+
+
+def candidate_rescore(hidden, lm_head, cand):
+    """Exact logits of each row's candidate tokens, ordered (logit descending, id ascending), with the log-softmax over the set:
+    ``(ids [R, Kc] int32, log-probabilities [R, Kc] fp32)``."""
+    assert hidden.dtype == lm_head.dtype and hidden.dtype in (torch.float16, torch.bfloat16)
+    h, w, c = hidden.contiguous(), lm_head.contiguous(), cand.to(torch.int32).contiguous()
+    rows, kc = c.shape
+    ids = torch.empty(rows, kc, dtype=torch.int32, device=h.device)
+    lp = torch.empty(rows, kc, dtype=torch.float32, device=h.device)
+    _check(lib().telb_candidate_rescore(_p(h), _p(w), _p(c), _p(ids), _p(lp), c_int(rows), c_int(h.shape[1]), c_int(kc),
+                                        c_int(w.shape[0]), c_int(int(h.dtype == torch.bfloat16)), _stream()), "candidate_rescore")
+    return ids, lp
+
+
 def kv_commit_path(pool, page_table, past_len, path, path_len) -> None:
     assert pool.is_contiguous() and pool.element_size() in (1, 2)
     if pool.element_size() == 1:            # FP8 pages: a row of D bytes moves as D / 2 16-bit elements

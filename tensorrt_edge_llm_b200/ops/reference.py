@@ -737,6 +737,106 @@ def eagle_tree_meta(parents: torch.Tensor, base_pos: torch.Tensor, depth_base: i
     return eagle_pack_mask(anc), depth, pos
 
 
+def dflash2_grouped_dynamic_conv(hidden: torch.Tensor, delta: torch.Tensor, base: torch.Tensor, residual: Optional[torch.Tensor],
+                                 block: int, group_size: int) -> torch.Tensor:
+    """One side of DFlash 2's per-token dynamic grouped depthwise convolution along a proposal block.
+
+    ``hidden [T, H]`` holds whole blocks of ``block`` rows; row ``t`` sits at position ``t % block``.  With ``K`` taps,
+    ``out[t, c] = Σ_{k < K, k <= pos(t)} (base[k, c] + delta[t, k, c // group_size]) · hidden[t - k, c]``: a causal filter that never
+    reads across a block boundary, whose taps are a fixed per-channel kernel plus a per-token, per-group offset
+    (``delta [T, K, H / group_size]``).  With ``residual`` the sum is added to it.  fp32 arithmetic, result in ``hidden``'s type.
+    (``cpp/kernels/speculative/dflash2GroupedDynamicConv.cu:80-125``.)"""
+    t, h = hidden.shape
+    k = base.shape[0]
+    x = hidden.float().view(t // block, block, h)
+    d = delta.float().view(t // block, block, k, h // group_size).repeat_interleave(group_size, dim=-1)      # [N, B, K, H]
+    w = base.float()[None, None] + d
+    out = torch.zeros_like(x)
+    for tap in range(min(k, block)):
+        out[:, tap:] += w[:, tap:, tap] * x[:, :block - tap]
+    out = out.view(t, h)
+    if residual is not None:
+        out = out + residual.float()
+    return out.to(hidden.dtype)
+
+
+def dflash2_selector_walk(cand_ids: torch.Tensor, unary: torch.Tensor, projected: torch.Tensor, anchor: torch.Tensor,
+                          pred_codebook: torch.Tensor, succ_codebook: torch.Tensor, temperatures: Optional[torch.Tensor] = None,
+                          uniforms: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """DFlash 2's chain selector: walk the proposal slots left to right, scoring slot ``s``'s candidates given the token chosen
+    for slot ``s - 1`` (the anchor — the last accepted token — for slot 0):
+
+        score[c] = unary[s, c] + Σ_r P[prev, r] · z[s, r] · Q[cand[s, c], r]
+
+    Greedy rows (no temperature, or one below 1e-3) take the best score (ties → the smaller token id); sampled rows draw from
+    ``softmax(score / temperature)`` with ``uniforms[b, s]``.  An id outside the vocabulary contributes no bilinear term.
+    Returns ``(tokens [B, S] int64, probabilities [B, S, K] fp32)`` — one-hot on greedy rows.
+    (``cpp/kernels/speculative/dflash2CandidateSelector.cu:69-176``.)"""
+    b, s, k = cand_ids.shape
+    vocab = pred_codebook.shape[0]
+    cand = cand_ids.long()
+    prev = anchor.long().clone()
+    tokens = torch.empty(b, s, dtype=torch.int64, device=cand.device)
+    probs = torch.zeros(b, s, k, dtype=torch.float32, device=cand.device)
+    pf, qf, z = pred_codebook.float(), succ_codebook.float(), projected.float()
+    greedy = torch.ones(b, dtype=torch.bool, device=cand.device) if temperatures is None else temperatures.float() < 1e-3
+    for step in range(s):
+        ok_prev = (prev >= 0) & (prev < vocab)
+        query = pf[prev.clamp(0, vocab - 1)] * z[:, step] * ok_prev[:, None]                        # [B, R]
+        c = cand[:, step]
+        ok_c = (c >= 0) & (c < vocab)
+        dot = torch.einsum("bkr,br->bk", qf[c.clamp(0, vocab - 1)], query) * ok_c
+        score = unary[:, step].float() + dot
+        # greedy: best score, the smaller token id among equals
+        best = score.amax(dim=-1, keepdim=True)
+        tie_ids = torch.where(score == best, c, torch.full_like(c, torch.iinfo(torch.int64).max))
+        sel = tie_ids.argmin(dim=-1)
+        p = torch.nn.functional.one_hot(sel, k).float()
+        if not bool(greedy.all()):
+            t = temperatures.float().clamp_min(1e-3)
+            ps = torch.softmax(score / t[:, None], dim=-1)
+            u = uniforms[:, step].float().clamp(0.0, 0.99999994)
+            ssel = (ps.cumsum(-1) > u[:, None]).float().argmax(dim=-1)
+            ssel = torch.where((ps.cumsum(-1) > u[:, None]).any(-1), ssel, torch.full_like(ssel, k - 1))
+            sel = torch.where(greedy, sel, ssel)
+            p = torch.where(greedy[:, None], p, ps)
+        prev = c.gather(1, sel[:, None])[:, 0]
+        tokens[:, step] = prev
+        probs[:, step] = p
+    return tokens, probs
+
+
+def candidate_rescore(hidden: torch.Tensor, lm_head: torch.Tensor, cand: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Exact scores of a candidate set: ``logit[r, c] = lm_head[cand[r, c]] · hidden[r]`` in fp32, candidates reordered by
+    (logit descending, token id ascending; a non-finite logit counts as -inf), log-softmax over the set.  Returns
+    ``(ids [R, Kc] int32, log-probabilities [R, Kc] fp32)``."""
+    cand = cand.long()
+    logits = torch.einsum("rkh,rh->rk", lm_head[cand].float(), hidden.float())
+    finite = torch.isfinite(logits)
+    ranked = torch.where(finite, logits, torch.full_like(logits, float("-inf")))
+    by_id = cand.argsort(dim=-1, stable=True)                              # ascending ids first, then a stable sort by value
+    ranked, cand, finite = ranked.gather(-1, by_id), cand.gather(-1, by_id), finite.gather(-1, by_id)
+    order = ranked.sort(dim=-1, descending=True, stable=True).indices
+    ranked, cand, finite = ranked.gather(-1, order), cand.gather(-1, order), finite.gather(-1, order)
+    lse = torch.logsumexp(ranked, dim=-1, keepdim=True)
+    lp = torch.where(finite, ranked - lse, torch.full_like(ranked, float("-inf")))
+    return cand.to(torch.int32), lp
+
+
+def low_rank_candidate_head(hidden: torch.Tensor, down_proj: torch.Tensor, up_proj: torch.Tensor, lm_head: torch.Tensor,
+                            num_candidates: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Candidate head of EAGLE-4 drafts (``tensorrt_edgellm/models/ops.py:636-679``): the ``num_candidates`` tokens with the
+    largest low-rank scores ``A (B h)`` (``B = down_proj [r, H]``, ``A = up_proj [V, r]``; ``B h`` accumulates in fp32 and is
+    rounded to the weights' 16-bit type, the scores are fp32; ties go to the smaller id, NaN ranks last), then
+    :func:`candidate_rescore` with the exact ``lm_head`` rows."""
+    h32 = hidden.float()
+    proj = (h32 @ down_proj.float().t()).to(down_proj.dtype if down_proj.dtype != torch.float32 else torch.float16)
+    scores = proj.float() @ up_proj.float().t()
+    scores = torch.where(torch.isnan(scores), torch.full_like(scores, float("-inf")), scores)
+    cand = scores.sort(dim=-1, descending=True, stable=True).indices[:, :num_candidates]
+    return candidate_rescore(hidden, lm_head, cand)
+
+
 def eagle_select_verify(p_sc, p_tok, p_par, p_dep, root, keep: int):
     b, npool = p_sc.shape
     dev = p_sc.device

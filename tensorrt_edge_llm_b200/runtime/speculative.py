@@ -73,6 +73,12 @@ def default_tap_layers(num_layers: int) -> List[int]:
     return ids
 
 
+def _dense_pick(draft, lp, k):
+    """Proposals of a draft without a ``pick`` of its own: top-k of a dense log-probability row, mapped through ``d2t``."""
+    sc, idx = lp.topk(min(k, lp.shape[-1]), dim=-1)
+    return sc, draft.d2t.long()[idx]
+
+
 class _VerifyGraph:
     """One captured tree-verification pass of the target for a fixed (batch, tree size): token ids, positions, ancestor
     mask, cache lengths and page-table rows live in static device buffers that are refilled before every replay (the first
@@ -260,15 +266,15 @@ class EagleDecoder:
         b, k, steps, n = len(seats), self.spec.top_k, self.spec.draft_steps, self.spec.verify_tokens
         timer = prof.timer()
         stage = timer.begin(prof.SPEC_DRAFT, batch=b)
-        d2t = self.draft.d2t.long()
-        lp0 = torch.stack([self.lp[s] for s in seats])                       # [B, Vd]
+        pick = getattr(self.draft, "pick", None) or (lambda lp_, k_: _dense_pick(self.draft, lp_, k_))
+        lp0 = torch.stack([self.lp[s] for s in seats])                       # [B, Vd] (candidate heads: [B, 2, Kc])
         h0 = torch.stack([self.hid[s] for s in seats])                       # [B, H]
-        k1 = min(k, lp0.shape[-1])
-        sc, idx = lp0.topk(k1, dim=-1)
+        sc, tok0 = pick(lp0, k)
+        k1 = sc.shape[-1]
         # candidate pool (depth-ordered): token, parent pool index (-1 = root), depth, cumulative score
-        p_tok, p_par, p_dep, p_sc = [d2t[idx]], [torch.full((b, k1), -1, device=dev)], [torch.ones(b, k1, dtype=torch.long, device=dev)], [sc]
+        p_tok, p_par, p_dep, p_sc = [tok0], [torch.full((b, k1), -1, device=dev)], [torch.ones(b, k1, dtype=torch.long, device=dev)], [sc]
         # draft rows fed so far: token, feature, parent row (-1 = none), depth, pool index
-        r_tok, r_feat, r_par, r_dep = d2t[idx], h0[:, None, :].expand(b, k1, h0.shape[-1]), torch.full((b, k1), -1, device=dev), torch.ones(b, k1, dtype=torch.long, device=dev)
+        r_tok, r_feat, r_par, r_dep = tok0, h0[:, None, :].expand(b, k1, h0.shape[-1]), torch.full((b, k1), -1, device=dev), torch.ones(b, k1, dtype=torch.long, device=dev)
         r_pool, r_sc = torch.arange(k1, device=dev).expand(b, k1), sc
         front0, kf = 0, k1                                                    # first row / width of the current frontier
         pool_base = k1
@@ -280,11 +286,9 @@ class EagleDecoder:
             want = [i * rows + front0 + j for i in range(b) for j in range(kf)]
             lp, h = self._draft_step(seats, self._embed(r_tok.reshape(-1)), r_feat.reshape(b * rows, -1).contiguous(), [rows] * b, want,
                                      tree_mask=mask, positions=pos)
-            lp = lp.view(b, kf, -1)
-            kc = min(k, lp.shape[-1])
-            csc, cidx = lp.topk(kc, dim=-1)                                   # [B, kf, kc]
+            csc, ctok = pick(lp.reshape(b, kf, *lp.shape[1:]), k)             # [B, kf, kc]
+            kc = csc.shape[-1]
             cum = r_sc[:, front0:front0 + kf, None] + csc
-            ctok = d2t[cidx]
             cpar = r_pool[:, front0:front0 + kf, None].expand(b, kf, kc)
             p_tok.append(ctok.reshape(b, -1)); p_par.append(cpar.reshape(b, -1)); p_sc.append(cum.reshape(b, -1))
             p_dep.append(torch.full((b, kf * kc), depth, dtype=torch.long, device=dev))

@@ -149,3 +149,86 @@ def test_eagle_decoder_on_gpu(cu):
             # bf16 kernels of different shapes may flip near-ties: accept the emitted token when it is
             # the arg-max or within a small margin of it
             assert t == int(top2.indices[j, 0]) or float(top2.values[j, 0] - logits[len(p) - 1 + j, t]) < 0.05
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,hid,vocab,kc", [(1, 64, 300, 5), (7, 1024, 4000, 64), (33, 4096, 20000, 200)])
+def test_candidate_rescore_kernel(cu, dtype, rows, hid, vocab, kc):
+    """Exact rescoring of an EAGLE-4 candidate set against the fp32 restatement: same ids in the same order (up to swaps of
+    logits that differ by rounding only), log-probabilities within 2e-3, and a tie / non-finite case bit for bit."""
+    g = torch.Generator().manual_seed(rows * kc)
+    h = (torch.randn(rows, hid, generator=g) / hid ** 0.5).to(dtype)
+    head = torch.randn(vocab, hid, generator=g).to(dtype)
+    cand = torch.stack([torch.randperm(vocab, generator=g)[:kc] for _ in range(rows)]).to(torch.int32)
+    want_ids, want_lp = ref.candidate_rescore(h, head, cand)
+    got_ids, got_lp = cu.candidate_rescore(h.cuda(), head.cuda(), cand.cuda())
+    got_ids, got_lp = got_ids.cpu(), got_lp.cpu()
+    assert torch.all(got_lp[:, :-1] >= got_lp[:, 1:])
+    for r in range(rows):
+        assert sorted(got_ids[r].tolist()) == sorted(want_ids[r].tolist())
+        by_id = {int(i): float(v) for i, v in zip(want_ids[r], want_lp[r])}
+        assert max(abs(by_id[int(i)] - float(v)) for i, v in zip(got_ids[r], got_lp[r])) < 2e-3
+    assert (got_ids == want_ids).float().mean() > 0.98
+    # ties go to the smaller id; a non-finite logit ranks last with log-probability -inf
+    h1 = torch.ones(1, 8, dtype=dtype)
+    hd = torch.zeros(6, 8, dtype=dtype)
+    hd[1] = 0.5; hd[4] = 0.5; hd[2] = 1.0; hd[3, 0] = float("inf")
+    c1 = torch.tensor([[4, 3, 2, 1, 0]], dtype=torch.int32)
+    ids, lp = cu.candidate_rescore(h1.cuda(), hd.cuda(), c1.cuda())
+    wi, wl = ref.candidate_rescore(h1, hd, c1)
+    assert ids.cpu().tolist() == wi.tolist() == [[2, 1, 4, 0, 3]]
+    assert lp[0, 4].item() == float("-inf") and torch.allclose(lp.cpu()[0, :4], wl[0, :4], atol=1e-5)
+
+
+def test_low_rank_candidate_head_on_gpu(cu):
+    from tensorrt_edge_llm_b200 import ops
+    g = torch.Generator().manual_seed(5)
+    rows, hid, rank, vocab, kc = 9, 512, 64, 8000, 32
+    h = (torch.randn(rows, hid, generator=g) / hid ** 0.5).half()
+    down, up, head = (torch.randn(*s, generator=g).half() for s in ((rank, hid), (vocab, rank), (vocab, hid)))
+    want_ids, want_lp = ref.low_rank_candidate_head(h, down, up, head, kc)
+    ids, lp = ops.low_rank_candidate_head(h.cuda(), down.cuda(), up.cuda(), head.cuda(), kc)
+    overlap = sum(len(set(a.tolist()) & set(b.tolist())) for a, b in zip(ids.cpu(), want_ids)) / (rows * kc)
+    assert overlap > 0.97                                   # the low-rank scores differ by 16-bit rounding at the cut only
+    same_top = ids.cpu()[:, 0] == want_ids[:, 0]
+    assert same_top.float().mean() >= 0.75 and torch.allclose(lp.cpu()[same_top, 0], want_lp[same_top, 0], atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("taps,block,group,hid", [(2, 16, 16, 2048), (3, 5, 8, 256), (1, 2, 2, 64), (4, 8, 32, 1024)])
+def test_dflash2_conv_kernel(cu, dtype, taps, block, group, hid):
+    g = torch.Generator().manual_seed(taps * hid)
+    n = 5
+    x = torch.randn(n * block, hid, generator=g).to(dtype)
+    delta = (torch.randn(n * block, taps, hid // group, generator=g) * 0.5).to(dtype)
+    base = torch.randn(taps, hid, generator=g).to(dtype)
+    res = torch.randn(n * block, hid, generator=g).to(dtype)
+    for r in (None, res):
+        want = ref.dflash2_grouped_dynamic_conv(x.float(), delta.float(), base.float(), None if r is None else r.float(), block, group)
+        got = cu.dflash2_grouped_dynamic_conv(x.cuda(), delta.cuda(), base.cuda(), None if r is None else r.cuda(), block, group)
+        assert got.dtype == dtype
+        tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
+        assert torch.allclose(got.float().cpu(), want, atol=tol * 4, rtol=tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("b,s,k,r", [(1, 15, 16, 256), (6, 7, 5, 64), (3, 1, 32, 1024)])
+def test_dflash2_selector_kernel(cu, dtype, b, s, k, r):
+    g = torch.Generator().manual_seed(b * s * k)
+    vocab = 500
+    cand = torch.stack([torch.stack([torch.randperm(vocab, generator=g)[:k] for _ in range(s)]) for _ in range(b)])
+    cand[0, 0, k - 1] = vocab + 3                                           # out-of-vocabulary candidate
+    unary = torch.randn(b, s, k, generator=g) * 2
+    z = torch.randn(b, s, r, generator=g).to(dtype)
+    pcb, qcb = (torch.randn(vocab, r, generator=g) * (2.0 / r ** 0.5)).to(dtype), torch.randn(vocab, r, generator=g).to(dtype)
+    anchor = torch.randint(0, vocab, (b,), generator=g)
+    want_tok, want_p = ref.dflash2_selector_walk(cand, unary, z, anchor, pcb, qcb)
+    tok, p = cu.dflash2_selector_walk(cand.cuda(), unary.cuda(), z.cuda(), anchor.cuda(), pcb.cuda(), qcb.cuda())
+    assert torch.equal(tok.cpu(), want_tok) and torch.equal(p.cpu(), want_p)
+    temps = torch.linspace(0.0, 1.5, b)
+    uni = torch.rand(b, s, generator=g)
+    want_tok, want_p = ref.dflash2_selector_walk(cand, unary, z, anchor, pcb, qcb, temps, uni)
+    tok, p = cu.dflash2_selector_walk(cand.cuda(), unary.cuda(), z.cuda(), anchor.cuda(), pcb.cuda(), qcb.cuda(), temps.cuda(), uni.cuda())
+    # a draw that lands within rounding of a bin edge may differ; everything downstream of it then differs too
+    same = (tok.cpu() == want_tok).all(dim=1)
+    assert same.float().mean() >= 0.6 and torch.allclose(p.cpu()[same], want_p[same], atol=2e-4)
