@@ -256,6 +256,16 @@ class ModelConfig:
     dflash2_selector_rank: int = 256
     dflash2_selector_top_k: int = 16
     dflash2_output_multiplier: float = 1.0
+    # LiLiCorr (dflash_projector_type "lilicorr"): a small bidirectional transformer over the lattice of per-slot top-k
+    # candidates that scores transitions between the candidates of consecutive slots
+    lilicorr_candidate_topk: int = 0
+    lilicorr_hidden_size: int = 0
+    lilicorr_num_layers: int = 0
+    lilicorr_num_heads: int = 0
+    lilicorr_mlp_ratio: float = 0.0
+    lilicorr_factor_dim: int = 0
+    lilicorr_vector_eps: float = 0.0
+    lilicorr_logit_scale: float = 0.0
     domino_pool_size: int = 2048
     domino_proj_dim: int = 256
     domino_gru_hidden_dim: int = 256
@@ -444,11 +454,11 @@ class ModelConfig:
             dflash_mask_token_id=int((llm.get("dflash_config") or {}).get("mask_token_id", llm.get("mask_token_id", 0)) or 0),
             dflash_shift_label=bool((llm.get("dflash_config") or {}).get("shift_label", llm.get("dflash_shift_label", False))),
             dflash_query_causal=bool((llm.get("dflash_config") or llm.get("jetspec_config") or {}).get("query_causal", llm.get("dflash_query_causal", False))),
-            dflash_projector_type=str((llm.get("dflash_config") or {}).get("projector_type", llm.get("dflash_projector_type", "")) or ""),
             domino_pool_size=int((llm.get("dflash_config") or {}).get("pool_size", llm.get("domino_pool_size", 2048)) or 2048),
             domino_proj_dim=int((llm.get("dflash_config") or {}).get("proj_dim", llm.get("domino_proj_dim", 256)) or 256),
             domino_gru_hidden_dim=int((llm.get("dflash_config") or {}).get("gru_hidden_dim", llm.get("domino_gru_hidden_dim", 256)) or 256),
-            **_parse_dflash2(llm, hf),
+            **{"dflash_projector_type": str((llm.get("dflash_config") or {}).get("projector_type", llm.get("dflash_projector_type", "")) or ""),
+               **_parse_dflash2(llm, hf)},
             draft_vocab_size=int(llm.get("draft_vocab_size", 0) or 0),
             eagle3_target_hidden_size=int(llm.get("target_hidden_size", 0) or 0),
             eagle3_norm_before_residual=bool(llm.get("norm_before_residual", False)),
@@ -595,15 +605,39 @@ def _parse_gemma(llm: Dict[str, Any], n_layers: int) -> Dict[str, Any]:
     return out
 
 
+_LILICORR_FIELDS = ("lilicorr_candidate_topk", "lilicorr_hidden_size", "lilicorr_num_layers", "lilicorr_num_heads", "lilicorr_mlp_ratio",
+                    "lilicorr_factor_dim", "lilicorr_vector_eps", "lilicorr_logit_scale")
+
+
 def _parse_dflash2(llm: dict, hf: dict) -> dict:
     """DFlash 2 fields of a draft checkpoint (architecture ``DFlash2DraftModel``) with the reference's rules
     (``tensorrt_edgellm/dflash.py:262-305``): block size 2..16, non-causal blocks, unique tapped layers, the convolution and
     selector sizes spelled out in ``dflash_config``."""
     archs = {str(a) for a in list(hf.get("architectures") or []) + list(llm.get("architectures") or [])}
-    if "DFlash2DraftModel" not in archs:
-        return {}
     f = {**(hf.get("dflash_config") or {}), **(llm.get("dflash_config") or {})}
-    for name in ("conv_kernel_size", "conv_group_size", "selector_rank", "selector_top_k"):
+    projector = str(f.get("projector_type", "") or "") or ("lilicorr" if "LiLiCorrDraftModel" in archs else "")
+    lilicorr = projector == "lilicorr"
+    if "DFlash2DraftModel" not in archs and not lilicorr:
+        return {}
+    extra = {}
+    if lilicorr:
+        if not f.get("lilicorr_enabled", False):
+            raise ValueError("LiLiCorr requires dflash_config.lilicorr_enabled=true")
+        missing = [n for n in _LILICORR_FIELDS if n not in f]
+        if missing:
+            raise ValueError(f"LiLiCorr requires dflash_config.{', '.join(missing)}")
+        extra = {n: (float(f[n]) if n in ("lilicorr_mlp_ratio", "lilicorr_vector_eps", "lilicorr_logit_scale") else int(f[n]))
+                 for n in _LILICORR_FIELDS}
+        k = extra["lilicorr_candidate_topk"]
+        if k <= 0 or k > 16 or k & (k - 1):
+            raise ValueError(f"LiLiCorr lilicorr_candidate_topk must be a power of two <= 16, got {k}")
+        for n, v in extra.items():
+            if not v > 0:
+                raise ValueError(f"LiLiCorr {n} must be positive, got {v}")
+        if not (f.get("target_layer_ids") or llm.get("target_layer_ids")):
+            raise ValueError("LiLiCorr requires at least one target-layer ID")
+        extra["dflash_projector_type"] = "lilicorr"
+    for name in ("conv_kernel_size", "conv_group_size") + (() if lilicorr else ("selector_rank", "selector_top_k")):
         if name not in f:
             raise ValueError(f"DFlash V2 requires dflash_config.{name}")
     causal = f.get("is_causal", llm.get("is_causal", hf.get("is_causal")))
@@ -620,14 +654,14 @@ def _parse_dflash2(llm: dict, hf: dict) -> dict:
     taps, group = int(f["conv_kernel_size"]), int(f["conv_group_size"])
     if not 1 <= taps <= 4 or group < 2 or group % 2:
         raise ValueError("DFlash V2 convolution: 1 to 4 taps and an even group size")
-    if not 1 <= int(f["selector_top_k"]) <= 32 or not 1 <= int(f["selector_rank"]) <= 1024:
+    if not lilicorr and (not 1 <= int(f["selector_top_k"]) <= 32 or not 1 <= int(f["selector_rank"]) <= 1024):
         raise ValueError("DFlash V2 selector: at most 32 candidates per slot and rank 1024")
     mult = f.get("output_multiplier")
     if mult is not None and not float(mult) > 0:
         raise ValueError(f"DFlash V2 output_multiplier must be positive, got {mult}")
     return {"dflash_version": 2, "dflash2_conv_kernel_size": taps, "dflash2_conv_group_size": group,
-            "dflash2_selector_rank": int(f["selector_rank"]), "dflash2_selector_top_k": int(f["selector_top_k"]),
-            "dflash2_output_multiplier": float(mult) if mult is not None else 1.0}
+            "dflash2_selector_rank": int(f.get("selector_rank", 0) or 0), "dflash2_selector_top_k": int(f.get("selector_top_k", 0) or 0),
+            "dflash2_output_multiplier": float(mult) if mult is not None else 1.0, **extra}
 
 
 _EAGLE4_KEYS = ("fc_norm", "norm_output", "efficient_lm_head_config")

@@ -17,12 +17,13 @@
 //                        (fixed per-channel taps plus per-token, per-group offsets; causal, never across a block edge).
 //   dflash2_selector     DFlash 2's chain selector: one CTA per sequence walks the proposal slots, scoring each slot's
 //                        candidates against the token chosen for the slot before (bilinear codebook term), greedy or sampled.
+//   lattice_chain_walk   LiLiCorr's walk over per-slot candidates with a [prev, next] transition table per slot.
 //   candidate_rescore    second half of the EAGLE-4 low-rank candidate head: exact fp32 logits of each row's candidate
 //                        tokens from their lm_head rows, candidates ordered by (logit descending, id ascending) and
 //                        log-softmax over the set.  The first half (two small GEMMs and a top-k) runs as library ops.
 //
 // Reference counterparts: cpp/plugins/lowRankCandidateHeadPlugin (candidate head),
-// cpp/kernels/speculative/dflash2GroupedDynamicConv.cu, dflash2CandidateSelector.cu (chain walk),
+// cpp/kernels/speculative/dflash2GroupedDynamicConv.cu, dflash2CandidateSelector.cu (chain walk), lilicorrChainWalk.cu,
 // cpp/kernels/speculative/speculativeKernels.cu (acceptGreedy, the tree construction
 // kernels at :509 and :571, commitSpecTargetKVBatchedKernel :1692), forceAcceptanceKernels.cu.
 #include "host_utils.h"
@@ -318,6 +319,49 @@ __global__ void __launch_bounds__(1024) dflash2_selector_kernel(const int* __res
     }
 }
 
+// One warp per sequence; lane k owns candidate k (topk <= 32).  transition [B, S, K, K] fp32.
+__global__ void __launch_bounds__(32) lattice_chain_walk_kernel(const int* __restrict__ cand, const float* __restrict__ transition,
+                                                                const float* __restrict__ temperatures, const float* __restrict__ uniforms,
+                                                                int* __restrict__ tokens, float* __restrict__ probs, int steps, int topk) {
+    pdl_prologue();
+    const int b = blockIdx.x, lane = threadIdx.x;
+    const bool greedy = temperatures == nullptr || temperatures[b] < 1e-3f;
+    const float inv_t = greedy ? 1.f : 1.f / temperatures[b];
+    int prev = 0;
+    for (int step = 0; step < steps; ++step) {
+        const size_t row = (size_t)b * steps + step;
+        const float sc = lane < topk ? transition[(row * topk + prev) * topk + lane] * inv_t : -INFINITY;
+        float mx = sc;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        int sel;
+        float p;
+        if (greedy) {
+            const unsigned best = __ballot_sync(0xffffffffu, lane < topk && sc == mx);
+            sel = best ? __ffs(best) - 1 : 0;                       // lowest index among the maxima (0 if every score is NaN)
+            p = lane == sel ? 1.f : 0.f;
+        } else {
+            const float e = lane < topk ? expf(sc - mx) : 0.f;
+            float sum = e;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            p = e / sum;
+            float cum = p;                                          // inclusive prefix sum over lanes
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float v = __shfl_up_sync(0xffffffffu, cum, o);
+                if (lane >= o) cum += v;
+            }
+            const float u = fminf(fmaxf(uniforms[row], 0.f), 0.99999994f);
+            const unsigned hit = __ballot_sync(0xffffffffu, lane < topk && u < cum);
+            sel = hit ? __ffs(hit) - 1 : topk - 1;
+        }
+        if (lane < topk) probs[row * topk + lane] = p;
+        if (lane == 0) tokens[row] = cand[row * topk + sel];
+        prev = sel;
+    }
+}
+
 // One CTA per row.  hidden [R, H] and lm_head [V, H] 16-bit, cand [R, kc] int32 (distinct ids per row).
 // Shared memory: H floats (the row), kc floats (logits), kc ints (ids).
 template <typename T>
@@ -501,5 +545,18 @@ extern "C" int telb_dflash2_selector(const int* cand, const float* unary, const 
     if (is_bf16) TELB_LAUNCH("dflash2_selector_kernel", (dflash2_selector_kernel<__nv_bfloat16>), grid, blk, 0, stream, cand, unary, (const __nv_bfloat16*)projected, anchor, (const __nv_bfloat16*)pred_cb, (const __nv_bfloat16*)succ_cb, temperatures, uniforms, tokens, probs, steps, topk, rank, vocab);
     else TELB_LAUNCH("dflash2_selector_kernel", (dflash2_selector_kernel<__half>), grid, blk, 0, stream, cand, unary, (const __half*)projected, anchor, (const __half*)pred_cb, (const __half*)succ_cb, temperatures, uniforms, tokens, probs, steps, topk, rank, vocab);
     TELB_CHECK_LAUNCH("dflash2_selector_kernel");
+    return 0;
+}
+
+// cand [batch, steps, topk] int32, transition [batch, steps, topk, topk] fp32; temperatures [batch] and uniforms [batch, steps] may be
+// null (greedy) → tokens [batch, steps] int32, probs [batch, steps, topk] fp32.
+extern "C" int telb_lattice_chain_walk(const int* cand, const float* transition, const float* temperatures, const float* uniforms,
+                                       int* tokens, float* probs, int batch, int steps, int topk, cudaStream_t stream) {
+    if (batch <= 0 || steps <= 0) return 0;
+    if (topk < 1 || topk > 32) return fail("telb_lattice_chain_walk: 1..32 candidates per slot");
+    if (temperatures != nullptr && uniforms == nullptr) return fail("telb_lattice_chain_walk: sampled rows need uniforms");
+    TELB_LAUNCH("lattice_chain_walk_kernel", lattice_chain_walk_kernel, dim3(batch), dim3(32), 0, stream, cand, transition, temperatures,
+                uniforms, tokens, probs, steps, topk);
+    TELB_CHECK_LAUNCH("lattice_chain_walk_kernel");
     return 0;
 }

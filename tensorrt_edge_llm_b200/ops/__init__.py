@@ -213,6 +213,13 @@ def dflash2_selector_walk(cand_ids, unary, projected, anchor, pred_codebook, suc
     return ref.dflash2_selector_walk(cand_ids, unary, projected, anchor, pred_codebook, succ_codebook, temperatures, uniforms)
 
 
+def lattice_chain_walk(cand_ids, transition, temperatures=None, uniforms=None):
+    """LiLiCorr's walk: per slot, the candidate with the best ``transition[slot, previous index, ·]`` (or a draw from its softmax)."""
+    if cand_ids.is_cuda and cand_ids.shape[-1] <= 32:
+        return cuda_ops().lattice_chain_walk(cand_ids, transition, temperatures, uniforms)
+    return ref.lattice_chain_walk(cand_ids, transition, temperatures, uniforms)
+
+
 def low_rank_candidate_head(hidden, down_proj, up_proj, lm_head, num_candidates):
     """EAGLE-4 candidate head: ``(ids [R, Kc] int32, log-probabilities [R, Kc] fp32)`` of the ``Kc`` tokens the low-rank
     scores pick, ordered by their exact logits.  On the GPU the two low-rank products and the top-k are library ops and the

@@ -942,6 +942,20 @@ def dflash2_selector_walk(cand_ids, unary, projected, anchor, pred_codebook, suc
     return tok.long(), pr
 
 
+def lattice_chain_walk(cand_ids, transition, temperatures=None, uniforms=None):
+    """Walk of a candidate lattice with per-slot ``[prev, next]`` transition scores: ``(tokens [B, S] int64, probabilities)``."""
+    b, s, k = cand_ids.shape
+    dev = cand_ids.device
+    c, tr = cand_ids.to(torch.int32).contiguous(), transition.float().contiguous()
+    t = None if temperatures is None else temperatures.to(device=dev, dtype=torch.float32).contiguous()
+    un = None if uniforms is None else uniforms.to(device=dev, dtype=torch.float32).contiguous()
+    tok = torch.empty(b, s, dtype=torch.int32, device=dev)
+    pr = torch.empty(b, s, k, dtype=torch.float32, device=dev)
+    _check(lib().telb_lattice_chain_walk(_p(c), _p(tr), _p(t), _p(un), _p(tok), _p(pr), c_int(b), c_int(s), c_int(k), _stream()),
+           "lattice_chain_walk")
+    return tok.long(), pr
+
+
 def candidate_rescore(hidden, lm_head, cand):
     """Exact logits of each row's candidate tokens, ordered (logit descending, id ascending), with the log-softmax over the set:
     ``(ids [R, Kc] int32, log-probabilities [R, Kc] fp32)``."""

@@ -806,6 +806,35 @@ def dflash2_selector_walk(cand_ids: torch.Tensor, unary: torch.Tensor, projected
     return tokens, probs
 
 
+def lattice_chain_walk(cand_ids: torch.Tensor, transition: torch.Tensor, temperatures: Optional[torch.Tensor] = None,
+                       uniforms: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Walk a candidate lattice slot by slot: ``transition[b, s, prev, next]`` scores candidate ``next`` of slot ``s`` given the
+    index chosen at slot ``s - 1`` (index 0 before the first slot).  Greedy rows take the best score (ties → the lowest index)
+    with a one-hot distribution; sampled rows draw from ``softmax(row / temperature)`` by inverse CDF on ``uniforms[b, s]``.
+    Returns ``(tokens [B, S] int64, probabilities [B, S, K] fp32)``.  (``cpp/kernels/speculative/lilicorrChainWalk.h``.)"""
+    b, s, k = cand_ids.shape
+    dev = cand_ids.device
+    prev = torch.zeros(b, dtype=torch.int64, device=dev)
+    tokens = torch.empty(b, s, dtype=torch.int64, device=dev)
+    probs = torch.zeros(b, s, k, dtype=torch.float32, device=dev)
+    greedy = torch.ones(b, dtype=torch.bool, device=dev) if temperatures is None else temperatures.float() < 1e-3
+    rows = torch.arange(b, device=dev)
+    for step in range(s):
+        row = transition[rows, step, prev].float()                                  # [B, K]
+        sel = row.argmax(dim=-1)                                                     # first maximum = lowest index
+        p = torch.nn.functional.one_hot(sel, k).float()
+        if not bool(greedy.all()):
+            ps = torch.softmax(row / temperatures.float().clamp_min(1e-3)[:, None], dim=-1)
+            hit = ps.cumsum(-1) > uniforms[:, step].float().clamp(0.0, 0.99999994)[:, None]
+            ssel = torch.where(hit.any(-1), hit.float().argmax(dim=-1), torch.full_like(sel, k - 1))
+            sel = torch.where(greedy, sel, ssel)
+            p = torch.where(greedy[:, None], p, ps)
+        tokens[:, step] = cand_ids[rows, step, sel]
+        probs[:, step] = p
+        prev = sel
+    return tokens, probs
+
+
 def candidate_rescore(hidden: torch.Tensor, lm_head: torch.Tensor, cand: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """Exact scores of a candidate set: ``logit[r, c] = lm_head[cand[r, c]] · hidden[r]`` in fp32, candidates reordered by
     (logit descending, token id ascending; a non-finite logit counts as -inf), log-softmax over the set.  Returns

@@ -212,3 +212,5 @@ class DFlashDecoder:
             self.r.kv.free(s)
             self.dkv.free(s)
             self.root.pop(s, None)
+            if hasattr(self.draft, "forget"):            # per-seat draft state (LiLiCorr's anchor row)
+                self.draft.forget(s)

@@ -232,3 +232,21 @@ def test_dflash2_selector_kernel(cu, dtype, b, s, k, r):
     # a draw that lands within rounding of a bin edge may differ; everything downstream of it then differs too
     same = (tok.cpu() == want_tok).all(dim=1)
     assert same.float().mean() >= 0.6 and torch.allclose(p.cpu()[same], want_p[same], atol=2e-4)
+
+
+@pytest.mark.parametrize("b,s,k", [(1, 15, 16), (9, 7, 4), (4, 3, 32), (2, 1, 1)])
+def test_lattice_chain_walk_kernel(cu, b, s, k):
+    g = torch.Generator().manual_seed(b * 100 + k)
+    cand = torch.randint(0, 50000, (b, s, k), generator=g)
+    tr = torch.randn(b, s, k, k, generator=g) * 3
+    if k > 3 and s > 2:
+        tr[0, 2, :, 1] = tr[0, 2, :, 3] = 50.0
+    want_tok, want_p = ref.lattice_chain_walk(cand, tr)
+    tok, p = cu.lattice_chain_walk(cand.cuda(), tr.cuda())
+    assert torch.equal(tok.cpu(), want_tok) and torch.equal(p.cpu(), want_p)
+    temps = torch.linspace(0.0, 1.6, b)
+    uni = torch.rand(b, s, generator=g)
+    want_tok, want_p = ref.lattice_chain_walk(cand, tr, temps, uni)
+    tok, p = cu.lattice_chain_walk(cand.cuda(), tr.cuda(), temps.cuda(), uni.cuda())
+    same = (tok.cpu() == want_tok).all(dim=1)
+    assert same.float().mean() >= 0.6 and torch.allclose(p.cpu()[same], want_p[same], atol=2e-5)
