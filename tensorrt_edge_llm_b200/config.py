@@ -256,6 +256,12 @@ class ModelConfig:
     dflash2_selector_rank: int = 256
     dflash2_selector_top_k: int = 16
     dflash2_output_multiplier: float = 1.0
+    # DSpark (dflash_projector_type "dspark"): the block draft plus a rank-R bigram ("Markov") correction of its logits and an
+    # optional confidence head that schedules the proposal length
+    dspark_markov_rank: int = 0
+    dspark_markov_head_type: str = ""
+    dspark_enable_confidence_head: bool = False
+    dspark_confidence_head_with_markov: bool = False
     # LiLiCorr (dflash_projector_type "lilicorr"): a small bidirectional transformer over the lattice of per-slot top-k
     # candidates that scores transitions between the candidates of consecutive slots
     lilicorr_candidate_topk: int = 0
@@ -367,7 +373,7 @@ class ModelConfig:
         if isinstance(d.get("diffusion"), dict):
             d["diffusion"] = DiffusionConfig(**d["diffusion"])
         known = {f.name for f in dataclasses.fields(cls)}
-        return cls(**{k: v for k, v in d.items() if k in known})
+        cfg = cls(**{k: v for k, v in d.items() if k in known})
 
     # -- HF parsing ------------------------------------------------------------------------
     @classmethod
@@ -405,7 +411,7 @@ class ModelConfig:
         family_extra = bool(extra)            # family-specific fields parsed above (they decide the sliding-window rule below)
         extra.setdefault("skip_softmax_prefill_table", skip.prefill_table)
         extra.setdefault("skip_softmax_decode_table", skip.decode_table)
-        return cls(
+        cfg = cls(
             model_type=model_type,
             vocab_size=int(llm["vocab_size"]),
             hidden_size=hidden,
@@ -465,6 +471,9 @@ class ModelConfig:
             **{"eagle3_target_layer_ids": list((hf.get("eagle_config") or {}).get("eagle_aux_hidden_state_layer_ids", []) or []),
                **_parse_eagle4(llm, hf)},
         )
+        for key, value in _parse_dspark(llm, hf).items():
+            setattr(cfg, key, value)
+        return cfg
 
     @classmethod
     def from_pretrained(cls, model_dir: str, mapping: Optional[Mapping] = None) -> "ModelConfig":
@@ -603,6 +612,35 @@ def _parse_gemma(llm: Dict[str, Any], n_layers: int) -> Dict[str, Any]:
     if llm.get("attn_logit_softcapping"):
         raise ValueError("attention logit soft-capping (Gemma 2) is not supported by the attention kernels")
     return out
+
+
+def _parse_dspark(llm: dict, hf: dict) -> dict:
+    """DSpark draft fields (``dspark_config``, a top-level ``markov_head_type`` or an architecture named ``…DSparkModel``;
+    ``tensorrt_edgellm/config.py:1880-1905``): the block geometry may sit at the top level instead of in ``dflash_config``, labels
+    are shifted by default, the Markov head is of type ``vanilla`` with a positive rank."""
+    archs = [str(a) for a in list(hf.get("architectures") or []) + list(llm.get("architectures") or [])]
+    d = hf.get("dspark_config") or llm.get("dspark_config") or {}
+    if not (d or llm.get("markov_head_type") or any(a.endswith("DSparkModel") for a in archs)):
+        return {}
+    f = hf.get("dflash_config") or llm.get("dflash_config") or {}
+    look = lambda key, default: d.get(key, f.get(key, llm.get(key, hf.get(key, default))))
+    head = str(look("markov_head_type", "") or "vanilla")
+    if head != "vanilla":
+        raise ValueError(f"DSpark supports markov_head_type 'vanilla' only, got {head!r}")
+    rank = int(look("markov_rank", 0) or 0)
+    if rank <= 0:
+        raise ValueError("DSpark requires a positive markov_rank")
+    block = int(look("block_size", 7))
+    if block < 2:
+        raise ValueError(f"DSpark block_size must be at least 2, got {block}")
+    return {"draft_type": "dflash", "dflash_projector_type": "dspark", "dflash_block_size": block,
+            "dflash_mask_token_id": int(look("mask_token_id", 0) or 0),
+            "dflash_target_layer_ids": [int(i) for i in (look("target_layer_ids", []) or [])],
+            "dflash_shift_label": bool(look("shift_label", True)),
+            "dflash_query_causal": bool(d.get("causal", llm.get("dflash_query_causal", f.get("causal", False)))),
+            "dspark_markov_rank": rank, "dspark_markov_head_type": head,
+            "dspark_enable_confidence_head": bool(look("enable_confidence_head", False)),
+            "dspark_confidence_head_with_markov": bool(look("confidence_head_with_markov", False))}
 
 
 _LILICORR_FIELDS = ("lilicorr_candidate_topk", "lilicorr_hidden_size", "lilicorr_num_layers", "lilicorr_num_heads", "lilicorr_mlp_ratio",

@@ -17,13 +17,15 @@
 //                        (fixed per-channel taps plus per-token, per-group offsets; causal, never across a block edge).
 //   dflash2_selector     DFlash 2's chain selector: one CTA per sequence walks the proposal slots, scoring each slot's
 //                        candidates against the token chosen for the slot before (bilinear codebook term), greedy or sampled.
+//   markov_greedy_step   DSpark's Markov head, one proposal step for the whole batch: logits + W2 · W1[prev] and its arg-max in
+//                        one pass over W2 (the winner is an atomic max of packed (value, id) keys, read by the next step).
 //   lattice_chain_walk   LiLiCorr's walk over per-slot candidates with a [prev, next] transition table per slot.
 //   candidate_rescore    second half of the EAGLE-4 low-rank candidate head: exact fp32 logits of each row's candidate
 //                        tokens from their lm_head rows, candidates ordered by (logit descending, id ascending) and
 //                        log-softmax over the set.  The first half (two small GEMMs and a top-k) runs as library ops.
 //
 // Reference counterparts: cpp/plugins/lowRankCandidateHeadPlugin (candidate head),
-// cpp/kernels/speculative/dflash2GroupedDynamicConv.cu, dflash2CandidateSelector.cu (chain walk), lilicorrChainWalk.cu,
+// cpp/kernels/speculative/dflash2GroupedDynamicConv.cu, dflash2CandidateSelector.cu (chain walk), lilicorrChainWalk.cu, dsparkKernels.cu (fused greedy Markov step),
 // cpp/kernels/speculative/speculativeKernels.cu (acceptGreedy, the tree construction
 // kernels at :509 and :571, commitSpecTargetKVBatchedKernel :1692), forceAcceptanceKernels.cu.
 #include "host_utils.h"
@@ -319,6 +321,71 @@ __global__ void __launch_bounds__(1024) dflash2_selector_kernel(const int* __res
     }
 }
 
+__device__ __forceinline__ unsigned long long pack_greedy_key(float v, int idx) {
+    if (!(v == v)) v = -INFINITY;                       // NaN never wins
+    if (v == 0.f) v = 0.f;                              // -0 and +0 are one value
+    uint32_t bits = __float_as_uint(v);
+    bits = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+    return (static_cast<unsigned long long>(bits) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(idx));   // ties: the lowest id
+}
+
+constexpr int kMarkovMaxRank = 512;
+constexpr int kMarkovWarps = 8;
+
+// One proposal step of the Markov head for every sequence.  logits [B, P, V] fp32; w1 [V1, R], w2 [V, R] 16-bit; slots [B, P] u64,
+// zeroed before step 0.  A CTA owns `rows_per_cta` vocabulary rows: it reads each W2 row once and scores it for all B sequences.
+// Dynamic shared memory: B * R floats (the queries W1[prev_b]) then B u64 (the CTA's best key per sequence).
+template <typename T>
+__global__ void __launch_bounds__(kMarkovWarps * 32) markov_greedy_step_kernel(const float* __restrict__ logits, const T* __restrict__ w1,
+                                                                               const T* __restrict__ w2, const int* __restrict__ first_prev,
+                                                                               unsigned long long* __restrict__ slots, int step, int P,
+                                                                               int V, int V1, int R, int B, int rows_per_cta) {
+    pdl_prologue();
+    extern __shared__ __align__(8) unsigned char mk_smem[];
+    float* s_q = reinterpret_cast<float*>(mk_smem);
+    unsigned long long* s_best = reinterpret_cast<unsigned long long*>(s_q + (((size_t)B * R + 1) & ~size_t(1)));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < B * R; i += blockDim.x) {
+        const int b = i / R, r = i - b * R;
+        int prev = step == 0 ? first_prev[b] : static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(slots[(size_t)b * P + step - 1] & 0xFFFFFFFFull));
+        prev = min(max(prev, 0), V1 - 1);
+        s_q[i] = Cvt<T>::to_f(w1[(size_t)prev * R + r]);
+    }
+    for (int b = threadIdx.x; b < B; b += blockDim.x) s_best[b] = 0ull;
+    __syncthreads();
+    const int row0 = blockIdx.x * rows_per_cta;
+    const int row1 = min(V, row0 + rows_per_cta);
+    constexpr int kPerLane = kMarkovMaxRank / 32;
+    for (int row = row0 + warp; row < row1; row += kMarkovWarps) {
+        float w[kPerLane];
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) {
+            const int r = lane + 32 * i;
+            w[i] = r < R ? Cvt<T>::to_f(w2[(size_t)row * R + r]) : 0.f;
+        }
+        for (int b = 0; b < B; ++b) {
+            float dot = 0.f;
+#pragma unroll
+            for (int i = 0; i < kPerLane; ++i) {
+                const int r = lane + 32 * i;
+                if (r < R) dot = fmaf(w[i], s_q[(size_t)b * R + r], dot);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            if (lane == 0) atomicMax(&s_best[b], pack_greedy_key(logits[((size_t)b * P + step) * V + row] + dot, row));
+        }
+    }
+    __syncthreads();
+    for (int b = threadIdx.x; b < B; b += blockDim.x)
+        if (s_best[b] != 0ull) atomicMax(&slots[(size_t)b * P + step], s_best[b]);
+}
+
+__global__ void markov_unpack_kernel(const unsigned long long* __restrict__ slots, int* __restrict__ tokens, int n) {
+    pdl_prologue();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) tokens[i] = static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(slots[i] & 0xFFFFFFFFull));
+}
+
 // One warp per sequence; lane k owns candidate k (topk <= 32).  transition [B, S, K, K] fp32.
 __global__ void __launch_bounds__(32) lattice_chain_walk_kernel(const int* __restrict__ cand, const float* __restrict__ transition,
                                                                 const float* __restrict__ temperatures, const float* __restrict__ uniforms,
@@ -558,5 +625,35 @@ extern "C" int telb_lattice_chain_walk(const int* cand, const float* transition,
     TELB_LAUNCH("lattice_chain_walk_kernel", lattice_chain_walk_kernel, dim3(batch), dim3(32), 0, stream, cand, transition, temperatures,
                 uniforms, tokens, probs, steps, topk);
     TELB_CHECK_LAUNCH("lattice_chain_walk_kernel");
+    return 0;
+}
+
+// The whole greedy Markov chain: `steps` launches over logits [batch, steps, vocab] (fp32), then the winners unpacked into
+// tokens [batch, steps].  slots is caller-provided scratch of batch * steps u64.  w1 [vocab1, rank], w2 [vocab, rank], 16-bit.
+extern "C" int telb_markov_greedy_chain(const float* logits, const void* w1, const void* w2, const int* first_prev,
+                                        unsigned long long* slots, int* tokens, int batch, int steps, int vocab, int vocab1, int rank,
+                                        int is_bf16, cudaStream_t stream) {
+    if (batch <= 0 || steps <= 0) return 0;
+    if (rank < 1 || rank > kMarkovMaxRank) return fail("telb_markov_greedy_chain: Markov rank 1..512");
+    const size_t smem = (((size_t)batch * rank + 1) & ~size_t(1)) * 4 + (size_t)batch * 8;
+    if (smem > 200 * 1024) return fail("telb_markov_greedy_chain: batch * rank too large for one CTA's shared memory");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(markov_greedy_step_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(markov_greedy_step_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return fail("cudaFuncSetAttribute(markov_greedy_step)", e);
+        configured = true;
+    }
+    cudaError_t e = cudaMemsetAsync(slots, 0, (size_t)batch * steps * 8, stream);
+    if (e != cudaSuccess) return fail("telb_markov_greedy_chain: memset", e);
+    const int rows_per_cta = 256;
+    const dim3 grid((vocab + rows_per_cta - 1) / rows_per_cta), blk(kMarkovWarps * 32);
+    for (int step = 0; step < steps; ++step) {
+        if (is_bf16) TELB_LAUNCH("markov_greedy_step_kernel", (markov_greedy_step_kernel<__nv_bfloat16>), grid, blk, smem, stream, logits, (const __nv_bfloat16*)w1, (const __nv_bfloat16*)w2, first_prev, slots, step, steps, vocab, vocab1, rank, batch, rows_per_cta);
+        else TELB_LAUNCH("markov_greedy_step_kernel", (markov_greedy_step_kernel<__half>), grid, blk, smem, stream, logits, (const __half*)w1, (const __half*)w2, first_prev, slots, step, steps, vocab, vocab1, rank, batch, rows_per_cta);
+        TELB_CHECK_LAUNCH("markov_greedy_step_kernel");
+    }
+    TELB_LAUNCH("markov_unpack_kernel", markov_unpack_kernel, dim3((batch * steps + 127) / 128), dim3(128), 0, stream, slots, tokens, batch * steps);
+    TELB_CHECK_LAUNCH("markov_unpack_kernel");
     return 0;
 }

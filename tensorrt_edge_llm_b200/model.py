@@ -30,7 +30,7 @@ def _ensure_builtin():
     from .models.default import CausalLM
     for t in ("llama", "qwen2", "qwen3", "mistral", "phi3", "gemma", "default"):
         _REGISTRY[t] = CausalLM
-    from .models import qwen3_moe, nemotron_h, eagle3, eagle4, mtp, gemma, diffusion_gemma, dflash, dflash2, lilicorr  # noqa: F401  (register themselves)
+    from .models import qwen3_moe, nemotron_h, eagle3, eagle4, mtp, gemma, diffusion_gemma, dflash, dflash2, lilicorr, dspark  # noqa: F401  (register themselves)
 
 
 def model_class_for(cfg: ModelConfig):
@@ -40,6 +40,8 @@ def model_class_for(cfg: ModelConfig):
     if cfg.draft_type == "dflash":
         if cfg.dflash_version == 2:
             return _REGISTRY["lilicorr" if cfg.dflash_projector_type == "lilicorr" else "dflash2"]
+        if cfg.dflash_projector_type == "dspark":
+            return _REGISTRY["dspark"]
         return _REGISTRY["domino" if cfg.dflash_projector_type == "domino" else "dflash"]
     if cfg.draft_type == "mtp":
         return _REGISTRY["mtp"]

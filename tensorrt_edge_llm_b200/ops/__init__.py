@@ -213,6 +213,15 @@ def dflash2_selector_walk(cand_ids, unary, projected, anchor, pred_codebook, suc
     return ref.dflash2_selector_walk(cand_ids, unary, projected, anchor, pred_codebook, succ_codebook, temperatures, uniforms)
 
 
+def markov_chain_propose(logits, w1, w2, first_prev, temperatures=None, uniforms=None):
+    """DSpark's Markov head: step ``i`` picks from ``logits[:, i] + W2 · W1[previous token]``.  All-greedy batches run as one
+    fused correction + arg-max kernel per step on the GPU; batches with sampled rows use library ops."""
+    if (logits.is_cuda and temperatures is None and w1.dtype in (torch.float16, torch.bfloat16) and w2.dtype == w1.dtype
+            and w1.shape[1] <= 512 and logits.shape[0] * w1.shape[1] <= 48 * 1024 and w2.shape[0] == logits.shape[-1]):
+        return cuda_ops().markov_greedy_chain(logits, w1, w2, first_prev)
+    return ref.markov_chain_propose(logits, w1, w2, first_prev, temperatures, uniforms)
+
+
 def lattice_chain_walk(cand_ids, transition, temperatures=None, uniforms=None):
     """LiLiCorr's walk: per slot, the candidate with the best ``transition[slot, previous index, ·]`` (or a draw from its softmax)."""
     if cand_ids.is_cuda and cand_ids.shape[-1] <= 32:

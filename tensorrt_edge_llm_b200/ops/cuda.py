@@ -942,6 +942,19 @@ def dflash2_selector_walk(cand_ids, unary, projected, anchor, pred_codebook, suc
     return tok.long(), pr
 
 
+def markov_greedy_chain(logits, w1, w2, first_prev):
+    """Greedy chain of DSpark's Markov head over ``logits [B, P, V]`` (fp32): ``P`` fused correction + arg-max launches."""
+    assert w1.dtype == w2.dtype and w1.dtype in (torch.float16, torch.bfloat16) and w1.shape[1] == w2.shape[1]
+    b, p, v = logits.shape
+    lg, a, c = logits.float().contiguous(), w1.contiguous(), w2.contiguous()
+    fp = first_prev.to(device=lg.device, dtype=torch.int32).contiguous()
+    slots = torch.empty(b * p, dtype=torch.int64, device=lg.device)
+    tok = torch.empty(b, p, dtype=torch.int32, device=lg.device)
+    _check(lib().telb_markov_greedy_chain(_p(lg), _p(a), _p(c), _p(fp), _p(slots), _p(tok), c_int(b), c_int(p), c_int(v), c_int(a.shape[0]),
+                                          c_int(a.shape[1]), c_int(int(a.dtype == torch.bfloat16)), _stream()), "markov_greedy_chain")
+    return tok.long()
+
+
 def lattice_chain_walk(cand_ids, transition, temperatures=None, uniforms=None):
     """Walk of a candidate lattice with per-slot ``[prev, next]`` transition scores: ``(tokens [B, S] int64, probabilities)``."""
     b, s, k = cand_ids.shape

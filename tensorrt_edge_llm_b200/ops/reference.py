@@ -806,6 +806,90 @@ def dflash2_selector_walk(cand_ids: torch.Tensor, unary: torch.Tensor, projected
     return tokens, probs
 
 
+def markov_chain_propose(logits: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, first_prev: torch.Tensor,
+                         temperatures: Optional[torch.Tensor] = None, uniforms: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """DSpark's Markov head: proposal step ``i`` picks from ``logits[:, i] + W2 · W1[prev]`` (a rank-``R`` bigram correction of
+    the backbone's logits) where ``prev`` is the token chosen at step ``i - 1`` (``first_prev`` — the last accepted token — at
+    step 0).  Greedy rows take the arg-max (ties → the lowest id); sampled rows draw from the softmax at their temperature
+    with ``uniforms[b, i]``.  ``logits [B, P, V]`` fp32, ``w1 [V, R]``, ``w2 [V, R]`` → tokens ``[B, P]`` int64.
+    (``cpp/kernels/speculative/dsparkKernels.cu:746-790`` and the fused greedy step after it.)"""
+    b, p, v = logits.shape
+    prev = first_prev.long().clamp(0, w1.shape[0] - 1)
+    out = torch.empty(b, p, dtype=torch.int64, device=logits.device)
+    w1f, w2f = w1.float(), w2.float()
+    greedy = torch.ones(b, dtype=torch.bool, device=logits.device) if temperatures is None else temperatures.float() < 1e-3
+    for step in range(p):
+        corrected = logits[:, step].float() + w1f[prev] @ w2f.t()
+        tok = corrected.argmax(dim=-1)
+        if not bool(greedy.all()):
+            ps = torch.softmax(corrected / temperatures.float().clamp_min(1e-3)[:, None], dim=-1)
+            hit = ps.cumsum(-1) > uniforms[:, step].float().clamp(0.0, 0.99999994)[:, None]
+            stok = torch.where(hit.any(-1), hit.float().argmax(dim=-1), torch.full_like(tok, v - 1))
+            tok = torch.where(greedy, tok, stok)
+        out[:, step] = tok
+        prev = tok
+    return out
+
+
+def markov_confidence(hidden: torch.Tensor, w1: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, first_prev: torch.Tensor,
+                      tokens: torch.Tensor, with_markov: bool) -> torch.Tensor:
+    """Per-step acceptance confidence of a DSpark proposal: ``sigmoid(w_h · hidden[b, i] (+ w_m · W1[prev_i]) + bias)`` with
+    ``prev_0 = first_prev`` and ``prev_i = tokens[b, i - 1]``; ``weight`` is ``[H]`` or ``[H + R]``.  fp32 ``[B, P]``."""
+    h = hidden.shape[-1]
+    logit = hidden.float() @ weight.float()[:h] + bias.float().reshape(-1)[0]
+    if with_markov:
+        prev = torch.cat([first_prev.long()[:, None], tokens.long()[:, :-1]], dim=1).clamp(0, w1.shape[0] - 1)
+        logit = logit + w1.float()[prev] @ weight.float()[h:]
+    return torch.sigmoid(logit)
+
+
+_SPS_DRAFT, _SPS_VERIFY_BASE, _SPS_VERIFY_TOKEN, _SPS_ACCEPT = 0.50, 1.00, 0.45, 0.02
+
+
+def confidence_proposal_lengths(conf: torch.Tensor, mode: str, value: float, min_len: int = 1, max_len: int = 0) -> torch.Tensor:
+    """Proposal length per sequence from per-step confidences ``[B, P]`` (the survival probability of step ``i`` is the product
+    of the confidences up to ``i``).
+
+    ``"threshold"``: the longest prefix whose survival stays at or above ``value`` (``value <= 0``: the maximum length).
+    ``"sps"``: the length that maximises expected emitted tokens per unit cost, ``(1 + Σ survival) / (0.5 + 1.0 + 0.45 · (len + 1)
+    + 0.02 · len)``, stopping once survival falls below the floor ``value``.
+    Lengths are clamped to ``[min_len, max_len]`` (``max_len <= 0``: P).  (``dsparkKernels.cu:664-744``.)"""
+    b, p = conf.shape
+    lo = max(1, min(p, min_len))
+    hi = max(lo, min(p, p if max_len <= 0 else max_len))
+    out = torch.empty(b, dtype=torch.int64)
+    c = conf.float().cpu()
+    for i in range(b):
+        if mode == "threshold":
+            if value <= 0:
+                out[i] = hi
+                continue
+            surv, sel = 1.0, lo
+            for step in range(hi):
+                surv *= float(c[i, step])
+                if surv >= value:
+                    sel = step + 1
+                else:
+                    break
+        elif mode == "sps":
+            floor = min(1.0, max(0.0, value))
+            surv, expected, best, sel = 1.0, 1.0, -float("inf"), lo
+            for step in range(hi):
+                length = step + 1
+                surv *= float(c[i, step])
+                expected += surv
+                if length >= lo:
+                    score = expected / max(_SPS_DRAFT + _SPS_VERIFY_BASE + _SPS_VERIFY_TOKEN * (length + 1) + _SPS_ACCEPT * length, 1e-6)
+                    if score > best:
+                        best, sel = score, length
+                if floor > 0 and surv < floor and length >= lo:
+                    break
+        else:
+            raise ValueError(f"unknown proposal-length schedule {mode!r}")
+        out[i] = max(lo, min(hi, sel))
+    return out
+
+
 def lattice_chain_walk(cand_ids: torch.Tensor, transition: torch.Tensor, temperatures: Optional[torch.Tensor] = None,
                        uniforms: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Walk a candidate lattice slot by slot: ``transition[b, s, prev, next]`` scores candidate ``next`` of slot ``s`` given the

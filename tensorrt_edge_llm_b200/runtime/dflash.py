@@ -138,8 +138,14 @@ class DFlashDecoder:
         n, b = len(seats), self.block
         drafts = self._propose(seats)                                     # [N, B-1] host
         chain = torch.cat([torch.tensor([[self.root[s]] for s in seats], dtype=torch.int64), drafts.long()], dim=1)
-        rows = chain.reshape(-1).to(torch.int32).to(self.device)
-        logits, feats = self._target_step(seats, rows, [b] * n)           # rows written at n .. n+B-1, not committed yet
+        # a draft with a confidence head (DSpark) may shorten a sequence's proposal: the verification step is ragged then
+        plens = getattr(self.draft, "last_proposal_lengths", None) if (self.sampling is None and forced_accept is None) else None
+        q_lens = [b] * n if plens is None else [1 + max(1, min(b - 1, int(v))) for v in plens]
+        starts = [0]
+        for q in q_lens:
+            starts.append(starts[-1] + q)
+        rows = (chain.reshape(-1) if plens is None else torch.cat([chain[i, :q] for i, q in enumerate(q_lens)])).to(torch.int32).to(self.device)
+        logits, feats = self._target_step(seats, rows, q_lens)            # rows written past the committed length, not committed yet
         sampled = None
         if self.sampling is not None and forced_accept is None:
             # the chain is a tree with one child per node: draft d is kept with the target's probability of d, a rejected
@@ -150,7 +156,7 @@ class DFlashDecoder:
             sampled = ((plen - 1).tolist(), bonus.tolist())
             choice = None
         else:
-            choice = ops.argmax(logits).view(n, b).to("cpu")              # target's token after each chain row
+            choice = ops.argmax(logits).to("cpu")                         # target's token after each chain row (flat over the ragged rows)
         out: List[List[int]] = []
         keep_rows, keep_lens = [], []
         for i, s in enumerate(seats):
@@ -159,13 +165,13 @@ class DFlashDecoder:
                 a = int(sampled[0][i])
                 toks = [int(t) for t in drafts[i, :a]] + [int(sampled[1][i])]
             else:
-                limit = b - 1 if forced_accept is None else min(int(forced_accept[i]), b - 1)
-                while a < limit and (forced_accept is not None or int(drafts[i, a]) == int(choice[i, a])):
+                limit = q_lens[i] - 1 if forced_accept is None else min(int(forced_accept[i]), b - 1)
+                while a < limit and (forced_accept is not None or int(drafts[i, a]) == int(choice[starts[i] + a])):
                     a += 1
-                toks = [int(t) for t in drafts[i, :a]] + [int(choice[i, a])]
+                toks = [int(t) for t in drafts[i, :a]] + [int(choice[starts[i] + a])]
             out.append(toks)
             self.r.kv.commit(s, a + 1)                                    # y0 and the accepted drafts are real history now
-            keep_rows.append(torch.arange(i * b, i * b + a + 1))
+            keep_rows.append(torch.arange(starts[i], starts[i] + a + 1))
             keep_lens.append(a + 1)
             self.root[s] = toks[-1]
         self._write_context(seats, feats.index_select(0, torch.cat(keep_rows).to(self.device)), keep_lens)

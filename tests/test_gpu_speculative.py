@@ -250,3 +250,28 @@ def test_lattice_chain_walk_kernel(cu, b, s, k):
     tok, p = cu.lattice_chain_walk(cand.cuda(), tr.cuda(), temps.cuda(), uni.cuda())
     same = (tok.cpu() == want_tok).all(dim=1)
     assert same.float().mean() >= 0.6 and torch.allclose(p.cpu()[same], want_p[same], atol=2e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("b,p,v,r", [(1, 6, 1000, 64), (5, 3, 4099, 256), (16, 6, 32000, 128), (2, 2, 300, 48)])
+def test_markov_greedy_chain_kernel(cu, dtype, b, p, v, r):
+    """Fused Markov correction + arg-max against the fp32 restatement; a step whose winner differs only through rounding of a
+    near-tie would change everything after it, so agreement is asked of whole chains and must hold for nearly all of them."""
+    g = torch.Generator().manual_seed(v + r)
+    logits = torch.randn(b, p, v, generator=g) * 3
+    w1 = (torch.randn(v, r, generator=g) / r ** 0.25).to(dtype)
+    w2 = (torch.randn(v, r, generator=g) / r ** 0.25).to(dtype)
+    first = torch.randint(0, v, (b,), generator=g)
+    want = ref.markov_chain_propose(logits, w1, w2, first)
+    got = cu.markov_greedy_chain(logits.cuda(), w1.cuda(), w2.cuda(), first.cuda()).cpu()
+    assert got.shape == (b, p) and int(got.min()) >= 0 and int(got.max()) < v
+    same = (got == want).all(dim=1)
+    assert same.float().mean() >= 0.9
+    # the correction matters: the uncorrected arg-max differs somewhere
+    assert not torch.equal(want, logits.argmax(-1)) or b * p < 4
+    # exact ties go to the lowest id
+    lg = torch.zeros(1, 2, 64)
+    lg[0, 0, 7] = lg[0, 0, 3] = 5.0
+    z = torch.zeros(64, 32, dtype=dtype)
+    tie = cu.markov_greedy_chain(lg.cuda(), z.cuda(), z.cuda(), torch.tensor([0]).cuda()).cpu()
+    assert tie.tolist() == [[3, 0]]
