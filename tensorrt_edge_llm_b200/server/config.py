@@ -17,14 +17,14 @@ class ServerConfigError(ValueError):
 
 @dataclass
 class SpeculativeConfig:
-    method: str                                    # "eagle3" | "mtp" | "dflash" | "domino" (the draft checkpoint decides the decoder)
+    method: str                                    # draft family; the draft checkpoint's own config decides the decoder and its head
     num_speculative_tokens: Optional[int] = None   # draft depth
     draft_model: str = ""
     draft_top_k: Optional[int] = None
     verify_tokens: Optional[int] = None
 
     def __post_init__(self):
-        if self.method not in ("eagle3", "mtp", "dflash", "domino"):
+        if self.method not in ("eagle3", "eagle4", "mtp", "dflash", "dflash2", "domino", "dspark", "lilicorr", "jetspec"):
             raise ServerConfigError(f"unknown speculative method {self.method!r}")
         for name in ("num_speculative_tokens", "draft_top_k", "verify_tokens"):
             v = getattr(self, name)
