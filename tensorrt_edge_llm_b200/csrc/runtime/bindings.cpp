@@ -9,6 +9,7 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include "inference_runtime.h"
 #include "json.h"
 #include "media.h"
 #include "paged_kv.h"
@@ -33,6 +34,23 @@ class PyRuntimeSession : public RuntimeSession {
     StepResult execute(const StepPlan& plan) override { PYBIND11_OVERRIDE_PURE(StepResult, RuntimeSession, execute, plan); }
     void release(int slot) override { PYBIND11_OVERRIDE_PURE(void, RuntimeSession, release, slot); }
 };
+
+// A session factory backed by a Python callable.  The factory and the sessions it returns are Python objects: the GIL is held
+// around every use, and a returned session keeps its Python object alive for as long as native code holds the pointer.
+static SessionFactory session_factory_from_python(py::function factory) {
+    auto shared_factory = std::make_shared<py::function>(std::move(factory));
+    return [shared_factory]() {
+        py::gil_scoped_acquire gil;
+        py::object obj = (*shared_factory)();
+        auto sp = obj.cast<std::shared_ptr<RuntimeSession>>();
+        auto keep = std::make_shared<py::object>(std::move(obj));
+        return std::shared_ptr<RuntimeSession>(sp.get(), [sp, keep](RuntimeSession*) mutable {
+            py::gil_scoped_acquire g;
+            keep.reset();
+            sp.reset();
+        });
+    };
+}
 
 PYBIND11_MODULE(_telb_runtime, m) {
     m.doc() = "Native runtime of the B200 Edge-LLM framework: paged KV bookkeeping, scheduler, streaming, tokenizer";
@@ -316,21 +334,7 @@ PYBIND11_MODULE(_telb_runtime, m) {
         .def("stats", &RequestHandle::stats);
     py::class_<RequestEngine>(m, "RequestEngine")
         .def(py::init([](EngineConfig cfg, py::function factory) {
-            // The factory and the sessions it returns are Python objects: hold the GIL around every use.
-            auto shared_factory = std::make_shared<py::function>(std::move(factory));
-            SessionFactory f = [shared_factory]() {
-                py::gil_scoped_acquire gil;
-                py::object obj = (*shared_factory)();
-                auto sp = obj.cast<std::shared_ptr<RuntimeSession>>();
-                // The session is a Python object with Python overrides: keep it alive for as long as
-                // the engine holds the pointer, and drop the reference under the GIL.
-                auto keep = std::make_shared<py::object>(std::move(obj));
-                return std::shared_ptr<RuntimeSession>(sp.get(), [sp, keep](RuntimeSession*) mutable {
-                    py::gil_scoped_acquire g;
-                    keep.reset();
-                    sp.reset();
-                });
-            };
+            SessionFactory f = session_factory_from_python(std::move(factory));
             py::gil_scoped_release rel;       // the constructor opens the first session on this thread, then starts the actor
             return new RequestEngine(cfg, f);
         }))
@@ -565,5 +569,118 @@ PYBIND11_MODULE(_telb_runtime, m) {
         .def("read", [](PleReadExecutor& ex, const PleTable& t, const PleReadPlan& plan, uintptr_t staging) {
             py::gil_scoped_release rel;
             ex.read(t, plan, reinterpret_cast<uint8_t*>(staging));
+        });
+
+    // ---- the façade ----
+    py::class_<LLMGenerationRequest::Entry>(m, "GenerationEntry")
+        .def(py::init<>())
+        .def_readwrite("messages", &LLMGenerationRequest::Entry::messages)
+        .def_readwrite("prompt", &LLMGenerationRequest::Entry::prompt)
+        .def_readwrite("prompt_ids", &LLMGenerationRequest::Entry::prompt_ids);
+    py::class_<LLMGenerationRequest>(m, "LLMGenerationRequest")
+        .def(py::init<>())
+        .def_readwrite("requests", &LLMGenerationRequest::requests)
+        .def_readwrite("max_generate_length", &LLMGenerationRequest::max_generate_length)
+        .def_readwrite("temperature", &LLMGenerationRequest::temperature)
+        .def_readwrite("top_k", &LLMGenerationRequest::top_k)
+        .def_readwrite("top_p", &LLMGenerationRequest::top_p)
+        .def_readwrite("seed", &LLMGenerationRequest::seed)
+        .def_readwrite("apply_chat_template", &LLMGenerationRequest::apply_chat_template)
+        .def_readwrite("add_generation_prompt", &LLMGenerationRequest::add_generation_prompt)
+        .def_readwrite("enable_thinking", &LLMGenerationRequest::enable_thinking)
+        .def_readwrite("ignore_eos", &LLMGenerationRequest::ignore_eos)
+        .def_readwrite("stop", &LLMGenerationRequest::stop)
+        .def_readwrite("stop_token_ids", &LLMGenerationRequest::stop_token_ids)
+        .def_readwrite("lora_name", &LLMGenerationRequest::lora_name)
+        .def_readwrite("num_logprobs", &LLMGenerationRequest::num_logprobs)
+        .def_readwrite("priority", &LLMGenerationRequest::priority)
+        .def_readwrite("disable_spec_decode", &LLMGenerationRequest::disable_spec_decode)
+        .def_readwrite("cache_lookup", &LLMGenerationRequest::cache_lookup)
+        .def_readwrite("cache_commit", &LLMGenerationRequest::cache_commit)
+        .def_readwrite("timeout_s", &LLMGenerationRequest::timeout_s);
+    py::class_<LLMGenerationResponse>(m, "LLMGenerationResponse")
+        .def(py::init<>())
+        .def_readonly("output_ids", &LLMGenerationResponse::output_ids)
+        .def_property_readonly("output_texts", [](const LLMGenerationResponse& r) {
+            py::list out;                                    // text cut by a length limit may end inside a UTF-8 sequence
+            for (const auto& t : r.output_texts) out.append(py::reinterpret_steal<py::object>(PyUnicode_DecodeUTF8(t.data(), (Py_ssize_t)t.size(), "replace")));
+            return out;
+        })
+        .def_readonly("finish_reasons", &LLMGenerationResponse::finish_reasons)
+        .def_readonly("errors", &LLMGenerationResponse::errors)
+        .def_readonly("stats", &LLMGenerationResponse::stats)
+        .def_readonly("logprobs", &LLMGenerationResponse::logprobs);
+    py::class_<LLMInferenceRuntime>(m, "LLMInferenceRuntime")
+        .def(py::init([](EngineConfig cfg, py::function factory, const Tokenizer& tokenizer, py::object chat_template, bool has_draft_model,
+                         py::object capture_hook) {
+            RuntimeOptions opt;
+            opt.engine = cfg;
+            opt.has_draft_model = has_draft_model;
+            if (!capture_hook.is_none()) {
+                auto hook = std::make_shared<py::function>(capture_hook.cast<py::function>());
+                opt.capture_hook = [hook]() {
+                    py::gil_scoped_acquire gil;
+                    return (*hook)().cast<bool>();
+                };
+            }
+            std::shared_ptr<const ChatTemplate> tpl;
+            if (!chat_template.is_none()) tpl = std::make_shared<ChatTemplate>(chat_template.cast<ChatTemplate>());
+            SessionFactory f = session_factory_from_python(std::move(factory));
+            auto tok = std::make_shared<Tokenizer>(tokenizer);
+            py::gil_scoped_release rel;          // the engine opens its first session on this thread, then starts the actor
+            return new LLMInferenceRuntime(std::move(opt), std::move(f), std::move(tok), std::move(tpl));
+        }), py::arg("engine_config"), py::arg("session_factory"), py::arg("tokenizer"), py::arg("chat_template") = py::none(),
+             py::arg("has_draft_model") = false, py::arg("capture_hook") = py::none())
+        .def("handle_request", [](LLMInferenceRuntime& rt, const LLMGenerationRequest& req, py::object on_tokens) {
+            LLMGenerationResponse resp;
+            std::string err;
+            StreamCallback cb;
+            if (!on_tokens.is_none()) {
+                auto fn = std::make_shared<py::function>(on_tokens.cast<py::function>());
+                cb = [fn](int i, const std::vector<int32_t>& toks, const std::string& text, bool finished) {
+                    py::gil_scoped_acquire gil;
+                    (*fn)(i, toks, py::reinterpret_steal<py::object>(PyUnicode_DecodeUTF8(text.data(), (Py_ssize_t)text.size(), "replace")), finished);
+                };
+            }
+            bool ok;
+            {
+                py::gil_scoped_release rel;
+                ok = rt.handle_request(req, resp, cb, &err);
+            }
+            if (!ok) throw std::runtime_error(err);
+            return resp;
+        }, py::arg("request"), py::arg("on_tokens") = py::none())
+        .def("build_prompt_ids", &LLMInferenceRuntime::build_prompt_ids)
+        .def("count_prompt_tokens", &LLMInferenceRuntime::count_prompt_tokens)
+        .def("capture_decoding_cuda_graph", [](LLMInferenceRuntime& rt) {
+            py::gil_scoped_release rel;
+            return rt.capture_decoding_cuda_graph();
+        })
+        .def("unavailable_reason", &LLMInferenceRuntime::unavailable_reason)
+        .def("has_draft_model", &LLMInferenceRuntime::has_draft_model)
+        .def("supports_seated_admission", &LLMInferenceRuntime::supports_seated_admission)
+        .def("supports_stepped_execution", &LLMInferenceRuntime::supports_stepped_execution)
+        .def("submit", [](LLMInferenceRuntime& rt, const GenerationRequest& r) {
+            std::string why;
+            auto h = rt.submit(r, &why);
+            return py::make_tuple(h, why);
+        })
+        .def("open_session", [](LLMInferenceRuntime& rt) {
+            std::shared_ptr<RuntimeSession> s;
+            {
+                py::gil_scoped_release rel;
+                s = rt.open_session();
+            }
+            return s;
+        })
+        .def("metrics", &LLMInferenceRuntime::metrics)
+        .def("queued", [](LLMInferenceRuntime& rt) { return rt.engine().queued(); })
+        .def("resident", [](LLMInferenceRuntime& rt) { return rt.engine().resident(); })
+        .def("status", [](LLMInferenceRuntime& rt) { return rt.engine().status(); })
+        .def("cancel", [](LLMInferenceRuntime& rt, uint64_t id) { rt.engine().cancel(id); })
+        .def("resolved_policy", [](LLMInferenceRuntime& rt) { return rt.engine().resolved_policy(); })
+        .def("shutdown", [](LLMInferenceRuntime& rt) {
+            py::gil_scoped_release rel;
+            rt.shutdown();
         });
 }

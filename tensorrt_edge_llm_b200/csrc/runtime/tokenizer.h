@@ -3,10 +3,9 @@
 // (Llama-2 / Mistral style).  encode / decode / id_to_piece / load_from_hf.
 //
 // Counterpart of cpp/tokenizer/tokenizer.{h,cpp} in the reference (which carries generated Unicode
-// tables, cpp/tokenizer/unicodeData.cpp).  Here Unicode classes are approximated: ASCII is exact;
-// other code points count as letters except the whitespace / punctuation / digit ranges listed in
-// tokenizer.cpp.  Text made of common scripts tokenises identically; exotic digits or symbols may
-// split differently from the Python tokenizer.
+// tables, cpp/tokenizer/unicodeData.cpp).  The letter, number and white-space classes of the
+// pre-tokeniser come from exact range tables (unicode_tables.inc, written by gen_unicode_tables.py
+// from Python's unicodedata), searched by bisection.
 #pragma once
 
 #include <cstdint>

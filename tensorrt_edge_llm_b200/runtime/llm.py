@@ -188,7 +188,16 @@ class LLM:
                                         max_snapshots=self._cache_limits[1], max_records=self._cache_limits[0],
                                         spec_decoder=self.spec_decoder, mirror=self._tp_mirror)
             return self.session             # kept for its counters (prefix hits, jump-forward tokens); the engine thread owns it
-        self.engine = rt.RequestEngine(cfg, make_session)
+        # With a native tokenizer the engine sits inside the native façade (csrc/runtime/inference_runtime.cpp), which adds
+        # handle_request (chat rendering, tokenisation, incremental detokenisation, textual stop sequences) on top of the same
+        # submit / metrics / status surface; otherwise the bare request engine.
+        self.native_runtime = None
+        if isinstance(self.tokenizer, rt.Tokenizer):
+            self.native_runtime = rt.LLMInferenceRuntime(cfg, make_session, self.tokenizer, getattr(self, "native_chat_template", None),
+                                                         self.spec_decoder is not None, None)
+            self.engine = self.native_runtime
+        else:
+            self.engine = rt.RequestEngine(cfg, make_session)
 
     def _native_request(self, ids, sp: SamplingParams, priority: int = 0):
         r = self._rt.GenerationRequest()
