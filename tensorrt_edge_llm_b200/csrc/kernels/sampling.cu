@@ -10,6 +10,9 @@
 // which threads arrive: a greedy row returns the lowest index of the maximum (the same answer as the
 // arg-max kernel) whatever else is in the batch, and seeded sampling is reproducible.
 //
+// token_logprobs: the log-probability of each row's chosen token and the k most likely tokens with theirs (one CTA per row:
+// an online max / sum-of-exponentials pass, then k ordered arg-max passes over the row, which stays in L2).
+//
 // Reference counterpart: cpp/sampler/sampling.cu (topKStage1/2, topP kernels, applyTokenBitmask,
 // applyLogitBias); semantics cpp/sampler/sampling.h:56-160 (kMaxSamplingTopK 1024).
 #include "host_utils.h"
@@ -215,9 +218,108 @@ __global__ void logit_bias_kernel(T* __restrict__ logits, long long stride, cons
     }
 }
 
+
+constexpr int kLogprobThreads = 512;
+constexpr int kMaxLogprobs = 32;
+
+// logits [rows, stride]; tokens [rows]; chosen [rows]; top_ids / top_vals [rows, k] ordered by (log-probability descending,
+// token id ascending).  Pass j finds the best element that comes after pick j - 1 in that order, so no exclusion list is kept.
+template <typename T>
+__global__ void __launch_bounds__(kLogprobThreads) token_logprobs_kernel(const T* __restrict__ logits, long long stride, int vocab,
+                                                                         const int* __restrict__ tokens, int k, float* __restrict__ chosen,
+                                                                         int* __restrict__ top_ids, float* __restrict__ top_vals) {
+    pdl_prologue();
+    __shared__ float s_m[kLogprobThreads / 32], s_s[kLogprobThreads / 32];
+    __shared__ unsigned long long s_key[kLogprobThreads / 32];
+    __shared__ float s_lse;
+    __shared__ unsigned long long s_prev;
+    const int row = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const T* p = logits + (size_t)row * stride;
+    float m = -INFINITY, sum = 0.f;
+    for (int i = tid; i < vocab; i += kLogprobThreads) {
+        const float v = load_logit(p, i);
+        if (v > m) {
+            sum = sum * __expf(m - v) + 1.f;
+            m = v;
+        } else if (v > -INFINITY) {
+            sum += __expf(v - m);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, sum, o);
+        const float mm = fmaxf(m, m2);
+        sum = (m == -INFINITY ? 0.f : sum * __expf(m - mm)) + (m2 == -INFINITY ? 0.f : s2 * __expf(m2 - mm));
+        m = mm;
+    }
+    if (lane == 0) {
+        s_m[warp] = m;
+        s_s[warp] = sum;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float mm = -INFINITY, ss = 0.f;
+        for (int w = 0; w < kLogprobThreads / 32; ++w) mm = fmaxf(mm, s_m[w]);
+        for (int w = 0; w < kLogprobThreads / 32; ++w)
+            if (s_m[w] > -INFINITY) ss += s_s[w] * __expf(s_m[w] - mm);
+        s_lse = mm + logf(ss);
+        const int t = min(max(tokens[row], 0), vocab - 1);
+        chosen[row] = load_logit(p, t) - s_lse;
+        s_prev = ~0ull;                                   // above every key: the first pass takes the overall best
+    }
+    __syncthreads();
+    const float lse = s_lse;
+    for (int j = 0; j < k; ++j) {
+        const unsigned long long prev = s_prev;
+        unsigned long long best = 0ull;
+        for (int i = tid; i < vocab; i += kLogprobThreads) {
+            float v = load_logit(p, i);
+            if (!(v == v)) v = -INFINITY;
+            if (v == 0.f) v = 0.f;
+            const unsigned long long key = (static_cast<unsigned long long>(order_key(v)) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(i));
+            if (key < prev && key > best) best = key;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+            best = other > best ? other : best;
+        }
+        if (lane == 0) s_key[warp] = best;
+        __syncthreads();
+        if (tid == 0) {
+            unsigned long long b = 0ull;
+            for (int w = 0; w < kLogprobThreads / 32; ++w) b = s_key[w] > b ? s_key[w] : b;
+            s_prev = b;
+            if (b != 0ull) {
+                top_ids[(size_t)row * k + j] = static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(b & 0xFFFFFFFFull));
+                top_vals[(size_t)row * k + j] = key_value(static_cast<uint32_t>(b >> 32)) - lse;
+            } else {                                      // fewer than k elements
+                top_ids[(size_t)row * k + j] = -1;
+                top_vals[(size_t)row * k + j] = -INFINITY;
+            }
+        }
+        __syncthreads();
+    }
+}
+
 }  // namespace telb
 
 using namespace telb;
+
+// Log-probability of tokens[row] under softmax(logits[row]) and the k (<= 32) most likely tokens with theirs.  dtype as in telb_sample.
+extern "C" int telb_token_logprobs(const void* logits, long long stride, int rows, int vocab, const int* tokens, int k, float* chosen,
+                                   int* top_ids, float* top_vals, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (k < 0 || k > kMaxLogprobs) return fail("telb_token_logprobs: 0..32 alternatives");
+    if (dtype == 2)
+        TELB_LAUNCH("token_logprobs_kernel", (token_logprobs_kernel<float>), dim3(rows), dim3(kLogprobThreads), 0, stream, (const float*)logits, stride, vocab, tokens, k, chosen, top_ids, top_vals);
+    else if (dtype == 1)
+        TELB_LAUNCH("token_logprobs_kernel", (token_logprobs_kernel<__nv_bfloat16>), dim3(rows), dim3(kLogprobThreads), 0, stream, (const __nv_bfloat16*)logits, stride, vocab, tokens, k, chosen, top_ids, top_vals);
+    else
+        TELB_LAUNCH("token_logprobs_kernel", (token_logprobs_kernel<__half>), dim3(rows), dim3(kLogprobThreads), 0, stream, (const __half*)logits, stride, vocab, tokens, k, chosen, top_ids, top_vals);
+    TELB_CHECK_LAUNCH("token_logprobs_kernel");
+    return 0;
+}
 
 // dtype: 0 = fp16, 1 = bf16, 2 = fp32
 extern "C" int telb_sample(const void* logits, long long stride, int rows, int vocab, const float* temperature,

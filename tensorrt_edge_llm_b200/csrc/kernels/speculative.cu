@@ -3,6 +3,9 @@
 //                        token equals the target model's arg-max at the current node; emits the accepted
 //                        path, its length and the bonus token.  A forced length per sequence (benchmark
 //                        mode, null = off) follows the first child instead of comparing tokens.
+//   spec_accept_sampling lossless acceptance for sampled requests: a node's children are tried in order, child c is kept with
+//                        the target's (residual) probability of its token, a rejected token leaves the distribution; when no
+//                        child is kept the bonus token is drawn from what is left.  One CTA per sequence, no host read.
 //   kv_commit_path       compact the accepted path in the paged cache: the entry written at tree slot
 //                        past + path[j] moves to past + j, for every layer / K,V / head, in place.
 //
@@ -429,6 +432,135 @@ __global__ void __launch_bounds__(32) lattice_chain_walk_kernel(const int* __res
     }
 }
 
+constexpr int kAcceptThreads = 256;
+constexpr int kAcceptMaxRejected = 64;
+
+// probs [B, N, V] fp32 (each row a distribution), tree_tokens / parents [B, N], uniforms [B, max_path, kw] (kw - 1 sibling trials and
+// one bonus draw per depth) -> path [B, max_path], path_len [B], bonus [B].  Sums run in double, like the host restatement.
+__global__ void __launch_bounds__(kAcceptThreads) spec_accept_sampling_kernel(const float* __restrict__ probs, const int* __restrict__ tree_tokens,
+                                                                              const int* __restrict__ parents, const float* __restrict__ uniforms,
+                                                                              int* __restrict__ path, int* __restrict__ path_len,
+                                                                              int* __restrict__ bonus, int N, int V, int max_path, int kw) {
+    pdl_prologue();
+    __shared__ double s_part[kAcceptThreads];
+    __shared__ int s_rej[kAcceptMaxRejected];
+    __shared__ int s_nrej, s_next, s_seg;
+    __shared__ double s_total, s_rejmass, s_before;
+    const int b = blockIdx.x, tid = threadIdx.x;
+    const int* tok = tree_tokens + (size_t)b * N;
+    const int* par = parents + (size_t)b * N;
+    const float* u = uniforms + (size_t)b * max_path * kw;
+    const int seg = (V + kAcceptThreads - 1) / kAcceptThreads;           // contiguous vocabulary segment per thread
+    const int lo = min(V, tid * seg), hi = min(V, lo + seg);
+    int cur = 0, ln = 1;
+    if (tid == 0) path[(size_t)b * max_path] = 0;
+    for (;;) {
+        const float* p = probs + ((size_t)b * N + cur) * V;
+        const int depth = ln - 1;
+        double part = 0.0;
+        for (int i = lo; i < hi; ++i) part += (double)p[i];
+        s_part[tid] = part;
+        __syncthreads();
+        if (tid == 0) {
+            double total = 0.0;
+            for (int i = 0; i < kAcceptThreads; ++i) total += s_part[i];
+            int nrej = 0, nxt = -1;
+            double rejmass = 0.0;
+            if (ln < max_path) {
+                int trial = 0;
+                for (int c = cur + 1; c < N; ++c) {
+                    if (par[c] != cur) continue;
+                    const int t = min(max(tok[c], 0), V - 1);
+                    bool gone = false;
+                    for (int j = 0; j < nrej; ++j) gone = gone || s_rej[j] == t;
+                    const double mass = total - rejmass;
+                    const double pc = (mass > 0.0 && !gone) ? (double)p[t] / mass : 0.0;
+                    if ((double)u[depth * kw + min(trial, kw - 2)] < pc) {
+                        nxt = c;
+                        break;
+                    }
+                    if (!gone && nrej < kAcceptMaxRejected) {
+                        s_rej[nrej++] = t;
+                        rejmass += (double)p[t];
+                    }
+                    ++trial;
+                }
+            }
+            if (nxt < 0 && total - rejmass <= 0.0) {       // every token with mass was a rejected candidate: fall back to the full row
+                nrej = 0;
+                rejmass = 0.0;
+            }
+            s_total = total;
+            s_rejmass = rejmass;
+            s_nrej = nrej;
+            s_next = nxt;
+        }
+        __syncthreads();
+        if (s_next >= 0) {
+            cur = s_next;
+            if (tid == 0) path[(size_t)b * max_path + ln] = cur;
+            ++ln;
+            __syncthreads();
+            continue;
+        }
+        // bonus draw: first index whose cumulative residual mass reaches u * mass
+        const int nrej = s_nrej;
+        if (nrej > 0) {                                     // segment sums without the rejected tokens
+            for (int j = 0; j < nrej; ++j) {
+                const int t = s_rej[j];
+                if (t >= lo && t < hi) part -= (double)p[t];
+            }
+        }
+        __syncthreads();
+        s_part[tid] = part;
+        __syncthreads();
+        if (tid == 0) {
+            const double target = (double)u[depth * kw + kw - 1] * (s_total - s_rejmass);
+            double cum = 0.0;
+            int sg = kAcceptThreads - 1;
+            for (int i = 0; i < kAcceptThreads; ++i) {
+                if (cum + s_part[i] >= target && s_part[i] > 0.0) {
+                    sg = i;
+                    break;
+                }
+                cum += s_part[i];
+            }
+            if (sg == kAcceptThreads - 1 && !(cum + s_part[sg] >= target)) {
+                // rounding left the target just above the total: the last segment that holds mass
+                cum = 0.0;
+                int last = 0;
+                for (int i = 0; i < kAcceptThreads; ++i)
+                    if (s_part[i] > 0.0) last = i;
+                for (int i = 0; i < last; ++i) cum += s_part[i];
+                sg = last;
+            }
+            s_seg = sg;
+            s_before = cum;
+        }
+        __syncthreads();
+        if (tid == s_seg) {
+            const double target = (double)u[depth * kw + kw - 1] * (s_total - s_rejmass);
+            double cum = s_before;
+            int pick = -1, last_mass = -1;
+            for (int i = lo; i < hi; ++i) {
+                double v = (double)p[i];
+                for (int j = 0; j < nrej; ++j)
+                    if (s_rej[j] == i) v = 0.0;
+                if (v > 0.0) last_mass = i;
+                cum += v;
+                if (cum >= target && v > 0.0) {
+                    pick = i;
+                    break;
+                }
+            }
+            if (pick < 0) pick = last_mass >= 0 ? last_mass : min(V - 1, max(lo, 0));
+            bonus[b] = pick;
+            path_len[b] = ln;
+        }
+        return;
+    }
+}
+
 // One CTA per row.  hidden [R, H] and lm_head [V, H] 16-bit, cand [R, kc] int32 (distinct ids per row).
 // Shared memory: H floats (the row), kc floats (logits), kc ints (ids).
 template <typename T>
@@ -655,5 +787,20 @@ extern "C" int telb_markov_greedy_chain(const float* logits, const void* w1, con
     }
     TELB_LAUNCH("markov_unpack_kernel", markov_unpack_kernel, dim3((batch * steps + 127) / 128), dim3(128), 0, stream, slots, tokens, batch * steps);
     TELB_CHECK_LAUNCH("markov_unpack_kernel");
+    return 0;
+}
+
+// Lossless tree acceptance for sampled requests.  probs [batch, nodes, vocab] fp32 rows of the target distribution at every tree
+// node; uniforms [batch, max_path, kw] with kw >= 2.
+extern "C" int telb_spec_accept_sampling(const float* probs, const int* tree_tokens, const int* parents, const float* uniforms, int* path,
+                                         int* path_len, int* bonus, int batch, int nodes, int vocab, int max_path, int kw,
+                                         cudaStream_t stream) {
+    if (batch <= 0) return 0;
+    if (nodes < 1 || max_path < 1 || kw < 2) return fail("telb_spec_accept_sampling: needs a tree, a path bound and at least two uniforms per depth");
+    cudaError_t e = cudaMemsetAsync(path, 0, (size_t)batch * max_path * sizeof(int), stream);
+    if (e != cudaSuccess) return fail("telb_spec_accept_sampling: memset", e);
+    TELB_LAUNCH("spec_accept_sampling_kernel", spec_accept_sampling_kernel, dim3(batch), dim3(kAcceptThreads), 0, stream, probs, tree_tokens,
+                parents, uniforms, path, path_len, bonus, nodes, vocab, max_path, kw);
+    TELB_CHECK_LAUNCH("spec_accept_sampling_kernel");
     return 0;
 }

@@ -182,6 +182,21 @@ def spec_accept_greedy(target_tokens, tree_tokens, parents, max_path, force_len=
     return ref.spec_accept_greedy(target_tokens, tree_tokens, parents, max_path, force_len)
 
 
+def token_logprobs(logits, tokens, k):
+    """Log-probability of each row's token and its ``k`` most likely tokens: ``(chosen, top_ids, top_values)``."""
+    if logits.is_cuda and logits.stride(-1) == 1 and k <= 32 and logits.dtype in (torch.float16, torch.bfloat16, torch.float32):
+        return cuda_ops().token_logprobs(logits, tokens, k)
+    return ref.token_logprobs(logits, tokens, k)
+
+
+def spec_accept_sampling(target_probs, tree_tokens, parents, max_path, uniforms):
+    """Lossless acceptance along a draft tree for sampled requests (sibling-by-sibling rejection against each node's target
+    distribution, bonus token from the residual): ``(path, path_len, bonus)``."""
+    if target_probs.is_cuda:
+        return cuda_ops().spec_accept_sampling(target_probs, tree_tokens, parents, max_path, uniforms)
+    return ref.spec_accept_sampling(target_probs, tree_tokens, parents, max_path, uniforms)
+
+
 def eagle_tree_meta(parents, base_pos, depth_base, pos_offset):
     """``(mask [B*R, W], depth [B, R], positions [B*R])`` of a batch of trees given as parent tables."""
     if parents.is_cuda:

@@ -675,6 +675,20 @@ def sample(logits, temperature, top_k, top_p, uniforms) -> torch.Tensor:
     return out
 
 
+def token_logprobs(logits, tokens, k: int):
+    """``(chosen [rows] fp32, top_ids [rows, k] int32, top_values [rows, k] fp32)``: log-probability of ``tokens[row]`` and the ``k``
+    most likely tokens of every row under ``softmax(logits[row])``."""
+    assert logits.dim() == 2 and logits.stride(1) == 1 and 0 <= k <= 32
+    rows, vocab = logits.shape
+    tok = tokens.to(device=logits.device, dtype=torch.int32).contiguous()
+    chosen = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    ids = torch.empty(rows, max(k, 1), dtype=torch.int32, device=logits.device)
+    vals = torch.empty(rows, max(k, 1), dtype=torch.float32, device=logits.device)
+    _check(lib().telb_token_logprobs(_p(logits), c_ll(logits.stride(0)), c_int(rows), c_int(vocab), _p(tok), c_int(k), _p(chosen), _p(ids),
+                                     _p(vals), c_int(_logit_dtype(logits)), _stream()), "token_logprobs")
+    return chosen, ids[:, :k], vals[:, :k]
+
+
 def apply_token_bitmask(logits: torch.Tensor, bitmask: torch.Tensor) -> torch.Tensor:
     """In place: entries whose bit is 0 in ``bitmask [rows, ceil(V/32)]`` become very negative."""
     _check(lib().telb_apply_token_bitmask(_p(logits), c_ll(logits.stride(0)), c_int(logits.shape[0]), c_int(logits.shape[1]),
@@ -940,6 +954,24 @@ def dflash2_selector_walk(cand_ids, unary, projected, anchor, pred_codebook, suc
                                        c_int(z.shape[-1]), c_int(pc.shape[0]), c_int(int(z.dtype == torch.bfloat16)), _stream()),
            "dflash2_selector")
     return tok.long(), pr
+
+
+def spec_accept_sampling(target_probs, tree_tokens, parents, max_path: int, uniforms):
+    """Lossless tree acceptance of sampled requests on the device: ``(path [B, max_path], path_len [B], bonus [B])`` int32."""
+    b, n, v = target_probs.shape
+    dev = target_probs.device
+    pr = target_probs.float().contiguous()
+    tok, par = tree_tokens.to(device=dev, dtype=torch.int32).contiguous(), parents.to(device=dev, dtype=torch.int32).contiguous()
+    u = uniforms.to(device=dev, dtype=torch.float32).contiguous()
+    assert u.shape[0] == b and u.shape[1] >= max_path and u.shape[2] >= 2
+    if u.shape[1] != max_path:
+        u = u[:, :max_path].contiguous()
+    path = torch.empty(b, max_path, dtype=torch.int32, device=dev)
+    plen = torch.empty(b, dtype=torch.int32, device=dev)
+    bonus = torch.empty(b, dtype=torch.int32, device=dev)
+    _check(lib().telb_spec_accept_sampling(_p(pr), _p(tok), _p(par), _p(u), _p(path), _p(plen), _p(bonus), c_int(b), c_int(n), c_int(v),
+                                           c_int(max_path), c_int(u.shape[2]), _stream()), "spec_accept_sampling")
+    return path, plen, bonus
 
 
 def markov_greedy_chain(logits, w1, w2, first_prev):

@@ -632,6 +632,17 @@ def sampling_probs(logits: torch.Tensor, temperature: float, top_k: int = 0, top
     return p
 
 
+def token_logprobs(logits: torch.Tensor, tokens: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Log-probability of ``tokens[row]`` and the ``k`` most likely tokens (ordered by probability, ties → the lower id) of every
+    row under ``softmax(logits[row])``: ``(chosen [rows], top_ids [rows, k] int32, top_values [rows, k])`` fp32."""
+    lp = torch.log_softmax(logits.float(), dim=-1)
+    chosen = lp.gather(1, tokens.long().to(lp.device)[:, None])[:, 0]
+    if k <= 0:
+        return chosen, torch.empty(lp.shape[0], 0, dtype=torch.int32, device=lp.device), torch.empty(lp.shape[0], 0, device=lp.device)
+    order = lp.sort(dim=-1, descending=True, stable=True)
+    return chosen, order.indices[:, :k].to(torch.int32), order.values[:, :k]
+
+
 def spec_accept_sampling(target_probs: torch.Tensor, tree_tokens: torch.Tensor, parents: torch.Tensor, max_path: int,
                          uniforms: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Lossless tree acceptance for sampled requests (``cpp/kernels/speculative/speculativeSamplingKernels.cu`` in the

@@ -120,13 +120,18 @@ def logprobs(processed: torch.Tensor, tokens: Sequence[int], states: Sequence[Op
     res: List[Optional[StepLogprobs]] = [None] * len(states)
     if not want:
         return res
-    lp = torch.log_softmax(processed[want].float(), dim=-1)
-    tok = torch.tensor([int(tokens[i]) for i in want], device=lp.device, dtype=torch.int64)
-    chosen = lp.gather(1, tok[:, None])[:, 0].tolist()
+    tok = torch.tensor([int(tokens[i]) for i in want], dtype=torch.int64).to(processed.device)
     kmax = max(states[i].num_logprobs for i in want)
-    top_v, top_i = (lp.topk(kmax, dim=-1) if kmax > 0 else (None, None))
-    top_v = top_v.tolist() if kmax > 0 else None
-    top_i = top_i.tolist() if kmax > 0 else None
+    rows = processed if len(want) == processed.shape[0] else processed[want]
+    if kmax <= 32:                      # one kernel per step on the GPU: log-sum-exp, the chosen token, k ordered arg-max passes
+        chosen_t, top_i_t, top_v_t = ops.token_logprobs(rows, tok, kmax)
+    else:
+        lp = torch.log_softmax(rows.float(), dim=-1)
+        chosen_t = lp.gather(1, tok[:, None])[:, 0]
+        top_v_t, top_i_t = lp.topk(kmax, dim=-1)
+    chosen = chosen_t.tolist()
+    top_v = top_v_t.tolist() if kmax > 0 else None
+    top_i = top_i_t.tolist() if kmax > 0 else None
     for j, i in enumerate(want):
         k = states[i].num_logprobs
         res[i] = StepLogprobs([chosen[j]], [top_i[j][:k]] if k > 0 else [[]], [top_v[j][:k]] if k > 0 else [[]])

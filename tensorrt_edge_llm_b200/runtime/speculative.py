@@ -344,8 +344,8 @@ class EagleDecoder:
             # bonus token from the residual (see ops.reference.spec_accept_sampling)
             sm = self.sampling
             probs = ops.ref.sampling_probs(logits, sm["temperature"], sm["top_k"], sm["top_p"]).view(b, nn_, -1)
-            path, plen, bonus = ops.ref.spec_accept_sampling(probs, tree_tok.to(torch.int32), tree_par.to(torch.int32), max_path,
-                                                              self._uniforms(b, max_path, k + 1))
+            path, plen, bonus = ops.spec_accept_sampling(probs, tree_tok.to(torch.int32), tree_par.to(torch.int32), max_path,
+                                                          self._uniforms(b, max_path, k + 1))
             path, plen, bonus = path.to(dev), plen.to(dev), bonus.to(dev)
         past_t = lt_dev
         ops.kv_commit_path(self.r.kv.pool, self.r.kv.table_rows(seats).to(dev), past_t, path, plen)

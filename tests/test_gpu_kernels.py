@@ -624,3 +624,27 @@ def test_mlp_with_fused_swiglu_matches_unfused(monkeypatch):
         assert torch.equal(fused(qa), plain(qb))
     assert fused.gate_up_proj.gate_up_interleaved and not plain.gate_up_proj.gate_up_interleaved
     assert torch.equal(fused.gate_up_proj.dequantized_weight(), plain.gate_up_proj.dequantized_weight())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,vocab,k", [(1, 100, 0), (5, 4099, 5), (64, 151936, 20), (3, 33, 32)])
+def test_token_logprobs_kernel(dtype, rows, vocab, k):
+    """Chosen-token and top-k log-probabilities against log_softmax + a stable sort of the same (rounded) logits."""
+    from tensorrt_edge_llm_b200.ops import cuda as cu
+    g = torch.Generator().manual_seed(vocab + k)
+    logits = (torch.randn(rows, vocab, generator=g) * 4).to(dtype)
+    logits[0, 7] = logits[0, 3] = logits.float().max() + 1       # a tie at the top: the lower id first
+    if vocab > 50:
+        logits[-1, 40:50] = float("-inf")                        # masked tokens (guided decoding)
+    tokens = torch.randint(0, vocab, (rows,), generator=g)
+    want = ref.token_logprobs(logits, tokens, k)
+    got = cu.token_logprobs(logits.cuda(), tokens.cuda(), k)
+    assert torch.allclose(got[0].cpu(), want[0], atol=2e-3)
+    if k:
+        assert torch.equal(got[1].cpu(), want[1]) and torch.allclose(got[2].cpu(), want[2], atol=2e-3)
+        assert got[1][0, :2].tolist() == [3, 7]
+    # a strided view (the last rows of a wider buffer) reads the right rows
+    wide = torch.zeros(rows, vocab + 8, dtype=dtype).cuda()
+    wide[:, :vocab] = logits.cuda()
+    again = cu.token_logprobs(wide[:, :vocab], tokens.cuda(), k)
+    assert torch.allclose(again[0], got[0]) and torch.equal(again[1], got[1])

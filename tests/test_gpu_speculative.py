@@ -275,3 +275,47 @@ def test_markov_greedy_chain_kernel(cu, dtype, b, p, v, r):
     z = torch.zeros(64, 32, dtype=dtype)
     tie = cu.markov_greedy_chain(lg.cuda(), z.cuda(), z.cuda(), torch.tensor([0]).cuda()).cpu()
     assert tie.tolist() == [[3, 0]]
+
+
+@pytest.mark.parametrize("b,n,v,k", [(1, 8, 50, 2), (6, 40, 5000, 4), (3, 61, 32000, 8)])
+def test_spec_accept_sampling_kernel(cu, b, n, v, k):
+    """Device rejection sampling against the host restatement on random trees: peaked target rows so that paths of every
+    length occur; a draw within rounding of a probability boundary may differ, so nearly all sequences must agree."""
+    g = torch.Generator().manual_seed(n * k)
+    tree, par = _random_tree(g, b, n, vocab=v)
+    probs = torch.softmax(torch.randn(b, n, v, generator=g) * 2.0, dim=-1)
+    for i in range(b):                                   # make some children likely under their parent's distribution
+        for c in range(1, n):
+            if c % 2:
+                probs[i, par[i, c], tree[i, c]] += 2.0
+        probs[i] /= probs[i].sum(-1, keepdim=True)
+    max_path = 6
+    agree = total = 0
+    lens = set()
+    for seed in range(4):
+        u = torch.rand(b, max_path, k + 1, generator=torch.Generator().manual_seed(seed))
+        want = ref.spec_accept_sampling(probs, tree, par, max_path, u)
+        got = cu.spec_accept_sampling(probs.cuda(), tree.cuda(), par.cuda(), max_path, u.cuda())
+        for i in range(b):
+            m = int(want[1][i])
+            lens.add(m)
+            same = int(got[1][i]) == m and got[0][i, :m].cpu().tolist() == want[0][i, :m].tolist() and int(got[2][i]) == int(want[2][i])
+            agree += int(same)
+            total += 1
+            assert 0 <= int(got[2][i]) < v and 1 <= int(got[1][i]) <= max_path
+    assert agree >= total - 1 and len(lens) >= 2
+    # a tree whose first child is certain, then a leaf: path root -> child, bonus from the child's row
+    pr = torch.zeros(1, 2, 10)
+    pr[0, 0, 4] = 1.0
+    pr[0, 1, 7] = 1.0
+    got = cu.spec_accept_sampling(pr.cuda(), torch.tensor([[0, 4]], dtype=torch.int32).cuda(), torch.tensor([[-1, 0]], dtype=torch.int32).cuda(), 4,
+                                  torch.full((1, 4, 3), 0.5).cuda())
+    assert got[1].tolist() == [2] and got[0][0, :2].tolist() == [0, 1] and got[2].tolist() == [7]
+    # the only token with mass is a rejected candidate (u above its probability cannot happen at p = 1, so force p < 1 ... = residual fallback)
+    pr = torch.zeros(1, 2, 10)
+    pr[0, 0, 4] = 0.25
+    pr[0, 0, 9] = 0.75
+    pr[0, 1, 1] = 1.0
+    got = cu.spec_accept_sampling(pr.cuda(), torch.tensor([[0, 4]], dtype=torch.int32).cuda(), torch.tensor([[-1, 0]], dtype=torch.int32).cuda(), 4,
+                                  torch.full((1, 4, 3), 0.9).cuda())
+    assert got[1].tolist() == [1] and got[2].tolist() == [9]
