@@ -55,12 +55,14 @@ def runtime_config_dict(cfg, max_batch_size: int, max_input_len: int, max_kv_cac
 
 
 def write_artifacts(model_dir: str, out_dir: str, tensor_parallel_size: int = 1, max_batch_size: int = 1, max_input_len: int = 4096,
-                    max_kv_cache_capacity: int = 8192, expert_parallel: bool = False) -> dict:
+                    max_kv_cache_capacity: int = 8192, expert_parallel: bool = False, externalize_weights=None) -> dict:
     """Prepare ``model_dir`` for ``tensor_parallel_size`` ranks and write the artefact set into ``out_dir``.  Returns the world
     configuration.  Raises ``KeyError`` when the checkpoint lacks a tensor some rank needs."""
     from ..config import Mapping, ModelConfig
     from ..model import model_class_for
+    from .external_weights import resolve_externalize_weights, split_state
     from .loader import load_weights
+    kinds = resolve_externalize_weights(externalize_weights)
     if os.path.abspath(model_dir) == os.path.abspath(out_dir):
         raise ValueError("the artefact directory must differ from the checkpoint directory (both hold *.safetensors files)")
     os.makedirs(out_dir, exist_ok=True)
@@ -71,12 +73,18 @@ def write_artifacts(model_dir: str, out_dir: str, tensor_parallel_size: int = 1,
         cfg = ModelConfig.from_pretrained(model_dir, mapping)
         model = model_class_for(cfg)(cfg, None)       # a real construction: buffers the checkpoint does not carry keep their defaults
         load_weights(model, model_dir, strict=True)
-        state = {k: v for k, v in model.state_dict().items()}
+        state, external = split_state({k: v for k, v in model.state_dict().items()}, kinds)
         fn = f"rank{rank}.safetensors"
         save_file(state, os.path.join(out_dir, fn), metadata={"format": "pt", "rank": str(rank), "world": str(tp)})
-        ranks.append({"rank": rank, "weights": fn, "bytes": os.path.getsize(os.path.join(out_dir, fn)),
-                      "sha256": _sha256(os.path.join(out_dir, fn)), "tensors": len(state)})
-        del model, state
+        entry = {"rank": rank, "weights": fn, "bytes": os.path.getsize(os.path.join(out_dir, fn)),
+                 "sha256": _sha256(os.path.join(out_dir, fn)), "tensors": len(state)}
+        if external:
+            xfn = f"rank{rank}.external.safetensors"
+            save_file(external, os.path.join(out_dir, xfn), metadata={"format": "pt", "rank": str(rank), "world": str(tp), "kinds": ",".join(kinds)})
+            entry["external"] = {"weights": xfn, "bytes": os.path.getsize(os.path.join(out_dir, xfn)), "sha256": _sha256(os.path.join(out_dir, xfn)),
+                                 "tensors": len(external), "kinds": kinds}
+        ranks.append(entry)
+        del model, state, external
     cfg = ModelConfig.from_pretrained(model_dir)
     with open(os.path.join(out_dir, "runtime_config.json"), "w", encoding="utf-8") as f:
         json.dump(runtime_config_dict(cfg, max_batch_size, max_input_len, max_kv_cache_capacity, tp), f, indent=1, default=str)
@@ -119,8 +127,9 @@ def artifact_model_config(engine_dir: str, mapping=None):
     return cfg, rc.get("deployment", {})
 
 
-def load_artifacts(engine_dir: str, mapping=None, comm=None, device="cpu", verify: bool = False):
-    """Build the rank's model from an artefact directory.  ``verify`` re-hashes the weight file against the world config."""
+def load_artifacts(engine_dir: str, mapping=None, comm=None, device="cpu", verify: bool = False, external_dir: Optional[str] = None):
+    """Build the rank's model from an artefact directory.  ``verify`` re-hashes the weight files against the world config;
+    ``external_dir`` reads the rank's externalised tensors from another directory (same file name)."""
     from ..model import model_class_for
     cfg, _ = artifact_model_config(engine_dir, mapping)
     world = read_world_config(engine_dir)
@@ -133,6 +142,15 @@ def load_artifacts(engine_dir: str, mapping=None, comm=None, device="cpu", verif
     model = model_class_for(cfg)(cfg, comm)
     f = SafetensorsFile(path)
     state: Dict[str, torch.Tensor] = {k: f.get(k) for k in f.keys()}
+    ext = entry.get("external")
+    if ext:
+        xpath = os.path.join(external_dir or engine_dir, ext["weights"])
+        if not os.path.isfile(xpath):
+            raise FileNotFoundError(f"{xpath}: the externalised weights ({', '.join(ext.get('kinds', []))}) of rank {cfg.mapping.tp_rank} are missing")
+        if verify and external_dir is None and _sha256(xpath) != ext["sha256"]:
+            raise ValueError(f"{xpath}: contents do not match the world configuration (sha256)")
+        xf = SafetensorsFile(xpath)
+        state.update({k: xf.get(k) for k in xf.keys()})
     own = model.state_dict()
     missing = sorted(set(own) - set(state))
     unexpected = sorted(set(state) - set(own))

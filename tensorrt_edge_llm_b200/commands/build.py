@@ -25,6 +25,8 @@ def main(argv=None) -> int:
     p.add_argument("--max-kv-cache-capacity", type=int, default=8192)
     p.add_argument("--tensor-parallel-size", type=int, default=1)
     p.add_argument("--expert-parallel", action="store_true", help="shard experts by id over the ranks (MoE checkpoints)")
+    p.add_argument("--externalize-weights", "--externalize_weights", default="",
+                   help="comma-separated kinds kept in a separate per-rank file: lm_head, ffn, moe, embedding, all")
     p.add_argument("--config-only", action="store_true", help="validate and write runtime_config.json only, no prepared weights")
     a = p.parse_args(argv)
     import torch
@@ -35,13 +37,17 @@ def main(argv=None) -> int:
     if not a.config_only and os.path.abspath(out_dir) != os.path.abspath(a.model_dir):
         try:
             world = write_artifacts(a.model_dir, out_dir, a.tensor_parallel_size, a.max_batch_size, a.max_input_len,
-                                    a.max_kv_cache_capacity, a.expert_parallel)
+                                    a.max_kv_cache_capacity, a.expert_parallel, a.externalize_weights or None)
         except KeyError as e:
             print(json.dumps({"ok": False, "missing": [str(e)]}))
             return 1
+        except ValueError as e:
+            print(json.dumps({"ok": False, "error": str(e)}))
+            return 2
         print(json.dumps({"ok": True, "runtime_config": os.path.join(out_dir, "runtime_config.json"),
                           "world_config": os.path.join(out_dir, "world_config.json"),
-                          "weights": [r["weights"] for r in world["ranks"]], "bytes": sum(r["bytes"] for r in world["ranks"])}))
+                          "weights": [r["weights"] for r in world["ranks"]], "bytes": sum(r["bytes"] for r in world["ranks"]),
+                          "external_weights": [r["external"]["weights"] for r in world["ranks"] if "external" in r]}))
         return 0
     missing = []
     for rank in range(a.tensor_parallel_size):

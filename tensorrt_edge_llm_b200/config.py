@@ -373,7 +373,7 @@ class ModelConfig:
         if isinstance(d.get("diffusion"), dict):
             d["diffusion"] = DiffusionConfig(**d["diffusion"])
         known = {f.name for f in dataclasses.fields(cls)}
-        cfg = cls(**{k: v for k, v in d.items() if k in known})
+        return cls(**{k: v for k, v in d.items() if k in known})
 
     # -- HF parsing ------------------------------------------------------------------------
     @classmethod

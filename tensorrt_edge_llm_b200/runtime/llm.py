@@ -573,6 +573,25 @@ class LLM:
             self.kv.free(s)
         return outs
 
+    def refit(self, source, names=None, timeout_s: float = 60.0) -> dict:
+        """Replace weights of the live model in place (``checkpoint/external_weights.py: refit``): ``source`` is a safetensors
+        file or a ``name → tensor`` dict named as the model's state (an artefact directory's ``rank<r>.external.safetensors``,
+        for instance).  Waits for the request engine to drain first; cached K/V of the old weights is never reused afterwards
+        (a new prefix-cache generation).  Tensor addresses do not change, so captured graphs stay valid."""
+        import time
+        from ..checkpoint.external_weights import refit as _refit
+        if self.engine is not None:
+            t0 = time.monotonic()
+            while self.engine.queued() or self.engine.resident():
+                if time.monotonic() - t0 > timeout_s:
+                    raise TimeoutError("refit: the request engine did not drain in time")
+                time.sleep(0.005)
+        stats = _refit(self.model, source, names)
+        self.runner.weights_epoch = int(getattr(self.runner, "weights_epoch", 0)) + 1
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        return stats
+
     def close(self):
         if self.engine is not None:
             self.engine.shutdown()

@@ -96,11 +96,12 @@ class ModelSession(rt.RuntimeSession):
         one adapter (LoRA wraps the QKV projection) is never adopted by the base model or by another adapter, and
         an adapter reloaded under the same name starts a new chain."""
         name = getattr(req, "lora_name", "") or ""
+        epoch = int(getattr(self.runner, "weights_epoch", 0))       # bumped by a refit: K/V of the old weights is never adopted
         if not name:
-            return 0
+            return int(rt.PrefixCache.extras_seed("", epoch, "weights")) if epoch else 0
         lora = getattr(self.runner, "lora", None)
         gen = lora.generation(name) if lora is not None and hasattr(lora, "generation") else 0
-        return int(rt.PrefixCache.extras_seed(name, int(gen), ""))
+        return int(rt.PrefixCache.extras_seed(name, int(gen), f"weights{epoch}" if epoch else ""))
 
     # ---- seam ------------------------------------------------------------------------------------
     def capabilities(self):

@@ -395,3 +395,94 @@ def test_runtime_names_of_the_reference_package():
     sess = runtime.open_session()
     assert sess.capabilities().max_batch_size == 2 and runtime.get_generation_metrics()["output_tokens"] == 8
     runtime.close()
+
+
+def test_externalized_weights_and_refit(tmp_path):
+    """Artefacts with the LM head and FFN tensors in a separate per-rank file load to the same model; refit replaces them in a
+    live LLM in place, changes its outputs to the new weights' and retires cached prefixes."""
+    import json
+    import torch
+    from tensorrt_edge_llm_b200 import AutoModel
+    from tensorrt_edge_llm_b200.checkpoint import external_weights as xw
+    from tensorrt_edge_llm_b200.checkpoint.artifacts import load_artifacts, write_artifacts
+    from tensorrt_edge_llm_b200.checkpoint.safetensors_io import SafetensorsFile, save_file
+    from tensorrt_edge_llm_b200.config import tiny_llama_config
+    from tensorrt_edge_llm_b200.runtime.llm import LLM
+    from tensorrt_edge_llm_b200.runtime.runner import SamplingParams
+
+    assert xw.resolve_externalize_weights("lm_head, int4_ffn") == ["ffn", "lm_head"] and xw.resolve_externalize_weights(None) == []
+    assert set(xw.resolve_externalize_weights("all")) == set(xw.EXTERNAL_WEIGHT_KINDS)
+    with pytest.raises(ValueError):
+        xw.resolve_externalize_weights("kv")
+    assert xw.kind_of("lm_head.weight") == "lm_head" and xw.kind_of("model.layers.3.mlp.down_proj.weight") == "ffn"
+    assert xw.kind_of("model.layers.0.mlp.experts.w13") == "moe" and xw.kind_of("model.embed_tokens.weight") == "embedding"
+    assert xw.kind_of("model.layers.0.self_attn.qkv_proj.weight") is None
+
+    def checkpoint(seed, d):
+        cfg = tiny_llama_config(num_hidden_layers=2, dtype="float32")
+        m = AutoModel.from_config(cfg, random_init=seed)
+        d.mkdir()
+        hf = {"model_type": "llama", "hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size, "num_hidden_layers": 2,
+              "num_attention_heads": cfg.num_attention_heads, "num_key_value_heads": cfg.num_key_value_heads, "vocab_size": cfg.vocab_size,
+              "head_dim": cfg.head_dim, "max_position_embeddings": cfg.max_position_embeddings, "rms_norm_eps": cfg.rms_norm_eps,
+              "rope_theta": cfg.rope_theta, "torch_dtype": "float32", "tie_word_embeddings": False}
+        (d / "config.json").write_text(json.dumps(hf))
+        state = {}
+        for k, v in m.state_dict().items():               # back to Hugging Face names: split the fused projections
+            if k.endswith("qkv_proj.weight"):
+                q, kv = cfg.q_size, cfg.kv_size
+                for name, part in zip(("q_proj", "k_proj", "v_proj"), v.split([q, kv, kv], 0)):
+                    state[k.replace("qkv_proj", name)] = part.contiguous()
+            elif k.endswith("gate_up_proj.weight"):
+                for name, part in zip(("gate_proj", "up_proj"), v.chunk(2, 0)):
+                    state[k.replace("gate_up_proj", name)] = part.contiguous()
+            else:
+                state[k] = v
+        save_file(state, str(d / "model.safetensors"))
+        return str(d)
+
+    src_a, src_b = checkpoint(1, tmp_path / "a"), checkpoint(2, tmp_path / "b")
+    world = write_artifacts(src_a, str(tmp_path / "ea"), externalize_weights="lm_head,ffn")
+    write_artifacts(src_b, str(tmp_path / "eb"), externalize_weights=["lm_head", "ffn"])
+    ext = world["ranks"][0]["external"]
+    names = set(SafetensorsFile(str(tmp_path / "ea" / ext["weights"])).keys())
+    assert ext["kinds"] == ["ffn", "lm_head"] and "lm_head.weight" in names and all(xw.kind_of(n) in ("ffn", "lm_head") for n in names)
+    assert not (names & set(SafetensorsFile(str(tmp_path / "ea" / "rank0.safetensors")).keys()))
+    model_a = load_artifacts(str(tmp_path / "ea"), verify=True)
+    ref_a = AutoModel.from_pretrained(src_a)
+    for (k, v), (_, w) in zip(model_a.state_dict().items(), ref_a.state_dict().items()):
+        assert torch.equal(v, w), k
+    # the external file of another preparation, read from its directory
+    mixed = load_artifacts(str(tmp_path / "ea"), external_dir=str(tmp_path / "eb"))
+    ref_b = AutoModel.from_pretrained(src_b)
+    assert torch.equal(mixed.lm_head.weight, ref_b.lm_head.weight) and torch.equal(mixed.model.embed_tokens.weight, ref_a.model.embed_tokens.weight)
+    (tmp_path / "ea" / ext["weights"]).rename(tmp_path / "ea" / "moved.safetensors")
+    with pytest.raises(FileNotFoundError):
+        load_artifacts(str(tmp_path / "ea"))
+    (tmp_path / "ea" / "moved.safetensors").rename(tmp_path / "ea" / ext["weights"])
+
+    # refit a live LLM: outputs follow the new weights, addresses stay, the prefix cache starts a new generation
+    llm = LLM(str(tmp_path / "ea"), device="cpu", max_batch_size=2, max_input_len=128, max_kv_cache_capacity=192,
+              enable_in_flight_batching=True, enable_prefix_cache=True, page_size=16)
+    prompt = list(range(3, 40))
+    sp = SamplingParams(max_tokens=5, ignore_eos=True)
+    before = llm.generate([prompt], sp)[0].token_ids
+    ptr = llm.model.lm_head.weight.data_ptr()
+    stats = llm.refit(str(tmp_path / "eb" / ext["weights"]))
+    assert stats["tensors"] == len(names) and stats["kinds"] == ["ffn", "lm_head"] and llm.model.lm_head.weight.data_ptr() == ptr
+    reused0 = llm.engine.metrics().prefix_reused_tokens
+    after = llm.generate([prompt], sp)[0].token_ids
+    assert llm.engine.metrics().prefix_reused_tokens == reused0           # nothing cached under the old weights was adopted
+    kv = KVCacheManager(mixed.cfg, num_pages=16, page_size=16, max_seats=1, max_pages_per_seq=12)
+    runner = ModelRunner(mixed, kv)
+    first = runner.prefill([0], [prompt]).argmax(-1)
+    want = [int(first[0])] + runner.decode_greedy([0], first, 4)[0].tolist()
+    assert after == want and after != before
+    again = llm.generate([prompt], sp)[0].token_ids                        # the new generation is cached and reused
+    assert again == after and llm.engine.metrics().prefix_reused_tokens > reused0
+    with pytest.raises(KeyError):
+        llm.refit({"no.such.tensor": torch.zeros(1)})
+    with pytest.raises(ValueError):
+        llm.refit({"lm_head.weight": torch.zeros(3, 3)})
+    assert llm.generate([prompt], sp)[0].token_ids == after                # a refused refit changed nothing
+    llm.close()
