@@ -6,6 +6,8 @@
 // Reference counterparts: CuTe-DSL rmsnorm (kernelSrcs/rmsnorm_cutedsl/rmsnorm.py),
 // cpp/kernels/posEncoding/applyRopeWriteKV.cu, cpp/kernels/embeddingKernels/embeddingKernels.cu,
 // cpp/kernels/common/argmaxKernel.cu, cpp/kernels/moe/moeActivationKernels.cu.
+#include <cuda_fp8.h>
+
 #include "host_utils.h"
 #include "tc5_common.cuh"
 
@@ -246,6 +248,45 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
     const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)id * hidden);
     uint4* dst = reinterpret_cast<uint4*>(out + row * hidden);
     for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// Embedding rows stored in FP8 (E4M3 bytes with one fp32 scale per row) or NVFP4 (two E2M1 codes per byte, low nibble first, one
+// E4M3 scale per 16 values, one fp32 scale for the table) and expanded while they are gathered.  One CTA per looked-up row.
+// FMT 0: FP8, FMT 1: NVFP4.  `scale` is fp32 [vocab] (FP8) or E4M3 bytes [vocab, hidden / 16] (NVFP4).
+template <typename T, int FMT>
+__global__ void embedding_quant_kernel(const int* __restrict__ ids, const uint8_t* __restrict__ data, const void* __restrict__ scale,
+                                       const float* __restrict__ global_scale, T* __restrict__ out, int hidden, int vocab) {
+    pdl_prologue();
+    const size_t row = blockIdx.x;
+    int id = ids[row];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    T* dst = out + row * hidden;
+    if constexpr (FMT == 0) {
+        const float s = reinterpret_cast<const float*>(scale)[id];
+        const uint8_t* src = data + (size_t)id * hidden;
+        for (int i = threadIdx.x * 2; i < hidden; i += blockDim.x * 2) {
+            const float a = __half2float(__half(__nv_cvt_fp8_to_halfraw(src[i], __NV_E4M3))) * s;
+            const float b = __half2float(__half(__nv_cvt_fp8_to_halfraw(src[i + 1], __NV_E4M3))) * s;
+            *reinterpret_cast<uint32_t*>(dst + i) = Cvt<T>::pack2(a, b);
+        }
+    } else {
+        const float gs = *global_scale;
+        const uint8_t* src = data + (size_t)id * (hidden / 2);
+        const uint8_t* sf = reinterpret_cast<const uint8_t*>(scale) + (size_t)id * (hidden / 16);
+        for (int i = threadIdx.x; i < hidden / 2; i += blockDim.x) {
+            const uint8_t byte = src[i];
+            const float bs = __half2float(__half(__nv_cvt_fp8_to_halfraw(sf[i >> 3], __NV_E4M3))) * gs;
+            float v[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int code = (byte >> (4 * h)) & 0xF;
+                const int m = code & 7;
+                const float mag = m < 2 ? 0.5f * m : (m < 4 ? 0.5f * m : (m == 4 ? 2.f : (m == 5 ? 3.f : (m == 6 ? 4.f : 6.f))));
+                v[h] = (code & 8) ? -mag : mag;
+            }
+            *reinterpret_cast<uint32_t*>(dst + 2 * i) = Cvt<T>::pack2(v[0] * bs, v[1] * bs);
+        }
+    }
 }
 
 // RoPE + optional per-head RMSNorm on q and k + paged KV write.
@@ -676,6 +717,23 @@ extern "C" int telb_embedding(const int* ids, const void* table, void* out, long
     if (hidden % 8) return fail("telb_embedding: hidden must be a multiple of 8");
     DISPATCH_T(is_bf16, { TELB_LAUNCH("embedding_kernel", (embedding_kernel<T>), dim3((unsigned)rows), dim3(128), 0, stream, ids, (const T*)table, (T*)out, hidden, vocab); })
     TELB_CHECK_LAUNCH("embedding_kernel");
+    return 0;
+}
+
+// fmt 0: data [vocab, hidden] E4M3, scale fp32 [vocab]; fmt 1: data [vocab, hidden / 2] packed E2M1, scale E4M3 [vocab, hidden / 16],
+// global_scale fp32 [1].  out [rows, hidden] 16-bit.
+extern "C" int telb_embedding_quant(const int* ids, const void* data, const void* scale, const float* global_scale, void* out, long long rows,
+                                    int hidden, int vocab, int fmt, int is_bf16, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (fmt != 0 && fmt != 1) return fail("telb_embedding_quant: format 0 (fp8) or 1 (nvfp4)");
+    if (hidden % 16) return fail("telb_embedding_quant: hidden must be a multiple of 16");
+    if (fmt == 1 && global_scale == nullptr) return fail("telb_embedding_quant: NVFP4 tables carry a global scale");
+    if (fmt == 0) {
+        DISPATCH_T(is_bf16, { TELB_LAUNCH("embedding_quant_kernel", (embedding_quant_kernel<T, 0>), dim3((unsigned)rows), dim3(128), 0, stream, ids, (const uint8_t*)data, scale, global_scale, (T*)out, hidden, vocab); })
+    } else {
+        DISPATCH_T(is_bf16, { TELB_LAUNCH("embedding_quant_kernel", (embedding_quant_kernel<T, 1>), dim3((unsigned)rows), dim3(128), 0, stream, ids, (const uint8_t*)data, scale, global_scale, (T*)out, hidden, vocab); })
+    }
+    TELB_CHECK_LAUNCH("embedding_quant_kernel");
     return 0;
 }
 

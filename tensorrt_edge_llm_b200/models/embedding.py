@@ -78,6 +78,10 @@ class QuantizedEmbedding(nn.Module):
         return sum(b.numel() * b.element_size() for b in self.buffers())
 
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        if self.data.is_cuda and self.out_dtype in (torch.float16, torch.bfloat16) and self.embedding_dim % 16 == 0:
+            from ..ops import cuda as cu           # one kernel: gather and expand (csrc/kernels/elementwise.cu)
+            out = cu.embedding_quant(ids.reshape(-1), self.data, self.scale, getattr(self, "global_scale", None), self.fmt, self.out_dtype)
+            return out.reshape(*ids.shape, self.embedding_dim)
         idx = ids.long()
         if self.fmt == "fp8":
             return (self.data[idx].float() * self.scale[idx][:, None]).to(self.out_dtype)

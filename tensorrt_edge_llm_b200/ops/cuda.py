@@ -202,6 +202,20 @@ def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def embedding_quant(ids, data, scale, global_scale, fmt: str, out_dtype) -> torch.Tensor:
+    """Gather rows of an FP8 (``data [V, H]`` E4M3, ``scale [V]`` fp32) or NVFP4 (``data [V, H / 2]``, ``scale [V, H / 16]`` E4M3,
+    ``global_scale``) embedding table and expand them to ``out_dtype`` in the same kernel."""
+    assert out_dtype in (torch.float16, torch.bfloat16) and fmt in ("fp8", "nvfp4")
+    ids = ids.to(torch.int32).contiguous()
+    hidden = data.shape[1] * (2 if fmt == "nvfp4" else 1)
+    out = torch.empty(ids.numel(), hidden, dtype=out_dtype, device=data.device)
+    d, sc = data.contiguous(), scale.contiguous()
+    gs = None if global_scale is None else global_scale.reshape(-1).float().contiguous()
+    _check(lib().telb_embedding_quant(_p(ids), _p(d), _p(sc), _p(gs), _p(out), c_ll(ids.numel()), c_int(hidden), c_int(data.shape[0]),
+                                      c_int(1 if fmt == "nvfp4" else 0), c_int(int(out_dtype == torch.bfloat16)), _stream()), "embedding_quant")
+    return out
+
+
 def gemm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
          alpha: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
          out: Optional[torch.Tensor] = None, mode: int = 0, splits: int = 0) -> torch.Tensor:

@@ -648,3 +648,21 @@ def test_token_logprobs_kernel(dtype, rows, vocab, k):
     wide[:, :vocab] = logits.cuda()
     again = cu.token_logprobs(wide[:, :vocab], tokens.cuda(), k)
     assert torch.allclose(again[0], got[0]) and torch.equal(again[1], got[1])
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("fmt", ["fp8", "nvfp4"])
+def test_quantized_embedding_gather_kernel(fmt, dtype):
+    """Gather + expand of FP8 / NVFP4 embedding rows in one kernel against the torch expansion of the same stored table."""
+    from tensorrt_edge_llm_b200.models.embedding import QuantizedEmbedding
+    g = torch.Generator().manual_seed(3)
+    table = (torch.randn(1000, 256, generator=g) * 0.05).to(dtype)
+    emb = QuantizedEmbedding.from_dense(table, fmt)
+    ids = torch.randint(0, 1000, (3, 17), generator=g)
+    want = emb(ids)                                           # CPU: torch ops
+    got = emb.cuda()(ids.cuda())
+    assert got.shape == (3, 17, 256) and got.dtype == dtype
+    assert torch.allclose(got.float().cpu(), want.float(), atol=1e-3, rtol=1e-2)
+    assert torch.allclose(got.float().cpu(), table[ids].float(), atol=0.02 if fmt == "nvfp4" else 5e-3)
+    out_of_range = emb.cuda()(torch.tensor([-5, 5000]).cuda())      # clamped like the dense gather
+    assert torch.equal(out_of_range[0], emb.cuda()(torch.tensor([0]).cuda())[0]) and torch.equal(out_of_range[1], emb.cuda()(torch.tensor([999]).cuda())[0])
