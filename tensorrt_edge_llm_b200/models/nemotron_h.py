@@ -51,6 +51,20 @@ class RecurrentState:
         for d in (self.conv, self.ssm, self.gdn):
             yield from d.values()
 
+    # ---- replay data -------------------------------------------------------------------------------------------------
+    # A speculative verification step advances every state over the whole draft chain.  While ``record`` is a dict the mixers
+    # also keep the inputs of their recurrent kernels for that step (a few KB per token and layer); when only a prefix of
+    # the chain is accepted, ``HybridCausalLM.replay_recurrent`` restores the saved rows and runs *only the recurrent kernels*
+    # over the accepted tokens again from those inputs: no projections, no attention, no MLP.
+    record = None
+
+    def begin_record(self) -> None:
+        self.record = {}
+
+    def end_record(self):
+        rec, self.record = self.record, None
+        return rec
+
     def snapshot(self, seats) -> list:
         """Copies of the state rows of ``seats`` (the commit policy of speculative verification restores them when a
         draft chain is only partly accepted; ``cpp/runtime/commitPolicy/`` in the reference)."""
@@ -130,6 +144,8 @@ class MambaMixer(nn.Module):
         m = self.m
         proj = self.in_proj(x)
         z, xbc, dt = proj.split([self.d_inner, self.d_inner + 2 * self.bc, self.nheads], dim=-1)
+        if state.record is not None:
+            state.record[layer_idx] = (xbc.contiguous(), dt.contiguous())
         xbc = ops.causal_conv1d(xbc.contiguous(), self.conv_weight, self.conv_bias, state.conv[layer_idx], meta, activation=True)
         xs, B, C = xbc.split([self.d_inner, self.bc, self.bc], dim=-1)
         t = x.shape[0]
@@ -138,6 +154,19 @@ class MambaMixer(nn.Module):
                          state.ssm[layer_idx], meta, z=None, dt_softplus=True, dt_limit=m.dt_limit)
         y = ops.gated_group_rmsnorm(y.reshape(t, self.d_inner), z.contiguous(), self.norm_weight, self.groups, self.eps)
         return self.out_proj(y)
+
+
+    @torch.no_grad()
+    def replay(self, saved, rows: torch.Tensor, meta: StepMeta, state: RecurrentState, layer_idx: int) -> None:
+        """Advance this layer's convolution and SSM state over the recorded inputs of ``rows`` (the accepted tokens)."""
+        m = self.m
+        xbc, dt = (t.index_select(0, rows) for t in saved)
+        xbc = ops.causal_conv1d(xbc, self.conv_weight, self.conv_bias, state.conv[layer_idx], meta, activation=True)
+        xs, B, C = xbc.split([self.d_inner, self.bc, self.bc], dim=-1)
+        t = xbc.shape[0]
+        ops.ssm_scan(xs.reshape(t, self.nheads, m.head_dim), dt, -torch.exp(self.A_log), B.reshape(t, self.groups, m.d_state),
+                     C.reshape(t, self.groups, m.d_state), self.D, self.dt_bias, state.ssm[layer_idx], meta, z=None, dt_softplus=True,
+                     dt_limit=m.dt_limit)
 
 
 class GatedDeltaNetMixer(nn.Module):
@@ -195,6 +224,8 @@ class GatedDeltaNetMixer(nn.Module):
         z = self.in_proj_z(x)
         b = self.in_proj_b(x)
         a = self.in_proj_a(x)
+        if state.record is not None:
+            state.record[layer_idx] = (qkv.contiguous(), a.contiguous(), b.contiguous())
         qkv = ops.causal_conv1d(qkv, self.conv_weight, None, state.conv[layer_idx], meta, activation=True)
         q, k, v = qkv.split([self.key_dim, self.key_dim, self.value_dim], dim=-1)
         o = ops.gated_delta_rule(q.reshape(t, self.hk, g.head_k_dim), k.reshape(t, self.hk, g.head_k_dim),
@@ -204,6 +235,17 @@ class GatedDeltaNetMixer(nn.Module):
         zf = z.float()
         o = (o.float() * (zf * torch.sigmoid(zf))).to(x.dtype)
         return self.out_proj(o)
+
+
+    @torch.no_grad()
+    def replay(self, saved, rows: torch.Tensor, meta: StepMeta, state: RecurrentState, layer_idx: int) -> None:
+        g = self.g
+        qkv, a, b = (t.index_select(0, rows) for t in saved)
+        qkv = ops.causal_conv1d(qkv, self.conv_weight, None, state.conv[layer_idx], meta, activation=True)
+        q, k, v = qkv.split([self.key_dim, self.key_dim, self.value_dim], dim=-1)
+        t = qkv.shape[0]
+        ops.gated_delta_rule(q.reshape(t, self.hk, g.head_k_dim), k.reshape(t, self.hk, g.head_k_dim), v.reshape(t, self.hv, g.head_v_dim),
+                             a, b, self.A_log, self.dt_bias, state.gdn[layer_idx], meta)
 
 
 class HybridLayer(nn.Module):
@@ -279,3 +321,17 @@ class HybridTransformer(nn.Module):
 class HybridCausalLM(CausalLM):
     transformer_cls = HybridTransformer
     needs_cache_set = True      # forward takes the cache manager (KV + recurrent pools), not the bare KV pool
+
+    @torch.no_grad()
+    def replay_recurrent(self, record: dict, rows: torch.Tensor, meta: StepMeta, cache) -> int:
+        """Advance the recurrent state of every Mamba / DeltaNet layer over the recorded kernel inputs of ``rows`` (row indices into
+        the recorded step, grouped by sequence as ``meta`` describes).  The caller has restored the state rows of those sequences
+        to what they were before the recorded step.  Returns the number of layers replayed.  This is the commit of a partly
+        accepted draft chain on a hybrid target: two small kernels per recurrent layer instead of a second pass through the
+        whole model (the reference's per-layer replay data, ``cpp/runtime/commitPolicy``, ``mtpStateScatterKernels``)."""
+        n = 0
+        for layer in self.model.layers:
+            if layer.kind in (LAYER_MAMBA, LAYER_GDN) and layer.idx in record:
+                layer.mixer.replay(record[layer.idx], rows, meta, cache.recurrent, layer.idx)
+                n += 1
+        return n

@@ -59,6 +59,7 @@ class SpecStats:
     emitted: int = 0
     draft_forwards: int = 0
     replays: int = 0                 # hybrid targets: sequences whose recurrent state was restored and replayed
+    recurrent_replays: int = 0       # ... of which from recorded kernel inputs (recurrent kernels only, no second model pass)
 
     @property
     def mean_accept_length(self) -> float:
@@ -322,6 +323,9 @@ class EagleDecoder:
         tree_tok, tree_par, tree_dep = ops.eagle_select_verify(p_sc, p_tok, p_par, p_dep, root, keep)
         tmask, _, pos = ops.eagle_tree_meta(tree_par, lt_dev, 0, 0)
         state_before = self.r.kv.recurrent.snapshot(seats) if self.hybrid else None
+        can_record = self.hybrid and hasattr(self.model, "replay_recurrent") and getattr(self, "use_recurrent_replay", True)
+        if can_record:
+            self.r.kv.recurrent.begin_record()          # the mixers keep their recurrent-kernel inputs of the verification pass
         greedy = self.sampling is None
         if self._graph_verify_ok(greedy):
             # fixed (batch, tree size) and a tree that already lives on the device: the whole target pass replays from a graph
@@ -352,15 +356,23 @@ class EagleDecoder:
         path_h, plen_h, bonus_h = path.tolist(), plen.tolist(), bonus.tolist()   # the round's one device→host read
         tok_h = tree_tok.tolist()
         if self.hybrid:
-            # commit policy: the recurrent state now holds all nn_ chain tokens; seats that accepted fewer get their
-            # saved rows back and the accepted prefix is run again (KV rows are rewritten with the same values)
+            # commit policy: the recurrent state now holds all nn_ chain tokens; seats that accepted fewer get their saved rows
+            # back and the state is advanced over the accepted prefix again — from the recorded kernel inputs of the verification
+            # pass (recurrent kernels only), or, without a record, by running the prefix through the model once more (KV rows
+            # are rewritten with the same values)
+            record = self.r.kv.recurrent.end_record() if can_record else None
             short = [i for i in range(b) if plen_h[i] < nn_]
             if short:
                 self.r.kv.recurrent.restore(seats, state_before, short)
                 sub = [seats[i] for i in short]
-                rows = torch.tensor([t for i in short for t in tok_h[i][:plen_h[i]]], dtype=torch.int32, device=dev)
                 meta = self.r._meta(sub, [plen_h[i] for i in short], logits_all=False)
-                self.model.hidden_states(rows, meta, self.r.cache)
+                if record:
+                    idx = torch.tensor([i * nn_ + j for i in short for j in range(plen_h[i])], dtype=torch.long, device=dev)
+                    self.model.replay_recurrent(record, idx, meta, self.r.cache)
+                    self.stats.recurrent_replays += len(short)
+                else:
+                    rows = torch.tensor([t for i in short for t in tok_h[i][:plen_h[i]]], dtype=torch.int32, device=dev)
+                    self.model.hidden_states(rows, meta, self.r.cache)
                 self.stats.replays += len(short)
         out: List[List[int]] = []
         acc_rows, acc_tok, q_lens = [], [], []

@@ -196,7 +196,19 @@ def test_hybrid_target_chain_verify_with_state_replay():
         _decoder(model, draft, SpecConfig(draft_steps=3, top_k=2, verify_tokens=8))
     # random draft: almost every chain is cut short, so nearly every round replays
     dec = _decoder(model, draft, SpecConfig(draft_steps=3, top_k=1, verify_tokens=4))
+    passes = []
+    orig = model.hidden_states
+    model.hidden_states = lambda *a, **k: (passes.append(1), orig(*a, **k))[1]
     assert dec.generate([0, 1], prompts, 14) == want and dec.stats.replays > 0
+    # every replay ran from the recorded kernel inputs: one model pass per prefill / verification round, none for a commit
+    assert dec.stats.recurrent_replays == dec.stats.replays
+    with_record = len(passes)
+    # the fallback (no record): the accepted prefix goes through the whole model again, same tokens, more passes
+    dec = _decoder(model, draft, SpecConfig(draft_steps=3, top_k=1, verify_tokens=4))
+    dec.use_recurrent_replay = False
+    passes.clear()
+    assert dec.generate([0, 1], prompts, 14) == want and dec.stats.recurrent_replays == 0 and len(passes) > with_record
+    model.hidden_states = orig
     # oracle draft: whole chains are accepted, no replay until the streams end
     streams = {i: prompts[i] + want[i] for i in range(2)}
     dec = _decoder(model, _OracleDraft(draft, streams), SpecConfig(draft_steps=3, top_k=1, verify_tokens=4))
