@@ -84,7 +84,7 @@ class QuantizedEmbedding(nn.Module):
             return out.reshape(*ids.shape, self.embedding_dim)
         idx = ids.long()
         if self.fmt == "fp8":
-            return (self.data[idx].float() * self.scale[idx][:, None]).to(self.out_dtype)
+            return (self.data[idx].float() * self.scale[idx][..., None]).to(self.out_dtype)
         return ref.nvfp4_dequantize(self.data[idx], self.scale[idx], self.global_scale).to(self.out_dtype)
 
 

@@ -319,3 +319,44 @@ def test_spec_accept_sampling_kernel(cu, b, n, v, k):
     got = cu.spec_accept_sampling(pr.cuda(), torch.tensor([[0, 4]], dtype=torch.int32).cuda(), torch.tensor([[-1, 0]], dtype=torch.int32).cuda(), 4,
                                   torch.full((1, 4, 3), 0.9).cuda())
     assert got[1].tolist() == [1] and got[2].tolist() == [9]
+
+
+def test_hybrid_chain_commit_from_replay_data_on_gpu(cu):
+    """Mamba2 / DeltaNet target on the GPU: a forced partial acceptance every round commits through the recorded recurrent-kernel
+    inputs; the recurrent state afterwards equals the one left by the full-model replay of the same accepted tokens."""
+    from tensorrt_edge_llm_b200 import AutoModel
+    from tensorrt_edge_llm_b200.config import GdnConfig, MambaConfig, hybrid_nemotron_config, tiny_llama_config
+    from tensorrt_edge_llm_b200.runtime.kv_cache import KVCacheManager
+    from tensorrt_edge_llm_b200.runtime.runner import ModelRunner
+    from tensorrt_edge_llm_b200.runtime.speculative import EagleDecoder, SpecConfig
+    dev = torch.device("cuda", 0)
+    cfg = hybrid_nemotron_config(num_hidden_layers=8, vocab_size=1000, hidden_size=512, intermediate_size=1024, num_attention_heads=8,
+                                 num_key_value_heads=2, head_dim=128, dtype="bfloat16", max_position_embeddings=1024,
+                                 mamba=MambaConfig(num_heads=8, head_dim=64, d_state=128, n_groups=2, conv_kernel=4),
+                                 gdn=GdnConfig(num_k_heads=2, num_v_heads=4, head_k_dim=128, head_v_dim=128, conv_kernel=4))
+    model = AutoModel.from_config(cfg, random_init=0, device=dev)
+    dcfg = tiny_llama_config(num_hidden_layers=1, hidden_size=512, intermediate_size=1024, num_attention_heads=8, num_key_value_heads=2,
+                             head_dim=128, vocab_size=1000, dtype="bfloat16")
+    dcfg.draft_type, dcfg.eagle3_target_hidden_size = "eagle3", 512
+    draft = AutoModel.from_config(dcfg, random_init=2, device=dev)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (40, 75)]
+
+    def run(use_record):
+        kv = KVCacheManager(cfg, num_pages=16, page_size=64, max_seats=4, max_pages_per_seq=4, device=dev)
+        dkv = KVCacheManager(dcfg, num_pages=16, page_size=64, max_seats=4, max_pages_per_seq=4, device=dev, num_layers=1)
+        r = ModelRunner(model, kv, max_num_tokens=8192)
+        r.use_cuda_graphs = False
+        dec = EagleDecoder(r, draft, dkv, SpecConfig(draft_steps=3, top_k=1, verify_tokens=4, force_accept_len=2))
+        dec.use_recurrent_replay = use_record
+        dec.prefill([0, 1], prompts)
+        out = [dec.round([0, 1]) for _ in range(5)]
+        torch.cuda.synchronize()
+        return out, [t.index_select(0, torch.tensor([0, 1], device=dev)).float().cpu() for t in kv.recurrent.pools()], dec.stats
+
+    out_a, state_a, stats_a = run(True)
+    out_b, state_b, stats_b = run(False)
+    assert stats_a.recurrent_replays == stats_a.replays == 10 and stats_b.recurrent_replays == 0 and stats_b.replays == 10
+    assert out_a == out_b
+    for x, y in zip(state_a, state_b):
+        assert torch.allclose(x, y, atol=2e-2, rtol=2e-2)
