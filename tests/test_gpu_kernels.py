@@ -663,6 +663,6 @@ def test_quantized_embedding_gather_kernel(fmt, dtype):
     got = emb.cuda()(ids.cuda())
     assert got.shape == (3, 17, 256) and got.dtype == dtype
     assert torch.allclose(got.float().cpu(), want.float(), atol=1e-3, rtol=1e-2)
-    assert torch.allclose(got.float().cpu(), table[ids].float(), atol=0.02 if fmt == "nvfp4" else 5e-3)
+    assert torch.allclose(got.float().cpu(), table[ids].float(), atol=0.03 if fmt == "nvfp4" else 0.02)
     out_of_range = emb.cuda()(torch.tensor([-5, 5000]).cuda())      # clamped like the dense gather
     assert torch.equal(out_of_range[0], emb.cuda()(torch.tensor([0]).cuda())[0]) and torch.equal(out_of_range[1], emb.cuda()(torch.tensor([999]).cuda())[0])
