@@ -832,13 +832,44 @@ __global__ void argmax_split_kernel(const T* __restrict__ logits, int* __restric
     const int lo = blockIdx.x * per, hi = min(vocab, lo + per);
     const T* p = logits + row * stride;
     unsigned long long best = 0ull;
-    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-        float v;
-        if constexpr (sizeof(T) == 4) v = (float)p[i]; else v = Cvt<T>::to_f(p[i]);
+    auto consider = [&](float v, int i) {
         uint32_t u = __float_as_uint(v);
         u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
         const unsigned long long key = ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)i);
         best = key > best ? key : best;
+    };
+    if constexpr (sizeof(T) == 2) {
+        // 16-byte loads over the aligned middle of the segment (8 values each); the ragged ends go one value at a time
+        const bool vec_ok = (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+        const int a0 = vec_ok ? min(hi, (lo + 7) & ~7) : hi;
+        const int a1 = vec_ok ? max(a0, hi & ~7) : hi;
+        for (int i = lo + threadIdx.x; i < a0; i += blockDim.x) consider(Cvt<T>::to_f(p[i]), i);
+        for (int c = a0 / 8 + threadIdx.x; c < a1 / 8; c += blockDim.x) {
+            const uint4 q = __ldg(reinterpret_cast<const uint4*>(p) + c);
+            const T* e = reinterpret_cast<const T*>(&q);
+            float bv = Cvt<T>::to_f(e[0]);
+            int bi = 0;
+#pragma unroll
+            for (int j = 1; j < 8; ++j) {
+                const float v = Cvt<T>::to_f(e[j]);
+                if (v > bv) {               // strict: the first of equal values keeps the lower index
+                    bv = v;
+                    bi = j;
+                }
+            }
+            bool has_nan = false;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) has_nan = has_nan || !(Cvt<T>::to_f(e[j]) == Cvt<T>::to_f(e[j]));
+            if (has_nan) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) consider(Cvt<T>::to_f(e[j]), c * 8 + j);      // keys order NaN like the scalar path does
+            } else {
+                consider(bv, c * 8 + bi);
+            }
+        }
+        for (int i = a1 + threadIdx.x; i < hi; i += blockDim.x) consider(Cvt<T>::to_f(p[i]), i);
+    } else {
+        for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) consider((float)p[i], i);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
