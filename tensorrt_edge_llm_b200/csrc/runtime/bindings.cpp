@@ -103,6 +103,12 @@ PYBIND11_MODULE(_telb_runtime, m) {
     py::class_<PrefixCache::Match>(m, "PrefixMatch")
         .def_readonly("pages", &PrefixCache::Match::pages)
         .def_readonly("tokens", &PrefixCache::Match::tokens);
+    py::class_<PrefixCache::EvictionPlan>(m, "EvictionPlan")
+        .def_readonly("pages_wanted", &PrefixCache::EvictionPlan::pages_wanted)
+        .def_readonly("reclaimable_pages", &PrefixCache::EvictionPlan::reclaimable_pages)
+        .def_readonly("pinned_skipped", &PrefixCache::EvictionPlan::pinned_skipped)
+        .def_readonly("satisfied", &PrefixCache::EvictionPlan::satisfied)
+        .def_readonly("victims", &PrefixCache::EvictionPlan::victims);
     py::class_<PrefixCache>(m, "PrefixCache")
         .def(py::init<PageAllocator&, int, int>(), py::arg("allocator"), py::arg("page_size"), py::arg("max_records") = 1024,
              py::keep_alive<1, 2>())
@@ -111,7 +117,10 @@ PYBIND11_MODULE(_telb_runtime, m) {
         .def_property_readonly("check_mismatches", &PrefixCache::check_mismatches)
         .def_static("extras_seed", &PrefixCache::extras_seed, py::arg("adapter") = "", py::arg("adapter_generation") = 0,
                     py::arg("isolation_key") = "")
-        .def("evict", &PrefixCache::evict)
+        .def("evict", [](PrefixCache& c, int pages_wanted) { return c.evict(pages_wanted); })
+        .def("evict_plan", [](PrefixCache& c, const PrefixCache::EvictionPlan& p) { return c.evict(p); })
+        .def("plan_eviction", &PrefixCache::plan_eviction)
+        .def("drop_records", &PrefixCache::drop_records)
         .def_property_readonly("records", &PrefixCache::records)
         .def_property_readonly("hits", &PrefixCache::hits)
         .def_property_readonly("misses", &PrefixCache::misses)

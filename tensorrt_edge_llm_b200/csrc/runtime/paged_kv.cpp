@@ -192,6 +192,7 @@ PrefixCache::Match PrefixCache::lookup(const std::vector<int32_t>& tokens, uint6
     Match m;
     const int full = (static_cast<int>(tokens.size()) - 1) / page_size_;   // leave >= 1 token to compute
     uint64_t parent = seed, check = seed;
+    std::vector<std::list<uint64_t>::iterator> chain;
     for (int b = 0; b < full; ++b) {
         const int32_t* blk = tokens.data() + static_cast<size_t>(b) * page_size_;
         const uint64_t h = hash_block(parent, blk, page_size_);
@@ -202,19 +203,27 @@ PrefixCache::Match PrefixCache::lookup(const std::vector<int32_t>& tokens, uint6
             ++mismatches_;
             break;
         }
-        lru_.splice(lru_.begin(), lru_, it->second.lru);
+        chain.push_back(it->second.lru);
         m.pages.push_back(it->second.page);
         m.tokens += page_size_;
         parent = h;
     }
+    touch_chain(chain);
     if (m.tokens > 0) ++hits_; else ++misses_;
     return m;
+}
+
+// Mark a chain of entries (given root first) as just used, leaves first: the root ends up the most recent of them, so eviction
+// from the old end of the list takes a chain's tail pages before the pages every continuation of the prefix depends on.
+void PrefixCache::touch_chain(const std::vector<std::list<uint64_t>::iterator>& chain) {
+    for (auto it = chain.rbegin(); it != chain.rend(); ++it) lru_.splice(lru_.begin(), lru_, *it);
 }
 
 int PrefixCache::insert(const std::vector<int32_t>& tokens, int filled_tokens, const std::vector<int32_t>& pages, uint64_t seed) {
     const int full = std::min<int>(filled_tokens, static_cast<int>(tokens.size())) / page_size_;
     uint64_t parent = seed, check = seed;
     int added = 0;
+    std::vector<std::list<uint64_t>::iterator> chain;
     for (int b = 0; b < full && b < static_cast<int>(pages.size()); ++b) {
         const int32_t* blk = tokens.data() + static_cast<size_t>(b) * page_size_;
         const uint64_t h = hash_block(parent, blk, page_size_);
@@ -226,31 +235,74 @@ int PrefixCache::insert(const std::vector<int32_t>& tokens, int filled_tokens, c
                 ++mismatches_;
                 break;
             }
-            lru_.splice(lru_.begin(), lru_, it->second.lru);
+            chain.push_back(it->second.lru);
             continue;
         }
-        if (static_cast<int>(map_.size()) >= max_records_ && evict(1) == 0) break;
+        if (static_cast<int>(map_.size()) >= max_records_) {
+            // at the record limit: drop the oldest record that is not part of the chain being registered
+            touch_chain(chain);
+            chain.clear();
+            if (drop_records(1) == 0) break;
+        }
         alloc_.retain({pages[b]});
         lru_.push_front(h);
         map_[h] = Entry{pages[b], check, lru_.begin()};
+        chain.push_back(lru_.begin());
         ++added;
     }
+    touch_chain(chain);
     return added;
 }
 
-int PrefixCache::evict(int pages_wanted) {
-    int released = 0;
-    while (released < pages_wanted && !lru_.empty()) {
+int PrefixCache::drop_records(int n) {
+    int dropped = 0;
+    while (dropped < n && !lru_.empty()) {
         const uint64_t h = lru_.back();
         lru_.pop_back();
         auto it = map_.find(h);
         if (it != map_.end()) {
             alloc_.release({it->second.page});
             map_.erase(it);
-            ++released;
+            ++dropped;
         }
     }
-    return released;
+    return dropped;
 }
+
+// Read-only simulation: walk the records from least to most recently used; a record's page comes back to the pool only when the
+// cache holds the last reference (no resident sequence shares it).  The plan is the shortest such run of victims that covers
+// the demand; records whose pages are still shared are passed over, since dropping them frees nothing and loses the entry.
+PrefixCache::EvictionPlan PrefixCache::plan_eviction(int pages_wanted) const {
+    EvictionPlan plan;
+    plan.pages_wanted = pages_wanted;
+    for (auto it = lru_.rbegin(); it != lru_.rend() && plan.reclaimable_pages < pages_wanted; ++it) {
+        auto e = map_.find(*it);
+        if (e == map_.end()) continue;
+        if (alloc_.refcount(e->second.page) == 1) {
+            plan.victims.push_back(*it);
+            ++plan.reclaimable_pages;
+        } else {
+            ++plan.pinned_skipped;
+        }
+    }
+    plan.satisfied = plan.reclaimable_pages >= pages_wanted;
+    return plan;
+}
+
+// Carry out a plan (records that vanished or became shared since it was made are passed over).  Returns the pages freed.
+int PrefixCache::evict(const EvictionPlan& plan) {
+    int freed = 0;
+    for (uint64_t h : plan.victims) {
+        auto it = map_.find(h);
+        if (it == map_.end() || alloc_.refcount(it->second.page) != 1) continue;
+        alloc_.release({it->second.page});
+        lru_.erase(it->second.lru);
+        map_.erase(it);
+        ++freed;
+    }
+    return freed;
+}
+
+int PrefixCache::evict(int pages_wanted) { return evict(plan_eviction(pages_wanted)); }
 
 }  // namespace telb

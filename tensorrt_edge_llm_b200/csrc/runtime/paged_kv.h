@@ -118,7 +118,21 @@ class PrefixCache {
     Match lookup(const std::vector<int32_t>& tokens, uint64_t seed = 0);
     // Register the first `filled_tokens` (whole pages only) of a sequence whose pages are `pages`.
     int insert(const std::vector<int32_t>& tokens, int filled_tokens, const std::vector<int32_t>& pages, uint64_t seed = 0);
-    int evict(int pages_wanted);          // returns pages released
+    // Eviction is planned before it is carried out.  A plan is the shortest run of least-recently-used records whose pages
+    // would actually return to the pool (the cache holds their last reference); records whose pages a resident sequence still
+    // shares are passed over.  Chains are touched leaves-first, so a prefix's later pages go before the pages every
+    // continuation depends on.
+    struct EvictionPlan {
+        int pages_wanted = 0;
+        int reclaimable_pages = 0;
+        int pinned_skipped = 0;           // records passed over because their page is shared with a resident sequence
+        bool satisfied = false;
+        std::vector<uint64_t> victims;    // block hashes, least recently used first
+    };
+    EvictionPlan plan_eviction(int pages_wanted) const;
+    int evict(const EvictionPlan& plan);  // returns pages freed
+    int evict(int pages_wanted);          // plan + evict; returns pages freed (0: nothing reclaimable)
+    int drop_records(int n);              // forget the n oldest records whatever their pages' state (record-count limit)
     int records() const { return static_cast<int>(map_.size()); }
     uint64_t hits() const { return hits_; }
     uint64_t misses() const { return misses_; }
@@ -130,6 +144,7 @@ class PrefixCache {
         uint64_t check;
         std::list<uint64_t>::iterator lru;
     };
+    void touch_chain(const std::vector<std::list<uint64_t>::iterator>& chain);
     PageAllocator& alloc_;
     int page_size_, max_records_;
     std::unordered_map<uint64_t, Entry> map_;

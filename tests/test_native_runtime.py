@@ -384,3 +384,42 @@ def test_kernel_library_load_failure_is_loud(monkeypatch):
         cu.lib()
     monkeypatch.delenv("TELB_TEST_FAIL_KERNEL_LIBRARY")
     assert cu.lib() is not None
+
+
+def test_prefix_cache_eviction_planner_and_chain_order():
+    """Eviction is planned read-only first: only pages whose last reference is the cache's count, shared pages are passed over,
+    and a chain's later pages go before the pages every continuation of the prefix depends on."""
+    t = rt.KVPageTable(num_pages=12, page_size=4, max_seats=3, max_pages_per_seq=6)
+    cache = rt.PrefixCache(t.allocator(), 4, 16)
+    a = list(range(100, 117))                       # 17 tokens: 4 full pages
+    t.reserve(0, 17)
+    assert cache.insert(a, 16, t.pages(0)) == 4
+    pages_a = list(t.pages(0))
+    t.free_seat(0)                                  # the cache now holds the only reference on 4 pages
+    b = a[:8] + list(range(200, 209))               # shares the first two pages, then diverges
+    m = cache.lookup(b)
+    assert m.tokens == 8 and m.pages == pages_a[:2]
+    t.adopt_prefix(1, m.pages, m.tokens)            # a resident sequence shares pages 0 and 1
+    free0 = t.free_pages
+    # read-only plan: pages 2 and 3 of chain a (its leaves) are reclaimable, the shared ones are passed over
+    plan = cache.plan_eviction(3)
+    assert plan.reclaimable_pages == 2 and not plan.satisfied and plan.pinned_skipped == 2 and len(plan.victims) == 2
+    assert cache.records == 4 and t.free_pages == free0                    # nothing changed
+    plan1 = cache.plan_eviction(1)
+    assert plan1.satisfied and len(plan1.victims) == 1
+    assert cache.evict_plan(plan1) == 1 and t.free_pages == free0 + 1 and cache.records == 3
+    # the victim was the chain's last page: the first three pages still match
+    assert cache.lookup(a).tokens == 12
+    # evict(n) returns pages actually freed and never drops records that would free nothing
+    assert cache.evict(5) == 1 and cache.records == 2 and t.free_pages == free0 + 2
+    assert cache.evict(5) == 0 and cache.records == 2
+    assert cache.lookup(a).tokens == 8                                     # the shared root pages are still indexed
+    t.free_seat(1)
+    assert cache.evict(5) == 2 and cache.records == 0 and t.free_pages == 12
+    # a stale plan is harmless: its victims are gone
+    assert cache.evict_plan(plan) == 0
+    # the record limit drops the oldest records whatever their state
+    small = rt.PrefixCache(t.allocator(), 4, 2)
+    t.reserve(2, 13)
+    assert small.insert(list(range(13)), 12, t.pages(2)) == 3 and small.records == 2
+    assert small.drop_records(5) == 2 and small.records == 0
