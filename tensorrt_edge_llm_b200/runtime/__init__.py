@@ -12,7 +12,8 @@ import importlib
 _NATIVE = ("RequestEngine", "RequestHandle", "StreamChannel", "StreamChunk", "FinishReason", "EngineConfig", "EngineMetrics",
            "EngineStatus", "SchedulingOptions", "ResolvedSchedulingPolicy", "SessionCapabilities", "GenerationRequest",
            "RuntimeSession", "StepPlanner", "StepPlan", "validate_scheduling_options", "resolve_scheduling_policy", "Tokenizer",
-           "ChatTemplate", "KVPageTable", "PrefixCache", "LLMEngineConfig", "ParallelConfig", "LoRAManager")
+           "ChatTemplate", "ChatMessage", "KVPageTable", "PrefixCache", "LLMEngineConfig", "ParallelConfig", "LoRAManager",
+           "LLMInferenceRuntime", "LLMGenerationRequest", "LLMGenerationResponse", "GenerationEntry")
 _LOCAL = {"LLM": ("llm", "LLM"), "LLMRuntime": ("facade", "LLMRuntime"), "SamplingParams": ("runner", "SamplingParams"),
           "ModelRunner": ("runner", "ModelRunner"), "ModelSession": ("session", "ModelSession"),
           "MultiStageRuntime": ("multistage", "MultiStageRuntime"), "KVCacheManager": ("kv_cache", "KVCacheManager")}
