@@ -262,7 +262,7 @@ class EagleDecoder:
     # ---- one speculative round ----------------------------------------------------------------
     @torch.no_grad()
     def round(self, seats: Sequence[int]) -> List[List[int]]:
-        """Returns the tokens emitted for every seat this round (accepted draft tokens + bonus)."""
+        """Returns the tokens emitted for every seat in one draft-verify pass (accepted draft tokens + bonus)."""
         sp, dev = self.spec, self.device
         b, k, steps, n = len(seats), self.spec.top_k, self.spec.draft_steps, self.spec.verify_tokens
         timer = prof.timer()
@@ -406,7 +406,7 @@ class EagleDecoder:
         return torch.rand(b, depth, width, generator=self._sample_gen)
 
     def _forced(self, b: int):
-        """Forced accept lengths of this round: a constant, or draws in ``1..draft_steps+1`` from a seeded
+        """Forced accept lengths of the current draft-verify pass: a constant, or draws in ``1..draft_steps+1`` from a seeded
         distribution whose mean is ``force_accept_mean`` (random weights accept almost nothing, so
         benchmarks of the verify / rewind path prescribe the lengths)."""
         sp = self.spec
