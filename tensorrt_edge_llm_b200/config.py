@@ -202,6 +202,11 @@ class ModelConfig:
     sliding_window: Optional[int] = None
     layer_windows: List[int] = field(default_factory=list)  # per layer: sliding window in tokens, 0 = full attention (empty = `sliding_window` everywhere)
     mrope_section: List[int] = field(default_factory=list)   # multimodal RoPE: rotary pairs per (temporal, height, width) component
+    # KV-shared layers: the last `num_kv_shared_layers` layers project no keys / values of their own and attend over the cache of
+    # a donor layer (the last layer before them with the same attention type).  `kv_donor_layers` overrides the rule per layer
+    # (-1 = the layer's own cache).
+    num_kv_shared_layers: int = 0
+    kv_donor_layers: List[int] = field(default_factory=list)
     rope_local_theta: float = 0.0                   # RoPE base of the sliding-window layers when it differs (Gemma 3)
     rope_local_scaling: Optional[Dict[str, Any]] = None
     query_pre_attn_scalar: float = 0.0              # attention scale = this ** -0.5 when set (Gemma), else head_dim ** -0.5
@@ -305,6 +310,25 @@ class ModelConfig:
     def compute_dtype(self) -> torch.dtype:
         return {"bfloat16": torch.bfloat16, "float16": torch.float16,
                 "float32": torch.float32}[self.dtype]
+
+    def kv_donor(self, layer_idx: int) -> int:
+        """The layer whose KV cache ``layer_idx`` attends over, or -1 when it writes and reads its own."""
+        if self.kv_donor_layers:
+            d = int(self.kv_donor_layers[layer_idx])
+            if d >= layer_idx:
+                raise ValueError(f"layer {layer_idx}: a KV donor must be an earlier layer, got {d}")
+            return d
+        n = int(self.num_kv_shared_layers or 0)
+        first = self.num_hidden_layers - n
+        if n <= 0 or layer_idx < first:
+            return -1
+        if first <= 0:
+            raise ValueError("num_kv_shared_layers leaves no layer with keys and values of its own")
+        kind = lambda i: bool(self.layer_windows[i]) if self.layer_windows else False
+        for d in range(first - 1, -1, -1):
+            if kind(d) == kind(layer_idx) and (not self.layer_types or self.layer_types[d] == LAYER_ATTENTION):
+                return d
+        raise ValueError(f"layer {layer_idx} shares KV but no earlier layer has its attention type")
 
     @property
     def is_eagle4_draft(self) -> bool:
@@ -465,6 +489,7 @@ class ModelConfig:
             domino_gru_hidden_dim=int((llm.get("dflash_config") or {}).get("gru_hidden_dim", llm.get("domino_gru_hidden_dim", 256)) or 256),
             **{"dflash_projector_type": str((llm.get("dflash_config") or {}).get("projector_type", llm.get("dflash_projector_type", "")) or ""),
                **_parse_dflash2(llm, hf)},
+            num_kv_shared_layers=int(llm.get("num_kv_shared_layers", 0) or 0),
             draft_vocab_size=int(llm.get("draft_vocab_size", 0) or 0),
             eagle3_target_hidden_size=int(llm.get("target_hidden_size", 0) or 0),
             eagle3_norm_before_residual=bool(llm.get("norm_before_residual", False)),

@@ -55,8 +55,13 @@ class Attention(nn.Module):
         self.sliding_window = cfg.sliding_window
         self.eps = cfg.rms_norm_eps
         h = cfg.hidden_size
-        self.qkv_proj = make_linear(cfg, f"{prefix}.qkv_proj", h, [cfg.q_size, cfg.kv_size, cfg.kv_size], TPMode.COL,
-                                    sources=["q_proj", "k_proj", "v_proj"], bias=cfg.attention_bias, row_ranges=kv_ranges)
+        # a KV-shared layer attends over its donor's cache (the decoder stack hands it that layer) and projects queries only
+        self.kv_donor = cfg.kv_donor(layer_idx) if hasattr(cfg, "kv_donor") else -1
+        if self.kv_donor >= 0:
+            self.qkv_proj = make_linear(cfg, f"{prefix}.qkv_proj", h, [cfg.q_size], TPMode.COL, sources=["q_proj"], bias=cfg.attention_bias)
+        else:
+            self.qkv_proj = make_linear(cfg, f"{prefix}.qkv_proj", h, [cfg.q_size, cfg.kv_size, cfg.kv_size], TPMode.COL,
+                                        sources=["q_proj", "k_proj", "v_proj"], bias=cfg.attention_bias, row_ranges=kv_ranges)
         self.o_proj = make_linear(cfg, f"{prefix}.o_proj", cfg.q_size, [h], TPMode.ROW)
         if cfg.has_qk_norm:
             self.q_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, cfg.compute_dtype)
@@ -94,7 +99,18 @@ class Attention(nn.Module):
                 self.kv_scales[i] = t.float().reshape(-1)[0]
         return False
 
+    def _forward_shared_kv(self, x, meta, kv_layer, cos_sin):
+        """KV-shared layer: queries only; ``kv_layer`` is the donor's cache, already holding this step's rows."""
+        if kv_layer.dtype == torch.float8_e4m3fn:
+            raise NotImplementedError("KV-shared layers over an FP8 cache are not built")
+        q = ops.rope_q(self.qkv_proj(x), kv_layer, meta, cos_sin, self.num_q_heads, self.head_dim,
+                       None if self.q_norm is None else self.q_norm.weight, self.eps)
+        o = ops.paged_attention(q, kv_layer, meta, self.scale, self.sliding_window, self.attention_sink_bias)
+        return self.o_proj(o.reshape(o.shape[0], -1))
+
     def forward(self, x: torch.Tensor, meta: StepMeta, kv_layer: torch.Tensor, cos_sin: torch.Tensor) -> torch.Tensor:
+        if self.kv_donor >= 0:
+            return self._forward_shared_kv(x, meta, kv_layer, cos_sin)
         qkv = self.qkv_proj(x)
         pool_layer = None
         if kv_layer.dtype == torch.float8_e4m3fn:
@@ -198,7 +214,8 @@ class Transformer(nn.Module):
         if capture_layers and rs_was:
             comm.rs_enabled = False          # tapping hidden states needs the whole residual stream on every rank
         for i, layer in enumerate(self.layers):
-            h, residual = layer(h, residual, meta, kv_cache[i], cos_sin, comm)
+            donor = getattr(getattr(layer, "self_attn", None), "kv_donor", -1)
+            h, residual = layer(h, residual, meta, kv_cache[donor if donor >= 0 else i], cos_sin, comm)
             if meta.deepstack is not None and i in meta.deepstack:
                 # deepstack binding (``cpp/runtime/features/deepstackBinding.cpp`` in the reference): the hidden state of a
                 # row is h + residual here, so adding the level's features to h adds them to the stream

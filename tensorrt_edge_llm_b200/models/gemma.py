@@ -91,7 +91,8 @@ class GemmaTransformer(nn.Module):
         residual = None
         taps = []
         for i, layer in enumerate(self.layers):
-            h, residual = layer(h, residual, meta, kv_cache[i], cos_sin, comm)
+            donor = layer.self_attn.kv_donor                 # KV-shared layers (num_kv_shared_layers) read an earlier layer's cache
+            h, residual = layer(h, residual, meta, kv_cache[donor if donor >= 0 else i], cos_sin, comm)
             if i in capture_layers:
                 taps.append((h.float() + residual.float()).to(h.dtype))
         x, _ = ops.add_rmsnorm(h, residual, self.norm.weight, self.norm.eps)

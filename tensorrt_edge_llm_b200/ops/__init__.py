@@ -115,6 +115,14 @@ def rope_kv_write(qkv, kv_layer, meta, cos_sin, num_q_heads, num_kv_heads, head_
                              q_norm_w, k_norm_w, eps)
 
 
+def rope_q(q, kv_layer, meta, cos_sin, num_q_heads, head_dim, q_norm_w=None, eps=1e-6):
+    """Per-head RMSNorm and RoPE of the queries of a layer that writes no keys / values (``kv_layer`` is only read later; the
+    GPU form runs the RoPE + KV-write kernel with zero KV heads, so nothing is stored)."""
+    if q.is_cuda:
+        return cuda_ops().rope_kv_write(q, kv_layer, meta, cos_sin, num_q_heads, 0, head_dim, q_norm_w, None, eps)
+    return ref.rope_q(q, meta, cos_sin, num_q_heads, head_dim, q_norm_w, eps)
+
+
 def paged_attention(q, kv_layer, meta, scale, sliding_window=None, sinks=None, causal=True):
     if q.is_cuda:
         return cuda_ops().paged_attention(q, kv_layer, meta, scale, sliding_window, sinks, causal=causal)

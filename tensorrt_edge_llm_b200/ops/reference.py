@@ -226,6 +226,20 @@ def rope_kv_write(qkv: torch.Tensor, kv_layer: torch.Tensor, meta: StepMeta, cos
     return q
 
 
+def rope_q(q: torch.Tensor, meta: StepMeta, cos_sin: torch.Tensor, num_q_heads: int, head_dim: int,
+           q_norm_w: Optional[torch.Tensor] = None, eps: float = 1e-6) -> torch.Tensor:
+    """Query side of :func:`rope_kv_write` alone (KV-shared layers attend over another layer's cache and write nothing):
+    ``q [T, Hq·D]`` → optional per-head RMSNorm, RoPE → ``[T, Hq, D]``."""
+    t = q.shape[0]
+    q = q.reshape(t, num_q_heads, head_dim)
+    if q_norm_w is not None:
+        q = _head_rmsnorm(q, q_norm_w, eps)
+    pos = meta.positions
+    if meta.rope_rows is not None:
+        cos_sin, pos = meta.rope_rows, meta.rope_pos
+    return apply_rope(q, pos, cos_sin)
+
+
 def gather_kv(kv_layer: torch.Tensor, page_table_row: torch.Tensor, length: int, page_size: int
               ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Dense ``k, v [Hkv, length, D]`` of one sequence from the paged pool."""

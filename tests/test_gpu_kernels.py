@@ -666,3 +666,46 @@ def test_quantized_embedding_gather_kernel(fmt, dtype):
     assert torch.allclose(got.float().cpu(), table[ids].float(), atol=0.03 if fmt == "nvfp4" else 0.02)
     out_of_range = emb.cuda()(torch.tensor([-5, 5000]).cuda())      # clamped like the dense gather
     assert torch.equal(out_of_range[0], emb.cuda()(torch.tensor([0]).cuda())[0]) and torch.equal(out_of_range[1], emb.cuda()(torch.tensor([999]).cuda())[0])
+
+
+@pytest.mark.parametrize("d,tokens", [(128, 5), (128, 1500), (64, 33), (256, 9)])
+def test_rope_q_only_writes_no_cache(d, tokens):
+    """Queries of a KV-shared layer: per-head RMSNorm + RoPE through the RoPE / KV-write kernels with zero KV heads."""
+    from tensorrt_edge_llm_b200 import ops
+    g = torch.Generator().manual_seed(d + tokens)
+    hq = 4
+    q = torch.randn(tokens, hq * d, generator=g).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(d, generator=g)).to(torch.bfloat16)
+    cs = ref.rope_cos_sin(4096, d, 1e4, None)
+    pages = (tokens + 63) // 64
+    meta = build_step_meta([tokens], [7], torch.arange(pages + 1, dtype=torch.int32)[None], 64)
+    kv = torch.full((pages + 1, 2, 2, 64, d), 3.0, dtype=torch.bfloat16)
+    want = ref.rope_q(q.float(), meta, cs, hq, d, w.float(), 1e-6)
+    kv_gpu = kv.cuda()
+    got = ops.rope_q(q.cuda(), kv_gpu, meta.to("cuda"), cs.cuda(), hq, d, w.cuda(), 1e-6)
+    assert got.shape == (tokens, hq, d) and _rel_err(got.float().cpu(), want) < 2e-2
+    assert torch.equal(kv_gpu.cpu(), kv)                      # nothing was stored
+
+
+def test_kv_shared_layers_gpu_matches_cpu():
+    from tensorrt_edge_llm_b200 import AutoModel
+    from tensorrt_edge_llm_b200.config import tiny_llama_config
+    from tensorrt_edge_llm_b200.runtime.kv_cache import KVCacheManager
+    from tensorrt_edge_llm_b200.runtime.runner import ModelRunner
+    cfg = tiny_llama_config(num_hidden_layers=4, hidden_size=512, intermediate_size=1024, num_attention_heads=8, num_key_value_heads=2,
+                            head_dim=128, vocab_size=1000, dtype="bfloat16")
+    cfg.num_kv_shared_layers = 2
+    model = AutoModel.from_config(cfg, random_init=0)
+    sd = {k: v.clone() for k, v in model.state_dict().items()}
+    seq = torch.randint(0, 1000, (70,), generator=torch.Generator().manual_seed(1)).tolist()
+
+    def run(device):
+        m = AutoModel.from_config(cfg)
+        m.load_state_dict(sd)
+        m = m.to(device)
+        r = ModelRunner(m, KVCacheManager(cfg, num_pages=8, page_size=64, max_seats=2, max_pages_per_seq=4, device=device))
+        r.use_cuda_graphs = False
+        return r.prefill([0], [seq[:-2]]).float().cpu(), r.step([0], [[seq[-2]]]).float().cpu(), r.step([0], [[seq[-1]]]).float().cpu()
+
+    for x, y in zip(run(torch.device("cuda", 0)), run(torch.device("cpu"))):
+        assert _rel_err(x, y) < 5e-2

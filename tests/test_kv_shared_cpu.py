@@ -1,0 +1,82 @@
+"""KV-shared layers: the last layers of a decoder project queries only and attend over an earlier layer's cache."""
+import pytest
+import torch
+
+from tensorrt_edge_llm_b200 import AutoModel
+from tensorrt_edge_llm_b200.config import tiny_llama_config
+from tensorrt_edge_llm_b200.ops import reference as ref
+from tensorrt_edge_llm_b200.runtime.kv_cache import KVCacheManager
+from tensorrt_edge_llm_b200.runtime.runner import ModelRunner
+
+
+def test_donor_rule():
+    cfg = tiny_llama_config(num_hidden_layers=6, dtype="float32")
+    assert [cfg.kv_donor(i) for i in range(6)] == [-1] * 6
+    cfg.num_kv_shared_layers = 2
+    assert [cfg.kv_donor(i) for i in range(6)] == [-1, -1, -1, -1, 3, 3]
+    # with alternating attention types a shared layer takes the last earlier layer of its own type
+    cfg.layer_windows = [8, 0, 8, 0, 8, 0]
+    assert [cfg.kv_donor(i) for i in range(6)] == [-1, -1, -1, -1, 2, 3]
+    cfg.kv_donor_layers = [-1, 0, -1, 2, 2, 0]
+    assert [cfg.kv_donor(i) for i in range(6)] == [-1, 0, -1, 2, 2, 0]
+    cfg.kv_donor_layers = [-1, 3, -1, -1, -1, -1]
+    with pytest.raises(ValueError):
+        cfg.kv_donor(1)
+    cfg.kv_donor_layers, cfg.num_kv_shared_layers = [], 6
+    with pytest.raises(ValueError):
+        cfg.kv_donor(0)
+
+
+def test_shared_layers_match_a_dense_restatement_and_decode_consistently():
+    cfg = tiny_llama_config(num_hidden_layers=4, dtype="float32")
+    cfg.num_kv_shared_layers = 2
+    model = AutoModel.from_config(cfg, random_init=5)
+    shared = model.model.layers[3].self_attn
+    assert shared.kv_donor == 1 and model.model.layers[2].self_attn.kv_donor == 1 and model.model.layers[1].self_attn.kv_donor == -1
+    # a shared layer carries a query projection only
+    assert tuple(shared.qkv_proj.weight.shape) == (cfg.q_size, cfg.hidden_size)
+    g = torch.Generator().manual_seed(0)
+    seq = torch.randint(0, cfg.vocab_size, (21,), generator=g).tolist()
+
+    # dense restatement: plain causal attention per layer, layers 2 and 3 reuse layer 1's rotated keys and its values
+    def dense(ids):
+        t = len(ids)
+        h = model.model.embed_tokens.weight[torch.tensor(ids)]
+        cs = model.cos_sin("cpu")
+        pos = torch.arange(t)
+        kept = {}
+        for i, layer in enumerate(model.model.layers):
+            a = layer.self_attn
+            x = ref.rmsnorm(h, layer.input_layernorm.weight, layer.input_layernorm.eps)
+            proj = x @ a.qkv_proj.weight.t()
+            if a.kv_donor < 0:
+                q, k, v = proj.split([cfg.q_size, cfg.kv_size, cfg.kv_size], -1)
+                k = ref.apply_rope(k.reshape(t, cfg.num_key_value_heads, cfg.head_dim), pos, cs)
+                v = v.reshape(t, cfg.num_key_value_heads, cfg.head_dim)
+                kept[i] = (k, v)
+            else:
+                q, (k, v) = proj, kept[a.kv_donor]
+            q = ref.apply_rope(q.reshape(t, cfg.num_attention_heads, cfg.head_dim), pos, cs)
+            rep = cfg.num_attention_heads // cfg.num_key_value_heads
+            kk, vv = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
+            sc = torch.einsum("qhd,khd->hqk", q, kk) * cfg.head_dim ** -0.5
+            sc = sc.masked_fill(torch.triu(torch.ones(t, t, dtype=torch.bool), 1), float("-inf"))
+            o = torch.einsum("hqk,khd->qhd", torch.softmax(sc, -1), vv).reshape(t, -1)
+            h = h + o @ a.o_proj.weight.t()
+            x = ref.rmsnorm(h, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.eps)
+            gu = x @ layer.mlp.gate_up_proj.weight.t()
+            gate, up = gu.chunk(2, -1)
+            h = h + (torch.nn.functional.silu(gate) * up) @ layer.mlp.down_proj.weight.t()
+        h = ref.rmsnorm(h, model.model.norm.weight, model.model.norm.eps)
+        return h @ model.lm_head.weight.t()
+
+    want = dense(seq)
+    kv = KVCacheManager(cfg, num_pages=8, page_size=16, max_seats=2, max_pages_per_seq=4)
+    r = ModelRunner(model, kv)
+    pre = r.prefill([0], [seq[:15]])
+    assert torch.allclose(pre[0], want[14], atol=2e-4)
+    for j in range(15, 21):                                   # token-by-token decode keeps reading the donor's cache
+        out = r.step([0], [[seq[j]]])
+        assert torch.allclose(out[0], want[j], atol=2e-4)
+    # the shared layers' own cache layers were never written
+    assert float(kv.pool[2].abs().sum()) == 0.0 and float(kv.pool[3].abs().sum()) == 0.0 and float(kv.pool[1].abs().sum()) > 0
