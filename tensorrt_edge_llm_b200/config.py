@@ -206,6 +206,10 @@ class ModelConfig:
     # a donor layer (the last layer before them with the same attention type).  `kv_donor_layers` overrides the rule per layer
     # (-1 = the layer's own cache).
     num_kv_shared_layers: int = 0
+    # Gemma-4 style attention variants: full-attention layers take their values from the key projection (no v_proj), and
+    # values pass a weightless per-head RMSNorm before they are cached
+    attention_k_eq_v: bool = False
+    has_value_norm: bool = False
     kv_donor_layers: List[int] = field(default_factory=list)
     rope_local_theta: float = 0.0                   # RoPE base of the sliding-window layers when it differs (Gemma 3)
     rope_local_scaling: Optional[Dict[str, Any]] = None
@@ -490,6 +494,8 @@ class ModelConfig:
             **{"dflash_projector_type": str((llm.get("dflash_config") or {}).get("projector_type", llm.get("dflash_projector_type", "")) or ""),
                **_parse_dflash2(llm, hf)},
             num_kv_shared_layers=int(llm.get("num_kv_shared_layers", 0) or 0),
+            attention_k_eq_v=bool(llm.get("attention_k_eq_v", False)),
+            has_value_norm=bool(llm.get("has_value_norm", llm.get("use_value_norm", False))),
             draft_vocab_size=int(llm.get("draft_vocab_size", 0) or 0),
             eagle3_target_hidden_size=int(llm.get("target_hidden_size", 0) or 0),
             eagle3_norm_before_residual=bool(llm.get("norm_before_residual", False)),

@@ -57,8 +57,16 @@ class Attention(nn.Module):
         h = cfg.hidden_size
         # a KV-shared layer attends over its donor's cache (the decoder stack hands it that layer) and projects queries only
         self.kv_donor = cfg.kv_donor(layer_idx) if hasattr(cfg, "kv_donor") else -1
+        win = cfg.layer_windows[layer_idx] if cfg.layer_windows else (cfg.sliding_window or 0)
+        self.k_eq_v = bool(getattr(cfg, "attention_k_eq_v", False)) and not win       # full-attention layers only
+        self.value_norm = bool(getattr(cfg, "has_value_norm", False))
         if self.kv_donor >= 0:
             self.qkv_proj = make_linear(cfg, f"{prefix}.qkv_proj", h, [cfg.q_size], TPMode.COL, sources=["q_proj"], bias=cfg.attention_bias)
+        elif self.k_eq_v:
+            if kv_ranges is not None:
+                raise ValueError("attention_k_eq_v with replicated KV heads under tensor parallelism is not built")
+            self.qkv_proj = make_linear(cfg, f"{prefix}.qkv_proj", h, [cfg.q_size, cfg.kv_size], TPMode.COL, sources=["q_proj", "k_proj"],
+                                        bias=cfg.attention_bias)
         else:
             self.qkv_proj = make_linear(cfg, f"{prefix}.qkv_proj", h, [cfg.q_size, cfg.kv_size, cfg.kv_size], TPMode.COL,
                                         sources=["q_proj", "k_proj", "v_proj"], bias=cfg.attention_bias, row_ranges=kv_ranges)
@@ -99,6 +107,17 @@ class Attention(nn.Module):
                 self.kv_scales[i] = t.float().reshape(-1)[0]
         return False
 
+    def _derive_values(self, qkv: torch.Tensor) -> torch.Tensor:
+        """Packed ``[q | k | v]`` of the variants whose values are not a plain projection: ``v = k`` (raw, before the key norm and
+        RoPE) when the layer has no value projection, and a weightless per-head RMSNorm on ``v``."""
+        qn, kn = self.num_q_heads * self.head_dim, self.num_kv_heads * self.head_dim
+        q, k = qkv[:, :qn], qkv[:, qn:qn + kn]
+        v = k if self.k_eq_v else qkv[:, qn + kn:]
+        if self.value_norm:
+            vf = v.float().reshape(-1, self.num_kv_heads, self.head_dim)
+            v = (vf * torch.rsqrt(vf.pow(2).mean(-1, keepdim=True) + self.eps)).reshape(v.shape[0], kn).to(qkv.dtype)
+        return torch.cat((q, k, v), dim=-1)
+
     def _forward_shared_kv(self, x, meta, kv_layer, cos_sin):
         """KV-shared layer: queries only; ``kv_layer`` is the donor's cache, already holding this step's rows."""
         if kv_layer.dtype == torch.float8_e4m3fn:
@@ -112,6 +131,8 @@ class Attention(nn.Module):
         if self.kv_donor >= 0:
             return self._forward_shared_kv(x, meta, kv_layer, cos_sin)
         qkv = self.qkv_proj(x)
+        if self.k_eq_v or self.value_norm:
+            qkv = self._derive_values(qkv)
         pool_layer = None
         if kv_layer.dtype == torch.float8_e4m3fn:
             pool_layer = kv_layer

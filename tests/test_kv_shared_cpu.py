@@ -80,3 +80,47 @@ def test_shared_layers_match_a_dense_restatement_and_decode_consistently():
         assert torch.allclose(out[0], want[j], atol=2e-4)
     # the shared layers' own cache layers were never written
     assert float(kv.pool[2].abs().sum()) == 0.0 and float(kv.pool[3].abs().sum()) == 0.0 and float(kv.pool[1].abs().sum()) > 0
+
+
+def test_values_from_keys_and_weightless_value_norm():
+    """``attention_k_eq_v``: full-attention layers have no value projection and cache the raw key projection as values;
+    ``has_value_norm``: values pass a weightless per-head RMSNorm.  Checked against a dense restatement of one layer stack."""
+    cfg = tiny_llama_config(num_hidden_layers=2, dtype="float32")
+    cfg.attention_k_eq_v, cfg.has_value_norm = True, True
+    cfg.layer_windows = [0, 64]                                # layer 0 full attention (k = v), layer 1 sliding (own v_proj)
+    model = AutoModel.from_config(cfg, random_init=7)
+    a0, a1 = model.model.layers[0].self_attn, model.model.layers[1].self_attn
+    assert a0.k_eq_v and not a1.k_eq_v
+    assert tuple(a0.qkv_proj.weight.shape) == (cfg.q_size + cfg.kv_size, cfg.hidden_size)
+    assert tuple(a1.qkv_proj.weight.shape) == (cfg.q_size + 2 * cfg.kv_size, cfg.hidden_size)
+    seq = torch.randint(0, cfg.vocab_size, (12,), generator=torch.Generator().manual_seed(2)).tolist()
+    t = len(seq)
+    h = model.model.embed_tokens.weight[torch.tensor(seq)]
+    cs, pos = model.cos_sin("cpu"), torch.arange(t)
+    for layer in model.model.layers:
+        a = layer.self_attn
+        x = ref.rmsnorm(h, layer.input_layernorm.weight, layer.input_layernorm.eps)
+        proj = x @ a.qkv_proj.weight.t()
+        if a.k_eq_v:
+            q, k = proj.split([cfg.q_size, cfg.kv_size], -1)
+            v = k
+        else:
+            q, k, v = proj.split([cfg.q_size, cfg.kv_size, cfg.kv_size], -1)
+        v = v.reshape(t, cfg.num_key_value_heads, cfg.head_dim)
+        v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps)
+        q = ref.apply_rope(q.reshape(t, cfg.num_attention_heads, cfg.head_dim), pos, cs)
+        k = ref.apply_rope(k.reshape(t, cfg.num_key_value_heads, cfg.head_dim), pos, cs)
+        rep = cfg.num_attention_heads // cfg.num_key_value_heads
+        sc = torch.einsum("qhd,khd->hqk", q, k.repeat_interleave(rep, 1)) * cfg.head_dim ** -0.5
+        sc = sc.masked_fill(torch.triu(torch.ones(t, t, dtype=torch.bool), 1), float("-inf"))
+        o = torch.einsum("hqk,khd->qhd", torch.softmax(sc, -1), v.repeat_interleave(rep, 1)).reshape(t, -1)
+        h = h + o @ a.o_proj.weight.t()
+        x = ref.rmsnorm(h, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.eps)
+        gate, up = (x @ layer.mlp.gate_up_proj.weight.t()).chunk(2, -1)
+        h = h + (torch.nn.functional.silu(gate) * up) @ layer.mlp.down_proj.weight.t()
+    want = ref.rmsnorm(h, model.model.norm.weight, model.model.norm.eps) @ model.lm_head.weight.t()
+    r = ModelRunner(model, KVCacheManager(cfg, num_pages=4, page_size=16, max_seats=1, max_pages_per_seq=2))
+    got = r.prefill([0], [seq[:8]])
+    assert torch.allclose(got[0], want[7], atol=2e-4)
+    for j in range(8, 12):
+        assert torch.allclose(r.step([0], [[seq[j]]])[0], want[j], atol=2e-4)
