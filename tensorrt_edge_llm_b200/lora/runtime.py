@@ -114,6 +114,20 @@ class LoraManager:
         self._wrapped[module_name] = w
         return w
 
+    def reserve_slots(self, slots_file: str) -> int:
+        """Wrap the layers a ``lora_slots.json`` (``trtedge insert-lora --model_dir``) declares adaptable, before any adapter is
+        loaded and before the model's first step; records the declared maximum rank.  Returns the number of layers wrapped."""
+        with open(slots_file, "r", encoding="utf-8") as f:
+            decl = json.load(f)
+        self.max_rank = int(decl.get("max_lora_rank", 0) or 0)
+        n = 0
+        for ckpt_mod in decl.get("slots", {}):
+            mod_name, _, _ = self._locate(ckpt_mod)
+            if mod_name not in self._wrapped:
+                self._wrap(mod_name)
+                n += 1
+        return n
+
     def _locate(self, ckpt_module: str) -> Tuple[str, int, LinearBase]:
         """Runtime module, source index of a checkpoint module name (``…self_attn.q_proj`` → ``…self_attn.qkv_proj``, 0)."""
         name = ckpt_module
@@ -137,6 +151,8 @@ class LoraManager:
         f = SafetensorsFile(os.path.join(adapter_dir, "lora_weights.safetensors"))
         with open(os.path.join(adapter_dir, "lora_config.json"), "r", encoding="utf-8") as fh:
             meta = json.load(fh)
+        if getattr(self, "max_rank", 0) and int(meta.get("rank", 0)) > self.max_rank:
+            raise ValueError(f"adapter {name!r} has rank {meta.get('rank')}, the model declares at most {self.max_rank}")
         if name in self.names:                      # reloading under a known name replaces the old weights
             for w in self._wrapped.values():
                 old = w.adapters.pop(name, None)

@@ -83,6 +83,12 @@ class LLM:
         self.runner.vocab_map = self._vocab_map
         self.lora = None
         self.runner.lora = None
+        slots = os.path.join(model, "lora_slots.json") if isinstance(model, str) else ""
+        if slots and os.path.isfile(slots):         # adapter slots declared ahead of time (`trtedge insert-lora --model_dir`)
+            from ..lora.runtime import LoraManager
+            self.lora = LoraManager(self.model)
+            self.runner.lora = self.lora
+            self.lora.reserve_slots(slots)
         eos0 = self.cfg.eos_token_id
         self.guided_vocab = lp.GuidedVocabulary(tokenizer, self.cfg.vocab_size, eos0 if isinstance(eos0, (list, tuple)) else [eos0])
         self.engine = None

@@ -96,6 +96,39 @@ def test_lora_process_and_merge(ckpt, tmp_path):
     assert not torch.allclose(_logits(ckpt, [3, 4, 5]), _logits(merged, [3, 4, 5]))
 
 
+def test_insert_lora_declares_slots_the_runtime_reserves(ckpt, tmp_path, capsys):
+    import shutil
+    from tensorrt_edge_llm_b200.lora.runtime import LoraLinear
+    from tensorrt_edge_llm_b200.runtime.llm import LLM
+    ad, rt_dir = str(tmp_path / "adapter"), str(tmp_path / "rt")
+    _adapter(ad)
+    model_dir = str(tmp_path / "model")
+    shutil.copytree(ckpt, model_dir)
+    assert trtedge(["insert-lora", "--lora_dir", ad, "--model_dir", model_dir, "--max-lora-rank", "8"]) == 0
+    decl = json.load(open(os.path.join(model_dir, "lora_slots.json")))
+    assert decl["max_lora_rank"] == 8 and decl["slots"]["model.layers.0.self_attn.q_proj"]["module"].endswith("self_attn.qkv_proj")
+    assert decl["slots"]["model.layers.0.self_attn.q_proj"]["source"] == 0 and decl["slots"]["model.layers.1.mlp.down_proj"]["in_features"] == 256
+    # an adapter that does not fit the model is refused and leaves the declaration alone
+    bad = str(tmp_path / "bad")
+    _adapter(bad)
+    f = SafetensorsFile(os.path.join(bad, "adapter_model.safetensors"))
+    t = {k: f.get(k).clone() for k in f.keys()}
+    t["base_model.model.model.layers.0.self_attn.q_proj.lora_A.weight"] = torch.zeros(4, 64)
+    save_file(t, os.path.join(bad, "adapter_model.safetensors"))
+    assert trtedge(["insert-lora", "--lora_dir", bad, "--model_dir", model_dir]) == 1
+    assert "do not fit" in capsys.readouterr().out
+    # the runtime wraps the declared layers at load and enforces the declared rank
+    llm = LLM(model_dir, device="cpu", max_batch_size=1, max_input_len=64, max_kv_cache_capacity=96)
+    assert llm.lora is not None and isinstance(llm.model.model.layers[0].self_attn.qkv_proj, LoraLinear)
+    assert isinstance(llm.model.model.layers[1].mlp.down_proj, LoraLinear) and not isinstance(llm.model.model.layers[0].mlp.down_proj, LoraLinear)
+    assert trtedge(["process-lora", "--input_dir", ad, "--output_dir", rt_dir]) == 0
+    llm.load_lora("style", rt_dir)
+    llm.lora.max_rank = 2
+    with pytest.raises(ValueError, match="rank"):
+        llm.load_lora("other", rt_dir)
+    llm.close()
+
+
 def test_lora_runtime_adapter_equals_merged_checkpoint(ckpt, tmp_path):
     from tensorrt_edge_llm_b200.lora import LoraManager
     ad, rt_dir, merged = str(tmp_path / "adapter"), str(tmp_path / "rt"), str(tmp_path / "merged")
