@@ -233,11 +233,27 @@ class ModelRunner:
         if sp.temperature < 1e-3:
             return self.pick(logits)
         n = logits.shape[0]
-        g = torch.Generator(device="cpu").manual_seed(sp.seed * 1000003 + step)
-        u = torch.rand(n, generator=g).to(logits.device)
         dev = logits.device
-        return self.to_full_vocab(ops.sample(logits, torch.full((n,), sp.temperature, device=dev),
-                                             torch.full((n,), sp.top_k, device=dev, dtype=torch.int32), torch.full((n,), sp.top_p, device=dev), u))
+        # uniforms: one generator stream per (seed, step), as before, but drawn for 64 steps at a time and uploaded in one copy;
+        # the per-row sampling parameters are constant over a generation and live on the device
+        blk, off = divmod(int(step), 64)
+        key = (sp.seed, n, blk, str(dev))
+        cache = self.__dict__.setdefault("_uniform_cache", {})
+        if key not in cache:
+            if len(cache) > 8:
+                cache.clear()
+            rows = [torch.rand(n, generator=torch.Generator(device="cpu").manual_seed(sp.seed * 1000003 + blk * 64 + j)) for j in range(64)]
+            cache[key] = torch.stack(rows).to(dev)
+        u = cache[key][off]
+        pkey = (n, float(sp.temperature), int(sp.top_k), float(sp.top_p), str(dev))
+        params = self.__dict__.setdefault("_sample_params", {})
+        if pkey not in params:
+            if len(params) > 16:
+                params.clear()
+            params[pkey] = (torch.full((n,), sp.temperature, device=dev), torch.full((n,), sp.top_k, device=dev, dtype=torch.int32),
+                            torch.full((n,), sp.top_p, device=dev))
+        t, k, p = params[pkey]
+        return self.to_full_vocab(ops.sample(logits, t, k, p, u))
 
     def to_full_vocab(self, cols: torch.Tensor) -> torch.Tensor:
         return cols if self.vocab_map is None else self.vocab_map[cols.long()]
