@@ -289,6 +289,34 @@ __global__ void embedding_quant_kernel(const int* __restrict__ ids, const uint8_
     }
 }
 
+// RoPE table: out[p, i] = att * cos(p * inv[i]), out[p, half + i] = att * sin(p * inv[i]); angles in double (positions reach
+// 10^5 and more, where an fp32 product has lost the fraction).  One thread per (position, pair).
+__global__ void rope_table_kernel(const double* __restrict__ inv, float att, float* __restrict__ out, int max_pos, int half) {
+    pdl_prologue();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)max_pos * half) return;
+    const int p = (int)(idx / half), i = (int)(idx - (long long)p * half);
+    double s, c;
+    sincos((double)p * inv[i], &s, &c);
+    out[(size_t)p * 2 * half + i] = (float)(c * att);
+    out[(size_t)p * 2 * half + half + i] = (float)(s * att);
+}
+
+// Multimodal RoPE rows: pair i of row t looks its angle up at the temporal, height or width position of the row, according to
+// the section the pair belongs to (sec0 pairs temporal, then sec1 height, the rest width).  cos_sin [P, 2 half], pos3 [3, T].
+__global__ void mrope_rows_kernel(const float* __restrict__ cos_sin, const int* __restrict__ pos3, float* __restrict__ out, int tokens,
+                                  int half, int table_rows, int sec0, int sec1) {
+    pdl_prologue();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)tokens * half) return;
+    const int t = (int)(idx / half), i = (int)(idx - (long long)t * half);
+    const int comp = i < sec0 ? 0 : (i < sec0 + sec1 ? 1 : 2);
+    int p = pos3[(size_t)comp * tokens + t];
+    p = min(max(p, 0), table_rows - 1);
+    out[(size_t)t * 2 * half + i] = cos_sin[(size_t)p * 2 * half + i];
+    out[(size_t)t * 2 * half + half + i] = cos_sin[(size_t)p * 2 * half + half + i];
+}
+
 // RoPE + optional per-head RMSNorm on q and k + paged KV write.
 // One warp per (token, head); lane l owns E = D/64 consecutive features of each half of the head
 // (rotate-half pairs are (i, i + D/2)), so every access is a contiguous E*2-byte vector and the
@@ -734,6 +762,24 @@ extern "C" int telb_embedding_quant(const int* ids, const void* data, const void
         DISPATCH_T(is_bf16, { TELB_LAUNCH("embedding_quant_kernel", (embedding_quant_kernel<T, 1>), dim3((unsigned)rows), dim3(128), 0, stream, ids, (const uint8_t*)data, scale, global_scale, (T*)out, hidden, vocab); })
     }
     TELB_CHECK_LAUNCH("embedding_quant_kernel");
+    return 0;
+}
+
+extern "C" int telb_rope_table(const double* inv_freq, float attention_factor, float* out, int max_pos, int half, cudaStream_t stream) {
+    if (max_pos <= 0 || half <= 0) return 0;
+    const long long n = (long long)max_pos * half;
+    TELB_LAUNCH("rope_table_kernel", rope_table_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, inv_freq, attention_factor, out, max_pos, half);
+    TELB_CHECK_LAUNCH("rope_table_kernel");
+    return 0;
+}
+
+extern "C" int telb_mrope_rows(const float* cos_sin, const int* pos3, float* out, int tokens, int half, int table_rows, int sec0, int sec1,
+                               cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (sec0 < 0 || sec1 < 0 || sec0 + sec1 > half) return fail("telb_mrope_rows: sections must fit the rotary pairs");
+    const long long n = (long long)tokens * half;
+    TELB_LAUNCH("mrope_rows_kernel", mrope_rows_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, cos_sin, pos3, out, tokens, half, table_rows, sec0, sec1);
+    TELB_CHECK_LAUNCH("mrope_rows_kernel");
     return 0;
 }
 

@@ -278,7 +278,7 @@ class CausalLM(nn.Module):
 
     def cos_sin(self, device) -> torch.Tensor:
         if self._cos_sin is None or self._cos_sin.device != torch.device(device):
-            self._cos_sin = ops.ref.rope_cos_sin(self.cfg.max_position_embeddings, self.cfg.rotary_dim,
+            self._cos_sin = ops.rope_cos_sin(self.cfg.max_position_embeddings, self.cfg.rotary_dim,
                                                  self.cfg.rope_theta, self.cfg.rope_scaling, device=device)
         return self._cos_sin
 
@@ -287,7 +287,7 @@ class CausalLM(nn.Module):
         cs = self.cos_sin(dev)
         if meta.positions3 is not None and self.cfg.mrope_section and meta.rope_rows is None:
             # multimodal RoPE: one [T, D] cos / sin row per token, built from its (t, h, w) position, shared by all layers
-            meta.rope_rows = ops.ref.mrope_rows(cs, meta.positions3, self.cfg.mrope_section)
+            meta.rope_rows = ops.mrope_rows(cs, meta.positions3, self.cfg.mrope_section)
             meta.rope_pos = torch.arange(meta.num_tokens, dtype=torch.int32, device=dev)
         return self.model(ids, meta, kv_cache, cs, self.comm, inputs_embeds, capture_layers)
 

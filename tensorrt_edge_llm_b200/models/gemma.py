@@ -106,8 +106,8 @@ class GemmaCausalLM(CausalLM):
     def cos_sin(self, device):
         if self._cos_sin is None or self._cos_sin[0].device != torch.device(device):
             c = self.cfg
-            full = ops.ref.rope_cos_sin(c.max_position_embeddings, c.rotary_dim, c.rope_theta, c.rope_scaling, device=device)
-            local = full if c.rope_local_theta <= 0 else ops.ref.rope_cos_sin(c.max_position_embeddings, c.rotary_dim, c.rope_local_theta,
+            full = ops.rope_cos_sin(c.max_position_embeddings, c.rotary_dim, c.rope_theta, c.rope_scaling, device=device)
+            local = full if c.rope_local_theta <= 0 else ops.rope_cos_sin(c.max_position_embeddings, c.rotary_dim, c.rope_local_theta,
                                                                                 c.rope_local_scaling, device=device)
             self._cos_sin = (full, local)
         return self._cos_sin

@@ -61,7 +61,7 @@ class MtpDraft(nn.Module):
 
     def cos_sin(self, device) -> torch.Tensor:
         if self._cos_sin is None or self._cos_sin.device != torch.device(device):
-            self._cos_sin = ops.ref.rope_cos_sin(self.cfg.max_position_embeddings, self.cfg.rotary_dim, self.cfg.rope_theta,
+            self._cos_sin = ops.rope_cos_sin(self.cfg.max_position_embeddings, self.cfg.rotary_dim, self.cfg.rope_theta,
                                                  self.cfg.rope_scaling, device=device)
         return self._cos_sin
 

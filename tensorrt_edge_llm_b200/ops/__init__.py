@@ -115,6 +115,23 @@ def rope_kv_write(qkv, kv_layer, meta, cos_sin, num_q_heads, num_kv_heads, head_
                              q_norm_w, k_norm_w, eps)
 
 
+def rope_cos_sin(max_pos, rotary_dim, theta, scaling=None, device="cpu"):
+    """RoPE ``[max_pos, rotary_dim]`` cos | sin table (fp32, angles in fp64) with the frequency scaling of the checkpoint; built by
+    a kernel when the table lives on a GPU."""
+    dev = torch.device(device)
+    if dev.type == "cuda":
+        inv, att = ref.rope_frequencies(max_pos, rotary_dim, theta, scaling)
+        return cuda_ops().rope_table(inv, att, max_pos, dev)
+    return ref.rope_cos_sin(max_pos, rotary_dim, theta, scaling, device=device)
+
+
+def mrope_rows(cos_sin, positions3, sections):
+    """Multimodal RoPE: per-row cos | sin tables gathered by each row's (temporal, height, width) positions."""
+    if cos_sin.is_cuda:
+        return cuda_ops().mrope_rows(cos_sin, positions3, sections)
+    return ref.mrope_rows(cos_sin, positions3, sections)
+
+
 def rope_q(q, kv_layer, meta, cos_sin, num_q_heads, head_dim, q_norm_w=None, eps=1e-6):
     """Per-head RMSNorm and RoPE of the queries of a layer that writes no keys / values (``kv_layer`` is only read later; the
     GPU form runs the RoPE + KV-write kernel with zero KV heads, so nothing is stored)."""

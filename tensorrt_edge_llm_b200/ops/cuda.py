@@ -245,6 +245,28 @@ def gemm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = N
     return out.reshape(*lead, n)
 
 
+def rope_table(inv_freq: torch.Tensor, attention_factor: float, max_pos: int, device) -> torch.Tensor:
+    """``[max_pos, 2 * len(inv_freq)]`` fp32 cos | sin table from fp64 inverse frequencies, built on the device."""
+    inv = inv_freq.to(device=device, dtype=torch.float64).contiguous()
+    out = torch.empty(max_pos, 2 * inv.numel(), dtype=torch.float32, device=device)
+    with torch.cuda.device(out.device):
+        _check(lib().telb_rope_table(_p(inv), c_float(float(attention_factor)), _p(out), c_int(max_pos), c_int(inv.numel()), _stream()), "rope_table")
+    return out
+
+
+def mrope_rows(cos_sin: torch.Tensor, positions3: torch.Tensor, sections) -> torch.Tensor:
+    """Per-row multimodal RoPE tables ``[T, D]`` gathered from the ordinary table by (temporal, height, width) positions."""
+    half = cos_sin.shape[-1] // 2
+    if len(sections) != 3 or sum(sections) != half:
+        raise ValueError(f"mrope sections {list(sections)} must be three counts summing to {half}")
+    cs = cos_sin.float().contiguous()
+    p3 = positions3.to(device=cs.device, dtype=torch.int32).contiguous()
+    out = torch.empty(p3.shape[1], 2 * half, dtype=torch.float32, device=cs.device)
+    _check(lib().telb_mrope_rows(_p(cs), _p(p3), _p(out), c_int(p3.shape[1]), c_int(half), c_int(cs.shape[0]), c_int(int(sections[0])),
+                                 c_int(int(sections[1])), _stream()), "mrope_rows")
+    return out
+
+
 def rope_kv_write(qkv, kv_layer, meta: StepMeta, cos_sin, num_q_heads, num_kv_heads, head_dim,
                   q_norm_w=None, k_norm_w=None, eps=1e-6) -> torch.Tensor:
     qkv = qkv.contiguous()

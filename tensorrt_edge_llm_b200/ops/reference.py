@@ -70,9 +70,8 @@ def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
 # RoPE
 
 
-def rope_cos_sin(max_pos: int, rotary_dim: int, theta: float, scaling: Optional[dict] = None,
-                 device="cpu") -> torch.Tensor:
-    """``[max_pos, rotary_dim]`` table: first half cos, second half sin (fp32).
+def rope_frequencies(max_pos: int, rotary_dim: int, theta: float, scaling: Optional[dict] = None) -> Tuple[torch.Tensor, float]:
+    """``(inverse frequencies [rotary_dim / 2] fp64, attention factor)`` of a RoPE table of ``max_pos`` positions.
 
     Supports the default, ``linear``, ``dynamic`` (NTK, evaluated at the table length), ``llama3``, ``yarn`` and
     ``longrope`` (per-pair short / long factors) frequency scalings — the ``RopeType`` set of
@@ -118,6 +117,14 @@ def rope_cos_sin(max_pos: int, rotary_dim: int, theta: float, scaling: Optional[
             ramp = ((torch.arange(half, dtype=torch.float64) - lo_i) / max(hi_i - lo_i, 1e-3)).clamp(0, 1)
             inv = inv / factor * ramp + inv * (1 - ramp)
             att = float(scaling.get("attention_factor") or (0.1 * math.log(factor) + 1.0))
+    return inv, att
+
+
+def rope_cos_sin(max_pos: int, rotary_dim: int, theta: float, scaling: Optional[dict] = None,
+                 device="cpu") -> torch.Tensor:
+    """``[max_pos, rotary_dim]`` table: first half cos, second half sin (fp32; angles in fp64), for the frequencies of
+    :func:`rope_frequencies`."""
+    inv, att = rope_frequencies(max_pos, rotary_dim, theta, scaling)
     pos = torch.arange(max_pos, dtype=torch.float64)
     ang = pos[:, None] * inv[None, :]
     return torch.cat([ang.cos() * att, ang.sin() * att], dim=-1).float().to(device)

@@ -709,3 +709,22 @@ def test_kv_shared_layers_gpu_matches_cpu():
 
     for x, y in zip(run(torch.device("cuda", 0)), run(torch.device("cpu"))):
         assert _rel_err(x, y) < 5e-2
+
+
+@pytest.mark.parametrize("scaling", [None, {"rope_type": "llama3", "factor": 8.0, "original_max_position_embeddings": 8192},
+                                     {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 4096}])
+def test_rope_table_and_mrope_rows_kernels(scaling):
+    """RoPE table built on the device (fp64 angles) against the host table, at positions where fp32 angles would have lost
+    their fraction; multimodal rows gathered by (t, h, w) positions against the torch gather."""
+    from tensorrt_edge_llm_b200 import ops
+    want = ref.rope_cos_sin(40000, 128, 1e6, scaling)
+    got = ops.rope_cos_sin(40000, 128, 1e6, scaling, device="cuda")
+    assert got.shape == want.shape and got.dtype == torch.float32
+    assert float((got.cpu() - want).abs().max()) < 2e-6
+    g = torch.Generator().manual_seed(0)
+    pos3 = torch.randint(0, 40000, (3, 77), generator=g, dtype=torch.int32)
+    sections = [16, 24, 24]
+    rows = ops.mrope_rows(got, pos3.cuda(), sections)
+    assert torch.equal(rows.cpu(), ref.mrope_rows(got.cpu(), pos3, sections))
+    with pytest.raises(ValueError):
+        ops.mrope_rows(got, pos3.cuda(), [16, 16, 16])
