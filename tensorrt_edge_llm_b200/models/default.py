@@ -321,6 +321,29 @@ class CausalLM(nn.Module):
         rows = x if meta.logits_idx.numel() == x.shape[0] else x.index_select(0, meta.logits_idx.long())
         return self.comm.argmax_sharded(self.lm_head(rows))
 
+    def candidates_from_hidden(self, x: torch.Tensor, meta: StepMeta, k: int):
+        """The sampler's candidate set without the full logits: every rank takes the ``k`` best logits of its vocabulary shard
+        and the ranks exchange those (``2 k`` numbers per row and rank instead of ``V / world`` logits).  The ``k`` best of
+        the whole vocabulary are always among them, so top-k / top-p sampling over the candidates equals sampling over the
+        gathered logits.  Returns ``(values [B, world · k] fp32, token ids [B, world · k] int64)``; with one rank (or a
+        replicated head) simply the top ``k``."""
+        rows = x if meta.logits_idx.numel() == x.shape[0] else x.index_select(0, meta.logits_idx.long())
+        shard = self.lm_head(rows).float()
+        kk = min(int(k), shard.shape[-1])
+        vals, idx = shard.topk(kk, dim=-1)
+        if not (self.lm_head.tp_mode == TPMode.COL and self.comm.world_size > 1):
+            return vals, idx
+        if self.cfg.vocab_size >= 1 << 24:
+            raise ValueError("candidate exchange packs token ids into fp32: the vocabulary must be below 2^24")
+        idx = idx + self.comm.rank * shard.shape[-1]
+        w, b = self.comm.world_size, vals.shape[0]
+        g = self.comm.all_gather_cols(torch.cat([vals, idx.to(torch.float32)], dim=-1).contiguous()).view(b, w, 2, kk)
+        return g[:, :, 0].reshape(b, w * kk).contiguous(), g[:, :, 1].reshape(b, w * kk).long()
+
+    def supports_candidate_sampling(self) -> bool:
+        """Whether :meth:`candidates_from_hidden` describes this model's logits (no transform between head and sampler)."""
+        return type(self).logits_from_hidden is CausalLM.logits_from_hidden
+
     def finalize(self):
         for m in self.modules():
             if hasattr(m, "finalize") and m is not self:

@@ -270,13 +270,48 @@ class ModelRunner:
             return self.pick(self.model(ids, meta, self.cache))
         return self.to_full_vocab(g(ids, meta, self.cache))
 
+    def _candidate_k(self, sp: SamplingParams) -> int:
+        """Candidates per vocabulary shard that make sampling over them exact, or 0 when the sampler needs every logit (no
+        top-k and no top-p cut) or the model's head is not sharded."""
+        comm = getattr(self.model, "comm", None)
+        if comm is None or getattr(comm, "world_size", 1) <= 1 or not hasattr(self.model, "candidates_from_hidden"):
+            return 0
+        if not self.model.supports_candidate_sampling() or self.vocab_map is not None:
+            return 0
+        if sp.top_k and sp.top_k > 0:
+            return min(int(sp.top_k), 1024)
+        return 1024 if sp.top_p < 1.0 else 0             # top-p alone: the sampler's own candidate cap
+
+    @torch.no_grad()
+    def step_candidates(self, seats: Sequence[int], token_lists: Sequence[Sequence[int]], k: int):
+        """One ragged decode step that ends in per-shard candidates instead of logits (tensor-parallel sampling without the
+        full-vocabulary gather): ``(values [B, world · k], token ids [B, world · k])``."""
+        q_lens = [len(t) for t in token_lists]
+        positions = None
+        if self.rope_delta and any(self.rope_delta.get(s) for s in seats):
+            positions = [self.kv.lengths[s] + self.rope_delta.get(s, 0) + j for s, q in zip(seats, q_lens) for j in range(q)]
+        meta = self._meta(seats, q_lens, False, None, positions)
+        ids = torch.tensor([t for ts in token_lists for t in ts], dtype=torch.int32).to(self.device)
+        x = self.model.hidden_states(ids, meta, self.cache)
+        out = self.model.candidates_from_hidden(x, meta, k)
+        for s, q in zip(seats, q_lens):
+            self.kv.commit(s, q)
+        return out
+
     @torch.no_grad()
     def decode_sampled(self, seats, first_tokens, steps, sp: SamplingParams) -> torch.Tensor:
         toks = first_tokens.to(torch.int32)
         cols = []
+        kc = self._candidate_k(sp)
         for i in range(steps):
-            logits = self.step(seats, [[int(t)] for t in toks.tolist()])
-            toks = self.sample(logits, sp, step=i + 1)
+            feed = [[int(t)] for t in toks.tolist()]
+            if kc:
+                # vocabulary-sharded head: sample over the exchanged per-shard candidates, then map the pick back to its token
+                vals, ids = self.step_candidates(seats, feed, kc)
+                pick = self.sample(vals, sp, step=i + 1).long()
+                toks = ids.gather(1, pick[:, None])[:, 0].to(torch.int32)
+            else:
+                toks = self.sample(self.step(seats, feed), sp, step=i + 1)
             cols.append(toks)
         return torch.stack(cols, dim=1)
 

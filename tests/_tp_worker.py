@@ -39,9 +39,16 @@ def main():
         logits = r.prefill([0, 1], prompts)
         first = logits.float().argmax(-1).to(torch.int32)
         toks = r.decode_greedy([0, 1], first, 6)
-        return logits.float().cpu(), toks.cpu()
+        # sampled decode: with a vocabulary-sharded head the ranks exchange per-shard candidates instead of the logits
+        from tensorrt_edge_llm_b200.runtime.runner import SamplingParams
+        sp = SamplingParams(temperature=0.8, top_k=20, seed=7)
+        kc = r._candidate_k(sp)
+        sampled = r.decode_sampled([0, 1], toks[:, -1], 5, sp)
+        sp2 = SamplingParams(temperature=0.7, top_p=0.9, seed=9)
+        sampled2 = r.decode_sampled([0, 1], sampled[:, -1], 4, sp2)
+        return logits.float().cpu(), toks.cpu(), torch.cat([sampled, sampled2], 1).cpu(), kc
 
-    ref_logits, ref_toks = run(None, None)
+    ref_logits, ref_toks, ref_sampled, _ = run(None, None)
     comm = make_comm(kind, dev)
     # vocabulary-sharded greedy pick: candidates per shard instead of gathered logits, ties across shards → lowest id
     g = torch.Generator().manual_seed(11)
@@ -60,7 +67,14 @@ def main():
             sys.exit(1)
     del want_ids
     mapping = Mapping(tp_size=world, tp_rank=rank, ep_size=world if expert_parallel else 1, ep_rank=rank if expert_parallel else 0)
-    tp_logits, tp_toks = run(mapping, comm)
+    tp_logits, tp_toks, tp_sampled, kc = run(mapping, comm)
+    sampled_same = (tp_sampled == ref_sampled).float().mean().item()
+    if world > 1 and kc != 20:
+        print(f"rank {rank}: sampled decoding did not take the candidate exchange (k = {kc})", flush=True)
+        sys.exit(1)
+    if (dev.type == "cpu" and sampled_same < 1.0) or sampled_same < 0.4:
+        print(f"rank {rank}: sampled tokens {tp_sampled.tolist()} != {ref_sampled.tolist()}", flush=True)
+        sys.exit(1)
     err = (tp_logits - ref_logits).abs().max().item()
     scale = ref_logits.abs().max().item()
     tol = 1e-4 if dev.type == "cpu" else 0.06
