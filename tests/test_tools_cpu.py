@@ -519,3 +519,53 @@ def test_externalized_weights_and_refit(tmp_path):
         llm.refit({"lm_head.weight": torch.zeros(3, 3)})
     assert llm.generate([prompt], sp)[0].token_ids == after                # a refused refit changed nothing
     llm.close()
+
+
+def test_stream_command_prints_pieces_as_they_are_generated(ckpt, tmp_path, capsys):
+    """``trtedge stream``: a request file through the native façade; the streamed pieces concatenate to what ``infer``'s path
+    (the Python generate call) produces for the same greedy requests."""
+    import shutil
+    from tokenizers import Regex, Tokenizer, decoders, models, pre_tokenizers, trainers
+    from tensorrt_edge_llm_b200.runtime import native as rt
+    from tensorrt_edge_llm_b200.runtime.llm import LLM
+    from tensorrt_edge_llm_b200.runtime.runner import SamplingParams
+    d = str(tmp_path / "m")
+    shutil.copytree(ckpt, d)
+    tok = Tokenizer(models.BPE())
+    pat = r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+"
+    tok.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.Split(Regex(pat), behavior="isolated"),
+                                                 pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+    tok.decoder = decoders.ByteLevel()
+    trainer = trainers.BpeTrainer(vocab_size=500, special_tokens=["<|endoftext|>", "<|im_start|>", "<|im_end|>"],
+                                  initial_alphabet=pre_tokenizers.ByteLevel.alphabet())
+    tok.train_from_iterator(["the quick brown fox jumps over the lazy dog " * 4, "hello world how are you today"] * 3, trainer)
+    tok.save(os.path.join(d, "tokenizer.json"))
+    with open(os.path.join(d, "tokenizer_config.json"), "w") as f:
+        json.dump({"eos_token": "<|im_end|>", "chat_template": "{% for m in messages %}<|im_start|>{{ m['role'] }}\n{{ m['content'] }}<|im_end|>\n{% endfor %}{% if add_generation_prompt %}<|im_start|>assistant\n{% endif %}"}, f)
+    body = {"temperature": 0.0, "max_generate_length": 6, "requests": [{"messages": [{"role": "user", "content": "hello world"}]},
+                                                                       {"messages": [{"role": "user", "content": "the lazy dog"}]}]}
+    req_file = str(tmp_path / "req.json")
+    with open(req_file, "w") as f:
+        json.dump(body, f)
+    capsys.readouterr()
+    assert trtedge(["stream", d, "--input-file", req_file, "--device", "cpu", "--max-kv-cache-capacity", "256", "--max-input-len", "128"]) == 0
+    lines = [json.loads(x) for x in capsys.readouterr().out.strip().splitlines()]
+    texts, toks = {0: "", 1: ""}, {0: [], 1: []}
+    for ev in lines:
+        if not ev.get("finished"):
+            texts[ev["request"]] += ev["text"]
+            toks[ev["request"]] += ev["tokens"]
+    done = [ev for ev in lines if ev.get("finished")]
+    assert len(done) == 2 and all(ev["generated_tokens"] == len(toks[ev["request"]]) and ev["error"] == "" for ev in done)
+    # the same prompts through the Python generate call
+    ntok = rt.Tokenizer.load_from_hf(d)
+    from tensorrt_edge_llm_b200.chat_template import ChatTemplate
+    tpl = ChatTemplate.load(d)
+    prompts = [list(ntok.encode(tpl.apply(r["messages"], True, enable_thinking=False))) for r in body["requests"]]
+    llm = LLM(d, device="cpu", max_batch_size=2, max_input_len=128, max_kv_cache_capacity=256)
+    want = [o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=6))]
+    llm.close()
+    assert [toks[0], toks[1]] == want
+    assert texts[0] == ntok.decode(want[0], True).decode("utf-8", "replace")
+    # --plain needs exactly one request
+    assert trtedge(["stream", d, "--input-file", req_file, "--plain", "--device", "cpu"]) == 2
