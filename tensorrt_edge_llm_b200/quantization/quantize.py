@@ -38,6 +38,79 @@ def _is_target(name: str, shape, exclude: Sequence[str]) -> bool:
     return mod.rsplit(".", 1)[-1] in _LINEAR_SUFFIXES
 
 
+def _int4_group_qdq(w: torch.Tensor, g: int) -> torch.Tensor:
+    """Symmetric 4-bit group quantise-dequantise of ``w [out, in]`` along the input dimension."""
+    wg = w.reshape(w.shape[0], w.shape[1] // g, g)
+    scale = (wg.abs().amax(-1, keepdim=True) / 7.0).clamp(min=1e-8)
+    return (torch.round(wg / scale).clamp(-8, 7) * scale).reshape(w.shape)
+
+
+@torch.no_grad()
+def awq_search(model_dir: str, calib_ids: Optional[torch.Tensor] = None, num_samples: int = 8, seq_len: int = 128, device: str = "cpu",
+               group_size: int = 128, grid: int = 20, max_rows: int = 512) -> Dict[str, torch.Tensor]:
+    """Activation-aware weight scaling (AWQ) for INT4 group quantisation.
+
+    Weights that multiply large activations matter more; scaling input channel ``c`` of ``W`` up by ``s_c`` before rounding
+    (and the activation down by the same factor at run time: the checkpoint's ``pre_quant_scale = 1 / s``) spends the 4-bit
+    grid where it counts.  Per linear layer — fused projections share their input, hence one scale vector — the search
+    takes ``s = mean|x|^alpha`` (normalised to geometric mean 1 between its extremes), tries ``alpha`` on a grid from 0
+    (plain rounding) to 1 and keeps the one with the smallest output error on calibration activations.
+    Returns ``{checkpoint module name: pre_quant_scale [in]}`` (fp32) for the layers where a scale other than 1 won.
+    (The search of ModelOpt's ``awq_lite``, which produces the ``pre_quant_scale`` tensors of INT4-AWQ checkpoints.)"""
+    from ..model import AutoModel
+    from ..models.linear import LinearBase
+    from ..runtime.kv_cache import KVCacheManager
+    from ..runtime.runner import ModelRunner
+    model = AutoModel.from_pretrained(model_dir, device=device)
+    cfg = model.cfg
+    if calib_ids is None:
+        calib_ids = torch.randint(0, cfg.vocab_size, (num_samples, seq_len), generator=torch.Generator().manual_seed(0))
+    acts: Dict[str, List[torch.Tensor]] = {}
+    hooks = []
+    for name, mod in model.named_modules():
+        if isinstance(mod, LinearBase) and name.rsplit(".", 1)[-1] != "lm_head":
+            def pre(m, args, name=name):
+                x = args[0]
+                if isinstance(x, torch.Tensor):
+                    rows = x.detach().reshape(-1, x.shape[-1]).float()
+                    keep = acts.setdefault(name, [])
+                    if sum(t.shape[0] for t in keep) < max_rows:
+                        keep.append(rows[:max_rows].cpu())
+            hooks.append(mod.register_forward_pre_hook(pre))
+    page = 64
+    pages_per_seq = (calib_ids.shape[1] + page - 1) // page + 1
+    kv = KVCacheManager(cfg, num_pages=pages_per_seq * 2, page_size=page, max_seats=2, max_pages_per_seq=pages_per_seq, device=device)
+    runner = ModelRunner(model, kv)
+    runner.use_cuda_graphs = False
+    for row in calib_ids.tolist():
+        runner.prefill([0], [row])
+        kv.free(0)
+    for h in hooks:
+        h.remove()
+    out: Dict[str, torch.Tensor] = {}
+    for name, mod in model.named_modules():
+        if not isinstance(mod, LinearBase) or name not in acts or not hasattr(mod, "weight") or not mod.weight.dtype.is_floating_point:
+            continue
+        w = mod.weight.detach().float().cpu()
+        if w.dim() != 2 or w.shape[1] % group_size:
+            continue
+        x = torch.cat(acts[name], 0)[:max_rows]
+        want = x @ w.t()
+        s_x = x.abs().mean(0).clamp(min=1e-4)
+        best_err, best_s = float((x @ _int4_group_qdq(w, group_size).t() - want).pow(2).mean()), None
+        for step in range(1, grid + 1):
+            sc = s_x.pow(step / grid)
+            sc = (sc / (sc.max() * sc.min()).sqrt()).clamp(min=1e-4)
+            err = float(((x / sc) @ _int4_group_qdq(w * sc, group_size).t() - want).pow(2).mean())
+            if err < best_err:
+                best_err, best_s = err, sc
+        if best_s is not None:
+            parent = name.rsplit(".", 1)[0] if "." in name else ""
+            for src in (mod.sources or [name.rsplit(".", 1)[-1]]):
+                out[(parent + "." if parent else "") + src] = (1.0 / best_s).float()
+    return out
+
+
 @torch.no_grad()
 def calibrate_input_scales(model_dir: str, calib_ids: Optional[torch.Tensor] = None, num_samples: int = 8, seq_len: int = 128,
                            device: str = "cpu") -> Dict[str, float]:
@@ -89,6 +162,7 @@ def quantize_and_export(model_dir: str, out_dir: str, quantization: str = "nvfp4
     qcfg = build_quant_config(quantization, exclude, kv_cache_quantization, None if quantization == "nvfp4" else group_size)
     os.makedirs(out_dir, exist_ok=True)
     scales = calibrate_input_scales(model_dir, calib_ids, device=device) if (calibrate and quantization == "nvfp4") else {}
+    pre_quant = awq_search(model_dir, calib_ids, device=device, group_size=group_size) if (calibrate and quantization == "int4_awq") else {}
     reader = CheckpointReader(model_dir)
     out: Dict[str, torch.Tensor] = {}
     n_q = 0
@@ -128,6 +202,10 @@ def quantize_and_export(model_dir: str, out_dir: str, quantization: str = "nvfp4
             if w.shape[1] % g or w.shape[0] % 2:
                 out[key] = t.clone()
                 continue
+            pqs = pre_quant.get(canon[:-len(".weight")])
+            if pqs is not None:                       # activation-aware scaling: W · diag(s) is rounded, the run time applies 1 / s
+                w = w / pqs.to(w.device)[None, :]
+                out[base + ".pre_quant_scale"] = pqs.to(t.dtype).cpu()
             wg = w.reshape(w.shape[0], w.shape[1] // g, g)
             scale = (wg.abs().amax(-1) / 7.0).clamp(min=1e-8)
             q = (torch.round(wg / scale[..., None]).clamp(-8, 7) + 8).to(torch.uint8).reshape(w.shape)

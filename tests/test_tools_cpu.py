@@ -569,3 +569,40 @@ def test_stream_command_prints_pieces_as_they_are_generated(ckpt, tmp_path, caps
     assert texts[0] == ntok.decode(want[0], True).decode("utf-8", "replace")
     # --plain needs exactly one request
     assert trtedge(["stream", d, "--input-file", req_file, "--plain", "--device", "cpu"]) == 2
+
+
+def test_awq_search_lowers_the_output_error_of_int4_rounding(tmp_path):
+    """Activation-aware scaling on a checkpoint whose activations have a few dominant channels: the searched
+    ``pre_quant_scale`` is shared by fused projections, differs from 1, and the quantised model's logits are closer to the
+    16-bit model's than with plain rounding."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from tensorrt_edge_llm_b200.quantization.quantize import awq_search, quantize_and_export
+    d = str(tmp_path / "m")
+    os.makedirs(d)
+    cfg = LlamaConfig(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                      head_dim=32, rms_norm_eps=1e-6, rope_theta=1e4, max_position_embeddings=256, tie_word_embeddings=False)
+    torch.manual_seed(0)
+    m = LlamaForCausalLM(cfg).float().eval()
+    with torch.no_grad():                                   # a few loud input channels: norm weights with outliers
+        for layer in m.model.layers:
+            layer.input_layernorm.weight[:6] = 12.0
+            layer.post_attention_layernorm.weight[10:14] = 9.0
+    save_file(dict(m.state_dict()), os.path.join(d, "model.safetensors"))
+    hf = cfg.to_dict()
+    hf["torch_dtype"] = "float32"
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(hf, f)
+    pqs = awq_search(d, group_size=64)
+    q, k, g, u = (pqs.get(f"model.layers.0.{n}") for n in ("self_attn.q_proj", "self_attn.k_proj", "mlp.gate_proj", "mlp.up_proj"))
+    assert q is not None and torch.equal(q, k) and g is not None and torch.equal(g, u)           # fused projections share a scale
+    assert float((q - 1).abs().max()) > 0.05 and q[:6].mean() < q[6:].mean()                      # loud channels are scaled up in W
+    ids = list(range(5, 60))
+    ref_logits = _logits(d, ids)
+    errs = {}
+    for calibrate in (False, True):
+        out = str(tmp_path / f"q{int(calibrate)}")
+        quantize_and_export(d, out, "int4_awq", calibrate=calibrate, group_size=64)
+        f = SafetensorsFile(os.path.join(out, "model.safetensors"))
+        assert ("model.layers.0.self_attn.q_proj.pre_quant_scale" in set(f.keys())) == calibrate
+        errs[calibrate] = float((_logits(out, ids) - ref_logits).pow(2).mean())
+    assert errs[True] < errs[False]
