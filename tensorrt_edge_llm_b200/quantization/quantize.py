@@ -46,17 +46,49 @@ def _int4_group_qdq(w: torch.Tensor, g: int) -> torch.Tensor:
 
 
 @torch.no_grad()
-def awq_search(model_dir: str, calib_ids: Optional[torch.Tensor] = None, num_samples: int = 8, seq_len: int = 128, device: str = "cpu",
-               group_size: int = 128, grid: int = 20, max_rows: int = 512) -> Dict[str, torch.Tensor]:
-    """Activation-aware weight scaling (AWQ) for INT4 group quantisation.
+def gptq_quantize(w: torch.Tensor, x: torch.Tensor, group: int = 128, block: int = 128, damp: float = 0.01):
+    """GPTQ for one linear layer: quantise ``w [out, in]`` to asymmetric 4-bit groups column by column, after each column
+    spreading its rounding error over the columns not yet quantised, weighted by the inverse Hessian of the layer's
+    least-squares objective ``|x (w - q)ᵀ|²`` (``H = 2 xᵀx / n`` from calibration rows ``x [n, in]``, damped by ``damp`` of
+    its mean diagonal).  A group's scale and zero point are taken from the group's columns as they stand when the walk
+    reaches them.  Returns ``(codes [out, in] in 0..15, scales [out, in / group], zeros [out, in / group])`` with
+    ``w ≈ (codes - zero) · scale``."""
+    w = w.float().clone()
+    n_out, n_in = w.shape
+    if n_in % group or block % group:
+        raise ValueError("GPTQ: the input size must be a multiple of the group, the block a multiple of the group")
+    h = (x.float().t() @ x.float()) * (2.0 / max(x.shape[0], 1))
+    dead = h.diagonal() == 0
+    h[dead, dead] = 1.0
+    w[:, dead] = 0.0
+    h += torch.eye(n_in) * damp * float(h.diagonal().mean())
+    u = torch.linalg.cholesky(torch.cholesky_inverse(torch.linalg.cholesky(h)), upper=True)
+    codes = torch.zeros_like(w)
+    scales = torch.zeros(n_out, n_in // group)
+    zeros = torch.zeros(n_out, n_in // group)
+    for i1 in range(0, n_in, block):
+        i2 = min(i1 + block, n_in)
+        w1, err1, u1 = w[:, i1:i2].clone(), torch.zeros(n_out, i2 - i1), u[i1:i2, i1:i2]
+        for i in range(i2 - i1):
+            col = i1 + i
+            if col % group == 0:
+                seg = w1[:, i:i + group]
+                lo, hi = seg.amin(1).clamp(max=0), seg.amax(1).clamp(min=0)
+                sc = ((hi - lo) / 15.0).clamp(min=1e-8)
+                scales[:, col // group], zeros[:, col // group] = sc, torch.round(-lo / sc).clamp(0, 15)
+            sc, zp = scales[:, col // group], zeros[:, col // group]
+            q = torch.round(w1[:, i] / sc + zp).clamp(0, 15)
+            codes[:, col] = q
+            e = (w1[:, i] - (q - zp) * sc) / u1[i, i]
+            w1[:, i:] -= e[:, None] * u1[i, i:][None, :]
+            err1[:, i] = e
+        w[:, i2:] -= err1 @ u[i1:i2, i2:]
+    return codes, scales, zeros
 
-    Weights that multiply large activations matter more; scaling input channel ``c`` of ``W`` up by ``s_c`` before rounding
-    (and the activation down by the same factor at run time: the checkpoint's ``pre_quant_scale = 1 / s``) spends the 4-bit
-    grid where it counts.  Per linear layer — fused projections share their input, hence one scale vector — the search
-    takes ``s = mean|x|^alpha`` (normalised to geometric mean 1 between its extremes), tries ``alpha`` on a grid from 0
-    (plain rounding) to 1 and keeps the one with the smallest output error on calibration activations.
-    Returns ``{checkpoint module name: pre_quant_scale [in]}`` (fp32) for the layers where a scale other than 1 won.
-    (The search of ModelOpt's ``awq_lite``, which produces the ``pre_quant_scale`` tensors of INT4-AWQ checkpoints.)"""
+
+def _collect_linear_inputs(model_dir: str, calib_ids, num_samples: int, seq_len: int, device: str, max_rows: int):
+    """Run the 16-bit model over calibration ids and keep up to ``max_rows`` input rows of every linear layer.
+    Returns ``(model, {runtime module name: rows [n, in] fp32 on the CPU})``."""
     from ..model import AutoModel
     from ..models.linear import LinearBase
     from ..runtime.kv_cache import KVCacheManager
@@ -72,10 +104,9 @@ def awq_search(model_dir: str, calib_ids: Optional[torch.Tensor] = None, num_sam
             def pre(m, args, name=name):
                 x = args[0]
                 if isinstance(x, torch.Tensor):
-                    rows = x.detach().reshape(-1, x.shape[-1]).float()
                     keep = acts.setdefault(name, [])
                     if sum(t.shape[0] for t in keep) < max_rows:
-                        keep.append(rows[:max_rows].cpu())
+                        keep.append(x.detach().reshape(-1, x.shape[-1]).float()[:max_rows].cpu())
             hooks.append(mod.register_forward_pre_hook(pre))
     page = 64
     pages_per_seq = (calib_ids.shape[1] + page - 1) // page + 1
@@ -85,8 +116,40 @@ def awq_search(model_dir: str, calib_ids: Optional[torch.Tensor] = None, num_sam
     for row in calib_ids.tolist():
         runner.prefill([0], [row])
         kv.free(0)
-    for h in hooks:
-        h.remove()
+    for hk in hooks:
+        hk.remove()
+    return model, {k: torch.cat(v, 0)[:max_rows] for k, v in acts.items()}
+
+
+@torch.no_grad()
+def gptq_calibration_rows(model_dir: str, calib_ids: Optional[torch.Tensor] = None, num_samples: int = 8, seq_len: int = 128,
+                          device: str = "cpu", max_rows: int = 512) -> Dict[str, torch.Tensor]:
+    """Calibration input rows per *checkpoint* linear module (fused projections share theirs), for :func:`gptq_quantize`."""
+    from ..models.linear import LinearBase
+    model, acts = _collect_linear_inputs(model_dir, calib_ids, num_samples, seq_len, device, max_rows)
+    out: Dict[str, torch.Tensor] = {}
+    for name, mod in model.named_modules():
+        if isinstance(mod, LinearBase) and name in acts:
+            parent = name.rsplit(".", 1)[0] if "." in name else ""
+            for src in (mod.sources or [name.rsplit(".", 1)[-1]]):
+                out[(parent + "." if parent else "") + src] = acts[name]
+    return out
+
+
+@torch.no_grad()
+def awq_search(model_dir: str, calib_ids: Optional[torch.Tensor] = None, num_samples: int = 8, seq_len: int = 128, device: str = "cpu",
+               group_size: int = 128, grid: int = 20, max_rows: int = 512) -> Dict[str, torch.Tensor]:
+    """Activation-aware weight scaling (AWQ) for INT4 group quantisation.
+
+    Weights that multiply large activations matter more; scaling input channel ``c`` of ``W`` up by ``s_c`` before rounding
+    (and the activation down by the same factor at run time: the checkpoint's ``pre_quant_scale = 1 / s``) spends the 4-bit
+    grid where it counts.  Per linear layer — fused projections share their input, hence one scale vector — the search
+    takes ``s = mean|x|^alpha`` (normalised to geometric mean 1 between its extremes), tries ``alpha`` on a grid from 0
+    (plain rounding) to 1 and keeps the one with the smallest output error on calibration activations.
+    Returns ``{checkpoint module name: pre_quant_scale [in]}`` (fp32) for the layers where a scale other than 1 won.
+    (The search of ModelOpt's ``awq_lite``, which produces the ``pre_quant_scale`` tensors of INT4-AWQ checkpoints.)"""
+    from ..models.linear import LinearBase
+    model, acts = _collect_linear_inputs(model_dir, calib_ids, num_samples, seq_len, device, max_rows)
     out: Dict[str, torch.Tensor] = {}
     for name, mod in model.named_modules():
         if not isinstance(mod, LinearBase) or name not in acts or not hasattr(mod, "weight") or not mod.weight.dtype.is_floating_point:
@@ -94,7 +157,7 @@ def awq_search(model_dir: str, calib_ids: Optional[torch.Tensor] = None, num_sam
         w = mod.weight.detach().float().cpu()
         if w.dim() != 2 or w.shape[1] % group_size:
             continue
-        x = torch.cat(acts[name], 0)[:max_rows]
+        x = acts[name]
         want = x @ w.t()
         s_x = x.abs().mean(0).clamp(min=1e-4)
         best_err, best_s = float((x @ _int4_group_qdq(w, group_size).t() - want).pow(2).mean()), None
@@ -163,6 +226,7 @@ def quantize_and_export(model_dir: str, out_dir: str, quantization: str = "nvfp4
     os.makedirs(out_dir, exist_ok=True)
     scales = calibrate_input_scales(model_dir, calib_ids, device=device) if (calibrate and quantization == "nvfp4") else {}
     pre_quant = awq_search(model_dir, calib_ids, device=device, group_size=group_size) if (calibrate and quantization == "int4_awq") else {}
+    gptq_rows = gptq_calibration_rows(model_dir, calib_ids, device=device) if (calibrate and quantization == "int4_gptq") else {}
     reader = CheckpointReader(model_dir)
     out: Dict[str, torch.Tensor] = {}
     n_q = 0
@@ -193,8 +257,15 @@ def quantize_and_export(model_dir: str, out_dir: str, quantization: str = "nvfp4
             if (quantization == "int4_gptq" and (w.shape[1] % g or w.shape[0] % 8)) or w.shape[1] % 32:
                 out[key] = t.clone()
                 continue
-            enc = {"int4_gptq": lambda x: rp.encode_gptq(x, g), "fp8": rp.encode_fp8, "int8_sq": rp.encode_int8_sq,
-                   "mxfp8": rp.encode_mxfp8, "q8_0": rp.encode_q8_0}[quantization](w.cpu())
+            rows = gptq_rows.get(canon[:-len(".weight")]) if quantization == "int4_gptq" else None
+            if rows is not None and rows.shape[1] == w.shape[1]:
+                # error-compensated rounding against the layer's calibration inputs, then the GPTQ tensor layout
+                codes, sc, zp = gptq_quantize(w.cpu(), rows, g, block=max(g, 128) if 128 % g == 0 or g % 128 == 0 else g)
+                enc = {"qweight": rp._pack_int32_nibbles(codes.t().contiguous(), 0), "qzeros": rp._pack_int32_nibbles((zp.t().contiguous() - 1) % 16, 1),
+                       "scales": sc.t().contiguous().to(torch.float16), "g_idx": (torch.arange(w.shape[1]) // g).to(torch.int32)}
+            else:
+                enc = {"int4_gptq": lambda x: rp.encode_gptq(x, g), "fp8": rp.encode_fp8, "int8_sq": rp.encode_int8_sq,
+                       "mxfp8": rp.encode_mxfp8, "q8_0": rp.encode_q8_0}[quantization](w.cpu())
             for name, v in enc.items():
                 out[base + "." + name] = v.reshape(-1) if v.dim() == 0 else v
         else:

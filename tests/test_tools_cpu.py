@@ -606,3 +606,28 @@ def test_awq_search_lowers_the_output_error_of_int4_rounding(tmp_path):
         assert ("model.layers.0.self_attn.q_proj.pre_quant_scale" in set(f.keys())) == calibrate
         errs[calibrate] = float((_logits(out, ids) - ref_logits).pow(2).mean())
     assert errs[True] < errs[False]
+
+
+def test_gptq_error_compensation_beats_plain_rounding(ckpt, tmp_path):
+    """GPTQ on correlated inputs: the layer's output error is well below round-to-nearest with the same group layout, the
+    export decodes to the compensated weights, and the quantised checkpoint loads."""
+    from tensorrt_edge_llm_b200.checkpoint import repacking as rp
+    from tensorrt_edge_llm_b200.quantization.quantize import gptq_quantize, quantize_and_export
+    g = torch.Generator().manual_seed(0)
+    n_in, n_out, group = 128, 48, 32
+    basis = torch.randn(8, n_in, generator=g)
+    x = torch.randn(400, 8, generator=g) @ basis + 0.05 * torch.randn(400, n_in, generator=g)      # low-rank, strongly correlated
+    w = torch.randn(n_out, n_in, generator=g)
+    codes, sc, zp = gptq_quantize(w, x, group, block=64)
+    assert codes.min() >= 0 and codes.max() <= 15 and sc.shape == (n_out, n_in // group)
+    w_gptq = (codes - zp.repeat_interleave(group, 1)) * sc.repeat_interleave(group, 1)
+    w_rtn = rp.decode_gptq(**rp.encode_gptq(w, group))
+    err = lambda wq: float((x @ (wq - w).t()).pow(2).mean())
+    assert err(w_gptq) < 0.5 * err(w_rtn)
+    out = str(tmp_path / "gq")
+    quantize_and_export(ckpt, out, "int4_gptq", group_size=64)
+    f = SafetensorsFile(os.path.join(out, "model.safetensors"))
+    assert f.info("model.layers.0.mlp.down_proj.qweight")[1] == [256 // 8, 128]
+    ids = list(range(5, 45))
+    a, b = _logits(ckpt, ids), _logits(out, ids)
+    assert float(torch.nn.functional.cosine_similarity(a - a.mean(), b - b.mean(), dim=-1)) > 0.97
