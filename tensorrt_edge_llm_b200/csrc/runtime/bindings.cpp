@@ -406,7 +406,47 @@ PYBIND11_MODULE(_telb_runtime, m) {
         .def_readwrite("dtype", &LLMEngineConfig::dtype)
         .def_readwrite("quantization", &LLMEngineConfig::quantization)
         .def_readwrite("decoding_strategies", &LLMEngineConfig::decoding_strategies)
-        .def_readwrite("world_size", &LLMEngineConfig::world_size);
+        .def_readwrite("world_size", &LLMEngineConfig::world_size)
+        .def_static("from_runtime_config", [](const std::string& text) { return LLMEngineConfig::from_runtime_config(Json::parse(text)); })
+        .def_readwrite("kv_cache_dtype", &LLMEngineConfig::kv_cache_dtype)
+        .def_readwrite("intermediate_size", &LLMEngineConfig::intermediate_size)
+        .def_readwrite("max_position_embeddings", &LLMEngineConfig::max_position_embeddings)
+        .def_readwrite("rotary_dim", &LLMEngineConfig::rotary_dim)
+        .def_readwrite("rms_norm_eps", &LLMEngineConfig::rms_norm_eps)
+        .def_readwrite("rope_theta", &LLMEngineConfig::rope_theta)
+        .def_readwrite("rope_scaling_type", &LLMEngineConfig::rope_scaling_type)
+        .def_readwrite("rope_scaling_factor", &LLMEngineConfig::rope_scaling_factor)
+        .def_readwrite("mrope_section", &LLMEngineConfig::mrope_section)
+        .def_readwrite("has_qk_norm", &LLMEngineConfig::has_qk_norm)
+        .def_readwrite("sliding_window", &LLMEngineConfig::sliding_window)
+        .def_readwrite("layer_windows", &LLMEngineConfig::layer_windows)
+        .def_readwrite("layer_types", &LLMEngineConfig::layer_types)
+        .def_readwrite("mlp_types", &LLMEngineConfig::mlp_types)
+        .def_readwrite("num_kv_shared_layers", &LLMEngineConfig::num_kv_shared_layers)
+        .def_readwrite("num_experts", &LLMEngineConfig::num_experts)
+        .def_readwrite("num_experts_per_tok", &LLMEngineConfig::num_experts_per_tok)
+        .def_readwrite("moe_intermediate_size", &LLMEngineConfig::moe_intermediate_size)
+        .def_readwrite("quant_group_size", &LLMEngineConfig::quant_group_size)
+        .def_readwrite("draft_type", &LLMEngineConfig::draft_type)
+        .def_readwrite("dflash_projector_type", &LLMEngineConfig::dflash_projector_type)
+        .def_readwrite("dflash_block_size", &LLMEngineConfig::dflash_block_size)
+        .def_readwrite("dflash_version", &LLMEngineConfig::dflash_version)
+        .def_readwrite("draft_candidate_count", &LLMEngineConfig::draft_candidate_count)
+        .def_readwrite("dspark_markov_rank", &LLMEngineConfig::dspark_markov_rank)
+        .def_readwrite("is_diffusion", &LLMEngineConfig::is_diffusion)
+        .def_readwrite("diffusion_canvas_length", &LLMEngineConfig::diffusion_canvas_length)
+        .def_readwrite("eos_token_ids", &LLMEngineConfig::eos_token_ids)
+        .def_readwrite("mamba_num_heads", &LLMEngineConfig::mamba_num_heads)
+        .def_readwrite("mamba_d_state", &LLMEngineConfig::mamba_d_state)
+        .def_readwrite("gdn_num_v_heads", &LLMEngineConfig::gdn_num_v_heads)
+        .def("is_hybrid", &LLMEngineConfig::is_hybrid)
+        .def("is_moe", &LLMEngineConfig::is_moe)
+        .def("num_attention_layers", &LLMEngineConfig::num_attention_layers)
+        .def("num_recurrent_layers", &LLMEngineConfig::num_recurrent_layers)
+        .def("kv_bytes_per_token", &LLMEngineConfig::kv_bytes_per_token)
+        .def("kv_pool_bytes", &LLMEngineConfig::kv_pool_bytes)
+        .def("recurrent_state_bytes_per_seat", &LLMEngineConfig::recurrent_state_bytes_per_seat)
+        .def("validate", &LLMEngineConfig::validate);
     py::class_<LoraAdapter>(m, "LoraAdapter")
         .def(py::init<>())
         .def_readwrite("name", &LoraAdapter::name).def_readwrite("path", &LoraAdapter::path)

@@ -66,8 +66,49 @@ struct LLMEngineConfig {
     std::string dtype = "bfloat16", quantization = "fp16", kv_cache_dtype = "auto";
     std::vector<std::string> decoding_strategies = {"vanilla"};
     int world_size = 1;
+    // ---- the rest of what a prepared model's runtime_config.json records (`from_runtime_config`) ----
+    int intermediate_size = 0, max_position_embeddings = 0, rotary_dim = 0;
+    double rms_norm_eps = 1e-6, rope_theta = 10000.0, rope_scaling_factor = 1.0, final_logit_softcapping = 0.0;
+    std::string rope_scaling_type;                 // "", linear, dynamic, llama3, yarn, longrope
+    std::vector<int> mrope_section;                // multimodal RoPE: rotary pairs per (t, h, w) component
+    bool has_qk_norm = false, attention_bias = false, attention_sink_bias = false, attention_k_eq_v = false, has_value_norm = false;
+    int sliding_window = 0;                        // 0 = none
+    std::vector<int> layer_windows;                // per layer (empty = sliding_window everywhere)
+    std::vector<std::string> layer_types;          // attention / mamba / gdn / none per layer
+    std::vector<std::string> mlp_types;            // mlp / moe / none per layer
+    int num_kv_shared_layers = 0;
+    int num_experts = 0, num_experts_per_tok = 0, moe_intermediate_size = 0, shared_expert_intermediate_size = 0;
+    std::string router_type;
+    int quant_group_size = 0;
+    std::string lm_head_quantization;
+    // recurrent mixers (0 when the model has none)
+    int mamba_num_heads = 0, mamba_head_dim = 0, mamba_d_state = 0, mamba_n_groups = 0, mamba_conv_kernel = 0;
+    int gdn_num_k_heads = 0, gdn_num_v_heads = 0, gdn_head_k_dim = 0, gdn_head_v_dim = 0, gdn_conv_kernel = 0;
+    // draft heads
+    std::string draft_type, dflash_projector_type;
+    int draft_vocab_size = 0, eagle3_num_target_layers = 0, dflash_block_size = 0, dflash_version = 1, dflash_mask_token_id = 0;
+    int draft_candidate_count = 0, dspark_markov_rank = 0;
+    bool eagle_fc_norm = false, eagle_norm_output = false, dspark_enable_confidence_head = false;
+    // block diffusion
+    bool is_diffusion = false;
+    int diffusion_canvas_length = 0, diffusion_max_steps = 0;
+    std::vector<int> eos_token_ids;
+    int bos_token_id = -1;
+
     static LLMEngineConfig from_json(const Json& j);
+    // From the `runtime_config.json` of a prepared model ({"model": {...}, "deployment": {...}}).
+    static LLMEngineConfig from_runtime_config(const Json& j);
     Json to_json() const;
+    // Derived quantities.
+    bool is_hybrid() const;
+    bool is_moe() const { return num_experts > 0; }
+    int num_attention_layers() const;              // layers that own a KV cache (KV-shared layers excluded)
+    int num_recurrent_layers() const;
+    long long kv_bytes_per_token() const;          // every KV-owning layer, K and V, at the cache's element size
+    long long kv_pool_bytes() const;               // max_batch_size sequences of max_kv_cache_capacity tokens, whole pages
+    long long recurrent_state_bytes_per_seat() const;
+    // Empty when the configuration is consistent, else the first problem found.
+    std::string validate() const;
 };
 
 // ---- LoRA registry ------------------------------------------------------------------------------

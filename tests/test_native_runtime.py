@@ -1,6 +1,8 @@
 """The C++ runtime (page table, prefix cache, scheduling policy, step planner, request engine,
 streaming, tokenizer, chat template) driven from Python with scripted sessions — no GPU."""
 import json
+
+import torch
 import threading
 import time
 
@@ -423,3 +425,45 @@ def test_prefix_cache_eviction_planner_and_chain_order():
     t.reserve(2, 13)
     assert small.insert(list(range(13)), 12, t.pages(2)) == 3 and small.records == 2
     assert small.drop_records(5) == 2 and small.records == 0
+
+
+def test_engine_config_from_a_prepared_models_runtime_config():
+    """The native config reads what `trtedge build` records: model geometry, quantisation, per-layer types, recurrent and draft
+    sections, deployment limits; its derived sizes match the Python cache manager's, and validation names the first problem."""
+    import dataclasses
+    from tensorrt_edge_llm_b200.checkpoint.artifacts import runtime_config_dict
+    from tensorrt_edge_llm_b200.config import GdnConfig, MambaConfig, QuantConfig, hybrid_nemotron_config, qwen3_8b_config
+    from tensorrt_edge_llm_b200.runtime.kv_cache import KVCacheManager
+    dense = qwen3_8b_config(dtype="float16", quant=QuantConfig(quant_type="nvfp4", group_size=16))
+    text = json.dumps(runtime_config_dict(dense, 64, 1024, 1216, 1), default=str)
+    c = rt.LLMEngineConfig.from_runtime_config(text)
+    assert (c.model_type, c.num_layers, c.num_heads, c.num_kv_heads, c.head_dim, c.vocab_size) == ("qwen3", 36, 32, 8, 128, 151936)
+    assert (c.quantization, c.quant_group_size, c.max_batch_size, c.max_input_len, c.max_kv_cache_capacity, c.kv_page_size) == ("nvfp4", 16, 64, 1024, 1216, 64)
+    assert c.has_qk_norm and c.rotary_dim == 128 and c.rope_theta == 1e6 and not c.is_hybrid() and not c.is_moe() and c.validate() == ""
+    assert c.num_attention_layers() == 36 and c.kv_bytes_per_token() == 2 * 36 * 8 * 128 * 2
+    kv = KVCacheManager(qwen3_8b_config(dtype="float16", num_hidden_layers=2), num_pages=8, page_size=64, max_seats=1, max_pages_per_seq=4)
+    assert kv.pool.element_size() * kv.pool[0, 0].numel() // 64 * 36 == c.kv_bytes_per_token()
+    assert c.kv_pool_bytes() == c.kv_bytes_per_token() * 64 * (19 * 64 + 1)
+    hyb = hybrid_nemotron_config(num_hidden_layers=8, vocab_size=500, hidden_size=64, intermediate_size=128, num_attention_heads=4,
+                                 num_key_value_heads=2, head_dim=16, dtype="bfloat16", max_position_embeddings=512,
+                                 mamba=MambaConfig(num_heads=4, head_dim=8, d_state=16, n_groups=2, conv_kernel=4),
+                                 gdn=GdnConfig(num_k_heads=2, num_v_heads=4, head_k_dim=8, head_v_dim=8, conv_kernel=4))
+    h = rt.LLMEngineConfig.from_runtime_config(json.dumps(runtime_config_dict(hyb, 2, 64, 128, 1), default=str))
+    assert h.is_hybrid() and h.num_recurrent_layers() == sum(t in ("mamba", "gdn") for t in hyb.layer_types)
+    assert h.num_attention_layers() == sum(t == "attention" for t in hyb.layer_types) and h.mamba_d_state == 16 and h.gdn_num_v_heads == 4
+    from tensorrt_edge_llm_b200.models.nemotron_h import RecurrentState
+    st = RecurrentState(hyb, 1, "cpu", torch.bfloat16)
+    assert h.recurrent_state_bytes_per_seat() == sum(t.numel() * t.element_size() for t in st.pools())
+    # validation
+    bad = rt.LLMEngineConfig.from_runtime_config(text)
+    bad.num_kv_heads = 5
+    assert "multiple" in bad.validate()
+    bad = rt.LLMEngineConfig.from_runtime_config(text)
+    bad.max_kv_cache_capacity = 100
+    assert "max_kv_cache_capacity" in bad.validate()
+    bad = rt.LLMEngineConfig.from_runtime_config(text)
+    bad.layer_types = ["attention"] * 3
+    assert "layer_types" in bad.validate()
+    draft = dataclasses.replace(dense, draft_type="dflash", dflash_block_size=8, dflash_version=2, dflash_projector_type="lilicorr")
+    d = rt.LLMEngineConfig.from_runtime_config(json.dumps(runtime_config_dict(draft, 1, 64, 128, 1), default=str))
+    assert (d.draft_type, d.dflash_block_size, d.dflash_version, d.dflash_projector_type) == ("dflash", 8, 2, "lilicorr")
