@@ -623,6 +623,22 @@ def _detect_qk_norm(model_dir: str, hf: Dict[str, Any]) -> Optional[bool]:
 
 def _parse_gemma(llm: Dict[str, Any], n_layers: int) -> Dict[str, Any]:
     """Gemma 2 / 3 text decoders: alternating sliding-window and full-attention layers with their own RoPE bases."""
+    # Gemma 3n / 4 checkpoints add pieces this decoder does not have; refuse them by name instead of loading them as Gemma 3
+    missing = []
+    gh = llm.get("global_head_dim")
+    if gh and int(gh) != int(llm.get("head_dim") or gh):
+        missing.append("full-attention layers with a head size of their own (global_head_dim)")
+    if llm.get("num_global_key_value_heads") and int(llm["num_global_key_value_heads"]) != int(llm.get("num_key_value_heads") or 0):
+        missing.append("full-attention layers with a KV head count of their own (num_global_key_value_heads)")
+    if int(llm.get("hidden_size_per_layer_input") or 0) > 0:
+        missing.append("per-layer input embeddings inside the decoder (hidden_size_per_layer_input)")
+    if llm.get("altup_num_inputs") or llm.get("laurel_rank"):
+        missing.append("AltUp / LAuReL blocks")
+    if int(llm.get("num_experts") or 0) > 0 or llm.get("enable_moe_block"):
+        missing.append("the Gemma mixture-of-experts block")
+    if missing:
+        raise NotImplementedError(f"{llm.get('model_type', 'gemma')}: this checkpoint needs " + "; ".join(missing) +
+                                  ", which the Gemma decoder here does not build")
     win = int(llm.get("sliding_window") or 0)
     kinds = llm.get("layer_types")
     if not kinds:

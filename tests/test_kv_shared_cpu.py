@@ -124,3 +124,18 @@ def test_values_from_keys_and_weightless_value_norm():
     assert torch.allclose(got[0], want[7], atol=2e-4)
     for j in range(8, 12):
         assert torch.allclose(r.step([0], [[seq[j]]])[0], want[j], atol=2e-4)
+
+
+def test_gemma_checkpoints_with_unbuilt_blocks_are_refused_by_name():
+    from tensorrt_edge_llm_b200.config import ModelConfig
+    base = {"model_type": "gemma3_text", "hidden_size": 64, "intermediate_size": 128, "num_hidden_layers": 6, "num_attention_heads": 4,
+            "num_key_value_heads": 2, "head_dim": 16, "vocab_size": 300, "sliding_window": 32, "rms_norm_eps": 1e-6, "torch_dtype": "float32"}
+    assert ModelConfig.from_hf_dict(base).layer_windows == [32, 32, 32, 32, 32, 0]
+    shared = ModelConfig.from_hf_dict({**base, "num_hidden_layers": 12, "sliding_window_pattern": 3, "num_kv_shared_layers": 2,
+                                       "attention_k_eq_v": True, "use_value_norm": True})
+    assert shared.num_kv_shared_layers == 2 and shared.attention_k_eq_v and shared.has_value_norm
+    assert shared.kv_donor(9) == -1 and shared.kv_donor(10) == 9 and shared.kv_donor(11) == 8      # sliding ← sliding, full ← full
+    for extra, word in (({"global_head_dim": 32}, "global_head_dim"), ({"hidden_size_per_layer_input": 8}, "per-layer input"),
+                        ({"altup_num_inputs": 4}, "AltUp"), ({"num_experts": 8}, "mixture-of-experts")):
+        with pytest.raises(NotImplementedError, match=word):
+            ModelConfig.from_hf_dict({**base, "model_type": "gemma4_text", **extra})
