@@ -436,8 +436,6 @@ class EagleDecoder:
                  eos_token_id: Optional[int] = None, sampling: Optional[dict] = None) -> List[List[int]]:
         """``sampling`` = ``{"temperature", "top_k", "top_p", "seed"}`` switches the verification from greedy matching to
         rejection sampling; the emitted tokens are then distributed as plain sampling from the target would be."""
-        if sampling is not None and self.hybrid:
-            raise NotImplementedError("sampled speculative decoding on hybrid targets is not built")
         self.sampling = dict(sampling) if sampling is not None and sampling.get("temperature", 0.0) >= 1e-3 else None
         self._sample_gen = None
         first = self.prefill(seats, prompts)

@@ -217,6 +217,14 @@ def test_hybrid_target_chain_verify_with_state_replay():
     # forced partial acceptance exercises restore + replay on every round and still matches
     dec = _decoder(model, _OracleDraft(draft, streams), SpecConfig(draft_steps=3, top_k=1, verify_tokens=4, force_accept_len=2))
     assert dec.generate([0, 1], prompts, 14) == want and dec.stats.replays >= 10
+    # sampled requests: rejection sampling along the chain, the same state commit; with a sharply peaked target and a very low
+    # temperature the draws are the arg-max, so the output is the greedy continuation again
+    with torch.no_grad():
+        model.lm_head.weight.mul_(400.0)
+    peaked = _greedy(model, prompts, 12)
+    dec = _decoder(model, draft, SpecConfig(draft_steps=3, top_k=1, verify_tokens=4))
+    got = dec.generate([0, 1], prompts, 12, sampling={"temperature": 0.002, "top_k": 0, "top_p": 1.0, "seed": 3})
+    assert got == peaked and dec.stats.recurrent_replays > 0
 
 
 def test_sampled_acceptance_reference_follows_the_target_distribution():
