@@ -32,6 +32,8 @@ class _Adapted:
 class LoraLinear(nn.Module):
     """Wraps a linear layer; adds the active adapter's low-rank update to its output."""
 
+    grouped_calls = 0                   # how often the stacked form ran (diagnostics / tests)
+
     def __init__(self, base: LinearBase):
         super().__init__()
         self.base = base
@@ -40,12 +42,69 @@ class LoraLinear(nn.Module):
         # per-step routing for batches that mix adapters: [(first row, end row, adapter name or None)], rows of the step
         self.segments: Optional[List[Tuple[int, int, Optional[str]]]] = None
         self.segment_rows = 0
+        self.row_gid: Optional[torch.Tensor] = None
+        self.adapter_ids: Dict[str, int] = {}
+        self.grouped = True             # steps that mix adapters use the stacked two-GEMM form (False: one GEMM pair per segment)
 
     def __getattr__(self, name):            # the model reads attributes such as fused_input_scale, tp_mode, weight
         try:
             return super().__getattr__(name)
         except AttributeError:
             return getattr(super().__getattr__("base"), name)
+
+    def _stacked(self, names: Tuple[str, ...]):
+        """Low-rank factors of several adapters side by side, per adapted column block of this layer:
+        ``[(col, n_out, A_cat [m · r, in], B_cat [n_out, m · r], r, {adapter: block index})]`` (ranks padded to the largest)."""
+        cache = self.__dict__.setdefault("_stack_cache", {})
+        plan = cache.get(names)
+        if plan is not None:
+            return plan
+        blocks: Dict[Tuple[int, int], List[Tuple[str, torch.Tensor, torch.Tensor]]] = {}
+        for name in names:
+            for a, b, col in self.adapters[name].parts:
+                blocks.setdefault((col, b.shape[0]), []).append((name, a, b))
+        plan = []
+        for (col, n_out), members in blocks.items():
+            r = max(a.shape[0] for _, a, _ in members)
+            a_cat = torch.zeros(len(members) * r, members[0][1].shape[1], dtype=members[0][1].dtype, device=members[0][1].device)
+            b_cat = torch.zeros(n_out, len(members) * r, dtype=members[0][2].dtype, device=members[0][2].device)
+            index = {}
+            for j, (name, a, b) in enumerate(members):
+                a_cat[j * r:j * r + a.shape[0]] = a
+                b_cat[:, j * r:j * r + b.shape[1]] = b
+                index[name] = j
+            plan.append((col, n_out, a_cat, b_cat, r, index))
+        if len(cache) > 8:
+            cache.clear()
+        cache[names] = plan
+        return plan
+
+    def _add_grouped(self, y, x, segments) -> None:
+        """Batches that mix adapters, in two GEMMs per column block whatever the number of segments (the reference's grouped LoRA
+        GEMM, ``cpp/kernels/lora/groupedLoraGemm``): every row is projected through all the step's adapters' ``A`` factors at
+        once, the blocks of the adapters a row does not use are zeroed, and one GEMM with the concatenated ``B`` factors adds
+        the updates.  The extra ``A`` work is ``m · r`` columns, tiny next to the layer itself."""
+        names = tuple(sorted({n for _, _, n in segments if n and n in self.adapters}))
+        if not names:
+            return
+        LoraLinear.grouped_calls += 1
+        rows = y.shape[0]
+        gid = self.row_gid                       # per row: the adapter's position in the manager's list (-1 = none), built once per step
+        if gid is None or gid.shape[0] != rows:
+            gid = torch.full((rows,), -1, dtype=torch.long)
+            for r0, r1, name in segments:
+                if name in self.adapter_ids and r1 > r0:
+                    gid[r0:r1] = self.adapter_ids[name]
+        gid = gid.to(y.device)
+        for col, n_out, a_cat, b_cat, r, index in self._stacked(names):
+            lut = torch.full((max(self.adapter_ids.values(), default=0) + 2,), -1, dtype=torch.long)
+            for name, j in index.items():
+                lut[self.adapter_ids[name] + 1] = j
+            owner = lut.to(y.device)[gid + 1]
+            t = ops.linear(x, a_cat)                                             # [T, m · r]
+            block = torch.arange(a_cat.shape[0], device=y.device) // r
+            t = t * (block[None, :] == owner[:, None]).to(t.dtype)
+            y[..., col:col + n_out] += ops.linear(t, b_cat)
 
     def _add(self, y, x16, ad: _Adapted):
         for a, b, col in ad.parts:
@@ -60,6 +119,10 @@ class LoraLinear(nn.Module):
             # of that request's adapter; rows without an adapter pass through
             if not isinstance(x, torch.Tensor):
                 raise RuntimeError("LoRA needs 16-bit activations: disable fused activation quantisation for adapted layers")
+            live = {n for _, _, n in self.segments if n and n in self.adapters}
+            if len(live) > 1 and self.grouped:
+                self._add_grouped(y, x, self.segments)
+                return y
             for r0, r1, name in self.segments:
                 ad = self.adapters.get(name) if name else None
                 if ad is not None and r1 > r0:
@@ -159,6 +222,8 @@ class LoraManager:
                 if old is not None and w.active is old:
                     w.active = None
         self._generation[name] = self._generation.get(name, 0) + 1
+        for w in self._wrapped.values():
+            w.__dict__.pop("_stack_cache", None)          # stacked factors are rebuilt with the new adapter set
         for ckpt_mod in meta["modules"]:
             mod_name, src, base = self._locate(ckpt_mod)
             a, b = f.get(f"lora_A_{ckpt_mod}").clone(), f.get(f"lora_B_{ckpt_mod}").clone()
@@ -184,9 +249,20 @@ class LoraManager:
                 rows = max(rows, r1)
             if not any(name for _, _, name in segments):
                 segments = None                      # nobody uses an adapter this step: skip the routing entirely
+        gid = None
+        ids = {n: i for i, n in enumerate(self.names)}
+        if segments is not None:
+            gid = torch.full((rows,), -1, dtype=torch.long)
+            for r0, r1, name in segments:
+                if name and r1 > r0:
+                    gid[r0:r1] = ids[name]
+            dev = next((w.base.weight.device for w in self._wrapped.values()), None)
+            if dev is not None:
+                gid = gid.to(dev)                     # one upload per step, shared by every adapted layer
         for w in self._wrapped.values():
             w.segments = list(segments) if segments is not None else None
             w.segment_rows = rows
+            w.row_gid, w.adapter_ids = gid, ids
 
     def set_active(self, name: Optional[str]) -> None:
         if name is not None and name not in self.names:

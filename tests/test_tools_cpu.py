@@ -359,10 +359,18 @@ def test_lora_per_request_under_in_flight_batching(ckpt, tmp_path):
     ifb.load_lora("one", r1)
     ifb.load_lora("two", r2)
     hs = [ifb.submit(p, SamplingParams(max_tokens=6, lora_name=n, ignore_eos=True)) for p, n in zip(prompts, ("one", None, "two"))]
+    from tensorrt_edge_llm_b200.lora.runtime import LoraLinear
+    calls0 = LoraLinear.grouped_calls
     got = [h.get(60.0) for h in hs]
     assert got == [one[0], base[1], two[2]]
+    assert LoraLinear.grouped_calls > calls0            # steps that mixed both adapters ran the stacked two-GEMM form
     with pytest.raises(ValueError):
         ifb.submit(prompts[0], SamplingParams(max_tokens=2, lora_name="three"))
+    # the per-segment form gives the same tokens
+    for w in ifb.lora._wrapped.values():
+        w.grouped = False
+    hs = [ifb.submit(p, SamplingParams(max_tokens=6, lora_name=n, ignore_eos=True)) for p, n in zip(prompts, ("one", None, "two"))]
+    assert [h.get(60.0) for h in hs] == got
     ifb.close()
 
 
