@@ -3,9 +3,9 @@
 // parts of chat requests (data: URIs are almost always PNG or JPEG) need no third-party decoder.
 //
 // Counterpart in the reference: cpp/runtime/imageUtils.cpp, which hands these formats to the stb_image header.
-// Covered: PNG non-interlaced, colour types 0 / 2 / 3 / 4 / 6, bit depths 1 / 2 / 4 / 8 / 16 (alpha is dropped, 16-bit
+// Covered: PNG non-interlaced and Adam7-interlaced, colour types 0 / 2 / 3 / 4 / 6, bit depths 1 / 2 / 4 / 8 / 16 (alpha is dropped, 16-bit
 // samples keep their high byte); JPEG sequential Huffman (SOF0 / SOF1), 8-bit, one or three components, sampling
-// factors 1 or 2, restart intervals.  Not covered (a clear error is raised): Adam7 interlacing, progressive,
+// factors 1 or 2, restart intervals.  Not covered (a clear error is raised): progressive,
 // arithmetic-coded, lossless and four-component JPEG.
 #include "media.h"
 
@@ -224,7 +224,7 @@ Image decode_png(const std::string& bytes) {
     }
     if (ctype < 0 || w == 0 || h == 0 || w > (1u << 15) || h > (1u << 15)) bad("PNG without a usable header");
     if (static_cast<uint64_t>(w) * h > max_image_pixels()) bad("PNG image has more pixels than the decoder's limit");
-    if (interlace) bad("interlaced (Adam7) PNG images are not read");
+    if (interlace != 0 && interlace != 1) bad("unknown PNG interlace method");
     int samples;
     switch (ctype) {
         case 0: samples = 1; break;
@@ -237,57 +237,82 @@ Image decode_png(const std::string& bytes) {
     const bool depth_ok = depth == 8 || ((ctype == 0 || ctype == 3) && (depth == 1 || depth == 2 || depth == 4)) || (ctype != 3 && depth == 16);
     if (!depth_ok) bad("PNG bit depth does not fit its colour type");
     if (ctype == 3 && palette.size() < 3) bad("palette PNG without a palette");
-    const size_t row_bytes = (static_cast<size_t>(w) * samples * depth + 7) / 8;
     const int bpp = std::max(1, samples * depth / 8);
-    const std::string raw = inflate_zlib(idat, (row_bytes + 1) * h);
-    if (raw.size() < (row_bytes + 1) * h) bad("PNG image data is shorter than its header says");
-    std::vector<uint8_t> prev(row_bytes, 0), cur(row_bytes);
+    // A non-interlaced image is one pass over every pixel; Adam7 stores seven reduced images (pixel (x0 + i dx, y0 + j dy) of pass
+    // p), each filtered on its own with a fresh "previous row".
+    struct Pass { uint32_t x0, y0, dx, dy; };
+    static const Pass kAdam7[7] = {{0, 0, 8, 8}, {4, 0, 8, 8}, {0, 4, 4, 8}, {2, 0, 4, 4}, {0, 2, 2, 4}, {1, 0, 2, 2}, {0, 1, 1, 2}};
+    static const Pass kWhole[1] = {{0, 0, 1, 1}};
+    const Pass* passes = interlace ? kAdam7 : kWhole;
+    const int n_pass = interlace ? 7 : 1;
+    auto pass_dims = [&](const Pass& ps, uint32_t& pw, uint32_t& ph) {
+        pw = w > ps.x0 ? (w - ps.x0 + ps.dx - 1) / ps.dx : 0;
+        ph = h > ps.y0 ? (h - ps.y0 + ps.dy - 1) / ps.dy : 0;
+    };
+    size_t raw_need = 0;
+    for (int q = 0; q < n_pass; ++q) {
+        uint32_t pw, ph;
+        pass_dims(passes[q], pw, ph);
+        if (pw && ph) raw_need += ((static_cast<size_t>(pw) * samples * depth + 7) / 8 + 1) * ph;
+    }
+    const std::string raw = inflate_zlib(idat, raw_need);
+    if (raw.size() < raw_need) bad("PNG image data is shorter than its header says");
     Image im;
     im.width = static_cast<int>(w);
     im.height = static_cast<int>(h);
     im.channels = 3;
     im.pixels.resize(static_cast<size_t>(w) * h * 3);
-    for (uint32_t y = 0; y < h; ++y) {
-        const uint8_t* src = reinterpret_cast<const uint8_t*>(raw.data()) + (row_bytes + 1) * y;
-        const int filter = src[0];
-        ++src;
-        for (size_t i = 0; i < row_bytes; ++i) {
-            const int a = i >= static_cast<size_t>(bpp) ? cur[i - bpp] : 0, b = prev[i], c = i >= static_cast<size_t>(bpp) ? prev[i - bpp] : 0;
-            int v = src[i];
-            switch (filter) {
-                case 0: break;
-                case 1: v += a; break;
-                case 2: v += b; break;
-                case 3: v += (a + b) >> 1; break;
-                case 4: v += paeth(a, b, c); break;
-                default: bad("unknown PNG row filter");
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(raw.data());
+    for (int q = 0; q < n_pass; ++q) {
+        const Pass& ps = passes[q];
+        uint32_t pw, ph;
+        pass_dims(ps, pw, ph);
+        if (!pw || !ph) continue;
+        const size_t row_bytes = (static_cast<size_t>(pw) * samples * depth + 7) / 8;
+        std::vector<uint8_t> prev(row_bytes, 0), cur(row_bytes);
+        for (uint32_t y = 0; y < ph; ++y) {
+            const int filter = src[0];
+            ++src;
+            for (size_t i = 0; i < row_bytes; ++i) {
+                const int a = i >= static_cast<size_t>(bpp) ? cur[i - bpp] : 0, b = prev[i], c = i >= static_cast<size_t>(bpp) ? prev[i - bpp] : 0;
+                int v = src[i];
+                switch (filter) {
+                    case 0: break;
+                    case 1: v += a; break;
+                    case 2: v += b; break;
+                    case 3: v += (a + b) >> 1; break;
+                    case 4: v += paeth(a, b, c); break;
+                    default: bad("unknown PNG row filter");
+                }
+                cur[i] = static_cast<uint8_t>(v);
             }
-            cur[i] = static_cast<uint8_t>(v);
-        }
-        uint8_t* dst = &im.pixels[static_cast<size_t>(y) * w * 3];
-        for (uint32_t x = 0; x < w; ++x) {
-            auto sample = [&](int k) -> int {           // k-th sample of pixel x, scaled to 8 bits
-                if (depth == 8) return cur[static_cast<size_t>(x) * samples + k];
-                if (depth == 16) return cur[(static_cast<size_t>(x) * samples + k) * 2];
-                const size_t bit = static_cast<size_t>(x) * depth;
-                const int v = (cur[bit >> 3] >> (8 - depth - static_cast<int>(bit & 7))) & ((1 << depth) - 1);
-                return ctype == 3 ? v : v * 255 / ((1 << depth) - 1);
-            };
-            if (ctype == 3) {
-                const size_t idx = static_cast<size_t>(sample(0)) * 3;
-                if (idx + 3 > palette.size()) bad("PNG palette index out of range");
-                dst[3 * x] = palette[idx];
-                dst[3 * x + 1] = palette[idx + 1];
-                dst[3 * x + 2] = palette[idx + 2];
-            } else if (ctype == 0 || ctype == 4) {
-                dst[3 * x] = dst[3 * x + 1] = dst[3 * x + 2] = static_cast<uint8_t>(sample(0));
-            } else {
-                dst[3 * x] = static_cast<uint8_t>(sample(0));
-                dst[3 * x + 1] = static_cast<uint8_t>(sample(1));
-                dst[3 * x + 2] = static_cast<uint8_t>(sample(2));
+            src += row_bytes;
+            uint8_t* row = &im.pixels[static_cast<size_t>(ps.y0 + y * ps.dy) * w * 3];
+            for (uint32_t x = 0; x < pw; ++x) {
+                uint8_t* dst = row + static_cast<size_t>(ps.x0 + x * ps.dx) * 3;
+                auto sample = [&](int k) -> int {           // k-th sample of pixel x of this pass, scaled to 8 bits
+                    if (depth == 8) return cur[static_cast<size_t>(x) * samples + k];
+                    if (depth == 16) return cur[(static_cast<size_t>(x) * samples + k) * 2];
+                    const size_t bit = static_cast<size_t>(x) * depth;
+                    const int v = (cur[bit >> 3] >> (8 - depth - static_cast<int>(bit & 7))) & ((1 << depth) - 1);
+                    return ctype == 3 ? v : v * 255 / ((1 << depth) - 1);
+                };
+                if (ctype == 3) {
+                    const size_t idx = static_cast<size_t>(sample(0)) * 3;
+                    if (idx + 3 > palette.size()) bad("PNG palette index out of range");
+                    dst[0] = palette[idx];
+                    dst[1] = palette[idx + 1];
+                    dst[2] = palette[idx + 2];
+                } else if (ctype == 0 || ctype == 4) {
+                    dst[0] = dst[1] = dst[2] = static_cast<uint8_t>(sample(0));
+                } else {
+                    dst[0] = static_cast<uint8_t>(sample(0));
+                    dst[1] = static_cast<uint8_t>(sample(1));
+                    dst[2] = static_cast<uint8_t>(sample(2));
+                }
             }
+            prev.swap(cur);
         }
-        prev.swap(cur);
     }
     return im;
 }
