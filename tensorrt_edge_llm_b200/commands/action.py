@@ -78,7 +78,7 @@ def run_requests(llm, expert, body, multimodal=None, template=None, num_steps: i
 
 def _wav(data: bytes):
     from ..runtime import native as rt
-    clip = rt.parse_wav(data)
+    clip = rt.parse_audio(data)
     import numpy as np
     return np.asarray(clip.samples, dtype=np.float32), clip.sample_rate
 

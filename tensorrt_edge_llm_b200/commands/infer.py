@@ -105,7 +105,7 @@ def _with_media(llm, multimodal, messages, render):
         if piece == server_app._IMG:
             req.image(next(it)[1])
         elif piece == server_app._AUD:
-            clip = rt.parse_wav(next(it)[1])
+            clip = rt.parse_audio(next(it)[1])
             req.audio(clip.samples, clip.sample_rate)
         elif piece:
             req.text(list(llm.tokenizer.encode(piece)))

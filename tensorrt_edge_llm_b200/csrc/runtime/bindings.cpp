@@ -507,6 +507,9 @@ PYBIND11_MODULE(_telb_runtime, m) {
         .def_property_readonly("samples", [](const AudioClip& c) { return py::array_t<float>(c.samples.size(), c.samples.data()); });
     m.def("parse_wav", [](py::bytes b) { return parse_wav(std::string(b)); });
     m.def("load_wav", &load_wav);
+    m.def("parse_flac", [](py::bytes b) { return parse_flac(std::string(b)); });
+    m.def("parse_audio", [](py::bytes b) { return parse_audio(std::string(b)); });
+    m.def("load_audio", &load_audio);
     m.def("resample_linear", [](py::array_t<float, py::array::c_style | py::array::forcecast> x, int from_rate, int to_rate) {
         std::vector<float> v(x.data(), x.data() + x.size());
         const auto y = resample_linear(v, from_rate, to_rate);

@@ -3,8 +3,8 @@
 //
 // Counterparts in the reference: cpp/runtime/{audioLoader,audioUtils,melSpectrogram,imageUtils}.cpp (which lean on
 // the third-party miniaudio and stb single-header libraries; here the formats that need no entropy decoder are
-// parsed directly: RIFF/WAVE PCM16 / PCM24 / PCM32 / float32, binary PPM / PGM and uncompressed BMP; PNG and
-// sequential JPEG have decoders of their own in image_codecs.cpp / jpeg_decoder.cpp).
+// parsed directly: RIFF/WAVE PCM16 / PCM24 / PCM32 / float32, binary PPM / PGM and uncompressed BMP; PNG, sequential
+// JPEG and FLAC have decoders of their own in image_codecs.cpp / jpeg_decoder.cpp / flac_decoder.cpp).
 #pragma once
 
 #include <cstdint>
@@ -20,6 +20,9 @@ struct AudioClip {
 
 AudioClip parse_wav(const std::string& bytes);                       // multi-channel input is averaged to mono
 AudioClip load_wav(const std::string& path);
+AudioClip parse_flac(const std::string& bytes);                      // native FLAC streams (flac_decoder.cpp); channels averaged to mono
+AudioClip parse_audio(const std::string& bytes);                     // by magic: RIFF/WAVE or FLAC
+AudioClip load_audio(const std::string& path);
 std::vector<float> resample_linear(const std::vector<float>& x, int from_rate, int to_rate);
 
 struct MelConfig {

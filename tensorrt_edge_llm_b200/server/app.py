@@ -270,7 +270,7 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
             if piece == _IMG:
                 req.image(next(it)[1])
             elif piece == _AUD:
-                clip = rt.parse_wav(next(it)[1])
+                clip = rt.parse_audio(next(it)[1])
                 req.audio(clip.samples, clip.sample_rate)
             elif piece:
                 req.text(encode(piece))
@@ -317,7 +317,7 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
             fmt = str(form.get("response_format", "json") or "json")
             if fmt not in ("json", "text"):
                 raise ValueError("response_format must be json or text")
-            clip = rt.parse_wav(data)
+            clip = rt.parse_audio(data)
             hint, language = str(form.get("prompt", "") or ""), str(form.get("language", "") or "")
             ask = "Transcribe the audio" + (f" (language: {language})" if language else "") + "." + (f" {hint}" if hint else "")
             prompt = template.apply([{"role": "user", "content": _AUD + ask}], True, None, False)
