@@ -1,8 +1,10 @@
-// Sequential Huffman JPEG decoder (ITU T.81 baseline / extended sequential, 8-bit samples).
+// Huffman JPEG decoder (ITU T.81 baseline / extended sequential and progressive, 8-bit samples).
 //
-// Flow: markers → quantisation tables (DQT), Huffman tables (DHT), frame header (SOF0 / SOF1), restart interval (DRI) →
-// for every MCU of the scan: per component block, a DC difference and run-length coded AC coefficients in zig-zag order
-// → dequantise → 8×8 inverse DCT → planes → chroma interpolated up to the luma grid → YCbCr → RGB.
+// Flow: markers → quantisation tables (DQT), Huffman tables (DHT), frame header (SOF0 / SOF1 / SOF2), restart interval
+// (DRI) → for every MCU of the scan: per component block, a DC difference and run-length coded AC coefficients in zig-zag
+// order → dequantise → 8×8 inverse DCT → planes → chroma interpolated up to the luma grid → YCbCr → RGB.
+// A progressive frame spreads each block's coefficients over several scans (a band of the zig-zag order, high bits first
+// and single correction bits later); its scans are merged into a coefficient store and transformed after the last one.
 // Counterpart in the reference: the stb_image header behind cpp/runtime/imageUtils.cpp.
 #include "media.h"
 
@@ -100,6 +102,9 @@ struct Component {
     int id = 0, h = 1, v = 1, tq = 0, td = 0, ta = 0, pred = 0;
     int stride = 0, rows = 0;
     std::vector<uint8_t> plane;
+    // progressive frames: every block's coefficients (natural order, not yet dequantised) live until the last scan
+    int bw = 0, bh = 0;
+    std::vector<int16_t> coef;
 };
 
 void idct8x8(const float* in, uint8_t* out, int stride) {
@@ -127,6 +132,133 @@ void idct8x8(const float* in, uint8_t* out, int stride) {
         }
 }
 
+// One scan of a progressive frame (ITU-T T.81 annex G): spectral selection ``ss..se`` and successive approximation
+// ``ah/al``.  DC scans may interleave several components; an AC scan holds one component and walks that component's own
+// block grid (the blocks that cover its samples, not the MCU-padded grid).  Returns the offset of the byte after the
+// scan's entropy-coded data.
+size_t decode_progressive_scan(const uint8_t* p, size_t n, size_t start, const std::vector<Component*>& sc, int ss, int se, int ah,
+                               int al, const std::array<JHuff, 4>& dc, const std::array<JHuff, 4>& ac, int width, int height,
+                               int hmax, int vmax, int mcux, int mcuy, int restart) {
+    if (ss > se || se > 63 || al > 13 || (ah != 0 && ah != al + 1)) bad("bad JPEG progressive scan parameters");
+    if (ss == 0 && se != 0) bad("a JPEG progressive scan mixes DC and AC coefficients");
+    if (ss > 0 && sc.size() != 1) bad("a JPEG progressive AC scan must hold one component");
+    for (const Component* c : sc) {
+        if (ss == 0 && ah == 0 && (c->td > 3 || !dc[c->td].set)) bad("JPEG scan uses a Huffman table that was not defined");
+        if (ss > 0 && (c->ta > 3 || !ac[c->ta].set)) bad("JPEG scan uses a Huffman table that was not defined");
+    }
+    BitsMsb s{p, n, start};
+    int eobrun = 0, until_restart = restart;
+    const int p1 = 1 << al, m1 = -(1 << al);
+
+    auto restart_if_due = [&]() {
+        if (!restart) return;
+        if (until_restart == 0) {
+            s.reset();
+            while (s.at + 1 < n && !(p[s.at] == 0xff && p[s.at + 1] >= 0xd0 && p[s.at + 1] <= 0xd7)) ++s.at;
+            if (s.at + 1 >= n) bad("JPEG restart marker missing");
+            s.at += 2;
+            for (Component* c : sc) c->pred = 0;
+            eobrun = 0;
+            until_restart = restart;
+        }
+        --until_restart;
+    };
+    auto refine = [&](int16_t& v) {                       // one correction bit for a coefficient that is already non-zero
+        if (s.bit() && (v & p1) == 0) v = static_cast<int16_t>(v + (v >= 0 ? p1 : m1));
+    };
+    auto block = [&](Component& c, int16_t* blk) {
+        if (ss == 0) {
+            if (ah == 0) {
+                const int t = decode_symbol(s, dc[c.td]);
+                if (t > 11) bad("bad JPEG DC category");
+                c.pred += extend(s.bits(t), t);
+                blk[0] = static_cast<int16_t>(c.pred * p1);
+            } else if (s.bit()) {
+                blk[0] = static_cast<int16_t>(blk[0] | p1);
+            }
+            return;
+        }
+        if (ah == 0) {                                    // first pass over this band
+            if (eobrun > 0) { --eobrun; return; }
+            for (int k = ss; k <= se; ++k) {
+                const int rs = decode_symbol(s, ac[c.ta]);
+                const int r = rs >> 4, sz = rs & 15;
+                if (sz == 0) {
+                    if (r < 15) {                         // end of band for this block and 2^r - 1 + extra following ones
+                        eobrun = (1 << r) - 1;
+                        if (r) eobrun += s.bits(r);
+                        break;
+                    }
+                    k += 15;                              // sixteen zeros
+                    continue;
+                }
+                k += r;
+                if (k > 63) bad("JPEG AC run leaves the block");
+                blk[kZigzag[k]] = static_cast<int16_t>(extend(s.bits(sz), sz) * p1);
+            }
+            return;
+        }
+        int k = ss;                                       // refinement pass
+        if (eobrun == 0) {
+            for (; k <= se; ++k) {
+                const int rs = decode_symbol(s, ac[c.ta]);
+                int r = rs >> 4, val = 0;
+                if (rs & 15) {
+                    if ((rs & 15) != 1) bad("bad JPEG refinement symbol");
+                    val = s.bit() ? p1 : m1;              // a coefficient that becomes non-zero in this pass
+                } else if (r != 15) {
+                    eobrun = 1 << r;                      // counts this block too
+                    if (r) eobrun += s.bits(r);
+                    break;
+                }
+                // step over r coefficients whose history is zero, correcting the non-zero ones passed on the way
+                while (k <= se) {
+                    int16_t& v = blk[kZigzag[k]];
+                    if (v != 0) refine(v);
+                    else if (--r < 0) break;
+                    ++k;
+                }
+                if (val) {
+                    if (k > 63) bad("JPEG AC run leaves the block");
+                    blk[kZigzag[k]] = static_cast<int16_t>(val);
+                }
+            }
+        }
+        if (eobrun > 0) {
+            for (; k <= se; ++k) {
+                int16_t& v = blk[kZigzag[k]];
+                if (v != 0) refine(v);
+            }
+            --eobrun;
+        }
+    };
+
+    for (Component* c : sc) c->pred = 0;
+    if (sc.size() > 1) {
+        for (int my = 0; my < mcuy; ++my)
+            for (int mx = 0; mx < mcux; ++mx) {
+                restart_if_due();
+                for (Component* c : sc)
+                    for (int by = 0; by < c->v; ++by)
+                        for (int bx = 0; bx < c->h; ++bx)
+                            block(*c, &c->coef[(static_cast<size_t>(my * c->v + by) * c->bw + mx * c->h + bx) * 64]);
+            }
+    } else {
+        Component& c = *sc[0];
+        const int cw = (width * c.h + hmax - 1) / hmax, ch = (height * c.v + vmax - 1) / vmax;
+        const int nbx = (cw + 7) / 8, nby = (ch + 7) / 8;
+        for (int by = 0; by < nby; ++by)
+            for (int bx = 0; bx < nbx; ++bx) {
+                restart_if_due();
+                block(c, &c.coef[(static_cast<size_t>(by) * c.bw + bx) * 64]);
+            }
+    }
+    // the next segment starts at the first marker that is neither a stuffed zero nor a restart marker
+    size_t at = s.at;
+    while (at + 1 < n && !(p[at] == 0xff && p[at + 1] != 0x00 && p[at + 1] != 0xff && !(p[at + 1] >= 0xd0 && p[at + 1] <= 0xd7))) ++at;
+    return at;
+}
+
 }  // namespace
 
 Image decode_jpeg(const std::string& bytes) {
@@ -138,7 +270,7 @@ Image decode_jpeg(const std::string& bytes) {
     std::vector<Component> comps;
     int width = 0, height = 0, restart = 0, adobe_transform = -1;
     size_t at = 2;
-    bool decoded = false;
+    bool decoded = false, progressive = false, any_scan = false;
     while (at + 4 <= n && !decoded) {
         if (p[at] != 0xff) { ++at; continue; }
         const int marker = p[at + 1];
@@ -172,7 +304,9 @@ Image decode_jpeg(const std::string& bytes) {
                 (tc ? ac : dc)[th].build(d + i + 1, d + i + 17, total);
                 i += 17 + total;
             }
-        } else if (marker == 0xc0 || marker == 0xc1) {                  // SOF0 / SOF1
+        } else if (marker == 0xc0 || marker == 0xc1 || marker == 0xc2) { // SOF0 / SOF1 / SOF2 (progressive)
+            if (!comps.empty()) bad("JPEG file with more than one frame header");
+            progressive = marker == 0xc2;
             if (dn < 6 || d[0] != 8) bad("only 8-bit JPEG images are read");
             height = (d[1] << 8) | d[2];
             width = (d[3] << 8) | d[4];
@@ -190,8 +324,6 @@ Image decode_jpeg(const std::string& bytes) {
                 for (int j = 0; j < k; ++j)
                     if (comps[j].id == comps[k].id) bad("JPEG frame header names a component twice");
             }
-        } else if (marker == 0xc2) {
-            bad("progressive JPEG images are not read (re-encode as baseline)");
         } else if (marker >= 0xc3 && marker <= 0xcf && marker != 0xc4 && marker != 0xc8 && marker != 0xcc) {
             bad("this JPEG coding process (lossless, hierarchical or arithmetic) is not read");
         } else if (marker == 0xdd) {                                    // DRI
@@ -199,6 +331,34 @@ Image decode_jpeg(const std::string& bytes) {
             restart = (d[0] << 8) | d[1];
         } else if (marker == 0xee) {                                    // APP14 "Adobe": colour transform flag
             if (dn >= 12 && !std::memcmp(d, "Adobe", 5)) adobe_transform = d[11];
+        } else if (marker == 0xda && progressive) {                     // SOS of a progressive frame: one of many scans
+            if (dn < 1) bad("truncated JPEG scan header");
+            const int ns = d[0];
+            if (ns < 1 || ns > static_cast<int>(comps.size()) || dn < 1 + 2 * static_cast<size_t>(ns) + 3) bad("bad JPEG scan header");
+            int hmax = 1, vmax = 1;
+            for (auto& c : comps) { hmax = std::max(hmax, c.h); vmax = std::max(vmax, c.v); }
+            const int mcux = (width + 8 * hmax - 1) / (8 * hmax), mcuy = (height + 8 * vmax - 1) / (8 * vmax);
+            if (!any_scan)
+                for (auto& c : comps) {
+                    c.bw = mcux * c.h;
+                    c.bh = mcuy * c.v;
+                    c.coef.assign(static_cast<size_t>(c.bw) * c.bh * 64, 0);
+                }
+            std::vector<Component*> sc;
+            for (int k = 0; k < ns; ++k) {
+                const int id = d[1 + 2 * k];
+                auto it = std::find_if(comps.begin(), comps.end(), [&](const Component& c) { return c.id == id; });
+                if (it == comps.end()) bad("JPEG scan names an unknown component");
+                if (std::find(sc.begin(), sc.end(), &*it) != sc.end()) bad("JPEG scan names a component twice");
+                it->td = d[2 + 2 * k] >> 4;
+                it->ta = d[2 + 2 * k] & 15;
+                sc.push_back(&*it);
+            }
+            const uint8_t* tail = d + 1 + 2 * ns;
+            at = decode_progressive_scan(p, n, at + len, sc, tail[0], tail[1], tail[2] >> 4, tail[2] & 15, dc, ac, width, height, hmax,
+                                         vmax, mcux, mcuy, restart);
+            any_scan = true;
+            continue;
         } else if (marker == 0xda) {                                    // SOS: decode the (single) scan
             if (comps.empty()) bad("JPEG scan before its frame header");
             const int ns = d[0];
@@ -267,6 +427,24 @@ Image decode_jpeg(const std::string& bytes) {
             decoded = true;
         }
         at += len;
+    }
+    if (progressive && any_scan) {
+        // every scan has been merged into the coefficient store: dequantise and transform each block once
+        float block[64];
+        for (auto& c : comps) {
+            c.stride = c.bw * 8;
+            c.rows = c.bh * 8;
+            c.plane.assign(static_cast<size_t>(c.stride) * c.rows, 0);
+            for (int by = 0; by < c.bh; ++by)
+                for (int bx = 0; bx < c.bw; ++bx) {
+                    const int16_t* blk = &c.coef[(static_cast<size_t>(by) * c.bw + bx) * 64];
+                    for (int z = 0; z < 64; ++z) block[z] = static_cast<float>(blk[z]) * qt[c.tq][z];
+                    idct8x8(block, &c.plane[static_cast<size_t>(by) * 8 * c.stride + bx * 8], c.stride);
+                }
+            c.coef.clear();
+            c.coef.shrink_to_fit();
+        }
+        decoded = true;
     }
     if (!decoded) bad("JPEG file without image data");
     int hmax = 1, vmax = 1;

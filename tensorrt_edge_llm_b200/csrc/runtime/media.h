@@ -52,7 +52,7 @@ struct Image {
 uint64_t max_image_pixels();
 Image parse_image(const std::string& bytes);                         // by magic: PNG, JPEG, PPM (P6), PGM (P5), BMP 24 / 32 bit
 Image decode_png(const std::string& bytes);                          // non-interlaced; always returns RGB
-Image decode_jpeg(const std::string& bytes);                         // sequential Huffman (baseline); always returns RGB
+Image decode_jpeg(const std::string& bytes);                         // sequential or progressive Huffman; always returns RGB
 // RFC 1950 zlib stream → bytes; throws when the output would exceed `max_output`.
 std::string inflate_zlib(const std::string& stream, size_t max_output);
 Image load_image(const std::string& path);

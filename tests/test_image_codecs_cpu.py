@@ -184,8 +184,6 @@ def test_jpeg_baseline_against_pillow():
         want = np.asarray(PIL.open(io.BytesIO(data)).convert("RGB")).astype(np.int32)
         got = _pixels(rt.decode_jpeg(data)).astype(np.int32)
         assert got.shape == (61, 77, 3) and np.abs(got - want).mean() < 0.8
-    with pytest.raises(RuntimeError, match="progressive"):
-        rt.decode_jpeg(_save(smooth, "JPEG", progressive=True))
     with pytest.raises(RuntimeError):
         rt.decode_jpeg(data[:200])
     with pytest.raises(RuntimeError, match="unsupported image container"):
@@ -204,6 +202,44 @@ def _patch_sos(data: bytes, edit) -> bytes:
     edit(hdr)
     b[i + 4:i + 2 + n] = hdr
     return bytes(b)
+
+
+def test_jpeg_progressive_against_pillow():
+    """Progressive frames (spectral selection and successive approximation over several scans) decode to the same
+    pixels as the baseline form of the same coefficients would: compared with Pillow's decode of the same bytes."""
+    rng = np.random.default_rng(11)
+    yy, xx = np.mgrid[0:97, 0:131]
+    smooth = np.stack([(xx * 2) % 256, (yy * 3) % 256, ((xx + yy) * 1.5) % 256], -1).astype(np.uint8)
+    noisy = np.clip(smooth.astype(np.int32) + rng.integers(-40, 40, smooth.shape), 0, 255).astype(np.uint8)
+    for img, sub, quality, tol_mean in ((smooth, 0, 92, 0.3), (noisy, 2, 75, 0.8), (noisy, 1, 50, 0.8), (smooth[:8, :8], 2, 90, 1.5)):
+        data = _save(img, "JPEG", quality=quality, subsampling=sub, progressive=True)
+        assert b"\xff\xc2" in data                                   # a progressive frame header
+        want = np.asarray(PIL.open(io.BytesIO(data)).convert("RGB")).astype(np.int32)
+        got = _pixels(rt.decode_jpeg(data)).astype(np.int32)
+        assert got.shape == want.shape
+        diff = np.abs(got - want)
+        assert diff.mean() < tol_mean and diff.max() <= 6, (sub, quality, diff.mean(), diff.max())
+    for kw in ({"restart_marker_blocks": 3}, {"restart_marker_rows": 1}):     # restart intervals inside every scan
+        try:
+            data = _save(noisy, "JPEG", quality=60, subsampling=2, progressive=True, **kw)
+        except TypeError:
+            continue
+        want = np.asarray(PIL.open(io.BytesIO(data)).convert("RGB")).astype(np.int32)
+        assert np.abs(_pixels(rt.decode_jpeg(data)).astype(np.int32) - want).mean() < 0.8
+    grey = _save(noisy[..., 0], "JPEG", quality=70, progressive=True)
+    got = _pixels(rt.decode_jpeg(grey))
+    want = np.asarray(PIL.open(io.BytesIO(grey)).convert("L")).astype(np.int32)
+    assert np.abs(got[..., 0].astype(np.int32) - want).max() <= 2
+    # a cut-off progressive file and one whose scan parameters are impossible both raise
+    with pytest.raises(RuntimeError):
+        rt.decode_jpeg(data[:150])
+    sos = data.index(b"\xff\xda")
+    ns = data[sos + 4]
+    broken = bytearray(data)
+    broken[sos + 5 + 2 * ns] = 9                                     # spectral start > spectral end
+    broken[sos + 6 + 2 * ns] = 3
+    with pytest.raises(RuntimeError):
+        rt.decode_jpeg(bytes(broken))
 
 
 def test_jpeg_malformed_scan_headers_raise_cleanly():
