@@ -12,6 +12,7 @@
 #include "inference_runtime.h"
 #include "json.h"
 #include "media.h"
+#include "multistage.h"
 #include "paged_kv.h"
 #include "ple.h"
 #include "runtime_core.h"
@@ -51,6 +52,87 @@ static SessionFactory session_factory_from_python(py::function factory) {
         });
     };
 }
+
+// ---- stage-graph values ↔ Python ----------------------------------------------------------------------------------------
+// str and bytes travel as native text / bytes, a plain list of ints as token ids; token ids and float tensors made by
+// native stages become a list / a numpy array; every other Python object rides through the graph untouched as an opaque handle.
+namespace msg = telb::multistage;
+
+static msg::PortValue port_from_python(const py::handle& h) {
+    if (h.is_none()) return msg::PortValue();
+    if (py::isinstance<py::str>(h)) return msg::PortValue::text(h.cast<std::string>());
+    if (py::isinstance<py::bytes>(h)) return msg::PortValue::bytes(h.cast<std::string>());
+    if (PyList_CheckExact(h.ptr()) && PyList_GET_SIZE(h.ptr()) > 0) {      // a plain list of token ids
+        const Py_ssize_t n = PyList_GET_SIZE(h.ptr());
+        std::vector<int32_t> ids(static_cast<size_t>(n));
+        bool all_ids = true;
+        for (Py_ssize_t i = 0; i < n && all_ids; ++i) {
+            PyObject* item = PyList_GET_ITEM(h.ptr(), i);
+            int overflow = 0;
+            const long v = PyLong_CheckExact(item) ? PyLong_AsLongAndOverflow(item, &overflow) : 0;
+            all_ids = PyLong_CheckExact(item) && !overflow && v >= INT32_MIN && v <= INT32_MAX;
+            ids[static_cast<size_t>(i)] = static_cast<int32_t>(v);
+        }
+        if (all_ids) return msg::PortValue::token_ids(std::move(ids));
+    }
+    auto* held = new py::object(py::reinterpret_borrow<py::object>(h));
+    return msg::PortValue::object(std::shared_ptr<void>(held, [](void* p) {
+        py::gil_scoped_acquire gil;
+        delete static_cast<py::object*>(p);
+    }));
+}
+
+static py::object port_to_python(const msg::PortValue& v) {
+    switch (v.kind) {
+        case msg::PortValue::Kind::kText: return py::str(v.data);
+        case msg::PortValue::Kind::kBytes: return py::bytes(v.data);
+        case msg::PortValue::Kind::kTokens: return py::cast(v.tokens);
+        case msg::PortValue::Kind::kFloats: {
+            py::array_t<float> a(static_cast<py::ssize_t>(v.values.size()), v.values.data());
+            return v.shape.empty() ? py::object(a) : py::object(a.attr("reshape")(py::cast(v.shape)));
+        }
+        case msg::PortValue::Kind::kOpaque: return *static_cast<py::object*>(v.opaque.get());
+        default: return py::none();
+    }
+}
+
+static msg::PortMap port_map_from_python(const py::dict& d) {
+    msg::PortMap m;
+    for (auto kv : d) {
+        msg::PortValue v = port_from_python(kv.second);
+        if (v.present()) m[kv.first.cast<std::string>()] = std::move(v);
+    }
+    return m;
+}
+
+static py::dict port_map_to_python(const msg::PortMap& m) {
+    py::dict d;
+    for (const auto& kv : m) d[py::str(kv.first)] = port_to_python(kv.second);
+    return d;
+}
+
+// A Python callable ``fn(spec, batch: list[dict]) -> list[dict]`` as a native stage.
+static msg::StageFn stage_fn_from_python(py::object fn) {
+    auto held = std::shared_ptr<py::object>(new py::object(std::move(fn)), [](py::object* p) {
+        py::gil_scoped_acquire gil;
+        delete p;
+    });
+    return [held](const msg::StageSpec& spec, const std::vector<msg::PortMap>& batch) {
+        py::gil_scoped_acquire gil;
+        py::list in;
+        for (const auto& m : batch) in.append(port_map_to_python(m));
+        py::object out = (*held)(spec, in);
+        std::vector<msg::PortMap> res;
+        for (auto item : out) res.push_back(port_map_from_python(item.cast<py::dict>()));
+        return res;
+    };
+}
+
+struct MultiStageOutput {
+    std::string text, stages, audio_pcm16;
+    std::vector<int32_t> token_ids;
+    int audio_sample_rate = 0, audio_channels = 0;
+};
 
 PYBIND11_MODULE(_telb_runtime, m) {
     m.doc() = "Native runtime of the B200 Edge-LLM framework: paged KV bookkeeping, scheduler, streaming, tokenizer";
@@ -735,4 +817,151 @@ PYBIND11_MODULE(_telb_runtime, m) {
             py::gil_scoped_release rel;
             rt.shutdown();
         });
+
+    // ---- stage graph ---------------------------------------------------------------------------------------------
+    py::module_ ms = m.def_submodule("multistage", "Stage-graph runtime: config, validation, routes, cohorts, run loop");
+    py::register_exception<msg::GraphError>(ms, "GraphError", PyExc_ValueError);
+    ms.attr("SCHEMA_VERSION") = msg::kSchemaVersion;
+    ms.attr("CONFIG_NAME") = msg::kConfigName;
+    py::class_<msg::InputPort>(ms, "InputPort")
+        .def_readonly("name", &msg::InputPort::name).def_readonly("source", &msg::InputPort::source)
+        .def_readonly("on_missing", &msg::InputPort::on_missing)
+        .def_property_readonly("from_request", &msg::InputPort::from_request)
+        .def_property_readonly("ref", &msg::InputPort::ref);
+    py::class_<msg::EmitPort>(ms, "EmitPort")
+        .def_readonly("id", &msg::EmitPort::id).def_readonly("kind", &msg::EmitPort::kind)
+        .def_readonly("transport", &msg::EmitPort::transport).def_readonly("terminal", &msg::EmitPort::terminal);
+    py::class_<msg::StageSpec>(ms, "StageSpec")
+        .def_readonly("id", &msg::StageSpec::id).def_readonly("runner", &msg::StageSpec::runner)
+        .def_readonly("artifact", &msg::StageSpec::artifact).def_readonly("kind", &msg::StageSpec::kind)
+        .def_readonly("inputs", &msg::StageSpec::inputs).def_readonly("emits", &msg::StageSpec::emits)
+        .def_readonly("max_batch", &msg::StageSpec::max_batch).def_readonly("max_seq", &msg::StageSpec::max_seq)
+        .def_property_readonly("config_json", [](const msg::StageSpec& s) { return s.config.dump(); });
+    py::class_<msg::Route>(ms, "Route")
+        .def_readonly("stages", &msg::Route::stages).def_readonly("terminals", &msg::Route::terminals)
+        .def_property_readonly("skipped", [](const msg::Route& r) {
+            py::dict d;
+            for (const auto& kv : r.skipped) d[py::str(kv.first)] = kv.second;
+            return d;
+        })
+        .def_property_readonly("error", [](const msg::Route& r) -> py::object { return r.error.empty() ? py::object(py::none()) : py::object(py::str(r.error)); });
+    py::class_<msg::StageGraph>(ms, "StageGraph")
+        .def_static("parse_text", &msg::StageGraph::parse_text, py::arg("text"), py::arg("root") = ".")
+        .def_static("load", &msg::StageGraph::load)
+        .def_readonly("stages", &msg::StageGraph::stages).def_readonly("terminals", &msg::StageGraph::terminals)
+        .def_readonly("root", &msg::StageGraph::root)
+        .def("stage", &msg::StageGraph::stage, py::return_value_policy::reference_internal)
+        .def("validate", [](const msg::StageGraph& g, bool check_runners) { return g.validate(check_runners ? &msg::RunnerTable::global() : nullptr); },
+             py::arg("check_runners") = true)
+        .def("topological", &msg::StageGraph::topological)
+        .def("to_json", [](const msg::StageGraph& g) { return g.to_json().dump(); });
+    ms.def("register_runner", [](const std::string& name, const std::string& kind, std::vector<std::string> inputs, std::vector<std::string> emits,
+                                 std::vector<std::string> required_config, bool batches) {
+        msg::RunnerDecl d;
+        d.name = name;
+        d.kind = kind;
+        d.inputs = std::move(inputs);
+        d.emits = std::move(emits);
+        d.required_config = std::move(required_config);
+        d.batches = batches;
+        msg::RunnerTable::global().add(std::move(d));
+    }, py::arg("name"), py::arg("kind"), py::arg("inputs") = std::vector<std::string>(), py::arg("emits") = std::vector<std::string>(),
+       py::arg("required_config") = std::vector<std::string>(), py::arg("batches") = true);
+    ms.def("runner_names", [] { return msg::RunnerTable::global().names(); });
+    ms.def("plan_route", [](const msg::StageGraph& g, const std::set<std::string>& fields, py::object want) {
+        if (want.is_none()) return msg::plan_route(g, fields, nullptr);
+        const auto w = want.cast<std::vector<std::string>>();
+        return msg::plan_route(g, fields, &w);
+    }, py::arg("graph"), py::arg("fields"), py::arg("want") = py::none());
+    py::class_<msg::StageResponse>(ms, "StageResponse")
+        .def_readonly("ok", &msg::StageResponse::ok)
+        .def_property_readonly("error", [](const msg::StageResponse& r) -> py::object { return r.ok ? py::object(py::none()) : py::object(py::str(r.error)); })
+        .def_property_readonly("outputs", [](const msg::StageResponse& r) {
+            py::dict d;
+            for (const auto& kv : r.outputs) d[py::str(kv.first)] = port_to_python(kv.second);
+            return d;
+        })
+        .def_property_readonly("stages_json", [](const msg::StageResponse& r) { return r.diagnostics().dump(); });
+    py::class_<MultiStageOutput>(ms, "MultiStageOutput")
+        .def_readonly("text", &MultiStageOutput::text).def_readonly("stages", &MultiStageOutput::stages)
+        .def_readonly("token_ids", &MultiStageOutput::token_ids)
+        .def_property_readonly("audio_pcm16", [](const MultiStageOutput& o) { return py::bytes(o.audio_pcm16); })
+        .def_readonly("audio_sample_rate", &MultiStageOutput::audio_sample_rate)
+        .def_readonly("audio_channels", &MultiStageOutput::audio_channels);
+    py::class_<msg::MultiStageRuntime>(ms, "MultiStageRuntime", "Runs requests through the stage graph of an engine directory")
+        .def(py::init<>())
+        .def(py::init([](const std::string& config_dir) {
+            auto rt = std::make_unique<msg::MultiStageRuntime>();
+            rt->load_dir(config_dir);
+            return rt;
+        }), py::arg("config_dir"))
+        .def("load", &msg::MultiStageRuntime::load, py::arg("graph"), py::arg("check_runners") = true)
+        .def("load_dir", &msg::MultiStageRuntime::load_dir, py::arg("path"), py::arg("check_runners") = true)
+        .def_property_readonly("graph", &msg::MultiStageRuntime::graph, py::return_value_policy::reference_internal)
+        .def_property_readonly("order", &msg::MultiStageRuntime::order)
+        .def("set_factory", [](msg::MultiStageRuntime& rt, const std::string& runner, py::object factory) {
+            auto held = std::shared_ptr<py::object>(new py::object(std::move(factory)), [](py::object* p) {
+                py::gil_scoped_acquire gil;
+                delete p;
+            });
+            rt.set_factory(runner, [held](const msg::StageSpec& spec, const std::string& root) {
+                py::gil_scoped_acquire gil;
+                return stage_fn_from_python((*held)(spec, root));
+            });
+        })
+        .def("set_stage", [](msg::MultiStageRuntime& rt, const std::string& id, py::object fn) { rt.set_stage(id, stage_fn_from_python(std::move(fn))); })
+        .def("stage_loaded", &msg::MultiStageRuntime::stage_loaded)
+        .def("submit", [](msg::MultiStageRuntime& rt, const py::dict& fields, std::vector<std::string> want, const std::string& cohort_key,
+                          std::shared_ptr<StreamChannel> text_sink, bool keep_unroutable) {
+            msg::StageRequest r;
+            r.fields = port_map_from_python(fields);
+            r.want = std::move(want);
+            r.cohort_key = cohort_key;
+            r.text_sink = std::move(text_sink);
+            std::string why;
+            const int idx = rt.submit(std::move(r), &why, keep_unroutable);
+            return py::make_tuple(idx, why);
+        }, py::arg("fields"), py::arg("want") = std::vector<std::string>(), py::arg("cohort_key") = "", py::arg("text_sink") = nullptr,
+           py::arg("keep_unroutable") = false)
+        .def_property_readonly("pending", &msg::MultiStageRuntime::pending)
+        .def("discard_pending", &msg::MultiStageRuntime::discard_pending)
+        .def("cohorts", [](const msg::MultiStageRuntime& rt, int batch_size) {
+            py::list out;
+            for (auto& c : rt.cohorts(batch_size)) out.append(py::make_tuple(c.members, c.route));
+            return out;
+        }, py::arg("batch_size") = 1)
+        .def("run", [](msg::MultiStageRuntime& rt, int batch_size) { return rt.run(batch_size); }, py::arg("batch_size") = 1)
+        .def("take", &msg::MultiStageRuntime::take)
+        .def("close", &msg::MultiStageRuntime::close)
+        // one request, the way the reference's binding runs it: text always, audio terminals only when asked for
+        .def("generate", [](msg::MultiStageRuntime& rt, const std::string& prompt, const std::string& style, const std::string& sampling, bool audio) {
+            msg::StageRequest r;
+            if (!prompt.empty()) r.fields["messages"] = msg::PortValue::text(prompt);
+            if (!style.empty()) r.fields["style"] = msg::PortValue::text(style);
+            if (!sampling.empty()) r.fields["sampling"] = msg::PortValue::text(sampling);
+            for (const auto& t : rt.graph().terminals) {
+                const size_t c = t.find(':');
+                const msg::StageSpec& spec = rt.graph().stage(t.substr(0, c));
+                for (const auto& e : spec.emits)
+                    if (e.id == t.substr(c + 1) && (e.kind != "audio" || audio)) r.want.push_back(t);
+            }
+            MultiStageOutput out;
+            r.audio_sink = [&out](const msg::PcmChunk& chunk) {
+                out.audio_pcm16 += chunk.pcm16;
+                out.audio_sample_rate = chunk.sample_rate;
+                out.audio_channels = chunk.channels;
+            };
+            std::string why;
+            if (rt.submit(std::move(r), &why) < 0) throw std::runtime_error("request refused: " + why);
+            rt.run(1);
+            const auto responses = rt.take();
+            const msg::StageResponse& resp = responses.front();
+            if (!resp.ok) throw std::runtime_error("request failed: " + resp.error);
+            out.stages = resp.diagnostics().dump();
+            for (const auto& kv : resp.outputs) {
+                if (kv.second.kind == msg::PortValue::Kind::kText) out.text += kv.second.data;
+                if (kv.second.kind == msg::PortValue::Kind::kTokens) out.token_ids = kv.second.tokens;
+            }
+            return out;
+        }, py::arg("prompt"), py::arg("style") = "", py::arg("sampling") = "", py::arg("audio") = false);
 }

@@ -5,21 +5,25 @@ and ``docs/source/developer_guide/software-design/multi-stage-graph.md``: ``mult
 (``id``, ``runner``, ``artifact``, ``kind``, ``inputs[{name, from, on_missing}]``, ``emits[{id, kind, transport,
 terminal}]``) and ``terminals``; a request runs only the stages whose inputs it can supply and whose outputs reach a
 requested terminal; requests that run the same stages form a cohort of at most ``max_batch``.
+
+The schema, its validation, the routes, the cohorts and the run loop are the native runtime's
+(``csrc/runtime/multistage.{h,cpp}``, bound as ``runtime.native.multistage``); this module is the Python face of it:
+dataclass views of a parsed graph, the table of Python stage classes, and a ``MultiStageRuntime`` that plugs those
+classes into the native loop as callables.
 """
 from __future__ import annotations
 
 import json
 import os
 from dataclasses import dataclass, field
-from typing import Any, Callable, Dict, List, Optional, Sequence, Set, Tuple
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
 
-SCHEMA_VERSION = 1
-CONFIG_NAME = "multistage_config.json"
-_ON_MISSING = ("fail", "skip", "prune")
+from . import native as _rt
 
-
-class GraphConfigError(ValueError):
-    pass
+_ms = _rt.multistage
+SCHEMA_VERSION = _ms.SCHEMA_VERSION
+CONFIG_NAME = _ms.CONFIG_NAME
+GraphConfigError = _ms.GraphError                      # a ValueError
 
 
 @dataclass
@@ -64,12 +68,33 @@ class GraphConfig:
     stages: List[StageConfig]
     terminals: List[str]
     root: str = "."
+    native: Any = None                    # the parsed native graph these views were made from
 
     def stage(self, sid: str) -> StageConfig:
         for s in self.stages:
             if s.id == sid:
                 return s
         raise KeyError(sid)
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {"schema_version": SCHEMA_VERSION, "terminals": list(self.terminals), "stages": [
+            {"id": s.id, "runner": s.runner, "artifact": s.artifact, "kind": s.kind, "max_batch": s.max_batch, "max_seq": s.max_seq,
+             "config": s.config, "inputs": [{"name": p.name, "from": p.source, "on_missing": p.on_missing} for p in s.inputs],
+             "emits": [{"id": e.id, "kind": e.kind, "transport": e.transport, "terminal": e.terminal} for e in s.emits]}
+            for s in self.stages]}
+
+
+def _native_graph(g: GraphConfig):
+    if g.native is None:                  # a graph assembled from the dataclasses by hand
+        g.native = _ms.StageGraph.parse_text(json.dumps(g.to_dict()), g.root)
+    return g.native
+
+
+def _view(ng) -> GraphConfig:
+    stages = [StageConfig(s.id, s.runner, s.artifact, s.kind, [InputPort(p.name, p.source, p.on_missing) for p in s.inputs],
+                          [EmitPort(e.id, e.kind, e.transport, e.terminal) for e in s.emits], s.max_batch, s.max_seq, json.loads(s.config_json))
+              for s in ng.stages]
+    return GraphConfig(stages, list(ng.terminals), ng.root, ng)
 
 
 # ---- runner table ----------------------------------------------------------------------------------------------------
@@ -102,6 +127,7 @@ _RUNNERS: Dict[str, RunnerDecl] = {}
 
 def register_runner(decl: RunnerDecl) -> None:
     _RUNNERS[decl.name] = decl
+    _ms.register_runner(decl.name, decl.kind, list(decl.inputs), list(decl.emits))
 
 
 def runner_names() -> List[str]:
@@ -148,19 +174,7 @@ register_runner(RunnerDecl("llm.backbone", "autoregressive", LLMBackboneStage, i
 def parse_graph(obj: Dict[str, Any], root: str = ".") -> GraphConfig:
     if not isinstance(obj, dict):
         raise GraphConfigError("the graph file must hold a JSON object")
-    if obj.get("schema_version") != SCHEMA_VERSION:
-        raise GraphConfigError(f"schema_version must be {SCHEMA_VERSION}")
-    stages: List[StageConfig] = []
-    for i, s in enumerate(obj.get("stages") or []):
-        try:
-            ins = [InputPort(p["name"], p["from"], p.get("on_missing", "fail")) for p in s.get("inputs", [])]
-            ems = [EmitPort(e["id"], e.get("kind", "tensor"), e.get("transport", "chunk_stream"), bool(e.get("terminal", False)))
-                   for e in s.get("emits", [])]
-            stages.append(StageConfig(s["id"], s["runner"], s.get("artifact", "."), s.get("kind", "autoregressive"), ins, ems,
-                                      int(s.get("max_batch", 0)), int(s.get("max_seq", 0)), dict(s.get("config", {}))))
-        except (KeyError, TypeError) as e:
-            raise GraphConfigError(f"stages[{i}] is missing {e}") from None
-    g = GraphConfig(stages, list(obj.get("terminals") or []), root)
+    g = _view(_ms.StageGraph.parse_text(json.dumps(obj), root))
     validate_graph(g)
     return g
 
@@ -171,55 +185,9 @@ def load_graph(path: str) -> GraphConfig:
         return parse_graph(json.load(fh), os.path.dirname(os.path.abspath(f)))
 
 
-def _topological(g: GraphConfig) -> List[str]:
-    deps = {s.id: {p.ref[0] for p in s.inputs if not p.from_request} for s in g.stages}
-    order: List[str] = []
-    while deps:
-        ready = sorted(k for k, d in deps.items() if not (d - set(order)))
-        if not ready:
-            raise GraphConfigError(f"the stages {sorted(deps)} form a cycle")
-        for k in ready:
-            order.append(k)
-            del deps[k]
-    return order
-
-
 def validate_graph(g: GraphConfig, check_runners: bool = True) -> List[str]:
     """Structure checks (and, with ``check_runners``, agreement with the runner table); returns the execution order."""
-    if not g.stages:
-        raise GraphConfigError("a graph needs at least one stage")
-    ids = [s.id for s in g.stages]
-    if len(set(ids)) != len(ids):
-        raise GraphConfigError("stage ids must be unique")
-    ports = {(s.id, e.id) for s in g.stages for e in s.emits}
-    for s in g.stages:
-        if len({e.id for e in s.emits}) != len(s.emits):
-            raise GraphConfigError(f"stage {s.id}: duplicate output port")
-        for p in s.inputs:
-            if p.on_missing not in _ON_MISSING:
-                raise GraphConfigError(f"stage {s.id}: on_missing must be one of {_ON_MISSING}")
-            if ":" not in p.source:
-                raise GraphConfigError(f"stage {s.id}: input {p.name!r} needs a source of the form <stage>:<port> or request:<field>")
-            if not p.from_request and p.ref not in ports:
-                raise GraphConfigError(f"stage {s.id}: input {p.name!r} reads {p.source!r}, which no stage emits")
-        if check_runners:
-            decl = _RUNNERS.get(s.runner)
-            if decl is None:
-                raise GraphConfigError(f"stage {s.id}: unknown runner {s.runner!r}; known: {runner_names()}")
-            if decl.kind != s.kind:
-                raise GraphConfigError(f"stage {s.id}: runner {s.runner} is {decl.kind}, the graph says {s.kind}")
-            bad_in = [p.name for p in s.inputs if decl.inputs and p.name not in decl.inputs]
-            bad_out = [e.id for e in s.emits if decl.emits and e.id not in decl.emits]
-            if bad_in or bad_out:
-                raise GraphConfigError(f"stage {s.id}: runner {s.runner} has no input {bad_in} / output {bad_out}")
-    marked = sorted(f"{s.id}:{e.id}" for s in g.stages for e in s.emits if e.terminal)
-    for t in g.terminals:
-        a, _, b = t.partition(":")
-        if (a, b) not in ports:
-            raise GraphConfigError(f"terminal {t!r} is not an output of any stage")
-    if sorted(g.terminals) != marked:
-        raise GraphConfigError(f"terminals {sorted(g.terminals)} differ from the outputs marked terminal {marked}")
-    return _topological(g)
+    return list(_native_graph(g).validate(check_runners))
 
 
 def one_stage_graph(max_batch: int = 8, has_audio: bool = False, has_image: bool = False) -> Dict[str, Any]:
@@ -255,107 +223,72 @@ class Route:
     error: Optional[str] = None
 
 
+def _route_view(r) -> Route:
+    return Route(list(r.stages), list(r.terminals), dict(r.skipped), r.error)
+
+
 def plan_route(g: GraphConfig, request: Dict[str, Any], want: Optional[Sequence[str]] = None) -> Route:
-    order = _topological(g)
-    want = list(want) if want is not None else list(g.terminals)
-    runnable: Set[str] = set()
-    skipped: Dict[str, str] = {}
-    for sid in order:
-        s = g.stage(sid)
-        why = None
-        for p in s.inputs:
-            present = (p.ref[1] in request and request[p.ref[1]] is not None) if p.from_request else p.ref[0] in runnable
-            if not present and p.on_missing != "skip":
-                why = f"input {p.name!r} ({p.source}) is missing"
-                break
-        if why is None:
-            runnable.add(sid)
-        else:
-            skipped[sid] = why
-    # keep only what reaches a requested terminal
-    needed: Set[str] = set()
-    frontier = [t.partition(":")[0] for t in want]
-    while frontier:
-        sid = frontier.pop()
-        if sid in needed or sid not in runnable:
-            continue
-        needed.add(sid)
-        frontier += [p.ref[0] for p in g.stage(sid).inputs if not p.from_request and p.ref[0] in runnable]
-    got = [t for t in want if t.partition(":")[0] in needed]
-    missing = [t for t in want if t not in got]
-    err = None
-    if missing:
-        err = "; ".join(f"{t} needs stage {t.partition(':')[0]}: {skipped.get(t.partition(':')[0], 'an upstream stage cannot run')}" for t in missing)
-    return Route([sid for sid in order if sid in needed], got, skipped, err)
+    fields = {k for k, v in request.items() if v is not None}
+    return _route_view(_ms.plan_route(_native_graph(g), fields, None if want is None else list(want)))
+
+
+def _cohort_key(r: Dict[str, Any]) -> str:
+    # settings that hold for a whole batch: requests that differ in them do not share a cohort
+    return json.dumps([r.get("sampling"), r.get("voice")], sort_keys=True, default=str)
 
 
 class MultiStageRuntime:
+    """The native run loop with Python stage classes plugged in.  ``stages`` hands in stages that are already loaded;
+    every other stage is built from the runner table on first use."""
+
     def __init__(self, graph: GraphConfig, stages: Optional[Dict[str, Stage]] = None):
         self.graph = graph
-        self.order = validate_graph(graph, check_runners=stages is None)
         self._stages: Dict[str, Stage] = dict(stages or {})
+        self._native = _ms.MultiStageRuntime()
+        self._native.load(_native_graph(graph), check_runners=stages is None)
+        self.order = list(self._native.order)
+        for sid, stage in self._stages.items():
+            self._native.set_stage(sid, self._callable(stage))
+        for runner in {s.runner for s in graph.stages}:
+            self._native.set_factory(runner, self._factory)
+
+    @staticmethod
+    def _callable(stage: Stage) -> Callable:
+        return lambda spec, batch: stage.run(batch)
+
+    def _factory(self, spec, root: str) -> Callable:
+        stage = _RUNNERS[spec.runner].factory(self.graph.stage(spec.id), root)
+        self._stages[spec.id] = stage
+        return self._callable(stage)
 
     @classmethod
     def load(cls, path: str) -> "MultiStageRuntime":
         return cls(load_graph(path))
 
-    def _stage(self, sid: str) -> Stage:
-        if sid not in self._stages:                      # stages load on first use: a text-only run never loads the vocoder
-            cfg = self.graph.stage(sid)
-            self._stages[sid] = _RUNNERS[cfg.runner].factory(cfg, self.graph.root)
-        return self._stages[sid]
+    def _submit_all(self, requests: Sequence[Dict[str, Any]], want) -> None:
+        self._native.discard_pending()
+        for r in requests:
+            fields = {k: v for k, v in r.items() if v is not None}
+            idx, why = self._native.submit(fields, list(want) if want is not None else [], _cohort_key(r), None, True)
+            if idx < 0:
+                self._native.discard_pending()
+                raise GraphConfigError(why)
 
     def cohorts(self, requests: Sequence[Dict[str, Any]], want, batch_size: int) -> List[Tuple[List[int], Route]]:
         """Group requests that run the same stages with the same batch-wide settings, in file order."""
-        cap = batch_size
-        for s in self.graph.stages:
-            if s.max_batch:
-                cap = min(cap, s.max_batch)
-        groups: List[Tuple[tuple, List[int], Route]] = []
-        for i, r in enumerate(requests):
-            route = plan_route(self.graph, r, want)
-            key = (tuple(route.stages), tuple(route.terminals), json.dumps(r.get("sampling"), sort_keys=True), r.get("voice"))
-            for k, idx, _ in groups:
-                if k == key and len(idx) < max(cap, 1):
-                    idx.append(i)
-                    break
-            else:
-                groups.append((key, [i], route))
-        return [(idx, route) for _, idx, route in groups]
+        self._submit_all(requests, want)
+        try:
+            return [(list(members), _route_view(route)) for members, route in self._native.cohorts(batch_size)]
+        finally:
+            self._native.discard_pending()
 
     def run(self, requests: Sequence[Dict[str, Any]], want: Optional[Sequence[str]] = None, batch_size: int = 1) -> List[Dict[str, Any]]:
-        results: List[Dict[str, Any]] = [{} for _ in requests]
-        for idx, route in self.cohorts(requests, want, batch_size):
-            values: List[Dict[Tuple[str, str], Any]] = [{} for _ in idx]
-            detail: Dict[str, Any] = {sid: {"ran": False, "reason": why} for sid, why in route.skipped.items()}
-            error = route.error
-            for sid in route.stages:
-                cfg = self.graph.stage(sid)
-                batch = []
-                for j, i in enumerate(idx):
-                    ins = {}
-                    for p in cfg.inputs:
-                        src = requests[i].get(p.ref[1]) if p.from_request else values[j].get(p.ref)
-                        if src is not None:
-                            ins[p.name] = src
-                    batch.append(ins)
-                try:
-                    outs = self._stage(sid).run(batch)
-                    for j, o in enumerate(outs):
-                        for port, v in o.items():
-                            values[j][(sid, port)] = v
-                    detail[sid] = {"ran": True, "batch": len(idx)}
-                except Exception as e:       # a failing stage fails its cohort, not the run
-                    error = f"stage {sid}: {type(e).__name__}: {e}"
-                    detail[sid] = {"ran": False, "reason": error}
-                    break
-            for j, i in enumerate(idx):
-                out = {t: values[j].get(tuple(t.split(":", 1))) for t in route.terminals}
-                ok = error is None and all(v is not None for v in out.values())
-                results[i] = {"ok": ok, "error": None if ok else (error or "a terminal produced nothing"), "outputs": out, "stages": detail}
-        return results
+        self._submit_all(requests, want)
+        self._native.run(batch_size)
+        return [{"ok": r.ok, "error": r.error, "outputs": r.outputs, "stages": json.loads(r.stages_json)} for r in self._native.take()]
 
     def close(self) -> None:
+        self._native.close()
         for s in self._stages.values():
             s.close()
         self._stages = {}

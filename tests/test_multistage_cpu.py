@@ -72,9 +72,67 @@ def test_cohorts_and_execution():
     assert res[0]["ok"] and res[0]["outputs"] == {"thinker:text": "re:ab", "code2wav:audio": [2 * ord(c) for c in "re:ab"]}
     assert res[1]["outputs"]["code2wav:audio"][-1] == 14 and res[2]["outputs"]["thinker:text"] == "re:de"
     assert not res[4]["ok"] and "missing" in res[4]["error"]
-    assert ("thinker", 2) in Scripted.calls and res[0]["stages"]["talker"] == {"ran": True, "batch": 2}
+    assert ("thinker", 2) in Scripted.calls and {k: res[0]["stages"]["talker"][k] for k in ("ran", "batch")} == {"ran": True, "batch": 2}
     text_only = rt.run(reqs[:1], want=["thinker:text"])
     assert text_only[0]["outputs"] == {"thinker:text": "re:ab"} and "talker" not in text_only[0]["stages"]
+
+
+def test_native_runtime_surface(tmp_path):
+    """The native class itself: load from a directory, stages as callables or through a factory, refusal at submit,
+    ``generate`` for one request, a runner that does not batch, a failing stage, token terminals on a stream channel."""
+    from tensorrt_edge_llm_b200.runtime import native as rt
+    nms = rt.multistage
+    nms.register_runner("native.echo", "autoregressive", ["prompt", "style"], ["text", "ids"], [], False)
+    nms.register_runner("native.voice", "iterative", ["text"], ["audio"], ["sample_rate"])
+    graph = {"schema_version": 1, "terminals": ["echo:text", "echo:ids", "voice:audio"], "stages": [
+        {"id": "echo", "runner": "native.echo", "kind": "autoregressive",
+         "inputs": [{"name": "prompt", "from": "request:messages"}, {"name": "style", "from": "request:style", "on_missing": "skip"}],
+         "emits": [{"id": "text", "kind": "text", "terminal": True}, {"id": "ids", "kind": "tokens", "terminal": True}]},
+        {"id": "voice", "runner": "native.voice", "kind": "iterative", "config": {"sample_rate": 16000},
+         "inputs": [{"name": "text", "from": "echo:text"}], "emits": [{"id": "audio", "kind": "audio", "terminal": True}]}]}
+    (tmp_path / nms.CONFIG_NAME).write_text(json.dumps(graph))
+    m = nms.MultiStageRuntime(str(tmp_path))
+    assert m.order == ["echo", "voice"] and m.graph.root == str(tmp_path) and json.loads(m.graph.to_json())["terminals"] == graph["terminals"]
+    sizes = []
+
+    def echo(spec, batch):
+        sizes.append(len(batch))
+        return [{"text": (r.get("style", "") + r["prompt"]).upper(), "ids": [len(r["prompt"]), 7]} for r in batch]
+
+    built = []
+
+    def voice_factory(spec, root):
+        built.append((spec.id, root, json.loads(spec.config_json)["sample_rate"]))
+        return lambda spec, batch: [{"audio": r["text"].encode() * 2} for r in batch]
+
+    m.set_stage("echo", echo)
+    m.set_factory("native.voice", voice_factory)
+    out = m.generate("hi", style="x")                               # text only: the voice stage is neither built nor run
+    assert out.text == "XHI" and built == [] and not m.stage_loaded("voice") and "voice" not in json.loads(out.stages)
+    out = m.generate("hi", audio=True)
+    assert out.audio_pcm16 == b"HIHI" and out.audio_sample_rate == 16000 and built == [("voice", str(tmp_path), 16000)]
+    with pytest.raises(RuntimeError, match="refused.*messages"):
+        m.generate("")                                              # no prompt: no terminal can be produced
+    assert m.submit({"messages": "a"}, ["echo:nothing"])[0] == -1
+    # a runner declared as not batching sees the cohort one request at a time
+    sizes.clear()
+    chan = rt.StreamChannel.create()
+    for i, text in enumerate(("a", "bb", "ccc")):
+        assert m.submit({"messages": text}, ["echo:ids"], "", chan if i == 0 else None)[0] == i
+    assert [members for members, _ in m.cohorts(8)] == [[0, 1, 2]]
+    res = m.run(8)
+    assert sizes == [1, 1, 1] and [r.outputs["echo:ids"] for r in res] == [[1, 7], [2, 7], [3, 7]] and m.pending == 0
+    chunk = chan.try_pop()
+    assert list(chunk.token_ids) == [1, 7] and chan.is_finished()
+    # a stage that raises fails its cohort with the stage named; a later run is unaffected
+    m.set_stage("echo", lambda spec, batch: (_ for _ in ()).throw(ValueError("boom")))
+    m.submit({"messages": "a"}, ["echo:text"])
+    r = m.run()[0]
+    assert not r.ok and "stage echo" in r.error and "boom" in r.error
+    # required config keys are part of the runner's declaration
+    del graph["stages"][1]["config"]
+    with pytest.raises(nms.GraphError, match="sample_rate"):
+        nms.StageGraph.parse_text(json.dumps(graph)).validate()
 
 
 def test_one_stage_graph_with_the_llm_backbone(tmp_path):
