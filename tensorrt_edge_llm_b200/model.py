@@ -30,7 +30,7 @@ def _ensure_builtin():
     from .models.default import CausalLM
     for t in ("llama", "qwen2", "qwen3", "mistral", "phi3", "gemma", "default"):
         _REGISTRY[t] = CausalLM
-    from .models import qwen3_moe, nemotron_h, eagle3, eagle4, mtp, gemma, diffusion_gemma, dflash, dflash2, lilicorr, dspark  # noqa: F401  (register themselves)
+    from .models import qwen3_moe, nemotron_h, eagle3, eagle4, mtp, gemma, diffusion_gemma, dflash, dflash2, lilicorr, dspark, tts  # noqa: F401  (register themselves)
 
 
 def model_class_for(cfg: ModelConfig):
