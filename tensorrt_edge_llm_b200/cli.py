@@ -23,6 +23,7 @@ COMMANDS = {
     "reduce-vocab": ("tensorrt_edge_llm_b200.commands.reduce_vocab", "Generate reduced-vocabulary artifacts"),
     "infer": ("tensorrt_edge_llm_b200.commands.infer", "Run a request file and write predictions"),
     "stream": ("tensorrt_edge_llm_b200.commands.stream", "Run a request file and print the answers while they are generated"),
+    "tts": ("tensorrt_edge_llm_b200.commands.tts", "Text to speech from a request file (talker, code predictor, vocoder)"),
     "multistage": ("tensorrt_edge_llm_b200.commands.multistage", "Run requests through a multi-stage graph"),
     "action": ("tensorrt_edge_llm_b200.commands.action", "Vision-language-action inference: reasoning text + trajectory"),
     "bench": ("tensorrt_edge_llm_b200.benchmarks.llm_bench", "Offline benchmark writing report.json"),

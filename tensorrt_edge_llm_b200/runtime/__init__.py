@@ -2,7 +2,7 @@
 native module — the request engine, handles, stream channels and scheduling options.
 
 ``tensorrt_edgellm.runtime`` resolves to this package, so the names of the reference's runtime module work unchanged:
-``LLMRuntime``, ``RequestEngine``, ``RequestHandle``, ``StreamChannel``, ``MultiStageRuntime``,
+``LLMRuntime``, ``RequestEngine``, ``RequestHandle``, ``StreamChannel``, ``MultiStageRuntime``, ``TTSRuntime``, ``TTS``,
 ``validate_scheduling_options`` (``python/nanobind/bindings.cpp:1359-1821``).  Attributes load lazily: importing the
 package does not load the native module or torch-heavy submodules until a name is used."""
 from __future__ import annotations
@@ -16,7 +16,8 @@ _NATIVE = ("RequestEngine", "RequestHandle", "StreamChannel", "StreamChunk", "Fi
            "LLMInferenceRuntime", "LLMGenerationRequest", "LLMGenerationResponse", "GenerationEntry")
 _LOCAL = {"LLM": ("llm", "LLM"), "LLMRuntime": ("facade", "LLMRuntime"), "SamplingParams": ("runner", "SamplingParams"),
           "ModelRunner": ("runner", "ModelRunner"), "ModelSession": ("session", "ModelSession"),
-          "MultiStageRuntime": ("multistage", "MultiStageRuntime"), "KVCacheManager": ("kv_cache", "KVCacheManager")}
+          "MultiStageRuntime": ("multistage", "MultiStageRuntime"), "KVCacheManager": ("kv_cache", "KVCacheManager"),
+          "TTS": ("tts", "TTS"), "TTSRuntime": ("tts", "TTSRuntime"), "TTSSampling": ("tts", "TTSSampling")}
 
 __all__ = sorted(_NATIVE + tuple(_LOCAL))
 

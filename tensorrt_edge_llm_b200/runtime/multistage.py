@@ -169,6 +169,53 @@ register_runner(RunnerDecl("llm.backbone", "autoregressive", LLMBackboneStage, i
                            emits=("text", "token_ids", "finish_reason")))
 
 
+class TalkerStage(Stage):
+    """``tts.talker``: text (or templated token ids) → the codec frame matrix, through the Talker / CodePredictor loop of the
+    speech pipeline in the artifact directory.  ``voice`` and ``sampling`` are optional inputs."""
+
+    def __init__(self, cfg: StageConfig, root: str, runtime=None):
+        super().__init__(cfg, root)
+        if runtime is None:
+            from .tts import load_tts
+            runtime = load_tts(os.path.normpath(os.path.join(root, cfg.artifact)), cfg.config.get("device", "cpu"))
+        self.runtime = runtime
+
+    def run(self, batch):
+        from .tts import TTSSampling
+        out = []
+        for r in batch:                                            # the frame loop holds one request at a time
+            text = r["text"]
+            ids = self.runtime.tokenize(text) if isinstance(text, str) else list(text)
+            sp = TTSSampling.from_dict({**self.cfg.config, **(r.get("sampling") or {})})
+            codes, reason, _, _ = self.runtime.generate_codes(ids, r.get("voice"), r.get("language"), sp)
+            out.append({"codes": codes, "finish_reason": reason})
+        return out
+
+
+class Code2WavStage(Stage):
+    """``tts.code2wav``: codec frame matrix → 16-bit PCM bytes (the graph's audio terminal)."""
+
+    def __init__(self, cfg: StageConfig, root: str, runtime=None):
+        super().__init__(cfg, root)
+        if runtime is None:
+            from .tts import load_tts
+            runtime = load_tts(os.path.normpath(os.path.join(root, cfg.artifact)), cfg.config.get("device", "cpu"))
+        self.vocoder, self.device = runtime.code2wav, runtime.device
+
+    def run(self, batch):
+        from ..models.tts import pcm16_bytes
+        out = []
+        for r in batch:
+            codes = r["codes"]
+            wav = self.vocoder(codes.t().contiguous()[None].to(self.device))[0] if codes.shape[0] else codes.new_zeros(0).float()
+            out.append({"audio": pcm16_bytes(wav)})
+        return out
+
+
+register_runner(RunnerDecl("tts.talker", "autoregressive", TalkerStage, inputs=("text", "voice", "language", "sampling"), emits=("codes", "finish_reason")))
+register_runner(RunnerDecl("tts.code2wav", "iterative", Code2WavStage, inputs=("codes",), emits=("audio",)))
+
+
 # ---- parsing and validation ------------------------------------------------------------------------------------------
 
 def parse_graph(obj: Dict[str, Any], root: str = ".") -> GraphConfig:

@@ -157,8 +157,9 @@ def _truncate_at_stop(text: str, stops) -> (str, bool):
 
 
 def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optional[ChatTemplate] = None,
-               model_name: str = "", multimodal=None) -> FastAPI:
-    """``multimodal``: a ``runtime.multimodal.MultimodalRunner`` over ``llm``; chat requests whose messages carry image or
+               model_name: str = "", multimodal=None, tts=None) -> FastAPI:
+    """``tts``: a ``runtime.tts.TTS`` (or ``TTSRuntime``); ``/v1/audio/speech`` and ``/v1/voices`` are answered by it.
+    ``multimodal``: a ``runtime.multimodal.MultimodalRunner`` over ``llm``; chat requests whose messages carry image or
     audio parts are then answered through it: on the request engine next to all other requests when in-flight batching is on,
     otherwise one at a time on the static path."""
     api = api or ApiConfig()
@@ -354,11 +355,72 @@ def create_app(llm: LLM, api: Optional[ApiConfig] = None, chat_template: Optiona
 
     @app.get("/v1/voices")
     async def voices():
-        return {"object": "list", "data": [{"id": v, "object": "voice"} for v in llm.list_voices()]}
+        names = list(llm.list_voices()) + (list(speech.voices()) if speech is not None else [])
+        return {"object": "list", "data": [{"id": v, "object": "voice"} for v in names]}
+
+    speech = getattr(tts, "runtime", tts)                   # the frame loop serves one request at a time
+    speech_lock = __import__("threading").Lock()
 
     @app.post("/v1/audio/speech")
     async def audio_speech(request: Request):
-        return _error(400, "the loaded model has no speech synthesis stage", code="model_capability")
+        """OpenAI speech route: ``input`` (text, or templated token ids), ``voice``, ``response_format`` ``wav`` | ``pcm``;
+        ``stream: true`` sends 16-bit PCM chunk by chunk while later frames are still being generated.  Extra keys:
+        ``language`` and the sampling keys of the reference's request file (``talker_temperature``, ``talker_top_k``,
+        ``talker_top_p``, ``repetition_penalty``, ``max_audio_length``, ``seed``)."""
+        if speech is None:
+            return _error(400, "the loaded model has no speech synthesis stage", code="model_capability")
+        from ..runtime.tts import TTSSampling
+        try:
+            body = await request.json()
+            text = body["input"]
+            if not (isinstance(text, str) and text) and not (isinstance(text, list) and text and all(isinstance(t, int) for t in text)):
+                raise ValueError("input must be a non-empty string or a list of token ids")
+            fmt = body.get("response_format", "wav")
+            if fmt not in ("wav", "pcm"):
+                raise ValueError("response_format must be wav or pcm")
+            voice, language = body.get("voice") or None, body.get("language") or None
+            if voice and voice.lower() not in speech.voices():
+                raise ValueError(f"unknown voice {voice!r}; available: {speech.voices()}")
+            sampling = TTSSampling.from_dict(body)
+            ids = speech.tokenize(text) if isinstance(text, str) else list(text)
+            speech.build_prefill(ids, voice, language)           # layout errors surface as 400s, before any audio is promised
+        except (KeyError, ValueError, TypeError) as e:
+            return _error(400, f"bad request: {e}")
+        import asyncio
+        import queue as queue_mod
+        from fastapi.responses import Response
+        loop = asyncio.get_running_loop()
+        if not body.get("stream"):
+            def run():
+                with speech_lock:
+                    return speech.generate(ids, voice, language, sampling)
+            out = await loop.run_in_executor(None, run)
+            data = out.wav_bytes() if fmt == "wav" else out.pcm16
+            return Response(content=data, media_type="audio/wav" if fmt == "wav" else "audio/pcm",
+                            headers={"x-audio-frames": str(out.frames), "x-sample-rate": str(out.sample_rate), "x-finish-reason": out.finish_reason})
+        chunks: "queue_mod.Queue" = queue_mod.Queue()
+
+        def produce():
+            try:
+                with speech_lock:
+                    speech.generate(ids, voice, language, sampling, chunk_frames=int(body.get("chunk_frames", 12)),
+                                    on_audio=lambda pcm, sr, final: chunks.put(pcm))
+            except Exception as e:          # the stream has begun: end it, the error goes to the log
+                print(f"speech generation failed: {type(e).__name__}: {e}")
+            finally:
+                chunks.put(None)
+
+        loop.run_in_executor(None, produce)
+
+        async def body_iter():
+            while True:
+                piece = await loop.run_in_executor(None, chunks.get)
+                if piece is None:
+                    return
+                if piece:
+                    yield piece
+
+        return StreamingResponse(body_iter(), media_type="audio/pcm", headers={"x-sample-rate": str(speech.code2wav.cfg.sample_rate)})
 
     # ---- OpenAI chat completions ---------------------------------------------------------------------------
     @app.post("/v1/chat/completions")

@@ -87,7 +87,11 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         if multimodal is not None and mc.max_image_tokens_per_image and hasattr(multimodal.vision.cfg, "spatial_merge_size"):
             vc = multimodal.vision.cfg                      # rows per image × pixels per row (patch × merge, squared)
             multimodal.max_pixels = mc.max_image_tokens_per_image * (vc.patch_size * vc.spatial_merge_size) ** 2
-    app = create_app(llm, cfg.api, template, model_name=os.path.basename(os.path.normpath(cfg.model.model)), multimodal=multimodal)
+    tts = None
+    if cfg.model.tts_model:
+        from ..runtime.tts import TTS
+        tts = TTS(cfg.model.tts_model, device=cfg.model.device or "cpu")
+    app = create_app(llm, cfg.api, template, model_name=os.path.basename(os.path.normpath(cfg.model.model)), multimodal=multimodal, tts=tts)
     try:
         uvicorn.run(app, host=cfg.api.host, port=cfg.api.port, log_level=cfg.api.log_level)
     finally:

@@ -77,6 +77,7 @@ class ModelConfig:
     tensor_parallel_size: int = 1
     kv_page_size: int = 64
     device: str = ""
+    tts_model: str = ""                            # directory of a speech pipeline (talker, code predictor, vocoder)
 
     def __post_init__(self):
         if self.max_batch_size < 1 or self.max_input_len < 1:
@@ -173,6 +174,8 @@ def create_argument_parser(prog: str = "trtedge serve") -> argparse.ArgumentPars
     m.add_argument("--tensor-parallel-size", type=int, default=1)
     m.add_argument("--kv-page-size", type=int, default=64, choices=[64, 128])
     m.add_argument("--device", default="")
+    m.add_argument("--tts-model", "--talker-engine-dir", dest="tts_model", default="",
+                   help="directory of a speech pipeline; enables /v1/audio/speech and /v1/voices")
     a = p.add_argument_group("api")
     a.add_argument("--host", default="0.0.0.0")
     a.add_argument("--port", type=int, default=8000)
@@ -216,7 +219,7 @@ def parse_server_config(argv: Optional[Sequence[str]] = None) -> ServerConfig:
         enable_in_flight_batching=ns.enable_in_flight_batching, ifb_scheduling_mode=ns.ifb_scheduling_mode,
         max_num_tokens=ns.max_num_tokens, max_chunk_tokens=ns.max_chunk_tokens, scheduling_policy=ns.scheduling_policy,
         preemption=ns.preemption, priority_reserved_slots=ns.priority_reserved_slots, max_pause_steps=ns.max_pause_steps,
-        tensor_parallel_size=ns.tensor_parallel_size, kv_page_size=ns.kv_page_size, device=ns.device)
+        tensor_parallel_size=ns.tensor_parallel_size, kv_page_size=ns.kv_page_size, device=ns.device, tts_model=ns.tts_model)
     api = ApiConfig(host=ns.host, port=ns.port, served_model_name=ns.served_model_name, api_key=ns.api_key,
                     reasoning_parser=ns.reasoning_parser, tool_call_parser=ns.tool_call_parser,
                     enable_auto_tool_choice=ns.enable_auto_tool_choice, max_queued_requests=ns.max_queued_requests,

@@ -158,3 +158,52 @@ def test_generate_streams_chunks_and_round_trips_through_a_directory(rt, tmp_pat
     assert T.TTS(d).list_voices() == ["eric", "ryan"] and TTSConfig.from_dict(rt.cfg.to_dict()) == rt.cfg
     with pytest.raises(ValueError, match="tokenizer"):
         rt.generate("plain text")
+
+
+def test_command_server_routes_and_stage_graph(rt, tmp_path):
+    """The same pipeline behind its three front doors: ``trtedge tts``, the HTTP speech routes, a two-stage graph."""
+    import json
+    from tensorrt_edge_llm_b200.cli import main as trtedge
+    d = T.save_tts(str(tmp_path / "tts"), rt)
+    greedy = {"talker_temperature": 0.0, "predictor_temperature": 0.0, "max_audio_length": 5}
+    want = rt.generate(TEXT, "ryan", sampling=T.TTSSampling.from_dict(greedy))
+    # command
+    req = tmp_path / "in.json"
+    req.write_text(json.dumps({**greedy, "speaker": "ryan", "requests": [{"token_ids": TEXT}, {"token_ids": TEXT, "speaker": "nobody"}]}))
+    rc = trtedge(["tts", "--model-dir", d, "--input-file", str(req), "--output-file", str(tmp_path / "out.json"), "--output-audio-dir", str(tmp_path / "wav")])
+    rep = json.loads((tmp_path / "out.json").read_text())["responses"]
+    assert rc == 1 and rep[0]["frames"] == want.frames and "unknown speaker" in rep[1]["error"]
+    assert (tmp_path / "wav" / "request_0.wav").read_bytes() == want.wav_bytes()
+    assert trtedge(["tts", "--model-dir", d, "--list-voices"]) == 0
+    # HTTP
+    from fastapi.testclient import TestClient
+    from tensorrt_edge_llm_b200.config import tiny_llama_config
+    from tensorrt_edge_llm_b200.runtime.llm import LLM
+    from tensorrt_edge_llm_b200.server.app import create_app
+    llm = LLM(tiny_llama_config(num_hidden_layers=1), device="cpu", max_batch_size=1, max_input_len=32, max_kv_cache_capacity=64, page_size=16)
+    try:
+        c = TestClient(create_app(llm, tts=T.TTS(rt)))
+        assert [v["id"] for v in c.get("/v1/voices").json()["data"]] == ["eric", "ryan"]
+        r = c.post("/v1/audio/speech", json={"input": TEXT, "voice": "ryan", **greedy})
+        assert r.status_code == 200 and r.headers["content-type"] == "audio/wav" and r.content == want.wav_bytes()
+        assert r.headers["x-audio-frames"] == str(want.frames)
+        r = c.post("/v1/audio/speech", json={"input": TEXT, "voice": "ryan", "response_format": "pcm", "stream": True, "chunk_frames": 2, **greedy})
+        assert r.status_code == 200 and len(r.content) == len(want.pcm16)
+        got = torch.frombuffer(bytearray(r.content), dtype=torch.int16).int()
+        assert (got - torch.frombuffer(bytearray(want.pcm16), dtype=torch.int16).int()).abs().max() <= 1
+        for bad in ({"input": TEXT, "voice": "nobody"}, {"input": ""}, {"input": TEXT, "response_format": "mp3"}, {"input": "text needs a tokenizer"}):
+            assert c.post("/v1/audio/speech", json=bad).status_code == 400
+    finally:
+        llm.close()
+    # stage graph: talker → vocoder, audio terminal as PCM bytes
+    from tensorrt_edge_llm_b200.runtime import multistage as ms
+    graph = {"schema_version": 1, "terminals": ["code2wav:audio"], "stages": [
+        {"id": "talker", "runner": "tts.talker", "artifact": "tts", "kind": "autoregressive", "config": greedy,
+         "inputs": [{"name": "text", "from": "request:text"}, {"name": "voice", "from": "request:voice", "on_missing": "skip"}],
+         "emits": [{"id": "codes", "kind": "codec"}]},
+        {"id": "code2wav", "runner": "tts.code2wav", "artifact": "tts", "kind": "iterative",
+         "inputs": [{"name": "codes", "from": "talker:codes"}], "emits": [{"id": "audio", "kind": "audio", "terminal": True}]}]}
+    m = ms.MultiStageRuntime(ms.parse_graph(graph, str(tmp_path)))
+    res = m.run([{"text": TEXT, "voice": "ryan"}])
+    assert res[0]["ok"] and res[0]["outputs"]["code2wav:audio"] == want.pcm16
+    m.close()
