@@ -33,6 +33,8 @@ def main(argv=None) -> int:
     p.add_argument("--output-file", "--outputFile", default=None, help="JSON report (frames, seconds, finish reason per request)")
     p.add_argument("--output-audio-dir", "--outputAudioDir", default=None, help="writes request_<i>.wav here")
     p.add_argument("--chunk-frames", type=int, default=0, help="vocode every N frames while the loop is still running (0 = once at the end)")
+    p.add_argument("--cp-spec-verify-size", type=int, default=0,
+                   help="CodePredictor head speculation: one committed depth plus N-1 drafted depths per pass (0 = off, 2..8)")
     p.add_argument("--device", default="cpu")
     p.add_argument("--list-voices", action="store_true")
     a = p.parse_args(argv)
@@ -53,6 +55,10 @@ def main(argv=None) -> int:
         defaults["speaker"] = a.speaker
     if a.language:
         defaults["language"] = a.language
+    if a.cp_spec_verify_size:
+        if not 2 <= a.cp_spec_verify_size <= 8:
+            p.error("--cp-spec-verify-size must be in 2..8 (1 leaves no draft slot)")
+        defaults["cp_spec_verify_size"] = a.cp_spec_verify_size
     if a.output_audio_dir:
         os.makedirs(a.output_audio_dir, exist_ok=True)
     report = []

@@ -44,6 +44,7 @@ class TTSSampling:
     predictor_top_p: float = 1.0
     max_audio_length: int = 4096            # codec frames
     seed: int = 42
+    cp_spec_verify_size: int = 0            # CodePredictor head speculation: one committed depth + N-1 drafted ones per pass (0 = off, 2..8)
 
     @classmethod
     def from_dict(cls, d: Dict) -> "TTSSampling":
@@ -165,6 +166,88 @@ class TTSRuntime:
                 h = cp.step_embeds([0], [model.project(row)])
         return codes, total
 
+    @staticmethod
+    def _distribution(logits: torch.Tensor, temperature: float, top_k: int, top_p: float) -> torch.Tensor:
+        """The distribution the sampler draws from, as probabilities ``[V]`` (one-hot for greedy settings)."""
+        logits = logits.float().reshape(-1)
+        if temperature < 1e-3:
+            return torch.nn.functional.one_hot(logits.argmax(), logits.numel()).float()
+        p = torch.softmax(logits / temperature, dim=-1)
+        order = torch.argsort(p, descending=True, stable=True)
+        sorted_p = p[order]
+        keep = torch.ones_like(sorted_p, dtype=torch.bool)
+        if top_k > 0:
+            keep[top_k:] = False
+        if top_p < 1.0:
+            keep &= (sorted_p.cumsum(0) - sorted_p) < top_p
+        keep[0] = True
+        out = torch.zeros_like(p)
+        out[order[keep]] = sorted_p[keep]
+        return out / out.sum()
+
+    @torch.no_grad()
+    def predict_residual_codes_speculative(self, talker_hidden: torch.Tensor, first_code: int, sp: TTSSampling, frame: int,
+                                           generator: Optional[torch.Generator] = None):
+        """The CodePredictor pass of one frame with head speculation.  All heads read the same residual stream, so head
+        ``j + t`` applied to the hidden state that head ``j`` reads is a draft of the code ``t`` depths ahead at the cost
+        of one matrix-vector product.  A round samples the next code from its own head (exact), drafts ``N - 1`` further
+        codes from the later heads, feeds all ``N`` embeddings in one pass and checks every draft against the distribution
+        its own depth produces: accepted with probability ``min(1, p / q)``, else redrawn from ``max(p - q, 0)`` and the
+        round ends there.  The codes are distributed exactly as in the one-code-per-pass loop; with greedy settings they
+        are identical.  Returns ``(codes, sum of embeddings, passes)``."""
+        cp, model = self.predictor, self.predictor.model
+        g, n = self.cfg.num_code_groups, int(sp.cp_spec_verify_size)
+        if not 2 <= n <= 8:
+            raise ValueError("cp_spec_verify_size must be in 2..8 (one committed depth plus at least one draft)")
+        gen = generator or torch.Generator().manual_seed(sp.seed * 7919 + frame)
+        dist = lambda lg: self._distribution(lg, sp.predictor_temperature, sp.predictor_top_k, sp.predictor_top_p)   # noqa: E731
+        draw = lambda p: int(torch.multinomial(p.cpu(), 1, generator=gen))                                          # noqa: E731
+        cp.kv.free(0)
+        c0_row = self.talker.embed_tokens([first_code])
+        h = cp.prefill_embeds([0], [model.project(torch.cat([talker_hidden.to(c0_row.dtype), c0_row], dim=0))])
+        codes: List[int] = []
+        total = torch.zeros_like(c0_row, dtype=torch.float32)
+        passes = 1
+
+        def commit(code: int) -> torch.Tensor:
+            row = model.embed(len(codes), torch.tensor([code], device=self.device))
+            codes.append(code)
+            total.add_(row.float())
+            return row
+
+        while len(codes) < g - 1:
+            j = len(codes)                                        # h is the state head j reads
+            rows = [commit(draw(dist(model.head_logits(h, j))))]
+            if len(codes) == g - 1:
+                break
+            drafts, q = [], []
+            for t in range(1, min(n, g - 1 - j)):
+                q.append(dist(model.head_logits(h, j + t)))
+                drafts.append(draw(q[-1]))
+                rows.append(model.embed(j + t, torch.tensor([drafts[-1]], device=self.device)))
+            x = model.project(torch.cat(rows, dim=0))
+            meta = cp._meta([0], [x.shape[0]], logits_all=True)
+            hs = model(None, meta, cp.cache, inputs_embeds=x.to(model.cfg.compute_dtype))   # one hidden row per fed row
+            passes += 1
+            accepted = 0
+            for t, d in enumerate(drafts):
+                p = dist(model.head_logits(hs[t:t + 1], j + 1 + t))
+                if float(torch.rand(1, generator=gen)) < min(1.0, float(p[d]) / max(float(q[t][d]), 1e-30)):
+                    commit(d)
+                    accepted += 1
+                    continue
+                residual = (p - q[t]).clamp_min(0)
+                commit(draw(residual / residual.sum() if float(residual.sum()) > 0 else p))
+                break
+            # rows kept in the cache: the exact code and the accepted drafts; a redrawn code is fed by the next round
+            cp.kv.commit(0, 1 + accepted)
+            if accepted == len(drafts):
+                h = hs[len(drafts):len(drafts) + 1]
+            elif len(codes) < g - 1:
+                h = cp.step_embeds([0], [model.project(model.embed(len(codes) - 1, torch.tensor([codes[-1]], device=self.device)))])
+                passes += 1
+        return codes, total, passes
+
     # ---- frame loop ----------------------------------------------------------------------------------------------------
     @torch.no_grad()
     def generate_codes(self, text_ids: Sequence[int], speaker: Optional[str] = None, language: Optional[str] = None,
@@ -193,8 +276,12 @@ class TTSRuntime:
                 reason = "eos"
                 break
             seen[code0] = True
-            rest, rest_sum = self.predict_residual_codes(tk.model.last_hidden, code0, sp, f)
-            predictor_steps += c.num_code_groups - 1
+            if sp.cp_spec_verify_size:
+                rest, rest_sum, passes = self.predict_residual_codes_speculative(tk.model.last_hidden, code0, sp, f)
+                predictor_steps += passes
+            else:
+                rest, rest_sum = self.predict_residual_codes(tk.model.last_hidden, code0, sp, f)
+                predictor_steps += c.num_code_groups - 1
             frames.append([code0] + rest)
             if on_frames is not None and chunk_frames > 0 and len(frames) - sent >= chunk_frames:
                 on_frames(torch.tensor(frames[sent:], dtype=torch.int32), False)

@@ -207,3 +207,42 @@ def test_command_server_routes_and_stage_graph(rt, tmp_path):
     res = m.run([{"text": TEXT, "voice": "ryan"}])
     assert res[0]["ok"] and res[0]["outputs"]["code2wav:audio"] == want.pcm16
     m.close()
+
+
+def test_code_predictor_head_speculation_is_lossless(rt):
+    """Greedy: the speculative pass returns the very codes of the one-code-per-pass loop, for every verify window.  Sampling:
+    the second residual code's empirical distribution matches the exact marginal computed by enumeration."""
+    c = rt.cfg
+    big = T.random_tts(seed=5, groups=7, codebook=24)
+    for r in (rt, big):
+        greedy = T.TTSSampling(talker_temperature=0.0, predictor_temperature=0.0, max_audio_length=4)
+        want = r.generate_codes(TEXT, "ryan", sampling=greedy)
+        for n in (2, 3, 8):
+            greedy.cp_spec_verify_size = n
+            got = r.generate_codes(TEXT, "ryan", sampling=greedy)
+            assert torch.equal(got[0], want[0]) and got[1] == want[1], n
+            assert got[3] <= want[0].shape[0] * (2 * (r.cfg.num_code_groups - 1))          # passes stay bounded
+    with pytest.raises(ValueError, match="2..8"):
+        rt.predict_residual_codes_speculative(torch.zeros(1, 64), 3, T.TTSSampling(cp_spec_verify_size=1), 0)
+    # make drafts worth accepting: when later heads agree with earlier ones' successors some rounds commit several codes
+    sp = T.TTSSampling(predictor_temperature=0.8, predictor_top_k=3, cp_spec_verify_size=3, seed=1)
+    rt.generate_codes(TEXT, "ryan", sampling=T.TTSSampling(talker_temperature=0.0, predictor_temperature=0.0, max_audio_length=1))
+    h = rt.talker.model.last_hidden.clone()
+    cp = rt.predictor.model
+    first = 5
+    # exact marginal of the second residual code: sum over the first one of P(c1) P(c2 | c1), by dense passes
+    x0 = cp.project(torch.cat([h, rt.talker.embed_tokens([first])], 0))
+    p1 = rt._distribution(cp.head_logits(_dense_hidden(cp, x0)[-1:], 0), 0.8, 3, 1.0)
+    exact = torch.zeros(c.codebook_size)
+    for c1 in torch.nonzero(p1).flatten().tolist():
+        x1 = torch.cat([x0, cp.project(cp.codec_embeddings[0][c1][None])], 0)
+        exact += p1[c1] * rt._distribution(cp.head_logits(_dense_hidden(cp, x1)[-1:], 1), 0.8, 3, 1.0)
+    counts = torch.zeros(c.codebook_size)
+    trials, multi = 700, 0
+    for i in range(trials):
+        codes, _, passes = rt.predict_residual_codes_speculative(h, first, sp, 0, generator=torch.Generator().manual_seed(1000 + i))
+        counts[codes[1]] += 1
+        multi += passes < 1 + (c.num_code_groups - 1)
+    tv = 0.5 * (counts / trials - exact).abs().sum()
+    assert tv < 0.08, tv
+    assert float(counts[exact == 0].sum()) == 0                      # nothing outside the exact support is ever produced
