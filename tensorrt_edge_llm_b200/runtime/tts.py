@@ -77,9 +77,10 @@ class TTSRuntime:
     """Owns the three models, their KV pools and the frame loop.  One request at a time (seat 0 of each pool)."""
 
     def __init__(self, cfg: TTSConfig, talker: TalkerCausalLM, predictor: CodePredictorCausalLM, front: TextFrontEnd, code2wav: Code2Wav,
-                 tokenizer=None, device="cpu", max_seq_len: int = 4096, page_size: int = 16):
+                 tokenizer=None, device="cpu", max_seq_len: int = 4096, page_size: int = 0):
         self.cfg, self.front, self.code2wav, self.tokenizer = cfg, front, code2wav, tokenizer
         self.device = torch.device(device)
+        page_size = page_size or (64 if self.device.type == "cuda" else 16)      # the device attention kernels take 64- or 128-token pages
         pages = (max_seq_len + page_size - 1) // page_size + 1
         self.talker = ModelRunner(talker, KVCacheManager(talker.cfg, num_pages=pages, page_size=page_size, max_seats=1, max_pages_per_seq=pages,
                                                          device=self.device), device=self.device)
@@ -371,7 +372,7 @@ def load_tts(model_dir: str, device="cpu", tokenizer=None, max_seq_len: int = 40
 
 
 def random_tts(seed: int = 0, device="cpu", hidden: int = 64, predictor_hidden: int = 32, groups: int = 4, codebook: int = 48,
-               text_vocab: int = 96, dtype: str = "float32", max_seq_len: int = 256) -> TTSRuntime:
+               text_vocab: int = 96, dtype: str = "float32", max_seq_len: int = 256, head_dim: int = 0) -> TTSRuntime:
     """A small randomly initialised pipeline of the real structure (tests, smoke runs; no checkpoint can be fetched here)."""
     from ..checkpoint.loader import init_random_weights
     ctrl = codebook                                               # control ids follow the audio codes
@@ -380,12 +381,14 @@ def random_tts(seed: int = 0, device="cpu", hidden: int = 64, predictor_hidden: 
                     codec_think_bos_id=ctrl + 5, codec_think_eos_id=ctrl + 6, tts_pad_token_id=text_vocab - 3, tts_bos_token_id=text_vocab - 2,
                     tts_eos_token_id=text_vocab - 1, speakers={"ryan": ctrl + 7, "eric": ctrl + 8}, languages={"english": ctrl + 9, "sichuan_dialect": ctrl + 10},
                     speaker_dialects={"eric": "sichuan_dialect"}, default_speaker="ryan")
+    heads = lambda h: max(2, h // (head_dim or 64))                            # noqa: E731  (head size 64 from hidden 128 up, or as asked)
     tcfg = tiny_llama_config(model_type="qwen3_tts_talker", vocab_size=ctrl + 12, hidden_size=hidden, intermediate_size=2 * hidden, num_hidden_layers=2,
-                             num_attention_heads=2, num_key_value_heads=1, head_dim=hidden // 2, has_qk_norm=True, dtype=dtype,
-                             max_position_embeddings=max(max_seq_len, 64))
+                             num_attention_heads=heads(hidden), num_key_value_heads=heads(hidden) // 2, head_dim=hidden // heads(hidden),
+                             has_qk_norm=True, dtype=dtype, max_position_embeddings=max(max_seq_len, 64))
     pcfg = tiny_llama_config(model_type="qwen3_tts_code_predictor", vocab_size=codebook, hidden_size=predictor_hidden,
-                             intermediate_size=2 * predictor_hidden, num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=1,
-                             head_dim=predictor_hidden // 2, has_qk_norm=True, dtype=dtype, max_position_embeddings=64)
+                             intermediate_size=2 * predictor_hidden, num_hidden_layers=2, num_attention_heads=heads(predictor_hidden),
+                             num_key_value_heads=heads(predictor_hidden) // 2, head_dim=predictor_hidden // heads(predictor_hidden),
+                             has_qk_norm=True, dtype=dtype, max_position_embeddings=64)
     wcfg = Code2WavConfig(codebook_size=codebook, codebook_dim=16, hidden_size=32, latent_dim=24, num_hidden_layers=2, num_attention_heads=2,
                           intermediate_size=48, sliding_window=4, num_quantizers=groups, upsampling_ratios=(2,), upsample_rates=(3, 2),
                           decoder_dim=32, sample_rate=24000)

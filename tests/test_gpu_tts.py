@@ -1,0 +1,28 @@
+"""Speech pipeline on the device: the Talker and CodePredictor run through the decoder kernels in bf16."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_tts_frame_loop_and_vocoder_on_the_device():
+    from tensorrt_edge_llm_b200.runtime import tts as T
+    rt = T.random_tts(seed=2, device="cuda", hidden=512, predictor_hidden=256, groups=4, codebook=500, dtype="bfloat16", max_seq_len=256, head_dim=128)
+    text = [1, 2, 3, 10, 11, 12, 13, 14, 4, 5, 6, 7, 8]
+    sp = T.TTSSampling(max_audio_length=6, seed=9)
+    a = rt.generate(text, "ryan", sampling=sp, chunk_frames=2)
+    b = rt.generate(text, "ryan", sampling=sp)
+    c = rt.cfg
+    assert a.frames >= 1 and torch.equal(a.codes, b.codes)                       # one seed, one answer
+    assert (a.codes >= 0).all() and (a.codes < c.codebook_size).all() and a.codes.shape[1] == c.num_code_groups
+    assert a.waveform.shape[0] == a.frames * rt.code2wav.cfg.samples_per_frame and torch.isfinite(a.waveform).all()
+    assert torch.allclose(a.waveform, b.waveform, atol=1e-4) and a.chunks == (a.frames + 1) // 2
+    # the first Talker step against an fp32 restatement on the host (same weights): the bf16 logits agree to bf16 accuracy
+    prefill, _, _ = rt.build_prefill(text, "ryan")
+    rt.talker.kv.free(0)
+    logits = rt.talker.prefill_embeds([0], [prefill]).float().cpu()
+    ref = T.random_tts(seed=2, device="cpu", hidden=512, predictor_hidden=256, groups=4, codebook=500, dtype="float32", max_seq_len=256, head_dim=128)
+    ref.talker.model.load_state_dict({k: v.float().cpu() for k, v in rt.talker.model.state_dict().items()})
+    ref.front.load_state_dict({k: v.float().cpu() for k, v in rt.front.state_dict().items()})
+    want = ref.talker.prefill_embeds([0], [prefill.float().cpu()]).float()
+    assert (logits - want).abs().max() < 0.05 * want.abs().max() + 0.02
