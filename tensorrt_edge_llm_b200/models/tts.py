@@ -28,7 +28,7 @@ from torch import nn
 from ..config import ModelConfig
 from ..model import register_model
 from ..ops.meta import StepMeta
-from .default import CausalLM, RMSNorm
+from .default import CausalLM
 
 
 # ---- configuration ---------------------------------------------------------------------------------------------------
@@ -291,13 +291,25 @@ class DecoderBlock(nn.Module):
         return x
 
 
+class _TorchRMSNorm(nn.Module):
+    """RMSNorm in plain torch ops: the vocoder runs in fp32, which the decoder stack's 16-bit norm kernel does not take."""
+
+    def __init__(self, dim: int, eps: float):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim))
+        self.eps = eps
+
+    def forward(self, x):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.eps) * self.weight
+
+
 class _SlidingLayer(nn.Module):
     def __init__(self, c: Code2WavConfig):
         super().__init__()
         h, d, nh = c.hidden_size, c.head_dim, c.num_attention_heads
         self.nh, self.d = nh, d
-        self.input_layernorm = RMSNorm(h, c.rms_norm_eps, torch.float32)
-        self.post_attention_layernorm = RMSNorm(h, c.rms_norm_eps, torch.float32)
+        self.input_layernorm = _TorchRMSNorm(h, c.rms_norm_eps)
+        self.post_attention_layernorm = _TorchRMSNorm(h, c.rms_norm_eps)
         self.q_proj, self.k_proj, self.v_proj = (nn.Linear(h, nh * d, bias=False) for _ in range(3))
         self.o_proj = nn.Linear(nh * d, h, bias=False)
         self.gate_proj, self.up_proj = nn.Linear(h, c.intermediate_size, bias=False), nn.Linear(h, c.intermediate_size, bias=False)
@@ -307,7 +319,7 @@ class _SlidingLayer(nn.Module):
 
     def forward(self, x, cos, sin, mask):
         b, t, _ = x.shape
-        y = self.input_layernorm(x.reshape(b * t, -1)).reshape(b, t, -1)
+        y = self.input_layernorm(x)
         q, k, v = (p(y).view(b, t, self.nh, self.d).transpose(1, 2) for p in (self.q_proj, self.k_proj, self.v_proj))
 
         def rot(u):
@@ -316,7 +328,7 @@ class _SlidingLayer(nn.Module):
 
         a = F.scaled_dot_product_attention(rot(q), rot(k), v, attn_mask=mask)
         x = x + self.o_proj(a.transpose(1, 2).reshape(b, t, -1)) * self.attn_scale
-        y = self.post_attention_layernorm(x.reshape(b * t, -1)).reshape(b, t, -1)
+        y = self.post_attention_layernorm(x)
         return x + self.down_proj(F.silu(self.gate_proj(y)) * self.up_proj(y)) * self.mlp_scale
 
 
@@ -332,7 +344,7 @@ class Code2Wav(nn.Module):
         self.acoustic_proj = nn.Conv1d(c.codebook_dim, c.latent_dim, 1, bias=False)
         self.pre_conv = CausalConv1d(c.latent_dim, c.hidden_size, 3)
         self.layers = nn.ModuleList([_SlidingLayer(c) for _ in range(c.num_hidden_layers)])
-        self.norm = RMSNorm(c.hidden_size, c.rms_norm_eps, torch.float32)
+        self.norm = _TorchRMSNorm(c.hidden_size, c.rms_norm_eps)
         self.post_proj = nn.Linear(c.hidden_size, c.latent_dim)
         self.upsample = nn.ModuleList([nn.Sequential(CausalTransConv1d(c.latent_dim, c.latent_dim, r, r), ConvNeXtBlock(c.latent_dim))
                                        for r in c.upsampling_ratios])
@@ -362,6 +374,12 @@ class Code2Wav(nn.Module):
 
     @torch.no_grad()
     def forward(self, codes: torch.Tensor) -> torch.Tensor:
+        # full-precision convolutions on the device too: with TF32 a chunk and the full decode pick different algorithms and
+        # their samples drift apart by more than a 16-bit PCM step
+        with torch.backends.cudnn.flags(enabled=True, benchmark=False, deterministic=False, allow_tf32=False):
+            return self._forward(codes)
+
+    def _forward(self, codes: torch.Tensor) -> torch.Tensor:
         c = self.cfg
         codes = codes.long().clamp_(0, c.codebook_size - 1)
         b, g, t = codes.shape
@@ -379,7 +397,7 @@ class Code2Wav(nn.Module):
         mask = (i[None, :] <= i[:, None]) & (i[None, :] > i[:, None] - c.sliding_window)
         for layer in self.layers:
             x = layer(x, cos, sin, mask)
-        x = self.post_proj(self.norm(x.reshape(b * t, -1)).reshape(b, t, -1)).transpose(1, 2)               # [B, latent, T]
+        x = self.post_proj(self.norm(x)).transpose(1, 2)               # [B, latent, T]
         for up in self.upsample:
             x = up(x)
         x = self.decoder_in(x)

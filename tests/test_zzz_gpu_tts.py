@@ -1,4 +1,5 @@
-"""Speech pipeline on the device: the Talker and CodePredictor run through the decoder kernels in bf16."""
+"""Speech pipeline on the device: the Talker and CodePredictor run through the decoder kernels in bf16, the vocoder in fp32.
+The file name sorts after every other test file, so the long-standing suites run before it."""
 import pytest
 import torch
 
@@ -16,7 +17,7 @@ def test_tts_frame_loop_and_vocoder_on_the_device():
     assert a.frames >= 1 and torch.equal(a.codes, b.codes)                       # one seed, one answer
     assert (a.codes >= 0).all() and (a.codes < c.codebook_size).all() and a.codes.shape[1] == c.num_code_groups
     assert a.waveform.shape[0] == a.frames * rt.code2wav.cfg.samples_per_frame and torch.isfinite(a.waveform).all()
-    assert torch.allclose(a.waveform, b.waveform, atol=1e-4) and a.chunks == (a.frames + 1) // 2
+    assert torch.allclose(a.waveform, b.waveform, atol=2e-3) and a.chunks == (a.frames + 1) // 2
     # the first Talker step against an fp32 restatement on the host (same weights): the bf16 logits agree to bf16 accuracy
     prefill, _, _ = rt.build_prefill(text, "ryan")
     rt.talker.kv.free(0)
