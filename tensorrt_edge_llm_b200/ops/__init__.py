@@ -293,3 +293,14 @@ def apply_token_bitmask(logits, bitmask):
     if logits.is_cuda:
         return cuda_ops().apply_token_bitmask(logits, bitmask)
     return ref.apply_token_bitmask(logits, bitmask)
+
+
+def ddtree_candidates(logits, k):
+    """Per-depth top-``k`` candidates of a block draft with whole-vocabulary log-probabilities (torch ops on the logits' device)."""
+    return ref.ddtree_candidates(logits, k)
+
+
+def ddtree_assemble(cand_ids, cand_lp, root_tokens, num_nodes, depth_confidence=None, survival_threshold=0.0):
+    """Best-first verification tree from per-depth candidates.  A few dozen nodes per sequence: assembled on the host from the
+    candidate lists (one small device→host copy), results returned on the candidates' device."""
+    return ref.ddtree_assemble(cand_ids, cand_lp, root_tokens, num_nodes, depth_confidence, survival_threshold)

@@ -1029,3 +1029,75 @@ def kv_fp8_store(kv_layer: torch.Tensor, stage: torch.Tensor, meta, scales: torc
         q = (rows / sc).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
         kv_layer[page, :, :, slot % psz] = q
         stage[page, :, :, slot % psz] = (q.float() * sc).to(stage.dtype)
+
+
+# ---- block-draft verification trees ---------------------------------------------------------------------------------
+
+def ddtree_candidates(logits: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-depth candidates of a block draft: the ``k`` most likely tokens of every row of ``logits [B, D, V]`` with their
+    log-probabilities over the whole vocabulary.  Returns ``(ids [B, D, k] int32, log-probabilities [B, D, k] fp32)``, each
+    list sorted by non-increasing log-probability (ties: lower token id first).
+    Parity: ``ddtreeSelectLogitCandidates`` (``cpp/kernels/speculative/ddtreeKernels.h``)."""
+    lp = torch.log_softmax(logits.float(), dim=-1)
+    # a stable sort on (-log-probability) keeps the lower token id first among equals
+    order = torch.argsort(-lp, dim=-1, stable=True)[..., :k]
+    return order.to(torch.int32), lp.gather(-1, order)
+
+
+def ddtree_assemble(cand_ids: torch.Tensor, cand_lp: torch.Tensor, root_tokens: torch.Tensor, num_nodes: int,
+                    depth_confidence: Optional[torch.Tensor] = None, survival_threshold: float = 0.0):
+    """Best-first assembly of a prefix-closed verification tree from per-depth candidate lists (the positions of a block
+    draft are predicted independently of each other, so every node of depth ``d`` has the same candidate children: row
+    ``d`` of the table).  Node 0 is the root (score 0).  Each step appends, among the next unused candidate of every node
+    already in the tree, the one with the highest prefix score (the sum of log-probabilities along its path, plus
+    ``log(confidence)`` of every depth when ``depth_confidence [B, D]`` is given); ties go to the lower parent index, then
+    the lower slot, then the lower token id.  A child never outscores its parent, so the result is the ``num_nodes - 1``
+    best prefixes of the whole candidate tree.  With a ``survival_threshold`` growth stops below depths whose confidence
+    product falls under it.  Returns ``(tokens, parents, depths [B, N] int32, scores [B, N] fp32, valid [B] int32)``;
+    rows past ``valid`` are padding (token = root token, parent 0, score -inf).
+    Parity: ``ddtreeAssemble`` (``cpp/kernels/speculative/ddtreeKernels.h``)."""
+    import heapq
+    ids, lps = cand_ids.cpu(), cand_lp.float().cpu()
+    b, depth_rows, k = ids.shape
+    roots = root_tokens.cpu().tolist()
+    conf = depth_confidence.float().cpu() if depth_confidence is not None else None
+    tok = torch.zeros(b, num_nodes, dtype=torch.int32)
+    par = torch.zeros(b, num_nodes, dtype=torch.int32)
+    dep = torch.zeros(b, num_nodes, dtype=torch.int32)
+    sc = torch.full((b, num_nodes), float("-inf"))
+    valid = torch.zeros(b, dtype=torch.int32)
+    for i in range(b):
+        tok[i] = int(roots[i])
+        sc[i, 0] = 0.0
+        gain = [0.0] * depth_rows                 # what entering depth d + 1 adds beside the token's own log-probability
+        alive = depth_rows
+        if conf is not None:
+            prod = 1.0
+            for d in range(depth_rows):
+                c = min(max(float(conf[i, d]), 0.0), 1.0)
+                prod *= c
+                gain[d] = math.log(c) if c > 0 else float("-inf")
+                if survival_threshold > 0 and prod < survival_threshold and alive == depth_rows:
+                    alive = d
+        heap: list = []                           # (-score, parent, slot, token)
+
+        def offer(node: int, slot: int) -> None:
+            d = int(dep[i, node])
+            if d >= alive or slot >= k:
+                return
+            lp = float(lps[i, d, slot])
+            if lp == float("-inf") or gain[d] == float("-inf"):
+                return
+            heapq.heappush(heap, (-(float(sc[i, node]) + lp + gain[d]), node, slot, int(ids[i, d, slot])))
+
+        offer(0, 0)
+        n = 1
+        while n < num_nodes and heap:
+            neg, node, slot, token = heapq.heappop(heap)
+            tok[i, n], par[i, n], dep[i, n], sc[i, n] = token, node, int(dep[i, node]) + 1, -neg
+            offer(node, slot + 1)                 # the parent's next candidate
+            offer(n, 0)                           # the new node's best child
+            n += 1
+        valid[i] = n
+    dev = cand_ids.device
+    return tok.to(dev), par.to(dev), dep.to(dev), sc.to(dev), valid.to(dev)

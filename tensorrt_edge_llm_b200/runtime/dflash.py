@@ -47,7 +47,12 @@ class DFlashDecoder:
     name = "dflash"
     is_speculative = True
 
-    def __init__(self, runner, draft, draft_kv: KVCacheManager, block_size: Optional[int] = None, mask_token_id: Optional[int] = None):
+    def __init__(self, runner, draft, draft_kv: KVCacheManager, block_size: Optional[int] = None, mask_token_id: Optional[int] = None,
+                 tree_top_k: int = 1, verify_tokens: int = 0):
+        """``tree_top_k > 1`` switches greedy requests from one chain per round to a verification tree: the ``tree_top_k``
+        most likely tokens of every block position are candidates, and the ``verify_tokens`` best prefixes (root included)
+        are verified in one target pass (``cpp/runtime/decoding/dsparkDecoder.cpp`` / ``dflashDecoder`` tree mode over
+        ``ddtreeBuild``)."""
         self.r, self.model, self.draft, self.dkv = runner, runner.model, draft, draft_kv
         if getattr(self.model.cfg, "is_hybrid", False):
             raise ValueError("DFlash decoding is not available for hybrid (recurrent-state) targets")
@@ -66,13 +71,23 @@ class DFlashDecoder:
         self._sample_gen: Optional[torch.Generator] = None
         self.root: Dict[int, int] = {}
         self._mask_cache: Dict[int, torch.Tensor] = {}
+        self.tree_top_k = int(tree_top_k)
+        if not 1 <= self.tree_top_k <= 8:
+            raise ValueError("tree_top_k must be in 1..8")
+        if self.tree_top_k > 1 and hasattr(draft, "propose_tokens"):
+            raise ValueError("tree verification needs a draft that returns per-position logits (this one proposes tokens itself)")
+        # every depth offers tree_top_k children per node, so the candidate tree holds k + k² + … nodes: never ask for more
+        possible = sum(min(self.tree_top_k ** d, 4096) for d in range(1, self.block))
+        self.verify_tokens = min(int(verify_tokens or 2 * self.block), 1 + possible, 64) if self.tree_top_k > 1 else 0
+        if self.tree_top_k > 1:
+            self.spec = _Headroom(max(self.block, self.verify_tokens))
 
     def kv_headroom(self) -> int:
-        return self.block
+        return max(self.block, self.verify_tokens)
 
     # ---- steps --------------------------------------------------------------------------------
-    def _target_step(self, seats, rows: torch.Tensor, q_lens):
-        meta = self.r._meta(seats, q_lens, logits_all=True)
+    def _target_step(self, seats, rows: torch.Tensor, q_lens, tree_mask=None, positions=None):
+        meta = self.r._meta(seats, q_lens, logits_all=True, tree_mask=tree_mask, positions=positions)
         uniq = sorted(set(self.taps))
         x, taps = self.model.hidden_states(rows, meta, self.r.cache, capture_layers=uniq)
         by_layer = dict(zip(uniq, taps))
@@ -87,8 +102,9 @@ class DFlashDecoder:
         for s, q in zip(seats, q_lens):
             self.dkv.commit(s, q)
 
-    def _propose(self, seats) -> torch.Tensor:
-        """Draft tokens ``[N, block - 1]`` after each sequence's current root."""
+    def _propose(self, seats, want_logits: bool = False) -> torch.Tensor:
+        """Draft tokens ``[N, block - 1]`` after each sequence's current root (``want_logits``: the block's logits
+        ``[N, block, V]`` instead, on the device)."""
         n, b = len(seats), self.block
         ids = torch.full((n, b), self.mask_id, dtype=torch.int32)
         ids[:, 0] = torch.tensor([self.root[s] for s in seats], dtype=torch.int32)
@@ -106,6 +122,8 @@ class DFlashDecoder:
         if hasattr(self.draft, "propose_tokens"):                        # Domino: proposals corrected by what precedes them
             return self.draft.propose_tokens(embeds, meta, self.dkv.pool, ids[:, 0].to(self.device), b).to("cpu")
         logits = self.draft.propose(embeds, meta, self.dkv.pool)        # block rows are written past the context, never committed
+        if want_logits:
+            return logits.view(n, b, -1)
         return ops.argmax(logits).view(n, b)[:, 1:].to("cpu")
 
     # ---- prefill / round -----------------------------------------------------------------------
@@ -136,6 +154,8 @@ class DFlashDecoder:
         """One draft → verify round; returns the new tokens of every sequence (accepted drafts + the target's next token).
         ``forced_accept`` prescribes the accepted draft count per sequence (benchmarks with random weights)."""
         n, b = len(seats), self.block
+        if self.tree_top_k > 1 and self.sampling is None and forced_accept is None:
+            return self._round_tree(seats)
         drafts = self._propose(seats)                                     # [N, B-1] host
         chain = torch.cat([torch.tensor([[self.root[s]] for s in seats], dtype=torch.int64), drafts.long()], dim=1)
         # a draft with a confidence head (DSpark) may shorten a sequence's proposal: the verification step is ragged then
@@ -175,6 +195,43 @@ class DFlashDecoder:
             keep_lens.append(a + 1)
             self.root[s] = toks[-1]
         self._write_context(seats, feats.index_select(0, torch.cat(keep_rows).to(self.device)), keep_lens)
+        self.stats.rounds += 1
+        self.stats.emitted += sum(len(t) for t in out)
+        return out
+
+    @torch.no_grad()
+    def _round_tree(self, seats: Sequence[int]) -> List[List[int]]:
+        """One draft → tree → verify round for greedy requests.  The block's positions are predicted independently, so the
+        candidates of a node depend on its depth only; the best ``verify_tokens - 1`` prefixes form the tree.  The target
+        scores every node in one pass under the tree's ancestor mask; the accepted path is the longest one on which each
+        node is the target's own choice after its parent, so the output equals plain greedy decoding."""
+        n, b, nodes = len(seats), self.block, self.verify_tokens
+        dev = self.device
+        logits = self._propose(seats, want_logits=True)                    # [N, B, V]; row j + 1 predicts the token at depth j + 1
+        ids, lp = ops.ddtree_candidates(logits[:, 1:], self.tree_top_k)
+        root = torch.tensor([self.root[s] for s in seats], dtype=torch.int32, device=dev)
+        tok, par, _, _, valid = ops.ddtree_assemble(ids, lp, root, nodes)
+        if int(valid.min()) < nodes:
+            raise RuntimeError("the candidate tree holds fewer nodes than verify_tokens")      # excluded by the constructor's cap
+        past = torch.tensor([self.r.kv.lengths[s] for s in seats], dtype=torch.int32, device=dev)
+        tmask, _, pos = ops.eagle_tree_meta(par, past, 0, 0)
+        tlogits, feats = self._target_step(seats, tok.reshape(-1).to(torch.int32), [nodes] * n, tree_mask=tmask, positions=pos)
+        choice = ops.argmax(tlogits).view(n, nodes).to(torch.int32)
+        path, plen, bonus = ops.spec_accept_greedy(choice, tok.to(torch.int32), par.to(torch.int32), b, 0)
+        # the accepted nodes' KV rows move to consecutive positions behind the committed history
+        ops.kv_commit_path(self.r.kv.pool, self.r.kv.table_rows(seats).to(dev), past, path, plen)
+        path_h, plen_h, bonus_h, tok_h = path.tolist(), plen.tolist(), bonus.tolist(), tok.tolist()
+        out: List[List[int]] = []
+        keep_rows, keep_lens = [], []
+        for i, s in enumerate(seats):
+            m = plen_h[i]
+            kept = path_h[i][:m]
+            out.append([tok_h[i][j] for j in kept[1:]] + [bonus_h[i]])
+            self.r.kv.commit(s, m)
+            keep_rows.extend(i * nodes + j for j in kept)
+            keep_lens.append(m)
+            self.root[s] = bonus_h[i]
+        self._write_context(seats, feats.index_select(0, torch.tensor(keep_rows, device=dev)), keep_lens)
         self.stats.rounds += 1
         self.stats.emitted += sum(len(t) for t in out)
         return out

@@ -108,7 +108,9 @@ class LLM:
                 draft.share_lm_head(self.model)
             spec = speculative or SpecConfig()
             is_dflash = draft.cfg.draft_type == "dflash"
-            headroom = draft.cfg.dflash_block_size + 8 if is_dflash else spec.verify_tokens + spec.draft_steps * spec.top_k
+            block_tree = is_dflash and spec.block_tree_top_k > 1 and not hasattr(draft, "propose_tokens")
+            headroom = (max(draft.cfg.dflash_block_size, min(spec.verify_tokens, 64) if block_tree else 0) + 8 if is_dflash
+                        else spec.verify_tokens + spec.draft_steps * spec.top_k)
             sp_pages = (max_kv_cache_capacity + headroom + page_size - 1) // page_size
             self.kv = KVCacheManager(self.cfg, (kv_pages or sp_pages * max_batch_size + 1), page_size, max_seats=max_batch_size,
                                      max_pages_per_seq=sp_pages, device=self.device, kv_dtype=kv_cache_dtype)
@@ -117,7 +119,8 @@ class LLM:
                                  device=self.device, num_layers=draft.cfg.num_hidden_layers if is_dflash else 1)
             if is_dflash:                      # block draft over target-derived keys / values (runtime/dflash.py)
                 from .dflash import DFlashDecoder
-                self.spec_decoder = DFlashDecoder(self.runner, draft, dkv)
+                self.spec_decoder = DFlashDecoder(self.runner, draft, dkv, tree_top_k=spec.block_tree_top_k if block_tree else 1,
+                                                  verify_tokens=min(spec.verify_tokens, 64) if block_tree else 0)
             else:
                 self.spec_decoder = EagleDecoder(self.runner, draft, dkv, spec)
         from .debug import LayerDumper, forced_tokens_from_env

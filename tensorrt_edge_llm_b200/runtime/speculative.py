@@ -43,8 +43,11 @@ class SpecConfig:
     force_accept_len: int = 0     # benchmark mode: nodes accepted per round (root included), tokens ignored
     force_accept_mean: float = 0.0  # benchmark mode: per-round lengths drawn from a seeded distribution with this mean
     force_seed: int = 0
+    block_tree_top_k: int = 1     # block drafts (DFlash): > 1 verifies a tree of that many candidates per position instead of one chain
 
     def __post_init__(self):
+        if not 1 <= self.block_tree_top_k <= 8:
+            raise ValueError("block_tree_top_k must be in 1..8")
         if not 1 <= self.verify_tokens <= 128:
             raise ValueError("verify_tokens must be in 1..128")
         if self.draft_steps < 1 or self.top_k < 1:

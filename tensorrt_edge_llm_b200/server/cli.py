@@ -28,7 +28,9 @@ def build_llm(cfg: ServerConfig):
         sc = m.speculative_config
         spec_kw = {"draft_model": sc.draft_model,
                    "speculative": SpecConfig(draft_steps=sc.num_speculative_tokens or 4, top_k=sc.draft_top_k or 8,
-                                             verify_tokens=sc.verify_tokens or 32)}
+                                             verify_tokens=sc.verify_tokens or 32,
+                                             # block drafts: an explicit draft_top_k above 1 asks for tree verification
+                                             block_tree_top_k=min(sc.draft_top_k, 8) if (sc.draft_top_k or 1) > 1 and sc.method in ("dflash", "jetspec") else 1)}
     tp_kw = {}
     if m.tensor_parallel_size > 1:
         # one process per GPU (launched with ``python -m torch.distributed.run --nproc-per-node N -m … serve …``): rank 0

@@ -250,3 +250,90 @@ def test_causal_block_variant_changes_proposals_not_outputs():
               num_attention_heads=4, num_key_value_heads=2, jetspec_config={"query_causal": True, "block_size": 8})
     c = ModelConfig.from_hf_dict(hf)
     assert c.draft_type == "dflash" and c.dflash_query_causal
+
+
+def test_ddtree_assembly_is_the_best_prefix_set():
+    """The assembled tree holds exactly the highest-scoring prefixes of the full candidate tree, prefix-closed, in
+    non-increasing score order along every path; confidence and the survival floor steer and stop the growth."""
+    import itertools
+
+    from tensorrt_edge_llm_b200 import ops
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(2, 4, 30, generator=g) * 2.0
+    ids, lp = ops.ddtree_candidates(logits, 3)
+    assert ids.shape == (2, 4, 3) and torch.equal(ids[..., 0].long(), logits.argmax(-1)) and (lp[..., :-1] >= lp[..., 1:]).all()
+    assert torch.allclose(lp, torch.log_softmax(logits, -1).gather(-1, ids.long()))
+    n = 12
+    tok, par, dep, sc, valid = ops.ddtree_assemble(ids, lp, torch.tensor([7, 9]), n)
+    assert valid.tolist() == [n, n] and tok[:, 0].tolist() == [7, 9] and (sc[:, 0] == 0).all() and (par[:, 0] == 0).all()
+    for i in range(2):
+        # brute force: every prefix (slot choice per depth) with its score
+        every = {}
+        for d in range(1, 5):
+            for slots in itertools.product(range(3), repeat=d):
+                every[slots] = sum(float(lp[i, j, s]) for j, s in enumerate(slots))
+        best = sorted(every.values(), reverse=True)[: n - 1]
+        assert torch.allclose(sc[i, 1:].sort(descending=True).values, torch.tensor(best), atol=1e-5)
+        paths = {0: ()}
+        for j in range(1, n):
+            p = int(par[i, j])
+            assert p < j and int(dep[i, j]) == int(dep[i, p]) + 1 and float(sc[i, j]) <= float(sc[i, p]) + 1e-6     # prefix-closed
+            slot = ids[i, int(dep[i, p])].tolist().index(int(tok[i, j]))
+            paths[j] = paths[p] + (slot,)
+            assert abs(every[paths[j]] - float(sc[i, j])) < 1e-5
+        assert len(set(paths.values())) == n                                                           # no prefix twice
+    # a depth the confidence head distrusts is reached later; below the survival floor it is not reached at all
+    conf = torch.tensor([[1.0, 0.05, 1.0, 1.0], [1.0, 1.0, 1.0, 1.0]])
+    _, _, dep_c, _, valid_c = ops.ddtree_assemble(ids, lp, torch.tensor([7, 9]), n, conf)
+    assert dep_c[0, 1:4].tolist() == [1, 1, 1] and dep[0, 1:4].tolist() != [1, 1, 1]                  # every depth-1 candidate first
+    assert torch.equal(dep_c[1], dep[1]) and valid_c.tolist() == [n, n]
+    _, _, dep_s, sc_s, valid_s = ops.ddtree_assemble(ids, lp, torch.tensor([7, 9]), n, conf, 0.5)
+    assert int(dep_s[0].max()) == 1 and valid_s.tolist() == [4, n] and torch.isinf(sc_s[0, 4:]).all()
+
+
+def test_tree_verification_is_lossless_and_accepts_at_least_the_chain():
+    prompts = [[5, 6, 7, 8, 9, 10, 11], [20, 21, 22]]
+    runner, draft, dkv, tcfg = _pair(block=6)
+    want = _greedy(tcfg, prompts, 24)
+    chain = DFlashDecoder(runner, draft, dkv)
+    assert chain.generate([0, 1], prompts, 24) == want
+    chain_rounds = chain.stats.rounds
+    chain.release([0, 1])
+    for k, nodes in ((2, 10), (3, 16), (8, 64)):
+        runner, draft, dkv, tcfg = _pair(block=6)
+        dec = DFlashDecoder(runner, draft, dkv, tree_top_k=k, verify_tokens=nodes)
+        assert dec.verify_tokens == nodes and dec.kv_headroom() == max(6, nodes)
+        assert dec.generate([0, 1], prompts, 24) == want                # the target's greedy continuation, token for token
+        # the tree's first chain is the chain decoder's proposal, so a round never accepts less
+        assert dec.stats.rounds <= chain_rounds
+        for s in (0, 1):
+            assert runner.kv.lengths[s] == dkv.lengths[s]
+        dec.release([0, 1])
+    # the node budget is capped by what the candidate tree can hold, and drafts that propose tokens themselves are refused
+    runner, draft, dkv, _ = _pair(block=3)
+    assert DFlashDecoder(runner, draft, dkv, tree_top_k=2, verify_tokens=50).verify_tokens == 1 + 2 + 4
+    import pytest
+    with pytest.raises(ValueError, match="1..8"):
+        DFlashDecoder(runner, draft, dkv, tree_top_k=9)
+
+
+def test_llm_front_end_switches_block_drafts_to_tree_verification():
+    from tensorrt_edge_llm_b200.runtime.llm import LLM, SamplingParams
+    from tensorrt_edge_llm_b200.runtime.speculative import SpecConfig
+    tcfg = tiny_llama_config(num_hidden_layers=4, vocab_size=120, dtype="float32")
+    dcfg = tiny_llama_config(num_hidden_layers=2, vocab_size=120, dtype="float32")
+    dcfg.draft_type, dcfg.dflash_block_size, dcfg.dflash_mask_token_id = "dflash", 5, 119
+    prompts = [[5, 6, 7, 8], [20, 21, 22, 23, 24, 25]]
+    kw = dict(device="cpu", max_batch_size=2, max_input_len=32, max_kv_cache_capacity=96, page_size=16)
+    plain = LLM(tcfg, **kw)
+    want = [o.token_ids for o in plain.generate(prompts, SamplingParams(max_tokens=18, ignore_eos=True))]
+    plain.close()
+    llm = LLM(tcfg, draft_model=dcfg, speculative=SpecConfig(block_tree_top_k=3, verify_tokens=20), **kw)
+    try:
+        assert llm.spec_decoder.tree_top_k == 3 and llm.spec_decoder.verify_tokens == 20
+        assert [o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=18, ignore_eos=True))] == want
+    finally:
+        llm.close()
+    chain = LLM(tcfg, draft_model=dcfg, speculative=SpecConfig(), **kw)          # the default stays one chain per round
+    assert chain.spec_decoder.tree_top_k == 1 and chain.spec_decoder.verify_tokens == 0
+    chain.close()
