@@ -88,6 +88,8 @@ class TTSConfig:
     tts_pad_token_id: int = 151671
     role_prefix_tokens: int = 3             # "<|im_start|>assistant\n"
     suffix_tokens: int = 5                  # "<|im_end|>\n<|im_start|>assistant\n"
+    role_prefix_ids: List[int] = field(default_factory=list)          # the template's token ids, for callers that hold bare text ids
+    suffix_ids: List[int] = field(default_factory=list)
     speakers: Dict[str, int] = field(default_factory=dict)            # name → codec id of the speaker row
     languages: Dict[str, int] = field(default_factory=dict)           # name → codec id of the language row
     speaker_dialects: Dict[str, str] = field(default_factory=dict)    # speaker → language it switches on by itself

@@ -171,7 +171,9 @@ register_runner(RunnerDecl("llm.backbone", "autoregressive", LLMBackboneStage, i
 
 class TalkerStage(Stage):
     """``tts.talker``: text (or templated token ids) → the codec frame matrix, through the Talker / CodePredictor loop of the
-    speech pipeline in the artifact directory.  ``voice`` and ``sampling`` are optional inputs."""
+    speech pipeline in the artifact directory.  ``voice`` and ``sampling`` are optional inputs.  ``token_ids`` instead of
+    ``text`` takes the bare ids a text decoder upstream generated (the thinker → talker hand-off of an audio-out
+    deployment) and wraps them in the speech prompt's template."""
 
     def __init__(self, cfg: StageConfig, root: str, runtime=None):
         super().__init__(cfg, root)
@@ -184,8 +186,11 @@ class TalkerStage(Stage):
         from .tts import TTSSampling
         out = []
         for r in batch:                                            # the frame loop holds one request at a time
-            text = r["text"]
-            ids = self.runtime.tokenize(text) if isinstance(text, str) else list(text)
+            if "text" in r:
+                text = r["text"]
+                ids = self.runtime.tokenize(text) if isinstance(text, str) else list(text)
+            else:
+                ids = self.runtime.template_ids(r["token_ids"])
             sp = TTSSampling.from_dict({**self.cfg.config, **(r.get("sampling") or {})})
             codes, reason, _, _ = self.runtime.generate_codes(ids, r.get("voice"), r.get("language"), sp)
             out.append({"codes": codes, "finish_reason": reason})
@@ -212,7 +217,8 @@ class Code2WavStage(Stage):
         return out
 
 
-register_runner(RunnerDecl("tts.talker", "autoregressive", TalkerStage, inputs=("text", "voice", "language", "sampling"), emits=("codes", "finish_reason")))
+register_runner(RunnerDecl("tts.talker", "autoregressive", TalkerStage, inputs=("text", "token_ids", "voice", "language", "sampling"),
+                           emits=("codes", "finish_reason")))
 register_runner(RunnerDecl("tts.code2wav", "iterative", Code2WavStage, inputs=("codes",), emits=("audio",)))
 
 
@@ -249,6 +255,21 @@ def one_stage_graph(max_batch: int = 8, has_audio: bool = False, has_image: bool
             "stages": [{"id": "llm", "runner": "llm.backbone", "artifact": ".", "kind": "autoregressive", "max_batch": max_batch,
                         "inputs": inputs, "emits": [{"id": "text", "kind": "text", "transport": "chunk_stream", "terminal": True},
                                                     {"id": "token_ids", "kind": "tokens", "transport": "chunk_stream"}]}]}
+
+
+def audio_out_graph(llm_artifact: str = ".", tts_artifact: str = "tts", max_batch: int = 8, talker_config: Optional[Dict[str, Any]] = None) -> Dict[str, Any]:
+    """The graph of an audio-out deployment: the text decoder answers, its generated ids go to the talker, the talker's codec
+    frames to the vocoder.  Terminals: the answer's text and the speech; a request that asks for the text only never loads
+    or runs the speech stages."""
+    return {"schema_version": SCHEMA_VERSION, "terminals": ["thinker:text", "code2wav:audio"], "stages": [
+        {"id": "thinker", "runner": "llm.backbone", "artifact": llm_artifact, "kind": "autoregressive", "max_batch": max_batch,
+         "inputs": [{"name": "prompt", "from": "request:messages"}, {"name": "sampling", "from": "request:sampling", "on_missing": "skip"}],
+         "emits": [{"id": "text", "kind": "text", "terminal": True}, {"id": "token_ids", "kind": "tokens"}]},
+        {"id": "talker", "runner": "tts.talker", "artifact": tts_artifact, "kind": "autoregressive", "config": dict(talker_config or {}),
+         "inputs": [{"name": "token_ids", "from": "thinker:token_ids"}, {"name": "voice", "from": "request:voice", "on_missing": "skip"}],
+         "emits": [{"id": "codes", "kind": "codec"}]},
+        {"id": "code2wav", "runner": "tts.code2wav", "artifact": tts_artifact, "kind": "iterative",
+         "inputs": [{"name": "codes", "from": "talker:codes"}], "emits": [{"id": "audio", "kind": "audio", "terminal": True}]}]}
 
 
 def write_graph(engine_dir: str, graph: Dict[str, Any]) -> str:

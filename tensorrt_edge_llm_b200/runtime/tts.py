@@ -102,6 +102,13 @@ class TTSRuntime:
             raise ValueError("this runtime was loaded without a tokenizer: pass token ids")
         return list(self.tokenizer.encode(f"<|im_start|>assistant\n{text}<|im_end|>\n<|im_start|>assistant\n"))
 
+    def template_ids(self, text_ids: Sequence[int]) -> List[int]:
+        """Bare text token ids (what a text decoder upstream produced) wrapped in the speech prompt's role prefix and suffix."""
+        c = self.cfg
+        if len(c.role_prefix_ids) != c.role_prefix_tokens or len(c.suffix_ids) != c.suffix_tokens:
+            raise ValueError("this pipeline's configuration does not carry the template's token ids (role_prefix_ids / suffix_ids)")
+        return list(c.role_prefix_ids) + [int(t) for t in text_ids] + list(c.suffix_ids)
+
     def _codec_rows(self, ids: Sequence[int]) -> torch.Tensor:
         return self.talker.embed_tokens(list(ids)).float()
 
@@ -380,7 +387,7 @@ def random_tts(seed: int = 0, device="cpu", hidden: int = 64, predictor_hidden: 
                     codec_pad_id=ctrl, codec_bos_id=ctrl + 1, codec_eos_id=ctrl + 2, codec_think_id=ctrl + 3, codec_nothink_id=ctrl + 4,
                     codec_think_bos_id=ctrl + 5, codec_think_eos_id=ctrl + 6, tts_pad_token_id=text_vocab - 3, tts_bos_token_id=text_vocab - 2,
                     tts_eos_token_id=text_vocab - 1, speakers={"ryan": ctrl + 7, "eric": ctrl + 8}, languages={"english": ctrl + 9, "sichuan_dialect": ctrl + 10},
-                    speaker_dialects={"eric": "sichuan_dialect"}, default_speaker="ryan")
+                    speaker_dialects={"eric": "sichuan_dialect"}, default_speaker="ryan", role_prefix_ids=[1, 2, 3], suffix_ids=[4, 5, 6, 7, 8])
     heads = lambda h: max(2, h // (head_dim or 64))                            # noqa: E731  (head size 64 from hidden 128 up, or as asked)
     tcfg = tiny_llama_config(model_type="qwen3_tts_talker", vocab_size=ctrl + 12, hidden_size=hidden, intermediate_size=2 * hidden, num_hidden_layers=2,
                              num_attention_heads=heads(hidden), num_key_value_heads=heads(hidden) // 2, head_dim=hidden // heads(hidden),

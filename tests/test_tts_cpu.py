@@ -246,3 +246,32 @@ def test_code_predictor_head_speculation_is_lossless(rt):
     tv = 0.5 * (counts / trials - exact).abs().sum()
     assert tv < 0.08, tv
     assert float(counts[exact == 0].sum()) == 0                      # nothing outside the exact support is ever produced
+
+
+def test_audio_out_graph_hands_the_text_decoder_ids_to_the_talker(rt, tmp_path):
+    """Thinker → talker → vocoder: the text decoder's generated ids are wrapped in the speech template and spoken; a
+    text-only request leaves the speech stages unloaded."""
+    from tensorrt_edge_llm_b200.config import tiny_llama_config
+    from tensorrt_edge_llm_b200.runtime import multistage as ms
+    from tensorrt_edge_llm_b200.runtime.llm import LLM
+    T.save_tts(str(tmp_path / "tts"), rt)
+    greedy = {"talker_temperature": 0.0, "predictor_temperature": 0.0, "max_audio_length": 4}
+    g = ms.parse_graph(ms.audio_out_graph(tts_artifact="tts", talker_config=greedy), str(tmp_path))
+    assert ms.validate_graph(g) == ["thinker", "talker", "code2wav"]
+    llm = LLM(tiny_llama_config(num_hidden_layers=1, vocab_size=80), device="cpu", max_batch_size=2, max_input_len=32, max_kv_cache_capacity=64, page_size=16)
+    try:
+        m = ms.MultiStageRuntime(g, stages={"thinker": ms.LLMBackboneStage(g.stage("thinker"), str(tmp_path), llm=llm)})
+        res = m.run([{"messages": [3, 4, 5], "sampling": {"max_tokens": 5}, "voice": "ryan"}])[0]
+        assert res["ok"], res["error"]
+        answer = res["stages"] and llm.generate([[3, 4, 5]], __import__("tensorrt_edge_llm_b200.runtime.runner", fromlist=["SamplingParams"]).SamplingParams(max_tokens=5))[0].token_ids
+        want = rt.generate(rt.template_ids(answer), "ryan", sampling=T.TTSSampling.from_dict(greedy))
+        assert res["outputs"]["code2wav:audio"] == want.pcm16 and len(want.pcm16) > 0
+        m2 = ms.MultiStageRuntime(g, stages={"thinker": ms.LLMBackboneStage(g.stage("thinker"), str(tmp_path), llm=llm)})
+        only_text = m2.run([{"messages": [3, 4, 5], "sampling": {"max_tokens": 5}}], want=["thinker:text"])[0]
+        assert only_text["ok"] and "talker" not in only_text["stages"] and "talker" not in m2._stages
+    finally:
+        llm.close()
+    assert rt.template_ids([9, 9]) == [1, 2, 3, 9, 9, 4, 5, 6, 7, 8]
+    bare = T.TTSConfig()
+    with pytest.raises(ValueError, match="role_prefix_ids"):
+        T.TTSRuntime.template_ids(type("R", (), {"cfg": bare})(), [1])
